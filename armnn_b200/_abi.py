@@ -1,0 +1,154 @@
+"""ctypes mirror of include/b200k.h: the parameter structs and function prototypes of the C ABI.
+
+The structs are declared once here and used for two different shared objects: the product library
+(libb200k.so, device pointers) and — in tests only — the CPU oracle, which takes the same structs
+with host pointers.  Field order and types must match the header exactly.
+"""
+import ctypes as C
+
+U8, S8, S16, S32, F32 = 0, 1, 2, 3, 4
+
+OK, E_INVALID, E_CUDA, E_UNSUPPORTED, E_NODEVICE, E_TIMEOUT, E_TOOBIG = 0, -1, -2, -3, -4, -5, -6
+
+
+class QTensor(C.Structure):
+    _fields_ = [("data", C.c_void_p), ("dtype", C.c_int32), ("scale", C.c_float),
+                ("zero_point", C.c_int32), ("scales", C.c_void_p)]
+
+
+class Conv2dParams(C.Structure):
+    _fields_ = [("x", QTensor), ("w", QTensor), ("bias", QTensor), ("y", QTensor),
+                ("n", C.c_int32), ("h", C.c_int32), ("wd", C.c_int32), ("c", C.c_int32),
+                ("oh", C.c_int32), ("ow", C.c_int32), ("oc", C.c_int32),
+                ("kh", C.c_int32), ("kw", C.c_int32),
+                ("stride_h", C.c_int32), ("stride_w", C.c_int32),
+                ("pad_top", C.c_int32), ("pad_left", C.c_int32),
+                ("dil_h", C.c_int32), ("dil_w", C.c_int32),
+                ("clamp_lo", C.c_int32), ("clamp_hi", C.c_int32),
+                ("acc_out", C.c_void_p), ("algo", C.c_int32), ("packed", C.c_void_p)]
+
+
+class FcParams(C.Structure):
+    _fields_ = [("x", QTensor), ("w", QTensor), ("bias", QTensor), ("y", QTensor),
+                ("m", C.c_int32), ("k", C.c_int32), ("n", C.c_int32), ("transpose_w", C.c_int32),
+                ("clamp_lo", C.c_int32), ("clamp_hi", C.c_int32),
+                ("acc_out", C.c_void_p), ("algo", C.c_int32)]
+
+
+class BmmParams(C.Structure):
+    _fields_ = [("x", QTensor), ("y", QTensor), ("out", QTensor),
+                ("batch", C.c_int32), ("m", C.c_int32), ("k", C.c_int32), ("n", C.c_int32),
+                ("transpose_x", C.c_int32), ("transpose_y", C.c_int32),
+                ("batch_stride_x", C.c_int64), ("batch_stride_y", C.c_int64),
+                ("acc_out", C.c_void_p)]
+
+
+class Pool2dParams(C.Structure):
+    _fields_ = [("x", QTensor), ("y", QTensor),
+                ("n", C.c_int32), ("h", C.c_int32), ("wd", C.c_int32), ("c", C.c_int32),
+                ("oh", C.c_int32), ("ow", C.c_int32),
+                ("pool_h", C.c_int32), ("pool_w", C.c_int32), ("stride_h", C.c_int32), ("stride_w", C.c_int32),
+                ("pad_top", C.c_int32), ("pad_bottom", C.c_int32), ("pad_left", C.c_int32), ("pad_right", C.c_int32),
+                ("pool_type", C.c_int32), ("padding_method", C.c_int32)]
+
+
+class MeanParams(C.Structure):
+    _fields_ = [("x", QTensor), ("y", QTensor),
+                ("n", C.c_int32), ("h", C.c_int32), ("wd", C.c_int32), ("c", C.c_int32)]
+
+
+class EltwiseParams(C.Structure):
+    _fields_ = [("a", QTensor), ("b", QTensor), ("out", QTensor), ("rank", C.c_int32),
+                ("shape_a", C.c_int32 * 4), ("shape_b", C.c_int32 * 4), ("shape_out", C.c_int32 * 4),
+                ("op", C.c_int32), ("clamp_lo", C.c_int32), ("clamp_hi", C.c_int32)]
+
+
+class ActivationParams(C.Structure):
+    _fields_ = [("x", QTensor), ("y", QTensor), ("count", C.c_int64), ("function", C.c_int32),
+                ("a", C.c_float), ("b", C.c_float)]
+
+
+class SoftmaxParams(C.Structure):
+    _fields_ = [("x", QTensor), ("y", QTensor), ("outer", C.c_int32), ("axis_size", C.c_int32),
+                ("inner", C.c_int32), ("beta", C.c_float)]
+
+
+class ConvertParams(C.Structure):
+    _fields_ = [("x", QTensor), ("y", QTensor), ("count", C.c_int64)]
+
+
+_P, _F, _I = C.c_void_p, C.c_float, C.c_int32
+
+
+class QLstmParams(C.Structure):
+    _fields_ = [
+        ("batch", _I), ("input_size", _I), ("num_units", _I), ("output_size", _I),
+        ("input", _P), ("input_scale", _F), ("input_zp", _I),
+        ("output_state_in", _P), ("output_state_scale", _F), ("output_state_zp", _I),
+        ("cell_state_in", _P), ("cell_state_scale", _F),
+        ("output_state_out", _P), ("cell_state_out", _P),
+        ("output", _P), ("output_scale", _F), ("output_zp", _I),
+        ("w_i2i", _P), ("w_i2f", _P), ("w_i2c", _P), ("w_i2o", _P),
+        ("s_i2i", _F), ("s_i2f", _F), ("s_i2c", _F), ("s_i2o", _F),
+        ("w_r2i", _P), ("w_r2f", _P), ("w_r2c", _P), ("w_r2o", _P),
+        ("s_r2i", _F), ("s_r2f", _F), ("s_r2c", _F), ("s_r2o", _F),
+        ("w_c2i", _P), ("w_c2f", _P), ("w_c2o", _P),
+        ("s_c2i", _F), ("s_c2f", _F), ("s_c2o", _F),
+        ("b_i", _P), ("b_f", _P), ("b_c", _P), ("b_o", _P),
+        ("s_bi", _F), ("s_bf", _F), ("s_bc", _F), ("s_bo", _F),
+        ("ln_i", _P), ("ln_f", _P), ("ln_c", _P), ("ln_o", _P),
+        ("s_lni", _F), ("s_lnf", _F), ("s_lnc", _F), ("s_lno", _F),
+        ("w_proj", _P), ("s_proj", _F),
+        ("b_proj", _P), ("s_bproj", _F),
+        ("cell_clip", _F), ("projection_clip", _F),
+        ("input_intermediate_scale", _F), ("forget_intermediate_scale", _F),
+        ("cell_intermediate_scale", _F), ("output_intermediate_scale", _F),
+        ("hidden_state_scale", _F), ("hidden_state_zp", _I),
+        ("scratch", _P), ("scratch_bytes", C.c_size_t),
+    ]
+
+
+# name -> (parameter struct, takes a stream argument in the product library)
+KERNEL_ENTRY_POINTS = {
+    "conv2d_q8": Conv2dParams,
+    "dwconv2d_q8": Conv2dParams,
+    "fully_connected_q8": FcParams,
+    "batch_matmul_q8": BmmParams,
+    "pool2d_q8": Pool2dParams,
+    "mean_hw_q8": MeanParams,
+    "eltwise_q8": EltwiseParams,
+    "activation_q8": ActivationParams,
+    "softmax_q8": SoftmaxParams,
+    "convert_q": ConvertParams,
+    "qlstm_step": QLstmParams,
+}
+
+# every symbol include/b200k.h declares
+EXPORTED_SYMBOLS = ["b200k_" + k for k in KERNEL_ENTRY_POINTS] + [
+    "b200k_device_open", "b200k_device_count", "b200k_last_error", "b200k_version",
+    "b200k_activation_clamp", "b200k_conv2d_pack_bytes", "b200k_conv2d_pack",
+    "b200k_qlstm_scratch_bytes",
+]
+
+
+def declare_product(lib):
+    """Attach prototypes to a loaded libb200k.so."""
+    for name, struct in KERNEL_ENTRY_POINTS.items():
+        fn = getattr(lib, "b200k_" + name)
+        fn.argtypes = [C.POINTER(struct), C.c_void_p]
+        fn.restype = C.c_int
+    lib.b200k_device_open.argtypes = [C.c_int]
+    lib.b200k_device_open.restype = C.c_int
+    lib.b200k_device_count.restype = C.c_int
+    lib.b200k_last_error.restype = C.c_char_p
+    lib.b200k_version.restype = C.c_char_p
+    lib.b200k_activation_clamp.argtypes = [C.c_int, C.c_float, C.c_float, C.c_float, C.c_int32, C.c_int32,
+                                           C.POINTER(C.c_int32), C.POINTER(C.c_int32)]
+    lib.b200k_activation_clamp.restype = C.c_int
+    lib.b200k_conv2d_pack_bytes.argtypes = [C.c_int32] * 4
+    lib.b200k_conv2d_pack_bytes.restype = C.c_size_t
+    lib.b200k_conv2d_pack.argtypes = [C.POINTER(Conv2dParams), C.c_void_p, C.c_void_p]
+    lib.b200k_conv2d_pack.restype = C.c_int
+    lib.b200k_qlstm_scratch_bytes.argtypes = [C.c_int32] * 3
+    lib.b200k_qlstm_scratch_bytes.restype = C.c_size_t
+    return lib

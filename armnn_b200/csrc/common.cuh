@@ -1,0 +1,149 @@
+// Shared device/host helpers of libb200k: error reporting, the fp32 requantisation that every
+// epilogue uses, and typed element access.
+//
+// All fp32 arithmetic that has to reproduce CpuRef goes through explicit round-to-nearest
+// intrinsics (no fused multiply-add, IEEE division), because the reference is built for baseline
+// x86-64 without FMA contraction (cmake/GlobalConfig.cmake:107,126 of the Arm NN tree).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include "../../include/b200k.h"
+
+namespace b200k {
+
+void set_error(const char* fmt, ...);
+
+#define B200K_REQUIRE(cond, code, ...)                                   \
+    do { if (!(cond)) { ::b200k::set_error(__VA_ARGS__); return (code); } } while (0)
+
+#define B200K_CUDA(call)                                                               \
+    do { cudaError_t e_ = (call);                                                      \
+         if (e_ != cudaSuccess) {                                                      \
+             ::b200k::set_error("%s failed: %s", #call, cudaGetErrorString(e_));      \
+             return B200K_E_CUDA; } } while (0)
+
+inline int check_launch(const char* what)
+{
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) { set_error("launch of %s failed: %s", what, cudaGetErrorString(e)); return B200K_E_CUDA; }
+    return B200K_OK;
+}
+
+inline bool is_q8(int dtype) { return dtype == B200K_U8 || dtype == B200K_S8; }
+
+__host__ __device__ inline void type_range(int dtype, int& lo, int& hi)
+{
+    switch (dtype) {
+        case B200K_U8:  lo = 0;      hi = 255;   break;
+        case B200K_S8:  lo = -128;   hi = 127;   break;
+        case B200K_S16: lo = -32768; hi = 32767; break;
+        default:        lo = INT32_MIN; hi = INT32_MAX; break;
+    }
+}
+
+// ---- armnn::Quantize / armnn::Dequantize (src/armnn/TypesUtils.cpp:29-56) on the device -------
+
+// q = clamp(float(zp) + round(v / scale), type_min, type_max); ties away from zero.
+__device__ __forceinline__ int quantize_dev(float v, float scale, int zp, float tlo, float thi)
+{
+    float r = roundf(__fdiv_rn(v, scale));
+    float q = __fadd_rn(__int2float_rn(zp), r);
+    q = fminf(fmaxf(q, tlo), thi);
+    return __float2int_rz(q);
+}
+
+// v = float(q - zp) * scale
+__device__ __forceinline__ float dequantize_dev(int q, float scale, int zp)
+{
+    return __fmul_rn(__int2float_rn(q - zp), scale);
+}
+
+// Epilogue of every contraction:  v = float(acc) * (sx * sw) + float(bias) * sb ; Quantize ; clamp.
+struct Requant {
+    float sx;            // input scale
+    float sy;            // output scale
+    int   zy;            // output zero point
+    float tlo, thi;      // output type range as float
+    int   clo, chi;      // fused-activation clamp (already inside the type range)
+    __device__ __forceinline__ int operator()(int acc, float sw, bool has_bias, int bq, float sb) const
+    {
+        float v = __fmul_rn(__int2float_rn(acc), __fmul_rn(sx, sw));
+        if (has_bias) v = __fadd_rn(v, __fmul_rn(__int2float_rn(bq), sb));
+        int q = quantize_dev(v, sy, zy, tlo, thi);
+        return min(max(q, clo), chi);
+    }
+};
+
+inline Requant make_requant(float sx, const b200k_qtensor& y, int clamp_lo, int clamp_hi)
+{
+    int lo, hi;
+    type_range(y.dtype, lo, hi);
+    Requant r;
+    r.sx = sx; r.sy = y.scale; r.zy = y.zero_point;
+    r.tlo = (float)lo; r.thi = (float)hi;
+    r.clo = clamp_lo > lo ? clamp_lo : lo;
+    r.chi = clamp_hi < hi ? clamp_hi : hi;
+    return r;
+}
+
+// ---- typed element access ------------------------------------------------------------------
+
+__device__ __forceinline__ int load_q_dev(const void* p, int dtype, long long i)
+{
+    switch (dtype) {
+        case B200K_U8:  return ((const uint8_t*)p)[i];
+        case B200K_S8:  return ((const int8_t*)p)[i];
+        case B200K_S16: return ((const int16_t*)p)[i];
+        default:        return ((const int32_t*)p)[i];
+    }
+}
+
+__device__ __forceinline__ void store_q_dev(void* p, int dtype, long long i, int q)
+{
+    switch (dtype) {
+        case B200K_U8:  ((uint8_t*)p)[i]  = (uint8_t)q;  break;
+        case B200K_S8:  ((int8_t*)p)[i]   = (int8_t)q;   break;
+        case B200K_S16: ((int16_t*)p)[i]  = (int16_t)q;  break;
+        default:        ((int32_t*)p)[i]  = q;           break;
+    }
+}
+
+// A tensor operand as the kernels see it (a trimmed b200k_qtensor plus the float type range).
+struct QView {
+    const void* data;
+    int   dtype;
+    float scale;
+    int   zp;
+    float tlo, thi;
+    __device__ __forceinline__ float get(long long i) const      // Decoder<float>::Get
+    {
+        if (dtype == B200K_F32) return ((const float*)data)[i];
+        return dequantize_dev(load_q_dev(data, dtype, i), scale, zp);
+    }
+    __device__ __forceinline__ int quant(float v) const { return quantize_dev(v, scale, zp, tlo, thi); }
+    __device__ __forceinline__ void set(long long i, float v) const   // Encoder<float>::Set
+    {
+        if (dtype == B200K_F32) { ((float*)data)[i] = v; return; }
+        store_q_dev((void*)data, dtype, i, quant(v));
+    }
+};
+
+inline QView make_view(const b200k_qtensor& t)
+{
+    int lo, hi;
+    type_range(t.dtype, lo, hi);
+    QView v;
+    v.data = t.data; v.dtype = t.dtype; v.scale = t.scale; v.zp = t.zero_point;
+    v.tlo = (float)lo; v.thi = (float)hi;
+    return v;
+}
+
+inline int elem_size(int dtype)
+{
+    switch (dtype) { case B200K_U8: case B200K_S8: return 1; case B200K_S16: return 2; default: return 4; }
+}
+
+inline unsigned div_up(long long a, long long b) { return (unsigned)((a + b - 1) / b); }
+
+}  // namespace b200k

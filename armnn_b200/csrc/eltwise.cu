@@ -1,0 +1,171 @@
+// ElementwiseBinary (Add / Mul / Sub / Div / Maximum / Minimum / SqDiff) with numpy-style broadcast,
+// standalone Activation, and Quantize / Dequantize / requantize.  All bandwidth-bound: same-shape 8-bit
+// operands take a 128-bit vector path (16 elements per thread), everything else a scalar path.
+// Arithmetic is CpuRef's: dequantise each operand with its own scale/offset, apply the fp32 operation
+// unfused, re-quantise (RefElementwiseBinaryWorkload.cpp:27-132, Activation.cpp:13-119,
+// RefQuantizeWorkload.cpp:14-45, Dequantize.cpp:11-28 of the Arm NN tree).
+#include "common.cuh"
+
+namespace b200k {
+
+__device__ __forceinline__ float binary_op(int op, float a, float b)
+{
+    switch (op) {
+        case 0:  return __fadd_rn(a, b);
+        case 1:  return __fdiv_rn(a, b);
+        case 2:  return a > b ? a : b;
+        case 3:  return a < b ? a : b;
+        case 4:  return __fmul_rn(a, b);
+        case 5:  return __fsub_rn(a, b);
+        default: { float d = __fsub_rn(a, b); return __fmul_rn(d, d); }
+    }
+}
+
+struct EltArgs {
+    QView a, b, out;
+    int op, clo, chi;
+    int dout[4];
+    long long sa[4], sb[4];
+    long long total;
+};
+
+__global__ void __launch_bounds__(256) eltwise_vec16_kernel(const EltArgs e)
+{
+    const long long idx = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 16;
+    if (idx >= e.total) return;
+    uint8_t ra[16], rb[16], ro[16];
+    *(uint4*)ra = *(const uint4*)((const uint8_t*)e.a.data + idx);
+    *(uint4*)rb = *(const uint4*)((const uint8_t*)e.b.data + idx);
+    #pragma unroll
+    for (int k = 0; k < 16; ++k) {
+        const int qa = e.a.dtype == B200K_U8 ? (int)ra[k] : (int)(int8_t)ra[k];
+        const int qb = e.b.dtype == B200K_U8 ? (int)rb[k] : (int)(int8_t)rb[k];
+        const float r = binary_op(e.op, dequantize_dev(qa, e.a.scale, e.a.zp), dequantize_dev(qb, e.b.scale, e.b.zp));
+        ro[k] = (uint8_t)min(max(e.out.quant(r), e.clo), e.chi);
+    }
+    *(uint4*)((uint8_t*)e.out.data + idx) = *(const uint4*)ro;
+}
+
+__global__ void __launch_bounds__(256) eltwise_generic_kernel(const EltArgs e)
+{
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= e.total) return;
+    long long t = idx;
+    const int i3 = (int)(t % e.dout[3]); t /= e.dout[3];
+    const int i2 = (int)(t % e.dout[2]); t /= e.dout[2];
+    const int i1 = (int)(t % e.dout[1]);
+    const int i0 = (int)(t / e.dout[1]);
+    const long long ia = i0 * e.sa[0] + i1 * e.sa[1] + i2 * e.sa[2] + i3 * e.sa[3];
+    const long long ib = i0 * e.sb[0] + i1 * e.sb[1] + i2 * e.sb[2] + i3 * e.sb[3];
+    const float r = binary_op(e.op, e.a.get(ia), e.b.get(ib));
+    if (e.out.dtype == B200K_F32) { ((float*)e.out.data)[idx] = r; return; }
+    store_q_dev((void*)e.out.data, e.out.dtype, idx, min(max(e.out.quant(r), e.clo), e.chi));
+}
+
+__device__ __forceinline__ float activation_f(int fn, float in, float a, float b)
+{
+    switch (fn) {
+        case 0:  return __fdiv_rn(1.f, __fadd_rn(1.f, expf(-in)));
+        case 1:  return __fmul_rn(a, tanhf(__fmul_rn(b, in)));
+        case 2:  return __fadd_rn(__fmul_rn(a, in), b);
+        case 3:  return fmaxf(0.f, in);
+        case 4:  return fminf(a, fmaxf(b, in));
+        case 5:  return logf(__fadd_rn(1.0f, expf(in)));
+        case 6:  return in > 0.0f ? in : __fmul_rn(in, a);
+        case 7:  return in < 0 ? -in : in;
+        case 8:  return __fsqrt_rn(in);
+        case 9:  return __fmul_rn(in, in);
+        case 10: return (in >= 0) ? in : __fmul_rn(a, __fsub_rn(expf(in), 1.f));
+        default: return __fdiv_rn(__fmul_rn(in, fminf(fmaxf(__fadd_rn(in, 3.f), 0.0f), 6.0f)), 6.f);
+    }
+}
+
+struct UnaryArgs { QView x, y; long long count; int fn; float a, b; };
+
+// fn < 0: plain conversion (Quantize / Dequantize / requantize)
+__global__ void __launch_bounds__(256) unary_kernel(const UnaryArgs u)
+{
+    const long long base = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    #pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const long long i = base + k;
+        if (i >= u.count) return;
+        float v = u.x.get(i);
+        if (u.fn >= 0) v = activation_f(u.fn, v, u.a, u.b);
+        u.y.set(i, v);
+    }
+}
+
+}  // namespace b200k
+
+using namespace b200k;
+
+extern "C" int b200k_eltwise_q8(const b200k_eltwise_params* p, void* stream)
+{
+    B200K_REQUIRE(p, B200K_E_INVALID, "eltwise_q8: null params");
+    B200K_REQUIRE(p->a.data && p->b.data && p->out.data, B200K_E_INVALID, "eltwise_q8: null tensor pointer");
+    B200K_REQUIRE(p->rank >= 1 && p->rank <= 4, B200K_E_UNSUPPORTED, "eltwise_q8: rank %d not in [1,4]", p->rank);
+    B200K_REQUIRE(p->op >= 0 && p->op <= 6, B200K_E_UNSUPPORTED, "eltwise_q8: unsupported binary operation %d", p->op);
+    B200K_REQUIRE(p->a.dtype != B200K_S32 && p->b.dtype != B200K_S32 && p->out.dtype != B200K_S32, B200K_E_UNSUPPORTED,
+                  "eltwise_q8: Signed32 not supported");
+    EltArgs e;
+    e.a = make_view(p->a); e.b = make_view(p->b); e.out = make_view(p->out);
+    e.op = p->op;
+    int lo, hi;
+    type_range(p->out.dtype, lo, hi);
+    e.clo = p->clamp_lo > lo ? p->clamp_lo : lo;
+    e.chi = p->clamp_hi < hi ? p->clamp_hi : hi;
+    int da[4] = {1, 1, 1, 1}, db[4] = {1, 1, 1, 1};
+    for (int i = 0; i < 4; ++i) e.dout[i] = 1;
+    bool same = true;
+    for (int i = 0; i < p->rank; ++i) {
+        const int d = 4 - p->rank + i;
+        da[d] = p->shape_a[i]; db[d] = p->shape_b[i]; e.dout[d] = p->shape_out[i];
+        B200K_REQUIRE(da[d] > 0 && db[d] > 0 && e.dout[d] > 0, B200K_E_INVALID, "eltwise_q8: non-positive dimension");
+        B200K_REQUIRE((da[d] == e.dout[d] || da[d] == 1) && (db[d] == e.dout[d] || db[d] == 1), B200K_E_INVALID,
+                      "eltwise_q8: shapes are not broadcast-compatible in dimension %d", i);
+        same = same && da[d] == e.dout[d] && db[d] == e.dout[d];
+    }
+    long long ta = 1, tb = 1;
+    e.total = 1;
+    for (int i = 3; i >= 0; --i) {
+        e.sa[i] = da[i] == 1 ? 0 : ta;  ta *= da[i];
+        e.sb[i] = db[i] == 1 ? 0 : tb;  tb *= db[i];
+        e.total *= e.dout[i];
+    }
+    cudaStream_t s = (cudaStream_t)stream;
+    const uintptr_t al = (uintptr_t)p->a.data | (uintptr_t)p->b.data | (uintptr_t)p->out.data;
+    if (same && is_q8(p->a.dtype) && is_q8(p->b.dtype) && is_q8(p->out.dtype) && (e.total % 16) == 0 && (al & 15) == 0) {
+        eltwise_vec16_kernel<<<div_up(e.total / 16, 256), 256, 0, s>>>(e);
+        return check_launch("eltwise_vec16_kernel");
+    }
+    eltwise_generic_kernel<<<div_up(e.total, 256), 256, 0, s>>>(e);
+    return check_launch("eltwise_generic_kernel");
+}
+
+static int launch_unary(const b200k_qtensor& x, const b200k_qtensor& y, long long count, int fn, float a, float b,
+                        void* stream, const char* what)
+{
+    B200K_REQUIRE(x.data && y.data, B200K_E_INVALID, "%s: null tensor pointer", what);
+    B200K_REQUIRE(count >= 0, B200K_E_INVALID, "%s: negative element count", what);
+    B200K_REQUIRE(x.dtype >= B200K_U8 && x.dtype <= B200K_F32 && y.dtype >= B200K_U8 && y.dtype <= B200K_F32 &&
+                  y.dtype != B200K_S32, B200K_E_UNSUPPORTED, "%s: unsupported data type", what);
+    if (count == 0) return B200K_OK;
+    UnaryArgs u;
+    u.x = make_view(x); u.y = make_view(y); u.count = count; u.fn = fn; u.a = a; u.b = b;
+    unary_kernel<<<div_up(div_up(count, 4), 256), 256, 0, (cudaStream_t)stream>>>(u);
+    return check_launch("unary_kernel");
+}
+
+extern "C" int b200k_activation_q8(const b200k_activation_params* p, void* stream)
+{
+    B200K_REQUIRE(p, B200K_E_INVALID, "activation_q8: null params");
+    B200K_REQUIRE(p->function >= 0 && p->function <= 11, B200K_E_UNSUPPORTED, "activation_q8: unsupported activation function %d", p->function);
+    return launch_unary(p->x, p->y, p->count, p->function, p->a, p->b, stream, "activation_q8");
+}
+
+extern "C" int b200k_convert_q(const b200k_convert_params* p, void* stream)
+{
+    B200K_REQUIRE(p, B200K_E_INVALID, "convert_q: null params");
+    return launch_unary(p->x, p->y, p->count, -1, 0.f, 0.f, stream, "convert_q");
+}

@@ -1,0 +1,114 @@
+// Layout-agnostic quantised matrix product on CUDA cores: BatchMatMul with optional transposes and
+// broadcast, and FullyConnected with non-transposed ([K, N]) weights.  16 x 16 output tile per CTA,
+// operands staged through shared memory as zero-point-corrected ints.  Shapes on this path are small
+// (attention-style batched products, unusual weight layouts); the large FullyConnected / 1x1
+// convolution GEMMs go through the implicit-GEMM kernels.
+#include <string.h>
+#include "common.cuh"
+
+namespace b200k {
+
+int launch_conv_dp4a(const b200k_conv2d_params* p, cudaStream_t stream);
+int conv2d_dispatch(const b200k_conv2d_params* p, cudaStream_t stream);
+
+struct BmmArgs {
+    const void* x; const void* y; void* out; int32_t* acc_out;
+    const int32_t* bias; const float* w_scales; const float* b_scales;
+    float w_scale, b_scale;
+    int x_dtype, y_dtype, out_dtype;
+    int zx, zy;
+    int B, M, K, N;
+    long long xs_m, xs_k, ys_k, ys_n;      // element strides
+    long long bsx, bsy;
+    Requant rq;
+};
+
+__global__ void __launch_bounds__(256) bmm_generic_kernel(const BmmArgs a)
+{
+    __shared__ int xs[16][17];
+    __shared__ int ys[16][17];
+    const int b = blockIdx.z;
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    const int m = blockIdx.y * 16 + ty, n = blockIdx.x * 16 + tx;
+    const long long xo = b * a.bsx, yo = b * a.bsy;
+    int acc = 0;
+    for (int k0 = 0; k0 < a.K; k0 += 16) {
+        // xs[ty][tx] = x[m, k0 + tx];  ys[ty][tx] = y[k0 + ty, n]
+        int kx = k0 + tx, ky = k0 + ty;
+        xs[ty][tx] = (m < a.M && kx < a.K) ? load_q_dev(a.x, a.x_dtype, xo + m * a.xs_m + kx * a.xs_k) - a.zx : 0;
+        ys[ty][tx] = (n < a.N && ky < a.K) ? load_q_dev(a.y, a.y_dtype, yo + ky * a.ys_k + n * a.ys_n) - a.zy : 0;
+        __syncthreads();
+        #pragma unroll
+        for (int k = 0; k < 16; ++k) acc += xs[ty][k] * ys[k][tx];
+        __syncthreads();
+    }
+    if (m < a.M && n < a.N) {
+        const long long oi = ((long long)b * a.M + m) * a.N + n;
+        if (a.acc_out) a.acc_out[oi] = acc;
+        const float swc = a.w_scales ? a.w_scales[n] : a.w_scale;
+        const float sbc = a.b_scales ? a.b_scales[n] : a.b_scale;
+        const int bq = a.bias ? a.bias[n] : 0;
+        store_q_dev(a.out, a.out_dtype, oi, a.rq(acc, swc, a.bias != nullptr, bq, sbc));
+    }
+}
+
+}  // namespace b200k
+
+using namespace b200k;
+
+extern "C" int b200k_batch_matmul_q8(const b200k_bmm_params* p, void* stream)
+{
+    B200K_REQUIRE(p, B200K_E_INVALID, "batch_matmul_q8: null params");
+    B200K_REQUIRE(p->x.data && p->y.data && p->out.data, B200K_E_INVALID, "batch_matmul_q8: null tensor pointer");
+    B200K_REQUIRE(is_q8(p->x.dtype) && is_q8(p->y.dtype) && is_q8(p->out.dtype), B200K_E_UNSUPPORTED,
+                  "batch_matmul_q8: only 8-bit quantised tensors are supported");
+    B200K_REQUIRE(p->batch > 0 && p->m > 0 && p->k > 0 && p->n > 0, B200K_E_INVALID, "batch_matmul_q8: bad shape");
+    B200K_REQUIRE(p->batch <= 65535, B200K_E_TOOBIG, "batch_matmul_q8: batch %d > 65535", p->batch);
+    BmmArgs a;
+    a.x = p->x.data; a.y = p->y.data; a.out = (void*)p->out.data; a.acc_out = p->acc_out;
+    a.bias = nullptr; a.w_scales = nullptr; a.b_scales = nullptr; a.w_scale = p->y.scale; a.b_scale = 0.f;
+    a.x_dtype = p->x.dtype; a.y_dtype = p->y.dtype; a.out_dtype = p->out.dtype;
+    a.zx = p->x.zero_point; a.zy = p->y.zero_point;
+    a.B = p->batch; a.M = p->m; a.K = p->k; a.N = p->n;
+    a.xs_m = p->transpose_x ? 1 : p->k;  a.xs_k = p->transpose_x ? p->m : 1;
+    a.ys_k = p->transpose_y ? 1 : p->n;  a.ys_n = p->transpose_y ? p->k : 1;
+    a.bsx = p->batch_stride_x; a.bsy = p->batch_stride_y;
+    int lo, hi;
+    type_range(p->out.dtype, lo, hi);
+    a.rq = make_requant(p->x.scale, p->out, lo, hi);
+    dim3 grid(div_up(p->n, 16), div_up(p->m, 16), p->batch);
+    bmm_generic_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(a);
+    return check_launch("bmm_generic_kernel");
+}
+
+extern "C" int b200k_fully_connected_q8(const b200k_fc_params* p, void* stream)
+{
+    B200K_REQUIRE(p, B200K_E_INVALID, "fully_connected_q8: null params");
+    B200K_REQUIRE(p->m > 0 && p->k > 0 && p->n > 0, B200K_E_INVALID, "fully_connected_q8: bad shape");
+    if (p->transpose_w) {
+        // x [m, k] is an NHWC tensor [m, 1, 1, k]; w [n, k] is [O, 1, 1, I]: a 1x1 convolution.
+        b200k_conv2d_params c;
+        memset(&c, 0, sizeof(c));
+        c.x = p->x; c.w = p->w; c.bias = p->bias; c.y = p->y;
+        c.n = p->m; c.h = 1; c.wd = 1; c.c = p->k; c.oh = 1; c.ow = 1; c.oc = p->n;
+        c.kh = c.kw = 1; c.stride_h = c.stride_w = 1; c.dil_h = c.dil_w = 1;
+        c.clamp_lo = p->clamp_lo; c.clamp_hi = p->clamp_hi; c.acc_out = p->acc_out; c.algo = p->algo;
+        return conv2d_dispatch(&c, (cudaStream_t)stream);
+    }
+    B200K_REQUIRE(p->x.data && p->w.data && p->y.data, B200K_E_INVALID, "fully_connected_q8: null tensor pointer");
+    B200K_REQUIRE(is_q8(p->x.dtype) && is_q8(p->w.dtype) && is_q8(p->y.dtype), B200K_E_UNSUPPORTED,
+                  "fully_connected_q8: only 8-bit quantised tensors are supported");
+    B200K_REQUIRE(!p->bias.data || p->bias.dtype == B200K_S32, B200K_E_INVALID, "fully_connected_q8: bias must be Signed32");
+    BmmArgs a;
+    a.x = p->x.data; a.y = p->w.data; a.out = (void*)p->y.data; a.acc_out = p->acc_out;
+    a.bias = (const int32_t*)p->bias.data; a.w_scales = p->w.scales; a.b_scales = p->bias.scales;
+    a.w_scale = p->w.scale; a.b_scale = p->bias.scale;
+    a.x_dtype = p->x.dtype; a.y_dtype = p->w.dtype; a.out_dtype = p->y.dtype;
+    a.zx = p->x.zero_point; a.zy = p->w.zero_point;
+    a.B = 1; a.M = p->m; a.K = p->k; a.N = p->n;
+    a.xs_m = p->k; a.xs_k = 1; a.ys_k = p->n; a.ys_n = 1; a.bsx = a.bsy = 0;
+    a.rq = make_requant(p->x.scale, p->y, p->clamp_lo, p->clamp_hi);
+    dim3 grid(div_up(p->n, 16), div_up(p->m, 16), 1);
+    bmm_generic_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(a);
+    return check_launch("bmm_generic_kernel");
+}

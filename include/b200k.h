@@ -1,0 +1,268 @@
+/*
+ * b200k.h — C ABI of libb200k.so, the sm_100a kernel library behind the Arm NN "B200Acc" backend.
+ *
+ * Every entry point is the device-side replacement of one CpuRef workload function of the
+ * Arm NN reference (paths below are relative to the Arm NN source tree).  The B200Acc backend
+ * plugin (armnn_b200/backend/, an IBackendInternal implementation) binds exactly these symbols:
+ * one call per IWorkload::Execute().
+ *
+ * Conventions
+ *  - plain C: raw device pointers, ints, floats; no C++ or torch types cross this line.
+ *  - every launcher is asynchronous on the caller's CUDA stream (passed as void*, a cudaStream_t).
+ *  - return value: 0 on success, a negative B200K_E_* code otherwise; never aborts, never throws.
+ *    b200k_last_error() returns a thread-local description of the last failure.
+ *  - tensors are dense, row-major, NHWC for 4-D image tensors (the only layout B200Acc accepts).
+ *  - quantisation follows armnn::Quantize / armnn::Dequantize (src/armnn/TypesUtils.cpp:29-56):
+ *        real = scale * (q - zero_point),   q = clamp(zero_point + round_half_away(real / scale)).
+ *  - "clamp_lo/clamp_hi" carry a fused activation (ReLu / BoundedReLu) as a clamp in the output's
+ *    quantised domain; use b200k_activation_clamp() to derive them.  Pass the type's full range
+ *    for "no activation".
+ */
+#ifndef B200K_H
+#define B200K_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200K_OK            0
+#define B200K_E_INVALID    -1   /* bad argument (null pointer, unsupported dtype / shape) */
+#define B200K_E_CUDA       -2   /* a CUDA runtime / driver call failed                      */
+#define B200K_E_UNSUPPORTED -3  /* valid request that this library does not implement        */
+#define B200K_E_NODEVICE   -4   /* no sm_100 device visible                                  */
+#define B200K_E_TIMEOUT    -5   /* a bounded device-side wait gave up (status word set)      */
+#define B200K_E_TOOBIG     -6   /* size beyond a documented fixed maximum                    */
+
+/* element types; numbering is private to this ABI (armnn::DataType in include/armnn/Types.hpp) */
+typedef enum {
+    B200K_U8  = 0,  /* QAsymmU8                          */
+    B200K_S8  = 1,  /* QAsymmS8 and QSymmS8              */
+    B200K_S16 = 2,  /* QSymmS16                          */
+    B200K_S32 = 3,  /* Signed32 (bias)                   */
+    B200K_F32 = 4   /* Float32                           */
+} b200k_dtype;
+
+/* A quantised tensor operand.  `scales` (device pointer, one float per channel of the quantisation
+ * axis) overrides `scale` when non-null: per-axis QSymmS8 weights and per-axis Signed32 bias
+ * (src/backends/reference/workloads/BaseIterator.hpp:794-830, 861-911). */
+typedef struct {
+    const void*  data;        /* device pointer                              */
+    int32_t      dtype;       /* b200k_dtype                                 */
+    float        scale;       /* per-tensor scale                            */
+    int32_t      zero_point;  /* per-tensor offset (0 for symmetric types)   */
+    const float* scales;      /* device pointer, per-axis scales, or NULL    */
+} b200k_qtensor;
+
+/* ---- device management ------------------------------------------------------------------- */
+
+/* Selects `device` for the calling thread and checks it is an sm_100 part.
+ * Replaces nothing in CpuRef (RefBackend::CreateBackendContext returns null,
+ * src/backends/reference/RefBackend.cpp:50-53); modelled on ClBackendContext
+ * (src/backends/cl/ClBackendContext.cpp:61-215). */
+int b200k_device_open(int device);
+int b200k_device_count(void);
+const char* b200k_last_error(void);
+const char* b200k_version(void);
+
+/* Quantised clamp range of a fused activation on an output tensor (scale, zero_point, dtype).
+ * kind: 0 = none, 1 = ReLu, 2 = BoundedReLu(a = upper, b = lower)
+ * (armnn::ActivationFunction, src/backends/reference/workloads/Activation.cpp:13-119).
+ * Pure host arithmetic. */
+int b200k_activation_clamp(int kind, float a, float b, float scale, int32_t zero_point,
+                           int32_t dtype, int32_t* clamp_lo, int32_t* clamp_hi);
+
+/* ---- Convolution2d / FullyConnected ------------------------------------------------------- */
+
+/* armnn::Convolve, non-depthwise branch (src/backends/reference/workloads/ConvImpl.cpp:68-233),
+ * called from RefConvolution2dWorkload::Execute (RefConvolution2dWorkload.cpp:33-58).
+ *   x [n, h, w, c]  U8 or S8        w [oc, kh, kw, c]  U8 or S8, per-tensor or per-axis(dim 0)
+ *   bias [oc] S32 with its own scale(s), or data == NULL       y [n, oh, ow, oc]  U8 or S8
+ * acc = sum over in-bounds taps of (x - zx)(w - zw)   (int32, exact)
+ * y   = clamp(zy + round((float(acc) * (sx * sw[oc]) + float(bias) * sb[oc]) / sy), lo, hi)
+ * all in IEEE fp32 without fused multiply-add.
+ * acc_out (optional, device int32 [n*oh*ow*oc]) receives the raw accumulators. */
+typedef struct {
+    b200k_qtensor x, w, bias, y;
+    int32_t n, h, wd, c;            /* input  N H W C  */
+    int32_t oh, ow, oc;             /* output H W C    */
+    int32_t kh, kw;
+    int32_t stride_h, stride_w;
+    int32_t pad_top, pad_left;
+    int32_t dil_h, dil_w;
+    int32_t clamp_lo, clamp_hi;
+    int32_t* acc_out;
+    int32_t algo;                   /* 0 = auto, 1 = CUDA-core dp4a kernel, 2 = tcgen05 kernel */
+    const void* packed;             /* optional result of b200k_conv2d_pack (device), or NULL   */
+} b200k_conv2d_params;
+
+int b200k_conv2d_q8(const b200k_conv2d_params* p, void* stream);
+
+/* Load-time weight preparation for the tcgen05 path: per-tap per-channel weight sums as a 2-D
+ * prefix table, int32 [(kh+1)*(kw+1)*oc], used to correct for zero-filled padding when zx != 0.
+ * CpuRef re-decodes the weights on every inference (ConvImpl.cpp:111-115); this replaces that.
+ * `packed` must hold b200k_conv2d_pack_bytes() bytes of device memory. */
+size_t b200k_conv2d_pack_bytes(int32_t oc, int32_t kh, int32_t kw, int32_t c);
+int b200k_conv2d_pack(const b200k_conv2d_params* p, void* packed, void* stream);
+
+/* armnn::FullyConnected (src/backends/reference/workloads/FullyConnected.cpp:13-65) from
+ * RefFullyConnectedWorkload::Execute (RefFullyConnectedWorkload.cpp:16-67).
+ *   x [m, k]   w [n, k] when transpose_w != 0 (m_TransposeWeightMatrix) else [k, n]
+ *   bias [n] or NULL   y [m, n];  per-axis weight scales index n.
+ * Same arithmetic and epilogue as b200k_conv2d_q8. */
+typedef struct {
+    b200k_qtensor x, w, bias, y;
+    int32_t m, k, n;
+    int32_t transpose_w;
+    int32_t clamp_lo, clamp_hi;
+    int32_t* acc_out;
+    int32_t algo;                   /* as b200k_conv2d_params.algo */
+} b200k_fc_params;
+
+int b200k_fully_connected_q8(const b200k_fc_params* p, void* stream);
+
+/* armnn::BatchMatMul (src/backends/reference/workloads/BatchMatMulImpl.cpp:15-139, 329-468) from
+ * RefBatchMatMulWorkload::Execute (RefBatchMatMulWorkload.cpp:19-47).
+ *   x [batch, m, k] (or [batch, k, m] when transpose_x), y [batch, k, n] (or [batch, n, k] when
+ *   transpose_y), out [batch, m, n]; batch_stride_* = 0 broadcasts that operand.
+ * Adjoint inputs are not implemented (the backend's layer-support predicate refuses them). */
+typedef struct {
+    b200k_qtensor x, y, out;
+    int32_t batch, m, k, n;
+    int32_t transpose_x, transpose_y;
+    int64_t batch_stride_x, batch_stride_y;   /* elements; 0 = broadcast */
+    int32_t* acc_out;
+} b200k_bmm_params;
+
+int b200k_batch_matmul_q8(const b200k_bmm_params* p, void* stream);
+
+/* ---- DepthwiseConvolution2d ---------------------------------------------------------------- */
+
+/* armnn::Convolve with depthwise = true (ConvImpl.cpp:100, 128-146) from
+ * RefDepthwiseConvolution2dWorkload::Execute (RefDepthwiseConvolution2dWorkload.cpp:38-62).
+ *   x [n, h, w, c]   w [1, kh, kw, oc], oc = c * depth_multiplier, per-axis scales index oc (dim 3)
+ * Same epilogue as b200k_conv2d_q8. */
+int b200k_dwconv2d_q8(const b200k_conv2d_params* p, void* stream);
+
+/* ---- Pooling2d / Mean ----------------------------------------------------------------------- */
+
+/* armnn::Pooling2d (src/backends/reference/workloads/Pooling2d.cpp:142-303).
+ * pool_type: 0 Max, 1 Average, 2 L2 (armnn::PoolingAlgorithm)
+ * padding_method: 0 IgnoreValue, 1 Exclude (armnn::PaddingMethod)
+ * fp32 arithmetic in CpuRef's own summation order, so results equal CpuRef's bit for bit. */
+typedef struct {
+    b200k_qtensor x, y;
+    int32_t n, h, wd, c, oh, ow;
+    int32_t pool_h, pool_w, stride_h, stride_w;
+    int32_t pad_top, pad_bottom, pad_left, pad_right;
+    int32_t pool_type, padding_method;
+} b200k_pool2d_params;
+
+int b200k_pool2d_q8(const b200k_pool2d_params* p, void* stream);
+
+/* armnn::Reduce with ReduceOperation::Mean over axes {1,2} of an NHWC tensor
+ * (src/backends/reference/workloads/Reduce.cpp:68-173, RefMeanWorkload.cpp:22-38).
+ * x [n, h, w, c] -> y [n, c] (keep_dims only changes the shape metadata). */
+typedef struct {
+    b200k_qtensor x, y;
+    int32_t n, h, wd, c;
+} b200k_mean_params;
+
+int b200k_mean_hw_q8(const b200k_mean_params* p, void* stream);
+
+/* ---- ElementwiseBinary / Activation ------------------------------------------------------- */
+
+/* ElementwiseBinaryFunction<std::plus / std::multiplies / ...> with BroadcastLoop
+ * (RefElementwiseBinaryWorkload.cpp:27-132, ElementwiseFunction.cpp:25-34, Broadcast.hpp:13-104).
+ * op follows armnn::BinaryOperation (include/armnn/Types.hpp:138-149): 0 Add, 1 Div, 2 Maximum,
+ * 3 Minimum, 4 Mul, 5 Sub, 6 SqDiff.  Shapes have equal rank <= 4 (padded with leading 1s); a
+ * dimension of size 1 broadcasts.  out = Q(deq(a) op deq(b)), then the clamp. */
+typedef struct {
+    b200k_qtensor a, b, out;
+    int32_t rank;
+    int32_t shape_a[4], shape_b[4], shape_out[4];
+    int32_t op;
+    int32_t clamp_lo, clamp_hi;
+} b200k_eltwise_params;
+
+int b200k_eltwise_q8(const b200k_eltwise_params* p, void* stream);
+
+/* armnn::Activation (src/backends/reference/workloads/Activation.cpp:13-119).
+ * function follows armnn::ActivationFunction numbering (include/armnn/Types.hpp):
+ * 0 Sigmoid, 1 TanH, 2 Linear, 3 ReLu, 4 BoundedReLu, 5 SoftReLu, 6 LeakyReLu, 7 Abs, 8 Sqrt,
+ * 9 Square, 10 Elu, 11 HardSwish. */
+typedef struct {
+    b200k_qtensor x, y;
+    int64_t count;
+    int32_t function;
+    float a, b;
+} b200k_activation_params;
+
+int b200k_activation_q8(const b200k_activation_params* p, void* stream);
+
+/* ---- Softmax --------------------------------------------------------------------------------- */
+
+/* armnn::Softmax (src/backends/reference/workloads/Softmax.cpp:17-70): softmax over the axis of
+ * length `axis_size`, for outer x inner independent rows, element stride `inner` along the axis. */
+typedef struct {
+    b200k_qtensor x, y;
+    int32_t outer, axis_size, inner;
+    float beta;
+} b200k_softmax_params;
+
+int b200k_softmax_q8(const b200k_softmax_params* p, void* stream);
+
+/* ---- Quantize / Dequantize ----------------------------------------------------------------- */
+
+/* QuantizeImpl (RefQuantizeWorkload.cpp:14-45) and armnn::Dequantize
+ * (src/backends/reference/workloads/Dequantize.cpp:11-28): any of F32/U8/S8/S16 -> any of
+ * F32/U8/S8/S16 through fp32, i.e. quantize, dequantize and requantize in one entry point. */
+typedef struct {
+    b200k_qtensor x, y;
+    int64_t count;
+} b200k_convert_params;
+
+int b200k_convert_q(const b200k_convert_params* p, void* stream);
+
+/* ---- QLstm ----------------------------------------------------------------------------------- */
+
+/* One RefQLstmWorkload::Execute step (src/backends/reference/workloads/RefQLstmWorkload.cpp:46-541,
+ * LstmUtils.cpp:16-256) reproduced operation by operation, including the re-quantisation of the
+ * int16 gate buffers after every multiply-accumulate (LstmUtils.cpp:87-111).
+ * Weight pointers are device pointers; a NULL pointer disables the corresponding option exactly as
+ * the reference's m_CifgEnabled / m_PeepholeEnabled / m_ProjectionEnabled / m_LayerNormEnabled do. */
+typedef struct {
+    int32_t batch, input_size, num_units, output_size;
+    /* tensors */
+    const int8_t*  input;            float input_scale;  int32_t input_zp;       /* [batch, input_size]  */
+    const int8_t*  output_state_in;  float output_state_scale; int32_t output_state_zp; /* [batch, output_size] */
+    const int16_t* cell_state_in;    float cell_state_scale;   /* [batch, num_units]  */
+    int8_t*  output_state_out;       /* [batch, output_size], same quantisation as output_state_in */
+    int16_t* cell_state_out;         /* [batch, num_units]   */
+    int8_t*  output;                 float output_scale; int32_t output_zp;      /* [batch, output_size] */
+    /* weights: int8 [num_units, input_size] / [num_units, output_size]; each with its scale */
+    const int8_t *w_i2i, *w_i2f, *w_i2c, *w_i2o;   float s_i2i, s_i2f, s_i2c, s_i2o;
+    const int8_t *w_r2i, *w_r2f, *w_r2c, *w_r2o;   float s_r2i, s_r2f, s_r2c, s_r2o;
+    const int16_t *w_c2i, *w_c2f, *w_c2o;          float s_c2i, s_c2f, s_c2o;   /* peephole [num_units] */
+    const int32_t *b_i, *b_f, *b_c, *b_o;          float s_bi, s_bf, s_bc, s_bo; /* gate biases          */
+    const int16_t *ln_i, *ln_f, *ln_c, *ln_o;      float s_lni, s_lnf, s_lnc, s_lno; /* layer-norm w   */
+    const int8_t  *w_proj;  float s_proj;          /* [output_size, num_units] */
+    const int32_t *b_proj;  float s_bproj;
+    /* descriptor (armnn::QLstmDescriptor, include/armnn/Descriptors.hpp) */
+    float cell_clip, projection_clip;
+    float input_intermediate_scale, forget_intermediate_scale, cell_intermediate_scale,
+          output_intermediate_scale;
+    float hidden_state_scale; int32_t hidden_state_zp;
+    /* scratch: device int16 [4 * batch * num_units] + int8/int32 as documented in qlstm.cu */
+    void*  scratch; size_t scratch_bytes;
+} b200k_qlstm_params;
+
+size_t b200k_qlstm_scratch_bytes(int32_t batch, int32_t num_units, int32_t output_size);
+int b200k_qlstm_step(const b200k_qlstm_params* p, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200K_H */

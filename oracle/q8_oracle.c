@@ -1,0 +1,623 @@
+/*
+ * q8_oracle.c — TEST INFRASTRUCTURE ONLY.  A plain-C CPU restatement of the Arm NN CpuRef
+ * arithmetic for the quantised operator hot path.  Nothing in the product (libb200k.so, the
+ * B200Acc backend, armnn_b200/) links, loads or calls this file; only tests/, the smoke check
+ * and the CPU-baseline leg of bench.py do, and only as the checker.
+ *
+ * Parity is pinned: tests/test_oracle_*.py check every function here against (i) known-answer
+ * vectors transcribed from the reference's own layer tests (tests/golden/ref_layer_tests.json)
+ * and (ii) outputs of the real CpuRef workloads compiled from the reference sources
+ * (oracle/_ref/, fixtures under tests/golden/ made by tests/golden/make_cpuref_fixtures.py).
+ *
+ * Two kinds of restatement, because CpuRef computes everything in fp32:
+ *  - contractions (conv / depthwise / fully-connected / batch-matmul): CpuRef sums
+ *    deq(x)*deq(w) in a float.  Here the sum is an exact int32 accumulator over the same loop
+ *    nest and index formulas, followed by ONE fp32 requantisation.  This is the function the
+ *    GPU must match bit for bit (accumulator and output); it equals CpuRef except on rounding
+ *    ties (+-1 LSB).
+ *  - everything else (pooling, mean, elementwise, activation, softmax, quantize/dequantize):
+ *    the same fp32 operations in the same order as CpuRef, so results equal CpuRef's exactly
+ *    (up to libm exp/tanh differences where those are used).
+ *
+ * Parameter structs are the ones of include/b200k.h, with HOST pointers.
+ * Build: gcc -O2 -fPIC -shared -ffp-contract=off -fopenmp (oracle/Makefile).
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+#include "../include/b200k.h"
+
+/* ---- armnn::Quantize / armnn::Dequantize, src/armnn/TypesUtils.cpp:29-56 ------------------- */
+
+static void type_range(int dtype, int32_t* lo, int32_t* hi)
+{
+    switch (dtype) {
+        case B200K_U8:  *lo = 0;       *hi = 255;    break;
+        case B200K_S8:  *lo = -128;    *hi = 127;    break;
+        case B200K_S16: *lo = -32768;  *hi = 32767;  break;
+        default:        *lo = INT32_MIN; *hi = INT32_MAX; break;
+    }
+}
+
+/* q = clamp(float(zp) + round(v / scale), type_min, type_max), TypesUtils.cpp:38-41 */
+static int32_t quantize_f(float v, float scale, int32_t zp, int dtype)
+{
+    int32_t lo, hi;
+    type_range(dtype, &lo, &hi);
+    volatile float d = v / scale;           /* volatile: keep the division in fp32, unfused */
+    float r = roundf(d);
+    float q = (float)zp + r;
+    q = fminf(fmaxf(q, (float)lo), (float)hi);
+    return (int32_t)q;
+}
+
+/* v = float(q - zp) * scale, TypesUtils.cpp:48-56 */
+static float dequantize_i(int32_t q, float scale, int32_t zp)
+{
+    return (float)(q - zp) * scale;
+}
+
+static int32_t load_q(const void* p, int dtype, int64_t i)
+{
+    switch (dtype) {
+        case B200K_U8:  return ((const uint8_t*)p)[i];
+        case B200K_S8:  return ((const int8_t*)p)[i];
+        case B200K_S16: return ((const int16_t*)p)[i];
+        case B200K_S32: return ((const int32_t*)p)[i];
+        default: return 0;
+    }
+}
+
+static void store_q(void* p, int dtype, int64_t i, int32_t q)
+{
+    switch (dtype) {
+        case B200K_U8:  ((uint8_t*)p)[i]  = (uint8_t)q;  break;
+        case B200K_S8:  ((int8_t*)p)[i]   = (int8_t)q;   break;
+        case B200K_S16: ((int16_t*)p)[i]  = (int16_t)q;  break;
+        case B200K_S32: ((int32_t*)p)[i]  = q;           break;
+        default: break;
+    }
+}
+
+/* Decoder<float>::Get for any supported element type (Decoders.hpp:63-126) */
+static float load_f(const b200k_qtensor* t, int64_t i)
+{
+    if (t->dtype == B200K_F32) return ((const float*)t->data)[i];
+    return dequantize_i(load_q(t->data, t->dtype, i), t->scale, t->zero_point);
+}
+
+/* Encoder<float>::Set (Encoders.hpp:18-91) */
+static void store_f(const b200k_qtensor* t, int64_t i, float v)
+{
+    if (t->dtype == B200K_F32) { ((float*)t->data)[i] = v; return; }
+    store_q((void*)t->data, t->dtype, i, quantize_f(v, t->scale, t->zero_point, t->dtype));
+}
+
+static int32_t clampi(int32_t v, int32_t lo, int32_t hi) { return v < lo ? lo : (v > hi ? hi : v); }
+
+int oracle_activation_clamp(int kind, float a, float b, float scale, int32_t zp, int32_t dtype,
+                            int32_t* lo, int32_t* hi)
+{
+    type_range(dtype, lo, hi);
+    if (kind == 1) {                       /* ReLu: max(0, x) */
+        int32_t q0 = quantize_f(0.0f, scale, zp, dtype);
+        if (q0 > *lo) *lo = q0;
+    } else if (kind == 2) {                /* BoundedReLu: min(a, max(b, x)) */
+        int32_t qb = quantize_f(b, scale, zp, dtype);
+        int32_t qa = quantize_f(a, scale, zp, dtype);
+        if (qb > *lo) *lo = qb;
+        if (qa < *hi) *hi = qa;
+    } else if (kind != 0) {
+        return B200K_E_INVALID;
+    }
+    return 0;
+}
+
+/* The one requantisation shared by all contractions:
+ *   v = float(acc) * (sx * sw) + float(bias) * sb ;  q = Quantize(v, sy, zy) ; clamp */
+static int32_t requant(int32_t acc, float sx, float sw, int has_bias, int32_t bq, float sb,
+                       float sy, int32_t zy, int dtype, int32_t clo, int32_t chi)
+{
+    volatile float m = sx * sw;
+    volatile float v = (float)acc * m;
+    if (has_bias) {
+        volatile float bf = (float)bq * sb;
+        v = v + bf;
+    }
+    return clampi(quantize_f(v, sy, zy, dtype), clo, chi);
+}
+
+/* ---- Convolve, ConvImpl.cpp:68-233 (NHWC; weights [O,H,W,I], depthwise [1,H,W,O]) ----------- */
+
+static int conv_impl(const b200k_conv2d_params* p, int depthwise)
+{
+    const int N = p->n, H = p->h, W = p->wd, C = p->c, OH = p->oh, OW = p->ow, OC = p->oc;
+    const int KH = p->kh, KW = p->kw;
+    const int zx = p->x.zero_point, zw = p->w.zero_point;
+    const int dm = depthwise ? OC / C : 1;          /* ConvImpl.cpp:100 */
+    if (!p->x.data || !p->w.data || !p->y.data) return B200K_E_INVALID;
+    #pragma omp parallel for collapse(2) schedule(static)
+    for (int b = 0; b < N; ++b)
+    for (int oy = 0; oy < OH; ++oy)
+    for (int ox = 0; ox < OW; ++ox)
+    for (int co = 0; co < OC; ++co) {
+        int32_t acc = 0;
+        for (int ky = 0; ky < KH; ++ky) {
+            int iy = oy * p->stride_h + ky * p->dil_h - p->pad_top;   /* :165, :170 */
+            if (iy < 0 || iy >= H) continue;                          /* padding tap: adds 0.0 */
+            for (int kx = 0; kx < KW; ++kx) {
+                int ix = ox * p->stride_w + kx * p->dil_w - p->pad_left;
+                if (ix < 0 || ix >= W) continue;
+                if (depthwise) {
+                    int ci = co / dm;                                         /* :138 */
+                    int64_t wi = (int64_t)kx * OC + co + (int64_t)ky * KW * OC; /* :140-141 */
+                    int64_t xi = (((int64_t)b * H + iy) * W + ix) * C + ci;
+                    acc += (load_q(p->x.data, p->x.dtype, xi) - zx) *
+                           (load_q(p->w.data, p->w.dtype, wi) - zw);
+                } else {
+                    int64_t wb = (((int64_t)co * KH + ky) * KW + kx) * C;      /* :149-152 */
+                    int64_t xb = (((int64_t)b * H + iy) * W + ix) * C;         /* :185-188 */
+                    if (p->x.dtype == B200K_S8 && p->w.dtype == B200K_S8) {
+                        const int8_t* xp = (const int8_t*)p->x.data + xb;
+                        const int8_t* wp = (const int8_t*)p->w.data + wb;
+                        int32_t s = 0;
+                        for (int ci = 0; ci < C; ++ci) s += ((int)xp[ci] - zx) * ((int)wp[ci] - zw);
+                        acc += s;
+                    } else if (p->x.dtype == B200K_U8 && p->w.dtype == B200K_U8) {
+                        const uint8_t* xp = (const uint8_t*)p->x.data + xb;
+                        const uint8_t* wp = (const uint8_t*)p->w.data + wb;
+                        int32_t s = 0;
+                        for (int ci = 0; ci < C; ++ci) s += ((int)xp[ci] - zx) * ((int)wp[ci] - zw);
+                        acc += s;
+                    } else {
+                        for (int ci = 0; ci < C; ++ci)
+                            acc += (load_q(p->x.data, p->x.dtype, xb + ci) - zx) *
+                                   (load_q(p->w.data, p->w.dtype, wb + ci) - zw);
+                    }
+                }
+            }
+        }
+        int64_t oi = (((int64_t)b * OH + oy) * OW + ox) * OC + co;             /* :214-217 */
+        if (p->acc_out) p->acc_out[oi] = acc;
+        float sw = p->w.scales ? p->w.scales[co] : p->w.scale;
+        int has_bias = p->bias.data != NULL;
+        int32_t bq = has_bias ? ((const int32_t*)p->bias.data)[co] : 0;
+        float sb = p->bias.scales ? p->bias.scales[co] : p->bias.scale;
+        store_q((void*)p->y.data, p->y.dtype, oi,
+                requant(acc, p->x.scale, sw, has_bias, bq, sb, p->y.scale, p->y.zero_point,
+                        p->y.dtype, p->clamp_lo, p->clamp_hi));
+    }
+    return 0;
+}
+
+int oracle_conv2d_q8(const b200k_conv2d_params* p)   { return conv_impl(p, 0); }
+int oracle_dwconv2d_q8(const b200k_conv2d_params* p) { return conv_impl(p, 1); }
+
+/* ---- FullyConnected, FullyConnected.cpp:13-65 --------------------------------------------- */
+
+int oracle_fully_connected_q8(const b200k_fc_params* p)
+{
+    const int M = p->m, K = p->k, N = p->n;
+    const int zx = p->x.zero_point, zw = p->w.zero_point;
+    if (!p->x.data || !p->w.data || !p->y.data) return B200K_E_INVALID;
+    #pragma omp parallel for schedule(static)
+    for (int m = 0; m < M; ++m)
+    for (int n = 0; n < N; ++n) {
+        int32_t acc = 0;
+        for (int k = 0; k < K; ++k) {
+            int64_t wi = p->transpose_w ? (int64_t)n * K + k : (int64_t)k * N + n;   /* :43-51 */
+            acc += (load_q(p->x.data, p->x.dtype, (int64_t)m * K + k) - zx) *
+                   (load_q(p->w.data, p->w.dtype, wi) - zw);
+        }
+        int64_t oi = (int64_t)m * N + n;
+        if (p->acc_out) p->acc_out[oi] = acc;
+        float sw = p->w.scales ? p->w.scales[n] : p->w.scale;
+        int has_bias = p->bias.data != NULL;
+        int32_t bq = has_bias ? ((const int32_t*)p->bias.data)[n] : 0;
+        float sb = p->bias.scales ? p->bias.scales[n] : p->bias.scale;
+        store_q((void*)p->y.data, p->y.dtype, oi,
+                requant(acc, p->x.scale, sw, has_bias, bq, sb, p->y.scale, p->y.zero_point,
+                        p->y.dtype, p->clamp_lo, p->clamp_hi));
+    }
+    return 0;
+}
+
+/* ---- BatchMatMul, BatchMatMulImpl.cpp:40-78 (sum over the shared axis, then Set) ------------- */
+
+int oracle_batch_matmul_q8(const b200k_bmm_params* p)
+{
+    const int B = p->batch, M = p->m, K = p->k, N = p->n;
+    if (!p->x.data || !p->y.data || !p->out.data) return B200K_E_INVALID;
+    int32_t lo, hi;
+    type_range(p->out.dtype, &lo, &hi);
+    for (int b = 0; b < B; ++b)
+    for (int m = 0; m < M; ++m)
+    for (int n = 0; n < N; ++n) {
+        int32_t acc = 0;
+        for (int k = 0; k < K; ++k) {
+            int64_t xi = b * p->batch_stride_x + (p->transpose_x ? (int64_t)k * M + m : (int64_t)m * K + k);
+            int64_t yi = b * p->batch_stride_y + (p->transpose_y ? (int64_t)n * K + k : (int64_t)k * N + n);
+            acc += (load_q(p->x.data, p->x.dtype, xi) - p->x.zero_point) *
+                   (load_q(p->y.data, p->y.dtype, yi) - p->y.zero_point);
+        }
+        int64_t oi = ((int64_t)b * M + m) * N + n;
+        if (p->acc_out) p->acc_out[oi] = acc;
+        store_q((void*)p->out.data, p->out.dtype, oi,
+                requant(acc, p->x.scale, p->y.scale, 0, 0, 0.f, p->out.scale, p->out.zero_point,
+                        p->out.dtype, lo, hi));
+    }
+    return 0;
+}
+
+/* ---- Pooling2d, Pooling2d.cpp:142-303 ----------------------------------------------------- */
+
+static int clamp_range(int* s, int* e, int maxr)       /* Pooling2d.cpp:121-134 */
+{
+    if (*s < 0 || *e > maxr) {
+        int a = *s < 0 ? 0 : *s;  if (a > maxr) a = maxr;
+        int b = *e < 0 ? 0 : *e;  if (b > maxr) b = maxr;
+        *s = a; *e = b;
+        return 1;
+    }
+    return 0;
+}
+
+int oracle_pool2d_q8(const b200k_pool2d_params* p)
+{
+    const int N = p->n, H = p->h, W = p->wd, C = p->c, OH = p->oh, OW = p->ow;
+    if (!p->x.data || !p->y.data) return B200K_E_INVALID;
+    if (p->pool_type < 0 || p->pool_type > 2) return B200K_E_INVALID;
+    #pragma omp parallel for collapse(2) schedule(static)
+    for (int n = 0; n < N; ++n)
+    for (int c = 0; c < C; ++c)
+    for (int oy = 0; oy < OH; ++oy) {
+        int hstart = oy * p->stride_h - p->pad_top;
+        int hend = hstart + p->pool_h;
+        if (hend > H + p->pad_bottom) hend = H + p->pad_bottom;          /* :194 */
+        int height = hend - hstart;
+        int hclamped = clamp_range(&hstart, &hend, H);
+        for (int ox = 0; ox < OW; ++ox) {
+            int wstart = ox * p->stride_w - p->pad_left;
+            int wend = wstart + p->pool_w;
+            if (wend > W + p->pad_right) wend = W + p->pad_right;        /* :206 */
+            float result = p->pool_type == 0 ? -3.402823466e+38f : 0.0f;
+            float area = (float)(height * (wend - wstart));              /* :209 */
+            int64_t oi = (((int64_t)n * OH + oy) * OW + ox) * C + c;
+            /* window entirely inside the padding: 0 by convention, :216-241 (OnPaddingOnly) */
+            if ((hend <= 0 || hstart > H) || (wend <= 0 || wstart > W)) {
+                store_f(&p->y, oi, 0.0f);
+                continue;
+            }
+            hclamped |= clamp_range(&wstart, &wend, W);                  /* :243 (sticky) */
+            if (hclamped && p->padding_method == 1)                      /* Exclude, :245-250 */
+                area = (float)((hend - hstart) * (wend - wstart));
+            for (int iy = hstart; iy < hend; ++iy)
+            for (int ix = wstart; ix < wend; ++ix) {
+                float v = load_f(&p->x, (((int64_t)n * H + iy) * W + ix) * C + c);
+                if (p->pool_type == 0) { if (v > result) result = v; }
+                else if (p->pool_type == 1) { volatile float s = result + v; result = s; }
+                else { volatile float sq = v * v; volatile float s = result + sq; result = s; }
+            }
+            if (p->pool_type == 1) { volatile float q = result / area; result = q; }
+            else if (p->pool_type == 2) { volatile float q = result / area; result = sqrtf(q); }
+            store_f(&p->y, oi, result);
+        }
+    }
+    return 0;
+}
+
+/* ---- Mean over H,W, Reduce.cpp:68-173 --------------------------------------------------------- */
+
+int oracle_mean_hw_q8(const b200k_mean_params* p)
+{
+    const int N = p->n, H = p->h, W = p->wd, C = p->c;
+    if (!p->x.data || !p->y.data) return B200K_E_INVALID;
+    for (int n = 0; n < N; ++n)
+    for (int c = 0; c < C; ++c) {
+        float acc = 0.0f;
+        for (int i = 0; i < H * W; ++i) {          /* row-major visit order == h, then w */
+            volatile float s = acc + load_f(&p->x, ((int64_t)n * H * W + i) * C + c);
+            acc = s;
+        }
+        volatile float m = acc / (float)(H * W);
+        store_f(&p->y, (int64_t)n * C + c, m);
+    }
+    return 0;
+}
+
+/* ---- ElementwiseBinary, RefElementwiseBinaryWorkload.cpp:27-132 + Broadcast.hpp:13-104 ------- */
+
+int oracle_eltwise_q8(const b200k_eltwise_params* p)
+{
+    int sa[4], sb[4], so[4], da[4] = {1,1,1,1}, db[4] = {1,1,1,1}, dout[4] = {1,1,1,1};
+    if (p->rank < 1 || p->rank > 4) return B200K_E_INVALID;
+    for (int i = 0; i < p->rank; ++i) {
+        da[4 - p->rank + i] = p->shape_a[i];
+        db[4 - p->rank + i] = p->shape_b[i];
+        dout[4 - p->rank + i] = p->shape_out[i];
+    }
+    int64_t ta = 1, tb = 1, to = 1;
+    for (int i = 3; i >= 0; --i) {
+        sa[i] = da[i] == 1 ? 0 : (int)ta;  ta *= da[i];
+        sb[i] = db[i] == 1 ? 0 : (int)tb;  tb *= db[i];
+        so[i] = (int)to;                   to *= dout[i];
+    }
+    for (int i0 = 0; i0 < dout[0]; ++i0)
+    for (int i1 = 0; i1 < dout[1]; ++i1)
+    for (int i2 = 0; i2 < dout[2]; ++i2)
+    for (int i3 = 0; i3 < dout[3]; ++i3) {
+        int64_t ia = (int64_t)i0 * sa[0] + (int64_t)i1 * sa[1] + (int64_t)i2 * sa[2] + (int64_t)i3 * sa[3];
+        int64_t ib = (int64_t)i0 * sb[0] + (int64_t)i1 * sb[1] + (int64_t)i2 * sb[2] + (int64_t)i3 * sb[3];
+        int64_t io = (int64_t)i0 * so[0] + (int64_t)i1 * so[1] + (int64_t)i2 * so[2] + (int64_t)i3 * so[3];
+        float a = load_f(&p->a, ia), b = load_f(&p->b, ib);
+        volatile float r;
+        switch (p->op) {
+            case 0: r = a + b; break;
+            case 1: r = a / b; break;
+            case 2: r = a > b ? a : b; break;
+            case 3: r = a < b ? a : b; break;
+            case 4: r = a * b; break;
+            case 5: r = a - b; break;
+            case 6: { volatile float d = a - b; r = d * d; break; }
+            default: return B200K_E_INVALID;
+        }
+        if (p->out.dtype == B200K_F32) { ((float*)p->out.data)[io] = r; continue; }
+        int32_t q = quantize_f(r, p->out.scale, p->out.zero_point, p->out.dtype);
+        store_q((void*)p->out.data, p->out.dtype, io, clampi(q, p->clamp_lo, p->clamp_hi));
+    }
+    return 0;
+}
+
+/* ---- Activation, Activation.cpp:13-119 ---------------------------------------------------------- */
+
+static float activation_f(float in, int fn, float a, float b)
+{
+    switch (fn) {
+        case 0:  return 1.f / (1.f + expf(-in));
+        case 1:  return a * tanhf(b * in);
+        case 2:  { volatile float t = a * in; return t + b; }
+        case 3:  return in > 0.f ? in : 0.f;
+        case 4:  { float t = in > b ? in : b; return t < a ? t : a; }
+        case 5:  return logf(1.0f + expf(in));
+        case 6:  return in > 0.0f ? in : (in * a);
+        case 7:  return in < 0 ? -in : in;
+        case 8:  return sqrtf(in);
+        case 9:  return in * in;
+        case 10: return (in >= 0) ? in : a * (expf(in) - 1);
+        case 11: { volatile float t = in + 3; float r = t > 0.0f ? t : 0.0f; r = r < 6.0f ? r : 6.0f;
+                   volatile float m = in * r; return m / 6; }
+        default: return NAN;
+    }
+}
+
+int oracle_activation_q8(const b200k_activation_params* p)
+{
+    if (!p->x.data || !p->y.data || p->function < 0 || p->function > 11) return B200K_E_INVALID;
+    for (int64_t i = 0; i < p->count; ++i)
+        store_f(&p->y, i, activation_f(load_f(&p->x, i), p->function, p->a, p->b));
+    return 0;
+}
+
+/* ---- Softmax, Softmax.cpp:17-70 --------------------------------------------------------------- */
+
+int oracle_softmax_q8(const b200k_softmax_params* p)
+{
+    if (!p->x.data || !p->y.data) return B200K_E_INVALID;
+    for (int o = 0; o < p->outer; ++o)
+    for (int in = 0; in < p->inner; ++in) {
+        int64_t base = (int64_t)o * p->axis_size * p->inner + in;
+        float mx = -3.402823466e+38f;
+        for (int i = 0; i < p->axis_size; ++i) {
+            float v = load_f(&p->x, base + (int64_t)i * p->inner);
+            if (v > mx) mx = v;
+        }
+        float sum = 0.0f;
+        for (int i = 0; i < p->axis_size; ++i) {
+            volatile float d = load_f(&p->x, base + (int64_t)i * p->inner) - mx;
+            volatile float t = d * p->beta;
+            volatile float s = sum + expf(t);
+            sum = s;
+        }
+        for (int i = 0; i < p->axis_size; ++i) {
+            volatile float d = load_f(&p->x, base + (int64_t)i * p->inner) - mx;
+            volatile float t = d * p->beta;
+            volatile float r = expf(t) / sum;
+            store_f(&p->y, base + (int64_t)i * p->inner, r);
+        }
+    }
+    return 0;
+}
+
+/* ---- Quantize / Dequantize / requantize, RefQuantizeWorkload.cpp:14-45, Dequantize.cpp:11-28 - */
+
+int oracle_convert_q(const b200k_convert_params* p)
+{
+    if (!p->x.data || !p->y.data) return B200K_E_INVALID;
+    for (int64_t i = 0; i < p->count; ++i) store_f(&p->y, i, load_f(&p->x, i));
+    return 0;
+}
+
+/* ---- QLstm, RefQLstmWorkload.cpp:46-541 with LstmUtils.cpp:16-256 ------------------------------
+ * A step-by-step restatement: every Encoder::Set / Decoder::Get of the reference is one
+ * quantize_f / dequantize_i here, in the reference's order, including the re-quantisation of the
+ * int16 gate accumulators after every multiply-accumulate (LstmUtils.cpp:87-111) and the scale
+ * switches on the gate buffers around layer normalisation (RefQLstmWorkload.cpp:331-364). */
+
+static int16_t q16(float v, float scale, int32_t zp) { return (int16_t)quantize_f(v, scale, zp, B200K_S16); }
+static float   d16(int16_t q, float scale, int32_t zp) { return dequantize_i(q, scale, zp); }
+
+/* MatrixBatchVectorMultiplyAccumulate, LstmUtils.cpp:87-111: out = Q(out + w * x) per element of K */
+static void matvec_acc(const int8_t* w, float sw, int rows, int cols, const int8_t* x, float sx, int zx,
+                       int batch, int16_t* out, float so, int zo)
+{
+    #pragma omp parallel for collapse(2) schedule(static)
+    for (int b = 0; b < batch; ++b)
+    for (int r = 0; r < rows; ++r) {
+        int16_t acc = out[b * rows + r];
+        for (int c = 0; c < cols; ++c) {
+            volatile float wf = dequantize_i(w[r * cols + c], sw, 0);
+            volatile float xf = dequantize_i(x[b * cols + c], sx, zx);
+            volatile float p = wf * xf;
+            volatile float s = d16(acc, so, zo) + p;
+            acc = q16(s, so, zo);
+        }
+        out[b * rows + r] = acc;
+    }
+}
+
+/* one gate after the mat-vecs: optional peephole, optional layer norm, activation
+ * (RefQLstmWorkload.cpp:321-364 for the input gate; the other gates repeat the pattern) */
+static void gate_post(const b200k_qlstm_params* p, int16_t* gate, float s_int,
+                      const int16_t* peep, float s_peep, const int16_t* cell, float s_cell,
+                      const int16_t* lnw, float s_lnw, const int32_t* bias, float s_bias, int tanh_act)
+{
+    const int B = p->batch, U = p->num_units;
+    float s = s_int;
+    if (peep) {                                    /* VectorBatchVectorCwiseProductAccumulate, :126-144 */
+        for (int b = 0; b < B; ++b) for (int u = 0; u < U; ++u) {
+            volatile float pr = d16(peep[u], s_peep, 0) * d16(cell[b * U + u], s_cell, 0);
+            volatile float t = d16(gate[b * U + u], s, 0) + pr;
+            gate[b * U + u] = q16(t, s, 0);
+        }
+    }
+    if (lnw) {
+        volatile float s_ln0 = p->input_scale * s_lnw;
+        volatile float s_ln = s_ln0 * 1024;
+        for (int b = 0; b < B; ++b) {             /* MeanStddevNormalization, :40-74 */
+            int16_t* g = gate + b * U;
+            float sum = 0.0f, sum_sq = 0.0f;
+            for (int i = 0; i < U; ++i) {
+                float v = d16(g[i], s, 0);
+                volatile float a = sum + v; sum = a;
+                volatile float sq = v * v;
+                volatile float c = sum_sq + sq; sum_sq = c;
+            }
+            volatile float mean = sum / (float)U;
+            volatile float ex2 = sum_sq / (float)U;
+            volatile float mm = mean * mean;
+            volatile float variance = ex2 - mm;
+            float stddev_inv;
+            if (variance == 0) stddev_inv = 1.0f / sqrtf(1e-8f);
+            else               stddev_inv = 1.0f / sqrtf(variance);
+            for (int i = 0; i < U; ++i) {
+                volatile float d = d16(g[i], s, 0) - mean;
+                volatile float n = d * stddev_inv;
+                g[i] = q16(n, s_ln, 0);
+            }
+        }
+        for (int b = 0; b < B; ++b) for (int u = 0; u < U; ++u) {   /* VectorBatchVectorCwiseProduct */
+            volatile float t = d16(lnw[u], s_lnw, 0) * d16(gate[b * U + u], s_ln, 0);
+            gate[b * U + u] = q16(t, s_ln, 0);
+        }
+        for (int b = 0; b < B; ++b) for (int u = 0; u < U; ++u) {   /* VectorBatchVectorAdd, bias */
+            volatile float bf = (float)bias[u] * s_bias;
+            volatile float t = d16(gate[b * U + u], s_ln, 0) + bf;
+            gate[b * U + u] = q16(t, 1.f / 4096, 0);
+        }
+        s = 1.f / 4096;
+    }
+    for (int i = 0; i < B * U; ++i) {               /* Activation, Activation.cpp:103-119 */
+        float v = d16(gate[i], s, 0);
+        float r = tanh_act ? 1.0f * tanhf(1.0f * v) : 1.f / (1.f + expf(-v));
+        gate[i] = q16(r, s_cell, 0);
+    }
+}
+
+int oracle_qlstm_step(const b200k_qlstm_params* p)
+{
+    const int B = p->batch, I = p->input_size, U = p->num_units, O = p->output_size;
+    const int cifg = p->w_i2i == NULL, peephole = p->w_c2f != NULL, ln = p->ln_f != NULL, proj = p->w_proj != NULL;
+    const float sc = p->cell_state_scale;
+    const size_t S = (size_t)B * U;
+    int16_t* gi = (int16_t*)calloc(S, 2); int16_t* gf = (int16_t*)calloc(S, 2);
+    int16_t* gc = (int16_t*)calloc(S, 2); int16_t* go = (int16_t*)calloc(S, 2);
+    int8_t* hidden = (int8_t*)malloc(S);
+    int16_t* out16 = (int16_t*)calloc((size_t)B * O, 2);
+    const int8_t* x = (const int8_t*)p->input; const int8_t* h = (const int8_t*)p->output_state_in;
+    const int16_t* cin = (const int16_t*)p->cell_state_in;
+    int16_t* cout = (int16_t*)p->cell_state_out;
+    int8_t* out = (int8_t*)p->output; int8_t* hout = (int8_t*)p->output_state_out;
+    if (!gi || !gf || !gc || !go || !hidden || !out16) return B200K_E_INVALID;
+    if (!proj && U != O) return B200K_E_INVALID;
+
+    /* input and recurrent mat-vecs, :289-319 */
+    if (!cifg) matvec_acc(p->w_i2i, p->s_i2i, U, I, x, p->input_scale, p->input_zp, B, gi, p->input_intermediate_scale, 0);
+    matvec_acc(p->w_i2f, p->s_i2f, U, I, x, p->input_scale, p->input_zp, B, gf, p->forget_intermediate_scale, 0);
+    matvec_acc(p->w_i2c, p->s_i2c, U, I, x, p->input_scale, p->input_zp, B, gc, p->cell_intermediate_scale, 0);
+    matvec_acc(p->w_i2o, p->s_i2o, U, I, x, p->input_scale, p->input_zp, B, go, p->output_intermediate_scale, 0);
+    if (!cifg) matvec_acc(p->w_r2i, p->s_r2i, U, O, h, p->output_state_scale, p->output_state_zp, B, gi, p->input_intermediate_scale, 0);
+    matvec_acc(p->w_r2f, p->s_r2f, U, O, h, p->output_state_scale, p->output_state_zp, B, gf, p->forget_intermediate_scale, 0);
+    matvec_acc(p->w_r2c, p->s_r2c, U, O, h, p->output_state_scale, p->output_state_zp, B, gc, p->cell_intermediate_scale, 0);
+    matvec_acc(p->w_r2o, p->s_r2o, U, O, h, p->output_state_scale, p->output_state_zp, B, go, p->output_intermediate_scale, 0);
+
+    if (!cifg)
+        gate_post(p, gi, p->input_intermediate_scale, peephole ? p->w_c2i : NULL, p->s_c2i, cin, sc,
+                  ln ? p->ln_i : NULL, p->s_lni, p->b_i, p->s_bi, 0);
+    gate_post(p, gf, p->forget_intermediate_scale, peephole ? p->w_c2f : NULL, p->s_c2f, cin, sc,
+              ln ? p->ln_f : NULL, p->s_lnf, p->b_f, p->s_bf, 0);
+    gate_post(p, gc, p->cell_intermediate_scale, NULL, 0.f, cin, sc,
+              ln ? p->ln_c : NULL, p->s_lnc, p->b_c, p->s_bc, 1);
+
+    /* cell state, :443-462 */
+    for (size_t i = 0; i < S; ++i) {
+        volatile float t = d16(gf[i], sc, 0) * d16(cin[i], sc, 0);
+        cout[i] = q16(t, sc, 0);
+    }
+    if (cifg) {
+        for (size_t i = 0; i < S; ++i) { volatile float t = 1.0f - d16(gf[i], sc, 0); gf[i] = q16(t, sc, 0); }
+    }
+    for (size_t i = 0; i < S; ++i) {
+        volatile float pr = d16(gc[i], sc, 0) * d16(cifg ? gf[i] : gi[i], sc, 0);
+        volatile float t = d16(cout[i], sc, 0) + pr;
+        cout[i] = q16(t, sc, 0);
+    }
+    if (p->cell_clip > 0.0f) {
+        for (size_t i = 0; i < S; ++i) {
+            float f = d16(cout[i], sc, 0);
+            float r = (p->cell_clip < f) ? p->cell_clip : f;
+            r = (-p->cell_clip > r) ? -p->cell_clip : r;
+            cout[i] = q16(r, sc, 0);
+        }
+    }
+    /* output gate (peephole reads the NEW cell state), :464-503 */
+    gate_post(p, go, p->output_intermediate_scale, peephole ? p->w_c2o : NULL, p->s_c2o, cout, sc,
+              ln ? p->ln_o : NULL, p->s_lno, p->b_o, p->s_bo, 0);
+    /* hidden = o * tanh(c), :505-511 */
+    for (size_t i = 0; i < S; ++i) {
+        float v = d16(cout[i], sc, 0);
+        gc[i] = q16(1.0f * tanhf(1.0f * v), sc, 0);
+    }
+    for (size_t i = 0; i < S; ++i) {
+        volatile float t = d16(go[i], sc, 0) * d16(gc[i], sc, 0);
+        hidden[i] = (int8_t)quantize_f(t, p->hidden_state_scale, p->hidden_state_zp, B200K_S8);
+    }
+    /* projection, :513-538 */
+    if (proj) {
+        if (p->b_proj)
+            for (int b = 0; b < B; ++b) for (int j = 0; j < O; ++j) {
+                volatile float bf = (float)p->b_proj[j] * p->s_bproj;
+                out16[b * O + j] = q16(bf, p->output_scale, p->output_zp);
+            }
+        matvec_acc(p->w_proj, p->s_proj, O, U, hidden, p->hidden_state_scale, p->hidden_state_zp, B,
+                   out16, p->output_scale, p->output_zp);
+        for (int i = 0; i < B * O; ++i)
+            out[i] = (int8_t)quantize_f(d16(out16[i], p->output_scale, p->output_zp), p->output_scale, p->output_zp, B200K_S8);
+        if (p->projection_clip > 0.0f)
+            for (int i = 0; i < B * O; ++i) {
+                float f = dequantize_i(out[i], p->output_scale, p->output_zp);
+                float r = (p->projection_clip < f) ? p->projection_clip : f;
+                r = (-p->projection_clip > r) ? -p->projection_clip : r;
+                out[i] = (int8_t)quantize_f(r, p->output_scale, p->output_zp, B200K_S8);
+            }
+    } else {
+        for (int i = 0; i < B * O; ++i)
+            out[i] = (int8_t)quantize_f(dequantize_i(hidden[i], p->hidden_state_scale, p->hidden_state_zp),
+                                        p->output_scale, p->output_zp, B200K_S8);
+    }
+    for (int i = 0; i < B * O; ++i)
+        hout[i] = (int8_t)quantize_f(dequantize_i(out[i], p->output_scale, p->output_zp),
+                                     p->output_state_scale, p->output_state_zp, B200K_S8);
+    free(gi); free(gf); free(gc); free(go); free(hidden); free(out16);
+    return 0;
+}

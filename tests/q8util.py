@@ -1,0 +1,357 @@
+"""Shared helpers for the parity tests.
+
+Three executors take the SAME parameter structs (include/b200k.h):
+  * ORACLE  — oracle/libq8oracle.so, the plain-C restatement (host pointers)
+  * CPUREF  — oracle/_ref/libarmnn_capi.so, the real CpuRef workloads of the reference (host pointers)
+  * GPU     — armnn_b200/libb200k.so, the product (device pointers, via torch for memory only)
+A test builds a case once (numpy arrays + geometry) and runs it on any of them.
+"""
+import ctypes as C
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from armnn_b200 import _abi  # noqa: E402
+
+NP_OF = {_abi.U8: np.uint8, _abi.S8: np.int8, _abi.S16: np.int16, _abi.S32: np.int32, _abi.F32: np.float32}
+RANGE = {_abi.U8: (0, 255), _abi.S8: (-128, 127), _abi.S16: (-32768, 32767)}
+
+ORACLE_PATH = os.path.join(ROOT, "oracle", "libq8oracle.so")
+CPUREF_PATH = os.path.join(ROOT, "oracle", "_ref", "libarmnn_capi.so")
+
+_oracle = None
+_cpuref = None
+
+
+def oracle():
+    global _oracle
+    if _oracle is None:
+        _oracle = C.CDLL(ORACLE_PATH)
+    return _oracle
+
+
+def have_cpuref():
+    return os.path.exists(CPUREF_PATH)
+
+
+def cpuref():
+    global _cpuref
+    if _cpuref is None:
+        _cpuref = C.CDLL(CPUREF_PATH)
+        _cpuref.cpuref_last_error.restype = C.c_char_p
+    return _cpuref
+
+
+def have_gpu():
+    try:
+        import torch
+        return torch.cuda.is_available()
+    except Exception:
+        return False
+
+
+class Host:
+    """numpy memory"""
+    name = "host"
+
+    def __init__(self):
+        self.keep = []
+
+    def inp(self, arr):
+        arr = np.ascontiguousarray(arr)
+        self.keep.append(arr)
+        return arr.ctypes.data
+
+    def out(self, shape, np_dtype):
+        a = np.zeros(shape, dtype=np_dtype)
+        self.keep.append(a)
+        return a, a.ctypes.data
+
+    def fetch(self, handle):
+        return handle
+
+
+class Cuda:
+    """torch CUDA memory (allocation and copies only)"""
+    name = "cuda"
+
+    def __init__(self):
+        import torch
+        self.torch = torch
+        self.keep = []
+
+    def inp(self, arr):
+        t = self.torch.from_numpy(np.ascontiguousarray(arr)).cuda()
+        self.keep.append(t)
+        return t.data_ptr()
+
+    def out(self, shape, np_dtype):
+        t = self.torch.zeros(tuple(shape), dtype=getattr(self.torch, np.dtype(np_dtype).name), device="cuda")
+        self.keep.append(t)
+        return t, t.data_ptr()
+
+    def fetch(self, handle):
+        self.torch.cuda.synchronize()
+        return handle.cpu().numpy()
+
+
+def qt(mem, arr, dtype, scale=1.0, zp=0, scales=None):
+    t = _abi.QTensor()
+    t.data = mem.inp(arr.astype(NP_OF[dtype], copy=False)) if arr is not None else None
+    t.dtype = dtype
+    t.scale = float(scale)
+    t.zero_point = int(zp)
+    t.scales = mem.inp(np.asarray(scales, dtype=np.float32)) if scales is not None else None
+    return t
+
+
+def qt_out(mem, shape, dtype, scale=1.0, zp=0):
+    handle, ptr = mem.out(shape, NP_OF[dtype])
+    t = _abi.QTensor()
+    t.data = ptr
+    t.dtype = dtype
+    t.scale = float(scale)
+    t.zero_point = int(zp)
+    t.scales = None
+    return t, handle
+
+
+def activation_clamp(kind, a, b, scale, zp, dtype):
+    lo, hi = C.c_int32(), C.c_int32()
+    rc = oracle().oracle_activation_clamp(C.c_int(kind), C.c_float(a), C.c_float(b), C.c_float(scale),
+                                          C.c_int32(zp), C.c_int32(dtype), C.byref(lo), C.byref(hi))
+    assert rc == 0
+    return lo.value, hi.value
+
+
+def out_size(i, k, s, pb, pa, d=1):
+    return (i + pb + pa - (d * (k - 1) + 1)) // s + 1
+
+
+# --------------------------------------------------------------------------------------------------
+# Cases.  Each case object knows how to fill the parameter struct for a memory space and how to call
+# each executor.
+# --------------------------------------------------------------------------------------------------
+
+class ConvCase:
+    """Convolution2d / DepthwiseConvolution2d (NHWC, weights OHWI or [1,H,W,O])."""
+
+    def __init__(self, x, w, bias, x_q, w_q, y_q, stride=(1, 1), pad=(0, 0, 0, 0), dil=(1, 1), act=(0, 0.0, 0.0),
+                 depthwise=False, w_scales=None, b_scale=None, b_scales=None, x_dtype=_abi.S8, w_dtype=_abi.S8,
+                 y_dtype=_abi.S8):
+        self.x, self.w, self.bias = x, w, bias
+        self.x_q, self.w_q, self.y_q = x_q, w_q, y_q           # (scale, zp)
+        self.w_scales, self.b_scale, self.b_scales = w_scales, b_scale, b_scales
+        self.stride, self.pad, self.dil, self.act = stride, pad, dil, act   # pad = (top, bottom, left, right)
+        self.depthwise = depthwise
+        self.x_dtype, self.w_dtype, self.y_dtype = x_dtype, w_dtype, y_dtype
+        n, h, wd, c = x.shape
+        if depthwise:
+            _, kh, kw, oc = w.shape
+        else:
+            oc, kh, kw, _ = w.shape
+        self.geom = (n, h, wd, c, oc, kh, kw)
+        self.oh = out_size(h, kh, stride[0], pad[0], pad[1], dil[0])
+        self.ow = out_size(wd, kw, stride[1], pad[2], pad[3], dil[1])
+
+    def params(self, mem, want_acc=False, algo=0):
+        n, h, wd, c, oc, kh, kw = self.geom
+        p = _abi.Conv2dParams()
+        p.x = qt(mem, self.x, self.x_dtype, *self.x_q)
+        p.w = qt(mem, self.w, self.w_dtype, self.w_q[0], self.w_q[1], self.w_scales)
+        if self.bias is not None:
+            p.bias = qt(mem, self.bias, _abi.S32, self.b_scale if self.b_scale is not None else 1.0, 0, self.b_scales)
+        p.y, y = qt_out(mem, (n, self.oh, self.ow, oc), self.y_dtype, *self.y_q)
+        p.n, p.h, p.wd, p.c, p.oh, p.ow, p.oc, p.kh, p.kw = n, h, wd, c, self.oh, self.ow, oc, kh, kw
+        p.stride_h, p.stride_w = self.stride
+        p.pad_top, p.pad_left = self.pad[0], self.pad[2]
+        p.dil_h, p.dil_w = self.dil
+        p.clamp_lo, p.clamp_hi = activation_clamp(self.act[0], self.act[1], self.act[2], self.y_q[0], self.y_q[1], self.y_dtype)
+        acc = None
+        if want_acc:
+            acc, ptr = mem.out((n, self.oh, self.ow, oc), np.int32)
+            p.acc_out = ptr
+        p.algo = algo
+        return p, y, acc
+
+    def run_oracle(self, want_acc=True):
+        mem = Host()
+        p, y, acc = self.params(mem, want_acc)
+        fn = oracle().oracle_dwconv2d_q8 if self.depthwise else oracle().oracle_conv2d_q8
+        assert fn(C.byref(p)) == 0
+        return y, acc
+
+    def run_cpuref(self):
+        mem = Host()
+        p, y, _ = self.params(mem)
+        rc = cpuref().cpuref_conv2d_q8(C.byref(p), C.c_int(int(self.depthwise)), C.c_int(self.act[0]),
+                                       C.c_float(self.act[1]), C.c_float(self.act[2]))
+        assert rc == 0, cpuref().cpuref_last_error().decode()
+        return y
+
+    def run_gpu(self, want_acc=True, algo=0):
+        from armnn_b200 import lib
+        mem = Cuda()
+        p, y, acc = self.params(mem, want_acc, algo)
+        lib.call("dwconv2d_q8" if self.depthwise else "conv2d_q8", p)
+        return mem.fetch(y), (mem.fetch(acc) if acc is not None else None)
+
+
+def random_conv_case(seed, n, h, wd, c, oc, kh, kw, stride=(1, 1), pad=(0, 0, 0, 0), dil=(1, 1), act=(0, 0., 0.),
+                     depthwise=False, x_dtype=_abi.S8, w_dtype=_abi.S8, y_dtype=_abi.S8, per_axis=True,
+                     x_q=(0.02, -3), y_scale=None, y_zp=None, bias=True, depth_multiplier=1):
+    """Seeded synthetic conv in the style of the benchmark configs: uniform activations over the
+    whole type range, weights uniform, per-output-channel scales uniform in [0.001, 0.01], int32 bias
+    uniform in [-1000, 1000] with scale sx * sw[c].  The output scale defaults to one that leaves
+    most outputs unsaturated so that the comparison is not vacuous."""
+    rng = np.random.default_rng(seed)
+    lo, hi = RANGE[x_dtype]
+    x = rng.integers(lo, hi + 1, size=(n, h, wd, c)).astype(NP_OF[x_dtype])
+    if depthwise:
+        oc = c * depth_multiplier
+        wshape = (1, kh, kw, oc)
+    else:
+        wshape = (oc, kh, kw, c)
+    if w_dtype == _abi.S8:
+        w = rng.integers(-127, 128, size=wshape).astype(np.int8)
+        w_zp = 0
+    else:
+        w = rng.integers(0, 256, size=wshape).astype(np.uint8)
+        w_zp = int(rng.integers(100, 156))
+    if per_axis and w_dtype == _abi.S8:
+        w_scales = rng.uniform(0.001, 0.01, size=oc).astype(np.float32)
+        w_q = (1.0, 0)
+        b_scales = (np.float32(x_q[0]) * w_scales).astype(np.float32)
+        b_scale = None
+    else:
+        w_scales = None
+        w_q = (float(np.float32(rng.uniform(0.001, 0.01))), w_zp)
+        b_scales = None
+        b_scale = float(np.float32(x_q[0]) * np.float32(w_q[0]))
+    b = rng.integers(-1000, 1001, size=oc).astype(np.int32) if bias else None
+    if y_scale is None:
+        k = kh * kw * (1 if depthwise else c)
+        mean_sw = float(np.mean(w_scales)) if w_scales is not None else w_q[0]
+        std = x_q[0] * mean_sw * 74.0 * 74.0 * np.sqrt(k)       # uniform int8 std ~ 74
+        y_scale = float(np.float32(std * 3.0 / 127.0))
+    if y_zp is None:
+        y_zp = 0 if y_dtype == _abi.S8 else 128
+    return ConvCase(x, w, b, x_q, w_q, (y_scale, y_zp), stride, pad, dil, act, depthwise, w_scales, b_scale, b_scales,
+                    x_dtype, w_dtype, y_dtype)
+
+
+class FcCase:
+    def __init__(self, x, w, bias, x_q, w_q, y_q, transpose_w=True, w_scales=None, b_scale=None, b_scales=None,
+                 act=(0, 0., 0.), x_dtype=_abi.S8, w_dtype=_abi.S8, y_dtype=_abi.S8):
+        self.__dict__.update(locals())
+        self.m, self.k = x.shape
+        self.n = w.shape[0] if transpose_w else w.shape[1]
+
+    def params(self, mem, want_acc=False, algo=0):
+        p = _abi.FcParams()
+        p.x = qt(mem, self.x, self.x_dtype, *self.x_q)
+        p.w = qt(mem, self.w, self.w_dtype, self.w_q[0], self.w_q[1], self.w_scales)
+        if self.bias is not None:
+            p.bias = qt(mem, self.bias, _abi.S32, self.b_scale if self.b_scale is not None else 1.0, 0, self.b_scales)
+        p.y, y = qt_out(mem, (self.m, self.n), self.y_dtype, *self.y_q)
+        p.m, p.k, p.n, p.transpose_w = self.m, self.k, self.n, int(self.transpose_w)
+        p.clamp_lo, p.clamp_hi = activation_clamp(self.act[0], self.act[1], self.act[2], self.y_q[0], self.y_q[1], self.y_dtype)
+        acc = None
+        if want_acc:
+            acc, ptr = mem.out((self.m, self.n), np.int32)
+            p.acc_out = ptr
+        p.algo = algo
+        return p, y, acc
+
+    def run_oracle(self, want_acc=True):
+        mem = Host()
+        p, y, acc = self.params(mem, want_acc)
+        assert oracle().oracle_fully_connected_q8(C.byref(p)) == 0
+        return y, acc
+
+    def run_cpuref(self):
+        mem = Host()
+        p, y, _ = self.params(mem)
+        rc = cpuref().cpuref_fully_connected_q8(C.byref(p), C.c_int(self.act[0]), C.c_float(self.act[1]), C.c_float(self.act[2]))
+        assert rc == 0, cpuref().cpuref_last_error().decode()
+        return y
+
+    def run_gpu(self, want_acc=True, algo=0):
+        from armnn_b200 import lib
+        mem = Cuda()
+        p, y, acc = self.params(mem, want_acc, algo)
+        lib.call("fully_connected_q8", p)
+        return mem.fetch(y), (mem.fetch(acc) if acc is not None else None)
+
+
+def random_fc_case(seed, m, k, n, transpose_w=True, x_q=(0.03, 5), per_axis=True, x_dtype=_abi.S8, w_dtype=_abi.S8,
+                   y_dtype=_abi.S8, act=(0, 0., 0.)):
+    rng = np.random.default_rng(seed)
+    lo, hi = RANGE[x_dtype]
+    x = rng.integers(lo, hi + 1, size=(m, k)).astype(NP_OF[x_dtype])
+    wshape = (n, k) if transpose_w else (k, n)
+    if w_dtype == _abi.S8:
+        w = rng.integers(-127, 128, size=wshape).astype(np.int8)
+        w_zp = 0
+    else:
+        w = rng.integers(0, 256, size=wshape).astype(np.uint8)
+        w_zp = int(rng.integers(100, 156))
+    if per_axis and w_dtype == _abi.S8:
+        w_scales = rng.uniform(0.001, 0.01, size=n).astype(np.float32)
+        w_q = (1.0, 0)
+        b_scales = (np.float32(x_q[0]) * w_scales).astype(np.float32)
+        b_scale = None
+        mean_sw = float(np.mean(w_scales))
+    else:
+        w_scales, b_scales = None, None
+        w_q = (float(np.float32(rng.uniform(0.001, 0.01))), w_zp)
+        b_scale = float(np.float32(x_q[0]) * np.float32(w_q[0]))
+        mean_sw = w_q[0]
+    b = rng.integers(-1000, 1001, size=n).astype(np.int32)
+    std = x_q[0] * mean_sw * 74.0 * 74.0 * np.sqrt(k)
+    y_q = (float(np.float32(std * 3.0 / 127.0)), 0 if y_dtype == _abi.S8 else 128)
+    return FcCase(x, w, b, x_q, w_q, y_q, transpose_w, w_scales, b_scale, b_scales, act, x_dtype, w_dtype, y_dtype)
+
+
+class SimpleCase:
+    """A case defined by a function that fills a params struct from a memory space."""
+
+    def __init__(self, entry, build, cpuref_extra=()):
+        self.entry, self.build, self.cpuref_extra = entry, build, cpuref_extra
+
+    def run_oracle(self):
+        mem = Host()
+        p, outs = self.build(mem)
+        rc = getattr(oracle(), "oracle_" + self.entry)(C.byref(p))
+        assert rc == 0, "oracle_%s returned %d" % (self.entry, rc)
+        return outs
+
+    def run_cpuref(self):
+        mem = Host()
+        p, outs = self.build(mem)
+        rc = getattr(cpuref(), "cpuref_" + self.entry)(C.byref(p), *self.cpuref_extra)
+        assert rc == 0, cpuref().cpuref_last_error().decode()
+        return outs
+
+    def run_gpu(self):
+        from armnn_b200 import lib
+        mem = Cuda()
+        p, outs = self.build(mem)
+        lib.call(self.entry, p)
+        return [mem.fetch(o) for o in outs]
+
+
+def diff_stats(a, b):
+    d = a.astype(np.int64) - b.astype(np.int64)
+    return {"max_abs": int(np.abs(d).max()) if d.size else 0,
+            "mismatch_frac": float(np.mean(d != 0)) if d.size else 0.0}
+
+
+def saturation(y, dtype):
+    lo, hi = RANGE[dtype]
+    return float(np.mean((y == lo) | (y == hi)))
