@@ -104,7 +104,6 @@ class QLstmParams(C.Structure):
         ("input_intermediate_scale", _F), ("forget_intermediate_scale", _F),
         ("cell_intermediate_scale", _F), ("output_intermediate_scale", _F),
         ("hidden_state_scale", _F), ("hidden_state_zp", _I),
-        ("scratch", _P), ("scratch_bytes", C.c_size_t),
     ]
 
 
@@ -127,7 +126,6 @@ KERNEL_ENTRY_POINTS = {
 EXPORTED_SYMBOLS = ["b200k_" + k for k in KERNEL_ENTRY_POINTS] + [
     "b200k_device_open", "b200k_device_count", "b200k_last_error", "b200k_version",
     "b200k_activation_clamp", "b200k_conv2d_pack_bytes", "b200k_conv2d_pack",
-    "b200k_qlstm_scratch_bytes",
 ]
 
 
@@ -149,6 +147,4 @@ def declare_product(lib):
     lib.b200k_conv2d_pack_bytes.restype = C.c_size_t
     lib.b200k_conv2d_pack.argtypes = [C.POINTER(Conv2dParams), C.c_void_p, C.c_void_p]
     lib.b200k_conv2d_pack.restype = C.c_int
-    lib.b200k_qlstm_scratch_bytes.argtypes = [C.c_int32] * 3
-    lib.b200k_qlstm_scratch_bytes.restype = C.c_size_t
     return lib

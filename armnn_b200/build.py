@@ -20,7 +20,7 @@ PLUGIN_DIR = os.path.join(HERE, "backend")
 PLUGIN = os.path.join(PLUGIN_DIR, "Nv_B200Acc_backend.so")
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-              "-fmad=false", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
+              "-fmad=false", "-Xcompiler", "-fPIC"]
 
 
 def _newer(target, sources):
@@ -59,7 +59,7 @@ def build_kernels(force=False, verbose=False):
         if p.returncode != 0:
             raise RuntimeError("nvcc failed:\n%s\n%s" % (" ".join(cmd), out))
     if force or procs or _newer(LIB, objs):
-        _run(["nvcc", "-shared", "-o", LIB] + objs + ["-lcuda"], verbose)
+        _run(["nvcc", "-shared", "-o", LIB] + objs, verbose)
     return LIB
 
 

@@ -1,0 +1,730 @@
+"""Host-side mirror of the Arm NN flow for the B200Acc backend:
+
+    INetwork (Add*Layer, slots, TensorInfo)  ->  Optimize(network, ["B200Acc"])  ->
+    IRuntime.LoadNetwork  ->  LoadedNetwork.EnqueueWorkload(inputs, outputs)
+
+Names, argument meaning and error behaviour follow the reference (include/armnn/INetwork.hpp,
+include/armnn/IRuntime.hpp, src/armnn/Network.cpp:2026-2271, src/armnn/LoadedNetwork.cpp:783-981 of the
+Arm NN tree): weights and biases are Constant layers feeding input slots 1 and 2, activations are separate
+layers that Optimize fuses into the producer when the quantisation allows it (what Neon/CL do in
+OptimizeSubgraphView, src/backends/cl/ClBackend.cpp:326-390), every layer must be supported by the backend or
+Optimize raises, and one workload per layer is enqueued on a CUDA stream.  Each workload is one call of the
+C ABI in include/b200k.h; torch is used for device memory, streams and events only.
+
+The C++ plugin under armnn_b200/backend/ implements the same decisions against the real IBackendInternal
+interface; this module is what the tests and the benchmark drive when no Arm NN runtime is around.
+"""
+import ctypes
+from enum import IntEnum
+
+import numpy as np
+
+from . import _abi, lib
+
+
+class DataType(IntEnum):            # include/armnn/Types.hpp:48-60
+    Float32 = 1
+    QAsymmU8 = 2
+    Signed32 = 3
+    QSymmS16 = 5
+    QSymmS8 = 6
+    QAsymmS8 = 7
+
+
+class ActivationFunction(IntEnum):  # include/armnn/Types.hpp:86-101
+    Sigmoid = 0
+    TanH = 1
+    Linear = 2
+    ReLu = 3
+    BoundedReLu = 4
+    SoftReLu = 5
+    LeakyReLu = 6
+    Abs = 7
+    Sqrt = 8
+    Square = 9
+    Elu = 10
+    HardSwish = 11
+
+
+class BinaryOperation(IntEnum):     # include/armnn/Types.hpp:138-149
+    Add = 0
+    Div = 1
+    Maximum = 2
+    Minimum = 3
+    Mul = 4
+    Sub = 5
+    SqDiff = 6
+
+
+class PoolingAlgorithm(IntEnum):
+    Max = 0
+    Average = 1
+    L2 = 2
+
+
+class PaddingMethod(IntEnum):
+    IgnoreValue = 0
+    Exclude = 1
+
+
+_ABI_DTYPE = {DataType.Float32: _abi.F32, DataType.QAsymmU8: _abi.U8, DataType.Signed32: _abi.S32,
+              DataType.QSymmS16: _abi.S16, DataType.QSymmS8: _abi.S8, DataType.QAsymmS8: _abi.S8}
+_NP_DTYPE = {DataType.Float32: np.float32, DataType.QAsymmU8: np.uint8, DataType.Signed32: np.int32,
+             DataType.QSymmS16: np.int16, DataType.QSymmS8: np.int8, DataType.QAsymmS8: np.int8}
+
+
+class InvalidArgumentException(ValueError):
+    """armnn::InvalidArgumentException"""
+
+
+class BackendUnavailableException(RuntimeError):
+    """armnn::BackendUnavailableException"""
+
+
+class TensorInfo:
+    """armnn::TensorInfo: shape, data type and per-tensor or per-axis quantisation."""
+
+    def __init__(self, shape, dtype, scale=1.0, offset=0, scales=None, quant_dim=None, constant=False):
+        self.shape = tuple(int(s) for s in shape)
+        self.dtype = DataType(dtype)
+        self.scale = float(np.float32(scale))
+        self.offset = int(offset)
+        self.scales = None if scales is None else np.asarray(scales, dtype=np.float32)
+        self.quant_dim = quant_dim
+        self.constant = constant
+
+    def GetNumElements(self):
+        return int(np.prod(self.shape)) if self.shape else 1
+
+    def GetNumBytes(self):
+        return self.GetNumElements() * np.dtype(_NP_DTYPE[self.dtype]).itemsize
+
+    def HasPerAxisQuantization(self):
+        return self.scales is not None
+
+    def same_quantization(self, other):
+        return (self.dtype == other.dtype and self.scales is None and other.scales is None and
+                self.scale == other.scale and self.offset == other.offset)
+
+    def __repr__(self):
+        return "TensorInfo(%s, %s, scale=%g, offset=%d%s)" % (self.shape, self.dtype.name, self.scale, self.offset,
+                                                               ", per-axis" if self.scales is not None else "")
+
+
+class OutputSlot:
+    def __init__(self, layer, index):
+        self.layer, self.index, self.info, self.connections = layer, index, None, []
+
+    def SetTensorInfo(self, info):
+        self.info = info
+
+    def GetTensorInfo(self):
+        return self.info
+
+    def Connect(self, input_slot):
+        if input_slot.source is not None:
+            raise InvalidArgumentException("input slot %d of %s is already connected" % (input_slot.index, input_slot.layer.name))
+        input_slot.source = self
+        self.connections.append(input_slot)
+
+
+class InputSlot:
+    def __init__(self, layer, index):
+        self.layer, self.index, self.source = layer, index, None
+
+
+class Layer:
+    def __init__(self, ltype, name, n_in, n_out, desc=None):
+        self.type, self.name, self.desc = ltype, name or ltype, dict(desc or {})
+        self.inputs = [InputSlot(self, i) for i in range(n_in)]
+        self.outputs = [OutputSlot(self, i) for i in range(n_out)]
+        self.fused_activation = None       # (function, a, b) set by Optimize
+        self.const_data = None             # Constant layers: numpy array
+
+    def GetInputSlot(self, i):
+        return self.inputs[i]
+
+    def GetOutputSlot(self, i=0):
+        return self.outputs[i]
+
+    def GetName(self):
+        return self.name
+
+
+class INetwork:
+    """Graph builder; one Add*Layer per reference method used on the hot path (include/armnn/INetwork.hpp)."""
+
+    def __init__(self):
+        self.layers = []
+
+    @staticmethod
+    def Create():
+        return INetwork()
+
+    def _add(self, layer):
+        self.layers.append(layer)
+        return layer
+
+    def AddInputLayer(self, binding_id, name=None):
+        return self._add(Layer("Input", name, 0, 1, {"id": binding_id}))
+
+    def AddOutputLayer(self, binding_id, name=None):
+        return self._add(Layer("Output", name, 1, 0, {"id": binding_id}))
+
+    def AddConstantLayer(self, data, info, name=None):
+        info.constant = True
+        layer = self._add(Layer("Constant", name, 0, 1))
+        layer.const_data = np.ascontiguousarray(np.asarray(data).astype(_NP_DTYPE[info.dtype], copy=False)).reshape(info.shape)
+        layer.outputs[0].SetTensorInfo(info)
+        return layer
+
+    def AddConvolution2dLayer(self, stride=(1, 1), pad=(0, 0, 0, 0), dilation=(1, 1), bias_enabled=True, name=None):
+        """pad = (top, bottom, left, right); NHWC; inputs: 0 data, 1 weights [O,H,W,I], 2 bias."""
+        return self._add(Layer("Convolution2d", name, 3 if bias_enabled else 2, 1,
+                               {"stride": stride, "pad": pad, "dilation": dilation, "bias": bias_enabled}))
+
+    def AddDepthwiseConvolution2dLayer(self, stride=(1, 1), pad=(0, 0, 0, 0), dilation=(1, 1), bias_enabled=True, name=None):
+        """weights [1,H,W,I*M]"""
+        return self._add(Layer("DepthwiseConvolution2d", name, 3 if bias_enabled else 2, 1,
+                               {"stride": stride, "pad": pad, "dilation": dilation, "bias": bias_enabled}))
+
+    def AddFullyConnectedLayer(self, transpose_weights=False, bias_enabled=True, name=None):
+        return self._add(Layer("FullyConnected", name, 3 if bias_enabled else 2, 1,
+                               {"transpose": transpose_weights, "bias": bias_enabled}))
+
+    def AddBatchMatMulLayer(self, transpose_x=False, transpose_y=False, adjoint_x=False, adjoint_y=False, name=None):
+        return self._add(Layer("BatchMatMul", name, 2, 1, {"tx": transpose_x, "ty": transpose_y,
+                                                            "ax": adjoint_x, "ay": adjoint_y}))
+
+    def AddActivationLayer(self, function, a=0.0, b=0.0, name=None):
+        return self._add(Layer("Activation", name, 1, 1, {"function": ActivationFunction(function), "a": float(a), "b": float(b)}))
+
+    def AddPooling2dLayer(self, pool_type, pool=(2, 2), stride=(2, 2), pad=(0, 0, 0, 0),
+                          padding_method=PaddingMethod.Exclude, name=None):
+        return self._add(Layer("Pooling2d", name, 1, 1, {"type": PoolingAlgorithm(pool_type), "pool": pool, "stride": stride,
+                                                          "pad": pad, "method": PaddingMethod(padding_method)}))
+
+    def AddElementwiseBinaryLayer(self, operation, name=None):
+        return self._add(Layer("ElementwiseBinary", name, 2, 1, {"op": BinaryOperation(operation)}))
+
+    def AddAdditionLayer(self, name=None):
+        return self.AddElementwiseBinaryLayer(BinaryOperation.Add, name)
+
+    def AddMultiplicationLayer(self, name=None):
+        return self.AddElementwiseBinaryLayer(BinaryOperation.Mul, name)
+
+    def AddSoftmaxLayer(self, beta=1.0, axis=-1, name=None):
+        return self._add(Layer("Softmax", name, 1, 1, {"beta": float(beta), "axis": int(axis)}))
+
+    def AddMeanLayer(self, axis=(1, 2), keep_dims=False, name=None):
+        return self._add(Layer("Mean", name, 1, 1, {"axis": tuple(axis), "keep_dims": keep_dims}))
+
+    def AddReshapeLayer(self, target_shape, name=None):
+        return self._add(Layer("Reshape", name, 1, 1, {"shape": tuple(target_shape)}))
+
+    def AddQuantizeLayer(self, name=None):
+        return self._add(Layer("Quantize", name, 1, 1))
+
+    def AddDequantizeLayer(self, name=None):
+        return self._add(Layer("Dequantize", name, 1, 1))
+
+    def AddQLstmLayer(self, descriptor, params, name=None):
+        """descriptor: dict of armnn::QLstmDescriptor fields; params: dict name -> (ndarray, TensorInfo) of the
+        LstmInputParams members.  Inputs: input, outputStateIn, cellStateIn.  Outputs: outputStateOut,
+        cellStateOut, output (include/armnn/INetwork.hpp AddQLstmLayer)."""
+        layer = self._add(Layer("QLstm", name, 3, 3, dict(descriptor)))
+        layer.qlstm_params = params
+        return layer
+
+
+# ---------------------------------------------------------------------------------------------------
+# Layer support (what B200LayerSupport::IsLayerSupported answers) and Optimize
+# ---------------------------------------------------------------------------------------------------
+
+_Q8 = (DataType.QAsymmU8, DataType.QAsymmS8, DataType.QSymmS8)
+
+
+def _infos(layer):
+    ins = [s.source.info if s.source is not None else None for s in layer.inputs]
+    outs = [s.info for s in layer.outputs]
+    return ins, outs
+
+
+def IsLayerSupported(layer):
+    """(supported, reason) for the B200Acc backend: 8-bit quantised NHWC hot path only."""
+    ins, outs = _infos(layer)
+    if any(i is None for i in ins):
+        return False, "unconnected input slot"
+    if any(o is None for o in outs):
+        return False, "output TensorInfo not set"
+    t = layer.type
+    if t in ("Input", "Output", "Constant", "Reshape"):
+        return True, ""
+    if t in ("Convolution2d", "DepthwiseConvolution2d", "FullyConnected"):
+        x, w, y = ins[0], ins[1], outs[0]
+        if x.dtype not in _Q8 or y.dtype not in _Q8 or w.dtype not in _Q8:
+            return False, "%s: input, weights and output must be 8-bit quantised" % t
+        if not w.constant:
+            return False, "%s: non-constant weights are not supported" % t
+        if len(ins) > 2 and ins[2].dtype != DataType.Signed32:
+            return False, "%s: bias must be Signed32" % t
+        if w.HasPerAxisQuantization():
+            want = {"Convolution2d": 0, "DepthwiseConvolution2d": 3}.get(t)
+            if t == "FullyConnected":
+                want = 0 if layer.desc["transpose"] else 1
+            if w.quant_dim != want:
+                return False, "%s: per-axis quantisation must be along the output-channel dimension" % t
+        return True, ""
+    if t == "BatchMatMul":
+        if layer.desc["ax"] or layer.desc["ay"]:
+            return False, "BatchMatMul: adjoint inputs are not supported"
+        if any(i.dtype not in _Q8 for i in ins) or outs[0].dtype not in _Q8:
+            return False, "BatchMatMul: 8-bit quantised tensors only"
+        return True, ""
+    if t in ("Pooling2d", "Mean", "ElementwiseBinary", "Activation", "Softmax"):
+        ok = (DataType.QAsymmU8, DataType.QAsymmS8, DataType.QSymmS16, DataType.Float32)
+        if any(i.dtype not in ok for i in ins) or outs[0].dtype not in ok:
+            return False, "%s: unsupported data type" % t
+        if t == "Mean" and tuple(layer.desc["axis"]) != (1, 2):
+            return False, "Mean: only reduction over H and W of an NHWC tensor is supported"
+        if t == "ElementwiseBinary" and len(outs[0].shape) > 4:
+            return False, "ElementwiseBinary: rank > 4"
+        return True, ""
+    if t in ("Quantize", "Dequantize"):
+        return True, ""
+    if t == "QLstm":
+        if ins[0].dtype != DataType.QAsymmS8 or ins[2].dtype != DataType.QSymmS16:
+            return False, "QLstm: input must be QAsymmS8 and cell state QSymmS16"
+        return True, ""
+    return False, "layer type %s is not on the B200Acc hot path" % t
+
+
+_FUSABLE_PRODUCERS = ("Convolution2d", "DepthwiseConvolution2d", "FullyConnected", "ElementwiseBinary")
+
+
+class OptimizedNetwork:
+    def __init__(self, layers, model_options):
+        self.layers, self.model_options = layers, model_options
+
+
+def Optimize(network, backend_preferences=("B200Acc",), model_options=None):
+    """Checks that B200Acc supports every layer (there is no fallback backend), fuses ReLu / BoundedReLu
+    activations into their producer, orders the graph.  Mirrors armnn::Optimize + OptimizeSubgraphView."""
+    if "B200Acc" not in tuple(backend_preferences):
+        raise InvalidArgumentException("this runtime only provides the B200Acc backend")
+    for layer in network.layers:
+        ok, reason = IsLayerSupported(layer)
+        if not ok:
+            raise InvalidArgumentException("Layer of type %s (%s) is not supported on requested backend B200Acc: %s"
+                                           % (layer.type, layer.name, reason))
+    # activation fusion
+    removed = set()
+    for act in network.layers:
+        if act.type != "Activation" or act.desc["function"] not in (ActivationFunction.ReLu, ActivationFunction.BoundedReLu):
+            continue
+        src = act.inputs[0].source
+        prod = src.layer
+        if prod.type not in _FUSABLE_PRODUCERS or prod.fused_activation is not None or len(src.connections) != 1:
+            continue
+        if prod.type == "ElementwiseBinary" and prod.desc["op"] not in (BinaryOperation.Add, BinaryOperation.Mul, BinaryOperation.Sub):
+            continue
+        if not src.info.same_quantization(act.outputs[0].info) or src.info.dtype == DataType.Float32:
+            continue
+        prod.fused_activation = (act.desc["function"], act.desc["a"], act.desc["b"])
+        # re-route the activation's consumers to the producer
+        src.connections = []
+        for consumer in act.outputs[0].connections:
+            consumer.source = src
+            src.connections.append(consumer)
+        removed.add(id(act))
+    layers = [l for l in network.layers if id(l) not in removed]
+    # topological order (layers may have been added in any order)
+    order, done = [], set()
+
+    def visit(l):
+        if id(l) in done:
+            return
+        for s in l.inputs:
+            visit(s.source.layer)
+        done.add(id(l))
+        order.append(l)
+    for l in layers:
+        visit(l)
+    return OptimizedNetwork(order, dict(model_options or {}))
+
+
+# ---------------------------------------------------------------------------------------------------
+# Runtime
+# ---------------------------------------------------------------------------------------------------
+
+def _qt(info, ptr, scales_ptr=None):
+    t = _abi.QTensor()
+    t.data = ptr
+    t.dtype = _ABI_DTYPE[info.dtype]
+    t.scale = info.scale
+    t.zero_point = info.offset
+    t.scales = scales_ptr
+    return t
+
+
+def _clamp(layer, info):
+    lo, hi = ctypes.c_int32(), ctypes.c_int32()
+    kind, a, b = 0, 0.0, 0.0
+    if layer.fused_activation is not None:
+        fn, a, b = layer.fused_activation
+        kind = 1 if fn == ActivationFunction.ReLu else 2
+    lib.check(lib.load_library().b200k_activation_clamp(kind, a, b, info.scale, info.offset, _ABI_DTYPE[info.dtype],
+                                                        ctypes.byref(lo), ctypes.byref(hi)))
+    return lo.value, hi.value
+
+
+class IRuntime:
+    """armnn::IRuntime for one device.  Raises BackendUnavailableException when the device cannot be opened."""
+
+    def __init__(self, device_id=0):
+        import torch
+        self.torch = torch
+        if not torch.cuda.is_available():
+            raise BackendUnavailableException("B200Acc: no CUDA device visible")
+        rc = lib.load_library().b200k_device_open(device_id)
+        if rc != 0:
+            raise BackendUnavailableException("B200Acc: " + lib.load_library().b200k_last_error().decode())
+        self.device = torch.device("cuda", device_id)
+        self.networks = {}
+
+    @staticmethod
+    def Create(device_id=0):
+        return IRuntime(device_id)
+
+    def LoadNetwork(self, optimized):
+        net = LoadedNetwork(self, optimized)
+        net_id = len(self.networks)
+        self.networks[net_id] = net
+        return net_id
+
+    def GetLoadedNetwork(self, net_id):
+        return self.networks[net_id]
+
+    def EnqueueWorkload(self, net_id, input_tensors, output_tensors):
+        return self.networks[net_id].EnqueueWorkload(input_tensors, output_tensors)
+
+    def UnloadNetwork(self, net_id):
+        del self.networks[net_id]
+
+
+class GraphProgram:
+    """Memory-agnostic part of a loaded network: one tensor per output slot and one prepared C-ABI parameter
+    struct per layer.  Subclasses say where tensors live (`_alloc`, `_upload`, `_ptr`, `_view`)."""
+
+    def __init__(self, optimized):
+        self.layers = optimized.layers
+        self.tensors = {}          # id(OutputSlot) -> tensor object of the memory space
+        self.aux = []              # per-axis scale arrays, QLstm weight copies: kept alive
+        self.workloads = []        # (layer, entry name, params struct)
+        self.inputs, self.outputs = {}, {}
+
+    # -- memory (overridden per memory space) ---------------------------------------------------------
+    def _alloc(self, info):
+        raise NotImplementedError
+
+    def _upload(self, array):
+        raise NotImplementedError
+
+    def _ptr(self, tensor):
+        raise NotImplementedError
+
+    def _view(self, tensor, shape):
+        raise NotImplementedError
+
+    def _dev(self, slot):
+        return self.tensors[id(slot)]
+
+    def _scales(self, info):
+        if info.scales is None:
+            return None
+        t = self._upload(info.scales.copy())
+        self.aux.append(t)
+        return self._ptr(t)
+
+    def _operand(self, slot):
+        return _qt(slot.info, self._ptr(self._dev(slot)), self._scales(slot.info))
+
+    # -- workload construction -------------------------------------------------------------------------
+    def _build(self):
+        for layer in self.layers:
+            t = layer.type
+            if t == "Input":
+                self.tensors[id(layer.outputs[0])] = self._alloc(layer.outputs[0].info)
+                self.inputs[layer.desc["id"]] = layer.outputs[0]
+                continue
+            if t == "Constant":
+                # RefConstantWorkload: one copy of the layer blob into its output handle, at load time
+                self.tensors[id(layer.outputs[0])] = self._upload(layer.const_data)
+                continue
+            if t == "Output":
+                self.outputs[layer.desc["id"]] = layer.inputs[0].source
+                continue
+            if t == "Reshape":
+                # aliasing view, no kernel (RefReshapeWorkload is a memcpy)
+                src = self._dev(layer.inputs[0].source)
+                self.tensors[id(layer.outputs[0])] = self._view(src, layer.outputs[0].info.shape)
+                continue
+            for o in layer.outputs:
+                self.tensors[id(o)] = self._alloc(o.info)
+            self.workloads.append((layer,) + getattr(self, "_make_" + t)(layer))
+
+    def _conv_params(self, layer, depthwise):
+        x, w = layer.inputs[0].source, layer.inputs[1].source
+        y = layer.outputs[0]
+        p = _abi.Conv2dParams()
+        p.x, p.w, p.y = self._operand(x), self._operand(w), self._operand(y)
+        if layer.desc["bias"]:
+            p.bias = self._operand(layer.inputs[2].source)
+        n, h, wd, c = x.info.shape
+        _, oh, ow, oc = y.info.shape
+        kh, kw = w.info.shape[1], w.info.shape[2]
+        p.n, p.h, p.wd, p.c, p.oh, p.ow, p.oc, p.kh, p.kw = n, h, wd, c, oh, ow, oc, kh, kw
+        p.stride_h, p.stride_w = layer.desc["stride"]
+        p.pad_top, p.pad_left = layer.desc["pad"][0], layer.desc["pad"][2]
+        p.dil_h, p.dil_w = layer.desc["dilation"]
+        p.clamp_lo, p.clamp_hi = _clamp(layer, y.info)
+        return p
+
+    def _make_Convolution2d(self, layer):
+        return "conv2d_q8", self._conv_params(layer, False)
+
+    def _make_DepthwiseConvolution2d(self, layer):
+        return "dwconv2d_q8", self._conv_params(layer, True)
+
+    def _make_FullyConnected(self, layer):
+        x, w, y = layer.inputs[0].source, layer.inputs[1].source, layer.outputs[0]
+        p = _abi.FcParams()
+        p.x, p.w, p.y = self._operand(x), self._operand(w), self._operand(y)
+        if layer.desc["bias"]:
+            p.bias = self._operand(layer.inputs[2].source)
+        p.m = x.info.shape[0]
+        p.k = int(np.prod(x.info.shape[1:]))                 # 4-D inputs are flattened (FullyConnected.cpp:16-24)
+        p.n = y.info.shape[-1]
+        p.transpose_w = int(layer.desc["transpose"])
+        p.clamp_lo, p.clamp_hi = _clamp(layer, y.info)
+        return "fully_connected_q8", p
+
+    def _make_BatchMatMul(self, layer):
+        x, yv, o = layer.inputs[0].source, layer.inputs[1].source, layer.outputs[0]
+        p = _abi.BmmParams()
+        p.x, p.y, p.out = self._operand(x), self._operand(yv), self._operand(o)
+        xs, ys, os_ = x.info.shape, yv.info.shape, o.info.shape
+        p.m, p.n = os_[-2], os_[-1]
+        p.k = xs[-2] if layer.desc["tx"] else xs[-1]
+        p.batch = int(np.prod(os_[:-2])) if len(os_) > 2 else 1
+        bx = int(np.prod(xs[:-2])) if len(xs) > 2 else 1
+        by = int(np.prod(ys[:-2])) if len(ys) > 2 else 1
+        if bx not in (1, p.batch) or by not in (1, p.batch):
+            raise InvalidArgumentException("BatchMatMul: partial batch broadcast is not supported")
+        p.batch_stride_x = xs[-1] * xs[-2] if bx == p.batch and p.batch > 1 else 0
+        p.batch_stride_y = ys[-1] * ys[-2] if by == p.batch and p.batch > 1 else 0
+        p.transpose_x, p.transpose_y = int(layer.desc["tx"]), int(layer.desc["ty"])
+        return "batch_matmul_q8", p
+
+    def _make_Pooling2d(self, layer):
+        x, y = layer.inputs[0].source, layer.outputs[0]
+        p = _abi.Pool2dParams()
+        p.x, p.y = self._operand(x), self._operand(y)
+        p.n, p.h, p.wd, p.c = x.info.shape
+        p.oh, p.ow = y.info.shape[1], y.info.shape[2]
+        p.pool_h, p.pool_w = layer.desc["pool"]
+        p.stride_h, p.stride_w = layer.desc["stride"]
+        p.pad_top, p.pad_bottom, p.pad_left, p.pad_right = layer.desc["pad"]
+        p.pool_type, p.padding_method = int(layer.desc["type"]), int(layer.desc["method"])
+        return "pool2d_q8", p
+
+    def _make_Mean(self, layer):
+        x, y = layer.inputs[0].source, layer.outputs[0]
+        p = _abi.MeanParams()
+        p.x, p.y = self._operand(x), self._operand(y)
+        p.n, p.h, p.wd, p.c = x.info.shape
+        return "mean_hw_q8", p
+
+    def _make_ElementwiseBinary(self, layer):
+        a, b, o = layer.inputs[0].source, layer.inputs[1].source, layer.outputs[0]
+        p = _abi.EltwiseParams()
+        p.a, p.b, p.out = self._operand(a), self._operand(b), self._operand(o)
+        rank = len(o.info.shape)
+        if len(a.info.shape) != rank or len(b.info.shape) != rank:
+            raise InvalidArgumentException("ElementwiseBinary: inputs and output must have the same rank")
+        p.rank = rank
+        for i in range(rank):
+            p.shape_a[i], p.shape_b[i], p.shape_out[i] = a.info.shape[i], b.info.shape[i], o.info.shape[i]
+        p.op = int(layer.desc["op"])
+        p.clamp_lo, p.clamp_hi = _clamp(layer, o.info) if o.info.dtype != DataType.Float32 else (0, 0)
+        return "eltwise_q8", p
+
+    def _make_Activation(self, layer):
+        x, y = layer.inputs[0].source, layer.outputs[0]
+        p = _abi.ActivationParams()
+        p.x, p.y = self._operand(x), self._operand(y)
+        p.count = x.info.GetNumElements()
+        p.function, p.a, p.b = int(layer.desc["function"]), layer.desc["a"], layer.desc["b"]
+        return "activation_q8", p
+
+    def _make_Softmax(self, layer):
+        x, y = layer.inputs[0].source, layer.outputs[0]
+        shape = x.info.shape
+        axis = layer.desc["axis"] % len(shape)
+        p = _abi.SoftmaxParams()
+        p.x, p.y = self._operand(x), self._operand(y)
+        p.outer = int(np.prod(shape[:axis])) if axis > 0 else 1
+        p.axis_size = shape[axis]
+        p.inner = int(np.prod(shape[axis + 1:])) if axis + 1 < len(shape) else 1
+        p.beta = layer.desc["beta"]
+        return "softmax_q8", p
+
+    def _make_convert(self, layer):
+        x, y = layer.inputs[0].source, layer.outputs[0]
+        p = _abi.ConvertParams()
+        p.x, p.y = self._operand(x), self._operand(y)
+        p.count = x.info.GetNumElements()
+        return "convert_q", p
+
+    _make_Quantize = _make_convert
+    _make_Dequantize = _make_convert
+
+    def _make_QLstm(self, layer):
+        x, h, c = (s.source for s in layer.inputs)
+        hout, cout, out = layer.outputs
+        d = layer.desc
+        p = _abi.QLstmParams()
+        p.batch, p.input_size = x.info.shape
+        p.output_size, p.num_units = h.info.shape[1], c.info.shape[1]
+        p.input, p.input_scale, p.input_zp = self._ptr(self._dev(x)), x.info.scale, x.info.offset
+        p.output_state_in, p.output_state_scale, p.output_state_zp = self._ptr(self._dev(h)), h.info.scale, h.info.offset
+        p.cell_state_in, p.cell_state_scale = self._ptr(self._dev(c)), c.info.scale
+        if not (hout.info.same_quantization(h.info) and cout.info.same_quantization(c.info)):
+            raise InvalidArgumentException("QLstm: state outputs must share the state inputs' quantisation")
+        p.output_state_out, p.cell_state_out = self._ptr(self._dev(hout)), self._ptr(self._dev(cout))
+        p.output, p.output_scale, p.output_zp = self._ptr(self._dev(out)), out.info.scale, out.info.offset
+        names = {"InputToInputWeights": ("w_i2i", "s_i2i"), "InputToForgetWeights": ("w_i2f", "s_i2f"),
+                 "InputToCellWeights": ("w_i2c", "s_i2c"), "InputToOutputWeights": ("w_i2o", "s_i2o"),
+                 "RecurrentToInputWeights": ("w_r2i", "s_r2i"), "RecurrentToForgetWeights": ("w_r2f", "s_r2f"),
+                 "RecurrentToCellWeights": ("w_r2c", "s_r2c"), "RecurrentToOutputWeights": ("w_r2o", "s_r2o"),
+                 "CellToInputWeights": ("w_c2i", "s_c2i"), "CellToForgetWeights": ("w_c2f", "s_c2f"),
+                 "CellToOutputWeights": ("w_c2o", "s_c2o"),
+                 "InputGateBias": ("b_i", None), "ForgetGateBias": ("b_f", None), "CellBias": ("b_c", None),
+                 "OutputGateBias": ("b_o", None),
+                 "InputLayerNormWeights": ("ln_i", "s_lni"), "ForgetLayerNormWeights": ("ln_f", "s_lnf"),
+                 "CellLayerNormWeights": ("ln_c", "s_lnc"), "OutputLayerNormWeights": ("ln_o", "s_lno"),
+                 "ProjectionWeights": ("w_proj", "s_proj"), "ProjectionBias": ("b_proj", "s_bproj")}
+        # The descriptor's ConstTensorHandles are only valid during workload creation
+        # (src/armnn/LoadedNetwork.cpp:396), so the workload owns device copies.
+        for key, (wf, sf) in names.items():
+            if key not in layer.qlstm_params or layer.qlstm_params[key] is None:
+                continue
+            data, info = layer.qlstm_params[key]
+            dev = self._upload(np.ascontiguousarray(np.asarray(data).astype(_NP_DTYPE[info.dtype])))
+            self.aux.append(dev)
+            setattr(p, wf, self._ptr(dev))
+            if sf:
+                setattr(p, sf, info.scale)
+        if d.get("LayerNormEnabled"):
+            # bias scale = layer-norm weight scale / 1024 (RefQLstmWorkload.cpp:261-287)
+            for g, key in (("i", "InputLayerNormWeights"), ("f", "ForgetLayerNormWeights"),
+                           ("c", "CellLayerNormWeights"), ("o", "OutputLayerNormWeights")):
+                if layer.qlstm_params.get(key) is not None:
+                    setattr(p, "s_b" + g, float(np.float32(layer.qlstm_params[key][1].scale) / np.float32(1024)))
+        else:
+            p.ln_i = p.ln_f = p.ln_c = p.ln_o = None
+        if d.get("CifgEnabled"):
+            p.w_i2i = p.w_r2i = None
+        if not d.get("PeepholeEnabled"):
+            p.w_c2i = p.w_c2f = p.w_c2o = None
+        if not d.get("ProjectionEnabled"):
+            p.w_proj = p.b_proj = None
+        p.cell_clip, p.projection_clip = d.get("CellClip", 0.0), d.get("ProjectionClip", 0.0)
+        p.input_intermediate_scale = d["InputIntermediateScale"]
+        p.forget_intermediate_scale = d["ForgetIntermediateScale"]
+        p.cell_intermediate_scale = d["CellIntermediateScale"]
+        p.output_intermediate_scale = d["OutputIntermediateScale"]
+        p.hidden_state_scale, p.hidden_state_zp = d["HiddenStateScale"], d["HiddenStateZeroPoint"]
+        return "qlstm_step", p
+
+
+
+class LoadedNetwork(GraphProgram):
+    """Device tensors + one workload (a prepared C-ABI call) per layer, enqueued in order on one stream."""
+
+    def __init__(self, runtime, optimized):
+        super().__init__(optimized)
+        torch = runtime.torch
+        self.rt, self.torch = runtime, torch
+        self.stream = torch.cuda.Stream(device=runtime.device)
+        self.graph = None
+        with torch.cuda.device(runtime.device):
+            self._build()
+
+    def _alloc(self, info):
+        tdt = getattr(self.torch, np.dtype(_NP_DTYPE[info.dtype]).name)
+        return self.torch.empty(info.shape if info.shape else (1,), dtype=tdt, device=self.rt.device)
+
+    def _upload(self, array):
+        return self.torch.from_numpy(np.ascontiguousarray(array)).to(self.rt.device)
+
+    def _ptr(self, tensor):
+        return tensor.data_ptr()
+
+    def _view(self, tensor, shape):
+        return tensor.view(shape)
+
+    # -- execution ---------------------------------------------------------------------------------
+    def launch_all(self, stream_handle):
+        """Enqueue every workload on the given CUDA stream; returns the number of kernels launched."""
+        l = lib.load_library()
+        for layer, entry, params in self.workloads:
+            rc = getattr(l, "b200k_" + entry)(ctypes.byref(params), ctypes.c_void_p(stream_handle))
+            if rc != 0:
+                raise RuntimeError("workload %s (%s) failed: %s" % (layer.name, entry, l.b200k_last_error().decode()))
+        return len(self.workloads)
+
+    def Execute(self):
+        """The workload queue only (inputs and outputs stay in device memory)."""
+        if self.graph is not None:
+            with self.torch.cuda.stream(self.stream):
+                self.graph.replay()
+            return len(self.workloads)
+        return self.launch_all(self.stream.cuda_stream)
+
+    def CaptureGraph(self):
+        """Capture the workload queue into a CUDA graph: removes the per-workload host launches."""
+        torch = self.torch
+        self.Execute()
+        self.stream.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=self.stream):
+            self.launch_all(torch.cuda.current_stream().cuda_stream)
+        self.graph = g
+
+    def EnqueueWorkload(self, input_tensors, output_tensors):
+        """input_tensors / output_tensors: {binding id: host torch tensor or numpy array}.  Host -> device
+        copies, the workload queue and device -> host copies all go to this network's stream; returns after
+        the outputs are in host memory (the Map(blocking) of the reference's output copy)."""
+        torch = self.torch
+        with torch.cuda.stream(self.stream):
+            for bid, host in input_tensors.items():
+                dst = self._dev(self.inputs[bid])
+                src = host if torch.is_tensor(host) else torch.from_numpy(host)
+                dst.view(-1).copy_(src.view(-1).view(dst.dtype), non_blocking=True)
+            self.Execute()
+            for bid, host in output_tensors.items():
+                src = self._dev(self.outputs[bid])
+                dst = host if torch.is_tensor(host) else torch.from_numpy(host)
+                dst.view(-1).view(src.dtype).copy_(src.view(-1), non_blocking=True)
+        self.stream.synchronize()
+        return 0
+
+    def input_tensor(self, binding_id):
+        return self._dev(self.inputs[binding_id])
+
+    def output_tensor(self, binding_id):
+        return self._dev(self.outputs[binding_id])
+
+    def tensor_of(self, slot):
+        return self._dev(slot)

@@ -236,6 +236,8 @@ int b200k_convert_q(const b200k_convert_params* p, void* stream);
 typedef struct {
     int32_t batch, input_size, num_units, output_size;
     /* tensors */
+    /* gate bias scales s_b*: the reference derives them as layer-norm weight scale / 1024
+     * (RefQLstmWorkload.cpp:261-287) and ignores the biases entirely without layer norm. */
     const int8_t*  input;            float input_scale;  int32_t input_zp;       /* [batch, input_size]  */
     const int8_t*  output_state_in;  float output_state_scale; int32_t output_state_zp; /* [batch, output_size] */
     const int16_t* cell_state_in;    float cell_state_scale;   /* [batch, num_units]  */
@@ -255,11 +257,8 @@ typedef struct {
     float input_intermediate_scale, forget_intermediate_scale, cell_intermediate_scale,
           output_intermediate_scale;
     float hidden_state_scale; int32_t hidden_state_zp;
-    /* scratch: device int16 [4 * batch * num_units] + int8/int32 as documented in qlstm.cu */
-    void*  scratch; size_t scratch_bytes;
 } b200k_qlstm_params;
 
-size_t b200k_qlstm_scratch_bytes(int32_t batch, int32_t num_units, int32_t output_size);
 int b200k_qlstm_step(const b200k_qlstm_params* p, void* stream);
 
 #ifdef __cplusplus

@@ -1,0 +1,257 @@
+"""The seeded parity cases, shared by the CPU tests (oracle vs golden / real CpuRef), the fixture generator and
+the GPU tests (CUDA vs oracle).  Every case is small enough for the oracle to finish in well under a second,
+and covers the edge cases the reference's own layer tests exercise: odd channel counts, strides, dilation,
+padding wider than the kernel, per-axis and per-tensor quantisation, both 8-bit signednesses and their mix,
+broadcast, ragged tails that do not fill a vector or a tile."""
+import numpy as np
+
+from q8util import (RANGE, NP_OF, FcCase, SimpleCase, _abi, activation_clamp, qt, qt_out, random_conv_case,
+                    random_fc_case, random_qlstm_case)
+
+U8, S8, S16, S32, F32 = _abi.U8, _abi.S8, _abi.S16, _abi.S32, _abi.F32
+
+
+def conv_cases():
+    c = {}
+    # the single-layer benchmark config, as specified (output scale 0.05 saturates ~2/3 of outputs) ...
+    c["config1_as_specified"] = lambda: random_conv_case(1234, 1, 56, 56, 64, 64, 3, 3, pad=(1, 1, 1, 1), act=(1, 0, 0),
+                                                         y_scale=0.05, y_zp=-128)
+    # ... and with an output scale that leaves most values unsaturated
+    c["config1_unsaturated"] = lambda: random_conv_case(1234, 1, 56, 56, 64, 64, 3, 3, pad=(1, 1, 1, 1), act=(1, 0, 0))
+    c["1x1_s1"] = lambda: random_conv_case(1, 2, 14, 14, 64, 128, 1, 1)
+    c["1x1_s2_shortcut"] = lambda: random_conv_case(2, 2, 14, 14, 64, 96, 1, 1, stride=(2, 2))
+    c["3x3_s2"] = lambda: random_conv_case(3, 1, 15, 15, 32, 48, 3, 3, stride=(2, 2), pad=(1, 1, 1, 1), act=(1, 0, 0))
+    c["7x7_s2_stem_c3"] = lambda: random_conv_case(4, 1, 32, 32, 3, 64, 7, 7, stride=(2, 2), pad=(2, 3, 2, 3), act=(1, 0, 0))
+    c["3x3_dilation2"] = lambda: random_conv_case(5, 1, 12, 12, 16, 16, 3, 3, pad=(2, 2, 2, 2), dil=(2, 2))
+    c["odd_channels_c5_oc7"] = lambda: random_conv_case(6, 2, 9, 7, 5, 7, 3, 3, pad=(1, 1, 1, 1))
+    c["c4_words"] = lambda: random_conv_case(7, 1, 10, 10, 12, 20, 3, 3, pad=(1, 1, 1, 1))
+    c["pad_wider_than_kernel"] = lambda: random_conv_case(8, 1, 6, 6, 16, 16, 3, 3, pad=(4, 4, 4, 4))
+    c["u8_u8_per_tensor_relu6"] = lambda: random_conv_case(9, 1, 12, 12, 32, 32, 3, 3, pad=(1, 1, 1, 1), x_dtype=U8, w_dtype=U8,
+                                                           y_dtype=U8, per_axis=False, x_q=(0.02, 121), y_zp=0, act=(2, 6.0, 0.0),
+                                                           y_scale=0.04)
+    c["u8_act_s8_per_axis"] = lambda: random_conv_case(10, 1, 8, 8, 16, 24, 1, 1, x_dtype=U8, y_dtype=U8, x_q=(0.5, 128))
+    c["s8_per_tensor_no_bias"] = lambda: random_conv_case(11, 1, 8, 8, 16, 16, 3, 3, pad=(1, 1, 1, 1), per_axis=False, bias=False)
+    c["rect_kernel_3x1_stride_1x2"] = lambda: random_conv_case(12, 1, 9, 11, 8, 8, 3, 1, stride=(1, 2), pad=(1, 1, 0, 0))
+    c["k_not_multiple_of_64"] = lambda: random_conv_case(13, 1, 5, 5, 48, 80, 3, 3, pad=(1, 1, 1, 1))
+    return c
+
+
+def dwconv_cases():
+    c = {}
+    c["3x3_s1_c32"] = lambda: random_conv_case(21, 2, 14, 14, 32, None, 3, 3, pad=(1, 1, 1, 1), depthwise=True, act=(2, 6.0, 0.0),
+                                               x_dtype=U8, w_dtype=U8, y_dtype=U8, per_axis=False, x_q=(0.02, 0), y_zp=0, y_scale=0.03)
+    c["3x3_s2_c96"] = lambda: random_conv_case(22, 1, 15, 15, 96, None, 3, 3, stride=(2, 2), pad=(0, 1, 0, 1), depthwise=True,
+                                               x_dtype=U8, w_dtype=U8, y_dtype=U8, per_axis=False, x_q=(0.02, 3), y_zp=0, y_scale=0.03)
+    c["s8_per_axis_c20"] = lambda: random_conv_case(23, 1, 9, 9, 20, None, 3, 3, pad=(1, 1, 1, 1), depthwise=True)
+    c["odd_c7"] = lambda: random_conv_case(24, 1, 7, 7, 7, None, 3, 3, pad=(1, 1, 1, 1), depthwise=True)
+    c["multiplier2"] = lambda: random_conv_case(25, 1, 6, 6, 8, None, 3, 3, pad=(1, 1, 1, 1), depthwise=True, depth_multiplier=2)
+    c["5x5_dilation2"] = lambda: random_conv_case(26, 1, 12, 12, 16, None, 5, 5, pad=(4, 4, 4, 4), dil=(2, 2), depthwise=True)
+    return c
+
+
+def fc_cases():
+    c = {}
+    c["m1_k1024"] = lambda: random_fc_case(31, 1, 1024, 1024)
+    c["m16_k1024"] = lambda: random_fc_case(32, 16, 1024, 1024)
+    c["m256_k1024"] = lambda: random_fc_case(33, 256, 1024, 1024)
+    c["m16_k4096_n512"] = lambda: random_fc_case(34, 16, 4096, 512)
+    c["odd_m3_k37_n11"] = lambda: random_fc_case(35, 3, 37, 11)
+    c["not_transposed"] = lambda: random_fc_case(36, 5, 64, 24, transpose_w=False)
+    c["u8_per_tensor_relu"] = lambda: random_fc_case(37, 8, 128, 64, x_dtype=U8, w_dtype=U8, y_dtype=U8, per_axis=False,
+                                                     x_q=(0.03, 120), act=(1, 0., 0.))
+    c["classifier_2048_1001"] = lambda: random_fc_case(38, 4, 2048, 1001, per_axis=False)
+    return c
+
+
+def _rand(rng, dtype, shape):
+    lo, hi = RANGE[dtype]
+    return rng.integers(lo, hi + 1, size=shape).astype(NP_OF[dtype])
+
+
+def bmm_cases():
+    def make(seed, batch, m, k, n, tx, ty, bcast_y=False, xd=S8, yd=S8):
+        def build(mem):
+            rng = np.random.default_rng(seed)
+            xs = (batch, k, m) if tx else (batch, m, k)
+            ys = ((1,) if bcast_y else (batch,)) + ((n, k) if ty else (k, n))
+            p = _abi.BmmParams()
+            p.x = qt(mem, _rand(rng, xd, xs), xd, 0.02, 3 if xd == S8 else 130)
+            p.y = qt(mem, _rand(rng, yd, ys), yd, 0.01, -2 if yd == S8 else 120)
+            p.out, out = qt_out(mem, (batch, m, n), S8, 0.02 * 0.01 * 74 * 74 * np.sqrt(k) * 3 / 127, 1)
+            p.batch, p.m, p.k, p.n = batch, m, k, n
+            p.transpose_x, p.transpose_y = int(tx), int(ty)
+            p.batch_stride_x = m * k
+            p.batch_stride_y = 0 if bcast_y else k * n
+            acc, p.acc_out = mem.out((batch, m, n), np.int32)
+            return p, [out, acc]
+        return lambda: SimpleCase("batch_matmul_q8", build)
+    return {"plain": make(41, 3, 17, 33, 9, False, False), "transpose_x": make(42, 2, 8, 16, 8, True, False),
+            "transpose_y": make(43, 2, 8, 16, 12, False, True), "broadcast_y": make(44, 4, 5, 20, 6, False, False, True),
+            "u8": make(45, 1, 16, 16, 16, False, False, xd=U8, yd=U8)}
+
+
+def pool_cases():
+    def make(seed, n, h, w, c, ptype, k, s, pad, method, dtype=S8, out_scale_mul=1.0):
+        def build(mem):
+            rng = np.random.default_rng(seed)
+            p = _abi.Pool2dParams()
+            zp = -5 if dtype == S8 else 7
+            p.x = qt(mem, _rand(rng, dtype, (n, h, w, c)), dtype, 0.1, zp)
+            oh = (h + pad[0] + pad[1] - k[0]) // s[0] + 1
+            ow = (w + pad[2] + pad[3] - k[1]) // s[1] + 1
+            p.y, y = qt_out(mem, (n, oh, ow, c), dtype, 0.1 * out_scale_mul, zp)
+            p.n, p.h, p.wd, p.c, p.oh, p.ow = n, h, w, c, oh, ow
+            p.pool_h, p.pool_w = k
+            p.stride_h, p.stride_w = s
+            p.pad_top, p.pad_bottom, p.pad_left, p.pad_right = pad
+            p.pool_type, p.padding_method = ptype, method
+            return p, [y]
+        return lambda: SimpleCase("pool2d_q8", build)
+    return {
+        "max_3x3_s2_pad1_c64": make(51, 2, 16, 16, 64, 0, (3, 3), (2, 2), (1, 1, 1, 1), 1),
+        "avg_global_7x7_c2048": make(52, 2, 7, 7, 2048, 1, (7, 7), (1, 1), (0, 0, 0, 0), 1, out_scale_mul=0.5),
+        "avg_3x3_exclude_pad": make(53, 1, 9, 9, 20, 1, (3, 3), (2, 2), (1, 1, 1, 1), 1),
+        "avg_3x3_ignore_value": make(54, 1, 9, 9, 20, 1, (3, 3), (2, 2), (1, 1, 1, 1), 0),
+        "l2_2x2_u8_c5": make(55, 1, 8, 8, 5, 2, (2, 2), (2, 2), (0, 0, 0, 0), 1, dtype=U8),
+        "max_u8_odd_c3": make(56, 1, 7, 7, 3, 0, (2, 2), (1, 1), (0, 0, 0, 0), 1, dtype=U8),
+        "avg_pad2_window3_ignore": make(57, 1, 5, 5, 8, 1, (3, 3), (2, 2), (2, 2, 2, 2), 0),
+        "max_pad2_window3": make(58, 1, 5, 5, 8, 0, (3, 3), (2, 2), (2, 2, 2, 2), 1),
+    }
+
+
+def mean_cases():
+    def make(seed, n, h, w, c, dtype=S8):
+        def build(mem):
+            rng = np.random.default_rng(seed)
+            p = _abi.MeanParams()
+            p.x = qt(mem, _rand(rng, dtype, (n, h, w, c)), dtype, 0.05, 3)
+            p.y, y = qt_out(mem, (n, c), dtype, 0.02, 1)
+            p.n, p.h, p.wd, p.c = n, h, w, c
+            return p, [y]
+        return lambda: SimpleCase("mean_hw_q8", build)
+    return {"7x7x1280_u8": make(61, 2, 7, 7, 1280, U8), "5x3x10": make(62, 3, 5, 3, 10)}
+
+
+def eltwise_cases():
+    def make(seed, sa, sb, op, dtype=S8, act=(0, 0., 0.), extra=()):
+        def build(mem):
+            rng = np.random.default_rng(seed)
+            so = tuple(max(a, b) for a, b in zip(sa, sb))
+            p = _abi.EltwiseParams()
+            za, zb, zo = (3, -7, -128 if act[0] else 5) if dtype == S8 else (120, 131, 0 if act[0] else 128)
+            p.a = qt(mem, _rand(rng, dtype, sa), dtype, 0.031, za)
+            p.b = qt(mem, _rand(rng, dtype, sb), dtype, 0.017, zb)
+            oscale = {0: 0.05, 4: 0.06, 5: 0.05, 2: 0.035, 3: 0.035, 1: 0.5, 6: 0.3}[op]
+            p.out, out = qt_out(mem, so, dtype, oscale, zo)
+            p.rank = len(so)
+            for i in range(len(so)):
+                p.shape_a[i], p.shape_b[i], p.shape_out[i] = sa[i], sb[i], so[i]
+            p.op = op
+            p.clamp_lo, p.clamp_hi = activation_clamp(act[0], act[1], act[2], oscale, zo, dtype)
+            return p, [out]
+        return lambda: SimpleCase("eltwise_q8", build, extra)
+    import ctypes as C
+    relu = (C.c_int(1), C.c_float(0), C.c_float(0))
+    none = (C.c_int(0), C.c_float(0), C.c_float(0))
+    return {
+        "add_residual_relu": make(71, (2, 14, 14, 64), (2, 14, 14, 64), 0, act=(1, 0., 0.), extra=relu),
+        "add_u8": make(72, (1, 7, 7, 24), (1, 7, 7, 24), 0, dtype=U8, extra=none),
+        "mul": make(73, (2, 5, 5, 16), (2, 5, 5, 16), 4, extra=none),
+        "sub_ragged": make(74, (1, 3, 5, 7), (1, 3, 5, 7), 5, extra=none),
+        "add_broadcast_channel": make(75, (2, 6, 6, 10), (1, 1, 1, 10), 0, extra=none),
+        "mul_broadcast_scalar": make(76, (1, 1, 1, 1), (2, 4, 4, 8), 4, extra=none),
+        "maximum": make(77, (3, 17), (3, 17), 2, extra=none),
+        "minimum_broadcast_row": make(78, (4, 1), (4, 9), 3, extra=none),
+    }
+
+
+def activation_cases():
+    def make(seed, fn, a, b, dtype=S8, count=1000, in_q=(0.05, 2), out_q=(0.05, 2)):
+        def build(mem):
+            rng = np.random.default_rng(seed)
+            p = _abi.ActivationParams()
+            p.x = qt(mem, _rand(rng, dtype, (count,)), dtype, *in_q)
+            p.y, y = qt_out(mem, (count,), dtype, *out_q)
+            p.count, p.function, p.a, p.b = count, fn, a, b
+            return p, [y]
+        return lambda: SimpleCase("activation_q8", build)
+    return {
+        "relu": make(81, 3, 0, 0), "bounded_relu6": make(82, 4, 6.0, 0.0, out_q=(0.03, -128)),
+        "sigmoid_u8": make(83, 0, 0, 0, dtype=U8, in_q=(0.05, 128), out_q=(1 / 256., 0)),
+        "tanh": make(84, 1, 1.0, 1.0, out_q=(1 / 128., 0)), "linear": make(85, 2, 0.7, -0.3),
+        "leaky_relu": make(86, 6, 0.1, 0), "abs": make(87, 7, 0, 0), "square": make(88, 9, 0, 0, out_q=(0.3, -128)),
+        "hard_swish": make(89, 11, 0, 0, count=1003), "sqrt_u8": make(90, 8, 0, 0, dtype=U8, in_q=(0.05, 0), out_q=(0.02, 0)),
+        "elu": make(91, 10, 1.0, 0), "soft_relu": make(92, 5, 0, 0),
+    }
+
+
+# activations that go through libm exp / tanh / log: the CUDA and glibc implementations may differ in the last
+# ulp, which can move a value across a rounding boundary
+TRANSCENDENTAL_ACTIVATIONS = ("sigmoid_u8", "tanh", "elu", "soft_relu")
+
+
+def softmax_cases():
+    def make(seed, outer, axis, inner, dtype=S8, beta=1.0):
+        def build(mem):
+            rng = np.random.default_rng(seed)
+            p = _abi.SoftmaxParams()
+            p.x = qt(mem, _rand(rng, dtype, (outer, axis, inner)), dtype, 0.06, 0 if dtype == S8 else 128)
+            p.y, y = qt_out(mem, (outer, axis, inner), dtype, 1 / 256., -128 if dtype == S8 else 0)
+            p.outer, p.axis_size, p.inner, p.beta = outer, axis, inner, beta
+            return p, [y]
+        return lambda: SimpleCase("softmax_q8", build)
+    return {"classifier_1001": make(101, 8, 1001, 1), "u8_rows_10": make(102, 5, 10, 1, dtype=U8),
+            "inner_axis": make(103, 3, 7, 4, beta=0.5), "single_element": make(104, 4, 1, 1)}
+
+
+def convert_cases():
+    def make(seed, xd, yd, count=1001, xq=(0.05, 3), yq=(0.07, -4)):
+        def build(mem):
+            rng = np.random.default_rng(seed)
+            p = _abi.ConvertParams()
+            if xd == F32:
+                x = (rng.standard_normal(count) * 4).astype(np.float32)
+                p.x = qt(mem, x, F32)
+            else:
+                p.x = qt(mem, _rand(rng, xd, (count,)), xd, *xq)
+            p.y, y = qt_out(mem, (count,), yd, *yq)
+            p.count = count
+            return p, [y]
+        return lambda: SimpleCase("convert_q", build)
+    return {"quantize_f32_s8": make(111, F32, S8), "quantize_f32_u8": make(112, F32, U8, yq=(0.05, 128)),
+            "quantize_f32_s16": make(113, F32, S16, yq=(0.001, 0)), "dequantize_s8": make(114, S8, F32),
+            "dequantize_u8": make(115, U8, F32, xq=(0.1, 120)), "requantize_u8_s8": make(116, U8, S8, xq=(0.05, 128)),
+            "requantize_s16_s8": make(117, S16, S8, xq=(0.0005, 0))}
+
+
+def qlstm_cases():
+    return {
+        "proj_ln": lambda: random_qlstm_case(121, 3, 40, 64, 32),
+        "proj_ln_zero_state": lambda: random_qlstm_case(122, 2, 40, 64, 32, state="zero"),
+        "peephole": lambda: random_qlstm_case(123, 2, 24, 32, 16, peephole=True),
+        "cifg": lambda: random_qlstm_case(124, 2, 24, 32, 16, cifg=True),
+        "no_layer_norm": lambda: random_qlstm_case(125, 2, 24, 32, 16, layer_norm=False),
+        "no_projection": lambda: random_qlstm_case(126, 2, 20, 32, 32, projection=False),
+        "cifg_peephole_unaligned": lambda: random_qlstm_case(127, 2, 13, 19, 11, cifg=True, peephole=True),
+        "config5_layer2_shape": lambda: random_qlstm_case(128, 2, 256, 512, 256),
+    }
+
+
+ALL_GROUPS = {"conv": conv_cases, "dwconv": dwconv_cases, "fc": fc_cases, "bmm": bmm_cases, "pool": pool_cases,
+              "mean": mean_cases, "eltwise": eltwise_cases, "activation": activation_cases, "softmax": softmax_cases,
+              "convert": convert_cases, "qlstm": qlstm_cases}
+
+
+def run_case(case, where):
+    """Outputs of a case as a list of arrays: [y, acc] for contractions, the case's output list otherwise."""
+    if where == "oracle":
+        r = case.run_oracle()
+    elif where == "cpuref":
+        r = case.run_cpuref()
+    else:
+        r = case.run_gpu()
+    if isinstance(r, tuple):
+        return [a for a in r if a is not None]
+    if isinstance(r, list):
+        return r
+    return [r]

@@ -1,0 +1,170 @@
+"""Test-only executors for graphs built with armnn_b200.network:
+
+  OracleNetwork  — runs the optimized graph layer by layer on the plain-C oracle (numpy memory).  It reuses
+                   GraphProgram, so the parameter structs are built by exactly the code the CUDA runtime uses;
+                   only the memory space and the callee differ.
+  ArmnnNetwork   — replays the same (un-optimized) INetwork into the real Arm NN runtime through the C binding
+                   in oracle/_ref/libarmnn_capi.so and runs it on CpuRef or, when the plugin is built and a GPU
+                   is present, on B200Acc.
+"""
+import ctypes as C
+import os
+
+import numpy as np
+
+from q8util import ROOT, cpuref, oracle
+
+from armnn_b200 import _abi
+from armnn_b200.network import _ABI_DTYPE, _NP_DTYPE, DataType, GraphProgram
+
+
+class OracleNetwork(GraphProgram):
+    def __init__(self, optimized):
+        super().__init__(optimized)
+        self._build()
+
+    def _alloc(self, info):
+        return np.zeros(info.shape if info.shape else (1,), dtype=_NP_DTYPE[info.dtype])
+
+    def _upload(self, array):
+        return np.ascontiguousarray(array)
+
+    def _ptr(self, tensor):
+        return tensor.ctypes.data
+
+    def _view(self, tensor, shape):
+        return tensor.reshape(shape)
+
+    def run(self, inputs, keep=None):
+        """inputs: {binding id: ndarray}.  Returns {binding id: ndarray}; `keep`, when a dict, receives
+        every intermediate tensor keyed by producing layer name (and output index)."""
+        for bid, arr in inputs.items():
+            dst = self._dev(self.inputs[bid])
+            dst[...] = np.asarray(arr).reshape(dst.shape).view(dst.dtype)
+        for layer, entry, params in self.workloads:
+            rc = getattr(oracle(), "oracle_" + entry)(C.byref(params))
+            assert rc == 0, "oracle_%s failed for %s" % (entry, layer.name)
+            if keep is not None:
+                for i, o in enumerate(layer.outputs):
+                    keep[layer.name if i == 0 else "%s:%d" % (layer.name, i)] = self._dev(o).copy()
+        return {bid: self._dev(slot).copy() for bid, slot in self.outputs.items()}
+
+
+PLUGIN_DIR = os.path.join(ROOT, "armnn_b200", "backend")
+PLUGIN_PATH = os.path.join(PLUGIN_DIR, "Nv_B200Acc_backend.so")
+
+
+def _shape_arr(shape):
+    return (C.c_int32 * len(shape))(*shape)
+
+
+class ArmnnNetwork:
+    """The same graph inside the real Arm NN runtime."""
+
+    _runtime = None
+
+    @classmethod
+    def runtime(cls):
+        if cls._runtime is None:
+            lib = cpuref()
+            lib.armnnc_runtime_create.restype = C.c_void_p
+            lib.armnnc_network_create.restype = C.c_void_p
+            lib.armnnc_load.restype = C.c_void_p
+            path = PLUGIN_DIR if os.path.exists(PLUGIN_PATH) else ""
+            cls._runtime = C.c_void_p(lib.armnnc_runtime_create(path.encode()))
+            assert cls._runtime.value, lib.cpuref_last_error().decode()
+        return cls._runtime
+
+    @staticmethod
+    def backend_available(name):
+        return bool(cpuref().armnnc_backend_available(ArmnnNetwork.runtime(), name.encode()))
+
+    def __init__(self, network, backends="CpuRef", device_id=-1, profiling=False):
+        lib = cpuref()
+        self.lib = lib
+        rt = self.runtime()
+        net = C.c_void_p(lib.armnnc_network_create())
+        ids = {}
+        self.in_infos, self.out_infos = [], []
+
+        def info_args(info):
+            return (_ABI_DTYPE[info.dtype], len(info.shape), _shape_arr(info.shape), C.c_float(info.scale), info.offset)
+
+        for layer in network.layers:
+            t, d = layer.type, layer.desc
+            if t == "Input":
+                ids[id(layer)] = lib.armnnc_add_input(net, d["id"], *info_args(layer.outputs[0].info))
+                self.in_infos.append((d["id"], layer.outputs[0].info))
+                continue
+            if t == "Constant":
+                info = layer.outputs[0].info
+                sc = info.scales
+                ids[id(layer)] = lib.armnnc_add_constant(
+                    net, _ABI_DTYPE[info.dtype], len(info.shape), _shape_arr(info.shape), C.c_float(info.scale), info.offset,
+                    sc.ctypes.data_as(C.c_void_p) if sc is not None else None, len(sc) if sc is not None else 0,
+                    info.quant_dim or 0, layer.const_data.ctypes.data_as(C.c_void_p))
+                continue
+            if t == "Output":
+                continue
+            if t in ("Convolution2d", "DepthwiseConvolution2d"):
+                lid = lib.armnnc_add_conv2d(net, int(t == "DepthwiseConvolution2d"), d["stride"][0], d["stride"][1],
+                                            d["pad"][0], d["pad"][1], d["pad"][2], d["pad"][3], d["dilation"][0],
+                                            d["dilation"][1], int(d["bias"]))
+            elif t == "FullyConnected":
+                lid = lib.armnnc_add_fully_connected(net, int(d["transpose"]), int(d["bias"]))
+            elif t == "Activation":
+                lid = lib.armnnc_add_activation(net, int(d["function"]), C.c_float(d["a"]), C.c_float(d["b"]))
+            elif t == "Pooling2d":
+                lid = lib.armnnc_add_pool2d(net, int(d["type"]), int(d["method"]), d["pool"][0], d["pool"][1], d["stride"][0],
+                                            d["stride"][1], d["pad"][0], d["pad"][1], d["pad"][2], d["pad"][3])
+            elif t == "ElementwiseBinary":
+                lid = lib.armnnc_add_elementwise_binary(net, int(d["op"]))
+            elif t == "Softmax":
+                lid = lib.armnnc_add_softmax(net, C.c_float(d["beta"]), d["axis"])
+            elif t == "Mean":
+                axes = (C.c_int32 * len(d["axis"]))(*d["axis"])
+                lid = lib.armnnc_add_mean(net, axes, len(d["axis"]), int(d["keep_dims"]))
+            elif t == "Reshape":
+                lid = lib.armnnc_add_reshape(net, len(d["shape"]), _shape_arr(d["shape"]))
+            elif t == "Quantize":
+                lid = lib.armnnc_add_quantize(net)
+            elif t == "Dequantize":
+                lid = lib.armnnc_add_dequantize(net)
+            else:
+                raise NotImplementedError("ArmnnNetwork: layer type %s" % t)
+            ids[id(layer)] = lid
+            for i, o in enumerate(layer.outputs):
+                lib.armnnc_set_output_info(net, lid, i, *info_args(o.info))
+        for layer in network.layers:
+            if layer.type == "Output":
+                src = layer.inputs[0].source
+                lib.armnnc_add_output(net, layer.desc["id"], ids[id(src.layer)], src.index)
+                self.out_infos.append((layer.desc["id"], src.info))
+                continue
+            for s in layer.inputs:
+                lib.armnnc_connect(net, ids[id(s.source.layer)], s.source.index, ids[id(layer)], s.index)
+        self.handle = C.c_void_p(lib.armnnc_load(rt, net, backends.encode(), device_id, int(profiling)))
+        err = lib.cpuref_last_error().decode()
+        lib.armnnc_network_destroy(net)
+        if not self.handle.value:
+            raise RuntimeError("armnn load failed: " + err)
+
+    def run(self, inputs):
+        ins = [np.ascontiguousarray(np.asarray(inputs[bid]).astype(_NP_DTYPE[info.dtype], copy=False)) for bid, info in self.in_infos]
+        outs = [np.zeros(info.shape, dtype=_NP_DTYPE[info.dtype]) for _, info in self.out_infos]
+        in_ptrs = (C.c_void_p * len(ins))(*[a.ctypes.data for a in ins])
+        out_ptrs = (C.c_void_p * len(outs))(*[a.ctypes.data for a in outs])
+        rc = self.lib.armnnc_enqueue(self.handle, in_ptrs, out_ptrs)
+        assert rc == 0, self.lib.cpuref_last_error().decode()
+        return {bid: o for (bid, _), o in zip(self.out_infos, outs)}
+
+    def close(self):
+        if self.handle is not None and self.handle.value:
+            self.lib.armnnc_unload(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -355,3 +355,111 @@ def diff_stats(a, b):
 def saturation(y, dtype):
     lo, hi = RANGE[dtype]
     return float(np.mean((y == lo) | (y == hi)))
+
+
+class QLstmCase:
+    """One QLstm step.  `w` maps ABI field names (w_i2f, ln_c, b_o, w_proj, ...) to numpy arrays;
+    `s` maps scale / scalar field names to numbers.  Absent optional weights disable the option."""
+
+    W_FIELDS = {"w_i2i": np.int8, "w_i2f": np.int8, "w_i2c": np.int8, "w_i2o": np.int8,
+                "w_r2i": np.int8, "w_r2f": np.int8, "w_r2c": np.int8, "w_r2o": np.int8,
+                "w_c2i": np.int16, "w_c2f": np.int16, "w_c2o": np.int16,
+                "b_i": np.int32, "b_f": np.int32, "b_c": np.int32, "b_o": np.int32,
+                "ln_i": np.int16, "ln_f": np.int16, "ln_c": np.int16, "ln_o": np.int16,
+                "w_proj": np.int8, "b_proj": np.int32}
+
+    def __init__(self, x, h, c, w, s):
+        self.x, self.h, self.c, self.w, self.s = x, h, c, w, s
+        self.batch, self.input_size = x.shape
+        self.output_size = h.shape[1]
+        self.num_units = c.shape[1]
+
+    def params(self, mem):
+        p = _abi.QLstmParams()
+        p.batch, p.input_size, p.num_units, p.output_size = self.batch, self.input_size, self.num_units, self.output_size
+        p.input = mem.inp(self.x.astype(np.int8))
+        p.output_state_in = mem.inp(self.h.astype(np.int8))
+        p.cell_state_in = mem.inp(self.c.astype(np.int16))
+        hout, p.output_state_out = mem.out((self.batch, self.output_size), np.int8)
+        cout, p.cell_state_out = mem.out((self.batch, self.num_units), np.int16)
+        out, p.output = mem.out((self.batch, self.output_size), np.int8)
+        for name, dt in self.W_FIELDS.items():
+            if self.w.get(name) is not None:
+                setattr(p, name, mem.inp(np.asarray(self.w[name]).astype(dt)))
+        for name, v in self.s.items():
+            setattr(p, name, v)
+        return p, [hout, cout, out]
+
+    def run_oracle(self):
+        mem = Host()
+        p, outs = self.params(mem)
+        assert oracle().oracle_qlstm_step(C.byref(p)) == 0
+        return outs
+
+    def run_cpuref(self):
+        mem = Host()
+        p, outs = self.params(mem)
+        rc = cpuref().cpuref_qlstm_step(C.byref(p))
+        assert rc == 0, cpuref().cpuref_last_error().decode()
+        return outs
+
+    def run_gpu(self):
+        from armnn_b200 import lib
+        mem = Cuda()
+        p, outs = self.params(mem)
+        lib.call("qlstm_step", p)
+        return [mem.fetch(o) for o in outs]
+
+
+def qlstm_scales(input_scale=0.0078125, out_scale=0.007, ln_scale=3.05182e-05, w_scale=0.00784314,
+                 proj_scale=0.00392157, cell_scale=3.05176e-05, layer_norm=True, projection=True):
+    """Quantisation parameters of the reference's projection + layer-norm QLstm test
+    (src/backends/backendsCommon/test/layerTests/LstmTestImpl.cpp:1937-1968)."""
+    f32 = lambda v: float(np.float32(v))
+    s = dict(input_scale=f32(input_scale), input_zp=0, output_state_scale=f32(out_scale), output_state_zp=0,
+             cell_state_scale=f32(cell_scale), output_scale=f32(out_scale), output_zp=0,
+             cell_clip=0.0, projection_clip=0.0,
+             input_intermediate_scale=f32(0.007059), forget_intermediate_scale=f32(0.007812),
+             cell_intermediate_scale=f32(0.007059), output_intermediate_scale=f32(0.007812),
+             hidden_state_scale=f32(0.007), hidden_state_zp=0)
+    for g in "ifco":
+        s["s_i2" + g] = f32(w_scale)
+        s["s_r2" + g] = f32(w_scale)
+    for g in "ifco":
+        s["s_b" + g] = float(np.float32(ln_scale) / np.float32(1024))
+        if layer_norm:
+            s["s_ln" + g] = f32(ln_scale)
+    if projection:
+        s["s_proj"] = f32(proj_scale)
+    return s
+
+
+def random_qlstm_case(seed, batch, input_size, num_units, output_size, layer_norm=True, projection=True, cifg=False,
+                      peephole=False, state="random"):
+    rng = np.random.default_rng(seed)
+    x = rng.integers(-128, 128, size=(batch, input_size)).astype(np.int8)
+    if state == "zero":
+        h = np.zeros((batch, output_size), np.int8)
+        c = np.zeros((batch, num_units), np.int16)
+    else:
+        h = rng.integers(-128, 128, size=(batch, output_size)).astype(np.int8)
+        c = rng.integers(-20000, 20000, size=(batch, num_units)).astype(np.int16)
+    w = {}
+    gates = "fco" if cifg else "ifco"
+    for g in gates:
+        w["w_i2" + g] = rng.integers(-127, 128, size=(num_units, input_size)).astype(np.int8)
+        w["w_r2" + g] = rng.integers(-127, 128, size=(num_units, output_size)).astype(np.int8)
+        # gate biases are mandatory in the descriptor although CpuRef only reads them with layer norm
+        w["b_" + g] = rng.integers(-8000000, 8000000, size=num_units).astype(np.int32)
+        if layer_norm:
+            w["ln_" + g] = rng.integers(3000, 30000, size=num_units).astype(np.int16)
+    if peephole:
+        for g in ("fo" if cifg else "ifo"):
+            w["w_c2" + g] = rng.integers(-20000, 20000, size=num_units).astype(np.int16)
+    if projection:
+        w["w_proj"] = rng.integers(-127, 128, size=(output_size, num_units)).astype(np.int8)
+    s = qlstm_scales(layer_norm=layer_norm, projection=projection)
+    if peephole:
+        for g in "ifo":
+            s["s_c2" + g] = float(np.float32(2.0 ** -15))
+    return QLstmCase(x, h, c, w, s)
