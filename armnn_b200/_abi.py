@@ -125,7 +125,7 @@ KERNEL_ENTRY_POINTS = {
 # every symbol include/b200k.h declares
 EXPORTED_SYMBOLS = ["b200k_" + k for k in KERNEL_ENTRY_POINTS] + [
     "b200k_device_open", "b200k_device_count", "b200k_last_error", "b200k_version",
-    "b200k_activation_clamp", "b200k_conv2d_pack_bytes", "b200k_conv2d_pack",
+    "b200k_activation_clamp", "b200k_conv2d_pack_bytes", "b200k_conv2d_pack", "b200k_sizeof_params",
 ]
 
 

@@ -82,3 +82,22 @@ extern "C" int b200k_activation_clamp(int kind, float a, float b, float scale, i
     *clamp_hi = hi;
     return B200K_OK;
 }
+
+// Size of each parameter struct as this library was compiled, so that a binding in another language can
+// check its own declaration of the struct against the header it was written from.
+extern "C" size_t b200k_sizeof_params(int which)
+{
+    switch (which) {
+        case 0: return sizeof(b200k_conv2d_params);
+        case 1: return sizeof(b200k_fc_params);
+        case 2: return sizeof(b200k_bmm_params);
+        case 3: return sizeof(b200k_pool2d_params);
+        case 4: return sizeof(b200k_mean_params);
+        case 5: return sizeof(b200k_eltwise_params);
+        case 6: return sizeof(b200k_activation_params);
+        case 7: return sizeof(b200k_softmax_params);
+        case 8: return sizeof(b200k_convert_params);
+        case 9: return sizeof(b200k_qlstm_params);
+        default: return 0;
+    }
+}

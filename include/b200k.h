@@ -261,6 +261,11 @@ typedef struct {
 
 int b200k_qlstm_step(const b200k_qlstm_params* p, void* stream);
 
+/* sizeof() of a parameter struct as compiled into the library, for bindings in other languages to check their
+ * own declarations: 0 conv2d, 1 fc, 2 bmm, 3 pool2d, 4 mean, 5 eltwise, 6 activation, 7 softmax, 8 convert,
+ * 9 qlstm.  No counterpart in the reference (its backends are linked as C++). */
+size_t b200k_sizeof_params(int which);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,97 @@
+"""Host-side logic of the INetwork -> Optimize -> LoadNetwork mirror, and whole graphs on the CPU oracle against
+the real Arm NN runtime on CpuRef (free-running, graph level).  No GPU needed."""
+import numpy as np
+import pytest
+
+from armnn_b200 import configs, network
+from armnn_b200.network import (ActivationFunction, DataType, INetwork, InvalidArgumentException, Optimize, TensorInfo)
+from q8util import diff_stats, have_cpuref
+
+needs_cpuref = pytest.mark.skipif(not have_cpuref(), reason="oracle/_ref not built (reference sources absent)")
+
+
+def _conv_relu(out_q_conv, out_q_act):
+    net = INetwork.Create()
+    il = net.AddInputLayer(0)
+    il.GetOutputSlot(0).SetTensorInfo(TensorInfo((1, 4, 4, 16), DataType.QAsymmS8, 0.1, 0))
+    w = net.AddConstantLayer(np.ones((16, 1, 1, 16), np.int8), TensorInfo((16, 1, 1, 16), DataType.QSymmS8, 0.1, 0))
+    cl = net.AddConvolution2dLayer(bias_enabled=False)
+    il.GetOutputSlot(0).Connect(cl.GetInputSlot(0))
+    w.GetOutputSlot(0).Connect(cl.GetInputSlot(1))
+    cl.GetOutputSlot(0).SetTensorInfo(TensorInfo((1, 4, 4, 16), DataType.QAsymmS8, *out_q_conv))
+    al = net.AddActivationLayer(ActivationFunction.ReLu)
+    cl.GetOutputSlot(0).Connect(al.GetInputSlot(0))
+    al.GetOutputSlot(0).SetTensorInfo(TensorInfo((1, 4, 4, 16), DataType.QAsymmS8, *out_q_act))
+    ol = net.AddOutputLayer(0)
+    al.GetOutputSlot(0).Connect(ol.GetInputSlot(0))
+    return net
+
+
+def test_optimize_fuses_relu_only_when_quantisation_matches():
+    opt = Optimize(_conv_relu((0.2, -128), (0.2, -128)))
+    types = [l.type for l in opt.layers]
+    assert "Activation" not in types
+    conv = [l for l in opt.layers if l.type == "Convolution2d"][0]
+    assert conv.fused_activation[0] == ActivationFunction.ReLu
+    opt = Optimize(_conv_relu((0.2, -128), (0.1, -128)))
+    assert "Activation" in [l.type for l in opt.layers]
+
+
+def test_optimize_refuses_unsupported_layers_there_is_no_cpu_fallback():
+    net = INetwork.Create()
+    il = net.AddInputLayer(0)
+    il.GetOutputSlot(0).SetTensorInfo(TensorInfo((2, 3, 4), DataType.QAsymmS8, 0.1, 0))
+    il2 = net.AddInputLayer(1)
+    il2.GetOutputSlot(0).SetTensorInfo(TensorInfo((2, 4, 4), DataType.QAsymmS8, 0.1, 0))
+    b = net.AddBatchMatMulLayer(adjoint_y=True)
+    il.GetOutputSlot(0).Connect(b.GetInputSlot(0))
+    il2.GetOutputSlot(0).Connect(b.GetInputSlot(1))
+    b.GetOutputSlot(0).SetTensorInfo(TensorInfo((2, 3, 4), DataType.QAsymmS8, 0.1, 0))
+    with pytest.raises(InvalidArgumentException, match="adjoint"):
+        Optimize(net)
+    with pytest.raises(InvalidArgumentException):
+        Optimize(_conv_relu((0.2, 0), (0.2, 0)), ["CpuRef"])
+
+
+def test_resnet50_layer_list_and_mac_count():
+    net, info = configs.resnet50(1, 224)
+    convs = [l for l in info["layers"] if l[1].startswith("conv")]
+    assert len(convs) == 53                                   # stem + 16 blocks x 3 + 4 projection shortcuts
+    assert info["macs"] == 4089186304                         # 4.09 GMAC per 224x224 image
+    opt = Optimize(net)
+    assert sum(1 for l in opt.layers if l.type == "Activation") == 0      # every ReLU fused
+    assert sum(1 for l in opt.layers if l.type == "ElementwiseBinary") == 16
+
+
+def _run_pair(net, info, dtype):
+    import hostnet
+    rng = np.random.default_rng(3)
+    lo, hi = (0, 256) if dtype == np.uint8 else (-128, 128)
+    x = rng.integers(lo, hi, size=info["input_shape"]).astype(dtype)
+    want = hostnet.ArmnnNetwork(net, "CpuRef").run({0: x})[0]
+    got = hostnet.OracleNetwork(Optimize(net)).run({0: x})[0]
+    return want, got
+
+
+@needs_cpuref
+def test_single_conv_graph_oracle_vs_armnn_cpuref(built):
+    want, got = _run_pair(*configs.single_conv(), np.int8)
+    st = diff_stats(want, got)
+    assert st["max_abs"] <= 1 and st["mismatch_frac"] < 1e-3, st
+
+
+@needs_cpuref
+def test_resnet50_reduced_oracle_vs_armnn_cpuref_free_running(built):
+    """Whole ResNet-50 graph (2 x 64 x 64 input) through the real Arm NN Optimizer/Runtime on CpuRef versus the
+    fused graph on the integer oracle: class scores within +-1 LSB."""
+    want, got = _run_pair(*configs.resnet50(2, 64), np.int8)
+    st = diff_stats(want, got)
+    assert st["max_abs"] <= 1 and st["mismatch_frac"] < 0.02, st
+    assert np.array_equal(want.argmax(1), got.argmax(1))
+
+
+@needs_cpuref
+def test_mobilenet_v2_reduced_oracle_vs_armnn_cpuref_free_running(built):
+    want, got = _run_pair(*configs.mobilenet_v2(1, 64), np.uint8)
+    st = diff_stats(want, got)
+    assert st["max_abs"] <= 2 and st["mismatch_frac"] < 0.05, st
