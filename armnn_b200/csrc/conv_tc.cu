@@ -1,0 +1,542 @@
+// tcgen05 implicit-GEMM Convolution2d / FullyConnected for 8-bit quantised NHWC tensors (sm_100a).
+//
+// GEMM view: D[M, N] = A[M, K] * B[N, K]^T with M = output pixels (n, oy, ox), N = output channels and
+// K = (ky, kx, c).  One CTA computes a 128 x BN tile of D:
+//   * a producer thread feeds a multi-stage shared-memory ring with TMA.  The weight tile is a plain 2-D box of
+//     the [OC, KH*KW*C] matrix.  The activation tile is fetched either as a 2-D box of [M, C] (1x1 stride-1
+//     convolutions and FullyConnected) or with TMA's im2col mode straight from the NHWC tensor: one copy
+//     delivers, for 128 consecutive output pixels, the channel slice of one filter tap, zero-filling taps that
+//     fall outside the image.  Both land in the 128-byte (or 64-byte) swizzled K-major layout tcgen05 reads.
+//   * one thread issues tcgen05.mma.kind::i8 (M = 128, N = BN, K = 32 per instruction); the int32 accumulator
+//     lives in tensor memory (BN columns x 128 lanes); tcgen05.commit releases ring slots and finally signals
+//     the epilogue.
+//   * eight epilogue warps read the accumulator with tcgen05.ld, apply the zero-point correction, bias and the
+//     fp32 requantisation, and store 8-bit outputs.
+//
+// Zero points.  TMA fills out-of-image taps with raw zeros, whereas the reference pads with the real value 0,
+// i.e. with the quantised value zx.  With symmetric weights (zw = 0)
+//     sum_valid (x - zx) w = sum_all x_filled w - zx * sum_valid w
+// and sum_valid w for an output pixel is the sum of per-tap channel sums over the rectangle of in-image taps,
+// read from a 2-D prefix table over (ky, kx) that b200k_conv2d_pack builds once per weight tensor.
+//
+// Requantisation is the same function as in the CUDA-core kernel and the CPU oracle (IEEE fp32, unfused).  The
+// division v / scale is evaluated as a multiplication by the reciprocal whenever the product is provably not
+// within reach of a rounding tie, and falls back to the exact division otherwise, so results are bit-identical.
+//
+// Every wait on an mbarrier is bounded; when a bound is hit the kernel raises a status word (read with
+// b200k_poll_status), drains and returns, so a logic error cannot hang the device.
+#include <cuda.h>
+#include <cudaTypedefs.h>
+#include "common.cuh"
+
+namespace b200k {
+
+constexpr int TC_BM = 128;
+constexpr int TC_THREADS = 320;                 // warp 0 producer, warp 1 MMA, warps 2-9 epilogue
+constexpr unsigned TC_SPIN_LIMIT = 1u << 22;
+
+__device__ int g_tc_status = 0;                 // 0 ok, otherwise the code of the wait that gave up
+
+struct TcArgs {
+    const int32_t* bias; void* y; int32_t* acc_out;
+    const float* w_scales; const float* b_scales;
+    const int32_t* prefix;                      // [(KH+1)*(KW+1)][OC] or null
+    float w_scale, b_scale;
+    int zx;                                     // true input zero point
+    int N, H, W, C, OH, OW, OC, KH, KW, sh, sw, pt, pl, dh, dw;
+    long long M;
+    int im2col;                                 // 0: A is a 2-D [M, C] matrix; 1: TMA im2col from NHWC
+    int cchunks;                                // C / BK
+    int nslices;                                // KH*KW*cchunks
+    int need_corr;                              // zx != 0
+    int need_rect;                              // need_corr and some tap can fall outside the image
+    int a_signed, b_signed;                     // operand element types: 1 = int8, 0 = uint8
+    Requant rq;
+    float inv_sy;
+};
+
+// ---- PTX wrappers --------------------------------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Bounded wait: returns false when the limit is hit.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity)
+{
+    const uint32_t addr = smem_u32(bar);
+    for (unsigned i = 0; i < TC_SPIN_LIMIT; ++i) {
+        uint32_t ok;
+        asm volatile("{\n\t.reg .pred p;\n\t"
+                     "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                     "selp.b32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y)
+{
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(smem_u32(dst)), "l"((uint64_t)map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tma_load_im2col(void* dst, const CUtensorMap* map, uint64_t* bar, int c, int w, int h,
+                                                int n, uint16_t off_w, uint16_t off_h)
+{
+    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes"
+                 " [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};"
+                 ::"r"(smem_u32(dst)), "l"((uint64_t)map), "r"(smem_u32(bar)), "r"(c), "r"(w), "r"(h), "r"(n),
+                   "h"(off_w), "h"(off_h) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after()  { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma_i8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "setp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t* r)
+{
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32"
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15,"
+                 " %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are one swizzle span (SWZ bytes) long:
+// 8-row groups are 8 * SWZ bytes apart (stride byte offset); the leading byte offset is unused for swizzled
+// K-major layouts; descriptor version 1; layout type 2 = 128-byte swizzle, 4 = 64-byte swizzle.
+template <int SWZ>
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFF) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)((8 * SWZ) >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)(SWZ == 128 ? 2 : 4) << 61;
+    return d;
+}
+
+// Quantize(v, sy, zy) with the division replaced by a reciprocal multiply when that cannot change the result.
+__device__ __forceinline__ int quantize_fast(float v, const Requant& rq, float inv_sy)
+{
+    const float y = __fmul_rn(v, inv_sy);
+    float r;
+    if (fabsf(y) < 512.f) {
+        const float n = rintf(y);
+        // |y - v/sy| <= 2^-13 here; away from a tie by more than 2^-10 the nearest integer is the answer
+        if (fabsf(fabsf(__fsub_rn(y, n)) - 0.5f) > 0.0009765625f) r = n;
+        else r = roundf(__fdiv_rn(v, rq.sy));
+    } else {
+        // beyond +-512 every 8-bit output clamps; only the sign matters (NaN cannot occur: finite inputs)
+        r = roundf(__fdiv_rn(v, rq.sy));
+    }
+    float q = __fadd_rn(__int2float_rn(rq.zy), r);
+    q = fminf(fmaxf(q, rq.tlo), rq.thi);
+    return min(max(__float2int_rz(q), rq.clo), rq.chi);
+}
+
+template <int BN, int SWZ, int STAGES>
+struct TcSmem {
+    static constexpr int A_BYTES = TC_BM * SWZ;
+    static constexpr int B_BYTES = BN * SWZ;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
+    // after the ring: float m[BN], float bterm[BN], barriers, tmem slot; the prefix slice follows (dynamic size)
+    static constexpr int FIXED_BYTES = RING_BYTES + 2 * BN * 4 + (2 * STAGES + 1) * 8 + 16;
+};
+
+template <int BN, int SWZ, int STAGES>
+__global__ void __launch_bounds__(TC_THREADS, (BN <= 128 ? 2 : 1))
+conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const TcArgs a)
+{
+    using L = TcSmem<BN, SWZ, STAGES>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    float* s_m = (float*)(smem + L::RING_BYTES);
+    float* s_bterm = s_m + BN;
+    uint64_t* full = (uint64_t*)(s_bterm + BN);
+    uint64_t* empty = full + STAGES;
+    uint64_t* acc_full = empty + STAGES;
+    uint32_t* tmem_slot = (uint32_t*)(acc_full + 1);
+    int32_t* s_prefix = (int32_t*)(tmem_slot + 4);          // [(KH+1)*(KW+1)][BN] when need_corr
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * BN;                         // first output channel of the tile
+    const long long m0 = (long long)blockIdx.y * TC_BM;     // first output pixel of the tile
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        mbar_init(acc_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    // per-channel epilogue constants of this tile
+    for (int j = threadIdx.x; j < BN; j += TC_THREADS) {
+        const int ch = n0 + j;
+        float mm = 0.f, bt = 0.f;
+        if (ch < a.OC) {
+            mm = __fmul_rn(a.rq.sx, a.w_scales ? a.w_scales[ch] : a.w_scale);
+            if (a.bias) bt = __fmul_rn(__int2float_rn(a.bias[ch]), a.b_scales ? a.b_scales[ch] : a.b_scale);
+        }
+        s_m[j] = mm;
+        s_bterm[j] = bt;
+    }
+    if (a.need_corr) {
+        const int cells = (a.KH + 1) * (a.KW + 1);
+        for (int i = threadIdx.x; i < cells * BN; i += TC_THREADS) {
+            const int cell = i / BN, j = i - cell * BN;
+            s_prefix[i] = (n0 + j < a.OC) ? a.prefix[(long long)cell * a.OC + n0 + j] : 0;
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ===================== TMA producer =====================
+        if (lane == 0) {
+            int w0 = 0, h0 = 0, nimg = 0;
+            if (a.im2col) {
+                const int ox = (int)(m0 % a.OW);
+                const long long t = m0 / a.OW;
+                const int oy = (int)(t % a.OH);
+                nimg = (int)(t / a.OH);
+                w0 = ox * a.sw - a.pl;
+                h0 = oy * a.sh - a.pt;
+            }
+            for (int s = 0; s < a.nslices; ++s) {
+                const int st = s % STAGES;
+                const uint32_t ph = (uint32_t)(s / STAGES) & 1u;
+                if (!mbar_wait(&empty[st], ph ^ 1u)) { atomicExch(&g_tc_status, 1); break; }
+                const int tap = s / a.cchunks;
+                const int c0 = (s - tap * a.cchunks) * SWZ;
+                uint8_t* sa = smem + st * L::STAGE_BYTES;
+                uint8_t* sb = sa + L::A_BYTES;
+                mbar_expect_tx(&full[st], L::STAGE_BYTES);
+                if (a.im2col) {
+                    const int ky = tap / a.KW, kx = tap - ky * a.KW;
+                    tma_load_im2col(sa, &tmA, &full[st], c0, w0, h0, nimg, (uint16_t)(kx * a.dw), (uint16_t)(ky * a.dh));
+                } else {
+                    tma_load_2d(sa, &tmA, &full[st], c0, (int)m0);
+                }
+                tma_load_2d(sb, &tmB, &full[st], tap * a.C + c0, n0);
+            }
+        }
+    } else if (warp == 1) {
+        // ===================== MMA issuer =====================
+        if (lane == 0) {
+            // instruction descriptor: D = S32 (bits 4-5 = 2); A / B format at bits 7 / 10 (1 = signed 8-bit,
+            // 0 = unsigned 8-bit); both operands K-major (bits 15, 16 = 0); N >> 3 at bit 17; M >> 4 at bit 24
+            const uint32_t id = (2u << 4) | ((uint32_t)a.a_signed << 7) | ((uint32_t)a.b_signed << 10) |
+                                ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+            for (int s = 0; s < a.nslices; ++s) {
+                const int st = s % STAGES;
+                const uint32_t ph = (uint32_t)(s / STAGES) & 1u;
+                if (!mbar_wait(&full[st], ph)) { atomicExch(&g_tc_status, 2); break; }
+                tc_fence_after();
+                const uint32_t sa = smem_u32(smem + st * L::STAGE_BYTES);
+                const uint64_t da = make_smem_desc<SWZ>(sa);
+                const uint64_t db = make_smem_desc<SWZ>(sa + L::A_BYTES);
+                #pragma unroll
+                for (int k = 0; k < SWZ / 32; ++k)
+                    tc_mma_i8(tmem_base, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), id, (s > 0 || k > 0) ? 1u : 0u);
+                tc_commit(&empty[st]);             // slot reusable once these MMAs have read it
+            }
+            tc_commit(acc_full);                   // accumulator complete
+        }
+    } else {
+        // ===================== epilogue =====================
+        const int ew = warp - 2;                   // 0..7
+        const int quad = warp & 3;                 // TMEM lane quadrant this warp may access
+        const int half = ew >> 2;                  // which half of the columns
+        const bool ok = mbar_wait(acc_full, 0);
+        if (!ok) atomicExch(&g_tc_status, 3);
+        tc_fence_after();
+        const int row = quad * 32 + lane;
+        const long long m = m0 + row;
+        const bool mvalid = m < a.M;
+        // rectangle of in-image taps of this pixel
+        int ky0 = 0, ky1 = a.KH, kx0 = 0, kx1 = a.KW;
+        if (a.need_rect) {
+            const int ox = (int)(m % a.OW);
+            const long long t = m / a.OW;
+            const int oy = (int)(t % a.OH);
+            const int iy = oy * a.sh - a.pt, ix = ox * a.sw - a.pl;
+            // smallest k with iy + k*d >= 0, first k with iy + k*d >= H
+            ky0 = iy < 0 ? (-iy + a.dh - 1) / a.dh : 0;
+            ky1 = iy >= a.H ? 0 : min(a.KH, (a.H - 1 - iy) / a.dh + 1);
+            kx0 = ix < 0 ? (-ix + a.dw - 1) / a.dw : 0;
+            kx1 = ix >= a.W ? 0 : min(a.KW, (a.W - 1 - ix) / a.dw + 1);
+            ky0 = min(ky0, a.KH); kx0 = min(kx0, a.KW);
+            ky1 = max(ky1, ky0);  kx1 = max(kx1, kx0);
+        }
+        const int pw = a.KW + 1;
+        const int32_t* p11 = s_prefix + (ky1 * pw + kx1) * BN;
+        const int32_t* p01 = s_prefix + (ky0 * pw + kx1) * BN;
+        const int32_t* p10 = s_prefix + (ky1 * pw + kx0) * BN;
+        const int32_t* p00 = s_prefix + (ky0 * pw + kx0) * BN;
+        const bool has_bias = a.bias != nullptr;
+        constexpr int COLS_PER_HALF = BN / 2;
+        #pragma unroll 1
+        for (int cb = 0; cb < COLS_PER_HALF; cb += 32) {
+            const int col0 = half * COLS_PER_HALF + cb;
+            uint32_t r[32];
+            if (ok) tc_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)col0, r);
+            if (!mvalid || !ok) continue;
+            uint32_t packed[8];
+            #pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const int col = col0 + j;
+                int acc = (int)r[j];
+                if (a.need_corr) acc -= a.zx * (p11[col] - p01[col] - p10[col] + p00[col]);
+                if (a.acc_out && n0 + col < a.OC) a.acc_out[m * a.OC + n0 + col] = acc;
+                float v = __fmul_rn(__int2float_rn(acc), s_m[col]);
+                if (has_bias) v = __fadd_rn(v, s_bterm[col]);
+                const int q = quantize_fast(v, a.rq, a.inv_sy);
+                if ((j & 3) == 0) packed[j >> 2] = 0;
+                packed[j >> 2] |= (uint32_t)(q & 0xff) << (8 * (j & 3));
+            }
+            if (n0 + col0 + 31 < a.OC) {
+                uint4* dst = (uint4*)((uint8_t*)a.y + m * a.OC + n0 + col0);
+                dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+            } else {
+                uint8_t* dst = (uint8_t*)a.y + m * a.OC + n0 + col0;
+                for (int j = 0; j < 32; ++j)
+                    if (n0 + col0 + j < a.OC) dst[j] = (uint8_t)(packed[j >> 2] >> (8 * (j & 3)));
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(BN) : "memory");
+    }
+}
+
+// ---- weight preparation: per-tap channel sums as a 2-D prefix table --------------------------------------------
+
+struct PackArgs { const uint8_t* w; int32_t* prefix; int w_u8, OC, KH, KW, C; };
+
+// prefix[(ky, kx)][oc] = sum over taps (y < ky, x < kx) and all channels of the raw weight value
+__global__ void conv_prefix_kernel(const PackArgs a)
+{
+    const int oc = blockIdx.x * blockDim.x + threadIdx.x;
+    if (oc >= a.OC) return;
+    const int pw = a.KW + 1;
+    for (int kx = 0; kx <= a.KW; ++kx) a.prefix[(long long)kx * a.OC + oc] = 0;
+    for (int ky = 1; ky <= a.KH; ++ky) {
+        a.prefix[(long long)(ky * pw) * a.OC + oc] = 0;
+        int rowsum = 0;
+        for (int kx = 1; kx <= a.KW; ++kx) {
+            const uint8_t* wp = a.w + (((long long)oc * a.KH + (ky - 1)) * a.KW + (kx - 1)) * a.C;
+            int s = 0;
+            for (int c = 0; c < a.C; ++c) s += a.w_u8 ? (int)wp[c] : (int)(int8_t)wp[c];
+            rowsum += s;
+            a.prefix[(long long)(ky * pw + kx) * a.OC + oc] = a.prefix[(long long)((ky - 1) * pw + kx) * a.OC + oc] + rowsum;
+        }
+    }
+}
+
+// ---- host side ---------------------------------------------------------------------------------------------------
+
+static PFN_cuTensorMapEncodeTiled_v12000 g_encode_tiled = nullptr;
+static PFN_cuTensorMapEncodeIm2col_v12000 g_encode_im2col = nullptr;
+
+static bool load_driver_entry_points()
+{
+    if (g_encode_tiled && g_encode_im2col) return true;
+    cudaDriverEntryPointQueryResult q;
+    void* f = nullptr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess || !f) return false;
+    g_encode_tiled = (PFN_cuTensorMapEncodeTiled_v12000)f;
+    f = nullptr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &f, cudaEnableDefault, &q) != cudaSuccess || !f) return false;
+    g_encode_im2col = (PFN_cuTensorMapEncodeIm2col_v12000)f;
+    return true;
+}
+
+static int pick_bn(int oc) { return (oc % 256 == 0) ? 256 : (oc % 128 == 0) ? 128 : 64; }
+
+bool conv_tc_eligible(const b200k_conv2d_params* p)
+{
+    if (!p->x.data || !p->w.data || !p->y.data) return false;
+    if (!is_q8(p->x.dtype) || !is_q8(p->w.dtype) || !is_q8(p->y.dtype)) return false;
+    if (p->c % 64 != 0 || p->oc % 64 != 0) return false;
+    if (p->w.zero_point != 0) return false;                              // symmetric weights only on this path
+    if ((((uintptr_t)p->x.data | (uintptr_t)p->w.data | (uintptr_t)p->y.data) & 15) != 0) return false;
+    if (p->x.zero_point != 0 && !p->packed) return false;              // needs the prefix table
+    if (p->kh > 15 || p->kw > 15) return false;
+    if (p->kh * p->dil_h > 255 || p->kw * p->dil_w > 255) return false;
+    if (p->stride_h > 8 || p->stride_w > 8) return false;
+    const long long M = (long long)p->n * p->oh * p->ow;
+    if ((M + TC_BM - 1) / TC_BM > 65535) return false;
+    const bool gemm = p->kh == 1 && p->kw == 1 && p->stride_h == 1 && p->stride_w == 1 && p->pad_top == 0 &&
+                      p->pad_left == 0 && p->oh == p->h && p->ow == p->wd;
+    if (!gemm) {
+        // im2col corners must fit the descriptor's signed 8-bit fields
+        const int up_w = (p->ow - 1) * p->stride_w + 1 - p->pad_left - p->wd;
+        const int up_h = (p->oh - 1) * p->stride_h + 1 - p->pad_top - p->h;
+        if (p->pad_left > 127 || p->pad_top > 127 || up_w < -128 || up_w > 127 || up_h < -128 || up_h > 127) return false;
+    }
+    const int bn = pick_bn(p->oc);
+    const size_t prefix_bytes = p->x.zero_point != 0 ? (size_t)(p->kh + 1) * (p->kw + 1) * bn * 4 : 0;
+    if (prefix_bytes > 48 * 1024) return false;
+    return true;
+}
+
+template <int BN, int SWZ, int STAGES>
+static int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const TcArgs& a, size_t prefix_bytes, cudaStream_t stream)
+{
+    using L = TcSmem<BN, SWZ, STAGES>;
+    const size_t smem = 1024 + L::FIXED_BYTES + prefix_bytes;
+    auto kern = conv_tc_kernel<BN, SWZ, STAGES>;
+    B200K_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    dim3 grid(div_up(a.OC, BN), div_up(a.M, TC_BM));
+    kern<<<grid, TC_THREADS, smem, stream>>>(tmA, tmB, a);
+    return check_launch("conv_tc_kernel");
+}
+
+int launch_conv_tc(const b200k_conv2d_params* p, cudaStream_t stream)
+{
+    B200K_REQUIRE(conv_tc_eligible(p), B200K_E_UNSUPPORTED, "conv2d_q8: not eligible for the tcgen05 kernel");
+    B200K_REQUIRE(load_driver_entry_points(), B200K_E_CUDA, "conv2d_q8: cuTensorMapEncode* not available from the driver");
+    TcArgs a;
+    a.bias = (const int32_t*)p->bias.data; a.y = (void*)p->y.data; a.acc_out = p->acc_out;
+    a.w_scales = p->w.scales; a.b_scales = p->bias.scales; a.w_scale = p->w.scale; a.b_scale = p->bias.scale;
+    a.prefix = (const int32_t*)p->packed;
+    a.zx = p->x.zero_point;
+    a.N = p->n; a.H = p->h; a.W = p->wd; a.C = p->c; a.OH = p->oh; a.OW = p->ow; a.OC = p->oc;
+    a.KH = p->kh; a.KW = p->kw; a.sh = p->stride_h; a.sw = p->stride_w; a.pt = p->pad_top; a.pl = p->pad_left;
+    a.dh = p->dil_h; a.dw = p->dil_w;
+    a.M = (long long)p->n * p->oh * p->ow;
+    const bool gemm = p->kh == 1 && p->kw == 1 && p->stride_h == 1 && p->stride_w == 1 && p->pad_top == 0 &&
+                      p->pad_left == 0 && p->oh == p->h && p->ow == p->wd;
+    a.im2col = gemm ? 0 : 1;
+    const int swz = (p->c % 128 == 0) ? 128 : 64;
+    a.cchunks = p->c / swz;
+    a.nslices = p->kh * p->kw * a.cchunks;
+    a.need_corr = a.zx != 0;
+    // can any tap of any output pixel leave the image?
+    const int last_y = (p->oh - 1) * p->stride_h - p->pad_top + (p->kh - 1) * p->dil_h;
+    const int last_x = (p->ow - 1) * p->stride_w - p->pad_left + (p->kw - 1) * p->dil_w;
+    const int rect = (a.need_corr && (p->pad_top > 0 || p->pad_left > 0 || last_y >= p->h || last_x >= p->wd)) ? 1 : 0;
+    a.need_rect = rect;
+    a.a_signed = p->x.dtype == B200K_S8;
+    a.b_signed = p->w.dtype == B200K_S8;
+    a.rq = make_requant(p->x.scale, p->y, p->clamp_lo, p->clamp_hi);
+    a.inv_sy = 1.0f / p->y.scale;
+
+    const int bn = pick_bn(p->oc);
+    CUtensorMap tmA, tmB;
+    const CUtensorMapSwizzle swizzle = swz == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+    {   // weights: 2-D [OC][K] matrix, box = swz bytes x bn rows
+        const cuuint64_t K = (cuuint64_t)p->kh * p->kw * p->c;
+        cuuint64_t dims[2] = {K, (cuuint64_t)p->oc};
+        cuuint64_t strides[1] = {K};
+        cuuint32_t box[2] = {(cuuint32_t)swz, (cuuint32_t)bn};
+        cuuint32_t estr[2] = {1, 1};
+        CUresult r = g_encode_tiled(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void*)p->w.data, dims, strides, box, estr,
+                                    CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        B200K_REQUIRE(r == CUDA_SUCCESS, B200K_E_CUDA, "conv2d_q8: cuTensorMapEncodeTiled(weights) failed with %d", (int)r);
+    }
+    if (gemm) {
+        cuuint64_t dims[2] = {(cuuint64_t)p->c, (cuuint64_t)a.M};
+        cuuint64_t strides[1] = {(cuuint64_t)p->c};
+        cuuint32_t box[2] = {(cuuint32_t)swz, (cuuint32_t)TC_BM};
+        cuuint32_t estr[2] = {1, 1};
+        CUresult r = g_encode_tiled(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void*)p->x.data, dims, strides, box, estr,
+                                    CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        B200K_REQUIRE(r == CUDA_SUCCESS, B200K_E_CUDA, "conv2d_q8: cuTensorMapEncodeTiled(input) failed with %d", (int)r);
+    } else {
+        cuuint64_t dims[4] = {(cuuint64_t)p->c, (cuuint64_t)p->wd, (cuuint64_t)p->h, (cuuint64_t)p->n};
+        cuuint64_t strides[3] = {(cuuint64_t)p->c, (cuuint64_t)p->wd * p->c, (cuuint64_t)p->h * p->wd * p->c};
+        int lower[2] = {-p->pad_left, -p->pad_top};
+        int upper[2] = {(p->ow - 1) * p->stride_w + 1 - p->pad_left - p->wd, (p->oh - 1) * p->stride_h + 1 - p->pad_top - p->h};
+        cuuint32_t estr[4] = {1, (cuuint32_t)p->stride_w, (cuuint32_t)p->stride_h, 1};
+        CUresult r = g_encode_im2col(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, (void*)p->x.data, dims, strides, lower, upper,
+                                     (cuuint32_t)swz, (cuuint32_t)TC_BM, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
+                                     CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        B200K_REQUIRE(r == CUDA_SUCCESS, B200K_E_CUDA, "conv2d_q8: cuTensorMapEncodeIm2col failed with %d", (int)r);
+        // Drivers up to 13.1 mis-encode im2col maps of tensors smaller than 128 KiB; the open-source CUTLASS
+        // im2col copy traits clear bit 21 of the second descriptor word in that case, and so does this.
+        int drv = 0;
+        if (cudaDriverGetVersion(&drv) == cudaSuccess && drv <= 13010 &&
+            (size_t)p->n * p->h * p->wd * p->c < 131072)
+            reinterpret_cast<uint64_t*>(&tmA)[1] &= ~(1ull << 21);
+    }
+    const size_t prefix_bytes = a.need_corr ? (size_t)(p->kh + 1) * (p->kw + 1) * bn * 4 : 0;
+    // stage counts: BN = 256 fills one SM (4 x 48 KB); BN <= 128 leaves room for two CTAs per SM, so that one CTA's
+    // epilogue overlaps the other's main loop
+    if (swz == 128) {
+        if (bn == 256) return launch_tc<256, 128, 4>(tmA, tmB, a, prefix_bytes, stream);
+        if (bn == 128) return launch_tc<128, 128, 3>(tmA, tmB, a, prefix_bytes, stream);
+        return launch_tc<64, 128, 4>(tmA, tmB, a, prefix_bytes, stream);
+    }
+    if (bn == 256) return launch_tc<256, 64, 4>(tmA, tmB, a, prefix_bytes, stream);
+    if (bn == 128) return launch_tc<128, 64, 4>(tmA, tmB, a, prefix_bytes, stream);
+    return launch_tc<64, 64, 4>(tmA, tmB, a, prefix_bytes, stream);
+}
+
+}  // namespace b200k
+
+using namespace b200k;
+
+extern "C" size_t b200k_conv2d_pack_bytes(int32_t oc, int32_t kh, int32_t kw, int32_t c)
+{
+    (void)c;
+    if (oc <= 0 || kh <= 0 || kw <= 0) return 0;
+    return (size_t)(kh + 1) * (kw + 1) * oc * sizeof(int32_t);
+}
+
+extern "C" int b200k_conv2d_pack(const b200k_conv2d_params* p, void* packed, void* stream)
+{
+    B200K_REQUIRE(p && packed, B200K_E_INVALID, "conv2d_pack: null argument");
+    B200K_REQUIRE(p->w.data && is_q8(p->w.dtype), B200K_E_INVALID, "conv2d_pack: weights must be an 8-bit device tensor");
+    B200K_REQUIRE(p->oc > 0 && p->kh > 0 && p->kw > 0 && p->c > 0, B200K_E_INVALID, "conv2d_pack: bad geometry");
+    PackArgs a;
+    a.w = (const uint8_t*)p->w.data; a.prefix = (int32_t*)packed; a.w_u8 = p->w.dtype == B200K_U8;
+    a.OC = p->oc; a.KH = p->kh; a.KW = p->kw; a.C = p->c;
+    conv_prefix_kernel<<<div_up(p->oc, 128), 128, 0, (cudaStream_t)stream>>>(a);
+    return check_launch("conv_prefix_kernel");
+}
+
+extern "C" int b200k_poll_status(void)
+{
+    int s = 0;
+    B200K_CUDA(cudaMemcpyFromSymbol(&s, g_tc_status, sizeof(int)));
+    if (s != 0) {
+        int zero = 0;
+        cudaMemcpyToSymbol(g_tc_status, &zero, sizeof(int));
+        set_error("a bounded device-side wait gave up (code %d: 1 producer, 2 MMA issuer, 3 epilogue)", s);
+        return B200K_E_TIMEOUT;
+    }
+    return B200K_OK;
+}

@@ -93,6 +93,7 @@ extern "C" int b200k_fully_connected_q8(const b200k_fc_params* p, void* stream)
         c.n = p->m; c.h = 1; c.wd = 1; c.c = p->k; c.oh = 1; c.ow = 1; c.oc = p->n;
         c.kh = c.kw = 1; c.stride_h = c.stride_w = 1; c.dil_h = c.dil_w = 1;
         c.clamp_lo = p->clamp_lo; c.clamp_hi = p->clamp_hi; c.acc_out = p->acc_out; c.algo = p->algo;
+        c.packed = p->packed;
         return conv2d_dispatch(&c, (cudaStream_t)stream);
     }
     B200K_REQUIRE(p->x.data && p->w.data && p->y.data, B200K_E_INVALID, "fully_connected_q8: null tensor pointer");

@@ -449,6 +449,11 @@ class GraphProgram:
     def _operand(self, slot):
         return _qt(slot.info, self._ptr(self._dev(slot)), self._scales(slot.info))
 
+    def _pack_weights(self, conv_params):
+        """Load-time weight preparation (b200k_conv2d_pack); returns a pointer or None.  Only the CUDA
+        runtime overrides this."""
+        return None
+
     # -- workload construction -------------------------------------------------------------------------
     def _build(self):
         for layer in self.layers:
@@ -488,6 +493,8 @@ class GraphProgram:
         p.pad_top, p.pad_left = layer.desc["pad"][0], layer.desc["pad"][2]
         p.dil_h, p.dil_w = layer.desc["dilation"]
         p.clamp_lo, p.clamp_hi = _clamp(layer, y.info)
+        if not depthwise:
+            p.packed = self._pack_weights(p)
         return p
 
     def _make_Convolution2d(self, layer):
@@ -507,6 +514,10 @@ class GraphProgram:
         p.n = y.info.shape[-1]
         p.transpose_w = int(layer.desc["transpose"])
         p.clamp_lo, p.clamp_hi = _clamp(layer, y.info)
+        if p.transpose_w:
+            c = _abi.Conv2dParams()
+            c.w, c.oc, c.kh, c.kw, c.c = p.w, p.n, 1, 1, p.k
+            p.packed = self._pack_weights(c)
         return "fully_connected_q8", p
 
     def _make_BatchMatMul(self, layer):
@@ -660,6 +671,8 @@ class LoadedNetwork(GraphProgram):
         self.graph = None
         with torch.cuda.device(runtime.device):
             self._build()
+            # constant uploads and weight packing ran on the current stream; the workloads run on self.stream
+            torch.cuda.synchronize(runtime.device)
 
     def _alloc(self, info):
         tdt = getattr(self.torch, np.dtype(_NP_DTYPE[info.dtype]).name)
@@ -673,6 +686,15 @@ class LoadedNetwork(GraphProgram):
 
     def _view(self, tensor, shape):
         return tensor.view(shape)
+
+    def _pack_weights(self, conv_params):
+        l = lib.load_library()
+        nbytes = l.b200k_conv2d_pack_bytes(conv_params.oc, conv_params.kh, conv_params.kw, conv_params.c)
+        table = self.torch.empty(nbytes // 4, dtype=self.torch.int32, device=self.rt.device)
+        self.aux.append(table)
+        lib.check(l.b200k_conv2d_pack(ctypes.byref(conv_params), ctypes.c_void_p(table.data_ptr()),
+                                      ctypes.c_void_p(self.torch.cuda.current_stream().cuda_stream)))
+        return table.data_ptr()
 
     # -- execution ---------------------------------------------------------------------------------
     def launch_all(self, stream_handle):

@@ -103,7 +103,9 @@ int b200k_conv2d_q8(const b200k_conv2d_params* p, void* stream);
 /* Load-time weight preparation for the tcgen05 path: per-tap per-channel weight sums as a 2-D
  * prefix table, int32 [(kh+1)*(kw+1)*oc], used to correct for zero-filled padding when zx != 0.
  * CpuRef re-decodes the weights on every inference (ConvImpl.cpp:111-115); this replaces that.
- * `packed` must hold b200k_conv2d_pack_bytes() bytes of device memory. */
+ * `packed` must hold b200k_conv2d_pack_bytes() bytes of device memory; only w, oc, kh, kw, c of the
+ * parameter struct are read.  Without a packed table, convolutions whose input zero point is not 0
+ * run on the CUDA-core kernel. */
 size_t b200k_conv2d_pack_bytes(int32_t oc, int32_t kh, int32_t kw, int32_t c);
 int b200k_conv2d_pack(const b200k_conv2d_params* p, void* packed, void* stream);
 
@@ -119,6 +121,7 @@ typedef struct {
     int32_t clamp_lo, clamp_hi;
     int32_t* acc_out;
     int32_t algo;                   /* as b200k_conv2d_params.algo */
+    const void* packed;             /* optional result of b200k_conv2d_pack for the [n, 1, 1, k] weights, or NULL */
 } b200k_fc_params;
 
 int b200k_fully_connected_q8(const b200k_fc_params* p, void* stream);
@@ -260,6 +263,11 @@ typedef struct {
 } b200k_qlstm_params;
 
 int b200k_qlstm_step(const b200k_qlstm_params* p, void* stream);
+
+/* Status of the bounded device-side waits of the tcgen05 kernels: B200K_OK, or B200K_E_TIMEOUT when a wait
+ * gave up since the last poll (the status word is then cleared).  Synchronises the device.  No counterpart in
+ * the reference. */
+int b200k_poll_status(void);
 
 /* sizeof() of a parameter struct as compiled into the library, for bindings in other languages to check their
  * own declarations: 0 conv2d, 1 fc, 2 bmm, 3 pool2d, 4 mean, 5 eltwise, 6 activation, 7 softmax, 8 convert,

@@ -129,6 +129,16 @@ def activation_clamp(kind, a, b, scale, zp, dtype):
     return lo.value, hi.value
 
 
+def gpu_pack(mem, conv_params):
+    """b200k_conv2d_pack into a fresh device buffer; returns its pointer."""
+    from armnn_b200 import lib
+    l = lib.load_library()
+    nbytes = l.b200k_conv2d_pack_bytes(conv_params.oc, conv_params.kh, conv_params.kw, conv_params.c)
+    _, ptr = mem.out((nbytes // 4,), np.int32)
+    lib.check(l.b200k_conv2d_pack(C.byref(conv_params), C.c_void_p(ptr), None))
+    return ptr
+
+
 def out_size(i, k, s, pb, pa, d=1):
     return (i + pb + pa - (d * (k - 1) + 1)) // s + 1
 
@@ -194,10 +204,12 @@ class ConvCase:
         assert rc == 0, cpuref().cpuref_last_error().decode()
         return y
 
-    def run_gpu(self, want_acc=True, algo=0):
+    def run_gpu(self, want_acc=True, algo=0, pack=True):
         from armnn_b200 import lib
         mem = Cuda()
         p, y, acc = self.params(mem, want_acc, algo)
+        if pack and not self.depthwise:
+            p.packed = gpu_pack(mem, p)
         lib.call("dwconv2d_q8" if self.depthwise else "conv2d_q8", p)
         return mem.fetch(y), (mem.fetch(acc) if acc is not None else None)
 
@@ -281,10 +293,14 @@ class FcCase:
         assert rc == 0, cpuref().cpuref_last_error().decode()
         return y
 
-    def run_gpu(self, want_acc=True, algo=0):
+    def run_gpu(self, want_acc=True, algo=0, pack=True):
         from armnn_b200 import lib
         mem = Cuda()
         p, y, acc = self.params(mem, want_acc, algo)
+        if pack and self.transpose_w:
+            c = _abi.Conv2dParams()
+            c.w, c.oc, c.kh, c.kw, c.c = p.w, self.n, 1, 1, self.k
+            p.packed = gpu_pack(mem, c)
         lib.call("fully_connected_q8", p)
         return mem.fetch(y), (mem.fetch(acc) if acc is not None else None)
 

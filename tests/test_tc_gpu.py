@@ -1,0 +1,86 @@
+"""The tcgen05 implicit-GEMM kernel (algo = 2, forced) against the CPU oracle: int32 accumulators and quantised
+outputs bit-exact.  Covers both activation fetch modes (2-D tile for 1x1/FullyConnected, TMA im2col for the rest),
+both swizzle widths (C = 64 -> 64-byte, C % 128 == 0 -> 128-byte), every N-tile width (64 / 128 / 256), ragged M
+tails, input zero points with and without padding (prefix-table correction), strides, dilation, uint8 inputs."""
+import numpy as np
+import pytest
+
+from q8util import _abi, diff_stats, random_conv_case, random_fc_case
+
+pytestmark = pytest.mark.gpu
+
+U8, S8 = _abi.U8, _abi.S8
+
+CONV = {
+    "gemm_c64_oc64": lambda: random_conv_case(201, 2, 14, 14, 64, 64, 1, 1),
+    "gemm_c128_oc128_tail": lambda: random_conv_case(202, 1, 13, 11, 128, 128, 1, 1, act=(1, 0, 0)),
+    "gemm_c256_oc256": lambda: random_conv_case(203, 2, 14, 14, 256, 256, 1, 1),
+    "gemm_c64_oc256_zx0": lambda: random_conv_case(204, 1, 28, 28, 64, 256, 1, 1, x_q=(0.02, 0)),
+    "gemm_u8_input": lambda: random_conv_case(205, 1, 14, 14, 128, 64, 1, 1, x_dtype=U8, y_dtype=U8, x_q=(0.02, 131)),
+    "gemm_k2048": lambda: random_conv_case(206, 1, 7, 7, 2048, 512, 1, 1),
+    "im2col_3x3_c64_config1": lambda: random_conv_case(1234, 1, 56, 56, 64, 64, 3, 3, pad=(1, 1, 1, 1), act=(1, 0, 0)),
+    "im2col_3x3_c128_batch3": lambda: random_conv_case(207, 3, 14, 14, 128, 128, 3, 3, pad=(1, 1, 1, 1)),
+    "im2col_3x3_zx0": lambda: random_conv_case(208, 2, 14, 14, 64, 64, 3, 3, pad=(1, 1, 1, 1), x_q=(0.02, 0)),
+    "im2col_3x3_stride2": lambda: random_conv_case(209, 2, 28, 28, 128, 128, 3, 3, stride=(2, 2), pad=(1, 1, 1, 1), act=(1, 0, 0)),
+    "im2col_3x3_stride2_tf_same": lambda: random_conv_case(210, 2, 28, 28, 64, 64, 3, 3, stride=(2, 2), pad=(0, 1, 0, 1)),
+    "im2col_1x1_stride2": lambda: random_conv_case(211, 2, 28, 28, 256, 512, 1, 1, stride=(2, 2)),
+    "im2col_3x3_dilation2": lambda: random_conv_case(212, 1, 14, 14, 64, 64, 3, 3, pad=(2, 2, 2, 2), dil=(2, 2)),
+    "im2col_7x7_pad3": lambda: random_conv_case(213, 1, 14, 14, 64, 64, 7, 7, pad=(3, 3, 3, 3)),
+    "im2col_no_pad_valid": lambda: random_conv_case(214, 1, 12, 12, 64, 128, 3, 3),
+    "im2col_rect_3x1": lambda: random_conv_case(215, 1, 9, 11, 64, 64, 3, 1, stride=(1, 2), pad=(1, 1, 0, 0)),
+    "im2col_odd_image_7x7": lambda: random_conv_case(216, 5, 7, 7, 512, 512, 3, 3, pad=(1, 1, 1, 1), act=(1, 0, 0)),
+}
+
+FC = {
+    "fc_m1": lambda: random_fc_case(221, 1, 1024, 1024),
+    "fc_m16": lambda: random_fc_case(222, 16, 1024, 1024),
+    "fc_m256": lambda: random_fc_case(223, 256, 1024, 1024),
+    "fc_m300_k4096_n256": lambda: random_fc_case(224, 300, 4096, 256),
+}
+
+
+def _poll():
+    from armnn_b200 import lib
+    lib.check(lib.load_library().b200k_poll_status())
+
+
+@pytest.mark.parametrize("name", list(CONV))
+def test_tcgen05_conv_bit_exact(built, name):
+    case = CONV[name]()
+    y, acc = case.run_oracle()
+    gy, gacc = case.run_gpu(algo=2)
+    _poll()
+    assert np.array_equal(acc, gacc), (name, diff_stats(acc, gacc))
+    assert np.array_equal(y, gy), (name, diff_stats(y, gy))
+
+
+@pytest.mark.parametrize("name", list(FC))
+def test_tcgen05_fully_connected_bit_exact(built, name):
+    case = FC[name]()
+    y, acc = case.run_oracle()
+    gy, gacc = case.run_gpu(algo=2)
+    _poll()
+    assert np.array_equal(acc, gacc), (name, diff_stats(acc, gacc))
+    assert np.array_equal(y, gy), (name, diff_stats(y, gy))
+
+
+def test_tcgen05_equals_cuda_core_kernel_at_full_size(built):
+    """At a size the oracle cannot finish quickly, the two independent CUDA implementations must agree exactly."""
+    case = random_conv_case(230, 32, 56, 56, 64, 64, 3, 3, pad=(1, 1, 1, 1), act=(1, 0, 0))
+    y1, a1 = case.run_gpu(algo=1)
+    y2, a2 = case.run_gpu(algo=2)
+    _poll()
+    assert np.array_equal(a1, a2) and np.array_equal(y1, y2)
+    case = random_conv_case(231, 32, 14, 14, 1024, 256, 1, 1, act=(1, 0, 0))
+    y1, a1 = case.run_gpu(algo=1)
+    y2, a2 = case.run_gpu(algo=2)
+    _poll()
+    assert np.array_equal(a1, a2) and np.array_equal(y1, y2)
+
+
+def test_ineligible_shapes_are_refused_when_forced(built):
+    from armnn_b200 import lib
+    case = random_conv_case(232, 1, 8, 8, 24, 24, 1, 1)
+    with pytest.raises(lib.B200KError) as e:
+        case.run_gpu(algo=2)
+    assert e.value.code == _abi.E_UNSUPPORTED
