@@ -25,7 +25,8 @@ class Conv2dParams(C.Structure):
                 ("pad_top", C.c_int32), ("pad_left", C.c_int32),
                 ("dil_h", C.c_int32), ("dil_w", C.c_int32),
                 ("clamp_lo", C.c_int32), ("clamp_hi", C.c_int32),
-                ("acc_out", C.c_void_p), ("algo", C.c_int32), ("packed", C.c_void_p)]
+                ("acc_out", C.c_void_p), ("algo", C.c_int32), ("packed", C.c_void_p),
+                ("add_operand", QTensor), ("add_out", QTensor)]
 
 
 class FcParams(C.Structure):

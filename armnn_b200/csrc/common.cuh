@@ -87,6 +87,42 @@ inline Requant make_requant(float sx, const b200k_qtensor& y, int clamp_lo, int 
     return r;
 }
 
+// Fused ElementwiseBinary Add behind a convolution epilogue: q1 is the convolution's own 8-bit output (formed with
+// `own`), the other operand is dequantised with its scale / offset, the fp32 sum is re-quantised with `out`.
+struct FusedAdd {
+    const uint8_t* res;          // null: no fusion
+    float res_scale; int res_zp; int res_u8;
+    Requant out;                 // quantisation and clamp of the Add's output
+    __device__ __forceinline__ int operator()(int q1, const Requant& own, long long i) const
+    {
+        const int rq8 = res_u8 ? (int)res[i] : (int)(int8_t)res[i];
+        const float fa = __fmul_rn(__int2float_rn(q1 - own.zy), own.sy);
+        const float fb = __fmul_rn(__int2float_rn(rq8 - res_zp), res_scale);
+        const int q = quantize_dev(__fadd_rn(fa, fb), out.sy, out.zy, out.tlo, out.thi);
+        return min(max(q, out.clo), out.chi);
+    }
+};
+
+// Fills the fused-add part of a launch from the C-ABI struct; returns false when the request is malformed.
+inline bool make_fused_add(const b200k_conv2d_params* p, Requant& own, FusedAdd& fa, void*& out_ptr)
+{
+    fa.res = nullptr;
+    out_ptr = (void*)p->y.data;
+    own = make_requant(p->x.scale, p->y, p->clamp_lo, p->clamp_hi);
+    if (!p->add_operand.data) return true;
+    if (!is_q8(p->add_operand.dtype) || !is_q8(p->add_out.dtype) || !p->add_out.data) return false;
+    if (!(p->add_operand.scale > 0.f) || !(p->add_out.scale > 0.f)) return false;
+    int lo, hi;
+    type_range(p->y.dtype, lo, hi);
+    own = make_requant(p->x.scale, p->y, lo, hi);                      // the intermediate carries no activation
+    fa.res = (const uint8_t*)p->add_operand.data;
+    fa.res_scale = p->add_operand.scale; fa.res_zp = p->add_operand.zero_point;
+    fa.res_u8 = p->add_operand.dtype == B200K_U8;
+    fa.out = make_requant(0.f, p->add_out, p->clamp_lo, p->clamp_hi);
+    out_ptr = (void*)p->add_out.data;
+    return true;
+}
+
 // ---- typed element access ------------------------------------------------------------------
 
 __device__ __forceinline__ int load_q_dev(const void* p, int dtype, long long i)

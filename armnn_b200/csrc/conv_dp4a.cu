@@ -28,6 +28,7 @@ struct ConvArgs {
     int K;                           // KH*KW*C
     long long M;                     // N*OH*OW
     Requant rq;
+    FusedAdd fa;
 };
 
 constexpr int BM = 64, BN = 64, BKW = 16;          // tile rows, cols, k-words (64 bytes) per slice
@@ -206,6 +207,7 @@ __global__ void __launch_bounds__(256) conv_dp4a_kernel(const ConvArgs a)
             const float sbc = a.b_scales ? a.b_scales[ch] : a.b_scale;
             const int bq = a.bias ? a.bias[ch] : 0;
             q[j] = a.rq(v, swc, a.bias != nullptr, bq, sbc);
+            if (a.fa.res) q[j] = a.fa(q[j], a.rq, m * a.OC + ch);
         }
         const int ch0 = n0 + tx * 4;
         uint8_t* yp = (uint8_t*)a.y + m * a.OC + ch0;
@@ -220,9 +222,9 @@ __global__ void __launch_bounds__(256) conv_dp4a_kernel(const ConvArgs a)
 }
 
 static int validate_common(const b200k_qtensor& x, const b200k_qtensor& w, const b200k_qtensor& bias,
-                           const b200k_qtensor& y, const char* what)
+                           const b200k_qtensor& y, bool y_stored, const char* what)
 {
-    B200K_REQUIRE(x.data && w.data && y.data, B200K_E_INVALID, "%s: null tensor pointer", what);
+    B200K_REQUIRE(x.data && w.data && (y.data || !y_stored), B200K_E_INVALID, "%s: null tensor pointer", what);
     B200K_REQUIRE(is_q8(x.dtype) && is_q8(w.dtype) && is_q8(y.dtype), B200K_E_UNSUPPORTED,
                   "%s: only 8-bit quantised input/weights/output are supported (got %d/%d/%d)", what,
                   x.dtype, w.dtype, y.dtype);
@@ -233,7 +235,7 @@ static int validate_common(const b200k_qtensor& x, const b200k_qtensor& w, const
 
 int launch_conv_dp4a(const b200k_conv2d_params* p, cudaStream_t stream)
 {
-    int rc = validate_common(p->x, p->w, p->bias, p->y, "conv2d_q8");
+    int rc = validate_common(p->x, p->w, p->bias, p->y, p->add_operand.data == nullptr, "conv2d_q8");
     if (rc) return rc;
     B200K_REQUIRE(p->n > 0 && p->h > 0 && p->wd > 0 && p->c > 0 && p->oh > 0 && p->ow > 0 && p->oc > 0 &&
                   p->kh > 0 && p->kw > 0 && p->stride_h > 0 && p->stride_w > 0 && p->dil_h > 0 && p->dil_w > 0 &&
@@ -255,7 +257,7 @@ int launch_conv_dp4a(const b200k_conv2d_params* p, cudaStream_t stream)
     a.dh = p->dil_h; a.dw = p->dil_w;
     a.K = (int)kk;
     a.M = (long long)p->n * p->oh * p->ow;
-    a.rq = make_requant(p->x.scale, p->y, p->clamp_lo, p->clamp_hi);
+    B200K_REQUIRE(make_fused_add(p, a.rq, a.fa, a.y), B200K_E_INVALID, "conv2d_q8: malformed fused add operand / output");
     dim3 grid(div_up(a.M, BM), div_up(a.OC, BN));
     const uintptr_t al = (uintptr_t)a.x | (uintptr_t)a.w;
     if ((a.C % 16) == 0 && (al & 15) == 0)      conv_dp4a_kernel<2><<<grid, 256, 0, stream>>>(a);

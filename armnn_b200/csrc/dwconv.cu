@@ -93,6 +93,7 @@ extern "C" int b200k_dwconv2d_q8(const b200k_conv2d_params* p, void* stream)
     B200K_REQUIRE(is_q8(p->x.dtype) && is_q8(p->w.dtype) && is_q8(p->y.dtype), B200K_E_UNSUPPORTED,
                   "dwconv2d_q8: only 8-bit quantised tensors are supported");
     B200K_REQUIRE(!p->bias.data || p->bias.dtype == B200K_S32, B200K_E_INVALID, "dwconv2d_q8: bias must be Signed32");
+    B200K_REQUIRE(!p->add_operand.data, B200K_E_UNSUPPORTED, "dwconv2d_q8: a fused Add is only available on Convolution2d");
     B200K_REQUIRE(p->n > 0 && p->h > 0 && p->wd > 0 && p->c > 0 && p->oh > 0 && p->ow > 0 && p->oc > 0 &&
                   p->kh > 0 && p->kw > 0 && p->stride_h > 0 && p->stride_w > 0 && p->dil_h > 0 && p->dil_w > 0,
                   B200K_E_INVALID, "dwconv2d_q8: bad geometry");

@@ -337,6 +337,37 @@ def Optimize(network, backend_preferences=("B200Acc",), model_options=None):
             consumer.source = src
             src.connections.append(consumer)
         removed.add(id(act))
+    # residual-add fusion: Convolution2d -> Add(other) [-> ReLu already folded into the Add] becomes one
+    # convolution workload whose epilogue adds the other operand (b200k_conv2d_params.add_operand)
+    for add in network.layers:
+        if add.type != "ElementwiseBinary" or add.desc["op"] != BinaryOperation.Add or id(add) in removed:
+            continue
+        out_info = add.outputs[0].info
+        if out_info.dtype not in _Q8:
+            continue
+        for side in (0, 1):
+            src, other = add.inputs[side].source, add.inputs[1 - side].source
+            conv = src.layer
+            if (conv.type != "Convolution2d" or conv.fused_activation is not None or len(src.connections) != 1 or
+                    getattr(conv, "fused_add", None) is not None or src.info.shape != out_info.shape or
+                    other.info.shape != out_info.shape or other.info.dtype not in _Q8 or other.layer is conv):
+                continue
+            conv.fused_add = {"conv_out_info": src.info}
+            conv.fused_activation = add.fused_activation
+            # the other operand becomes an extra input of the convolution layer (after data, weights, bias)
+            extra = InputSlot(conv, len(conv.inputs))
+            conv.inputs.append(extra)
+            other.connections = [c for c in other.connections if c is not add.inputs[1 - side]]
+            extra.source = other
+            other.connections.append(extra)
+            # the convolution now produces the Add's output
+            src.info = out_info
+            src.connections = []
+            for consumer in add.outputs[0].connections:
+                consumer.source = src
+                src.connections.append(consumer)
+            removed.add(id(add))
+            break
     layers = [l for l in network.layers if id(l) not in removed]
     # topological order (layers may have been added in any order)
     order, done = [], set()
@@ -493,6 +524,12 @@ class GraphProgram:
         p.pad_top, p.pad_left = layer.desc["pad"][0], layer.desc["pad"][2]
         p.dil_h, p.dil_w = layer.desc["dilation"]
         p.clamp_lo, p.clamp_hi = _clamp(layer, y.info)
+        fused = getattr(layer, "fused_add", None)
+        if fused is not None:
+            # y carries the convolution's own quantisation only; the stored tensor is the Add's output
+            p.add_out = p.y
+            p.y = _qt(fused["conv_out_info"], None)
+            p.add_operand = self._operand(layer.inputs[-1].source)
         if not depthwise:
             p.packed = self._pack_weights(p)
         return p

@@ -96,6 +96,13 @@ typedef struct {
     int32_t* acc_out;
     int32_t algo;                   /* 0 = auto, 1 = CUDA-core dp4a kernel, 2 = tcgen05 kernel */
     const void* packed;             /* optional result of b200k_conv2d_pack (device), or NULL   */
+    /* Fused ElementwiseBinary Add (Convolution2d only; add_operand.data == NULL: none).  The convolution's own
+     * 8-bit result q = Q_y(conv) is formed with y's scale / zero point but not stored (y.data is ignored), then
+     *     add_out = clamp(Q_out(deq_y(q) + deq(add_operand)))
+     * exactly as RefConvolution2dWorkload followed by RefElementwiseBinaryWorkload (and a ReLu / BoundedReLu
+     * Activation expressed through clamp_lo / clamp_hi, which then refer to add_out) would produce.
+     * add_operand and add_out have the convolution's output shape (no broadcast). */
+    b200k_qtensor add_operand, add_out;
 } b200k_conv2d_params;
 
 int b200k_conv2d_q8(const b200k_conv2d_params* p, void* stream);

@@ -136,7 +136,10 @@ static int conv_impl(const b200k_conv2d_params* p, int depthwise)
     const int KH = p->kh, KW = p->kw;
     const int zx = p->x.zero_point, zw = p->w.zero_point;
     const int dm = depthwise ? OC / C : 1;          /* ConvImpl.cpp:100 */
-    if (!p->x.data || !p->w.data || !p->y.data) return B200K_E_INVALID;
+    const int fused = !depthwise && p->add_operand.data != NULL;
+    if (!p->x.data || !p->w.data || (!fused && !p->y.data) || (fused && !p->add_out.data)) return B200K_E_INVALID;
+    int32_t ylo, yhi;
+    type_range(p->y.dtype, &ylo, &yhi);
     #pragma omp parallel for collapse(2) schedule(static)
     for (int b = 0; b < N; ++b)
     for (int oy = 0; oy < OH; ++oy)
@@ -184,6 +187,16 @@ static int conv_impl(const b200k_conv2d_params* p, int depthwise)
         int has_bias = p->bias.data != NULL;
         int32_t bq = has_bias ? ((const int32_t*)p->bias.data)[co] : 0;
         float sb = p->bias.scales ? p->bias.scales[co] : p->bias.scale;
+        if (fused) {
+            /* RefConvolution2dWorkload, then RefElementwiseBinaryWorkload(Add) on its 8-bit output, then the clamp */
+            int32_t q1 = requant(acc, p->x.scale, sw, has_bias, bq, sb, p->y.scale, p->y.zero_point, p->y.dtype, ylo, yhi);
+            volatile float fa = dequantize_i(q1, p->y.scale, p->y.zero_point);
+            volatile float fb = load_f(&p->add_operand, oi);
+            volatile float r = fa + fb;
+            store_q((void*)p->add_out.data, p->add_out.dtype, oi,
+                    clampi(quantize_f(r, p->add_out.scale, p->add_out.zero_point, p->add_out.dtype), p->clamp_lo, p->clamp_hi));
+            continue;
+        }
         store_q((void*)p->y.data, p->y.dtype, oi,
                 requant(acc, p->x.scale, sw, has_bias, bq, sb, p->y.scale, p->y.zero_point,
                         p->y.dtype, p->clamp_lo, p->clamp_hi));

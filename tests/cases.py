@@ -33,6 +33,9 @@ def conv_cases():
     c["s8_per_tensor_no_bias"] = lambda: random_conv_case(11, 1, 8, 8, 16, 16, 3, 3, pad=(1, 1, 1, 1), per_axis=False, bias=False)
     c["rect_kernel_3x1_stride_1x2"] = lambda: random_conv_case(12, 1, 9, 11, 8, 8, 3, 1, stride=(1, 2), pad=(1, 1, 0, 0))
     c["k_not_multiple_of_64"] = lambda: random_conv_case(13, 1, 5, 5, 48, 80, 3, 3, pad=(1, 1, 1, 1))
+    c["fused_add_relu_1x1"] = lambda: random_conv_case(14, 2, 14, 14, 64, 256, 1, 1, act=(1, 0, 0), fused_add=True)
+    c["fused_add_3x3_odd"] = lambda: random_conv_case(15, 1, 7, 9, 12, 20, 3, 3, pad=(1, 1, 1, 1), fused_add=True)
+    c["fused_add_u8"] = lambda: random_conv_case(16, 1, 8, 8, 16, 24, 1, 1, x_dtype=U8, y_dtype=U8, x_q=(0.5, 128), fused_add=True)
     return c
 
 

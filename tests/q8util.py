@@ -153,7 +153,8 @@ class ConvCase:
 
     def __init__(self, x, w, bias, x_q, w_q, y_q, stride=(1, 1), pad=(0, 0, 0, 0), dil=(1, 1), act=(0, 0.0, 0.0),
                  depthwise=False, w_scales=None, b_scale=None, b_scales=None, x_dtype=_abi.S8, w_dtype=_abi.S8,
-                 y_dtype=_abi.S8):
+                 y_dtype=_abi.S8, add=None):
+        self.add = add                 # None, or (other operand array, (scale, zp), (out scale, out zp)): fused Add
         self.x, self.w, self.bias = x, w, bias
         self.x_q, self.w_q, self.y_q = x_q, w_q, y_q           # (scale, zp)
         self.w_scales, self.b_scale, self.b_scales = w_scales, b_scale, b_scales
@@ -181,7 +182,13 @@ class ConvCase:
         p.stride_h, p.stride_w = self.stride
         p.pad_top, p.pad_left = self.pad[0], self.pad[2]
         p.dil_h, p.dil_w = self.dil
-        p.clamp_lo, p.clamp_hi = activation_clamp(self.act[0], self.act[1], self.act[2], self.y_q[0], self.y_q[1], self.y_dtype)
+        out_q = self.y_q
+        if self.add is not None:
+            other, other_q, out_q = self.add
+            p.add_operand = qt(mem, other, self.y_dtype, *other_q)
+            p.add_out, y = qt_out(mem, (n, self.oh, self.ow, oc), self.y_dtype, *out_q)
+            p.y.data = None
+        p.clamp_lo, p.clamp_hi = activation_clamp(self.act[0], self.act[1], self.act[2], out_q[0], out_q[1], self.y_dtype)
         acc = None
         if want_acc:
             acc, ptr = mem.out((n, self.oh, self.ow, oc), np.int32)
@@ -198,6 +205,24 @@ class ConvCase:
 
     def run_cpuref(self):
         mem = Host()
+        if self.add is not None:
+            # three separate CpuRef workloads: Convolution2d, ElementwiseBinary(Add), Activation
+            plain = ConvCase(self.x, self.w, self.bias, self.x_q, self.w_q, self.y_q, self.stride, self.pad, self.dil,
+                             (0, 0., 0.), self.depthwise, self.w_scales, self.b_scale, self.b_scales, self.x_dtype,
+                             self.w_dtype, self.y_dtype)
+            conv_out = plain.run_cpuref()
+            other, other_q, out_q = self.add
+            e = _abi.EltwiseParams()
+            e.a = qt(mem, conv_out, self.y_dtype, *self.y_q)
+            e.b = qt(mem, other, self.y_dtype, *other_q)
+            e.out, out = qt_out(mem, conv_out.shape, self.y_dtype, *out_q)
+            e.rank = 4
+            for i in range(4):
+                e.shape_a[i] = e.shape_b[i] = e.shape_out[i] = conv_out.shape[i]
+            e.op = 0
+            rc = cpuref().cpuref_eltwise_q8(C.byref(e), C.c_int(self.act[0]), C.c_float(self.act[1]), C.c_float(self.act[2]))
+            assert rc == 0, cpuref().cpuref_last_error().decode()
+            return out
         p, y, _ = self.params(mem)
         rc = cpuref().cpuref_conv2d_q8(C.byref(p), C.c_int(int(self.depthwise)), C.c_int(self.act[0]),
                                        C.c_float(self.act[1]), C.c_float(self.act[2]))
@@ -216,7 +241,7 @@ class ConvCase:
 
 def random_conv_case(seed, n, h, wd, c, oc, kh, kw, stride=(1, 1), pad=(0, 0, 0, 0), dil=(1, 1), act=(0, 0., 0.),
                      depthwise=False, x_dtype=_abi.S8, w_dtype=_abi.S8, y_dtype=_abi.S8, per_axis=True,
-                     x_q=(0.02, -3), y_scale=None, y_zp=None, bias=True, depth_multiplier=1):
+                     x_q=(0.02, -3), y_scale=None, y_zp=None, bias=True, depth_multiplier=1, fused_add=False):
     """Seeded synthetic conv in the style of the benchmark configs: uniform activations over the
     whole type range, weights uniform, per-output-channel scales uniform in [0.001, 0.01], int32 bias
     uniform in [-1000, 1000] with scale sx * sw[c].  The output scale defaults to one that leaves
@@ -253,8 +278,16 @@ def random_conv_case(seed, n, h, wd, c, oc, kh, kw, stride=(1, 1), pad=(0, 0, 0,
         y_scale = float(np.float32(std * 3.0 / 127.0))
     if y_zp is None:
         y_zp = 0 if y_dtype == _abi.S8 else 128
-    return ConvCase(x, w, b, x_q, w_q, (y_scale, y_zp), stride, pad, dil, act, depthwise, w_scales, b_scale, b_scales,
+    case = ConvCase(x, w, b, x_q, w_q, (y_scale, y_zp), stride, pad, dil, act, depthwise, w_scales, b_scale, b_scales,
                     x_dtype, w_dtype, y_dtype)
+    if fused_add:
+        # residual operand at a different scale / offset, output wide enough for the sum
+        lo, hi = RANGE[y_dtype]
+        other = rng.integers(lo, hi + 1, size=(n, case.oh, case.ow, oc)).astype(NP_OF[y_dtype])
+        other_q = (float(np.float32(y_scale * 0.8)), y_zp + 3)
+        out_zp = lo if act[0] else y_zp - 2
+        case.add = (other, other_q, (float(np.float32(y_scale * 1.3)), out_zp))
+    return case
 
 
 class FcCase:

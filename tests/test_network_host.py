@@ -60,7 +60,9 @@ def test_resnet50_layer_list_and_mac_count():
     assert info["macs"] == 4089186304                         # 4.09 GMAC per 224x224 image
     opt = Optimize(net)
     assert sum(1 for l in opt.layers if l.type == "Activation") == 0      # every ReLU fused
-    assert sum(1 for l in opt.layers if l.type == "ElementwiseBinary") == 16
+    # every residual Add (+ ReLU) is folded into the epilogue of the block's last convolution
+    assert sum(1 for l in opt.layers if l.type == "ElementwiseBinary") == 0
+    assert sum(1 for l in opt.layers if getattr(l, "fused_add", None) is not None) == 16
 
 
 def _run_pair(net, info, dtype):
