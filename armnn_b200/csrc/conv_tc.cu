@@ -26,13 +26,15 @@
 // Every wait on an mbarrier is bounded; when a bound is hit the kernel raises a status word (read with
 // b200k_poll_status), drains and returns, so a logic error cannot hang the device.
 #include <cuda.h>
+#include <stdlib.h>
 #include <cudaTypedefs.h>
 #include "common.cuh"
 
 namespace b200k {
 
 constexpr int TC_BM = 128;
-constexpr int TC_THREADS = 320;                 // warp 0 producer, warp 1 MMA, warps 2-9 epilogue
+constexpr int TC_EPI_WARPS = 16;
+constexpr int TC_THREADS = 64 + 32 * TC_EPI_WARPS;   // warp 0 producer, warp 1 MMA issuer, then the epilogue warps
 constexpr unsigned TC_SPIN_LIMIT = 1u << 22;
 
 __device__ int g_tc_status = 0;                 // 0 ok, otherwise the code of the wait that gave up
@@ -57,6 +59,7 @@ struct TcArgs {
     const uint8_t* res; float res_scale; int res_zp; int res_u8;
     Requant rq2;
     float inv_sy2;
+    int debug;                                  // 0 normal; 1: main loop without MMAs; 2: main loop without TMA loads
 };
 
 // ---- PTX wrappers --------------------------------------------------------------------------------------
@@ -111,6 +114,15 @@ __device__ __forceinline__ void tc_mma_i8(uint32_t tmem_d, uint64_t adesc, uint6
                  "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
                  ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t* r)
+{
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32"
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t* r)
 {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32"
@@ -139,23 +151,94 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr)
     return d;
 }
 
-// Quantize(v, sy, zy) with the division replaced by a reciprocal multiply when that cannot change the result.
-__device__ __forceinline__ int quantize_fast(float v, const Requant& rq, float inv_sy)
+// The epilogue arithmetic is written to stay off the conversion/transcendental (XU) pipe, which issues only 16 lanes
+// per clock per SM and throttled the first version of this kernel: float <-> int conversions and rounding are done
+// with the 1.5 * 2^23 magic constant on the FP32 pipe, and the only conversion instruction left is the int32 -> fp32
+// of the accumulator.
+constexpr float TC_MAGIC = 12582912.0f;          // 1.5 * 2^23: x + MAGIC - MAGIC == rint(x) for |x| < 2^22
+
+struct QuantF {                                  // one quantisation target, everything as fp32
+    float sy, inv_sy, zy, lo, hi;                // lo / hi: type range intersected with the activation clamp
+};
+
+// Quantize(v, sy, zy) then clamp, returned as an integer-valued float.  The division v / sy is evaluated as a
+// multiplication by the reciprocal whenever that provably cannot change the rounded result: |v * inv - v / sy| is
+// below 2^-12 for |v / sy| < 512 (beyond which every 8-bit output saturates whatever the rounding), so unless the
+// product lies within 2^-11 of a rounding tie its nearest integer is round(v / sy).  Otherwise the exact division
+// and round-half-away are evaluated, as armnn::Quantize does.
+__device__ __forceinline__ float quantize_f32(float v, const QuantF& q)
 {
-    const float y = __fmul_rn(v, inv_sy);
-    float r;
-    if (fabsf(y) < 512.f) {
-        const float n = rintf(y);
-        // |y - v/sy| <= 2^-13 here; away from a tie by more than 2^-10 the nearest integer is the answer
-        if (fabsf(fabsf(__fsub_rn(y, n)) - 0.5f) > 0.0009765625f) r = n;
-        else r = roundf(__fdiv_rn(v, rq.sy));
-    } else {
-        // beyond +-512 every 8-bit output clamps; only the sign matters (NaN cannot occur: finite inputs)
-        r = roundf(__fdiv_rn(v, rq.sy));
+    const float y = __fmul_rn(v, q.inv_sy);
+    float n = __fsub_rn(__fadd_rn(y, TC_MAGIC), TC_MAGIC);
+    const float e = fabsf(__fsub_rn(y, n)) - 0.5f;
+    if (fabsf(e) <= 0.00048828125f) n = roundf(__fdiv_rn(v, q.sy));
+    return fminf(fmaxf(__fadd_rn(q.zy, n), q.lo), q.hi);
+}
+
+// integer-valued float in [-128, 255] -> its low byte (two's complement)
+__device__ __forceinline__ uint32_t f32_to_byte_bits(float qf) { return __float_as_uint(__fadd_rn(qf, TC_MAGIC)); }
+
+// bytes of a packed word as integer-valued floats (signed or unsigned 8-bit)
+__device__ __forceinline__ float byte_to_f32(uint32_t word, int idx, bool is_u8)
+{
+    // place the byte in the mantissa of 2^23 + 2^22: value = MAGIC + byte (after flipping the sign bit for int8)
+    const uint32_t b = __byte_perm(word ^ (is_u8 ? 0u : 0x80808080u), 0x4B400000u, 0x7650 + idx);
+    return __fsub_rn(__uint_as_float(b), is_u8 ? TC_MAGIC : TC_MAGIC + 128.0f);
+}
+
+struct EpiConsts {
+    QuantF q1, q2;                               // the convolution's own quantisation; the fused Add's output
+    float res_zp, res_scale; bool res_u8; int zx;
+    const int32_t *p11, *p01, *p10, *p00;        // prefix-table rows of this thread's tap rectangle
+};
+
+// 16 accumulator columns of one output pixel -> 16 output bytes.  FUSED: add the residual operand (16 bytes in rv).
+// INTERIOR: every tap of every pixel of the warp is inside the image, so the zero-point correction is the
+// per-channel constant in s_corr; otherwise it comes from the pixel's tap rectangle in the prefix table.
+template <bool FUSED, bool INTERIOR>
+__device__ __forceinline__ uint4 epi_chunk(const uint32_t* r, const uint4 rv, const float* s_m, const float* s_bterm,
+                                           const int32_t* s_corr, int col0, const EpiConsts& ec)
+{
+    const uint32_t resw[4] = {rv.x, rv.y, rv.z, rv.w};
+    uint32_t packed[4];
+    #pragma unroll
+    for (int g = 0; g < 4; ++g) {                              // 4 columns at a time: 128-bit shared loads
+        const float4 mv = *(const float4*)&s_m[g * 4];
+        const float4 bv = *(const float4*)&s_bterm[g * 4];
+        int4 cv;
+        if (INTERIOR) {
+            cv = *(const int4*)&s_corr[g * 4];
+        } else {
+            const int col = col0 + g * 4;
+            const int4 c11 = *(const int4*)&ec.p11[col], c01 = *(const int4*)&ec.p01[col];
+            const int4 c10 = *(const int4*)&ec.p10[col], c00 = *(const int4*)&ec.p00[col];
+            cv.x = ec.zx * (c11.x - c01.x - c10.x + c00.x);
+            cv.y = ec.zx * (c11.y - c01.y - c10.y + c00.y);
+            cv.z = ec.zx * (c11.z - c01.z - c10.z + c00.z);
+            cv.w = ec.zx * (c11.w - c01.w - c10.w + c00.w);
+        }
+        const float mm[4] = {mv.x, mv.y, mv.z, mv.w};
+        const float bb[4] = {bv.x, bv.y, bv.z, bv.w};
+        const int cc[4] = {cv.x, cv.y, cv.z, cv.w};
+        uint32_t bits[4];
+        #pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int acc = (int)r[g * 4 + e] - cc[e];
+            // v = float(acc) * (sx * sw) + float(bias) * sb   (bterm is +0.0 without a bias)
+            const float v = __fadd_rn(__fmul_rn(__int2float_rn(acc), mm[e]), bb[e]);
+            float qf = quantize_f32(v, ec.q1);
+            if (FUSED) {
+                // fused ElementwiseBinary Add: the convolution's own 8-bit output is formed first, then both operands
+                // are dequantised, added in fp32 and re-quantised, as the two separate workloads do
+                const float fa = __fmul_rn(__fsub_rn(qf, ec.q1.zy), ec.q1.sy);
+                const float fb = __fmul_rn(__fsub_rn(byte_to_f32(resw[g], e, ec.res_u8), ec.res_zp), ec.res_scale);
+                qf = quantize_f32(__fadd_rn(fa, fb), ec.q2);
+            }
+            bits[e] = f32_to_byte_bits(qf);
+        }
+        packed[g] = __byte_perm(__byte_perm(bits[0], bits[1], 0x0040), __byte_perm(bits[2], bits[3], 0x0040), 0x5410);
     }
-    float q = __fadd_rn(__int2float_rn(rq.zy), r);
-    q = fminf(fmaxf(q, rq.tlo), rq.thi);
-    return min(max(__float2int_rz(q), rq.clo), rq.chi);
+    return make_uint4(packed[0], packed[1], packed[2], packed[3]);
 }
 
 template <int BN, int SWZ>
@@ -165,14 +248,15 @@ struct TcSmem {
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int STAGES = (196608 / STAGE_BYTES) < 8 ? (196608 / STAGE_BYTES) : 8;
     static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
-    // after the ring: float m[BN], float bterm[BN], barriers (full, empty, acc_full[2], acc_empty[2]), tmem slot;
+    // after the ring: float m[BN], float bterm[BN], int corr[BN], barriers (full, empty, acc_full[2], acc_empty[2]),
+    // tmem slot;
     // the prefix slice follows (dynamic size)
-    static constexpr int FIXED_BYTES = RING_BYTES + 2 * BN * 4 + (2 * STAGES + 4) * 8 + 16;
+    static constexpr int FIXED_BYTES = RING_BYTES + 3 * BN * 4 + (2 * STAGES + 4) * 8 + 16;
 };
 
-__device__ __forceinline__ void epi_barrier()       // the 8 epilogue warps only (named barrier 1)
+__device__ __forceinline__ void epi_barrier()       // the epilogue warps only (named barrier 1)
 {
-    asm volatile("bar.sync 1, 256;" ::: "memory");
+    asm volatile("bar.sync 1, %0;" ::"n"(32 * TC_EPI_WARPS) : "memory");
 }
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar)
 {
@@ -193,7 +277,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     float* s_m = (float*)(smem + L::RING_BYTES);
     float* s_bterm = s_m + BN;
-    uint64_t* full = (uint64_t*)(s_bterm + BN);
+    int32_t* s_corr = (int32_t*)(s_bterm + BN);             // zx * (sum of all taps) per channel
+    uint64_t* full = (uint64_t*)(s_corr + BN);
     uint64_t* empty = full + STAGES;
     uint64_t* acc_full = empty + STAGES;                    // [2]
     uint64_t* acc_empty = acc_full + 2;                     // [2]
@@ -207,7 +292,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 8); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], TC_EPI_WARPS); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -244,6 +329,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     const int c0 = (s - tap * a.cchunks) * SWZ;
                     uint8_t* sa = smem + st * L::STAGE_BYTES;
                     uint8_t* sb = sa + L::A_BYTES;
+                    if (a.debug == 2) { mbar_arrive(&full[st]); continue; }
                     mbar_expect_tx(&full[st], L::STAGE_BYTES);
                     if (a.im2col) {
                         const int ky = tap / a.KW, kx = tap - ky * a.KW;
@@ -276,6 +362,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     const uint32_t ph = (g / STAGES) & 1u;
                     if (!mbar_wait(&full[st], ph)) { atomicExch(&g_tc_status, 2); alive = false; break; }
                     tc_fence_after();
+                    if (a.debug == 1) { mbar_arrive(&empty[st]); continue; }
                     const uint32_t sa = smem_u32(smem + st * L::STAGE_BYTES);
                     const uint64_t da = make_smem_desc<SWZ>(sa);
                     const uint64_t db = make_smem_desc<SWZ>(sa + L::A_BYTES);
@@ -289,13 +376,21 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
     } else {
         // ===================== epilogue =====================
-        const int ew = warp - 2;                   // 0..7
-        const int quad = warp & 3;                 // TMEM lane quadrant this warp may access
-        const int half = ew >> 2;                  // which half of the columns
-        const int etid = threadIdx.x - 64;         // 0..255 among the epilogue threads
-        const bool has_bias = a.bias != nullptr;
+        // 16 warps: warp & 3 selects the TMEM lane quadrant (a hardware restriction), the other two bits select a
+        // quarter of the tile's columns; each warp walks its columns in chunks of 16.
+        const int ew = warp - 2;
+        const int quad = warp & 3;
+        const int part = ew >> 2;
+        const int etid = threadIdx.x - 64;
         const int pw = a.KW + 1;
-        constexpr int COLS_PER_HALF = BN / 2;
+        const int cells = (a.KH + 1) * pw;
+        constexpr int COLS_PER_PART = BN / 4;
+        EpiConsts ec;
+        ec.q1.sy = a.rq.sy; ec.q1.inv_sy = a.inv_sy; ec.q1.zy = (float)a.rq.zy;
+        ec.q1.lo = fmaxf(a.rq.tlo, (float)a.rq.clo); ec.q1.hi = fminf(a.rq.thi, (float)a.rq.chi);
+        ec.q2.sy = a.rq2.sy; ec.q2.inv_sy = a.inv_sy2; ec.q2.zy = (float)a.rq2.zy;
+        ec.q2.lo = fmaxf(a.rq2.tlo, (float)a.rq2.clo); ec.q2.hi = fminf(a.rq2.thi, (float)a.rq2.chi);
+        ec.res_zp = (float)a.res_zp; ec.res_scale = a.res_scale; ec.res_u8 = a.res_u8 != 0; ec.zx = a.zx;
         int cur_n0 = -1;
         int it = 0;
         for (int t = blockIdx.x; t < ntiles; t += gridDim.x, ++it) {
@@ -305,14 +400,14 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             if (n0 != cur_n0) {
                 // per-channel constants of this n-tile (all epilogue warps are between tiles here)
                 epi_barrier();
-                for (int j = etid; j < BN; j += 256) {
+                for (int j = etid; j < BN; j += 32 * TC_EPI_WARPS) {
                     const int ch = n0 + j;
                     s_m[j] = __fmul_rn(a.rq.sx, a.w_scales ? a.w_scales[ch] : a.w_scale);
                     s_bterm[j] = a.bias ? __fmul_rn(__int2float_rn(a.bias[ch]), a.b_scales ? a.b_scales[ch] : a.b_scale) : 0.f;
+                    s_corr[j] = a.need_corr ? a.zx * a.prefix[(long long)(cells - 1) * a.OC + ch] : 0;
                 }
-                if (a.need_corr) {
-                    const int cells = (a.KH + 1) * pw;
-                    for (int i = etid; i < cells * BN; i += 256) {
+                if (a.need_rect) {
+                    for (int i = etid; i < cells * BN; i += 32 * TC_EPI_WARPS) {
                         const int cell = i / BN, j = i - cell * BN;
                         s_prefix[i] = a.prefix[(long long)cell * a.OC + n0 + j];
                     }
@@ -329,9 +424,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             // rectangle of in-image taps of this pixel
             int ky0 = 0, ky1 = a.KH, kx0 = 0, kx1 = a.KW;
             if (a.need_rect) {
-                const int ox = (int)(m % a.OW);
-                const long long q = m / a.OW;
-                const int oy = (int)(q % a.OH);
+                const unsigned mu = (unsigned)m;               // M < 2^31
+                const unsigned qd = mu / (unsigned)a.OW;
+                const int ox = (int)(mu - qd * (unsigned)a.OW);
+                const int oy = (int)(qd % (unsigned)a.OH);
                 const int iy = oy * a.sh - a.pt, ix = ox * a.sw - a.pl;
                 // first in-image tap, one past the last in-image tap
                 ky0 = iy < 0 ? (-iy + a.dh - 1) / a.dh : 0;
@@ -341,50 +437,39 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 ky0 = min(ky0, a.KH); kx0 = min(kx0, a.KW);
                 ky1 = max(ky1, ky0);  kx1 = max(kx1, kx0);
             }
-            const int32_t* p11 = s_prefix + (ky1 * pw + kx1) * BN;
-            const int32_t* p01 = s_prefix + (ky0 * pw + kx1) * BN;
-            const int32_t* p10 = s_prefix + (ky1 * pw + kx0) * BN;
-            const int32_t* p00 = s_prefix + (ky0 * pw + kx0) * BN;
+            const bool interior = ky0 == 0 && kx0 == 0 && ky1 == a.KH && kx1 == a.KW;
+            const bool warp_interior = __all_sync(0xffffffffu, interior || !mvalid);
+            ec.p11 = s_prefix + (ky1 * pw + kx1) * BN;
+            ec.p01 = s_prefix + (ky0 * pw + kx1) * BN;
+            ec.p10 = s_prefix + (ky1 * pw + kx0) * BN;
+            ec.p00 = s_prefix + (ky0 * pw + kx0) * BN;
             const uint32_t tacc = tmem_base + (uint32_t)(buf * BN) + ((uint32_t)(quad * 32) << 16);
             #pragma unroll 1
-            for (int cb = 0; cb < COLS_PER_HALF; cb += 32) {
-                const int col0 = half * COLS_PER_HALF + cb;
-                uint32_t r[32];
-                tc_ld32(tacc + (uint32_t)col0, r);
+            for (int cb = 0; cb < COLS_PER_PART; cb += 16) {
+                const int col0 = part * COLS_PER_PART + cb;
+                uint32_t r[16];
+                tc_ld16(tacc + (uint32_t)col0, r);
                 if (!mvalid) continue;
                 const long long obase = m * a.OC + n0 + col0;
-                uint32_t resw[8];
-                if (a.res) {
-                    const uint4* rp = (const uint4*)(a.res + obase);
-                    const uint4 r0 = rp[0], r1 = rp[1];
-                    resw[0] = r0.x; resw[1] = r0.y; resw[2] = r0.z; resw[3] = r0.w;
-                    resw[4] = r1.x; resw[5] = r1.y; resw[6] = r1.z; resw[7] = r1.w;
-                }
-                uint32_t packed[8];
-                #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const int col = col0 + j;
-                    int acc = (int)r[j];
-                    if (a.need_corr) acc -= a.zx * (p11[col] - p01[col] - p10[col] + p00[col]);
-                    if (a.acc_out) a.acc_out[obase + j] = acc;
-                    float v = __fmul_rn(__int2float_rn(acc), s_m[col]);
-                    if (has_bias) v = __fadd_rn(v, s_bterm[col]);
-                    int q = quantize_fast(v, a.rq, a.inv_sy);
-                    if (a.res) {
-                        // fused ElementwiseBinary Add: the convolution's own 8-bit output is formed first, then
-                        // both operands are dequantised, added in fp32 and re-quantised, as the two workloads do
-                        const uint32_t rb = (resw[j >> 2] >> (8 * (j & 3))) & 0xff;
-                        const int rq8 = a.res_u8 ? (int)rb : (int)(int8_t)rb;
-                        const float fa = __fmul_rn(__int2float_rn(q - a.rq.zy), a.rq.sy);
-                        const float fb = __fmul_rn(__int2float_rn(rq8 - a.res_zp), a.res_scale);
-                        q = quantize_fast(__fadd_rn(fa, fb), a.rq2, a.inv_sy2);
+                if (a.acc_out) {                               // raw accumulators for the bit-exactness tests
+                    for (int j = 0; j < 16; ++j) {
+                        const int col = col0 + j;
+                        const int c = warp_interior ? s_corr[col]
+                                                    : ec.zx * (ec.p11[col] - ec.p01[col] - ec.p10[col] + ec.p00[col]);
+                        a.acc_out[obase + j] = (int)r[j] - c;
                     }
-                    if ((j & 3) == 0) packed[j >> 2] = 0;
-                    packed[j >> 2] |= (uint32_t)(q & 0xff) << (8 * (j & 3));
                 }
-                uint4* dst = (uint4*)((uint8_t*)a.y + obase);
-                dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                uint4 outv;
+                if (a.res) {
+                    const uint4 rv = *(const uint4*)(a.res + obase);
+                    if (warp_interior) outv = epi_chunk<true, true>(r, rv, s_m + col0, s_bterm + col0, s_corr + col0, col0, ec);
+                    else               outv = epi_chunk<true, false>(r, rv, s_m + col0, s_bterm + col0, s_corr + col0, col0, ec);
+                } else {
+                    const uint4 rv = make_uint4(0, 0, 0, 0);
+                    if (warp_interior) outv = epi_chunk<false, true>(r, rv, s_m + col0, s_bterm + col0, s_corr + col0, col0, ec);
+                    else               outv = epi_chunk<false, false>(r, rv, s_m + col0, s_bterm + col0, s_corr + col0, col0, ec);
+                }
+                *(uint4*)((uint8_t*)a.y + obase) = outv;
             }
             // this warp has finished reading the accumulator buffer
             tc_fence_before();
@@ -535,6 +620,9 @@ int launch_conv_tc(const b200k_conv2d_params* p, cudaStream_t stream)
     a.res = fa.res; a.res_scale = fa.res_scale; a.res_zp = fa.res_zp; a.res_u8 = fa.res_u8;
     a.rq2 = fa.out;
     a.inv_sy2 = fa.res ? 1.0f / p->add_out.scale : 0.f;
+    // Measurement aid (results are wrong in modes 1 and 2): isolates the TMA side or the MMA side of the main loop.
+    static const int debug_mode = getenv("B200K_TC_DEBUG") ? atoi(getenv("B200K_TC_DEBUG")) : 0;
+    a.debug = debug_mode;
 
     const int bn = pick_bn(p->oc);
     CUtensorMap tmA, tmB;
