@@ -13,6 +13,13 @@
 //   * eight epilogue warps read the accumulator with tcgen05.ld, apply the zero-point correction, bias and the
 //     fp32 requantisation, and store 8-bit outputs.
 //
+// Convolutions with very few input channels (the 3-channel network stems) cannot feed TMA directly: a pixel is
+// not a 16-byte unit.  For those a pre-pass re-packs the input into caller-provided scratch as
+// [N][Hp][Wp][8 or 16] with the spatial padding materialised (filled with the input zero point) and the channels
+// padded, and the kernel runs in "row-window" mode: a tile is one output row, and the A operand of filter row ky is
+// a tiled TMA box over an overlapping-window view of the packed rows (window = KW pixels = one 64- or 128-byte
+// K-slice, window stride = stride_w pixels), so K = KH slices.  The weights are re-packed to match at load time.
+//
 // Zero points.  TMA fills out-of-image taps with raw zeros, whereas the reference pads with the real value 0,
 // i.e. with the quantised value zx.  With symmetric weights (zw = 0)
 //     sum_valid (x - zx) w = sum_all x_filled w - zx * sum_valid w
@@ -27,6 +34,7 @@
 // b200k_poll_status), drains and returns, so a logic error cannot hang the device.
 #include <cuda.h>
 #include <stdlib.h>
+#include <string.h>
 #include <cudaTypedefs.h>
 #include "common.cuh"
 
@@ -47,7 +55,11 @@ struct TcArgs {
     int zx;                                     // true input zero point
     int N, H, W, C, OH, OW, OC, KH, KW, sh, sw, pt, pl, dh, dw;
     long long M;
-    int im2col;                                 // 0: A is a 2-D [M, C] matrix; 1: TMA im2col from NHWC
+    int im2col;                                 // 0: A is a 2-D [M, C] matrix; 1: TMA im2col from NHWC; 2: row-window
+    int tile_rows;                              // valid rows of an M-tile: 128, or OW in row-window mode
+    int ntm;                                    // number of M-tiles
+    int kstride;                                // bytes between consecutive taps in a weight row (C, or the window)
+    uint32_t stage_tx;                          // bytes one ring stage receives
     int cchunks;                                // C / BK
     int nslices;                                // KH*KW*cchunks
     int need_corr;                              // zx != 0
@@ -92,6 +104,11 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, u
 {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
                  ::"r"(smem_u32(dst)), "l"((uint64_t)map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2, int c3)
+{
+    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+                 ::"r"(smem_u32(dst)), "l"((uint64_t)map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
 }
 __device__ __forceinline__ void tma_load_im2col(void* dst, const CUtensorMap* map, uint64_t* bar, int c, int w, int h,
                                                 int n, uint16_t off_w, uint16_t off_h)
@@ -287,8 +304,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int ntn = a.OC / BN;                              // n-tiles (OC is a multiple of BN)
-    const int ntm = (int)((a.M + TC_BM - 1) / TC_BM);
-    const int ntiles = ntn * ntm;
+    const int ntiles = ntn * a.ntm;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -311,9 +327,12 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             bool alive = true;
             for (int t = blockIdx.x; t < ntiles && alive; t += gridDim.x) {
                 const int n0 = (t % ntn) * BN;
-                const long long m0 = (long long)(t / ntn) * TC_BM;
+                const long long m0 = (long long)(t / ntn) * a.tile_rows;
                 int w0 = 0, h0 = 0, nimg = 0;
-                if (a.im2col) {
+                if (a.im2col == 2) {
+                    nimg = (int)((t / ntn) / a.OH);
+                    h0 = (int)((t / ntn) % a.OH) * a.sh;          // first packed row of this output row
+                } else if (a.im2col) {
                     const int ox = (int)(m0 % a.OW);
                     const long long q = m0 / a.OW;
                     const int oy = (int)(q % a.OH);
@@ -330,14 +349,16 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     uint8_t* sa = smem + st * L::STAGE_BYTES;
                     uint8_t* sb = sa + L::A_BYTES;
                     if (a.debug == 2) { mbar_arrive(&full[st]); continue; }
-                    mbar_expect_tx(&full[st], L::STAGE_BYTES);
-                    if (a.im2col) {
+                    mbar_expect_tx(&full[st], a.stage_tx);
+                    if (a.im2col == 2) {
+                        tma_load_4d(sa, &tmA, &full[st], 0, 0, h0 + tap * a.dh, nimg);   // tap = filter row
+                    } else if (a.im2col) {
                         const int ky = tap / a.KW, kx = tap - ky * a.KW;
                         tma_load_im2col(sa, &tmA, &full[st], c0, w0, h0, nimg, (uint16_t)(kx * a.dw), (uint16_t)(ky * a.dh));
                     } else {
                         tma_load_2d(sa, &tmA, &full[st], c0, (int)m0);
                     }
-                    tma_load_2d(sb, &tmB, &full[st], tap * a.C + c0, n0);
+                    tma_load_2d(sb, &tmB, &full[st], tap * a.kstride + c0, n0);
                 }
             }
         }
@@ -395,7 +416,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         int it = 0;
         for (int t = blockIdx.x; t < ntiles; t += gridDim.x, ++it) {
             const int n0 = (t % ntn) * BN;
-            const long long m0 = (long long)(t / ntn) * TC_BM;
+            const long long m0 = (long long)(t / ntn) * a.tile_rows;
             const int buf = it & 1;
             if (n0 != cur_n0) {
                 // per-channel constants of this n-tile (all epilogue warps are between tiles here)
@@ -420,7 +441,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             tc_fence_after();
             const int row = quad * 32 + lane;
             const long long m = m0 + row;
-            const bool mvalid = m < a.M;
+            const bool mvalid = row < a.tile_rows && m < a.M;
             // rectangle of in-image taps of this pixel
             int ky0 = 0, ky1 = a.KH, kx0 = 0, kx1 = a.KW;
             if (a.need_rect) {
@@ -510,6 +531,78 @@ __global__ void conv_prefix_kernel(const PackArgs a)
     }
 }
 
+// ---- row-window mode: plan, weight re-pack (load time) and input re-pack (every call) -------------------------
+
+struct RowPlan {
+    bool ok;
+    int cpad;                 // channels per packed pixel (8 or 16 bytes)
+    int swz;                  // window bytes = K-slice = swizzle span (64 or 128)
+    int hp, wp;               // packed rows / pixels per row (spatial padding materialised)
+    size_t scratch_bytes;     // packed input
+    size_t wpack_offset;      // offset of the re-packed weights inside `packed`
+};
+
+static RowPlan row_window_plan(const b200k_conv2d_params* p)
+{
+    RowPlan r;
+    memset(&r, 0, sizeof(r));
+    if (p->c > 16 || p->c < 1 || p->dil_w != 1 || p->ow > TC_BM || p->oc % 64 != 0 || p->kh > 15 || p->kw > 15) return r;
+    if (p->w.zero_point != 0 || p->stride_w > 8 || p->stride_h > 8) return r;
+    r.cpad = (p->c <= 8 && (p->stride_w * 8) % 16 == 0) ? 8 : 16;
+    const int window = p->kw * r.cpad;
+    if (window > 128) return r;
+    r.swz = window <= 64 ? 64 : 128;
+    r.hp = (p->oh - 1) * p->stride_h + (p->kh - 1) * p->dil_h + 1;
+    r.wp = (p->ow - 1) * p->stride_w + r.swz / r.cpad;
+    if ((r.wp * r.cpad) % 16 != 0) r.wp += 1;
+    r.scratch_bytes = (size_t)p->n * r.hp * r.wp * r.cpad;
+    r.wpack_offset = (size_t)(p->kh + 1) * (p->kw + 1) * p->oc * sizeof(int32_t);
+    r.ok = true;
+    return r;
+}
+
+struct RowWeightArgs { const uint8_t* w; uint8_t* wp; int OC, KH, KW, C, cpad, swz; };
+
+// wp[oc][ky][kx * cpad + c] = w[oc][ky][kx][c]; every other byte of the swz-wide window is 0
+__global__ void row_weight_pack_kernel(const RowWeightArgs a)
+{
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= a.OC * a.KH * a.swz) return;
+    const int b = i % a.swz;
+    const int ky = (i / a.swz) % a.KH;
+    const int oc = i / (a.swz * a.KH);
+    const int kx = b / a.cpad, c = b - kx * a.cpad;
+    uint8_t v = 0;
+    if (kx < a.KW && c < a.C) v = a.w[(((long long)oc * a.KH + ky) * a.KW + kx) * a.C + c];
+    a.wp[i] = v;
+}
+
+struct RowInputArgs { const uint8_t* x; uint8_t* xp; int N, H, W, C, hp, wp, cpad, pt, pl; unsigned fill; long long total; };
+
+// xp[n][yp][xq][0..cpad) = x[n][yp - pt][xq - pl][0..C) inside the image, the input zero point everywhere else
+template <int CPAD>
+__global__ void __launch_bounds__(256) row_input_pack_kernel(const RowInputArgs a)
+{
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= a.total) return;
+    const int xq = (int)(i % a.wp);
+    const long long t = i / a.wp;
+    const int yp = (int)(t % a.hp);
+    const int n = (int)(t / a.hp);
+    const int iy = yp - a.pt, ix = xq - a.pl;
+    uint8_t v[CPAD];
+    #pragma unroll
+    for (int c = 0; c < CPAD; ++c) v[c] = (uint8_t)a.fill;
+    if (iy >= 0 && iy < a.H && ix >= 0 && ix < a.W) {
+        const uint8_t* src = a.x + (((long long)n * a.H + iy) * a.W + ix) * a.C;
+        #pragma unroll
+        for (int c = 0; c < CPAD; ++c)
+            if (c < a.C) v[c] = src[c];
+    }
+    if (CPAD == 8) *(uint2*)(a.xp + i * 8) = *(const uint2*)v;
+    else           *(uint4*)(a.xp + i * 16) = *(const uint4*)v;
+}
+
 // ---- host side ---------------------------------------------------------------------------------------------------
 
 static PFN_cuTensorMapEncodeTiled_v12000 g_encode_tiled = nullptr;
@@ -530,8 +623,22 @@ static bool load_driver_entry_points()
 
 static int pick_bn(int oc) { return (oc % 256 == 0) ? 256 : (oc % 128 == 0) ? 128 : 64; }
 
+static bool row_window_eligible(const b200k_conv2d_params* p)
+{
+    const RowPlan r = row_window_plan(p);
+    if (!r.ok || !p->packed || !p->scratch || p->scratch_bytes < r.scratch_bytes) return false;
+    const void* outp = p->add_operand.data ? p->add_out.data : p->y.data;
+    if (!p->x.data || !p->w.data || !outp) return false;
+    if (!is_q8(p->x.dtype) || !is_q8(p->w.dtype) || !is_q8(p->y.dtype)) return false;
+    if ((((uintptr_t)p->scratch | (uintptr_t)p->packed | (uintptr_t)outp) & 15) != 0) return false;
+    if (p->add_operand.data && ((((uintptr_t)p->add_operand.data) & 15) != 0)) return false;
+    if ((long long)p->n * p->oh > (1ll << 30) || (long long)p->n * p->oh * p->ow > (1ll << 31) - TC_BM) return false;
+    return true;
+}
+
 bool conv_tc_eligible(const b200k_conv2d_params* p)
 {
+    if (p->c <= 16) return row_window_eligible(p);
     const void* outp = p->add_operand.data ? p->add_out.data : p->y.data;
     if (!p->x.data || !p->w.data || !outp) return false;
     if (!is_q8(p->x.dtype) || !is_q8(p->w.dtype) || !is_q8(p->y.dtype)) return false;
@@ -581,7 +688,7 @@ static int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const TcArg
         B200K_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured = smem;
     }
-    const long long tiles = (long long)(a.OC / BN) * ((a.M + TC_BM - 1) / TC_BM);
+    const long long tiles = (long long)(a.OC / BN) * a.ntm;
     const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
     kern<<<grid, TC_THREADS, smem, stream>>>(tmA, tmB, a);
     return check_launch("conv_tc_kernel");
@@ -600,17 +707,23 @@ int launch_conv_tc(const b200k_conv2d_params* p, cudaStream_t stream)
     a.KH = p->kh; a.KW = p->kw; a.sh = p->stride_h; a.sw = p->stride_w; a.pt = p->pad_top; a.pl = p->pad_left;
     a.dh = p->dil_h; a.dw = p->dil_w;
     a.M = (long long)p->n * p->oh * p->ow;
-    const bool gemm = p->kh == 1 && p->kw == 1 && p->stride_h == 1 && p->stride_w == 1 && p->pad_top == 0 &&
+    const RowPlan rowp = p->c <= 16 ? row_window_plan(p) : RowPlan{};
+    const bool row_mode = rowp.ok;
+    const bool gemm = !row_mode && p->kh == 1 && p->kw == 1 && p->stride_h == 1 && p->stride_w == 1 && p->pad_top == 0 &&
                       p->pad_left == 0 && p->oh == p->h && p->ow == p->wd;
-    a.im2col = gemm ? 0 : 1;
-    const int swz = (p->c % 128 == 0) ? 128 : 64;
-    a.cchunks = p->c / swz;
-    a.nslices = p->kh * p->kw * a.cchunks;
+    a.im2col = row_mode ? 2 : gemm ? 0 : 1;
+    const int swz = row_mode ? rowp.swz : (p->c % 128 == 0) ? 128 : 64;
+    a.cchunks = row_mode ? 1 : p->c / swz;
+    a.nslices = row_mode ? p->kh : p->kh * p->kw * a.cchunks;
+    a.tile_rows = row_mode ? p->ow : TC_BM;
+    a.ntm = row_mode ? p->n * p->oh : (int)((a.M + TC_BM - 1) / TC_BM);
+    a.kstride = row_mode ? swz : p->c;
     a.need_corr = a.zx != 0;
     // can any tap of any output pixel leave the image?
     const int last_y = (p->oh - 1) * p->stride_h - p->pad_top + (p->kh - 1) * p->dil_h;
     const int last_x = (p->ow - 1) * p->stride_w - p->pad_left + (p->kw - 1) * p->dil_w;
-    const int rect = (a.need_corr && (p->pad_top > 0 || p->pad_left > 0 || last_y >= p->h || last_x >= p->wd)) ? 1 : 0;
+    // (row-window mode materialises the padding with the zero point itself: no tap is ever "outside")
+    const int rect = (!row_mode && a.need_corr && (p->pad_top > 0 || p->pad_left > 0 || last_y >= p->h || last_x >= p->wd)) ? 1 : 0;
     a.need_rect = rect;
     a.a_signed = p->x.dtype == B200K_S8;
     a.b_signed = p->w.dtype == B200K_S8;
@@ -627,18 +740,41 @@ int launch_conv_tc(const b200k_conv2d_params* p, cudaStream_t stream)
     const int bn = pick_bn(p->oc);
     CUtensorMap tmA, tmB;
     const CUtensorMapSwizzle swizzle = swz == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
-    {   // weights: 2-D [OC][K] matrix, box = swz bytes x bn rows
-        const cuuint64_t K = (cuuint64_t)p->kh * p->kw * p->c;
+    a.stage_tx = (uint32_t)((a.tile_rows + bn) * swz);
+    {   // weights: 2-D [OC][K] matrix, box = swz bytes x bn rows (row-window mode: the re-packed [OC][KH * swz] copy)
+        const cuuint64_t K = row_mode ? (cuuint64_t)p->kh * swz : (cuuint64_t)p->kh * p->kw * p->c;
+        const void* wptr = row_mode ? (const void*)((const uint8_t*)p->packed + rowp.wpack_offset) : p->w.data;
         cuuint64_t dims[2] = {K, (cuuint64_t)p->oc};
         cuuint64_t strides[1] = {K};
         cuuint32_t box[2] = {(cuuint32_t)swz, (cuuint32_t)bn};
         cuuint32_t estr[2] = {1, 1};
-        CUresult r = g_encode_tiled(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void*)p->w.data, dims, strides, box, estr,
+        CUresult r = g_encode_tiled(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void*)wptr, dims, strides, box, estr,
                                     CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         B200K_REQUIRE(r == CUDA_SUCCESS, B200K_E_CUDA, "conv2d_q8: cuTensorMapEncodeTiled(weights) failed with %d", (int)r);
     }
-    if (gemm) {
+    if (row_mode) {
+        // re-pack the input into the caller's scratch, then view it as overlapping windows: dim0 = the window's bytes,
+        // dim1 = output column (stride = stride_w pixels), dim2 = packed row, dim3 = image
+        RowInputArgs ra;
+        ra.x = (const uint8_t*)p->x.data; ra.xp = (uint8_t*)p->scratch;
+        ra.N = p->n; ra.H = p->h; ra.W = p->wd; ra.C = p->c; ra.hp = rowp.hp; ra.wp = rowp.wp; ra.cpad = rowp.cpad;
+        ra.pt = p->pad_top; ra.pl = p->pad_left; ra.fill = (unsigned)(p->x.zero_point & 0xff);
+        ra.total = (long long)p->n * rowp.hp * rowp.wp;
+        if (rowp.cpad == 8) row_input_pack_kernel<8><<<div_up(ra.total, 256), 256, 0, stream>>>(ra);
+        else                row_input_pack_kernel<16><<<div_up(ra.total, 256), 256, 0, stream>>>(ra);
+        int rc = check_launch("row_input_pack_kernel");
+        if (rc) return rc;
+        const cuuint64_t rowb = (cuuint64_t)rowp.wp * rowp.cpad;
+        cuuint64_t dims[4] = {(cuuint64_t)swz, (cuuint64_t)p->ow, (cuuint64_t)rowp.hp, (cuuint64_t)p->n};
+        cuuint64_t strides[3] = {(cuuint64_t)p->stride_w * rowp.cpad, rowb, rowb * rowp.hp};
+        cuuint32_t box[4] = {(cuuint32_t)swz, (cuuint32_t)p->ow, 1, 1};
+        cuuint32_t estr[4] = {1, 1, 1, 1};
+        CUresult r = g_encode_tiled(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, p->scratch, dims, strides, box, estr,
+                                    CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        B200K_REQUIRE(r == CUDA_SUCCESS, B200K_E_CUDA, "conv2d_q8: cuTensorMapEncodeTiled(row windows) failed with %d", (int)r);
+    } else if (gemm) {
         cuuint64_t dims[2] = {(cuuint64_t)p->c, (cuuint64_t)a.M};
         cuuint64_t strides[1] = {(cuuint64_t)p->c};
         cuuint32_t box[2] = {(cuuint32_t)swz, (cuuint32_t)TC_BM};
@@ -681,9 +817,17 @@ using namespace b200k;
 
 extern "C" size_t b200k_conv2d_pack_bytes(int32_t oc, int32_t kh, int32_t kw, int32_t c)
 {
-    (void)c;
     if (oc <= 0 || kh <= 0 || kw <= 0) return 0;
-    return (size_t)(kh + 1) * (kw + 1) * oc * sizeof(int32_t);
+    size_t n = (size_t)(kh + 1) * (kw + 1) * oc * sizeof(int32_t);      // prefix table
+    if (c <= 16) n += (size_t)oc * kh * 128;                              // row-window weights (widest window)
+    return n;
+}
+
+extern "C" size_t b200k_conv2d_scratch_bytes(const b200k_conv2d_params* p)
+{
+    if (!p || p->c > 16) return 0;
+    const RowPlan r = row_window_plan(p);
+    return r.ok ? r.scratch_bytes : 0;
 }
 
 extern "C" int b200k_conv2d_pack(const b200k_conv2d_params* p, void* packed, void* stream)
@@ -695,7 +839,24 @@ extern "C" int b200k_conv2d_pack(const b200k_conv2d_params* p, void* packed, voi
     a.w = (const uint8_t*)p->w.data; a.prefix = (int32_t*)packed; a.w_u8 = p->w.dtype == B200K_U8;
     a.OC = p->oc; a.KH = p->kh; a.KW = p->kw; a.C = p->c;
     conv_prefix_kernel<<<div_up(p->oc, 128), 128, 0, (cudaStream_t)stream>>>(a);
-    return check_launch("conv_prefix_kernel");
+    int rc = check_launch("conv_prefix_kernel");
+    if (rc || p->c > 16) return rc;
+    // weights of a few-channel convolution, re-packed for the row-window mode (needs kw, c and stride_w)
+    b200k_conv2d_params q = *p;
+    if (q.stride_w <= 0) q.stride_w = 1;
+    if (q.stride_h <= 0) q.stride_h = 1;
+    if (q.dil_w <= 0) q.dil_w = 1;
+    if (q.dil_h <= 0) q.dil_h = 1;
+    if (q.ow <= 0) q.ow = 1;
+    if (q.oh <= 0) q.oh = 1;
+    if (q.n <= 0) q.n = 1;
+    const RowPlan r = row_window_plan(&q);
+    if (!r.ok) return B200K_OK;
+    RowWeightArgs wa;
+    wa.w = (const uint8_t*)p->w.data; wa.wp = (uint8_t*)packed + r.wpack_offset;
+    wa.OC = p->oc; wa.KH = p->kh; wa.KW = p->kw; wa.C = p->c; wa.cpad = r.cpad; wa.swz = r.swz;
+    row_weight_pack_kernel<<<div_up((long long)p->oc * p->kh * r.swz, 256), 256, 0, (cudaStream_t)stream>>>(wa);
+    return check_launch("row_weight_pack_kernel");
 }
 
 extern "C" int b200k_poll_status(void)

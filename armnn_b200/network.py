@@ -485,6 +485,9 @@ class GraphProgram:
         runtime overrides this."""
         return None
 
+    def _attach_scratch(self, conv_params):
+        """Per-call scratch of a convolution workload (b200k_conv2d_scratch_bytes); CUDA runtime only."""
+
     # -- workload construction -------------------------------------------------------------------------
     def _build(self):
         for layer in self.layers:
@@ -532,6 +535,7 @@ class GraphProgram:
             p.add_operand = self._operand(layer.inputs[-1].source)
         if not depthwise:
             p.packed = self._pack_weights(p)
+            self._attach_scratch(p)
         return p
 
     def _make_Convolution2d(self, layer):
@@ -732,6 +736,13 @@ class LoadedNetwork(GraphProgram):
         lib.check(l.b200k_conv2d_pack(ctypes.byref(conv_params), ctypes.c_void_p(table.data_ptr()),
                                       ctypes.c_void_p(self.torch.cuda.current_stream().cuda_stream)))
         return table.data_ptr()
+
+    def _attach_scratch(self, conv_params):
+        nbytes = lib.load_library().b200k_conv2d_scratch_bytes(ctypes.byref(conv_params))
+        if nbytes:
+            buf = self.torch.empty(nbytes, dtype=self.torch.uint8, device=self.rt.device)
+            self.aux.append(buf)
+            conv_params.scratch, conv_params.scratch_bytes = buf.data_ptr(), nbytes
 
     # -- execution ---------------------------------------------------------------------------------
     def launch_all(self, stream_handle):

@@ -103,6 +103,11 @@ typedef struct {
      * Activation expressed through clamp_lo / clamp_hi, which then refer to add_out) would produce.
      * add_operand and add_out have the convolution's output shape (no broadcast). */
     b200k_qtensor add_operand, add_out;
+    /* Per-call device scratch (b200k_conv2d_scratch_bytes() bytes, 16-byte aligned) for convolutions with at most
+     * 16 input channels (network stems): the tcgen05 path re-packs the input there on every call.  NULL or too
+     * small: such convolutions run on the CUDA-core kernel. */
+    void* scratch;
+    size_t scratch_bytes;
 } b200k_conv2d_params;
 
 int b200k_conv2d_q8(const b200k_conv2d_params* p, void* stream);
@@ -115,6 +120,10 @@ int b200k_conv2d_q8(const b200k_conv2d_params* p, void* stream);
  * run on the CUDA-core kernel. */
 size_t b200k_conv2d_pack_bytes(int32_t oc, int32_t kh, int32_t kw, int32_t c);
 int b200k_conv2d_pack(const b200k_conv2d_params* p, void* packed, void* stream);
+/* Bytes of per-call scratch b200k_conv2d_q8 wants for this geometry (0 for most shapes).  For c <= 16 the packed
+ * table additionally holds the weights re-laid-out per filter row, which depends on kw, c and stride_w: those
+ * must be set when calling b200k_conv2d_pack. */
+size_t b200k_conv2d_scratch_bytes(const b200k_conv2d_params* p);
 
 /* armnn::FullyConnected (src/backends/reference/workloads/FullyConnected.cpp:13-65) from
  * RefFullyConnectedWorkload::Execute (RefFullyConnectedWorkload.cpp:16-67).

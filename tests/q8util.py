@@ -235,6 +235,10 @@ class ConvCase:
         p, y, acc = self.params(mem, want_acc, algo)
         if pack and not self.depthwise:
             p.packed = gpu_pack(mem, p)
+            nbytes = lib.load_library().b200k_conv2d_scratch_bytes(C.byref(p))
+            if nbytes:
+                _, p.scratch = mem.out((nbytes,), np.uint8)
+                p.scratch_bytes = nbytes
         lib.call("dwconv2d_q8" if self.depthwise else "conv2d_q8", p)
         return mem.fetch(y), (mem.fetch(acc) if acc is not None else None)
 

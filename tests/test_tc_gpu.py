@@ -32,6 +32,13 @@ CONV = {
     "im2col_fused_add": lambda: random_conv_case(218, 2, 14, 14, 64, 64, 3, 3, pad=(1, 1, 1, 1), fused_add=True),
     "gemm_many_tiles_persistent": lambda: random_conv_case(219, 4, 56, 56, 64, 256, 1, 1, act=(1, 0, 0)),
     "im2col_many_tiles_persistent": lambda: random_conv_case(220, 6, 28, 28, 128, 128, 3, 3, pad=(1, 1, 1, 1)),
+    "rowwin_stem_7x7_s2_c3": lambda: random_conv_case(240, 2, 64, 64, 3, 64, 7, 7, stride=(2, 2), pad=(2, 3, 2, 3), act=(1, 0, 0)),
+    "rowwin_stem_224": lambda: random_conv_case(241, 1, 224, 224, 3, 64, 7, 7, stride=(2, 2), pad=(2, 3, 2, 3), act=(1, 0, 0)),
+    "rowwin_3x3_s2_c3_u8": lambda: random_conv_case(242, 2, 32, 32, 3, 64, 3, 3, stride=(2, 2), pad=(0, 1, 0, 1), x_dtype=U8,
+                                                     y_dtype=U8, x_q=(0.02, 128)),
+    "rowwin_3x3_s1_c4": lambda: random_conv_case(243, 1, 20, 20, 4, 128, 3, 3, pad=(1, 1, 1, 1)),
+    "rowwin_5x5_s1_c16_dil_h2": lambda: random_conv_case(244, 1, 24, 24, 16, 64, 5, 5, pad=(4, 4, 2, 2), dil=(2, 1)),
+    "rowwin_1x1_c8_zx0": lambda: random_conv_case(245, 2, 9, 9, 8, 64, 1, 1, x_q=(0.02, 0)),
     "im2col_odd_image_7x7": lambda: random_conv_case(216, 5, 7, 7, 512, 512, 3, 3, pad=(1, 1, 1, 1), act=(1, 0, 0)),
 }
 
