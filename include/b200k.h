@@ -125,6 +125,16 @@ int b200k_conv2d_pack(const b200k_conv2d_params* p, void* packed, void* stream);
  * must be set when calling b200k_conv2d_pack. */
 size_t b200k_conv2d_scratch_bytes(const b200k_conv2d_params* p);
 
+/* Same operation as b200k_conv2d_q8 for callers that cannot hand over freshly allocated device buffers (a memory
+ * pool frozen before models are loaded, an allocator that is off limits after start-up).  p->packed and p->scratch
+ * are ignored: the weight table is rebuilt on every call and, like the re-packed input, lives in a 16 MiB device
+ * array built into the library (1 MiB for the table, 15 MiB for the input; every GPU that loads the library holds
+ * it until the process exits).  Shapes needing more return B200K_E_TOOBIG.  No cudaMalloc / cudaFree happens
+ * inside.  The first call on each device looks up the array's device address and should therefore come before any
+ * stream capture.  All calls share the array: calls that may overlap on the GPU (different streams) race.
+ * This entry point has no counterpart in the reference. */
+int b200k_conv2d_q8_static(const b200k_conv2d_params* p, void* stream);
+
 /* armnn::FullyConnected (src/backends/reference/workloads/FullyConnected.cpp:13-65) from
  * RefFullyConnectedWorkload::Execute (RefFullyConnectedWorkload.cpp:16-67).
  *   x [m, k]   w [n, k] when transpose_w != 0 (m_TransposeWeightMatrix) else [k, n]
