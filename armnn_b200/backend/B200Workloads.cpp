@@ -1,0 +1,567 @@
+// Workloads of the B200Acc backend: one per layer type on the quantised hot path, each one call of the libb200k
+// C ABI (include/b200k.h) on the backend's CUDA stream, plus the workload factory that creates them.
+//
+// A workload fills its parameter struct once, in its constructor, from the queue descriptor and the WorkloadInfo
+// (exactly the information the CpuRef workload of the same layer reads in Execute), resolves device pointers from
+// the tensor handles at Execute time, and launches asynchronously.  Nothing here computes on the CPU.
+#include "B200Workloads.hpp"
+
+#include <armnn/Exceptions.hpp>
+#include <armnn/backends/MemCopyWorkload.hpp>
+#include <armnn/backends/TensorHandle.hpp>
+#include <armnn/utility/PolymorphicDowncast.hpp>
+#include <backendsCommon/MemImportWorkload.hpp>
+#include <backendsCommon/MemSyncWorkload.hpp>
+
+#include <cstring>
+#include <functional>
+#include <mutex>
+
+#include "b200k.h"
+
+namespace armnn
+{
+
+namespace
+{
+
+int ToB200k(DataType t)
+{
+    switch (t)
+    {
+        case DataType::QAsymmU8: return B200K_U8;
+        case DataType::QAsymmS8:
+        case DataType::QSymmS8:  return B200K_S8;
+        case DataType::QSymmS16: return B200K_S16;
+        case DataType::Signed32: return B200K_S32;
+        case DataType::Float32:  return B200K_F32;
+        default: throw InvalidArgumentException("B200Acc: unsupported data type");
+    }
+}
+
+void* Dev(const ITensorHandle* h)
+{
+    return PolymorphicDowncast<const B200TensorHandle*>(h)->Device();
+}
+
+void Written(const ITensorHandle* h)
+{
+    PolymorphicDowncast<const B200TensorHandle*>(h)->MarkDeviceWritten();
+}
+
+// Small device arrays owned by a workload (per-axis scales, QLstm weights, packed tables, scratch).
+struct DeviceBlobs
+{
+    std::vector<void*> ptrs;
+    ~DeviceBlobs() { for (void* p : ptrs) { cudaFree(p); } }
+    void* Alloc(size_t bytes)
+    {
+        void* p = nullptr;
+        B200Device::Get().MakeCurrent();
+        B200Check(cudaMalloc(&p, bytes ? bytes : 16), "cudaMalloc");
+        ptrs.push_back(p);
+        return p;
+    }
+    void* Upload(const void* host, size_t bytes)
+    {
+        void* p = Alloc(bytes);
+        B200Check(cudaMemcpy(p, host, bytes, cudaMemcpyHostToDevice), "cudaMemcpy H2D");
+        return p;
+    }
+};
+
+b200k_qtensor Operand(const TensorInfo& info, DeviceBlobs& blobs)
+{
+    b200k_qtensor t;
+    std::memset(&t, 0, sizeof(t));
+    t.dtype = ToB200k(info.GetDataType());
+    if (info.HasMultipleQuantizationScales())
+    {
+        const std::vector<float> s = info.GetQuantizationScales();
+        t.scales = static_cast<const float*>(blobs.Upload(s.data(), s.size() * sizeof(float)));
+        t.scale = 1.0f;
+        t.zero_point = 0;
+    }
+    else if (IsQuantizedType(info.GetDataType()) || info.GetDataType() == DataType::Signed32)
+    {
+        t.scale = info.GetQuantizationScale();
+        t.zero_point = info.GetQuantizationOffset();
+    }
+    else
+    {
+        t.scale = 1.0f;
+    }
+    return t;
+}
+
+void Clamp(const ActivationDescriptor* act, const TensorInfo& out, int32_t& lo, int32_t& hi)
+{
+    int kind = 0;
+    float a = 0.f, b = 0.f;
+    if (act)
+    {
+        if (act->m_Function == ActivationFunction::ReLu) { kind = 1; }
+        else if (act->m_Function == ActivationFunction::BoundedReLu) { kind = 2; a = act->m_A; b = act->m_B; }
+        else { throw InvalidArgumentException("B200Acc: only ReLu / BoundedReLu can be fused"); }
+    }
+    B200CheckStatus(b200k_activation_clamp(kind, a, b, out.GetQuantizationScale(), out.GetQuantizationOffset(),
+                                           ToB200k(out.GetDataType()), &lo, &hi));
+}
+
+// Generic workload: `launch` is built by the factory and owns everything it needs.
+template <typename QueueDescriptor>
+class B200Workload : public BaseWorkload<QueueDescriptor>
+{
+public:
+    using Launch = std::function<void(const QueueDescriptor&, cudaStream_t)>;
+    B200Workload(const QueueDescriptor& d, const WorkloadInfo& info, Launch launch)
+        : BaseWorkload<QueueDescriptor>(d, info), m_Launch(std::move(launch)) {}
+    void Execute() const override
+    {
+        B200Device& dev = B200Device::Get();
+        dev.MakeCurrent();
+        m_Launch(this->m_Data, dev.Stream());
+        for (ITensorHandle* h : this->m_Data.m_Outputs) { Written(h); }
+    }
+private:
+    Launch m_Launch;
+};
+
+template <typename QD>
+std::unique_ptr<IWorkload> Make(const QueueDescriptor& d, const WorkloadInfo& info, typename B200Workload<QD>::Launch fn)
+{
+    return std::make_unique<B200Workload<QD>>(*PolymorphicDowncast<const QD*>(&d), info, std::move(fn));
+}
+
+struct ConvState
+{
+    b200k_conv2d_params p;
+    DeviceBlobs blobs;
+    void* packed = nullptr;
+    std::once_flag once;
+};
+
+template <typename QD>
+std::unique_ptr<IWorkload> MakeConv(const QueueDescriptor& d, const WorkloadInfo& info, bool depthwise)
+{
+    const QD& qd = *PolymorphicDowncast<const QD*>(&d);
+    const auto& prm = qd.m_Parameters;
+    if (prm.m_DataLayout != DataLayout::NHWC) { throw InvalidArgumentException("B200Acc: NHWC only"); }
+    auto st = std::make_shared<ConvState>();
+    b200k_conv2d_params& p = st->p;
+    std::memset(&p, 0, sizeof(p));
+    const TensorInfo& x = info.m_InputTensorInfos[0];
+    const TensorInfo& w = info.m_InputTensorInfos[1];
+    const TensorInfo& y = info.m_OutputTensorInfos[0];
+    p.x = Operand(x, st->blobs);
+    p.w = Operand(w, st->blobs);
+    p.y = Operand(y, st->blobs);
+    if (prm.m_BiasEnabled) { p.bias = Operand(info.m_InputTensorInfos[2], st->blobs); }
+    p.n = x.GetShape()[0]; p.h = x.GetShape()[1]; p.wd = x.GetShape()[2]; p.c = x.GetShape()[3];
+    p.oh = y.GetShape()[1]; p.ow = y.GetShape()[2]; p.oc = y.GetShape()[3];
+    p.kh = w.GetShape()[1]; p.kw = w.GetShape()[2];
+    p.stride_h = prm.m_StrideY; p.stride_w = prm.m_StrideX;
+    p.pad_top = prm.m_PadTop; p.pad_left = prm.m_PadLeft;
+    p.dil_h = prm.m_DilationY; p.dil_w = prm.m_DilationX;
+    Clamp(qd.template GetAdditionalInformation<ActivationDescriptor>(), y, p.clamp_lo, p.clamp_hi);
+    if (!depthwise)
+    {
+        st->packed = st->blobs.Alloc(b200k_conv2d_pack_bytes(p.oc, p.kh, p.kw, p.c));
+        const size_t scratch = b200k_conv2d_scratch_bytes(&p);
+        if (scratch) { p.scratch = st->blobs.Alloc(scratch); p.scratch_bytes = scratch; }
+    }
+    return Make<QD>(d, info, [st, depthwise](const QD& data, cudaStream_t s)
+    {
+        b200k_conv2d_params& q = st->p;
+        q.x.data = Dev(data.m_Inputs[0]);
+        q.w.data = Dev(data.m_Inputs[1]);
+        if (q.bias.dtype == B200K_S32 && data.m_Inputs.size() > 2) { q.bias.data = Dev(data.m_Inputs[2]); }
+        q.y.data = Dev(data.m_Outputs[0]);
+        if (depthwise) { B200CheckStatus(b200k_dwconv2d_q8(&q, s)); return; }
+        // The weight bytes reach the device when the Constant workloads run, which is after workload creation and
+        // PostAllocationConfigure (src/armnn/LoadedNetwork.cpp:559-568): build the weight table on first use.
+        std::call_once(st->once, [&] { B200CheckStatus(b200k_conv2d_pack(&q, st->packed, s)); q.packed = st->packed; });
+        B200CheckStatus(b200k_conv2d_q8(&q, s));
+    });
+}
+
+struct FcState
+{
+    b200k_fc_params p;
+    DeviceBlobs blobs;
+    void* packed = nullptr;
+    std::once_flag once;
+};
+
+std::unique_ptr<IWorkload> MakeFc(const QueueDescriptor& d, const WorkloadInfo& info)
+{
+    const auto& qd = *PolymorphicDowncast<const FullyConnectedQueueDescriptor*>(&d);
+    auto st = std::make_shared<FcState>();
+    b200k_fc_params& p = st->p;
+    std::memset(&p, 0, sizeof(p));
+    const TensorInfo& x = info.m_InputTensorInfos[0];
+    const TensorInfo& w = info.m_InputTensorInfos[1];
+    const TensorInfo& y = info.m_OutputTensorInfos[0];
+    p.x = Operand(x, st->blobs);
+    p.w = Operand(w, st->blobs);
+    p.y = Operand(y, st->blobs);
+    if (qd.m_Parameters.m_BiasEnabled) { p.bias = Operand(info.m_InputTensorInfos[2], st->blobs); }
+    p.m = x.GetShape()[0];
+    p.k = x.GetNumElements() / x.GetShape()[0];          // inputs of rank > 2 are flattened (FullyConnected.cpp:16-24)
+    p.n = y.GetShape()[y.GetNumDimensions() - 1];
+    p.transpose_w = qd.m_Parameters.m_TransposeWeightMatrix ? 1 : 0;
+    Clamp(qd.GetAdditionalInformation<ActivationDescriptor>(), y, p.clamp_lo, p.clamp_hi);
+    if (p.transpose_w) { st->packed = st->blobs.Alloc(b200k_conv2d_pack_bytes(p.n, 1, 1, p.k)); }
+    return Make<FullyConnectedQueueDescriptor>(d, info, [st](const FullyConnectedQueueDescriptor& data, cudaStream_t s)
+    {
+        b200k_fc_params& q = st->p;
+        q.x.data = Dev(data.m_Inputs[0]);
+        q.w.data = Dev(data.m_Inputs[1]);
+        if (q.bias.dtype == B200K_S32 && data.m_Inputs.size() > 2) { q.bias.data = Dev(data.m_Inputs[2]); }
+        q.y.data = Dev(data.m_Outputs[0]);
+        if (st->packed)
+        {
+            std::call_once(st->once, [&]
+            {
+                b200k_conv2d_params c;
+                std::memset(&c, 0, sizeof(c));
+                c.w = q.w; c.oc = q.n; c.kh = 1; c.kw = 1; c.c = q.k;
+                B200CheckStatus(b200k_conv2d_pack(&c, st->packed, s));
+                q.packed = st->packed;
+            });
+        }
+        B200CheckStatus(b200k_fully_connected_q8(&q, s));
+    });
+}
+
+template <typename P>
+struct SimpleState
+{
+    P p;
+    DeviceBlobs blobs;
+};
+
+std::unique_ptr<IWorkload> MakeEltwise(const QueueDescriptor& d, const WorkloadInfo& info, BinaryOperation op,
+                                       const ActivationDescriptor* act)
+{
+    auto st = std::make_shared<SimpleState<b200k_eltwise_params>>();
+    b200k_eltwise_params& p = st->p;
+    std::memset(&p, 0, sizeof(p));
+    const TensorInfo& a = info.m_InputTensorInfos[0];
+    const TensorInfo& b = info.m_InputTensorInfos[1];
+    const TensorInfo& o = info.m_OutputTensorInfos[0];
+    p.a = Operand(a, st->blobs); p.b = Operand(b, st->blobs); p.out = Operand(o, st->blobs);
+    p.rank = static_cast<int32_t>(o.GetNumDimensions());
+    if (p.rank > 4 || a.GetNumDimensions() != o.GetNumDimensions() || b.GetNumDimensions() != o.GetNumDimensions())
+    {
+        throw InvalidArgumentException("B200Acc: elementwise operands must share a rank <= 4");
+    }
+    for (int i = 0; i < p.rank; ++i)
+    {
+        p.shape_a[i] = a.GetShape()[i]; p.shape_b[i] = b.GetShape()[i]; p.shape_out[i] = o.GetShape()[i];
+    }
+    p.op = static_cast<int32_t>(op);
+    if (o.GetDataType() != DataType::Float32) { Clamp(act, o, p.clamp_lo, p.clamp_hi); }
+    auto fn = [st](const QueueDescriptor& data, cudaStream_t s)
+    {
+        b200k_eltwise_params& q = st->p;
+        q.a.data = Dev(data.m_Inputs[0]); q.b.data = Dev(data.m_Inputs[1]); q.out.data = Dev(data.m_Outputs[0]);
+        B200CheckStatus(b200k_eltwise_q8(&q, s));
+    };
+    if (auto* e = dynamic_cast<const ElementwiseBinaryQueueDescriptor*>(&d))
+    {
+        return std::make_unique<B200Workload<ElementwiseBinaryQueueDescriptor>>(*e, info, fn);
+    }
+    if (auto* e = dynamic_cast<const AdditionQueueDescriptor*>(&d))
+    {
+        return std::make_unique<B200Workload<AdditionQueueDescriptor>>(*e, info, fn);
+    }
+    if (auto* e = dynamic_cast<const MultiplicationQueueDescriptor*>(&d))
+    {
+        return std::make_unique<B200Workload<MultiplicationQueueDescriptor>>(*e, info, fn);
+    }
+    return nullptr;
+}
+
+// Device copies of the QLstm weights: the descriptor's ConstTensorHandles are released by the layer right after
+// CreateWorkload (src/armnn/LoadedNetwork.cpp:396), as RefQLstmWorkload's AssignScopedTensorHandle copies show.
+std::unique_ptr<IWorkload> MakeQLstm(const QueueDescriptor& d, const WorkloadInfo& info)
+{
+    const auto& qd = *PolymorphicDowncast<const QLstmQueueDescriptor*>(&d);
+    auto st = std::make_shared<SimpleState<b200k_qlstm_params>>();
+    b200k_qlstm_params& p = st->p;
+    std::memset(&p, 0, sizeof(p));
+    const TensorInfo& x = info.m_InputTensorInfos[0];
+    const TensorInfo& h = info.m_InputTensorInfos[1];
+    const TensorInfo& c = info.m_InputTensorInfos[2];
+    const TensorInfo& out = info.m_OutputTensorInfos[2];
+    p.batch = x.GetShape()[0]; p.input_size = x.GetShape()[1];
+    p.output_size = h.GetShape()[1]; p.num_units = c.GetShape()[1];
+    p.input_scale = x.GetQuantizationScale(); p.input_zp = x.GetQuantizationOffset();
+    p.output_state_scale = h.GetQuantizationScale(); p.output_state_zp = h.GetQuantizationOffset();
+    p.cell_state_scale = c.GetQuantizationScale();
+    p.output_scale = out.GetQuantizationScale(); p.output_zp = out.GetQuantizationOffset();
+    const auto& prm = qd.m_Parameters;
+    auto up = [&](const ConstTensorHandle* t, float* scale) -> const void*
+    {
+        if (!t) { return nullptr; }
+        if (scale) { *scale = t->GetTensorInfo().GetQuantizationScale(); }
+        return st->blobs.Upload(t->GetConstTensor<void>(), t->GetTensorInfo().GetNumBytes());
+    };
+    if (!prm.m_CifgEnabled)
+    {
+        p.w_i2i = static_cast<const int8_t*>(up(qd.m_InputToInputWeights, &p.s_i2i));
+        p.w_r2i = static_cast<const int8_t*>(up(qd.m_RecurrentToInputWeights, &p.s_r2i));
+    }
+    p.w_i2f = static_cast<const int8_t*>(up(qd.m_InputToForgetWeights, &p.s_i2f));
+    p.w_i2c = static_cast<const int8_t*>(up(qd.m_InputToCellWeights, &p.s_i2c));
+    p.w_i2o = static_cast<const int8_t*>(up(qd.m_InputToOutputWeights, &p.s_i2o));
+    p.w_r2f = static_cast<const int8_t*>(up(qd.m_RecurrentToForgetWeights, &p.s_r2f));
+    p.w_r2c = static_cast<const int8_t*>(up(qd.m_RecurrentToCellWeights, &p.s_r2c));
+    p.w_r2o = static_cast<const int8_t*>(up(qd.m_RecurrentToOutputWeights, &p.s_r2o));
+    if (prm.m_PeepholeEnabled)
+    {
+        if (!prm.m_CifgEnabled) { p.w_c2i = static_cast<const int16_t*>(up(qd.m_CellToInputWeights, &p.s_c2i)); }
+        p.w_c2f = static_cast<const int16_t*>(up(qd.m_CellToForgetWeights, &p.s_c2f));
+        p.w_c2o = static_cast<const int16_t*>(up(qd.m_CellToOutputWeights, &p.s_c2o));
+    }
+    if (prm.m_LayerNormEnabled)
+    {
+        // gate biases are only read with layer norm, at scale (layer-norm weight scale / 1024)
+        // (RefQLstmWorkload.cpp:261-287)
+        if (!prm.m_CifgEnabled)
+        {
+            p.ln_i = static_cast<const int16_t*>(up(qd.m_InputLayerNormWeights, &p.s_lni));
+            p.b_i = static_cast<const int32_t*>(up(qd.m_InputGateBias, nullptr));
+            p.s_bi = p.s_lni / 1024;
+        }
+        p.ln_f = static_cast<const int16_t*>(up(qd.m_ForgetLayerNormWeights, &p.s_lnf));
+        p.ln_c = static_cast<const int16_t*>(up(qd.m_CellLayerNormWeights, &p.s_lnc));
+        p.ln_o = static_cast<const int16_t*>(up(qd.m_OutputLayerNormWeights, &p.s_lno));
+        p.b_f = static_cast<const int32_t*>(up(qd.m_ForgetGateBias, nullptr)); p.s_bf = p.s_lnf / 1024;
+        p.b_c = static_cast<const int32_t*>(up(qd.m_CellBias, nullptr));       p.s_bc = p.s_lnc / 1024;
+        p.b_o = static_cast<const int32_t*>(up(qd.m_OutputGateBias, nullptr)); p.s_bo = p.s_lno / 1024;
+    }
+    if (prm.m_ProjectionEnabled)
+    {
+        p.w_proj = static_cast<const int8_t*>(up(qd.m_ProjectionWeights, &p.s_proj));
+        p.b_proj = static_cast<const int32_t*>(up(qd.m_ProjectionBias, &p.s_bproj));
+    }
+    p.cell_clip = prm.m_CellClip; p.projection_clip = prm.m_ProjectionClip;
+    p.input_intermediate_scale = prm.m_InputIntermediateScale;
+    p.forget_intermediate_scale = prm.m_ForgetIntermediateScale;
+    p.cell_intermediate_scale = prm.m_CellIntermediateScale;
+    p.output_intermediate_scale = prm.m_OutputIntermediateScale;
+    p.hidden_state_scale = prm.m_HiddenStateScale; p.hidden_state_zp = prm.m_HiddenStateZeroPoint;
+    return Make<QLstmQueueDescriptor>(d, info, [st](const QLstmQueueDescriptor& data, cudaStream_t s)
+    {
+        b200k_qlstm_params& q = st->p;
+        q.input = static_cast<const int8_t*>(Dev(data.m_Inputs[0]));
+        q.output_state_in = static_cast<const int8_t*>(Dev(data.m_Inputs[1]));
+        q.cell_state_in = static_cast<const int16_t*>(Dev(data.m_Inputs[2]));
+        q.output_state_out = static_cast<int8_t*>(Dev(data.m_Outputs[0]));
+        q.cell_state_out = static_cast<int16_t*>(Dev(data.m_Outputs[1]));
+        q.output = static_cast<int8_t*>(Dev(data.m_Outputs[2]));
+        B200CheckStatus(b200k_qlstm_step(&q, s));
+    });
+}
+
+}  // namespace
+
+B200WorkloadFactory::B200WorkloadFactory(const std::shared_ptr<B200MemoryManager>& memoryManager)
+    : m_MemoryManager(memoryManager) {}
+
+const BackendId& B200WorkloadFactory::GetBackendId() const
+{
+    static const BackendId s_Id{B200BackendId()};
+    return s_Id;
+}
+
+bool B200WorkloadFactory::IsLayerSupported(const IConnectableLayer& layer, Optional<DataType> dataType, std::string& reason)
+{
+    static const BackendId s_Id{B200BackendId()};
+    return IWorkloadFactory::IsLayerSupported(s_Id, layer, dataType, reason);
+}
+
+std::unique_ptr<ITensorHandle> B200WorkloadFactory::CreateTensorHandle(const TensorInfo& info, const bool) const
+{
+    return std::make_unique<B200TensorHandle>(info);
+}
+
+std::unique_ptr<ITensorHandle> B200WorkloadFactory::CreateTensorHandle(const TensorInfo& info, DataLayout, const bool) const
+{
+    return std::make_unique<B200TensorHandle>(info);
+}
+
+std::unique_ptr<IWorkload> B200WorkloadFactory::CreateWorkload(LayerType type, const QueueDescriptor& d,
+                                                               const WorkloadInfo& info) const
+{
+    switch (type)
+    {
+        case LayerType::Input:
+            return std::make_unique<CopyMemGenericWorkload>(*PolymorphicDowncast<const InputQueueDescriptor*>(&d), info);
+        case LayerType::Output:
+            return std::make_unique<CopyMemGenericWorkload>(*PolymorphicDowncast<const OutputQueueDescriptor*>(&d), info);
+        case LayerType::MemCopy:
+            return std::make_unique<CopyMemGenericWorkload>(*PolymorphicDowncast<const MemCopyQueueDescriptor*>(&d), info);
+        case LayerType::MemImport:
+            return std::make_unique<ImportMemGenericWorkload>(*PolymorphicDowncast<const MemImportQueueDescriptor*>(&d), info);
+        case LayerType::Constant:
+        {
+            // RefConstantWorkload: one copy of the layer's blob into its output handle; LoadedNetwork executes
+            // Constant workloads once at load time (src/armnn/LoadedNetwork.cpp:565-568)
+            return Make<ConstantQueueDescriptor>(d, info, [](const ConstantQueueDescriptor& data, cudaStream_t s)
+            {
+                const ConstTensorHandle* src = data.m_LayerOutput;
+                if (!src) { throw InvalidArgumentException("B200Acc: Constant workload without data"); }
+                B200Check(cudaMemcpyAsync(Dev(data.m_Outputs[0]), src->GetConstTensor<void>(),
+                                          src->GetTensorInfo().GetNumBytes(), cudaMemcpyHostToDevice, s), "cudaMemcpyAsync H2D");
+                B200Check(cudaStreamSynchronize(s), "cudaStreamSynchronize");
+            });
+        }
+        case LayerType::Reshape:
+        {
+            const size_t bytes = info.m_InputTensorInfos[0].GetNumBytes();
+            return Make<ReshapeQueueDescriptor>(d, info, [bytes](const ReshapeQueueDescriptor& data, cudaStream_t s)
+            {
+                B200Check(cudaMemcpyAsync(Dev(data.m_Outputs[0]), Dev(data.m_Inputs[0]), bytes, cudaMemcpyDeviceToDevice, s),
+                          "cudaMemcpyAsync D2D");
+            });
+        }
+        case LayerType::Convolution2d:
+            return MakeConv<Convolution2dQueueDescriptor>(d, info, false);
+        case LayerType::DepthwiseConvolution2d:
+            return MakeConv<DepthwiseConvolution2dQueueDescriptor>(d, info, true);
+        case LayerType::FullyConnected:
+            return MakeFc(d, info);
+        case LayerType::ElementwiseBinary:
+        {
+            const auto& qd = *PolymorphicDowncast<const ElementwiseBinaryQueueDescriptor*>(&d);
+            return MakeEltwise(d, info, qd.m_Parameters.m_Operation, qd.GetAdditionalInformation<ActivationDescriptor>());
+        }
+        case LayerType::Addition:
+            return MakeEltwise(d, info, BinaryOperation::Add, d.GetAdditionalInformation<ActivationDescriptor>());
+        case LayerType::Multiplication:
+            return MakeEltwise(d, info, BinaryOperation::Mul, d.GetAdditionalInformation<ActivationDescriptor>());
+        case LayerType::Activation:
+        {
+            const auto& qd = *PolymorphicDowncast<const ActivationQueueDescriptor*>(&d);
+            auto st = std::make_shared<SimpleState<b200k_activation_params>>();
+            std::memset(&st->p, 0, sizeof(st->p));
+            st->p.x = Operand(info.m_InputTensorInfos[0], st->blobs);
+            st->p.y = Operand(info.m_OutputTensorInfos[0], st->blobs);
+            st->p.count = info.m_InputTensorInfos[0].GetNumElements();
+            st->p.function = static_cast<int32_t>(qd.m_Parameters.m_Function);
+            st->p.a = qd.m_Parameters.m_A; st->p.b = qd.m_Parameters.m_B;
+            return Make<ActivationQueueDescriptor>(d, info, [st](const ActivationQueueDescriptor& data, cudaStream_t s)
+            {
+                st->p.x.data = Dev(data.m_Inputs[0]); st->p.y.data = Dev(data.m_Outputs[0]);
+                B200CheckStatus(b200k_activation_q8(&st->p, s));
+            });
+        }
+        case LayerType::Pooling2d:
+        {
+            const auto& qd = *PolymorphicDowncast<const Pooling2dQueueDescriptor*>(&d);
+            const auto& q = qd.m_Parameters;
+            if (q.m_DataLayout != DataLayout::NHWC) { throw InvalidArgumentException("B200Acc: NHWC only"); }
+            auto st = std::make_shared<SimpleState<b200k_pool2d_params>>();
+            b200k_pool2d_params& p = st->p;
+            std::memset(&p, 0, sizeof(p));
+            const TensorInfo& x = info.m_InputTensorInfos[0];
+            const TensorInfo& y = info.m_OutputTensorInfos[0];
+            p.x = Operand(x, st->blobs); p.y = Operand(y, st->blobs);
+            p.n = x.GetShape()[0]; p.h = x.GetShape()[1]; p.wd = x.GetShape()[2]; p.c = x.GetShape()[3];
+            p.oh = y.GetShape()[1]; p.ow = y.GetShape()[2];
+            p.pool_h = q.m_PoolHeight; p.pool_w = q.m_PoolWidth; p.stride_h = q.m_StrideY; p.stride_w = q.m_StrideX;
+            p.pad_top = q.m_PadTop; p.pad_bottom = q.m_PadBottom; p.pad_left = q.m_PadLeft; p.pad_right = q.m_PadRight;
+            p.pool_type = static_cast<int32_t>(q.m_PoolType); p.padding_method = static_cast<int32_t>(q.m_PaddingMethod);
+            return Make<Pooling2dQueueDescriptor>(d, info, [st](const Pooling2dQueueDescriptor& data, cudaStream_t s)
+            {
+                st->p.x.data = Dev(data.m_Inputs[0]); st->p.y.data = Dev(data.m_Outputs[0]);
+                B200CheckStatus(b200k_pool2d_q8(&st->p, s));
+            });
+        }
+        case LayerType::Mean:
+        {
+            auto st = std::make_shared<SimpleState<b200k_mean_params>>();
+            b200k_mean_params& p = st->p;
+            std::memset(&p, 0, sizeof(p));
+            const TensorInfo& x = info.m_InputTensorInfos[0];
+            p.x = Operand(x, st->blobs); p.y = Operand(info.m_OutputTensorInfos[0], st->blobs);
+            p.n = x.GetShape()[0]; p.h = x.GetShape()[1]; p.wd = x.GetShape()[2]; p.c = x.GetShape()[3];
+            return Make<MeanQueueDescriptor>(d, info, [st](const MeanQueueDescriptor& data, cudaStream_t s)
+            {
+                st->p.x.data = Dev(data.m_Inputs[0]); st->p.y.data = Dev(data.m_Outputs[0]);
+                B200CheckStatus(b200k_mean_hw_q8(&st->p, s));
+            });
+        }
+        case LayerType::Softmax:
+        {
+            const auto& qd = *PolymorphicDowncast<const SoftmaxQueueDescriptor*>(&d);
+            auto st = std::make_shared<SimpleState<b200k_softmax_params>>();
+            b200k_softmax_params& p = st->p;
+            std::memset(&p, 0, sizeof(p));
+            const TensorInfo& x = info.m_InputTensorInfos[0];
+            p.x = Operand(x, st->blobs); p.y = Operand(info.m_OutputTensorInfos[0], st->blobs);
+            const int rank = static_cast<int>(x.GetNumDimensions());
+            int axis = qd.m_Parameters.m_Axis < 0 ? rank + qd.m_Parameters.m_Axis : qd.m_Parameters.m_Axis;
+            p.outer = 1; p.inner = 1;
+            for (int i = 0; i < axis; ++i) { p.outer *= x.GetShape()[i]; }
+            for (int i = axis + 1; i < rank; ++i) { p.inner *= x.GetShape()[i]; }
+            p.axis_size = x.GetShape()[axis];
+            p.beta = qd.m_Parameters.m_Beta;
+            return Make<SoftmaxQueueDescriptor>(d, info, [st](const SoftmaxQueueDescriptor& data, cudaStream_t s)
+            {
+                st->p.x.data = Dev(data.m_Inputs[0]); st->p.y.data = Dev(data.m_Outputs[0]);
+                B200CheckStatus(b200k_softmax_q8(&st->p, s));
+            });
+        }
+        case LayerType::Quantize:
+        case LayerType::Dequantize:
+        {
+            auto st = std::make_shared<SimpleState<b200k_convert_params>>();
+            std::memset(&st->p, 0, sizeof(st->p));
+            st->p.x = Operand(info.m_InputTensorInfos[0], st->blobs);
+            st->p.y = Operand(info.m_OutputTensorInfos[0], st->blobs);
+            st->p.count = info.m_InputTensorInfos[0].GetNumElements();
+            auto fn = [st](const QueueDescriptor& data, cudaStream_t s)
+            {
+                st->p.x.data = Dev(data.m_Inputs[0]); st->p.y.data = Dev(data.m_Outputs[0]);
+                B200CheckStatus(b200k_convert_q(&st->p, s));
+            };
+            if (type == LayerType::Quantize) { return Make<QuantizeQueueDescriptor>(d, info, fn); }
+            return Make<DequantizeQueueDescriptor>(d, info, fn);
+        }
+        case LayerType::BatchMatMul:
+        {
+            const auto& qd = *PolymorphicDowncast<const BatchMatMulQueueDescriptor*>(&d);
+            auto st = std::make_shared<SimpleState<b200k_bmm_params>>();
+            b200k_bmm_params& p = st->p;
+            std::memset(&p, 0, sizeof(p));
+            const TensorInfo& x = info.m_InputTensorInfos[0];
+            const TensorInfo& y = info.m_InputTensorInfos[1];
+            const TensorInfo& o = info.m_OutputTensorInfos[0];
+            p.x = Operand(x, st->blobs); p.y = Operand(y, st->blobs); p.out = Operand(o, st->blobs);
+            const unsigned ro = o.GetNumDimensions(), rx = x.GetNumDimensions(), ry = y.GetNumDimensions();
+            p.m = o.GetShape()[ro - 2]; p.n = o.GetShape()[ro - 1];
+            p.transpose_x = qd.m_Parameters.m_TransposeX; p.transpose_y = qd.m_Parameters.m_TransposeY;
+            p.k = p.transpose_x ? x.GetShape()[rx - 2] : x.GetShape()[rx - 1];
+            p.batch = static_cast<int32_t>(o.GetNumElements() / (static_cast<unsigned>(p.m) * p.n));
+            const int bx = static_cast<int>(x.GetNumElements() / (x.GetShape()[rx - 1] * x.GetShape()[rx - 2]));
+            const int by = static_cast<int>(y.GetNumElements() / (y.GetShape()[ry - 1] * y.GetShape()[ry - 2]));
+            p.batch_stride_x = (bx == p.batch && p.batch > 1) ? static_cast<int64_t>(p.m) * p.k : 0;
+            p.batch_stride_y = (by == p.batch && p.batch > 1) ? static_cast<int64_t>(p.k) * p.n : 0;
+            return Make<BatchMatMulQueueDescriptor>(d, info, [st](const BatchMatMulQueueDescriptor& data, cudaStream_t s)
+            {
+                st->p.x.data = Dev(data.m_Inputs[0]); st->p.y.data = Dev(data.m_Inputs[1]); st->p.out.data = Dev(data.m_Outputs[0]);
+                B200CheckStatus(b200k_batch_matmul_q8(&st->p, s));
+            });
+        }
+        case LayerType::QLstm:
+            return MakeQLstm(d, info);
+        default:
+            return nullptr;       // LoadedNetwork turns a null workload into an exception: there is no CPU fallback
+    }
+}
+
+}  // namespace armnn

@@ -42,7 +42,8 @@ def have_cpuref():
 def cpuref():
     global _cpuref
     if _cpuref is None:
-        _cpuref = C.CDLL(CPUREF_PATH)
+        # RTLD_GLOBAL: the B200Acc plugin, dlopen()ed later by the Arm NN runtime, resolves libarmnn's symbols
+        _cpuref = C.CDLL(CPUREF_PATH, mode=C.RTLD_GLOBAL)
         _cpuref.cpuref_last_error.restype = C.c_char_p
     return _cpuref
 

@@ -1,0 +1,84 @@
+"""The C++ backend plugin (armnn_b200/backend -> Nv_B200Acc_backend.so) inside the unmodified Arm NN runtime:
+dynamic loading and registration (no GPU needed), and — on a GPU — whole graphs through INetwork -> Optimize({B200Acc})
+-> LoadNetwork -> EnqueueWorkload against the same graph on CpuRef in the same process."""
+import os
+
+import numpy as np
+import pytest
+
+from q8util import diff_stats, have_cpuref
+
+import hostnet
+
+needs_plugin = pytest.mark.skipif(not (have_cpuref() and os.path.exists(hostnet.PLUGIN_PATH)),
+                                  reason="Arm NN runtime (oracle/_ref) or the plugin is not built")
+
+
+@needs_plugin
+def test_plugin_is_found_loaded_and_registered_by_the_runtime():
+    assert hostnet.ArmnnNetwork.backend_available("CpuRef")
+    assert hostnet.ArmnnNetwork.backend_available("B200Acc")
+
+
+def _pair(net, info, dtype, seed=3):
+    rng = np.random.default_rng(seed)
+    lo, hi = (0, 256) if dtype == np.uint8 else (-128, 128)
+    x = rng.integers(lo, hi, size=info["input_shape"]).astype(dtype)
+    ref = hostnet.ArmnnNetwork(net, "CpuRef").run({0: x})[0]
+    got = hostnet.ArmnnNetwork(net, "B200Acc").run({0: x})[0]
+    return x, ref, got
+
+
+@needs_plugin
+@pytest.mark.gpu
+def test_single_conv_through_the_runtime_matches_cpuref():
+    from armnn_b200 import configs
+    for args in ({}, {"output_scale": 0.33}):
+        _, ref, got = _pair(*configs.single_conv(**args), np.int8)
+        st = diff_stats(ref, got)
+        assert st["max_abs"] <= 1 and st["mismatch_frac"] < 1e-3, st
+
+
+@needs_plugin
+@pytest.mark.gpu
+def test_resnet50_reduced_through_the_runtime_matches_cpuref_and_the_python_mirror():
+    from armnn_b200 import configs, network
+    net, info = configs.resnet50(2, 64)
+    x, ref, got = _pair(net, info, np.int8)
+    st = diff_stats(ref, got)
+    assert st["max_abs"] <= 1 and st["mismatch_frac"] < 0.02, st
+    assert np.array_equal(ref.argmax(1), got.argmax(1))
+    # the plugin and the Python host mirror drive the same kernels: identical class scores
+    rt = network.IRuntime.Create(0)
+    ln = rt.GetLoadedNetwork(rt.LoadNetwork(network.Optimize(net)))
+    y = np.zeros(info["output_shape"], np.int8)
+    ln.EnqueueWorkload({0: x}, {0: y})
+    assert diff_stats(y, got)["max_abs"] <= 1
+
+
+@needs_plugin
+@pytest.mark.gpu
+def test_mobilenet_v2_reduced_through_the_runtime_matches_cpuref():
+    from armnn_b200 import configs
+    _, ref, got = _pair(*configs.mobilenet_v2(1, 64), np.uint8)
+    st = diff_stats(ref, got)
+    assert st["max_abs"] <= 2 and st["mismatch_frac"] < 0.05, st
+
+
+@needs_plugin
+@pytest.mark.gpu
+def test_unsupported_layer_makes_optimize_fail_instead_of_falling_back():
+    from armnn_b200.network import DataType, INetwork, TensorInfo
+    net = INetwork.Create()
+    il = net.AddInputLayer(0)
+    il.GetOutputSlot(0).SetTensorInfo(TensorInfo((1, 8), DataType.Float32))
+    sl = net.AddSoftmaxLayer()
+    il.GetOutputSlot(0).Connect(sl.GetInputSlot(0))
+    sl.GetOutputSlot(0).SetTensorInfo(TensorInfo((1, 8), DataType.Float32))
+    ml = net.AddMeanLayer((1,))
+    sl.GetOutputSlot(0).Connect(ml.GetInputSlot(0))
+    ml.GetOutputSlot(0).SetTensorInfo(TensorInfo((1,), DataType.Float32))
+    ol = net.AddOutputLayer(0)
+    ml.GetOutputSlot(0).Connect(ol.GetInputSlot(0))
+    with pytest.raises(RuntimeError):
+        hostnet.ArmnnNetwork(net, "B200Acc")
