@@ -71,6 +71,9 @@ struct TcArgs {
     const uint8_t* res; float res_scale; int res_zp; int res_u8;
     Requant rq2;
     float inv_sy2;
+    int stages;                                 // ring depth chosen by the launcher (<= 8)
+    int prefix_ints;                            // ints of shared memory reserved for the prefix slice
+    const uint8_t* add_lut;                     // [256][256] table of the fused Add (or null: evaluate arithmetically)
     int debug;                                  // 0 normal; 1: main loop without MMAs; 2: main loop without TMA loads
 };
 
@@ -207,6 +210,7 @@ struct EpiConsts {
     QuantF q1, q2;                               // the convolution's own quantisation; the fused Add's output
     float res_zp, res_scale; bool res_u8; int zx;
     const int32_t *p11, *p01, *p10, *p00;        // prefix-table rows of this thread's tap rectangle
+    const uint8_t* lut;                          // shared-memory copy of the fused-add table, or null
 };
 
 // 16 accumulator columns of one output pixel -> 16 output bytes.  FUSED: add the residual operand (16 bytes in rv).
@@ -244,6 +248,14 @@ __device__ __forceinline__ uint4 epi_chunk(const uint32_t* r, const uint4 rv, co
             // v = float(acc) * (sx * sw) + float(bias) * sb   (bterm is +0.0 without a bias)
             const float v = __fadd_rn(__fmul_rn(__int2float_rn(acc), mm[e]), bb[e]);
             float qf = quantize_f32(v, ec.q1);
+            if (FUSED && ec.lut) {
+                // The fused Add maps (convolution output byte, other operand byte) to the output byte; both operands
+                // are per-tensor quantised, so the whole second quantisation is a 64 K-entry table built at load time
+                // with the exact arithmetic of the branch below.
+                const uint32_t idx = __byte_perm(f32_to_byte_bits(qf), resw[g], 0x0004 + e) & 0xffffu;   // (conv byte << 8) | other byte
+                bits[e] = ec.lut[idx];
+                continue;
+            }
             if (FUSED) {
                 // fused ElementwiseBinary Add: the convolution's own 8-bit output is formed first, then both operands
                 // are dequantised, added in fp32 and re-quantised, as the two separate workloads do
@@ -263,12 +275,10 @@ struct TcSmem {
     static constexpr int A_BYTES = TC_BM * SWZ;
     static constexpr int B_BYTES = BN * SWZ;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int STAGES = (196608 / STAGE_BYTES) < 8 ? (196608 / STAGE_BYTES) : 8;
-    static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
-    // after the ring: float m[BN], float bterm[BN], int corr[BN], barriers (full, empty, acc_full[2], acc_empty[2]),
-    // tmem slot;
-    // the prefix slice follows (dynamic size)
-    static constexpr int FIXED_BYTES = RING_BYTES + 3 * BN * 4 + (2 * STAGES + 4) * 8 + 16;
+    static constexpr int MAX_STAGES = 8;
+    // after the ring (a.stages x STAGE_BYTES): float m[BN], float bterm[BN], int corr[BN], barriers (full[8], empty[8],
+    // acc_full[2], acc_empty[2]), tmem slot; then the prefix slice and the fused-add table (dynamic sizes)
+    static constexpr int CONST_BYTES = 3 * BN * 4 + (2 * MAX_STAGES + 4) * 8 + 16;
 };
 
 __device__ __forceinline__ void epi_barrier()       // the epilogue warps only (named barrier 1)
@@ -289,18 +299,20 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
 conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const TcArgs a)
 {
     using L = TcSmem<BN, SWZ>;
-    constexpr int STAGES = L::STAGES;
+    constexpr int MAX_STAGES = L::MAX_STAGES;
+    const int STAGES = a.stages;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    float* s_m = (float*)(smem + L::RING_BYTES);
+    float* s_m = (float*)(smem + (size_t)STAGES * L::STAGE_BYTES);
     float* s_bterm = s_m + BN;
     int32_t* s_corr = (int32_t*)(s_bterm + BN);             // zx * (sum of all taps) per channel
     uint64_t* full = (uint64_t*)(s_corr + BN);
-    uint64_t* empty = full + STAGES;
-    uint64_t* acc_full = empty + STAGES;                    // [2]
+    uint64_t* empty = full + MAX_STAGES;
+    uint64_t* acc_full = empty + MAX_STAGES;                // [2]
     uint64_t* acc_empty = acc_full + 2;                     // [2]
     uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
-    int32_t* s_prefix = (int32_t*)(tmem_slot + 4);          // [(KH+1)*(KW+1)][BN] when need_corr
+    int32_t* s_prefix = (int32_t*)(tmem_slot + 4);          // [(KH+1)*(KW+1)][BN] when need_rect
+    uint8_t* s_lut = (uint8_t*)(s_prefix + a.prefix_ints);  // [256][256] fused-add table when a.add_lut
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int ntn = a.OC / BN;                              // n-tiles (OC is a multiple of BN)
@@ -314,6 +326,11 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(2 * BN) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    if (a.add_lut) {
+        const uint4* src = (const uint4*)a.add_lut;
+        uint4* dst = (uint4*)s_lut;
+        for (int i = threadIdx.x; i < 65536 / 16; i += TC_THREADS) dst[i] = src[i];
     }
     tc_fence_before();
     __syncthreads();
@@ -412,6 +429,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         ec.q2.sy = a.rq2.sy; ec.q2.inv_sy = a.inv_sy2; ec.q2.zy = (float)a.rq2.zy;
         ec.q2.lo = fmaxf(a.rq2.tlo, (float)a.rq2.clo); ec.q2.hi = fminf(a.rq2.thi, (float)a.rq2.chi);
         ec.res_zp = (float)a.res_zp; ec.res_scale = a.res_scale; ec.res_u8 = a.res_u8 != 0; ec.zx = a.zx;
+        ec.lut = a.add_lut ? s_lut : nullptr;
         int cur_n0 = -1;
         int it = 0;
         for (int t = blockIdx.x; t < ntiles; t += gridDim.x, ++it) {
@@ -603,6 +621,31 @@ __global__ void __launch_bounds__(256) row_input_pack_kernel(const RowInputArgs 
     else           *(uint4*)(a.xp + i * 16) = *(const uint4*)v;
 }
 
+// ---- fused-add table ---------------------------------------------------------------------------------------------
+
+struct AddLutArgs { uint8_t* lut; int y_u8, res_u8; float sy; int zy; float sr; int zr; Requant out; };
+
+// lut[(conv byte << 8) | other byte] = clamp(Q_out(deq_y(conv) + deq(other))): RefElementwiseBinaryWorkload(Add)
+// followed by the fused activation, evaluated once per pair of 8-bit values with the exact fp32 arithmetic
+__global__ void add_lut_kernel(const AddLutArgs a)
+{
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;       // 65536 threads
+    const int b1 = i >> 8, b2 = i & 255;
+    const int q1 = a.y_u8 ? b1 : (int)(int8_t)b1;
+    const int q2 = a.res_u8 ? b2 : (int)(int8_t)b2;
+    const float fa = __fmul_rn(__int2float_rn(q1 - a.zy), a.sy);
+    const float fb = __fmul_rn(__int2float_rn(q2 - a.zr), a.sr);
+    const int q = quantize_dev(__fadd_rn(fa, fb), a.out.sy, a.out.zy, a.out.tlo, a.out.thi);
+    a.lut[i] = (uint8_t)min(max(q, a.out.clo), a.out.chi);
+}
+
+static size_t add_lut_offset(int oc, int kh, int kw, int c)
+{
+    size_t n = (size_t)(kh + 1) * (kw + 1) * oc * sizeof(int32_t);
+    if (c <= 16) n += (size_t)oc * kh * 128;
+    return (n + 255) & ~(size_t)255;
+}
+
 // ---- host side ---------------------------------------------------------------------------------------------------
 
 static PFN_cuTensorMapEncodeTiled_v12000 g_encode_tiled = nullptr;
@@ -681,7 +724,16 @@ template <int BN, int SWZ>
 static int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const TcArgs& a, size_t prefix_bytes, cudaStream_t stream)
 {
     using L = TcSmem<BN, SWZ>;
-    const size_t smem = 1024 + L::FIXED_BYTES + prefix_bytes;
+    const size_t lut_bytes = a.add_lut ? 65536 : 0;
+    const size_t budget = 227 * 1024;                                   // opt-in shared memory per CTA on sm_100
+    const size_t rest = 1024 + L::CONST_BYTES + prefix_bytes + lut_bytes;
+    int stages = (int)((budget - rest) / L::STAGE_BYTES);
+    if (stages > L::MAX_STAGES) stages = L::MAX_STAGES;
+    B200K_REQUIRE(stages >= 2, B200K_E_TOOBIG, "conv2d_q8: shared memory exhausted (%zu bytes of tables)", rest);
+    TcArgs a2 = a;
+    a2.stages = stages;
+    a2.prefix_ints = (int)(prefix_bytes / 4);
+    const size_t smem = rest + (size_t)stages * L::STAGE_BYTES;
     auto kern = conv_tc_kernel<BN, SWZ>;
     static size_t configured = 0;                      // per instantiation: largest dynamic smem size set so far
     if (smem > configured) {
@@ -690,7 +742,7 @@ static int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const TcArg
     }
     const long long tiles = (long long)(a.OC / BN) * a.ntm;
     const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
-    kern<<<grid, TC_THREADS, smem, stream>>>(tmA, tmB, a);
+    kern<<<grid, TC_THREADS, smem, stream>>>(tmA, tmB, a2);
     return check_launch("conv_tc_kernel");
 }
 
@@ -733,6 +785,8 @@ int launch_conv_tc(const b200k_conv2d_params* p, cudaStream_t stream)
     a.res = fa.res; a.res_scale = fa.res_scale; a.res_zp = fa.res_zp; a.res_u8 = fa.res_u8;
     a.rq2 = fa.out;
     a.inv_sy2 = fa.res ? 1.0f / p->add_out.scale : 0.f;
+    // b200k_conv2d_pack builds the fused-add table when it is given the add operand: callers pass the same struct
+    a.add_lut = (fa.res && p->packed) ? (const uint8_t*)p->packed + add_lut_offset(p->oc, p->kh, p->kw, p->c) : nullptr;
     // Measurement aid (results are wrong in modes 1 and 2): isolates the TMA side or the MMA side of the main loop.
     static const int debug_mode = getenv("B200K_TC_DEBUG") ? atoi(getenv("B200K_TC_DEBUG")) : 0;
     a.debug = debug_mode;
@@ -800,7 +854,7 @@ int launch_conv_tc(const b200k_conv2d_params* p, cudaStream_t stream)
             (size_t)p->n * p->h * p->wd * p->c < 131072)
             reinterpret_cast<uint64_t*>(&tmA)[1] &= ~(1ull << 21);
     }
-    const size_t prefix_bytes = a.need_corr ? (size_t)(p->kh + 1) * (p->kw + 1) * bn * 4 : 0;
+    const size_t prefix_bytes = a.need_rect ? (size_t)(p->kh + 1) * (p->kw + 1) * bn * 4 : 0;
     if (swz == 128) {
         if (bn == 256) return launch_tc<256, 128>(tmA, tmB, a, prefix_bytes, stream);
         if (bn == 128) return launch_tc<128, 128>(tmA, tmB, a, prefix_bytes, stream);
@@ -818,9 +872,8 @@ using namespace b200k;
 extern "C" size_t b200k_conv2d_pack_bytes(int32_t oc, int32_t kh, int32_t kw, int32_t c)
 {
     if (oc <= 0 || kh <= 0 || kw <= 0) return 0;
-    size_t n = (size_t)(kh + 1) * (kw + 1) * oc * sizeof(int32_t);      // prefix table
-    if (c <= 16) n += (size_t)oc * kh * 128;                              // row-window weights (widest window)
-    return n;
+    // prefix table, row-window weights for few-channel convolutions (widest window), fused-add table
+    return add_lut_offset(oc, kh, kw, c) + 65536;
 }
 
 extern "C" size_t b200k_conv2d_scratch_bytes(const b200k_conv2d_params* p)
@@ -840,7 +893,19 @@ extern "C" int b200k_conv2d_pack(const b200k_conv2d_params* p, void* packed, voi
     a.OC = p->oc; a.KH = p->kh; a.KW = p->kw; a.C = p->c;
     conv_prefix_kernel<<<div_up(p->oc, 128), 128, 0, (cudaStream_t)stream>>>(a);
     int rc = check_launch("conv_prefix_kernel");
-    if (rc || p->c > 16) return rc;
+    if (rc) return rc;
+    if (p->add_operand.data && is_q8(p->add_operand.dtype) && is_q8(p->add_out.dtype) && is_q8(p->y.dtype)) {
+        // table of the fused Add for exactly these quantisation parameters and this clamp
+        AddLutArgs la;
+        la.lut = (uint8_t*)packed + add_lut_offset(p->oc, p->kh, p->kw, p->c);
+        la.y_u8 = p->y.dtype == B200K_U8; la.res_u8 = p->add_operand.dtype == B200K_U8;
+        la.sy = p->y.scale; la.zy = p->y.zero_point; la.sr = p->add_operand.scale; la.zr = p->add_operand.zero_point;
+        la.out = make_requant(0.f, p->add_out, p->clamp_lo, p->clamp_hi);
+        add_lut_kernel<<<256, 256, 0, (cudaStream_t)stream>>>(la);
+        rc = check_launch("add_lut_kernel");
+        if (rc) return rc;
+    }
+    if (p->c > 16) return rc;
     // weights of a few-channel convolution, re-packed for the row-window mode (needs kw, c and stride_w)
     b200k_conv2d_params q = *p;
     if (q.stride_w <= 0) q.stride_w = 1;
