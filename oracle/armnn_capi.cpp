@@ -577,6 +577,56 @@ int armnnc_add_reshape(void* vn, int rank, const int32_t* shape)
     return add_layer(n, n->net->AddReshapeLayer(d));
 }
 
+// QLstm layer from a b200k_qlstm_params whose weight pointers are HOST pointers (copied by Arm NN); only the weight,
+// scale and descriptor fields are read.  Optional weights are null pointers.
+int armnnc_add_qlstm(void* vn, const b200k_qlstm_params* p)
+{
+    auto* n = static_cast<CNet*>(vn);
+    const unsigned I = p->input_size, U = p->num_units, O = p->output_size;
+    QLstmDescriptor d;
+    d.m_CifgEnabled = p->w_i2i == nullptr;
+    d.m_PeepholeEnabled = p->w_c2f != nullptr;
+    d.m_ProjectionEnabled = p->w_proj != nullptr;
+    d.m_LayerNormEnabled = p->ln_f != nullptr;
+    d.m_CellClip = p->cell_clip; d.m_ProjectionClip = p->projection_clip;
+    d.m_InputIntermediateScale = p->input_intermediate_scale; d.m_ForgetIntermediateScale = p->forget_intermediate_scale;
+    d.m_CellIntermediateScale = p->cell_intermediate_scale; d.m_OutputIntermediateScale = p->output_intermediate_scale;
+    d.m_HiddenStateScale = p->hidden_state_scale; d.m_HiddenStateZeroPoint = p->hidden_state_zp;
+    std::vector<std::unique_ptr<ConstTensor>> keep;
+    auto ct = [&](const void* data, TensorShape shape, DataType dt, float scale) -> const ConstTensor* {
+        if (!data) return nullptr;
+        TensorInfo info(shape, dt, scale, 0);
+        info.SetConstant(true);
+        keep.push_back(std::make_unique<ConstTensor>(info, data));
+        return keep.back().get();
+    };
+    LstmInputParams q;
+    q.m_InputToInputWeights = ct(p->w_i2i, {U, I}, DataType::QSymmS8, p->s_i2i);
+    q.m_InputToForgetWeights = ct(p->w_i2f, {U, I}, DataType::QSymmS8, p->s_i2f);
+    q.m_InputToCellWeights = ct(p->w_i2c, {U, I}, DataType::QSymmS8, p->s_i2c);
+    q.m_InputToOutputWeights = ct(p->w_i2o, {U, I}, DataType::QSymmS8, p->s_i2o);
+    q.m_RecurrentToInputWeights = ct(p->w_r2i, {U, O}, DataType::QSymmS8, p->s_r2i);
+    q.m_RecurrentToForgetWeights = ct(p->w_r2f, {U, O}, DataType::QSymmS8, p->s_r2f);
+    q.m_RecurrentToCellWeights = ct(p->w_r2c, {U, O}, DataType::QSymmS8, p->s_r2c);
+    q.m_RecurrentToOutputWeights = ct(p->w_r2o, {U, O}, DataType::QSymmS8, p->s_r2o);
+    q.m_CellToInputWeights = ct(p->w_c2i, {U}, DataType::QSymmS16, p->s_c2i);
+    q.m_CellToForgetWeights = ct(p->w_c2f, {U}, DataType::QSymmS16, p->s_c2f);
+    q.m_CellToOutputWeights = ct(p->w_c2o, {U}, DataType::QSymmS16, p->s_c2o);
+    q.m_InputGateBias = ct(p->b_i, {U}, DataType::Signed32, p->s_bi);
+    q.m_ForgetGateBias = ct(p->b_f, {U}, DataType::Signed32, p->s_bf);
+    q.m_CellBias = ct(p->b_c, {U}, DataType::Signed32, p->s_bc);
+    q.m_OutputGateBias = ct(p->b_o, {U}, DataType::Signed32, p->s_bo);
+    q.m_InputLayerNormWeights = ct(p->ln_i, {U}, DataType::QSymmS16, p->s_lni);
+    q.m_ForgetLayerNormWeights = ct(p->ln_f, {U}, DataType::QSymmS16, p->s_lnf);
+    q.m_CellLayerNormWeights = ct(p->ln_c, {U}, DataType::QSymmS16, p->s_lnc);
+    q.m_OutputLayerNormWeights = ct(p->ln_o, {U}, DataType::QSymmS16, p->s_lno);
+    q.m_ProjectionWeights = ct(p->w_proj, {O, U}, DataType::QSymmS8, p->s_proj);
+    q.m_ProjectionBias = ct(p->b_proj, {O}, DataType::Signed32, p->s_bproj);
+    try {
+        return add_layer(n, n->net->AddQLstmLayer(d, q));
+    } catch (const std::exception& e) { g_err = e.what(); return -1; }
+}
+
 int armnnc_add_quantize(void* vn)   { auto* n = static_cast<CNet*>(vn); return add_layer(n, n->net->AddQuantizeLayer()); }
 int armnnc_add_dequantize(void* vn) { auto* n = static_cast<CNet*>(vn); return add_layer(n, n->net->AddDequantizeLayer()); }
 

@@ -130,6 +130,9 @@ class ArmnnNetwork:
                 lid = lib.armnnc_add_quantize(net)
             elif t == "Dequantize":
                 lid = lib.armnnc_add_dequantize(net)
+            elif t == "QLstm":
+                lid = lib.armnnc_add_qlstm(net, C.byref(self._qlstm_params(layer)))
+                assert lid >= 0, lib.cpuref_last_error().decode()
             else:
                 raise NotImplementedError("ArmnnNetwork: layer type %s" % t)
             ids[id(layer)] = lid
@@ -148,6 +151,50 @@ class ArmnnNetwork:
         lib.armnnc_network_destroy(net)
         if not self.handle.value:
             raise RuntimeError("armnn load failed: " + err)
+
+    _QLSTM_FIELDS = {"InputToInputWeights": ("w_i2i", "s_i2i"), "InputToForgetWeights": ("w_i2f", "s_i2f"),
+                     "InputToCellWeights": ("w_i2c", "s_i2c"), "InputToOutputWeights": ("w_i2o", "s_i2o"),
+                     "RecurrentToInputWeights": ("w_r2i", "s_r2i"), "RecurrentToForgetWeights": ("w_r2f", "s_r2f"),
+                     "RecurrentToCellWeights": ("w_r2c", "s_r2c"), "RecurrentToOutputWeights": ("w_r2o", "s_r2o"),
+                     "CellToInputWeights": ("w_c2i", "s_c2i"), "CellToForgetWeights": ("w_c2f", "s_c2f"),
+                     "CellToOutputWeights": ("w_c2o", "s_c2o"), "InputGateBias": ("b_i", "s_bi"),
+                     "ForgetGateBias": ("b_f", "s_bf"), "CellBias": ("b_c", "s_bc"), "OutputGateBias": ("b_o", "s_bo"),
+                     "InputLayerNormWeights": ("ln_i", "s_lni"), "ForgetLayerNormWeights": ("ln_f", "s_lnf"),
+                     "CellLayerNormWeights": ("ln_c", "s_lnc"), "OutputLayerNormWeights": ("ln_o", "s_lno"),
+                     "ProjectionWeights": ("w_proj", "s_proj"), "ProjectionBias": ("b_proj", "s_bproj")}
+
+    def _qlstm_params(self, layer):
+        """b200k_qlstm_params with HOST weight pointers, as armnnc_add_qlstm wants."""
+        d = layer.desc
+        p = _abi.QLstmParams()
+        x, h, c = (s.source.info for s in layer.inputs)
+        p.batch, p.input_size = x.shape
+        p.output_size, p.num_units = h.shape[1], c.shape[1]
+        self._keep = getattr(self, "_keep", [])
+        for key, (wf, sf) in self._QLSTM_FIELDS.items():
+            item = layer.qlstm_params.get(key)
+            if item is None:
+                continue
+            data, info = item
+            arr = np.ascontiguousarray(np.asarray(data).astype(_NP_DTYPE[info.dtype]))
+            self._keep.append(arr)
+            setattr(p, wf, arr.ctypes.data)
+            setattr(p, sf, info.scale)
+        if d.get("CifgEnabled"):
+            p.w_i2i = p.w_r2i = None
+        if not d.get("PeepholeEnabled"):
+            p.w_c2i = p.w_c2f = p.w_c2o = None
+        if not d.get("LayerNormEnabled"):
+            p.ln_i = p.ln_f = p.ln_c = p.ln_o = None
+        if not d.get("ProjectionEnabled"):
+            p.w_proj = p.b_proj = None
+        p.cell_clip, p.projection_clip = d.get("CellClip", 0.0), d.get("ProjectionClip", 0.0)
+        p.input_intermediate_scale = d["InputIntermediateScale"]
+        p.forget_intermediate_scale = d["ForgetIntermediateScale"]
+        p.cell_intermediate_scale = d["CellIntermediateScale"]
+        p.output_intermediate_scale = d["OutputIntermediateScale"]
+        p.hidden_state_scale, p.hidden_state_zp = d["HiddenStateScale"], d["HiddenStateZeroPoint"]
+        return p
 
     def run(self, inputs):
         ins = [np.ascontiguousarray(np.asarray(inputs[bid]).astype(_NP_DTYPE[info.dtype], copy=False)) for bid, info in self.in_infos]

@@ -97,3 +97,27 @@ def test_mobilenet_v2_reduced_oracle_vs_armnn_cpuref_free_running(built):
     want, got = _run_pair(*configs.mobilenet_v2(1, 64), np.uint8)
     st = diff_stats(want, got)
     assert st["max_abs"] <= 2 and st["mismatch_frac"] < 0.05, st
+
+
+@needs_cpuref
+def test_qlstm_stack_three_steps_oracle_vs_armnn_cpuref(built):
+    """The 3-layer QLstm graph through the real Arm NN runtime on CpuRef versus the oracle, states fed back for three
+    timesteps: identical int8 outputs and int16 cell states (the oracle restates CpuRef operation by operation)."""
+    import hostnet
+    net, info = configs.qlstm_stack(batch=2, num_units=64, output_size=32)
+    ref_net = hostnet.ArmnnNetwork(net, "CpuRef")
+    on = hostnet.OracleNetwork(Optimize(net))
+    rng = np.random.default_rng(4)
+    state = {}
+    for l in range(info["layers"]):
+        state[1 + 2 * l] = np.zeros((2, 32), np.int8)
+        state[2 + 2 * l] = np.zeros((2, 64), np.int16)
+    for step in range(3):
+        x = rng.integers(-128, 128, size=info["input_shape"]).astype(np.int8)
+        ins = {0: x}
+        ins.update(state)
+        want = ref_net.run(ins)
+        got = on.run(ins)
+        for k in want:
+            assert np.array_equal(want[k], got[k]), (step, k)
+        state = {k: want[k] for k in state}

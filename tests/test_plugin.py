@@ -82,3 +82,28 @@ def test_unsupported_layer_makes_optimize_fail_instead_of_falling_back():
     ml.GetOutputSlot(0).Connect(ol.GetInputSlot(0))
     with pytest.raises(RuntimeError):
         hostnet.ArmnnNetwork(net, "B200Acc")
+
+
+@needs_plugin
+@pytest.mark.gpu
+def test_qlstm_stack_through_the_runtime_matches_cpuref():
+    from armnn_b200 import configs
+    net, info = configs.qlstm_stack(batch=4, num_units=64, output_size=32)
+    ref_net = hostnet.ArmnnNetwork(net, "CpuRef")
+    gpu_net = hostnet.ArmnnNetwork(net, "B200Acc")
+    rng = np.random.default_rng(6)
+    state = {}
+    for l in range(info["layers"]):
+        state[1 + 2 * l] = np.zeros((4, 32), np.int8)
+        state[2 + 2 * l] = np.zeros((4, 64), np.int16)
+    for step in range(3):
+        x = rng.integers(-128, 128, size=info["input_shape"]).astype(np.int8)
+        ins = {0: x}
+        ins.update(state)
+        want = ref_net.run(ins)
+        got = gpu_net.run(ins)
+        for k in want:
+            st = diff_stats(want[k], got[k])
+            tol = 2 if want[k].dtype == np.int16 else 1
+            assert st["max_abs"] <= tol and st["mismatch_frac"] <= 0.01, (step, k, st)
+        state = {k: want[k] for k in state}
