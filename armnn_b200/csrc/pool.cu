@@ -105,6 +105,44 @@ __global__ void __launch_bounds__(256) pool2d_kernel(const PoolArgs a)
     store_vec_f<VEC>(a.y, oi, r);
 }
 
+// Max pooling whose input and output share type, scale and offset: dequantisation is monotone (scale > 0) and
+// Quantize(Dequantize(q)) == q, so the result is the maximum of the quantised bytes themselves — SIMD byte maxima, no
+// floating point.  A window with no valid tap yields Quantize(lowest float) = the type minimum, a padding-only window
+// Quantize(0) = the zero point, as in the general kernel.
+__global__ void __launch_bounds__(256) maxpool_same_quant_kernel(const PoolArgs a)
+{
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= a.total) return;
+    const int cg = a.C / 16;
+    const int c = (int)(idx % cg) * 16;
+    long long t = idx / cg;
+    const int ox = (int)(t % a.OW); t /= a.OW;
+    const int oy = (int)(t % a.OH);
+    const int n = (int)(t / a.OH);
+    int hstart = oy * a.sh - a.pt;
+    int hend = min(hstart + a.ph, a.H + a.pb);
+    clamp_range(hstart, hend, a.H);
+    int wstart = ox * a.sw - a.pl;
+    int wend = min(wstart + a.pw, a.W + a.pr);
+    const bool is_u8 = a.x.dtype == B200K_U8;
+    uint4 r;
+    if ((hend <= 0 || hstart > a.H) || (wend <= 0 || wstart > a.W)) {
+        const unsigned z = 0x01010101u * (unsigned)(a.x.zp & 0xff);
+        r = make_uint4(z, z, z, z);
+    } else {
+        clamp_range(wstart, wend, a.W);
+        const unsigned lowest = is_u8 ? 0u : 0x80808080u;
+        r = make_uint4(lowest, lowest, lowest, lowest);
+        for (int iy = hstart; iy < hend; ++iy)
+            for (int ix = wstart; ix < wend; ++ix) {
+                const uint4 v = *(const uint4*)((const uint8_t*)a.x.data + (((long long)n * a.H + iy) * a.W + ix) * a.C + c);
+                if (is_u8) { r.x = __vmaxu4(r.x, v.x); r.y = __vmaxu4(r.y, v.y); r.z = __vmaxu4(r.z, v.z); r.w = __vmaxu4(r.w, v.w); }
+                else       { r.x = __vmaxs4(r.x, v.x); r.y = __vmaxs4(r.y, v.y); r.z = __vmaxs4(r.z, v.z); r.w = __vmaxs4(r.w, v.w); }
+            }
+    }
+    *(uint4*)((uint8_t*)a.y.data + (((long long)n * a.OH + oy) * a.OW + ox) * a.C + c) = r;
+}
+
 struct MeanArgs { QView x, y; int N, HW, C; long long total; };
 
 template <int VEC>
@@ -161,6 +199,11 @@ extern "C" int b200k_pool2d_q8(const b200k_pool2d_params* p, void* stream)
     const int vec = pick_vec(p->x, p->y, p->c);
     a.total = (long long)p->n * p->oh * p->ow * (p->c / vec);
     cudaStream_t s = (cudaStream_t)stream;
+    if (vec == 16 && p->pool_type == 0 && p->x.dtype == p->y.dtype && p->x.scale == p->y.scale &&
+        p->x.zero_point == p->y.zero_point && p->x.scale > 0.f) {
+        maxpool_same_quant_kernel<<<div_up(a.total, 256), 256, 0, s>>>(a);
+        return check_launch("maxpool_same_quant_kernel");
+    }
     if (vec == 16)     pool2d_kernel<16><<<div_up(a.total, 256), 256, 0, s>>>(a);
     else if (vec == 4) pool2d_kernel<4><<<div_up(a.total, 256), 256, 0, s>>>(a);
     else               pool2d_kernel<1><<<div_up(a.total, 256), 256, 0, s>>>(a);
