@@ -43,7 +43,8 @@ namespace b200k {
 constexpr int TC_BM = 128;
 constexpr int TC_EPI_WARPS = 16;
 constexpr int TC_THREADS = 64 + 32 * TC_EPI_WARPS;   // warp 0 producer, warp 1 MMA issuer, then the epilogue warps
-constexpr unsigned TC_SPIN_LIMIT = 1u << 22;
+constexpr unsigned TC_WAIT_HINT_NS = 20000;              // one suspended try_wait lasts at most this long
+constexpr long long TC_WAIT_LIMIT_CYCLES = 4000000000ll;  // about two seconds: no wait of a healthy launch comes near
 
 __device__ int g_tc_status = 0;                 // 0 ok, otherwise the code of the wait that gave up
 
@@ -93,19 +94,21 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes)
 {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
-// Bounded wait: returns false when the limit is hit.
+// Bounded wait: returns false when the time limit is hit.  try_wait suspends the thread until the phase completes or
+// the hint (in ns) expires, so a waiting thread polls rarely and leaves the issue slots to the epilogue warps.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity)
 {
     const uint32_t addr = smem_u32(bar);
-    for (unsigned i = 0; i < TC_SPIN_LIMIT; ++i) {
+    const long long t0 = clock64();
+    for (;;) {
         uint32_t ok;
         asm volatile("{\n\t.reg .pred p;\n\t"
-                     "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                     "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
                      "selp.b32 %0, 1, 0, p;\n\t}"
-                     : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
+                     : "=r"(ok) : "r"(addr), "r"(parity), "r"(TC_WAIT_HINT_NS) : "memory");
         if (ok) return true;
+        if (clock64() - t0 > TC_WAIT_LIMIT_CYCLES) return false;
     }
-    return false;
 }
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y)
 {
@@ -228,46 +231,45 @@ __device__ __noinline__ float add_exact(float qf, float rf, const AddExact& x)
 }
 
 // Two-wide fp32 arithmetic (one instruction for two IEEE round-to-nearest operations): the epilogue is bound by
-// instruction issue, not by the arithmetic pipes.
-__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c)
+// instruction issue, not by the arithmetic pipes.  Pairs travel in 64-bit registers.
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pack2(float lo, float hi)
 {
-    float2 d;
-    asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\t"
-        "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
-        "fma.rn.f32x2 rd, ra, rb, rc;\n\t"
-        "mov.b64 {%0, %1}, rd;\n\t}"
-        : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+    f32x2 d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(lo), "f"(hi));
     return d;
 }
-__device__ __forceinline__ float2 add2(float2 a, float2 b)
+__device__ __forceinline__ void unpack2(f32x2 v, float& lo, float& hi)
 {
-    float2 d;
-    asm("{\n\t.reg .b64 ra, rb, rd;\n\t"
-        "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
-        "add.rn.f32x2 rd, ra, rb;\n\t"
-        "mov.b64 {%0, %1}, rd;\n\t}"
-        : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c)
+{
+    f32x2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
     return d;
 }
-__device__ __forceinline__ float2 sub2(float2 a, float2 b)
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b)
 {
-    float2 d;
-    asm("{\n\t.reg .b64 ra, rb, rd;\n\t"
-        "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
-        "sub.rn.f32x2 rd, ra, rb;\n\t"
-        "mov.b64 {%0, %1}, rd;\n\t}"
-        : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+    f32x2 d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
     return d;
 }
-__device__ __forceinline__ float2 mul2(float2 a, float2 b)
+__device__ __forceinline__ f32x2 sub2(f32x2 a, f32x2 b)
 {
-    float2 d;
-    asm("{\n\t.reg .b64 ra, rb, rd;\n\t"
-        "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
-        "mul.rn.f32x2 rd, ra, rb;\n\t"
-        "mov.b64 {%0, %1}, rd;\n\t}"
-        : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+    f32x2 d;
+    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
     return d;
+}
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b)
+{
+    f32x2 d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ void lds_2x2(uint32_t addr, f32x2& a, f32x2& b)   // four consecutive floats as two pairs
+{
+    asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "r"(addr));
 }
 
 // 128-bit shared-memory accesses by 32-bit shared address (keeps them out of the generic address space)
@@ -321,25 +323,25 @@ template <bool FUSED>
 __device__ __forceinline__ uint4 epi_chunk(const uint32_t* r, const uint4 rv, const EpiAddr& ad, const EpiConsts& ec)
 {
     const uint32_t resw[4] = {rv.x ^ ec.res_flip, rv.y ^ ec.res_flip, rv.z ^ ec.res_flip, rv.w ^ ec.res_flip};
-    const float2 magic = make_float2(TC_MAGIC, TC_MAGIC);
+    const f32x2 magic = pack2(TC_MAGIC, TC_MAGIC);
     uint32_t packed[4];
     #pragma unroll
     for (int g = 0; g < 4; ++g) {                              // 4 columns at a time: 128-bit shared loads
-        const uint4 Mw = lds128(ad.M + g * 16), Bw = lds128(ad.Bc + g * 16);
-        const float2 M01 = make_float2(__uint_as_float(Mw.x), __uint_as_float(Mw.y));
-        const float2 M23 = make_float2(__uint_as_float(Mw.z), __uint_as_float(Mw.w));
-        const float2 B01 = make_float2(__uint_as_float(Bw.x), __uint_as_float(Bw.y));
-        const float2 B23 = make_float2(__uint_as_float(Bw.z), __uint_as_float(Bw.w));
-        const float2 a01 = make_float2(__int2float_rn((int)r[g * 4 + 0]), __int2float_rn((int)r[g * 4 + 1]));
-        const float2 a23 = make_float2(__int2float_rn((int)r[g * 4 + 2]), __int2float_rn((int)r[g * 4 + 3]));
-        const float2 y01 = fma2(a01, M01, B01), y23 = fma2(a23, M23, B23);
-        const float2 t01 = add2(y01, magic), t23 = add2(y23, magic);
-        const float2 n01 = sub2(t01, magic), n23 = sub2(t23, magic);
-        const float2 d01 = sub2(y01, n01), d23 = sub2(y23, n23);
-        const float2 s01 = mul2(d01, d01), s23 = mul2(d23, d23);
-        float t[4] = {t01.x, t01.y, t23.x, t23.y};
-        float n[4] = {n01.x, n01.y, n23.x, n23.y};
-        const bool f0 = s01.x >= ec.thr1, f1 = s01.y >= ec.thr1, f2 = s23.x >= ec.thr1, f3 = s23.y >= ec.thr1;
+        f32x2 M01, M23, B01, B23;
+        lds_2x2(ad.M + g * 16, M01, M23);
+        lds_2x2(ad.Bc + g * 16, B01, B23);
+        const f32x2 a01 = pack2(__int2float_rn((int)r[g * 4 + 0]), __int2float_rn((int)r[g * 4 + 1]));
+        const f32x2 a23 = pack2(__int2float_rn((int)r[g * 4 + 2]), __int2float_rn((int)r[g * 4 + 3]));
+        const f32x2 y01 = fma2(a01, M01, B01), y23 = fma2(a23, M23, B23);
+        const f32x2 t01 = add2(y01, magic), t23 = add2(y23, magic);
+        const f32x2 n01 = sub2(t01, magic), n23 = sub2(t23, magic);
+        const f32x2 d01 = sub2(y01, n01), d23 = sub2(y23, n23);
+        const f32x2 s01 = mul2(d01, d01), s23 = mul2(d23, d23);
+        float t[4], n[4], sq[4];
+        unpack2(t01, t[0], t[1]); unpack2(t23, t[2], t[3]);
+        unpack2(s01, sq[0], sq[1]); unpack2(s23, sq[2], sq[3]);
+        if (FUSED) { unpack2(n01, n[0], n[1]); unpack2(n23, n[2], n[3]); }
+        const bool f0 = sq[0] >= ec.thr1, f1 = sq[1] >= ec.thr1, f2 = sq[2] >= ec.thr1, f3 = sq[3] >= ec.thr1;
         if (__any_sync(0xffffffffu, f0 | f1 | f2 | f3)) {
             const bool ff[4] = {f0, f1, f2, f3};
             #pragma unroll
@@ -366,19 +368,22 @@ __device__ __forceinline__ uint4 epi_chunk(const uint32_t* r, const uint4 rv, co
                 // other operand's byte placed in the mantissa of 2^23 + 2^22: value = MAGIC + byte
                 rf[e] = __uint_as_float(__byte_perm(resw[g], 0x4B400000u, 0x7650 + e));
             }
-            const float2 rb = make_float2(ec.res_bias, ec.res_bias), A1 = make_float2(ec.a1, ec.a1);
-            const float2 A2 = make_float2(ec.a2, ec.a2), C0 = make_float2(ec.c0, ec.c0);
-            const float2 r01 = sub2(make_float2(rf[0], rf[1]), rb), r23 = sub2(make_float2(rf[2], rf[3]), rb);
-            const float2 z01 = fma2(make_float2(qf[0], qf[1]), A1, fma2(r01, A2, C0));
-            const float2 z23 = fma2(make_float2(qf[2], qf[3]), A1, fma2(r23, A2, C0));
-            const float2 u01 = add2(z01, magic), u23 = add2(z23, magic);
-            const float2 e01 = sub2(z01, sub2(u01, magic)), e23 = sub2(z23, sub2(u23, magic));
-            const float2 w01 = mul2(e01, e01), w23 = mul2(e23, e23);
-            float u[4] = {u01.x, u01.y, u23.x, u23.y};
-            const bool h0 = w01.x >= ec.thr2, h1 = w01.y >= ec.thr2, h2 = w23.x >= ec.thr2, h3 = w23.y >= ec.thr2;
+            const f32x2 rb = pack2(ec.res_bias, ec.res_bias), A1 = pack2(ec.a1, ec.a1);
+            const f32x2 A2 = pack2(ec.a2, ec.a2), C0 = pack2(ec.c0, ec.c0);
+            const f32x2 r01 = sub2(pack2(rf[0], rf[1]), rb), r23 = sub2(pack2(rf[2], rf[3]), rb);
+            const f32x2 z01 = fma2(pack2(qf[0], qf[1]), A1, fma2(r01, A2, C0));
+            const f32x2 z23 = fma2(pack2(qf[2], qf[3]), A1, fma2(r23, A2, C0));
+            const f32x2 u01 = add2(z01, magic), u23 = add2(z23, magic);
+            const f32x2 e01 = sub2(z01, sub2(u01, magic)), e23 = sub2(z23, sub2(u23, magic));
+            const f32x2 w01 = mul2(e01, e01), w23 = mul2(e23, e23);
+            float u[4], wq[4];
+            unpack2(u01, u[0], u[1]); unpack2(u23, u[2], u[3]);
+            unpack2(w01, wq[0], wq[1]); unpack2(w23, wq[2], wq[3]);
+            const bool h0 = wq[0] >= ec.thr2, h1 = wq[1] >= ec.thr2, h2 = wq[2] >= ec.thr2, h3 = wq[3] >= ec.thr2;
             if (__any_sync(0xffffffffu, h0 | h1 | h2 | h3)) {
                 const bool hh[4] = {h0, h1, h2, h3};
-                const float rr[4] = {r01.x, r01.y, r23.x, r23.y};
+                float rr[4];
+                unpack2(r01, rr[0], rr[1]); unpack2(r23, rr[2], rr[3]);
                 #pragma unroll
                 for (int e = 0; e < 4; ++e)
                     if (hh[e]) u[e] = __fadd_rn(add_exact(qf[e], rr[e], ec.ax), TC_MAGIC);
@@ -481,8 +486,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     if (warp == 0) {
         // ===================== TMA producer =====================
         if (lane == 0) {
-            uint32_t g = 0;                                  // slices issued so far (ring position)
-            uint32_t unit = 0;                               // output units announced so far
+            int st = 0; uint32_t ph = 0;                     // ring position: stage and its phase bit
+            int ub = 0; uint32_t uph = 0;                    // unit-buffer position (kept without divisions)
             bool alive = true;
             for (int t = blockIdx.x; t < ntiles && alive; t += gridDim.x) {
                 const int n0 = (t % ntn) * BN;
@@ -500,34 +505,35 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     w0 = ox * a.sw - a.pl;
                     h0 = oy * a.sh - a.pt;
                 }
-                for (int s = 0; s < a.nslices; ++s, ++g) {
-                    const int st = g % STAGES;
-                    const uint32_t ph = (g / STAGES) & 1u;
+                int tap = 0, cc = 0;                              // slice = (filter tap, channel chunk)
+                for (int s = 0; s < a.nslices; ++s) {
                     if (!mbar_wait(&empty[st], ph ^ 1u)) { atomicExch(&g_tc_status, 1); alive = false; break; }
-                    const int tap = s / a.cchunks;
-                    const int c0 = (s - tap * a.cchunks) * SWZ;
+                    const int c0 = cc * SWZ;
                     uint8_t* sa = smem + st * L::STAGE_BYTES;
                     uint8_t* sb = sa + L::A_BYTES;
-                    if (a.debug == 2) { mbar_arrive(&full[st]); continue; }
-                    mbar_expect_tx(&full[st], a.stage_tx);
+                    const int cur = st, cur_tap = tap;
+                    if (++st == STAGES) { st = 0; ph ^= 1u; }
+                    if (++cc == a.cchunks) { cc = 0; ++tap; }
+                    if (a.debug == 2) { mbar_arrive(&full[cur]); continue; }
+                    mbar_expect_tx(&full[cur], a.stage_tx);
                     if (a.im2col == 2) {
-                        tma_load_4d(sa, &tmA, &full[st], 0, 0, h0 + tap * a.dh, nimg);   // tap = filter row
+                        tma_load_4d(sa, &tmA, &full[cur], 0, 0, h0 + cur_tap * a.dh, nimg);   // tap = filter row
                     } else if (a.im2col) {
-                        const int ky = tap / a.KW, kx = tap - ky * a.KW;
-                        tma_load_im2col(sa, &tmA, &full[st], c0, w0, h0, nimg, (uint16_t)(kx * a.dw), (uint16_t)(ky * a.dh));
+                        const int ky = cur_tap / a.KW, kx = cur_tap - ky * a.KW;
+                        tma_load_im2col(sa, &tmA, &full[cur], c0, w0, h0, nimg, (uint16_t)(kx * a.dw), (uint16_t)(ky * a.dh));
                     } else {
-                        tma_load_2d(sa, &tmA, &full[st], c0, (int)m0);
+                        tma_load_2d(sa, &tmA, &full[cur], c0, (int)m0);
                     }
-                    tma_load_2d(sb, &tmB, &full[st], tap * a.kstride + c0, n0);
+                    tma_load_2d(sb, &tmB, &full[cur], cur_tap * a.kstride + c0, n0);
                 }
                 if (a.res && alive) {
                     // the fused Add's other operand, one unit at a time, into the buffer the epilogue will overwrite
-                    for (int us = 0; us < UNITS; ++us, ++unit) {
-                        const int ub = unit % NIO;
-                        if (!mbar_wait(&io_empty[ub], ((unit / NIO) & 1u) ^ 1u)) { atomicExch(&g_tc_status, 6); alive = false; break; }
+                    for (int us = 0; us < UNITS; ++us) {
+                        if (!mbar_wait(&io_empty[ub], uph ^ 1u)) { atomicExch(&g_tc_status, 6); alive = false; break; }
                         mbar_expect_tx(&io_full[ub], IO_BYTES);
                         tma_load_3d(s_io + (size_t)ub * IO_BYTES, &tmR, &io_full[ub], n0 + us * UW,
                                     a.im2col == 2 ? 0 : (int)m0, a.im2col == 2 ? tm : 0);
+                        if (++ub == NIO) { ub = 0; uph ^= 1u; }
                     }
                 }
             }
@@ -539,7 +545,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             // 0 = unsigned 8-bit); both operands K-major (bits 15, 16 = 0); N >> 3 at bit 17; M >> 4 at bit 24
             const uint32_t id = (2u << 4) | ((uint32_t)a.a_signed << 7) | ((uint32_t)a.b_signed << 10) |
                                 ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
-            uint32_t g = 0;
+            int st = 0; uint32_t ph = 0;                     // ring position
             bool alive = true;
             int it = 0;
             for (int t = blockIdx.x; t < ntiles && alive; t += gridDim.x, ++it) {
@@ -548,19 +554,19 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 if (!mbar_wait(&acc_empty[buf], (((uint32_t)it >> 1) & 1u) ^ 1u)) { atomicExch(&g_tc_status, 4); break; }
                 tc_fence_after();
                 const uint32_t tacc = tmem_base + (uint32_t)(buf * BN);
-                for (int s = 0; s < a.nslices; ++s, ++g) {
-                    const int st = g % STAGES;
-                    const uint32_t ph = (g / STAGES) & 1u;
+                for (int s = 0; s < a.nslices; ++s) {
                     if (!mbar_wait(&full[st], ph)) { atomicExch(&g_tc_status, 2); alive = false; break; }
                     tc_fence_after();
-                    if (a.debug == 1) { mbar_arrive(&empty[st]); continue; }
-                    const uint32_t sa = smem_u32(smem + st * L::STAGE_BYTES);
+                    const int cur = st;
+                    if (++st == STAGES) { st = 0; ph ^= 1u; }
+                    if (a.debug == 1) { mbar_arrive(&empty[cur]); continue; }
+                    const uint32_t sa = smem_u32(smem + cur * L::STAGE_BYTES);
                     const uint64_t da = make_smem_desc<SWZ>(sa);
                     const uint64_t db = make_smem_desc<SWZ>(sa + L::A_BYTES);
                     #pragma unroll
                     for (int k = 0; k < SWZ / 32; ++k)
                         tc_mma_i8(tacc, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), id, (s > 0 || k > 0) ? 1u : 0u);
-                    tc_commit(&empty[st]);             // slot reusable once these MMAs have read it
+                    tc_commit(&empty[cur]);            // slot reusable once these MMAs have read it
                 }
                 if (alive) tc_commit(&acc_full[buf]);  // accumulator of this tile complete
             }
@@ -593,7 +599,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         ec.thr2 = a.add_eps < 0.5f ? (0.5f - a.add_eps) * (0.5f - a.add_eps) : 0.f;
         int cur_n0 = -1;
         int it = 0;
-        uint32_t unit = 0;
+        int ub = 0, prev_ub = 0; uint32_t uph = 0;           // unit-buffer position (kept without divisions)
+        bool first_unit = true;
         bool dead = false;
         for (int t = blockIdx.x; t < ntiles; t += gridDim.x, ++it) {
             const int n0 = (t % ntn) * BN;
@@ -668,8 +675,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const uint32_t a_cc = smem_u32(corr_row), a_Bc = smem_u32(s_Bc + cls * BN);
             const uint32_t tacc = tmem_base + (uint32_t)(buf * BN) + ((uint32_t)(quad * 32) << 16);
             #pragma unroll 1
-            for (int us = 0; us < UNITS; ++us, ++unit) {
-                const int ub = unit % NIO;
+            for (int us = 0; us < UNITS; ++us) {
                 uint8_t* io_row = s_io + (size_t)ub * IO_BYTES + row * UW;
                 const int colw = us * UW + part * (UW / 4);    // first column of this warp in this unit
                 uint32_t r[CPW][16];
@@ -683,7 +689,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&acc_empty[buf]);
                 }
-                if (a.res && !dead && !mbar_wait(&io_full[ub], (unit / NIO) & 1u)) { atomicExch(&g_tc_status, 5); dead = true; }
+                if (a.res && !dead && !mbar_wait(&io_full[ub], uph)) { atomicExch(&g_tc_status, 5); dead = true; }
                 #pragma unroll
                 for (int k = 0; k < CPW; ++k) {
                     const int col0 = colw + k * 16;
@@ -702,7 +708,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     // every earlier store of this quadrant has been read out of shared memory: the buffer of the
                     // previous unit is free for the producer, and the next unit's buffer for the epilogue
                     asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-                    if (a.res && unit >= 1) mbar_arrive(&io_empty[(unit - 1) % NIO]);
+                    if (a.res && !first_unit) mbar_arrive(&io_empty[prev_ub]);
                 }
                 quad_barrier(quad);
                 if (leader) {
@@ -712,6 +718,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                                      a.im2col == 2 ? row0 : (int)(m0 + row0), a.im2col == 2 ? tm : 0);
                     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                 }
+                first_unit = false;
+                prev_ub = ub;
+                if (++ub == NIO) { ub = 0; uph ^= 1u; }
             }
         }
         if (leader) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");

@@ -196,6 +196,9 @@ def run_b200(args):
         return float(t.item())
 
     # ---- device-resident throughput ----
+    ln.Execute()
+    torch.cuda.synchronize()
+    ln.CaptureGraph()          # the whole workload queue as one CUDA graph: no per-workload host launch in the step
     for _ in range(args.warmup):
         ln.Execute()
     barrier()
