@@ -42,6 +42,7 @@ namespace b200k {
 
 constexpr int TC_BM = 128;
 constexpr int TC_EPI_WARPS = 16;
+constexpr int TC_LUT_TAG_WORDS = 12;
 constexpr int TC_THREADS = 64 + 32 * TC_EPI_WARPS;   // warp 0 producer, warp 1 MMA issuer, then the epilogue warps
 constexpr unsigned TC_WAIT_HINT_NS = 20000;              // one suspended try_wait lasts at most this long
 constexpr long long TC_WAIT_LIMIT_CYCLES = 4000000000ll;  // about two seconds: no wait of a healthy launch comes near
@@ -70,7 +71,9 @@ struct TcArgs {
     // fused ElementwiseBinary Add (res != null): y = Q2(deq(Q(conv)) + deq(res)), clamp in rq2
     const uint8_t* res; float res_scale; int res_zp; int res_u8;
     Requant rq2;
-    float add_a1, add_a2, add_c0, add_eps;      // one-FMA estimate of the fused Add and its tie margin
+    float inv_sy;                               // RN(1 / rq.sy), correctly rounded (see epi_chunk)
+    const uint8_t* add_lut;                     // fused-add table built by b200k_conv2d_pack (+ its tag), or null
+    uint32_t lut_tag[TC_LUT_TAG_WORDS];         // the tag a table made for exactly this launch carries
     int stages;                                 // ring depth chosen by the launcher (<= 8)
     int nio;                                    // unit buffers of the output path: 2, or 3 with a fused Add
     // zero-point correction classes: pixels whose in-image tap rectangle [ky0, ky1) x [kx0, kx1) is the same share
@@ -95,18 +98,21 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes)
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
 // Bounded wait: returns false when the time limit is hit.  try_wait suspends the thread until the phase completes or
-// the hint (in ns) expires, so a waiting thread polls rarely and leaves the issue slots to the epilogue warps.
+// a hardware time limit expires, so a waiting thread polls rarely; the clock is read once per 32 polls.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity)
 {
     const uint32_t addr = smem_u32(bar);
     const long long t0 = clock64();
     for (;;) {
-        uint32_t ok;
-        asm volatile("{\n\t.reg .pred p;\n\t"
-                     "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-                     "selp.b32 %0, 1, 0, p;\n\t}"
-                     : "=r"(ok) : "r"(addr), "r"(parity), "r"(TC_WAIT_HINT_NS) : "memory");
-        if (ok) return true;
+        #pragma unroll 1
+        for (int i = 0; i < 32; ++i) {
+            uint32_t ok;
+            asm volatile("{\n\t.reg .pred p;\n\t"
+                         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+                         "selp.b32 %0, 1, 0, p;\n\t}"
+                         : "=r"(ok) : "r"(addr), "r"(parity), "r"(TC_WAIT_HINT_NS) : "memory");
+            if (ok) return true;
+        }
         if (clock64() - t0 > TC_WAIT_LIMIT_CYCLES) return false;
     }
 }
@@ -211,23 +217,28 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr)
 // of the accumulator.
 constexpr float TC_MAGIC = 12582912.0f;          // 1.5 * 2^23: x + MAGIC - MAGIC == rint(x) for |x| < 2^22
 
-struct QuantF { float sy, zy, lo, hi; };         // lo / hi: type range intersected with the activation clamp
+// Reference arithmetic of one output value (unfused IEEE fp32), used by the rare fix-up pass:
+// v = fl(fl(acc * m) + b); q = clamp(zy + round_half_away(fl(v / sy))), then for a fused Add both operands are
+// dequantised, added and re-quantised (RefElementwiseBinaryWorkload), followed by the activation clamp.
+struct EpiExact {
+    float sy1, zy1, lo1, hi1;                    // the convolution's own quantisation (plain clamp bounds)
+    int fused, res_u8;
+    float zr, sr, sy2, zy2, lo2, hi2;
+};
 
-// Exact requantisation of one accumulator, as the reference evaluates it (unfused IEEE fp32).  Out of line: it runs
-// only for the few values whose one-FMA estimate lies next to a rounding tie.
-__device__ __noinline__ float requant_exact(int acc, float m, float b, float sy, float zy)
+__device__ __forceinline__ int exact_value(int acc, float m, float b, uint32_t res_byte, const EpiExact& x)
 {
     const float v = __fadd_rn(__fmul_rn(__int2float_rn(acc), m), b);
-    return __fadd_rn(zy, roundf(__fdiv_rn(v, sy)));
-}
-
-// Exact fused Add: both operands dequantised, added in fp32 and re-quantised (RefElementwiseBinaryWorkload).
-struct AddExact { float zy1, sy1, zr, sr, sy2, zy2; };
-__device__ __noinline__ float add_exact(float qf, float rf, const AddExact& x)
-{
-    const float fa = __fmul_rn(__fsub_rn(qf, x.zy1), x.sy1);
-    const float fb = __fmul_rn(__fsub_rn(rf, x.zr), x.sr);
-    return __fadd_rn(x.zy2, roundf(__fdiv_rn(__fadd_rn(fa, fb), x.sy2)));
+    float n = __fadd_rn(x.zy1, roundf(__fdiv_rn(v, x.sy1)));
+    n = fminf(fmaxf(n, x.lo1), x.hi1);
+    if (x.fused) {
+        const int rq = x.res_u8 ? (int)res_byte : (int)(int8_t)res_byte;
+        const float fa = __fmul_rn(__fsub_rn(n, x.zy1), x.sy1);
+        const float fb = __fmul_rn(__fsub_rn(__int2float_rn(rq), x.zr), x.sr);
+        n = __fadd_rn(x.zy2, roundf(__fdiv_rn(__fadd_rn(fa, fb), x.sy2)));
+        n = fminf(fmaxf(n, x.lo2), x.hi2);
+    }
+    return __float2int_rn(n);
 }
 
 // Two-wide fp32 arithmetic (one instruction for two IEEE round-to-nearest operations): the epilogue is bound by
@@ -272,7 +283,7 @@ __device__ __forceinline__ void lds_2x2(uint32_t addr, f32x2& a, f32x2& b)   // 
     asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "r"(addr));
 }
 
-// 128-bit shared-memory accesses by 32-bit shared address (keeps them out of the generic address space)
+// shared-memory accesses by 32-bit shared address (keeps them out of the generic address space)
 __device__ __forceinline__ uint4 lds128(uint32_t addr)
 {
     uint4 v;
@@ -295,105 +306,90 @@ __device__ __forceinline__ int lds_s32(uint32_t addr)
     asm volatile("ld.shared.s32 %0, [%1];" : "=r"(v) : "r"(addr));
     return v;
 }
+__device__ __forceinline__ uint32_t lds_u8(uint32_t addr)
+{
+    uint32_t v;
+    asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
 
 struct EpiConsts {
-    QuantF q1, q2;                               // the convolution's own quantisation; the fused Add's output
-    float thr1;                                  // (0.5 - eps1)^2 for the first estimate's tie test
-    float a1, a2, c0, thr2;                      // fused Add estimate: q2 ~ q1 * a1 + r * a2 + c0; (0.5 - eps2)^2
-    AddExact ax;
-    float res_bias; uint32_t res_flip;           // decode of the other operand's bytes
+    f32x2 inv2, nsy2, magic2, zy2, zero2;        // pairs of: RN(1 / sy), -sy, the rounding constant, zero point (+ bias), 0
+    float lo, hi;                                // clamp bounds in the biased domain (MAGIC + ...)
+    uint32_t lut;                                // shared address of the fused-add table minus 0x4B400000
 };
 
 // shared-memory addresses of the per-channel tables at the chunk's first column
-struct EpiAddr { uint32_t M, Bc, m, b, cc; };
+struct EpiAddr { uint32_t m, b, cc; };
 
-// 16 accumulator columns of one output pixel -> 16 output bytes.  FUSED: add the other operand (16 bytes in rv).
+// 16 accumulator columns of one output pixel -> 16 output bytes, branch-free.  FUSED: look the result of the fused
+// Add up with the other operand's byte (16 bytes in rv).
 //
-// Requantisation.  The exact chain is v = fl(fl(acc * m) + b); q = clamp(zy + round(fl(v / sy))) with acc = raw - corr
-// (the zero-point correction).  The estimate y = fma(float(raw), M, B') with M = fl(m / sy) and
-// B' = fl(fl(fl(b / sy) + zy) - fl(corr * M)) differs from zy + fl(v / sy) by at most
-// 2^-24 * (3074 + 4|b / sy| + 4|corr M|) while |y - zy| <= 512, so its nearest integer n is the exact result unless y
-// lies within eps1 = 2^-24 * (4096 + 8|b / sy| + 8|corr M|) of a rounding tie, i.e. unless (y - n)^2 >= (0.5 - eps1)^2;
-// then the exact chain is evaluated.  Beyond 512 every 8-bit output saturates in the direction of y's sign (and the
-// magic-constant rounding, although coarse there, keeps sign and magnitude; a stray tie flag only costs time).
-// The fused Add is estimated the same way: q2 ~ fma(q1, a1, fma(r, a2, c0)) with a1 = sy1 / sy2, a2 = sr / sy2,
-// c0 = zy2 - zy1 a1 - zr a2, whose distance from the exact chain is below 2^-24 * 255 * (9 (a1 + a2) + 3); eps2 is
-// twice that.  Tie flags are tested once per four values with a warp vote, so the common path has no branches.
+// The reference chain is v = fl(fl(acc * m) + b); q = clamp(zy + round_half_away(fl(v / sy))).  The division is
+// evaluated exactly without the division unit: with y = RN(1 / sy) (prepared on the host), q0 = fl(v * y),
+// r = fma(-q0, sy, v) (exact) and q1 = fma(r, y, q0), q1 is the correctly rounded quotient (Markstein's theorem; it
+// needs a correctly rounded y and a normal-range quotient — for tiny or huge quotients the last bit does not matter,
+// they round to 0 or saturate).  Rounding to an integer uses the 1.5 * 2^23 constant, which rounds halves to even where
+// the reference rounds them away from zero: |q1 - n| = 0.5 exactly marks those values (and any value too large for the
+// constant), the maximum of |q1 - n| over the chunk is handed back in dmax, and the caller re-evaluates a flagged chunk
+// with the plain reference arithmetic.
 template <bool FUSED>
-__device__ __forceinline__ uint4 epi_chunk(const uint32_t* r, const uint4 rv, const EpiAddr& ad, const EpiConsts& ec)
+__device__ __forceinline__ uint4 epi_chunk(const uint32_t* r, const uint4 rv, const EpiAddr& ad, const EpiConsts& ec, float& dmax)
 {
-    const uint32_t resw[4] = {rv.x ^ ec.res_flip, rv.y ^ ec.res_flip, rv.z ^ ec.res_flip, rv.w ^ ec.res_flip};
-    const f32x2 magic = pack2(TC_MAGIC, TC_MAGIC);
+    const uint32_t resw[4] = {rv.x, rv.y, rv.z, rv.w};
     uint32_t packed[4];
     #pragma unroll
     for (int g = 0; g < 4; ++g) {                              // 4 columns at a time: 128-bit shared loads
-        f32x2 M01, M23, B01, B23;
-        lds_2x2(ad.M + g * 16, M01, M23);
-        lds_2x2(ad.Bc + g * 16, B01, B23);
-        const f32x2 a01 = pack2(__int2float_rn((int)r[g * 4 + 0]), __int2float_rn((int)r[g * 4 + 1]));
-        const f32x2 a23 = pack2(__int2float_rn((int)r[g * 4 + 2]), __int2float_rn((int)r[g * 4 + 3]));
-        const f32x2 y01 = fma2(a01, M01, B01), y23 = fma2(a23, M23, B23);
-        const f32x2 t01 = add2(y01, magic), t23 = add2(y23, magic);
-        const f32x2 n01 = sub2(t01, magic), n23 = sub2(t23, magic);
-        const f32x2 d01 = sub2(y01, n01), d23 = sub2(y23, n23);
-        const f32x2 s01 = mul2(d01, d01), s23 = mul2(d23, d23);
-        float t[4], n[4], sq[4];
-        unpack2(t01, t[0], t[1]); unpack2(t23, t[2], t[3]);
-        unpack2(s01, sq[0], sq[1]); unpack2(s23, sq[2], sq[3]);
-        if (FUSED) { unpack2(n01, n[0], n[1]); unpack2(n23, n[2], n[3]); }
-        const bool f0 = sq[0] >= ec.thr1, f1 = sq[1] >= ec.thr1, f2 = sq[2] >= ec.thr1, f3 = sq[3] >= ec.thr1;
-        if (__any_sync(0xffffffffu, f0 | f1 | f2 | f3)) {
-            const bool ff[4] = {f0, f1, f2, f3};
-            #pragma unroll
-            for (int e = 0; e < 4; ++e)
-                if (ff[e]) {
-                    const int col = g * 4 + e;
-                    n[e] = requant_exact((int)r[col] - lds_s32(ad.cc + col * 4), lds_f32(ad.m + col * 4), lds_f32(ad.b + col * 4),
-                                         ec.q1.sy, ec.q1.zy);
-                    t[e] = __fadd_rn(n[e], TC_MAGIC);
-                }
-        }
+        f32x2 m01, m23, b01, b23;
+        lds_2x2(ad.m + g * 16, m01, m23);
+        lds_2x2(ad.b + g * 16, b01, b23);
+        const uint4 cv = lds128(ad.cc + g * 16);
+        const f32x2 a01 = pack2(__int2float_rn((int)r[g * 4 + 0] - (int)cv.x), __int2float_rn((int)r[g * 4 + 1] - (int)cv.y));
+        const f32x2 a23 = pack2(__int2float_rn((int)r[g * 4 + 2] - (int)cv.z), __int2float_rn((int)r[g * 4 + 3] - (int)cv.w));
+        // acc * m as an FMA with a zero addend: the assembler contracts a packed multiply feeding a packed add into
+        // one FMA (a single rounding) even with explicit rounding modifiers, which the reference does not do
+        const f32x2 v01 = add2(fma2(a01, m01, ec.zero2), b01), v23 = add2(fma2(a23, m23, ec.zero2), b23);
+        const f32x2 p01 = mul2(v01, ec.inv2), p23 = mul2(v23, ec.inv2);
+        const f32x2 q01 = fma2(fma2(p01, ec.nsy2, v01), ec.inv2, p01), q23 = fma2(fma2(p23, ec.nsy2, v23), ec.inv2, p23);
+        const f32x2 t01 = add2(q01, ec.magic2), t23 = add2(q23, ec.magic2);
+        const f32x2 d01 = sub2(q01, sub2(t01, ec.magic2)), d23 = sub2(q23, sub2(t23, ec.magic2));
+        const f32x2 z01 = add2(t01, ec.zy2), z23 = add2(t23, ec.zy2);
+        float d[4], z[4];
+        unpack2(d01, d[0], d[1]); unpack2(d23, d[2], d[3]);
+        unpack2(z01, z[0], z[1]); unpack2(z23, z[2], z[3]);
+        dmax = fmaxf(fmaxf(dmax, fabsf(d[0])), fabsf(d[1]));
+        dmax = fmaxf(fmaxf(dmax, fabsf(d[2])), fabsf(d[3]));
         uint32_t bits[4];
-        if (!FUSED) {
-            // clamp in the biased domain: the low byte of t's bit pattern is the two's-complement output byte
-            #pragma unroll
-            for (int e = 0; e < 4; ++e) bits[e] = __float_as_uint(fminf(fmaxf(t[e], ec.q1.lo + TC_MAGIC), ec.q1.hi + TC_MAGIC));
-        } else {
-            // fused ElementwiseBinary Add: the convolution's own 8-bit output is formed first, then both operands
-            // are dequantised, added in fp32 and re-quantised, as the two separate workloads do
-            float qf[4], rf[4];
-            #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                qf[e] = fminf(fmaxf(n[e], ec.q1.lo), ec.q1.hi);
-                // other operand's byte placed in the mantissa of 2^23 + 2^22: value = MAGIC + byte
-                rf[e] = __uint_as_float(__byte_perm(resw[g], 0x4B400000u, 0x7650 + e));
+        #pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            // clamp in the biased domain: the low byte of the bit pattern is the output byte
+            bits[e] = __float_as_uint(fminf(fmaxf(z[e], ec.lo), ec.hi));
+            if (FUSED) {
+                // bits = 0x4B4000qq with qq = conv output - type minimum: (qq << 8 | other byte) indexes the table
+                bits[e] = lds_u8(__byte_perm(bits[e], resw[g], 0x3204 + e) + ec.lut);
             }
-            const f32x2 rb = pack2(ec.res_bias, ec.res_bias), A1 = pack2(ec.a1, ec.a1);
-            const f32x2 A2 = pack2(ec.a2, ec.a2), C0 = pack2(ec.c0, ec.c0);
-            const f32x2 r01 = sub2(pack2(rf[0], rf[1]), rb), r23 = sub2(pack2(rf[2], rf[3]), rb);
-            const f32x2 z01 = fma2(pack2(qf[0], qf[1]), A1, fma2(r01, A2, C0));
-            const f32x2 z23 = fma2(pack2(qf[2], qf[3]), A1, fma2(r23, A2, C0));
-            const f32x2 u01 = add2(z01, magic), u23 = add2(z23, magic);
-            const f32x2 e01 = sub2(z01, sub2(u01, magic)), e23 = sub2(z23, sub2(u23, magic));
-            const f32x2 w01 = mul2(e01, e01), w23 = mul2(e23, e23);
-            float u[4], wq[4];
-            unpack2(u01, u[0], u[1]); unpack2(u23, u[2], u[3]);
-            unpack2(w01, wq[0], wq[1]); unpack2(w23, wq[2], wq[3]);
-            const bool h0 = wq[0] >= ec.thr2, h1 = wq[1] >= ec.thr2, h2 = wq[2] >= ec.thr2, h3 = wq[3] >= ec.thr2;
-            if (__any_sync(0xffffffffu, h0 | h1 | h2 | h3)) {
-                const bool hh[4] = {h0, h1, h2, h3};
-                float rr[4];
-                unpack2(r01, rr[0], rr[1]); unpack2(r23, rr[2], rr[3]);
-                #pragma unroll
-                for (int e = 0; e < 4; ++e)
-                    if (hh[e]) u[e] = __fadd_rn(add_exact(qf[e], rr[e], ec.ax), TC_MAGIC);
-            }
-            #pragma unroll
-            for (int e = 0; e < 4; ++e) bits[e] = __float_as_uint(fminf(fmaxf(u[e], ec.q2.lo + TC_MAGIC), ec.q2.hi + TC_MAGIC));
         }
         packed[g] = __byte_perm(__byte_perm(bits[0], bits[1], 0x0040), __byte_perm(bits[2], bits[3], 0x0040), 0x5410);
     }
     return make_uint4(packed[0], packed[1], packed[2], packed[3]);
+}
+
+// The fix-up pass of one chunk: re-reads the 16 accumulators from tensor memory and evaluates them with the reference
+// arithmetic.  Out of line; a warp calls it as a whole.
+__device__ __noinline__ void epi_fixup(uint32_t taddr, uint32_t slot, uint4 rv, uint32_t a_m, uint32_t a_b, uint32_t a_cc,
+                                       const EpiExact& x)
+{
+    uint32_t r[16];
+    tc_ld16(taddr, r);
+    const uint32_t resw[4] = {rv.x, rv.y, rv.z, rv.w};
+    uint32_t out[4] = {0, 0, 0, 0};
+    #pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        const int q = exact_value((int)r[j] - lds_s32(a_cc + j * 4), lds_f32(a_m + j * 4), lds_f32(a_b + j * 4),
+                                  (resw[j >> 2] >> (8 * (j & 3))) & 0xffu, x);
+        out[j >> 2] |= ((uint32_t)q & 0xffu) << (8 * (j & 3));
+    }
+    sts128(slot, make_uint4(out[0], out[1], out[2], out[3]));
 }
 
 template <int BN, int SWZ>
@@ -406,10 +402,10 @@ struct TcSmem {
     static constexpr int UNITS = BN / UW;                   // units per tile
     static constexpr int IO_BYTES = TC_BM * UW;             // one unit buffer: [128 rows][UW], TMA-swizzled
     static constexpr int MAX_IO = 3;
-    // after the ring (stages x STAGE_BYTES) and the unit buffers (nio x IO_BYTES): per-channel m, bterm, M [BN each],
+    // after the ring (stages x STAGE_BYTES) and the unit buffers (nio x IO_BYTES): per-channel m, bterm [BN each],
     // barriers (full[8], empty[8], acc_full[2], acc_empty[2], io_full[3], io_empty[3]), tmem slot + eps slot; then the
-    // zero-point correction tables [classes][BN]: corr (int) and B' (float) (dynamic size)
-    static constexpr int CONST_BYTES = 3 * BN * 4 + (2 * MAX_STAGES + 4 + 2 * MAX_IO) * 8 + 16;
+    // zero-point correction table [classes][BN], then the fused-add table (dynamic sizes)
+    static constexpr int CONST_BYTES = 2 * BN * 4 + (2 * MAX_STAGES + 4 + 2 * MAX_IO) * 8 + 16;
 };
 
 __device__ __forceinline__ void epi_barrier()       // the epilogue warps only (named barrier 1)
@@ -452,17 +448,16 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     uint8_t* s_io = smem + (size_t)STAGES * L::STAGE_BYTES;
     float* s_m = (float*)(s_io + (size_t)NIO * IO_BYTES);
     float* s_bterm = s_m + BN;
-    float* s_M = s_bterm + BN;                              // estimate: q ~ acc * M + B, trusted away from ties
-    uint64_t* full = (uint64_t*)(s_M + BN);
+    uint64_t* full = (uint64_t*)(s_bterm + BN);
     uint64_t* empty = full + MAX_STAGES;
     uint64_t* acc_full = empty + MAX_STAGES;                // [2]
     uint64_t* acc_empty = acc_full + 2;                     // [2]
     uint64_t* io_full = acc_empty + 2;                      // [3] other operand's unit has landed
     uint64_t* io_empty = io_full + L::MAX_IO;               // [3] the unit buffer's last store has been read out
     uint32_t* tmem_slot = (uint32_t*)(io_empty + L::MAX_IO);
-    int* s_eps = (int*)(tmem_slot + 1);                     // bit pattern of the tile-wide tie margin
-    int32_t* s_cc = (int32_t*)(tmem_slot + 4);              // [classes][BN] zero-point corrections (exact path)
-    float* s_Bc = (float*)(s_cc + a.ncls * BN);             // [classes][BN] B with the correction folded in (estimate)
+    uint32_t* s_lut_ok = tmem_slot + 1;                     // the fused-add table in global memory carries our tag
+    int32_t* s_cc = (int32_t*)(tmem_slot + 4);              // [classes][BN] zero-point corrections
+    uint8_t* s_lut = (uint8_t*)(s_cc + a.ncls * BN);        // [256][256] fused-add table
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int ntn = a.OC / BN;                              // n-tiles (OC is a multiple of BN)
@@ -473,6 +468,13 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], TC_EPI_WARPS); }
         for (int b = 0; b < L::MAX_IO; ++b) { mbar_init(&io_full[b], 1); mbar_init(&io_empty[b], 4); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        // a table is used only if it was built for exactly this launch's quantisation parameters
+        uint32_t ok = a.add_lut != nullptr;
+        if (ok) {
+            const uint32_t* tag = (const uint32_t*)(a.add_lut + 65536);
+            for (int i = 0; i < TC_LUT_TAG_WORDS; ++i) ok &= (tag[i] == a.lut_tag[i]);
+        }
+        *s_lut_ok = ok;
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(2 * BN) : "memory");
@@ -482,6 +484,15 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    const bool lut_ok = *s_lut_ok != 0;
+    if (a.add_lut) {                                        // uniform over the CTA
+        if (lut_ok) {
+            const uint4* src = (const uint4*)a.add_lut;
+            uint4* dst = (uint4*)s_lut;
+            for (int i = threadIdx.x; i < 65536 / 16; i += TC_THREADS) dst[i] = src[i];
+        }
+        __syncthreads();
+    }
 
     if (warp == 0) {
         // ===================== TMA producer =====================
@@ -585,18 +596,27 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int row = quad * 32 + lane;
         const uint32_t sw_x = UW == 128 ? (uint32_t)(row & 7) : (uint32_t)((row >> 1) & 3);   // TMA swizzle of this row
         const int pw = a.KW + 1;
+        const bool fused = a.res != nullptr;
+        const bool use_lut = fused && lut_ok;
+        const bool always_fix = fused && !lut_ok;            // no table: every chunk takes the reference arithmetic
+        const bool dump_acc = a.acc_out != nullptr;
+        EpiExact ex;
+        ex.sy1 = a.rq.sy; ex.zy1 = (float)a.rq.zy;
+        ex.lo1 = fmaxf(a.rq.tlo, (float)a.rq.clo); ex.hi1 = fminf(a.rq.thi, (float)a.rq.chi);
+        ex.fused = fused; ex.res_u8 = a.res_u8; ex.zr = (float)a.res_zp; ex.sr = a.res_scale;
+        ex.sy2 = a.rq2.sy; ex.zy2 = (float)a.rq2.zy;
+        ex.lo2 = fmaxf(a.rq2.tlo, (float)a.rq2.clo); ex.hi2 = fminf(a.rq2.thi, (float)a.rq2.chi);
         EpiConsts ec;
-        ec.q1.sy = a.rq.sy; ec.q1.zy = (float)a.rq.zy;
-        ec.q1.lo = fmaxf(a.rq.tlo, (float)a.rq.clo); ec.q1.hi = fminf(a.rq.thi, (float)a.rq.chi);
-        ec.q2.sy = a.rq2.sy; ec.q2.zy = (float)a.rq2.zy;
-        ec.q2.lo = fmaxf(a.rq2.tlo, (float)a.rq2.clo); ec.q2.hi = fminf(a.rq2.thi, (float)a.rq2.chi);
-        ec.a1 = a.add_a1; ec.a2 = a.add_a2; ec.c0 = a.add_c0;
-        ec.ax.zy1 = (float)a.rq.zy; ec.ax.sy1 = a.rq.sy; ec.ax.zr = (float)a.res_zp; ec.ax.sr = a.res_scale;
-        ec.ax.sy2 = a.rq2.sy; ec.ax.zy2 = (float)a.rq2.zy;
-        ec.res_flip = a.res_u8 ? 0u : 0x80808080u;
-        ec.res_bias = a.res_u8 ? TC_MAGIC : TC_MAGIC + 128.0f;
-        ec.thr1 = 0.f;
-        ec.thr2 = a.add_eps < 0.5f ? (0.5f - a.add_eps) * (0.5f - a.add_eps) : 0.f;
+        ec.inv2 = pack2(a.inv_sy, a.inv_sy);
+        ec.nsy2 = pack2(-a.rq.sy, -a.rq.sy);
+        ec.magic2 = pack2(TC_MAGIC, TC_MAGIC);
+        ec.zero2 = pack2(0.f, 0.f);
+        // with the table the first stage yields (value - type minimum), a byte in 0..255, to index it
+        const float zb = use_lut ? ex.zy1 - a.rq.tlo : ex.zy1;
+        ec.zy2 = pack2(zb, zb);
+        ec.lo = use_lut ? TC_MAGIC : TC_MAGIC + ex.lo1;
+        ec.hi = use_lut ? TC_MAGIC + 255.0f : TC_MAGIC + ex.hi1;
+        ec.lut = smem_u32(s_lut) - 0x4B400000u;
         int cur_n0 = -1;
         int it = 0;
         int ub = 0, prev_ub = 0; uint32_t uph = 0;           // unit-buffer position (kept without divisions)
@@ -610,43 +630,24 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             if (n0 != cur_n0) {
                 // per-channel constants of this n-tile (all epilogue warps are between tiles here)
                 epi_barrier();
-                if (etid == 0) *s_eps = 0;
-                epi_barrier();
                 for (int j = etid; j < BN; j += 32 * TC_EPI_WARPS) {
                     const int ch = n0 + j;
-                    const float m = __fmul_rn(a.rq.sx, a.w_scales ? a.w_scales[ch] : a.w_scale);
-                    const float b = a.bias ? __fmul_rn(__int2float_rn(a.bias[ch]), a.b_scales ? a.b_scales[ch] : a.b_scale) : 0.f;
-                    const float bs = __fdiv_rn(b, a.rq.sy);
-                    const float M = __fdiv_rn(m, a.rq.sy);
-                    const float B = __fadd_rn(bs, (float)a.rq.zy);
-                    s_m[j] = m;
-                    s_bterm[j] = b;
-                    s_M[j] = M;
-                    float gmax = 0.f;                        // largest |corr * M| over the classes
-                    for (int cls = 0; cls < a.ncls; ++cls) {
-                        int v = 0;
-                        if (a.need_corr) {
-                            const int yp = a.ypair[cls / a.ncx], xp = a.xpair[cls % a.ncx];
-                            const int y0 = yp >> 4, y1 = yp & 15, x0 = xp >> 4, x1 = xp & 15;
-                            const int32_t* P = a.prefix + ch;
-                            v = a.zx * (P[(long long)(y1 * pw + x1) * a.OC] - P[(long long)(y0 * pw + x1) * a.OC] -
-                                        P[(long long)(y1 * pw + x0) * a.OC] + P[(long long)(y0 * pw + x0) * a.OC]);
-                        }
-                        const float cm = __fmul_rn(__int2float_rn(v), M);
-                        s_cc[cls * BN + j] = v;
-                        s_Bc[cls * BN + j] = __fsub_rn(B, cm);
-                        gmax = fmaxf(gmax, fabsf(cm));
+                    s_m[j] = __fmul_rn(a.rq.sx, a.w_scales ? a.w_scales[ch] : a.w_scale);
+                    s_bterm[j] = a.bias ? __fmul_rn(__int2float_rn(a.bias[ch]), a.b_scales ? a.b_scales[ch] : a.b_scale) : 0.f;
+                }
+                for (int i = etid; i < a.ncls * BN; i += 32 * TC_EPI_WARPS) {
+                    const int cls = i / BN, j = i - cls * BN;
+                    int v = 0;
+                    if (a.need_corr) {
+                        const int yp = a.ypair[cls / a.ncx], xp = a.xpair[cls % a.ncx];
+                        const int y0 = yp >> 4, y1 = yp & 15, x0 = xp >> 4, x1 = xp & 15;
+                        const int32_t* P = a.prefix + n0 + j;
+                        v = a.zx * (P[(long long)(y1 * pw + x1) * a.OC] - P[(long long)(y0 * pw + x1) * a.OC] -
+                                    P[(long long)(y1 * pw + x0) * a.OC] + P[(long long)(y0 * pw + x0) * a.OC]);
                     }
-                    // tie margin (see epi_chunk); beyond any sensible magnitude every value takes the exact chain
-                    const float mag = fabsf(bs) + gmax;
-                    const float eps = mag < 65536.f ? (4096.f + 8.f * mag) * 5.9604644775390625e-8f : 1.0f;
-                    atomicMax(s_eps, __float_as_int(eps));
+                    s_cc[i] = v;
                 }
                 epi_barrier();
-                {
-                    const float eps = __int_as_float(*s_eps);
-                    ec.thr1 = eps < 0.5f ? (0.5f - eps) * (0.5f - eps) : 0.f;    // 0: every value is "near a tie"
-                }
                 cur_n0 = n0;
             }
             if (!dead && !mbar_wait(&acc_full[buf], ((uint32_t)it >> 1) & 1u)) { atomicExch(&g_tc_status, 3); dead = true; }
@@ -671,8 +672,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 cls = mvalid ? a.ycls[ky0 * 16 + ky1] * a.ncx + a.xcls[kx0 * 16 + kx1] : 0;
             }
             const int32_t* corr_row = s_cc + cls * BN;
-            const uint32_t a_M = smem_u32(s_M), a_m = smem_u32(s_m), a_b = smem_u32(s_bterm);
-            const uint32_t a_cc = smem_u32(corr_row), a_Bc = smem_u32(s_Bc + cls * BN);
+            const uint32_t a_m = smem_u32(s_m), a_b = smem_u32(s_bterm), a_cc = smem_u32(corr_row);
             const uint32_t tacc = tmem_base + (uint32_t)(buf * BN) + ((uint32_t)(quad * 32) << 16);
             #pragma unroll 1
             for (int us = 0; us < UNITS; ++us) {
@@ -683,32 +683,35 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 for (int k = 0; k < CPW; ++k) tc_ld16_issue(tacc + (uint32_t)(colw + k * 16), r[k]);
                 #pragma unroll
                 for (int k = 0; k < CPW; ++k) tc_ld16_wait(r[k]);
+                if (fused && !dead && !mbar_wait(&io_full[ub], uph)) { atomicExch(&g_tc_status, 5); dead = true; }
+                #pragma unroll
+                for (int k = 0; k < CPW; ++k) {
+                    const int col0 = colw + k * 16;
+                    const uint32_t slot = smem_u32(io_row) + ((((uint32_t)(part * CPW + k)) ^ sw_x) << 4);
+                    if (dump_acc && mvalid) {                      // raw accumulators for the bit-exactness tests
+                        for (int j = 0; j < 16; ++j) a.acc_out[m * a.OC + n0 + col0 + j] = (int)r[k][j] - corr_row[col0 + j];
+                    }
+                    const EpiAddr ad = {a_m + col0 * 4, a_b + col0 * 4, a_cc + col0 * 4};
+                    const uint4 rv = fused ? lds128(slot) : make_uint4(0, 0, 0, 0);
+                    float dmax = always_fix ? 1.0f : 0.0f;
+                    const uint4 outv = use_lut ? epi_chunk<true>(r[k], rv, ad, ec, dmax) : epi_chunk<false>(r[k], rv, ad, ec, dmax);
+                    sts128(slot, outv);
+                    // an exact half (the reference rounds it away from zero), a value beyond the rounding constant, or
+                    // no table: the whole warp redoes this chunk with the reference arithmetic
+                    if (__any_sync(0xffffffffu, dmax >= 0.5f)) epi_fixup(tacc + (uint32_t)col0, slot, rv, ad.m, ad.b, ad.cc, ex);
+                }
                 if (us == UNITS - 1) {
                     // this warp has finished reading the accumulator buffer
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&acc_empty[buf]);
                 }
-                if (a.res && !dead && !mbar_wait(&io_full[ub], uph)) { atomicExch(&g_tc_status, 5); dead = true; }
-                #pragma unroll
-                for (int k = 0; k < CPW; ++k) {
-                    const int col0 = colw + k * 16;
-                    const uint32_t slot = smem_u32(io_row) + ((((uint32_t)(part * CPW + k)) ^ sw_x) << 4);
-                    if (a.acc_out && mvalid) {                     // raw accumulators for the bit-exactness tests
-                        for (int j = 0; j < 16; ++j) a.acc_out[m * a.OC + n0 + col0 + j] = (int)r[k][j] - corr_row[col0 + j];
-                    }
-                    const EpiAddr ad = {a_M + col0 * 4, a_Bc + col0 * 4, a_m + col0 * 4, a_b + col0 * 4, a_cc + col0 * 4};
-                    uint4 outv;
-                    if (a.res) outv = epi_chunk<true>(r[k], lds128(slot), ad, ec);
-                    else       outv = epi_chunk<false>(r[k], make_uint4(0, 0, 0, 0), ad, ec);
-                    sts128(slot, outv);
-                }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the TMA store
                 if (leader) {
                     // every earlier store of this quadrant has been read out of shared memory: the buffer of the
                     // previous unit is free for the producer, and the next unit's buffer for the epilogue
                     asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-                    if (a.res && !first_unit) mbar_arrive(&io_empty[prev_ub]);
+                    if (fused && !first_unit) mbar_arrive(&io_empty[prev_ub]);
                 }
                 quad_barrier(quad);
                 if (leader) {
@@ -830,6 +833,61 @@ __global__ void __launch_bounds__(256) row_input_pack_kernel(const RowInputArgs 
     else           *(uint4*)(a.xp + i * 16) = *(const uint4*)v;
 }
 
+// ---- fused-add table ---------------------------------------------------------------------------------------------
+
+struct AddLutArgs { uint8_t* lut; int y_u8, res_u8; float sy; int zy; float sr; int zr; Requant out; uint32_t tag[TC_LUT_TAG_WORDS]; };
+
+// lut[(conv value - type minimum) << 8 | other operand's byte] = output byte of RefElementwiseBinaryWorkload(Add)
+// followed by the fused activation, evaluated once per pair of 8-bit values with the reference fp32 arithmetic.  The
+// tag behind the table names the quantisation parameters it was built for.
+__global__ void add_lut_kernel(const AddLutArgs a)
+{
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;       // 65536 threads
+    const int b1 = i >> 8, b2 = i & 255;
+    const int q1 = a.y_u8 ? b1 : b1 - 128;
+    const int q2 = a.res_u8 ? b2 : (int)(int8_t)b2;
+    const float fa = __fmul_rn(__int2float_rn(q1 - a.zy), a.sy);
+    const float fb = __fmul_rn(__int2float_rn(q2 - a.zr), a.sr);
+    const int q = quantize_dev(__fadd_rn(fa, fb), a.out.sy, a.out.zy, a.out.tlo, a.out.thi);
+    a.lut[i] = (uint8_t)min(max(q, a.out.clo), a.out.chi);
+    if (i < TC_LUT_TAG_WORDS) ((uint32_t*)(a.lut + 65536))[i] = a.tag[i];
+}
+
+static size_t add_lut_offset(int oc, int kh, int kw, int c)
+{
+    size_t n = (size_t)(kh + 1) * (kw + 1) * oc * sizeof(int32_t);
+    if (c <= 16) n += (size_t)oc * kh * 128;
+    return (n + 255) & ~(size_t)255;
+}
+
+static uint32_t f32_bits(float f) { uint32_t u; memcpy(&u, &f, 4); return u; }
+
+// what identifies a fused-add table: both operands' and the output's quantisation, and the activation clamp
+static void make_lut_tag(const b200k_conv2d_params* p, uint32_t* tag)
+{
+    const Requant out = make_requant(0.f, p->add_out, p->clamp_lo, p->clamp_hi);
+    tag[0] = 0x4C555431u;
+    tag[1] = f32_bits(p->y.scale);           tag[2] = (uint32_t)p->y.zero_point;           tag[3] = (uint32_t)p->y.dtype;
+    tag[4] = f32_bits(p->add_operand.scale); tag[5] = (uint32_t)p->add_operand.zero_point; tag[6] = (uint32_t)p->add_operand.dtype;
+    tag[7] = f32_bits(p->add_out.scale);     tag[8] = (uint32_t)p->add_out.zero_point;     tag[9] = (uint32_t)p->add_out.dtype;
+    tag[10] = (uint32_t)out.clo;             tag[11] = (uint32_t)out.chi;
+}
+
+// RN(1 / b): the double quotient rounded to float is within one ulp; the exact residuals 1 - b * y (products of two
+// 24-bit significands are exact in double) pick the nearest of the three candidates.
+static float rn_reciprocal(float b)
+{
+    const float y = (float)(1.0 / (double)b);
+    const float cand[3] = {nextafterf(y, 0.f), y, nextafterf(y, INFINITY)};
+    float best = y;
+    double err = 1e300;
+    for (int i = 0; i < 3; ++i) {
+        const double e = fabs(1.0 - (double)b * (double)cand[i]);
+        if (e < err) { err = e; best = cand[i]; }
+    }
+    return best;
+}
+
 // ---- host side ---------------------------------------------------------------------------------------------------
 
 static PFN_cuTensorMapEncodeTiled_v12000 g_encode_tiled = nullptr;
@@ -929,7 +987,7 @@ bool conv_tc_eligible(const b200k_conv2d_params* p)
     }
     if (p->x.zero_point != 0) {
         const TapClasses tc = tap_classes(p);
-        if (!tc.ok || (size_t)tc.ncy * tc.ncx * pick_bn(p->oc) * 8 > 40 * 1024) return false;
+        if (!tc.ok || (size_t)tc.ncy * tc.ncx * pick_bn(p->oc) * 4 > 32 * 1024) return false;
     }
     return true;
 }
@@ -951,7 +1009,7 @@ static int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUten
 {
     using L = TcSmem<BN, SWZ>;
     const size_t budget = 227 * 1024;                                   // opt-in shared memory per CTA on sm_100
-    const size_t rest = 1024 + L::CONST_BYTES + (size_t)a.ncls * BN * 8 + (size_t)a.nio * L::IO_BYTES;
+    const size_t rest = 1024 + L::CONST_BYTES + (size_t)a.ncls * BN * 4 + (size_t)a.nio * L::IO_BYTES + (a.add_lut ? 65536 : 0);
     B200K_REQUIRE(rest + 2 * L::STAGE_BYTES <= budget, B200K_E_TOOBIG, "conv2d_q8: shared memory exhausted (%zu bytes of tables)", rest);
     int stages = (int)((budget - rest) / L::STAGE_BYTES);
     if (stages > L::MAX_STAGES) stages = L::MAX_STAGES;
@@ -1007,15 +1065,12 @@ int launch_conv_tc(const b200k_conv2d_params* p, cudaStream_t stream)
     B200K_REQUIRE(make_fused_add(p, a.rq, fa, a.y), B200K_E_INVALID, "conv2d_q8: malformed fused add operand / output");
     a.res = fa.res; a.res_scale = fa.res_scale; a.res_zp = fa.res_zp; a.res_u8 = fa.res_u8;
     a.rq2 = fa.out;
-    a.add_a1 = a.add_a2 = a.add_c0 = a.add_eps = 0.f;
-    if (fa.res) {
-        // estimate of the fused Add (see epi_chunk); absurd scale ratios switch it off (every value exact)
-        const double r1 = (double)p->y.scale / (double)p->add_out.scale, r2 = (double)fa.res_scale / (double)p->add_out.scale;
-        a.add_a1 = (float)r1; a.add_a2 = (float)r2;
-        a.add_c0 = (float)((double)p->add_out.zero_point - (double)p->y.zero_point * r1 - (double)fa.res_zp * r2);
-        const double eps = ldexp(255.0 * (9.0 * (r1 + r2) + 3.0), -23);
-        a.add_eps = eps < 0.03125 ? (float)eps : INFINITY;
-    }
+    a.inv_sy = rn_reciprocal(p->y.scale);
+    // b200k_conv2d_pack builds the fused-add table when it is given the add operand; the kernel checks its tag and
+    // falls back to the reference arithmetic (slow) when the table was made for other parameters
+    a.add_lut = (fa.res && p->packed) ? (const uint8_t*)p->packed + add_lut_offset(p->oc, p->kh, p->kw, p->c) : nullptr;
+    memset(a.lut_tag, 0, sizeof(a.lut_tag));
+    if (fa.res) make_lut_tag(p, a.lut_tag);
     a.nio = fa.res ? 3 : 2;
     a.ncy = a.ncx = a.ncls = 1;
     memset(a.ypair, 0, sizeof(a.ypair)); memset(a.xpair, 0, sizeof(a.xpair));
@@ -1137,10 +1192,8 @@ using namespace b200k;
 extern "C" size_t b200k_conv2d_pack_bytes(int32_t oc, int32_t kh, int32_t kw, int32_t c)
 {
     if (oc <= 0 || kh <= 0 || kw <= 0) return 0;
-    // prefix table, then the row-window weights of few-channel convolutions (widest window)
-    size_t n = (size_t)(kh + 1) * (kw + 1) * oc * sizeof(int32_t);
-    if (c <= 16) n += (size_t)oc * kh * 128;
-    return (n + 255) & ~(size_t)255;
+    // prefix table, row-window weights of few-channel convolutions (widest window), fused-add table and its tag
+    return add_lut_offset(oc, kh, kw, c) + 65536 + 64;
 }
 
 extern "C" size_t b200k_conv2d_scratch_bytes(const b200k_conv2d_params* p)
@@ -1161,6 +1214,21 @@ extern "C" int b200k_conv2d_pack(const b200k_conv2d_params* p, void* packed, voi
     conv_prefix_kernel<<<div_up(p->oc, 128), 128, 0, (cudaStream_t)stream>>>(a);
     int rc = check_launch("conv_prefix_kernel");
     if (rc) return rc;
+    uint8_t* lut = (uint8_t*)packed + add_lut_offset(p->oc, p->kh, p->kw, p->c);
+    if (p->add_operand.data && is_q8(p->add_operand.dtype) && is_q8(p->add_out.dtype) && is_q8(p->y.dtype)) {
+        // table of the fused Add for exactly these quantisation parameters and this clamp
+        AddLutArgs la;
+        la.lut = lut;
+        la.y_u8 = p->y.dtype == B200K_U8; la.res_u8 = p->add_operand.dtype == B200K_U8;
+        la.sy = p->y.scale; la.zy = p->y.zero_point; la.sr = p->add_operand.scale; la.zr = p->add_operand.zero_point;
+        la.out = make_requant(0.f, p->add_out, p->clamp_lo, p->clamp_hi);
+        make_lut_tag(p, la.tag);
+        add_lut_kernel<<<256, 256, 0, (cudaStream_t)stream>>>(la);
+        rc = check_launch("add_lut_kernel");
+        if (rc) return rc;
+    } else {
+        B200K_CUDA(cudaMemsetAsync(lut + 65536, 0, 64, (cudaStream_t)stream));      // no table: no tag
+    }
     if (p->c > 16) return rc;
     // weights of a few-channel convolution, re-packed for the row-window mode (needs kw, c and stride_w)
     b200k_conv2d_params q = *p;
