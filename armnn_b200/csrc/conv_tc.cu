@@ -43,6 +43,12 @@ namespace b200k {
 constexpr int TC_BM = 128;
 constexpr int TC_EPI_WARPS = 16;
 constexpr int TC_LUT_TAG_WORDS = 12;
+// Fused-add table: 256 rows (convolution value) of 256 entries (other operand's byte), rows 260 bytes apart so that
+// the shared-memory bank of an entry depends on both indices: the other operand of a residual block is full of
+// repeated values (half of a ReLU output is the zero point), and with a 256-byte pitch lanes that share it would all
+// hit one bank.
+constexpr int TC_LUT_PITCH = 260;
+constexpr int TC_LUT_BYTES = 256 * TC_LUT_PITCH;
 constexpr int TC_THREADS = 64 + 32 * TC_EPI_WARPS;   // warp 0 producer, warp 1 MMA issuer, then the epilogue warps
 constexpr unsigned TC_WAIT_HINT_NS = 20000;              // one suspended try_wait lasts at most this long
 constexpr long long TC_WAIT_LIMIT_CYCLES = 4000000000ll;  // about two seconds: no wait of a healthy launch comes near
@@ -102,7 +108,7 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes)
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity)
 {
     const uint32_t addr = smem_u32(bar);
-    const long long t0 = clock64();
+    long long t0 = 0;
     for (;;) {
         #pragma unroll 1
         for (int i = 0; i < 32; ++i) {
@@ -113,7 +119,9 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity)
                          : "=r"(ok) : "r"(addr), "r"(parity), "r"(TC_WAIT_HINT_NS) : "memory");
             if (ok) return true;
         }
-        if (clock64() - t0 > TC_WAIT_LIMIT_CYCLES) return false;
+        const long long now = clock64();
+        if (t0 == 0) t0 = now;
+        else if (now - t0 > TC_WAIT_LIMIT_CYCLES) return false;
     }
 }
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y)
@@ -316,7 +324,7 @@ __device__ __forceinline__ uint32_t lds_u8(uint32_t addr)
 struct EpiConsts {
     f32x2 inv2, nsy2, magic2, zy2, zero2;        // pairs of: RN(1 / sy), -sy, the rounding constant, zero point (+ bias), 0
     float lo, hi;                                // clamp bounds in the biased domain (MAGIC + ...)
-    uint32_t lut;                                // shared address of the fused-add table minus 0x4B400000
+    uint32_t lut;                                // shared address of the fused-add table minus 0x4B400000 * pitch
 };
 
 // shared-memory addresses of the per-channel tables at the chunk's first column
@@ -365,8 +373,9 @@ __device__ __forceinline__ uint4 epi_chunk(const uint32_t* r, const uint4 rv, co
             // clamp in the biased domain: the low byte of the bit pattern is the output byte
             bits[e] = __float_as_uint(fminf(fmaxf(z[e], ec.lo), ec.hi));
             if (FUSED) {
-                // bits = 0x4B4000qq with qq = conv output - type minimum: (qq << 8 | other byte) indexes the table
-                bits[e] = lds_u8(__byte_perm(bits[e], resw[g], 0x3204 + e) + ec.lut);
+                // bits = 0x4B4000qq with qq = conv output - type minimum: entry qq * pitch + other byte; ec.lut holds the
+                // table's address minus 0x4B400000 * pitch, a multiple of 256, and the byte goes into its low 8 bits
+                bits[e] = lds_u8(bits[e] * (uint32_t)TC_LUT_PITCH + __byte_perm(resw[g], ec.lut, 0x7650 + e));
             }
         }
         packed[g] = __byte_perm(__byte_perm(bits[0], bits[1], 0x0040), __byte_perm(bits[2], bits[3], 0x0040), 0x5410);
@@ -457,7 +466,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     uint32_t* tmem_slot = (uint32_t*)(io_empty + L::MAX_IO);
     uint32_t* s_lut_ok = tmem_slot + 1;                     // the fused-add table in global memory carries our tag
     int32_t* s_cc = (int32_t*)(tmem_slot + 4);              // [classes][BN] zero-point corrections
-    uint8_t* s_lut = (uint8_t*)(s_cc + a.ncls * BN);        // [256][256] fused-add table
+    uint8_t* s_lut = (uint8_t*)(((uintptr_t)(s_cc + a.ncls * BN) + 255) & ~(uintptr_t)255);   // fused-add table, 256-byte aligned
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int ntn = a.OC / BN;                              // n-tiles (OC is a multiple of BN)
@@ -471,7 +480,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         // a table is used only if it was built for exactly this launch's quantisation parameters
         uint32_t ok = a.add_lut != nullptr;
         if (ok) {
-            const uint32_t* tag = (const uint32_t*)(a.add_lut + 65536);
+            const uint32_t* tag = (const uint32_t*)(a.add_lut + TC_LUT_BYTES);
             for (int i = 0; i < TC_LUT_TAG_WORDS; ++i) ok &= (tag[i] == a.lut_tag[i]);
         }
         *s_lut_ok = ok;
@@ -489,7 +498,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (lut_ok) {
             const uint4* src = (const uint4*)a.add_lut;
             uint4* dst = (uint4*)s_lut;
-            for (int i = threadIdx.x; i < 65536 / 16; i += TC_THREADS) dst[i] = src[i];
+            for (int i = threadIdx.x; i < TC_LUT_BYTES / 16; i += TC_THREADS) dst[i] = src[i];
         }
         __syncthreads();
     }
@@ -616,7 +625,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         ec.zy2 = pack2(zb, zb);
         ec.lo = use_lut ? TC_MAGIC : TC_MAGIC + ex.lo1;
         ec.hi = use_lut ? TC_MAGIC + 255.0f : TC_MAGIC + ex.hi1;
-        ec.lut = smem_u32(s_lut) - 0x4B400000u;
+        ec.lut = smem_u32(s_lut) - 0x4B400000u * (uint32_t)TC_LUT_PITCH;
         int cur_n0 = -1;
         int it = 0;
         int ub = 0, prev_ub = 0; uint32_t uph = 0;           // unit-buffer position (kept without divisions)
@@ -837,7 +846,7 @@ __global__ void __launch_bounds__(256) row_input_pack_kernel(const RowInputArgs 
 
 struct AddLutArgs { uint8_t* lut; int y_u8, res_u8; float sy; int zy; float sr; int zr; Requant out; uint32_t tag[TC_LUT_TAG_WORDS]; };
 
-// lut[(conv value - type minimum) << 8 | other operand's byte] = output byte of RefElementwiseBinaryWorkload(Add)
+// lut[(conv value - type minimum) * pitch + other operand's byte] = output byte of RefElementwiseBinaryWorkload(Add)
 // followed by the fused activation, evaluated once per pair of 8-bit values with the reference fp32 arithmetic.  The
 // tag behind the table names the quantisation parameters it was built for.
 __global__ void add_lut_kernel(const AddLutArgs a)
@@ -849,8 +858,8 @@ __global__ void add_lut_kernel(const AddLutArgs a)
     const float fa = __fmul_rn(__int2float_rn(q1 - a.zy), a.sy);
     const float fb = __fmul_rn(__int2float_rn(q2 - a.zr), a.sr);
     const int q = quantize_dev(__fadd_rn(fa, fb), a.out.sy, a.out.zy, a.out.tlo, a.out.thi);
-    a.lut[i] = (uint8_t)min(max(q, a.out.clo), a.out.chi);
-    if (i < TC_LUT_TAG_WORDS) ((uint32_t*)(a.lut + 65536))[i] = a.tag[i];
+    a.lut[b1 * TC_LUT_PITCH + b2] = (uint8_t)min(max(q, a.out.clo), a.out.chi);
+    if (i < TC_LUT_TAG_WORDS) ((uint32_t*)(a.lut + TC_LUT_BYTES))[i] = a.tag[i];
 }
 
 static size_t add_lut_offset(int oc, int kh, int kw, int c)
@@ -1009,7 +1018,7 @@ static int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUten
 {
     using L = TcSmem<BN, SWZ>;
     const size_t budget = 227 * 1024;                                   // opt-in shared memory per CTA on sm_100
-    const size_t rest = 1024 + L::CONST_BYTES + (size_t)a.ncls * BN * 4 + (size_t)a.nio * L::IO_BYTES + (a.add_lut ? 65536 : 0);
+    const size_t rest = 1024 + L::CONST_BYTES + (size_t)a.ncls * BN * 4 + (size_t)a.nio * L::IO_BYTES + (a.add_lut ? TC_LUT_BYTES + 256 : 0);
     B200K_REQUIRE(rest + 2 * L::STAGE_BYTES <= budget, B200K_E_TOOBIG, "conv2d_q8: shared memory exhausted (%zu bytes of tables)", rest);
     int stages = (int)((budget - rest) / L::STAGE_BYTES);
     if (stages > L::MAX_STAGES) stages = L::MAX_STAGES;
@@ -1193,7 +1202,7 @@ extern "C" size_t b200k_conv2d_pack_bytes(int32_t oc, int32_t kh, int32_t kw, in
 {
     if (oc <= 0 || kh <= 0 || kw <= 0) return 0;
     // prefix table, row-window weights of few-channel convolutions (widest window), fused-add table and its tag
-    return add_lut_offset(oc, kh, kw, c) + 65536 + 64;
+    return add_lut_offset(oc, kh, kw, c) + TC_LUT_BYTES + 64;
 }
 
 extern "C" size_t b200k_conv2d_scratch_bytes(const b200k_conv2d_params* p)
@@ -1227,7 +1236,7 @@ extern "C" int b200k_conv2d_pack(const b200k_conv2d_params* p, void* packed, voi
         rc = check_launch("add_lut_kernel");
         if (rc) return rc;
     } else {
-        B200K_CUDA(cudaMemsetAsync(lut + 65536, 0, 64, (cudaStream_t)stream));      // no table: no tag
+        B200K_CUDA(cudaMemsetAsync(lut + TC_LUT_BYTES, 0, 64, (cudaStream_t)stream));      // no table: no tag
     }
     if (p->c > 16) return rc;
     // weights of a few-channel convolution, re-packed for the row-window mode (needs kw, c and stride_w)
