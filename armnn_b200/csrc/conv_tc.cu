@@ -81,6 +81,7 @@ struct TcArgs {
     const uint8_t* add_lut;                     // fused-add table built by b200k_conv2d_pack (+ its tag), or null
     uint32_t lut_tag[TC_LUT_TAG_WORDS];         // the tag a table made for exactly this launch carries
     int stages;                                 // ring depth chosen by the launcher (<= 8)
+    int bstat;                                  // weights stay in shared memory for the whole launch (one n-tile, small K)
     int nio;                                    // unit buffers of the output path: 2, or 3 with a fused Add
     // zero-point correction classes: pixels whose in-image tap rectangle [ky0, ky1) x [kx0, kx1) is the same share
     // one row of per-channel corrections.  ypair / xpair list the distinct (k0 << 4 | k1) of the geometry, ycls / xcls
@@ -412,9 +413,9 @@ struct TcSmem {
     static constexpr int IO_BYTES = TC_BM * UW;             // one unit buffer: [128 rows][UW], TMA-swizzled
     static constexpr int MAX_IO = 3;
     // after the ring (stages x STAGE_BYTES) and the unit buffers (nio x IO_BYTES): per-channel m, bterm [BN each],
-    // barriers (full[8], empty[8], acc_full[2], acc_empty[2], io_full[3], io_empty[3]), tmem slot + eps slot; then the
+    // barriers (full[8], empty[8], acc_full[2], acc_empty[2], io_full[3], io_empty[3], w_full), tmem slot + eps slot; then the
     // zero-point correction table [classes][BN], then the fused-add table (dynamic sizes)
-    static constexpr int CONST_BYTES = 2 * BN * 4 + (2 * MAX_STAGES + 4 + 2 * MAX_IO) * 8 + 16;
+    static constexpr int CONST_BYTES = 2 * BN * 4 + (2 * MAX_STAGES + 4 + 2 * MAX_IO + 2) * 8 + 16;
 };
 
 __device__ __forceinline__ void epi_barrier()       // the epilogue warps only (named barrier 1)
@@ -454,7 +455,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int NIO = a.nio;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint8_t* s_io = smem + (size_t)STAGES * L::STAGE_BYTES;
+    // weight-stationary launches: all K-slices of the (only) weight tile first, then a ring of activation tiles only
+    const int stage_stride = a.bstat ? L::A_BYTES : L::STAGE_BYTES;
+    uint8_t* ring = smem + (a.bstat ? (size_t)a.nslices * L::B_BYTES : 0);
+    uint8_t* s_io = ring + (size_t)STAGES * stage_stride;
     float* s_m = (float*)(s_io + (size_t)NIO * IO_BYTES);
     float* s_bterm = s_m + BN;
     uint64_t* full = (uint64_t*)(s_bterm + BN);
@@ -463,7 +467,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     uint64_t* acc_empty = acc_full + 2;                     // [2]
     uint64_t* io_full = acc_empty + 2;                      // [3] other operand's unit has landed
     uint64_t* io_empty = io_full + L::MAX_IO;               // [3] the unit buffer's last store has been read out
-    uint32_t* tmem_slot = (uint32_t*)(io_empty + L::MAX_IO);
+    uint64_t* w_full = io_empty + L::MAX_IO;                // the stationary weight tile has landed
+    uint32_t* tmem_slot = (uint32_t*)(w_full + 2);
     uint32_t* s_lut_ok = tmem_slot + 1;                     // the fused-add table in global memory carries our tag
     int32_t* s_cc = (int32_t*)(tmem_slot + 4);              // [classes][BN] zero-point corrections
     uint8_t* s_lut = (uint8_t*)(((uintptr_t)(s_cc + a.ncls * BN) + 255) & ~(uintptr_t)255);   // fused-add table, 256-byte aligned
@@ -476,6 +481,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], TC_EPI_WARPS); }
         for (int b = 0; b < L::MAX_IO; ++b) { mbar_init(&io_full[b], 1); mbar_init(&io_empty[b], 4); }
+        mbar_init(w_full, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         // a table is used only if it was built for exactly this launch's quantisation parameters
         uint32_t ok = a.add_lut != nullptr;
@@ -509,6 +515,13 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             int st = 0; uint32_t ph = 0;                     // ring position: stage and its phase bit
             int ub = 0; uint32_t uph = 0;                    // unit-buffer position (kept without divisions)
             bool alive = true;
+            if (a.bstat && a.debug != 2) {
+                mbar_expect_tx(w_full, (uint32_t)a.nslices * L::B_BYTES);
+                for (int s = 0; s < a.nslices; ++s) {
+                    const int tap = s / a.cchunks;
+                    tma_load_2d(smem + (size_t)s * L::B_BYTES, &tmB, w_full, tap * a.kstride + (s - tap * a.cchunks) * SWZ, 0);
+                }
+            }
             for (int t = blockIdx.x; t < ntiles && alive; t += gridDim.x) {
                 const int n0 = (t % ntn) * BN;
                 const int tm = t / ntn;
@@ -529,7 +542,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 for (int s = 0; s < a.nslices; ++s) {
                     if (!mbar_wait(&empty[st], ph ^ 1u)) { atomicExch(&g_tc_status, 1); alive = false; break; }
                     const int c0 = cc * SWZ;
-                    uint8_t* sa = smem + st * L::STAGE_BYTES;
+                    uint8_t* sa = ring + st * stage_stride;
                     uint8_t* sb = sa + L::A_BYTES;
                     const int cur = st, cur_tap = tap;
                     if (++st == STAGES) { st = 0; ph ^= 1u; }
@@ -544,7 +557,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     } else {
                         tma_load_2d(sa, &tmA, &full[cur], c0, (int)m0);
                     }
-                    tma_load_2d(sb, &tmB, &full[cur], cur_tap * a.kstride + c0, n0);
+                    if (!a.bstat) tma_load_2d(sb, &tmB, &full[cur], cur_tap * a.kstride + c0, n0);
                 }
                 if (a.res && alive) {
                     // the fused Add's other operand, one unit at a time, into the buffer the epilogue will overwrite
@@ -568,6 +581,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             int st = 0; uint32_t ph = 0;                     // ring position
             bool alive = true;
             int it = 0;
+            if (a.bstat && a.debug != 2 && !mbar_wait(w_full, 0)) { atomicExch(&g_tc_status, 7); alive = false; }
+            tc_fence_after();
             for (int t = blockIdx.x; t < ntiles && alive; t += gridDim.x, ++it) {
                 const int buf = it & 1;
                 // the epilogue must have drained this accumulator buffer (two tiles ago)
@@ -580,9 +595,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     const int cur = st;
                     if (++st == STAGES) { st = 0; ph ^= 1u; }
                     if (a.debug == 1) { mbar_arrive(&empty[cur]); continue; }
-                    const uint32_t sa = smem_u32(smem + cur * L::STAGE_BYTES);
+                    const uint32_t sa = smem_u32(ring + cur * stage_stride);
                     const uint64_t da = make_smem_desc<SWZ>(sa);
-                    const uint64_t db = make_smem_desc<SWZ>(sa + L::A_BYTES);
+                    const uint64_t db = make_smem_desc<SWZ>(a.bstat ? smem_u32(smem + (size_t)s * L::B_BYTES) : sa + L::A_BYTES);
                     #pragma unroll
                     for (int k = 0; k < SWZ / 32; ++k)
                         tc_mma_i8(tacc, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), id, (s > 0 || k > 0) ? 1u : 0u);
@@ -1020,11 +1035,18 @@ static int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUten
     const size_t budget = 227 * 1024;                                   // opt-in shared memory per CTA on sm_100
     const size_t rest = 1024 + L::CONST_BYTES + (size_t)a.ncls * BN * 4 + (size_t)a.nio * L::IO_BYTES + (a.add_lut ? TC_LUT_BYTES + 256 : 0);
     B200K_REQUIRE(rest + 2 * L::STAGE_BYTES <= budget, B200K_E_TOOBIG, "conv2d_q8: shared memory exhausted (%zu bytes of tables)", rest);
-    int stages = (int)((budget - rest) / L::STAGE_BYTES);
-    if (stages > L::MAX_STAGES) stages = L::MAX_STAGES;
     TcArgs a2 = a;
+    // One n-tile and a weight tile of at most 64 KiB over all of K: keep it in shared memory for the whole launch, so
+    // that the ring (and the L2 bandwidth behind it) carries activations only.
+    const size_t wbytes = (size_t)a.nslices * L::B_BYTES;
+    a2.bstat = (a.OC == BN && wbytes <= 64 * 1024 && rest + wbytes + 4 * L::A_BYTES <= budget) ? 1 : 0;
+    const size_t stride = a2.bstat ? L::A_BYTES : L::STAGE_BYTES;
+    const size_t fixed = rest + (a2.bstat ? wbytes : 0);
+    int stages = (int)((budget - fixed) / stride);
+    if (stages > L::MAX_STAGES) stages = L::MAX_STAGES;
     a2.stages = stages;
-    const size_t smem = rest + (size_t)stages * L::STAGE_BYTES;
+    if (a2.bstat) a2.stage_tx = (uint32_t)(a.stage_tx - L::B_BYTES);
+    const size_t smem = fixed + (size_t)stages * stride;
     auto kern = conv_tc_kernel<BN, SWZ>;
     static size_t configured = 0;                      // per instantiation: largest dynamic smem size set so far
     if (smem > configured) {
@@ -1264,7 +1286,8 @@ extern "C" int b200k_poll_status(void)
     if (s != 0) {
         int zero = 0;
         cudaMemcpyToSymbol(g_tc_status, &zero, sizeof(int));
-        set_error("a bounded device-side wait gave up (code %d: 1 producer, 2 MMA issuer, 3 epilogue)", s);
+        set_error("a bounded device-side wait gave up (code %d: 1 producer/ring, 2 MMA issuer/ring, 3 epilogue/accumulator, "
+                  "4 MMA issuer/accumulator buffer, 5 epilogue/add operand, 6 producer/unit buffer, 7 MMA issuer/weights)", s);
         return B200K_E_TIMEOUT;
     }
     return B200K_OK;
