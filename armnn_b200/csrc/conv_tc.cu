@@ -82,7 +82,7 @@ struct TcArgs {
     uint32_t lut_tag[TC_LUT_TAG_WORDS];         // the tag a table made for exactly this launch carries
     int stages;                                 // ring depth chosen by the launcher (<= 8)
     int bstat;                                  // weights stay in shared memory for the whole launch (one n-tile, small K)
-    int nio;                                    // unit buffers of the output path: 2, or 3 with a fused Add
+    int nio;                                    // shared buffers for units of the fused Add's other operand: 0 or 2
     // zero-point correction classes: pixels whose in-image tap rectangle [ky0, ky1) x [kx0, kx1) is the same share
     // one row of per-channel corrections.  ypair / xpair list the distinct (k0 << 4 | k1) of the geometry, ycls / xcls
     // map such a code back to its position in the list.
@@ -187,10 +187,10 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, u
     asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
                  ::"r"(smem_u32(dst)), "l"((uint64_t)map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2) : "memory");
 }
-__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, const void* src, int c0, int c1, int c2)
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src_saddr, int c0, int c1, int c2)
 {
     asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
-                 ::"l"((uint64_t)map), "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2) : "memory");
+                 ::"l"((uint64_t)map), "r"(src_saddr), "r"(c0), "r"(c1), "r"(c2) : "memory");
 }
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t* r)
 {
@@ -384,13 +384,21 @@ __device__ __forceinline__ uint4 epi_chunk(const uint32_t* r, const uint4 rv, co
     return make_uint4(packed[0], packed[1], packed[2], packed[3]);
 }
 
-// The fix-up pass of one chunk: re-reads the 16 accumulators from tensor memory and evaluates them with the reference
-// arithmetic.  Out of line; a warp calls it as a whole.
-__device__ __noinline__ void epi_fixup(uint32_t taddr, uint32_t slot, uint4 rv, uint32_t a_m, uint32_t a_b, uint32_t a_cc,
-                                       const EpiExact& x)
+// The cold pass of one chunk, out of line and outside the hot loop; a warp calls it as a whole.  It re-reads the 16
+// accumulators from tensor memory and (fix) evaluates them with the reference arithmetic (other operand's bytes at
+// res_slot, result to out_slot) and / or (acc_row) writes the raw accumulators of a valid row out for the bit-exactness
+// tests.
+__device__ __noinline__ void epi_cold(uint32_t taddr, uint32_t res_slot, uint32_t out_slot, uint32_t a_m, uint32_t a_b,
+                                      uint32_t a_cc, const EpiExact& x, bool fix, int32_t* acc_row)
 {
     uint32_t r[16];
     tc_ld16(taddr, r);
+    if (acc_row) {
+        #pragma unroll
+        for (int j = 0; j < 16; ++j) acc_row[j] = (int)r[j] - lds_s32(a_cc + j * 4);
+    }
+    if (!fix) return;
+    const uint4 rv = x.fused ? lds128(res_slot) : make_uint4(0, 0, 0, 0);
     const uint32_t resw[4] = {rv.x, rv.y, rv.z, rv.w};
     uint32_t out[4] = {0, 0, 0, 0};
     #pragma unroll
@@ -399,7 +407,7 @@ __device__ __noinline__ void epi_fixup(uint32_t taddr, uint32_t slot, uint4 rv, 
                                   (resw[j >> 2] >> (8 * (j & 3))) & 0xffu, x);
         out[j >> 2] |= ((uint32_t)q & 0xffu) << (8 * (j & 3));
     }
-    sts128(slot, make_uint4(out[0], out[1], out[2], out[3]));
+    sts128(out_slot, make_uint4(out[0], out[1], out[2], out[3]));
 }
 
 template <int BN, int SWZ>
@@ -422,10 +430,6 @@ __device__ __forceinline__ void epi_barrier()       // the epilogue warps only (
 {
     asm volatile("bar.sync 1, %0;" ::"n"(32 * TC_EPI_WARPS) : "memory");
 }
-__device__ __forceinline__ void quad_barrier(int quad)   // the four epilogue warps that share a TMEM lane quadrant
-{
-    asm volatile("bar.sync %0, 128;" ::"r"(2 + quad) : "memory");
-}
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar)
 {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -436,12 +440,12 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar)
 // accumulator is double-buffered in tensor memory, so the TMA producer, the MMA issuer and the epilogue warps of
 // consecutive tiles overlap.
 //
-// Output path.  A tile leaves in units of 128 rows x UW (<= 128) columns.  The epilogue warps write a unit's bytes
-// into a shared-memory buffer laid out as the TMA swizzle expects (conflict-free 16-byte stores, one row per lane);
-// the four warps of a lane quadrant meet at a named barrier and one thread sends the quadrant's 32 rows with a TMA
-// store, which clips rows beyond the tensor.  With a fused Add the producer has TMA-loaded the other operand's unit
-// into the same buffer beforehand, and each thread overwrites the 16 bytes it has just consumed.  Buffers rotate
-// (2 without, 3 with a fused Add): before a buffer is re-used its last store has been waited for by the issuing thread.
+// Output path.  A tile leaves in units of 128 rows x UW (<= 128) columns; each epilogue warp owns 32 rows x UW / 4
+// columns of a unit.  It writes its bytes into a private shared-memory buffer laid out as the TMA swizzle expects
+// (conflict-free 16-byte stores, one row per lane) and one of its lanes sends the buffer with a TMA store, which clips
+// rows beyond the tensor; before the buffer is written again that lane has waited for the store to have read it.  No
+// epilogue warp waits for another one.  With a fused Add the producer TMA-loads the other operand's unit into one of
+// two shared buffers; every epilogue warp releases it after reading its part.
 template <int BN, int SWZ>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -459,7 +463,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int stage_stride = a.bstat ? L::A_BYTES : L::STAGE_BYTES;
     uint8_t* ring = smem + (a.bstat ? (size_t)a.nslices * L::B_BYTES : 0);
     uint8_t* s_io = ring + (size_t)STAGES * stage_stride;
-    float* s_m = (float*)(s_io + (size_t)NIO * IO_BYTES);
+    float* s_m = (float*)(s_io + (size_t)(1 + NIO) * IO_BYTES);      // [0]: the warps' staging buffers; then NIO operand units
     float* s_bterm = s_m + BN;
     uint64_t* full = (uint64_t*)(s_bterm + BN);
     uint64_t* empty = full + MAX_STAGES;
@@ -480,7 +484,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], TC_EPI_WARPS); }
-        for (int b = 0; b < L::MAX_IO; ++b) { mbar_init(&io_full[b], 1); mbar_init(&io_empty[b], 4); }
+        for (int b = 0; b < L::MAX_IO; ++b) { mbar_init(&io_full[b], 1); mbar_init(&io_empty[b], TC_EPI_WARPS); }
         mbar_init(w_full, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         // a table is used only if it was built for exactly this launch's quantisation parameters
@@ -564,7 +568,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     for (int us = 0; us < UNITS; ++us) {
                         if (!mbar_wait(&io_empty[ub], uph ^ 1u)) { atomicExch(&g_tc_status, 6); alive = false; break; }
                         mbar_expect_tx(&io_full[ub], IO_BYTES);
-                        tma_load_3d(s_io + (size_t)ub * IO_BYTES, &tmR, &io_full[ub], n0 + us * UW,
+                        tma_load_3d(s_io + (size_t)(1 + ub) * IO_BYTES, &tmR, &io_full[ub], n0 + us * UW,
                                     a.im2col == 2 ? 0 : (int)m0, a.im2col == 2 ? tm : 0);
                         if (++ub == NIO) { ub = 0; uph ^= 1u; }
                     }
@@ -615,7 +619,6 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int quad = warp & 3;
         const int part = ew >> 2;
         const int etid = threadIdx.x - 64;
-        const bool leader = part == 0 && lane == 0;          // issues this quadrant's stores
         constexpr int CPW = UW / 64;                          // 16-column chunks per warp and unit
         const int row = quad * 32 + lane;
         const uint32_t sw_x = UW == 128 ? (uint32_t)(row & 7) : (uint32_t)((row >> 1) & 3);   // TMA swizzle of this row
@@ -643,8 +646,11 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         ec.lut = smem_u32(s_lut) - 0x4B400000u * (uint32_t)TC_LUT_PITCH;
         int cur_n0 = -1;
         int it = 0;
-        int ub = 0, prev_ub = 0; uint32_t uph = 0;           // unit-buffer position (kept without divisions)
-        bool first_unit = true;
+        int ub = 0; uint32_t uph = 0;                        // operand-buffer position (kept without divisions)
+        // this warp's staging buffer: [32 rows][UW / 4 bytes], 32-byte TMA swizzle when a row is 32 bytes
+        const uint32_t st_base = smem_u32(s_io) + (uint32_t)ew * (32 * (UW / 4));
+        const uint32_t st_row = st_base + (uint32_t)lane * (UW / 4);
+        const uint32_t st_sw = UW == 128 ? (uint32_t)((lane >> 2) & 1) : 0u;
         bool dead = false;
         for (int t = blockIdx.x; t < ntiles; t += gridDim.x, ++it) {
             const int n0 = (t % ntn) * BN;
@@ -700,7 +706,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const uint32_t tacc = tmem_base + (uint32_t)(buf * BN) + ((uint32_t)(quad * 32) << 16);
             #pragma unroll 1
             for (int us = 0; us < UNITS; ++us) {
-                uint8_t* io_row = s_io + (size_t)ub * IO_BYTES + row * UW;
+                const uint32_t res_row = smem_u32(s_io + (size_t)(1 + ub) * IO_BYTES + row * UW);
                 const int colw = us * UW + part * (UW / 4);    // first column of this warp in this unit
                 uint32_t r[CPW][16];
                 #pragma unroll
@@ -708,21 +714,40 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 #pragma unroll
                 for (int k = 0; k < CPW; ++k) tc_ld16_wait(r[k]);
                 if (fused && !dead && !mbar_wait(&io_full[ub], uph)) { atomicExch(&g_tc_status, 5); dead = true; }
+                // this warp's previous store has been read out of its staging buffer
+                if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                __syncwarp();
+                uint32_t fixmask = 0;                              // chunks the cold pass has to redo (warp-uniform)
                 #pragma unroll
                 for (int k = 0; k < CPW; ++k) {
                     const int col0 = colw + k * 16;
-                    const uint32_t slot = smem_u32(io_row) + ((((uint32_t)(part * CPW + k)) ^ sw_x) << 4);
-                    if (dump_acc && mvalid) {                      // raw accumulators for the bit-exactness tests
-                        for (int j = 0; j < 16; ++j) a.acc_out[m * a.OC + n0 + col0 + j] = (int)r[k][j] - corr_row[col0 + j];
-                    }
                     const EpiAddr ad = {a_m + col0 * 4, a_b + col0 * 4, a_cc + col0 * 4};
-                    const uint4 rv = fused ? lds128(slot) : make_uint4(0, 0, 0, 0);
                     float dmax = always_fix ? 1.0f : 0.0f;
-                    const uint4 outv = use_lut ? epi_chunk<true>(r[k], rv, ad, ec, dmax) : epi_chunk<false>(r[k], rv, ad, ec, dmax);
-                    sts128(slot, outv);
+                    uint4 outv;
+                    if (use_lut) outv = epi_chunk<true>(r[k], lds128(res_row + ((((uint32_t)(part * CPW + k)) ^ sw_x) << 4)), ad, ec, dmax);
+                    else         outv = epi_chunk<false>(r[k], make_uint4(0, 0, 0, 0), ad, ec, dmax);
                     // an exact half (the reference rounds it away from zero), a value beyond the rounding constant, or
-                    // no table: the whole warp redoes this chunk with the reference arithmetic
-                    if (__any_sync(0xffffffffu, dmax >= 0.5f)) epi_fixup(tacc + (uint32_t)col0, slot, rv, ad.m, ad.b, ad.cc, ex);
+                    // no table: the chunk is left to the cold pass
+                    const bool fix = __any_sync(0xffffffffu, dmax >= 0.5f);
+                    if (!fix) sts128(st_row + (((uint32_t)k ^ st_sw) << 4), outv);
+                    fixmask |= fix ? (1u << k) : 0u;
+                }
+                if (fixmask != 0 || dump_acc) {
+                    #pragma unroll 1
+                    for (int k = 0; k < CPW; ++k) {
+                        const int col0 = colw + k * 16;
+                        const bool fix = (fixmask >> k) & 1u;
+                        if (!fix && !dump_acc) continue;
+                        epi_cold(tacc + (uint32_t)col0, res_row + ((((uint32_t)(part * CPW + k)) ^ sw_x) << 4),
+                                 st_row + (((uint32_t)k ^ st_sw) << 4), a_m + col0 * 4, a_b + col0 * 4, a_cc + col0 * 4, ex, fix,
+                                 (dump_acc && mvalid) ? a.acc_out + m * a.OC + n0 + col0 : nullptr);
+                    }
+                }
+                if (fused) {
+                    // this warp has finished reading the other operand's unit
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&io_empty[ub]);
+                    if (++ub == NIO) { ub = 0; uph ^= 1u; }
                 }
                 if (us == UNITS - 1) {
                     // this warp has finished reading the accumulator buffer
@@ -731,26 +756,16 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     if (lane == 0) mbar_arrive(&acc_empty[buf]);
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the TMA store
-                if (leader) {
-                    // every earlier store of this quadrant has been read out of shared memory: the buffer of the
-                    // previous unit is free for the producer, and the next unit's buffer for the epilogue
-                    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-                    if (fused && !first_unit) mbar_arrive(&io_empty[prev_ub]);
-                }
-                quad_barrier(quad);
-                if (leader) {
+                __syncwarp();
+                if (lane == 0) {
                     const int row0 = quad * 32;
                     if (row0 < a.tile_rows && m0 + row0 < a.M)
-                        tma_store_3d(&tmY, s_io + (size_t)ub * IO_BYTES + row0 * UW, n0 + us * UW,
-                                     a.im2col == 2 ? row0 : (int)(m0 + row0), a.im2col == 2 ? tm : 0);
+                        tma_store_3d(&tmY, st_base, n0 + colw, a.im2col == 2 ? row0 : (int)(m0 + row0), a.im2col == 2 ? tm : 0);
                     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                 }
-                first_unit = false;
-                prev_ub = ub;
-                if (++ub == NIO) { ub = 0; uph ^= 1u; }
             }
         }
-        if (leader) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     }
 
     tc_fence_before();
@@ -1033,7 +1048,7 @@ static int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUten
 {
     using L = TcSmem<BN, SWZ>;
     const size_t budget = 227 * 1024;                                   // opt-in shared memory per CTA on sm_100
-    const size_t rest = 1024 + L::CONST_BYTES + (size_t)a.ncls * BN * 4 + (size_t)a.nio * L::IO_BYTES + (a.add_lut ? TC_LUT_BYTES + 256 : 0);
+    const size_t rest = 1024 + L::CONST_BYTES + (size_t)a.ncls * BN * 4 + (size_t)(1 + a.nio) * L::IO_BYTES + (a.add_lut ? TC_LUT_BYTES + 256 : 0);
     B200K_REQUIRE(rest + 2 * L::STAGE_BYTES <= budget, B200K_E_TOOBIG, "conv2d_q8: shared memory exhausted (%zu bytes of tables)", rest);
     TcArgs a2 = a;
     // One n-tile and a weight tile of at most 64 KiB over all of K: keep it in shared memory for the whole launch, so
@@ -1102,7 +1117,7 @@ int launch_conv_tc(const b200k_conv2d_params* p, cudaStream_t stream)
     a.add_lut = (fa.res && p->packed) ? (const uint8_t*)p->packed + add_lut_offset(p->oc, p->kh, p->kw, p->c) : nullptr;
     memset(a.lut_tag, 0, sizeof(a.lut_tag));
     if (fa.res) make_lut_tag(p, a.lut_tag);
-    a.nio = fa.res ? 3 : 2;
+    a.nio = fa.res ? 2 : 0;
     a.ncy = a.ncx = a.ncls = 1;
     memset(a.ypair, 0, sizeof(a.ypair)); memset(a.xpair, 0, sizeof(a.xpair));
     memset(a.ycls, 0, sizeof(a.ycls));   memset(a.xcls, 0, sizeof(a.xcls));
@@ -1192,9 +1207,11 @@ int launch_conv_tc(const b200k_conv2d_params* p, cudaStream_t stream)
         cuuint64_t strides[2] = {(cuuint64_t)p->oc, (cuuint64_t)p->oc * rows};
         cuuint32_t estr[3] = {1, 1, 1};
         const CUtensorMapSwizzle usw = uw == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
-        cuuint32_t box_st[3] = {(cuuint32_t)uw, 32, 1};
+        // stores: one epilogue warp's 32 rows x uw / 4 columns
+        cuuint32_t box_st[3] = {(cuuint32_t)(uw / 4), 32, 1};
         CUresult r = g_encode_tiled(&tmY, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, a.y, dims, strides, box_st, estr,
-                                    CU_TENSOR_MAP_INTERLEAVE_NONE, usw, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                                    CU_TENSOR_MAP_INTERLEAVE_NONE, uw == 128 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                                    CU_TENSOR_MAP_L2_PROMOTION_NONE,
                                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         B200K_REQUIRE(r == CUDA_SUCCESS, B200K_E_CUDA, "conv2d_q8: cuTensorMapEncodeTiled(output) failed with %d", (int)r);
         tmR = tmY;
