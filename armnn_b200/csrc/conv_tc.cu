@@ -50,7 +50,7 @@ constexpr int TC_LUT_TAG_WORDS = 12;
 constexpr int TC_LUT_PITCH = 260;
 constexpr int TC_LUT_BYTES = 256 * TC_LUT_PITCH;
 constexpr int TC_THREADS = 64 + 32 * TC_EPI_WARPS;   // warp 0 producer, warp 1 MMA issuer, then the epilogue warps
-constexpr unsigned TC_WAIT_HINT_NS = 20000;              // one suspended try_wait lasts at most this long
+
 constexpr long long TC_WAIT_LIMIT_CYCLES = 4000000000ll;  // about two seconds: no wait of a healthy launch comes near
 
 __device__ int g_tc_status = 0;                 // 0 ok, otherwise the code of the wait that gave up
@@ -115,9 +115,9 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity)
         for (int i = 0; i < 32; ++i) {
             uint32_t ok;
             asm volatile("{\n\t.reg .pred p;\n\t"
-                         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+                         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
                          "selp.b32 %0, 1, 0, p;\n\t}"
-                         : "=r"(ok) : "r"(addr), "r"(parity), "r"(TC_WAIT_HINT_NS) : "memory");
+                         : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
             if (ok) return true;
         }
         const long long now = clock64();
@@ -1048,9 +1048,12 @@ static int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUten
 {
     using L = TcSmem<BN, SWZ>;
     const size_t budget = 227 * 1024;                                   // opt-in shared memory per CTA on sm_100
-    const size_t rest = 1024 + L::CONST_BYTES + (size_t)a.ncls * BN * 4 + (size_t)(1 + a.nio) * L::IO_BYTES + (a.add_lut ? TC_LUT_BYTES + 256 : 0);
-    B200K_REQUIRE(rest + 2 * L::STAGE_BYTES <= budget, B200K_E_TOOBIG, "conv2d_q8: shared memory exhausted (%zu bytes of tables)", rest);
     TcArgs a2 = a;
+    size_t rest = 1024 + L::CONST_BYTES + (size_t)a.ncls * BN * 4 + (size_t)(1 + a.nio) * L::IO_BYTES + (a.add_lut ? TC_LUT_BYTES + 256 : 0);
+    // a third buffer for the fused Add's other operand (its loads then run a whole unit ahead of the epilogue) when the
+    // ring keeps at least three stages
+    if (a.nio == 2 && rest + L::IO_BYTES + 3 * L::STAGE_BYTES <= budget) { a2.nio = 3; rest += L::IO_BYTES; }
+    B200K_REQUIRE(rest + 2 * L::STAGE_BYTES <= budget, B200K_E_TOOBIG, "conv2d_q8: shared memory exhausted (%zu bytes of tables)", rest);
     // One n-tile and a weight tile of at most 64 KiB over all of K: keep it in shared memory for the whole launch, so
     // that the ring (and the L2 bandwidth behind it) carries activations only.
     const size_t wbytes = (size_t)a.nslices * L::B_BYTES;

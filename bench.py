@@ -29,6 +29,11 @@ GLOBAL_BATCH = 256
 IMAGE = 224
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum per convolution launch, averaged over the 53 convolution launches of
+# one batch-256 step (one ncu capture of this file's own command; see profiles/resnet50_b256_launch_list.md)
+CONV_DRAM_BYTES_PER_LAUNCH = 102.2e6
+
+
 def _peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -260,7 +265,7 @@ def run_b200(args):
     if fam[top]["macs"] > 0:
         achieved = 2.0 * fam[top]["macs"] / (fam[top]["ms"] / 1e3) / 1e12
         roofline = {"bound": "tensor", "kernel": top, "achieved": achieved, "peak": tensor_peak, "unit": "TFLOP/s",
-                    "frac": achieved / tensor_peak, "traffic": None,
+                    "frac": achieved / tensor_peak, "traffic": CONV_DRAM_BYTES_PER_LAUNCH if world == 1 else None,
                     "note": "int8 ops (2 x MAC) per launch / mean CUDA-event duration of the %d %s launches in one "
                             "instrumented pass; peak = 2 x %s sustained bf16 cuBLAS TFLOP/s (int8 is twice the bf16 rate); "
                             "share of step time %.2f" % (fam[top]["launches"], top, peaks["source"], fam[top]["ms"] / total_ms)}
