@@ -61,6 +61,11 @@ struct TcArgs {
     const int32_t* prefix;                      // [(KH+1)*(KW+1)][OC] or null
     float w_scale, b_scale;
     int zx;                                     // true input zero point
+    int zw;                                     // weight zero point (per-tensor asymmetric weights), 0 otherwise
+    int rowsum;                                 // zw != 0: the kernel also accumulates the sum of every A row (see below)
+    int mask_cpad, mask_kw;                     // row-window mode: which bytes of a K-slice are real taps (for the row sums)
+    int ntn;                                    // n-tiles: ceil(OC / BN); columns beyond OC are padding
+    int tmem_cols;                              // tensor-memory columns to allocate (power of two)
     int N, H, W, C, OH, OW, OC, KH, KW, sh, sw, pt, pl, dh, dw;
     long long M;
     int im2col;                                 // 0: A is a 2-D [M, C] matrix; 1: TMA im2col from NHWC; 2: row-window
@@ -343,7 +348,8 @@ struct EpiAddr { uint32_t m, b, cc; };
 // constant), the maximum of |q1 - n| over the chunk is handed back in dmax, and the caller re-evaluates a flagged chunk
 // with the plain reference arithmetic.
 template <bool FUSED>
-__device__ __forceinline__ uint4 epi_chunk(const uint32_t* r, const uint4 rv, const EpiAddr& ad, const EpiConsts& ec, float& dmax)
+__device__ __forceinline__ uint4 epi_chunk(const uint32_t* r, const uint4 rv, const EpiAddr& ad, const EpiConsts& ec, int rowterm,
+                                           float& dmax)
 {
     const uint32_t resw[4] = {rv.x, rv.y, rv.z, rv.w};
     uint32_t packed[4];
@@ -353,8 +359,9 @@ __device__ __forceinline__ uint4 epi_chunk(const uint32_t* r, const uint4 rv, co
         lds_2x2(ad.m + g * 16, m01, m23);
         lds_2x2(ad.b + g * 16, b01, b23);
         const uint4 cv = lds128(ad.cc + g * 16);
-        const f32x2 a01 = pack2(__int2float_rn((int)r[g * 4 + 0] - (int)cv.x), __int2float_rn((int)r[g * 4 + 1] - (int)cv.y));
-        const f32x2 a23 = pack2(__int2float_rn((int)r[g * 4 + 2] - (int)cv.z), __int2float_rn((int)r[g * 4 + 3] - (int)cv.w));
+        // rowterm: weight zero point x the sum of this pixel's activations (0 for symmetric weights)
+        const f32x2 a01 = pack2(__int2float_rn((int)r[g * 4 + 0] - (int)cv.x - rowterm), __int2float_rn((int)r[g * 4 + 1] - (int)cv.y - rowterm));
+        const f32x2 a23 = pack2(__int2float_rn((int)r[g * 4 + 2] - (int)cv.z - rowterm), __int2float_rn((int)r[g * 4 + 3] - (int)cv.w - rowterm));
         // acc * m as an FMA with a zero addend: the assembler contracts a packed multiply feeding a packed add into
         // one FMA (a single rounding) even with explicit rounding modifiers, which the reference does not do
         const f32x2 v01 = add2(fma2(a01, m01, ec.zero2), b01), v23 = add2(fma2(a23, m23, ec.zero2), b23);
@@ -389,13 +396,13 @@ __device__ __forceinline__ uint4 epi_chunk(const uint32_t* r, const uint4 rv, co
 // res_slot, result to out_slot) and / or (acc_row) writes the raw accumulators of a valid row out for the bit-exactness
 // tests.
 __device__ __noinline__ void epi_cold(uint32_t taddr, uint32_t res_slot, uint32_t out_slot, uint32_t a_m, uint32_t a_b,
-                                      uint32_t a_cc, const EpiExact& x, bool fix, int32_t* acc_row)
+                                      uint32_t a_cc, const EpiExact& x, bool fix, int32_t* acc_row, int rowterm)
 {
     uint32_t r[16];
     tc_ld16(taddr, r);
     if (acc_row) {
         #pragma unroll
-        for (int j = 0; j < 16; ++j) acc_row[j] = (int)r[j] - lds_s32(a_cc + j * 4);
+        for (int j = 0; j < 16; ++j) acc_row[j] = (int)r[j] - lds_s32(a_cc + j * 4) - rowterm;
     }
     if (!fix) return;
     const uint4 rv = x.fused ? lds128(res_slot) : make_uint4(0, 0, 0, 0);
@@ -403,7 +410,7 @@ __device__ __noinline__ void epi_cold(uint32_t taddr, uint32_t res_slot, uint32_
     uint32_t out[4] = {0, 0, 0, 0};
     #pragma unroll
     for (int j = 0; j < 16; ++j) {
-        const int q = exact_value((int)r[j] - lds_s32(a_cc + j * 4), lds_f32(a_m + j * 4), lds_f32(a_b + j * 4),
+        const int q = exact_value((int)r[j] - lds_s32(a_cc + j * 4) - rowterm, lds_f32(a_m + j * 4), lds_f32(a_b + j * 4),
                                   (resw[j >> 2] >> (8 * (j & 3))) & 0xffu, x);
         out[j >> 2] |= ((uint32_t)q & 0xffu) << (8 * (j & 3));
     }
@@ -459,9 +466,13 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int NIO = a.nio;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    // row sums (asymmetric weights): a 16-row B tile of ones at the very start, multiplied with every A slice into 16
+    // extra accumulator columns, so that column 0 of them is the sum of the row's activations over the valid taps
+    uint8_t* s_ones = smem;
+    uint8_t* s_wst = smem + (a.rowsum ? 16 * SWZ : 0);
     // weight-stationary launches: all K-slices of the (only) weight tile first, then a ring of activation tiles only
     const int stage_stride = a.bstat ? L::A_BYTES : L::STAGE_BYTES;
-    uint8_t* ring = smem + (a.bstat ? (size_t)a.nslices * L::B_BYTES : 0);
+    uint8_t* ring = s_wst + (a.bstat ? (size_t)a.nslices * L::B_BYTES : 0);
     uint8_t* s_io = ring + (size_t)STAGES * stage_stride;
     float* s_m = (float*)(s_io + (size_t)(1 + NIO) * IO_BYTES);      // [0]: the warps' staging buffers; then NIO operand units
     float* s_bterm = s_m + BN;
@@ -478,7 +489,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     uint8_t* s_lut = (uint8_t*)(((uintptr_t)(s_cc + a.ncls * BN) + 255) & ~(uintptr_t)255);   // fused-add table, 256-byte aligned
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int ntn = a.OC / BN;                              // n-tiles (OC is a multiple of BN)
+    const int ntn = a.ntn;                                  // n-tiles; the last one may reach beyond OC (zero weights, clipped stores)
     const int ntiles = ntn * a.ntm;
 
     if (threadIdx.x == 0) {
@@ -496,8 +507,19 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         *s_lut_ok = ok;
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(2 * BN) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(a.tmem_cols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    if (a.rowsum) {
+        // 16 identical logical rows of ones (in row-window mode: ones on the bytes that are real taps), each stored with
+        // the swizzle of its own row index
+        for (int i = threadIdx.x; i < 16 * SWZ; i += TC_THREADS) {
+            const int row = i / SWZ, k = i - row * SWZ;
+            const bool real = a.mask_cpad == 0 || ((k / a.mask_cpad) < a.mask_kw && (k % a.mask_cpad) < a.C);
+            const int sw = SWZ == 128 ? (row & 7) : ((row >> 1) & 3);
+            s_ones[row * SWZ + ((((k >> 4) ^ sw) << 4) | (k & 15))] = real ? 1 : 0;
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     tc_fence_before();
     __syncthreads();
@@ -523,7 +545,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 mbar_expect_tx(w_full, (uint32_t)a.nslices * L::B_BYTES);
                 for (int s = 0; s < a.nslices; ++s) {
                     const int tap = s / a.cchunks;
-                    tma_load_2d(smem + (size_t)s * L::B_BYTES, &tmB, w_full, tap * a.kstride + (s - tap * a.cchunks) * SWZ, 0);
+                    tma_load_2d(s_wst + (size_t)s * L::B_BYTES, &tmB, w_full, tap * a.kstride + (s - tap * a.cchunks) * SWZ, 0);
                 }
             }
             for (int t = blockIdx.x; t < ntiles && alive; t += gridDim.x) {
@@ -582,6 +604,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             // 0 = unsigned 8-bit); both operands K-major (bits 15, 16 = 0); N >> 3 at bit 17; M >> 4 at bit 24
             const uint32_t id = (2u << 4) | ((uint32_t)a.a_signed << 7) | ((uint32_t)a.b_signed << 10) |
                                 ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+            // the row-sum MMA: same A, B = the ones tile (unsigned), N = 16
+            const uint32_t id_rs = (2u << 4) | ((uint32_t)a.a_signed << 7) | ((uint32_t)(16 >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+            const uint64_t d_ones = make_smem_desc<SWZ>(smem_u32(s_ones));
             int st = 0; uint32_t ph = 0;                     // ring position
             bool alive = true;
             int it = 0;
@@ -601,10 +626,16 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     if (a.debug == 1) { mbar_arrive(&empty[cur]); continue; }
                     const uint32_t sa = smem_u32(ring + cur * stage_stride);
                     const uint64_t da = make_smem_desc<SWZ>(sa);
-                    const uint64_t db = make_smem_desc<SWZ>(a.bstat ? smem_u32(smem + (size_t)s * L::B_BYTES) : sa + L::A_BYTES);
+                    const uint64_t db = make_smem_desc<SWZ>(a.bstat ? smem_u32(s_wst + (size_t)s * L::B_BYTES) : sa + L::A_BYTES);
                     #pragma unroll
                     for (int k = 0; k < SWZ / 32; ++k)
                         tc_mma_i8(tacc, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), id, (s > 0 || k > 0) ? 1u : 0u);
+                    if (a.rowsum) {
+                        const uint32_t tacc_rs = tmem_base + (uint32_t)(2 * BN + buf * 16);
+                        #pragma unroll
+                        for (int k = 0; k < SWZ / 32; ++k)
+                            tc_mma_i8(tacc_rs, da + (uint64_t)(k * 2), d_ones + (uint64_t)(k * 2), id_rs, (s > 0 || k > 0) ? 1u : 0u);
+                    }
                     tc_commit(&empty[cur]);            // slot reusable once these MMAs have read it
                 }
                 if (alive) tc_commit(&acc_full[buf]);  // accumulator of this tile complete
@@ -661,19 +692,21 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 // per-channel constants of this n-tile (all epilogue warps are between tiles here)
                 epi_barrier();
                 for (int j = etid; j < BN; j += 32 * TC_EPI_WARPS) {
-                    const int ch = n0 + j;
+                    const int ch = min(n0 + j, a.OC - 1);           // columns beyond OC are padding: any finite constants do
                     s_m[j] = __fmul_rn(a.rq.sx, a.w_scales ? a.w_scales[ch] : a.w_scale);
                     s_bterm[j] = a.bias ? __fmul_rn(__int2float_rn(a.bias[ch]), a.b_scales ? a.b_scales[ch] : a.b_scale) : 0.f;
                 }
                 for (int i = etid; i < a.ncls * BN; i += 32 * TC_EPI_WARPS) {
                     const int cls = i / BN, j = i - cls * BN;
                     int v = 0;
-                    if (a.need_corr) {
+                    if (a.need_corr && n0 + j < a.OC) {
+                        // sum over the in-image taps of (x - zx)(w - zw) - x w + zw x = -zx w + zx zw
                         const int yp = a.ypair[cls / a.ncx], xp = a.xpair[cls % a.ncx];
                         const int y0 = yp >> 4, y1 = yp & 15, x0 = xp >> 4, x1 = xp & 15;
                         const int32_t* P = a.prefix + n0 + j;
                         v = a.zx * (P[(long long)(y1 * pw + x1) * a.OC] - P[(long long)(y0 * pw + x1) * a.OC] -
-                                    P[(long long)(y1 * pw + x0) * a.OC] + P[(long long)(y0 * pw + x0) * a.OC]);
+                                    P[(long long)(y1 * pw + x0) * a.OC] + P[(long long)(y0 * pw + x0) * a.OC]) -
+                            (y1 - y0) * (x1 - x0) * a.C * a.zx * a.zw;
                     }
                     s_cc[i] = v;
                 }
@@ -701,6 +734,14 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 ky1 = max(ky1, ky0);  kx1 = max(kx1, kx0);
                 cls = mvalid ? a.ycls[ky0 * 16 + ky1] * a.ncx + a.xcls[kx0 * 16 + kx1] : 0;
             }
+            int rowterm = 0;
+            if (a.rowsum) {
+                uint32_t rs;
+                asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(rs)
+                             : "r"(tmem_base + (uint32_t)(2 * BN + buf * 16) + ((uint32_t)(quad * 32) << 16)));
+                asm volatile("tcgen05.wait::ld.sync.aligned;" : "+r"(rs) :: "memory");
+                rowterm = a.zw * (int)rs;
+            }
             const int32_t* corr_row = s_cc + cls * BN;
             const uint32_t a_m = smem_u32(s_m), a_b = smem_u32(s_bterm), a_cc = smem_u32(corr_row);
             const uint32_t tacc = tmem_base + (uint32_t)(buf * BN) + ((uint32_t)(quad * 32) << 16);
@@ -708,6 +749,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             for (int us = 0; us < UNITS; ++us) {
                 const uint32_t res_row = smem_u32(s_io + (size_t)(1 + ub) * IO_BYTES + row * UW);
                 const int colw = us * UW + part * (UW / 4);    // first column of this warp in this unit
+                const bool active = n0 + colw < a.OC;          // otherwise: padding columns, nothing to compute or store
+                if (active) {
                 uint32_t r[CPW][16];
                 #pragma unroll
                 for (int k = 0; k < CPW; ++k) tc_ld16_issue(tacc + (uint32_t)(colw + k * 16), r[k]);
@@ -724,8 +767,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     const EpiAddr ad = {a_m + col0 * 4, a_b + col0 * 4, a_cc + col0 * 4};
                     float dmax = always_fix ? 1.0f : 0.0f;
                     uint4 outv;
-                    if (use_lut) outv = epi_chunk<true>(r[k], lds128(res_row + ((((uint32_t)(part * CPW + k)) ^ sw_x) << 4)), ad, ec, dmax);
-                    else         outv = epi_chunk<false>(r[k], make_uint4(0, 0, 0, 0), ad, ec, dmax);
+                    if (use_lut) outv = epi_chunk<true>(r[k], lds128(res_row + ((((uint32_t)(part * CPW + k)) ^ sw_x) << 4)), ad, ec, rowterm, dmax);
+                    else         outv = epi_chunk<false>(r[k], make_uint4(0, 0, 0, 0), ad, ec, rowterm, dmax);
                     // an exact half (the reference rounds it away from zero), a value beyond the rounding constant, or
                     // no table: the chunk is left to the cold pass
                     const bool fix = __any_sync(0xffffffffu, dmax >= 0.5f);
@@ -740,8 +783,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         if (!fix && !dump_acc) continue;
                         epi_cold(tacc + (uint32_t)col0, res_row + ((((uint32_t)(part * CPW + k)) ^ sw_x) << 4),
                                  st_row + (((uint32_t)k ^ st_sw) << 4), a_m + col0 * 4, a_b + col0 * 4, a_cc + col0 * 4, ex, fix,
-                                 (dump_acc && mvalid) ? a.acc_out + m * a.OC + n0 + col0 : nullptr);
+                                 (dump_acc && mvalid && n0 + col0 < a.OC) ? a.acc_out + m * a.OC + n0 + col0 : nullptr, rowterm);
                     }
+                }
                 }
                 if (fused) {
                     // this warp has finished reading the other operand's unit
@@ -759,7 +803,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 __syncwarp();
                 if (lane == 0) {
                     const int row0 = quad * 32;
-                    if (row0 < a.tile_rows && m0 + row0 < a.M)
+                    if (active && row0 < a.tile_rows && m0 + row0 < a.M)
                         tma_store_3d(&tmY, st_base, n0 + colw, a.im2col == 2 ? row0 : (int)(m0 + row0), a.im2col == 2 ? tm : 0);
                     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                 }
@@ -772,7 +816,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(a.tmem_cols) : "memory");
     }
 }
 
@@ -815,8 +859,8 @@ static RowPlan row_window_plan(const b200k_conv2d_params* p)
 {
     RowPlan r;
     memset(&r, 0, sizeof(r));
-    if (p->c > 16 || p->c < 1 || p->dil_w != 1 || p->ow > TC_BM || p->oc % 64 != 0 || p->kh > 15 || p->kw > 15) return r;
-    if (p->w.zero_point != 0 || p->stride_w > 8 || p->stride_h > 8) return r;
+    if (p->c > 16 || p->c < 1 || p->dil_w != 1 || p->ow > TC_BM || p->oc % 16 != 0 || p->kh > 15 || p->kw > 15) return r;
+    if (p->stride_w > 8 || p->stride_h > 8) return r;
     r.cpad = (p->c <= 8 && (p->stride_w * 8) % 16 == 0) ? 8 : 16;
     const int window = p->kw * r.cpad;
     if (window > 128) return r;
@@ -848,7 +892,7 @@ __global__ void row_weight_pack_kernel(const RowWeightArgs a)
 
 struct RowInputArgs { const uint8_t* x; uint8_t* xp; int N, H, W, C, hp, wp, cpad, pt, pl; unsigned fill; long long total; };
 
-// xp[n][yp][xq][0..cpad) = x[n][yp - pt][xq - pl][0..C) inside the image, the input zero point everywhere else
+// xp[n][yp][xq][0..C) = x[n][yp - pt][xq - pl][0..C) inside the image, the input zero point outside; [C..cpad) = 0
 template <int CPAD>
 __global__ void __launch_bounds__(256) row_input_pack_kernel(const RowInputArgs a)
 {
@@ -861,7 +905,7 @@ __global__ void __launch_bounds__(256) row_input_pack_kernel(const RowInputArgs 
     const int iy = yp - a.pt, ix = xq - a.pl;
     uint8_t v[CPAD];
     #pragma unroll
-    for (int c = 0; c < CPAD; ++c) v[c] = (uint8_t)a.fill;
+    for (int c = 0; c < CPAD; ++c) v[c] = c < a.C ? (uint8_t)a.fill : (uint8_t)0;
     if (iy >= 0 && iy < a.H && ix >= 0 && ix < a.W) {
         const uint8_t* src = a.x + (((long long)n * a.H + iy) * a.W + ix) * a.C;
         #pragma unroll
@@ -945,7 +989,17 @@ static bool load_driver_entry_points()
     return true;
 }
 
-static int pick_bn(int oc) { return (oc % 256 == 0) ? 256 : (oc % 128 == 0) ? 128 : 64; }
+// Tile width: the candidate that pads OC least (ties: the widest).  With row sums the accumulators need 16 more
+// columns per buffer, which leaves no room for two 256-column buffers in the 512 columns of tensor memory.
+static int pick_bn(int oc, bool rowsum)
+{
+    int best = 64, waste = ((oc + 63) / 64) * 64 - oc;
+    for (int bn = 128; bn <= (rowsum ? 128 : 256); bn *= 2) {
+        const int w = ((oc + bn - 1) / bn) * bn - oc;
+        if (w <= waste) { best = bn; waste = w; }
+    }
+    return best;
+}
 
 // Distinct in-image tap ranges [k0, k1) along one axis, over all output positions of that axis.
 struct TapClasses {
@@ -1007,8 +1061,8 @@ bool conv_tc_eligible(const b200k_conv2d_params* p)
     if (!p->x.data || !p->w.data || !outp) return false;
     if (!is_q8(p->x.dtype) || !is_q8(p->w.dtype) || !is_q8(p->y.dtype)) return false;
     if (p->add_operand.data && ((((uintptr_t)p->add_operand.data | (uintptr_t)p->add_out.data) & 15) != 0)) return false;
-    if (p->c % 64 != 0 || p->oc % 64 != 0) return false;
-    if (p->w.zero_point != 0) return false;                              // symmetric weights only on this path
+    if (p->c % 16 != 0 || p->oc % 16 != 0) return false;               // TMA: 16-byte pixel and row strides
+    if (p->w.zero_point != 0 && p->w.scales) return false;             // per-axis weights are symmetric
     if ((((uintptr_t)p->x.data | (uintptr_t)p->w.data | (uintptr_t)outp) & 15) != 0) return false;
     if (p->x.zero_point != 0 && !p->packed) return false;              // needs the prefix table
     if (p->kh > 15 || p->kw > 15) return false;
@@ -1026,7 +1080,7 @@ bool conv_tc_eligible(const b200k_conv2d_params* p)
     }
     if (p->x.zero_point != 0) {
         const TapClasses tc = tap_classes(p);
-        if (!tc.ok || (size_t)tc.ncy * tc.ncx * pick_bn(p->oc) * 4 > 32 * 1024) return false;
+        if (!tc.ok || (size_t)tc.ncy * tc.ncx * pick_bn(p->oc, p->w.zero_point != 0) * 4 > 32 * 1024) return false;
     }
     return true;
 }
@@ -1049,7 +1103,8 @@ static int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUten
     using L = TcSmem<BN, SWZ>;
     const size_t budget = 227 * 1024;                                   // opt-in shared memory per CTA on sm_100
     TcArgs a2 = a;
-    size_t rest = 1024 + L::CONST_BYTES + (size_t)a.ncls * BN * 4 + (size_t)(1 + a.nio) * L::IO_BYTES + (a.add_lut ? TC_LUT_BYTES + 256 : 0);
+    size_t rest = 1024 + L::CONST_BYTES + (size_t)a.ncls * BN * 4 + (size_t)(1 + a.nio) * L::IO_BYTES + (a.add_lut ? TC_LUT_BYTES + 256 : 0) +
+                  (a.rowsum ? 16 * SWZ : 0);
     // a third buffer for the fused Add's other operand (its loads then run a whole unit ahead of the epilogue) when the
     // ring keeps at least three stages
     if (a.nio == 2 && rest + L::IO_BYTES + 3 * L::STAGE_BYTES <= budget) { a2.nio = 3; rest += L::IO_BYTES; }
@@ -1057,12 +1112,13 @@ static int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUten
     // One n-tile and a weight tile of at most 64 KiB over all of K: keep it in shared memory for the whole launch, so
     // that the ring (and the L2 bandwidth behind it) carries activations only.
     const size_t wbytes = (size_t)a.nslices * L::B_BYTES;
-    a2.bstat = (a.OC == BN && wbytes <= 64 * 1024 && rest + wbytes + 4 * L::A_BYTES <= budget) ? 1 : 0;
+    a2.bstat = (a.ntn == 1 && wbytes <= 64 * 1024 && rest + wbytes + 4 * L::A_BYTES <= budget) ? 1 : 0;
     const size_t stride = a2.bstat ? L::A_BYTES : L::STAGE_BYTES;
     const size_t fixed = rest + (a2.bstat ? wbytes : 0);
     int stages = (int)((budget - fixed) / stride);
     if (stages > L::MAX_STAGES) stages = L::MAX_STAGES;
     a2.stages = stages;
+    a2.tmem_cols = 2 * BN + (a.rowsum ? 32 : 0) <= 128 ? 128 : 2 * BN + (a.rowsum ? 32 : 0) <= 256 ? 256 : 512;
     if (a2.bstat) a2.stage_tx = (uint32_t)(a.stage_tx - L::B_BYTES);
     const size_t smem = fixed + (size_t)stages * stride;
     auto kern = conv_tc_kernel<BN, SWZ>;
@@ -1071,7 +1127,7 @@ static int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUten
         B200K_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured = smem;
     }
-    const long long tiles = (long long)(a.OC / BN) * a.ntm;
+    const long long tiles = (long long)a.ntn * a.ntm;
     const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
     kern<<<grid, TC_THREADS, smem, stream>>>(tmA, tmB, tmY, tmR, a2);
     return check_launch("conv_tc_kernel");
@@ -1086,6 +1142,8 @@ int launch_conv_tc(const b200k_conv2d_params* p, cudaStream_t stream)
     a.w_scales = p->w.scales; a.b_scales = p->bias.scales; a.w_scale = p->w.scale; a.b_scale = p->bias.scale;
     a.prefix = (const int32_t*)p->packed;
     a.zx = p->x.zero_point;
+    a.zw = p->w.scales ? 0 : p->w.zero_point;
+    a.rowsum = a.zw != 0;
     a.N = p->n; a.H = p->h; a.W = p->wd; a.C = p->c; a.OH = p->oh; a.OW = p->ow; a.OC = p->oc;
     a.KH = p->kh; a.KW = p->kw; a.sh = p->stride_h; a.sw = p->stride_w; a.pt = p->pad_top; a.pl = p->pad_left;
     a.dh = p->dil_h; a.dw = p->dil_w;
@@ -1095,8 +1153,10 @@ int launch_conv_tc(const b200k_conv2d_params* p, cudaStream_t stream)
     const bool gemm = !row_mode && p->kh == 1 && p->kw == 1 && p->stride_h == 1 && p->stride_w == 1 && p->pad_top == 0 &&
                       p->pad_left == 0 && p->oh == p->h && p->ow == p->wd;
     a.im2col = row_mode ? 2 : gemm ? 0 : 1;
-    const int swz = row_mode ? rowp.swz : (p->c % 128 == 0) ? 128 : 64;
-    a.cchunks = row_mode ? 1 : p->c / swz;
+    const int swz = row_mode ? rowp.swz : p->c >= 128 ? 128 : 64;
+    a.cchunks = row_mode ? 1 : (p->c + swz - 1) / swz;     // the last chunk of a tap may reach beyond C: TMA fills A with zeros there
+    a.mask_cpad = row_mode ? rowp.cpad : 0;
+    a.mask_kw = p->kw;
     a.nslices = row_mode ? p->kh : p->kh * p->kw * a.cchunks;
     a.tile_rows = row_mode ? p->ow : TC_BM;
     a.ntm = row_mode ? p->n * p->oh : (int)((a.M + TC_BM - 1) / TC_BM);
@@ -1136,7 +1196,8 @@ int launch_conv_tc(const b200k_conv2d_params* p, cudaStream_t stream)
     static const int debug_mode = getenv("B200K_TC_DEBUG") ? atoi(getenv("B200K_TC_DEBUG")) : 0;
     a.debug = debug_mode;
 
-    const int bn = pick_bn(p->oc);
+    const int bn = pick_bn(p->oc, a.rowsum != 0);
+    a.ntn = (p->oc + bn - 1) / bn;
     CUtensorMap tmA, tmB;
     const CUtensorMapSwizzle swizzle = swz == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
     a.stage_tx = (uint32_t)((a.tile_rows + bn) * swz);

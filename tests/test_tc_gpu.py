@@ -40,6 +40,27 @@ CONV = {
     "rowwin_5x5_s1_c16_dil_h2": lambda: random_conv_case(244, 1, 24, 24, 16, 64, 5, 5, pad=(4, 4, 2, 2), dil=(2, 1)),
     "rowwin_1x1_c8_zx0": lambda: random_conv_case(245, 2, 9, 9, 8, 64, 1, 1, x_q=(0.02, 0)),
     "im2col_odd_image_7x7": lambda: random_conv_case(216, 5, 7, 7, 512, 512, 3, 3, pad=(1, 1, 1, 1), act=(1, 0, 0)),
+    # channel counts that are multiples of 16 only: the last K-slice and the last N-tile are padding
+    "gemm_c96_oc144": lambda: random_conv_case(250, 2, 14, 14, 96, 144, 1, 1, act=(1, 0, 0)),
+    "gemm_c16_oc96": lambda: random_conv_case(251, 1, 28, 28, 32, 96, 1, 1),
+    "gemm_c192_oc32": lambda: random_conv_case(252, 2, 14, 14, 192, 32, 1, 1),
+    "gemm_c960_oc320": lambda: random_conv_case(253, 1, 7, 7, 960, 320, 1, 1),
+    "im2col_3x3_c32_oc48": lambda: random_conv_case(254, 2, 14, 14, 32, 48, 3, 3, pad=(1, 1, 1, 1)),
+    # per-tensor uint8 weights with a zero point: row sums of the activations from a second, 16-column MMA
+    "gemm_u8w_c64_oc64": lambda: random_conv_case(260, 2, 14, 14, 64, 64, 1, 1, x_dtype=U8, w_dtype=U8, y_dtype=U8, x_q=(0.02, 128)),
+    "gemm_u8w_c144_oc32_relu6": lambda: random_conv_case(261, 2, 28, 28, 144, 32, 1, 1, x_dtype=U8, w_dtype=U8, y_dtype=U8,
+                                                          x_q=(0.03, 0), act=(2, 6.0, 0.0), y_zp=0),
+    "gemm_u8w_c32_oc192_zx": lambda: random_conv_case(262, 1, 28, 28, 32, 192, 1, 1, x_dtype=U8, w_dtype=U8, y_dtype=U8, x_q=(0.02, 117)),
+    "gemm_u8w_c320_oc1280": lambda: random_conv_case(263, 2, 7, 7, 320, 1280, 1, 1, x_dtype=U8, w_dtype=U8, y_dtype=U8, x_q=(0.02, 128)),
+    "gemm_u8w_s8x": lambda: random_conv_case(264, 1, 14, 14, 128, 128, 1, 1, w_dtype=U8),
+    "im2col_u8w_3x3_pad": lambda: random_conv_case(265, 2, 14, 14, 64, 64, 3, 3, pad=(1, 1, 1, 1), x_dtype=U8, w_dtype=U8, y_dtype=U8,
+                                                    x_q=(0.02, 121)),
+    "gemm_u8w_fused_add": lambda: random_conv_case(266, 2, 14, 14, 192, 32, 1, 1, x_dtype=U8, w_dtype=U8, y_dtype=U8, x_q=(0.02, 128),
+                                                    fused_add=True),
+    "rowwin_u8w_stem_3x3_s2_oc32": lambda: random_conv_case(267, 2, 64, 64, 3, 32, 3, 3, stride=(2, 2), pad=(0, 1, 0, 1), x_dtype=U8,
+                                                            w_dtype=U8, y_dtype=U8, x_q=(0.02, 128), act=(2, 6.0, 0.0), y_zp=0),
+    "rowwin_u8w_5x5_c4": lambda: random_conv_case(268, 1, 20, 20, 4, 48, 5, 5, pad=(2, 2, 2, 2), x_dtype=U8, w_dtype=U8, y_dtype=U8,
+                                                  x_q=(0.02, 100)),
 }
 
 FC = {
@@ -63,6 +84,10 @@ def test_tcgen05_conv_bit_exact(built, name):
     _poll()
     assert np.array_equal(acc, gacc), (name, diff_stats(acc, gacc))
     assert np.array_equal(y, gy), (name, diff_stats(y, gy))
+    # the accumulator dump goes through the kernel's cold pass: the plain launch must agree as well
+    gy2, _ = case.run_gpu(want_acc=False, algo=2)
+    _poll()
+    assert np.array_equal(y, gy2), (name, diff_stats(y, gy2))
 
 
 @pytest.mark.parametrize("name", list(FC))
