@@ -62,10 +62,10 @@ struct TcArgs {
     float w_scale, b_scale;
     int zx;                                     // true input zero point
     int zw;                                     // weight zero point (per-tensor asymmetric weights), 0 otherwise
-    int rowsum;                                 // zw != 0: the kernel also accumulates the sum of every A row (see below)
+    int nzw;                                    // zw != 0: constant B tiles (1 or 2) that add -zw x (row sum of A) to every column
+    int zw_val[2];                              // their values: -min(zw, 128) and -(zw - 128), each fits int8
     int mask_cpad, mask_kw;                     // row-window mode: which bytes of a K-slice are real taps (for the row sums)
     int ntn;                                    // n-tiles: ceil(OC / BN); columns beyond OC are padding
-    int tmem_cols;                              // tensor-memory columns to allocate (power of two)
     int N, H, W, C, OH, OW, OC, KH, KW, sh, sw, pt, pl, dh, dw;
     long long M;
     int im2col;                                 // 0: A is a 2-D [M, C] matrix; 1: TMA im2col from NHWC; 2: row-window
@@ -348,8 +348,7 @@ struct EpiAddr { uint32_t m, b, cc; };
 // constant), the maximum of |q1 - n| over the chunk is handed back in dmax, and the caller re-evaluates a flagged chunk
 // with the plain reference arithmetic.
 template <bool FUSED>
-__device__ __forceinline__ uint4 epi_chunk(const uint32_t* r, const uint4 rv, const EpiAddr& ad, const EpiConsts& ec, int rowterm,
-                                           float& dmax)
+__device__ __forceinline__ uint4 epi_chunk(const uint32_t* r, const uint4 rv, const EpiAddr& ad, const EpiConsts& ec, float& dmax)
 {
     const uint32_t resw[4] = {rv.x, rv.y, rv.z, rv.w};
     uint32_t packed[4];
@@ -359,9 +358,8 @@ __device__ __forceinline__ uint4 epi_chunk(const uint32_t* r, const uint4 rv, co
         lds_2x2(ad.m + g * 16, m01, m23);
         lds_2x2(ad.b + g * 16, b01, b23);
         const uint4 cv = lds128(ad.cc + g * 16);
-        // rowterm: weight zero point x the sum of this pixel's activations (0 for symmetric weights)
-        const f32x2 a01 = pack2(__int2float_rn((int)r[g * 4 + 0] - (int)cv.x - rowterm), __int2float_rn((int)r[g * 4 + 1] - (int)cv.y - rowterm));
-        const f32x2 a23 = pack2(__int2float_rn((int)r[g * 4 + 2] - (int)cv.z - rowterm), __int2float_rn((int)r[g * 4 + 3] - (int)cv.w - rowterm));
+        const f32x2 a01 = pack2(__int2float_rn((int)r[g * 4 + 0] - (int)cv.x), __int2float_rn((int)r[g * 4 + 1] - (int)cv.y));
+        const f32x2 a23 = pack2(__int2float_rn((int)r[g * 4 + 2] - (int)cv.z), __int2float_rn((int)r[g * 4 + 3] - (int)cv.w));
         // acc * m as an FMA with a zero addend: the assembler contracts a packed multiply feeding a packed add into
         // one FMA (a single rounding) even with explicit rounding modifiers, which the reference does not do
         const f32x2 v01 = add2(fma2(a01, m01, ec.zero2), b01), v23 = add2(fma2(a23, m23, ec.zero2), b23);
@@ -396,13 +394,13 @@ __device__ __forceinline__ uint4 epi_chunk(const uint32_t* r, const uint4 rv, co
 // res_slot, result to out_slot) and / or (acc_row) writes the raw accumulators of a valid row out for the bit-exactness
 // tests.
 __device__ __noinline__ void epi_cold(uint32_t taddr, uint32_t res_slot, uint32_t out_slot, uint32_t a_m, uint32_t a_b,
-                                      uint32_t a_cc, const EpiExact& x, bool fix, int32_t* acc_row, int rowterm)
+                                      uint32_t a_cc, const EpiExact& x, bool fix, int32_t* acc_row)
 {
     uint32_t r[16];
     tc_ld16(taddr, r);
     if (acc_row) {
         #pragma unroll
-        for (int j = 0; j < 16; ++j) acc_row[j] = (int)r[j] - lds_s32(a_cc + j * 4) - rowterm;
+        for (int j = 0; j < 16; ++j) acc_row[j] = (int)r[j] - lds_s32(a_cc + j * 4);
     }
     if (!fix) return;
     const uint4 rv = x.fused ? lds128(res_slot) : make_uint4(0, 0, 0, 0);
@@ -410,7 +408,7 @@ __device__ __noinline__ void epi_cold(uint32_t taddr, uint32_t res_slot, uint32_
     uint32_t out[4] = {0, 0, 0, 0};
     #pragma unroll
     for (int j = 0; j < 16; ++j) {
-        const int q = exact_value((int)r[j] - lds_s32(a_cc + j * 4) - rowterm, lds_f32(a_m + j * 4), lds_f32(a_b + j * 4),
+        const int q = exact_value((int)r[j] - lds_s32(a_cc + j * 4), lds_f32(a_m + j * 4), lds_f32(a_b + j * 4),
                                   (resw[j >> 2] >> (8 * (j & 3))) & 0xffu, x);
         out[j >> 2] |= ((uint32_t)q & 0xffu) << (8 * (j & 3));
     }
@@ -466,10 +464,11 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int NIO = a.nio;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    // row sums (asymmetric weights): a 16-row B tile of ones at the very start, multiplied with every A slice into 16
-    // extra accumulator columns, so that column 0 of them is the sum of the row's activations over the valid taps
-    uint8_t* s_ones = smem;
-    uint8_t* s_wst = smem + (a.rowsum ? 16 * SWZ : 0);
+    // Asymmetric weights: sum x (w - zw) = sum x w + sum x (-zw).  The second sum comes from one or two more MMAs per
+    // K-slice against constant B tiles (every entry -zw, split in two int8 values when zw > 128) at the very start of
+    // shared memory, so the accumulator already holds it and the epilogue is unchanged.
+    uint8_t* s_zw = smem;
+    uint8_t* s_wst = smem + (size_t)a.nzw * L::B_BYTES;
     // weight-stationary launches: all K-slices of the (only) weight tile first, then a ring of activation tiles only
     const int stage_stride = a.bstat ? L::A_BYTES : L::STAGE_BYTES;
     uint8_t* ring = s_wst + (a.bstat ? (size_t)a.nslices * L::B_BYTES : 0);
@@ -507,17 +506,18 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         *s_lut_ok = ok;
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(a.tmem_cols) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(2 * BN) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    if (a.rowsum) {
-        // 16 identical logical rows of ones (in row-window mode: ones on the bytes that are real taps), each stored with
-        // the swizzle of its own row index
-        for (int i = threadIdx.x; i < 16 * SWZ; i += TC_THREADS) {
-            const int row = i / SWZ, k = i - row * SWZ;
+    if (a.nzw) {
+        // BN identical logical rows (in row-window mode: zero on the bytes of a slice that are no real taps), each stored
+        // with the swizzle of its own row index
+        for (int i = threadIdx.x; i < a.nzw * BN * SWZ; i += TC_THREADS) {
+            const int z = i / (BN * SWZ), j = i - z * (BN * SWZ);
+            const int row = j / SWZ, k = j - row * SWZ;
             const bool real = a.mask_cpad == 0 || ((k / a.mask_cpad) < a.mask_kw && (k % a.mask_cpad) < a.C);
             const int sw = SWZ == 128 ? (row & 7) : ((row >> 1) & 3);
-            s_ones[row * SWZ + ((((k >> 4) ^ sw) << 4) | (k & 15))] = real ? 1 : 0;
+            s_zw[z * L::B_BYTES + row * SWZ + ((((k >> 4) ^ sw) << 4) | (k & 15))] = real ? (uint8_t)(int8_t)a.zw_val[z] : (uint8_t)0;
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -604,9 +604,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             // 0 = unsigned 8-bit); both operands K-major (bits 15, 16 = 0); N >> 3 at bit 17; M >> 4 at bit 24
             const uint32_t id = (2u << 4) | ((uint32_t)a.a_signed << 7) | ((uint32_t)a.b_signed << 10) |
                                 ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
-            // the row-sum MMA: same A, B = the ones tile (unsigned), N = 16
-            const uint32_t id_rs = (2u << 4) | ((uint32_t)a.a_signed << 7) | ((uint32_t)(16 >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
-            const uint64_t d_ones = make_smem_desc<SWZ>(smem_u32(s_ones));
+            // the zero-point MMAs: same A, B = a constant int8 tile
+            const uint32_t id_zw = (2u << 4) | ((uint32_t)a.a_signed << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
             int st = 0; uint32_t ph = 0;                     // ring position
             bool alive = true;
             int it = 0;
@@ -630,11 +629,11 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     #pragma unroll
                     for (int k = 0; k < SWZ / 32; ++k)
                         tc_mma_i8(tacc, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), id, (s > 0 || k > 0) ? 1u : 0u);
-                    if (a.rowsum) {
-                        const uint32_t tacc_rs = tmem_base + (uint32_t)(2 * BN + buf * 16);
+                    for (int z = 0; z < a.nzw; ++z) {
+                        const uint64_t dz = make_smem_desc<SWZ>(smem_u32(s_zw + (size_t)z * L::B_BYTES));
                         #pragma unroll
                         for (int k = 0; k < SWZ / 32; ++k)
-                            tc_mma_i8(tacc_rs, da + (uint64_t)(k * 2), d_ones + (uint64_t)(k * 2), id_rs, (s > 0 || k > 0) ? 1u : 0u);
+                            tc_mma_i8(tacc, da + (uint64_t)(k * 2), dz + (uint64_t)(k * 2), id_zw, 1u);
                     }
                     tc_commit(&empty[cur]);            // slot reusable once these MMAs have read it
                 }
@@ -734,23 +733,15 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 ky1 = max(ky1, ky0);  kx1 = max(kx1, kx0);
                 cls = mvalid ? a.ycls[ky0 * 16 + ky1] * a.ncx + a.xcls[kx0 * 16 + kx1] : 0;
             }
-            int rowterm = 0;
-            if (a.rowsum) {
-                uint32_t rs;
-                asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(rs)
-                             : "r"(tmem_base + (uint32_t)(2 * BN + buf * 16) + ((uint32_t)(quad * 32) << 16)));
-                asm volatile("tcgen05.wait::ld.sync.aligned;" : "+r"(rs) :: "memory");
-                rowterm = a.zw * (int)rs;
-            }
             const int32_t* corr_row = s_cc + cls * BN;
             const uint32_t a_m = smem_u32(s_m), a_b = smem_u32(s_bterm), a_cc = smem_u32(corr_row);
             const uint32_t tacc = tmem_base + (uint32_t)(buf * BN) + ((uint32_t)(quad * 32) << 16);
+            // units in which this warp has real columns (a prefix: the last n-tile may reach beyond OC)
+            const int nact = min(UNITS, max(0, (a.OC - n0 - part * (UW / 4) + UW - 1) / UW));
             #pragma unroll 1
-            for (int us = 0; us < UNITS; ++us) {
+            for (int us = 0; us < nact; ++us) {
                 const uint32_t res_row = smem_u32(s_io + (size_t)(1 + ub) * IO_BYTES + row * UW);
                 const int colw = us * UW + part * (UW / 4);    // first column of this warp in this unit
-                const bool active = n0 + colw < a.OC;          // otherwise: padding columns, nothing to compute or store
-                if (active) {
                 uint32_t r[CPW][16];
                 #pragma unroll
                 for (int k = 0; k < CPW; ++k) tc_ld16_issue(tacc + (uint32_t)(colw + k * 16), r[k]);
@@ -767,8 +758,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     const EpiAddr ad = {a_m + col0 * 4, a_b + col0 * 4, a_cc + col0 * 4};
                     float dmax = always_fix ? 1.0f : 0.0f;
                     uint4 outv;
-                    if (use_lut) outv = epi_chunk<true>(r[k], lds128(res_row + ((((uint32_t)(part * CPW + k)) ^ sw_x) << 4)), ad, ec, rowterm, dmax);
-                    else         outv = epi_chunk<false>(r[k], make_uint4(0, 0, 0, 0), ad, ec, rowterm, dmax);
+                    if (use_lut) outv = epi_chunk<true>(r[k], lds128(res_row + ((((uint32_t)(part * CPW + k)) ^ sw_x) << 4)), ad, ec, dmax);
+                    else         outv = epi_chunk<false>(r[k], make_uint4(0, 0, 0, 0), ad, ec, dmax);
                     // an exact half (the reference rounds it away from zero), a value beyond the rounding constant, or
                     // no table: the chunk is left to the cold pass
                     const bool fix = __any_sync(0xffffffffu, dmax >= 0.5f);
@@ -783,9 +774,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         if (!fix && !dump_acc) continue;
                         epi_cold(tacc + (uint32_t)col0, res_row + ((((uint32_t)(part * CPW + k)) ^ sw_x) << 4),
                                  st_row + (((uint32_t)k ^ st_sw) << 4), a_m + col0 * 4, a_b + col0 * 4, a_cc + col0 * 4, ex, fix,
-                                 (dump_acc && mvalid && n0 + col0 < a.OC) ? a.acc_out + m * a.OC + n0 + col0 : nullptr, rowterm);
+                                 (dump_acc && mvalid && n0 + col0 < a.OC) ? a.acc_out + m * a.OC + n0 + col0 : nullptr);
                     }
-                }
                 }
                 if (fused) {
                     // this warp has finished reading the other operand's unit
@@ -793,21 +783,27 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     if (lane == 0) mbar_arrive(&io_empty[ub]);
                     if (++ub == NIO) { ub = 0; uph ^= 1u; }
                 }
-                if (us == UNITS - 1) {
-                    // this warp has finished reading the accumulator buffer
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&acc_empty[buf]);
-                }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the TMA store
                 __syncwarp();
                 if (lane == 0) {
                     const int row0 = quad * 32;
-                    if (active && row0 < a.tile_rows && m0 + row0 < a.M)
+                    if (row0 < a.tile_rows && m0 + row0 < a.M)
                         tma_store_3d(&tmY, st_base, n0 + colw, a.im2col == 2 ? row0 : (int)(m0 + row0), a.im2col == 2 ? tm : 0);
                     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                 }
             }
+            if (fused) {
+                // padding-only units: nothing to read, but the operand buffers still want this warp's release
+                for (int us = nact; us < UNITS; ++us) {
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&io_empty[ub]);
+                    if (++ub == NIO) { ub = 0; uph ^= 1u; }
+                }
+            }
+            // this warp has finished reading the accumulator buffer
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
         }
         if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     }
@@ -816,7 +812,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(a.tmem_cols) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
     }
 }
 
@@ -989,12 +985,11 @@ static bool load_driver_entry_points()
     return true;
 }
 
-// Tile width: the candidate that pads OC least (ties: the widest).  With row sums the accumulators need 16 more
-// columns per buffer, which leaves no room for two 256-column buffers in the 512 columns of tensor memory.
-static int pick_bn(int oc, bool rowsum)
+// Tile width: the candidate that pads OC least (ties: the widest).
+static int pick_bn(int oc)
 {
     int best = 64, waste = ((oc + 63) / 64) * 64 - oc;
-    for (int bn = 128; bn <= (rowsum ? 128 : 256); bn *= 2) {
+    for (int bn = 128; bn <= 256; bn *= 2) {
         const int w = ((oc + bn - 1) / bn) * bn - oc;
         if (w <= waste) { best = bn; waste = w; }
     }
@@ -1080,7 +1075,7 @@ bool conv_tc_eligible(const b200k_conv2d_params* p)
     }
     if (p->x.zero_point != 0) {
         const TapClasses tc = tap_classes(p);
-        if (!tc.ok || (size_t)tc.ncy * tc.ncx * pick_bn(p->oc, p->w.zero_point != 0) * 4 > 32 * 1024) return false;
+        if (!tc.ok || (size_t)tc.ncy * tc.ncx * pick_bn(p->oc) * 4 > 32 * 1024) return false;
     }
     return true;
 }
@@ -1104,7 +1099,7 @@ static int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUten
     const size_t budget = 227 * 1024;                                   // opt-in shared memory per CTA on sm_100
     TcArgs a2 = a;
     size_t rest = 1024 + L::CONST_BYTES + (size_t)a.ncls * BN * 4 + (size_t)(1 + a.nio) * L::IO_BYTES + (a.add_lut ? TC_LUT_BYTES + 256 : 0) +
-                  (a.rowsum ? 16 * SWZ : 0);
+                  (size_t)a.nzw * L::B_BYTES;
     // a third buffer for the fused Add's other operand (its loads then run a whole unit ahead of the epilogue) when the
     // ring keeps at least three stages
     if (a.nio == 2 && rest + L::IO_BYTES + 3 * L::STAGE_BYTES <= budget) { a2.nio = 3; rest += L::IO_BYTES; }
@@ -1118,7 +1113,6 @@ static int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUten
     int stages = (int)((budget - fixed) / stride);
     if (stages > L::MAX_STAGES) stages = L::MAX_STAGES;
     a2.stages = stages;
-    a2.tmem_cols = 2 * BN + (a.rowsum ? 32 : 0) <= 128 ? 128 : 2 * BN + (a.rowsum ? 32 : 0) <= 256 ? 256 : 512;
     if (a2.bstat) a2.stage_tx = (uint32_t)(a.stage_tx - L::B_BYTES);
     const size_t smem = fixed + (size_t)stages * stride;
     auto kern = conv_tc_kernel<BN, SWZ>;
@@ -1143,7 +1137,9 @@ int launch_conv_tc(const b200k_conv2d_params* p, cudaStream_t stream)
     a.prefix = (const int32_t*)p->packed;
     a.zx = p->x.zero_point;
     a.zw = p->w.scales ? 0 : p->w.zero_point;
-    a.rowsum = a.zw != 0;
+    a.nzw = a.zw == 0 ? 0 : (a.zw <= 128 ? 1 : 2);
+    a.zw_val[0] = -(a.zw < 128 ? a.zw : 128);
+    a.zw_val[1] = -(a.zw - 128);
     a.N = p->n; a.H = p->h; a.W = p->wd; a.C = p->c; a.OH = p->oh; a.OW = p->ow; a.OC = p->oc;
     a.KH = p->kh; a.KW = p->kw; a.sh = p->stride_h; a.sw = p->stride_w; a.pt = p->pad_top; a.pl = p->pad_left;
     a.dh = p->dil_h; a.dw = p->dil_w;
@@ -1196,7 +1192,7 @@ int launch_conv_tc(const b200k_conv2d_params* p, cudaStream_t stream)
     static const int debug_mode = getenv("B200K_TC_DEBUG") ? atoi(getenv("B200K_TC_DEBUG")) : 0;
     a.debug = debug_mode;
 
-    const int bn = pick_bn(p->oc, a.rowsum != 0);
+    const int bn = pick_bn(p->oc);
     a.ntn = (p->oc + bn - 1) / bn;
     CUtensorMap tmA, tmB;
     const CUtensorMapSwizzle swizzle = swz == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;

@@ -6,7 +6,8 @@ import os
 from . import _abi
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libb200k.so")
+# B200K_LIBRARY selects another build of the same library (A/B comparisons of kernel variants)
+LIB_PATH = os.environ.get("B200K_LIBRARY") or os.path.join(_HERE, "libb200k.so")
 _lib = None
 
 
