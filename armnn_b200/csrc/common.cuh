@@ -6,6 +6,7 @@
 // x86-64 without FMA contraction (cmake/GlobalConfig.cmake:107,126 of the Arm NN tree).
 #pragma once
 #include <cuda_runtime.h>
+#include <math.h>
 #include <stdint.h>
 #include <stdio.h>
 #include "../../include/b200k.h"
@@ -51,6 +52,36 @@ __device__ __forceinline__ int quantize_dev(float v, float scale, int zp, float 
     float q = __fadd_rn(__int2float_rn(zp), r);
     q = fminf(fmaxf(q, tlo), thi);
     return __float2int_rz(q);
+}
+
+// RN(1 / b): the double quotient rounded to float is within one ulp; the exact residuals 1 - b * y (products of two
+// 24-bit significands are exact in double) pick the nearest of the three candidates.
+inline float rn_reciprocal(float b)
+{
+    const float y = (float)(1.0 / (double)b);
+    const float cand[3] = {nextafterf(y, 0.f), y, nextafterf(y, INFINITY)};
+    float best = y;
+    double err = 1e300;
+    for (int i = 0; i < 3; ++i) {
+        const double e = fabs(1.0 - (double)b * (double)cand[i]);
+        if (e < err) { err = e; best = cand[i]; }
+    }
+    return best;
+}
+
+// The contraction epilogue v = fl(fl(acc * m) + b); q = clamp(zy + round_half_away(fl(v / sy)), lo, hi) without the
+// division unit: with y = RN(1 / sy) from the host, p = fl(v * y) and q = fma(fma(-p, sy, v), y, p) is the correctly
+// rounded quotient (Markstein); it is rounded with the 1.5 * 2^23 constant (halves to even) and only exact halves, or
+// values too large for the constant, go through roundf.  lo / hi: type range intersected with the activation clamp.
+__device__ __forceinline__ int requant_fast(int acc, float m, float b, bool has_bias, float sy, float inv_sy, float zy, float lo, float hi)
+{
+    float v = __fmul_rn(__int2float_rn(acc), m);
+    if (has_bias) v = __fadd_rn(v, b);
+    const float p = __fmul_rn(v, inv_sy);
+    const float q = __fmaf_rn(__fmaf_rn(-p, sy, v), inv_sy, p);
+    float n = __fsub_rn(__fadd_rn(q, 12582912.0f), 12582912.0f);
+    if (fabsf(__fsub_rn(q, n)) == 0.5f || !(fabsf(q) < 4194304.0f)) n = roundf(q);
+    return __float2int_rn(fminf(fmaxf(__fadd_rn(zy, n), lo), hi));
 }
 
 // v = float(q - zp) * scale

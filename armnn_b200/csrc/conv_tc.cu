@@ -952,21 +952,6 @@ static void make_lut_tag(const b200k_conv2d_params* p, uint32_t* tag)
     tag[10] = (uint32_t)out.clo;             tag[11] = (uint32_t)out.chi;
 }
 
-// RN(1 / b): the double quotient rounded to float is within one ulp; the exact residuals 1 - b * y (products of two
-// 24-bit significands are exact in double) pick the nearest of the three candidates.
-static float rn_reciprocal(float b)
-{
-    const float y = (float)(1.0 / (double)b);
-    const float cand[3] = {nextafterf(y, 0.f), y, nextafterf(y, INFINITY)};
-    float best = y;
-    double err = 1e300;
-    for (int i = 0; i < 3; ++i) {
-        const double e = fabs(1.0 - (double)b * (double)cand[i]);
-        if (e < err) { err = e; best = cand[i]; }
-    }
-    return best;
-}
-
 // ---- host side ---------------------------------------------------------------------------------------------------
 
 static PFN_cuTensorMapEncodeTiled_v12000 g_encode_tiled = nullptr;

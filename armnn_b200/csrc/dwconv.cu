@@ -82,6 +82,154 @@ __global__ void __launch_bounds__(256) dwconv_kernel(const DwArgs a)
     *(V*)(a.y + ob) = outv;
 }
 
+// ---- 3x3, depth multiplier 1, stride 1 or 2: the MobileNet shapes ------------------------------------------------
+//
+// A thread owns four channels (one 32-bit word of the NHWC pixel) and a strip of DW_STRIP output pixels of one output
+// row; consecutive threads walk the channel axis, so loads and stores are coalesced.  The three input rows of a
+// window column are transposed (two byte permutes per channel) into one word per channel [row0, row1, row2, -], so a
+// window column costs one dp4a per channel against the equally transposed weights, and a column is loaded and
+// transposed once however many windows it belongs to.  Zero points: out-of-image taps are replaced by the input zero
+// point (their (x - zx) is 0, as in the reference, which skips them), and
+//     sum (x - zx)(w - zw) = sum x w - zw sum x - (zx sum w - 9 zx zw)
+// with the column sums of x from one more dp4a per column and channel and the bracket a per-channel constant.
+constexpr int DW_STRIP = 8;
+
+template <bool XU, bool WU>
+__device__ __forceinline__ int dp4a_mixed(uint32_t x, uint32_t w, int acc)
+{
+    int d;
+    if (XU && WU)       asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(x), "r"(w), "r"(acc));
+    else if (XU && !WU) asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(x), "r"(w), "r"(acc));
+    else if (!XU && WU) asm("dp4a.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(x), "r"(w), "r"(acc));
+    else                asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(x), "r"(w), "r"(acc));
+    return d;
+}
+
+// bytes c of three words -> one word [a.c, b.c, c.c, a.0]
+__device__ __forceinline__ uint32_t gather3(uint32_t r0, uint32_t r1, uint32_t r2, int c)
+{
+    const uint32_t t = __byte_perm(r0, r1, ((4 + c) << 4) | c);
+    return __byte_perm(t, r2, ((4 + c) << 8) | 0x10);
+}
+
+struct Dw3Args {
+    DwArgs d;
+    float inv_sy, lo, hi;
+    int strips;                     // strips per output row
+};
+
+template <int STRIDE, bool XU, bool WU>
+__global__ void __launch_bounds__(256) dwconv3x3_kernel(const Dw3Args a3)
+{
+    const DwArgs& a = a3.d;
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= a.total) return;
+    const int cw = a.C / 4;
+    const int cq = (int)(idx % cw);                        // channel word
+    long long t = idx / cw;
+    const int strip = (int)(t % a3.strips); t /= a3.strips;
+    const int oy = (int)(t % a.OH);
+    const int n = (int)(t / a.OH);
+    const int ch0 = cq * 4;
+    const uint32_t zxw = 0x01010101u * (uint32_t)(a.zx & 0xff);
+
+    // weights of the four channels, transposed per window column; per-channel constants
+    uint32_t wcol[3][4];
+    int kconst[4];
+    float m[4], b[4];
+    {
+        uint32_t wr[3][3];
+        #pragma unroll
+        for (int ky = 0; ky < 3; ++ky)
+            #pragma unroll
+            for (int kx = 0; kx < 3; ++kx) wr[ky][kx] = *(const uint32_t*)(a.w + ((long long)ky * 3 + kx) * a.OC + ch0);
+        #pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            int wsum = 0;
+            #pragma unroll
+            for (int kx = 0; kx < 3; ++kx) {
+                wcol[kx][c] = gather3(wr[0][kx], wr[1][kx], wr[2][kx], c) & 0x00ffffffu;
+                wsum = WU ? (int)__dp4a(wcol[kx][c], 0x00010101u, (unsigned)wsum) : __dp4a((int)wcol[kx][c], 0x00010101, wsum);
+            }
+            kconst[c] = a.zx * wsum - 9 * a.zx * a.zw;
+            const int ch = ch0 + c;
+            m[c] = __fmul_rn(a.rq.sx, a.w_scales ? a.w_scales[ch] : a.w_scale);
+            b[c] = a.bias ? __fmul_rn(__int2float_rn(a.bias[ch]), a.b_scales ? a.b_scales[ch] : a.b_scale) : 0.f;
+        }
+    }
+    const int iy0 = oy * STRIDE - a.pt;
+    const bool rv0 = iy0 >= 0 && iy0 < a.H, rv1 = iy0 + 1 >= 0 && iy0 + 1 < a.H, rv2 = iy0 + 2 >= 0 && iy0 + 2 < a.H;
+    const uint8_t* row0 = a.x + (((long long)n * a.H + iy0) * a.W) * a.C + ch0;
+    const uint8_t* row1 = row0 + (long long)a.W * a.C;
+    const uint8_t* row2 = row1 + (long long)a.W * a.C;
+
+    // one window column: three rows of the channel word at input column ix, transposed; and its byte sums
+    uint32_t xcol[3][4];
+    int xsum[3][4];
+    auto load_col = [&](int slot, int ix) {
+        const bool cv = ix >= 0 && ix < a.W;
+        const long long off = (long long)ix * a.C;
+        const uint32_t r0 = (cv && rv0) ? *(const uint32_t*)(row0 + off) : zxw;
+        const uint32_t r1 = (cv && rv1) ? *(const uint32_t*)(row1 + off) : zxw;
+        const uint32_t r2 = (cv && rv2) ? *(const uint32_t*)(row2 + off) : zxw;
+        #pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            xcol[slot][c] = gather3(r0, r1, r2, c);
+            xsum[slot][c] = a.zw != 0 ? dp4a_mixed<XU, true>(xcol[slot][c], 0x00010101u, 0) : 0;
+        }
+    };
+
+    const int ox0 = strip * DW_STRIP;
+    int ix = ox0 * STRIDE - a.pl;
+    load_col(0, ix); load_col(1, ix + 1); load_col(2, ix + 2);
+    #pragma unroll
+    for (int s = 0; s < DW_STRIP; ++s) {
+        const int ox = ox0 + s;
+        if (ox >= a.OW) break;
+        if (s > 0) {
+            if (STRIDE == 1) {
+                #pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    xcol[0][c] = xcol[1][c]; xsum[0][c] = xsum[1][c];
+                    xcol[1][c] = xcol[2][c]; xsum[1][c] = xsum[2][c];
+                }
+                load_col(2, ix + 2);
+            } else {
+                #pragma unroll
+                for (int c = 0; c < 4; ++c) { xcol[0][c] = xcol[2][c]; xsum[0][c] = xsum[2][c]; }
+                load_col(1, ix + 1); load_col(2, ix + 2);
+            }
+        }
+        const long long ob = (((long long)n * a.OH + oy) * a.OW + ox) * a.OC + ch0;
+        uint32_t outw = 0;
+        #pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            int acc = 0;
+            #pragma unroll
+            for (int j = 0; j < 3; ++j) acc = dp4a_mixed<XU, WU>(xcol[j][c], wcol[j][c], acc);
+            acc -= a.zw * (xsum[0][c] + xsum[1][c] + xsum[2][c]) + kconst[c];
+            if (a.acc_out) a.acc_out[ob + c] = acc;
+            const int q = requant_fast(acc, m[c], b[c], a.bias != nullptr, a.rq.sy, a3.inv_sy, (float)a.rq.zy, a3.lo, a3.hi);
+            outw |= ((uint32_t)q & 0xffu) << (8 * c);
+        }
+        *(uint32_t*)(a.y + ob) = outw;
+        ix += STRIDE;
+    }
+}
+
+template <int STRIDE>
+static void launch_dw3(const Dw3Args& a, cudaStream_t s)
+{
+    const unsigned grid = (unsigned)div_up(a.d.total, 256);
+    if (a.d.x_u8) {
+        if (a.d.w_u8) dwconv3x3_kernel<STRIDE, true, true><<<grid, 256, 0, s>>>(a);
+        else          dwconv3x3_kernel<STRIDE, true, false><<<grid, 256, 0, s>>>(a);
+    } else {
+        if (a.d.w_u8) dwconv3x3_kernel<STRIDE, false, true><<<grid, 256, 0, s>>>(a);
+        else          dwconv3x3_kernel<STRIDE, false, false><<<grid, 256, 0, s>>>(a);
+    }
+}
+
 }  // namespace b200k
 
 using namespace b200k;
@@ -112,6 +260,19 @@ extern "C" int b200k_dwconv2d_q8(const b200k_conv2d_params* p, void* stream)
     const long long pixels = (long long)p->n * p->oh * p->ow;
     const uintptr_t al = (uintptr_t)a.x | (uintptr_t)a.w | (uintptr_t)a.y;
     cudaStream_t s = (cudaStream_t)stream;
+    if (a.dm == 1 && a.KH == 3 && a.KW == 3 && a.dh == 1 && a.dw == 1 && a.sh == a.sw && (a.sh == 1 || a.sh == 2) &&
+        (a.C % 4) == 0 && (al & 3) == 0) {
+        Dw3Args a3;
+        a3.d = a;
+        a3.inv_sy = rn_reciprocal(p->y.scale);
+        a3.lo = fmaxf(a.rq.tlo, (float)a.rq.clo);
+        a3.hi = fminf(a.rq.thi, (float)a.rq.chi);
+        a3.strips = (a.OW + DW_STRIP - 1) / DW_STRIP;
+        a3.d.total = (long long)p->n * p->oh * a3.strips * (a.C / 4);
+        if (a.sh == 1) launch_dw3<1>(a3, s);
+        else           launch_dw3<2>(a3, s);
+        return check_launch("dwconv3x3_kernel");
+    }
     if (a.dm == 1 && (a.C % 16) == 0 && (al & 15) == 0) {
         a.total = pixels * (a.OC / 16);
         dwconv_kernel<16><<<div_up(a.total, 256), 256, 0, s>>>(a);
