@@ -84,6 +84,18 @@ __device__ __forceinline__ int requant_fast(int acc, float m, float b, bool has_
     return __float2int_rn(fminf(fmaxf(__fadd_rn(zy, n), lo), hi));
 }
 
+// four 8-bit products summed into acc, each operand signed or unsigned
+template <bool XU, bool WU>
+__device__ __forceinline__ int dp4a_mixed(uint32_t x, uint32_t w, int acc)
+{
+    int d;
+    if (XU && WU)       asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(x), "r"(w), "r"(acc));
+    else if (XU && !WU) asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(x), "r"(w), "r"(acc));
+    else if (!XU && WU) asm("dp4a.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(x), "r"(w), "r"(acc));
+    else                asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(x), "r"(w), "r"(acc));
+    return d;
+}
+
 // v = float(q - zp) * scale
 __device__ __forceinline__ float dequantize_dev(int q, float scale, int zp)
 {

@@ -970,13 +970,30 @@ static bool load_driver_entry_points()
     return true;
 }
 
-// Tile width: the candidate that pads OC least (ties: the widest).
-static int pick_bn(int oc)
+static int sm_count()
 {
-    int best = 64, waste = ((oc + 63) / 64) * 64 - oc;
-    for (int bn = 128; bn <= 256; bn *= 2) {
-        const int w = ((oc + bn - 1) / bn) * bn - oc;
-        if (w <= waste) { best = bn; waste = w; }
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    }
+    return n;
+}
+
+// Tile width.  The kernel is persistent with one CTA per SM, and on the network shapes a tile's cost is its epilogue
+// (proportional to its columns) plus a fixed part, so the estimate of a launch is waves x (columns + fixed), with
+// waves = ceil(tiles / SMs): narrow tiles fill the SMs when there are few rows, wide tiles win when there are many
+// (fewer re-reads of the activation tile).  Ties go to the wider tile.
+static int pick_bn(int oc, long long ntm)
+{
+    const long long sms = sm_count();
+    int best = 64;
+    long long best_cost = -1;
+    for (int bn = 64; bn <= 256; bn *= 2) {
+        const long long tiles = ntm * ((oc + bn - 1) / bn);
+        const long long cost = ((tiles + sms - 1) / sms) * (bn + 96);
+        if (best_cost < 0 || cost <= best_cost) { best = bn; best_cost = cost; }
     }
     return best;
 }
@@ -1060,21 +1077,11 @@ bool conv_tc_eligible(const b200k_conv2d_params* p)
     }
     if (p->x.zero_point != 0) {
         const TapClasses tc = tap_classes(p);
-        if (!tc.ok || (size_t)tc.ncy * tc.ncx * pick_bn(p->oc) * 4 > 32 * 1024) return false;
+        if (!tc.ok || (size_t)tc.ncy * tc.ncx * pick_bn(p->oc, (M + TC_BM - 1) / TC_BM) * 4 > 32 * 1024) return false;
     }
     return true;
 }
 
-static int sm_count()
-{
-    static int n = 0;
-    if (n == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-    }
-    return n;
-}
 
 template <int BN, int SWZ>
 static int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmY, const CUtensorMap& tmR,
@@ -1177,7 +1184,7 @@ int launch_conv_tc(const b200k_conv2d_params* p, cudaStream_t stream)
     static const int debug_mode = getenv("B200K_TC_DEBUG") ? atoi(getenv("B200K_TC_DEBUG")) : 0;
     a.debug = debug_mode;
 
-    const int bn = pick_bn(p->oc);
+    const int bn = pick_bn(p->oc, a.ntm);
     a.ntn = (p->oc + bn - 1) / bn;
     CUtensorMap tmA, tmB;
     const CUtensorMapSwizzle swizzle = swz == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;

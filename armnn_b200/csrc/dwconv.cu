@@ -94,17 +94,6 @@ __global__ void __launch_bounds__(256) dwconv_kernel(const DwArgs a)
 // with the column sums of x from one more dp4a per column and channel and the bracket a per-channel constant.
 constexpr int DW_STRIP = 8;
 
-template <bool XU, bool WU>
-__device__ __forceinline__ int dp4a_mixed(uint32_t x, uint32_t w, int acc)
-{
-    int d;
-    if (XU && WU)       asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(x), "r"(w), "r"(acc));
-    else if (XU && !WU) asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(x), "r"(w), "r"(acc));
-    else if (!XU && WU) asm("dp4a.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(x), "r"(w), "r"(acc));
-    else                asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(x), "r"(w), "r"(acc));
-    return d;
-}
-
 // bytes c of three words -> one word [a.c, b.c, c.c, a.0]
 __device__ __forceinline__ uint32_t gather3(uint32_t r0, uint32_t r1, uint32_t r2, int c)
 {

@@ -10,6 +10,7 @@ namespace b200k {
 
 int launch_conv_dp4a(const b200k_conv2d_params* p, cudaStream_t stream);
 int conv2d_dispatch(const b200k_conv2d_params* p, cudaStream_t stream);
+bool conv_tc_eligible(const b200k_conv2d_params* p);
 
 struct BmmArgs {
     const void* x; const void* y; void* out; int32_t* acc_out;
@@ -81,6 +82,141 @@ extern "C" int b200k_batch_matmul_q8(const b200k_bmm_params* p, void* stream)
     return check_launch("bmm_generic_kernel");
 }
 
+// ---- FullyConnected with [N, K] weights that the tcgen05 kernel cannot take (N not a multiple of 16: classifier heads)
+//
+// A block owns FC_COLS output columns (one per warp) and FC_ROWS rows of x, which it stages in shared memory once.
+// A warp streams its weight row through registers 16 bytes per lane at a time and multiplies it with every staged row
+// (dp4a); the per-lane partial sums of the FC_ROWS rows are then reduced across the warp so that lane r ends up with
+// row r, applies the zero-point terms  sum (x - zx)(w - zw) = sum x w - zw sum x - zx sum w + K zx zw  and the
+// requantisation, and stores one byte.
+constexpr int FC_ROWS = 32, FC_COLS = 8, FC_KT = 2048;
+
+struct FcRowsArgs {
+    const uint8_t* x; const uint8_t* w; const int32_t* bias; uint8_t* y; int32_t* acc_out;
+    const float* w_scales; const float* b_scales;
+    float w_scale, b_scale;
+    int zx, zw, M, K, N;
+    Requant rq;
+    float inv_sy, lo, hi;
+};
+
+template <bool XU, bool WU>
+__global__ void __launch_bounds__(32 * FC_COLS) fc_rows_kernel(const FcRowsArgs a)
+{
+    extern __shared__ uint4 s_x[];                           // [FC_ROWS][kt / 16]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n = blockIdx.x * FC_COLS + warp;
+    const int m0 = blockIdx.y * FC_ROWS;
+    const int rows = min(FC_ROWS, a.M - m0);
+    int acc[FC_ROWS], xs[FC_ROWS];
+    #pragma unroll
+    for (int r = 0; r < FC_ROWS; ++r) { acc[r] = 0; xs[r] = 0; }
+    int wsum = 0;
+    for (int k0 = 0; k0 < a.K; k0 += FC_KT) {
+        const int kt = min(FC_KT, a.K - k0), kv = kt / 16;
+        __syncthreads();
+        for (int i = threadIdx.x; i < FC_ROWS * kv; i += 32 * FC_COLS) {
+            const int r = i / kv, c = i - r * kv;
+            s_x[i] = r < rows ? *(const uint4*)(a.x + (long long)(m0 + r) * a.K + k0 + c * 16) : make_uint4(0, 0, 0, 0);
+        }
+        __syncthreads();
+        if (n < a.N) {
+            for (int c = lane; c < kv; c += 32) {
+                const uint4 wv = *(const uint4*)(a.w + (long long)n * a.K + k0 + c * 16);
+                wsum = dp4a_mixed<WU, true>(wv.x, 0x01010101u, wsum);
+                wsum = dp4a_mixed<WU, true>(wv.y, 0x01010101u, wsum);
+                wsum = dp4a_mixed<WU, true>(wv.z, 0x01010101u, wsum);
+                wsum = dp4a_mixed<WU, true>(wv.w, 0x01010101u, wsum);
+                #pragma unroll
+                for (int r = 0; r < FC_ROWS; ++r) {
+                    const uint4 xv = s_x[r * kv + c];
+                    int t = acc[r];
+                    t = dp4a_mixed<XU, WU>(xv.x, wv.x, t);
+                    t = dp4a_mixed<XU, WU>(xv.y, wv.y, t);
+                    t = dp4a_mixed<XU, WU>(xv.z, wv.z, t);
+                    t = dp4a_mixed<XU, WU>(xv.w, wv.w, t);
+                    acc[r] = t;
+                    if (a.zw != 0) {
+                        int u = xs[r];
+                        u = dp4a_mixed<XU, true>(xv.x, 0x01010101u, u);
+                        u = dp4a_mixed<XU, true>(xv.y, 0x01010101u, u);
+                        u = dp4a_mixed<XU, true>(xv.z, 0x01010101u, u);
+                        u = dp4a_mixed<XU, true>(xv.w, 0x01010101u, u);
+                        xs[r] = u;
+                    }
+                }
+            }
+        }
+    }
+    if (n >= a.N) return;
+    // warp reduction that leaves row r's total in lane r: halve the row set five times
+    #pragma unroll
+    for (int r = 0; r < FC_ROWS; ++r) acc[r] -= a.zw * xs[r];
+    #pragma unroll
+    for (int off = 16, cnt = FC_ROWS; off >= 1; off >>= 1, cnt >>= 1) {
+        const bool upper = (lane & off) != 0;
+        #pragma unroll
+        for (int r = 0; r < cnt / 2; ++r) {
+            const int keep = upper ? acc[r + cnt / 2] : acc[r];
+            const int send = upper ? acc[r] : acc[r + cnt / 2];
+            acc[r] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+        }
+    }
+    #pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) wsum += __shfl_xor_sync(0xffffffffu, wsum, off);
+    // step "off" sends the half of the remaining rows whose bit "off" differs from the lane's: lane l ends with row l
+    const int r = lane;
+    if (r >= rows) return;
+    const int total = acc[0] - a.zx * wsum + a.K * a.zx * a.zw;
+    const long long o = (long long)(m0 + r) * a.N + n;
+    if (a.acc_out) a.acc_out[o] = total;
+    const float m = __fmul_rn(a.rq.sx, a.w_scales ? a.w_scales[n] : a.w_scale);
+    const float b = a.bias ? __fmul_rn(__int2float_rn(a.bias[n]), a.b_scales ? a.b_scales[n] : a.b_scale) : 0.f;
+    a.y[o] = (uint8_t)requant_fast(total, m, b, a.bias != nullptr, a.rq.sy, a.inv_sy, (float)a.rq.zy, a.lo, a.hi);
+}
+
+static bool fc_rows_eligible(const b200k_fc_params* p)
+{
+    if (!p->x.data || !p->w.data || !p->y.data) return false;
+    if (!is_q8(p->x.dtype) || !is_q8(p->w.dtype) || !is_q8(p->y.dtype)) return false;
+    if (p->bias.data && p->bias.dtype != B200K_S32) return false;
+    if (p->k % 16 != 0 || ((((uintptr_t)p->x.data) | ((uintptr_t)p->w.data)) & 15) != 0) return false;
+    if (p->w.scales && p->w.zero_point != 0) return false;
+    return true;
+}
+
+static int launch_fc_rows(const b200k_fc_params* p, cudaStream_t stream)
+{
+    FcRowsArgs a;
+    a.x = (const uint8_t*)p->x.data; a.w = (const uint8_t*)p->w.data; a.bias = (const int32_t*)p->bias.data;
+    a.y = (uint8_t*)p->y.data; a.acc_out = p->acc_out;
+    a.w_scales = p->w.scales; a.b_scales = p->bias.scales; a.w_scale = p->w.scale; a.b_scale = p->bias.scale;
+    a.zx = p->x.zero_point; a.zw = p->w.scales ? 0 : p->w.zero_point;
+    a.M = p->m; a.K = p->k; a.N = p->n;
+    a.rq = make_requant(p->x.scale, p->y, p->clamp_lo, p->clamp_hi);
+    a.inv_sy = rn_reciprocal(p->y.scale);
+    a.lo = fmaxf(a.rq.tlo, (float)a.rq.clo);
+    a.hi = fminf(a.rq.thi, (float)a.rq.chi);
+    const int kt = p->k < FC_KT ? p->k : FC_KT;
+    const size_t smem = (size_t)FC_ROWS * kt;
+    const dim3 grid(div_up(p->n, FC_COLS), div_up(p->m, FC_ROWS), 1);
+    const bool xu = p->x.dtype == B200K_U8, wu = p->w.dtype == B200K_U8;
+    #define B200K_FC_ROWS(XU, WU)                                                                                      \
+        do {                                                                                                           \
+            static bool configured = false;                                                                            \
+            if (!configured) {                                                                                         \
+                B200K_CUDA(cudaFuncSetAttribute(fc_rows_kernel<XU, WU>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
+                                                FC_ROWS * FC_KT));                                                     \
+                configured = true;                                                                                     \
+            }                                                                                                          \
+            fc_rows_kernel<XU, WU><<<grid, 32 * FC_COLS, smem, stream>>>(a);                                           \
+        } while (0)
+    if (xu) { if (wu) B200K_FC_ROWS(true, true); else B200K_FC_ROWS(true, false); }
+    else    { if (wu) B200K_FC_ROWS(false, true); else B200K_FC_ROWS(false, false); }
+    #undef B200K_FC_ROWS
+    return check_launch("fc_rows_kernel");
+}
+
 extern "C" int b200k_fully_connected_q8(const b200k_fc_params* p, void* stream)
 {
     B200K_REQUIRE(p, B200K_E_INVALID, "fully_connected_q8: null params");
@@ -94,6 +230,8 @@ extern "C" int b200k_fully_connected_q8(const b200k_fc_params* p, void* stream)
         c.kh = c.kw = 1; c.stride_h = c.stride_w = 1; c.dil_h = c.dil_w = 1;
         c.clamp_lo = p->clamp_lo; c.clamp_hi = p->clamp_hi; c.acc_out = p->acc_out; c.algo = p->algo;
         c.packed = p->packed;
+        // the tcgen05 kernel when it can take the shape; otherwise the row kernel; the CUDA-core convolution for the rest
+        if (p->algo == 0 && !conv_tc_eligible(&c) && fc_rows_eligible(p)) return launch_fc_rows(p, (cudaStream_t)stream);
         return conv2d_dispatch(&c, (cudaStream_t)stream);
     }
     B200K_REQUIRE(p->x.data && p->w.data && p->y.data, B200K_E_INVALID, "fully_connected_q8: null tensor pointer");

@@ -196,7 +196,10 @@ extern "C" int b200k_pool2d_q8(const b200k_pool2d_params* p, void* stream)
     a.ph = p->pool_h; a.pw = p->pool_w; a.sh = p->stride_h; a.sw = p->stride_w;
     a.pt = p->pad_top; a.pb = p->pad_bottom; a.pl = p->pad_left; a.pr = p->pad_right;
     a.type = p->pool_type; a.exclude = p->padding_method == 1;
-    const int vec = pick_vec(p->x, p->y, p->c);
+    int vec = pick_vec(p->x, p->y, p->c);
+    // few outputs with large windows (global average pooling): narrower vectors give more threads to hide the latency
+    // of the window's loads
+    if (vec == 16 && (long long)p->n * p->oh * p->ow * (p->c / 16) < 148 * 1024) vec = 4;
     a.total = (long long)p->n * p->oh * p->ow * (p->c / vec);
     cudaStream_t s = (cudaStream_t)stream;
     if (vec == 16 && p->pool_type == 0 && p->x.dtype == p->y.dtype && p->x.scale == p->y.scale &&

@@ -1,6 +1,7 @@
 """Device-time micro-benchmarks of single workloads and of whole graphs, layer by layer, through the public API
 (INetwork -> Optimize -> IRuntime.LoadNetwork -> LoadedNetwork).  Inputs are seeded random bytes, resident in device
-memory; times are CUDA-event durations on the network's stream (best of --reps after 3 warm-up passes).
+memory; times are CUDA-event durations on the network's stream (best of --reps after 3 warm-up passes); single
+workloads are replayed as a CUDA graph so that the host's launch latency stays out of the interval.
 
     python -m armnn_b200.microbench conv --n 64 --h 56 --w 56 --c 64 --oc 256 --k 1 --relu --add
     python -m armnn_b200.microbench conv --n 32 --h 32 --w 32 --c 8192 --oc 2048 --k 1 --relu      # a large GEMM
@@ -29,12 +30,18 @@ def _fill_inputs(ln, torch, seed=1000):
         t.copy_(torch.from_numpy(host).cuda())
 
 
-def _load(net):
+def _load(net, graph=False):
+    """graph: replay the workload queue as one CUDA graph, which takes the host's launch latency (tens of
+    microseconds per workload from Python) out of the measured interval."""
     import torch
     from armnn_b200 import network
     rt = network.IRuntime.Create(0)
     ln = rt.GetLoadedNetwork(rt.LoadNetwork(network.Optimize(net)))
     _fill_inputs(ln, torch)
+    if graph:
+        ln.Execute()
+        torch.cuda.synchronize()
+        ln.CaptureGraph()
     return ln, torch
 
 
@@ -121,7 +128,7 @@ def main(argv=None):
 
     if args.cmd == "conv":
         net, macs = conv_graph(args.n, args.h, args.w, args.c, args.oc, args.k, args.stride, args.relu, args.add)
-        ln, torch = _load(net)
+        ln, torch = _load(net, graph=True)
         ms = _time_whole(ln, torch, args.reps)
         out = ln.output_tensor(0)
         nbytes = args.n * args.h * args.w * args.c + out.numel() * (2 if args.add else 1)
@@ -132,7 +139,7 @@ def main(argv=None):
         cases = [(args.m, args.k, args.n)] if args.cmd == "fc" else [(m, k, k) for k in (1024, 4096) for m in (1, 16, 256, 4096)]
         for m, k, n in cases:
             net, info = configs.fc_sweep_case(m, k, n)
-            ln, torch = _load(net)
+            ln, torch = _load(net, graph=True)
             ms = _time_whole(ln, torch, getattr(args, "reps", 5))
             nbytes = m * k + n * k + m * n
             print("fc  M=%-5d K=%-5d N=%-5d  %.4f ms  %8.1f TOP/s  %7.0f GB/s" % (m, k, n, ms, 2.0 * info["macs"] / ms / 1e9, nbytes / ms / 1e6))
@@ -152,7 +159,10 @@ def main(argv=None):
                 print("%-22s %-12s %-22s %-22s %8.3f %8.1f %8.0f" % (layer.name, l[1], l[2], l[3], t, 2 * l[4] / t / 1e9 if l[4] else 0.0, (inb + outb) / t / 1e6))
             else:
                 print("%-22s %-12s %-22s %-22s %8.3f" % (layer.name, entry, "", "", t))
-        print("sum of layers %.3f ms; whole queue back to back %.3f ms" % (total, _time_whole(ln, torch, args.reps)))
+        eager = _time_whole(ln, torch, args.reps)
+        ln.CaptureGraph()
+        print("sum of layers %.3f ms; whole queue back to back %.3f ms eager, %.3f ms as one CUDA graph" % (
+            total, eager, _time_whole(ln, torch, args.reps)))
     elif args.cmd == "qlstm":
         net, info = configs.qlstm_stack(batch=args.batch)
         ln, torch = _load(net)

@@ -63,6 +63,13 @@ def fc_cases():
     c["u8_per_tensor_relu"] = lambda: random_fc_case(37, 8, 128, 64, x_dtype=U8, w_dtype=U8, y_dtype=U8, per_axis=False,
                                                      x_q=(0.03, 120), act=(1, 0., 0.))
     c["classifier_2048_1001"] = lambda: random_fc_case(38, 4, 2048, 1001, per_axis=False)
+    # the row kernel: N not a multiple of 16, several row chunks and K chunks, every operand signedness, zero points
+    c["rows_m70_k2048_n1001"] = lambda: random_fc_case(39, 70, 2048, 1001, per_axis=False)
+    c["rows_m33_k4112_n40_per_axis"] = lambda: random_fc_case(40, 33, 4112, 40)
+    c["rows_u8_zero_points"] = lambda: random_fc_case(41, 37, 1280, 1001, x_dtype=U8, w_dtype=U8, y_dtype=U8, per_axis=False,
+                                                      x_q=(0.03, 119), act=(1, 0, 0))
+    c["rows_s8x_u8w"] = lambda: random_fc_case(42, 9, 256, 21, w_dtype=U8, per_axis=False)
+    c["rows_u8x_s8w"] = lambda: random_fc_case(43, 9, 256, 21, x_dtype=U8, y_dtype=U8, per_axis=True, x_q=(0.03, 100))
     return c
 
 
