@@ -487,6 +487,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     int32_t* s_cc = (int32_t*)(tmem_slot + 4);              // [classes][BN] zero-point corrections
     uint8_t* s_lut = (uint8_t*)(((uintptr_t)(s_cc + a.ncls * BN) + 255) & ~(uintptr_t)255);   // fused-add table, 256-byte aligned
 
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");     // the next kernel of the stream may begin its set-up
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int ntn = a.ntn;                                  // n-tiles; the last one may reach beyond OC (zero weights, clipped stores)
     const int ntiles = ntn * a.ntm;
@@ -497,13 +498,6 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         for (int b = 0; b < L::MAX_IO; ++b) { mbar_init(&io_full[b], 1); mbar_init(&io_empty[b], TC_EPI_WARPS); }
         mbar_init(w_full, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        // a table is used only if it was built for exactly this launch's quantisation parameters
-        uint32_t ok = a.add_lut != nullptr;
-        if (ok) {
-            const uint32_t* tag = (const uint32_t*)(a.add_lut + TC_LUT_BYTES);
-            for (int i = 0; i < TC_LUT_TAG_WORDS; ++i) ok &= (tag[i] == a.lut_tag[i]);
-        }
-        *s_lut_ok = ok;
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(2 * BN) : "memory");
@@ -525,15 +519,6 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const bool lut_ok = *s_lut_ok != 0;
-    if (a.add_lut) {                                        // uniform over the CTA
-        if (lut_ok) {
-            const uint4* src = (const uint4*)a.add_lut;
-            uint4* dst = (uint4*)s_lut;
-            for (int i = threadIdx.x; i < TC_LUT_BYTES / 16; i += TC_THREADS) dst[i] = src[i];
-        }
-        __syncthreads();
-    }
 
     if (warp == 0) {
         // ===================== TMA producer =====================
@@ -541,6 +526,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             int st = 0; uint32_t ph = 0;                     // ring position: stage and its phase bit
             int ub = 0; uint32_t uph = 0;                    // unit-buffer position (kept without divisions)
             bool alive = true;
+            // weights, scales, bias and tables do not depend on the previous kernel of the stream; activations do
             if (a.bstat && a.debug != 2) {
                 mbar_expect_tx(w_full, (uint32_t)a.nslices * L::B_BYTES);
                 for (int s = 0; s < a.nslices; ++s) {
@@ -548,6 +534,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     tma_load_2d(s_wst + (size_t)s * L::B_BYTES, &tmB, w_full, tap * a.kstride + (s - tap * a.cchunks) * SWZ, 0);
                 }
             }
+            asm volatile("griddepcontrol.wait;" ::: "memory");
             for (int t = blockIdx.x; t < ntiles && alive; t += gridDim.x) {
                 const int n0 = (t % ntn) * BN;
                 const int tm = t / ntn;
@@ -654,6 +641,25 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const uint32_t sw_x = UW == 128 ? (uint32_t)(row & 7) : (uint32_t)((row >> 1) & 3);   // TMA swizzle of this row
         const int pw = a.KW + 1;
         const bool fused = a.res != nullptr;
+        // The fused-add table is staged by the epilogue warps alone, while the producer and the MMA issuer already work
+        // on the first tile.  A table is used only if it was built for exactly this launch's quantisation parameters.
+        bool lut_ok = false;
+        if (a.add_lut) {
+            if (etid == 0) {
+                uint32_t ok = 1;
+                const uint32_t* tag = (const uint32_t*)(a.add_lut + TC_LUT_BYTES);
+                for (int i = 0; i < TC_LUT_TAG_WORDS; ++i) ok &= (tag[i] == a.lut_tag[i]);
+                *s_lut_ok = ok;
+            }
+            epi_barrier();
+            lut_ok = *s_lut_ok != 0;
+            if (lut_ok) {
+                const uint4* src = (const uint4*)a.add_lut;
+                uint4* dst = (uint4*)s_lut;
+                for (int i = etid; i < TC_LUT_BYTES / 16; i += 32 * TC_EPI_WARPS) dst[i] = src[i];
+            }
+            epi_barrier();
+        }
         const bool use_lut = fused && lut_ok;
         const bool always_fix = fused && !lut_ok;            // no table: every chunk takes the reference arithmetic
         const bool dump_acc = a.acc_out != nullptr;
@@ -805,7 +811,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[buf]);
         }
-        if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+        // shared memory may go once the last store has read it; its global writes complete with the kernel
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
     }
 
     tc_fence_before();
@@ -1115,7 +1122,20 @@ static int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUten
     }
     const long long tiles = (long long)a.ntn * a.ntm;
     const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
-    kern<<<grid, TC_THREADS, smem, stream>>>(tmA, tmB, tmY, tmR, a2);
+    // Programmatic dependent launch: the grid may start while its predecessor in the stream drains (its set-up touches
+    // nothing the predecessor writes); the producer thread waits for the predecessor before its first activation load.
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3((unsigned)grid, 1, 1);
+    cfg.blockDim = dim3(TC_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    B200K_CUDA(cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmY, tmR, a2));
     return check_launch("conv_tc_kernel");
 }
 
