@@ -130,6 +130,71 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity)
         else if (now - t0 > TC_WAIT_LIMIT_CYCLES) return false;
     }
 }
+// The single-thread roles (TMA producer, MMA issuer) run one dependent instruction chain per K-slice; everything in
+// that chain is latency.  They test a barrier once inline by shared address and only fall into the bounded polling
+// loop when it is not ready yet.
+__device__ __forceinline__ bool mbar_test(uint32_t bar_saddr, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                 "selp.b32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar_saddr), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_slow(uint32_t bar_saddr, uint32_t parity)
+{
+    long long t0 = 0;
+    for (;;) {
+        #pragma unroll 1
+        for (int i = 0; i < 32; ++i)
+            if (mbar_test(bar_saddr, parity)) return true;
+        const long long now = clock64();
+        if (t0 == 0) t0 = now;
+        else if (now - t0 > TC_WAIT_LIMIT_CYCLES) return false;
+    }
+}
+__device__ __forceinline__ bool mbar_wait_fast(uint32_t bar_saddr, uint32_t parity)
+{
+    return mbar_test(bar_saddr, parity) || mbar_wait_slow(bar_saddr, parity);
+}
+__device__ __forceinline__ void tma_load_2d_s(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y)
+{
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tma_load_4d_s(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2, int c3)
+{
+    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+                 ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+__device__ __forceinline__ void tma_load_im2col_s(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c, int w, int h,
+                                                  int n, uint16_t off_w, uint16_t off_h)
+{
+    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes"
+                 " [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};"
+                 ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(c), "r"(w), "r"(h), "r"(n), "h"(off_w), "h"(off_h) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx_s(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_s(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_commit_s(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_i8_acc(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc)   // D += A B
+{
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "setp.eq.b32 p, 0, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc) : "memory");
+}
+
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y)
 {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
@@ -526,6 +591,11 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             int st = 0; uint32_t ph = 0;                     // ring position: stage and its phase bit
             int ub = 0; uint32_t uph = 0;                    // unit-buffer position (kept without divisions)
             bool alive = true;
+            const uint32_t ring_addr = smem_u32(ring), full_addr = smem_u32(full), empty_addr = smem_u32(empty);
+            const int nslices = a.nslices, cchunks = a.cchunks, kstride = a.kstride, mode = a.im2col, debug = a.debug;
+            const int dh = a.dh, dw = a.dw, KW = a.KW;
+            const bool bstat = a.bstat != 0;
+            const uint32_t stage_tx = a.stage_tx;
             // weights, scales, bias and tables do not depend on the previous kernel of the stream; activations do
             if (a.bstat && a.debug != 2) {
                 mbar_expect_tx(w_full, (uint32_t)a.nslices * L::B_BYTES);
@@ -551,26 +621,28 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     w0 = ox * a.sw - a.pl;
                     h0 = oy * a.sh - a.pt;
                 }
-                int tap = 0, cc = 0;                              // slice = (filter tap, channel chunk)
-                for (int s = 0; s < a.nslices; ++s) {
-                    if (!mbar_wait(&empty[st], ph ^ 1u)) { atomicExch(&g_tc_status, 1); alive = false; break; }
+                // slice = (filter tap (ky, kx), channel chunk); everything the loop needs is kept incrementally
+                int ky = 0, kx = 0, cc = 0, kcol = 0;             // kcol: the slice's first byte in a weight row
+                for (int s = 0; s < nslices; ++s) {
+                    if (!mbar_wait_fast(empty_addr + st * 8, ph ^ 1u)) { atomicExch(&g_tc_status, 1); alive = false; break; }
+                    const uint32_t sa = ring_addr + st * stage_stride;
+                    const uint32_t fb = full_addr + st * 8;
                     const int c0 = cc * SWZ;
-                    uint8_t* sa = ring + st * stage_stride;
-                    uint8_t* sb = sa + L::A_BYTES;
-                    const int cur = st, cur_tap = tap;
-                    if (++st == STAGES) { st = 0; ph ^= 1u; }
-                    if (++cc == a.cchunks) { cc = 0; ++tap; }
-                    if (a.debug == 2) { mbar_arrive(&full[cur]); continue; }
-                    mbar_expect_tx(&full[cur], a.stage_tx);
-                    if (a.im2col == 2) {
-                        tma_load_4d(sa, &tmA, &full[cur], 0, 0, h0 + cur_tap * a.dh, nimg);   // tap = filter row
-                    } else if (a.im2col) {
-                        const int ky = cur_tap / a.KW, kx = cur_tap - ky * a.KW;
-                        tma_load_im2col(sa, &tmA, &full[cur], c0, w0, h0, nimg, (uint16_t)(kx * a.dw), (uint16_t)(ky * a.dh));
+                    if (debug == 2) {
+                        mbar_arrive_s(fb);
                     } else {
-                        tma_load_2d(sa, &tmA, &full[cur], c0, (int)m0);
+                        mbar_expect_tx_s(fb, stage_tx);
+                        if (mode == 2)      tma_load_4d_s(sa, &tmA, fb, 0, 0, h0 + ky * dh, nimg);          // slice = filter row
+                        else if (mode == 1) tma_load_im2col_s(sa, &tmA, fb, c0, w0, h0, nimg, (uint16_t)(kx * dw), (uint16_t)(ky * dh));
+                        else                tma_load_2d_s(sa, &tmA, fb, c0, (int)m0);
+                        if (!bstat) tma_load_2d_s(sa + L::A_BYTES, &tmB, fb, kcol + c0, n0);
                     }
-                    if (!a.bstat) tma_load_2d(sb, &tmB, &full[cur], cur_tap * a.kstride + c0, n0);
+                    if (++st == STAGES) { st = 0; ph ^= 1u; }
+                    if (++cc == cchunks) {
+                        cc = 0; kcol += kstride;
+                        if (mode == 2) ++ky;
+                        else if (++kx == KW) { kx = 0; ++ky; }
+                    }
                 }
                 if (a.res && alive) {
                     // the fused Add's other operand, one unit at a time, into the buffer the epilogue will overwrite
@@ -596,7 +668,16 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             int st = 0; uint32_t ph = 0;                     // ring position
             bool alive = true;
             int it = 0;
-            if (a.bstat && a.debug != 2 && !mbar_wait(w_full, 0)) { atomicExch(&g_tc_status, 7); alive = false; }
+            const uint32_t full_addr = smem_u32(full), empty_addr = smem_u32(empty);
+            const int nslices = a.nslices, nzw = a.nzw, debug = a.debug;
+            const bool bstat = a.bstat != 0;
+            // descriptors differ from stage to stage only in the 14-bit start-address field: one add per slice
+            const uint64_t da0 = make_smem_desc<SWZ>(smem_u32(ring));
+            const uint64_t db0 = make_smem_desc<SWZ>(bstat ? smem_u32(s_wst) : smem_u32(ring) + L::A_BYTES);
+            const uint64_t dstage = (uint64_t)(stage_stride >> 4);
+            const uint64_t dwslice = (uint64_t)(L::B_BYTES >> 4);
+            const uint64_t dz0 = make_smem_desc<SWZ>(smem_u32(s_zw));
+            if (bstat && debug != 2 && !mbar_wait(w_full, 0)) { atomicExch(&g_tc_status, 7); alive = false; }
             tc_fence_after();
             for (int t = blockIdx.x; t < ntiles && alive; t += gridDim.x, ++it) {
                 const int buf = it & 1;
@@ -604,25 +685,26 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 if (!mbar_wait(&acc_empty[buf], (((uint32_t)it >> 1) & 1u) ^ 1u)) { atomicExch(&g_tc_status, 4); break; }
                 tc_fence_after();
                 const uint32_t tacc = tmem_base + (uint32_t)(buf * BN);
-                for (int s = 0; s < a.nslices; ++s) {
-                    if (!mbar_wait(&full[st], ph)) { atomicExch(&g_tc_status, 2); alive = false; break; }
+                uint64_t dbs = db0;                              // stationary weights: the slice's tile
+                for (int s = 0; s < nslices; ++s) {
+                    if (!mbar_wait_fast(full_addr + st * 8, ph)) { atomicExch(&g_tc_status, 2); alive = false; break; }
                     tc_fence_after();
-                    const int cur = st;
+                    const uint32_t eb = empty_addr + st * 8;
+                    const uint64_t da = da0 + dstage * (uint64_t)st;
+                    const uint64_t db = bstat ? dbs : db0 + dstage * (uint64_t)st;
+                    dbs += dwslice;
                     if (++st == STAGES) { st = 0; ph ^= 1u; }
-                    if (a.debug == 1) { mbar_arrive(&empty[cur]); continue; }
-                    const uint32_t sa = smem_u32(ring + cur * stage_stride);
-                    const uint64_t da = make_smem_desc<SWZ>(sa);
-                    const uint64_t db = make_smem_desc<SWZ>(a.bstat ? smem_u32(s_wst + (size_t)s * L::B_BYTES) : sa + L::A_BYTES);
+                    if (debug == 1) { mbar_arrive_s(eb); continue; }
+                    if (s == 0) tc_mma_i8(tacc, da, db, id, 0u);
+                    else        tc_mma_i8_acc(tacc, da, db, id);
                     #pragma unroll
-                    for (int k = 0; k < SWZ / 32; ++k)
-                        tc_mma_i8(tacc, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), id, (s > 0 || k > 0) ? 1u : 0u);
-                    for (int z = 0; z < a.nzw; ++z) {
-                        const uint64_t dz = make_smem_desc<SWZ>(smem_u32(s_zw + (size_t)z * L::B_BYTES));
+                    for (int k = 1; k < SWZ / 32; ++k) tc_mma_i8_acc(tacc, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), id);
+                    for (int z = 0; z < nzw; ++z) {
+                        const uint64_t dz = dz0 + dwslice * (uint64_t)z;
                         #pragma unroll
-                        for (int k = 0; k < SWZ / 32; ++k)
-                            tc_mma_i8(tacc, da + (uint64_t)(k * 2), dz + (uint64_t)(k * 2), id_zw, 1u);
+                        for (int k = 0; k < SWZ / 32; ++k) tc_mma_i8_acc(tacc, da + (uint64_t)(k * 2), dz + (uint64_t)(k * 2), id_zw);
                     }
-                    tc_commit(&empty[cur]);            // slot reusable once these MMAs have read it
+                    tc_commit_s(eb);                   // slot reusable once these MMAs have read it
                 }
                 if (alive) tc_commit(&acc_full[buf]);  // accumulator of this tile complete
             }
