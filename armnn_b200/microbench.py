@@ -45,7 +45,9 @@ def _load(net, graph=False):
     return ln, torch
 
 
-def _time_whole(ln, torch, reps):
+def _time_whole(ln, torch, reps, inner=1):
+    """Best of `reps` intervals of `inner` back-to-back passes each (per pass).  Several passes per interval keep the
+    launch latency of the first one from dominating a short workload."""
     for _ in range(3):
         ln.Execute()
     torch.cuda.synchronize()
@@ -54,10 +56,11 @@ def _time_whole(ln, torch, reps):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         with torch.cuda.stream(ln.stream):
             e0.record()
-            ln.Execute()
+            for _ in range(inner):
+                ln.Execute()
             e1.record()
         torch.cuda.synchronize()
-        best = min(best, e0.elapsed_time(e1))
+        best = min(best, e0.elapsed_time(e1) / inner)
     return best
 
 
@@ -129,7 +132,7 @@ def main(argv=None):
     if args.cmd == "conv":
         net, macs = conv_graph(args.n, args.h, args.w, args.c, args.oc, args.k, args.stride, args.relu, args.add)
         ln, torch = _load(net, graph=True)
-        ms = _time_whole(ln, torch, args.reps)
+        ms = _time_whole(ln, torch, args.reps, inner=10)
         out = ln.output_tensor(0)
         nbytes = args.n * args.h * args.w * args.c + out.numel() * (2 if args.add else 1)
         print("conv %dx%d/%d  [%d,%d,%d,%d] -> %s%s  %.4f ms  %.1f TOP/s  %.0f GB/s (tensors once)" % (
@@ -140,7 +143,7 @@ def main(argv=None):
         for m, k, n in cases:
             net, info = configs.fc_sweep_case(m, k, n)
             ln, torch = _load(net, graph=True)
-            ms = _time_whole(ln, torch, getattr(args, "reps", 5))
+            ms = _time_whole(ln, torch, getattr(args, "reps", 5), inner=10)
             nbytes = m * k + n * k + m * n
             print("fc  M=%-5d K=%-5d N=%-5d  %.4f ms  %8.1f TOP/s  %7.0f GB/s" % (m, k, n, ms, 2.0 * info["macs"] / ms / 1e9, nbytes / ms / 1e6))
     elif args.cmd == "layers":
