@@ -395,7 +395,8 @@ __device__ __forceinline__ uint32_t lds_u8(uint32_t addr)
 struct EpiConsts {
     f32x2 inv2, nsy2, magic2, zy2, zero2;        // pairs of: RN(1 / sy), -sy, the rounding constant, zero point (+ bias), 0
     float lo, hi;                                // clamp bounds in the biased domain (MAGIC + ...)
-    uint32_t lut;                                // shared address of the fused-add table minus 0x4B400000 * pitch
+    uint32_t lut;                                // shared address of the fused-add table
+    bool sat, sat_u8;                            // the clamp is exactly the range of the (unsigned / signed) 8-bit output type
 };
 
 // shared-memory addresses of the per-channel tables at the chunk's first column
@@ -412,7 +413,7 @@ struct EpiAddr { uint32_t m, b, cc; };
 // the reference rounds them away from zero: |q1 - n| = 0.5 exactly marks those values (and any value too large for the
 // constant), the maximum of |q1 - n| over the chunk is handed back in dmax, and the caller re-evaluates a flagged chunk
 // with the plain reference arithmetic.
-template <bool FUSED>
+template <bool FUSED, bool SAT>
 __device__ __forceinline__ uint4 epi_chunk(const uint32_t* r, const uint4 rv, const EpiAddr& ad, const EpiConsts& ec, float& dmax)
 {
     const uint32_t resw[4] = {rv.x, rv.y, rv.z, rv.w};
@@ -431,23 +432,34 @@ __device__ __forceinline__ uint4 epi_chunk(const uint32_t* r, const uint4 rv, co
         const f32x2 p01 = mul2(v01, ec.inv2), p23 = mul2(v23, ec.inv2);
         const f32x2 q01 = fma2(fma2(p01, ec.nsy2, v01), ec.inv2, p01), q23 = fma2(fma2(p23, ec.nsy2, v23), ec.inv2, p23);
         const f32x2 t01 = add2(q01, ec.magic2), t23 = add2(q23, ec.magic2);
-        const f32x2 d01 = sub2(q01, sub2(t01, ec.magic2)), d23 = sub2(q23, sub2(t23, ec.magic2));
-        const f32x2 z01 = add2(t01, ec.zy2), z23 = add2(t23, ec.zy2);
+        const f32x2 n01 = sub2(t01, ec.magic2), n23 = sub2(t23, ec.magic2);
+        const f32x2 d01 = sub2(q01, n01), d23 = sub2(q23, n23);
         float d[4], z[4];
         unpack2(d01, d[0], d[1]); unpack2(d23, d[2], d[3]);
-        unpack2(z01, z[0], z[1]); unpack2(z23, z[2], z[3]);
         dmax = fmaxf(fmaxf(dmax, fabsf(d[0])), fabsf(d[1]));
         dmax = fmaxf(fmaxf(dmax, fabsf(d[2])), fabsf(d[3]));
         uint32_t bits[4];
-        #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            // clamp in the biased domain: the low byte of the bit pattern is the output byte
-            bits[e] = __float_as_uint(fminf(fmaxf(z[e], ec.lo), ec.hi));
-            if (FUSED) {
-                // bits = 0x4B4000qq with qq = conv output - type minimum: entry qq * pitch + other byte; ec.lut holds the
-                // table's address minus 0x4B400000 * pitch, a multiple of 256, and the byte goes into its low 8 bits
-                bits[e] = lds_u8(bits[e] * (uint32_t)TC_LUT_PITCH + __byte_perm(resw[g], ec.lut, 0x7650 + e));
+        if (FUSED || SAT) {
+            // the clamp is the 8-bit type's own range: one saturating conversion of n + zero point (an integer-valued
+            // float; with the table: minus the type minimum, a byte in 0..255) replaces the two min/max
+            const f32x2 z01 = add2(n01, ec.zy2), z23 = add2(n23, ec.zy2);
+            unpack2(z01, z[0], z[1]); unpack2(z23, z[2], z[3]);
+            #pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                if (FUSED || ec.sat_u8) asm("cvt.rni.sat.u8.f32 %0, %1;" : "=r"(bits[e]) : "f"(z[e]));
+                else                    asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(bits[e]) : "f"(z[e]));
+                if (FUSED) {
+                    // entry (conv output - type minimum) * pitch + other byte; ec.lut holds the table's address, a
+                    // multiple of 256, and the other operand's byte goes into its low 8 bits
+                    bits[e] = lds_u8(bits[e] * (uint32_t)TC_LUT_PITCH + __byte_perm(resw[g], ec.lut, 0x7650 + e));
+                }
             }
+        } else {
+            const f32x2 z01 = add2(t01, ec.zy2), z23 = add2(t23, ec.zy2);
+            unpack2(z01, z[0], z[1]); unpack2(z23, z[2], z[3]);
+            // clamp in the biased domain: the low byte of the bit pattern is the output byte
+            #pragma unroll
+            for (int e = 0; e < 4; ++e) bits[e] = __float_as_uint(fminf(fmaxf(z[e], ec.lo), ec.hi));
         }
         packed[g] = __byte_perm(__byte_perm(bits[0], bits[1], 0x0040), __byte_perm(bits[2], bits[3], 0x0040), 0x5410);
     }
@@ -761,7 +773,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         ec.zy2 = pack2(zb, zb);
         ec.lo = use_lut ? TC_MAGIC : TC_MAGIC + ex.lo1;
         ec.hi = use_lut ? TC_MAGIC + 255.0f : TC_MAGIC + ex.hi1;
-        ec.lut = smem_u32(s_lut) - 0x4B400000u * (uint32_t)TC_LUT_PITCH;
+        ec.lut = smem_u32(s_lut);
+        ec.sat = !use_lut && ex.lo1 == a.rq.tlo && ex.hi1 == a.rq.thi;
+        ec.sat_u8 = a.rq.tlo == 0.f;
         int cur_n0 = -1;
         int it = 0;
         int ub = 0; uint32_t uph = 0;                        // operand-buffer position (kept without divisions)
@@ -846,8 +860,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     const EpiAddr ad = {a_m + col0 * 4, a_b + col0 * 4, a_cc + col0 * 4};
                     float dmax = always_fix ? 1.0f : 0.0f;
                     uint4 outv;
-                    if (use_lut) outv = epi_chunk<true>(r[k], lds128(res_row + ((((uint32_t)(part * CPW + k)) ^ sw_x) << 4)), ad, ec, dmax);
-                    else         outv = epi_chunk<false>(r[k], make_uint4(0, 0, 0, 0), ad, ec, dmax);
+                    if (use_lut)     outv = epi_chunk<true, true>(r[k], lds128(res_row + ((((uint32_t)(part * CPW + k)) ^ sw_x) << 4)), ad, ec, dmax);
+                    else if (ec.sat) outv = epi_chunk<false, true>(r[k], make_uint4(0, 0, 0, 0), ad, ec, dmax);
+                    else             outv = epi_chunk<false, false>(r[k], make_uint4(0, 0, 0, 0), ad, ec, dmax);
                     // an exact half (the reference rounds it away from zero), a value beyond the rounding constant, or
                     // no table: the chunk is left to the cold pass
                     const bool fix = __any_sync(0xffffffffu, dmax >= 0.5f);
