@@ -66,6 +66,7 @@ struct TcArgs {
     int zw_val[2];                              // their values: -min(zw, 128) and -(zw - 128), each fits int8
     int mask_cpad, mask_kw;                     // row-window mode: which bytes of a K-slice are real taps (for the row sums)
     int ntn;                                    // n-tiles: ceil(OC / BN); columns beyond OC are padding
+    int kvalid_c;                               // real input channels per tap (C, or fewer when the caller zero-padded them)
     int N, H, W, C, OH, OW, OC, KH, KW, sh, sw, pt, pl, dh, dw;
     long long M;
     int im2col;                                 // 0: A is a 2-D [M, C] matrix; 1: TMA im2col from NHWC; 2: row-window
@@ -807,7 +808,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         const int32_t* P = a.prefix + n0 + j;
                         v = a.zx * (P[(long long)(y1 * pw + x1) * a.OC] - P[(long long)(y0 * pw + x1) * a.OC] -
                                     P[(long long)(y1 * pw + x0) * a.OC] + P[(long long)(y0 * pw + x0) * a.OC]) -
-                            (y1 - y0) * (x1 - x0) * a.C * a.zx * a.zw;
+                            (y1 - y0) * (x1 - x0) * a.kvalid_c * a.zx * a.zw;
                     }
                     s_cc[i] = v;
                 }
@@ -1236,7 +1237,7 @@ static int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUten
     return check_launch("conv_tc_kernel");
 }
 
-int launch_conv_tc(const b200k_conv2d_params* p, cudaStream_t stream)
+int launch_conv_tc(const b200k_conv2d_params* p, cudaStream_t stream, int kvalid_c)
 {
     B200K_REQUIRE(conv_tc_eligible(p), B200K_E_UNSUPPORTED, "conv2d_q8: not eligible for the tcgen05 kernel");
     B200K_REQUIRE(load_driver_entry_points(), B200K_E_CUDA, "conv2d_q8: cuTensorMapEncode* not available from the driver");
@@ -1245,6 +1246,7 @@ int launch_conv_tc(const b200k_conv2d_params* p, cudaStream_t stream)
     a.w_scales = p->w.scales; a.b_scales = p->bias.scales; a.w_scale = p->w.scale; a.b_scale = p->bias.scale;
     a.prefix = (const int32_t*)p->packed;
     a.zx = p->x.zero_point;
+    a.kvalid_c = kvalid_c > 0 ? kvalid_c : p->c;
     a.zw = p->w.scales ? 0 : p->w.zero_point;
     a.nzw = a.zw == 0 ? 0 : (a.zw <= 128 ? 1 : 2);
     a.zw_val[0] = -(a.zw < 128 ? a.zw : 128);
@@ -1402,25 +1404,23 @@ int launch_conv_tc(const b200k_conv2d_params* p, cudaStream_t stream)
     return launch_tc<64, 64>(tmA, tmB, tmY, tmR, a, stream);
 }
 
-}  // namespace b200k
 
-using namespace b200k;
 
-extern "C" size_t b200k_conv2d_pack_bytes(int32_t oc, int32_t kh, int32_t kw, int32_t c)
+size_t tc_pack_bytes(int oc, int kh, int kw, int c)
 {
     if (oc <= 0 || kh <= 0 || kw <= 0) return 0;
     // prefix table, row-window weights of few-channel convolutions (widest window), fused-add table and its tag
     return add_lut_offset(oc, kh, kw, c) + TC_LUT_BYTES + 64;
 }
 
-extern "C" size_t b200k_conv2d_scratch_bytes(const b200k_conv2d_params* p)
+size_t tc_scratch_bytes(const b200k_conv2d_params* p)
 {
     if (!p || p->c > 16) return 0;
     const RowPlan r = row_window_plan(p);
     return r.ok ? r.scratch_bytes : 0;
 }
 
-extern "C" int b200k_conv2d_pack(const b200k_conv2d_params* p, void* packed, void* stream)
+int tc_pack(const b200k_conv2d_params* p, void* packed, cudaStream_t stream)
 {
     B200K_REQUIRE(p && packed, B200K_E_INVALID, "conv2d_pack: null argument");
     B200K_REQUIRE(p->w.data && is_q8(p->w.dtype), B200K_E_INVALID, "conv2d_pack: weights must be an 8-bit device tensor");
@@ -1464,6 +1464,10 @@ extern "C" int b200k_conv2d_pack(const b200k_conv2d_params* p, void* packed, voi
     row_weight_pack_kernel<<<div_up((long long)p->oc * p->kh * r.swz, 256), 256, 0, (cudaStream_t)stream>>>(wa);
     return check_launch("row_weight_pack_kernel");
 }
+
+}  // namespace b200k
+
+using namespace b200k;
 
 extern "C" int b200k_poll_status(void)
 {

@@ -352,6 +352,10 @@ def Optimize(network, backend_preferences=("B200Acc",), model_options=None):
                     getattr(conv, "fused_add", None) is not None or src.info.shape != out_info.shape or
                     other.info.shape != out_info.shape or other.info.dtype not in _Q8 or other.layer is conv):
                 continue
+            if out_info.shape[-1] % 16 != 0:
+                # such a convolution runs on channel-padded copies (b200k_conv2d_scratch_bytes), which has no fused
+                # Add: the Add stays a workload of its own
+                continue
             conv.fused_add = {"conv_out_info": src.info}
             conv.fused_activation = add.fused_activation
             # the other operand becomes an extra input of the convolution layer (after data, weights, bias)

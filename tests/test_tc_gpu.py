@@ -59,6 +59,12 @@ CONV = {
                                                     fused_add=True),
     "rowwin_u8w_stem_3x3_s2_oc32": lambda: random_conv_case(267, 2, 64, 64, 3, 32, 3, 3, stride=(2, 2), pad=(0, 1, 0, 1), x_dtype=U8,
                                                             w_dtype=U8, y_dtype=U8, x_q=(0.02, 128), act=(2, 6.0, 0.0), y_zp=0),
+    # channel counts that are multiples of 8 only: zero-padded copies in scratch (input) and / or a padded output
+    "padded_c24_oc144_u8w": lambda: random_conv_case(270, 2, 28, 28, 24, 144, 1, 1, x_dtype=U8, w_dtype=U8, y_dtype=U8,
+                                                     x_q=(0.02, 128), act=(2, 6.0, 0.0), y_zp=0),
+    "padded_c144_oc24_u8w": lambda: random_conv_case(271, 2, 28, 28, 144, 24, 1, 1, x_dtype=U8, w_dtype=U8, y_dtype=U8, x_q=(0.02, 111)),
+    "padded_c24_oc24_s8_3x3": lambda: random_conv_case(272, 1, 14, 14, 24, 24, 3, 3, pad=(1, 1, 1, 1)),
+    "padded_c40_oc72_stride2": lambda: random_conv_case(273, 2, 14, 14, 40, 72, 3, 3, stride=(2, 2), pad=(0, 1, 0, 1), act=(1, 0, 0)),
     "rowwin_u8w_5x5_c4": lambda: random_conv_case(268, 1, 20, 20, 4, 48, 5, 5, pad=(2, 2, 2, 2), x_dtype=U8, w_dtype=U8, y_dtype=U8,
                                                   x_q=(0.02, 100)),
 }
@@ -116,7 +122,13 @@ def test_tcgen05_equals_cuda_core_kernel_at_full_size(built):
 
 def test_ineligible_shapes_are_refused_when_forced(built):
     from armnn_b200 import lib
-    case = random_conv_case(232, 1, 8, 8, 24, 24, 1, 1)
+    # channel counts that are not multiples of 8 cannot even use the zero-padded copies
+    case = random_conv_case(232, 1, 8, 8, 20, 28, 1, 1)
     with pytest.raises(lib.B200KError) as e:
         case.run_gpu(algo=2)
+    assert e.value.code == _abi.E_UNSUPPORTED
+    # multiples of 8 can, but only with the packed tables and the scratch: without them the forced launch is refused
+    case = random_conv_case(233, 1, 8, 8, 24, 24, 1, 1)
+    with pytest.raises(lib.B200KError) as e:
+        case.run_gpu(algo=2, pack=False)
     assert e.value.code == _abi.E_UNSUPPORTED
