@@ -86,7 +86,7 @@ struct TcArgs {
     float inv_sy;                               // RN(1 / rq.sy), correctly rounded (see epi_chunk)
     const uint8_t* add_lut;                     // fused-add table built by b200k_conv2d_pack (+ its tag), or null
     uint32_t lut_tag[TC_LUT_TAG_WORDS];         // the tag a table made for exactly this launch carries
-    int stages;                                 // ring depth chosen by the launcher (<= 8)
+    int stages;                                 // ring depth chosen by the launcher (<= 16)
     int bstat;                                  // weights stay in shared memory for the whole launch (one n-tile, small K)
     int nio;                                    // shared buffers for units of the fused Add's other operand: 0 or 2
     // zero-point correction classes: pixels whose in-image tap rectangle [ky0, ky1) x [kx0, kx1) is the same share
@@ -498,13 +498,13 @@ struct TcSmem {
     static constexpr int A_BYTES = TC_BM * SWZ;
     static constexpr int B_BYTES = BN * SWZ;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int MAX_STAGES = 8;
+    static constexpr int MAX_STAGES = 16;
     static constexpr int UW = BN < 128 ? BN : 128;          // width of one output unit: bytes = columns
     static constexpr int UNITS = BN / UW;                   // units per tile
     static constexpr int IO_BYTES = TC_BM * UW;             // one unit buffer: [128 rows][UW], TMA-swizzled
     static constexpr int MAX_IO = 3;
     // after the ring (stages x STAGE_BYTES) and the unit buffers (nio x IO_BYTES): per-channel m, bterm [BN each],
-    // barriers (full[8], empty[8], acc_full[2], acc_empty[2], io_full[3], io_empty[3], w_full), tmem slot + eps slot; then the
+    // barriers (full[16], empty[16], acc_full[2], acc_empty[2], io_full[3], io_empty[3], w_full), tmem slot + eps slot; then the
     // zero-point correction table [classes][BN], then the fused-add table (dynamic sizes)
     static constexpr int CONST_BYTES = 2 * BN * 4 + (2 * MAX_STAGES + 4 + 2 * MAX_IO + 2) * 8 + 16;
 };
