@@ -84,12 +84,12 @@ extern "C" int b200k_batch_matmul_q8(const b200k_bmm_params* p, void* stream)
 
 // ---- FullyConnected with [N, K] weights that the tcgen05 kernel cannot take (N not a multiple of 16: classifier heads)
 //
-// A block owns FC_COLS output columns (one per warp) and FC_ROWS rows of x, which it stages in shared memory once.
+// A block owns FC_COLS output columns (one per warp) and FC_ROWS (4, 16 or 32: the smallest that covers M) rows of x, which it stages in shared memory once.
 // A warp streams its weight row through registers 16 bytes per lane at a time and multiplies it with every staged row
 // (dp4a); the per-lane partial sums of the FC_ROWS rows are then reduced across the warp so that lane r ends up with
 // row r, applies the zero-point terms  sum (x - zx)(w - zw) = sum x w - zw sum x - zx sum w + K zx zw  and the
 // requantisation, and stores one byte.
-constexpr int FC_ROWS = 32, FC_COLS = 8, FC_KT = 2048;
+constexpr int FC_COLS = 8, FC_KT = 2048;              // rows per block: 4, 16 or 32 (template parameter)
 
 struct FcRowsArgs {
     const uint8_t* x; const uint8_t* w; const int32_t* bias; uint8_t* y; int32_t* acc_out;
@@ -100,7 +100,7 @@ struct FcRowsArgs {
     float inv_sy, lo, hi;
 };
 
-template <bool XU, bool WU>
+template <bool XU, bool WU, int FC_ROWS>
 __global__ void __launch_bounds__(32 * FC_COLS) fc_rows_kernel(const FcRowsArgs a)
 {
     extern __shared__ uint4 s_x[];                           // [FC_ROWS][kt / 16]
@@ -152,8 +152,14 @@ __global__ void __launch_bounds__(32 * FC_COLS) fc_rows_kernel(const FcRowsArgs 
     // warp reduction that leaves row r's total in lane r: halve the row set five times
     #pragma unroll
     for (int r = 0; r < FC_ROWS; ++r) acc[r] -= a.zw * xs[r];
+    // first fold the lanes that will share a row (FC_ROWS < 32), then halve the row set once per remaining lane bit
     #pragma unroll
-    for (int off = 16, cnt = FC_ROWS; off >= 1; off >>= 1, cnt >>= 1) {
+    for (int off = 16; off >= FC_ROWS; off >>= 1) {
+        #pragma unroll
+        for (int r = 0; r < FC_ROWS; ++r) acc[r] += __shfl_xor_sync(0xffffffffu, acc[r], off);
+    }
+    #pragma unroll
+    for (int off = FC_ROWS / 2, cnt = FC_ROWS; off >= 1; off >>= 1, cnt >>= 1) {
         const bool upper = (lane & off) != 0;
         #pragma unroll
         for (int r = 0; r < cnt / 2; ++r) {
@@ -164,9 +170,10 @@ __global__ void __launch_bounds__(32 * FC_COLS) fc_rows_kernel(const FcRowsArgs 
     }
     #pragma unroll
     for (int off = 16; off >= 1; off >>= 1) wsum += __shfl_xor_sync(0xffffffffu, wsum, off);
-    // step "off" sends the half of the remaining rows whose bit "off" differs from the lane's: lane l ends with row l
+    // step "off" sends the half of the remaining rows whose bit "off" differs from the lane's: lane l ends with row
+    // l mod FC_ROWS (lanes FC_ROWS.. hold copies)
     const int r = lane;
-    if (r >= rows) return;
+    if (r >= FC_ROWS || r >= rows) return;
     const int total = acc[0] - a.zx * wsum + a.K * a.zx * a.zw;
     const long long o = (long long)(m0 + r) * a.N + n;
     if (a.acc_out) a.acc_out[o] = total;
@@ -198,21 +205,27 @@ static int launch_fc_rows(const b200k_fc_params* p, cudaStream_t stream)
     a.lo = fmaxf(a.rq.tlo, (float)a.rq.clo);
     a.hi = fminf(a.rq.thi, (float)a.rq.chi);
     const int kt = p->k < FC_KT ? p->k : FC_KT;
-    const size_t smem = (size_t)FC_ROWS * kt;
-    const dim3 grid(div_up(p->n, FC_COLS), div_up(p->m, FC_ROWS), 1);
     const bool xu = p->x.dtype == B200K_U8, wu = p->w.dtype == B200K_U8;
-    #define B200K_FC_ROWS(XU, WU)                                                                                      \
+    #define B200K_FC_ROWS(XU, WU, RB)                                                                                  \
         do {                                                                                                           \
             static bool configured = false;                                                                            \
             if (!configured) {                                                                                         \
-                B200K_CUDA(cudaFuncSetAttribute(fc_rows_kernel<XU, WU>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
-                                                FC_ROWS * FC_KT));                                                     \
+                B200K_CUDA(cudaFuncSetAttribute(fc_rows_kernel<XU, WU, RB>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                                RB * FC_KT));                                                          \
                 configured = true;                                                                                     \
             }                                                                                                          \
-            fc_rows_kernel<XU, WU><<<grid, 32 * FC_COLS, smem, stream>>>(a);                                           \
+            const dim3 grid(div_up(p->n, FC_COLS), div_up(p->m, RB), 1);                                               \
+            fc_rows_kernel<XU, WU, RB><<<grid, 32 * FC_COLS, (size_t)RB * kt, stream>>>(a);                            \
         } while (0)
-    if (xu) { if (wu) B200K_FC_ROWS(true, true); else B200K_FC_ROWS(true, false); }
-    else    { if (wu) B200K_FC_ROWS(false, true); else B200K_FC_ROWS(false, false); }
+    #define B200K_FC_TYPES(RB)                                                                                         \
+        do {                                                                                                           \
+            if (xu) { if (wu) B200K_FC_ROWS(true, true, RB); else B200K_FC_ROWS(true, false, RB); }                    \
+            else    { if (wu) B200K_FC_ROWS(false, true, RB); else B200K_FC_ROWS(false, false, RB); }                  \
+        } while (0)
+    if (p->m <= 4)       B200K_FC_TYPES(4);
+    else if (p->m <= 16) B200K_FC_TYPES(16);
+    else                 B200K_FC_TYPES(32);
+    #undef B200K_FC_TYPES
     #undef B200K_FC_ROWS
     return check_launch("fc_rows_kernel");
 }
@@ -231,7 +244,9 @@ extern "C" int b200k_fully_connected_q8(const b200k_fc_params* p, void* stream)
         c.clamp_lo = p->clamp_lo; c.clamp_hi = p->clamp_hi; c.acc_out = p->acc_out; c.algo = p->algo;
         c.packed = p->packed;
         // the tcgen05 kernel when it can take the shape; otherwise the row kernel; the CUDA-core convolution for the rest
-        if (p->algo == 0 && !conv_tc_eligible(&c) && fc_rows_eligible(p)) return launch_fc_rows(p, (cudaStream_t)stream);
+        // (a few rows are a weight-streaming problem: the row kernel spreads the columns over every SM, whereas the
+        // tensor-core kernel would give each 64-column tile's whole K loop to one CTA)
+        if (p->algo == 0 && fc_rows_eligible(p) && (p->m <= 4 || !conv_tc_eligible(&c))) return launch_fc_rows(p, (cudaStream_t)stream);
         return conv2d_dispatch(&c, (cudaStream_t)stream);
     }
     B200K_REQUIRE(p->x.data && p->w.data && p->y.data, B200K_E_INVALID, "fully_connected_q8: null tensor pointer");
