@@ -29,6 +29,27 @@ __device__ __forceinline__ float q16zf(float v, float scale, float zp)
     return fminf(fmaxf(__fadd_rn(zp, roundf(__fdiv_rn(v, scale))), -32768.f), 32767.f);
 }
 
+// round_half_away(fl(v / scale)) without the division unit, for the long chains: with inv = RN(1 / scale)
+// (__frcp_rn), p = fl(v * inv) and q = fma(fma(-p, scale, v), inv, p) is the correctly rounded quotient (Markstein);
+// q is rounded with the 1.5 * 2^23 constant (halves to even), and only when q is an exact half or too large for the
+// constant does roundf decide.
+__device__ __forceinline__ float round_div_fast(float v, float scale, float inv)
+{
+    const float p = __fmul_rn(v, inv);
+    const float q = __fmaf_rn(__fmaf_rn(-p, scale, v), inv, p);
+    float n = __fsub_rn(__fadd_rn(q, 12582912.0f), 12582912.0f);
+    if (fabsf(__fsub_rn(q, n)) >= 0.5f) n = roundf(q);
+    return n;
+}
+__device__ __forceinline__ float q16f_fast(float v, float scale, float inv)
+{
+    return fminf(fmaxf(round_div_fast(v, scale, inv), -32768.f), 32767.f);
+}
+__device__ __forceinline__ float q16zf_fast(float v, float scale, float inv, float zp)
+{
+    return fminf(fmaxf(__fadd_rn(zp, round_div_fast(v, scale, inv)), -32768.f), 32767.f);
+}
+
 struct QlArgs {
     b200k_qlstm_params p;
     int cifg, peephole, ln, proj;
@@ -39,6 +60,7 @@ template <bool VEC>
 __device__ __forceinline__ void chain2(float& accA, float& accB, const int8_t* wA, const int8_t* wB, float swA, float swB,
                                         const float* v, int K, float sGA, float sGB, bool hasB)
 {
+    const float iGA = __frcp_rn(sGA), iGB = __frcp_rn(sGB);
     if (VEC) {
         for (int k0 = 0; k0 < K; k0 += 16) {
             int8_t ra[16], rb[16];
@@ -47,15 +69,15 @@ __device__ __forceinline__ void chain2(float& accA, float& accB, const int8_t* w
             #pragma unroll
             for (int j = 0; j < 16; ++j) {
                 const float x = v[k0 + j];
-                accA = q16f(__fadd_rn(__fmul_rn(accA, sGA), __fmul_rn(__fmul_rn((float)ra[j], swA), x)), sGA);
-                if (hasB) accB = q16f(__fadd_rn(__fmul_rn(accB, sGB), __fmul_rn(__fmul_rn((float)rb[j], swB), x)), sGB);
+                accA = q16f_fast(__fadd_rn(__fmul_rn(accA, sGA), __fmul_rn(__fmul_rn((float)ra[j], swA), x)), sGA, iGA);
+                if (hasB) accB = q16f_fast(__fadd_rn(__fmul_rn(accB, sGB), __fmul_rn(__fmul_rn((float)rb[j], swB), x)), sGB, iGB);
             }
         }
     } else {
         for (int k = 0; k < K; ++k) {
             const float x = v[k];
-            accA = q16f(__fadd_rn(__fmul_rn(accA, sGA), __fmul_rn(__fmul_rn((float)wA[k], swA), x)), sGA);
-            if (hasB) accB = q16f(__fadd_rn(__fmul_rn(accB, sGB), __fmul_rn(__fmul_rn((float)wB[k], swB), x)), sGB);
+            accA = q16f_fast(__fadd_rn(__fmul_rn(accA, sGA), __fmul_rn(__fmul_rn((float)wA[k], swA), x)), sGA, iGA);
+            if (hasB) accB = q16f_fast(__fadd_rn(__fmul_rn(accB, sGB), __fmul_rn(__fmul_rn((float)wB[k], swB), x)), sGB, iGB);
         }
     }
 }
@@ -196,7 +218,7 @@ __global__ void __launch_bounds__(QL_THREADS) qlstm_step_kernel(const QlArgs a)
     __syncthreads();
 
     // ---- projection (int16 accumulator at the OUTPUT's scale and offset) and outputs
-    const float so = p.output_scale, zo = (float)p.output_zp;
+    const float so = p.output_scale, zo = (float)p.output_zp, iso = __frcp_rn(p.output_scale);
     for (int j = tid; j < O; j += QL_THREADS) {
         float out8;
         if (a.proj) {
@@ -205,7 +227,7 @@ __global__ void __launch_bounds__(QL_THREADS) qlstm_step_kernel(const QlArgs a)
             const int8_t* w = p.w_proj + (long long)j * U;
             for (int k = 0; k < U; ++k) {
                 const float d = __fmul_rn(__fsub_rn(acc, zo), so);
-                acc = q16zf(__fadd_rn(d, __fmul_rn(__fmul_rn((float)w[k], p.s_proj), hid[k])), so, zo);
+                acc = q16zf_fast(__fadd_rn(d, __fmul_rn(__fmul_rn((float)w[k], p.s_proj), hid[k])), so, iso, zo);
             }
             out8 = fminf(fmaxf(__fadd_rn(zo, roundf(__fdiv_rn(__fmul_rn(__fsub_rn(acc, zo), so), so))), -128.f), 127.f);
             if (p.projection_clip > 0.0f) {
