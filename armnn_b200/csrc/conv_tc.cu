@@ -10,8 +10,8 @@
 //   * one thread issues tcgen05.mma.kind::i8 (M = 128, N = BN, K = 32 per instruction); the int32 accumulator
 //     lives in tensor memory (BN columns x 128 lanes); tcgen05.commit releases ring slots and finally signals
 //     the epilogue.
-//   * eight epilogue warps read the accumulator with tcgen05.ld, apply the zero-point correction, bias and the
-//     fp32 requantisation, and store 8-bit outputs.
+//   * sixteen epilogue warps read the accumulator with tcgen05.ld, apply the zero-point correction, bias and the
+//     fp32 requantisation (and a fused residual Add), and send their 8-bit outputs with their own TMA stores.
 //
 // Convolutions with very few input channels (the 3-channel network stems) cannot feed TMA directly: a pixel is
 // not a 16-byte unit.  For those a pre-pass re-packs the input into caller-provided scratch as
@@ -21,14 +21,15 @@
 // K-slice, window stride = stride_w pixels), so K = KH slices.  The weights are re-packed to match at load time.
 //
 // Zero points.  TMA fills out-of-image taps with raw zeros, whereas the reference pads with the real value 0,
-// i.e. with the quantised value zx.  With symmetric weights (zw = 0)
-//     sum_valid (x - zx) w = sum_all x_filled w - zx * sum_valid w
-// and sum_valid w for an output pixel is the sum of per-tap channel sums over the rectangle of in-image taps,
-// read from a 2-D prefix table over (ky, kx) that b200k_conv2d_pack builds once per weight tensor.
+// i.e. with the quantised value zx:
+//     sum_valid (x - zx)(w - zw) = sum_all x_filled w - zw sum_all x_filled - zx sum_valid w + K_valid zx zw.
+// sum_valid w of an output pixel is the sum of per-tap channel sums over the rectangle of in-image taps, read from a
+// 2-D prefix table over (ky, kx) that b200k_conv2d_pack builds once per weight tensor; pixels with the same rectangle
+// form a class, and the last two terms are a per-class, per-channel constant kept in shared memory.  The second term
+// (per-tensor asymmetric weights) is accumulated by the tensor core itself from constant B tiles holding -zw.
 //
-// Requantisation is the same function as in the CUDA-core kernel and the CPU oracle (IEEE fp32, unfused).  The
-// division v / scale is evaluated as a multiplication by the reciprocal whenever the product is provably not
-// within reach of a rounding tie, and falls back to the exact division otherwise, so results are bit-identical.
+// Requantisation is the same function as in the CUDA-core kernel and the CPU oracle (IEEE fp32, unfused), evaluated
+// without the division unit and bit-identically (see epi_chunk).
 //
 // Every wait on an mbarrier is bounded; when a bound is hit the kernel raises a status word (read with
 // b200k_poll_status), drains and returns, so a logic error cannot hang the device.
@@ -201,19 +202,6 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, u
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
                  ::"r"(smem_u32(dst)), "l"((uint64_t)map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
 }
-__device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2, int c3)
-{
-    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
-                 ::"r"(smem_u32(dst)), "l"((uint64_t)map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
-}
-__device__ __forceinline__ void tma_load_im2col(void* dst, const CUtensorMap* map, uint64_t* bar, int c, int w, int h,
-                                                int n, uint16_t off_w, uint16_t off_h)
-{
-    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes"
-                 " [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};"
-                 ::"r"(smem_u32(dst)), "l"((uint64_t)map), "r"(smem_u32(bar)), "r"(c), "r"(w), "r"(h), "r"(n),
-                   "h"(off_w), "h"(off_h) : "memory");
-}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after()  { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_commit(uint64_t* bar)
@@ -262,18 +250,6 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t sr
 {
     asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
                  ::"l"((uint64_t)map), "r"(src_saddr), "r"(c0), "r"(c1), "r"(c2) : "memory");
-}
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t* r)
-{
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32"
-                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15,"
-                 " %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-                 : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
 // Shared-memory matrix descriptor of a K-major tile whose rows are one swizzle span (SWZ bytes) long:
