@@ -1,5 +1,5 @@
 #!/usr/bin/env python
-"""Benchmark of the B200Acc hot path: int8 ResNet-50 images/s (BASELINE.json `metric`, configs[3]).
+"""Benchmark of the B200Acc hot path: int8 ResNet-50 images/s at global batch 256 (the headline configuration).
 
     python bench.py [--gpus N] [--steps K] [--warmup W]            the B200 arm
     python bench.py --impl reference [--steps K] [--warmup W]      the reference's own CpuRef on host cores
