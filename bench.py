@@ -30,7 +30,7 @@ IMAGE = 224
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum per convolution launch, averaged over the 53 convolution launches of
-# one batch-256 step (one ncu capture of this file's own command; see profiles/resnet50_b256_launch_list.md)
+# one batch-256 step, from an ncu capture of this file's own command
 CONV_DRAM_BYTES_PER_LAUNCH = 102.5e6
 
 
