@@ -794,6 +794,83 @@ class LoadedNetwork(GraphProgram):
         self.stream.synchronize()
         return 0
 
+    # -- pipelined execution: the next request's input copy overlaps this request's compute ---------------
+    def _input_consumers_end(self):
+        """Workloads [0, k) include every workload that reads a network input directly."""
+        input_ids = {id(slot) for slot in self.inputs.values()}
+        k = 0
+        for i, (layer, entry, params) in enumerate(self.workloads):
+            if any(id(s.source) in input_ids for s in layer.inputs):
+                k = i + 1
+        return k
+
+    def CapturePipelined(self):
+        """Prepare EnqueueAsync / WaitOutputs: the workload queue as two CUDA graphs (the workloads that read the
+        network inputs, then the rest), a copy stream, and two sets of pinned output staging buffers."""
+        torch = self.torch
+        l = lib.load_library()
+        self.launch_all(self.stream.cuda_stream)
+        self.stream.synchronize()
+        k = self._input_consumers_end()
+
+        def capture(lo, hi):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=self.stream):
+                h = torch.cuda.current_stream().cuda_stream
+                for layer, entry, params in self.workloads[lo:hi]:
+                    rc = getattr(l, "b200k_" + entry)(ctypes.byref(params), ctypes.c_void_p(h))
+                    if rc != 0:
+                        raise RuntimeError("workload %s (%s) failed: %s" % (layer.name, entry, l.b200k_last_error().decode()))
+            return g
+        self._head, self._tail = capture(0, k), (capture(k, len(self.workloads)) if k < len(self.workloads) else None)
+        self._copy_stream = torch.cuda.Stream(device=self.rt.device)
+        self._input_free = None
+        self._staging = [{bid: torch.empty(tuple(self._dev(slot).shape), dtype=self._dev(slot).dtype).pin_memory()
+                          for bid, slot in self.outputs.items()} for _ in range(2)]
+        self._tickets = 0
+
+    def EnqueueAsync(self, input_tensors):
+        """Host -> device copy of the inputs on the copy stream (as soon as the previous request's input has been
+        consumed), then the workload queue and the device -> host copy of every output into pinned staging on the
+        network's stream.  Returns a ticket for WaitOutputs; at most two requests may be in flight.  Host inputs
+        should be pinned, otherwise the copy is synchronous."""
+        torch = self.torch
+        cs = self._copy_stream
+        with torch.cuda.stream(cs):
+            if self._input_free is not None:
+                cs.wait_event(self._input_free)
+            for bid, host in input_tensors.items():
+                dst = self._dev(self.inputs[bid])
+                src = host if torch.is_tensor(host) else torch.from_numpy(host)
+                dst.view(-1).copy_(src.view(-1).view(dst.dtype), non_blocking=True)
+            ready = torch.cuda.Event()
+            ready.record(cs)
+        slot = self._tickets % 2
+        self._tickets += 1
+        with torch.cuda.stream(self.stream):
+            self.stream.wait_event(ready)
+            self._head.replay()
+            self._input_free = torch.cuda.Event()
+            self._input_free.record(self.stream)
+            if self._tail is not None:
+                self._tail.replay()
+            for bid, out in self.outputs.items():
+                self._staging[slot][bid].copy_(self._dev(out), non_blocking=True)
+            done = torch.cuda.Event()
+            done.record(self.stream)
+        return slot, done
+
+    def WaitOutputs(self, ticket, output_tensors):
+        """Blocks until the request of `ticket` has finished and copies its outputs to the given host tensors."""
+        torch = self.torch
+        slot, done = ticket
+        done.synchronize()
+        for bid, host in output_tensors.items():
+            dst = host if torch.is_tensor(host) else torch.from_numpy(host)
+            src = self._staging[slot][bid]
+            dst.view(-1).view(src.dtype).copy_(src.view(-1))
+        return 0
+
     def input_tensor(self, binding_id):
         return self._dev(self.inputs[binding_id])
 

@@ -96,3 +96,35 @@ def test_qlstm_stack_five_steps_free_running(built):
         # step cannot compound (the per-step bar is what is asserted)
         state_g = {k: want[k].copy() for k in state_g}
         state_o = {k: want[k].copy() for k in state_o}
+
+
+def test_pipelined_requests_match_blocking_enqueue():
+    """EnqueueAsync / WaitOutputs (input copy of request i + 1 under the compute of request i) returns, request by
+    request, what the blocking EnqueueWorkload returns."""
+    import torch
+    from armnn_b200 import configs, network
+    net, info = configs.resnet50(2, 64)
+    rt = network.IRuntime.Create(0)
+    ln = rt.GetLoadedNetwork(rt.LoadNetwork(network.Optimize(net, ["B200Acc"])))
+    rng = np.random.default_rng(7)
+    xs = [torch.from_numpy(rng.integers(-128, 128, size=info["input_shape"]).astype(np.int8)).pin_memory() for _ in range(4)]
+    want = []
+    for x in xs:
+        y = torch.empty(info["output_shape"], dtype=torch.int8)
+        ln.EnqueueWorkload({0: x}, {0: y})
+        want.append(y.clone())
+    ln.CapturePipelined()
+    got, prev = [], None
+    for x in xs:
+        t = ln.EnqueueAsync({0: x})
+        if prev is not None:
+            y = torch.empty(info["output_shape"], dtype=torch.int8)
+            ln.WaitOutputs(prev, {0: y})
+            got.append(y)
+        prev = t
+    y = torch.empty(info["output_shape"], dtype=torch.int8)
+    ln.WaitOutputs(prev, {0: y})
+    got.append(y)
+    assert len({w.numpy().tobytes() for w in want}) > 1          # the requests really differ
+    for w, g in zip(want, got):
+        assert torch.equal(w, g)
