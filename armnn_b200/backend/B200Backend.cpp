@@ -269,6 +269,77 @@ public:
                                                {"AllOrNothing", false}});
     }
 
+    /// Convolution2d -> ElementwiseBinary(Add, other) [-> Activation{ReLu, BoundedReLu}] becomes one PreCompiled layer
+    /// (inputs: data, weights[, bias], other) whose workload adds the other operand in the convolution's epilogue:
+    /// the residual connections of ResNet-style graphs then cost no pass over memory of their own.  The result is what
+    /// the three CpuRef workloads in a row produce (the convolution's own 8-bit result is formed, not stored).
+    void FuseResidualAdds(const SubgraphView& subgraph, OptimizationViews& views, std::map<LayerGuid, Layer*>& untouched) const
+    {
+        for (auto it = subgraph.begin(); it != subgraph.end(); ++it)
+        {
+            Layer& l = *PolymorphicDowncast<Layer*>(*it);
+            if (l.GetType() != LayerType::ElementwiseBinary || untouched.find(l.GetGuid()) == untouched.end()) { continue; }
+            auto* add = PolymorphicDowncast<ElementwiseBinaryLayer*>(&l);
+            if (add->GetParameters().m_Operation != BinaryOperation::Add) { continue; }
+            if (add->GetAdditionalInformation<ActivationDescriptor>() != nullptr) { continue; }
+            const TensorInfo& addOut = add->GetOutputSlot(0).GetTensorInfo();
+            if (!Is8Bit(addOut) || addOut.GetNumDimensions() != 4 || addOut.GetShape()[3] % 16 != 0) { continue; }
+            for (unsigned int side = 0; side < 2; ++side)
+            {
+                OutputSlot* src = add->GetInputSlot(side).GetConnectedOutputSlot();
+                OutputSlot* other = add->GetInputSlot(1 - side).GetConnectedOutputSlot();
+                if (!src || !other) { continue; }
+                Layer& producer = src->GetOwningLayer();
+                if (producer.GetType() != LayerType::Convolution2d || untouched.find(producer.GetGuid()) == untouched.end() ||
+                    &other->GetOwningLayer() == &producer || src->GetNumConnections() != 1) { continue; }
+                auto* conv = PolymorphicDowncast<Convolution2dLayer*>(&producer);
+                if (conv->GetAdditionalInformation<ActivationDescriptor>() != nullptr ||
+                    conv->GetParameters().m_DataLayout != DataLayout::NHWC) { continue; }
+                const TensorInfo& convOut = src->GetTensorInfo();
+                const TensorInfo& otherInfo = other->GetTensorInfo();
+                if (!Is8Bit(convOut) || convOut.HasMultipleQuantizationScales() || !Is8Bit(otherInfo) ||
+                    convOut.GetShape() != addOut.GetShape() || otherInfo.GetShape() != addOut.GetShape()) { continue; }
+
+                ActivationLayer* act = nullptr;
+                if (add->GetOutputSlot(0).GetNumConnections() == 1)
+                {
+                    Layer& child = add->GetOutputSlot(0).GetConnection(0)->GetOwningLayer();
+                    if (child.GetType() == LayerType::Activation && untouched.find(child.GetGuid()) != untouched.end())
+                    {
+                        auto* a = PolymorphicDowncast<ActivationLayer*>(&child);
+                        const ActivationFunction fn = a->GetParameters().m_Function;
+                        if ((fn == ActivationFunction::ReLu || fn == ActivationFunction::BoundedReLu) &&
+                            SameQuantisation(addOut, a->GetOutputSlot(0).GetTensorInfo())) { act = a; }
+                    }
+                }
+
+                auto* blob = new B200FusedConvAdd;
+                blob->m_Convolution = conv->GetParameters();
+                blob->m_ConvolutionOutput = convOut;
+                if (act) { blob->m_HasActivation = true; blob->m_Activation = act->GetParameters(); }
+                CompiledBlobPtr blobPtr(blob, [](const void* p) { delete static_cast<const B200FusedConvAdd*>(p); });
+                const unsigned int convInputs = conv->GetNumInputSlots();
+                const std::string name = std::string("fused-") + add->GetName() + "-into-" + conv->GetName();
+                IConnectableLayer* fused = views.GetINetwork()->AddPrecompiledLayer(
+                    PreCompiledDescriptor(convInputs + 1, 1), std::move(blobPtr), Optional<BackendId>(GetId()), name.c_str());
+                Layer* last = act ? static_cast<Layer*>(act) : static_cast<Layer*>(add);
+                fused->GetOutputSlot(0).SetTensorInfo(last->GetOutputSlot(0).GetTensorInfo());
+
+                SubgraphView::IConnectableLayers layers{conv, add};
+                if (act) { layers.push_back(act); }
+                SubgraphView::IInputSlots inputs;
+                for (unsigned int i = 0; i < convInputs; ++i) { inputs.push_back(&conv->GetInputSlot(i)); }
+                inputs.push_back(&add->GetInputSlot(1 - side));
+                SubgraphView::IOutputSlots outputs{&last->GetOutputSlot(0)};
+                views.AddSubstitution({SubgraphView(std::move(layers), std::move(inputs), std::move(outputs)), SubgraphView(fused)});
+                untouched.erase(conv->GetGuid());
+                untouched.erase(add->GetGuid());
+                if (act) { untouched.erase(act->GetGuid()); }
+                break;
+            }
+        }
+    }
+
     /// Fold Activation{ReLu, BoundedReLu} into the producing Convolution2d / DepthwiseConvolution2d / FullyConnected /
     /// ElementwiseBinary when both tensors carry the same quantisation: the workload then clamps in the quantised
     /// domain, which is exactly what the separate CpuRef Activation workload would compute.
@@ -281,9 +352,11 @@ public:
             Layer& l = *PolymorphicDowncast<Layer*>(*it);
             untouched.insert({l.GetGuid(), &l});
         }
+        FuseResidualAdds(subgraph, views, untouched);
         for (auto it = subgraph.begin(); it != subgraph.end(); ++it)
         {
             Layer& base = *PolymorphicDowncast<Layer*>(*it);
+            if (untouched.find(base.GetGuid()) == untouched.end()) { continue; }
             const LayerType t = base.GetType();
             if (t != LayerType::Convolution2d && t != LayerType::DepthwiseConvolution2d && t != LayerType::FullyConnected &&
                 t != LayerType::ElementwiseBinary) { continue; }

@@ -141,35 +141,51 @@ struct ConvState
     std::once_flag once;
 };
 
-template <typename QD>
-std::unique_ptr<IWorkload> MakeConv(const QueueDescriptor& d, const WorkloadInfo& info, bool depthwise)
+// Geometry, quantisation and buffers of a convolution from the layer's descriptor and tensor infos
+// (data, weights[, bias] -> y); `act` clamps y, or the fused Add's output when there is one.
+template <typename Descriptor>
+void FillConv(ConvState& st, const Descriptor& prm, const TensorInfo& x, const TensorInfo& w, const TensorInfo* bias,
+              const TensorInfo& y, bool depthwise)
 {
-    const QD& qd = *PolymorphicDowncast<const QD*>(&d);
-    const auto& prm = qd.m_Parameters;
     if (prm.m_DataLayout != DataLayout::NHWC) { throw InvalidArgumentException("B200Acc: NHWC only"); }
-    auto st = std::make_shared<ConvState>();
-    b200k_conv2d_params& p = st->p;
+    b200k_conv2d_params& p = st.p;
     std::memset(&p, 0, sizeof(p));
-    const TensorInfo& x = info.m_InputTensorInfos[0];
-    const TensorInfo& w = info.m_InputTensorInfos[1];
-    const TensorInfo& y = info.m_OutputTensorInfos[0];
-    p.x = Operand(x, st->blobs);
-    p.w = Operand(w, st->blobs);
-    p.y = Operand(y, st->blobs);
-    if (prm.m_BiasEnabled) { p.bias = Operand(info.m_InputTensorInfos[2], st->blobs); }
+    p.x = Operand(x, st.blobs);
+    p.w = Operand(w, st.blobs);
+    p.y = Operand(y, st.blobs);
+    if (prm.m_BiasEnabled && bias) { p.bias = Operand(*bias, st.blobs); }
     p.n = x.GetShape()[0]; p.h = x.GetShape()[1]; p.wd = x.GetShape()[2]; p.c = x.GetShape()[3];
     p.oh = y.GetShape()[1]; p.ow = y.GetShape()[2]; p.oc = y.GetShape()[3];
     p.kh = w.GetShape()[1]; p.kw = w.GetShape()[2];
     p.stride_h = prm.m_StrideY; p.stride_w = prm.m_StrideX;
     p.pad_top = prm.m_PadTop; p.pad_left = prm.m_PadLeft;
     p.dil_h = prm.m_DilationY; p.dil_w = prm.m_DilationX;
-    Clamp(qd.template GetAdditionalInformation<ActivationDescriptor>(), y, p.clamp_lo, p.clamp_hi);
     if (!depthwise)
     {
-        st->packed = st->blobs.Alloc(b200k_conv2d_pack_bytes(p.oc, p.kh, p.kw, p.c));
+        st.packed = st.blobs.Alloc(b200k_conv2d_pack_bytes(p.oc, p.kh, p.kw, p.c));
         const size_t scratch = b200k_conv2d_scratch_bytes(&p);
-        if (scratch) { p.scratch = st->blobs.Alloc(scratch); p.scratch_bytes = scratch; }
+        if (scratch) { p.scratch = st.blobs.Alloc(scratch); p.scratch_bytes = scratch; }
     }
+}
+
+// The weight bytes reach the device when the Constant workloads run, which is after workload creation and
+// PostAllocationConfigure (src/armnn/LoadedNetwork.cpp:559-568): build the weight table on first use.
+void LaunchConv(ConvState& st, cudaStream_t s)
+{
+    b200k_conv2d_params& q = st.p;
+    std::call_once(st.once, [&] { B200CheckStatus(b200k_conv2d_pack(&q, st.packed, s)); q.packed = st.packed; });
+    B200CheckStatus(b200k_conv2d_q8(&q, s));
+}
+
+template <typename QD>
+std::unique_ptr<IWorkload> MakeConv(const QueueDescriptor& d, const WorkloadInfo& info, bool depthwise)
+{
+    const QD& qd = *PolymorphicDowncast<const QD*>(&d);
+    auto st = std::make_shared<ConvState>();
+    const TensorInfo& y = info.m_OutputTensorInfos[0];
+    FillConv(*st, qd.m_Parameters, info.m_InputTensorInfos[0], info.m_InputTensorInfos[1],
+             info.m_InputTensorInfos.size() > 2 ? &info.m_InputTensorInfos[2] : nullptr, y, depthwise);
+    Clamp(qd.template GetAdditionalInformation<ActivationDescriptor>(), y, st->p.clamp_lo, st->p.clamp_hi);
     return Make<QD>(d, info, [st, depthwise](const QD& data, cudaStream_t s)
     {
         b200k_conv2d_params& q = st->p;
@@ -178,10 +194,37 @@ std::unique_ptr<IWorkload> MakeConv(const QueueDescriptor& d, const WorkloadInfo
         if (q.bias.dtype == B200K_S32 && data.m_Inputs.size() > 2) { q.bias.data = Dev(data.m_Inputs[2]); }
         q.y.data = Dev(data.m_Outputs[0]);
         if (depthwise) { B200CheckStatus(b200k_dwconv2d_q8(&q, s)); return; }
-        // The weight bytes reach the device when the Constant workloads run, which is after workload creation and
-        // PostAllocationConfigure (src/armnn/LoadedNetwork.cpp:559-568): build the weight table on first use.
-        std::call_once(st->once, [&] { B200CheckStatus(b200k_conv2d_pack(&q, st->packed, s)); q.packed = st->packed; });
-        B200CheckStatus(b200k_conv2d_q8(&q, s));
+        LaunchConv(*st, s);
+    });
+}
+
+// Convolution2d -> Add [-> Activation] folded into one PreCompiled layer by B200Backend::OptimizeSubgraphView:
+// inputs (data, weights[, bias], other operand), output = the Add's (Activation's) output.
+std::unique_ptr<IWorkload> MakeFusedConvAdd(const QueueDescriptor& d, const WorkloadInfo& info, const B200FusedConvAdd& fused)
+{
+    const size_t nIn = info.m_InputTensorInfos.size();
+    const bool bias = fused.m_Convolution.m_BiasEnabled;
+    if (nIn != (bias ? 4u : 3u) || info.m_OutputTensorInfos.size() != 1)
+    {
+        throw InvalidArgumentException("B200Acc: fused convolution + Add expects (data, weights[, bias], operand) -> output");
+    }
+    auto st = std::make_shared<ConvState>();
+    const TensorInfo& other = info.m_InputTensorInfos[nIn - 1];
+    const TensorInfo& out = info.m_OutputTensorInfos[0];
+    FillConv(*st, fused.m_Convolution, info.m_InputTensorInfos[0], info.m_InputTensorInfos[1],
+             bias ? &info.m_InputTensorInfos[2] : nullptr, fused.m_ConvolutionOutput, false);
+    st->p.add_operand = Operand(other, st->blobs);
+    st->p.add_out = Operand(out, st->blobs);
+    Clamp(fused.m_HasActivation ? &fused.m_Activation : nullptr, out, st->p.clamp_lo, st->p.clamp_hi);
+    return Make<PreCompiledQueueDescriptor>(d, info, [st, bias, nIn](const PreCompiledQueueDescriptor& data, cudaStream_t s)
+    {
+        b200k_conv2d_params& q = st->p;
+        q.x.data = Dev(data.m_Inputs[0]);
+        q.w.data = Dev(data.m_Inputs[1]);
+        if (bias) { q.bias.data = Dev(data.m_Inputs[2]); }
+        q.add_operand.data = Dev(data.m_Inputs[nIn - 1]);
+        q.add_out.data = Dev(data.m_Outputs[0]);
+        LaunchConv(*st, s);
     });
 }
 
@@ -559,6 +602,13 @@ std::unique_ptr<IWorkload> B200WorkloadFactory::CreateWorkload(LayerType type, c
         }
         case LayerType::QLstm:
             return MakeQLstm(d, info);
+        case LayerType::PreCompiled:
+        {
+            const auto& qd = *PolymorphicDowncast<const PreCompiledQueueDescriptor*>(&d);
+            const auto* fused = static_cast<const B200FusedConvAdd*>(qd.m_PreCompiledObject);
+            if (!fused || fused->m_Magic != B200FusedConvAdd::Magic) { return nullptr; }
+            return MakeFusedConvAdd(d, info, *fused);
+        }
         default:
             return nullptr;       // LoadedNetwork turns a null workload into an exception: there is no CPU fallback
     }

@@ -2,7 +2,9 @@
 // src/backends/reference/RefWorkloadFactory.cpp:146-676 of the Arm NN tree).
 #pragma once
 
+#include <armnn/Descriptors.hpp>
 #include <armnn/Optional.hpp>
+#include <armnn/Tensor.hpp>
 #include <armnn/backends/WorkloadFactory.hpp>
 #include <armnn/backends/Workload.hpp>
 #include <armnn/backends/WorkloadData.hpp>
@@ -11,6 +13,20 @@
 
 namespace armnn
 {
+
+/// What B200Backend::OptimizeSubgraphView stores in the PreCompiled layer that replaces
+/// Convolution2d -> ElementwiseBinary(Add) [-> Activation{ReLu, BoundedReLu}]: the layer's inputs are the
+/// convolution's (data, weights[, bias]) followed by the Add's other operand, its output is the Add's (or the
+/// Activation's) output.  The workload is one b200k_conv2d_q8 call with add_operand / add_out set.
+struct B200FusedConvAdd
+{
+    static constexpr uint32_t Magic = 0xB200ADD1u;
+    uint32_t                m_Magic = Magic;
+    Convolution2dDescriptor m_Convolution;
+    TensorInfo              m_ConvolutionOutput;     ///< quantisation of the convolution's own (never stored) result
+    bool                    m_HasActivation = false;
+    ActivationDescriptor    m_Activation;            ///< applied to the Add's output
+};
 
 class B200WorkloadFactory : public IWorkloadFactory
 {

@@ -675,6 +675,30 @@ void* armnnc_load(void* vr, void* vn, const char* backends, int device_id, int p
     } catch (const std::exception& e) { g_err = e.what(); return nullptr; }
 }
 
+// Optimize only (no device needed): writes one "LayerType name" line per layer of the optimized graph, in
+// execution order, into buf; returns the number of bytes needed, 0 on failure.
+size_t armnnc_optimized_layers(void* vr, void* vn, const char* backends, char* buf, size_t cap)
+{
+    auto* r = static_cast<CRuntime*>(vr);
+    auto* n = static_cast<CNet*>(vn);
+    struct Lister : IStrategy {
+        std::ostringstream os;
+        void ExecuteStrategy(const IConnectableLayer* layer, const BaseDescriptor&, const std::vector<ConstTensor>&,
+                             const char* name, const LayerBindingId) override
+        { os << GetLayerTypeAsCString(layer->GetType()) << " " << (name ? name : "") << "\n"; }
+    } lister;
+    try {
+        std::vector<std::string> messages;
+        IOptimizedNetworkPtr opt = Optimize(*n->net, {BackendId(backends)}, r->rt->GetDeviceSpec(), OptimizerOptionsOpaque(),
+                                            Optional<std::vector<std::string>&>(messages));
+        if (!opt) { g_err = "Optimize returned null"; for (auto& m : messages) g_err += "; " + m; return 0; }
+        opt->ExecuteStrategy(lister);
+    } catch (const std::exception& e) { g_err = e.what(); return 0; }
+    std::string s = lister.os.str();
+    if (buf && cap) { size_t k = std::min(cap - 1, s.size()); std::memcpy(buf, s.data(), k); buf[k] = 0; }
+    return s.size() + 1;
+}
+
 void armnnc_unload(void* vl)
 {
     auto* l = static_cast<CLoaded*>(vl);

@@ -79,7 +79,9 @@ class ArmnnNetwork:
     def backend_available(name):
         return bool(cpuref().armnnc_backend_available(ArmnnNetwork.runtime(), name.encode()))
 
-    def __init__(self, network, backends="CpuRef", device_id=-1, profiling=False):
+    def __init__(self, network, backends="CpuRef", device_id=-1, profiling=False, optimize_only=False):
+        """optimize_only: no LoadNetwork (needs no device); `self.optimized_layers` lists the optimized graph as
+        (layer type, name) in execution order."""
         lib = cpuref()
         self.lib = lib
         rt = self.runtime()
@@ -146,6 +148,18 @@ class ArmnnNetwork:
                 continue
             for s in layer.inputs:
                 lib.armnnc_connect(net, ids[id(s.source.layer)], s.source.index, ids[id(layer)], s.index)
+        if optimize_only:
+            lib.armnnc_optimized_layers.restype = C.c_size_t
+            need = lib.armnnc_optimized_layers(rt, net, backends.encode(), None, C.c_size_t(0))
+            err = lib.cpuref_last_error().decode()
+            buf = C.create_string_buffer(max(int(need), 1))
+            lib.armnnc_optimized_layers(rt, net, backends.encode(), buf, C.c_size_t(len(buf)))
+            lib.armnnc_network_destroy(net)
+            if not need:
+                raise RuntimeError("armnn optimize failed: " + err)
+            self.optimized_layers = [tuple(line.split(" ", 1)) for line in buf.value.decode().splitlines()]
+            self.handle = C.c_void_p(None)
+            return
         self.handle = C.c_void_p(lib.armnnc_load(rt, net, backends.encode(), device_id, int(profiling)))
         err = lib.cpuref_last_error().decode()
         lib.armnnc_network_destroy(net)

@@ -20,6 +20,25 @@ def test_plugin_is_found_loaded_and_registered_by_the_runtime():
     assert hostnet.ArmnnNetwork.backend_available("B200Acc")
 
 
+@needs_plugin
+def test_optimize_folds_activations_and_residual_adds_into_the_convolutions():
+    """Optimize({B200Acc}) inside the unmodified runtime: B200Backend::OptimizeSubgraphView leaves no Activation layer
+    and replaces Convolution2d -> Add -> ReLu by one PreCompiled layer wherever the channel count allows it."""
+    from collections import Counter
+    from armnn_b200 import configs
+    net, _ = configs.resnet50(1, 64)
+    kinds = Counter(t for t, _ in hostnet.ArmnnNetwork(net, "B200Acc", optimize_only=True).optimized_layers)
+    assert kinds["PreCompiled"] == 16 and kinds["ElementwiseBinary"] == 0 and kinds["Activation"] == 0
+    assert kinds["Convolution2d"] == 53 - 16
+    net, _ = configs.mobilenet_v2(1, 64)
+    kinds = Counter(t for t, _ in hostnet.ArmnnNetwork(net, "B200Acc", optimize_only=True).optimized_layers)
+    # ten residual Adds; the one with 24 channels (not a multiple of 16) stays a layer of its own
+    assert kinds["PreCompiled"] == 9 and kinds["ElementwiseBinary"] == 1 and kinds["Activation"] == 0
+    # the same graphs on CpuRef keep every layer
+    kinds = Counter(t for t, _ in hostnet.ArmnnNetwork(net, "CpuRef", optimize_only=True).optimized_layers)
+    assert kinds["PreCompiled"] == 0 and kinds["ElementwiseBinary"] == 10
+
+
 def _pair(net, info, dtype, seed=3):
     rng = np.random.default_rng(seed)
     lo, hi = (0, 256) if dtype == np.uint8 else (-128, 128)
