@@ -173,6 +173,7 @@ public:
     bool AfterUnloadNetwork(NetworkId) override { return true; }
     bool AfterEnqueueWorkload(NetworkId) override
     {
+        B200Device::NextEpoch();                          // imported inputs are uploaded afresh by the next inference
         return cudaStreamSynchronize(B200Device::Get().Stream()) == cudaSuccess && b200k_poll_status() == B200K_OK;
     }
 };

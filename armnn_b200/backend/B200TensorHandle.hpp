@@ -5,6 +5,13 @@
 // (src/backends/backendsCommon/MemCopyWorkload.cpp:51-64), so a device handle owns a pinned host staging buffer:
 // Map() = stream synchronise + device->host copy when the device copy is newer, Unmap() = host->device copy.
 // The blocking Map of the output handle is the only per-inference synchronisation point.
+//
+// With INetworkProperties{MemorySource::Malloc, MemorySource::Malloc} (or IRuntime::ImportInputs / ImportOutputs) the
+// core hands the user's own buffers to Import() instead (src/armnn/LoadedNetwork.cpp:1008-1030, 1086-1115, 1401-1520):
+// an imported handle has no staging buffer; its device copy is filled straight from the user's memory when the first
+// workload of an inference reads it, and a handle a workload has written is copied straight into the user's memory
+// by the Map() of the core's SyncMemGenericWorkload.  A buffer that comes back for a second inference is page-locked
+// (cudaHostRegister) until Unimport(), so that its transfers are asynchronous DMA.
 #pragma once
 
 #include <armnn/backends/IMemoryManager.hpp>
@@ -13,6 +20,8 @@
 #include <armnn/backends/TensorHandle.hpp>
 
 #include <cuda_runtime.h>
+
+#include <cstdint>
 
 namespace armnn
 {
@@ -28,6 +37,9 @@ public:
     static B200Device& Get();
     static void Configure(int deviceId);            // before first use; throws BackendUnavailableException
     cudaStream_t Stream() const { return m_Stream; }
+    /// Counts inferences (advanced by IBackendContext::AfterEnqueueWorkload): an imported input is uploaded once per epoch.
+    static uint64_t Epoch();
+    static void NextEpoch();
     int Id() const { return m_Device; }
     void MakeCurrent() const;
 private:
@@ -67,6 +79,14 @@ public:
     void CopyOutTo(void* memory) const override;
     void CopyInFrom(const void* memory) override;
 
+    unsigned int GetImportFlags() const override { return static_cast<unsigned int>(MemorySource::Malloc); }
+    bool CanBeImported(void* memory, MemorySource source) override { return memory != nullptr && source == MemorySource::Malloc; }
+    bool Import(void* memory, MemorySource source) override;
+    void Unimport() override;
+    /// For a workload about to read this handle: when it is an imported network input, bring the user's memory to
+    /// the device (once per inference).
+    void SyncImportedToDevice() const;
+
     /// Device pointer for kernels (allocates on first use).
     void* Device() const;
     /// A workload has written the device copy: the next Map() must read it back.
@@ -81,6 +101,11 @@ private:
     mutable void* m_Host = nullptr;                  // pinned staging
     mutable bool m_DeviceNewer = false;
     mutable bool m_ReadOnlyMapping = false;
+    void PinIfReused() const;
+    void* m_Imported = nullptr;                      // the user's buffer (host), or nullptr
+    mutable bool m_Registered = false;               // we page-locked m_Imported
+    mutable unsigned int m_Transfers = 0;            // transfers from / to m_Imported so far
+    mutable uint64_t m_UploadEpoch = 0;
 };
 
 class B200TensorHandleFactory : public ITensorHandleFactory
@@ -104,7 +129,7 @@ public:
     bool SupportsSubTensors() const override { return false; }
     bool SupportsMapUnmap() const override { return true; }
     MemorySourceFlags GetExportFlags() const override { return 0; }
-    MemorySourceFlags GetImportFlags() const override { return 0; }
+    MemorySourceFlags GetImportFlags() const override { return static_cast<MemorySourceFlags>(MemorySource::Malloc); }
 
 private:
     std::shared_ptr<B200MemoryManager> m_MemoryManager;

@@ -120,9 +120,15 @@ public:
     {
         B200Device& dev = B200Device::Get();
         dev.MakeCurrent();
+        for (ITensorHandle* h : this->m_Data.m_Inputs) { PolymorphicDowncast<const B200TensorHandle*>(h)->SyncImportedToDevice(); }
         m_Launch(this->m_Data, dev.Stream());
         for (ITensorHandle* h : this->m_Data.m_Outputs) { Written(h); }
     }
+    // handles are resolved at Execute time, so the core may swap in its pre-imported handles
+    // (src/armnn/LoadedNetwork.cpp:821-833, 877-894)
+    bool SupportsTensorHandleReplacement() const override { return true; }
+    void ReplaceInputTensorHandle(ITensorHandle* h, unsigned int slot) override { this->m_Data.m_Inputs[slot] = h; }
+    void ReplaceOutputTensorHandle(ITensorHandle* h, unsigned int slot) override { this->m_Data.m_Outputs[slot] = h; }
 private:
     Launch m_Launch;
 };

@@ -422,6 +422,11 @@ struct CLoaded {
     CRuntime* rt;
     NetworkId id;
     std::vector<std::pair<int, TensorInfo>> inputs, outputs;
+    // IRuntime::ImportInputs / ImportOutputs state of armnnc_enqueue_preimported
+    std::vector<const void*> pre_in_ptrs;
+    std::vector<void*> pre_out_ptrs;
+    std::vector<ImportedInputId> pre_in;
+    std::vector<ImportedOutputId> pre_out;
 };
 
 TensorInfo info_from(int dtype, int rank, const int32_t* shape, float scale, int32_t zp, const float* scales,
@@ -640,9 +645,12 @@ int armnnc_add_output(void* vn, int binding, int from_layer, int from_slot)
 }
 
 // Optimize for the comma-separated backend preference list and load.  device_id >= 0 is passed to
-// the B200Acc backend as ModelOption "DeviceId".
-void* armnnc_load(void* vr, void* vn, const char* backends, int device_id, int profiling)
+// the B200Acc backend as ModelOption "DeviceId".  flags: bit 0 = profiling, bit 1 = load with
+// INetworkProperties{MemorySource::Malloc, MemorySource::Malloc} (EnqueueWorkload imports the caller's buffers).
+void* armnnc_load(void* vr, void* vn, const char* backends, int device_id, int flags)
 {
+    const int profiling = flags & 1;
+    const MemorySource io = (flags & 2) ? MemorySource::Malloc : MemorySource::Undefined;
     auto* r = static_cast<CRuntime*>(vr);
     auto* n = static_cast<CNet*>(vn);
     try {
@@ -658,13 +666,14 @@ void* armnnc_load(void* vr, void* vn, const char* backends, int device_id, int p
         OptimizerOptionsOpaque oo;
         if (device_id >= 0) oo.AddModelOption(BackendOptions("B200Acc", {{"DeviceId", device_id}}));
         oo.SetProfilingEnabled(profiling != 0);
+        if (flags & 2) { oo.SetImportEnabled(true); oo.SetExportEnabled(true); }
         std::vector<std::string> messages;
         IOptimizedNetworkPtr opt = Optimize(*n->net, prefs, r->rt->GetDeviceSpec(), oo, Optional<std::vector<std::string>&>(messages));
         if (!opt) { g_err = "Optimize returned null"; for (auto& m : messages) g_err += "; " + m; return nullptr; }
         auto* l = new CLoaded;
         l->rt = r;
         std::string err;
-        INetworkProperties props(MemorySource::Undefined, MemorySource::Undefined, profiling != 0);
+        INetworkProperties props(io, io, profiling != 0);
         if (r->rt->LoadNetwork(l->id, std::move(opt), err, props) != Status::Success) {
             g_err = "LoadNetwork failed: " + err;
             delete l;
@@ -721,6 +730,36 @@ int armnnc_enqueue(void* vl, const void* const* inputs, void* const* outputs)
         for (size_t i = 0; i < l->outputs.size(); ++i)
             out.emplace_back(l->outputs[i].first, Tensor(l->outputs[i].second, outputs[i]));
         return l->rt->rt->EnqueueWorkload(l->id, in, out) == Status::Success ? 0 : -1;
+    } catch (const std::exception& e) { g_err = e.what(); return -1; }
+}
+
+// The same through the pre-import API: the first call (and any call with other pointers) imports the buffers with
+// IRuntime::ImportInputs / ImportOutputs(MemorySource::Malloc); EnqueueWorkload then runs on the imported ids only.
+int armnnc_enqueue_preimported(void* vl, const void* const* inputs, void* const* outputs)
+{
+    auto* l = static_cast<CLoaded*>(vl);
+    try {
+        std::vector<const void*> in_ptrs(inputs, inputs + l->inputs.size());
+        std::vector<void*> out_ptrs(outputs, outputs + l->outputs.size());
+        if (in_ptrs != l->pre_in_ptrs || out_ptrs != l->pre_out_ptrs) {
+            InputTensors in;
+            OutputTensors out;
+            for (size_t i = 0; i < l->inputs.size(); ++i) {
+                TensorInfo info = l->inputs[i].second;
+                info.SetConstant(true);
+                in.emplace_back(l->inputs[i].first, ConstTensor(info, inputs[i]));
+            }
+            for (size_t i = 0; i < l->outputs.size(); ++i)
+                out.emplace_back(l->outputs[i].first, Tensor(l->outputs[i].second, outputs[i]));
+            l->pre_in = l->rt->rt->ImportInputs(l->id, in, MemorySource::Malloc);
+            l->pre_out = l->rt->rt->ImportOutputs(l->id, out, MemorySource::Malloc);
+            if (l->pre_in.size() != l->inputs.size() || l->pre_out.size() != l->outputs.size()) {
+                g_err = "ImportInputs / ImportOutputs did not import every tensor";
+                return -2;
+            }
+            l->pre_in_ptrs = in_ptrs; l->pre_out_ptrs = out_ptrs;
+        }
+        return l->rt->rt->EnqueueWorkload(l->id, {}, {}, l->pre_in, l->pre_out) == Status::Success ? 0 : -1;
     } catch (const std::exception& e) { g_err = e.what(); return -1; }
 }
 

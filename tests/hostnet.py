@@ -79,9 +79,10 @@ class ArmnnNetwork:
     def backend_available(name):
         return bool(cpuref().armnnc_backend_available(ArmnnNetwork.runtime(), name.encode()))
 
-    def __init__(self, network, backends="CpuRef", device_id=-1, profiling=False, optimize_only=False):
+    def __init__(self, network, backends="CpuRef", device_id=-1, profiling=False, optimize_only=False, import_io=False):
         """optimize_only: no LoadNetwork (needs no device); `self.optimized_layers` lists the optimized graph as
-        (layer type, name) in execution order."""
+        (layer type, name) in execution order.  import_io: load with INetworkProperties{Malloc, Malloc}, so that
+        EnqueueWorkload imports the caller's buffers instead of copying them."""
         lib = cpuref()
         self.lib = lib
         rt = self.runtime()
@@ -160,7 +161,7 @@ class ArmnnNetwork:
             self.optimized_layers = [tuple(line.split(" ", 1)) for line in buf.value.decode().splitlines()]
             self.handle = C.c_void_p(None)
             return
-        self.handle = C.c_void_p(lib.armnnc_load(rt, net, backends.encode(), device_id, int(profiling)))
+        self.handle = C.c_void_p(lib.armnnc_load(rt, net, backends.encode(), device_id, int(profiling) | (2 if import_io else 0)))
         err = lib.cpuref_last_error().decode()
         lib.armnnc_network_destroy(net)
         if not self.handle.value:
@@ -218,6 +219,15 @@ class ArmnnNetwork:
         rc = self.lib.armnnc_enqueue(self.handle, in_ptrs, out_ptrs)
         assert rc == 0, self.lib.cpuref_last_error().decode()
         return {bid: o for (bid, _), o in zip(self.out_infos, outs)}
+
+    def run_into(self, ins, outs, preimported=False):
+        """EnqueueWorkload on caller-owned arrays ({binding id: ndarray}, used in place: no copies made here).
+        preimported: through IRuntime::ImportInputs / ImportOutputs, importing the buffers on first use."""
+        in_ptrs = (C.c_void_p * len(self.in_infos))(*[ins[bid].ctypes.data for bid, _ in self.in_infos])
+        out_ptrs = (C.c_void_p * len(self.out_infos))(*[outs[bid].ctypes.data for bid, _ in self.out_infos])
+        fn = self.lib.armnnc_enqueue_preimported if preimported else self.lib.armnnc_enqueue
+        rc = fn(self.handle, in_ptrs, out_ptrs)
+        assert rc == 0, self.lib.cpuref_last_error().decode()
 
     def close(self):
         if self.handle is not None and self.handle.value:

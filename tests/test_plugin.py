@@ -126,3 +126,28 @@ def test_qlstm_stack_through_the_runtime_matches_cpuref():
             tol = 2 if want[k].dtype == np.int16 else 1
             assert st["max_abs"] <= tol and st["mismatch_frac"] <= 0.01, (step, k, st)
         state = {k: want[k] for k in state}
+
+
+@needs_plugin
+@pytest.mark.gpu
+@pytest.mark.parametrize("mode", ["import", "preimport"])
+def test_imported_io_buffers_match_copied_ones(mode):
+    """INetworkProperties{Malloc, Malloc} (the core calls ITensorHandle::Import on every EnqueueWorkload) and
+    IRuntime::ImportInputs / ImportOutputs (imported once, buffers rewritten in place between inferences) give the
+    results of the copying path, inference after inference."""
+    from armnn_b200 import configs
+    net, info = configs.resnet50(2, 64)
+    copied = hostnet.ArmnnNetwork(net, "B200Acc")
+    imported = hostnet.ArmnnNetwork(net, "B200Acc", import_io=(mode == "import"))
+    rng = np.random.default_rng(11)
+    x = np.zeros(info["input_shape"], np.int8)
+    y = np.zeros(info["output_shape"], np.int8)
+    seen = set()
+    for _ in range(4):
+        x[...] = rng.integers(-128, 128, size=x.shape)
+        want = copied.run({0: x})[0]
+        y[...] = 0
+        imported.run_into({0: x}, {0: y}, preimported=(mode == "preimport"))
+        assert np.array_equal(want, y)
+        seen.add(y.tobytes())
+    assert len(seen) > 1
