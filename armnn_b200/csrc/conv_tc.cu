@@ -50,7 +50,13 @@ constexpr int TC_LUT_TAG_WORDS = 12;
 // hit one bank.
 constexpr int TC_LUT_PITCH = 260;
 constexpr int TC_LUT_BYTES = 256 * TC_LUT_PITCH;
-constexpr int TC_THREADS = 64 + 32 * TC_EPI_WARPS;   // warp 0 producer, warp 1 MMA issuer, then the epilogue warps
+// One thread issues a TMA load (wait for the slot, arm its barrier, issue) about every 170 ns, whatever the size of the
+// box, and several issuing threads scale linearly (measured: 172 / 87 / 44 ns per load with 1 / 2 / 4 warps).  With one
+// producer thread every K-slice costs 0.2 - 0.45 us, more than its MMAs take unless the tile is very wide, so the
+// K-slices are dealt round-robin to TC_PRODUCERS producer threads, each in a warp of its own.
+constexpr int TC_PRODUCERS = 4;
+// warp 0: producer 0; warp 1: MMA issuer; then the epilogue warps; then producers 1 .. TC_PRODUCERS - 1
+constexpr int TC_THREADS = 64 + 32 * TC_EPI_WARPS + 32 * (TC_PRODUCERS - 1);
 
 constexpr long long TC_WAIT_LIMIT_CYCLES = 4000000000ll;  // about two seconds: no wait of a healthy launch comes near
 
@@ -88,6 +94,7 @@ struct TcArgs {
     const uint8_t* add_lut;                     // fused-add table built by b200k_conv2d_pack (+ its tag), or null
     uint32_t lut_tag[TC_LUT_TAG_WORDS];         // the tag a table made for exactly this launch carries
     int stages;                                 // ring depth chosen by the launcher (<= 16)
+    int nprod;                                  // producer threads that take turns: 1, 2 or 4, never more than stages
     int bstat;                                  // weights stay in shared memory for the whole launch (one n-tile, small K)
     int nio;                                    // shared buffers for units of the fused Add's other operand: 0 or 2
     // zero-point correction classes: pixels whose in-image tap rectangle [ky0, ky1) x [kx0, kx1) is the same share
@@ -96,12 +103,25 @@ struct TcArgs {
     int ncy, ncx, ncls;
     uint8_t ypair[16], xpair[16];
     uint8_t ycls[256], xcls[256];
-    int debug;                                  // 0 normal; 1: main loop without MMAs; 2: main loop without TMA loads
+    int debug;                                  // timing experiments (results are wrong): bit 0 no MMAs, bit 1 no TMA loads, bit 2 no epilogue work
 };
 
 // ---- PTX wrappers --------------------------------------------------------------------------------------
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+// One lane of a converged warp.  The single-thread roles are written as warp-uniform code, in which only the issuing
+// instructions themselves are restricted to the elected lane: TMA, MMA and mbarrier instructions take their operands from
+// uniform registers, and inside a branch on the lane index every operand would have to be moved there one by one, which
+// made each issue cost 100 - 170 cycles.
+__device__ __forceinline__ bool elect_one()
+{
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "elect.sync _|p, 0xffffffff;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+    return pred != 0;
+}
 
 __device__ __forceinline__ void mbar_init(uint64_t* bar, int count)
 {
@@ -542,7 +562,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     uint8_t* s_lut = (uint8_t*)(((uintptr_t)(s_cc + a.ncls * BN) + 255) & ~(uintptr_t)255);   // fused-add table, 256-byte aligned
 
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");     // the next kernel of the stream may begin its set-up
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;   // warp: provably uniform
     const int ntn = a.ntn;                                  // n-tiles; the last one may reach beyond OC (zero weights, clipped stores)
     const int ntiles = ntn * a.ntm;
 
@@ -574,9 +594,15 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    if (warp == 0) {
-        // ===================== TMA producer =====================
-        if (lane == 0) {
+    const int prod = warp == 0 ? 0 : (warp >= 2 + TC_EPI_WARPS ? warp - (1 + TC_EPI_WARPS) : -1);
+    if (prod >= 0) {
+        // ===================== TMA producers =====================
+        // Every producer walks all tiles and K-slices and issues the loads of every nprod-th slice (counted over the
+        // whole launch), so the ring is still filled in order; producer 0 also loads the stationary weights and the
+        // fused Add's operand.  Producers beyond nprod (short rings) never get a turn.
+        {
+            uint32_t turn = 0;                               // global slice counter modulo the number of active producers
+            const uint32_t turn_mask = (uint32_t)a.nprod - 1u;
             int st = 0; uint32_t ph = 0;                     // ring position: stage and its phase bit
             int ub = 0; uint32_t uph = 0;                    // unit-buffer position (kept without divisions)
             bool alive = true;
@@ -586,7 +612,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const bool bstat = a.bstat != 0;
             const uint32_t stage_tx = a.stage_tx;
             // weights, scales, bias and tables do not depend on the previous kernel of the stream; activations do
-            if (a.bstat && a.debug != 2) {
+            if (a.bstat && !(a.debug & 2) && prod == 0 && elect_one()) {
                 mbar_expect_tx(w_full, (uint32_t)a.nslices * L::B_BYTES);
                 for (int s = 0; s < a.nslices; ++s) {
                     const int tap = s / a.cchunks;
@@ -613,19 +639,24 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 // slice = (filter tap (ky, kx), channel chunk); everything the loop needs is kept incrementally
                 int ky = 0, kx = 0, cc = 0, kcol = 0;             // kcol: the slice's first byte in a weight row
                 for (int s = 0; s < nslices; ++s) {
-                    if (!mbar_wait_fast(empty_addr + st * 8, ph ^ 1u)) { atomicExch(&g_tc_status, 1); alive = false; break; }
-                    const uint32_t sa = ring_addr + st * stage_stride;
-                    const uint32_t fb = full_addr + st * 8;
-                    const int c0 = cc * SWZ;
-                    if (debug == 2) {
-                        mbar_arrive_s(fb);
-                    } else {
-                        mbar_expect_tx_s(fb, stage_tx);
-                        if (mode == 2)      tma_load_4d_s(sa, &tmA, fb, 0, 0, h0 + ky * dh, nimg);          // slice = filter row
-                        else if (mode == 1) tma_load_im2col_s(sa, &tmA, fb, c0, w0, h0, nimg, (uint16_t)(kx * dw), (uint16_t)(ky * dh));
-                        else                tma_load_2d_s(sa, &tmA, fb, c0, (int)m0);
-                        if (!bstat) tma_load_2d_s(sa + L::A_BYTES, &tmB, fb, kcol + c0, n0);
+                    if (turn == (uint32_t)prod) {
+                        if (!__all_sync(0xffffffffu, mbar_wait_fast(empty_addr + st * 8, ph ^ 1u))) { atomicExch(&g_tc_status, 1); alive = false; break; }
+                        const uint32_t sa = ring_addr + st * stage_stride;
+                        const uint32_t fb = full_addr + st * 8;
+                        const int c0 = cc * SWZ;
+                        if (elect_one()) {
+                            if (debug & 2) {
+                                mbar_arrive_s(fb);
+                            } else {
+                                mbar_expect_tx_s(fb, stage_tx);
+                                if (mode == 2)      tma_load_4d_s(sa, &tmA, fb, 0, 0, h0 + ky * dh, nimg);      // slice = filter row
+                                else if (mode == 1) tma_load_im2col_s(sa, &tmA, fb, c0, w0, h0, nimg, (uint16_t)(kx * dw), (uint16_t)(ky * dh));
+                                else                tma_load_2d_s(sa, &tmA, fb, c0, (int)m0);
+                                if (!bstat) tma_load_2d_s(sa + L::A_BYTES, &tmB, fb, kcol + c0, n0);
+                            }
+                        }
                     }
+                    turn = (turn + 1) & turn_mask;
                     if (++st == STAGES) { st = 0; ph ^= 1u; }
                     if (++cc == cchunks) {
                         cc = 0; kcol += kstride;
@@ -633,13 +664,15 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         else if (++kx == KW) { kx = 0; ++ky; }
                     }
                 }
-                if (a.res && alive) {
+                if (a.res && alive && prod == 0) {
                     // the fused Add's other operand, one unit at a time, into the buffer the epilogue will overwrite
                     for (int us = 0; us < UNITS; ++us) {
-                        if (!mbar_wait(&io_empty[ub], uph ^ 1u)) { atomicExch(&g_tc_status, 6); alive = false; break; }
-                        mbar_expect_tx(&io_full[ub], IO_BYTES);
-                        tma_load_3d(s_io + (size_t)(1 + ub) * IO_BYTES, &tmR, &io_full[ub], n0 + us * UW,
-                                    a.im2col == 2 ? 0 : (int)m0, a.im2col == 2 ? tm : 0);
+                        if (!__all_sync(0xffffffffu, mbar_wait(&io_empty[ub], uph ^ 1u))) { atomicExch(&g_tc_status, 6); alive = false; break; }
+                        if (elect_one()) {
+                            mbar_expect_tx(&io_full[ub], IO_BYTES);
+                            tma_load_3d(s_io + (size_t)(1 + ub) * IO_BYTES, &tmR, &io_full[ub], n0 + us * UW,
+                                        a.im2col == 2 ? 0 : (int)m0, a.im2col == 2 ? tm : 0);
+                        }
                         if (++ub == NIO) { ub = 0; uph ^= 1u; }
                     }
                 }
@@ -647,7 +680,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
     } else if (warp == 1) {
         // ===================== MMA issuer =====================
-        if (lane == 0) {
+        {
             // instruction descriptor: D = S32 (bits 4-5 = 2); A / B format at bits 7 / 10 (1 = signed 8-bit,
             // 0 = unsigned 8-bit); both operands K-major (bits 15, 16 = 0); N >> 3 at bit 17; M >> 4 at bit 24
             const uint32_t id = (2u << 4) | ((uint32_t)a.a_signed << 7) | ((uint32_t)a.b_signed << 10) |
@@ -666,36 +699,41 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const uint64_t dstage = (uint64_t)(stage_stride >> 4);
             const uint64_t dwslice = (uint64_t)(L::B_BYTES >> 4);
             const uint64_t dz0 = make_smem_desc<SWZ>(smem_u32(s_zw));
-            if (bstat && debug != 2 && !mbar_wait(w_full, 0)) { atomicExch(&g_tc_status, 7); alive = false; }
+            if (bstat && !(debug & 2) && !__all_sync(0xffffffffu, mbar_wait(w_full, 0))) { atomicExch(&g_tc_status, 7); alive = false; }
             tc_fence_after();
             for (int t = blockIdx.x; t < ntiles && alive; t += gridDim.x, ++it) {
                 const int buf = it & 1;
                 // the epilogue must have drained this accumulator buffer (two tiles ago)
-                if (!mbar_wait(&acc_empty[buf], (((uint32_t)it >> 1) & 1u) ^ 1u)) { atomicExch(&g_tc_status, 4); break; }
+                if (!__all_sync(0xffffffffu, mbar_wait(&acc_empty[buf], (((uint32_t)it >> 1) & 1u) ^ 1u))) { atomicExch(&g_tc_status, 4); break; }
                 tc_fence_after();
                 const uint32_t tacc = tmem_base + (uint32_t)(buf * BN);
                 uint64_t dbs = db0;                              // stationary weights: the slice's tile
                 for (int s = 0; s < nslices; ++s) {
-                    if (!mbar_wait_fast(full_addr + st * 8, ph)) { atomicExch(&g_tc_status, 2); alive = false; break; }
+                    if (!__all_sync(0xffffffffu, mbar_wait_fast(full_addr + st * 8, ph))) { atomicExch(&g_tc_status, 2); alive = false; break; }
                     tc_fence_after();
                     const uint32_t eb = empty_addr + st * 8;
                     const uint64_t da = da0 + dstage * (uint64_t)st;
                     const uint64_t db = bstat ? dbs : db0 + dstage * (uint64_t)st;
                     dbs += dwslice;
                     if (++st == STAGES) { st = 0; ph ^= 1u; }
-                    if (debug == 1) { mbar_arrive_s(eb); continue; }
-                    if (s == 0) tc_mma_i8(tacc, da, db, id, 0u);
-                    else        tc_mma_i8_acc(tacc, da, db, id);
-                    #pragma unroll
-                    for (int k = 1; k < SWZ / 32; ++k) tc_mma_i8_acc(tacc, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), id);
-                    for (int z = 0; z < nzw; ++z) {
-                        const uint64_t dz = dz0 + dwslice * (uint64_t)z;
-                        #pragma unroll
-                        for (int k = 0; k < SWZ / 32; ++k) tc_mma_i8_acc(tacc, da + (uint64_t)(k * 2), dz + (uint64_t)(k * 2), id_zw);
+                    if (elect_one()) {                 // the same lane every time: a commit covers the MMAs of its own thread
+                        if (debug & 1) {
+                            mbar_arrive_s(eb);
+                        } else {
+                            if (s == 0) tc_mma_i8(tacc, da, db, id, 0u);
+                            else        tc_mma_i8_acc(tacc, da, db, id);
+                            #pragma unroll
+                            for (int k = 1; k < SWZ / 32; ++k) tc_mma_i8_acc(tacc, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), id);
+                            for (int z = 0; z < nzw; ++z) {
+                                const uint64_t dz = dz0 + dwslice * (uint64_t)z;
+                                #pragma unroll
+                                for (int k = 0; k < SWZ / 32; ++k) tc_mma_i8_acc(tacc, da + (uint64_t)(k * 2), dz + (uint64_t)(k * 2), id_zw);
+                            }
+                            tc_commit_s(eb);           // slot reusable once these MMAs have read it
+                        }
                     }
-                    tc_commit_s(eb);                   // slot reusable once these MMAs have read it
                 }
-                if (alive) tc_commit(&acc_full[buf]);  // accumulator of this tile complete
+                if (alive && elect_one()) tc_commit(&acc_full[buf]);  // accumulator of this tile complete
             }
         }
     } else {
@@ -816,7 +854,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const uint32_t a_m = smem_u32(s_m), a_b = smem_u32(s_bterm), a_cc = smem_u32(corr_row);
             const uint32_t tacc = tmem_base + (uint32_t)(buf * BN) + ((uint32_t)(quad * 32) << 16);
             // units in which this warp has real columns (a prefix: the last n-tile may reach beyond OC)
-            const int nact = min(UNITS, max(0, (a.OC - n0 - part * (UW / 4) + UW - 1) / UW));
+            const int nact = ((a.debug & 4) && !fused) ? 0 : min(UNITS, max(0, (a.OC - n0 - part * (UW / 4) + UW - 1) / UW));
             #pragma unroll 1
             for (int us = 0; us < nact; ++us) {
                 const uint32_t res_row = smem_u32(s_io + (size_t)(1 + ub) * IO_BYTES + row * UW);
@@ -1186,6 +1224,10 @@ static int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUten
     int stages = (int)((budget - fixed) / stride);
     if (stages > L::MAX_STAGES) stages = L::MAX_STAGES;
     a2.stages = stages;
+    // A producer tells "slot consumed" from "slot consumed one ring pass earlier" by the barrier's phase parity alone,
+    // which is only sound while it cannot run more than one pass ahead of the consumer: its previous turn (nprod
+    // slices back) must lie within the same ring pass as the slot it waits for, i.e. nprod <= stages.
+    a2.nprod = stages >= TC_PRODUCERS ? TC_PRODUCERS : (stages >= 2 ? 2 : 1);
     if (a2.bstat) a2.stage_tx = (uint32_t)(a.stage_tx - L::B_BYTES);
     const size_t smem = fixed + (size_t)stages * stride;
     auto kern = conv_tc_kernel<BN, SWZ>;
@@ -1275,7 +1317,7 @@ int launch_conv_tc(const b200k_conv2d_params* p, cudaStream_t stream, int kvalid
         memcpy(a.ypair, tc.ypair, 16); memcpy(a.xpair, tc.xpair, 16);
         memcpy(a.ycls, tc.ycls, 256);  memcpy(a.xcls, tc.xcls, 256);
     }
-    // Measurement aid (results are wrong in modes 1 and 2): isolates the TMA side or the MMA side of the main loop.
+    // Measurement aid (results are wrong when set): a bit mask that switches off the MMAs, the TMA loads or the epilogue work.
     static const int debug_mode = getenv("B200K_TC_DEBUG") ? atoi(getenv("B200K_TC_DEBUG")) : 0;
     a.debug = debug_mode;
 

@@ -29,6 +29,9 @@ CONV = {
     "im2col_no_pad_valid": lambda: random_conv_case(214, 1, 12, 12, 64, 128, 3, 3),
     "im2col_rect_3x1": lambda: random_conv_case(215, 1, 9, 11, 64, 64, 3, 1, stride=(1, 2), pad=(1, 1, 0, 0)),
     "gemm_fused_add_relu": lambda: random_conv_case(217, 2, 28, 28, 128, 512, 1, 1, act=(1, 0, 0), fused_add=True),
+    # wide tiles + fused-add table leave a ring of two stages: several tiles per CTA, several K-slices per tile, so the
+    # ring wraps many times with more producer warps than stages
+    "gemm_fused_add_short_ring": lambda: random_conv_case(219, 24, 56, 56, 256, 256, 1, 1, act=(1, 0, 0), fused_add=True),
     "im2col_fused_add": lambda: random_conv_case(218, 2, 14, 14, 64, 64, 3, 3, pad=(1, 1, 1, 1), fused_add=True),
     "gemm_many_tiles_persistent": lambda: random_conv_case(219, 4, 56, 56, 64, 256, 1, 1, act=(1, 0, 0)),
     "im2col_many_tiles_persistent": lambda: random_conv_case(220, 6, 28, 28, 128, 128, 3, 3, pad=(1, 1, 1, 1)),
