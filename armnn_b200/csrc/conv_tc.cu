@@ -50,11 +50,14 @@ constexpr int TC_LUT_TAG_WORDS = 12;
 // hit one bank.
 constexpr int TC_LUT_PITCH = 260;
 constexpr int TC_LUT_BYTES = 256 * TC_LUT_PITCH;
-// One thread issues a TMA load (wait for the slot, arm its barrier, issue) about every 170 ns, whatever the size of the
-// box, and several issuing threads scale linearly (measured: 172 / 87 / 44 ns per load with 1 / 2 / 4 warps).  With one
-// producer thread every K-slice costs 0.2 - 0.45 us, more than its MMAs take unless the tile is very wide, so the
-// K-slices are dealt round-robin to TC_PRODUCERS producer threads, each in a warp of its own.
-constexpr int TC_PRODUCERS = 4;
+// The K-slices are dealt round-robin to TC_PRODUCERS producer warps.  Issuing a load (wait for the slot, arm its
+// barrier, issue) is a chain of dependent shared-memory operations in one thread; for narrow tiles, whose MMAs are short,
+// one producer cannot keep up (stem and 3 x 3 layers with 64 channels ran 25 % slower with one producer than with
+// two), while four cost the epilogue-bound layers more issue slots than they gain elsewhere.
+#ifndef B200K_TC_PRODUCERS
+#define B200K_TC_PRODUCERS 2
+#endif
+constexpr int TC_PRODUCERS = B200K_TC_PRODUCERS;     // 1, 2 or 4
 // warp 0: producer 0; warp 1: MMA issuer; then the epilogue warps; then producers 1 .. TC_PRODUCERS - 1
 constexpr int TC_THREADS = 64 + 32 * TC_EPI_WARPS + 32 * (TC_PRODUCERS - 1);
 
@@ -95,6 +98,7 @@ struct TcArgs {
     uint32_t lut_tag[TC_LUT_TAG_WORDS];         // the tag a table made for exactly this launch carries
     int stages;                                 // ring depth chosen by the launcher (<= 16)
     int nprod;                                  // producer threads that take turns: 1, 2 or 4, never more than stages
+    int group;                                  // K-slices per ring stage: they share the stage's pair of barriers
     int bstat;                                  // weights stay in shared memory for the whole launch (one n-tile, small K)
     int nio;                                    // shared buffers for units of the fused Add's other operand: 0 or 2
     // zero-point correction classes: pixels whose in-image tap rectangle [ky0, ky1) x [kx0, kx1) is the same share
@@ -546,7 +550,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // weight-stationary launches: all K-slices of the (only) weight tile first, then a ring of activation tiles only
     const int stage_stride = a.bstat ? L::A_BYTES : L::STAGE_BYTES;
     uint8_t* ring = s_wst + (a.bstat ? (size_t)a.nslices * L::B_BYTES : 0);
-    uint8_t* s_io = ring + (size_t)STAGES * stage_stride;
+    uint8_t* s_io = ring + (size_t)STAGES * a.group * stage_stride;
     float* s_m = (float*)(s_io + (size_t)(1 + NIO) * IO_BYTES);      // [0]: the warps' staging buffers; then NIO operand units
     float* s_bterm = s_m + BN;
     uint64_t* full = (uint64_t*)(s_bterm + BN);
@@ -560,6 +564,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     uint32_t* s_lut_ok = tmem_slot + 1;                     // the fused-add table in global memory carries our tag
     int32_t* s_cc = (int32_t*)(tmem_slot + 4);              // [classes][BN] zero-point corrections
     uint8_t* s_lut = (uint8_t*)(((uintptr_t)(s_cc + a.ncls * BN) + 255) & ~(uintptr_t)255);   // fused-add table, 256-byte aligned
+    // per K-slice: {channel offset, im2col offsets (x | y << 16), weight column, packed-row offset}: the producers read
+    // their coordinates from here instead of carrying tap counters through every slice
+    uint4* s_tab = (uint4*)(s_lut + (a.add_lut ? TC_LUT_BYTES : 0));
 
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");     // the next kernel of the stream may begin its set-up
     const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;   // warp: provably uniform
@@ -589,6 +596,12 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
+    for (int i = threadIdx.x; i < a.nslices; i += TC_THREADS) {
+        const int tap = i / a.cchunks, c0 = (i - tap * a.cchunks) * SWZ;
+        const int ky = a.im2col == 2 ? tap : tap / a.KW, kx = a.im2col == 2 ? 0 : tap - ky * a.KW;
+        s_tab[i] = make_uint4((uint32_t)c0, (uint32_t)(kx * a.dw) | ((uint32_t)(ky * a.dh) << 16), (uint32_t)(tap * a.kstride + c0),
+                              (uint32_t)(ky * a.dh));
+    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -597,75 +610,81 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int prod = warp == 0 ? 0 : (warp >= 2 + TC_EPI_WARPS ? warp - (1 + TC_EPI_WARPS) : -1);
     if (prod >= 0) {
         // ===================== TMA producers =====================
-        // Every producer walks all tiles and K-slices and issues the loads of every nprod-th slice (counted over the
-        // whole launch), so the ring is still filled in order; producer 0 also loads the stationary weights and the
-        // fused Add's operand.  Producers beyond nprod (short rings) never get a turn.
+        // The ring is filled stage by stage (a stage = `group` consecutive K-slices of one tile); the stages are dealt
+        // round-robin to the active producers, which all walk the same sequence of tiles and stages.  Producer 0 also
+        // loads the stationary weights and the fused Add's operand.  Producers beyond nprod (short rings) never get a
+        // turn.  Everything a producer does per stage that is not its own is a handful of uniform instructions: these
+        // are single chains of dependent instructions, whose latency (not throughput) is what a stage costs.
         {
-            uint32_t turn = 0;                               // global slice counter modulo the number of active producers
+            uint32_t turn = 0;                               // global stage counter modulo the number of active producers
             const uint32_t turn_mask = (uint32_t)a.nprod - 1u;
+            const int group = a.group, gpt = a.nslices / a.group;          // slices per stage, stages per tile
             int st = 0; uint32_t ph = 0;                     // ring position: stage and its phase bit
             int ub = 0; uint32_t uph = 0;                    // unit-buffer position (kept without divisions)
             bool alive = true;
             const uint32_t ring_addr = smem_u32(ring), full_addr = smem_u32(full), empty_addr = smem_u32(empty);
-            const int nslices = a.nslices, cchunks = a.cchunks, kstride = a.kstride, mode = a.im2col, debug = a.debug;
-            const int dh = a.dh, dw = a.dw, KW = a.KW;
+            const uint32_t tab_addr = smem_u32(s_tab);
+            const int mode = a.im2col, debug = a.debug;
             const bool bstat = a.bstat != 0;
-            const uint32_t stage_tx = a.stage_tx;
+            const uint32_t group_tx = a.stage_tx * (uint32_t)a.group;
+            const uint32_t group_stride = (uint32_t)stage_stride * (uint32_t)a.group;
             // weights, scales, bias and tables do not depend on the previous kernel of the stream; activations do
             if (a.bstat && !(a.debug & 2) && prod == 0 && elect_one()) {
                 mbar_expect_tx(w_full, (uint32_t)a.nslices * L::B_BYTES);
-                for (int s = 0; s < a.nslices; ++s) {
-                    const int tap = s / a.cchunks;
-                    tma_load_2d(s_wst + (size_t)s * L::B_BYTES, &tmB, w_full, tap * a.kstride + (s - tap * a.cchunks) * SWZ, 0);
-                }
+                for (int s = 0; s < a.nslices; ++s)
+                    tma_load_2d(s_wst + (size_t)s * L::B_BYTES, &tmB, w_full, (int)s_tab[s].z, 0);
             }
             asm volatile("griddepcontrol.wait;" ::: "memory");
             for (int t = blockIdx.x; t < ntiles && alive; t += gridDim.x) {
-                const int n0 = (t % ntn) * BN;
-                const int tm = t / ntn;
-                const long long m0 = (long long)tm * a.tile_rows;
-                int w0 = 0, h0 = 0, nimg = 0;
-                if (a.im2col == 2) {
-                    nimg = tm / a.OH;
-                    h0 = (tm % a.OH) * a.sh;                      // first packed row of this output row
-                } else if (a.im2col) {
-                    const int ox = (int)(m0 % a.OW);
-                    const long long q = m0 / a.OW;
-                    const int oy = (int)(q % a.OH);
-                    nimg = (int)(q / a.OH);
-                    w0 = ox * a.sw - a.pl;
-                    h0 = oy * a.sh - a.pt;
-                }
-                // slice = (filter tap (ky, kx), channel chunk); everything the loop needs is kept incrementally
-                int ky = 0, kx = 0, cc = 0, kcol = 0;             // kcol: the slice's first byte in a weight row
-                for (int s = 0; s < nslices; ++s) {
+                // tile coordinates: only worked out by a producer that loads something of this tile
+                int n0 = 0, tm = 0, w0 = 0, h0 = 0, nimg = 0;
+                long long m0 = 0;
+                bool have = false;
+                auto locate = [&]() {
+                    n0 = (t % ntn) * BN;
+                    tm = t / ntn;
+                    m0 = (long long)tm * a.tile_rows;
+                    if (a.im2col == 2) {
+                        nimg = tm / a.OH;
+                        h0 = (tm % a.OH) * a.sh;                  // first packed row of this output row
+                    } else if (a.im2col) {
+                        const int ox = (int)(m0 % a.OW);
+                        const long long q = m0 / a.OW;
+                        const int oy = (int)(q % a.OH);
+                        nimg = (int)(q / a.OH);
+                        w0 = ox * a.sw - a.pl;
+                        h0 = oy * a.sh - a.pt;
+                    }
+                    have = true;
+                };
+                uint32_t te = tab_addr;                           // table entry of the stage's first slice
+                for (int g = 0; g < gpt && alive; ++g, te += 16u * (uint32_t)group) {
                     if (turn == (uint32_t)prod) {
-                        if (!__all_sync(0xffffffffu, mbar_wait_fast(empty_addr + st * 8, ph ^ 1u))) { atomicExch(&g_tc_status, 1); alive = false; break; }
-                        const uint32_t sa = ring_addr + st * stage_stride;
+                        if (!have) locate();
+                        if (!__all_sync(0xffffffffu, mbar_wait_fast(empty_addr + st * 8, ph ^ 1u))) { atomicExch(&g_tc_status, 1); alive = false; }
                         const uint32_t fb = full_addr + st * 8;
-                        const int c0 = cc * SWZ;
-                        if (elect_one()) {
+                        if (alive && elect_one()) {
                             if (debug & 2) {
                                 mbar_arrive_s(fb);
                             } else {
-                                mbar_expect_tx_s(fb, stage_tx);
-                                if (mode == 2)      tma_load_4d_s(sa, &tmA, fb, 0, 0, h0 + ky * dh, nimg);      // slice = filter row
-                                else if (mode == 1) tma_load_im2col_s(sa, &tmA, fb, c0, w0, h0, nimg, (uint16_t)(kx * dw), (uint16_t)(ky * dh));
-                                else                tma_load_2d_s(sa, &tmA, fb, c0, (int)m0);
-                                if (!bstat) tma_load_2d_s(sa + L::A_BYTES, &tmB, fb, kcol + c0, n0);
+                                mbar_expect_tx_s(fb, group_tx);
+                                uint32_t sa = ring_addr + (uint32_t)st * group_stride;
+                                for (int gs = 0; gs < group; ++gs, sa += (uint32_t)stage_stride) {
+                                    const uint4 e = lds128(te + 16u * (uint32_t)gs);
+                                    if (mode == 2)      tma_load_4d_s(sa, &tmA, fb, 0, 0, h0 + (int)e.w, nimg);      // slice = filter row
+                                    else if (mode == 1) tma_load_im2col_s(sa, &tmA, fb, (int)e.x, w0, h0, nimg, (uint16_t)(e.y & 0xffffu), (uint16_t)(e.y >> 16));
+                                    else                tma_load_2d_s(sa, &tmA, fb, (int)e.x, (int)m0);
+                                    if (!bstat) tma_load_2d_s(sa + L::A_BYTES, &tmB, fb, (int)e.z, n0);
+                                }
                             }
                         }
                     }
                     turn = (turn + 1) & turn_mask;
                     if (++st == STAGES) { st = 0; ph ^= 1u; }
-                    if (++cc == cchunks) {
-                        cc = 0; kcol += kstride;
-                        if (mode == 2) ++ky;
-                        else if (++kx == KW) { kx = 0; ++ky; }
-                    }
                 }
                 if (a.res && alive && prod == 0) {
                     // the fused Add's other operand, one unit at a time, into the buffer the epilogue will overwrite
+                    if (!have) locate();
                     for (int us = 0; us < UNITS; ++us) {
                         if (!__all_sync(0xffffffffu, mbar_wait(&io_empty[ub], uph ^ 1u))) { atomicExch(&g_tc_status, 6); alive = false; break; }
                         if (elect_one()) {
@@ -687,17 +706,20 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                                 ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
             // the zero-point MMAs: same A, B = a constant int8 tile
             const uint32_t id_zw = (2u << 4) | ((uint32_t)a.a_signed << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
-            int st = 0; uint32_t ph = 0;                     // ring position
+            const int group = a.group, gpt = a.nslices / a.group;          // slices per stage, stages per tile
+            int st = 0; uint32_t ph = 0;                     // ring position: stage and its phase bit
             bool alive = true;
             int it = 0;
             const uint32_t full_addr = smem_u32(full), empty_addr = smem_u32(empty);
-            const int nslices = a.nslices, nzw = a.nzw, debug = a.debug;
+            const int nzw = a.nzw, debug = a.debug;
             const bool bstat = a.bstat != 0;
-            // descriptors differ from stage to stage only in the 14-bit start-address field: one add per slice
+            // descriptors differ from slot to slot only in the 14-bit start-address field: one add per slice
             const uint64_t da0 = make_smem_desc<SWZ>(smem_u32(ring));
             const uint64_t db0 = make_smem_desc<SWZ>(bstat ? smem_u32(s_wst) : smem_u32(ring) + L::A_BYTES);
             const uint64_t dstage = (uint64_t)(stage_stride >> 4);
+            const uint64_t dgroup = dstage * (uint64_t)a.group;
             const uint64_t dwslice = (uint64_t)(L::B_BYTES >> 4);
+            const uint64_t dbstep = bstat ? dwslice : dstage;            // from one slice's weight tile to the next
             const uint64_t dz0 = make_smem_desc<SWZ>(smem_u32(s_zw));
             if (bstat && !(debug & 2) && !__all_sync(0xffffffffu, mbar_wait(w_full, 0))) { atomicExch(&g_tc_status, 7); alive = false; }
             tc_fence_after();
@@ -707,31 +729,31 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 if (!__all_sync(0xffffffffu, mbar_wait(&acc_empty[buf], (((uint32_t)it >> 1) & 1u) ^ 1u))) { atomicExch(&g_tc_status, 4); break; }
                 tc_fence_after();
                 const uint32_t tacc = tmem_base + (uint32_t)(buf * BN);
-                uint64_t dbs = db0;                              // stationary weights: the slice's tile
-                for (int s = 0; s < nslices; ++s) {
+                uint64_t dbs = db0;                              // stationary weights: the stage's first tile
+                for (int g = 0; g < gpt; ++g, dbs += dwslice * (uint64_t)group) {
                     if (!__all_sync(0xffffffffu, mbar_wait_fast(full_addr + st * 8, ph))) { atomicExch(&g_tc_status, 2); alive = false; break; }
                     tc_fence_after();
                     const uint32_t eb = empty_addr + st * 8;
-                    const uint64_t da = da0 + dstage * (uint64_t)st;
-                    const uint64_t db = bstat ? dbs : db0 + dstage * (uint64_t)st;
-                    dbs += dwslice;
-                    if (++st == STAGES) { st = 0; ph ^= 1u; }
                     if (elect_one()) {                 // the same lane every time: a commit covers the MMAs of its own thread
                         if (debug & 1) {
                             mbar_arrive_s(eb);
                         } else {
-                            if (s == 0) tc_mma_i8(tacc, da, db, id, 0u);
-                            else        tc_mma_i8_acc(tacc, da, db, id);
-                            #pragma unroll
-                            for (int k = 1; k < SWZ / 32; ++k) tc_mma_i8_acc(tacc, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), id);
-                            for (int z = 0; z < nzw; ++z) {
-                                const uint64_t dz = dz0 + dwslice * (uint64_t)z;
+                            uint64_t da = da0 + dgroup * (uint64_t)st;
+                            uint64_t db = bstat ? dbs : db0 + dgroup * (uint64_t)st;
+                            for (int gs = 0; gs < group; ++gs, da += dstage, db += dbstep) {
+                                tc_mma_i8(tacc, da, db, id, (uint32_t)(g | gs));        // the tile's first MMA overwrites
                                 #pragma unroll
-                                for (int k = 0; k < SWZ / 32; ++k) tc_mma_i8_acc(tacc, da + (uint64_t)(k * 2), dz + (uint64_t)(k * 2), id_zw);
+                                for (int k = 1; k < SWZ / 32; ++k) tc_mma_i8_acc(tacc, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), id);
+                                for (int z = 0; z < nzw; ++z) {
+                                    const uint64_t dz = dz0 + dwslice * (uint64_t)z;
+                                    #pragma unroll
+                                    for (int k = 0; k < SWZ / 32; ++k) tc_mma_i8_acc(tacc, da + (uint64_t)(k * 2), dz + (uint64_t)(k * 2), id_zw);
+                                }
                             }
-                            tc_commit_s(eb);           // slot reusable once these MMAs have read it
+                            tc_commit_s(eb);           // stage reusable once these MMAs have read it
                         }
                     }
+                    if (++st == STAGES) { st = 0; ph ^= 1u; }
                 }
                 if (alive && elect_one()) tc_commit(&acc_full[buf]);  // accumulator of this tile complete
             }
@@ -1209,7 +1231,8 @@ static int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUten
     using L = TcSmem<BN, SWZ>;
     const size_t budget = 227 * 1024;                                   // opt-in shared memory per CTA on sm_100
     TcArgs a2 = a;
-    size_t rest = 1024 + L::CONST_BYTES + (size_t)a.ncls * BN * 4 + (size_t)(1 + a.nio) * L::IO_BYTES + (a.add_lut ? TC_LUT_BYTES + 256 : 0) +
+    size_t rest = 1024 + L::CONST_BYTES + (size_t)a.ncls * BN * 4 + (size_t)(1 + a.nio) * L::IO_BYTES + (a.add_lut ? TC_LUT_BYTES : 0) + 256 +
+                  (size_t)a.nslices * 16 +
                   (size_t)a.nzw * L::B_BYTES;
     // a third buffer for the fused Add's other operand (its loads then run a whole unit ahead of the epilogue) when the
     // ring keeps at least three stages
@@ -1221,15 +1244,25 @@ static int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUten
     a2.bstat = (a.ntn == 1 && wbytes <= 64 * 1024 && rest + wbytes + 4 * L::A_BYTES <= budget) ? 1 : 0;
     const size_t stride = a2.bstat ? L::A_BYTES : L::STAGE_BYTES;
     const size_t fixed = rest + (a2.bstat ? wbytes : 0);
-    int stages = (int)((budget - fixed) / stride);
-    if (stages > L::MAX_STAGES) stages = L::MAX_STAGES;
+    // Ring: `stages` stages of `group` K-slices each.  Waiting for a stage, arming and releasing its barriers cost the
+    // producer and the MMA issuer about as much as issuing two MMAs, so narrow tiles (short MMAs) want several slices per
+    // stage: the largest divisor of the slice count, up to 8, that still leaves three stages.
+    const int slots = (int)((budget - fixed) / stride);
+    int group = 1, stages = slots < L::MAX_STAGES ? slots : L::MAX_STAGES;
+    for (int g = 8; g >= 2; --g) {
+        if (a.nslices % g != 0 || slots / g < 3) continue;
+        group = g;
+        stages = slots / g < L::MAX_STAGES ? slots / g : L::MAX_STAGES;
+        break;
+    }
+    a2.group = group;
     a2.stages = stages;
     // A producer tells "slot consumed" from "slot consumed one ring pass earlier" by the barrier's phase parity alone,
     // which is only sound while it cannot run more than one pass ahead of the consumer: its previous turn (nprod
     // slices back) must lie within the same ring pass as the slot it waits for, i.e. nprod <= stages.
     a2.nprod = stages >= TC_PRODUCERS ? TC_PRODUCERS : (stages >= 2 ? 2 : 1);
     if (a2.bstat) a2.stage_tx = (uint32_t)(a.stage_tx - L::B_BYTES);
-    const size_t smem = fixed + (size_t)stages * stride;
+    const size_t smem = fixed + (size_t)stages * group * stride;
     auto kern = conv_tc_kernel<BN, SWZ>;
     static size_t configured = 0;                      // per instantiation: largest dynamic smem size set so far
     if (smem > configured) {
