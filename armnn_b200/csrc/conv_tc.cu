@@ -1457,8 +1457,7 @@ int launch_conv_tc(const b200k_conv2d_params* p, cudaStream_t stream, int kvalid
         // batch 256: 1x1 and 3x3 convolutions with 64 or 128 output channels run 10 - 30 % faster this way, the 7x7 stem
         // in row-window mode 9 % slower, so that mode keeps one group.)
         static const bool no_groups = getenv("B200K_TC_NOGROUPS") != nullptr;     // measurement aid
-        static const bool row_groups = getenv("B200K_TC_ROWGROUPS") != nullptr;   // measurement aid
-        a.eg = (a.ntn == 1 && !fa.res && (!row_mode || row_groups) && !no_groups) ? (bn == 64 ? 4 : (bn == 128 ? 2 : 1)) : 1;
+        a.eg = (a.ntn == 1 && !fa.res && !row_mode && !no_groups) ? (bn == 64 ? 4 : (bn == 128 ? 2 : 1)) : 1;
         // stores: one epilogue warp's 32 rows x (eg * uw / 4) columns
         const int stw = a.eg * uw / 4;
         cuuint32_t box_st[3] = {(cuuint32_t)stw, 32, 1};
