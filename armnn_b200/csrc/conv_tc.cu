@@ -564,6 +564,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     uint64_t* io_full = acc_empty + L::MAX_ACC;             // [3] other operand's unit has landed
     uint64_t* io_empty = io_full + L::MAX_IO;               // [3] the unit buffer's last store has been read out
     uint64_t* w_full = io_empty + L::MAX_IO;                // the stationary weight tile has landed
+    uint64_t* lut_full = w_full + 1;                        // the fused-add table has landed
     uint32_t* tmem_slot = (uint32_t*)(w_full + 2);
     uint32_t* s_lut_ok = tmem_slot + 1;                     // the fused-add table in global memory carries our tag
     int32_t* s_cc = (int32_t*)(tmem_slot + 4);              // [classes][BN] zero-point corrections
@@ -577,12 +578,17 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int ntn = a.ntn;                                  // n-tiles; the last one may reach beyond OC (zero weights, clipped stores)
     const int ntiles = ntn * a.ntm;
 
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        for (int b = 0; b < L::MAX_ACC; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], TC_EPI_WARPS / EG); }
-        for (int b = 0; b < L::MAX_IO; ++b) { mbar_init(&io_full[b], 1); mbar_init(&io_empty[b], TC_EPI_WARPS); }
-        mbar_init(w_full, 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    {
+        // the barriers lie in one array (full, empty, acc_full, acc_empty, io_full, io_empty, w_full, lut_full): one
+        // thread each, instead of one thread for all 58 of them
+        constexpr int NBAR = 2 * MAX_STAGES + 2 * L::MAX_ACC + 2 * L::MAX_IO + 2;
+        const int i = threadIdx.x;
+        if (i < NBAR) {
+            const bool acc_e = i >= 2 * MAX_STAGES + L::MAX_ACC && i < 2 * MAX_STAGES + 2 * L::MAX_ACC;
+            const bool io_e = i >= 2 * MAX_STAGES + 2 * L::MAX_ACC + L::MAX_IO && i < 2 * MAX_STAGES + 2 * L::MAX_ACC + 2 * L::MAX_IO;
+            mbar_init(&full[i], acc_e ? TC_EPI_WARPS / EG : (io_e ? TC_EPI_WARPS : 1));
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        }
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(BN << NACC_LOG2) : "memory");
@@ -637,6 +643,12 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 mbar_expect_tx(w_full, (uint32_t)a.nslices * L::B_BYTES);
                 for (int s = 0; s < a.nslices; ++s)
                     tma_load_2d(s_wst + (size_t)s * L::B_BYTES, &tmB, w_full, (int)s_tab[s].z, 0);
+            }
+            if (a.add_lut && prod == 0 && elect_one()) {
+                // the fused-add table: one bulk copy (the epilogue checks its tag before using it)
+                mbar_expect_tx(lut_full, (uint32_t)TC_LUT_BYTES);
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                             ::"r"(smem_u32(s_lut)), "l"(a.add_lut), "r"((uint32_t)TC_LUT_BYTES), "r"(smem_u32(lut_full)) : "memory");
             }
             asm volatile("griddepcontrol.wait;" ::: "memory");
             for (int t = blockIdx.x; t < ntiles && alive; t += gridDim.x) {
@@ -781,8 +793,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const uint32_t sw_x = UW == 128 ? (uint32_t)(row & 7) : (uint32_t)((row >> 1) & 3);   // TMA swizzle of this row
         const int pw = a.KW + 1;
         const bool fused = a.res != nullptr;
-        // The fused-add table is staged by the epilogue warps alone, while the producer and the MMA issuer already work
-        // on the first tile.  A table is used only if it was built for exactly this launch's quantisation parameters.
+        // The fused-add table arrives by a bulk copy the producer has issued.  A table is used only if it was built
+        // for exactly this launch's quantisation parameters.
         bool lut_ok = false;
         if (a.add_lut) {
             if (etid == 0) {
@@ -793,12 +805,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             }
             epi_barrier();
             lut_ok = *s_lut_ok != 0;
-            if (lut_ok) {
-                const uint4* src = (const uint4*)a.add_lut;
-                uint4* dst = (uint4*)s_lut;
-                for (int i = etid; i < TC_LUT_BYTES / 16; i += 32 * TC_EPI_WARPS) dst[i] = src[i];
-            }
-            epi_barrier();
+            // the producer's bulk copy of the table
+            if (!mbar_wait(lut_full, 0)) { atomicExch(&g_tc_status, 8); lut_ok = false; }
         }
         const bool use_lut = fused && lut_ok;
         const bool always_fix = fused && !lut_ok;            // no table: every chunk takes the reference arithmetic
@@ -1560,7 +1568,7 @@ extern "C" int b200k_poll_status(void)
         int zero = 0;
         cudaMemcpyToSymbol(g_tc_status, &zero, sizeof(int));
         set_error("a bounded device-side wait gave up (code %d: 1 producer/ring, 2 MMA issuer/ring, 3 epilogue/accumulator, "
-                  "4 MMA issuer/accumulator buffer, 5 epilogue/add operand, 6 producer/unit buffer, 7 MMA issuer/weights)", s);
+                  "4 MMA issuer/accumulator buffer, 5 epilogue/add operand, 6 producer/unit buffer, 7 MMA issuer/weights, 8 epilogue/add table)", s);
         return B200K_E_TIMEOUT;
     }
     return B200K_OK;
