@@ -2,16 +2,20 @@
 //
 // GEMM view: D[M, N] = A[M, K] * B[N, K]^T with M = output pixels (n, oy, ox), N = output channels and
 // K = (ky, kx, c).  One CTA computes a 128 x BN tile of D:
-//   * a producer thread feeds a multi-stage shared-memory ring with TMA.  The weight tile is a plain 2-D box of
+//   * two producer warps (one elected lane each, taking turns by stage) feed a shared-memory ring with TMA; a ring
+//     stage holds one to eight K-slices behind one pair of barriers.  The weight tile is a plain 2-D box of
 //     the [OC, KH*KW*C] matrix.  The activation tile is fetched either as a 2-D box of [M, C] (1x1 stride-1
 //     convolutions and FullyConnected) or with TMA's im2col mode straight from the NHWC tensor: one copy
 //     delivers, for 128 consecutive output pixels, the channel slice of one filter tap, zero-filling taps that
 //     fall outside the image.  Both land in the 128-byte (or 64-byte) swizzled K-major layout tcgen05 reads.
-//   * one thread issues tcgen05.mma.kind::i8 (M = 128, N = BN, K = 32 per instruction); the int32 accumulator
-//     lives in tensor memory (BN columns x 128 lanes); tcgen05.commit releases ring slots and finally signals
-//     the epilogue.
-//   * sixteen epilogue warps read the accumulator with tcgen05.ld, apply the zero-point correction, bias and the
-//     fp32 requantisation (and a fused residual Add), and send their 8-bit outputs with their own TMA stores.
+//   * one elected lane of the issuer warp issues tcgen05.mma.kind::i8 (M = 128, N = BN, K = 32 per instruction);
+//     the int32 accumulators live in tensor memory (2 to 8 buffers of BN columns x 128 lanes); tcgen05.commit
+//     releases ring stages and finally signals the epilogue.
+//   * sixteen epilogue warps, in one, two or four groups that work on different tiles, read an accumulator with
+//     tcgen05.ld, apply the zero-point correction, bias and the fp32 requantisation (and a fused residual Add), and
+//     send their 8-bit outputs with their own TMA stores.
+//   The producer and issuer roles are warp-uniform code (every lane runs the loops, elect.sync guards the issuing
+//   instructions), because TMA, MMA and mbarrier instructions take uniform-register operands.
 //
 // Convolutions with very few input channels (the 3-channel network stems) cannot feed TMA directly: a pixel is
 // not a 16-byte unit.  For those a pre-pass re-packs the input into caller-provided scratch as
@@ -504,9 +508,10 @@ struct TcSmem {
     static constexpr int UNITS = BN / UW;                   // units per tile
     static constexpr int IO_BYTES = TC_BM * UW;             // one unit buffer: [128 rows][UW], TMA-swizzled
     static constexpr int MAX_IO = 3;
-    // after the ring (stages x STAGE_BYTES) and the unit buffers (nio x IO_BYTES): per-channel m, bterm [BN each],
-    // barriers (full[16], empty[16], acc_full[8], acc_empty[8], io_full[3], io_empty[3], w_full), tmem slot + eps slot; then the
-    // zero-point correction table [classes][BN], then the fused-add table (dynamic sizes)
+    // after the ring (stages x group x STAGE_BYTES), the staging buffers (EG x IO_BYTES) and the unit buffers
+    // (nio x IO_BYTES): per-channel m, bterm [BN each], barriers (full[16], empty[16], acc_full[8], acc_empty[8],
+    // io_full[3], io_empty[3], w_full, lut_full), tmem slot + table-valid slot; then the zero-point correction table
+    // [classes][BN], the fused-add table and the K-slice coordinate table (dynamic sizes)
     static constexpr int MAX_ACC = 8;
     static constexpr int CONST_BYTES = 2 * BN * 4 + (2 * MAX_STAGES + 2 * MAX_ACC + 2 * MAX_IO + 2) * 8 + 16;
 };
@@ -521,12 +526,12 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar)
 }
 
 // Persistent kernel: one CTA per SM walks the tile list (n-tile fastest, so CTAs running at the same time share
-// activation tiles in L2).  The shared-memory ring and its barriers run continuously across tiles, and the
-// accumulator is double-buffered in tensor memory, so the TMA producer, the MMA issuer and the epilogue warps of
+// activation tiles in L2).  The shared-memory ring and its barriers run continuously across tiles, and there are
+// 2 * EG accumulator buffers in tensor memory, so the TMA producers, the MMA issuer and the epilogue warps of
 // consecutive tiles overlap.
 //
-// Output path.  A tile leaves in units of 128 rows x UW (<= 128) columns; each epilogue warp owns 32 rows x UW / 4
-// columns of a unit.  It writes its bytes into a private shared-memory buffer laid out as the TMA swizzle expects
+// Output path.  A tile leaves in units of 128 rows x UW (<= 128) columns; each epilogue warp owns 32 rows x
+// EG * UW / 4 columns of a unit of its group's tile (EG = 1: all sixteen warps on one tile).  It writes its bytes into a private shared-memory buffer laid out as the TMA swizzle expects
 // (conflict-free 16-byte stores, one row per lane) and one of its lanes sends the buffer with a TMA store, which clips
 // rows beyond the tensor; before the buffer is written again that lane has waited for the store to have read it.  No
 // epilogue warp waits for another one.  With a fused Add the producer TMA-loads the other operand's unit into one of
