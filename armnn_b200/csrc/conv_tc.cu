@@ -1165,6 +1165,8 @@ static int sm_count()
 static int pick_bn(int oc, long long ntm)
 {
     const long long sms = sm_count();
+    static const int forced = getenv("B200K_TC_FORCE_BN") ? atoi(getenv("B200K_TC_FORCE_BN")) : 0;    // measurement aid
+    if (forced == 64 || forced == 128 || forced == 256) return forced;
     int best = 64;
     long long best_cost = -1;
     for (int bn = 64; bn <= 256; bn *= 2) {

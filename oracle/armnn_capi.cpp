@@ -573,6 +573,13 @@ int armnnc_add_mean(void* vn, const int32_t* axes, int n_axes, int keep_dims)
     return add_layer(n, n->net->AddMeanLayer(d));
 }
 
+int armnnc_add_batch_matmul(void* vn, int transpose_x, int transpose_y, int adjoint_x, int adjoint_y)
+{
+    auto* n = static_cast<CNet*>(vn);
+    BatchMatMulDescriptor d(transpose_x != 0, transpose_y != 0, adjoint_x != 0, adjoint_y != 0);
+    return add_layer(n, n->net->AddBatchMatMulLayer(d));
+}
+
 int armnnc_add_reshape(void* vn, int rank, const int32_t* shape)
 {
     auto* n = static_cast<CNet*>(vn);

@@ -122,6 +122,8 @@ class ArmnnNetwork:
                                             d["stride"][1], d["pad"][0], d["pad"][1], d["pad"][2], d["pad"][3])
             elif t == "ElementwiseBinary":
                 lid = lib.armnnc_add_elementwise_binary(net, int(d["op"]))
+            elif t == "BatchMatMul":
+                lid = lib.armnnc_add_batch_matmul(net, int(d["tx"]), int(d["ty"]), int(d.get("ax", False)), int(d.get("ay", False)))
             elif t == "Softmax":
                 lid = lib.armnnc_add_softmax(net, C.c_float(d["beta"]), d["axis"])
             elif t == "Mean":

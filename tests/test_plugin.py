@@ -151,3 +151,34 @@ def test_imported_io_buffers_match_copied_ones(mode):
         assert np.array_equal(want, y)
         seen.add(y.tobytes())
     assert len(seen) > 1
+
+
+@needs_plugin
+@pytest.mark.gpu
+@pytest.mark.parametrize("tx,ty", [(False, False), (False, True), (True, False)])
+def test_batch_matmul_through_the_runtime_matches_cpuref(tx, ty):
+    """BatchMatMul (attention-shaped: a batch of 8 heads, 64 x 32 by 32 x 48) with transposed operands through the real
+    runtime on both backends; QAsymmS8 per-tensor operands as RefLayerSupport.cpp:697-740 allows."""
+    from armnn_b200.network import DataType, INetwork, TensorInfo
+    b, m, k, n = 8, 64, 32, 48
+    net = INetwork.Create()
+    x_shape = (b, k, m) if tx else (b, m, k)
+    y_shape = (b, n, k) if ty else (b, k, n)
+    ix = net.AddInputLayer(0)
+    ix.GetOutputSlot(0).SetTensorInfo(TensorInfo(x_shape, DataType.QAsymmS8, 0.05, 3))
+    iy = net.AddInputLayer(1)
+    iy.GetOutputSlot(0).SetTensorInfo(TensorInfo(y_shape, DataType.QAsymmS8, 0.04, -5))
+    l = net.AddBatchMatMulLayer(transpose_x=tx, transpose_y=ty)
+    ix.GetOutputSlot(0).Connect(l.GetInputSlot(0))
+    iy.GetOutputSlot(0).Connect(l.GetInputSlot(1))
+    l.GetOutputSlot(0).SetTensorInfo(TensorInfo((b, m, n), DataType.QAsymmS8, 0.9, 7))
+    ol = net.AddOutputLayer(0)
+    l.GetOutputSlot(0).Connect(ol.GetInputSlot(0))
+    rng = np.random.default_rng(21)
+    x = rng.integers(-128, 128, size=x_shape).astype(np.int8)
+    y = rng.integers(-128, 128, size=y_shape).astype(np.int8)
+    ref = hostnet.ArmnnNetwork(net, "CpuRef").run({0: x, 1: y})[0]
+    got = hostnet.ArmnnNetwork(net, "B200Acc").run({0: x, 1: y})[0]
+    st = diff_stats(ref, got)
+    assert st["max_abs"] <= 1 and st["mismatch_frac"] < 0.01, st
+    assert np.unique(ref).size > 50                          # not saturated
