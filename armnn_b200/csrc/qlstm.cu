@@ -55,31 +55,46 @@ struct QlArgs {
     int cifg, peephole, ln, proj;
 };
 
-// acc <- chain over k of Q16(acc*sG + (w[k]*sw) * v[k]) for two independent chains (A and B)
+// acc <- chain over k of Q16(acc*sG + (w[k]*sw) * v[k]) for two independent chains (A and B), both evaluated by
+// packed two-wide fp32 instructions (the chains of a row keep the schedulers' issue slots busy, so halving the
+// instruction count is what counts).  v2 holds every value twice, as (x, x) pairs.  Products that the reference
+// rounds before adding are formed as fma2(a, b, 0): a packed multiply feeding a packed add would be contracted.
+// Quantize to int16: Markstein's correctly rounded quotient, the 1.5 * 2^23 rounding constant, and roundf for the
+// exact halves it rounds to even where the reference rounds away from zero (see round_div_fast).
 template <bool VEC>
 __device__ __forceinline__ void chain2(float& accA, float& accB, const int8_t* wA, const int8_t* wB, float swA, float swB,
-                                        const float* v, int K, float sGA, float sGB, bool hasB)
+                                        const float2* v2, int K, float sGA, float sGB, bool hasB)
 {
     const float iGA = __frcp_rn(sGA), iGB = __frcp_rn(sGB);
+    const f32x2 sG2 = pack2(sGA, sGB), nsG2 = pack2(-sGA, -sGB), iG2 = pack2(iGA, iGB), sw2 = pack2(swA, swB);
+    const f32x2 zero2 = pack2(0.f, 0.f), magic2 = pack2(12582912.0f, 12582912.0f);
+    f32x2 acc2 = pack2(accA, accB);
+    auto step = [&](float wa, float wb, int k) {
+        const float2 xx = v2[k];
+        const f32x2 t2 = fma2(fma2(pack2(wa, wb), sw2, zero2), pack2(xx.x, xx.y), zero2);    // fl(fl(w * sw) * x)
+        const f32x2 a2 = add2(fma2(acc2, sG2, zero2), t2);                                    // fl(fl(acc * sG) + t)
+        const f32x2 p2 = mul2(a2, iG2);
+        const f32x2 q2 = fma2(fma2(p2, nsG2, a2), iG2, p2);                                   // RN(a / sG)
+        const f32x2 n2 = sub2(add2(q2, magic2), magic2);
+        float qa, qb, na, nb;
+        unpack2(q2, qa, qb); unpack2(n2, na, nb);
+        if (fabsf(__fsub_rn(qa, na)) >= 0.5f) na = roundf(qa);
+        if (fabsf(__fsub_rn(qb, nb)) >= 0.5f) nb = roundf(qb);
+        acc2 = pack2(fminf(fmaxf(na, -32768.f), 32767.f), fminf(fmaxf(nb, -32768.f), 32767.f));
+    };
     if (VEC) {
         for (int k0 = 0; k0 < K; k0 += 16) {
             int8_t ra[16], rb[16];
             *(uint4*)ra = *(const uint4*)(wA + k0);
             if (hasB) *(uint4*)rb = *(const uint4*)(wB + k0);
+            else      *(uint4*)rb = make_uint4(0, 0, 0, 0);
             #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                const float x = v[k0 + j];
-                accA = q16f_fast(__fadd_rn(__fmul_rn(accA, sGA), __fmul_rn(__fmul_rn((float)ra[j], swA), x)), sGA, iGA);
-                if (hasB) accB = q16f_fast(__fadd_rn(__fmul_rn(accB, sGB), __fmul_rn(__fmul_rn((float)rb[j], swB), x)), sGB, iGB);
-            }
+            for (int j = 0; j < 16; ++j) step((float)ra[j], (float)rb[j], k0 + j);
         }
     } else {
-        for (int k = 0; k < K; ++k) {
-            const float x = v[k];
-            accA = q16f_fast(__fadd_rn(__fmul_rn(accA, sGA), __fmul_rn(__fmul_rn((float)wA[k], swA), x)), sGA, iGA);
-            if (hasB) accB = q16f_fast(__fadd_rn(__fmul_rn(accB, sGB), __fmul_rn(__fmul_rn((float)wB[k], swB), x)), sGB, iGB);
-        }
+        for (int k = 0; k < K; ++k) step((float)wA[k], hasB ? (float)wB[k] : 0.f, k);
     }
+    unpack2(acc2, accA, accB);
 }
 
 template <bool VEC_I, bool VEC_O>
@@ -89,16 +104,21 @@ __global__ void __launch_bounds__(QL_THREADS) qlstm_step_kernel(const QlArgs a)
     const int I = p.input_size, U = p.num_units, O = p.output_size;
     const int b = blockIdx.x, tid = threadIdx.x;
     extern __shared__ float sm[];
-    float* xf = sm;                 // [I]   dequantised input row
-    float* hf = xf + I;             // [O]   dequantised previous output state
-    float* gate = hf + O;           // [4][U] int16 gate buffers as integer-valued floats (i, f, c, o)
+    float2* xf = (float2*)sm;       // [I]   dequantised input row, every value twice (for the two-wide chains)
+    float2* hf = xf + I;            // [O]   dequantised previous output state, likewise
+    float* gate = (float*)(hf + O); // [4][U] int16 gate buffers as integer-valued floats (i, f, c, o)
     float* cell = gate + 4 * U;     // [U]   new cell state (integer-valued)
     float* hid = cell + U;          // [U]   dequantised hidden state
     float* stat = hid + U;          // [4][2] mean, 1/stddev per gate
 
-    for (int k = tid; k < I; k += QL_THREADS) xf[k] = dequantize_dev(p.input[(long long)b * I + k], p.input_scale, p.input_zp);
-    for (int k = tid; k < O; k += QL_THREADS)
-        hf[k] = dequantize_dev(p.output_state_in[(long long)b * O + k], p.output_state_scale, p.output_state_zp);
+    for (int k = tid; k < I; k += QL_THREADS) {
+        const float v = dequantize_dev(p.input[(long long)b * I + k], p.input_scale, p.input_zp);
+        xf[k] = make_float2(v, v);
+    }
+    for (int k = tid; k < O; k += QL_THREADS) {
+        const float v = dequantize_dev(p.output_state_in[(long long)b * O + k], p.output_state_scale, p.output_state_zp);
+        hf[k] = make_float2(v, v);
+    }
     __syncthreads();
 
     const int8_t* wi[4] = {p.w_i2i, p.w_i2f, p.w_i2c, p.w_i2o};
@@ -271,7 +291,7 @@ extern "C" int b200k_qlstm_step(const b200k_qlstm_params* p, void* stream)
                   B200K_E_INVALID, "qlstm_step: layer norm needs all layer-norm weights and gate biases");
     B200K_REQUIRE(a.proj || p->num_units == p->output_size, B200K_E_INVALID,
                   "qlstm_step: without projection the output size must equal the number of units");
-    const size_t smem = sizeof(float) * ((size_t)p->input_size + p->output_size + 6 * (size_t)p->num_units + 8);
+    const size_t smem = sizeof(float) * (2 * ((size_t)p->input_size + p->output_size) + 6 * (size_t)p->num_units + 8);
     B200K_REQUIRE(smem <= 200 * 1024, B200K_E_TOOBIG, "qlstm_step: layer too large for the shared-memory resident kernel");
     const bool vi = (p->input_size % 16) == 0 &&
                     ((((uintptr_t)p->w_i2i | (uintptr_t)p->w_i2f | (uintptr_t)p->w_i2c | (uintptr_t)p->w_i2o) & 15) == 0);
