@@ -265,4 +265,25 @@ __device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b)
     return d;
 }
 
+
+// requant_fast for two values at once in two-wide fp32 instructions (m2, b2: the two channels' constants; the other
+// constants the same value twice).  Returns the two results as integer-valued floats (already clamped).
+__device__ __forceinline__ void requant_fast2(int acc0, int acc1, f32x2 m2, f32x2 b2, f32x2 sy2n, f32x2 inv2, f32x2 zy2, float lo, float hi,
+                                              float& r0, float& r1)
+{
+    const f32x2 zero2 = pack2(0.f, 0.f), magic2 = pack2(12582912.0f, 12582912.0f);
+    const f32x2 v2 = add2(fma2(pack2(__int2float_rn(acc0), __int2float_rn(acc1)), m2, zero2), b2);   // fl(fl(acc * m) + b)
+    const f32x2 p2 = mul2(v2, inv2);
+    const f32x2 q2 = fma2(fma2(p2, sy2n, v2), inv2, p2);
+    const f32x2 n2 = sub2(add2(q2, magic2), magic2);
+    float q0, q1, n0, n1;
+    unpack2(q2, q0, q1); unpack2(n2, n0, n1);
+    if (fabsf(__fsub_rn(q0, n0)) == 0.5f || !(fabsf(q0) < 4194304.0f)) n0 = roundf(q0);
+    if (fabsf(__fsub_rn(q1, n1)) == 0.5f || !(fabsf(q1) < 4194304.0f)) n1 = roundf(q1);
+    float z0, z1;
+    unpack2(add2(pack2(n0, n1), zy2), z0, z1);
+    r0 = fminf(fmaxf(z0, lo), hi);
+    r1 = fminf(fmaxf(z1, lo), hi);
+}
+
 }  // namespace b200k

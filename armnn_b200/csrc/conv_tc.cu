@@ -1205,6 +1205,7 @@ bool conv_tc_eligible(const b200k_conv2d_params* p)
     if ((((uintptr_t)p->x.data | (uintptr_t)p->w.data | (uintptr_t)outp) & 15) != 0) return false;
     if (p->x.zero_point != 0 && !p->packed) return false;              // needs the prefix table
     if (p->kh > 15 || p->kw > 15) return false;
+    if ((long long)p->kh * p->kw * ((p->c + 63) / 64) > 2048) return false;   // K-slice table in shared memory: at most 32 KiB
     if (p->kh * p->dil_h > 255 || p->kw * p->dil_w > 255) return false;
     if (p->stride_h > 8 || p->stride_w > 8) return false;
     const long long M = (long long)p->n * p->oh * p->ow;

@@ -146,6 +146,8 @@ __global__ void __launch_bounds__(256) dwconv3x3_kernel(const Dw3Args a3)
             b[c] = a.bias ? __fmul_rn(__int2float_rn(a.bias[ch]), a.b_scales ? a.b_scales[ch] : a.b_scale) : 0.f;
         }
     }
+    const f32x2 m01 = pack2(m[0], m[1]), m23 = pack2(m[2], m[3]), b01 = pack2(b[0], b[1]), b23 = pack2(b[2], b[3]);
+    const f32x2 nsy2 = pack2(-a.rq.sy, -a.rq.sy), inv2 = pack2(a3.inv_sy, a3.inv_sy), zy2 = pack2((float)a.rq.zy, (float)a.rq.zy);
     const int iy0 = oy * STRIDE - a.pt;
     const bool rv0 = iy0 >= 0 && iy0 < a.H, rv1 = iy0 + 1 >= 0 && iy0 + 1 < a.H, rv2 = iy0 + 2 >= 0 && iy0 + 2 < a.H;
     const uint8_t* row0 = a.x + (((long long)n * a.H + iy0) * a.W) * a.C + ch0;
@@ -190,17 +192,22 @@ __global__ void __launch_bounds__(256) dwconv3x3_kernel(const Dw3Args a3)
             }
         }
         const long long ob = (((long long)n * a.OH + oy) * a.OW + ox) * a.OC + ch0;
-        uint32_t outw = 0;
+        int acc[4];
         #pragma unroll
         for (int c = 0; c < 4; ++c) {
-            int acc = 0;
+            acc[c] = 0;
             #pragma unroll
-            for (int j = 0; j < 3; ++j) acc = dp4a_mixed<XU, WU>(xcol[j][c], wcol[j][c], acc);
-            acc -= a.zw * (xsum[0][c] + xsum[1][c] + xsum[2][c]) + kconst[c];
-            if (a.acc_out) a.acc_out[ob + c] = acc;
-            const int q = requant_fast(acc, m[c], b[c], a.bias != nullptr, a.rq.sy, a3.inv_sy, (float)a.rq.zy, a3.lo, a3.hi);
-            outw |= ((uint32_t)q & 0xffu) << (8 * c);
+            for (int j = 0; j < 3; ++j) acc[c] = dp4a_mixed<XU, WU>(xcol[j][c], wcol[j][c], acc[c]);
+            acc[c] -= a.zw * (xsum[0][c] + xsum[1][c] + xsum[2][c]) + kconst[c];
+            if (a.acc_out) a.acc_out[ob + c] = acc[c];
         }
+        // exact requantisation, two channels per instruction (b is 0 without a bias: adding it changes nothing, as the
+        // sum of a finite value and +0 is that value)
+        float r[4];
+        requant_fast2(acc[0], acc[1], m01, b01, nsy2, inv2, zy2, a3.lo, a3.hi, r[0], r[1]);
+        requant_fast2(acc[2], acc[3], m23, b23, nsy2, inv2, zy2, a3.lo, a3.hi, r[2], r[3]);
+        const uint32_t outw = ((uint32_t)__float2int_rn(r[0]) & 0xffu) | (((uint32_t)__float2int_rn(r[1]) & 0xffu) << 8) |
+                              (((uint32_t)__float2int_rn(r[2]) & 0xffu) << 16) | (((uint32_t)__float2int_rn(r[3]) & 0xffu) << 24);
         *(uint32_t*)(a.y + ob) = outw;
         ix += STRIDE;
     }
