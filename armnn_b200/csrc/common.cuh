@@ -7,6 +7,7 @@
 #pragma once
 #include <cuda_runtime.h>
 #include <math.h>
+#include <string.h>
 #include <stdint.h>
 #include <stdio.h>
 #include "../../include/b200k.h"
@@ -284,6 +285,33 @@ __device__ __forceinline__ void requant_fast2(int acc0, int acc1, f32x2 m2, f32x
     unpack2(add2(pack2(n0, n1), zy2), z0, z1);
     r0 = fminf(fmaxf(z0, lo), hi);
     r1 = fminf(fmaxf(z1, lo), hi);
+}
+
+
+// Programmatic dependent launch.  A grid launched with launch_pdl may be scheduled while its predecessor in the stream
+// is still draining; its threads call pdl_enter() before they touch anything the predecessor may write (that is:
+// first thing), which also lets the grid after it be scheduled early.  Kernels launched the plain way keep the full
+// stream dependency.
+__device__ __forceinline__ void pdl_enter()
+{
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+template <typename... KArgs, typename... Args>
+static inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args)
+{
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);      // errors surface in check_launch (cudaGetLastError)
 }
 
 }  // namespace b200k

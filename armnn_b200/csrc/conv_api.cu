@@ -81,6 +81,7 @@ static b200k_conv2d_params padded_params(const b200k_conv2d_params* p, const Pad
 // dst[row][0..wd) = src[row][0..ws) followed by zeros (wd > ws) or cut (wd < ws); widths in units of 8 bytes
 __global__ void __launch_bounds__(256) repitch_rows_kernel(const uint2* src, uint2* dst, long long rows, int ws, int wd)
 {
+    pdl_enter();
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= rows * wd) return;
     const long long row = i / wd;
@@ -122,16 +123,16 @@ static int launch_padded(const b200k_conv2d_params* p, const PadPlan& pl, const 
 {
     const long long pixels_in = (long long)p->n * p->h * p->wd, pixels_out = (long long)p->n * p->oh * p->ow;
     if (p->c % 16 != 0) {
-        repitch_rows_kernel<<<div_up(pixels_in * (pl.cpad / 8), 256), 256, 0, stream>>>(
-            (const uint2*)p->x.data, (uint2*)q.x.data, pixels_in, p->c / 8, pl.cpad / 8);
+        launch_pdl(repitch_rows_kernel, dim3((unsigned)div_up(pixels_in * (pl.cpad / 8), 256)), dim3(256), 0, stream,
+                   (const uint2*)p->x.data, (uint2*)q.x.data, pixels_in, p->c / 8, pl.cpad / 8);
         int rc = check_launch("repitch_rows_kernel");
         if (rc) return rc;
     }
     int rc = launch_conv_tc(&q, stream, p->c);
     if (rc) return rc;
     if (p->oc % 16 != 0) {
-        repitch_rows_kernel<<<div_up(pixels_out * (p->oc / 8), 256), 256, 0, stream>>>(
-            (const uint2*)q.y.data, (uint2*)p->y.data, pixels_out, pl.ocpad / 8, p->oc / 8);
+        launch_pdl(repitch_rows_kernel, dim3((unsigned)div_up(pixels_out * (p->oc / 8), 256)), dim3(256), 0, stream,
+                   (const uint2*)q.y.data, (uint2*)p->y.data, pixels_out, pl.ocpad / 8, p->oc / 8);
         rc = check_launch("repitch_rows_kernel");
         if (rc) return rc;
         if (p->acc_out) {

@@ -1032,6 +1032,7 @@ struct RowInputArgs { const uint8_t* x; uint8_t* xp; int N, H, W, C, hp, wp, cpa
 template <int CPAD>
 __global__ void __launch_bounds__(256) row_input_pack_kernel(const RowInputArgs a)
 {
+    pdl_enter();
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= a.total) return;
     const int xq = (int)(i % a.wp);
@@ -1381,8 +1382,8 @@ int launch_conv_tc(const b200k_conv2d_params* p, cudaStream_t stream, int kvalid
         ra.N = p->n; ra.H = p->h; ra.W = p->wd; ra.C = p->c; ra.hp = rowp.hp; ra.wp = rowp.wp; ra.cpad = rowp.cpad;
         ra.pt = p->pad_top; ra.pl = p->pad_left; ra.fill = (unsigned)(p->x.zero_point & 0xff);
         ra.total = (long long)p->n * rowp.hp * rowp.wp;
-        if (rowp.cpad == 8) row_input_pack_kernel<8><<<div_up(ra.total, 256), 256, 0, stream>>>(ra);
-        else                row_input_pack_kernel<16><<<div_up(ra.total, 256), 256, 0, stream>>>(ra);
+        if (rowp.cpad == 8) launch_pdl(row_input_pack_kernel<8>, dim3((unsigned)div_up(ra.total, 256)), dim3(256), 0, stream, ra);
+        else                launch_pdl(row_input_pack_kernel<16>, dim3((unsigned)div_up(ra.total, 256)), dim3(256), 0, stream, ra);
         int rc = check_launch("row_input_pack_kernel");
         if (rc) return rc;
         const cuuint64_t rowb = (cuuint64_t)rowp.wp * rowp.cpad;

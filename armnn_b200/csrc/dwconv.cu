@@ -36,6 +36,7 @@ __device__ __forceinline__ void unpack(const typename VecT<VEC>::type& v, bool i
 template <int VEC>
 __global__ void __launch_bounds__(256) dwconv_kernel(const DwArgs a)
 {
+    pdl_enter();
     using V = typename VecT<VEC>::type;
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= a.total) return;
@@ -110,6 +111,7 @@ struct Dw3Args {
 template <int STRIDE, bool XU, bool WU>
 __global__ void __launch_bounds__(256) dwconv3x3_kernel(const Dw3Args a3)
 {
+    pdl_enter();
     const DwArgs& a = a3.d;
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= a.total) return;
@@ -218,11 +220,11 @@ static void launch_dw3(const Dw3Args& a, cudaStream_t s)
 {
     const unsigned grid = (unsigned)div_up(a.d.total, 256);
     if (a.d.x_u8) {
-        if (a.d.w_u8) dwconv3x3_kernel<STRIDE, true, true><<<grid, 256, 0, s>>>(a);
-        else          dwconv3x3_kernel<STRIDE, true, false><<<grid, 256, 0, s>>>(a);
+        if (a.d.w_u8) launch_pdl(dwconv3x3_kernel<STRIDE, true, true>, dim3((unsigned)(grid)), dim3(256), 0, s, a);
+        else          launch_pdl(dwconv3x3_kernel<STRIDE, true, false>, dim3((unsigned)(grid)), dim3(256), 0, s, a);
     } else {
-        if (a.d.w_u8) dwconv3x3_kernel<STRIDE, false, true><<<grid, 256, 0, s>>>(a);
-        else          dwconv3x3_kernel<STRIDE, false, false><<<grid, 256, 0, s>>>(a);
+        if (a.d.w_u8) launch_pdl(dwconv3x3_kernel<STRIDE, false, true>, dim3((unsigned)(grid)), dim3(256), 0, s, a);
+        else          launch_pdl(dwconv3x3_kernel<STRIDE, false, false>, dim3((unsigned)(grid)), dim3(256), 0, s, a);
     }
 }
 
@@ -271,13 +273,13 @@ extern "C" int b200k_dwconv2d_q8(const b200k_conv2d_params* p, void* stream)
     }
     if (a.dm == 1 && (a.C % 16) == 0 && (al & 15) == 0) {
         a.total = pixels * (a.OC / 16);
-        dwconv_kernel<16><<<div_up(a.total, 256), 256, 0, s>>>(a);
+        launch_pdl(dwconv_kernel<16>, dim3((unsigned)(div_up(a.total, 256))), dim3(256), 0, s, a);
     } else if (a.dm == 1 && (a.C % 4) == 0 && (al & 3) == 0) {
         a.total = pixels * (a.OC / 4);
-        dwconv_kernel<4><<<div_up(a.total, 256), 256, 0, s>>>(a);
+        launch_pdl(dwconv_kernel<4>, dim3((unsigned)(div_up(a.total, 256))), dim3(256), 0, s, a);
     } else {
         a.total = pixels * a.OC;
-        dwconv_kernel<1><<<div_up(a.total, 256), 256, 0, s>>>(a);
+        launch_pdl(dwconv_kernel<1>, dim3((unsigned)(div_up(a.total, 256))), dim3(256), 0, s, a);
     }
     return check_launch("dwconv_kernel");
 }

@@ -31,6 +31,7 @@ struct EltArgs {
 
 __global__ void __launch_bounds__(256) eltwise_vec16_kernel(const EltArgs e)
 {
+    pdl_enter();
     const long long idx = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 16;
     if (idx >= e.total) return;
     uint8_t ra[16], rb[16], ro[16];
@@ -48,6 +49,7 @@ __global__ void __launch_bounds__(256) eltwise_vec16_kernel(const EltArgs e)
 
 __global__ void __launch_bounds__(256) eltwise_generic_kernel(const EltArgs e)
 {
+    pdl_enter();
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= e.total) return;
     long long t = idx;
@@ -85,6 +87,7 @@ struct UnaryArgs { QView x, y; long long count; int fn; float a, b; };
 // fn < 0: plain conversion (Quantize / Dequantize / requantize)
 __global__ void __launch_bounds__(256) unary_kernel(const UnaryArgs u)
 {
+    pdl_enter();
     const long long base = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
     #pragma unroll
     for (int k = 0; k < 4; ++k) {
@@ -136,10 +139,10 @@ extern "C" int b200k_eltwise_q8(const b200k_eltwise_params* p, void* stream)
     cudaStream_t s = (cudaStream_t)stream;
     const uintptr_t al = (uintptr_t)p->a.data | (uintptr_t)p->b.data | (uintptr_t)p->out.data;
     if (same && is_q8(p->a.dtype) && is_q8(p->b.dtype) && is_q8(p->out.dtype) && (e.total % 16) == 0 && (al & 15) == 0) {
-        eltwise_vec16_kernel<<<div_up(e.total / 16, 256), 256, 0, s>>>(e);
+        launch_pdl(eltwise_vec16_kernel, dim3((unsigned)(div_up(e.total / 16, 256))), dim3(256), 0, s, e);
         return check_launch("eltwise_vec16_kernel");
     }
-    eltwise_generic_kernel<<<div_up(e.total, 256), 256, 0, s>>>(e);
+    launch_pdl(eltwise_generic_kernel, dim3((unsigned)(div_up(e.total, 256))), dim3(256), 0, s, e);
     return check_launch("eltwise_generic_kernel");
 }
 
@@ -153,7 +156,7 @@ static int launch_unary(const b200k_qtensor& x, const b200k_qtensor& y, long lon
     if (count == 0) return B200K_OK;
     UnaryArgs u;
     u.x = make_view(x); u.y = make_view(y); u.count = count; u.fn = fn; u.a = a; u.b = b;
-    unary_kernel<<<div_up(div_up(count, 4), 256), 256, 0, (cudaStream_t)stream>>>(u);
+    launch_pdl(unary_kernel, dim3((unsigned)(div_up(div_up(count, 4), 256))), dim3(256), 0, (cudaStream_t)stream, u);
     return check_launch("unary_kernel");
 }
 

@@ -103,6 +103,7 @@ struct FcRowsArgs {
 template <bool XU, bool WU, int FC_ROWS>
 __global__ void __launch_bounds__(32 * FC_COLS) fc_rows_kernel(const FcRowsArgs a)
 {
+    pdl_enter();
     extern __shared__ uint4 s_x[];                           // [FC_ROWS][kt / 16]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n = blockIdx.x * FC_COLS + warp;
@@ -215,7 +216,7 @@ static int launch_fc_rows(const b200k_fc_params* p, cudaStream_t stream)
                 configured = true;                                                                                     \
             }                                                                                                          \
             const dim3 grid(div_up(p->n, FC_COLS), div_up(p->m, RB), 1);                                               \
-            fc_rows_kernel<XU, WU, RB><<<grid, 32 * FC_COLS, (size_t)RB * kt, stream>>>(a);                            \
+            launch_pdl(fc_rows_kernel<XU, WU, RB>, grid, dim3(32 * FC_COLS), (size_t)RB * kt, stream, a);              \
         } while (0)
     #define B200K_FC_TYPES(RB)                                                                                         \
         do {                                                                                                           \

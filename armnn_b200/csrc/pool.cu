@@ -55,6 +55,7 @@ __device__ __forceinline__ void store_vec_f(const QView& t, long long i, const f
 template <int VEC>
 __global__ void __launch_bounds__(256) pool2d_kernel(const PoolArgs a)
 {
+    pdl_enter();
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= a.total) return;
     const int cg = a.C / VEC;
@@ -111,6 +112,7 @@ __global__ void __launch_bounds__(256) pool2d_kernel(const PoolArgs a)
 // Quantize(0) = the zero point, as in the general kernel.
 __global__ void __launch_bounds__(256) maxpool_same_quant_kernel(const PoolArgs a)
 {
+    pdl_enter();
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= a.total) return;
     const int cg = a.C / 16;
@@ -148,6 +150,7 @@ struct MeanArgs { QView x, y; int N, HW, C; long long total; };
 template <int VEC>
 __global__ void __launch_bounds__(128) mean_hw_kernel(const MeanArgs a)
 {
+    pdl_enter();
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= a.total) return;
     const int cg = a.C / VEC;
@@ -204,12 +207,12 @@ extern "C" int b200k_pool2d_q8(const b200k_pool2d_params* p, void* stream)
     cudaStream_t s = (cudaStream_t)stream;
     if (vec == 16 && p->pool_type == 0 && p->x.dtype == p->y.dtype && p->x.scale == p->y.scale &&
         p->x.zero_point == p->y.zero_point && p->x.scale > 0.f) {
-        maxpool_same_quant_kernel<<<div_up(a.total, 256), 256, 0, s>>>(a);
+        launch_pdl(maxpool_same_quant_kernel, dim3((unsigned)(div_up(a.total, 256))), dim3(256), 0, s, a);
         return check_launch("maxpool_same_quant_kernel");
     }
-    if (vec == 16)     pool2d_kernel<16><<<div_up(a.total, 256), 256, 0, s>>>(a);
-    else if (vec == 4) pool2d_kernel<4><<<div_up(a.total, 256), 256, 0, s>>>(a);
-    else               pool2d_kernel<1><<<div_up(a.total, 256), 256, 0, s>>>(a);
+    if (vec == 16)     launch_pdl(pool2d_kernel<16>, dim3((unsigned)(div_up(a.total, 256))), dim3(256), 0, s, a);
+    else if (vec == 4) launch_pdl(pool2d_kernel<4>, dim3((unsigned)(div_up(a.total, 256))), dim3(256), 0, s, a);
+    else               launch_pdl(pool2d_kernel<1>, dim3((unsigned)(div_up(a.total, 256))), dim3(256), 0, s, a);
     return check_launch("pool2d_kernel");
 }
 
@@ -225,8 +228,8 @@ extern "C" int b200k_mean_hw_q8(const b200k_mean_params* p, void* stream)
     const int vec = pick_vec(p->x, p->y, p->c);
     a.total = (long long)p->n * (p->c / vec);
     cudaStream_t s = (cudaStream_t)stream;
-    if (vec == 16)     mean_hw_kernel<16><<<div_up(a.total, 128), 128, 0, s>>>(a);
-    else if (vec == 4) mean_hw_kernel<4><<<div_up(a.total, 128), 128, 0, s>>>(a);
-    else               mean_hw_kernel<1><<<div_up(a.total, 128), 128, 0, s>>>(a);
+    if (vec == 16)     launch_pdl(mean_hw_kernel<16>, dim3((unsigned)(div_up(a.total, 128))), dim3(128), 0, s, a);
+    else if (vec == 4) launch_pdl(mean_hw_kernel<4>, dim3((unsigned)(div_up(a.total, 128))), dim3(128), 0, s, a);
+    else               launch_pdl(mean_hw_kernel<1>, dim3((unsigned)(div_up(a.total, 128))), dim3(128), 0, s, a);
     return check_launch("mean_hw_kernel");
 }

@@ -100,6 +100,7 @@ __device__ __forceinline__ void chain2(float& accA, float& accB, const int8_t* w
 template <bool VEC_I, bool VEC_O>
 __global__ void __launch_bounds__(QL_THREADS) qlstm_step_kernel(const QlArgs a)
 {
+    pdl_enter();
     const b200k_qlstm_params& p = a.p;
     const int I = p.input_size, U = p.num_units, O = p.output_size;
     const int b = blockIdx.x, tid = threadIdx.x;
@@ -300,7 +301,7 @@ extern "C" int b200k_qlstm_step(const b200k_qlstm_params* p, void* stream)
     cudaStream_t s = (cudaStream_t)stream;
     auto launch = [&](auto kern) -> int {
         if (smem > 48 * 1024) B200K_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        kern<<<p->batch, QL_THREADS, smem, s>>>(a);
+        launch_pdl(kern, dim3((unsigned)p->batch), dim3(QL_THREADS), smem, s, a);
         return check_launch("qlstm_step_kernel");
     };
     if (vi && vo)  return launch(qlstm_step_kernel<true, true>);

@@ -15,6 +15,7 @@ constexpr int SM_THREADS = 128;
 
 __global__ void __launch_bounds__(SM_THREADS) softmax_kernel(const SoftmaxArgs a)
 {
+    pdl_enter();
     extern __shared__ float ex[];            // [axis]
     __shared__ float red[SM_THREADS / 32];
     __shared__ float s_max, s_sum;
@@ -68,6 +69,6 @@ extern "C" int b200k_softmax_q8(const b200k_softmax_params* p, void* stream)
     a.outer = p->outer; a.axis = p->axis_size; a.inner = p->inner; a.beta = p->beta;
     const long long rows = (long long)p->outer * p->inner;
     B200K_REQUIRE(rows < (1ll << 31), B200K_E_TOOBIG, "softmax_q8: too many rows");
-    softmax_kernel<<<(unsigned)rows, SM_THREADS, p->axis_size * sizeof(float), (cudaStream_t)stream>>>(a);
+    launch_pdl(softmax_kernel, dim3((unsigned)rows), dim3(SM_THREADS), p->axis_size * sizeof(float), (cudaStream_t)stream, a);
     return check_launch("softmax_kernel");
 }
