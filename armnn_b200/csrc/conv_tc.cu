@@ -1275,7 +1275,7 @@ static int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUten
     const long long tiles = (long long)a.ntn * a.ntm;
     const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
     // Programmatic dependent launch: the grid may start while its predecessor in the stream drains (its set-up touches
-    // nothing the predecessor writes); the producer thread waits for the predecessor before its first activation load.
+    // nothing the predecessor writes); the producer threads wait for the predecessor before their first activation load.
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = dim3((unsigned)grid, 1, 1);
