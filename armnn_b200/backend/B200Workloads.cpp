@@ -457,15 +457,20 @@ std::unique_ptr<IWorkload> B200WorkloadFactory::CreateWorkload(LayerType type, c
             return std::make_unique<ImportMemGenericWorkload>(*PolymorphicDowncast<const MemImportQueueDescriptor*>(&d), info);
         case LayerType::Constant:
         {
-            // RefConstantWorkload: one copy of the layer's blob into its output handle; LoadedNetwork executes
-            // Constant workloads once at load time (src/armnn/LoadedNetwork.cpp:565-568)
-            return Make<ConstantQueueDescriptor>(d, info, [](const ConstantQueueDescriptor& data, cudaStream_t s)
+            // One copy of the layer's blob into its output handle.  LoadedNetwork executes the Constant workloads at load
+            // time (src/armnn/LoadedNetwork.cpp:565-568) and then again with every inference, as members of the workload
+            // queue (LoadedNetwork.cpp:1267): like ClConstantWorkload (src/backends/cl/workloads/ClConstantWorkload.cpp:61)
+            // only the first execution copies.
+            auto ranOnce = std::make_shared<bool>(false);
+            return Make<ConstantQueueDescriptor>(d, info, [ranOnce](const ConstantQueueDescriptor& data, cudaStream_t s)
             {
+                if (*ranOnce) { return; }
                 const ConstTensorHandle* src = data.m_LayerOutput;
                 if (!src) { throw InvalidArgumentException("B200Acc: Constant workload without data"); }
                 B200Check(cudaMemcpyAsync(Dev(data.m_Outputs[0]), src->GetConstTensor<void>(),
                                           src->GetTensorInfo().GetNumBytes(), cudaMemcpyHostToDevice, s), "cudaMemcpyAsync H2D");
                 B200Check(cudaStreamSynchronize(s), "cudaStreamSynchronize");
+                *ranOnce = true;
             });
         }
         case LayerType::Reshape:
