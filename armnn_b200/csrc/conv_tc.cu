@@ -189,6 +189,19 @@ __device__ __forceinline__ bool mbar_wait_fast(uint32_t bar_saddr, uint32_t pari
 {
     return mbar_test(bar_saddr, parity) || mbar_wait_slow(bar_saddr, parity);
 }
+// For waits whose owner is ahead of the work by construction (a producer that finds the ring full, the MMA issuer
+// that finds no free accumulator buffer: the epilogue is the bottleneck then): sleep between polls, so that the
+// waiting warp leaves its scheduler's issue slots to the epilogue warps it shares the scheduler with.
+__device__ __forceinline__ bool mbar_wait_idle(uint32_t bar_saddr, uint32_t parity)
+{
+    if (mbar_test(bar_saddr, parity) || mbar_test(bar_saddr, parity)) return true;
+    const long long t0 = clock64();
+    for (;;) {
+        __nanosleep(200);
+        if (mbar_test(bar_saddr, parity)) return true;
+        if (clock64() - t0 > TC_WAIT_LIMIT_CYCLES) return false;
+    }
+}
 __device__ __forceinline__ void tma_load_2d_s(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y)
 {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
@@ -645,7 +658,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 for (int g = 0; g < gpt && alive; ++g, te += 16u * (uint32_t)group) {
                     if (turn == (uint32_t)prod) {
                         if (!have) locate();
-                        if (!__all_sync(0xffffffffu, mbar_wait_fast(empty_addr + st * 8, ph ^ 1u))) { atomicExch(&g_tc_status, 1); alive = false; }
+                        if (!__all_sync(0xffffffffu, mbar_wait_idle(empty_addr + st * 8, ph ^ 1u))) { atomicExch(&g_tc_status, 1); alive = false; }
                         const uint32_t fb = full_addr + st * 8;
                         if (alive && elect_one()) {
                             if (debug & 2) {
@@ -710,7 +723,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             for (int t = blockIdx.x; t < ntiles && alive; t += gridDim.x, ++it) {
                 const int buf = it & ((1 << NACC_LOG2) - 1);
                 // the epilogue must have drained this accumulator buffer (one round of the buffers ago)
-                if (!__all_sync(0xffffffffu, mbar_wait(&acc_empty[buf], (((uint32_t)it >> NACC_LOG2) & 1u) ^ 1u))) { atomicExch(&g_tc_status, 4); break; }
+                if (!__all_sync(0xffffffffu, mbar_wait_idle(smem_u32(&acc_empty[buf]), (((uint32_t)it >> NACC_LOG2) & 1u) ^ 1u))) { atomicExch(&g_tc_status, 4); break; }
                 tc_fence_after();
                 const uint32_t tacc = tmem_base + (uint32_t)(buf * BN);
                 uint64_t dbs = db0;                              // stationary weights: the stage's first tile
