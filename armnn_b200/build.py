@@ -6,6 +6,7 @@
 Artefacts are written in-tree next to the sources and are git-ignored:
     armnn_b200/libb200k.so                 the kernel library (C ABI of include/b200k.h)
     armnn_b200/backend/Nv_B200Acc_backend.so   the IBackendInternal plugin (needs Arm NN headers)
+    armnn_b200/build/issue_cost            probe of TMA / mbarrier issue costs (csrc/probes/)
 """
 import glob
 import os
@@ -91,8 +92,21 @@ def build_plugin(force=False, verbose=False):
     return PLUGIN
 
 
+def build_probes(force=False, verbose=False):
+    """Stand-alone measurement programs under csrc/probes/ -> armnn_b200/build/<name>."""
+    outs = []
+    for src in sorted(glob.glob(os.path.join(CSRC, "probes", "*.cu"))):
+        out = os.path.join(HERE, "build", os.path.basename(src)[:-3])
+        os.makedirs(os.path.dirname(out), exist_ok=True)
+        if force or _newer(out, [src]):
+            _run(["nvcc", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-o", out, src, "-lcuda"], verbose)
+        outs.append(out)
+    return outs
+
+
 def build_all(force=False, verbose=False):
     build_kernels(force, verbose)
+    build_probes(force, verbose)
     build_plugin(force, verbose)
 
 
