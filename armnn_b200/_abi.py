@@ -128,6 +128,7 @@ KERNEL_ENTRY_POINTS = {
 EXPORTED_SYMBOLS = ["b200k_" + k for k in KERNEL_ENTRY_POINTS] + [
     "b200k_device_open", "b200k_device_count", "b200k_last_error", "b200k_version",
     "b200k_activation_clamp", "b200k_conv2d_pack_bytes", "b200k_conv2d_pack", "b200k_conv2d_scratch_bytes", "b200k_conv2d_q8_static", "b200k_sizeof_params", "b200k_poll_status",
+    "b200k_kernel_launches",
 ]
 
 
@@ -137,6 +138,8 @@ def declare_product(lib):
         fn = getattr(lib, "b200k_" + name)
         fn.argtypes = [C.POINTER(struct), C.c_void_p]
         fn.restype = C.c_int
+    lib.b200k_kernel_launches.argtypes = []
+    lib.b200k_kernel_launches.restype = C.c_ulonglong
     lib.b200k_device_open.argtypes = [C.c_int]
     lib.b200k_device_open.restype = C.c_int
     lib.b200k_device_count.restype = C.c_int

@@ -2,6 +2,7 @@
 #include <math.h>
 #include <stdarg.h>
 #include <string.h>
+#include <atomic>
 #include "common.cuh"
 
 namespace b200k {
@@ -16,11 +17,16 @@ void set_error(const char* fmt, ...)
     va_end(ap);
 }
 
+static std::atomic<unsigned long long> g_launches{0};
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
 }  // namespace b200k
 
 using namespace b200k;
 
 extern "C" const char* b200k_last_error(void) { return g_err; }
+
+extern "C" unsigned long long b200k_kernel_launches(void) { return g_launches.load(std::memory_order_relaxed); }
 
 extern "C" const char* b200k_version(void) { return "b200k 0.1 (sm_100a)"; }
 

@@ -25,8 +25,11 @@ void set_error(const char* fmt, ...);
              ::b200k::set_error("%s failed: %s", #call, cudaGetErrorString(e_));      \
              return B200K_E_CUDA; } } while (0)
 
+void count_launch();                       // one more kernel launched (api.cu)
+
 inline int check_launch(const char* what)
 {
+    count_launch();
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) { set_error("launch of %s failed: %s", what, cudaGetErrorString(e)); return B200K_E_CUDA; }
     return B200K_OK;

@@ -752,18 +752,19 @@ class LoadedNetwork(GraphProgram):
     def launch_all(self, stream_handle):
         """Enqueue every workload on the given CUDA stream; returns the number of kernels launched."""
         l = lib.load_library()
+        before = l.b200k_kernel_launches()
         for layer, entry, params in self.workloads:
             rc = getattr(l, "b200k_" + entry)(ctypes.byref(params), ctypes.c_void_p(stream_handle))
             if rc != 0:
                 raise RuntimeError("workload %s (%s) failed: %s" % (layer.name, entry, l.b200k_last_error().decode()))
-        return len(self.workloads)
+        return int(l.b200k_kernel_launches() - before)
 
     def Execute(self):
         """The workload queue only (inputs and outputs stay in device memory)."""
         if self.graph is not None:
             with self.torch.cuda.stream(self.stream):
                 self.graph.replay()
-            return len(self.workloads)
+            return self.graph_kernels
         return self.launch_all(self.stream.cuda_stream)
 
     def CaptureGraph(self):
@@ -773,7 +774,7 @@ class LoadedNetwork(GraphProgram):
         self.stream.synchronize()
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g, stream=self.stream):
-            self.launch_all(torch.cuda.current_stream().cuda_stream)
+            self.graph_kernels = self.launch_all(torch.cuda.current_stream().cuda_stream)    # kernel nodes of the graph
         self.graph = g
 
     def EnqueueWorkload(self, input_tensors, output_tensors):

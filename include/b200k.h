@@ -295,6 +295,11 @@ int b200k_qlstm_step(const b200k_qlstm_params* p, void* stream);
  * the reference. */
 int b200k_poll_status(void);
 
+/* Kernels this library has launched in this process so far (every launch of every entry point counts; a launch
+ * recorded into a CUDA graph during stream capture counts once).  For callers that report how many of the library's
+ * kernels a measured region ran.  No counterpart in the reference. */
+unsigned long long b200k_kernel_launches(void);
+
 /* sizeof() of a parameter struct as compiled into the library, for bindings in other languages to check their
  * own declarations: 0 conv2d, 1 fc, 2 bmm, 3 pool2d, 4 mean, 5 eltwise, 6 activation, 7 softmax, 8 convert,
  * 9 qlstm.  No counterpart in the reference (its backends are linked as C++). */
