@@ -522,7 +522,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     constexpr int MAX_STAGES = L::MAX_STAGES;
     constexpr int UW = L::UW, UNITS = L::UNITS, IO_BYTES = L::IO_BYTES;
     constexpr int NACC_LOG2 = EG == 1 ? 1 : (EG == 2 ? 2 : 3);          // 2, 4 or 8 accumulator buffers in TMEM
-    static_assert(EG == 1 || EG * BN == 256, "epilogue groups: 256 / BN tiles at once");
+    static_assert(EG == 1 || EG * BN <= 256, "epilogue groups: at most 256 / BN tiles at once");
     const int STAGES = a.stages;
     const int NIO = a.nio;
     extern __shared__ uint8_t smem_raw[];
@@ -1447,10 +1447,12 @@ int launch_conv_tc(const b200k_conv2d_params* p, cudaStream_t stream, int kvalid
         const CUtensorMapSwizzle usw = uw == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
         // Epilogue groups: with one n-tile and no fused Add, 256 / bn (at most 4) tiles are in the epilogue at once, each
         // on its own accumulator buffer and a quarter (half) of the epilogue warps.  (Measured on ResNet-50's layers at
-        // batch 256: 1x1 and 3x3 convolutions with 64 or 128 output channels run 10 - 30 % faster this way, the 7x7 stem
-        // in row-window mode 9 % slower, so that mode keeps one group.)
+        // batch 256: 1x1 and 3x3 convolutions with 64 or 128 output channels run 10 - 30 % faster this way.)
         static const bool no_groups = getenv("B200K_TC_NOGROUPS") != nullptr;     // measurement aid
         a.eg = (a.ntn == 1 && !fa.res && !row_mode && !no_groups) ? (bn == 64 ? 4 : (bn == 128 ? 2 : 1)) : 1;
+        // row-window mode (network stems): two groups (0.41 -> 0.32 ms for ResNet-50's stem at batch 256; four were slower
+        // than one there)
+        if (row_mode && !no_groups && a.ntn == 1 && !fa.res && bn == 64) a.eg = 2;
         // stores: one epilogue warp's 32 rows x (eg * uw / 4) columns
         const int stw = a.eg * uw / 4;
         cuuint32_t box_st[3] = {(cuuint32_t)stw, 32, 1};
@@ -1473,10 +1475,12 @@ int launch_conv_tc(const b200k_conv2d_params* p, cudaStream_t stream, int kvalid
     if (swz == 128) {
         if (bn == 256) return launch_tc<256, 128, 1>(tmA, tmB, tmY, tmR, a, stream);
         if (bn == 128) return grouped ? launch_tc<128, 128, 2>(tmA, tmB, tmY, tmR, a, stream) : launch_tc<128, 128, 1>(tmA, tmB, tmY, tmR, a, stream);
+        if (a.eg == 2) return launch_tc<64, 128, 2>(tmA, tmB, tmY, tmR, a, stream);
         return grouped ? launch_tc<64, 128, 4>(tmA, tmB, tmY, tmR, a, stream) : launch_tc<64, 128, 1>(tmA, tmB, tmY, tmR, a, stream);
     }
     if (bn == 256) return launch_tc<256, 64, 1>(tmA, tmB, tmY, tmR, a, stream);
     if (bn == 128) return grouped ? launch_tc<128, 64, 2>(tmA, tmB, tmY, tmR, a, stream) : launch_tc<128, 64, 1>(tmA, tmB, tmY, tmR, a, stream);
+    if (a.eg == 2) return launch_tc<64, 64, 2>(tmA, tmB, tmY, tmR, a, stream);
     return grouped ? launch_tc<64, 64, 4>(tmA, tmB, tmY, tmR, a, stream) : launch_tc<64, 64, 1>(tmA, tmB, tmY, tmR, a, stream);
 }
 
