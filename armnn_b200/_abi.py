@@ -27,7 +27,7 @@ class Conv2dParams(C.Structure):
                 ("clamp_lo", C.c_int32), ("clamp_hi", C.c_int32),
                 ("acc_out", C.c_void_p), ("algo", C.c_int32), ("packed", C.c_void_p),
                 ("add_operand", QTensor), ("add_out", QTensor),
-                ("scratch", C.c_void_p), ("scratch_bytes", C.c_size_t)]
+                ("scratch", C.c_void_p), ("scratch_bytes", C.c_size_t), ("selftest_us", C.c_int32)]
 
 
 class FcParams(C.Structure):

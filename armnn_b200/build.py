@@ -6,7 +6,8 @@
 Artefacts are written in-tree next to the sources and are git-ignored:
     armnn_b200/libb200k.so                 the kernel library (C ABI of include/b200k.h)
     armnn_b200/backend/Nv_B200Acc_backend.so   the IBackendInternal plugin (needs Arm NN headers)
-    armnn_b200/build/issue_cost            probe of TMA / mbarrier issue costs (csrc/probes/)
+
+The Arm NN source tree (headers only are needed) is found through the environment variable ARMNN_ROOT.
 """
 import glob
 import os
@@ -65,10 +66,10 @@ def build_kernels(force=False, verbose=False):
 
 
 def armnn_root():
-    """Location of an Arm NN source tree (headers only are needed), or None."""
-    for cand in (os.environ.get("ARMNN_ROOT"), "/root/reference"):
-        if cand and os.path.isfile(os.path.join(cand, "include", "armnn", "backends", "IBackendInternal.hpp")):
-            return cand
+    """Location of an Arm NN source tree (headers only are needed): $ARMNN_ROOT, or None."""
+    cand = os.environ.get("ARMNN_ROOT")
+    if cand and os.path.isfile(os.path.join(cand, "include", "armnn", "backends", "IBackendInternal.hpp")):
+        return cand
     return None
 
 
@@ -92,21 +93,8 @@ def build_plugin(force=False, verbose=False):
     return PLUGIN
 
 
-def build_probes(force=False, verbose=False):
-    """Stand-alone measurement programs under csrc/probes/ -> armnn_b200/build/<name>."""
-    outs = []
-    for src in sorted(glob.glob(os.path.join(CSRC, "probes", "*.cu"))):
-        out = os.path.join(HERE, "build", os.path.basename(src)[:-3])
-        os.makedirs(os.path.dirname(out), exist_ok=True)
-        if force or _newer(out, [src]):
-            _run(["nvcc", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-o", out, src, "-lcuda"], verbose)
-        outs.append(out)
-    return outs
-
-
 def build_all(force=False, verbose=False):
     build_kernels(force, verbose)
-    build_probes(force, verbose)
     build_plugin(force, verbose)
 
 

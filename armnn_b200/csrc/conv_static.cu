@@ -67,6 +67,8 @@ extern "C" int b200k_conv2d_q8_static(const b200k_conv2d_params* p, void* stream
     q.scratch_bytes = scratch;
     // Both regions are overwritten in full before they are read (the table by the pack kernels below, the input
     // region by the convolution's own re-pack), so nothing left over from an earlier call can leak into this one.
+    // The pack kernels are ordinary launches: they have completed before the convolution's grid starts, which reads
+    // the tables ahead of its programmatic-dependency wait (see tc_pack).
     rc = b200k_conv2d_pack(&q, base, stream);
     if (rc) return rc;
     return conv2d_dispatch(&q, (cudaStream_t)stream);

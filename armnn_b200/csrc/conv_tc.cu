@@ -39,8 +39,10 @@
 // b200k_poll_status), drains and returns, so a logic error cannot hang the device.
 #include <cuda.h>
 #include <stdlib.h>
+#include <atomic>
 #include <string.h>
 #include <cudaTypedefs.h>
+#include <type_traits>
 #include "common.cuh"
 
 namespace b200k {
@@ -69,6 +71,14 @@ constexpr long long TC_WAIT_LIMIT_CYCLES = 4000000000ll;  // about two seconds: 
 
 __device__ int g_tc_status = 0;                 // 0 ok, otherwise the code of the wait that gave up
 
+// Constants of the hot path, filled in by the host: they sit in the kernel's parameter space, so the packed
+// instructions read them as constant-bank operands and they take no registers.  Each is the same value twice.
+struct EpiConsts {
+    float2 inv2, nsy2, magic2, zero2, neg2;      // RN(1 / sy), -sy, MAGIC, 0, -1
+    float2 zoff_lut2, zoff_sat2, zoff_clamp2;    // what is added to t = MAGIC + n (see epi_chunk), per way of ending
+    float lo, hi;                                // EPI_CLAMP: clamp bounds in the biased domain (MAGIC + ...)
+};
+
 struct TcArgs {
     const int32_t* bias; void* y; int32_t* acc_out;
     const float* w_scales; const float* b_scales;
@@ -77,7 +87,7 @@ struct TcArgs {
     int zx;                                     // true input zero point
     int zw;                                     // weight zero point (per-tensor asymmetric weights), 0 otherwise
     int nzw;                                    // zw != 0: constant B tiles (1 or 2) that add -zw x (row sum of A) to every column
-    int zw_val[2];                              // their values: -min(zw, 128) and -(zw - 128), each fits int8
+    int zw_val[2];                              // their int8 values, which add up to -zw
     int mask_cpad, mask_kw;                     // row-window mode: which bytes of a K-slice are real taps (for the row sums)
     int ntn;                                    // n-tiles: ceil(OC / BN); columns beyond OC are padding
     int kvalid_c;                               // real input channels per tap (C, or fewer when the caller zero-padded them)
@@ -98,6 +108,7 @@ struct TcArgs {
     const uint8_t* res; float res_scale; int res_zp; int res_u8;
     Requant rq2;
     float inv_sy;                               // RN(1 / rq.sy), correctly rounded (see epi_chunk)
+    EpiConsts ep;                               // the hot path's constants
     const uint8_t* add_lut;                     // fused-add table built by b200k_conv2d_pack (+ its tag), or null
     uint32_t lut_tag[TC_LUT_TAG_WORDS];         // the tag a table made for exactly this launch carries
     int stages;                                 // ring depth chosen by the launcher (<= 16)
@@ -105,14 +116,16 @@ struct TcArgs {
     int group;                                  // K-slices per ring stage: they share the stage's pair of barriers
     int eg;                                     // epilogue groups (1, 2 or 4): group g takes the tiles with index = g mod eg
     int bstat;                                  // weights stay in shared memory for the whole launch (one n-tile, small K)
-    int nio;                                    // shared buffers for units of the fused Add's other operand: 0 or 2
+    int nio;                                    // shared buffers for units of the fused Add's other operand: 0, 2 or 3
+    int nstg;                                   // staging buffers per epilogue warp: 1 or 2
     // zero-point correction classes: pixels whose in-image tap rectangle [ky0, ky1) x [kx0, kx1) is the same share
     // one row of per-channel corrections.  ypair / xpair list the distinct (k0 << 4 | k1) of the geometry, ycls / xcls
     // map such a code back to its position in the list.
     int ncy, ncx, ncls;
     uint8_t ypair[16], xpair[16];
     uint8_t ycls[256], xcls[256];
-    int debug;                                  // timing experiments (results are wrong): bit 0 no MMAs, bit 1 no TMA loads, bit 2 no epilogue work
+    long long wait_limit;                       // clock64 ticks after which a device-side wait gives up
+    int skip_loads;                             // fault-injection self-test: the producers issue no loads (see b200k_conv2d_params.selftest_us)
 };
 
 // ---- PTX wrappers --------------------------------------------------------------------------------------
@@ -142,7 +155,7 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes)
 }
 // Bounded wait: returns false when the time limit is hit.  try_wait suspends the thread until the phase completes or
 // a hardware time limit expires, so a waiting thread polls rarely; the clock is read once per 32 polls.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity)
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, long long limit)
 {
     const uint32_t addr = smem_u32(bar);
     long long t0 = 0;
@@ -158,7 +171,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity)
         }
         const long long now = clock64();
         if (t0 == 0) t0 = now;
-        else if (now - t0 > TC_WAIT_LIMIT_CYCLES) return false;
+        else if (now - t0 > limit) return false;
     }
 }
 // The single-thread roles (TMA producer, MMA issuer) run one dependent instruction chain per K-slice; everything in
@@ -173,7 +186,7 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar_saddr, uint32_t parity)
                  : "=r"(ok) : "r"(bar_saddr), "r"(parity) : "memory");
     return ok != 0;
 }
-__device__ __forceinline__ bool mbar_wait_slow(uint32_t bar_saddr, uint32_t parity)
+__device__ __forceinline__ bool mbar_wait_slow(uint32_t bar_saddr, uint32_t parity, long long limit)
 {
     long long t0 = 0;
     for (;;) {
@@ -182,24 +195,24 @@ __device__ __forceinline__ bool mbar_wait_slow(uint32_t bar_saddr, uint32_t pari
             if (mbar_test(bar_saddr, parity)) return true;
         const long long now = clock64();
         if (t0 == 0) t0 = now;
-        else if (now - t0 > TC_WAIT_LIMIT_CYCLES) return false;
+        else if (now - t0 > limit) return false;
     }
 }
-__device__ __forceinline__ bool mbar_wait_fast(uint32_t bar_saddr, uint32_t parity)
+__device__ __forceinline__ bool mbar_wait_fast(uint32_t bar_saddr, uint32_t parity, long long limit)
 {
-    return mbar_test(bar_saddr, parity) || mbar_wait_slow(bar_saddr, parity);
+    return mbar_test(bar_saddr, parity) || mbar_wait_slow(bar_saddr, parity, limit);
 }
 // For waits whose owner is ahead of the work by construction (a producer that finds the ring full, the MMA issuer
 // that finds no free accumulator buffer: the epilogue is the bottleneck then): sleep between polls, so that the
 // waiting warp leaves its scheduler's issue slots to the epilogue warps it shares the scheduler with.
-__device__ __forceinline__ bool mbar_wait_idle(uint32_t bar_saddr, uint32_t parity)
+__device__ __forceinline__ bool mbar_wait_idle(uint32_t bar_saddr, uint32_t parity, long long limit)
 {
     if (mbar_test(bar_saddr, parity) || mbar_test(bar_saddr, parity)) return true;
     const long long t0 = clock64();
     for (;;) {
         __nanosleep(200);
         if (mbar_test(bar_saddr, parity)) return true;
-        if (clock64() - t0 > TC_WAIT_LIMIT_CYCLES) return false;
+        if (clock64() - t0 > limit) return false;
     }
 }
 __device__ __forceinline__ void tma_load_2d_s(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y)
@@ -311,9 +324,14 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr)
 
 // The epilogue arithmetic is written to stay off the conversion/transcendental (XU) pipe, which issues only 16 lanes
 // per clock per SM and throttled the first version of this kernel: float <-> int conversions and rounding are done
-// with the 1.5 * 2^23 magic constant on the FP32 pipe, and the only conversion instruction left is the int32 -> fp32
-// of the accumulator.
+// with the 1.5 * 2^23 magic constant on the FP32 pipe, and the only conversion instructions left are the int32 -> fp32
+// of the accumulator and one saturating float -> byte conversion.
 constexpr float TC_MAGIC = 12582912.0f;          // 1.5 * 2^23: x + MAGIC - MAGIC == rint(x) for |x| < 2^22
+// |q - rint(q)| at or above this sends a chunk to the reference arithmetic: 0.5 = exact halves (and overflow) only
+#ifndef B200K_TC_FIX_THRESHOLD
+#define B200K_TC_FIX_THRESHOLD 0.5f
+#endif
+constexpr float TC_FIX_THRESHOLD = B200K_TC_FIX_THRESHOLD;
 
 // Reference arithmetic of one output value (unfused IEEE fp32), used by the rare fix-up pass:
 // v = fl(fl(acc * m) + b); q = clamp(zy + round_half_away(fl(v / sy))), then for a fused Add both operands are
@@ -337,11 +355,6 @@ __device__ __forceinline__ int exact_value(int acc, float m, float b, uint32_t r
         n = fminf(fmaxf(n, x.lo2), x.hi2);
     }
     return __float2int_rn(n);
-}
-
-__device__ __forceinline__ void lds_2x2(uint32_t addr, f32x2& a, f32x2& b)   // four consecutive floats as two pairs
-{
-    asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "r"(addr));
 }
 
 // shared-memory accesses by 32-bit shared address (keeps them out of the generic address space)
@@ -374,89 +387,109 @@ __device__ __forceinline__ uint32_t lds_u8(uint32_t addr)
     return v;
 }
 
-struct EpiConsts {
-    f32x2 inv2, nsy2, magic2, zy2, zero2;        // pairs of: RN(1 / sy), -sy, the rounding constant, zero point (+ bias), 0
-    float lo, hi;                                // clamp bounds in the biased domain (MAGIC + ...)
-    uint32_t lut;                                // shared address of the fused-add table
-    bool sat, sat_u8;                            // the clamp is exactly the range of the (unsigned / signed) 8-bit output type
+// What the last step of the hot path is: look the fused Add up in its table, convert with the output type's own
+// saturation (the clamp is exactly the type's range), or clamp to a narrower activation range.
+enum { EPI_LUT = 0, EPI_SAT_U8 = 1, EPI_SAT_S8 = 2, EPI_CLAMP = 3 };
+
+__device__ __forceinline__ void lds_f2x2(uint32_t addr, float2& a, float2& b)   // four consecutive floats as two pairs
+{
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(a.x), "=f"(a.y), "=f"(b.x), "=f"(b.y) : "r"(addr));
+}
+
+// 16 accumulator columns of one output pixel -> 16 output bytes, branch-free.  EPI_LUT: look the result of the fused
+// Add up with the other operand's byte (16 bytes in rv).  The fp32 arithmetic runs two values per instruction
+// (__ffma2_rn and friends: one issue slot for two IEEE round-to-nearest operations).
+//
+// The reference chain is v = fl(fl(acc * m) + b); q = fl(v / sy); n = round_half_away(q); out = clamp(zy + n).
+// The division is evaluated exactly without the division unit: with y = RN(1 / sy) (prepared on the host), p = fl(v * y),
+// r = fma(-p, sy, v) (exact) and q = fma(r, y, p), q is the correctly rounded quotient (Markstein's theorem; it needs a
+// correctly rounded y and a normal-range quotient; for tiny or huge quotients the last bit does not matter, they round
+// to 0 or saturate).  t = q + MAGIC rounds to an integer, halves to even where the reference rounds them away from
+// zero: |q - n| = 0.5 exactly marks those values (and any value too large for the constant); the maximum of |q - n|
+// over the chunk is handed back in dmax, and the caller re-evaluates a flagged chunk with the plain reference
+// arithmetic (a few values per million).
+// Where a chunk's per-channel constants (m = sx * sw, b = bias * sb, cc = zero-point correction) come from.
+// TabShared: tables in shared memory, read with 128-bit loads that every lane of the warp repeats (all lanes work on
+// the same columns): 12 bytes per output and lane through the shared-memory pipe.
+struct TabShared {
+    uint32_t m, b, cc;                          // shared addresses at the chunk's first column
+    __device__ __forceinline__ void load(int g, float2& m01, float2& m23, float2& b01, float2& b23, int4& c) const
+    {
+        lds_f2x2(m + g * 16, m01, m23);
+        lds_f2x2(b + g * 16, b01, b23);
+        const uint4 cv = lds128(cc + g * 16);
+        c = make_int4((int)cv.x, (int)cv.y, (int)cv.z, (int)cv.w);
+    }
+};
+// TabParam: tables in the kernel's parameter space (constant bank).  The column index is the same for the whole warp,
+// so the loads are uniform loads and the values are uniform-register operands of the arithmetic: no shared-memory
+// traffic and no vector registers.
+struct TabParam {
+    const float* m; const float* b; const int* cc;   // at the chunk's first column
+    __device__ __forceinline__ void load(int g, float2& m01, float2& m23, float2& b01, float2& b23, int4& c) const
+    {
+        m01 = make_float2(m[g * 4 + 0], m[g * 4 + 1]); m23 = make_float2(m[g * 4 + 2], m[g * 4 + 3]);
+        b01 = make_float2(b[g * 4 + 0], b[g * 4 + 1]); b23 = make_float2(b[g * 4 + 2], b[g * 4 + 3]);
+        c = make_int4(cc[g * 4 + 0], cc[g * 4 + 1], cc[g * 4 + 2], cc[g * 4 + 3]);
+    }
 };
 
-// shared-memory addresses of the per-channel tables at the chunk's first column
-struct EpiAddr { uint32_t m, b, cc; };
-
-// 16 accumulator columns of one output pixel -> 16 output bytes, branch-free.  FUSED: look the result of the fused
-// Add up with the other operand's byte (16 bytes in rv).
-//
-// The reference chain is v = fl(fl(acc * m) + b); q = clamp(zy + round_half_away(fl(v / sy))).  The division is
-// evaluated exactly without the division unit: with y = RN(1 / sy) (prepared on the host), q0 = fl(v * y),
-// r = fma(-q0, sy, v) (exact) and q1 = fma(r, y, q0), q1 is the correctly rounded quotient (Markstein's theorem; it
-// needs a correctly rounded y and a normal-range quotient — for tiny or huge quotients the last bit does not matter,
-// they round to 0 or saturate).  Rounding to an integer uses the 1.5 * 2^23 constant, which rounds halves to even where
-// the reference rounds them away from zero: |q1 - n| = 0.5 exactly marks those values (and any value too large for the
-// constant), the maximum of |q1 - n| over the chunk is handed back in dmax, and the caller re-evaluates a flagged chunk
-// with the plain reference arithmetic.
-template <bool FUSED, bool SAT>
-__device__ __forceinline__ uint4 epi_chunk(const uint32_t* r, const uint4 rv, const EpiAddr& ad, const EpiConsts& ec, float& dmax)
+template <int KIND, class Tab>
+__device__ __forceinline__ uint4 epi_chunk(const uint32_t* r, const uint4 rv, const Tab& ad, const EpiConsts& ec, const uint32_t lut, float& dmax)
 {
+    const float2 zoff2 = KIND == EPI_LUT ? ec.zoff_lut2 : (KIND == EPI_CLAMP ? ec.zoff_clamp2 : ec.zoff_sat2);
     const uint32_t resw[4] = {rv.x, rv.y, rv.z, rv.w};
     uint32_t packed[4];
     #pragma unroll
     for (int g = 0; g < 4; ++g) {                              // 4 columns at a time: 128-bit shared loads
-        f32x2 m01, m23, b01, b23;
-        lds_2x2(ad.m + g * 16, m01, m23);
-        lds_2x2(ad.b + g * 16, b01, b23);
-        const uint4 cv = lds128(ad.cc + g * 16);
-        const f32x2 a01 = pack2(__int2float_rn((int)r[g * 4 + 0] - (int)cv.x), __int2float_rn((int)r[g * 4 + 1] - (int)cv.y));
-        const f32x2 a23 = pack2(__int2float_rn((int)r[g * 4 + 2] - (int)cv.z), __int2float_rn((int)r[g * 4 + 3] - (int)cv.w));
-        // acc * m as an FMA with a zero addend: the assembler contracts a packed multiply feeding a packed add into
-        // one FMA (a single rounding) even with explicit rounding modifiers, which the reference does not do
-        const f32x2 v01 = add2(fma2(a01, m01, ec.zero2), b01), v23 = add2(fma2(a23, m23, ec.zero2), b23);
-        const f32x2 p01 = mul2(v01, ec.inv2), p23 = mul2(v23, ec.inv2);
-        const f32x2 q01 = fma2(fma2(p01, ec.nsy2, v01), ec.inv2, p01), q23 = fma2(fma2(p23, ec.nsy2, v23), ec.inv2, p23);
-        const f32x2 t01 = add2(q01, ec.magic2), t23 = add2(q23, ec.magic2);
-        const f32x2 n01 = sub2(t01, ec.magic2), n23 = sub2(t23, ec.magic2);
-        const f32x2 d01 = sub2(q01, n01), d23 = sub2(q23, n23);
-        float d[4], z[4];
-        unpack2(d01, d[0], d[1]); unpack2(d23, d[2], d[3]);
-        dmax = fmaxf(fmaxf(dmax, fabsf(d[0])), fabsf(d[1]));
-        dmax = fmaxf(fmaxf(dmax, fabsf(d[2])), fabsf(d[3]));
+        float2 m01, m23, b01, b23;
+        int4 cv;
+        ad.load(g, m01, m23, b01, b23, cv);
+        const float2 a01 = make_float2(__int2float_rn((int)r[g * 4 + 0] - cv.x), __int2float_rn((int)r[g * 4 + 1] - cv.y));
+        const float2 a23 = make_float2(__int2float_rn((int)r[g * 4 + 2] - cv.z), __int2float_rn((int)r[g * 4 + 3] - cv.w));
+        // acc * m as an FMA with a zero addend: a packed multiply feeding a packed add must not be contracted into
+        // one FMA (a single rounding), which the reference does not do
+        const float2 v01 = __fadd2_rn(__ffma2_rn(a01, m01, ec.zero2), b01), v23 = __fadd2_rn(__ffma2_rn(a23, m23, ec.zero2), b23);
+        const float2 p01 = __ffma2_rn(v01, ec.inv2, ec.zero2), p23 = __ffma2_rn(v23, ec.inv2, ec.zero2);
+        const float2 q01 = __ffma2_rn(__ffma2_rn(p01, ec.nsy2, v01), ec.inv2, p01), q23 = __ffma2_rn(__ffma2_rn(p23, ec.nsy2, v23), ec.inv2, p23);
+        const float2 t01 = __fadd2_rn(q01, ec.magic2), t23 = __fadd2_rn(q23, ec.magic2);
+        const float2 n01 = __ffma2_rn(ec.magic2, ec.neg2, t01), n23 = __ffma2_rn(ec.magic2, ec.neg2, t23);   // rint(q) = t - MAGIC (exact)
+        const float2 d01 = __ffma2_rn(n01, ec.neg2, q01), d23 = __ffma2_rn(n23, ec.neg2, q23);       // q - n (exact)
+        dmax = fmaxf(fmaxf(dmax, fabsf(d01.x)), fabsf(d01.y));
+        dmax = fmaxf(fmaxf(dmax, fabsf(d23.x)), fabsf(d23.y));
+        // z = t - zoff (exact).  SAT / LUT: zoff = MAGIC - zero point (with the table: minus the type minimum as well), so
+        // z is the integer-valued result itself; CLAMP: zoff = -zero point, z stays in the biased domain
+        const float2 z01 = __fadd2_rn(t01, zoff2), z23 = __fadd2_rn(t23, zoff2);
+        const float z[4] = {z01.x, z01.y, z23.x, z23.y};
         uint32_t bits[4];
-        if (FUSED || SAT) {
-            // the clamp is the 8-bit type's own range: one saturating conversion of n + zero point (an integer-valued
-            // float; with the table: minus the type minimum, a byte in 0..255) replaces the two min/max
-            const f32x2 z01 = add2(n01, ec.zy2), z23 = add2(n23, ec.zy2);
-            unpack2(z01, z[0], z[1]); unpack2(z23, z[2], z[3]);
-            #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                if (FUSED || ec.sat_u8) asm("cvt.rni.sat.u8.f32 %0, %1;" : "=r"(bits[e]) : "f"(z[e]));
-                else                    asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(bits[e]) : "f"(z[e]));
-                if (FUSED) {
-                    // entry (conv output - type minimum) * pitch + other byte; ec.lut holds the table's address, a
-                    // multiple of 256, and the other operand's byte goes into its low 8 bits
-                    bits[e] = lds_u8(bits[e] * (uint32_t)TC_LUT_PITCH + __byte_perm(resw[g], ec.lut, 0x7650 + e));
-                }
-            }
-        } else {
-            const f32x2 z01 = add2(t01, ec.zy2), z23 = add2(t23, ec.zy2);
-            unpack2(z01, z[0], z[1]); unpack2(z23, z[2], z[3]);
+        if (KIND == EPI_CLAMP) {
             // clamp in the biased domain: the low byte of the bit pattern is the output byte
             #pragma unroll
             for (int e = 0; e < 4; ++e) bits[e] = __float_as_uint(fminf(fmaxf(z[e], ec.lo), ec.hi));
+        } else {
+            // the clamp is the 8-bit type's own range: one saturating conversion replaces the two min / max
+            #pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                if (KIND == EPI_SAT_S8) asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(bits[e]) : "f"(z[e]));
+                else                    asm("cvt.rni.sat.u8.f32 %0, %1;" : "=r"(bits[e]) : "f"(z[e]));
+                if (KIND == EPI_LUT) {
+                    // entry (conv output - type minimum) * pitch + other byte; lut holds the table's address, a
+                    // multiple of 256, and the other operand's byte goes into its low 8 bits
+                    bits[e] = lds_u8(bits[e] * (uint32_t)TC_LUT_PITCH + __byte_perm(resw[g], lut, 0x7650 + e));
+                }
+            }
         }
         packed[g] = __byte_perm(__byte_perm(bits[0], bits[1], 0x0040), __byte_perm(bits[2], bits[3], 0x0040), 0x5410);
     }
     return make_uint4(packed[0], packed[1], packed[2], packed[3]);
 }
 
-// The cold pass of one chunk, out of line and outside the hot loop; a warp calls it as a whole.  It re-reads the 16
-// accumulators from tensor memory and (fix) evaluates them with the reference arithmetic (other operand's bytes at
-// res_slot, result to out_slot) and / or (acc_row) writes the raw accumulators of a valid row out for the bit-exactness
-// tests.
-__device__ __noinline__ void epi_cold(uint32_t taddr, uint32_t res_slot, uint32_t out_slot, uint32_t a_m, uint32_t a_b,
-                                      uint32_t a_cc, const EpiExact& x, bool fix, int32_t* acc_row)
+// The cold pass of one chunk (rare, or the accumulator dump of the tests): from the 16 accumulators still in
+// registers, (fix) evaluate them with the reference arithmetic (other operand's bytes at res_slot, result to out_slot)
+// and / or (acc_row) write the raw accumulators of a valid row out for the bit-exactness tests.
+__device__ __forceinline__ void epi_cold(const uint32_t* r, uint32_t res_slot, uint32_t out_slot, uint32_t a_m, uint32_t a_b,
+                                         uint32_t a_cc, const EpiExact& x, bool fix, int32_t* acc_row)
 {
-    uint32_t r[16];
-    tc_ld16(taddr, r);
     if (acc_row) {
         #pragma unroll
         for (int j = 0; j < 16; ++j) acc_row[j] = (int)r[j] - lds_s32(a_cc + j * 4);
@@ -536,7 +569,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int stage_stride = a.bstat ? L::A_BYTES : L::STAGE_BYTES;
     uint8_t* ring = s_wst + (a.bstat ? (size_t)a.nslices * L::B_BYTES : 0);
     uint8_t* s_io = ring + (size_t)STAGES * a.group * stage_stride;
-    float* s_m = (float*)(s_io + (size_t)(EG + NIO) * IO_BYTES);   // first the warps' staging buffers (eg units' worth), then NIO operand units
+    float* s_m = (float*)(s_io + (size_t)(a.nstg * EG + NIO) * IO_BYTES);   // first the warps' staging buffers (nstg * eg units' worth), then NIO operand units
     float* s_bterm = s_m + BN;
     uint64_t* full = (uint64_t*)(s_bterm + BN);
     uint64_t* empty = full + MAX_STAGES;
@@ -615,12 +648,13 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             bool alive = true;
             const uint32_t ring_addr = smem_u32(ring), full_addr = smem_u32(full), empty_addr = smem_u32(empty);
             const uint32_t tab_addr = smem_u32(s_tab);
-            const int mode = a.im2col, debug = a.debug;
-            const bool bstat = a.bstat != 0;
+            const int mode = a.im2col;
+            const bool bstat = a.bstat != 0, skip_loads = a.skip_loads != 0;
+            const long long wait_limit = a.wait_limit;
             const uint32_t group_tx = a.stage_tx * (uint32_t)a.group;
             const uint32_t group_stride = (uint32_t)stage_stride * (uint32_t)a.group;
             // weights, scales, bias and tables do not depend on the previous kernel of the stream; activations do
-            if (a.bstat && !(a.debug & 2) && prod == 0 && elect_one()) {
+            if (a.bstat && !skip_loads && prod == 0 && elect_one()) {
                 mbar_expect_tx(w_full, (uint32_t)a.nslices * L::B_BYTES);
                 for (int s = 0; s < a.nslices; ++s)
                     tma_load_2d(s_wst + (size_t)s * L::B_BYTES, &tmB, w_full, (int)s_tab[s].z, 0);
@@ -658,35 +692,32 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 for (int g = 0; g < gpt && alive; ++g, te += 16u * (uint32_t)group) {
                     if (turn == (uint32_t)prod) {
                         if (!have) locate();
-                        if (!__all_sync(0xffffffffu, mbar_wait_idle(empty_addr + st * 8, ph ^ 1u))) { atomicExch(&g_tc_status, 1); alive = false; }
+                        if (!__all_sync(0xffffffffu, mbar_wait_idle(empty_addr + st * 8, ph ^ 1u, wait_limit))) { atomicExch(&g_tc_status, 1); alive = false; }
                         const uint32_t fb = full_addr + st * 8;
-                        if (alive && elect_one()) {
-                            if (debug & 2) {
-                                mbar_arrive_s(fb);
-                            } else {
-                                mbar_expect_tx_s(fb, group_tx);
-                                uint32_t sa = ring_addr + (uint32_t)st * group_stride;
-                                for (int gs = 0; gs < group; ++gs, sa += (uint32_t)stage_stride) {
-                                    const uint4 e = lds128(te + 16u * (uint32_t)gs);
-                                    if (mode == 2)      tma_load_4d_s(sa, &tmA, fb, 0, 0, h0 + (int)e.w, nimg);      // slice = filter row
-                                    else if (mode == 1) tma_load_im2col_s(sa, &tmA, fb, (int)e.x, w0, h0, nimg, (uint16_t)(e.y & 0xffffu), (uint16_t)(e.y >> 16));
-                                    else                tma_load_2d_s(sa, &tmA, fb, (int)e.x, (int)m0);
-                                    if (!bstat) tma_load_2d_s(sa + L::A_BYTES, &tmB, fb, (int)e.z, n0);
-                                }
+                        // (self-test: no loads are issued, so the stage never fills and every waiter runs into its limit)
+                        if (alive && !skip_loads && elect_one()) {
+                            mbar_expect_tx_s(fb, group_tx);
+                            uint32_t sa = ring_addr + (uint32_t)st * group_stride;
+                            for (int gs = 0; gs < group; ++gs, sa += (uint32_t)stage_stride) {
+                                const uint4 e = lds128(te + 16u * (uint32_t)gs);
+                                if (mode == 2)      tma_load_4d_s(sa, &tmA, fb, 0, 0, h0 + (int)e.w, nimg);      // slice = filter row
+                                else if (mode == 1) tma_load_im2col_s(sa, &tmA, fb, (int)e.x, w0, h0, nimg, (uint16_t)(e.y & 0xffffu), (uint16_t)(e.y >> 16));
+                                else                tma_load_2d_s(sa, &tmA, fb, (int)e.x, (int)m0);
+                                if (!bstat) tma_load_2d_s(sa + L::A_BYTES, &tmB, fb, (int)e.z, n0);
                             }
                         }
                     }
                     turn = (turn + 1) & turn_mask;
                     if (++st == STAGES) { st = 0; ph ^= 1u; }
                 }
-                if (a.res && alive && prod == 0) {
+                if (a.res && alive && !skip_loads && prod == 0) {
                     // the fused Add's other operand, one unit at a time, into the buffer the epilogue will overwrite
                     if (!have) locate();
                     for (int us = 0; us < UNITS; ++us) {
-                        if (!__all_sync(0xffffffffu, mbar_wait(&io_empty[ub], uph ^ 1u))) { atomicExch(&g_tc_status, 6); alive = false; break; }
+                        if (!__all_sync(0xffffffffu, mbar_wait(&io_empty[ub], uph ^ 1u, wait_limit))) { atomicExch(&g_tc_status, 6); alive = false; break; }
                         if (elect_one()) {
                             mbar_expect_tx(&io_full[ub], IO_BYTES);
-                            tma_load_3d(s_io + (size_t)(1 + ub) * IO_BYTES, &tmR, &io_full[ub], n0 + us * UW,
+                            tma_load_3d(s_io + (size_t)(a.nstg * EG + ub) * IO_BYTES, &tmR, &io_full[ub], n0 + us * UW,
                                         a.im2col == 2 ? 0 : (int)m0, a.im2col == 2 ? tm : 0);
                         }
                         if (++ub == NIO) { ub = 0; uph ^= 1u; }
@@ -708,8 +739,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             bool alive = true;
             int it = 0;
             const uint32_t full_addr = smem_u32(full), empty_addr = smem_u32(empty);
-            const int nzw = a.nzw, debug = a.debug;
+            const int nzw = a.nzw;
             const bool bstat = a.bstat != 0;
+            const long long wait_limit = a.wait_limit;
             // descriptors differ from slot to slot only in the 14-bit start-address field: one add per slice
             const uint64_t da0 = make_smem_desc<SWZ>(smem_u32(ring));
             const uint64_t db0 = make_smem_desc<SWZ>(bstat ? smem_u32(s_wst) : smem_u32(ring) + L::A_BYTES);
@@ -718,37 +750,33 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const uint64_t dwslice = (uint64_t)(L::B_BYTES >> 4);
             const uint64_t dbstep = bstat ? dwslice : dstage;            // from one slice's weight tile to the next
             const uint64_t dz0 = make_smem_desc<SWZ>(smem_u32(s_zw));
-            if (bstat && !(debug & 2) && !__all_sync(0xffffffffu, mbar_wait(w_full, 0))) { atomicExch(&g_tc_status, 7); alive = false; }
+            if (bstat && !__all_sync(0xffffffffu, mbar_wait(w_full, 0, wait_limit))) { atomicExch(&g_tc_status, 7); alive = false; }
             tc_fence_after();
             for (int t = blockIdx.x; t < ntiles && alive; t += gridDim.x, ++it) {
                 const int buf = it & ((1 << NACC_LOG2) - 1);
                 // the epilogue must have drained this accumulator buffer (one round of the buffers ago)
-                if (!__all_sync(0xffffffffu, mbar_wait_idle(smem_u32(&acc_empty[buf]), (((uint32_t)it >> NACC_LOG2) & 1u) ^ 1u))) { atomicExch(&g_tc_status, 4); break; }
+                if (!__all_sync(0xffffffffu, mbar_wait_idle(smem_u32(&acc_empty[buf]), (((uint32_t)it >> NACC_LOG2) & 1u) ^ 1u, wait_limit))) { atomicExch(&g_tc_status, 4); break; }
                 tc_fence_after();
                 const uint32_t tacc = tmem_base + (uint32_t)(buf * BN);
                 uint64_t dbs = db0;                              // stationary weights: the stage's first tile
                 for (int g = 0; g < gpt; ++g, dbs += dwslice * (uint64_t)group) {
-                    if (!__all_sync(0xffffffffu, mbar_wait_fast(full_addr + st * 8, ph))) { atomicExch(&g_tc_status, 2); alive = false; break; }
+                    if (!__all_sync(0xffffffffu, mbar_wait_fast(full_addr + st * 8, ph, wait_limit))) { atomicExch(&g_tc_status, 2); alive = false; break; }
                     tc_fence_after();
                     const uint32_t eb = empty_addr + st * 8;
                     if (elect_one()) {                 // the same lane every time: a commit covers the MMAs of its own thread
-                        if (debug & 1) {
-                            mbar_arrive_s(eb);
-                        } else {
-                            uint64_t da = da0 + dgroup * (uint64_t)st;
-                            uint64_t db = bstat ? dbs : db0 + dgroup * (uint64_t)st;
-                            for (int gs = 0; gs < group; ++gs, da += dstage, db += dbstep) {
-                                tc_mma_i8(tacc, da, db, id, (uint32_t)(g | gs));        // the tile's first MMA overwrites
+                        uint64_t da = da0 + dgroup * (uint64_t)st;
+                        uint64_t db = bstat ? dbs : db0 + dgroup * (uint64_t)st;
+                        for (int gs = 0; gs < group; ++gs, da += dstage, db += dbstep) {
+                            tc_mma_i8(tacc, da, db, id, (uint32_t)(g | gs));        // the tile's first MMA overwrites
+                            #pragma unroll
+                            for (int k = 1; k < SWZ / 32; ++k) tc_mma_i8_acc(tacc, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), id);
+                            for (int z = 0; z < nzw; ++z) {
+                                const uint64_t dz = dz0 + dwslice * (uint64_t)z;
                                 #pragma unroll
-                                for (int k = 1; k < SWZ / 32; ++k) tc_mma_i8_acc(tacc, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), id);
-                                for (int z = 0; z < nzw; ++z) {
-                                    const uint64_t dz = dz0 + dwslice * (uint64_t)z;
-                                    #pragma unroll
-                                    for (int k = 0; k < SWZ / 32; ++k) tc_mma_i8_acc(tacc, da + (uint64_t)(k * 2), dz + (uint64_t)(k * 2), id_zw);
-                                }
+                                for (int k = 0; k < SWZ / 32; ++k) tc_mma_i8_acc(tacc, da + (uint64_t)(k * 2), dz + (uint64_t)(k * 2), id_zw);
                             }
-                            tc_commit_s(eb);           // stage reusable once these MMAs have read it
                         }
+                        tc_commit_s(eb);           // stage reusable once these MMAs have read it
                     }
                     if (++st == STAGES) { st = 0; ph ^= 1u; }
                 }
@@ -769,7 +797,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int grp = (ew >> 2) / ppg;
         const int part = (ew >> 2) - grp * ppg;
         const int etid = threadIdx.x - 64;
-        constexpr int CPW = UW / 64;                          // 16-column chunks per warp and unit
+        constexpr int NCH = EG * UW / 64;                     // 16-column chunks per warp and unit: 1, 2 or 4
+        const int NSTG_UNITS = a.nstg * EG;                   // unit-sized buffers the staging area takes
         const int row = quad * 32 + lane;
         const uint32_t sw_x = UW == 128 ? (uint32_t)(row & 7) : (uint32_t)((row >> 1) & 3);   // TMA swizzle of this row
         const int pw = a.KW + 1;
@@ -787,37 +816,34 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             epi_barrier();
             lut_ok = *s_lut_ok != 0;
             // the producer's bulk copy of the table
-            if (!mbar_wait(lut_full, 0)) { atomicExch(&g_tc_status, 8); lut_ok = false; }
+            if (!mbar_wait(lut_full, 0, a.wait_limit)) { atomicExch(&g_tc_status, 8); lut_ok = false; }
         }
         const bool use_lut = fused && lut_ok;
         const bool always_fix = fused && !lut_ok;            // no table: every chunk takes the reference arithmetic
         const bool dump_acc = a.acc_out != nullptr;
-        EpiExact ex;
-        ex.sy1 = a.rq.sy; ex.zy1 = (float)a.rq.zy;
-        ex.lo1 = fmaxf(a.rq.tlo, (float)a.rq.clo); ex.hi1 = fminf(a.rq.thi, (float)a.rq.chi);
-        ex.fused = fused; ex.res_u8 = a.res_u8; ex.zr = (float)a.res_zp; ex.sr = a.res_scale;
-        ex.sy2 = a.rq2.sy; ex.zy2 = (float)a.rq2.zy;
-        ex.lo2 = fmaxf(a.rq2.tlo, (float)a.rq2.clo); ex.hi2 = fminf(a.rq2.thi, (float)a.rq2.chi);
-        EpiConsts ec;
-        ec.inv2 = pack2(a.inv_sy, a.inv_sy);
-        ec.nsy2 = pack2(-a.rq.sy, -a.rq.sy);
-        ec.magic2 = pack2(TC_MAGIC, TC_MAGIC);
-        ec.zero2 = pack2(0.f, 0.f);
-        // with the table the first stage yields (value - type minimum), a byte in 0..255, to index it
-        const float zb = use_lut ? ex.zy1 - a.rq.tlo : ex.zy1;
-        ec.zy2 = pack2(zb, zb);
-        ec.lo = use_lut ? TC_MAGIC : TC_MAGIC + ex.lo1;
-        ec.hi = use_lut ? TC_MAGIC + 255.0f : TC_MAGIC + ex.hi1;
-        ec.lut = smem_u32(s_lut);
-        ec.sat = !use_lut && ex.lo1 == a.rq.tlo && ex.hi1 == a.rq.thi;
-        ec.sat_u8 = a.rq.tlo == 0.f;
+        // the reference arithmetic's constants: only the cold pass uses them, which rebuilds them from the launch
+        // arguments instead of keeping them in registers through the hot loop
+        auto make_exact = [&]() {
+            EpiExact ex;
+            ex.sy1 = a.rq.sy; ex.zy1 = (float)a.rq.zy;
+            ex.lo1 = fmaxf(a.rq.tlo, (float)a.rq.clo); ex.hi1 = fminf(a.rq.thi, (float)a.rq.chi);
+            ex.fused = fused; ex.res_u8 = a.res_u8; ex.zr = (float)a.res_zp; ex.sr = a.res_scale;
+            ex.sy2 = a.rq2.sy; ex.zy2 = (float)a.rq2.zy;
+            ex.lo2 = fmaxf(a.rq2.tlo, (float)a.rq2.clo); ex.hi2 = fminf(a.rq2.thi, (float)a.rq2.chi);
+            return ex;
+        };
+        const float lo1 = fmaxf(a.rq.tlo, (float)a.rq.clo), hi1 = fminf(a.rq.thi, (float)a.rq.chi), zy1 = (float)a.rq.zy;
+        // how the hot path ends (warp-uniform, fixed for the launch)
+        const int kind = use_lut ? EPI_LUT
+                       : (lo1 == a.rq.tlo && hi1 == a.rq.thi) ? (a.rq.tlo == 0.f ? EPI_SAT_U8 : EPI_SAT_S8) : EPI_CLAMP;
+        const uint32_t lut_addr = smem_u32(s_lut);
         int cur_n0 = -1;
-        int it = 0;
-        int ub = 0; uint32_t uph = 0;                        // operand-buffer position (kept without divisions)
-        // this warp's staging buffer: [32 rows][W = eg * UW / 4 bytes], laid out as the TMA store's swizzle of that width
+        // this warp's staging buffers: [32 rows][W = eg * UW / 4 bytes] each, laid out as the TMA store's swizzle of that
+        // width.  With two of them (a.nstg == 2) a unit's store is still reading one buffer while the next unit is
+        // written into the other, so the warp never waits for a store it has only just issued.
         constexpr uint32_t W = (uint32_t)EG * (UW / 4);
-        const uint32_t st_base = smem_u32(s_io) + (uint32_t)ew * (32u * W);
-        const uint32_t st_row = st_base + (uint32_t)lane * W;
+        const uint32_t st_base0 = smem_u32(s_io) + (uint32_t)ew * (32u * W);
+        const uint32_t st_flip = a.nstg == 2 ? (uint32_t)EG * (uint32_t)IO_BYTES : 0u;     // distance to the second buffer
         const uint32_t st_sw = W == 64 ? (uint32_t)((lane >> 1) & 3) : (W == 32 ? (uint32_t)((lane >> 2) & 1) : 0u);
         bool dead = false;
         auto stage_constants = [&](int n0) {
@@ -850,112 +876,141 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         // groups only exist with a single n-tile: its constants are staged once, by all warps, before any warp could
         // find itself without a tile
         if (eg > 1) stage_constants(0);
-        for (int t = blockIdx.x; t < ntiles; t += gridDim.x, ++it) {
-            if ((it & (eg - 1)) != grp) continue;
-            const int n0 = (t % ntn) * BN;
-            const int tm = t / ntn;
-            const long long m0 = (long long)tm * a.tile_rows;
-            const int buf = it & ((1 << NACC_LOG2) - 1);
-            if (n0 != cur_n0) stage_constants(n0);
-            if (!dead && !mbar_wait(&acc_full[buf], ((uint32_t)it >> NACC_LOG2) & 1u)) { atomicExch(&g_tc_status, 3); dead = true; }
-            tc_fence_after();
-            const long long m = m0 + row;
-            const bool mvalid = row < a.tile_rows && m < a.M;
-            // class of this pixel's rectangle of in-image taps
-            int cls = 0;
-            if (a.need_rect) {
-                const unsigned mu = (unsigned)m;               // M < 2^31
-                const unsigned qd = mu / (unsigned)a.OW;
-                const int ox = (int)(mu - qd * (unsigned)a.OW);
-                const int oy = (int)(qd % (unsigned)a.OH);
-                const int iy = oy * a.sh - a.pt, ix = ox * a.sw - a.pl;
-                // first in-image tap, one past the last in-image tap
-                int ky0 = iy < 0 ? (-iy + a.dh - 1) / a.dh : 0;
-                int ky1 = iy >= a.H ? 0 : min(a.KH, (a.H - 1 - iy) / a.dh + 1);
-                int kx0 = ix < 0 ? (-ix + a.dw - 1) / a.dw : 0;
-                int kx1 = ix >= a.W ? 0 : min(a.KW, (a.W - 1 - ix) / a.dw + 1);
-                ky0 = min(ky0, a.KH); kx0 = min(kx0, a.KW);
-                ky1 = max(ky1, ky0);  kx1 = max(kx1, kx0);
-                cls = mvalid ? a.ycls[ky0 * 16 + ky1] * a.ncx + a.xcls[kx0 * 16 + kx1] : 0;
-            }
-            const int32_t* corr_row = s_cc + cls * BN;
-            const uint32_t a_m = smem_u32(s_m), a_b = smem_u32(s_bterm), a_cc = smem_u32(corr_row);
-            const uint32_t tacc = tmem_base + (uint32_t)(buf * BN) + ((uint32_t)(quad * 32) << 16);
-            // units in which this warp has real columns (a prefix: the last n-tile may reach beyond OC)
-            const int nact = ((a.debug & 4) && !fused) ? 0 : min(UNITS, max(0, (a.OC - n0 - part * (int)W + UW - 1) / UW));
-            #pragma unroll 1
-            for (int us = 0; us < nact; ++us) {
-                const uint32_t res_row = smem_u32(s_io + (size_t)(1 + ub) * IO_BYTES + row * UW);    // (fused: eg == 1)
-                const int colw = us * UW + part * (int)W;      // first column of this warp in this unit
+        // The tile loop exists once per way the hot path ends (KIND, fixed for the launch), chosen by one switch below, so
+        // that the per-chunk code is straight-line.
+        auto run_tiles = [&](auto kind_tag) {
+            constexpr int KIND = decltype(kind_tag)::value;
+            int it = 0;
+            int ub = 0; uint32_t uph = 0;                    // operand-buffer position (kept without divisions)
+            uint32_t st_base = st_base0;
+            for (int t = blockIdx.x; t < ntiles; t += gridDim.x, ++it) {
+                if ((it & (eg - 1)) != grp) continue;
+                const int n0 = (t % ntn) * BN;
+                const int tm = t / ntn;
+                const long long m0 = (long long)tm * a.tile_rows;
+                const int buf = it & ((1 << NACC_LOG2) - 1);
+                if (n0 != cur_n0) stage_constants(n0);
+                if (!dead && !mbar_wait(&acc_full[buf], ((uint32_t)it >> NACC_LOG2) & 1u, a.wait_limit)) { atomicExch(&g_tc_status, 3); dead = true; }
+                tc_fence_after();
+                const long long m = m0 + row;
+                const bool mvalid = row < a.tile_rows && m < a.M;
+                // class of this pixel's rectangle of in-image taps
+                int cls = 0;
+                if (a.need_rect) {
+                    const unsigned mu = (unsigned)m;               // M < 2^31
+                    const unsigned qd = mu / (unsigned)a.OW;
+                    const int ox = (int)(mu - qd * (unsigned)a.OW);
+                    const int oy = (int)(qd % (unsigned)a.OH);
+                    const int iy = oy * a.sh - a.pt, ix = ox * a.sw - a.pl;
+                    // first in-image tap, one past the last in-image tap
+                    int ky0 = iy < 0 ? (-iy + a.dh - 1) / a.dh : 0;
+                    int ky1 = iy >= a.H ? 0 : min(a.KH, (a.H - 1 - iy) / a.dh + 1);
+                    int kx0 = ix < 0 ? (-ix + a.dw - 1) / a.dw : 0;
+                    int kx1 = ix >= a.W ? 0 : min(a.KW, (a.W - 1 - ix) / a.dw + 1);
+                    ky0 = min(ky0, a.KH); kx0 = min(kx0, a.KW);
+                    ky1 = max(ky1, ky0);  kx1 = max(kx1, kx0);
+                    cls = mvalid ? a.ycls[ky0 * 16 + ky1] * a.ncx + a.xcls[kx0 * 16 + kx1] : 0;
+                }
+                const int32_t* corr_row = s_cc + cls * BN;
+                const uint32_t a_m = smem_u32(s_m), a_b = smem_u32(s_bterm), a_cc = smem_u32(corr_row);
+                const uint32_t tacc = tmem_base + (uint32_t)(buf * BN) + ((uint32_t)(quad * 32) << 16);
+                // units in which this warp has real columns (a prefix: the last n-tile may reach beyond OC)
+                const int nact = min(UNITS, max(0, (a.OC - n0 - part * (int)W + UW - 1) / UW));
                 #pragma unroll 1
-                for (int sp = 0; sp < EG; ++sp) {              // a quarter of the unit's columns at a time
-                    const int cols = colw + sp * (UW / 4);
-                    uint32_t r[CPW][16];
-                    #pragma unroll
-                    for (int k = 0; k < CPW; ++k) tc_ld16_issue(tacc + (uint32_t)(cols + k * 16), r[k]);
-                    #pragma unroll
-                    for (int k = 0; k < CPW; ++k) tc_ld16_wait(r[k]);
-                    if (sp == 0) {
-                        if (fused && !dead && !mbar_wait(&io_full[ub], uph)) { atomicExch(&g_tc_status, 5); dead = true; }
-                        // this warp's previous store has been read out of its staging buffer
-                        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-                        __syncwarp();
+                for (int us = 0; us < nact; ++us) {
+                    const int colw = us * UW + part * (int)W;      // first column of this warp in this unit
+                    const uint32_t res_row = smem_u32(s_io + (size_t)(NSTG_UNITS + ub) * IO_BYTES + row * UW);    // (fused: eg == 1)
+                    // The warp's NCH chunks of 16 columns go through two register sets that take turns: the loads of
+                    // the first two are issued before the unit's waits; a set is reloaded (chunk + 2) as soon as its
+                    // chunk has been computed.  (tcgen05.wait::ld waits for every load the thread has issued.)
+                    uint32_t r[2][16];
+                    tc_ld16_issue(tacc + (uint32_t)colw, r[0]);
+                    if (NCH > 1) tc_ld16_issue(tacc + (uint32_t)(colw + 16), r[1]);
+                    if (fused && !dead && !mbar_wait(&io_full[ub], uph, a.wait_limit)) { atomicExch(&g_tc_status, 5); dead = true; }
+                    // the store that last used this staging buffer has read it out
+                    if (lane == 0) {
+                        if (st_flip) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                        else         asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
                     }
-                    uint32_t fixmask = 0;                          // chunks the cold pass has to redo (warp-uniform)
+                    __syncwarp();
+                    const uint32_t st_row = st_base + (uint32_t)lane * W;
+                    float dm[NCH];
                     #pragma unroll
-                    for (int k = 0; k < CPW; ++k) {
-                        const int col0 = cols + k * 16;
-                        const EpiAddr ad = {a_m + col0 * 4, a_b + col0 * 4, a_cc + col0 * 4};
-                        float dmax = always_fix ? 1.0f : 0.0f;
-                        uint4 outv;
-                        if (use_lut)     outv = epi_chunk<true, true>(r[k], lds128(res_row + ((((uint32_t)(part * CPW + k)) ^ sw_x) << 4)), ad, ec, dmax);
-                        else if (ec.sat) outv = epi_chunk<false, true>(r[k], make_uint4(0, 0, 0, 0), ad, ec, dmax);
-                        else             outv = epi_chunk<false, false>(r[k], make_uint4(0, 0, 0, 0), ad, ec, dmax);
-                        // an exact half (the reference rounds it away from zero), a value beyond the rounding constant,
-                        // or no table: the chunk is left to the cold pass
-                        const bool fix = __any_sync(0xffffffffu, dmax >= 0.5f);
-                        if (!fix) sts128(st_row + (((uint32_t)(sp * CPW + k) ^ st_sw) << 4), outv);
-                        fixmask |= fix ? (1u << k) : 0u;
+                    for (int j = 0; j < NCH; ++j) {
+                        if ((j & 1) == 0) {
+                            tc_ld16_wait(r[0]);
+                            if (j + 1 < NCH) tc_ld16_wait(r[1]);
+                        }
+                        const int col0 = colw + j * 16;
+                        const TabShared ad = {a_m + col0 * 4, a_b + col0 * 4, a_cc + col0 * 4};
+                        const uint4 rv = KIND == EPI_LUT ? lds128(res_row + ((((uint32_t)(part * NCH + j)) ^ sw_x) << 4)) : make_uint4(0, 0, 0, 0);
+                        dm[j] = 0.0f;
+                        const uint4 outv = epi_chunk<KIND>(r[j & 1], rv, ad, a.ep, lut_addr, dm[j]);
+                        sts128(st_row + (((uint32_t)j ^ st_sw) << 4), outv);
+                        if (j + 2 < NCH) tc_ld16_issue(tacc + (uint32_t)(colw + (j + 2) * 16), r[j & 1]);
                     }
-                    if (fixmask != 0 || dump_acc) {
+                    float dall = dm[0];
+                    #pragma unroll
+                    for (int j = 1; j < NCH; ++j) dall = fmaxf(dall, dm[j]);
+                    // an exact half (which the reference rounds away from zero) or a value beyond the rounding constant,
+                    // no usable table, or the accumulator dump of the tests: the cold pass redoes those chunks from a
+                    // second read of the accumulators
+                    if (__any_sync(0xffffffffu, dall >= TC_FIX_THRESHOLD) || always_fix || dump_acc) {
+                        const EpiExact ex = make_exact();
                         #pragma unroll 1
-                        for (int k = 0; k < CPW; ++k) {
-                            const int col0 = cols + k * 16;
-                            const bool fix = (fixmask >> k) & 1u;
+                        for (int j = 0; j < NCH; ++j) {
+                            float dj = dm[0];
+                            #pragma unroll
+                            for (int jj = 1; jj < NCH; ++jj) dj = jj == j ? dm[jj] : dj;
+                            const bool fix = always_fix || __any_sync(0xffffffffu, dj >= TC_FIX_THRESHOLD);
                             if (!fix && !dump_acc) continue;
-                            epi_cold(tacc + (uint32_t)col0, res_row + ((((uint32_t)(part * CPW + k)) ^ sw_x) << 4),
-                                     st_row + (((uint32_t)(sp * CPW + k) ^ st_sw) << 4), a_m + col0 * 4, a_b + col0 * 4, a_cc + col0 * 4, ex, fix,
+                            const int col0 = colw + j * 16;
+                            uint32_t rr[16];
+                            tc_ld16(tacc + (uint32_t)col0, rr);
+                            epi_cold(rr, res_row + ((((uint32_t)(part * NCH + j)) ^ sw_x) << 4), st_row + (((uint32_t)j ^ st_sw) << 4),
+                                     a_m + col0 * 4, a_b + col0 * 4, a_cc + col0 * 4, ex, fix,
                                      (dump_acc && mvalid && n0 + col0 < a.OC) ? a.acc_out + m * a.OC + n0 + col0 : nullptr);
                         }
                     }
+                    if (fused) {
+                        // this warp has finished reading the other operand's unit
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&io_empty[ub]);
+                        if (++ub == NIO) { ub = 0; uph ^= 1u; }
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the TMA store
+                    __syncwarp();
+                    if (lane == 0) {
+                        const int row0 = quad * 32;
+                        if (row0 < a.tile_rows && m0 + row0 < a.M)
+                            tma_store_3d(&tmY, st_base, n0 + colw, a.im2col == 2 ? row0 : (int)(m0 + row0), a.im2col == 2 ? tm : 0);
+                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    }
+                    st_base = st_base == st_base0 ? st_base0 + st_flip : st_base0;
                 }
                 if (fused) {
-                    // this warp has finished reading the other operand's unit
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&io_empty[ub]);
-                    if (++ub == NIO) { ub = 0; uph ^= 1u; }
+                    // padding-only units: nothing to read, but the operand buffers still want this warp's release.  The
+                    // warp first waits for the unit's load like everybody else: an arrival that came before the buffer's
+                    // previous use was complete would be counted towards that use and release the buffer under a slower
+                    // warp.
+                    for (int us = nact; us < UNITS; ++us) {
+                        if (!dead && !mbar_wait(&io_full[ub], uph, a.wait_limit)) { atomicExch(&g_tc_status, 5); dead = true; }
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&io_empty[ub]);
+                        if (++ub == NIO) { ub = 0; uph ^= 1u; }
+                    }
                 }
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the TMA store
+                // this warp has finished reading the accumulator buffer
+                tc_fence_before();
                 __syncwarp();
-                if (lane == 0) {
-                    const int row0 = quad * 32;
-                    if (row0 < a.tile_rows && m0 + row0 < a.M)
-                        tma_store_3d(&tmY, st_base, n0 + colw, a.im2col == 2 ? row0 : (int)(m0 + row0), a.im2col == 2 ? tm : 0);
-                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-                }
+                if (lane == 0) mbar_arrive(&acc_empty[buf]);
             }
-            if (fused) {
-                // padding-only units: nothing to read, but the operand buffers still want this warp's release
-                for (int us = nact; us < UNITS; ++us) {
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&io_empty[ub]);
-                    if (++ub == NIO) { ub = 0; uph ^= 1u; }
-                }
-            }
-            // this warp has finished reading the accumulator buffer
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&acc_empty[buf]);
+        };
+        switch (kind) {
+            case EPI_LUT:    run_tiles(std::integral_constant<int, EPI_LUT>{}); break;
+            case EPI_SAT_U8: run_tiles(std::integral_constant<int, EPI_SAT_U8>{}); break;
+            case EPI_SAT_S8: run_tiles(std::integral_constant<int, EPI_SAT_S8>{}); break;
+            default:         run_tiles(std::integral_constant<int, EPI_CLAMP>{}); break;
         }
         // shared memory may go once the last store has read it; its global writes complete with the kernel
         if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
@@ -1124,13 +1179,25 @@ static bool load_driver_entry_points()
     return true;
 }
 
+// State that CUDA keeps per device (SM count, the opt-in shared-memory size of a kernel) is cached per device: a
+// process may drive several GPUs, one network and one host thread each.
+constexpr int TC_MAX_DEVICES = 64;
+
+static int current_device()
+{
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= TC_MAX_DEVICES) dev = 0;
+    return dev;
+}
+
 static int sm_count()
 {
-    static int n = 0;
+    static std::atomic<int> cached[TC_MAX_DEVICES];
+    const int dev = current_device();
+    int n = cached[dev].load(std::memory_order_relaxed);
     if (n == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
         if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev].store(n, std::memory_order_relaxed);
     }
     return n;
 }
@@ -1142,8 +1209,6 @@ static int sm_count()
 static int pick_bn(int oc, long long ntm)
 {
     const long long sms = sm_count();
-    static const int forced = getenv("B200K_TC_FORCE_BN") ? atoi(getenv("B200K_TC_FORCE_BN")) : 0;    // measurement aid
-    if (forced == 64 || forced == 128 || forced == 256) return forced;
     int best = 64;
     long long best_cost = -1;
     for (int bn = 64; bn <= 256; bn *= 2) {
@@ -1194,6 +1259,25 @@ static TapClasses tap_classes(const b200k_conv2d_params* p)
     return t;
 }
 
+// Zero points must lie in their element type's range (the constant -zw tiles and the padding fill are 8-bit values),
+// and the output scale in a range where its reciprocal is an ordinary number.
+static bool quantisation_in_range(const b200k_conv2d_params* p)
+{
+    int lo, hi;
+    type_range(p->x.dtype, lo, hi);
+    if (p->x.zero_point < lo || p->x.zero_point > hi) return false;
+    type_range(p->w.dtype, lo, hi);
+    if (!p->w.scales && (p->w.zero_point < lo || p->w.zero_point > hi)) return false;
+    type_range(p->y.dtype, lo, hi);
+    if (p->y.zero_point < lo || p->y.zero_point > hi) return false;
+    if (!(p->y.scale > 1e-30f && p->y.scale < 1e30f)) return false;
+    if (p->add_operand.data) {
+        type_range(p->add_out.dtype, lo, hi);
+        if (p->add_out.zero_point < lo || p->add_out.zero_point > hi) return false;
+    }
+    return true;
+}
+
 static bool row_window_eligible(const b200k_conv2d_params* p)
 {
     const RowPlan r = row_window_plan(p);
@@ -1201,6 +1285,7 @@ static bool row_window_eligible(const b200k_conv2d_params* p)
     const void* outp = p->add_operand.data ? p->add_out.data : p->y.data;
     if (!p->x.data || !p->w.data || !outp) return false;
     if (!is_q8(p->x.dtype) || !is_q8(p->w.dtype) || !is_q8(p->y.dtype)) return false;
+    if (!quantisation_in_range(p)) return false;
     if ((((uintptr_t)p->scratch | (uintptr_t)p->packed | (uintptr_t)outp) & 15) != 0) return false;
     if (p->add_operand.data && ((((uintptr_t)p->add_operand.data) & 15) != 0)) return false;
     if ((long long)p->n * p->oh > (1ll << 30) || (long long)p->n * p->oh * p->ow > (1ll << 31) - TC_BM) return false;
@@ -1213,6 +1298,7 @@ bool conv_tc_eligible(const b200k_conv2d_params* p)
     const void* outp = p->add_operand.data ? p->add_out.data : p->y.data;
     if (!p->x.data || !p->w.data || !outp) return false;
     if (!is_q8(p->x.dtype) || !is_q8(p->w.dtype) || !is_q8(p->y.dtype)) return false;
+    if (!quantisation_in_range(p)) return false;
     if (p->add_operand.data && ((((uintptr_t)p->add_operand.data | (uintptr_t)p->add_out.data) & 15) != 0)) return false;
     if (p->c % 16 != 0 || p->oc % 16 != 0) return false;               // TMA: 16-byte pixel and row strides
     if (p->w.zero_point != 0 && p->w.scales) return false;             // per-axis weights are symmetric
@@ -1250,8 +1336,10 @@ static int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUten
     size_t rest = 1024 + L::CONST_BYTES + (size_t)a.ncls * BN * 4 + (size_t)(EG + a.nio) * L::IO_BYTES + (a.add_lut ? TC_LUT_BYTES : 0) + 256 +
                   (size_t)a.nslices * 16 +
                   (size_t)a.nzw * L::B_BYTES;
-    // a third buffer for the fused Add's other operand (its loads then run a whole unit ahead of the epilogue) when the
-    // ring keeps at least three stages
+    // a second staging buffer per epilogue warp, then a third buffer for the fused Add's other operand (its loads then
+    // run a whole unit ahead of the epilogue), each when the ring keeps at least three stages
+    a2.nstg = 1;
+    if (rest + (size_t)EG * L::IO_BYTES + 3 * L::STAGE_BYTES <= budget) { a2.nstg = 2; rest += (size_t)EG * L::IO_BYTES; }
     if (a.nio == 2 && rest + L::IO_BYTES + 3 * L::STAGE_BYTES <= budget) { a2.nio = 3; rest += L::IO_BYTES; }
     B200K_REQUIRE(rest + 2 * L::STAGE_BYTES <= budget, B200K_E_TOOBIG, "conv2d_q8: shared memory exhausted (%zu bytes of tables)", rest);
     // One n-tile and a weight tile of at most 64 KiB over all of K: keep it in shared memory for the whole launch, so
@@ -1280,10 +1368,14 @@ static int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUten
     if (a2.bstat) a2.stage_tx = (uint32_t)(a.stage_tx - L::B_BYTES);
     const size_t smem = fixed + (size_t)stages * group * stride;
     auto kern = conv_tc_kernel<BN, SWZ, EG>;
-    static size_t configured = 0;                      // per instantiation: largest dynamic smem size set so far
-    if (smem > configured) {
+    // per instantiation and device: the largest dynamic shared-memory size opted into so far (a racing second thread
+    // at worst repeats the call)
+    static std::atomic<size_t> configured[TC_MAX_DEVICES];
+    const int dev = current_device();
+    if (smem > configured[dev].load(std::memory_order_acquire)) {
         B200K_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        configured = smem;
+        size_t seen = configured[dev].load(std::memory_order_relaxed);
+        while (seen < smem && !configured[dev].compare_exchange_weak(seen, smem, std::memory_order_release)) {}
     }
     const long long tiles = (long long)a.ntn * a.ntm;
     const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
@@ -1315,9 +1407,10 @@ int launch_conv_tc(const b200k_conv2d_params* p, cudaStream_t stream, int kvalid
     a.zx = p->x.zero_point;
     a.kvalid_c = kvalid_c > 0 ? kvalid_c : p->c;
     a.zw = p->w.scales ? 0 : p->w.zero_point;
-    a.nzw = a.zw == 0 ? 0 : (a.zw <= 128 ? 1 : 2);
-    a.zw_val[0] = -(a.zw < 128 ? a.zw : 128);
-    a.zw_val[1] = -(a.zw - 128);
+    // -zw as one int8 tile value, or as the sum of two when it does not fit (zw > 128, or zw = -128 whose negative is +128)
+    a.nzw = a.zw == 0 ? 0 : ((a.zw <= 128 && a.zw > -128) ? 1 : 2);
+    a.zw_val[0] = a.nzw == 2 ? (a.zw > 0 ? -128 : 64) : -a.zw;
+    a.zw_val[1] = a.nzw == 2 ? -a.zw - a.zw_val[0] : 0;
     a.N = p->n; a.H = p->h; a.W = p->wd; a.C = p->c; a.OH = p->oh; a.OW = p->ow; a.OC = p->oc;
     a.KH = p->kh; a.KW = p->kw; a.sh = p->stride_h; a.sw = p->stride_w; a.pt = p->pad_top; a.pl = p->pad_left;
     a.dh = p->dil_h; a.dw = p->dil_w;
@@ -1349,6 +1442,20 @@ int launch_conv_tc(const b200k_conv2d_params* p, cudaStream_t stream, int kvalid
     a.res = fa.res; a.res_scale = fa.res_scale; a.res_zp = fa.res_zp; a.res_u8 = fa.res_u8;
     a.rq2 = fa.out;
     a.inv_sy = rn_reciprocal(p->y.scale);
+    {
+        // t = MAGIC + n comes out of the rounding; adding zoff (an integer below 2^24, so exact) gives: with the
+        // fused-add table the table's row index n + zy - type minimum, a byte in 0..255; with the type's own saturation
+        // the result n + zy itself; with an explicit clamp the biased result MAGIC + n + zy, clamped in that domain
+        const float zy1 = (float)a.rq.zy;
+        const float lo1 = fmaxf(a.rq.tlo, (float)a.rq.clo), hi1 = fminf(a.rq.thi, (float)a.rq.chi);
+        auto two = [](float v) { return make_float2(v, v); };
+        a.ep.inv2 = two(a.inv_sy); a.ep.nsy2 = two(-a.rq.sy); a.ep.magic2 = two(TC_MAGIC); a.ep.zero2 = two(0.f); a.ep.neg2 = two(-1.f);
+        a.ep.zoff_lut2 = two((zy1 - a.rq.tlo) - TC_MAGIC);
+        a.ep.zoff_sat2 = two(zy1 - TC_MAGIC);
+        a.ep.zoff_clamp2 = two(zy1);
+        a.ep.lo = TC_MAGIC + lo1;
+        a.ep.hi = TC_MAGIC + hi1;
+    }
     // b200k_conv2d_pack builds the fused-add table when it is given the add operand; the kernel checks its tag and
     // falls back to the reference arithmetic (slow) when the table was made for other parameters
     a.add_lut = (fa.res && p->packed) ? (const uint8_t*)p->packed + add_lut_offset(p->oc, p->kh, p->kw, p->c) : nullptr;
@@ -1366,9 +1473,9 @@ int launch_conv_tc(const b200k_conv2d_params* p, cudaStream_t stream, int kvalid
         memcpy(a.ypair, tc.ypair, 16); memcpy(a.xpair, tc.xpair, 16);
         memcpy(a.ycls, tc.ycls, 256);  memcpy(a.xcls, tc.xcls, 256);
     }
-    // Measurement aid (results are wrong when set): a bit mask that switches off the MMAs, the TMA loads or the epilogue work.
-    static const int debug_mode = getenv("B200K_TC_DEBUG") ? atoi(getenv("B200K_TC_DEBUG")) : 0;
-    a.debug = debug_mode;
+    // bounded waits: about two seconds, or the caller's self-test limit (clock64 runs at no more than 2 GHz)
+    a.skip_loads = p->selftest_us > 0 ? 1 : 0;
+    a.wait_limit = p->selftest_us > 0 ? (long long)p->selftest_us * 2000ll : TC_WAIT_LIMIT_CYCLES;
 
     const int bn = pick_bn(p->oc, a.ntm);
     a.ntn = (p->oc + bn - 1) / bn;
@@ -1448,11 +1555,10 @@ int launch_conv_tc(const b200k_conv2d_params* p, cudaStream_t stream, int kvalid
         // Epilogue groups: with one n-tile and no fused Add, 256 / bn (at most 4) tiles are in the epilogue at once, each
         // on its own accumulator buffer and a quarter (half) of the epilogue warps.  (Measured on ResNet-50's layers at
         // batch 256: 1x1 and 3x3 convolutions with 64 or 128 output channels run 10 - 30 % faster this way.)
-        static const bool no_groups = getenv("B200K_TC_NOGROUPS") != nullptr;     // measurement aid
-        a.eg = (a.ntn == 1 && !fa.res && !row_mode && !no_groups) ? (bn == 64 ? 4 : (bn == 128 ? 2 : 1)) : 1;
+        a.eg = (a.ntn == 1 && !fa.res && !row_mode) ? (bn == 64 ? 4 : (bn == 128 ? 2 : 1)) : 1;
         // row-window mode (network stems): two groups (0.41 -> 0.32 ms for ResNet-50's stem at batch 256; four were slower
         // than one there)
-        if (row_mode && !no_groups && a.ntn == 1 && !fa.res && bn == 64) a.eg = 2;
+        if (row_mode && a.ntn == 1 && !fa.res && bn == 64) a.eg = 2;
         // stores: one epilogue warp's 32 rows x (eg * uw / 4) columns
         const int stw = a.eg * uw / 4;
         cuuint32_t box_st[3] = {(cuuint32_t)stw, 32, 1};
@@ -1500,6 +1606,10 @@ size_t tc_scratch_bytes(const b200k_conv2d_params* p)
     return r.ok ? r.scratch_bytes : 0;
 }
 
+// The kernels below are launched the plain way (full stream dependency, no programmatic dependent launch) on purpose:
+// conv_tc_kernel reads the prefix table, the re-packed weights and the fused-add table BEFORE its griddepcontrol.wait,
+// which is only sound while whatever wrote them has completed when the convolution's grid starts.  A caller that
+// packs and convolves back to back on one stream (b200k_conv2d_q8_static does) relies on that.
 int tc_pack(const b200k_conv2d_params* p, void* packed, cudaStream_t stream)
 {
     B200K_REQUIRE(p && packed, B200K_E_INVALID, "conv2d_pack: null argument");

@@ -4,6 +4,7 @@
 // (attention-style batched products, unusual weight layouts); the large FullyConnected / 1x1
 // convolution GEMMs go through the implicit-GEMM kernels.
 #include <string.h>
+#include <atomic>
 #include "common.cuh"
 
 namespace b200k {
@@ -209,11 +210,14 @@ static int launch_fc_rows(const b200k_fc_params* p, cudaStream_t stream)
     const bool xu = p->x.dtype == B200K_U8, wu = p->w.dtype == B200K_U8;
     #define B200K_FC_ROWS(XU, WU, RB)                                                                                  \
         do {                                                                                                           \
-            static bool configured = false;                                                                            \
-            if (!configured) {                                                                                         \
+            /* the opt-in is per device: one flag per device index */                                                  \
+            static std::atomic<bool> configured[64];                                                                   \
+            int dev_ = 0;                                                                                              \
+            if (cudaGetDevice(&dev_) != cudaSuccess || dev_ < 0 || dev_ >= 64) dev_ = 0;                               \
+            if (!configured[dev_].load(std::memory_order_acquire)) {                                                   \
                 B200K_CUDA(cudaFuncSetAttribute(fc_rows_kernel<XU, WU, RB>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                                                 RB * FC_KT));                                                          \
-                configured = true;                                                                                     \
+                configured[dev_].store(true, std::memory_order_release);                                               \
             }                                                                                                          \
             const dim3 grid(div_up(p->n, FC_COLS), div_up(p->m, RB), 1);                                               \
             launch_pdl(fc_rows_kernel<XU, WU, RB>, grid, dim3(32 * FC_COLS), (size_t)RB * kt, stream, a);              \

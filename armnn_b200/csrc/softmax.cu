@@ -12,6 +12,7 @@ namespace b200k {
 struct SoftmaxArgs { QView x, y; int outer, axis, inner; float beta; };
 
 constexpr int SM_THREADS = 128;
+constexpr int SM_MAX_AXIS = (48 * 1024 - 64) / 4;        // dynamic floats + the static words below stay within 48 KiB
 
 __global__ void __launch_bounds__(SM_THREADS) softmax_kernel(const SoftmaxArgs a)
 {
@@ -62,8 +63,10 @@ extern "C" int b200k_softmax_q8(const b200k_softmax_params* p, void* stream)
     B200K_REQUIRE(p->x.data && p->y.data, B200K_E_INVALID, "softmax_q8: null tensor pointer");
     B200K_REQUIRE(p->outer > 0 && p->axis_size > 0 && p->inner > 0, B200K_E_INVALID, "softmax_q8: bad shape");
     B200K_REQUIRE(p->x.dtype != B200K_S32 && p->y.dtype != B200K_S32, B200K_E_UNSUPPORTED, "softmax_q8: Signed32 not supported");
-    B200K_REQUIRE(p->axis_size <= 12288, B200K_E_TOOBIG, "softmax_q8: axis length %d exceeds the 12288 this kernel stages in shared memory",
-                  p->axis_size);
+    // one float per element of the axis in dynamic shared memory, next to the kernel's few static words, within the
+    // 48 KiB every launch may use without opting in
+    B200K_REQUIRE(p->axis_size <= SM_MAX_AXIS, B200K_E_TOOBIG, "softmax_q8: axis length %d exceeds the %d this kernel stages in shared memory",
+                  p->axis_size, SM_MAX_AXIS);
     SoftmaxArgs a;
     a.x = make_view(p->x); a.y = make_view(p->y);
     a.outer = p->outer; a.axis = p->axis_size; a.inner = p->inner; a.beta = p->beta;

@@ -6,8 +6,7 @@ import os
 from . import _abi
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-# B200K_LIBRARY selects another build of the same library (A/B comparisons of kernel variants)
-LIB_PATH = os.environ.get("B200K_LIBRARY") or os.path.join(_HERE, "libb200k.so")
+LIB_PATH = os.path.join(_HERE, "libb200k.so")
 _lib = None
 
 

@@ -108,6 +108,12 @@ typedef struct {
      * small: such convolutions run on the CUDA-core kernel. */
     void* scratch;
     size_t scratch_bytes;
+    /* Self-test of the bounded device-side waits of the tcgen05 kernel; 0 (the normal case) switches it off.  With
+     * selftest_us > 0 the kernel's TMA producers issue no loads and every device-side wait gives up after about
+     * selftest_us microseconds: the launch ends by itself, its output is meaningless, and the next
+     * b200k_poll_status() returns B200K_E_TIMEOUT.  This is the failure a broken pipeline would produce, injected
+     * from the host; nothing faults, traps or spins without a limit.  Ignored by the CUDA-core kernels. */
+    int32_t selftest_us;
 } b200k_conv2d_params;
 
 int b200k_conv2d_q8(const b200k_conv2d_params* p, void* stream);

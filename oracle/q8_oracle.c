@@ -7,7 +7,7 @@
  * Parity is pinned: tests/test_oracle_*.py check every function here against (i) known-answer
  * vectors transcribed from the reference's own layer tests (tests/golden/ref_layer_tests.json)
  * and (ii) outputs of the real CpuRef workloads compiled from the reference sources
- * (oracle/_ref/, fixtures under tests/golden/ made by tests/golden/make_cpuref_fixtures.py).
+ * (oracle/_ref/, driven by tests/test_oracle_vs_cpuref.py).
  *
  * Two kinds of restatement, because CpuRef computes everything in fp32:
  *  - contractions (conv / depthwise / fully-connected / batch-matmul): CpuRef sums

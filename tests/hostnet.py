@@ -35,13 +35,20 @@ class OracleNetwork(GraphProgram):
     def _view(self, tensor, shape):
         return tensor.reshape(shape)
 
-    def run(self, inputs, keep=None):
+    def run(self, inputs, keep=None, force=None):
         """inputs: {binding id: ndarray}.  Returns {binding id: ndarray}; `keep`, when a dict, receives
-        every intermediate tensor keyed by producing layer name (and output index)."""
+        every intermediate tensor keyed by producing layer name (and output index).  `force`, when a dict
+        {(workload index, input index): ndarray}, overwrites that workload's input tensor just before it runs
+        (teacher forcing of single layers with another executor's intermediate results)."""
         for bid, arr in inputs.items():
             dst = self._dev(self.inputs[bid])
             dst[...] = np.asarray(arr).reshape(dst.shape).view(dst.dtype)
-        for layer, entry, params in self.workloads:
+        for wi, (layer, entry, params) in enumerate(self.workloads):
+            if force:
+                for ii, s in enumerate(layer.inputs):
+                    if (wi, ii) in force:
+                        dst = self._dev(s.source)
+                        dst[...] = np.asarray(force[(wi, ii)]).reshape(dst.shape).view(dst.dtype)
             rc = getattr(oracle(), "oracle_" + entry)(C.byref(params))
             assert rc == 0, "oracle_%s failed for %s" % (entry, layer.name)
             if keep is not None:

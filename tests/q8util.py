@@ -246,7 +246,7 @@ class ConvCase:
 
 def random_conv_case(seed, n, h, wd, c, oc, kh, kw, stride=(1, 1), pad=(0, 0, 0, 0), dil=(1, 1), act=(0, 0., 0.),
                      depthwise=False, x_dtype=_abi.S8, w_dtype=_abi.S8, y_dtype=_abi.S8, per_axis=True,
-                     x_q=(0.02, -3), y_scale=None, y_zp=None, bias=True, depth_multiplier=1, fused_add=False):
+                     x_q=(0.02, -3), y_scale=None, y_zp=None, bias=True, depth_multiplier=1, fused_add=False, w_zp=None):
     """Seeded synthetic conv in the style of the benchmark configs: uniform activations over the
     whole type range, weights uniform, per-output-channel scales uniform in [0.001, 0.01], int32 bias
     uniform in [-1000, 1000] with scale sx * sw[c].  The output scale defaults to one that leaves
@@ -259,12 +259,13 @@ def random_conv_case(seed, n, h, wd, c, oc, kh, kw, stride=(1, 1), pad=(0, 0, 0,
         wshape = (1, kh, kw, oc)
     else:
         wshape = (oc, kh, kw, c)
+    # w_zp: an explicit per-tensor weight zero point (QAsymmS8 / QAsymmU8 weights); default 0 for int8, random for uint8
     if w_dtype == _abi.S8:
-        w = rng.integers(-127, 128, size=wshape).astype(np.int8)
-        w_zp = 0
+        w = rng.integers(-128 if w_zp is not None else -127, 128, size=wshape).astype(np.int8)
+        w_zp = 0 if w_zp is None else int(w_zp)
     else:
         w = rng.integers(0, 256, size=wshape).astype(np.uint8)
-        w_zp = int(rng.integers(100, 156))
+        w_zp = int(rng.integers(100, 156)) if w_zp is None else int(w_zp)
     if per_axis and w_dtype == _abi.S8:
         w_scales = rng.uniform(0.001, 0.01, size=oc).astype(np.float32)
         w_q = (1.0, 0)

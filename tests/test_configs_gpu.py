@@ -1,0 +1,171 @@
+"""The benchmark configurations at the sizes they are specified with, on the GPU, against the CPU oracle and the real
+CpuRef.
+
+The oracle cannot push 256 images of 224 x 224 through ResNet-50 in test time, but every operator on this path is
+independent across batch rows (Convolution2d, Pooling2d, Add, FullyConnected and Softmax per image, QLstm per batch
+row: the layer norm runs over one row, LstmUtils.cpp:46-71 of the Arm NN tree), so the full-size GPU run is checked
+on a subset of rows: the oracle runs the batch-1 graph (same seeded weights) on rows {first, middle, last}, and
+every layer's slice of the GPU tensors must equal it bit for bit (softmax: +-1 LSB).  The same rows then go through the
+real CpuRef end to end (free running, 15 s per 224-pixel image): CpuRef sums in fp32, so single layers differ from the
+exact-integer accumulation on rounding ties (+-1 LSB, tests/test_oracle_vs_cpuref.py) and those differences may
+propagate; the test bounds the drift of the class scores and checks the arg-max.
+"""
+import numpy as np
+import pytest
+
+from q8util import _abi, diff_stats, have_cpuref, random_fc_case
+
+pytestmark = pytest.mark.gpu
+
+
+def _load(net):
+    from armnn_b200 import network
+    rt = network.IRuntime.Create(0)
+    opt = network.Optimize(net, ["B200Acc"])
+    return rt, opt, rt.GetLoadedNetwork(rt.LoadNetwork(opt))
+
+
+def _rows_against_oracle(make, batch, image, rows, dtype, seed):
+    """GPU at (batch, image) vs the oracle's batch-1 graph on `rows`: every workload's output slice."""
+    import hostnet
+    from armnn_b200 import network
+    net, info = make(batch, image)
+    rt, opt, ln = _load(net)
+    rng = np.random.default_rng(seed)
+    lo, hi = (0, 256) if dtype == np.uint8 else (-128, 128)
+    x = rng.integers(lo, hi, size=info["input_shape"]).astype(dtype)
+    y = np.zeros(info["output_shape"], dtype)
+    ln.EnqueueWorkload({0: x}, {0: y})
+    net1, _ = make(1, image)
+    on = hostnet.OracleNetwork(network.Optimize(net1, ["B200Acc"]))
+    checked = 0
+    for r in rows:
+        keep = {}
+        want = on.run({0: x[r:r + 1]}, keep)[0]
+        for layer, entry, _ in ln.workloads:
+            got = ln.tensor_of(layer.outputs[0])[r:r + 1].cpu().numpy()
+            ref = keep[layer.name].reshape(got.shape)
+            if entry == "softmax_q8":
+                st = diff_stats(ref, got)
+                assert st["max_abs"] <= 1 and st["mismatch_frac"] <= 0.01, (r, layer.name, st)
+            else:
+                assert np.array_equal(ref, got), (r, layer.name, entry, diff_stats(ref, got))
+            checked += 1
+        assert diff_stats(want, y[r:r + 1])["max_abs"] <= 1
+    assert checked == len(rows) * len(ln.workloads)
+    return make(1, image)[0], x, y          # a fresh, un-optimized batch-1 graph for the CpuRef run
+
+
+def _rows_against_cpuref(net1, x, y, rows, max_drift):
+    """The same rows through the real CpuRef, free running: bounded drift of the scores, equal arg-max wherever CpuRef's
+    own top score leads by more than the drift."""
+    import hostnet
+    ref = hostnet.ArmnnNetwork(net1, "CpuRef")
+    hist = {}
+    for r in rows:
+        want = ref.run({0: x[r:r + 1]})[0].reshape(-1).astype(np.int32)
+        got = y[r].reshape(-1).astype(np.int32)
+        d = np.abs(want - got)
+        for v in d:
+            hist[int(v)] = hist.get(int(v), 0) + 1
+        assert d.max() <= max_drift, (r, int(d.max()))
+        top = np.sort(want)[::-1]
+        if top[0] - top[1] > 2 * max_drift:
+            assert int(np.argmax(want)) == int(np.argmax(got)), r
+    ref.close()
+    print("free-running |GPU - CpuRef| histogram of the class scores over rows %s: %s" % (list(rows), dict(sorted(hist.items()))))
+
+
+def test_resnet50_batch256_224_rows_every_layer_vs_oracle_and_cpuref(built):
+    """BASELINE configuration 4 as specified: batch 256, 224 x 224 (the shape bench.py times)."""
+    from armnn_b200 import configs
+    rows = (0, 127, 255)
+    net1, x, y = _rows_against_oracle(configs.resnet50, 256, 224, rows, np.int8, seed=41)
+    if have_cpuref():
+        _rows_against_cpuref(net1, x, y, rows, max_drift=3)
+
+
+def test_mobilenet_v2_batch64_224_rows_every_layer_vs_oracle_and_cpuref(built):
+    """BASELINE configuration 3 as specified: batch 64, 224 x 224, all QAsymmU8."""
+    from armnn_b200 import configs
+    rows = (0, 31, 63)
+    net1, x, y = _rows_against_oracle(configs.mobilenet_v2, 64, 224, rows, np.uint8, seed=42)
+    if have_cpuref():
+        _rows_against_cpuref(net1, x, y, rows, max_drift=3)
+
+
+@pytest.mark.parametrize("m,k", [(4096, 1024), (256, 4096), (4096, 4096)])
+def test_fc_sweep_large_points_sampled_rows(built, m, k):
+    """BASELINE configuration 2's large points (QAsymmS8 x per-axis QSymmS8, int32 bias): the full GPU output, accumulators
+    and bytes, against the oracle on 32 sampled rows (rows of a FullyConnected are independent)."""
+    from q8util import FcCase
+    case = random_fc_case(7000 + m + k, m, k, k)
+    gy, gacc = case.run_gpu(algo=0)
+    from armnn_b200 import lib
+    lib.check(lib.load_library().b200k_poll_status())
+    rows = np.unique(np.concatenate([[0, 1, 127, 128, m - 1], np.random.default_rng(m * k).integers(0, m, size=27)]))
+    sub = FcCase(case.x[rows], case.w, case.bias, case.x_q, case.w_q, case.y_q, True, case.w_scales, case.b_scale,
+                 case.b_scales, case.act, case.x_dtype, case.w_dtype, case.y_dtype)
+    y, acc = sub.run_oracle()
+    assert np.array_equal(acc, gacc[rows]), diff_stats(acc, gacc[rows])
+    assert np.array_equal(y, gy[rows]), diff_stats(y, gy[rows])
+    # saturation stays low, so the comparison means something
+    assert np.mean((gy == -128) | (gy == 127)) < 0.05
+
+
+def test_qlstm_stack_batch128_200_steps_teacher_forced_and_free_running(built):
+    """BASELINE configuration 5 as specified: 3 stacked QLstm layers, batch 128, 200 timesteps, states fed back on the
+    GPU side by the GPU's own outputs (free running).  The oracle runs a subset of batch rows twice: teacher-forced (every
+    layer of every step gets the GPU's own inputs for those rows, states and the layer below's output alike; the per-step
+    bar of the one-step tests is asserted for each layer) and free running from its own state (the drift against the GPU
+    is reported and bounded)."""
+    import hostnet
+    from armnn_b200 import configs, network
+    B, T = 128, 200
+    rows = np.array([0, 37, 64, 127])
+    net, info = configs.qlstm_stack(batch=B)
+    rt, opt, ln = _load(net)
+    net_s, info_s = configs.qlstm_stack(batch=len(rows))
+    on_tf = hostnet.OracleNetwork(network.Optimize(net_s, ["B200Acc"]))
+    on_fr = hostnet.OracleNetwork(network.Optimize(net_s, ["B200Acc"]))
+    L = info["layers"]
+    state = {}
+    for l in range(L):
+        state[1 + 2 * l] = np.zeros((B, info["output_size"]), np.int8)
+        state[2 + 2 * l] = np.zeros((B, info["num_units"]), np.int16)
+    free = {k: v[rows].copy() for k, v in state.items()}
+    xs = np.random.default_rng(55).integers(-128, 128, size=(T,) + tuple(info["input_shape"])).astype(np.int8)
+    worst = {"h": 0, "c": 0}
+    drift_h, drift_c = [], []
+    for t in range(T):
+        ins = {0: xs[t]}
+        ins.update(state)
+        outs = {0: np.zeros(info["output_shape"], np.int8)}
+        outs.update({k: np.zeros_like(v) for k, v in state.items()})
+        ln.EnqueueWorkload(ins, outs)
+        # teacher-forced: the oracle continues from the GPU's state of the previous step
+        ins_o = {0: xs[t][rows]}
+        ins_o.update({k: v[rows] for k, v in state.items()})
+        # layer l > 0 reads the GPU's output of layer l - 1 (third output slot of the QLstm layer below)
+        force = {}
+        for wi in range(1, len(ln.workloads)):
+            below = ln.workloads[wi - 1][0]
+            force[(wi, 0)] = ln.tensor_of(below.outputs[2])[rows].cpu().numpy()
+        want = on_tf.run(ins_o, force=force)
+        for k in outs:
+            st = diff_stats(want[k], outs[k][rows])
+            tol = 2 if outs[k].dtype == np.int16 else 1
+            assert st["max_abs"] <= tol and st["mismatch_frac"] <= 0.01, (t, k, st)
+            worst["c" if outs[k].dtype == np.int16 else "h"] = max(worst["c" if outs[k].dtype == np.int16 else "h"], st["max_abs"])
+        # free-running: the oracle continues from its own state
+        ins_f = {0: xs[t][rows]}
+        ins_f.update(free)
+        wf = on_fr.run(ins_f)
+        free = {k: wf[k].copy() for k in free}
+        drift_h.append(max(diff_stats(wf[1 + 2 * l], outs[1 + 2 * l][rows])["max_abs"] for l in range(L)))
+        drift_c.append(max(diff_stats(wf[2 + 2 * l], outs[2 + 2 * l][rows])["max_abs"] for l in range(L)))
+        state = {k: outs[k] for k in state}
+    print("QLstm b128 x 200 steps: teacher-forced worst |delta| h %d, c %d; free-running drift max h %d, c %d; at step 200 h %d, c %d"
+          % (worst["h"], worst["c"], max(drift_h), max(drift_c), drift_h[-1], drift_c[-1]))
+    # the recurrence contracts (gates are sigmoids of layer-normed sums): a 1-LSB difference does not grow without bound
+    assert max(drift_h) <= 255 and max(drift_c) <= 65535, (max(drift_h), max(drift_c))

@@ -70,6 +70,19 @@ CONV = {
     "padded_c40_oc72_stride2": lambda: random_conv_case(273, 2, 14, 14, 40, 72, 3, 3, stride=(2, 2), pad=(0, 1, 0, 1), act=(1, 0, 0)),
     "rowwin_u8w_5x5_c4": lambda: random_conv_case(268, 1, 20, 20, 4, 48, 5, 5, pad=(2, 2, 2, 2), x_dtype=U8, w_dtype=U8, y_dtype=U8,
                                                   x_q=(0.02, 100)),
+    # per-tensor weight zero points at the ends of their type's range: -zw = +128 does not fit one int8 tile value
+    "gemm_s8w_zp_minus128": lambda: random_conv_case(280, 2, 14, 14, 64, 64, 1, 1, per_axis=False, w_zp=-128),
+    "gemm_s8w_zp_plus127": lambda: random_conv_case(281, 2, 14, 14, 128, 96, 1, 1, per_axis=False, w_zp=127),
+    "im2col_s8w_zp_minus128_pad": lambda: random_conv_case(282, 1, 14, 14, 64, 64, 3, 3, pad=(1, 1, 1, 1), per_axis=False, w_zp=-128),
+    "gemm_u8w_zp_255": lambda: random_conv_case(283, 1, 14, 14, 64, 128, 1, 1, x_dtype=U8, w_dtype=U8, y_dtype=U8, x_q=(0.02, 7), w_zp=255),
+    "gemm_u8w_zp_128": lambda: random_conv_case(284, 1, 14, 14, 64, 64, 1, 1, x_dtype=U8, w_dtype=U8, y_dtype=U8, x_q=(0.02, 255), w_zp=128),
+    # fused Add whose last n-tile is partly padding (some epilogue warps have no columns in its second unit), in
+    # row-window mode and as a plain GEMM: the operand buffers' release must not run ahead of slower warps
+    "rowwin_fused_add_partial_tile": lambda: random_conv_case(5713, 18, 42, 24, 16, 160, 1, 1, fused_add=True),
+    "gemm_fused_add_partial_tile": lambda: random_conv_case(287, 8, 28, 28, 64, 160, 1, 1, act=(1, 0, 0), fused_add=True),
+    # explicit clamp narrower than the type on both sides (BoundedReLu with a non-zero lower bound), int8 and uint8
+    "gemm_clamp_both_s8": lambda: random_conv_case(285, 2, 14, 14, 64, 128, 1, 1, act=(2, 3.0, -1.0)),
+    "gemm_clamp_both_u8": lambda: random_conv_case(286, 2, 14, 14, 64, 64, 1, 1, x_dtype=U8, y_dtype=U8, x_q=(0.02, 128), act=(2, 2.0, -2.0)),
 }
 
 FC = {
@@ -121,6 +134,44 @@ def test_tcgen05_equals_cuda_core_kernel_at_full_size(built):
     y2, a2 = case.run_gpu(algo=2)
     _poll()
     assert np.array_equal(a1, a2) and np.array_equal(y1, y2)
+
+
+def test_bounded_waits_give_up_and_report_a_timeout(built):
+    """The failure path of the tcgen05 kernel, injected from the host: with selftest_us set the TMA producers issue no
+    loads, so the MMA issuer, the epilogue warps and (once the ring is full) the producers all run into their wait
+    limit of a few milliseconds, the kernel returns by itself and the status word says so.  The device stays usable:
+    the next ordinary launch is bit-exact."""
+    import ctypes as C
+    import time
+    from q8util import Cuda, gpu_pack
+    from armnn_b200 import lib
+    l = lib.load_library()
+    case = random_conv_case(290, 2, 14, 14, 64, 64, 1, 1)
+    mem = Cuda()
+    p, y, _ = case.params(mem, False, 2)
+    p.packed = gpu_pack(mem, p)
+    p.selftest_us = 3000
+    t0 = time.perf_counter()
+    lib.call("conv2d_q8", p)
+    rc = l.b200k_poll_status()                      # synchronises
+    elapsed = time.perf_counter() - t0
+    assert rc == _abi.E_TIMEOUT, rc
+    assert b"wait gave up" in l.b200k_last_error()
+    assert elapsed < 1.0, elapsed                   # a handful of 3 ms limits, not the two-second default
+    assert l.b200k_poll_status() == 0               # the status word was cleared by the poll
+    want, _ = case.run_oracle(want_acc=False)
+    got, _ = case.run_gpu(want_acc=False, algo=2)
+    _poll()
+    assert np.array_equal(want, got)
+
+
+def test_zero_points_outside_the_type_range_are_refused(built):
+    from armnn_b200 import lib
+    case = random_conv_case(291, 1, 8, 8, 64, 64, 1, 1, per_axis=False, w_zp=-128)
+    case.w_q = (case.w_q[0], -200)                  # not an int8 value: the tcgen05 path must not take it
+    with pytest.raises(lib.B200KError) as e:
+        case.run_gpu(algo=2)
+    assert e.value.code == _abi.E_UNSUPPORTED
 
 
 def test_ineligible_shapes_are_refused_when_forced(built):

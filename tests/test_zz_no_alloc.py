@@ -3,8 +3,9 @@ a workload living inside a server whose GPU memory pool is carved up once at sta
 and the re-packed input in a device array compiled into the library instead of in caller buffers.
 
 The check: through the C ABI, its output equals the ordinary entry point's (which gets caller-allocated buffers)
-bit for bit — the tolerance every convolution test here uses — on two calls in a row with different inputs, so
-that contents left in the shared array by the first call are shown not to matter.  Collected last on purpose."""
+and the CPU oracle's bit for bit — the tolerance every convolution test here uses — on calls in a row with
+different inputs, shapes and table contents (a fused-add table, zero-padded channel copies), so that what one call
+leaves in the shared array is shown not to matter to the next.  Collected last on purpose."""
 import ctypes as C
 
 import numpy as np
@@ -31,7 +32,10 @@ def _both(case):
     q, y_static, _ = case.params(mem, False, 2)
     lib.check(l.b200k_conv2d_q8_static(C.byref(q), None))
     lib.check(l.b200k_poll_status())
-    return mem.fetch(y_ref), mem.fetch(y_static)
+    a, b = mem.fetch(y_ref), mem.fetch(y_static)
+    want, _ = case.run_oracle(want_acc=False)
+    assert np.array_equal(want, b), "static entry point differs from the oracle"
+    return a, b
 
 
 def test_static_scratch_entry_point_matches_the_ordinary_one_twice(built):
@@ -46,6 +50,22 @@ def test_static_scratch_entry_point_matches_the_ordinary_one_twice(built):
     third = random_conv_case(303, 1, 14, 14, 64, 64, 3, 3, pad=(1, 1, 1, 1))
     a, b = _both(third)
     assert np.array_equal(a, b)
+
+
+def test_static_scratch_entry_point_rebuilds_tables_between_different_layers(built):
+    """The shared array also holds the fused-add table and the zero-padded weight copies of channel counts that are
+    multiples of 8 only; both are rebuilt by every call.  Two fused Adds with different quantisation around a
+    24-channel convolution: a table or a padded copy left over from the previous call would change the result."""
+    add1 = random_conv_case(305, 2, 14, 14, 64, 256, 1, 1, act=(1, 0, 0), fused_add=True)
+    a, b = _both(add1)
+    assert a.any() and np.array_equal(a, b)
+    padded = random_conv_case(306, 2, 28, 28, 24, 144, 1, 1, x_dtype=_abi.U8, w_dtype=_abi.U8, y_dtype=_abi.U8,
+                              x_q=(0.02, 128), act=(2, 6.0, 0.0), y_zp=0)
+    a, b = _both(padded)
+    assert a.any() and np.array_equal(a, b)
+    add2 = random_conv_case(307, 1, 14, 14, 128, 256, 1, 1, fused_add=True, x_q=(0.03, 7))
+    a, b = _both(add2)
+    assert a.any() and np.array_equal(a, b)
 
 
 def test_static_scratch_entry_point_rejects_oversized_problems(built):
