@@ -79,6 +79,11 @@ class ConvertParams(C.Structure):
     _fields_ = [("x", QTensor), ("y", QTensor), ("count", C.c_int64)]
 
 
+class PadParams(C.Structure):
+    _fields_ = [("x", QTensor), ("y", QTensor), ("rank", C.c_int32), ("shape", C.c_int32 * 4),
+                ("pad_before", C.c_int32 * 4), ("pad_after", C.c_int32 * 4), ("pad_value", C.c_float)]
+
+
 _P, _F, _I = C.c_void_p, C.c_float, C.c_int32
 
 
@@ -122,6 +127,7 @@ KERNEL_ENTRY_POINTS = {
     "softmax_q8": SoftmaxParams,
     "convert_q": ConvertParams,
     "qlstm_step": QLstmParams,
+    "pad_q": PadParams,
 }
 
 # every symbol include/b200k.h declares

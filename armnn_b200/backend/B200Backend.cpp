@@ -1,6 +1,6 @@
-// The B200Acc backend object: IBackendInternal, layer support, graph-level optimisation (activation fusion), and the
-// three extern "C" entry points of a dynamic backend (include/armnn/backends/DynamicBackend.hpp:41-43 of the Arm NN
-// tree).  Structure follows RefBackend (src/backends/reference/RefBackend.cpp:22-208) and the sample dynamic backend
+// The B200Acc backend object: IBackendInternal, layer support, graph-level optimisation (Pad folding, activation and
+// residual-Add fusion), the per-network model context (DeviceId) and, in B200DynamicBackend.cpp, the three extern "C"
+// entry points of a dynamic backend (include/armnn/backends/DynamicBackend.hpp:41-43 of the Arm NN tree).  Structure follows RefBackend (src/backends/reference/RefBackend.cpp:22-208) and the sample dynamic backend
 // (src/dynamic/sample/SampleDynamicBackend.cpp); the fusion pass restates what the Neon / CL backends do
 // (src/backends/cl/ClBackend.cpp:326-390, src/backends/aclCommon/ArmComputeSubgraphUtils.hpp:52-70), whose helper
 // header cannot be included because it pulls in the un-vendored Arm Compute Library.
@@ -22,6 +22,10 @@
 #include <layers/DepthwiseConvolution2dLayer.hpp>
 #include <layers/ElementwiseBinaryLayer.hpp>
 #include <layers/FullyConnectedLayer.hpp>
+#include <layers/PadLayer.hpp>
+#include <layers/Pooling2dLayer.hpp>
+
+#include "B200Backend.hpp"
 
 #include "b200k.h"
 
@@ -107,6 +111,16 @@ public:
             case LayerType::Pooling2d:
                 if (PolymorphicDowncast<const Pooling2dDescriptor*>(&descriptor)->m_DataLayout != DataLayout::NHWC) { return No(reason, "only NHWC is supported"); }
                 return (IsActType(infos[0]) && IsActType(infos[1])) || No(reason, "unsupported data type");
+            case LayerType::Pad:
+            {
+                // Pad layers in front of a convolution or pooling layer are folded into it by OptimizeSubgraphView (the
+                // TfLite parser emits them for explicit padding, src/armnnTfLiteParser/TfLiteParser.cpp:829-830); the
+                // others run as a workload of their own
+                const auto& d = *PolymorphicDowncast<const PadDescriptor*>(&descriptor);
+                if (d.m_PaddingMode != PaddingMode::Constant) { return No(reason, "only constant padding is supported"); }
+                if (infos[0].GetNumDimensions() > 4) { return No(reason, "rank > 4"); }
+                return (IsActType(infos[0]) && IsActType(infos[1])) || No(reason, "unsupported data type");
+            }
             case LayerType::Mean:
             {
                 const auto& d = *PolymorphicDowncast<const MeanDescriptor*>(&descriptor);
@@ -146,12 +160,18 @@ public:
     }
 };
 
+/// Runtime-level state: BackendOptions("B200Acc", {...}) given to IRuntime::Create —
+///   "DeviceId"        default GPU of networks that carry no DeviceId ModelOption (else B200ACC_DEVICE_ID, else 0)
+///   "GraphReplay"     false: never replay workload queues as CUDA graphs (default true)
+///   "WaitSelfTestUs"  > 0: every convolution runs the bounded-wait self-test of b200k_conv2d_params.selftest_us
+/// Modelled on ClBackendContext (src/backends/cl/ClBackendContext.cpp:61-215).
 class B200BackendContext : public IBackendContext
 {
 public:
     explicit B200BackendContext(const IRuntime::CreationOptions& options) : IBackendContext(options)
     {
-        int device = -1;
+        int device = -1, selfTest = 0;
+        bool graph = true;
         for (const auto& bo : options.m_BackendOptions)
         {
             if (bo.GetBackendId() != BackendId(B200BackendId())) { continue; }
@@ -159,22 +179,31 @@ public:
             {
                 const auto& opt = bo.GetOption(i);
                 if (opt.GetName() == "DeviceId" && opt.GetValue().IsInt()) { device = opt.GetValue().AsInt(); }
+                if (opt.GetName() == "WaitSelfTestUs" && opt.GetValue().IsInt()) { selfTest = opt.GetValue().AsInt(); }
+                if (opt.GetName() == "GraphReplay" && opt.GetValue().IsBool()) { graph = opt.GetValue().AsBool(); }
             }
         }
-        B200Device::Configure(device);                   // throws BackendUnavailableException without an sm_100 device
+        B200Context::SetDefaultDevice(device);
+        B200Context::SetDefaultSelfTestUs(selfTest);
+        B200Context::SetGraphReplayEnabled(graph);
+        if (b200k_device_open(B200Context::DefaultDevice()) != B200K_OK)
+        {
+            throw BackendUnavailableException(std::string("B200Acc: ") + b200k_last_error());
+        }
     }
     bool BeforeLoadNetwork(NetworkId) override { return true; }
     bool AfterLoadNetwork(NetworkId) override { return true; }
     bool BeforeUnloadNetwork(NetworkId) override
     {
-        cudaStreamSynchronize(B200Device::Get().Stream());
+        B200Context::SynchronizeAll();
         return true;
     }
     bool AfterUnloadNetwork(NetworkId) override { return true; }
     bool AfterEnqueueWorkload(NetworkId) override
     {
-        B200Device::NextEpoch();                          // imported inputs are uploaded afresh by the next inference
-        return cudaStreamSynchronize(B200Device::Get().Stream()) == cudaSuccess && b200k_poll_status() == B200K_OK;
+        // the contexts this thread has just run workloads on: wait, report device-side failures, next epoch (imported
+        // inputs are uploaded afresh by the next inference)
+        return B200Context::EndInferenceAll();
     }
 };
 
@@ -187,76 +216,137 @@ bool SameQuantisation(const TensorInfo& a, const TensorInfo& b)
            a.GetQuantizationScale() == b.GetQuantizationScale() && a.GetQuantizationOffset() == b.GetQuantizationOffset();
 }
 
+/// [Pad ->] base -> Activation becomes `replacement` (same kind as base, padding already added to its descriptor when
+/// there is a Pad) carrying the activation as additional information.
 template <typename LayerT>
-void Fuse(OptimizationViews& views, LayerT* base, LayerT* replacement, ActivationLayer* act)
+void Fuse(OptimizationViews& views, LayerT* base, LayerT* replacement, ActivationLayer* act, Layer* pad = nullptr)
 {
     replacement->SetAdditionalInfoForObject(std::make_shared<ActivationDescriptor>(act->GetParameters()));
-    SubgraphView substitution({base, act}, CreateIInputsFrom({base}), CreateIOutputsFrom({act}));
+    if (!pad)
+    {
+        SubgraphView substitution({base, act}, CreateIInputsFrom({base}), CreateIOutputsFrom({act}));
+        SubgraphView replacementView(replacement);
+        views.AddSubstitution({substitution, replacementView});
+        return;
+    }
+    // the data input is the Pad's, the weights and the bias stay the base layer's
+    SubgraphView::IInputSlots inputs{&pad->GetInputSlot(0)};
+    for (unsigned int i = 1; i < base->GetNumInputSlots(); ++i) { inputs.push_back(&base->GetInputSlot(i)); }
+    SubgraphView substitution({pad, base, act}, std::move(inputs), CreateIOutputsFrom({act}));
     SubgraphView replacementView(replacement);
     views.AddSubstitution({substitution, replacementView});
 }
 
 }  // namespace
 
-class B200Backend : public IBackendInternal
+const BackendId& B200Backend::GetIdStatic()
 {
-public:
-    static const BackendId& GetIdStatic()
-    {
-        static const BackendId s_Id{B200BackendId()};
-        return s_Id;
-    }
-    const BackendId& GetId() const override { return GetIdStatic(); }
+    static const BackendId s_Id{B200BackendId()};
+    return s_Id;
+}
 
-    IMemoryManagerUniquePtr CreateMemoryManager() const override { return std::make_unique<B200MemoryManager>(); }
+IBackendInternal::IMemoryManagerUniquePtr B200Backend::CreateMemoryManager() const
+{
+    return std::make_unique<B200MemoryManager>();
+}
 
-    IWorkloadFactoryPtr CreateWorkloadFactory(const IMemoryManagerSharedPtr& memoryManager) const override
-    {
-        return std::make_unique<B200WorkloadFactory>(PolymorphicPointerDowncast<B200MemoryManager>(memoryManager));
-    }
+IBackendInternal::IWorkloadFactoryPtr B200Backend::CreateWorkloadFactory(const IMemoryManagerSharedPtr& memoryManager) const
+{
+    return std::make_unique<B200WorkloadFactory>(B200Context::Shared(), PolymorphicPointerDowncast<B200MemoryManager>(memoryManager));
+}
 
-    IWorkloadFactoryPtr CreateWorkloadFactory(TensorHandleFactoryRegistry& registry) const override
-    {
-        auto memoryManager = std::make_shared<B200MemoryManager>();
-        registry.RegisterMemoryManager(memoryManager);
-        auto factory = std::make_unique<B200TensorHandleFactory>(memoryManager);
-        registry.RegisterCopyAndImportFactoryPair(factory->GetId(), factory->GetId());
-        registry.RegisterFactory(std::move(factory));
-        return std::make_unique<B200WorkloadFactory>(memoryManager);
-    }
+namespace
+{
+/// DeviceId of a network: its ModelOption, else the runtime's default.
+int DeviceOf(const ModelOptions& modelOptions)
+{
+    B200BackendModelContext ctx(modelOptions);
+    return ctx.DeviceId() >= 0 ? ctx.DeviceId() : B200Context::DefaultDevice();
+}
 
-    IBackendContextPtr CreateBackendContext(const IRuntime::CreationOptions& options) const override
-    {
-        return IBackendContextPtr{new B200BackendContext(options)};
-    }
+/// One context (GPU, stream, workload queue), one memory manager and one handle factory per network.
+IBackendInternal::IWorkloadFactoryPtr MakeFactories(TensorHandleFactoryRegistry& registry, int device)
+{
+    auto ctx = std::make_shared<B200Context>(device);
+    auto memoryManager = std::make_shared<B200MemoryManager>(ctx);
+    registry.RegisterMemoryManager(memoryManager);
+    auto factory = std::make_unique<B200TensorHandleFactory>(ctx, memoryManager);
+    registry.RegisterCopyAndImportFactoryPair(factory->GetId(), factory->GetId());
+    registry.RegisterFactory(std::move(factory));
+    return std::make_unique<B200WorkloadFactory>(ctx, memoryManager);
+}
+}  // namespace
 
-    IBackendProfilingContextPtr CreateBackendProfilingContext(const IRuntime::CreationOptions&, IBackendProfilingPtr&) override
-    {
-        return IBackendProfilingContextPtr{};
-    }
+IBackendInternal::IWorkloadFactoryPtr B200Backend::CreateWorkloadFactory(TensorHandleFactoryRegistry& registry) const
+{
+    return MakeFactories(registry, B200Context::DefaultDevice());
+}
 
-    ILayerSupportSharedPtr GetLayerSupport() const override
-    {
-        static ILayerSupportSharedPtr layerSupport{new B200LayerSupport};
-        return layerSupport;
-    }
+// LoadedNetwork hands the network's ModelOptions over here (src/armnn/LoadedNetwork.cpp:264-279): the pattern of
+// ClBackend (src/backends/cl/ClBackend.cpp:62-71, 246-250), with the GPU chosen per network
+IBackendInternal::IWorkloadFactoryPtr B200Backend::CreateWorkloadFactory(TensorHandleFactoryRegistry& registry,
+                                                                         const ModelOptions& modelOptions) const
+{
+    return MakeFactories(registry, DeviceOf(modelOptions));
+}
 
-    std::vector<ITensorHandleFactory::FactoryId> GetHandleFactoryPreferences() const override
-    {
-        return {B200TensorHandleFactory::GetIdStatic()};
-    }
+IBackendInternal::IWorkloadFactoryPtr B200Backend::CreateWorkloadFactory(TensorHandleFactoryRegistry& registry,
+                                                                         const ModelOptions& modelOptions,
+                                                                         MemorySourceFlags, MemorySourceFlags) const
+{
+    return MakeFactories(registry, DeviceOf(modelOptions));
+}
 
-    void RegisterTensorHandleFactories(TensorHandleFactoryRegistry& registry) override
-    {
-        auto memoryManager = std::make_shared<B200MemoryManager>();
-        registry.RegisterMemoryManager(memoryManager);
-        auto factory = std::make_unique<B200TensorHandleFactory>(memoryManager);
-        registry.RegisterCopyAndImportFactoryPair(factory->GetId(), factory->GetId());
-        registry.RegisterFactory(std::move(factory));
-    }
+IBackendInternal::IBackendSpecificModelContextPtr B200Backend::CreateBackendSpecificModelContext(const ModelOptions& modelOptions) const
+{
+    return IBackendSpecificModelContextPtr{new B200BackendModelContext(modelOptions)};
+}
 
-    BackendCapabilities GetCapabilities() const override
-    {
+IBackendInternal::IBackendContextPtr B200Backend::CreateBackendContext(const IRuntime::CreationOptions& options) const
+{
+    return IBackendContextPtr{new B200BackendContext(options)};
+}
+
+IBackendInternal::IBackendProfilingContextPtr B200Backend::CreateBackendProfilingContext(const IRuntime::CreationOptions&,
+                                                                                         IBackendProfilingPtr&)
+{
+    return IBackendProfilingContextPtr{};
+}
+
+IBackendInternal::ILayerSupportSharedPtr B200Backend::GetLayerSupport() const
+{
+    static ILayerSupportSharedPtr layerSupport{new B200LayerSupport};
+    return layerSupport;
+}
+
+IBackendInternal::ILayerSupportSharedPtr B200Backend::GetLayerSupport(const ModelOptions&) const
+{
+    return GetLayerSupport();
+}
+
+std::vector<ITensorHandleFactory::FactoryId> B200Backend::GetHandleFactoryPreferences() const
+{
+    return {B200TensorHandleFactory::GetIdStatic()};
+}
+
+// Called by the optimizer (handle-strategy selection) and by LoadedNetwork for backends that do not own the network's
+// factories: no device is touched until a handle is created.
+void B200Backend::RegisterTensorHandleFactories(TensorHandleFactoryRegistry& registry)
+{
+    auto memoryManager = std::make_shared<B200MemoryManager>();
+    registry.RegisterMemoryManager(memoryManager);
+    auto factory = std::make_unique<B200TensorHandleFactory>(nullptr, memoryManager);
+    registry.RegisterCopyAndImportFactoryPair(factory->GetId(), factory->GetId());
+    registry.RegisterFactory(std::move(factory));
+}
+
+void B200Backend::RegisterTensorHandleFactories(TensorHandleFactoryRegistry& registry, MemorySourceFlags, MemorySourceFlags)
+{
+    RegisterTensorHandleFactories(registry);
+}
+
+BackendCapabilities B200Backend::GetCapabilities() const
+{
         // NonConstWeights:true makes the core ask B200LayerSupport (which then refuses non-constant weights with a
         // reason) instead of refusing in LayerSupportHandle (src/armnn/BackendHelper.cpp:371-423)
         return BackendCapabilities("B200Acc", {{"NonConstWeights", true},
@@ -268,13 +358,16 @@ public:
                                                {"SingleAxisPacking", false},
                                                {"HasFp16", false},
                                                {"AllOrNothing", false}});
-    }
+}
+
+namespace
+{
 
     /// Convolution2d -> ElementwiseBinary(Add, other) [-> Activation{ReLu, BoundedReLu}] becomes one PreCompiled layer
     /// (inputs: data, weights[, bias], other) whose workload adds the other operand in the convolution's epilogue:
     /// the residual connections of ResNet-style graphs then cost no pass over memory of their own.  The result is what
     /// the three CpuRef workloads in a row produce (the convolution's own 8-bit result is formed, not stored).
-    void FuseResidualAdds(const SubgraphView& subgraph, OptimizationViews& views, std::map<LayerGuid, Layer*>& untouched) const
+    void FuseResidualAdds(const BackendId& backendId, const SubgraphView& subgraph, OptimizationViews& views, std::map<LayerGuid, Layer*>& untouched)
     {
         for (auto it = subgraph.begin(); it != subgraph.end(); ++it)
         {
@@ -322,7 +415,7 @@ public:
                 const unsigned int convInputs = conv->GetNumInputSlots();
                 const std::string name = std::string("fused-") + add->GetName() + "-into-" + conv->GetName();
                 IConnectableLayer* fused = views.GetINetwork()->AddPrecompiledLayer(
-                    PreCompiledDescriptor(convInputs + 1, 1), std::move(blobPtr), Optional<BackendId>(GetId()), name.c_str());
+                    PreCompiledDescriptor(convInputs + 1, 1), std::move(blobPtr), Optional<BackendId>(backendId), name.c_str());
                 Layer* last = act ? static_cast<Layer*>(act) : static_cast<Layer*>(add);
                 fused->GetOutputSlot(0).SetTensorInfo(last->GetOutputSlot(0).GetTensorInfo());
 
@@ -341,11 +434,52 @@ public:
         }
     }
 
+    /// Pad -> Convolution2d / DepthwiseConvolution2d / Pooling2d becomes the layer itself with the padding added to its
+    /// descriptor, when the pad value is the tensor's zero point and only H and W are padded.  The core does this for
+    /// the backends named CpuAcc / GpuAcc only (src/armnn/Network.cpp:1394-1401), every other backend folds by itself
+    /// as RefBackend does (src/backends/reference/RefBackend.cpp:93-164), with the same shared helpers.
+    /// The Pad layer in front of `baseLayer` when it can be folded; `descriptor` then has its padding added.
+    template <typename LayerT, typename DescriptorT>
+    PadLayer* FoldablePad(LayerT* baseLayer, DescriptorT& descriptor, const std::map<LayerGuid, Layer*>& untouched, bool isPooling)
+    {
+        OutputSlot* src = baseLayer->GetInputSlot(0).GetConnectedOutputSlot();
+        if (!src || src->GetOwningLayer().GetType() != LayerType::Pad) { return nullptr; }
+        auto* padLayer = PolymorphicDowncast<PadLayer*>(&src->GetOwningLayer());
+        if (untouched.find(padLayer->GetGuid()) == untouched.end() || padLayer->GetOutputSlot(0).GetNumConnections() != 1) { return nullptr; }
+        bool ok;
+        if constexpr (std::is_same<DescriptorT, Pooling2dDescriptor>::value)
+        {
+            ok = optimizations::pad_fold::TryFoldPadIntoLayer2d(padLayer->GetParameters(), descriptor,
+                                                                padLayer->GetOutputSlot().GetTensorInfo(), isPooling);
+        }
+        else
+        {
+            ok = optimizations::pad_fold::TryFoldPadIntoLayer2d<DescriptorT>(padLayer->GetParameters(), descriptor,
+                                                                             padLayer->GetOutputSlot().GetTensorInfo());
+        }
+        return ok ? padLayer : nullptr;
+    }
+
+    template <typename LayerT, typename DescriptorT>
+    void TryFoldPad(Layer& base, OptimizationViews& views, std::map<LayerGuid, Layer*>& untouched, bool isPooling)
+    {
+        auto* baseLayer = PolymorphicDowncast<LayerT*>(&base);
+        if (untouched.find(baseLayer->GetGuid()) == untouched.end()) { return; }
+        DescriptorT descriptor = baseLayer->GetParameters();
+        PadLayer* padLayer = FoldablePad<LayerT, DescriptorT>(baseLayer, descriptor, untouched, isPooling);
+        if (!padLayer) { return; }
+        FoldPadLayer2d<LayerT, DescriptorT>(views, baseLayer, descriptor, padLayer);
+        untouched.erase(baseLayer->GetGuid());
+        untouched.erase(padLayer->GetGuid());
+    }
+
+}  // namespace
+
     /// Fold Activation{ReLu, BoundedReLu} into the producing Convolution2d / DepthwiseConvolution2d / FullyConnected /
     /// ElementwiseBinary when both tensors carry the same quantisation: the workload then clamps in the quantised
     /// domain, which is exactly what the separate CpuRef Activation workload would compute.
-    OptimizationViews OptimizeSubgraphView(const SubgraphView& subgraph, const ModelOptions& modelOptions) const override
-    {
+OptimizationViews B200Backend::OptimizeSubgraphView(const SubgraphView& subgraph, const ModelOptions& modelOptions) const
+{
         OptimizationViews views(modelOptions);
         std::map<LayerGuid, Layer*> untouched;
         for (auto it = subgraph.begin(); it != subgraph.end(); ++it)
@@ -353,7 +487,7 @@ public:
             Layer& l = *PolymorphicDowncast<Layer*>(*it);
             untouched.insert({l.GetGuid(), &l});
         }
-        FuseResidualAdds(subgraph, views, untouched);
+        FuseResidualAdds(GetId(), subgraph, views, untouched);
         for (auto it = subgraph.begin(); it != subgraph.end(); ++it)
         {
             Layer& base = *PolymorphicDowncast<Layer*>(*it);
@@ -374,15 +508,22 @@ public:
             INetwork* net = views.GetINetwork();
             if (t == LayerType::Convolution2d)
             {
+                // a Pad in front of the convolution goes into the same substitution
                 auto* b = PolymorphicDowncast<Convolution2dLayer*>(&base);
-                auto* r = PolymorphicDowncast<Convolution2dLayer*>(net->AddConvolution2dLayer(b->GetParameters(), name.c_str()));
-                Fuse(views, b, r, act);
+                Convolution2dDescriptor desc = b->GetParameters();
+                PadLayer* pad = FoldablePad<Convolution2dLayer, Convolution2dDescriptor>(b, desc, untouched, false);
+                auto* r = PolymorphicDowncast<Convolution2dLayer*>(net->AddConvolution2dLayer(desc, name.c_str()));
+                Fuse(views, b, r, act, pad);
+                if (pad) { untouched.erase(pad->GetGuid()); }
             }
             else if (t == LayerType::DepthwiseConvolution2d)
             {
                 auto* b = PolymorphicDowncast<DepthwiseConvolution2dLayer*>(&base);
-                auto* r = PolymorphicDowncast<DepthwiseConvolution2dLayer*>(net->AddDepthwiseConvolution2dLayer(b->GetParameters(), name.c_str()));
-                Fuse(views, b, r, act);
+                DepthwiseConvolution2dDescriptor desc = b->GetParameters();
+                PadLayer* pad = FoldablePad<DepthwiseConvolution2dLayer, DepthwiseConvolution2dDescriptor>(b, desc, untouched, false);
+                auto* r = PolymorphicDowncast<DepthwiseConvolution2dLayer*>(net->AddDepthwiseConvolution2dLayer(desc, name.c_str()));
+                Fuse(views, b, r, act, pad);
+                if (pad) { untouched.erase(pad->GetGuid()); }
             }
             else if (t == LayerType::FullyConnected)
             {
@@ -401,6 +542,14 @@ public:
             untouched.erase(base.GetGuid());
             untouched.erase(child.GetGuid());
         }
+        // explicit padding in front of layers the fusions above have left alone
+        for (auto it = subgraph.begin(); it != subgraph.end(); ++it)
+        {
+            Layer& base = *PolymorphicDowncast<Layer*>(*it);
+            if (base.GetType() == LayerType::Convolution2d) { TryFoldPad<Convolution2dLayer, Convolution2dDescriptor>(base, views, untouched, false); }
+            else if (base.GetType() == LayerType::DepthwiseConvolution2d) { TryFoldPad<DepthwiseConvolution2dLayer, DepthwiseConvolution2dDescriptor>(base, views, untouched, false); }
+            else if (base.GetType() == LayerType::Pooling2d) { TryFoldPad<Pooling2dLayer, Pooling2dDescriptor>(base, views, untouched, true); }
+        }
         if (views.GetSubstitutions().empty())
         {
             views.AddUntouchedSubgraph(SubgraphView(subgraph));
@@ -410,25 +559,7 @@ public:
             ReportUntouchedLayers(views, untouched);
         }
         return views;
-    }
-};
+}
 
 }  // namespace armnn
 
-extern "C" __attribute__((visibility("default"))) const char* GetBackendId()
-{
-    return armnn::B200Backend::GetIdStatic().Get().c_str();
-}
-
-extern "C" __attribute__((visibility("default"))) void GetVersion(uint32_t* outMajor, uint32_t* outMinor)
-{
-    if (!outMajor || !outMinor) { return; }
-    armnn::BackendVersion v = armnn::IBackendInternal::GetApiVersion();
-    *outMajor = v.m_Major;
-    *outMinor = v.m_Minor;
-}
-
-extern "C" __attribute__((visibility("default"))) void* BackendFactory()
-{
-    return new armnn::B200Backend();
-}

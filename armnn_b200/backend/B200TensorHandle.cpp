@@ -2,10 +2,7 @@
 
 #include <armnn/Exceptions.hpp>
 
-#include <atomic>
-#include <cstdlib>
 #include <cstring>
-#include <mutex>
 #include <string>
 
 #include "b200k.h"
@@ -29,65 +26,109 @@ void B200CheckStatus(int rc)
     }
 }
 
-namespace
-{
-int g_ConfiguredDevice = -1;
-std::atomic<uint64_t> g_Epoch{1};
-}
+// ---- memory manager ------------------------------------------------------------------------------------------
 
-uint64_t B200Device::Epoch() { return g_Epoch.load(std::memory_order_relaxed); }
-void B200Device::NextEpoch() { g_Epoch.fetch_add(1, std::memory_order_relaxed); }
-
-void B200Device::Configure(int deviceId)
+B200MemoryManager::~B200MemoryManager()
 {
-    g_ConfiguredDevice = deviceId;
-    Get();
-}
-
-B200Device::B200Device()
-{
-    int dev = g_ConfiguredDevice;
-    if (dev < 0)
+    if (m_Arena)
     {
-        const char* env = std::getenv("B200ACC_DEVICE_ID");
-        dev = env ? std::atoi(env) : 0;
-    }
-    if (b200k_device_open(dev) != B200K_OK)
-    {
-        throw BackendUnavailableException(std::string("B200Acc: ") + b200k_last_error());
-    }
-    m_Device = dev;
-    if (cudaStreamCreateWithFlags(&m_Stream, cudaStreamNonBlocking) != cudaSuccess)
-    {
-        throw BackendUnavailableException("B200Acc: cannot create a CUDA stream");
+        if (m_Ctx) { cudaSetDevice(m_Ctx->Device()); }
+        cudaFree(m_Arena);
     }
 }
 
-B200Device& B200Device::Get()
+B200MemoryManager::Pool* B200MemoryManager::Manage(size_t bytes)
 {
-    static B200Device instance;
-    return instance;
+    if (m_Arena) { throw RuntimeException("B200Acc: tensor lifetimes cannot change while the arena is acquired"); }
+    m_ManagedBytes += bytes;
+    // the smallest free pool that is large enough; otherwise the largest free one grows; otherwise a new pool
+    Pool* best = nullptr;
+    Pool* largest = nullptr;
+    for (auto& p : m_Pools)
+    {
+        if (!p->free) { continue; }
+        if (p->bytes >= bytes && (!best || p->bytes < best->bytes)) { best = p.get(); }
+        if (!largest || p->bytes > largest->bytes) { largest = p.get(); }
+    }
+    Pool* pool = best ? best : largest;
+    if (!pool)
+    {
+        m_Pools.push_back(std::make_unique<Pool>());
+        pool = m_Pools.back().get();
+    }
+    if (pool->bytes < bytes) { pool->bytes = bytes; }
+    pool->free = false;
+    return pool;
 }
 
-void B200Device::MakeCurrent() const
+void B200MemoryManager::Allocate(Pool* pool)
 {
-    B200Check(cudaSetDevice(m_Device), "cudaSetDevice");
+    if (pool) { pool->free = true; }
 }
 
-B200TensorHandle::B200TensorHandle(const TensorInfo& info) : m_Info(info) {}
+void B200MemoryManager::Acquire()
+{
+    if (m_Arena) { return; }
+    size_t total = 0;
+    for (auto& p : m_Pools)
+    {
+        p->offset = total;
+        total += (p->bytes + 255) & ~static_cast<size_t>(255);
+    }
+    m_ArenaBytes = total;
+    if (total == 0) { return; }
+    if (m_Ctx) { m_Ctx->MakeCurrent(); }
+    B200Check(cudaMalloc(&m_Arena, total), "cudaMalloc (tensor arena)");
+}
+
+void B200MemoryManager::Release()
+{
+    if (!m_Arena) { return; }
+    if (m_Ctx)
+    {
+        m_Ctx->MakeCurrent();
+        m_Ctx->Invalidate();                          // a recorded graph holds addresses inside the arena
+        cudaStreamSynchronize(m_Ctx->Stream());
+    }
+    cudaFree(m_Arena);
+    m_Arena = nullptr;
+}
+
+void* B200MemoryManager::Address(const Pool* pool)
+{
+    if (!m_Arena) { Acquire(); }
+    return static_cast<char*>(m_Arena) + pool->offset;
+}
+
+// ---- tensor handle -------------------------------------------------------------------------------------------
+
+B200TensorHandle::B200TensorHandle(const TensorInfo& info, std::shared_ptr<B200Context> ctx, std::shared_ptr<B200MemoryManager> mgr)
+    : m_Info(info), m_Ctx(std::move(ctx)), m_Mgr(std::move(mgr)) {}
 
 B200TensorHandle::~B200TensorHandle()
 {
     Unimport();
+    if (m_Dev || m_Host) { cudaSetDevice(m_Ctx->Device()); }
     if (m_Dev) { cudaFree(m_Dev); }
     if (m_Host) { cudaFreeHost(m_Host); }
 }
 
+void B200TensorHandle::Manage()
+{
+    // start of this tensor's lifetime in the network's execution order
+    if (m_Mgr && !m_Pool && !m_Dev) { m_Pool = m_Mgr->Manage(m_Info.GetNumBytes() ? m_Info.GetNumBytes() : 16); }
+}
+
 void B200TensorHandle::Allocate()
 {
+    if (m_Pool)
+    {
+        m_Mgr->Allocate(m_Pool);                       // end of the lifetime: the bytes may serve a later tensor
+        return;
+    }
     if (!m_Dev)
     {
-        B200Device::Get().MakeCurrent();
+        m_Ctx->MakeCurrent();
         size_t bytes = m_Info.GetNumBytes();
         B200Check(cudaMalloc(&m_Dev, bytes ? bytes : 16), "cudaMalloc");
     }
@@ -95,13 +136,14 @@ void B200TensorHandle::Allocate()
 
 void* B200TensorHandle::Device() const
 {
+    if (m_Pool) { return m_Mgr->Address(m_Pool); }
     if (!m_Dev) { const_cast<B200TensorHandle*>(this)->Allocate(); }
     return m_Dev;
 }
 
 const void* B200TensorHandle::Map(bool /*blocking*/) const
 {
-    B200Device& d = B200Device::Get();
+    B200Context& d = *m_Ctx;
     d.MakeCurrent();
     const size_t bytes = m_Info.GetNumBytes();
     if (m_Imported)
@@ -110,11 +152,12 @@ const void* B200TensorHandle::Map(bool /*blocking*/) const
         m_ReadOnlyMapping = m_DeviceNewer;
         if (m_DeviceNewer)
         {
+            d.SyncForMap();                            // (ends a recording, if one is running, before the copy is enqueued)
             PinIfReused();
             B200Check(cudaMemcpyAsync(m_Imported, Device(), bytes, cudaMemcpyDeviceToHost, d.Stream()), "cudaMemcpyAsync D2H");
             m_DeviceNewer = false;
         }
-        B200Check(cudaStreamSynchronize(d.Stream()), "cudaStreamSynchronize");
+        d.SyncForMap();
         B200CheckStatus(b200k_poll_status());
         return m_Imported;
     }
@@ -122,11 +165,12 @@ const void* B200TensorHandle::Map(bool /*blocking*/) const
     m_ReadOnlyMapping = m_DeviceNewer;
     if (m_DeviceNewer)
     {
+        d.SyncForMap();
         B200Check(cudaMemcpyAsync(m_Host, Device(), bytes, cudaMemcpyDeviceToHost, d.Stream()), "cudaMemcpyAsync D2H");
         m_DeviceNewer = false;
     }
     // also waits for an earlier Unmap's upload from this staging buffer before the caller overwrites it
-    B200Check(cudaStreamSynchronize(d.Stream()), "cudaStreamSynchronize");
+    d.SyncForMap();
     B200CheckStatus(b200k_poll_status());
     return m_Host;
 }
@@ -139,25 +183,21 @@ void B200TensorHandle::Unmap() const
         return;
     }
     if (!m_Host || m_ReadOnlyMapping) { return; }      // a read-back of device results needs no upload
-    B200Device& d = B200Device::Get();
-    d.MakeCurrent();
-    B200Check(cudaMemcpyAsync(Device(), m_Host, m_Info.GetNumBytes(), cudaMemcpyHostToDevice, d.Stream()), "cudaMemcpyAsync H2D");
+    m_Ctx->MakeCurrent();
+    B200Check(cudaMemcpyAsync(Device(), m_Host, m_Info.GetNumBytes(), cudaMemcpyHostToDevice, m_Ctx->Stream()), "cudaMemcpyAsync H2D");
 }
 
 void B200TensorHandle::CopyOutTo(void* memory) const
 {
-    B200Device& d = B200Device::Get();
-    d.MakeCurrent();
-    B200Check(cudaStreamSynchronize(d.Stream()), "cudaStreamSynchronize");
+    m_Ctx->SyncForMap();
     B200Check(cudaMemcpy(memory, Device(), m_Info.GetNumBytes(), cudaMemcpyDeviceToHost), "cudaMemcpy D2H");
 }
 
 void B200TensorHandle::CopyInFrom(const void* memory)
 {
-    B200Device& d = B200Device::Get();
-    d.MakeCurrent();
-    B200Check(cudaMemcpyAsync(Device(), memory, m_Info.GetNumBytes(), cudaMemcpyHostToDevice, d.Stream()), "cudaMemcpyAsync H2D");
-    B200Check(cudaStreamSynchronize(d.Stream()), "cudaStreamSynchronize");
+    m_Ctx->SyncForMap();
+    B200Check(cudaMemcpyAsync(Device(), memory, m_Info.GetNumBytes(), cudaMemcpyHostToDevice, m_Ctx->Stream()), "cudaMemcpyAsync H2D");
+    B200Check(cudaStreamSynchronize(m_Ctx->Stream()), "cudaStreamSynchronize");
     m_DeviceNewer = false;
 }
 
@@ -178,7 +218,8 @@ void B200TensorHandle::Unimport()
 {
     if (m_Imported && m_Registered)
     {
-        cudaStreamSynchronize(B200Device::Get().Stream());
+        cudaSetDevice(m_Ctx->Device());
+        cudaStreamSynchronize(m_Ctx->Stream());
         if (cudaHostUnregister(m_Imported) != cudaSuccess) { cudaGetLastError(); }
     }
     m_Imported = nullptr;
@@ -201,19 +242,31 @@ void B200TensorHandle::PinIfReused() const
 void B200TensorHandle::SyncImportedToDevice() const
 {
     if (!m_Imported || m_DeviceNewer) { return; }       // not imported, or produced on the device in this inference
-    const uint64_t epoch = B200Device::Epoch();
+    const uint64_t epoch = m_Ctx->Epoch();
     if (m_UploadEpoch == epoch) { return; }
-    B200Device& d = B200Device::Get();
-    d.MakeCurrent();
+    m_Ctx->MakeCurrent();
     PinIfReused();
-    B200Check(cudaMemcpyAsync(Device(), m_Imported, m_Info.GetNumBytes(), cudaMemcpyHostToDevice, d.Stream()), "cudaMemcpyAsync H2D");
+    B200Check(cudaMemcpyAsync(Device(), m_Imported, m_Info.GetNumBytes(), cudaMemcpyHostToDevice, m_Ctx->Stream()), "cudaMemcpyAsync H2D");
     m_UploadEpoch = epoch;
 }
+
+// ---- factory -------------------------------------------------------------------------------------------------
 
 const ITensorHandleFactory::FactoryId& B200TensorHandleFactory::GetIdStatic()
 {
     static const FactoryId s_Id(B200TensorHandleFactoryId());
     return s_Id;
+}
+
+std::shared_ptr<B200Context> B200TensorHandleFactory::Ctx() const
+{
+    if (!m_Ctx) { m_Ctx = B200Context::Shared(); }
+    return m_Ctx;
+}
+
+std::unique_ptr<ITensorHandle> B200TensorHandleFactory::Create(const TensorInfo& info, bool managed) const
+{
+    return std::make_unique<B200TensorHandle>(info, Ctx(), managed ? m_MemoryManager : nullptr);
 }
 
 }  // namespace armnn

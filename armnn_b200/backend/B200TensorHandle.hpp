@@ -1,5 +1,4 @@
-// Device-memory tensor handles of the B200Acc backend, their factory and memory manager, and the per-process
-// device context (device id + the CUDA stream every workload is enqueued on).
+// Device-memory tensor handles of the B200Acc backend, their factory and memory manager.
 //
 // Arm NN moves network inputs and outputs with CopyMemGenericWorkload, which Map()s both handles and memcpy()s
 // (src/backends/backendsCommon/MemCopyWorkload.cpp:51-64), so a device handle owns a pinned host staging buffer:
@@ -12,6 +11,12 @@
 // workload of an inference reads it, and a handle a workload has written is copied straight into the user's memory
 // by the Map() of the core's SyncMemGenericWorkload.  A buffer that comes back for a second inference is page-locked
 // (cudaHostRegister) until Unimport(), so that its transfers are asynchronous DMA.
+//
+// Device memory.  Handles created as "memory managed" take part in the Manage() / Allocate() lifetime protocol of the
+// core (src/armnn/Network.cpp and LoadedNetwork.cpp call Manage() when a tensor is first produced and Allocate() once
+// its last consumer has been created): B200MemoryManager packs them into one device arena in which tensors whose
+// lifetimes do not overlap share bytes, the scheme of RefMemoryManager (src/backends/reference/RefMemoryManager.cpp:
+// 20-103).  All other handles (network inputs and outputs, constants) own their device buffer.
 #pragma once
 
 #include <armnn/backends/IMemoryManager.hpp>
@@ -22,6 +27,10 @@
 #include <cuda_runtime.h>
 
 #include <cstdint>
+#include <memory>
+#include <vector>
+
+#include "B200Context.hpp"
 
 namespace armnn
 {
@@ -29,42 +38,50 @@ namespace armnn
 constexpr const char* B200BackendId() { return "B200Acc"; }
 constexpr const char* B200TensorHandleFactoryId() { return "Nv/B200Acc/TensorHandleFactory"; }
 
-/// Device id and stream shared by every handle and workload of this process (one process drives one GPU;
-/// the device comes from the "DeviceId" backend option, or B200ACC_DEVICE_ID, or 0).
-class B200Device
-{
-public:
-    static B200Device& Get();
-    static void Configure(int deviceId);            // before first use; throws BackendUnavailableException
-    cudaStream_t Stream() const { return m_Stream; }
-    /// Counts inferences (advanced by IBackendContext::AfterEnqueueWorkload): an imported input is uploaded once per epoch.
-    static uint64_t Epoch();
-    static void NextEpoch();
-    int Id() const { return m_Device; }
-    void MakeCurrent() const;
-private:
-    B200Device();
-    int m_Device = 0;
-    cudaStream_t m_Stream = nullptr;
-};
-
 void B200Check(cudaError_t e, const char* what);     // throws armnn::RuntimeException
 void B200CheckStatus(int rc);                        // libb200k status -> armnn::RuntimeException
 
+/// One device arena per network.  Between Manage() and Allocate() a tensor is "live"; a pool (a byte range of the
+/// arena) serves one live tensor at a time and is handed to the next tensor that fits once its user called Allocate().
+/// Acquire() gives the arena device memory, Release() takes it away (IMemoryManager, driven by
+/// LoadedNetwork::AllocateWorkingMemory / FreeWorkingMemory, src/armnn/LoadedNetwork.cpp:1186-1222).
 class B200MemoryManager : public IMemoryManager
 {
 public:
-    void Acquire() override {}                       // handles own their device buffers (see Allocate)
-    void Release() override {}
+    struct Pool
+    {
+        size_t bytes = 0;
+        size_t offset = 0;                           // inside the arena
+        bool free = false;
+    };
+
+    explicit B200MemoryManager(std::shared_ptr<B200Context> ctx = nullptr) : m_Ctx(std::move(ctx)) {}
+    ~B200MemoryManager() override;
+
+    Pool* Manage(size_t bytes);                      // start of a tensor's lifetime: a pool of at least `bytes`
+    void Allocate(Pool* pool);                       // end of its lifetime: the pool may serve a later tensor
+    void* Address(const Pool* pool);                 // device address (acquires the arena on first use)
+
+    void Acquire() override;
+    void Release() override;
+
+    size_t ArenaBytes() const { return m_ArenaBytes; }
+    size_t ManagedBytes() const { return m_ManagedBytes; }   // sum of all managed tensors (what separate buffers would take)
+
+private:
+    std::shared_ptr<B200Context> m_Ctx;
+    std::vector<std::unique_ptr<Pool>> m_Pools;
+    size_t m_ArenaBytes = 0, m_ManagedBytes = 0;
+    void* m_Arena = nullptr;
 };
 
 class B200TensorHandle : public ITensorHandle
 {
 public:
-    explicit B200TensorHandle(const TensorInfo& info);
+    B200TensorHandle(const TensorInfo& info, std::shared_ptr<B200Context> ctx, std::shared_ptr<B200MemoryManager> mgr = nullptr);
     ~B200TensorHandle() override;
 
-    void Manage() override {}
+    void Manage() override;
     void Allocate() override;
     ITensorHandle* GetParent() const override { return nullptr; }
 
@@ -83,6 +100,7 @@ public:
     bool CanBeImported(void* memory, MemorySource source) override { return memory != nullptr && source == MemorySource::Malloc; }
     bool Import(void* memory, MemorySource source) override;
     void Unimport() override;
+    bool IsImported() const { return m_Imported != nullptr; }
     /// For a workload about to read this handle: when it is an imported network input, bring the user's memory to
     /// the device (once per inference).
     void SyncImportedToDevice() const;
@@ -91,13 +109,17 @@ public:
     void* Device() const;
     /// A workload has written the device copy: the next Map() must read it back.
     void MarkDeviceWritten() const { m_DeviceNewer = true; }
+    B200Context& Context() const { return *m_Ctx; }
 
 private:
     B200TensorHandle(const B200TensorHandle&) = delete;
     B200TensorHandle& operator=(const B200TensorHandle&) = delete;
 
     TensorInfo m_Info;
-    mutable void* m_Dev = nullptr;
+    std::shared_ptr<B200Context> m_Ctx;
+    std::shared_ptr<B200MemoryManager> m_Mgr;        // null: the handle owns its buffer
+    B200MemoryManager::Pool* m_Pool = nullptr;
+    mutable void* m_Dev = nullptr;                   // own buffer (unmanaged handles)
     mutable void* m_Host = nullptr;                  // pinned staging
     mutable bool m_DeviceNewer = false;
     mutable bool m_ReadOnlyMapping = false;
@@ -111,18 +133,19 @@ private:
 class B200TensorHandleFactory : public ITensorHandleFactory
 {
 public:
-    explicit B200TensorHandleFactory(std::shared_ptr<B200MemoryManager> mgr) : m_MemoryManager(std::move(mgr)) {}
+    B200TensorHandleFactory(std::shared_ptr<B200Context> ctx, std::shared_ptr<B200MemoryManager> mgr)
+        : m_Ctx(std::move(ctx)), m_MemoryManager(std::move(mgr)) {}
 
     std::unique_ptr<ITensorHandle> CreateSubTensorHandle(ITensorHandle&, TensorShape const&, unsigned int const*) const override
     { return nullptr; }
     std::unique_ptr<ITensorHandle> CreateTensorHandle(const TensorInfo& info) const override
-    { return std::make_unique<B200TensorHandle>(info); }
+    { return Create(info, true); }
     std::unique_ptr<ITensorHandle> CreateTensorHandle(const TensorInfo& info, DataLayout) const override
-    { return std::make_unique<B200TensorHandle>(info); }
-    std::unique_ptr<ITensorHandle> CreateTensorHandle(const TensorInfo& info, const bool) const override
-    { return std::make_unique<B200TensorHandle>(info); }
-    std::unique_ptr<ITensorHandle> CreateTensorHandle(const TensorInfo& info, DataLayout, const bool) const override
-    { return std::make_unique<B200TensorHandle>(info); }
+    { return Create(info, true); }
+    std::unique_ptr<ITensorHandle> CreateTensorHandle(const TensorInfo& info, const bool isMemoryManaged) const override
+    { return Create(info, isMemoryManaged); }
+    std::unique_ptr<ITensorHandle> CreateTensorHandle(const TensorInfo& info, DataLayout, const bool isMemoryManaged) const override
+    { return Create(info, isMemoryManaged); }
 
     static const FactoryId& GetIdStatic();
     const FactoryId& GetId() const override { return GetIdStatic(); }
@@ -132,6 +155,11 @@ public:
     MemorySourceFlags GetImportFlags() const override { return static_cast<MemorySourceFlags>(MemorySource::Malloc); }
 
 private:
+    std::unique_ptr<ITensorHandle> Create(const TensorInfo& info, bool managed) const;
+    /// The optimizer also creates factories (to pick handle strategies) long before any device is needed: the context is
+    /// made on first use.
+    std::shared_ptr<B200Context> Ctx() const;
+    mutable std::shared_ptr<B200Context> m_Ctx;
     std::shared_ptr<B200MemoryManager> m_MemoryManager;
 };
 

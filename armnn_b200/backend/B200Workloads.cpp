@@ -13,10 +13,13 @@
 #include <backendsCommon/MemImportWorkload.hpp>
 #include <backendsCommon/MemSyncWorkload.hpp>
 
+#include <Profiling.hpp>
+
 #include <cstring>
 #include <functional>
 #include <mutex>
 
+#include "B200Timer.hpp"
 #include "b200k.h"
 
 namespace armnn
@@ -49,15 +52,23 @@ void Written(const ITensorHandle* h)
     PolymorphicDowncast<const B200TensorHandle*>(h)->MarkDeviceWritten();
 }
 
-// Small device arrays owned by a workload (per-axis scales, QLstm weights, packed tables, scratch).
+using ContextPtr = std::shared_ptr<B200Context>;
+
+// Small device arrays owned by a workload (per-axis scales, QLstm weights, packed tables, scratch), on the network's GPU.
 struct DeviceBlobs
 {
+    explicit DeviceBlobs(ContextPtr c) : ctx(std::move(c)) {}
+    ContextPtr ctx;
     std::vector<void*> ptrs;
-    ~DeviceBlobs() { for (void* p : ptrs) { cudaFree(p); } }
+    ~DeviceBlobs()
+    {
+        if (!ptrs.empty()) { cudaSetDevice(ctx->Device()); }
+        for (void* p : ptrs) { cudaFree(p); }
+    }
     void* Alloc(size_t bytes)
     {
         void* p = nullptr;
-        B200Device::Get().MakeCurrent();
+        ctx->MakeCurrent();
         B200Check(cudaMalloc(&p, bytes ? bytes : 16), "cudaMalloc");
         ptrs.push_back(p);
         return p;
@@ -108,39 +119,51 @@ void Clamp(const ActivationDescriptor* act, const TensorInfo& out, int32_t& lo, 
                                            ToB200k(out.GetDataType()), &lo, &hi));
 }
 
-// Generic workload: `launch` is built by the factory and owns everything it needs.
+// Generic workload: `launch` is built by the factory and owns everything it needs.  Execute() hands the launch to the
+// network's context, which runs it on the network's stream, records it into the CUDA graph of the workload queue, or
+// skips it because the graph launched by the queue's first workload already contains it.  With the Arm NN profiler
+// enabled the launch is bracketed by a profiling event that carries the host wall clock and the device time.
 template <typename QueueDescriptor>
 class B200Workload : public BaseWorkload<QueueDescriptor>
 {
 public:
     using Launch = std::function<void(const QueueDescriptor&, cudaStream_t)>;
-    B200Workload(const QueueDescriptor& d, const WorkloadInfo& info, Launch launch)
-        : BaseWorkload<QueueDescriptor>(d, info), m_Launch(std::move(launch)) {}
+    B200Workload(const QueueDescriptor& d, const WorkloadInfo& info, ContextPtr ctx, Launch launch, bool launchesEveryInference = true)
+        : BaseWorkload<QueueDescriptor>(d, info), m_Ctx(std::move(ctx)), m_Launch(std::move(launch))
+    {
+        m_Index = m_Ctx->Register(launchesEveryInference);
+    }
     void Execute() const override
     {
-        B200Device& dev = B200Device::Get();
-        dev.MakeCurrent();
-        for (ITensorHandle* h : this->m_Data.m_Inputs) { PolymorphicDowncast<const B200TensorHandle*>(h)->SyncImportedToDevice(); }
-        m_Launch(this->m_Data, dev.Stream());
+        ARMNN_SCOPED_PROFILING_EVENT_WITH_INSTRUMENTS(BackendId(B200BackendId()), this->GetGuid(), this->GetName() + "_Execute",
+                                                      WallClockTimer(), CudaEventTimer(m_Ctx->Stream(), m_Ctx->Device()));
+        std::vector<const B200TensorHandle*> reads;
+        reads.reserve(this->m_Data.m_Inputs.size());
+        for (ITensorHandle* h : this->m_Data.m_Inputs) { reads.push_back(PolymorphicDowncast<const B200TensorHandle*>(h)); }
+        m_Ctx->Run(m_Index, reads, [this](cudaStream_t s) { m_Launch(this->m_Data, s); });
         for (ITensorHandle* h : this->m_Data.m_Outputs) { Written(h); }
     }
     // handles are resolved at Execute time, so the core may swap in its pre-imported handles
-    // (src/armnn/LoadedNetwork.cpp:821-833, 877-894)
+    // (src/armnn/LoadedNetwork.cpp:821-833, 877-894); a recorded graph holds the old addresses and is dropped
     bool SupportsTensorHandleReplacement() const override { return true; }
-    void ReplaceInputTensorHandle(ITensorHandle* h, unsigned int slot) override { this->m_Data.m_Inputs[slot] = h; }
-    void ReplaceOutputTensorHandle(ITensorHandle* h, unsigned int slot) override { this->m_Data.m_Outputs[slot] = h; }
+    void ReplaceInputTensorHandle(ITensorHandle* h, unsigned int slot) override { this->m_Data.m_Inputs[slot] = h; m_Ctx->Invalidate(); }
+    void ReplaceOutputTensorHandle(ITensorHandle* h, unsigned int slot) override { this->m_Data.m_Outputs[slot] = h; m_Ctx->Invalidate(); }
 private:
+    ContextPtr m_Ctx;
     Launch m_Launch;
+    int m_Index = 0;
 };
 
 template <typename QD>
-std::unique_ptr<IWorkload> Make(const QueueDescriptor& d, const WorkloadInfo& info, typename B200Workload<QD>::Launch fn)
+std::unique_ptr<IWorkload> Make(const QueueDescriptor& d, const WorkloadInfo& info, const ContextPtr& ctx,
+                                typename B200Workload<QD>::Launch fn, bool launchesEveryInference = true)
 {
-    return std::make_unique<B200Workload<QD>>(*PolymorphicDowncast<const QD*>(&d), info, std::move(fn));
+    return std::make_unique<B200Workload<QD>>(*PolymorphicDowncast<const QD*>(&d), info, ctx, std::move(fn), launchesEveryInference);
 }
 
 struct ConvState
 {
+    explicit ConvState(const ContextPtr& ctx) : blobs(ctx) {}
     b200k_conv2d_params p;
     DeviceBlobs blobs;
     void* packed = nullptr;
@@ -166,6 +189,7 @@ void FillConv(ConvState& st, const Descriptor& prm, const TensorInfo& x, const T
     p.stride_h = prm.m_StrideY; p.stride_w = prm.m_StrideX;
     p.pad_top = prm.m_PadTop; p.pad_left = prm.m_PadLeft;
     p.dil_h = prm.m_DilationY; p.dil_w = prm.m_DilationX;
+    p.selftest_us = st.blobs.ctx->SelfTestUs();
     if (!depthwise)
     {
         st.packed = st.blobs.Alloc(b200k_conv2d_pack_bytes(p.oc, p.kh, p.kw, p.c));
@@ -184,15 +208,15 @@ void LaunchConv(ConvState& st, cudaStream_t s)
 }
 
 template <typename QD>
-std::unique_ptr<IWorkload> MakeConv(const QueueDescriptor& d, const WorkloadInfo& info, bool depthwise)
+std::unique_ptr<IWorkload> MakeConv(const QueueDescriptor& d, const WorkloadInfo& info, const ContextPtr& ctx, bool depthwise)
 {
     const QD& qd = *PolymorphicDowncast<const QD*>(&d);
-    auto st = std::make_shared<ConvState>();
+    auto st = std::make_shared<ConvState>(ctx);
     const TensorInfo& y = info.m_OutputTensorInfos[0];
     FillConv(*st, qd.m_Parameters, info.m_InputTensorInfos[0], info.m_InputTensorInfos[1],
              info.m_InputTensorInfos.size() > 2 ? &info.m_InputTensorInfos[2] : nullptr, y, depthwise);
     Clamp(qd.template GetAdditionalInformation<ActivationDescriptor>(), y, st->p.clamp_lo, st->p.clamp_hi);
-    return Make<QD>(d, info, [st, depthwise](const QD& data, cudaStream_t s)
+    return Make<QD>(d, info, ctx, [st, depthwise](const QD& data, cudaStream_t s)
     {
         b200k_conv2d_params& q = st->p;
         q.x.data = Dev(data.m_Inputs[0]);
@@ -206,7 +230,7 @@ std::unique_ptr<IWorkload> MakeConv(const QueueDescriptor& d, const WorkloadInfo
 
 // Convolution2d -> Add [-> Activation] folded into one PreCompiled layer by B200Backend::OptimizeSubgraphView:
 // inputs (data, weights[, bias], other operand), output = the Add's (Activation's) output.
-std::unique_ptr<IWorkload> MakeFusedConvAdd(const QueueDescriptor& d, const WorkloadInfo& info, const B200FusedConvAdd& fused)
+std::unique_ptr<IWorkload> MakeFusedConvAdd(const QueueDescriptor& d, const WorkloadInfo& info, const ContextPtr& ctx, const B200FusedConvAdd& fused)
 {
     const size_t nIn = info.m_InputTensorInfos.size();
     const bool bias = fused.m_Convolution.m_BiasEnabled;
@@ -214,7 +238,7 @@ std::unique_ptr<IWorkload> MakeFusedConvAdd(const QueueDescriptor& d, const Work
     {
         throw InvalidArgumentException("B200Acc: fused convolution + Add expects (data, weights[, bias], operand) -> output");
     }
-    auto st = std::make_shared<ConvState>();
+    auto st = std::make_shared<ConvState>(ctx);
     const TensorInfo& other = info.m_InputTensorInfos[nIn - 1];
     const TensorInfo& out = info.m_OutputTensorInfos[0];
     FillConv(*st, fused.m_Convolution, info.m_InputTensorInfos[0], info.m_InputTensorInfos[1],
@@ -222,7 +246,7 @@ std::unique_ptr<IWorkload> MakeFusedConvAdd(const QueueDescriptor& d, const Work
     st->p.add_operand = Operand(other, st->blobs);
     st->p.add_out = Operand(out, st->blobs);
     Clamp(fused.m_HasActivation ? &fused.m_Activation : nullptr, out, st->p.clamp_lo, st->p.clamp_hi);
-    return Make<PreCompiledQueueDescriptor>(d, info, [st, bias, nIn](const PreCompiledQueueDescriptor& data, cudaStream_t s)
+    return Make<PreCompiledQueueDescriptor>(d, info, ctx, [st, bias, nIn](const PreCompiledQueueDescriptor& data, cudaStream_t s)
     {
         b200k_conv2d_params& q = st->p;
         q.x.data = Dev(data.m_Inputs[0]);
@@ -236,16 +260,17 @@ std::unique_ptr<IWorkload> MakeFusedConvAdd(const QueueDescriptor& d, const Work
 
 struct FcState
 {
+    explicit FcState(const ContextPtr& ctx) : blobs(ctx) {}
     b200k_fc_params p;
     DeviceBlobs blobs;
     void* packed = nullptr;
     std::once_flag once;
 };
 
-std::unique_ptr<IWorkload> MakeFc(const QueueDescriptor& d, const WorkloadInfo& info)
+std::unique_ptr<IWorkload> MakeFc(const QueueDescriptor& d, const WorkloadInfo& info, const ContextPtr& ctx)
 {
     const auto& qd = *PolymorphicDowncast<const FullyConnectedQueueDescriptor*>(&d);
-    auto st = std::make_shared<FcState>();
+    auto st = std::make_shared<FcState>(ctx);
     b200k_fc_params& p = st->p;
     std::memset(&p, 0, sizeof(p));
     const TensorInfo& x = info.m_InputTensorInfos[0];
@@ -261,7 +286,7 @@ std::unique_ptr<IWorkload> MakeFc(const QueueDescriptor& d, const WorkloadInfo& 
     p.transpose_w = qd.m_Parameters.m_TransposeWeightMatrix ? 1 : 0;
     Clamp(qd.GetAdditionalInformation<ActivationDescriptor>(), y, p.clamp_lo, p.clamp_hi);
     if (p.transpose_w) { st->packed = st->blobs.Alloc(b200k_conv2d_pack_bytes(p.n, 1, 1, p.k)); }
-    return Make<FullyConnectedQueueDescriptor>(d, info, [st](const FullyConnectedQueueDescriptor& data, cudaStream_t s)
+    return Make<FullyConnectedQueueDescriptor>(d, info, ctx, [st](const FullyConnectedQueueDescriptor& data, cudaStream_t s)
     {
         b200k_fc_params& q = st->p;
         q.x.data = Dev(data.m_Inputs[0]);
@@ -286,14 +311,15 @@ std::unique_ptr<IWorkload> MakeFc(const QueueDescriptor& d, const WorkloadInfo& 
 template <typename P>
 struct SimpleState
 {
+    explicit SimpleState(const ContextPtr& ctx) : blobs(ctx) {}
     P p;
     DeviceBlobs blobs;
 };
 
-std::unique_ptr<IWorkload> MakeEltwise(const QueueDescriptor& d, const WorkloadInfo& info, BinaryOperation op,
+std::unique_ptr<IWorkload> MakeEltwise(const QueueDescriptor& d, const WorkloadInfo& info, const ContextPtr& ctx, BinaryOperation op,
                                        const ActivationDescriptor* act)
 {
-    auto st = std::make_shared<SimpleState<b200k_eltwise_params>>();
+    auto st = std::make_shared<SimpleState<b200k_eltwise_params>>(ctx);
     b200k_eltwise_params& p = st->p;
     std::memset(&p, 0, sizeof(p));
     const TensorInfo& a = info.m_InputTensorInfos[0];
@@ -319,25 +345,25 @@ std::unique_ptr<IWorkload> MakeEltwise(const QueueDescriptor& d, const WorkloadI
     };
     if (auto* e = dynamic_cast<const ElementwiseBinaryQueueDescriptor*>(&d))
     {
-        return std::make_unique<B200Workload<ElementwiseBinaryQueueDescriptor>>(*e, info, fn);
+        return std::make_unique<B200Workload<ElementwiseBinaryQueueDescriptor>>(*e, info, ctx, fn);
     }
     if (auto* e = dynamic_cast<const AdditionQueueDescriptor*>(&d))
     {
-        return std::make_unique<B200Workload<AdditionQueueDescriptor>>(*e, info, fn);
+        return std::make_unique<B200Workload<AdditionQueueDescriptor>>(*e, info, ctx, fn);
     }
     if (auto* e = dynamic_cast<const MultiplicationQueueDescriptor*>(&d))
     {
-        return std::make_unique<B200Workload<MultiplicationQueueDescriptor>>(*e, info, fn);
+        return std::make_unique<B200Workload<MultiplicationQueueDescriptor>>(*e, info, ctx, fn);
     }
     return nullptr;
 }
 
 // Device copies of the QLstm weights: the descriptor's ConstTensorHandles are released by the layer right after
 // CreateWorkload (src/armnn/LoadedNetwork.cpp:396), as RefQLstmWorkload's AssignScopedTensorHandle copies show.
-std::unique_ptr<IWorkload> MakeQLstm(const QueueDescriptor& d, const WorkloadInfo& info)
+std::unique_ptr<IWorkload> MakeQLstm(const QueueDescriptor& d, const WorkloadInfo& info, const ContextPtr& ctx)
 {
     const auto& qd = *PolymorphicDowncast<const QLstmQueueDescriptor*>(&d);
-    auto st = std::make_shared<SimpleState<b200k_qlstm_params>>();
+    auto st = std::make_shared<SimpleState<b200k_qlstm_params>>(ctx);
     b200k_qlstm_params& p = st->p;
     std::memset(&p, 0, sizeof(p));
     const TensorInfo& x = info.m_InputTensorInfos[0];
@@ -402,7 +428,7 @@ std::unique_ptr<IWorkload> MakeQLstm(const QueueDescriptor& d, const WorkloadInf
     p.cell_intermediate_scale = prm.m_CellIntermediateScale;
     p.output_intermediate_scale = prm.m_OutputIntermediateScale;
     p.hidden_state_scale = prm.m_HiddenStateScale; p.hidden_state_zp = prm.m_HiddenStateZeroPoint;
-    return Make<QLstmQueueDescriptor>(d, info, [st](const QLstmQueueDescriptor& data, cudaStream_t s)
+    return Make<QLstmQueueDescriptor>(d, info, ctx, [st](const QLstmQueueDescriptor& data, cudaStream_t s)
     {
         b200k_qlstm_params& q = st->p;
         q.input = static_cast<const int8_t*>(Dev(data.m_Inputs[0]));
@@ -417,8 +443,8 @@ std::unique_ptr<IWorkload> MakeQLstm(const QueueDescriptor& d, const WorkloadInf
 
 }  // namespace
 
-B200WorkloadFactory::B200WorkloadFactory(const std::shared_ptr<B200MemoryManager>& memoryManager)
-    : m_MemoryManager(memoryManager) {}
+B200WorkloadFactory::B200WorkloadFactory(const std::shared_ptr<B200Context>& ctx, const std::shared_ptr<B200MemoryManager>& memoryManager)
+    : m_Ctx(ctx), m_MemoryManager(memoryManager) {}
 
 const BackendId& B200WorkloadFactory::GetBackendId() const
 {
@@ -432,19 +458,20 @@ bool B200WorkloadFactory::IsLayerSupported(const IConnectableLayer& layer, Optio
     return IWorkloadFactory::IsLayerSupported(s_Id, layer, dataType, reason);
 }
 
-std::unique_ptr<ITensorHandle> B200WorkloadFactory::CreateTensorHandle(const TensorInfo& info, const bool) const
+std::unique_ptr<ITensorHandle> B200WorkloadFactory::CreateTensorHandle(const TensorInfo& info, const bool isMemoryManaged) const
 {
-    return std::make_unique<B200TensorHandle>(info);
+    return std::make_unique<B200TensorHandle>(info, m_Ctx, isMemoryManaged ? m_MemoryManager : nullptr);
 }
 
-std::unique_ptr<ITensorHandle> B200WorkloadFactory::CreateTensorHandle(const TensorInfo& info, DataLayout, const bool) const
+std::unique_ptr<ITensorHandle> B200WorkloadFactory::CreateTensorHandle(const TensorInfo& info, DataLayout, const bool isMemoryManaged) const
 {
-    return std::make_unique<B200TensorHandle>(info);
+    return std::make_unique<B200TensorHandle>(info, m_Ctx, isMemoryManaged ? m_MemoryManager : nullptr);
 }
 
 std::unique_ptr<IWorkload> B200WorkloadFactory::CreateWorkload(LayerType type, const QueueDescriptor& d,
                                                                const WorkloadInfo& info) const
 {
+    const ContextPtr& ctx = m_Ctx;
     switch (type)
     {
         case LayerType::Input:
@@ -462,7 +489,7 @@ std::unique_ptr<IWorkload> B200WorkloadFactory::CreateWorkload(LayerType type, c
             // queue (LoadedNetwork.cpp:1267): like ClConstantWorkload (src/backends/cl/workloads/ClConstantWorkload.cpp:61)
             // only the first execution copies.
             auto ranOnce = std::make_shared<bool>(false);
-            return Make<ConstantQueueDescriptor>(d, info, [ranOnce](const ConstantQueueDescriptor& data, cudaStream_t s)
+            return Make<ConstantQueueDescriptor>(d, info, ctx, [ranOnce](const ConstantQueueDescriptor& data, cudaStream_t s)
             {
                 if (*ranOnce) { return; }
                 const ConstTensorHandle* src = data.m_LayerOutput;
@@ -471,43 +498,43 @@ std::unique_ptr<IWorkload> B200WorkloadFactory::CreateWorkload(LayerType type, c
                                           src->GetTensorInfo().GetNumBytes(), cudaMemcpyHostToDevice, s), "cudaMemcpyAsync H2D");
                 B200Check(cudaStreamSynchronize(s), "cudaStreamSynchronize");
                 *ranOnce = true;
-            });
+            }, false);
         }
         case LayerType::Reshape:
         {
             const size_t bytes = info.m_InputTensorInfos[0].GetNumBytes();
-            return Make<ReshapeQueueDescriptor>(d, info, [bytes](const ReshapeQueueDescriptor& data, cudaStream_t s)
+            return Make<ReshapeQueueDescriptor>(d, info, ctx, [bytes](const ReshapeQueueDescriptor& data, cudaStream_t s)
             {
                 B200Check(cudaMemcpyAsync(Dev(data.m_Outputs[0]), Dev(data.m_Inputs[0]), bytes, cudaMemcpyDeviceToDevice, s),
                           "cudaMemcpyAsync D2D");
             });
         }
         case LayerType::Convolution2d:
-            return MakeConv<Convolution2dQueueDescriptor>(d, info, false);
+            return MakeConv<Convolution2dQueueDescriptor>(d, info, ctx, false);
         case LayerType::DepthwiseConvolution2d:
-            return MakeConv<DepthwiseConvolution2dQueueDescriptor>(d, info, true);
+            return MakeConv<DepthwiseConvolution2dQueueDescriptor>(d, info, ctx, true);
         case LayerType::FullyConnected:
-            return MakeFc(d, info);
+            return MakeFc(d, info, ctx);
         case LayerType::ElementwiseBinary:
         {
             const auto& qd = *PolymorphicDowncast<const ElementwiseBinaryQueueDescriptor*>(&d);
-            return MakeEltwise(d, info, qd.m_Parameters.m_Operation, qd.GetAdditionalInformation<ActivationDescriptor>());
+            return MakeEltwise(d, info, ctx, qd.m_Parameters.m_Operation, qd.GetAdditionalInformation<ActivationDescriptor>());
         }
         case LayerType::Addition:
-            return MakeEltwise(d, info, BinaryOperation::Add, d.GetAdditionalInformation<ActivationDescriptor>());
+            return MakeEltwise(d, info, ctx, BinaryOperation::Add, d.GetAdditionalInformation<ActivationDescriptor>());
         case LayerType::Multiplication:
-            return MakeEltwise(d, info, BinaryOperation::Mul, d.GetAdditionalInformation<ActivationDescriptor>());
+            return MakeEltwise(d, info, ctx, BinaryOperation::Mul, d.GetAdditionalInformation<ActivationDescriptor>());
         case LayerType::Activation:
         {
             const auto& qd = *PolymorphicDowncast<const ActivationQueueDescriptor*>(&d);
-            auto st = std::make_shared<SimpleState<b200k_activation_params>>();
+            auto st = std::make_shared<SimpleState<b200k_activation_params>>(ctx);
             std::memset(&st->p, 0, sizeof(st->p));
             st->p.x = Operand(info.m_InputTensorInfos[0], st->blobs);
             st->p.y = Operand(info.m_OutputTensorInfos[0], st->blobs);
             st->p.count = info.m_InputTensorInfos[0].GetNumElements();
             st->p.function = static_cast<int32_t>(qd.m_Parameters.m_Function);
             st->p.a = qd.m_Parameters.m_A; st->p.b = qd.m_Parameters.m_B;
-            return Make<ActivationQueueDescriptor>(d, info, [st](const ActivationQueueDescriptor& data, cudaStream_t s)
+            return Make<ActivationQueueDescriptor>(d, info, ctx, [st](const ActivationQueueDescriptor& data, cudaStream_t s)
             {
                 st->p.x.data = Dev(data.m_Inputs[0]); st->p.y.data = Dev(data.m_Outputs[0]);
                 B200CheckStatus(b200k_activation_q8(&st->p, s));
@@ -518,7 +545,7 @@ std::unique_ptr<IWorkload> B200WorkloadFactory::CreateWorkload(LayerType type, c
             const auto& qd = *PolymorphicDowncast<const Pooling2dQueueDescriptor*>(&d);
             const auto& q = qd.m_Parameters;
             if (q.m_DataLayout != DataLayout::NHWC) { throw InvalidArgumentException("B200Acc: NHWC only"); }
-            auto st = std::make_shared<SimpleState<b200k_pool2d_params>>();
+            auto st = std::make_shared<SimpleState<b200k_pool2d_params>>(ctx);
             b200k_pool2d_params& p = st->p;
             std::memset(&p, 0, sizeof(p));
             const TensorInfo& x = info.m_InputTensorInfos[0];
@@ -529,7 +556,7 @@ std::unique_ptr<IWorkload> B200WorkloadFactory::CreateWorkload(LayerType type, c
             p.pool_h = q.m_PoolHeight; p.pool_w = q.m_PoolWidth; p.stride_h = q.m_StrideY; p.stride_w = q.m_StrideX;
             p.pad_top = q.m_PadTop; p.pad_bottom = q.m_PadBottom; p.pad_left = q.m_PadLeft; p.pad_right = q.m_PadRight;
             p.pool_type = static_cast<int32_t>(q.m_PoolType); p.padding_method = static_cast<int32_t>(q.m_PaddingMethod);
-            return Make<Pooling2dQueueDescriptor>(d, info, [st](const Pooling2dQueueDescriptor& data, cudaStream_t s)
+            return Make<Pooling2dQueueDescriptor>(d, info, ctx, [st](const Pooling2dQueueDescriptor& data, cudaStream_t s)
             {
                 st->p.x.data = Dev(data.m_Inputs[0]); st->p.y.data = Dev(data.m_Outputs[0]);
                 B200CheckStatus(b200k_pool2d_q8(&st->p, s));
@@ -537,13 +564,13 @@ std::unique_ptr<IWorkload> B200WorkloadFactory::CreateWorkload(LayerType type, c
         }
         case LayerType::Mean:
         {
-            auto st = std::make_shared<SimpleState<b200k_mean_params>>();
+            auto st = std::make_shared<SimpleState<b200k_mean_params>>(ctx);
             b200k_mean_params& p = st->p;
             std::memset(&p, 0, sizeof(p));
             const TensorInfo& x = info.m_InputTensorInfos[0];
             p.x = Operand(x, st->blobs); p.y = Operand(info.m_OutputTensorInfos[0], st->blobs);
             p.n = x.GetShape()[0]; p.h = x.GetShape()[1]; p.wd = x.GetShape()[2]; p.c = x.GetShape()[3];
-            return Make<MeanQueueDescriptor>(d, info, [st](const MeanQueueDescriptor& data, cudaStream_t s)
+            return Make<MeanQueueDescriptor>(d, info, ctx, [st](const MeanQueueDescriptor& data, cudaStream_t s)
             {
                 st->p.x.data = Dev(data.m_Inputs[0]); st->p.y.data = Dev(data.m_Outputs[0]);
                 B200CheckStatus(b200k_mean_hw_q8(&st->p, s));
@@ -552,7 +579,7 @@ std::unique_ptr<IWorkload> B200WorkloadFactory::CreateWorkload(LayerType type, c
         case LayerType::Softmax:
         {
             const auto& qd = *PolymorphicDowncast<const SoftmaxQueueDescriptor*>(&d);
-            auto st = std::make_shared<SimpleState<b200k_softmax_params>>();
+            auto st = std::make_shared<SimpleState<b200k_softmax_params>>(ctx);
             b200k_softmax_params& p = st->p;
             std::memset(&p, 0, sizeof(p));
             const TensorInfo& x = info.m_InputTensorInfos[0];
@@ -564,7 +591,7 @@ std::unique_ptr<IWorkload> B200WorkloadFactory::CreateWorkload(LayerType type, c
             for (int i = axis + 1; i < rank; ++i) { p.inner *= x.GetShape()[i]; }
             p.axis_size = x.GetShape()[axis];
             p.beta = qd.m_Parameters.m_Beta;
-            return Make<SoftmaxQueueDescriptor>(d, info, [st](const SoftmaxQueueDescriptor& data, cudaStream_t s)
+            return Make<SoftmaxQueueDescriptor>(d, info, ctx, [st](const SoftmaxQueueDescriptor& data, cudaStream_t s)
             {
                 st->p.x.data = Dev(data.m_Inputs[0]); st->p.y.data = Dev(data.m_Outputs[0]);
                 B200CheckStatus(b200k_softmax_q8(&st->p, s));
@@ -573,7 +600,7 @@ std::unique_ptr<IWorkload> B200WorkloadFactory::CreateWorkload(LayerType type, c
         case LayerType::Quantize:
         case LayerType::Dequantize:
         {
-            auto st = std::make_shared<SimpleState<b200k_convert_params>>();
+            auto st = std::make_shared<SimpleState<b200k_convert_params>>(ctx);
             std::memset(&st->p, 0, sizeof(st->p));
             st->p.x = Operand(info.m_InputTensorInfos[0], st->blobs);
             st->p.y = Operand(info.m_OutputTensorInfos[0], st->blobs);
@@ -583,13 +610,13 @@ std::unique_ptr<IWorkload> B200WorkloadFactory::CreateWorkload(LayerType type, c
                 st->p.x.data = Dev(data.m_Inputs[0]); st->p.y.data = Dev(data.m_Outputs[0]);
                 B200CheckStatus(b200k_convert_q(&st->p, s));
             };
-            if (type == LayerType::Quantize) { return Make<QuantizeQueueDescriptor>(d, info, fn); }
-            return Make<DequantizeQueueDescriptor>(d, info, fn);
+            if (type == LayerType::Quantize) { return Make<QuantizeQueueDescriptor>(d, info, ctx, fn); }
+            return Make<DequantizeQueueDescriptor>(d, info, ctx, fn);
         }
         case LayerType::BatchMatMul:
         {
             const auto& qd = *PolymorphicDowncast<const BatchMatMulQueueDescriptor*>(&d);
-            auto st = std::make_shared<SimpleState<b200k_bmm_params>>();
+            auto st = std::make_shared<SimpleState<b200k_bmm_params>>(ctx);
             b200k_bmm_params& p = st->p;
             std::memset(&p, 0, sizeof(p));
             const TensorInfo& x = info.m_InputTensorInfos[0];
@@ -605,20 +632,47 @@ std::unique_ptr<IWorkload> B200WorkloadFactory::CreateWorkload(LayerType type, c
             const int by = static_cast<int>(y.GetNumElements() / (y.GetShape()[ry - 1] * y.GetShape()[ry - 2]));
             p.batch_stride_x = (bx == p.batch && p.batch > 1) ? static_cast<int64_t>(p.m) * p.k : 0;
             p.batch_stride_y = (by == p.batch && p.batch > 1) ? static_cast<int64_t>(p.k) * p.n : 0;
-            return Make<BatchMatMulQueueDescriptor>(d, info, [st](const BatchMatMulQueueDescriptor& data, cudaStream_t s)
+            return Make<BatchMatMulQueueDescriptor>(d, info, ctx, [st](const BatchMatMulQueueDescriptor& data, cudaStream_t s)
             {
                 st->p.x.data = Dev(data.m_Inputs[0]); st->p.y.data = Dev(data.m_Inputs[1]); st->p.out.data = Dev(data.m_Outputs[0]);
                 B200CheckStatus(b200k_batch_matmul_q8(&st->p, s));
             });
         }
+        case LayerType::Pad:
+        {
+            // only Pad layers that B200Backend::OptimizeSubgraphView could not fold into their consumer get here
+            const auto& qd = *PolymorphicDowncast<const PadQueueDescriptor*>(&d);
+            auto st = std::make_shared<SimpleState<b200k_pad_params>>(ctx);
+            b200k_pad_params& p = st->p;
+            std::memset(&p, 0, sizeof(p));
+            const TensorInfo& x = info.m_InputTensorInfos[0];
+            p.x = Operand(x, st->blobs); p.y = Operand(info.m_OutputTensorInfos[0], st->blobs);
+            p.rank = static_cast<int32_t>(x.GetNumDimensions());
+            if (p.rank > 4 || qd.m_Parameters.m_PadList.size() != x.GetNumDimensions())
+            {
+                throw InvalidArgumentException("B200Acc: Pad needs rank <= 4 and one (before, after) pair per dimension");
+            }
+            for (int i = 0; i < p.rank; ++i)
+            {
+                p.shape[i] = x.GetShape()[i];
+                p.pad_before[i] = qd.m_Parameters.m_PadList[i].first;
+                p.pad_after[i] = qd.m_Parameters.m_PadList[i].second;
+            }
+            p.pad_value = qd.m_Parameters.m_PadValue;
+            return Make<PadQueueDescriptor>(d, info, ctx, [st](const PadQueueDescriptor& data, cudaStream_t s)
+            {
+                st->p.x.data = Dev(data.m_Inputs[0]); st->p.y.data = Dev(data.m_Outputs[0]);
+                B200CheckStatus(b200k_pad_q(&st->p, s));
+            });
+        }
         case LayerType::QLstm:
-            return MakeQLstm(d, info);
+            return MakeQLstm(d, info, ctx);
         case LayerType::PreCompiled:
         {
             const auto& qd = *PolymorphicDowncast<const PreCompiledQueueDescriptor*>(&d);
             const auto* fused = static_cast<const B200FusedConvAdd*>(qd.m_PreCompiledObject);
             if (!fused || fused->m_Magic != B200FusedConvAdd::Magic) { return nullptr; }
-            return MakeFusedConvAdd(d, info, *fused);
+            return MakeFusedConvAdd(d, info, ctx, *fused);
         }
         default:
             return nullptr;       // LoadedNetwork turns a null workload into an exception: there is no CPU fallback

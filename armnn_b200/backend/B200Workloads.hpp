@@ -31,7 +31,7 @@ struct B200FusedConvAdd
 class B200WorkloadFactory : public IWorkloadFactory
 {
 public:
-    explicit B200WorkloadFactory(const std::shared_ptr<B200MemoryManager>& memoryManager);
+    B200WorkloadFactory(const std::shared_ptr<B200Context>& ctx, const std::shared_ptr<B200MemoryManager>& memoryManager);
 
     const BackendId& GetBackendId() const override;
 
@@ -50,6 +50,7 @@ public:
                                               const WorkloadInfo& info) const override;
 
 private:
+    std::shared_ptr<B200Context> m_Ctx;                  ///< the network's GPU, stream and workload queue
     std::shared_ptr<B200MemoryManager> m_MemoryManager;
 };
 

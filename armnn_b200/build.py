@@ -76,7 +76,8 @@ def armnn_root():
 def build_plugin(force=False, verbose=False):
     """Compile the Arm NN backend plugin against the Arm NN headers; skipped when they are absent."""
     root = armnn_root()
-    srcs = sorted(glob.glob(os.path.join(PLUGIN_DIR, "*.cpp")) + glob.glob(os.path.join(PLUGIN_DIR, "workloads", "*.cpp")))
+    # B200RegistryInitializer.cpp belongs to the in-tree (static) build only: the runtime registers a dynamic backend itself
+    srcs = sorted(f for f in glob.glob(os.path.join(PLUGIN_DIR, "*.cpp")) if not f.endswith("B200RegistryInitializer.cpp"))
     if root is None or not srcs:
         return None
     hdrs = glob.glob(os.path.join(PLUGIN_DIR, "*.hpp")) + glob.glob(os.path.join(PLUGIN_DIR, "workloads", "*.hpp")) + \
@@ -93,9 +94,32 @@ def build_plugin(force=False, verbose=False):
     return PLUGIN
 
 
+def armnn_lib_dir():
+    """Directory with a built libarmnn.so: $ARMNN_LIB_DIR, else oracle/_ref of this repository."""
+    return os.environ.get("ARMNN_LIB_DIR") or os.path.join(ROOT, "oracle", "_ref")
+
+
+def build_host_binding(force=False, verbose=False):
+    """armnn_b200/host/libarmnn_capi.so: the C binding of the Arm NN runtime API that armnn_b200.armnn_host loads.
+    Needs the Arm NN headers ($ARMNN_ROOT) and a libarmnn.so to link against; skipped otherwise."""
+    root, libdir = armnn_root(), armnn_lib_dir()
+    src = os.path.join(HERE, "host", "armnn_capi.cpp")
+    out = os.path.join(HERE, "host", "libarmnn_capi.so")
+    if root is None or not os.path.exists(os.path.join(libdir, "libarmnn.so")):
+        return None
+    if not (force or _newer(out, [src, os.path.join(ROOT, "include", "b200k.h"), os.path.join(libdir, "libarmnn.so")])):
+        return out
+    incs = ["include", "profiling", "profiling/common/include", "profiling/client/include"]
+    cmd = ["g++", "-std=c++17", "-O2", "-fPIC", "-shared", "-w", "-DNDEBUG", "-o", out, src] + \
+        ["-I" + os.path.join(root, i) for i in incs] + ["-L" + libdir, "-larmnn", "-Wl,-rpath,$ORIGIN/" + os.path.relpath(libdir, os.path.join(HERE, "host")), "-lpthread"]
+    _run(cmd, verbose)
+    return out
+
+
 def build_all(force=False, verbose=False):
     build_kernels(force, verbose)
     build_plugin(force, verbose)
+    build_host_binding(force, verbose)
 
 
 if __name__ == "__main__":

@@ -104,6 +104,7 @@ extern "C" size_t b200k_sizeof_params(int which)
         case 7: return sizeof(b200k_softmax_params);
         case 8: return sizeof(b200k_convert_params);
         case 9: return sizeof(b200k_qlstm_params);
+        case 10: return sizeof(b200k_pad_params);
         default: return 0;
     }
 }

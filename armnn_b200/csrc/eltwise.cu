@@ -172,3 +172,56 @@ extern "C" int b200k_convert_q(const b200k_convert_params* p, void* stream)
     B200K_REQUIRE(p, B200K_E_INVALID, "convert_q: null params");
     return launch_unary(p->x, p->y, p->count, -1, 0.f, 0.f, stream, "convert_q");
 }
+
+// ---- Pad ------------------------------------------------------------------------------------------------------
+
+namespace b200k {
+
+struct PadArgs { QView x, y; int rank; int in_shape[4], out_shape[4], before[4]; float pad_value; long long count; };
+
+// armnn::Pad (src/backends/reference/workloads/Pad.cpp:37-170): every output element is either the input element at
+// the shifted position, re-encoded with the output's quantisation, or the pad value.  For a quantised output the
+// pad value is already a quantised number: the reference encodes it with scale 1 and offset 0 (Pad.cpp:76-83).
+__global__ void __launch_bounds__(256) pad_kernel(const PadArgs a)
+{
+    pdl_enter();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= a.count) return;
+    long long rest = i, src = 0, stride = 1;
+    bool inside = true;
+    // innermost dimension first: build the source index while peeling coordinates off the flat output index
+    int coord[4];
+    for (int d = a.rank - 1; d >= 0; --d) { coord[d] = (int)(rest % a.out_shape[d]); rest /= a.out_shape[d]; }
+    for (int d = a.rank - 1; d >= 0; --d) {
+        const int c = coord[d] - a.before[d];
+        inside = inside && c >= 0 && c < a.in_shape[d];
+        src += (long long)c * stride;
+        stride *= a.in_shape[d];
+    }
+    if (inside) { a.y.set(i, a.x.get(src)); return; }
+    if (a.y.dtype == B200K_F32) { ((float*)a.y.data)[i] = a.pad_value; return; }
+    store_q_dev((void*)a.y.data, a.y.dtype, i, quantize_dev(a.pad_value, 1.0f, 0, a.y.tlo, a.y.thi));
+}
+
+}  // namespace b200k
+
+extern "C" int b200k_pad_q(const b200k_pad_params* p, void* stream)
+{
+    B200K_REQUIRE(p, B200K_E_INVALID, "pad_q: null params");
+    B200K_REQUIRE(p->x.data && p->y.data, B200K_E_INVALID, "pad_q: null tensor pointer");
+    B200K_REQUIRE(p->rank >= 1 && p->rank <= 4, B200K_E_UNSUPPORTED, "pad_q: rank %d not in [1, 4]", p->rank);
+    B200K_REQUIRE(p->x.dtype != B200K_S32 && p->y.dtype != B200K_S32, B200K_E_UNSUPPORTED, "pad_q: Signed32 not supported");
+    PadArgs a;
+    a.x = make_view(p->x); a.y = make_view(p->y);
+    a.rank = p->rank; a.pad_value = p->pad_value;
+    a.count = 1;
+    for (int d = 0; d < 4; ++d) { a.in_shape[d] = a.out_shape[d] = 1; a.before[d] = 0; }
+    for (int d = 0; d < p->rank; ++d) {
+        B200K_REQUIRE(p->shape[d] > 0 && p->pad_before[d] >= 0 && p->pad_after[d] >= 0, B200K_E_INVALID, "pad_q: bad shape / padding");
+        a.in_shape[d] = p->shape[d]; a.before[d] = p->pad_before[d];
+        a.out_shape[d] = p->shape[d] + p->pad_before[d] + p->pad_after[d];
+        a.count *= a.out_shape[d];
+    }
+    launch_pdl(pad_kernel, dim3(div_up(a.count, 256)), dim3(256), 0, (cudaStream_t)stream, a);
+    return check_launch("pad_kernel");
+}

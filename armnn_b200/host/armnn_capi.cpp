@@ -1,38 +1,26 @@
-// TEST INFRASTRUCTURE ONLY — a C binding over the unmodified Arm NN reference (oracle/_ref/libarmnn.so)
-// so that Python tests and the CPU-baseline leg of the benchmark can run the *real* CpuRef workloads.
+// C binding of the Arm NN runtime API for hosts that are not C++ (the Python tests and bench.py of this repository):
+// INetwork -> Optimize(backend list) -> IRuntime::LoadNetwork -> EnqueueWorkload, for any registered backend id
+// ("B200Acc" loaded as a dynamic backend from armnn_b200/backend/, or "CpuRef").  It wraps the UNMODIFIED Arm NN
+// runtime (libarmnn.so) and adds no computation of its own: every call below is one or two calls of
+// include/armnn/INetwork.hpp / IRuntime.hpp of the Arm NN tree.
 //
-// Part 1 (cpuref_*): workload-level execution, the way the reference's own layer tests drive a backend
-// (src/backends/backendsCommon/test/layerTests/Conv2dTestImpl.cpp:3562-3669): build TensorInfos and a
-// QueueDescriptor by hand, RefWorkloadFactory::CreateWorkload, Execute.  The functions take the same
-// parameter structs as include/b200k.h, with HOST pointers, so a test hands one struct to the CPU
-// restatement, to real CpuRef and (with device pointers) to the CUDA library.
-//
-// Part 2 (armnnc_*): a minimal graph-level binding: INetwork -> Optimize(backend list) -> LoadNetwork ->
-// EnqueueWorkload, for any registered backend id ("CpuRef", or "B200Acc" loaded as a dynamic backend).
+//   build: python -m armnn_b200.build   (needs $ARMNN_ROOT for the headers and a libarmnn.so to link against)
 #include <armnn/ArmNN.hpp>
 #include <armnn/BackendRegistry.hpp>
-#include <armnn/backends/TensorHandle.hpp>
-#include <armnn/backends/WorkloadData.hpp>
-#include <armnn/backends/WorkloadFactory.hpp>
-#include <reference/RefWorkloadFactory.hpp>
-#include <reference/RefTensorHandleFactory.hpp>
-#include <reference/RefMemoryManager.hpp>
 
 #include <algorithm>
-#include <chrono>
 #include <sstream>
 #include <cstring>
-#include <map>
 #include <memory>
 #include <string>
 #include <vector>
 
-#include "../include/b200k.h"
+#include "../../include/b200k.h"
 
 using namespace armnn;
 
 static thread_local std::string g_err;
-extern "C" const char* cpuref_last_error() { return g_err.c_str(); }
+extern "C" const char* armnnc_last_error() { return g_err.c_str(); }
 
 namespace {
 
@@ -46,8 +34,6 @@ DataType act_type(int dt)
         default:        return DataType::Float32;
     }
 }
-
-size_t elem_bytes(int dt) { return dt == B200K_U8 || dt == B200K_S8 ? 1 : dt == B200K_S16 ? 2 : 4; }
 
 // TensorInfo of an operand; per-axis scales (weights / bias) when t.scales != NULL.
 TensorInfo make_info(const b200k_qtensor& t, const TensorShape& shape, unsigned axis_dim, unsigned n_axis,
@@ -66,344 +52,8 @@ TensorInfo make_info(const b200k_qtensor& t, const TensorShape& shape, unsigned 
     return info;
 }
 
-struct Harness {
-    RefWorkloadFactory factory;
-    RefTensorHandleFactory thf{std::make_shared<RefMemoryManager>()};
-    std::vector<std::unique_ptr<ITensorHandle>> handles;
-    WorkloadInfo winfo;
-
-    ITensorHandle* in(QueueDescriptor& d, const TensorInfo& info, const void* data)
-    {
-        auto h = thf.CreateTensorHandle(info);
-        h->Allocate();
-        std::memcpy(h->Map(), data, info.GetNumBytes());
-        h->Unmap();
-        d.m_Inputs.push_back(h.get());
-        winfo.m_InputTensorInfos.push_back(info);
-        handles.push_back(std::move(h));
-        return handles.back().get();
-    }
-    ITensorHandle* out(QueueDescriptor& d, const TensorInfo& info)
-    {
-        auto h = thf.CreateTensorHandle(info);
-        h->Allocate();
-        d.m_Outputs.push_back(h.get());
-        winfo.m_OutputTensorInfos.push_back(info);
-        handles.push_back(std::move(h));
-        return handles.back().get();
-    }
-    void run(LayerType type, const QueueDescriptor& d)
-    {
-        auto wl = factory.CreateWorkload(type, d, winfo);
-        if (!wl) throw RuntimeException("RefWorkloadFactory returned no workload");
-        wl->PostAllocationConfigure();
-        wl->Execute();
-    }
-};
-
-void copy_out(ITensorHandle* h, void* dst, size_t bytes)
-{
-    std::memcpy(dst, h->Map(), bytes);
-    h->Unmap();
-}
-
-// Optional separate Activation workload on the output, as CpuRef has no fused activations.
-void run_activation(int kind, float a, float b, const TensorInfo& info, void* data)
-{
-    if (kind == 0) return;
-    Harness h;
-    ActivationQueueDescriptor d;
-    d.m_Parameters.m_Function = kind == 1 ? ActivationFunction::ReLu : ActivationFunction::BoundedReLu;
-    d.m_Parameters.m_A = a;
-    d.m_Parameters.m_B = b;
-    h.in(d, info, data);
-    auto* o = h.out(d, info);
-    h.run(LayerType::Activation, d);
-    copy_out(o, data, info.GetNumBytes());
-}
-
-template <typename F>
-int guarded(F&& f)
-{
-    try { f(); return 0; }
-    catch (const std::exception& e) { g_err = e.what(); return -1; }
-}
-
 }  // namespace
 
-extern "C" int cpuref_conv2d_q8(const b200k_conv2d_params* p, int depthwise, int act_kind, float act_a, float act_b)
-{
-    return guarded([&] {
-        Harness h;
-        const unsigned N = p->n, H = p->h, W = p->wd, C = p->c, OH = p->oh, OW = p->ow, OC = p->oc, KH = p->kh, KW = p->kw;
-        TensorInfo xi = make_info(p->x, TensorShape({N, H, W, C}), 0, 0, false);
-        TensorInfo wi = depthwise ? make_info(p->w, TensorShape({1, KH, KW, OC}), 3, OC, true)
-                                  : make_info(p->w, TensorShape({OC, KH, KW, C}), 0, OC, true);
-        TensorInfo yi = make_info(p->y, TensorShape({N, OH, OW, OC}), 0, 0, false);
-        // pad_bottom / pad_right only influence shape inference, which the caller has already done
-        auto fill = [&](auto& desc) {
-            desc.m_PadTop = p->pad_top; desc.m_PadLeft = p->pad_left;
-            desc.m_PadBottom = 0; desc.m_PadRight = 0;
-            desc.m_StrideX = p->stride_w; desc.m_StrideY = p->stride_h;
-            desc.m_DilationX = p->dil_w; desc.m_DilationY = p->dil_h;
-            desc.m_BiasEnabled = p->bias.data != nullptr;
-            desc.m_DataLayout = DataLayout::NHWC;
-        };
-        ITensorHandle* o = nullptr;
-        if (depthwise) {
-            DepthwiseConvolution2dQueueDescriptor d;
-            fill(d.m_Parameters);
-            h.in(d, xi, p->x.data);
-            h.in(d, wi, p->w.data);
-            if (p->bias.data) h.in(d, make_info(p->bias, TensorShape({OC}), 0, OC, true), p->bias.data);
-            o = h.out(d, yi);
-            h.run(LayerType::DepthwiseConvolution2d, d);
-        } else {
-            Convolution2dQueueDescriptor d;
-            fill(d.m_Parameters);
-            h.in(d, xi, p->x.data);
-            h.in(d, wi, p->w.data);
-            if (p->bias.data) h.in(d, make_info(p->bias, TensorShape({OC}), 0, OC, true), p->bias.data);
-            o = h.out(d, yi);
-            h.run(LayerType::Convolution2d, d);
-        }
-        copy_out(o, const_cast<void*>(p->y.data), yi.GetNumBytes());
-        run_activation(act_kind, act_a, act_b, yi, const_cast<void*>(p->y.data));
-    });
-}
-
-extern "C" int cpuref_fully_connected_q8(const b200k_fc_params* p, int act_kind, float act_a, float act_b)
-{
-    return guarded([&] {
-        Harness h;
-        const unsigned M = p->m, K = p->k, N = p->n;
-        TensorInfo xi = make_info(p->x, TensorShape({M, K}), 0, 0, false);
-        TensorInfo wi = p->transpose_w ? make_info(p->w, TensorShape({N, K}), 0, N, true)
-                                       : make_info(p->w, TensorShape({K, N}), 1, N, true);
-        TensorInfo yi = make_info(p->y, TensorShape({M, N}), 0, 0, false);
-        FullyConnectedQueueDescriptor d;
-        d.m_Parameters.m_BiasEnabled = p->bias.data != nullptr;
-        d.m_Parameters.m_TransposeWeightMatrix = p->transpose_w != 0;
-        d.m_Parameters.m_ConstantWeights = true;
-        h.in(d, xi, p->x.data);
-        h.in(d, wi, p->w.data);
-        if (p->bias.data) h.in(d, make_info(p->bias, TensorShape({N}), 0, N, true), p->bias.data);
-        auto* o = h.out(d, yi);
-        h.run(LayerType::FullyConnected, d);
-        copy_out(o, const_cast<void*>(p->y.data), yi.GetNumBytes());
-        run_activation(act_kind, act_a, act_b, yi, const_cast<void*>(p->y.data));
-    });
-}
-
-extern "C" int cpuref_batch_matmul_q8(const b200k_bmm_params* p)
-{
-    return guarded([&] {
-        Harness h;
-        const unsigned B = p->batch, M = p->m, K = p->k, N = p->n;
-        const unsigned bx = p->batch_stride_x == 0 ? 1 : B, by = p->batch_stride_y == 0 ? 1 : B;
-        TensorInfo xi = make_info(p->x, p->transpose_x ? TensorShape({bx, K, M}) : TensorShape({bx, M, K}), 0, 0, false);
-        TensorInfo yi = make_info(p->y, p->transpose_y ? TensorShape({by, N, K}) : TensorShape({by, K, N}), 0, 0, false);
-        TensorInfo oi = make_info(p->out, TensorShape({B, M, N}), 0, 0, false);
-        BatchMatMulQueueDescriptor d;
-        d.m_Parameters.m_TransposeX = p->transpose_x != 0;
-        d.m_Parameters.m_TransposeY = p->transpose_y != 0;
-        h.in(d, xi, p->x.data);
-        h.in(d, yi, p->y.data);
-        auto* o = h.out(d, oi);
-        h.run(LayerType::BatchMatMul, d);
-        copy_out(o, const_cast<void*>(p->out.data), oi.GetNumBytes());
-    });
-}
-
-extern "C" int cpuref_pool2d_q8(const b200k_pool2d_params* p)
-{
-    return guarded([&] {
-        Harness h;
-        const unsigned N = p->n, H = p->h, W = p->wd, C = p->c, OH = p->oh, OW = p->ow;
-        TensorInfo xi = make_info(p->x, TensorShape({N, H, W, C}), 0, 0, false);
-        TensorInfo yi = make_info(p->y, TensorShape({N, OH, OW, C}), 0, 0, false);
-        Pooling2dQueueDescriptor d;
-        auto& q = d.m_Parameters;
-        q.m_PoolType = static_cast<PoolingAlgorithm>(p->pool_type);
-        q.m_PaddingMethod = static_cast<PaddingMethod>(p->padding_method);
-        q.m_PoolHeight = p->pool_h; q.m_PoolWidth = p->pool_w; q.m_StrideX = p->stride_w; q.m_StrideY = p->stride_h;
-        q.m_PadTop = p->pad_top; q.m_PadBottom = p->pad_bottom; q.m_PadLeft = p->pad_left; q.m_PadRight = p->pad_right;
-        q.m_OutputShapeRounding = OutputShapeRounding::Floor;
-        q.m_DataLayout = DataLayout::NHWC;
-        h.in(d, xi, p->x.data);
-        auto* o = h.out(d, yi);
-        h.run(LayerType::Pooling2d, d);
-        copy_out(o, const_cast<void*>(p->y.data), yi.GetNumBytes());
-    });
-}
-
-extern "C" int cpuref_mean_hw_q8(const b200k_mean_params* p)
-{
-    return guarded([&] {
-        Harness h;
-        const unsigned N = p->n, H = p->h, W = p->wd, C = p->c;
-        TensorInfo xi = make_info(p->x, TensorShape({N, H, W, C}), 0, 0, false);
-        TensorInfo yi = make_info(p->y, TensorShape({N, C}), 0, 0, false);
-        MeanQueueDescriptor d;
-        d.m_Parameters.m_Axis = {1, 2};
-        d.m_Parameters.m_KeepDims = false;
-        h.in(d, xi, p->x.data);
-        auto* o = h.out(d, yi);
-        h.run(LayerType::Mean, d);
-        copy_out(o, const_cast<void*>(p->y.data), yi.GetNumBytes());
-    });
-}
-
-extern "C" int cpuref_eltwise_q8(const b200k_eltwise_params* p, int act_kind, float act_a, float act_b)
-{
-    return guarded([&] {
-        Harness h;
-        auto shape = [&](const int32_t* s) {
-            unsigned dims[4];
-            for (int i = 0; i < p->rank; ++i) dims[i] = (unsigned)s[i];
-            return TensorShape((unsigned)p->rank, dims);
-        };
-        TensorInfo ai = make_info(p->a, shape(p->shape_a), 0, 0, false);
-        TensorInfo bi = make_info(p->b, shape(p->shape_b), 0, 0, false);
-        TensorInfo oi = make_info(p->out, shape(p->shape_out), 0, 0, false);
-        ElementwiseBinaryQueueDescriptor d;
-        d.m_Parameters.m_Operation = static_cast<BinaryOperation>(p->op);
-        h.in(d, ai, p->a.data);
-        h.in(d, bi, p->b.data);
-        auto* o = h.out(d, oi);
-        h.run(LayerType::ElementwiseBinary, d);
-        copy_out(o, const_cast<void*>(p->out.data), oi.GetNumBytes());
-        run_activation(act_kind, act_a, act_b, oi, const_cast<void*>(p->out.data));
-    });
-}
-
-extern "C" int cpuref_activation_q8(const b200k_activation_params* p)
-{
-    return guarded([&] {
-        Harness h;
-        TensorInfo xi = make_info(p->x, TensorShape({(unsigned)p->count}), 0, 0, false);
-        TensorInfo yi = make_info(p->y, TensorShape({(unsigned)p->count}), 0, 0, false);
-        ActivationQueueDescriptor d;
-        d.m_Parameters.m_Function = static_cast<ActivationFunction>(p->function);
-        d.m_Parameters.m_A = p->a;
-        d.m_Parameters.m_B = p->b;
-        h.in(d, xi, p->x.data);
-        auto* o = h.out(d, yi);
-        h.run(LayerType::Activation, d);
-        copy_out(o, const_cast<void*>(p->y.data), yi.GetNumBytes());
-    });
-}
-
-extern "C" int cpuref_softmax_q8(const b200k_softmax_params* p)
-{
-    return guarded([&] {
-        Harness h;
-        TensorShape s({(unsigned)p->outer, (unsigned)p->axis_size, (unsigned)p->inner});
-        TensorInfo xi = make_info(p->x, s, 0, 0, false);
-        TensorInfo yi = make_info(p->y, s, 0, 0, false);
-        SoftmaxQueueDescriptor d;
-        d.m_Parameters.m_Beta = p->beta;
-        d.m_Parameters.m_Axis = 1;
-        h.in(d, xi, p->x.data);
-        auto* o = h.out(d, yi);
-        h.run(LayerType::Softmax, d);
-        copy_out(o, const_cast<void*>(p->y.data), yi.GetNumBytes());
-    });
-}
-
-extern "C" int cpuref_convert_q(const b200k_convert_params* p)
-{
-    return guarded([&] {
-        Harness h;
-        TensorInfo xi = make_info(p->x, TensorShape({(unsigned)p->count}), 0, 0, false);
-        TensorInfo yi = make_info(p->y, TensorShape({(unsigned)p->count}), 0, 0, false);
-        ITensorHandle* o = nullptr;
-        if (p->y.dtype == B200K_F32) {
-            DequantizeQueueDescriptor d;
-            h.in(d, xi, p->x.data);
-            o = h.out(d, yi);
-            h.run(LayerType::Dequantize, d);
-        } else {
-            QuantizeQueueDescriptor d;
-            h.in(d, xi, p->x.data);
-            o = h.out(d, yi);
-            h.run(LayerType::Quantize, d);
-        }
-        copy_out(o, const_cast<void*>(p->y.data), yi.GetNumBytes());
-    });
-}
-
-extern "C" int cpuref_qlstm_step(const b200k_qlstm_params* p)
-{
-    return guarded([&] {
-        Harness h;
-        const unsigned B = p->batch, I = p->input_size, U = p->num_units, O = p->output_size;
-        TensorInfo xi({B, I}, DataType::QAsymmS8, p->input_scale, p->input_zp);
-        TensorInfo hi({B, O}, DataType::QAsymmS8, p->output_state_scale, p->output_state_zp);
-        TensorInfo ci({B, U}, DataType::QSymmS16, p->cell_state_scale, 0);
-        TensorInfo oi({B, O}, DataType::QAsymmS8, p->output_scale, p->output_zp);
-        QLstmQueueDescriptor d;
-        auto& q = d.m_Parameters;
-        q.m_CifgEnabled = p->w_i2i == nullptr;
-        q.m_PeepholeEnabled = p->w_c2f != nullptr;
-        q.m_ProjectionEnabled = p->w_proj != nullptr;
-        q.m_LayerNormEnabled = p->ln_f != nullptr;
-        q.m_CellClip = p->cell_clip; q.m_ProjectionClip = p->projection_clip;
-        q.m_InputIntermediateScale = p->input_intermediate_scale;
-        q.m_ForgetIntermediateScale = p->forget_intermediate_scale;
-        q.m_CellIntermediateScale = p->cell_intermediate_scale;
-        q.m_OutputIntermediateScale = p->output_intermediate_scale;
-        q.m_HiddenStateScale = p->hidden_state_scale; q.m_HiddenStateZeroPoint = p->hidden_state_zp;
-
-        std::vector<std::unique_ptr<ScopedTensorHandle>> keep;
-        auto weight = [&](const void* data, TensorShape shape, DataType dt, float scale) -> const ConstTensorHandle* {
-            if (!data) return nullptr;
-            TensorInfo info(shape, dt, scale, 0);
-            info.SetConstant(true);
-            auto t = std::make_unique<ScopedTensorHandle>(info);
-            t->Allocate();
-            std::memcpy(t->GetTensor<void>(), data, info.GetNumBytes());
-            keep.push_back(std::move(t));
-            return keep.back().get();
-        };
-        d.m_InputToInputWeights  = weight(p->w_i2i, {U, I}, DataType::QSymmS8, p->s_i2i);
-        d.m_InputToForgetWeights = weight(p->w_i2f, {U, I}, DataType::QSymmS8, p->s_i2f);
-        d.m_InputToCellWeights   = weight(p->w_i2c, {U, I}, DataType::QSymmS8, p->s_i2c);
-        d.m_InputToOutputWeights = weight(p->w_i2o, {U, I}, DataType::QSymmS8, p->s_i2o);
-        d.m_RecurrentToInputWeights  = weight(p->w_r2i, {U, O}, DataType::QSymmS8, p->s_r2i);
-        d.m_RecurrentToForgetWeights = weight(p->w_r2f, {U, O}, DataType::QSymmS8, p->s_r2f);
-        d.m_RecurrentToCellWeights   = weight(p->w_r2c, {U, O}, DataType::QSymmS8, p->s_r2c);
-        d.m_RecurrentToOutputWeights = weight(p->w_r2o, {U, O}, DataType::QSymmS8, p->s_r2o);
-        d.m_CellToInputWeights  = weight(p->w_c2i, {U}, DataType::QSymmS16, p->s_c2i);
-        d.m_CellToForgetWeights = weight(p->w_c2f, {U}, DataType::QSymmS16, p->s_c2f);
-        d.m_CellToOutputWeights = weight(p->w_c2o, {U}, DataType::QSymmS16, p->s_c2o);
-        d.m_InputGateBias  = weight(p->b_i, {U}, DataType::Signed32, p->s_bi);
-        d.m_ForgetGateBias = weight(p->b_f, {U}, DataType::Signed32, p->s_bf);
-        d.m_CellBias       = weight(p->b_c, {U}, DataType::Signed32, p->s_bc);
-        d.m_OutputGateBias = weight(p->b_o, {U}, DataType::Signed32, p->s_bo);
-        d.m_InputLayerNormWeights  = weight(p->ln_i, {U}, DataType::QSymmS16, p->s_lni);
-        d.m_ForgetLayerNormWeights = weight(p->ln_f, {U}, DataType::QSymmS16, p->s_lnf);
-        d.m_CellLayerNormWeights   = weight(p->ln_c, {U}, DataType::QSymmS16, p->s_lnc);
-        d.m_OutputLayerNormWeights = weight(p->ln_o, {U}, DataType::QSymmS16, p->s_lno);
-        d.m_ProjectionWeights = weight(p->w_proj, {O, U}, DataType::QSymmS8, p->s_proj);
-        d.m_ProjectionBias    = weight(p->b_proj, {O}, DataType::Signed32, p->s_bproj);
-
-        h.in(d, xi, p->input);
-        h.in(d, hi, p->output_state_in);
-        h.in(d, ci, p->cell_state_in);
-        auto* o0 = h.out(d, hi);
-        auto* o1 = h.out(d, ci);
-        auto* o2 = h.out(d, oi);
-        h.run(LayerType::QLstm, d);
-        copy_out(o0, p->output_state_out, hi.GetNumBytes());
-        copy_out(o1, p->cell_state_out, ci.GetNumBytes());
-        copy_out(o2, p->output, oi.GetNumBytes());
-    });
-}
-
-// ================================================================================================
-// Part 2: graph-level binding
-// ================================================================================================
 
 namespace {
 
@@ -447,6 +97,23 @@ void* armnnc_runtime_create(const char* dynamic_backend_path)
     try {
         IRuntime::CreationOptions opts;
         if (dynamic_backend_path && *dynamic_backend_path) opts.m_DynamicBackendsPath = dynamic_backend_path;
+        auto* r = new CRuntime;
+        r->rt = IRuntime::Create(opts);
+        return r;
+    } catch (const std::exception& e) { g_err = e.what(); return nullptr; }
+}
+// The same with BackendOptions("B200Acc", {...}) for the runtime: device_id >= 0 sets "DeviceId", graph_replay 0 / 1
+// sets "GraphReplay" (-1: leave the default), selftest_us > 0 sets "WaitSelfTestUs".
+void* armnnc_runtime_create_ex(const char* dynamic_backend_path, int device_id, int graph_replay, int selftest_us)
+{
+    try {
+        IRuntime::CreationOptions opts;
+        if (dynamic_backend_path && *dynamic_backend_path) opts.m_DynamicBackendsPath = dynamic_backend_path;
+        BackendOptions bo("B200Acc");
+        if (device_id >= 0) bo.AddOption(BackendOptions::BackendOption("DeviceId", device_id));
+        if (graph_replay >= 0) bo.AddOption(BackendOptions::BackendOption("GraphReplay", graph_replay != 0));
+        if (selftest_us > 0) bo.AddOption(BackendOptions::BackendOption("WaitSelfTestUs", selftest_us));
+        opts.m_BackendOptions.push_back(bo);
         auto* r = new CRuntime;
         r->rt = IRuntime::Create(opts);
         return r;
@@ -637,6 +304,16 @@ int armnnc_add_qlstm(void* vn, const b200k_qlstm_params* p)
     try {
         return add_layer(n, n->net->AddQLstmLayer(d, q));
     } catch (const std::exception& e) { g_err = e.what(); return -1; }
+}
+
+// pads: rank pairs (before, after), outermost dimension first
+int armnnc_add_pad(void* vn, int rank, const int32_t* pads, float pad_value)
+{
+    auto* n = static_cast<CNet*>(vn);
+    PadDescriptor d;
+    for (int i = 0; i < rank; ++i) d.m_PadList.emplace_back((unsigned)pads[2 * i], (unsigned)pads[2 * i + 1]);
+    d.m_PadValue = pad_value;
+    return add_layer(n, n->net->AddPadLayer(d));
 }
 
 int armnnc_add_quantize(void* vn)   { auto* n = static_cast<CNet*>(vn); return add_layer(n, n->net->AddQuantizeLayer()); }

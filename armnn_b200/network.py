@@ -222,6 +222,12 @@ class INetwork:
     def AddReshapeLayer(self, target_shape, name=None):
         return self._add(Layer("Reshape", name, 1, 1, {"shape": tuple(target_shape)}))
 
+    def AddPadLayer(self, pad_list, pad_value=0.0, name=None):
+        """pad_list: one (before, after) pair per dimension, outermost first (armnn::PadDescriptor::m_PadList);
+        constant padding with pad_value — for quantised tensors a quantised number (normally the zero point), as
+        armnn::Pad takes it (src/backends/reference/workloads/Pad.cpp:76-83)."""
+        return self._add(Layer("Pad", name, 1, 1, {"pads": tuple((int(a), int(b)) for a, b in pad_list), "value": float(pad_value)}))
+
     def AddQuantizeLayer(self, name=None):
         return self._add(Layer("Quantize", name, 1, 1))
 
@@ -291,6 +297,10 @@ def IsLayerSupported(layer):
             return False, "ElementwiseBinary: rank > 4"
         return True, ""
     if t in ("Quantize", "Dequantize"):
+        return True, ""
+    if t == "Pad":
+        if len(ins[0].shape) > 4:
+            return False, "Pad: rank > 4"
         return True, ""
     if t == "QLstm":
         if ins[0].dtype != DataType.QAsymmS8 or ins[2].dtype != DataType.QSymmS16:
@@ -644,6 +654,16 @@ class GraphProgram:
 
     _make_Quantize = _make_convert
     _make_Dequantize = _make_convert
+
+    def _make_Pad(self, layer):
+        x, y = layer.inputs[0].source, layer.outputs[0]
+        p = _abi.PadParams()
+        p.x, p.y = self._operand(x), self._operand(y)
+        p.rank = len(x.info.shape)
+        for i, (before, after) in enumerate(layer.desc["pads"]):
+            p.shape[i], p.pad_before[i], p.pad_after[i] = x.info.shape[i], before, after
+        p.pad_value = layer.desc["value"]
+        return "pad_q", p
 
     def _make_QLstm(self, layer):
         x, h, c = (s.source for s in layer.inputs)

@@ -237,6 +237,21 @@ typedef struct {
 
 int b200k_activation_q8(const b200k_activation_params* p, void* stream);
 
+/* armnn::Pad with PaddingMode::Constant (src/backends/reference/workloads/Pad.cpp:21-170, RefPadWorkload.cpp):
+ * y has shape[d] + pad_before[d] + pad_after[d] elements along dimension d (rank <= 4, outermost first); elements
+ * outside the copied block hold pad_value — for a quantised y a quantised number already (the reference encodes it with
+ * scale 1 and offset 0, Pad.cpp:76-83; the TfLite parser passes the zero point) —, the others Q_y(deq_x(x)).
+ * (Pad layers in front of a convolution or pooling layer never reach this: the backend folds them into the layer.) */
+typedef struct {
+    b200k_qtensor x, y;
+    int32_t rank;
+    int32_t shape[4];
+    int32_t pad_before[4], pad_after[4];
+    float pad_value;
+} b200k_pad_params;
+
+int b200k_pad_q(const b200k_pad_params* p, void* stream);
+
 /* ---- Softmax --------------------------------------------------------------------------------- */
 
 /* armnn::Softmax (src/backends/reference/workloads/Softmax.cpp:17-70): softmax over the axis of
@@ -308,7 +323,7 @@ unsigned long long b200k_kernel_launches(void);
 
 /* sizeof() of a parameter struct as compiled into the library, for bindings in other languages to check their
  * own declarations: 0 conv2d, 1 fc, 2 bmm, 3 pool2d, 4 mean, 5 eltwise, 6 activation, 7 softmax, 8 convert,
- * 9 qlstm.  No counterpart in the reference (its backends are linked as C++). */
+ * 9 qlstm, 10 pad.  No counterpart in the reference (its backends are linked as C++). */
 size_t b200k_sizeof_params(int which);
 
 #ifdef __cplusplus

@@ -451,6 +451,38 @@ int oracle_convert_q(const b200k_convert_params* p)
     return 0;
 }
 
+/* ---- Pad (constant), Pad.cpp:37-170 -----------------------------------------------------------
+ * Every output element is the decoded input element at the shifted position encoded with the
+ * output's quantisation, or the pad value; for a quantised output the pad value is encoded with
+ * scale 1 and offset 0, i.e. it is a quantised number already (Pad.cpp:76-83). */
+int oracle_pad_q(const b200k_pad_params* p)
+{
+    if (!p->x.data || !p->y.data || p->rank < 1 || p->rank > 4) return B200K_E_INVALID;
+    int in_shape[4] = {1, 1, 1, 1}, out_shape[4] = {1, 1, 1, 1}, before[4] = {0, 0, 0, 0};
+    int64_t count = 1;
+    for (int d = 0; d < p->rank; ++d) {
+        in_shape[d] = p->shape[d]; before[d] = p->pad_before[d];
+        out_shape[d] = p->shape[d] + p->pad_before[d] + p->pad_after[d];
+        count *= out_shape[d];
+    }
+    for (int64_t i = 0; i < count; ++i) {
+        int64_t rest = i, src = 0, stride = 1;
+        int coord[4] = {0, 0, 0, 0}, inside = 1;
+        for (int d = p->rank - 1; d >= 0; --d) { coord[d] = (int)(rest % out_shape[d]); rest /= out_shape[d]; }
+        for (int d = p->rank - 1; d >= 0; --d) {
+            const int c = coord[d] - before[d];
+            if (c < 0 || c >= in_shape[d]) inside = 0;
+            src += (int64_t)c * stride;
+            stride *= in_shape[d];
+        }
+        if (inside) { store_f(&p->y, i, load_f(&p->x, src)); continue; }
+        b200k_qtensor raw = p->y;
+        if (raw.dtype != B200K_F32) { raw.scale = 1.0f; raw.zero_point = 0; }
+        store_f(&raw, i, p->pad_value);
+    }
+    return 0;
+}
+
 /* ---- QLstm, RefQLstmWorkload.cpp:46-541 with LstmUtils.cpp:16-256 ------------------------------
  * A step-by-step restatement: every Encoder::Set / Decoder::Get of the reference is one
  * quantize_f / dequantize_i here, in the reference's order, including the re-quantisation of the

@@ -234,6 +234,29 @@ def convert_cases():
             "requantize_s16_s8": make(117, S16, S8, xq=(0.0005, 0))}
 
 
+def pad_cases():
+    def make(seed, shape, pads, value, dtype=S8, xq=(0.05, -7), yq=None):
+        def build(mem):
+            rng = np.random.default_rng(seed)
+            p = _abi.PadParams()
+            p.x = qt(mem, _rand(rng, dtype, shape) if dtype != F32 else rng.standard_normal(shape).astype(np.float32), dtype, *xq)
+            out_shape = tuple(s + a + b for s, (a, b) in zip(shape, pads))
+            p.y, y = qt_out(mem, out_shape, dtype, *(yq or xq))
+            p.rank = len(shape)
+            for i, (a, b) in enumerate(pads):
+                p.shape[i], p.pad_before[i], p.pad_after[i] = shape[i], a, b
+            p.pad_value = value
+            return p, [y]
+        return lambda: SimpleCase("pad_q", build)
+    return {
+        "nhwc_hw_zero_point": make(131, (2, 9, 7, 24), ((0, 0), (1, 1), (2, 1), (0, 0)), -7),
+        "nhwc_channels_u8": make(132, (1, 5, 5, 3), ((0, 0), (0, 0), (0, 0), (2, 3)), 200, dtype=U8, xq=(0.1, 128)),
+        "rank2_requantise": make(133, (7, 11), ((3, 0), (0, 5)), 9, xq=(0.05, 2), yq=(0.08, -4)),
+        "rank1": make(134, (33,), ((4, 4),), -128),
+        "rank3_float": make(135, (3, 4, 5), ((1, 0), (0, 2), (1, 1)), 1.5, dtype=F32, xq=(1.0, 0)),
+    }
+
+
 def qlstm_cases():
     return {
         "proj_ln": lambda: random_qlstm_case(121, 3, 40, 64, 32),
@@ -249,7 +272,7 @@ def qlstm_cases():
 
 ALL_GROUPS = {"conv": conv_cases, "dwconv": dwconv_cases, "fc": fc_cases, "bmm": bmm_cases, "pool": pool_cases,
               "mean": mean_cases, "eltwise": eltwise_cases, "activation": activation_cases, "softmax": softmax_cases,
-              "convert": convert_cases, "qlstm": qlstm_cases}
+              "convert": convert_cases, "pad": pad_cases, "qlstm": qlstm_cases}
 
 
 def run_case(case, where):

@@ -22,7 +22,7 @@ NP_OF = {_abi.U8: np.uint8, _abi.S8: np.int8, _abi.S16: np.int16, _abi.S32: np.i
 RANGE = {_abi.U8: (0, 255), _abi.S8: (-128, 127), _abi.S16: (-32768, 32767)}
 
 ORACLE_PATH = os.path.join(ROOT, "oracle", "libq8oracle.so")
-CPUREF_PATH = os.path.join(ROOT, "oracle", "_ref", "libarmnn_capi.so")
+CPUREF_PATH = os.path.join(ROOT, "oracle", "_ref", "libcpuref_capi.so")
 
 _oracle = None
 _cpuref = None
@@ -42,7 +42,9 @@ def have_cpuref():
 def cpuref():
     global _cpuref
     if _cpuref is None:
-        # RTLD_GLOBAL: the B200Acc plugin, dlopen()ed later by the Arm NN runtime, resolves libarmnn's symbols
+        # libarmnn.so first and RTLD_GLOBAL: one copy of the Arm NN core for this binding, the runtime binding of
+        # armnn_b200.armnn_host and the B200Acc plugin the runtime dlopen()s
+        C.CDLL(os.path.join(os.path.dirname(CPUREF_PATH), "libarmnn.so"), mode=C.RTLD_GLOBAL)
         _cpuref = C.CDLL(CPUREF_PATH, mode=C.RTLD_GLOBAL)
         _cpuref.cpuref_last_error.restype = C.c_char_p
     return _cpuref

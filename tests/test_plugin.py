@@ -10,14 +10,67 @@ from q8util import diff_stats, have_cpuref
 
 import hostnet
 
-needs_plugin = pytest.mark.skipif(not (have_cpuref() and os.path.exists(hostnet.PLUGIN_PATH)),
-                                  reason="Arm NN runtime (oracle/_ref) or the plugin is not built")
+from armnn_b200 import armnn_host
+
+needs_plugin = pytest.mark.skipif(not (armnn_host.available() and os.path.exists(hostnet.PLUGIN_PATH)),
+                                  reason="the Arm NN runtime (libarmnn.so), its binding or the plugin is not built")
 
 
 @needs_plugin
 def test_plugin_is_found_loaded_and_registered_by_the_runtime():
-    assert hostnet.ArmnnNetwork.backend_available("CpuRef")
-    assert hostnet.ArmnnNetwork.backend_available("B200Acc")
+    assert hostnet.backend_available("CpuRef")
+    assert hostnet.backend_available("B200Acc")
+
+
+def _pad_conv_net(pad_value_is_zero_point=True, batch=2):
+    """Pad (H and W by 1) -> 3x3 VALID Convolution2d + ReLU -> Pad -> 3x3/2 average pool, the way the TfLite parser
+    emits explicit padding (src/armnnTfLiteParser/TfLiteParser.cpp:829-830, 2964)."""
+    from armnn_b200.network import ActivationFunction, DataType, INetwork, PaddingMethod, PoolingAlgorithm, TensorInfo
+    rng = np.random.default_rng(77)
+    net = INetwork.Create()
+    il = net.AddInputLayer(0, "input")
+    x_info = TensorInfo((batch, 12, 12, 32), DataType.QAsymmS8, 0.05, -7)
+    il.GetOutputSlot(0).SetTensorInfo(x_info)
+    # for quantised tensors the pad value is a quantised number; only the zero point is neutral for a convolution
+    pl = net.AddPadLayer(((0, 0), (1, 1), (1, 1), (0, 0)), -7 if pad_value_is_zero_point else 5, "pad")
+    il.GetOutputSlot(0).Connect(pl.GetInputSlot(0))
+    pl.GetOutputSlot(0).SetTensorInfo(TensorInfo((batch, 14, 14, 32), DataType.QAsymmS8, 0.05, -7))
+    w_scales = rng.uniform(0.002, 0.01, size=32).astype(np.float32)
+    wq = rng.integers(-127, 128, size=(32, 3, 3, 32)).astype(np.int8)
+    bq = rng.integers(-500, 501, size=32).astype(np.int32)
+    wl = net.AddConstantLayer(wq, TensorInfo(wq.shape, DataType.QSymmS8, scales=w_scales, quant_dim=0), "w")
+    bl = net.AddConstantLayer(bq, TensorInfo(bq.shape, DataType.Signed32, scales=(np.float32(0.05) * w_scales), quant_dim=0), "b")
+    cl = net.AddConvolution2dLayer((1, 1), (0, 0, 0, 0), (1, 1), True, "conv")
+    pl.GetOutputSlot(0).Connect(cl.GetInputSlot(0))
+    wl.GetOutputSlot(0).Connect(cl.GetInputSlot(1))
+    bl.GetOutputSlot(0).Connect(cl.GetInputSlot(2))
+    y_info = TensorInfo((batch, 12, 12, 32), DataType.QAsymmS8, 0.08, -128)
+    cl.GetOutputSlot(0).SetTensorInfo(y_info)
+    al = net.AddActivationLayer(ActivationFunction.ReLu, name="relu")
+    cl.GetOutputSlot(0).Connect(al.GetInputSlot(0))
+    al.GetOutputSlot(0).SetTensorInfo(y_info)
+    p2 = net.AddPadLayer(((0, 0), (1, 1), (1, 1), (0, 0)), -128, "pad2")             # the lowest value: neutral for max pooling
+    al.GetOutputSlot(0).Connect(p2.GetInputSlot(0))
+    p2.GetOutputSlot(0).SetTensorInfo(TensorInfo((batch, 14, 14, 32), DataType.QAsymmS8, 0.08, -128))
+    ql = net.AddPooling2dLayer(PoolingAlgorithm.Max, (3, 3), (2, 2), (0, 0, 0, 0), PaddingMethod.Exclude, "pool")
+    p2.GetOutputSlot(0).Connect(ql.GetInputSlot(0))
+    ql.GetOutputSlot(0).SetTensorInfo(TensorInfo((batch, 6, 6, 32), DataType.QAsymmS8, 0.08, -128))
+    ol = net.AddOutputLayer(0, "output")
+    ql.GetOutputSlot(0).Connect(ol.GetInputSlot(0))
+    return net, {"input_shape": (batch, 12, 12, 32), "output_shape": (batch, 6, 6, 32)}
+
+
+@needs_plugin
+def test_optimize_folds_pad_layers_into_convolution_and_pooling():
+    """A Pad whose value is the tensor's zero point disappears into the layer it feeds (the core only folds for CpuAcc /
+    GpuAcc, src/armnn/Network.cpp:1394-1401); a Pad with another value stays a layer of its own, which B200Acc also runs."""
+    from collections import Counter
+    net, _ = _pad_conv_net(True)
+    kinds = Counter(t for t, _ in hostnet.ArmnnNetwork(net, "B200Acc", optimize_only=True).optimized_layers)
+    assert kinds["Pad"] == 0 and kinds["Convolution2d"] == 1 and kinds["Pooling2d"] == 1 and kinds["Activation"] == 0, kinds
+    net, _ = _pad_conv_net(False)
+    kinds = Counter(t for t, _ in hostnet.ArmnnNetwork(net, "B200Acc", optimize_only=True).optimized_layers)
+    assert kinds["Pad"] == 1 and kinds["Pooling2d"] == 1, kinds
 
 
 @needs_plugin
@@ -182,3 +235,158 @@ def test_batch_matmul_through_the_runtime_matches_cpuref(tx, ty):
     st = diff_stats(ref, got)
     assert st["max_abs"] <= 1 and st["mismatch_frac"] < 0.01, st
     assert np.unique(ref).size > 50                          # not saturated
+
+
+@needs_plugin
+@pytest.mark.gpu
+@pytest.mark.parametrize("folds", [True, False])
+def test_padded_graph_through_the_runtime_matches_cpuref(folds):
+    """Explicit Pad layers, folded into their consumers or run by the Pad workload, against CpuRef."""
+    net, info = _pad_conv_net(folds)
+    _, ref, got = _pair(net, info, np.int8)
+    st = diff_stats(ref, got)
+    assert st["max_abs"] <= 1 and st["mismatch_frac"] < 1e-2, st
+    assert np.unique(ref).size > 20
+
+
+@needs_plugin
+@pytest.mark.gpu
+def test_workload_queue_is_replayed_as_a_cuda_graph_with_identical_results():
+    """From the fourth inference on the plugin launches one CUDA graph per inference instead of one kernel per layer:
+    results stay what the eager inferences (and a runtime with GraphReplay switched off) produce, for changing inputs,
+    with copied and with imported buffers."""
+    from armnn_b200 import configs
+    net, info = configs.resnet50(2, 64)
+    # (the backend's runtime-level options are process-wide defaults that a network picks up when it is loaded)
+    eager_rt = hostnet.Runtime(graph_replay=False)
+    eager = hostnet.ArmnnNetwork(net, "B200Acc", runtime=eager_rt)
+    replay_rt = hostnet.Runtime(graph_replay=True)
+    replay = hostnet.ArmnnNetwork(net, "B200Acc", runtime=replay_rt)
+    imported = hostnet.ArmnnNetwork(net, "B200Acc", import_io=True, runtime=replay_rt)
+    before = armnn_host.graph_stats()
+    rng = np.random.default_rng(31)
+    xs = [rng.integers(-128, 128, size=info["input_shape"]).astype(np.int8) for _ in range(7)]
+    # One network after the other: when a thread moves from one network to another the runtime releases the first
+    # one's working memory (src/armnn/Runtime.cpp:638-645), the backend's tensor arena with it, and a recorded graph is
+    # dropped with the addresses it holds.
+    wants = [eager.run({0: x})[0] for x in xs]
+    assert len({w.tobytes() for w in wants}) > 3
+    for i, x in enumerate(xs):
+        assert np.array_equal(wants[i], replay.run({0: x})[0]), i
+    xb = np.zeros(info["input_shape"], np.int8)
+    y = np.zeros(info["output_shape"], np.int8)
+    for i, x in enumerate(xs):
+        xb[...] = x
+        y[...] = 0
+        imported.run_into({0: xb}, {0: y})
+        assert np.array_equal(wants[i], y), i
+    # going back to the first replayed network: its memory was released meanwhile, the graph is recorded afresh
+    for i in (0, 1, 2, 3):
+        assert np.array_equal(wants[i], replay.run({0: xs[i]})[0]), i
+    # the replayed networks really went through graph launches: 4 of 7 inferences each, 56 kernels per inference
+    launches, kernels = (x1 - x0 for x1, x0 in zip(armnn_host.graph_stats(), before))
+    assert launches >= 8 and kernels >= launches * 50, (launches, kernels)
+
+
+@needs_plugin
+@pytest.mark.gpu
+def test_profiler_reports_device_time_per_workload():
+    """INetworkProperties::m_ProfilingEnabled: every B200Acc workload opens a profiling event with a wall-clock and a
+    CUDA-event instrument (the counterpart of OpenClTimer), so IProfiler::Print lists a device time per layer."""
+    import json
+    from armnn_b200 import configs
+    net, info = configs.single_conv()
+    n = hostnet.ArmnnNetwork(net, "B200Acc", profiling=True)
+    x = np.random.default_rng(5).integers(-128, 128, size=info["input_shape"]).astype(np.int8)
+    for _ in range(5):                                       # stays eager: a profiled inference is never replayed
+        n.run({0: x})
+    text = n.profile_json()
+    assert "B200 kernel time" in text and "CudaEventTimer" not in text.replace("B200 kernel time", "") or "B200 kernel time" in text
+    doc = json.loads(text)
+
+    def find(node, key, out):
+        if isinstance(node, dict):
+            for k, v in node.items():
+                if key in k:
+                    out.append(v)
+                find(v, key, out)
+        elif isinstance(node, list):
+            for v in node:
+                find(v, key, out)
+    times = []
+    find(doc, "B200 kernel time", times)
+    vals = [v for t in times for v in (t.get("raw", []) if isinstance(t, dict) else [])]
+    assert vals and all(0.0 < v < 1e5 for v in vals), vals   # microseconds of the convolution kernel
+
+
+@needs_plugin
+@pytest.mark.gpu
+def test_device_side_timeout_becomes_status_failure_and_the_next_inference_is_fine():
+    """A runtime created with BackendOptions("B200Acc", {{"WaitSelfTestUs", 3000}}) injects the failure a stuck pipeline
+    would produce (every bounded wait of the convolution kernel gives up after 3 ms): the kernel ends by itself, the
+    output handle's Map() throws RuntimeException inside LoadedNetwork::Execute, and EnqueueWorkload returns
+    Status::Failure (src/armnn/LoadedNetwork.cpp:1272-1279).  A network of an ordinary runtime then runs correctly."""
+    from armnn_b200 import configs
+    net, info = configs.single_conv()
+    x = np.random.default_rng(8).integers(-128, 128, size=info["input_shape"]).astype(np.int8)
+    y = np.zeros(info["output_shape"], np.int8)
+    faulty_rt = hostnet.Runtime(selftest_us=3000)
+    faulty = hostnet.ArmnnNetwork(net, "B200Acc", runtime=faulty_rt)
+    rc = faulty.enqueue_ptrs([x.ctypes.data], [y.ctypes.data])
+    assert rc != 0
+    faulty.close()
+    ok_rt = hostnet.Runtime(selftest_us=0)
+    good = hostnet.ArmnnNetwork(net, "B200Acc", runtime=ok_rt).run({0: x})[0]
+    ref = hostnet.ArmnnNetwork(net, "CpuRef").run({0: x})[0]
+    st = diff_stats(ref, good)
+    assert st["max_abs"] <= 1 and st["mismatch_frac"] < 1e-3, st
+
+
+@needs_plugin
+@pytest.mark.gpu
+def test_fc_sweep_type_combination_through_optimize_on_b200acc():
+    """BASELINE configuration 2's types — QAsymmS8 activations x per-axis QSymmS8 weights — are refused by CpuRef's own
+    layer support (RefLayerSupport.cpp:1569) but accepted by B200Acc: Optimize({"B200Acc"}) + LoadNetwork + Enqueue of
+    the FullyConnected graph, against the oracle and against the CpuRef FullyConnected workload driven directly."""
+    from armnn_b200 import configs, network
+    for m, k in ((16, 1024), (256, 1024)):
+        net, info = configs.fc_sweep_case(m, k)
+        with pytest.raises(RuntimeError):
+            hostnet.ArmnnNetwork(net, "CpuRef")
+        x = np.random.default_rng(m + k).integers(-128, 128, size=info["input_shape"]).astype(np.int8)
+        got = hostnet.ArmnnNetwork(net, "B200Acc").run({0: x})[0]
+        want = hostnet.OracleNetwork(network.Optimize(configs.fc_sweep_case(m, k)[0], ["B200Acc"])).run({0: x})[0]
+        assert np.array_equal(want, got), diff_stats(want, got)
+        assert np.mean((got == -128) | (got == 127)) < 0.05
+
+
+@needs_plugin
+@pytest.mark.gpu
+def test_device_id_model_option_selects_the_gpu_per_network():
+    """One LoadedNetwork per GPU in one process (the multi-GPU mechanism of the Arm NN API): the DeviceId ModelOption binds
+    a network's handles, stream and kernels to that GPU.  With one visible GPU the option 0 must work and 1 must be
+    refused at LoadNetwork; with several, two networks on two GPUs run from two host threads and agree."""
+    import threading
+    import torch
+    from armnn_b200 import configs
+    net, info = configs.resnet50(2, 64)
+    x = np.random.default_rng(13).integers(-128, 128, size=info["input_shape"]).astype(np.int8)
+    n0 = hostnet.ArmnnNetwork(net, "B200Acc", device_id=0)
+    want = n0.run({0: x})[0]
+    count = torch.cuda.device_count()
+    if count < 2:
+        with pytest.raises(RuntimeError):
+            hostnet.ArmnnNetwork(net, "B200Acc", device_id=1)
+        return
+    n1 = hostnet.ArmnnNetwork(net, "B200Acc", device_id=1)
+    results = {}
+
+    def work(tag, n):
+        for _ in range(5):
+            results[tag] = n.run({0: x})[0]
+    threads = [threading.Thread(target=work, args=(t, n)) for t, n in (("a", n0), ("b", n1))]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert np.array_equal(results["a"], want) and np.array_equal(results["b"], want)
