@@ -134,7 +134,7 @@ KERNEL_ENTRY_POINTS = {
 EXPORTED_SYMBOLS = ["b200k_" + k for k in KERNEL_ENTRY_POINTS] + [
     "b200k_device_open", "b200k_device_count", "b200k_last_error", "b200k_version",
     "b200k_activation_clamp", "b200k_conv2d_pack_bytes", "b200k_conv2d_pack", "b200k_conv2d_scratch_bytes", "b200k_conv2d_q8_static", "b200k_sizeof_params", "b200k_poll_status",
-    "b200k_kernel_launches",
+    "b200k_kernel_launches", "b200k_int8_mma_peak",
 ]
 
 
@@ -159,6 +159,8 @@ def declare_product(lib):
     lib.b200k_conv2d_pack.argtypes = [C.POINTER(Conv2dParams), C.c_void_p, C.c_void_p]
     lib.b200k_conv2d_pack.restype = C.c_int
     lib.b200k_poll_status.restype = C.c_int
+    lib.b200k_int8_mma_peak.argtypes = [C.POINTER(C.c_double), C.c_void_p]
+    lib.b200k_int8_mma_peak.restype = C.c_int
     lib.b200k_conv2d_q8_static.argtypes = [C.POINTER(Conv2dParams), C.c_void_p]
     lib.b200k_conv2d_q8_static.restype = C.c_int
     lib.b200k_conv2d_scratch_bytes.argtypes = [C.POINTER(Conv2dParams)]

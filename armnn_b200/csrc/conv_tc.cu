@@ -1655,9 +1655,100 @@ int tc_pack(const b200k_conv2d_params* p, void* packed, cudaStream_t stream)
     return check_launch("row_weight_pack_kernel");
 }
 
+// ---- int8 tensor-core ceiling ---------------------------------------------------------------------------------
+//
+// What the tcgen05 pipe can do when nothing else is in the way: every CTA (one per SM) issues kind::i8 MMAs of
+// 128 x 256 x 32 back to back on one pair of shared-memory tiles (no loads, no epilogue), 64 per commit.  The result
+// is the denominator for "fraction of the int8 tensor peak" figures measured on the same device and clocks.
+struct PeakArgs { int rounds; long long wait_limit; int* status; };
+
+__global__ void __launch_bounds__(128, 1) mma_peak_kernel(const PeakArgs a)
+{
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* s_a = smem;                                   // 128 rows x 128 bytes, 128-byte swizzle
+    uint8_t* s_b = smem + 128 * 128;                       // 256 rows x 128 bytes
+    uint64_t* bar = (uint64_t*)(s_b + 256 * 128);
+    uint32_t* tmem_slot = (uint32_t*)(bar + 1);
+    for (int i = threadIdx.x; i < (128 + 256) * 128 / 16; i += blockDim.x) ((uint4*)smem)[i] = make_uint4(0x01010101u, 0x02020202u, 0x01010101u, 0x02020202u);
+    if (threadIdx.x == 0) { mbar_init(bar, 1); asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    const int warp = threadIdx.x >> 5;
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(256) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    if (warp == 0) {
+        const uint32_t id = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+        const uint64_t da = make_smem_desc<128>(smem_u32(s_a)), db = make_smem_desc<128>(smem_u32(s_b));
+        bool alive = true;
+        for (int r = 0; r < a.rounds && alive; ++r) {
+            if (elect_one()) {
+                #pragma unroll 1
+                for (int i = 0; i < 16; ++i) {
+                    #pragma unroll
+                    for (int k = 0; k < 4; ++k) tc_mma_i8(tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), id, (uint32_t)(r | i | k));
+                }
+                tc_commit(bar);
+            }
+            if (!__all_sync(0xffffffffu, mbar_wait(bar, (uint32_t)(r & 1), a.wait_limit))) { atomicExch(a.status, 1); alive = false; }
+            tc_fence_after();
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256) : "memory");
+    }
+}
+
 }  // namespace b200k
 
 using namespace b200k;
+
+extern "C" int b200k_int8_mma_peak(double* tops, void* stream_)
+{
+    B200K_REQUIRE(tops, B200K_E_INVALID, "int8_mma_peak: null output");
+    cudaStream_t stream = (cudaStream_t)stream_;
+    const int sms = sm_count(), rounds = 2000;
+    const size_t smem = 1024 + (128 + 256) * 128 + 64;
+    B200K_CUDA(cudaFuncSetAttribute(mma_peak_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    int* status = nullptr;
+    B200K_CUDA(cudaMalloc(&status, sizeof(int)));
+    B200K_CUDA(cudaMemsetAsync(status, 0, sizeof(int), stream));
+    cudaEvent_t e0, e1;
+    B200K_CUDA(cudaEventCreate(&e0));
+    B200K_CUDA(cudaEventCreate(&e1));
+    PeakArgs a;
+    a.rounds = rounds; a.wait_limit = TC_WAIT_LIMIT_CYCLES; a.status = status;
+    double best = 0.0;
+    int rc = B200K_OK;
+    for (int rep = 0; rep < 4 && rc == B200K_OK; ++rep) {          // the first repetition warms up
+        cudaEventRecord(e0, stream);
+        mma_peak_kernel<<<sms, 128, smem, stream>>>(a);
+        cudaEventRecord(e1, stream);
+        rc = check_launch("mma_peak_kernel");
+        if (cudaEventSynchronize(e1) != cudaSuccess) { set_error("int8_mma_peak: %s", cudaGetErrorString(cudaGetLastError())); rc = B200K_E_CUDA; break; }
+        float ms = 0.f;
+        cudaEventElapsedTime(&ms, e0, e1);
+        const double ops = 2.0 * 128.0 * 256.0 * 32.0 * 64.0 * rounds * sms;
+        if (rep > 0 && ms > 0.f && ops / (ms * 1e-3) / 1e12 > best) best = ops / (ms * 1e-3) / 1e12;
+    }
+    int st = 0;
+    if (rc == B200K_OK) cudaMemcpy(&st, status, sizeof(int), cudaMemcpyDeviceToHost);
+    cudaFree(status);
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    if (rc != B200K_OK) return rc;
+    B200K_REQUIRE(st == 0, B200K_E_TIMEOUT, "int8_mma_peak: a bounded wait gave up");
+    *tops = best;
+    return B200K_OK;
+}
 
 extern "C" int b200k_poll_status(void)
 {

@@ -316,6 +316,12 @@ int b200k_qlstm_step(const b200k_qlstm_params* p, void* stream);
  * the reference. */
 int b200k_poll_status(void);
 
+/* Measures what the tcgen05 int8 pipe of the current device sustains with nothing else in the way: one CTA per SM
+ * issuing kind::i8 MMAs (128 x 256 x 32) back to back on resident shared-memory tiles for about a millisecond, best of
+ * three repetitions, in TOP/s (2 x MAC).  The denominator of "fraction of the int8 tensor peak" figures.  Allocates a
+ * status word and synchronises.  No counterpart in the reference. */
+int b200k_int8_mma_peak(double* tops, void* stream);
+
 /* Kernels this library has launched in this process so far (every launch of every entry point counts; a launch
  * recorded into a CUDA graph during stream capture counts once).  For callers that report how many of the library's
  * kernels a measured region ran.  No counterpart in the reference. */
