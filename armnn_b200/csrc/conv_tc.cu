@@ -75,6 +75,7 @@ __device__ int g_tc_status = 0;                 // 0 ok, otherwise the code of t
 // instructions read them as constant-bank operands and they take no registers.  Each is the same value twice.
 struct EpiConsts {
     float2 inv2, nsy2, magic2, zero2, neg2;      // RN(1 / sy), -sy, MAGIC, 0, -1
+    float2 nmagic2;                              // -MAGIC
     float2 zoff_lut2, zoff_sat2, zoff_clamp2;    // what is added to t = MAGIC + n (see epi_chunk), per way of ending
     float lo, hi;                                // EPI_CLAMP: clamp bounds in the biased domain (MAGIC + ...)
 };
@@ -122,6 +123,7 @@ struct TcArgs {
     // one row of per-channel corrections.  ypair / xpair list the distinct (k0 << 4 | k1) of the geometry, ycls / xcls
     // map such a code back to its position in the list.
     int ncy, ncx, ncls;
+    int acc_big;                                // |accumulator| or |accumulator - correction| can reach 2^24 (see epi_chunk_fast)
     uint8_t ypair[16], xpair[16];
     uint8_t ycls[256], xcls[256];
     long long wait_limit;                       // clock64 ticks after which a device-side wait gives up
@@ -340,6 +342,7 @@ struct EpiExact {
     float sy1, zy1, lo1, hi1;                    // the convolution's own quantisation (plain clamp bounds)
     int fused, res_u8;
     float zr, sr, sy2, zy2, lo2, hi2;
+    int always;                                  // no usable fused-add table: every value takes this arithmetic
 };
 
 __device__ __forceinline__ int exact_value(int acc, float m, float b, uint32_t res_byte, const EpiExact& x)
@@ -484,6 +487,150 @@ __device__ __forceinline__ uint4 epi_chunk(const uint32_t* r, const uint4 rv, co
     return make_uint4(packed[0], packed[1], packed[2], packed[3]);
 }
 
+// ---- the hot path: one fused multiply-add per value, and a proof that its rounding is the reference's -----------
+//
+// The reference chain (above) is three roundings away from the real number R = ((acc - cc) m + b) / sy.  The hot path
+// evaluates q" = fma(float(acc), mq, bq) with mq = RN(m / sy) and bq = (b - cc m) / sy + zoff (zoff = the output zero
+// point, for the table also minus the type minimum) prepared per n-tile to within one rounding, so that
+//     |reference q + zoff - q"| <= E = 1.5 * 2^-24 * (4 Rmax + 3 RZmax + 2 max|b / sy| + 4 max|bq| + |zoff|)
+// for every value that can round to something inside the output range (Rmax, RZmax: the largest |R| and |R + zoff| that
+// do).  t = q" + MAGIC rounds q" to an integer n; whenever |q" - n| < 0.5 - E the reference's q lies on the same side of
+// every rounding boundary, so n is the reference's result and the halves-away-from-zero rule cannot matter.  A group of
+// four values in which some lane sees |q" - n| >= 0.5 - E (about one group in twenty) is re-evaluated with the
+// reference arithmetic itself (epi_fix_group).  Values whose q" is huge lose the integer grid of the magic constant:
+// either they are flagged like the others or they saturate, as the reference's do.
+struct TabFast { uint32_t mq, bq; };            // shared addresses at the chunk's first column (bq: this lane's class row)
+
+template <int KIND>
+__device__ __forceinline__ uint4 epi_chunk_fast(const uint32_t* r, const uint4 rv, const TabFast& ad, const EpiConsts& ec, const uint32_t lut,
+                                                float* dmg)
+{
+    const uint32_t resw[4] = {rv.x, rv.y, rv.z, rv.w};
+    uint32_t packed[4];
+    #pragma unroll
+    for (int g = 0; g < 4; ++g) {
+        float2 m01, m23, b01, b23;
+        lds_f2x2(ad.mq + g * 16, m01, m23);
+        lds_f2x2(ad.bq + g * 16, b01, b23);
+        const float2 a01 = make_float2(__int2float_rn((int)r[g * 4 + 0]), __int2float_rn((int)r[g * 4 + 1]));
+        const float2 a23 = make_float2(__int2float_rn((int)r[g * 4 + 2]), __int2float_rn((int)r[g * 4 + 3]));
+        const float2 q01 = __ffma2_rn(a01, m01, b01), q23 = __ffma2_rn(a23, m23, b23);
+        const float2 t01 = __fadd2_rn(q01, ec.magic2), t23 = __fadd2_rn(q23, ec.magic2);
+        const float2 n01 = __fadd2_rn(t01, ec.nmagic2), n23 = __fadd2_rn(t23, ec.nmagic2);       // rint(q") (exact)
+        const float2 d01 = __ffma2_rn(n01, ec.neg2, q01), d23 = __ffma2_rn(n23, ec.neg2, q23);   // q" - n (exact)
+        dmg[g] = fmaxf(fmaxf(fabsf(d01.x), fabsf(d01.y)), fmaxf(fabsf(d23.x), fabsf(d23.y)));
+        const float z[4] = {n01.x, n01.y, n23.x, n23.y};
+        if (KIND == EPI_CLAMP) {
+            // clamp in the biased domain: the low byte of the bit pattern is the output byte
+            const float tt[4] = {t01.x, t01.y, t23.x, t23.y};
+            uint32_t bits[4];
+            #pragma unroll
+            for (int e = 0; e < 4; ++e) bits[e] = __float_as_uint(fminf(fmaxf(tt[e], ec.lo), ec.hi));
+            packed[g] = __byte_perm(__byte_perm(bits[0], bits[1], 0x0040), __byte_perm(bits[2], bits[3], 0x0040), 0x5410);
+        } else if (KIND == EPI_LUT) {
+            uint32_t bits[4];
+            #pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                asm("cvt.rni.sat.u8.f32 %0, %1;" : "=r"(bits[e]) : "f"(z[e]));
+                // entry (conv output - type minimum) * pitch + other byte; lut holds the table's address, a multiple of
+                // 256, and the other operand's byte goes into its low 8 bits
+                bits[e] = lds_u8(bits[e] * (uint32_t)TC_LUT_PITCH + __byte_perm(resw[g], lut, 0x7650 + e));
+            }
+            packed[g] = __byte_perm(__byte_perm(bits[0], bits[1], 0x0040), __byte_perm(bits[2], bits[3], 0x0040), 0x5410);
+        } else {
+            // the clamp is the 8-bit type's own range: integer conversion, then two saturating packs
+            int i0, i1, i2, i3;
+            asm("cvt.rni.s32.f32 %0, %1;" : "=r"(i0) : "f"(z[0]));
+            asm("cvt.rni.s32.f32 %0, %1;" : "=r"(i1) : "f"(z[1]));
+            asm("cvt.rni.s32.f32 %0, %1;" : "=r"(i2) : "f"(z[2]));
+            asm("cvt.rni.s32.f32 %0, %1;" : "=r"(i3) : "f"(z[3]));
+            uint32_t hi16;
+            if (KIND == EPI_SAT_S8) {
+                asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi16) : "r"(i3), "r"(i2), "r"(0));
+                asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(packed[g]) : "r"(i1), "r"(i0), "r"(hi16));
+            } else {
+                asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(hi16) : "r"(i3), "r"(i2), "r"(0));
+                asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(packed[g]) : "r"(i1), "r"(i0), "r"(hi16));
+            }
+        }
+    }
+    return make_uint4(packed[0], packed[1], packed[2], packed[3]);
+}
+
+// Four values the hot path could not vouch for: the reference chain itself, division evaluated exactly by
+// Markstein's correction (see epi_chunk), rounded with the magic constant; only a value that is an exact half (which
+// the reference rounds away from zero) or beyond the constant goes on to the plain reference arithmetic.  Kept out of
+// line: it runs for a few per cent of the groups and would otherwise be inlined sixteen times into every tile loop.
+template <int KIND>
+__device__ __noinline__ uint32_t epi_fix_group(int a0, int a1, int a2, int a3, uint32_t a_m, uint32_t a_b, uint32_t a_cc, uint32_t resw,
+                                               const EpiConsts* ecp, uint32_t lut, const EpiExact* x)
+{
+    const EpiConsts& ec = *ecp;
+    const float2 zoff2 = KIND == EPI_LUT ? ec.zoff_lut2 : (KIND == EPI_CLAMP ? ec.zoff_clamp2 : ec.zoff_sat2);
+    float2 m01, m23, b01, b23;
+    lds_f2x2(a_m, m01, m23);
+    lds_f2x2(a_b, b01, b23);
+    const uint4 cv = lds128(a_cc);
+    const int acc[4] = {a0 - (int)cv.x, a1 - (int)cv.y, a2 - (int)cv.z, a3 - (int)cv.w};
+    const float2 a01 = make_float2(__int2float_rn(acc[0]), __int2float_rn(acc[1]));
+    const float2 a23 = make_float2(__int2float_rn(acc[2]), __int2float_rn(acc[3]));
+    const float2 v01 = __fadd2_rn(__ffma2_rn(a01, m01, ec.zero2), b01), v23 = __fadd2_rn(__ffma2_rn(a23, m23, ec.zero2), b23);
+    const float2 p01 = __ffma2_rn(v01, ec.inv2, ec.zero2), p23 = __ffma2_rn(v23, ec.inv2, ec.zero2);
+    const float2 q01 = __ffma2_rn(__ffma2_rn(p01, ec.nsy2, v01), ec.inv2, p01), q23 = __ffma2_rn(__ffma2_rn(p23, ec.nsy2, v23), ec.inv2, p23);
+    const float2 t01 = __fadd2_rn(q01, ec.magic2), t23 = __fadd2_rn(q23, ec.magic2);
+    const float2 n01 = __fadd2_rn(t01, ec.nmagic2), n23 = __fadd2_rn(t23, ec.nmagic2);
+    const float2 d01 = __ffma2_rn(n01, ec.neg2, q01), d23 = __ffma2_rn(n23, ec.neg2, q23);
+    const float dmax = fmaxf(fmaxf(fabsf(d01.x), fabsf(d01.y)), fmaxf(fabsf(d23.x), fabsf(d23.y)));
+    const float2 z01 = __fadd2_rn(t01, zoff2), z23 = __fadd2_rn(t23, zoff2);
+    const float z[4] = {z01.x, z01.y, z23.x, z23.y};
+    uint32_t bits[4];
+    #pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        if (KIND == EPI_CLAMP) {
+            bits[e] = __float_as_uint(fminf(fmaxf(z[e], ec.lo), ec.hi));
+        } else {
+            if (KIND == EPI_SAT_S8) asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(bits[e]) : "f"(z[e]));
+            else                    asm("cvt.rni.sat.u8.f32 %0, %1;" : "=r"(bits[e]) : "f"(z[e]));
+            if (KIND == EPI_LUT) bits[e] = lds_u8(bits[e] * (uint32_t)TC_LUT_PITCH + __byte_perm(resw, lut, 0x7650 + e));
+        }
+    }
+    uint32_t out = __byte_perm(__byte_perm(bits[0], bits[1], 0x0040), __byte_perm(bits[2], bits[3], 0x0040), 0x5410);
+    if (!(dmax < 0.5f) || x->always) {
+        // (no usable table, an exact half, or a value too large for the constant)
+        out = 0;
+        #pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int q = exact_value(acc[j], lds_f32(a_m + j * 4), lds_f32(a_b + j * 4), (resw >> (8 * j)) & 0xffu, *x);
+            out |= ((uint32_t)q & 0xffu) << (8 * j);
+        }
+    }
+    return out;
+}
+
+// bq of one (class, column) to within one rounding of its last operation: X = (b - cc m) / sy from error-free
+// products and sums (cc split into two exactly representable parts), one correction step on the quotient, + zoff.
+__device__ __forceinline__ float epi_make_bq(float b, int cc, float m, float sy, float inv_sy, float zoff)
+{
+    const float ch = __int2float_rn(cc & ~0xfff), cl = __int2float_rn(cc & 0xfff);   // both exact
+    const float p1 = __fmul_rn(ch, m), e1 = __fmaf_rn(ch, m, -p1);                   // ch m = p1 + e1
+    const float p2 = __fmul_rn(cl, m), e2 = __fmaf_rn(cl, m, -p2);
+    // s1 + r1 = b - p1, s2 + r2 = s1 - p2 (two-sum)
+    const float s1 = __fsub_rn(b, p1);
+    const float bb1 = __fsub_rn(s1, b);
+    const float r1 = __fadd_rn(__fsub_rn(b, __fsub_rn(s1, bb1)), __fsub_rn(-p1, bb1));
+    const float s2 = __fsub_rn(s1, p2);
+    const float bb2 = __fsub_rn(s2, s1);
+    const float r2 = __fadd_rn(__fsub_rn(s1, __fsub_rn(s2, bb2)), __fsub_rn(-p2, bb2));
+    const float tail = __fsub_rn(__fsub_rn(__fadd_rn(r1, r2), e1), e2);
+    const float hi = __fadd_rn(s2, tail);
+    const float bb3 = __fsub_rn(hi, s2);
+    const float lo = __fadd_rn(__fsub_rn(s2, __fsub_rn(hi, bb3)), __fsub_rn(tail, bb3));
+    const float q0 = __fmul_rn(hi, inv_sy);
+    const float rem = __fadd_rn(__fmaf_rn(-q0, sy, hi), lo);
+    const float q = __fmaf_rn(rem, inv_sy, q0);
+    return __fadd_rn(q, zoff);
+}
+
 // The cold pass of one chunk (rare, or the accumulator dump of the tests): from the 16 accumulators still in
 // registers, (fix) evaluate them with the reference arithmetic (other operand's bytes at res_slot, result to out_slot)
 // and / or (acc_row) write the raw accumulators of a valid row out for the bit-exactness tests.
@@ -582,7 +729,11 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     uint32_t* tmem_slot = (uint32_t*)(w_full + 2);
     uint32_t* s_lut_ok = tmem_slot + 1;                     // the fused-add table in global memory carries our tag
     int32_t* s_cc = (int32_t*)(tmem_slot + 4);              // [classes][BN] zero-point corrections
-    uint8_t* s_lut = (uint8_t*)(((uintptr_t)(s_cc + a.ncls * BN) + 255) & ~(uintptr_t)255);   // fused-add table, 256-byte aligned
+    float* s_mq = (float*)(s_cc + a.ncls * BN);             // [BN] hot-path multiplier m / sy
+    float* s_bq = s_mq + BN;                                // [classes][BN] hot-path addend (see epi_chunk_fast)
+    uint32_t* s_emax = (uint32_t*)(s_bq + a.ncls * BN);     // [2][2] max |bq|, max |b / sy| of a staging (bit patterns), double-buffered
+    EpiExact* s_ex = (EpiExact*)(s_emax + 4);               // the reference arithmetic's constants (epi_fix_group)
+    uint8_t* s_lut = (uint8_t*)(((uintptr_t)(s_emax + 4 + 16) + 255) & ~(uintptr_t)255);   // fused-add table, 256-byte aligned
     // per K-slice: {channel offset, im2col offsets (x | y << 16), weight column, packed-row offset}: the producers read
     // their coordinates from here instead of carrying tap counters through every slice
     uint4* s_tab = (uint4*)(s_lut + (a.add_lut ? TC_LUT_BYTES : 0));
@@ -620,6 +771,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
+    if (threadIdx.x < 4) s_emax[threadIdx.x] = 0u;
     for (int i = threadIdx.x; i < a.nslices; i += TC_THREADS) {
         const int tap = i / a.cchunks, c0 = (i - tap * a.cchunks) * SWZ;
         const int ky = a.im2col == 2 ? tap : tap / a.KW, kx = a.im2col == 2 ? 0 : tap - ky * a.KW;
@@ -830,8 +982,11 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             ex.fused = fused; ex.res_u8 = a.res_u8; ex.zr = (float)a.res_zp; ex.sr = a.res_scale;
             ex.sy2 = a.rq2.sy; ex.zy2 = (float)a.rq2.zy;
             ex.lo2 = fmaxf(a.rq2.tlo, (float)a.rq2.clo); ex.hi2 = fminf(a.rq2.thi, (float)a.rq2.chi);
+            ex.always = always_fix;
             return ex;
         };
+        static_assert(sizeof(EpiExact) <= 64, "EpiExact outgrew its shared-memory slot");
+        if (etid == 0) *s_ex = make_exact();                  // (published by the first staging's barriers)
         const float lo1 = fmaxf(a.rq.tlo, (float)a.rq.clo), hi1 = fminf(a.rq.thi, (float)a.rq.chi), zy1 = (float)a.rq.zy;
         // how the hot path ends (warp-uniform, fixed for the launch)
         const int kind = use_lut ? EPI_LUT
@@ -846,17 +1001,26 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const uint32_t st_flip = a.nstg == 2 ? (uint32_t)EG * (uint32_t)IO_BYTES : 0u;     // distance to the second buffer
         const uint32_t st_sw = W == 64 ? (uint32_t)((lane >> 1) & 3) : (W == 32 ? (uint32_t)((lane >> 2) & 1) : 0u);
         bool dead = false;
+        // what the hot path adds to the requantised value: the output zero point; with the table also minus the type minimum
+        const float zoff = use_lut ? zy1 - a.rq.tlo : zy1;
+        float thr = 0.0f;                                    // 0.5 - E of the staged n-tile (see epi_chunk_fast); 0: no hot path
+        int stagings = 0;
         auto stage_constants = [&](int n0) {
             {
                 // per-channel constants of this n-tile (all epilogue warps are between tiles here)
                 epi_barrier();
+                uint32_t* emax = s_emax + 2 * (stagings & 1);
+                float bq_max = 0.f, bsy_max = 0.f;
                 for (int j = etid; j < BN; j += 32 * TC_EPI_WARPS) {
                     const int ch = min(n0 + j, a.OC - 1);           // columns beyond OC are padding: any finite constants do
-                    s_m[j] = __fmul_rn(a.rq.sx, a.w_scales ? a.w_scales[ch] : a.w_scale);
+                    const float m = __fmul_rn(a.rq.sx, a.w_scales ? a.w_scales[ch] : a.w_scale);
+                    s_m[j] = m;
+                    s_mq[j] = __fdiv_rn(m, a.rq.sy);
                     s_bterm[j] = a.bias ? __fmul_rn(__int2float_rn(a.bias[ch]), a.b_scales ? a.b_scales[ch] : a.b_scale) : 0.f;
                 }
                 for (int i = etid; i < a.ncls * BN; i += 32 * TC_EPI_WARPS) {
                     const int cls = i / BN, j = i - cls * BN;
+                    const int ch = min(n0 + j, a.OC - 1);
                     int v = 0;
                     if (a.need_corr && n0 + j < a.OC) {
                         // sum over the in-image taps of (x - zx)(w - zw) - x w + zw x = -zx w + zx zw
@@ -868,8 +1032,34 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                             (y1 - y0) * (x1 - x0) * a.kvalid_c * a.zx * a.zw;
                     }
                     s_cc[i] = v;
+                    // (recomputed rather than read back: another thread wrote s_m[j] and s_bterm[j])
+                    const float m = __fmul_rn(a.rq.sx, a.w_scales ? a.w_scales[ch] : a.w_scale);
+                    const float b = a.bias ? __fmul_rn(__int2float_rn(a.bias[ch]), a.b_scales ? a.b_scales[ch] : a.b_scale) : 0.f;
+                    const float bq = epi_make_bq(b, v, m, a.rq.sy, a.inv_sy, zoff);
+                    s_bq[i] = bq;
+                    bq_max = fmaxf(bq_max, fabsf(bq));
+                    bsy_max = fmaxf(bsy_max, fabsf(__fmul_rn(b, a.inv_sy)));
                 }
+                // (NaN or infinity anywhere turns into a huge bound: no hot path for this n-tile)
+                const uint32_t w0 = __reduce_max_sync(0xffffffffu, __float_as_uint(bq_max <= 3.0e38f ? bq_max : 3.0e38f));
+                const uint32_t w1 = __reduce_max_sync(0xffffffffu, __float_as_uint(bsy_max <= 3.0e38f ? bsy_max : 3.0e38f));
+                if (lane == 0) { atomicMax(&emax[0], w0); atomicMax(&emax[1], w1); }
                 epi_barrier();
+                {
+                    const float rz = 257.0f;                                                                 // |R + zoff| of interest
+                    const float rmax = fmaxf(fabsf(a.rq.tlo - 1.0f - zy1), fabsf(a.rq.thi + 1.0f - zy1));    // |R| of interest
+                    // big: an accumulator (or accumulator minus correction) of this launch can exceed 2^24, where the
+                    // conversions to fp32 round as well
+                    const float big = a.acc_big ? 1.0f : 0.0f;
+                    const float bsy = 1.0001f * __uint_as_float(emax[1]), bqm = __uint_as_float(emax[0]);
+                    const float e = 1.1f * 5.9604645e-8f *
+                                    ((3.0f + big) * rmax + (1.0f + big) * bsy + (1.0f + big) * (rz + bqm) + 2.0f * bqm + fabsf(zoff) + rz);
+                    // a bound this large means unusual scales: everything takes the reference arithmetic
+                    thr = (always_fix || !(e < 0.0625f)) ? 0.0f : 0.5f - e;
+                }
+                // the other slot: every thread has long finished reading it (it served the staging before this one)
+                if (etid == 0) { s_emax[2 * ((stagings + 1) & 1)] = 0u; s_emax[2 * ((stagings + 1) & 1) + 1] = 0u; }
+                ++stagings;
                 cur_n0 = n0;
             }
         };
@@ -913,6 +1103,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 }
                 const int32_t* corr_row = s_cc + cls * BN;
                 const uint32_t a_m = smem_u32(s_m), a_b = smem_u32(s_bterm), a_cc = smem_u32(corr_row);
+                const uint32_t a_mq = smem_u32(s_mq), a_bq = smem_u32(s_bq + cls * BN);
                 const uint32_t tacc = tmem_base + (uint32_t)(buf * BN) + ((uint32_t)(quad * 32) << 16);
                 // units in which this warp has real columns (a prefix: the last n-tile may reach beyond OC)
                 const int nact = min(UNITS, max(0, (a.OC - n0 - part * (int)W + UW - 1) / UW));
@@ -934,7 +1125,6 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     }
                     __syncwarp();
                     const uint32_t st_row = st_base + (uint32_t)lane * W;
-                    float dm[NCH];
                     #pragma unroll
                     for (int j = 0; j < NCH; ++j) {
                         if ((j & 1) == 0) {
@@ -942,34 +1132,39 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                             if (j + 1 < NCH) tc_ld16_wait(r[1]);
                         }
                         const int col0 = colw + j * 16;
-                        const TabShared ad = {a_m + col0 * 4, a_b + col0 * 4, a_cc + col0 * 4};
+                        const TabFast ad = {a_mq + col0 * 4, a_bq + col0 * 4};
                         const uint4 rv = KIND == EPI_LUT ? lds128(res_row + ((((uint32_t)(part * NCH + j)) ^ sw_x) << 4)) : make_uint4(0, 0, 0, 0);
-                        dm[j] = 0.0f;
-                        const uint4 outv = epi_chunk<KIND>(r[j & 1], rv, ad, a.ep, lut_addr, dm[j]);
+                        float dmg[4];
+                        uint4 outv = epi_chunk_fast<KIND>(r[j & 1], rv, ad, a.ep, lut_addr, dmg);
+                        // groups the hot path cannot vouch for (|q" - n| within E of a half, a huge value, or no usable
+                        // table at all: thr = 0) take the reference arithmetic, from the accumulators still in registers
+                        if (__any_sync(0xffffffffu, fmaxf(fmaxf(dmg[0], dmg[1]), fmaxf(dmg[2], dmg[3])) >= thr)) {
+                            const uint32_t* rr = r[j & 1];
+                            const uint32_t resw[4] = {rv.x, rv.y, rv.z, rv.w};
+                            uint32_t w[4] = {outv.x, outv.y, outv.z, outv.w};
+                            #pragma unroll
+                            for (int g = 0; g < 4; ++g) {
+                                if (__any_sync(0xffffffffu, dmg[g] >= thr))
+                                    w[g] = epi_fix_group<KIND>((int)rr[g * 4], (int)rr[g * 4 + 1], (int)rr[g * 4 + 2], (int)rr[g * 4 + 3],
+                                                               a_m + (col0 + g * 4) * 4, a_b + (col0 + g * 4) * 4, a_cc + (col0 + g * 4) * 4, resw[g],
+                                                               &a.ep, lut_addr, s_ex);
+                            }
+                            outv = make_uint4(w[0], w[1], w[2], w[3]);
+                        }
                         sts128(st_row + (((uint32_t)j ^ st_sw) << 4), outv);
                         if (j + 2 < NCH) tc_ld16_issue(tacc + (uint32_t)(colw + (j + 2) * 16), r[j & 1]);
                     }
-                    float dall = dm[0];
-                    #pragma unroll
-                    for (int j = 1; j < NCH; ++j) dall = fmaxf(dall, dm[j]);
-                    // an exact half (which the reference rounds away from zero) or a value beyond the rounding constant,
-                    // no usable table, or the accumulator dump of the tests: the cold pass redoes those chunks from a
-                    // second read of the accumulators
-                    if (__any_sync(0xffffffffu, dall >= TC_FIX_THRESHOLD) || always_fix || dump_acc) {
+                    // the accumulator dump of the tests: from a second read of the accumulators
+                    if (dump_acc) {
                         const EpiExact ex = make_exact();
                         #pragma unroll 1
                         for (int j = 0; j < NCH; ++j) {
-                            float dj = dm[0];
-                            #pragma unroll
-                            for (int jj = 1; jj < NCH; ++jj) dj = jj == j ? dm[jj] : dj;
-                            const bool fix = always_fix || __any_sync(0xffffffffu, dj >= TC_FIX_THRESHOLD);
-                            if (!fix && !dump_acc) continue;
                             const int col0 = colw + j * 16;
                             uint32_t rr[16];
                             tc_ld16(tacc + (uint32_t)col0, rr);
                             epi_cold(rr, res_row + ((((uint32_t)(part * NCH + j)) ^ sw_x) << 4), st_row + (((uint32_t)j ^ st_sw) << 4),
-                                     a_m + col0 * 4, a_b + col0 * 4, a_cc + col0 * 4, ex, fix,
-                                     (dump_acc && mvalid && n0 + col0 < a.OC) ? a.acc_out + m * a.OC + n0 + col0 : nullptr);
+                                     a_m + col0 * 4, a_b + col0 * 4, a_cc + col0 * 4, ex, false,
+                                     (mvalid && n0 + col0 < a.OC) ? a.acc_out + m * a.OC + n0 + col0 : nullptr);
                         }
                     }
                     if (fused) {
@@ -1333,7 +1528,7 @@ static int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUten
     using L = TcSmem<BN, SWZ>;
     const size_t budget = 227 * 1024;                                   // opt-in shared memory per CTA on sm_100
     TcArgs a2 = a;
-    size_t rest = 1024 + L::CONST_BYTES + (size_t)a.ncls * BN * 4 + (size_t)(EG + a.nio) * L::IO_BYTES + (a.add_lut ? TC_LUT_BYTES : 0) + 256 +
+    size_t rest = 1024 + L::CONST_BYTES + ((size_t)a.ncls * 2 + 1) * BN * 4 + 16 + 64 + (size_t)(EG + a.nio) * L::IO_BYTES + (a.add_lut ? TC_LUT_BYTES : 0) + 256 +
                   (size_t)a.nslices * 16 +
                   (size_t)a.nzw * L::B_BYTES;
     // a second staging buffer per epilogue warp, then a third buffer for the fused Add's other operand (its loads then
@@ -1449,7 +1644,7 @@ int launch_conv_tc(const b200k_conv2d_params* p, cudaStream_t stream, int kvalid
         const float zy1 = (float)a.rq.zy;
         const float lo1 = fmaxf(a.rq.tlo, (float)a.rq.clo), hi1 = fminf(a.rq.thi, (float)a.rq.chi);
         auto two = [](float v) { return make_float2(v, v); };
-        a.ep.inv2 = two(a.inv_sy); a.ep.nsy2 = two(-a.rq.sy); a.ep.magic2 = two(TC_MAGIC); a.ep.zero2 = two(0.f); a.ep.neg2 = two(-1.f);
+        a.ep.inv2 = two(a.inv_sy); a.ep.nsy2 = two(-a.rq.sy); a.ep.magic2 = two(TC_MAGIC); a.ep.zero2 = two(0.f); a.ep.neg2 = two(-1.f); a.ep.nmagic2 = two(-TC_MAGIC);
         a.ep.zoff_lut2 = two((zy1 - a.rq.tlo) - TC_MAGIC);
         a.ep.zoff_sat2 = two(zy1 - TC_MAGIC);
         a.ep.zoff_clamp2 = two(zy1);
@@ -1462,6 +1657,15 @@ int launch_conv_tc(const b200k_conv2d_params* p, cudaStream_t stream, int kvalid
     memset(a.lut_tag, 0, sizeof(a.lut_tag));
     if (fa.res) make_lut_tag(p, a.lut_tag);
     a.nio = fa.res ? 2 : 0;
+    {
+        // worst-case magnitudes: taps * max |x| * max |w| for the accumulator (with the -zw term), zx * taps * max |w| +
+        // taps |zx zw| for the correction
+        const long long taps = (long long)p->kh * p->kw * p->c;
+        const long long xm = p->x.dtype == B200K_U8 ? 255 : 128, wm = p->w.dtype == B200K_U8 ? 255 : 128;
+        const long long azx = a.zx < 0 ? -a.zx : a.zx, azw = a.zw < 0 ? -a.zw : a.zw;
+        const long long amax = taps * xm * (wm + azw), cmax = azx * taps * (wm + azw);
+        a.acc_big = amax + cmax >= (1ll << 24) ? 1 : 0;
+    }
     a.ncy = a.ncx = a.ncls = 1;
     memset(a.ypair, 0, sizeof(a.ypair)); memset(a.xpair, 0, sizeof(a.xpair));
     memset(a.ycls, 0, sizeof(a.ycls));   memset(a.xcls, 0, sizeof(a.xcls));
@@ -1750,9 +1954,17 @@ extern "C" int b200k_int8_mma_peak(double* tops, void* stream_)
     return B200K_OK;
 }
 
+namespace b200k { int fc_stream_poll_status(); }
+
 extern "C" int b200k_poll_status(void)
 {
     int s = 0;
+    const int fs = fc_stream_poll_status();
+    if (fs != 0) {
+        set_error("a bounded device-side wait of the weight-streaming FullyConnected kernel gave up (code %d: 1 producer/ring slot, "
+                  "2 consumer/weights)", fs);
+        return B200K_E_TIMEOUT;
+    }
     B200K_CUDA(cudaMemcpyFromSymbol(&s, g_tc_status, sizeof(int)));
     if (s != 0) {
         int zero = 0;

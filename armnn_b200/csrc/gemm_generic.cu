@@ -12,6 +12,8 @@ namespace b200k {
 int launch_conv_dp4a(const b200k_conv2d_params* p, cudaStream_t stream);
 int conv2d_dispatch(const b200k_conv2d_params* p, cudaStream_t stream);
 bool conv_tc_eligible(const b200k_conv2d_params* p);
+bool fc_stream_eligible(const b200k_fc_params* p);
+int launch_fc_stream(const b200k_fc_params* p, cudaStream_t stream);
 
 struct BmmArgs {
     const void* x; const void* y; void* out; int32_t* acc_out;
@@ -251,6 +253,8 @@ extern "C" int b200k_fully_connected_q8(const b200k_fc_params* p, void* stream)
         // the tcgen05 kernel when it can take the shape; otherwise the row kernel; the CUDA-core convolution for the rest
         // (a few rows are a weight-streaming problem: the row kernel spreads the columns over every SM, whereas the
         // tensor-core kernel would give each 64-column tile's whole K loop to one CTA)
+        // at most 16 rows: nothing but a read of the weights, which the streaming kernel spreads over every SM
+        if (p->algo == 0 && fc_stream_eligible(p)) return launch_fc_stream(p, (cudaStream_t)stream);
         if (p->algo == 0 && fc_rows_eligible(p) && (p->m <= 4 || !conv_tc_eligible(&c))) return launch_fc_rows(p, (cudaStream_t)stream);
         return conv2d_dispatch(&c, (cudaStream_t)stream);
     }

@@ -70,6 +70,15 @@ def fc_cases():
                                                       x_q=(0.03, 119), act=(1, 0, 0))
     c["rows_s8x_u8w"] = lambda: random_fc_case(42, 9, 256, 21, w_dtype=U8, per_axis=False)
     c["rows_u8x_s8w"] = lambda: random_fc_case(43, 9, 256, 21, x_dtype=U8, y_dtype=U8, per_axis=True, x_q=(0.03, 100))
+    # the weight-streaming kernel (at most 16 rows, K a multiple of 64): the sweep's largest point, row-count and column
+    # tails, one and two row halves, both zero points, every operand signedness
+    c["stream_m16_k4096_n4096"] = lambda: random_fc_case(44, 16, 4096, 4096)
+    c["stream_m1_k4096_n4096"] = lambda: random_fc_case(45, 1, 4096, 4096)
+    c["stream_m7_k8192_n1000_u8_zp"] = lambda: random_fc_case(46, 7, 8192, 1000, x_dtype=U8, w_dtype=U8, y_dtype=U8, per_axis=False,
+                                                             x_q=(0.03, 119), act=(1, 0, 0))
+    c["stream_m1_k64_n7"] = lambda: random_fc_case(47, 1, 64, 7)
+    c["stream_m13_k192_n130"] = lambda: random_fc_case(48, 13, 192, 130, x_dtype=U8, y_dtype=U8, x_q=(0.03, 100))
+    c["stream_m9_k1024_n2500_s8x_u8w"] = lambda: random_fc_case(49, 9, 1024, 2500, w_dtype=U8, per_axis=False)
     return c
 
 
