@@ -351,6 +351,33 @@ def fc_sweep_case(m, k, n=None, seed_name=None):
     return net, {"macs": m * k * n, "input_shape": (m, k), "output_shape": (m, n)}
 
 
+def fc_stack(m, k, depth, seed_name=None):
+    """`depth` FullyConnected layers K -> K in a chain, each with its own weights (the quantisation of fc_sweep_case,
+    every output feeding the next layer at scale 0.03, offset 5): with depth * K * K bytes above the L2 capacity a
+    replay reads every weight from HBM, and the per-launch cost is spread over the chain."""
+    rng = _rng(seed_name or "fc_stack_%d_%d_%d" % (m, k, depth))
+    net = INetwork.Create()
+    il = net.AddInputLayer(0, "input")
+    il.GetOutputSlot(0).SetTensorInfo(TensorInfo((m, k), DataType.QAsymmS8, 0.03, 5))
+    cur = il.GetOutputSlot(0)
+    for d in range(depth):
+        w_scales = rng.uniform(0.001, 0.01, size=k).astype(np.float32)
+        wq = rng.integers(-127, 128, size=(k, k)).astype(np.int8)
+        bq = rng.integers(-1000, 1001, size=k).astype(np.int32)
+        wl = net.AddConstantLayer(wq, TensorInfo(wq.shape, DataType.QSymmS8, scales=w_scales, quant_dim=0), "w%d" % d)
+        bl = net.AddConstantLayer(bq, TensorInfo(bq.shape, DataType.Signed32, scales=(np.float32(0.03) * w_scales), quant_dim=0), "b%d" % d)
+        fl = net.AddFullyConnectedLayer(True, True, "fc%d" % d)
+        cur.Connect(fl.GetInputSlot(0))
+        wl.GetOutputSlot(0).Connect(fl.GetInputSlot(1))
+        bl.GetOutputSlot(0).Connect(fl.GetInputSlot(2))
+        # the next layer reads this output as (0.03, 5) whatever its real spread: only the traffic matters here
+        fl.GetOutputSlot(0).SetTensorInfo(TensorInfo((m, k), DataType.QAsymmS8, 0.03, 5))
+        cur = fl.GetOutputSlot(0)
+    ol = net.AddOutputLayer(0, "output")
+    cur.Connect(ol.GetInputSlot(0))
+    return net, {"macs": depth * m * k * k, "input_shape": (m, k), "output_shape": (m, k), "depth": depth}
+
+
 QLSTM_SCALES = dict(input=2.0 ** -7, hidden=0.007, cell=2.0 ** -15, weights=0.00784314, layer_norm=3.05182e-05,
                     intermediate_i=0.007059, intermediate_f=0.007812, projection=0.00392157)
 

@@ -71,6 +71,22 @@ constexpr long long TC_WAIT_LIMIT_CYCLES = 4000000000ll;  // about two seconds: 
 
 __device__ int g_tc_status = 0;                 // 0 ok, otherwise the code of the wait that gave up
 
+// Phase time stamps of CTA 0 (nanoseconds, %globaltimer), compiled in only with -DB200K_TRACE, which the build never sets.
+#ifdef B200K_TRACE
+__device__ unsigned long long g_tc_trace[16];
+__device__ __forceinline__ void tc_trace(int i)
+{
+    if (blockIdx.x == 0 && (threadIdx.x & 31) == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        g_tc_trace[i] = t;
+    }
+}
+#define TC_TRACE(i) tc_trace(i)
+#else
+#define TC_TRACE(i) do { } while (0)
+#endif
+
 // Constants of the hot path, filled in by the host: they sit in the kernel's parameter space, so the packed
 // instructions read them as constant-bank operands and they take no registers.  Each is the same value twice.
 struct EpiConsts {
@@ -738,6 +754,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // their coordinates from here instead of carrying tap counters through every slice
     uint4* s_tab = (uint4*)(s_lut + (a.add_lut ? TC_LUT_BYTES : 0));
 
+    if (threadIdx.x == 0) TC_TRACE(0);
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");     // the next kernel of the stream may begin its set-up
     const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;   // warp: provably uniform
     const int ntn = a.ntn;                                  // n-tiles; the last one may reach beyond OC (zero weights, clipped stores)
@@ -782,6 +799,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    if (threadIdx.x == 0) TC_TRACE(1);
 
     const int prod = warp == 0 ? 0 : (warp >= 2 + TC_EPI_WARPS ? warp - (1 + TC_EPI_WARPS) : -1);
     if (prod >= 0) {
@@ -819,6 +837,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             }
             asm volatile("griddepcontrol.wait;" ::: "memory");
             for (int t = blockIdx.x; t < ntiles && alive; t += gridDim.x) {
+                if (prod == 0 && t == blockIdx.x) TC_TRACE(2);
                 // tile coordinates: only worked out by a producer that loads something of this tile
                 int n0 = 0, tm = 0, w0 = 0, h0 = 0, nimg = 0;
                 long long m0 = 0;
@@ -903,6 +922,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const uint64_t dbstep = bstat ? dwslice : dstage;            // from one slice's weight tile to the next
             const uint64_t dz0 = make_smem_desc<SWZ>(smem_u32(s_zw));
             if (bstat && !__all_sync(0xffffffffu, mbar_wait(w_full, 0, wait_limit))) { atomicExch(&g_tc_status, 7); alive = false; }
+            TC_TRACE(3);
             tc_fence_after();
             for (int t = blockIdx.x; t < ntiles && alive; t += gridDim.x, ++it) {
                 const int buf = it & ((1 << NACC_LOG2) - 1);
@@ -933,6 +953,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     if (++st == STAGES) { st = 0; ph ^= 1u; }
                 }
                 if (alive && elect_one()) tc_commit(&acc_full[buf]);  // accumulator of this tile complete
+                if (it == 0) TC_TRACE(4);
             }
         }
     } else {
@@ -971,6 +992,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             if (!mbar_wait(lut_full, 0, a.wait_limit)) { atomicExch(&g_tc_status, 8); lut_ok = false; }
         }
         const bool use_lut = fused && lut_ok;
+        if (ew == 0) TC_TRACE(5);
         const bool always_fix = fused && !lut_ok;            // no table: every chunk takes the reference arithmetic
         const bool dump_acc = a.acc_out != nullptr;
         // the reference arithmetic's constants: only the cold pass uses them, which rebuilds them from the launch
@@ -1066,6 +1088,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         // groups only exist with a single n-tile: its constants are staged once, by all warps, before any warp could
         // find itself without a tile
         if (eg > 1) stage_constants(0);
+        if (ew == 0) TC_TRACE(6);
         // The tile loop exists once per way the hot path ends (KIND, fixed for the launch), chosen by one switch below, so
         // that the per-chunk code is straight-line.
         auto run_tiles = [&](auto kind_tag) {
@@ -1081,6 +1104,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 const int buf = it & ((1 << NACC_LOG2) - 1);
                 if (n0 != cur_n0) stage_constants(n0);
                 if (!dead && !mbar_wait(&acc_full[buf], ((uint32_t)it >> NACC_LOG2) & 1u, a.wait_limit)) { atomicExch(&g_tc_status, 3); dead = true; }
+                if (ew == 0 && t == blockIdx.x) TC_TRACE(7);
                 tc_fence_after();
                 const long long m = m0 + row;
                 const bool mvalid = row < a.tile_rows && m < a.M;
@@ -1135,7 +1159,12 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         const TabFast ad = {a_mq + col0 * 4, a_bq + col0 * 4};
                         const uint4 rv = KIND == EPI_LUT ? lds128(res_row + ((((uint32_t)(part * NCH + j)) ^ sw_x) << 4)) : make_uint4(0, 0, 0, 0);
                         float dmg[4];
+#ifdef B200K_X_NOMATH
+                        dmg[0] = dmg[1] = dmg[2] = dmg[3] = 0.f;
+                        uint4 outv = make_uint4(r[j & 1][0] ^ r[j & 1][4] ^ rv.x, r[j & 1][1] ^ r[j & 1][5] ^ ad.mq, r[j & 1][2] ^ r[j & 1][6], r[j & 1][3] ^ r[j & 1][7]);
+#else
                         uint4 outv = epi_chunk_fast<KIND>(r[j & 1], rv, ad, a.ep, lut_addr, dmg);
+#endif
                         // groups the hot path cannot vouch for (|q" - n| within E of a half, a huge value, or no usable
                         // table at all: thr = 0) take the reference arithmetic, from the accumulators still in registers
                         if (__any_sync(0xffffffffu, fmaxf(fmaxf(dmg[0], dmg[1]), fmaxf(dmg[2], dmg[3])) >= thr)) {
@@ -1177,8 +1206,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     __syncwarp();
                     if (lane == 0) {
                         const int row0 = quad * 32;
+#ifndef B200K_X_NOSTORE
                         if (row0 < a.tile_rows && m0 + row0 < a.M)
                             tma_store_3d(&tmY, st_base, n0 + colw, a.im2col == 2 ? row0 : (int)(m0 + row0), a.im2col == 2 ? tm : 0);
+#endif
                         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                     }
                     st_base = st_base == st_base0 ? st_base0 + st_flip : st_base0;
@@ -1199,6 +1230,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&acc_empty[buf]);
+                if (ew == 0 && t == blockIdx.x) TC_TRACE(8);
+                if (ew == 0) TC_TRACE(9);
             }
         };
         switch (kind) {
@@ -1209,6 +1242,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         // shared memory may go once the last store has read it; its global writes complete with the kernel
         if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        if (ew == 0) TC_TRACE(10);
     }
 
     tc_fence_before();
@@ -1216,6 +1250,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(BN << NACC_LOG2) : "memory");
+        TC_TRACE(11);
     }
 }
 
@@ -1953,6 +1988,15 @@ extern "C" int b200k_int8_mma_peak(double* tops, void* stream_)
     *tops = best;
     return B200K_OK;
 }
+
+#ifdef B200K_TRACE
+extern "C" int b200k_tc_trace(unsigned long long* out16)
+{
+    B200K_CUDA(cudaDeviceSynchronize());
+    B200K_CUDA(cudaMemcpyFromSymbol(out16, g_tc_trace, sizeof(unsigned long long) * 16));
+    return B200K_OK;
+}
+#endif
 
 namespace b200k { int fc_stream_poll_status(); }
 

@@ -16,7 +16,7 @@
 // 16 x 8 sums are added through shared memory.
 //
 // Zero points: sum (x - zx)(w - zw) = sum x w - zw sum x - zx sum w + K zx zw; sum x per input row is formed once per
-// launch, sum w per weight row comes from a second MMA against an all-ones A (only when zx != 0).  The requantisation
+// launch, sum w per weight row from the bytes each lane has loaded anyway (only when zx != 0).  The requantisation
 // is requant_fast, the same function as in the other FullyConnected kernels.
 //
 // Every wait on an mbarrier is bounded: a wait that gives up raises a status word (b200k_poll_status) and the CTA
@@ -180,31 +180,50 @@ __global__ void __launch_bounds__(FS_THREADS, 1) fc_stream_kernel(const FsArgs a
         const int n0 = u * a.R;
         const int rows = min(a.R, a.N - n0);
         if (!dead && !fs_wait(&full[s], ph, a.wait_limit)) { atomicExch(&g_fs_status, 2); dead = true; }
-        int acc[4] = {0, 0, 0, 0}, wsum[4] = {0, 0, 0, 0};
+        // four independent accumulator sets: consecutive MMAs do not wait for one another (a dependent mma.sync chain,
+        // not the weight stream, would otherwise set the time per unit)
+        int acc[4][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}, {0, 0, 0, 0}, {0, 0, 0, 0}};
+        int wl = 0;                                          // this lane's share of sum w of weight row g
         const uint32_t w_addr = fs_smem_u32(s_ring) + (uint32_t)((s * a.R + g) * a.pitch + t * 16);
         if (!dead) {
-            for (int b = warp; b < nblk; b += FS_WARPS) {
-                const uint4 xa = fs_lds128(xa_addr + b * 64);
-                const uint4 xb = two_halves ? fs_lds128(xb_addr + b * 64) : make_uint4(0, 0, 0, 0);
-                const uint4 wv = g < rows ? fs_lds128(w_addr + b * 64) : make_uint4(0, 0, 0, 0);
-                fs_mma<XU, WU>(acc, xa.x, xb.x, xa.y, xb.y, wv.x, wv.y);
-                fs_mma<XU, WU>(acc, xa.z, xb.z, xa.w, xb.w, wv.z, wv.w);
+            const bool wrow = g < rows;
+            #pragma unroll 2
+            for (int b = warp; b < nblk; b += 2 * FS_WARPS) {
+                const int b2 = b + FS_WARPS;
+                const bool second = b2 < nblk;
+                const uint4 xa0 = fs_lds128(xa_addr + b * 64);
+                const uint4 xb0 = two_halves ? fs_lds128(xb_addr + b * 64) : make_uint4(0, 0, 0, 0);
+                const uint4 wv0 = wrow ? fs_lds128(w_addr + b * 64) : make_uint4(0, 0, 0, 0);
+                const uint4 xa1 = second ? fs_lds128(xa_addr + b2 * 64) : make_uint4(0, 0, 0, 0);
+                const uint4 xb1 = (second && two_halves) ? fs_lds128(xb_addr + b2 * 64) : make_uint4(0, 0, 0, 0);
+                const uint4 wv1 = (second && wrow) ? fs_lds128(w_addr + b2 * 64) : make_uint4(0, 0, 0, 0);
+                fs_mma<XU, WU>(acc[0], xa0.x, xb0.x, xa0.y, xb0.y, wv0.x, wv0.y);
+                fs_mma<XU, WU>(acc[1], xa0.z, xb0.z, xa0.w, xb0.w, wv0.z, wv0.w);
+                fs_mma<XU, WU>(acc[2], xa1.x, xb1.x, xa1.y, xb1.y, wv1.x, wv1.y);
+                fs_mma<XU, WU>(acc[3], xa1.z, xb1.z, xa1.w, xb1.w, wv1.z, wv1.w);
                 if (a.zx != 0) {
-                    fs_mma<XU, WU>(wsum, 0x01010101u, 0x01010101u, 0x01010101u, 0x01010101u, wv.x, wv.y);
-                    fs_mma<XU, WU>(wsum, 0x01010101u, 0x01010101u, 0x01010101u, 0x01010101u, wv.z, wv.w);
+                    wl = dp4a_mixed<WU, true>(wv0.x, 0x01010101u, wl); wl = dp4a_mixed<WU, true>(wv0.y, 0x01010101u, wl);
+                    wl = dp4a_mixed<WU, true>(wv0.z, 0x01010101u, wl); wl = dp4a_mixed<WU, true>(wv0.w, 0x01010101u, wl);
+                    wl = dp4a_mixed<WU, true>(wv1.x, 0x01010101u, wl); wl = dp4a_mixed<WU, true>(wv1.y, 0x01010101u, wl);
+                    wl = dp4a_mixed<WU, true>(wv1.z, 0x01010101u, wl); wl = dp4a_mixed<WU, true>(wv1.w, 0x01010101u, wl);
                 }
             }
         }
+        #pragma unroll
+        for (int c = 0; c < 4; ++c) acc[0][c] += acc[1][c] + acc[2][c] + acc[3][c];
+        // sum w of row g: the four lanes of a group hold the four 16-byte columns
+        wl += __shfl_xor_sync(0xffffffffu, wl, 1);
+        wl += __shfl_xor_sync(0xffffffffu, wl, 2);
         // this warp has read its part of the stage
         __syncwarp();
         if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(fs_smem_u32(&empty[s])) : "memory");
         if (++s == a.stages) { s = 0; ph ^= 1u; }
         // partial sums of this warp: C fragment (row g: columns 2t, 2t + 1; row g + 8 likewise)
         int* part = s_part + ((it & 1) * FS_WARPS + warp) * 128;
-        part[g * 8 + 2 * t] = acc[0]; part[g * 8 + 2 * t + 1] = acc[1];
-        part[(g + 8) * 8 + 2 * t] = acc[2]; part[(g + 8) * 8 + 2 * t + 1] = acc[3];
+        part[g * 8 + 2 * t] = acc[0][0]; part[g * 8 + 2 * t + 1] = acc[0][1];
+        part[(g + 8) * 8 + 2 * t] = acc[0][2]; part[(g + 8) * 8 + 2 * t + 1] = acc[0][3];
         int* wpart = s_wpart + ((it & 1) * FS_WARPS + warp) * 8;
-        if (g == 0) { wpart[2 * t] = wsum[0]; wpart[2 * t + 1] = wsum[1]; }
+        if (t == 0) wpart[g] = wl;
         fs_consumer_barrier();
         if (ctid < 128) {
             const int m = ctid >> 3, nl = ctid & 7;
@@ -260,10 +279,16 @@ int launch_fc_stream(const b200k_fc_params* p, cudaStream_t stream)
     a.M = p->m; a.K = p->k; a.N = p->n;
     a.pitch = p->k + 64;
     a.mp = p->m <= 8 ? 8 : 16;
-    // rows per unit: as many as still leave every SM several units (balance), at most 8 (the MMA's width)
+    // rows per unit (at most 8, the MMA's width): the fewest rounds of units over the SMs, each round costing a fixed
+    // quarter of a microsecond (barrier, reduction, requantisation) plus the unit's share of the SM's 43 GB/s of HBM
     a.R = 1;
-    for (int r = 8; r > 1; r >>= 1) {
-        if ((p->n + r - 1) / r >= 4 * sms) { a.R = r; break; }
+    {
+        double best = 1e30;
+        for (int r = 1; r <= 8; r <<= 1) {
+            const long long u = (p->n + r - 1) / r;
+            const double cost = (double)((u + sms - 1) / sms) * (0.25 + (double)r * p->k / 43.0e3);
+            if (cost < best * 0.999) { best = cost; a.R = r; }
+        }
     }
     const size_t budget = 227 * 1024;
     const size_t fixed = (size_t)a.mp * a.pitch + (2 * FS_WARPS * 128 + 2 * FS_WARPS * 8 + 16) * 4 + 2 * FS_MAX_STAGES * 8 + 128;

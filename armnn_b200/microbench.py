@@ -146,6 +146,15 @@ def main(argv=None):
             ms = _time_whole(ln, torch, getattr(args, "reps", 5), inner=10)
             nbytes = m * k + n * k + m * n
             print("fc  M=%-5d K=%-5d N=%-5d  %.4f ms  %8.1f TOP/s  %7.0f GB/s" % (m, k, n, ms, 2.0 * info["macs"] / ms / 1e9, nbytes / ms / 1e6))
+            if k == n:
+                # a chain of layers with their own weights in one graph: per-layer time without the launch of a graph per
+                # layer, and (K = 4096: 10 x 16.8 MB) with every weight read from HBM
+                depth = max(2, min(64, -(-160 * 1024 * 1024 // (k * k))))
+                net, info = configs.fc_stack(m, k, depth)
+                ln, torch = _load(net, graph=True)
+                ms = _time_whole(ln, torch, getattr(args, "reps", 5), inner=10) / depth
+                print("    chain of %2d: %.4f ms per layer  %8.1f TOP/s  %7.0f GB/s (weights %s)" % (
+                    depth, ms, 2.0 * m * k * k / ms / 1e9, nbytes / ms / 1e6, "from HBM" if depth * k * k > 126e6 else "L2-resident"))
     elif args.cmd == "layers":
         net, info = (configs.resnet50 if args.net == "resnet50" else configs.mobilenet_v2)(args.batch, 224)
         ln, torch = _load(net)
