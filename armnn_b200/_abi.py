@@ -42,7 +42,7 @@ class BmmParams(C.Structure):
                 ("batch", C.c_int32), ("m", C.c_int32), ("k", C.c_int32), ("n", C.c_int32),
                 ("transpose_x", C.c_int32), ("transpose_y", C.c_int32),
                 ("batch_stride_x", C.c_int64), ("batch_stride_y", C.c_int64),
-                ("acc_out", C.c_void_p)]
+                ("acc_out", C.c_void_p), ("algo", C.c_int32)]
 
 
 class Pool2dParams(C.Structure):

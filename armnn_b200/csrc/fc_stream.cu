@@ -38,7 +38,7 @@ struct FsArgs {
     const float* w_scales; const float* b_scales;
     float w_scale, b_scale;
     int zx, zw, M, K, N;
-    int R, stages, pitch, mp;                        // weight rows per unit, ring depth, row pitch in bytes, staged input rows (8 or 16)
+    int R, stages, pitch, mp;                        // weight rows per unit, ring depth, row pitch in bytes, staged input rows (= M)
     float sx, sy, inv_sy, zy, lo, hi;
     long long wait_limit;
 };
@@ -95,7 +95,7 @@ __device__ __forceinline__ void fs_consumer_barrier()
 }
 
 template <bool XU, bool WU>
-__global__ void __launch_bounds__(FS_THREADS, 1) fc_stream_kernel(const FsArgs a)
+__global__ void __launch_bounds__(FS_THREADS, 2) fc_stream_kernel(const FsArgs a)
 {
     extern __shared__ __align__(128) uint8_t fs_smem[];
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -147,7 +147,7 @@ __global__ void __launch_bounds__(FS_THREADS, 1) fc_stream_kernel(const FsArgs a
         const int kv = a.K / 16;
         for (int i = ctid; i < a.mp * kv; i += 32 * FS_WARPS) {
             const int r = i / kv, c = i - r * kv;
-            const uint4 v = r < a.M ? *(const uint4*)(a.x + (size_t)r * a.K + c * 16) : make_uint4(0, 0, 0, 0);
+            const uint4 v = *(const uint4*)(a.x + (size_t)r * a.K + c * 16);
             *(uint4*)(s_x + (size_t)r * a.pitch + c * 16) = v;
         }
         fs_consumer_barrier();
@@ -172,7 +172,7 @@ __global__ void __launch_bounds__(FS_THREADS, 1) fc_stream_kernel(const FsArgs a
     const int g = lane >> 2, t = lane & 3;
     const uint32_t xa_addr = fs_smem_u32(s_x) + (uint32_t)(g * a.pitch + t * 16);
     const uint32_t xb_addr = xa_addr + (uint32_t)(8 * a.pitch);
-    const bool two_halves = a.mp > 8;
+    const bool row_a = g < a.M, row_b = g + 8 < a.M;        // fragment rows without an input row are zero
     const int nblk = a.K / 64;
     int s = 0; uint32_t ph = 0, it = 0;
     bool dead = false;
@@ -191,11 +191,11 @@ __global__ void __launch_bounds__(FS_THREADS, 1) fc_stream_kernel(const FsArgs a
             for (int b = warp; b < nblk; b += 2 * FS_WARPS) {
                 const int b2 = b + FS_WARPS;
                 const bool second = b2 < nblk;
-                const uint4 xa0 = fs_lds128(xa_addr + b * 64);
-                const uint4 xb0 = two_halves ? fs_lds128(xb_addr + b * 64) : make_uint4(0, 0, 0, 0);
+                const uint4 xa0 = row_a ? fs_lds128(xa_addr + b * 64) : make_uint4(0, 0, 0, 0);
+                const uint4 xb0 = row_b ? fs_lds128(xb_addr + b * 64) : make_uint4(0, 0, 0, 0);
                 const uint4 wv0 = wrow ? fs_lds128(w_addr + b * 64) : make_uint4(0, 0, 0, 0);
-                const uint4 xa1 = second ? fs_lds128(xa_addr + b2 * 64) : make_uint4(0, 0, 0, 0);
-                const uint4 xb1 = (second && two_halves) ? fs_lds128(xb_addr + b2 * 64) : make_uint4(0, 0, 0, 0);
+                const uint4 xa1 = (second && row_a) ? fs_lds128(xa_addr + b2 * 64) : make_uint4(0, 0, 0, 0);
+                const uint4 xb1 = (second && row_b) ? fs_lds128(xb_addr + b2 * 64) : make_uint4(0, 0, 0, 0);
                 const uint4 wv1 = (second && wrow) ? fs_lds128(w_addr + b2 * 64) : make_uint4(0, 0, 0, 0);
                 fs_mma<XU, WU>(acc[0], xa0.x, xb0.x, xa0.y, xb0.y, wv0.x, wv0.y);
                 fs_mma<XU, WU>(acc[1], xa0.z, xb0.z, xa0.w, xb0.w, wv0.z, wv0.w);
@@ -256,8 +256,7 @@ bool fc_stream_eligible(const b200k_fc_params* p)
     if (p->w.scales && p->w.zero_point != 0) return false;
     // the input rows and at least two one-row stages must fit
     const size_t pitch = (size_t)p->k + 64;
-    const int mp = p->m <= 8 ? 8 : 16;
-    return (size_t)(mp + 2) * pitch + 16 * 1024 <= 227 * 1024 && (long long)p->k * 255 * 255 < (1ll << 31);
+    return (size_t)(p->m + 2) * pitch + 16 * 1024 <= 227 * 1024 && (long long)p->k * 255 * 255 < (1ll << 31);
 }
 
 int launch_fc_stream(const b200k_fc_params* p, cudaStream_t stream)
@@ -278,24 +277,30 @@ int launch_fc_stream(const b200k_fc_params* p, cudaStream_t stream)
     a.zx = p->x.zero_point; a.zw = p->w.scales ? 0 : p->w.zero_point;
     a.M = p->m; a.K = p->k; a.N = p->n;
     a.pitch = p->k + 64;
-    a.mp = p->m <= 8 ? 8 : 16;
-    // rows per unit (at most 8, the MMA's width): the fewest rounds of units over the SMs, each round costing a fixed
-    // quarter of a microsecond (barrier, reduction, requantisation) plus the unit's share of the SM's 43 GB/s of HBM
-    a.R = 1;
+    a.mp = p->m;
+    // Two CTAs fit an SM when each takes at most half of its shared memory: under programmatic dependent launch the
+    // next layer's CTAs then become resident while this layer's are still computing and their producers stream weights
+    // in the meantime, which hides the launch and the first loads' latency.  That only pays while each CTA still keeps
+    // about 90 KB of weights in flight (an SM's share of the HBM bandwidth times the latency under load): with one or
+    // two input rows, say.  Otherwise one CTA per SM with all of the shared memory.
+    // Rows per unit (at most 8, the MMA's width): the fewest rounds of units over the SMs, each round costing a fixed
+    // quarter of a microsecond (barrier, reduction, requantisation) plus the unit's share of the SM's 43 GB/s of HBM.
+    const size_t fixed = (size_t)a.mp * a.pitch + (2 * FS_WARPS * 128 + 2 * FS_WARPS * 8 + 16) * 4 + 2 * FS_MAX_STAGES * 8 + 128;
+    const size_t budget = fixed + 90 * 1024 <= 112 * 1024 ? 112 * 1024 : 227 * 1024;
+    a.R = 0;
     {
         double best = 1e30;
         for (int r = 1; r <= 8; r <<= 1) {
+            if (fixed + (size_t)3 * r * a.pitch > budget && r > 1) break;
+            if (fixed + (size_t)2 * r * a.pitch > budget) break;
             const long long u = (p->n + r - 1) / r;
             const double cost = (double)((u + sms - 1) / sms) * (0.25 + (double)r * p->k / 43.0e3);
             if (cost < best * 0.999) { best = cost; a.R = r; }
         }
     }
-    const size_t budget = 227 * 1024;
-    const size_t fixed = (size_t)a.mp * a.pitch + (2 * FS_WARPS * 128 + 2 * FS_WARPS * 8 + 16) * 4 + 2 * FS_MAX_STAGES * 8 + 128;
-    while (a.R > 1 && fixed + 2 * (size_t)a.R * a.pitch > budget) a.R >>= 1;
+    B200K_REQUIRE(a.R > 0, B200K_E_TOOBIG, "fully_connected_q8: K = %d does not fit the streaming kernel", p->k);
     long long stages = (long long)((budget - fixed) / ((size_t)a.R * a.pitch));
     if (stages > FS_MAX_STAGES) stages = FS_MAX_STAGES;
-    B200K_REQUIRE(stages >= 2, B200K_E_TOOBIG, "fully_connected_q8: K = %d does not fit the streaming kernel", p->k);
     a.stages = (int)stages;
     const Requant rq = make_requant(p->x.scale, p->y, p->clamp_lo, p->clamp_hi);
     a.sx = rq.sx; a.sy = rq.sy; a.inv_sy = rn_reciprocal(p->y.scale); a.zy = (float)rq.zy;
@@ -308,7 +313,7 @@ int launch_fc_stream(const b200k_fc_params* p, cudaStream_t stream)
     #define B200K_FS_LAUNCH(XU, WU, IDX)                                                                              \
         do {                                                                                                          \
             if (!configured[dev][IDX].load(std::memory_order_acquire)) {                                              \
-                B200K_CUDA(cudaFuncSetAttribute(fc_stream_kernel<XU, WU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget)); \
+                B200K_CUDA(cudaFuncSetAttribute(fc_stream_kernel<XU, WU>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024)); \
                 configured[dev][IDX].store(true, std::memory_order_release);                                          \
             }                                                                                                         \
             launch_pdl(fc_stream_kernel<XU, WU>, grid, dim3(FS_THREADS), smem, stream, a);                            \

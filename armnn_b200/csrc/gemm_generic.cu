@@ -1,8 +1,6 @@
-// Layout-agnostic quantised matrix product on CUDA cores: BatchMatMul with optional transposes and
-// broadcast, and FullyConnected with non-transposed ([K, N]) weights.  16 x 16 output tile per CTA,
-// operands staged through shared memory as zero-point-corrected ints.  Shapes on this path are small
-// (attention-style batched products, unusual weight layouts); the large FullyConnected / 1x1
-// convolution GEMMs go through the implicit-GEMM kernels.
+// Layout-agnostic quantised matrix product on CUDA cores: the fallback of BatchMatMul (whose default is the
+// tensor-core kernel of bmm_mma.cu) and FullyConnected with non-transposed ([K, N]) weights.  16 x 16 output tile per
+// CTA, operands staged through shared memory as zero-point-corrected ints.
 #include <string.h>
 #include <atomic>
 #include "common.cuh"
@@ -13,6 +11,8 @@ int launch_conv_dp4a(const b200k_conv2d_params* p, cudaStream_t stream);
 int conv2d_dispatch(const b200k_conv2d_params* p, cudaStream_t stream);
 bool conv_tc_eligible(const b200k_conv2d_params* p);
 bool fc_stream_eligible(const b200k_fc_params* p);
+bool bmm_mma_eligible(const b200k_bmm_params* p);
+int launch_bmm_mma(const b200k_bmm_params* p, cudaStream_t stream);
 int launch_fc_stream(const b200k_fc_params* p, cudaStream_t stream);
 
 struct BmmArgs {
@@ -68,6 +68,8 @@ extern "C" int b200k_batch_matmul_q8(const b200k_bmm_params* p, void* stream)
                   "batch_matmul_q8: only 8-bit quantised tensors are supported");
     B200K_REQUIRE(p->batch > 0 && p->m > 0 && p->k > 0 && p->n > 0, B200K_E_INVALID, "batch_matmul_q8: bad shape");
     B200K_REQUIRE(p->batch <= 65535, B200K_E_TOOBIG, "batch_matmul_q8: batch %d > 65535", p->batch);
+    B200K_REQUIRE(p->algo == 0 || p->algo == 1, B200K_E_INVALID, "batch_matmul_q8: algo %d not in {0,1}", p->algo);
+    if (p->algo == 0 && bmm_mma_eligible(p)) return launch_bmm_mma(p, (cudaStream_t)stream);
     BmmArgs a;
     a.x = p->x.data; a.y = p->y.data; a.out = (void*)p->out.data; a.acc_out = p->acc_out;
     a.bias = nullptr; a.w_scales = nullptr; a.b_scales = nullptr; a.w_scale = p->y.scale; a.b_scale = 0.f;

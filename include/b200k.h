@@ -169,6 +169,8 @@ typedef struct {
     int32_t transpose_x, transpose_y;
     int64_t batch_stride_x, batch_stride_y;   /* elements; 0 = broadcast */
     int32_t* acc_out;
+    int32_t algo;                             /* 0 = tensor-core kernel (mma.sync on 128 x 128 tiles, either layout of
+                                                 either operand), 1 = the CUDA-core kernel */
 } b200k_bmm_params;
 
 int b200k_batch_matmul_q8(const b200k_bmm_params* p, void* stream);

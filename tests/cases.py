@@ -104,9 +104,34 @@ def bmm_cases():
             acc, p.acc_out = mem.out((batch, m, n), np.int32)
             return p, [out, acc]
         return lambda: SimpleCase("batch_matmul_q8", build)
-    return {"plain": make(41, 3, 17, 33, 9, False, False), "transpose_x": make(42, 2, 8, 16, 8, True, False),
-            "transpose_y": make(43, 2, 8, 16, 12, False, True), "broadcast_y": make(44, 4, 5, 20, 6, False, False, True),
-            "u8": make(45, 1, 16, 16, 16, False, False, xd=U8, yd=U8)}
+    c = {"plain": make(41, 3, 17, 33, 9, False, False), "transpose_x": make(42, 2, 8, 16, 8, True, False),
+         "transpose_y": make(43, 2, 8, 16, 12, False, True), "broadcast_y": make(44, 4, 5, 20, 6, False, False, True),
+         "u8": make(45, 1, 16, 16, 16, False, False, xd=U8, yd=U8)}
+    # the tensor-core kernel: several 128 x 128 tiles with ragged edges, every layout of either operand (16-byte
+    # aligned rows and not), K beyond one 64-byte step and not a multiple of it, every signedness, broadcast
+    for i, (tx, ty) in enumerate(((False, False), (False, True), (True, False), (True, True))):
+        c["tiles_tx%d_ty%d" % (tx, ty)] = make(50 + i, 2, 200, 150, 170, tx, ty)
+        c["aligned_tx%d_ty%d" % (tx, ty)] = make(54 + i, 3, 256, 128, 144, tx, ty)
+    c["attention_qk"] = make(58, 12, 128, 64, 128, False, True)
+    c["attention_pv_u8x"] = make(59, 12, 128, 128, 64, False, False, xd=U8)
+    c["u8y_transposed_both"] = make(60, 2, 70, 96, 130, True, True, yd=U8)
+    c["broadcast_y_tiles"] = make(61, 5, 130, 80, 64, False, False, True)
+    c["k1"] = make(62, 1, 3, 1, 5, False, False)
+    # the CUDA-core kernel stays reachable
+    def generic(case):
+        def build():
+            sc = case()
+            inner = sc.build
+            def build2(mem):
+                p, outs = inner(mem)
+                p.algo = 1
+                return p, outs
+            sc.build = build2
+            return sc
+        return build
+    c["generic_plain"] = generic(make(63, 3, 17, 33, 9, False, False))
+    c["generic_transposed"] = generic(make(64, 2, 40, 50, 30, True, True, xd=U8))
+    return c
 
 
 def pool_cases():

@@ -44,6 +44,18 @@ def test_cuda_matches_oracle(built, group, name, factory):
             assert st["max_abs"] <= tol and st["mismatch_frac"] <= 0.01, (group, name, st)
 
 
+def _golden_bmm():
+    from test_oracle_vs_cpuref import golden_bmm_cases
+    return list(golden_bmm_cases())
+
+
+@pytest.mark.parametrize("name,case,expected", _golden_bmm(), ids=[c[0] for c in _golden_bmm()])
+def test_batch_matmul_known_answers(built, name, case, expected):
+    """The BatchMatMul<QAsymmS8> vectors of the reference's own layer tests, on the tensor-core kernel."""
+    got = cases.run_case(case, "gpu")[0]
+    assert np.array_equal(got.astype(np.int64).ravel(), expected.ravel()), name
+
+
 def test_error_reporting_instead_of_aborting():
     """Bad arguments come back as negative codes with a message (never a crash)."""
     import ctypes

@@ -78,7 +78,40 @@ def _golden_cases():
     yield "qlstm_projection_layernorm", ql, np.array(g["output"]).reshape(B, O), g["tolerance"], 2
 
 
-GOLDEN_CASES = list(_golden_cases())
+def golden_bmm_cases():
+    """BatchMatMul<QAsymmS8> known answers (tests/golden/transcribe_batch_matmul.py): (name, case, expected)."""
+    for name, g in GOLDEN.items():
+        if not name.startswith("batch_matmul_"):
+            continue
+        xs, ys = g["x_shape"], g["y_shape"]
+        batch = int(np.prod(xs[:-2])) if len(xs) > 2 else 1
+        ybatch = int(np.prod(ys[:-2])) if len(ys) > 2 else 1
+        tx, ty = bool(g["transpose_x"]), bool(g["transpose_y"])
+        m, k = (xs[-1], xs[-2]) if tx else (xs[-2], xs[-1])
+        n = ys[-2] if ty else ys[-1]
+
+        def build(mem, g=g, xs=xs, ys=ys, batch=batch, ybatch=ybatch, tx=tx, ty=ty, m=m, k=k, n=n):
+            p = _abi.BmmParams()
+            p.x = qt(mem, np.array(g["x"], np.int8).reshape(xs), _abi.S8, g["scale"], g["zp"])
+            p.y = qt(mem, np.array(g["y"], np.int8).reshape(ys), _abi.S8, g["scale"], g["zp"])
+            p.out, out = qt_out(mem, (batch, m, n), _abi.S8, g["scale"], g["zp"])
+            p.batch, p.m, p.k, p.n = batch, m, k, n
+            p.transpose_x, p.transpose_y = int(tx), int(ty)
+            p.batch_stride_x = m * k
+            p.batch_stride_y = k * n if ybatch == batch else 0
+            return p, [out]
+        # the lists hold the tests' real values; armnnUtils::QuantizedVector<int8_t> saturates them (3DBatch expects 267 -> 127)
+        yield name, SimpleCase("batch_matmul_q8", build), np.clip(np.array(g["out"]), -128, 127)
+
+
+def _all_golden():
+    for c in _golden_cases():
+        yield c
+    for name, case, expected in golden_bmm_cases():
+        yield name, case, expected, GOLDEN[name]["tolerance"], 0
+
+
+GOLDEN_CASES = list(_all_golden())
 
 
 @pytest.mark.parametrize("name,case,expected,tol,out_index", GOLDEN_CASES, ids=[c[0] for c in GOLDEN_CASES])
