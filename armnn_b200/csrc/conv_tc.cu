@@ -33,7 +33,7 @@
 // (per-tensor asymmetric weights) is accumulated by the tensor core itself from constant B tiles holding -zw.
 //
 // Requantisation is the same function as in the CUDA-core kernel and the CPU oracle (IEEE fp32, unfused), evaluated
-// without the division unit and bit-identically (see epi_chunk).
+// without the division unit and bit-identically (see epi_chunk_fast and epi_fix_group).
 //
 // Every wait on an mbarrier is bounded; when a bound is hit the kernel raises a status word (read with
 // b200k_poll_status), drains and returns, so a logic error cannot hang the device.
@@ -92,7 +92,7 @@ __device__ __forceinline__ void tc_trace(int i)
 struct EpiConsts {
     float2 inv2, nsy2, magic2, zero2, neg2;      // RN(1 / sy), -sy, MAGIC, 0, -1
     float2 nmagic2;                              // -MAGIC
-    float2 zoff_lut2, zoff_sat2, zoff_clamp2;    // what is added to t = MAGIC + n (see epi_chunk), per way of ending
+    float2 zoff_lut2, zoff_sat2, zoff_clamp2;    // what is added to t = MAGIC + n (see epi_fix_group), per way of ending
     float lo, hi;                                // EPI_CLAMP: clamp bounds in the biased domain (MAGIC + ...)
 };
 
@@ -124,7 +124,7 @@ struct TcArgs {
     // fused ElementwiseBinary Add (res != null): y = Q2(deq(Q(conv)) + deq(res)), clamp in rq2
     const uint8_t* res; float res_scale; int res_zp; int res_u8;
     Requant rq2;
-    float inv_sy;                               // RN(1 / rq.sy), correctly rounded (see epi_chunk)
+    float inv_sy;                               // RN(1 / rq.sy), correctly rounded (see epi_fix_group)
     EpiConsts ep;                               // the hot path's constants
     const uint8_t* add_lut;                     // fused-add table built by b200k_conv2d_pack (+ its tag), or null
     uint32_t lut_tag[TC_LUT_TAG_WORDS];         // the tag a table made for exactly this launch carries
@@ -345,11 +345,6 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr)
 // with the 1.5 * 2^23 magic constant on the FP32 pipe, and the only conversion instructions left are the int32 -> fp32
 // of the accumulator and one saturating float -> byte conversion.
 constexpr float TC_MAGIC = 12582912.0f;          // 1.5 * 2^23: x + MAGIC - MAGIC == rint(x) for |x| < 2^22
-// |q - rint(q)| at or above this sends a chunk to the reference arithmetic: 0.5 = exact halves (and overflow) only
-#ifndef B200K_TC_FIX_THRESHOLD
-#define B200K_TC_FIX_THRESHOLD 0.5f
-#endif
-constexpr float TC_FIX_THRESHOLD = B200K_TC_FIX_THRESHOLD;
 
 // Reference arithmetic of one output value (unfused IEEE fp32), used by the rare fix-up pass:
 // v = fl(fl(acc * m) + b); q = clamp(zy + round_half_away(fl(v / sy))), then for a fused Add both operands are
@@ -415,93 +410,11 @@ __device__ __forceinline__ void lds_f2x2(uint32_t addr, float2& a, float2& b)   
     asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(a.x), "=f"(a.y), "=f"(b.x), "=f"(b.y) : "r"(addr));
 }
 
-// 16 accumulator columns of one output pixel -> 16 output bytes, branch-free.  EPI_LUT: look the result of the fused
-// Add up with the other operand's byte (16 bytes in rv).  The fp32 arithmetic runs two values per instruction
+// The reference chain of one output value is
+//     v = fl(fl(acc * m) + b);  q = fl(v / sy);  n = round_half_away(q);  out = clamp(zy + n)
+// with m = sx * sw, b = bias * sb per channel and acc the accumulator minus the zero-point correction cc (followed, for a
+// fused Add, by the re-quantisation that the table holds).  The fp32 arithmetic below runs two values per instruction
 // (__ffma2_rn and friends: one issue slot for two IEEE round-to-nearest operations).
-//
-// The reference chain is v = fl(fl(acc * m) + b); q = fl(v / sy); n = round_half_away(q); out = clamp(zy + n).
-// The division is evaluated exactly without the division unit: with y = RN(1 / sy) (prepared on the host), p = fl(v * y),
-// r = fma(-p, sy, v) (exact) and q = fma(r, y, p), q is the correctly rounded quotient (Markstein's theorem; it needs a
-// correctly rounded y and a normal-range quotient; for tiny or huge quotients the last bit does not matter, they round
-// to 0 or saturate).  t = q + MAGIC rounds to an integer, halves to even where the reference rounds them away from
-// zero: |q - n| = 0.5 exactly marks those values (and any value too large for the constant); the maximum of |q - n|
-// over the chunk is handed back in dmax, and the caller re-evaluates a flagged chunk with the plain reference
-// arithmetic (a few values per million).
-// Where a chunk's per-channel constants (m = sx * sw, b = bias * sb, cc = zero-point correction) come from.
-// TabShared: tables in shared memory, read with 128-bit loads that every lane of the warp repeats (all lanes work on
-// the same columns): 12 bytes per output and lane through the shared-memory pipe.
-struct TabShared {
-    uint32_t m, b, cc;                          // shared addresses at the chunk's first column
-    __device__ __forceinline__ void load(int g, float2& m01, float2& m23, float2& b01, float2& b23, int4& c) const
-    {
-        lds_f2x2(m + g * 16, m01, m23);
-        lds_f2x2(b + g * 16, b01, b23);
-        const uint4 cv = lds128(cc + g * 16);
-        c = make_int4((int)cv.x, (int)cv.y, (int)cv.z, (int)cv.w);
-    }
-};
-// TabParam: tables in the kernel's parameter space (constant bank).  The column index is the same for the whole warp,
-// so the loads are uniform loads and the values are uniform-register operands of the arithmetic: no shared-memory
-// traffic and no vector registers.
-struct TabParam {
-    const float* m; const float* b; const int* cc;   // at the chunk's first column
-    __device__ __forceinline__ void load(int g, float2& m01, float2& m23, float2& b01, float2& b23, int4& c) const
-    {
-        m01 = make_float2(m[g * 4 + 0], m[g * 4 + 1]); m23 = make_float2(m[g * 4 + 2], m[g * 4 + 3]);
-        b01 = make_float2(b[g * 4 + 0], b[g * 4 + 1]); b23 = make_float2(b[g * 4 + 2], b[g * 4 + 3]);
-        c = make_int4(cc[g * 4 + 0], cc[g * 4 + 1], cc[g * 4 + 2], cc[g * 4 + 3]);
-    }
-};
-
-template <int KIND, class Tab>
-__device__ __forceinline__ uint4 epi_chunk(const uint32_t* r, const uint4 rv, const Tab& ad, const EpiConsts& ec, const uint32_t lut, float& dmax)
-{
-    const float2 zoff2 = KIND == EPI_LUT ? ec.zoff_lut2 : (KIND == EPI_CLAMP ? ec.zoff_clamp2 : ec.zoff_sat2);
-    const uint32_t resw[4] = {rv.x, rv.y, rv.z, rv.w};
-    uint32_t packed[4];
-    #pragma unroll
-    for (int g = 0; g < 4; ++g) {                              // 4 columns at a time: 128-bit shared loads
-        float2 m01, m23, b01, b23;
-        int4 cv;
-        ad.load(g, m01, m23, b01, b23, cv);
-        const float2 a01 = make_float2(__int2float_rn((int)r[g * 4 + 0] - cv.x), __int2float_rn((int)r[g * 4 + 1] - cv.y));
-        const float2 a23 = make_float2(__int2float_rn((int)r[g * 4 + 2] - cv.z), __int2float_rn((int)r[g * 4 + 3] - cv.w));
-        // acc * m as an FMA with a zero addend: a packed multiply feeding a packed add must not be contracted into
-        // one FMA (a single rounding), which the reference does not do
-        const float2 v01 = __fadd2_rn(__ffma2_rn(a01, m01, ec.zero2), b01), v23 = __fadd2_rn(__ffma2_rn(a23, m23, ec.zero2), b23);
-        const float2 p01 = __ffma2_rn(v01, ec.inv2, ec.zero2), p23 = __ffma2_rn(v23, ec.inv2, ec.zero2);
-        const float2 q01 = __ffma2_rn(__ffma2_rn(p01, ec.nsy2, v01), ec.inv2, p01), q23 = __ffma2_rn(__ffma2_rn(p23, ec.nsy2, v23), ec.inv2, p23);
-        const float2 t01 = __fadd2_rn(q01, ec.magic2), t23 = __fadd2_rn(q23, ec.magic2);
-        const float2 n01 = __ffma2_rn(ec.magic2, ec.neg2, t01), n23 = __ffma2_rn(ec.magic2, ec.neg2, t23);   // rint(q) = t - MAGIC (exact)
-        const float2 d01 = __ffma2_rn(n01, ec.neg2, q01), d23 = __ffma2_rn(n23, ec.neg2, q23);       // q - n (exact)
-        dmax = fmaxf(fmaxf(dmax, fabsf(d01.x)), fabsf(d01.y));
-        dmax = fmaxf(fmaxf(dmax, fabsf(d23.x)), fabsf(d23.y));
-        // z = t - zoff (exact).  SAT / LUT: zoff = MAGIC - zero point (with the table: minus the type minimum as well), so
-        // z is the integer-valued result itself; CLAMP: zoff = -zero point, z stays in the biased domain
-        const float2 z01 = __fadd2_rn(t01, zoff2), z23 = __fadd2_rn(t23, zoff2);
-        const float z[4] = {z01.x, z01.y, z23.x, z23.y};
-        uint32_t bits[4];
-        if (KIND == EPI_CLAMP) {
-            // clamp in the biased domain: the low byte of the bit pattern is the output byte
-            #pragma unroll
-            for (int e = 0; e < 4; ++e) bits[e] = __float_as_uint(fminf(fmaxf(z[e], ec.lo), ec.hi));
-        } else {
-            // the clamp is the 8-bit type's own range: one saturating conversion replaces the two min / max
-            #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                if (KIND == EPI_SAT_S8) asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(bits[e]) : "f"(z[e]));
-                else                    asm("cvt.rni.sat.u8.f32 %0, %1;" : "=r"(bits[e]) : "f"(z[e]));
-                if (KIND == EPI_LUT) {
-                    // entry (conv output - type minimum) * pitch + other byte; lut holds the table's address, a
-                    // multiple of 256, and the other operand's byte goes into its low 8 bits
-                    bits[e] = lds_u8(bits[e] * (uint32_t)TC_LUT_PITCH + __byte_perm(resw[g], lut, 0x7650 + e));
-                }
-            }
-        }
-        packed[g] = __byte_perm(__byte_perm(bits[0], bits[1], 0x0040), __byte_perm(bits[2], bits[3], 0x0040), 0x5410);
-    }
-    return make_uint4(packed[0], packed[1], packed[2], packed[3]);
-}
 
 // ---- the hot path: one fused multiply-add per value, and a proof that its rounding is the reference's -----------
 //
@@ -573,10 +486,14 @@ __device__ __forceinline__ uint4 epi_chunk_fast(const uint32_t* r, const uint4 r
     return make_uint4(packed[0], packed[1], packed[2], packed[3]);
 }
 
-// Four values the hot path could not vouch for: the reference chain itself, division evaluated exactly by
-// Markstein's correction (see epi_chunk), rounded with the magic constant; only a value that is an exact half (which
-// the reference rounds away from zero) or beyond the constant goes on to the plain reference arithmetic.  Kept out of
-// line: it runs for a few per cent of the groups and would otherwise be inlined sixteen times into every tile loop.
+// Four values the hot path could not vouch for: the reference chain itself.  The division is evaluated exactly without
+// the division unit: with y = RN(1 / sy) (prepared on the host), p = fl(v * y), r = fma(-p, sy, v) (exact) and
+// q = fma(r, y, p), q is the correctly rounded quotient (Markstein's theorem; it needs a correctly rounded y and a
+// normal-range quotient; for tiny or huge quotients the last bit does not matter, they round to 0 or saturate).
+// t = q + MAGIC rounds to an integer, halves to even where the reference rounds them away from zero: |q - n| = 0.5
+// exactly marks those values (and any value too large for the constant), and only they go on to the plain reference
+// arithmetic (exact_value).  Kept out of line: it runs for a few per cent of the groups and would otherwise be inlined
+// sixteen times into every tile loop.
 template <int KIND>
 __device__ __noinline__ uint32_t epi_fix_group(int a0, int a1, int a2, int a3, uint32_t a_m, uint32_t a_b, uint32_t a_cc, uint32_t resw,
                                                const EpiConsts* ecp, uint32_t lut, const EpiExact* x)
@@ -1159,12 +1076,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         const TabFast ad = {a_mq + col0 * 4, a_bq + col0 * 4};
                         const uint4 rv = KIND == EPI_LUT ? lds128(res_row + ((((uint32_t)(part * NCH + j)) ^ sw_x) << 4)) : make_uint4(0, 0, 0, 0);
                         float dmg[4];
-#ifdef B200K_X_NOMATH
-                        dmg[0] = dmg[1] = dmg[2] = dmg[3] = 0.f;
-                        uint4 outv = make_uint4(r[j & 1][0] ^ r[j & 1][4] ^ rv.x, r[j & 1][1] ^ r[j & 1][5] ^ ad.mq, r[j & 1][2] ^ r[j & 1][6], r[j & 1][3] ^ r[j & 1][7]);
-#else
                         uint4 outv = epi_chunk_fast<KIND>(r[j & 1], rv, ad, a.ep, lut_addr, dmg);
-#endif
                         // groups the hot path cannot vouch for (|q" - n| within E of a half, a huge value, or no usable
                         // table at all: thr = 0) take the reference arithmetic, from the accumulators still in registers
                         if (__any_sync(0xffffffffu, fmaxf(fmaxf(dmg[0], dmg[1]), fmaxf(dmg[2], dmg[3])) >= thr)) {
@@ -1206,10 +1118,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     __syncwarp();
                     if (lane == 0) {
                         const int row0 = quad * 32;
-#ifndef B200K_X_NOSTORE
                         if (row0 < a.tile_rows && m0 + row0 < a.M)
                             tma_store_3d(&tmY, st_base, n0 + colw, a.im2col == 2 ? row0 : (int)(m0 + row0), a.im2col == 2 ? tm : 0);
-#endif
                         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                     }
                     st_base = st_base == st_base0 ? st_base0 + st_flip : st_base0;
@@ -1374,7 +1284,7 @@ __global__ void add_lut_kernel(const AddLutArgs a)
 static size_t add_lut_offset(int oc, int kh, int kw, int c)
 {
     size_t n = (size_t)(kh + 1) * (kw + 1) * oc * sizeof(int32_t);
-    if (c <= 16) n += (size_t)oc * kh * 128;
+    if (c <= 16) n += 2 * (size_t)oc * kh * 128;            // row-window weights, then the direct-stem weights
     return (n + 255) & ~(size_t)255;
 }
 
@@ -1522,9 +1432,11 @@ static bool row_window_eligible(const b200k_conv2d_params* p)
     return true;
 }
 
+static bool stem_direct_eligible(const b200k_conv2d_params* p);
+
 bool conv_tc_eligible(const b200k_conv2d_params* p)
 {
-    if (p->c <= 16) return row_window_eligible(p);
+    if (p->c <= 16) return stem_direct_eligible(p) || row_window_eligible(p);
     const void* outp = p->add_operand.data ? p->add_out.data : p->y.data;
     if (!p->x.data || !p->w.data || !outp) return false;
     if (!is_q8(p->x.dtype) || !is_q8(p->w.dtype) || !is_q8(p->y.dtype)) return false;
@@ -1626,8 +1538,476 @@ static int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUten
     return check_launch("conv_tc_kernel");
 }
 
+
+// ---- few-channel convolutions (network stems) straight from the NHWC input -----------------------------------------
+//
+// A 3-channel pixel is not a TMA unit, and im2col rows of a 7 x 7 x 3 window overlap almost entirely.  This kernel
+// keeps the rows themselves in shared memory and lets the tensor core read the overlapping windows where they lie:
+//   * a loader thread brings the raw input rows in with bulk copies, well ahead; expander warps rewrite each into a ring
+//     of "packed rows": the spatial
+//     padding materialised with the input zero point, every pixel padded to cpad = 16 / stride_w bytes, so that the
+//     window of output pixel ox starts exactly 16 * ox bytes into the row;
+//   * the A operand of filter row ky is a K-major, non-swizzled matrix descriptor over one packed row with a row pitch of
+//     16 bytes (8-row groups 128 bytes apart, K chunks 16 bytes apart): row ox of the matrix is bytes [16 ox, 16 ox + WB)
+//     of the packed row, i.e. the window, and consecutive rows overlap.  Nothing is copied per window.
+//   * the weights are re-packed at load time as [ky][OC / 8][WB / 16][8][16] (the same canonical layout) with zero in
+//     the padded channel lanes, and stay in shared memory for the whole launch;
+//   * a CTA walks a contiguous range of output rows (a tile is one output row), so every input row is expanded once per
+//     CTA and serves KH / stride_h tiles; accumulators are double-buffered in tensor memory and sixteen epilogue warps
+//     requantise them with the same code as the main kernel and store their bytes directly.
+// Padding taps hold the zero point, so sum (x - zx) w = sum x w - zx sum_all w: one correction per channel, no border
+// classes.  Symmetric weights only (zero point 0).  Every wait is bounded as in the main kernel.
+constexpr int ST_SLOTS = 32;                    // packed-row ring
+constexpr int ST_LOOKAHEAD = 4;                 // tiles the expanders may run ahead of the MMAs
+constexpr int ST_DONE = 8;                      // ring of per-tile "MMAs complete" barriers
+constexpr int ST_EXPANDERS = 4;
+constexpr int ST_RAW = 16;                      // ring of raw input rows (bulk copies in flight ahead of the expanders)
+constexpr int ST_THREADS = 32 * (2 + ST_EXPANDERS + TC_EPI_WARPS);     // MMA issuer, row loader, expanders, epilogue
+
+struct StemArgs {
+    const uint8_t* x; uint8_t* y; int32_t* acc_out;
+    const uint8_t* wpk; const int32_t* wsum;
+    const int32_t* bias; const float* w_scales; const float* b_scales;
+    float w_scale, b_scale;
+    int N, H, W, C, OH, OW, OC, KH, KW, sh, sw, pt, pl;
+    int cpad, WB, slot_bytes, raw_bytes, Hp, Wp, tiles, tmem_cols;
+    int zx, a_signed, b_signed, acc_big;
+    Requant rq;
+    float inv_sy;
+    EpiConsts ep;
+    long long wait_limit;
+};
+
+__device__ __forceinline__ uint64_t make_smem_desc_plain(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFF) >> 4);
+    d |= (uint64_t)(lbo_bytes >> 4) << 16;      // K chunk (16 bytes) to K chunk
+    d |= (uint64_t)(sbo_bytes >> 4) << 32;      // 8-row group to 8-row group
+    d |= (uint64_t)1 << 46;
+    return d;                                   // layout type 0: no swizzle
+}
+
+__global__ void __launch_bounds__(ST_THREADS, 1) conv_stem_kernel(const __grid_constant__ StemArgs a)
+{
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* s_rows = smem;                                            // [ST_SLOTS][slot_bytes]
+    uint8_t* s_w = s_rows + (size_t)ST_SLOTS * a.slot_bytes;           // [KH][OC * WB]
+    float* s_m = (float*)(s_w + (size_t)a.KH * a.OC * a.WB);
+    float* s_bterm = s_m + a.OC;
+    int32_t* s_cc = (int32_t*)(s_bterm + a.OC);
+    float* s_mq = (float*)(s_cc + a.OC);
+    float* s_bq = s_mq + a.OC;
+    uint32_t* s_emax = (uint32_t*)(s_bq + a.OC);                       // [2]
+    EpiExact* s_ex = (EpiExact*)(s_emax + 4);
+    uint64_t* row_full = (uint64_t*)(s_emax + 4 + 16);                 // [ST_SLOTS]
+    uint64_t* mma_done = row_full + ST_SLOTS;                          // [ST_DONE]
+    uint64_t* acc_full = mma_done + ST_DONE;                           // [2]
+    uint64_t* acc_empty = acc_full + 2;                                // [2]
+    uint64_t* w_full = acc_empty + 2;
+    uint64_t* raw_full = w_full + 1;                                   // [ST_RAW] a raw row has landed
+    uint64_t* raw_empty = raw_full + ST_RAW;                           // [ST_RAW] its expander has read it
+    uint32_t* tmem_slot = (uint32_t*)(raw_empty + ST_RAW);
+    uint8_t* s_raw = (uint8_t*)(((uintptr_t)(tmem_slot + 4) + 127) & ~(uintptr_t)127);   // [ST_RAW][raw_bytes]
+
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
+    // this CTA's contiguous range of tiles (output rows)
+    const int t_begin = (int)((long long)a.tiles * blockIdx.x / gridDim.x), t_end = (int)((long long)a.tiles * (blockIdx.x + 1) / gridDim.x);
+    const int ntiles = t_end - t_begin;
+    const long long v0 = (long long)(t_begin / a.OH) * a.Hp + (long long)(t_begin % a.OH) * a.sh;     // first virtual row
+    const long long wait_limit = a.wait_limit;
+
+    if (threadIdx.x < ST_SLOTS + ST_DONE + 5 + 2 * ST_RAW) {
+        const int i = threadIdx.x;
+        mbar_init(&row_full[i], (i >= ST_SLOTS + ST_DONE + 2 && i < ST_SLOTS + ST_DONE + 4) ? TC_EPI_WARPS : 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (threadIdx.x < 4) s_emax[threadIdx.x] = 0u;
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(a.tmem_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ===================== weights, then the MMAs =====================
+        if (elect_one()) {
+            const uint32_t wbytes = (uint32_t)(a.KH * a.OC * a.WB);
+            mbar_expect_tx(w_full, wbytes);
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                         ::"r"(smem_u32(s_w)), "l"(a.wpk), "r"(wbytes), "r"(smem_u32(w_full)) : "memory");
+        }
+        const uint32_t id = (2u << 4) | ((uint32_t)a.a_signed << 7) | ((uint32_t)a.b_signed << 10) |
+                            ((uint32_t)(a.OC >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+        bool alive = __all_sync(0xffffffffu, mbar_wait(w_full, 0, wait_limit));
+        if (!alive) atomicExch(&g_tc_status, 7);
+        const uint32_t rows_addr = smem_u32(s_rows), w_addr = smem_u32(s_w);
+        const uint32_t w_sbo = (uint32_t)(a.WB / 16) * 128u;
+        for (int i = 0; i < ntiles && alive; ++i) {
+            const int t = t_begin + i;
+            const long long lo = (long long)(t / a.OH) * a.Hp + (long long)(t % a.OH) * a.sh - v0;      // first packed row, relative
+            const int buf = i & 1;
+            for (int ky = 0; ky < a.KH && alive; ++ky) {
+                const long long rv = lo + ky;
+                if (!__all_sync(0xffffffffu, mbar_wait(&row_full[rv % ST_SLOTS], (uint32_t)(rv / ST_SLOTS) & 1u, wait_limit))) { atomicExch(&g_tc_status, 2); alive = false; }
+            }
+            if (alive && !__all_sync(0xffffffffu, mbar_wait(&acc_empty[buf], (((uint32_t)i >> 1) & 1u) ^ 1u, wait_limit))) { atomicExch(&g_tc_status, 4); alive = false; }
+            if (!alive) break;
+            tc_fence_after();
+            if (elect_one()) {
+                const uint32_t tacc = tmem_base + (uint32_t)(buf * a.OC);
+                for (int ky = 0; ky < a.KH; ++ky) {
+                    const long long rv = lo + ky;
+                    const uint64_t da = make_smem_desc_plain(rows_addr + (uint32_t)(rv % ST_SLOTS) * (uint32_t)a.slot_bytes, 16u, 128u);
+                    const uint64_t db = make_smem_desc_plain(w_addr + (uint32_t)(ky * a.OC * a.WB), 128u, w_sbo);
+                    for (int kk = 0; kk < a.WB / 32; ++kk)
+                        tc_mma_i8(tacc, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 16), id, (ky | kk) != 0 ? 1u : 0u);
+                }
+                tc_commit(&acc_full[buf]);
+                tc_commit(&mma_done[i % ST_DONE]);
+            }
+            __syncwarp();
+        }
+    } else if (warp == 1) {
+        // ===================== loader: raw input rows into the raw ring =====================
+        asm volatile("griddepcontrol.wait;" ::: "memory");                 // the input comes from the kernel before this one
+        if (lane == 0) {
+            long long next = 0, loaded = 0;
+            bool alive = true;
+            for (int i = 0; i < ntiles && alive; ++i) {
+                const int t = t_begin + i;
+                const int n = t / a.OH, oy = t % a.OH;
+                const long long lo = (long long)n * a.Hp + (long long)oy * a.sh - v0;
+                for (long long rv = lo > next ? lo : next; rv < lo + a.KH && alive; ++rv) {
+                    const int iy = (int)(rv - lo) + oy * a.sh - a.pt;
+                    if (iy < 0 || iy >= a.H) continue;                       // a padding row: nothing to load
+                    const int rs = (int)(loaded % ST_RAW);
+                    if (!mbar_wait(&raw_empty[rs], ((uint32_t)(loaded / ST_RAW) & 1u) ^ 1u, wait_limit)) { atomicExch(&g_tc_status, 1); alive = false; break; }
+                    const uint32_t bytes = (uint32_t)(a.W * a.C);
+                    mbar_expect_tx(&raw_full[rs], bytes);
+                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                                 ::"r"(smem_u32(s_raw + (size_t)rs * a.raw_bytes)), "l"(a.x + ((long long)n * a.H + iy) * bytes), "r"(bytes),
+                                   "r"(smem_u32(&raw_full[rs])) : "memory");
+                    ++loaded;
+                }
+                if (lo + a.KH > next) next = lo + a.KH;
+            }
+        }
+    } else if (warp <= 1 + ST_EXPANDERS) {
+        // ===================== expanders: raw rows -> packed rows =====================
+        const int e = warp - 2;
+        long long next = 0, loaded = 0;                                      // packed rows dealt out; raw rows consumed (all warps count alike)
+        bool alive = true;
+        const uint32_t zx4 = (uint32_t)(a.zx & 0xff) * 0x01010101u;
+        for (int i = 0; i < ntiles && alive; ++i) {
+            const int t = t_begin + i;
+            const int n = t / a.OH, oy = t % a.OH;
+            const long long lo = (long long)n * a.Hp + (long long)oy * a.sh - v0;
+            if (i >= ST_LOOKAHEAD) {
+                const int j = i - ST_LOOKAHEAD;
+                if (!mbar_wait(&mma_done[j % ST_DONE], (uint32_t)(j / ST_DONE) & 1u, wait_limit)) { atomicExch(&g_tc_status, 1); alive = false; break; }
+            }
+            for (long long rv = lo > next ? lo : next; rv < lo + a.KH && alive; ++rv) {
+                const int iy = (int)(rv - lo) + oy * a.sh - a.pt;
+                const bool inside_y = iy >= 0 && iy < a.H;
+                const long long my_raw = loaded;
+                if (inside_y) ++loaded;
+                if ((int)(rv % ST_EXPANDERS) != e) continue;
+                uint8_t* slot = s_rows + (size_t)(rv % ST_SLOTS) * a.slot_bytes;
+                const int rs = (int)(my_raw % ST_RAW);
+                const uint8_t* src = s_raw + (size_t)rs * a.raw_bytes;
+                if (inside_y && !mbar_wait(&raw_full[rs], (uint32_t)(my_raw / ST_RAW) & 1u, wait_limit)) { atomicExch(&g_tc_status, 2); alive = false; break; }
+                const uint32_t cmask = a.C >= 4 ? 0xffffffffu : (1u << (8 * a.C)) - 1u;
+                #pragma unroll 4
+                for (int px = lane; px < a.Wp; px += 32) {
+                    const int ix = px - a.pl;
+                    uint32_t w0 = zx4, w1 = zx4, w2 = zx4, w3 = zx4;
+                    if (inside_y && ix >= 0 && ix < a.W) {
+                        if (a.C <= 4) {
+                            // the pixel's bytes out of the two aligned words that hold them (the raw ring has slack behind every row)
+                            const int off = ix * a.C;
+                            const uint32_t* q32 = (const uint32_t*)(src + (off & ~3));
+                            w0 = __funnelshift_r(q32[0], q32[1], 8 * (off & 3)) & cmask;
+                            w1 = 0; w2 = 0; w3 = 0;
+                        } else {
+                            const uint8_t* q = src + ix * a.C;
+                            unsigned long long lo8 = 0, hi8 = 0;             // bytes 0..7 and 8..15 of the packed pixel
+                            for (int c = 0; c < a.C; ++c) {
+                                const unsigned long long b = q[c];
+                                if (c < 8) lo8 |= b << (8 * c); else hi8 |= b << (8 * (c - 8));
+                            }
+                            w0 = (uint32_t)lo8; w1 = (uint32_t)(lo8 >> 32); w2 = (uint32_t)hi8; w3 = (uint32_t)(hi8 >> 32);
+                        }
+                    }
+                    if (a.cpad == 8) *(uint2*)(slot + px * 8) = make_uint2(w0, w1);
+                    else             *(uint4*)(slot + px * 16) = make_uint4(w0, w1, w2, w3);
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic-proxy writes -> visible to the MMA's reads
+                __syncwarp();
+                if (lane == 0) {
+                    if (inside_y) mbar_arrive(&raw_empty[rs]);
+                    mbar_arrive(&row_full[rv % ST_SLOTS]);
+                }
+            }
+            if (lo + a.KH > next) next = lo + a.KH;
+        }
+    } else {
+        // ===================== epilogue =====================
+        const int ew = warp - (2 + ST_EXPANDERS);
+        const int quad = warp & 3, part = ew >> 2;
+        const int etid = threadIdx.x - 32 * (2 + ST_EXPANDERS);
+        const int nchunks = a.OC / 16;
+        const float lo1 = fmaxf(a.rq.tlo, (float)a.rq.clo), hi1 = fminf(a.rq.thi, (float)a.rq.chi), zy1 = (float)a.rq.zy;
+        const int kind = (lo1 == a.rq.tlo && hi1 == a.rq.thi) ? (a.rq.tlo == 0.f ? EPI_SAT_U8 : EPI_SAT_S8) : EPI_CLAMP;
+        if (etid == 0) {
+            EpiExact ex;
+            ex.sy1 = a.rq.sy; ex.zy1 = zy1; ex.lo1 = lo1; ex.hi1 = hi1;
+            ex.fused = 0; ex.res_u8 = 0; ex.zr = 0.f; ex.sr = 0.f; ex.sy2 = 1.f; ex.zy2 = 0.f; ex.lo2 = 0.f; ex.hi2 = 0.f; ex.always = 0;
+            *s_ex = ex;
+        }
+        // per-channel constants (one n-tile, one class)
+        {
+            float bq_max = 0.f, bsy_max = 0.f;
+            for (int j = etid; j < a.OC; j += 32 * TC_EPI_WARPS) {
+                const float m = __fmul_rn(a.rq.sx, a.w_scales ? a.w_scales[j] : a.w_scale);
+                const float b = a.bias ? __fmul_rn(__int2float_rn(a.bias[j]), a.b_scales ? a.b_scales[j] : a.b_scale) : 0.f;
+                const int cc = a.zx * a.wsum[j];
+                s_m[j] = m; s_bterm[j] = b; s_cc[j] = cc;
+                s_mq[j] = __fdiv_rn(m, a.rq.sy);
+                const float bq = epi_make_bq(b, cc, m, a.rq.sy, a.inv_sy, zy1);
+                s_bq[j] = bq;
+                bq_max = fmaxf(bq_max, fabsf(bq));
+                bsy_max = fmaxf(bsy_max, fabsf(__fmul_rn(b, a.inv_sy)));
+            }
+            const uint32_t w0 = __reduce_max_sync(0xffffffffu, __float_as_uint(bq_max <= 3.0e38f ? bq_max : 3.0e38f));
+            const uint32_t w1 = __reduce_max_sync(0xffffffffu, __float_as_uint(bsy_max <= 3.0e38f ? bsy_max : 3.0e38f));
+            if (lane == 0) { atomicMax(&s_emax[0], w0); atomicMax(&s_emax[1], w1); }
+        }
+        epi_barrier();
+        float thr;
+        {
+            const float rz = 257.0f;
+            const float rmax = fmaxf(fabsf(a.rq.tlo - 1.0f - zy1), fabsf(a.rq.thi + 1.0f - zy1));
+            const float big = a.acc_big ? 1.0f : 0.0f;
+            const float bsy = 1.0001f * __uint_as_float(s_emax[1]), bqm = __uint_as_float(s_emax[0]);
+            const float e = 1.1f * 5.9604645e-8f * ((3.0f + big) * rmax + (1.0f + big) * bsy + (1.0f + big) * (rz + bqm) + 2.0f * bqm + fabsf(zy1) + rz);
+            thr = !(e < 0.0625f) ? 0.0f : 0.5f - e;
+        }
+        const uint32_t a_m = smem_u32(s_m), a_b = smem_u32(s_bterm), a_cc = smem_u32(s_cc), a_mq = smem_u32(s_mq), a_bq = smem_u32(s_bq);
+        const int px = quad * 32 + lane;
+        const bool valid = px < a.OW;
+        bool dead = false;
+        // A warp's share of a tile is nchunks / 4 chunks of 16 columns (one, for 64 channels): too little to hide the
+        // tensor-memory load behind.  So the loads of the next (chunk, tile) are issued before the arithmetic of the
+        // current one, and an accumulator buffer is released as soon as the warp has its last chunk in registers.
+        auto run_tiles = [&](auto kind_tag) {
+            constexpr int KIND = decltype(kind_tag)::value;
+            const int cpw = part < nchunks ? (nchunks - part + 3) / 4 : 0;          // chunks per warp and tile
+            uint32_t r0[16], r1[16];
+            // chunk k of tile i (this warp's k-th: column chunk part + 4 k); the first chunk of a tile waits for its accumulator
+            auto issue = [&](int i, int k, uint32_t* dst) {
+                if (k == 0) {
+                    if (!dead && !mbar_wait(&acc_full[i & 1], ((uint32_t)i >> 1) & 1u, wait_limit)) { atomicExch(&g_tc_status, 3); dead = true; }
+                    tc_fence_after();
+                }
+                tc_ld16_issue(tmem_base + (uint32_t)((i & 1) * a.OC) + ((uint32_t)(quad * 32) << 16) + (uint32_t)((part + 4 * k) * 16), dst);
+            };
+            int i = 0, k = 0;                                 // the chunk whose load is in flight / being worked on
+            if (cpw > 0 && ntiles > 0) issue(0, 0, r0);
+            // (two register sets that take turns: the step is instantiated once for each, so both stay in registers)
+            auto step = [&](uint32_t* rc, uint32_t* rn) {
+                const int c = part + 4 * k;
+                const int t = t_begin + i;
+                tc_ld16_wait(rc);
+                int ni = i, nk = k + 1;
+                if (nk == cpw) {
+                    // the warp's last chunk of tile i is in registers
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&acc_empty[i & 1]);
+                    nk = 0; ni = i + 1;
+                }
+                if (ni < ntiles) issue(ni, nk, rn);
+                uint8_t* orow = a.y + ((long long)t * a.OW + px) * a.OC;
+                const TabFast ad = {a_mq + c * 64, a_bq + c * 64};
+                float dmg[4];
+                uint4 outv = epi_chunk_fast<KIND>(rc, make_uint4(0, 0, 0, 0), ad, a.ep, 0u, dmg);
+                if (__any_sync(0xffffffffu, fmaxf(fmaxf(dmg[0], dmg[1]), fmaxf(dmg[2], dmg[3])) >= thr)) {
+                    uint32_t w[4] = {outv.x, outv.y, outv.z, outv.w};
+                    #pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        if (__any_sync(0xffffffffu, dmg[g] >= thr))
+                            w[g] = epi_fix_group<KIND>((int)rc[g * 4], (int)rc[g * 4 + 1], (int)rc[g * 4 + 2], (int)rc[g * 4 + 3],
+                                                       a_m + (c * 16 + g * 4) * 4, a_b + (c * 16 + g * 4) * 4, a_cc + (c * 16 + g * 4) * 4, 0u,
+                                                       &a.ep, 0u, s_ex);
+                    }
+                    outv = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+                if (valid && !dead) {
+                    *(uint4*)(orow + c * 16) = outv;
+                    if (a.acc_out) {
+                        int32_t* arow = a.acc_out + ((long long)t * a.OW + px) * a.OC + c * 16;
+                        #pragma unroll
+                        for (int j = 0; j < 16; ++j) arow[j] = (int)rc[j] - lds_s32(a_cc + (c * 16 + j) * 4);
+                    }
+                }
+                i = ni; k = nk;
+            };
+            while (cpw > 0 && i < ntiles) {
+                step(r0, r1);
+                if (i < ntiles) step(r1, r0);
+            }
+            // warps without a chunk (fewer than four chunks per tile) still release every accumulator buffer
+            if (cpw == 0) {
+                for (int j = 0; j < ntiles; ++j) {
+                    if (!dead && !mbar_wait(&acc_full[j & 1], ((uint32_t)j >> 1) & 1u, wait_limit)) { atomicExch(&g_tc_status, 3); dead = true; }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&acc_empty[j & 1]);
+                }
+            }
+        };
+        switch (kind) {
+            case EPI_SAT_U8: run_tiles(std::integral_constant<int, EPI_SAT_U8>{}); break;
+            case EPI_SAT_S8: run_tiles(std::integral_constant<int, EPI_SAT_S8>{}); break;
+            default:         run_tiles(std::integral_constant<int, EPI_CLAMP>{}); break;
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(a.tmem_cols) : "memory");
+    }
+}
+
+struct StemPlan { bool ok; int cpad, WB, slot_bytes, raw_bytes, Wp, Hp; size_t wbytes, smem; int tmem_cols; };
+
+static StemPlan stem_plan(const b200k_conv2d_params* p)
+{
+    StemPlan r;
+    memset(&r, 0, sizeof(r));
+    if (p->c < 1 || p->c > 16 || p->dil_w != 1 || p->dil_h != 1 || p->ow > TC_BM || p->ow < 1) return r;
+    if (p->stride_w != 1 && p->stride_w != 2) return r;
+    if (p->stride_h < 1 || p->stride_h > 4 || p->kh < 1 || p->kh > 11 || p->kw < 1) return r;
+    if (p->oc % 16 != 0 || p->oc < 16 || p->oc > 256) return r;
+    r.cpad = 16 / p->stride_w;
+    if (p->c > r.cpad) return r;
+    r.WB = (p->kw * r.cpad + 31) & ~31;
+    if (r.WB > 128) return r;
+    r.slot_bytes = ((TC_BM - 1) * 16 + r.WB + 127) & ~127;
+    r.Wp = (p->ow - 1) * p->stride_w + p->kw;
+    if ((long long)r.Wp * r.cpad > r.slot_bytes) return r;
+    r.Hp = (p->oh - 1) * p->stride_h + p->kh;
+    r.wbytes = (size_t)p->kh * p->oc * r.WB;
+    if (r.wbytes > 64 * 1024) return r;
+    r.tmem_cols = 32;
+    while (r.tmem_cols < 2 * p->oc) r.tmem_cols <<= 1;
+    // raw rows arrive by bulk copies: whole rows of a multiple of 16 bytes
+    if (((long long)p->wd * p->c) % 16 != 0) return r;
+    r.raw_bytes = (p->wd * p->c + 8 + 127) & ~127;         // (+8: the expanders read whole words around a pixel)
+    r.smem = 1024 + (size_t)ST_SLOTS * r.slot_bytes + r.wbytes + (size_t)p->oc * 20 + 16 + 64 + (ST_SLOTS + ST_DONE + 5 + 2 * ST_RAW) * 8 + 16 +
+             128 + (size_t)ST_RAW * r.raw_bytes;
+    r.ok = r.smem <= 227 * 1024;
+    return r;
+}
+
+// wpk[ky][oc / 8][chunk][oc % 8][16]: byte b of chunk = window byte chunk * 16 + b = (kx, c) with kx = byte / cpad, c = byte % cpad
+struct StemWeightArgs { const uint8_t* w; uint8_t* wpk; int OC, KH, KW, C, cpad, WB; };
+__global__ void stem_weight_pack_kernel(const StemWeightArgs a)
+{
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= a.KH * a.OC * a.WB) return;
+    const int b = i & 15;
+    const int r8 = (i >> 4) & 7;
+    const int rest = i >> 7;
+    const int chunks = a.WB / 16;
+    const int chunk = rest % chunks;
+    const int og = (rest / chunks) % (a.OC / 8);
+    const int ky = rest / (chunks * (a.OC / 8));
+    const int oc = og * 8 + r8, wb = chunk * 16 + b;
+    const int kx = wb / a.cpad, c = wb - kx * a.cpad;
+    uint8_t v = 0;
+    if (kx < a.KW && c < a.C) v = a.w[(((long long)oc * a.KH + ky) * a.KW + kx) * a.C + c];
+    a.wpk[i] = v;
+}
+
+static size_t stem_wpack_offset(const b200k_conv2d_params* p)
+{
+    return (size_t)(p->kh + 1) * (p->kw + 1) * p->oc * sizeof(int32_t) + (size_t)p->oc * p->kh * 128;
+}
+
+static bool stem_direct_eligible(const b200k_conv2d_params* p)
+{
+    if (p->add_operand.data || p->selftest_us > 0 || !p->packed) return false;
+    if (!p->x.data || !p->w.data || !p->y.data) return false;
+    if (!is_q8(p->x.dtype) || !is_q8(p->w.dtype) || !is_q8(p->y.dtype)) return false;
+    if (!p->w.scales && p->w.zero_point != 0) return false;                   // symmetric weights only
+    if (p->bias.data && p->bias.dtype != B200K_S32) return false;
+    if (!quantisation_in_range(p)) return false;
+    if ((((uintptr_t)p->packed | (uintptr_t)p->y.data | (uintptr_t)p->x.data) & 15) != 0) return false;
+    if (p->acc_out && (((uintptr_t)p->acc_out) & 3) != 0) return false;
+    if ((long long)p->n * p->oh > (1ll << 30)) return false;
+    return stem_plan(p).ok;
+}
+
+static int launch_conv_stem(const b200k_conv2d_params* p, cudaStream_t stream)
+{
+    const StemPlan pl = stem_plan(p);
+    StemArgs a;
+    a.x = (const uint8_t*)p->x.data; a.y = (uint8_t*)p->y.data; a.acc_out = p->acc_out;
+    a.wpk = (const uint8_t*)p->packed + stem_wpack_offset(p);
+    a.wsum = (const int32_t*)p->packed + (long long)(p->kh * (p->kw + 1) + p->kw) * p->oc;       // prefix[(KH, KW)]: all taps
+    a.bias = (const int32_t*)p->bias.data; a.w_scales = p->w.scales; a.b_scales = p->bias.scales;
+    a.w_scale = p->w.scale; a.b_scale = p->bias.scale;
+    a.N = p->n; a.H = p->h; a.W = p->wd; a.C = p->c; a.OH = p->oh; a.OW = p->ow; a.OC = p->oc;
+    a.KH = p->kh; a.KW = p->kw; a.sh = p->stride_h; a.sw = p->stride_w; a.pt = p->pad_top; a.pl = p->pad_left;
+    a.cpad = pl.cpad; a.WB = pl.WB; a.slot_bytes = pl.slot_bytes; a.raw_bytes = pl.raw_bytes; a.Hp = pl.Hp; a.Wp = pl.Wp;
+    a.tiles = p->n * p->oh; a.tmem_cols = pl.tmem_cols;
+    a.zx = p->x.zero_point;
+    a.a_signed = p->x.dtype == B200K_S8; a.b_signed = p->w.dtype == B200K_S8;
+    {
+        const long long taps = (long long)p->kh * p->kw * p->c;
+        const long long xm = p->x.dtype == B200K_U8 ? 255 : 128, wm = p->w.dtype == B200K_U8 ? 255 : 128;
+        const long long azx = a.zx < 0 ? -a.zx : a.zx;
+        a.acc_big = taps * xm * wm + azx * taps * wm >= (1ll << 24) ? 1 : 0;
+    }
+    a.rq = make_requant(p->x.scale, p->y, p->clamp_lo, p->clamp_hi);
+    a.inv_sy = rn_reciprocal(p->y.scale);
+    {
+        auto two = [](float v) { return make_float2(v, v); };
+        const float lo1 = fmaxf(a.rq.tlo, (float)a.rq.clo), hi1 = fminf(a.rq.thi, (float)a.rq.chi), zy1 = (float)a.rq.zy;
+        a.ep.inv2 = two(a.inv_sy); a.ep.nsy2 = two(-a.rq.sy); a.ep.magic2 = two(TC_MAGIC); a.ep.zero2 = two(0.f); a.ep.neg2 = two(-1.f);
+        a.ep.nmagic2 = two(-TC_MAGIC);
+        a.ep.zoff_lut2 = two((zy1 - a.rq.tlo) - TC_MAGIC);
+        a.ep.zoff_sat2 = two(zy1 - TC_MAGIC);
+        a.ep.zoff_clamp2 = two(zy1);
+        a.ep.lo = TC_MAGIC + lo1;
+        a.ep.hi = TC_MAGIC + hi1;
+    }
+    a.wait_limit = TC_WAIT_LIMIT_CYCLES;
+    static std::atomic<bool> configured[TC_MAX_DEVICES];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= TC_MAX_DEVICES) dev = 0;
+    if (!configured[dev].load(std::memory_order_acquire)) {
+        B200K_CUDA(cudaFuncSetAttribute(conv_stem_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        configured[dev].store(true, std::memory_order_release);
+    }
+    const int sms = sm_count();
+    const int grid = a.tiles < sms ? a.tiles : sms;
+    launch_pdl(conv_stem_kernel, dim3((unsigned)grid), dim3(ST_THREADS), pl.smem, stream, a);
+    return check_launch("conv_stem_kernel");
+}
+
 int launch_conv_tc(const b200k_conv2d_params* p, cudaStream_t stream, int kvalid_c)
 {
+    // few-channel stems: straight from the NHWC input when the geometry allows it (no re-packed copy of the input)
+    if (p->c <= 16 && kvalid_c == 0 && stem_direct_eligible(p)) return launch_conv_stem(p, stream);
     B200K_REQUIRE(conv_tc_eligible(p), B200K_E_UNSUPPORTED, "conv2d_q8: not eligible for the tcgen05 kernel");
     B200K_REQUIRE(load_driver_entry_points(), B200K_E_CUDA, "conv2d_q8: cuTensorMapEncode* not available from the driver");
     TcArgs a;
@@ -1891,7 +2271,17 @@ int tc_pack(const b200k_conv2d_params* p, void* packed, cudaStream_t stream)
     wa.w = (const uint8_t*)p->w.data; wa.wp = (uint8_t*)packed + r.wpack_offset;
     wa.OC = p->oc; wa.KH = p->kh; wa.KW = p->kw; wa.C = p->c; wa.cpad = r.cpad; wa.swz = r.swz;
     row_weight_pack_kernel<<<div_up((long long)p->oc * p->kh * r.swz, 256), 256, 0, (cudaStream_t)stream>>>(wa);
-    return check_launch("row_weight_pack_kernel");
+    rc = check_launch("row_weight_pack_kernel");
+    if (rc) return rc;
+    const StemPlan sp = stem_plan(&q);
+    if (sp.cpad > 0 && sp.WB > 0 && sp.WB <= 128 && p->oc % 8 == 0) {
+        StemWeightArgs sa;
+        sa.w = (const uint8_t*)p->w.data; sa.wpk = (uint8_t*)packed + stem_wpack_offset(p);
+        sa.OC = p->oc; sa.KH = p->kh; sa.KW = p->kw; sa.C = p->c; sa.cpad = sp.cpad; sa.WB = sp.WB;
+        stem_weight_pack_kernel<<<div_up((long long)p->kh * p->oc * sp.WB, 256), 256, 0, (cudaStream_t)stream>>>(sa);
+        rc = check_launch("stem_weight_pack_kernel");
+    }
+    return rc;
 }
 
 // ---- int8 tensor-core ceiling ---------------------------------------------------------------------------------
