@@ -18,6 +18,7 @@ bool conv_tc_eligible(const b200k_conv2d_params* p);
 size_t tc_pack_bytes(int oc, int kh, int kw, int c);
 size_t tc_scratch_bytes(const b200k_conv2d_params* p);
 int tc_pack(const b200k_conv2d_params* p, void* packed, cudaStream_t stream);
+int tc_pack_host_tables(const b200k_conv2d_params* p, void* packed, cudaStream_t stream);
 
 static size_t up256(size_t v) { return (v + 255) & ~(size_t)255; }
 static int up16(int v) { return (v + 15) & ~15; }
@@ -188,11 +189,14 @@ extern "C" size_t b200k_conv2d_scratch_bytes(const b200k_conv2d_params* p)
     return 0;
 }
 
-extern "C" int b200k_conv2d_pack(const b200k_conv2d_params* p, void* packed, void* stream)
+namespace b200k {
+// host_tables: also read a fused-Add layer's per-channel constants back (a stream synchronisation: load time only)
+int conv2d_pack_impl(const b200k_conv2d_params* p, void* packed, cudaStream_t s, bool host_tables)
 {
     B200K_REQUIRE(p && packed, B200K_E_INVALID, "conv2d_pack: null argument");
-    cudaStream_t s = (cudaStream_t)stream;
     int rc = tc_pack(p, packed, s);
+    if (rc) return rc;
+    if (host_tables) rc = tc_pack_host_tables(p, packed, s);
     if (rc || !wants_padding(p->oc, p->c)) return rc;
     // zero-padded copies of the weights, the bias and the per-channel scales, and the tables of the padded problem
     const PadPlan pl = pad_plan(p);
@@ -212,4 +216,10 @@ extern "C" int b200k_conv2d_pack(const b200k_conv2d_params* p, void* packed, voi
     q.c = pl.cpad; q.oc = pl.ocpad;
     q.w.data = region + pl.w_off;
     return tc_pack(&q, region + pl.inner_off, s);
+}
+}  // namespace b200k
+
+extern "C" int b200k_conv2d_pack(const b200k_conv2d_params* p, void* packed, void* stream)
+{
+    return conv2d_pack_impl(p, packed, (cudaStream_t)stream, true);
 }

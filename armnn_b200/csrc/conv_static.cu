@@ -12,6 +12,7 @@
 
 namespace b200k {
 int conv2d_dispatch(const b200k_conv2d_params* p, cudaStream_t stream);
+int conv2d_pack_impl(const b200k_conv2d_params* p, void* packed, cudaStream_t s, bool host_tables);
 }
 
 using namespace b200k;
@@ -69,7 +70,8 @@ extern "C" int b200k_conv2d_q8_static(const b200k_conv2d_params* p, void* stream
     // region by the convolution's own re-pack), so nothing left over from an earlier call can leak into this one.
     // The pack kernels are ordinary launches: they have completed before the convolution's grid starts, which reads
     // the tables ahead of its programmatic-dependency wait (see tc_pack).
-    rc = b200k_conv2d_pack(&q, base, stream);
+    // (device-side tables only: nothing here may wait for the stream)
+    rc = conv2d_pack_impl(&q, base, (cudaStream_t)stream, false);
     if (rc) return rc;
     return conv2d_dispatch(&q, (cudaStream_t)stream);
 }

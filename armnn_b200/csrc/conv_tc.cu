@@ -43,6 +43,10 @@
 #include <string.h>
 #include <cudaTypedefs.h>
 #include <type_traits>
+#include <memory>
+#include <mutex>
+#include <unordered_map>
+#include <vector>
 #include "common.cuh"
 
 namespace b200k {
@@ -140,6 +144,7 @@ struct TcArgs {
     // map such a code back to its position in the list.
     int ncy, ncx, ncls;
     int acc_big;                                // |accumulator| or |accumulator - correction| can reach 2^24 (see epi_chunk_fast)
+    float thr_host;                             // parameter-space tables: 0.5 - E as the host computed it
     uint8_t ypair[16], xpair[16];
     uint8_t ycls[256], xcls[256];
     long long wait_limit;                       // clock64 ticks after which a device-side wait gives up
@@ -428,10 +433,34 @@ __device__ __forceinline__ void lds_f2x2(uint32_t addr, float2& a, float2& b)   
 // four values in which some lane sees |q" - n| >= 0.5 - E (about one group in twenty) is re-evaluated with the
 // reference arithmetic itself (epi_fix_group).  Values whose q" is huge lose the integer grid of the magic constant:
 // either they are flagged like the others or they saturate, as the reference's do.
-struct TabFast { uint32_t mq, bq; };            // shared addresses at the chunk's first column (bq: this lane's class row)
+// Where mq and bq come from.  TabFast: tables in shared memory, read with 128-bit loads that every lane of the warp
+// repeats (all lanes work on the same columns; bq: this lane's class row): four wavefronts of the shared-memory pipe per
+// four outputs and table.  TabFastP: tables in the kernel's parameter space (constant bank): the column index is the
+// same for the whole warp, so the loads are uniform loads that do not touch the shared-memory pipe at all, which is
+// what bounds the fused-Add epilogue (its table lookups live there too).  Only launches whose tables the host can
+// compute (see HostPack) and that have a single class of pixels take that form.
+struct TabFast {
+    uint32_t mq, bq;
+    __device__ __forceinline__ void load(int g, float2& m01, float2& m23, float2& b01, float2& b23) const
+    {
+        lds_f2x2(mq + g * 16, m01, m23);
+        lds_f2x2(bq + g * 16, b01, b23);
+    }
+};
+struct TabFastP {
+    const float* mq; const float* bq;
+    __device__ __forceinline__ void load(int g, float2& m01, float2& m23, float2& b01, float2& b23) const
+    {
+        m01 = make_float2(mq[g * 4 + 0], mq[g * 4 + 1]); m23 = make_float2(mq[g * 4 + 2], mq[g * 4 + 3]);
+        b01 = make_float2(bq[g * 4 + 0], bq[g * 4 + 1]); b23 = make_float2(bq[g * 4 + 2], bq[g * 4 + 3]);
+    }
+};
+constexpr int TC_PTAB_MAX = 2048;               // output channels whose tables fit the parameter space (16 KiB of the 32 KiB)
+struct TcTabs { float mq[TC_PTAB_MAX]; float bq[TC_PTAB_MAX]; };
+struct TcNoTabs { int unused; };
 
-template <int KIND>
-__device__ __forceinline__ uint4 epi_chunk_fast(const uint32_t* r, const uint4 rv, const TabFast& ad, const EpiConsts& ec, const uint32_t lut,
+template <int KIND, class Tab>
+__device__ __forceinline__ uint4 epi_chunk_fast(const uint32_t* r, const uint4 rv, const Tab& ad, const EpiConsts& ec, const uint32_t lut,
                                                 float* dmg)
 {
     const uint32_t resw[4] = {rv.x, rv.y, rv.z, rv.w};
@@ -439,8 +468,7 @@ __device__ __forceinline__ uint4 epi_chunk_fast(const uint32_t* r, const uint4 r
     #pragma unroll
     for (int g = 0; g < 4; ++g) {
         float2 m01, m23, b01, b23;
-        lds_f2x2(ad.mq + g * 16, m01, m23);
-        lds_f2x2(ad.bq + g * 16, b01, b23);
+        ad.load(g, m01, m23, b01, b23);
         const float2 a01 = make_float2(__int2float_rn((int)r[g * 4 + 0]), __int2float_rn((int)r[g * 4 + 1]));
         const float2 a23 = make_float2(__int2float_rn((int)r[g * 4 + 2]), __int2float_rn((int)r[g * 4 + 3]));
         const float2 q01 = __ffma2_rn(a01, m01, b01), q23 = __ffma2_rn(a23, m23, b23);
@@ -625,11 +653,11 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar)
 // rows beyond the tensor; before the buffer is written again that lane has waited for the store to have read it.  No
 // epilogue warp waits for another one.  With a fused Add the producer TMA-loads the other operand's unit into one of
 // two shared buffers; every epilogue warp releases it after reading its part.
-template <int BN, int SWZ, int EG>
+template <int BN, int SWZ, int EG, bool PTAB>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmY, const __grid_constant__ CUtensorMap tmR,
-               const __grid_constant__ TcArgs a)
+               const __grid_constant__ TcArgs a, const __grid_constant__ std::conditional_t<PTAB, TcTabs, TcNoTabs> tabs)
 {
     using L = TcSmem<BN, SWZ>;
     constexpr int MAX_STAGES = L::MAX_STAGES;
@@ -995,6 +1023,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                                     ((3.0f + big) * rmax + (1.0f + big) * bsy + (1.0f + big) * (rz + bqm) + 2.0f * bqm + fabsf(zoff) + rz);
                     // a bound this large means unusual scales: everything takes the reference arithmetic
                     thr = (always_fix || !(e < 0.0625f)) ? 0.0f : 0.5f - e;
+                    // (parameter-space tables come with the host's own bound)
+                    if (PTAB) thr = always_fix ? 0.0f : a.thr_host;
                 }
                 // the other slot: every thread has long finished reading it (it served the staging before this one)
                 if (etid == 0) { s_emax[2 * ((stagings + 1) & 1)] = 0u; s_emax[2 * ((stagings + 1) & 1) + 1] = 0u; }
@@ -1073,10 +1103,16 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                             if (j + 1 < NCH) tc_ld16_wait(r[1]);
                         }
                         const int col0 = colw + j * 16;
-                        const TabFast ad = {a_mq + col0 * 4, a_bq + col0 * 4};
                         const uint4 rv = KIND == EPI_LUT ? lds128(res_row + ((((uint32_t)(part * NCH + j)) ^ sw_x) << 4)) : make_uint4(0, 0, 0, 0);
                         float dmg[4];
-                        uint4 outv = epi_chunk_fast<KIND>(r[j & 1], rv, ad, a.ep, lut_addr, dmg);
+                        uint4 outv;
+                        if constexpr (PTAB) {
+                            const TabFastP ad = {tabs.mq + n0 + col0, tabs.bq + n0 + col0};
+                            outv = epi_chunk_fast<KIND>(r[j & 1], rv, ad, a.ep, lut_addr, dmg);
+                        } else {
+                            const TabFast ad = {a_mq + col0 * 4, a_bq + col0 * 4};
+                            outv = epi_chunk_fast<KIND>(r[j & 1], rv, ad, a.ep, lut_addr, dmg);
+                        }
                         // groups the hot path cannot vouch for (|q" - n| within E of a half, a huge value, or no usable
                         // table at all: thr = 0) take the reference arithmetic, from the accumulators still in registers
                         if (__any_sync(0xffffffffu, fmaxf(fmaxf(dmg[0], dmg[1]), fmaxf(dmg[2], dmg[3])) >= thr)) {
@@ -1468,10 +1504,13 @@ bool conv_tc_eligible(const b200k_conv2d_params* p)
 }
 
 
-template <int BN, int SWZ, int EG>
+template <int BN, int SWZ, int EG, bool PTAB = false>
 static int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmY, const CUtensorMap& tmR,
-                     const TcArgs& a, cudaStream_t stream)
+                     const TcArgs& a, cudaStream_t stream, const TcTabs* tabs = nullptr)
 {
+    if constexpr (EG == 1 && !PTAB) {
+        if (tabs) return launch_tc<BN, SWZ, EG, true>(tmA, tmB, tmY, tmR, a, stream, tabs);
+    }
     using L = TcSmem<BN, SWZ>;
     const size_t budget = 227 * 1024;                                   // opt-in shared memory per CTA on sm_100
     TcArgs a2 = a;
@@ -1509,7 +1548,7 @@ static int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUten
     a2.nprod = stages >= TC_PRODUCERS ? TC_PRODUCERS : (stages >= 2 ? 2 : 1);
     if (a2.bstat) a2.stage_tx = (uint32_t)(a.stage_tx - L::B_BYTES);
     const size_t smem = fixed + (size_t)stages * group * stride;
-    auto kern = conv_tc_kernel<BN, SWZ, EG>;
+    auto kern = conv_tc_kernel<BN, SWZ, EG, PTAB>;
     // per instantiation and device: the largest dynamic shared-memory size opted into so far (a racing second thread
     // at worst repeats the call)
     static std::atomic<size_t> configured[TC_MAX_DEVICES];
@@ -1534,7 +1573,12 @@ static int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUten
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    B200K_CUDA(cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmY, tmR, a2));
+    if constexpr (PTAB) {
+        B200K_CUDA(cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmY, tmR, a2, *tabs));
+    } else {
+        const TcNoTabs none = {0};
+        B200K_CUDA(cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmY, tmR, a2, none));
+    }
     return check_launch("conv_tc_kernel");
 }
 
@@ -2004,6 +2048,106 @@ static int launch_conv_stem(const b200k_conv2d_params* p, cudaStream_t stream)
     return check_launch("conv_stem_kernel");
 }
 
+
+// ---- host copies of a fused-Add convolution's per-channel constants ------------------------------------------------
+//
+// The fused-Add epilogue is bound by the shared-memory pipe (table lookups), so its mq / bq tables go through the
+// kernel's parameter space instead (TabFastP), which means the host has to know them.  b200k_conv2d_pack therefore
+// reads the per-channel weight sums, scales and bias of such a layer back once (a few KB, at load time) and keeps
+// them keyed by the packed buffer's address; a launch uses them when the buffer and the four device arrays are the
+// ones that were packed, and otherwise stages its tables on the device as every other launch does.
+struct HostPack {
+    const void* w; const void* w_scales; const void* bias; const void* b_scales;
+    int oc, kh, kw, c;
+    std::vector<float> ws, bs;
+    std::vector<int32_t> bias_v, wsum;
+};
+static std::mutex g_hp_mutex;
+static std::unordered_map<const void*, std::shared_ptr<HostPack>> g_hp;
+
+int tc_pack_host_tables(const b200k_conv2d_params* p, void* packed, cudaStream_t stream)
+{
+    {
+        std::lock_guard<std::mutex> lock(g_hp_mutex);
+        g_hp.erase(packed);
+    }
+    if (!p->add_operand.data || p->oc > TC_PTAB_MAX || p->oc % 16 != 0 || p->c <= 16) return B200K_OK;
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) { cudaGetLastError(); return B200K_OK; }
+    auto hp = std::make_shared<HostPack>();
+    hp->w = p->w.data; hp->w_scales = p->w.scales; hp->bias = p->bias.data; hp->b_scales = p->bias.scales;
+    hp->oc = p->oc; hp->kh = p->kh; hp->kw = p->kw; hp->c = p->c;
+    const size_t n = (size_t)p->oc;
+    hp->wsum.resize(n);
+    B200K_CUDA(cudaMemcpyAsync(hp->wsum.data(), (const int32_t*)packed + (size_t)(p->kh * (p->kw + 1) + p->kw) * n, n * 4, cudaMemcpyDeviceToHost, stream));
+    if (p->w.scales) { hp->ws.resize(n); B200K_CUDA(cudaMemcpyAsync(hp->ws.data(), p->w.scales, n * 4, cudaMemcpyDeviceToHost, stream)); }
+    if (p->bias.data) { hp->bias_v.resize(n); B200K_CUDA(cudaMemcpyAsync(hp->bias_v.data(), p->bias.data, n * 4, cudaMemcpyDeviceToHost, stream)); }
+    if (p->bias.data && p->bias.scales) { hp->bs.resize(n); B200K_CUDA(cudaMemcpyAsync(hp->bs.data(), p->bias.scales, n * 4, cudaMemcpyDeviceToHost, stream)); }
+    B200K_CUDA(cudaStreamSynchronize(stream));
+    std::lock_guard<std::mutex> lock(g_hp_mutex);
+    g_hp[packed] = hp;
+    return B200K_OK;
+}
+
+// epi_make_bq on the host (the same operations in the same order; fmaf is the IEEE fused multiply-add)
+static float host_make_bq(float b, int cc, float m, float sy, float inv_sy, float zoff)
+{
+    const float ch = (float)(cc & ~0xfff), cl = (float)(cc & 0xfff);
+    const float p1 = ch * m, e1 = fmaf(ch, m, -p1);
+    const float p2 = cl * m, e2 = fmaf(cl, m, -p2);
+    const float s1 = b - p1;
+    const float bb1 = s1 - b;
+    const float r1 = (b - (s1 - bb1)) + (-p1 - bb1);
+    const float s2 = s1 - p2;
+    const float bb2 = s2 - s1;
+    const float r2 = (s1 - (s2 - bb2)) + (-p2 - bb2);
+    const float tail = ((r1 + r2) - e1) - e2;
+    const float hi = s2 + tail;
+    const float bb3 = hi - s2;
+    const float lo = (s2 - (hi - bb3)) + (tail - bb3);
+    const float q0 = hi * inv_sy;
+    const float rem = fmaf(-q0, sy, hi) + lo;
+    const float q = fmaf(rem, inv_sy, q0);
+    return q + zoff;
+}
+
+// Fills the parameter-space tables of a fused-Add launch from the host copies; false: not available for this launch.
+static bool host_tables_for(const b200k_conv2d_params* p, const TcArgs& a, TcTabs* tabs, float* thr_out)
+{
+    if (!p->packed || a.ncls != 1 || a.im2col == 2 || p->oc > TC_PTAB_MAX) return false;
+    std::shared_ptr<HostPack> hp;
+    {
+        std::lock_guard<std::mutex> lock(g_hp_mutex);
+        auto it = g_hp.find(p->packed);
+        if (it == g_hp.end()) return false;
+        hp = it->second;
+    }
+    if (hp->w != p->w.data || hp->w_scales != p->w.scales || hp->bias != p->bias.data || hp->b_scales != p->bias.scales ||
+        hp->oc != p->oc || hp->kh != p->kh || hp->kw != p->kw || hp->c != p->c) return false;
+    const float sx = a.rq.sx, sy = a.rq.sy, inv_sy = a.inv_sy, zy1 = (float)a.rq.zy;
+    const float zoff = zy1 - a.rq.tlo;                       // the table's index: minus the type minimum
+    float bq_max = 0.f, bsy_max = 0.f;
+    for (int ch = 0; ch < p->oc; ++ch) {
+        const float m = sx * (p->w.scales ? hp->ws[ch] : p->w.scale);
+        const float b = p->bias.data ? (float)hp->bias_v[ch] * (p->bias.scales ? hp->bs[ch] : p->bias.scale) : 0.f;
+        const int cc = a.need_corr ? a.zx * hp->wsum[ch] - p->kh * p->kw * a.kvalid_c * a.zx * a.zw : 0;
+        tabs->mq[ch] = m / sy;
+        const float bq = host_make_bq(b, cc, m, sy, inv_sy, zoff);
+        tabs->bq[ch] = bq;
+        bq_max = fmaxf(bq_max, fabsf(bq));
+        bsy_max = fmaxf(bsy_max, fabsf(b * inv_sy));
+    }
+    for (int ch = p->oc; ch < TC_PTAB_MAX; ++ch) { tabs->mq[ch] = 0.f; tabs->bq[ch] = 0.f; }
+    if (!(bq_max <= 3.0e38f) || !(bsy_max <= 3.0e38f)) return false;
+    const float rz = 257.0f;
+    const float rmax = fmaxf(fabsf(a.rq.tlo - 1.0f - zy1), fabsf(a.rq.thi + 1.0f - zy1));
+    const float big = a.acc_big ? 1.0f : 0.0f;
+    const float bsy = 1.0001f * bsy_max;
+    const float e = 1.1f * 5.9604645e-8f * ((3.0f + big) * rmax + (1.0f + big) * bsy + (1.0f + big) * (rz + bq_max) + 2.0f * bq_max + fabsf(zoff) + rz);
+    *thr_out = !(e < 0.0625f) ? 0.0f : 0.5f - e;
+    return true;
+}
+
 int launch_conv_tc(const b200k_conv2d_params* p, cudaStream_t stream, int kvalid_c)
 {
     // few-channel stems: straight from the NHWC input when the geometry allows it (no re-packed copy of the input)
@@ -2197,16 +2341,21 @@ int launch_conv_tc(const b200k_conv2d_params* p, cudaStream_t stream, int kvalid
         }
     }
     const bool grouped = a.eg > 1;
+    // a fused Add whose per-channel constants the host knows: tables through the parameter space
+    TcTabs tabs_storage;
+    const TcTabs* host_tabs = nullptr;
+    a.thr_host = 0.f;
+    if (fa.res && a.eg == 1 && kvalid_c == 0 && host_tables_for(p, a, &tabs_storage, &a.thr_host)) host_tabs = &tabs_storage;
     if (swz == 128) {
-        if (bn == 256) return launch_tc<256, 128, 1>(tmA, tmB, tmY, tmR, a, stream);
-        if (bn == 128) return grouped ? launch_tc<128, 128, 2>(tmA, tmB, tmY, tmR, a, stream) : launch_tc<128, 128, 1>(tmA, tmB, tmY, tmR, a, stream);
+        if (bn == 256) return launch_tc<256, 128, 1>(tmA, tmB, tmY, tmR, a, stream, host_tabs);
+        if (bn == 128) return grouped ? launch_tc<128, 128, 2>(tmA, tmB, tmY, tmR, a, stream) : launch_tc<128, 128, 1>(tmA, tmB, tmY, tmR, a, stream, host_tabs);
         if (a.eg == 2) return launch_tc<64, 128, 2>(tmA, tmB, tmY, tmR, a, stream);
-        return grouped ? launch_tc<64, 128, 4>(tmA, tmB, tmY, tmR, a, stream) : launch_tc<64, 128, 1>(tmA, tmB, tmY, tmR, a, stream);
+        return grouped ? launch_tc<64, 128, 4>(tmA, tmB, tmY, tmR, a, stream) : launch_tc<64, 128, 1>(tmA, tmB, tmY, tmR, a, stream, host_tabs);
     }
-    if (bn == 256) return launch_tc<256, 64, 1>(tmA, tmB, tmY, tmR, a, stream);
-    if (bn == 128) return grouped ? launch_tc<128, 64, 2>(tmA, tmB, tmY, tmR, a, stream) : launch_tc<128, 64, 1>(tmA, tmB, tmY, tmR, a, stream);
+    if (bn == 256) return launch_tc<256, 64, 1>(tmA, tmB, tmY, tmR, a, stream, host_tabs);
+    if (bn == 128) return grouped ? launch_tc<128, 64, 2>(tmA, tmB, tmY, tmR, a, stream) : launch_tc<128, 64, 1>(tmA, tmB, tmY, tmR, a, stream, host_tabs);
     if (a.eg == 2) return launch_tc<64, 64, 2>(tmA, tmB, tmY, tmR, a, stream);
-    return grouped ? launch_tc<64, 64, 4>(tmA, tmB, tmY, tmR, a, stream) : launch_tc<64, 64, 1>(tmA, tmB, tmY, tmR, a, stream);
+    return grouped ? launch_tc<64, 64, 4>(tmA, tmB, tmY, tmR, a, stream) : launch_tc<64, 64, 1>(tmA, tmB, tmY, tmR, a, stream, host_tabs);
 }
 
 
@@ -2221,6 +2370,8 @@ size_t tc_pack_bytes(int oc, int kh, int kw, int c)
 size_t tc_scratch_bytes(const b200k_conv2d_params* p)
 {
     if (!p || p->c > 16) return 0;
+    // the direct stem kernel reads the input where it lies: no packed copy
+    if (!p->add_operand.data && (p->w.scales || p->w.zero_point == 0) && p->selftest_us == 0 && stem_plan(p).ok) return 0;
     const RowPlan r = row_window_plan(p);
     return r.ok ? r.scratch_bytes : 0;
 }

@@ -71,10 +71,10 @@ def test_static_scratch_entry_point_rebuilds_tables_between_different_layers(bui
 def test_static_scratch_entry_point_rejects_oversized_problems(built):
     from armnn_b200 import lib
     l = lib.load_library()
-    big = random_conv_case(304, 1, 8, 8, 3, 64, 3, 3)
+    # 24 channels run on zero-padded copies of the input and the output, which live in the scratch
+    big = random_conv_case(304, 1, 8, 8, 24, 24, 3, 3)
     mem = Cuda()
     p, _, _ = big.params(mem, False, 2)
-    p.n, p.h, p.wd, p.oh, p.ow = 4096, 224, 224, 111, 111          # geometry only: needs far more than 15 MiB
-    p.stride_h = p.stride_w = 2
+    p.n, p.h, p.wd, p.oh, p.ow = 4096, 224, 224, 222, 222          # geometry only: needs far more than 15 MiB
     assert l.b200k_conv2d_q8_static(C.byref(p), None) == _abi.E_TOOBIG
     assert b"exceeds" in l.b200k_last_error()
