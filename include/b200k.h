@@ -103,9 +103,10 @@ typedef struct {
      * Activation expressed through clamp_lo / clamp_hi, which then refer to add_out) would produce.
      * add_operand and add_out have the convolution's output shape (no broadcast). */
     b200k_qtensor add_operand, add_out;
-    /* Per-call device scratch (b200k_conv2d_scratch_bytes() bytes, 16-byte aligned) for convolutions with at most
-     * 16 input channels (network stems): the tcgen05 path re-packs the input there on every call.  NULL or too
-     * small: such convolutions run on the CUDA-core kernel. */
+    /* Per-call device scratch (b200k_conv2d_scratch_bytes() bytes, 16-byte aligned; 0 for most layers): zero-padded
+     * copies for channel counts that are multiples of 8 but not of 16, and the re-packed input of those few-channel
+     * stems that the direct stem kernel cannot take (asymmetric per-tensor weights, a fused Add, rows that are not a
+     * multiple of 16 bytes).  NULL or too small: such convolutions run on the CUDA-core kernel. */
     void* scratch;
     size_t scratch_bytes;
     /* Self-test of the bounded device-side waits of the tcgen05 kernel; 0 (the normal case) switches it off.  With
@@ -145,7 +146,8 @@ int b200k_conv2d_q8_static(const b200k_conv2d_params* p, void* stream);
  * RefFullyConnectedWorkload::Execute (RefFullyConnectedWorkload.cpp:16-67).
  *   x [m, k]   w [n, k] when transpose_w != 0 (m_TransposeWeightMatrix) else [k, n]
  *   bias [n] or NULL   y [m, n];  per-axis weight scales index n.
- * Same arithmetic and epilogue as b200k_conv2d_q8. */
+ * Same arithmetic and epilogue as b200k_conv2d_q8.  With at most 16 rows (and [n, k] weights, k a multiple of 64) the
+ * layer runs on a weight-streaming kernel instead of the convolution kernels when algo == 0. */
 typedef struct {
     b200k_qtensor x, w, bias, y;
     int32_t m, k, n;
