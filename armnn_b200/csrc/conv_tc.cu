@@ -77,7 +77,7 @@ __device__ int g_tc_status = 0;                 // 0 ok, otherwise the code of t
 
 // Phase time stamps of CTA 0 (nanoseconds, %globaltimer), compiled in only with -DB200K_TRACE, which the build never sets.
 #ifdef B200K_TRACE
-__device__ unsigned long long g_tc_trace[16];
+__device__ unsigned long long g_tc_trace[64];
 __device__ __forceinline__ void tc_trace(int i)
 {
     if (blockIdx.x == 0 && (threadIdx.x & 31) == 0) {
@@ -826,6 +826,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     turn = (turn + 1) & turn_mask;
                     if (++st == STAGES) { st = 0; ph ^= 1u; }
                 }
+                if (prod == 0 && (t - (int)blockIdx.x) / (int)gridDim.x < 8) TC_TRACE(16 + (t - (int)blockIdx.x) / (int)gridDim.x);
                 if (a.res && alive && !skip_loads && prod == 0) {
                     // the fused Add's other operand, one unit at a time, into the buffer the epilogue will overwrite
                     if (!have) locate();
@@ -899,6 +900,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 }
                 if (alive && elect_one()) tc_commit(&acc_full[buf]);  // accumulator of this tile complete
                 if (it == 0) TC_TRACE(4);
+                if (it < 8) TC_TRACE(24 + it);
             }
         }
     } else {
@@ -1050,8 +1052,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 const long long m0 = (long long)tm * a.tile_rows;
                 const int buf = it & ((1 << NACC_LOG2) - 1);
                 if (n0 != cur_n0) stage_constants(n0);
+                if (ew == 0 && it < 8) TC_TRACE(56 + it);
                 if (!dead && !mbar_wait(&acc_full[buf], ((uint32_t)it >> NACC_LOG2) & 1u, a.wait_limit)) { atomicExch(&g_tc_status, 3); dead = true; }
                 if (ew == 0 && t == blockIdx.x) TC_TRACE(7);
+                if (ew == 0 && it < 8) TC_TRACE(32 + it);
                 tc_fence_after();
                 const long long m = m0 + row;
                 const bool mvalid = row < a.tile_rows && m < a.M;
@@ -1173,10 +1177,12 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     }
                 }
                 // this warp has finished reading the accumulator buffer
+                if (ew == 0 && it < 8) TC_TRACE(48 + it);
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&acc_empty[buf]);
                 if (ew == 0 && t == blockIdx.x) TC_TRACE(8);
+                if (ew == 0 && it < 8) TC_TRACE(40 + it);
                 if (ew == 0) TC_TRACE(9);
             }
         };
@@ -2531,10 +2537,10 @@ extern "C" int b200k_int8_mma_peak(double* tops, void* stream_)
 }
 
 #ifdef B200K_TRACE
-extern "C" int b200k_tc_trace(unsigned long long* out16)
+extern "C" int b200k_tc_trace(unsigned long long* out64)
 {
     B200K_CUDA(cudaDeviceSynchronize());
-    B200K_CUDA(cudaMemcpyFromSymbol(out16, g_tc_trace, sizeof(unsigned long long) * 16));
+    B200K_CUDA(cudaMemcpyFromSymbol(out64, g_tc_trace, sizeof(unsigned long long) * 64));
     return B200K_OK;
 }
 #endif

@@ -251,7 +251,7 @@ def _layer_pass(torch, network, ln, info, passes):
     return best
 
 
-def _plugin_e2e(torch, net, info, local, steps, warmup, barrier, max_over_ranks, rank):
+def _plugin_e2e(torch, net, info, local, steps, warmup, barrier, max_over_ranks, rank, n_nets=2):
     """End to end through the Arm NN runtime + B200Acc plugin: two LoadedNetworks on this GPU, one host thread each,
     pre-imported pinned buffers; returns (seconds for `steps` requests, bytes in, bytes out, graph kernels per step)."""
     import numpy as np
@@ -259,7 +259,7 @@ def _plugin_e2e(torch, net, info, local, steps, warmup, barrier, max_over_ranks,
     rt = armnn_host.Runtime(device_id=local)
     nets, bufs = [], []
     rng = np.random.default_rng(2000 + rank)
-    for i in range(2):
+    for i in range(n_nets):
         n = armnn_host.ArmnnNetwork(net, "B200Acc", device_id=local, runtime=rt)
         x = torch.from_numpy(rng.integers(-128, 128, size=info["input_shape"]).astype(np.int8)).pin_memory()
         y = torch.empty(info["output_shape"], dtype=torch.int8).pin_memory()
@@ -275,14 +275,14 @@ def _plugin_e2e(torch, net, info, local, steps, warmup, barrier, max_over_ranks,
                 return
 
     def run(total):
-        counts = [total - total // 2, total // 2]
+        counts = [total // n_nets + (1 if i < total % n_nets else 0) for i in range(n_nets)]
         threads = [threading.Thread(target=work, args=(i, c)) for i, c in enumerate(counts) if c > 0]
         for t in threads:
             t.start()
         for t in threads:
             t.join()
 
-    run(max(2 * warmup, 8))                       # warm-up: weight packing, graph recording (two warm inferences + one)
+    run(max(n_nets * warmup, 4 * n_nets))         # warm-up: weight packing, graph recording (two warm inferences + one)
     g0 = armnn_host.graph_stats()
     barrier()
     t0 = time.perf_counter()
@@ -336,12 +336,12 @@ def run_b200(args):
     if args.api == "plugin" and armnn_host.available() and os.path.exists(armnn_host.PLUGIN_PATH):
         sampler.start()
         e2e_s, h2d, d2h, glaunches, gkernels = _plugin_e2e(torch, configs.resnet50(per_gpu, IMAGE)[0], info, local, args.steps,
-                                                           args.warmup, barrier, max_over_ranks, rank)
+                                                           args.warmup, barrier, max_over_ranks, rank, args.e2e_nets)
         sampler.pause()
         e2e = {"value": GLOBAL_BATCH * args.steps / e2e_s, "unit": "images/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                "ms_per_step": e2e_s / args.steps * 1e3,
                "api": "IRuntime::EnqueueWorkload on the B200Acc plugin inside the unmodified Arm NN runtime, pre-imported "
-                      "pinned host buffers, two LoadedNetworks / host threads per GPU",
+                      "pinned host buffers, %d LoadedNetworks / host threads per GPU" % args.e2e_nets,
                "graph_launches": glaunches, "graph_kernels": gkernels}
     else:
         # the Python mirror's pipelined requests (the Arm NN runtime library is not present on this machine)
@@ -542,6 +542,7 @@ def main():
     ap.add_argument("--api", default="plugin", choices=["plugin", "mirror"],
                     help="what the end-to-end number goes through: the Arm NN runtime + B200Acc plugin, or the Python mirror")
     ap.add_argument("--config", default="resnet50", choices=["resnet50", "single_conv", "fc_sweep", "mobilenet_v2", "qlstm"])
+    ap.add_argument("--e2e-nets", type=int, default=2, help="LoadedNetworks (one host thread each) per GPU in the end-to-end loop")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
