@@ -1047,8 +1047,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             uint32_t st_base = st_base0;
             for (int t = blockIdx.x; t < ntiles; t += gridDim.x, ++it) {
                 if ((it & (eg - 1)) != grp) continue;
-                const int n0 = (t % ntn) * BN;
-                const int tm = t / ntn;
+                // (a single n-tile is the common case of the epilogue-bound layers: no divisions then)
+                const int tm = ntn == 1 ? t : t / ntn;
+                const int n0 = ntn == 1 ? 0 : (t - tm * ntn) * BN;
                 const long long m0 = (long long)tm * a.tile_rows;
                 const int buf = it & ((1 << NACC_LOG2) - 1);
                 if (n0 != cur_n0) stage_constants(n0);

@@ -542,7 +542,7 @@ def main():
     ap.add_argument("--api", default="plugin", choices=["plugin", "mirror"],
                     help="what the end-to-end number goes through: the Arm NN runtime + B200Acc plugin, or the Python mirror")
     ap.add_argument("--config", default="resnet50", choices=["resnet50", "single_conv", "fc_sweep", "mobilenet_v2", "qlstm"])
-    ap.add_argument("--e2e-nets", type=int, default=2, help="LoadedNetworks (one host thread each) per GPU in the end-to-end loop")
+    ap.add_argument("--e2e-nets", type=int, default=4, help="LoadedNetworks (one host thread each) per GPU in the end-to-end loop")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
