@@ -1327,7 +1327,7 @@ __global__ void add_lut_kernel(const AddLutArgs a)
 static size_t add_lut_offset(int oc, int kh, int kw, int c)
 {
     size_t n = (size_t)(kh + 1) * (kw + 1) * oc * sizeof(int32_t);
-    if (c <= 16) n += 2 * (size_t)oc * kh * 128;            // row-window weights, then the direct-stem weights
+    if (c <= 16) n += 3 * (size_t)oc * kh * 128;            // row-window weights, then the direct-stem weights in both pixel widths
     return (n + 255) & ~(size_t)255;
 }
 
@@ -1608,9 +1608,9 @@ static int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUten
 //     requantise them with the same code as the main kernel and store their bytes directly.
 // Padding taps hold the zero point, so sum (x - zx) w = sum x w - zx sum_all w: one correction per channel, no border
 // classes.  Symmetric weights only (zero point 0).  Every wait is bounded as in the main kernel.
-constexpr int ST_SLOTS = 32;                    // packed-row ring
+constexpr int ST_SLOTS = 32;                    // packed-row ring (a power of two)
 constexpr int ST_LOOKAHEAD = 4;                 // tiles the expanders may run ahead of the MMAs
-constexpr int ST_DONE = 8;                      // ring of per-tile "MMAs complete" barriers
+constexpr int ST_DONE = 8;                      // ring of per-tile "MMAs complete" barriers (a power of two)
 constexpr int ST_EXPANDERS = 4;
 constexpr int ST_RAW = 16;                      // ring of raw input rows (bulk copies in flight ahead of the expanders)
 constexpr int ST_THREADS = 32 * (2 + ST_EXPANDERS + TC_EPI_WARPS);     // MMA issuer, row loader, expanders, epilogue
@@ -1622,6 +1622,7 @@ struct StemArgs {
     float w_scale, b_scale;
     int N, H, W, C, OH, OW, OC, KH, KW, sh, sw, pt, pl;
     int cpad, WB, slot_bytes, raw_bytes, Hp, Wp, tiles, tmem_cols;
+    int split;                                  // 4-byte pixels, even / odd output pixels as the two 64-row halves of a tile
     int zx, a_signed, b_signed, acc_big;
     Requant rq;
     float inv_sy;
@@ -1662,6 +1663,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv_stem_kernel(const __grid_c
     uint32_t* tmem_slot = (uint32_t*)(raw_empty + ST_RAW);
     uint8_t* s_raw = (uint8_t*)(((uintptr_t)(tmem_slot + 4) + 127) & ~(uintptr_t)127);   // [ST_RAW][raw_bytes]
 
+    if (threadIdx.x == 0) TC_TRACE(0);
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
     // this CTA's contiguous range of tiles (output rows)
@@ -1699,30 +1701,42 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv_stem_kernel(const __grid_c
         if (!alive) atomicExch(&g_tc_status, 7);
         const uint32_t rows_addr = smem_u32(s_rows), w_addr = smem_u32(s_w);
         const uint32_t w_sbo = (uint32_t)(a.WB / 16) * 128u;
+        // The issuing warp is one dependent chain per tile, and that chain is what the tile rate hangs on: relative row
+        // indices in 32 bits, only the rows no earlier tile has waited for are waited for, descriptors advance by adds.
+        const uint64_t da0 = make_smem_desc_plain(rows_addr, 16u, 128u);
+        const uint64_t db0 = make_smem_desc_plain(w_addr, 128u, w_sbo);
+        const uint64_t da_slot = (uint64_t)(a.slot_bytes >> 4), db_ky = (uint64_t)((a.OC * a.WB) >> 4);
+        const int kks = a.WB / 32;
+        int n = t_begin / a.OH, oy = t_begin - n * a.OH;
+        const int base_n = n, base_oy = oy;                 // (v0 = base_n * Hp + base_oy * sh)
+        int waited = 0;                                      // packed rows [0, waited) have been seen complete
         for (int i = 0; i < ntiles && alive; ++i) {
-            const int t = t_begin + i;
-            const long long lo = (long long)(t / a.OH) * a.Hp + (long long)(t % a.OH) * a.sh - v0;      // first packed row, relative
+            const int lo = (n - base_n) * a.Hp + (oy - base_oy) * a.sh;                              // first packed row, relative
             const int buf = i & 1;
-            for (int ky = 0; ky < a.KH && alive; ++ky) {
-                const long long rv = lo + ky;
-                if (!__all_sync(0xffffffffu, mbar_wait(&row_full[rv % ST_SLOTS], (uint32_t)(rv / ST_SLOTS) & 1u, wait_limit))) { atomicExch(&g_tc_status, 2); alive = false; }
+            for (int rv = lo > waited ? lo : waited; rv < lo + a.KH && alive; ++rv) {
+                if (!__all_sync(0xffffffffu, mbar_wait(&row_full[rv & (ST_SLOTS - 1)], (uint32_t)(rv / ST_SLOTS) & 1u, wait_limit))) { atomicExch(&g_tc_status, 2); alive = false; }
             }
+            waited = lo + a.KH;
+            if (i < 8) TC_TRACE(16 + i);
             if (alive && !__all_sync(0xffffffffu, mbar_wait(&acc_empty[buf], (((uint32_t)i >> 1) & 1u) ^ 1u, wait_limit))) { atomicExch(&g_tc_status, 4); alive = false; }
             if (!alive) break;
             tc_fence_after();
             if (elect_one()) {
                 const uint32_t tacc = tmem_base + (uint32_t)(buf * a.OC);
-                for (int ky = 0; ky < a.KH; ++ky) {
-                    const long long rv = lo + ky;
-                    const uint64_t da = make_smem_desc_plain(rows_addr + (uint32_t)(rv % ST_SLOTS) * (uint32_t)a.slot_bytes, 16u, 128u);
-                    const uint64_t db = make_smem_desc_plain(w_addr + (uint32_t)(ky * a.OC * a.WB), 128u, w_sbo);
-                    for (int kk = 0; kk < a.WB / 32; ++kk)
+                uint64_t db = db0;
+                int slot = lo & (ST_SLOTS - 1);
+                for (int ky = 0; ky < a.KH; ++ky, db += db_ky) {
+                    const uint64_t da = da0 + da_slot * (uint64_t)slot;
+                    for (int kk = 0; kk < kks; ++kk)
                         tc_mma_i8(tacc, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 16), id, (ky | kk) != 0 ? 1u : 0u);
+                    slot = (slot + 1) & (ST_SLOTS - 1);
                 }
                 tc_commit(&acc_full[buf]);
-                tc_commit(&mma_done[i % ST_DONE]);
+                tc_commit(&mma_done[i & (ST_DONE - 1)]);
             }
             __syncwarp();
+            if (i < 8) TC_TRACE(24 + i);
+            if (++oy == a.OH) { oy = 0; ++n; }
         }
     } else if (warp == 1) {
         // ===================== loader: raw input rows into the raw ring =====================
@@ -1747,6 +1761,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv_stem_kernel(const __grid_c
                     ++loaded;
                 }
                 if (lo + a.KH > next) next = lo + a.KH;
+                if (i < 8) TC_TRACE(56 + i);
             }
         }
     } else if (warp <= 1 + ST_EXPANDERS) {
@@ -1759,6 +1774,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv_stem_kernel(const __grid_c
             const int t = t_begin + i;
             const int n = t / a.OH, oy = t % a.OH;
             const long long lo = (long long)n * a.Hp + (long long)oy * a.sh - v0;
+            if (e == 0 && i == 1) TC_TRACE(12);
             if (i >= ST_LOOKAHEAD) {
                 const int j = i - ST_LOOKAHEAD;
                 if (!mbar_wait(&mma_done[j % ST_DONE], (uint32_t)(j / ST_DONE) & 1u, wait_limit)) { atomicExch(&g_tc_status, 1); alive = false; break; }
@@ -1772,20 +1788,51 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv_stem_kernel(const __grid_c
                 uint8_t* slot = s_rows + (size_t)(rv % ST_SLOTS) * a.slot_bytes;
                 const int rs = (int)(my_raw % ST_RAW);
                 const uint8_t* src = s_raw + (size_t)rs * a.raw_bytes;
+                if (e == 0 && rv == 8) TC_TRACE(8);
                 if (inside_y && !mbar_wait(&raw_full[rs], (uint32_t)(my_raw / ST_RAW) & 1u, wait_limit)) { atomicExch(&g_tc_status, 2); alive = false; break; }
+                if (e == 0 && rv == 8) TC_TRACE(9);
                 const uint32_t cmask = a.C >= 4 ? 0xffffffffu : (1u << (8 * a.C)) - 1u;
-                #pragma unroll 4
-                for (int px = lane; px < a.Wp; px += 32) {
-                    const int ix = px - a.pl;
-                    uint32_t w0 = zx4, w1 = zx4, w2 = zx4, w3 = zx4;
-                    if (inside_y && ix >= 0 && ix < a.W) {
-                        if (a.C <= 4) {
+                const uint32_t slot_addr = smem_u32(slot), src_addr = smem_u32(src);
+                if (a.C <= 4) {
+                    // All of the row's loads first, then all of its stores: through generic pointers the compiler has to
+                    // assume that a store may alias the next pixel's load, which serialises the row (1.8 us measured).
+                    constexpr int MAXP = 9;                                  // pixels per lane: Wp * cpad <= slot_bytes
+                    uint32_t pw[MAXP];
+                    #pragma unroll
+                    for (int k = 0; k < MAXP; ++k) {
+                        const int px = lane + 32 * k, ix = px - a.pl;
+                        uint32_t w0 = zx4;
+                        if (px < a.Wp && inside_y && ix >= 0 && ix < a.W) {
                             // the pixel's bytes out of the two aligned words that hold them (the raw ring has slack behind every row)
                             const int off = ix * a.C;
-                            const uint32_t* q32 = (const uint32_t*)(src + (off & ~3));
-                            w0 = __funnelshift_r(q32[0], q32[1], 8 * (off & 3)) & cmask;
-                            w1 = 0; w2 = 0; w3 = 0;
+                            const uint32_t qa = src_addr + (uint32_t)(off & ~3);
+                            uint32_t lo32, hi32;
+                            asm("ld.shared.b32 %0, [%1];" : "=r"(lo32) : "r"(qa));
+                            asm("ld.shared.b32 %0, [%1 + 4];" : "=r"(hi32) : "r"(qa));
+                            w0 = __funnelshift_r(lo32, hi32, 8 * (off & 3)) & cmask;
+                        }
+                        pw[k] = w0;
+                    }
+                    #pragma unroll
+                    for (int k = 0; k < MAXP; ++k) {
+                        const int px = lane + 32 * k, ix = px - a.pl;
+                        if (px >= a.Wp) continue;
+                        const bool real = inside_y && ix >= 0 && ix < a.W;
+                        const uint32_t fill = real ? 0u : zx4;               // the pixel's bytes beyond the first word
+                        if (a.cpad == 4) {
+                            asm volatile("st.shared.b32 [%0], %1;" ::"r"(slot_addr + (uint32_t)(px * 4)), "r"(pw[k]) : "memory");
+                            if (px >= 2) asm volatile("st.shared.b32 [%0], %1;" ::"r"(slot_addr + (uint32_t)(1024 + px * 4 - 8)), "r"(pw[k]) : "memory");   // the copy the odd pixels are read from
+                        } else if (a.cpad == 8) {
+                            asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(slot_addr + (uint32_t)(px * 8)), "r"(pw[k]), "r"(fill) : "memory");
                         } else {
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(slot_addr + (uint32_t)(px * 16)), "r"(pw[k]), "r"(fill), "r"(fill), "r"(fill) : "memory");
+                        }
+                    }
+                } else {
+                    for (int px = lane; px < a.Wp; px += 32) {
+                        const int ix = px - a.pl;
+                        uint32_t w0 = zx4, w1 = zx4, w2 = zx4, w3 = zx4;
+                        if (inside_y && ix >= 0 && ix < a.W) {
                             const uint8_t* q = src + ix * a.C;
                             unsigned long long lo8 = 0, hi8 = 0;             // bytes 0..7 and 8..15 of the packed pixel
                             for (int c = 0; c < a.C; ++c) {
@@ -1794,18 +1841,21 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv_stem_kernel(const __grid_c
                             }
                             w0 = (uint32_t)lo8; w1 = (uint32_t)(lo8 >> 32); w2 = (uint32_t)hi8; w3 = (uint32_t)(hi8 >> 32);
                         }
+                        if (a.cpad == 8) *(uint2*)(slot + px * 8) = make_uint2(w0, w1);
+                        else             *(uint4*)(slot + px * 16) = make_uint4(w0, w1, w2, w3);
                     }
-                    if (a.cpad == 8) *(uint2*)(slot + px * 8) = make_uint2(w0, w1);
-                    else             *(uint4*)(slot + px * 16) = make_uint4(w0, w1, w2, w3);
                 }
+                if (e == 0 && rv == 8) TC_TRACE(10);
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic-proxy writes -> visible to the MMA's reads
                 __syncwarp();
+                if (e == 0 && rv == 8) TC_TRACE(11);
                 if (lane == 0) {
                     if (inside_y) mbar_arrive(&raw_empty[rs]);
                     mbar_arrive(&row_full[rv % ST_SLOTS]);
                 }
             }
             if (lo + a.KH > next) next = lo + a.KH;
+            if (e == 0 && i < 8) TC_TRACE(48 + i);
         }
     } else {
         // ===================== epilogue =====================
@@ -1850,7 +1900,8 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv_stem_kernel(const __grid_c
             thr = !(e < 0.0625f) ? 0.0f : 0.5f - e;
         }
         const uint32_t a_m = smem_u32(s_m), a_b = smem_u32(s_bterm), a_cc = smem_u32(s_cc), a_mq = smem_u32(s_mq), a_bq = smem_u32(s_bq);
-        const int px = quad * 32 + lane;
+        const int trow = quad * 32 + lane;                  // row of the tile = lane of tensor memory
+        const int px = a.split ? (trow & 63) * 2 + (trow >> 6) : trow;
         const bool valid = px < a.OW;
         bool dead = false;
         // A warp's share of a tile is nchunks / 4 chunks of 16 columns (one, for 64 channels): too little to hide the
@@ -1875,6 +1926,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv_stem_kernel(const __grid_c
                 const int c = part + 4 * k;
                 const int t = t_begin + i;
                 tc_ld16_wait(rc);
+                if (ew == 0 && k == 0 && i < 8) TC_TRACE(32 + i);
                 int ni = i, nk = k + 1;
                 if (nk == cpw) {
                     // the warp's last chunk of tile i is in registers
@@ -1907,6 +1959,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv_stem_kernel(const __grid_c
                         for (int j = 0; j < 16; ++j) arow[j] = (int)rc[j] - lds_s32(a_cc + (c * 16 + j) * 4);
                     }
                 }
+                if (ew == 0 && nk == 0 && i < 8) TC_TRACE(40 + i);
                 i = ni; k = nk;
             };
             while (cpw > 0 && i < ntiles) {
@@ -1937,7 +1990,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) conv_stem_kernel(const __grid_c
     }
 }
 
-struct StemPlan { bool ok; int cpad, WB, slot_bytes, raw_bytes, Wp, Hp; size_t wbytes, smem; int tmem_cols; };
+struct StemPlan { bool ok; int cpad, WB, slot_bytes, raw_bytes, Wp, Hp, split; size_t wbytes, smem; int tmem_cols; };
 
 static StemPlan stem_plan(const b200k_conv2d_params* p)
 {
@@ -1948,6 +2001,12 @@ static StemPlan stem_plan(const b200k_conv2d_params* p)
     if (p->stride_h < 1 || p->stride_h > 4 || p->kh < 1 || p->kh > 11 || p->kw < 1) return r;
     if (p->oc % 16 != 0 || p->oc < 16 || p->oc > 256) return r;
     r.cpad = 16 / p->stride_w;
+    // Stride 2 with at most four channels: 4-byte pixels.  Windows of even output pixels then start 16 bytes apart, and
+    // so do those of odd ones, 8 bytes later: the even pixels are rows 0..63 of the tile, the odd ones rows 64..127, read
+    // from a second copy of the packed row that is shifted by 8 bytes and lies 1024 bytes (eight 8-row groups) behind the
+    // first.  A 7-pixel window is 28 bytes: one K = 32 MMA per filter row instead of two.
+    r.split = (p->stride_w == 2 && p->c <= 4 && p->ow <= 124 && ((p->ow - 1) * 2 + p->kw) * 4 <= 1024) ? 1 : 0;
+    if (r.split) r.cpad = 4;
     if (p->c > r.cpad) return r;
     r.WB = (p->kw * r.cpad + 31) & ~31;
     if (r.WB > 128) return r;
@@ -1988,9 +2047,11 @@ __global__ void stem_weight_pack_kernel(const StemWeightArgs a)
     a.wpk[i] = v;
 }
 
-static size_t stem_wpack_offset(const b200k_conv2d_params* p)
+// split: the 4-byte-pixel layout (packed next to the other one, so that the choice can be made per launch: it depends
+// on the output width, which is not a property of the weights)
+static size_t stem_wpack_offset(const b200k_conv2d_params* p, int split)
 {
-    return (size_t)(p->kh + 1) * (p->kw + 1) * p->oc * sizeof(int32_t) + (size_t)p->oc * p->kh * 128;
+    return (size_t)(p->kh + 1) * (p->kw + 1) * p->oc * sizeof(int32_t) + (size_t)p->oc * p->kh * 128 * (split ? 2 : 1);
 }
 
 static bool stem_direct_eligible(const b200k_conv2d_params* p)
@@ -2004,7 +2065,8 @@ static bool stem_direct_eligible(const b200k_conv2d_params* p)
     if ((((uintptr_t)p->packed | (uintptr_t)p->y.data | (uintptr_t)p->x.data) & 15) != 0) return false;
     if (p->acc_out && (((uintptr_t)p->acc_out) & 3) != 0) return false;
     if ((long long)p->n * p->oh > (1ll << 30)) return false;
-    return stem_plan(p).ok;
+    const StemPlan pl = stem_plan(p);
+    return pl.ok && (long long)p->n * pl.Hp < (1ll << 30);        // (relative packed-row indices are 32-bit)
 }
 
 static int launch_conv_stem(const b200k_conv2d_params* p, cudaStream_t stream)
@@ -2012,13 +2074,14 @@ static int launch_conv_stem(const b200k_conv2d_params* p, cudaStream_t stream)
     const StemPlan pl = stem_plan(p);
     StemArgs a;
     a.x = (const uint8_t*)p->x.data; a.y = (uint8_t*)p->y.data; a.acc_out = p->acc_out;
-    a.wpk = (const uint8_t*)p->packed + stem_wpack_offset(p);
+    a.wpk = (const uint8_t*)p->packed + stem_wpack_offset(p, pl.split);
     a.wsum = (const int32_t*)p->packed + (long long)(p->kh * (p->kw + 1) + p->kw) * p->oc;       // prefix[(KH, KW)]: all taps
     a.bias = (const int32_t*)p->bias.data; a.w_scales = p->w.scales; a.b_scales = p->bias.scales;
     a.w_scale = p->w.scale; a.b_scale = p->bias.scale;
     a.N = p->n; a.H = p->h; a.W = p->wd; a.C = p->c; a.OH = p->oh; a.OW = p->ow; a.OC = p->oc;
     a.KH = p->kh; a.KW = p->kw; a.sh = p->stride_h; a.sw = p->stride_w; a.pt = p->pad_top; a.pl = p->pad_left;
     a.cpad = pl.cpad; a.WB = pl.WB; a.slot_bytes = pl.slot_bytes; a.raw_bytes = pl.raw_bytes; a.Hp = pl.Hp; a.Wp = pl.Wp;
+    a.split = pl.split;
     a.tiles = p->n * p->oh; a.tmem_cols = pl.tmem_cols;
     a.zx = p->x.zero_point;
     a.a_signed = p->x.dtype == B200K_S8; a.b_signed = p->w.dtype == B200K_S8;
@@ -2431,13 +2494,19 @@ int tc_pack(const b200k_conv2d_params* p, void* packed, cudaStream_t stream)
     row_weight_pack_kernel<<<div_up((long long)p->oc * p->kh * r.swz, 256), 256, 0, (cudaStream_t)stream>>>(wa);
     rc = check_launch("row_weight_pack_kernel");
     if (rc) return rc;
-    const StemPlan sp = stem_plan(&q);
-    if (sp.cpad > 0 && sp.WB > 0 && sp.WB <= 128 && p->oc % 8 == 0) {
-        StemWeightArgs sa;
-        sa.w = (const uint8_t*)p->w.data; sa.wpk = (uint8_t*)packed + stem_wpack_offset(p);
-        sa.OC = p->oc; sa.KH = p->kh; sa.KW = p->kw; sa.C = p->c; sa.cpad = sp.cpad; sa.WB = sp.WB;
-        stem_weight_pack_kernel<<<div_up((long long)p->kh * p->oc * sp.WB, 256), 256, 0, (cudaStream_t)stream>>>(sa);
-        rc = check_launch("stem_weight_pack_kernel");
+    // the direct stem kernel's weights: pixels of 16 / stride_w bytes and, for stride 2 with at most four channels, of 4
+    if (p->oc % 8 == 0 && (q.stride_w == 1 || q.stride_w == 2)) {
+        for (int split = 0; split < 2 && rc == B200K_OK; ++split) {
+            const int cpad = split ? 4 : 16 / q.stride_w;
+            if (split && !(q.stride_w == 2 && p->c <= 4)) break;
+            const int WB = (p->kw * cpad + 31) & ~31;
+            if (p->c > cpad || WB > 128) continue;
+            StemWeightArgs sa;
+            sa.w = (const uint8_t*)p->w.data; sa.wpk = (uint8_t*)packed + stem_wpack_offset(p, split);
+            sa.OC = p->oc; sa.KH = p->kh; sa.KW = p->kw; sa.C = p->c; sa.cpad = cpad; sa.WB = WB;
+            stem_weight_pack_kernel<<<div_up((long long)p->kh * p->oc * WB, 256), 256, 0, (cudaStream_t)stream>>>(sa);
+            rc = check_launch("stem_weight_pack_kernel");
+        }
     }
     return rc;
 }
