@@ -80,9 +80,9 @@ class Runtime:
 
 
 def graph_stats():
-    """(CUDA-graph launches, kernel nodes in them) of the B200Acc plugin in this process so far."""
-    Runtime.default()
-    plugin = C.CDLL(PLUGIN_PATH)                  # already loaded by the runtime: same handle
+    """(CUDA-graph launches, kernel nodes in them) of the B200Acc plugin in this process so far.  Creates no runtime:
+    a second IRuntime would replace the process-wide default device of the first."""
+    plugin = C.CDLL(PLUGIN_PATH)                  # the handle the runtime already holds, if one was created
     a, b = C.c_uint64(0), C.c_uint64(0)
     plugin.B200AccGraphStats(C.byref(a), C.byref(b))
     return a.value, b.value

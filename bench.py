@@ -195,12 +195,12 @@ def _dist():
     def barrier():
         if world > 1:
             dist.barrier()
-        torch.cuda.synchronize()
+        torch.cuda.synchronize(local)
 
     def max_over_ranks(seconds):
         if world == 1:
             return seconds
-        t = torch.tensor([seconds], dtype=torch.float64, device="cuda")
+        t = torch.tensor([seconds], dtype=torch.float64, device=torch.device("cuda", local))
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
@@ -287,7 +287,7 @@ def _plugin_e2e(torch, net, info, local, steps, warmup, barrier, max_over_ranks,
     barrier()
     t0 = time.perf_counter()
     run(steps)
-    torch.cuda.synchronize()
+    torch.cuda.synchronize(local)
     seconds = max_over_ranks(time.perf_counter() - t0)
     barrier()
     g1 = armnn_host.graph_stats()
