@@ -331,6 +331,26 @@ def run_b200(args):
     del ln, rt
     torch.cuda.empty_cache()
 
+    # ---- the same graph at 256 images per GPU (N > 1): separates the per-GPU batch effect from the number of GPUs ----
+    weak = None
+    if world > 1:
+        wnet, winfo = configs.resnet50(GLOBAL_BATCH, IMAGE)
+        wrt = network.IRuntime.Create(local)
+        wln = wrt.GetLoadedNetwork(wrt.LoadNetwork(network.Optimize(wnet, ["B200Acc"])))
+        wln.input_tensor(0).copy_(torch.from_numpy(rng.integers(-128, 128, size=winfo["input_shape"]).astype(np.int8)).cuda())
+        wln.Execute()
+        torch.cuda.synchronize(local)
+        wln.CaptureGraph()
+        for _ in range(args.warmup):
+            wln.Execute()
+        wregions, _ = _timed_regions(torch, wln, args.steps, max(3, args.repeats // 2), barrier, max_over_ranks)
+        wsec = statistics.median(wregions)
+        weak = {"value": GLOBAL_BATCH * world * args.steps / wsec, "unit": "images/s", "per_gpu_batch": GLOBAL_BATCH,
+                "global_batch": GLOBAL_BATCH * world, "ms_per_step": wsec / args.steps * 1e3,
+                "note": "device-resident like `value`, every GPU at the N = 1 batch"}
+        del wln, wrt
+        torch.cuda.empty_cache()
+
     # ---- end to end with host buffers ----
     e2e = None
     if args.api == "plugin" and armnn_host.available() and os.path.exists(armnn_host.PLUGIN_PATH):
@@ -409,7 +429,7 @@ def run_b200(args):
             "steps": args.steps, "warmup": args.warmup, "repeats": args.repeats, "ms_per_step": step_ms,
             "ms_per_step_regions": [round(r / args.steps * 1e3, 4) for r in regions], "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "int8 (int32 accumulate, fp32 requantise)", "data": "synthetic",
-            "config": _config(world), "e2e": e2e, "gpu_launches": launches,
+            "config": _config(world), "e2e": e2e, "weak_scaling": weak, "gpu_launches": launches,
             "clocks": sampler.summary(), "roofline": roofline,
             "kernel_families": {k: {"ms_per_step": v["ms"], "launches_per_step": v["launches"], "share": v["ms"] / total_ms,
                                     "gb_per_s": v["bytes"] / (v["ms"] / 1e3) / 1e9} for k, v in fam.items()},
