@@ -568,30 +568,6 @@ __device__ __noinline__ uint32_t epi_fix_group(int a0, int a1, int a2, int a3, u
     return out;
 }
 
-// bq of one (class, column) to within one rounding of its last operation: X = (b - cc m) / sy from error-free
-// products and sums (cc split into two exactly representable parts), one correction step on the quotient, + zoff.
-__device__ __forceinline__ float epi_make_bq(float b, int cc, float m, float sy, float inv_sy, float zoff)
-{
-    const float ch = __int2float_rn(cc & ~0xfff), cl = __int2float_rn(cc & 0xfff);   // both exact
-    const float p1 = __fmul_rn(ch, m), e1 = __fmaf_rn(ch, m, -p1);                   // ch m = p1 + e1
-    const float p2 = __fmul_rn(cl, m), e2 = __fmaf_rn(cl, m, -p2);
-    // s1 + r1 = b - p1, s2 + r2 = s1 - p2 (two-sum)
-    const float s1 = __fsub_rn(b, p1);
-    const float bb1 = __fsub_rn(s1, b);
-    const float r1 = __fadd_rn(__fsub_rn(b, __fsub_rn(s1, bb1)), __fsub_rn(-p1, bb1));
-    const float s2 = __fsub_rn(s1, p2);
-    const float bb2 = __fsub_rn(s2, s1);
-    const float r2 = __fadd_rn(__fsub_rn(s1, __fsub_rn(s2, bb2)), __fsub_rn(-p2, bb2));
-    const float tail = __fsub_rn(__fsub_rn(__fadd_rn(r1, r2), e1), e2);
-    const float hi = __fadd_rn(s2, tail);
-    const float bb3 = __fsub_rn(hi, s2);
-    const float lo = __fadd_rn(__fsub_rn(s2, __fsub_rn(hi, bb3)), __fsub_rn(tail, bb3));
-    const float q0 = __fmul_rn(hi, inv_sy);
-    const float rem = __fadd_rn(__fmaf_rn(-q0, sy, hi), lo);
-    const float q = __fmaf_rn(rem, inv_sy, q0);
-    return __fadd_rn(q, zoff);
-}
-
 // The cold pass of one chunk (rare, or the accumulator dump of the tests): from the 16 accumulators still in
 // registers, (fix) evaluate them with the reference arithmetic (other operand's bytes at res_slot, result to out_slot)
 // and / or (acc_row) write the raw accumulators of a valid row out for the bit-exactness tests.

@@ -49,6 +49,26 @@ def dwconv_cases():
     c["odd_c7"] = lambda: random_conv_case(24, 1, 7, 7, 7, None, 3, 3, pad=(1, 1, 1, 1), depthwise=True)
     c["multiplier2"] = lambda: random_conv_case(25, 1, 6, 6, 8, None, 3, 3, pad=(1, 1, 1, 1), depthwise=True, depth_multiplier=2)
     c["5x5_dilation2"] = lambda: random_conv_case(26, 1, 12, 12, 16, None, 5, 5, pad=(4, 4, 4, 4), dil=(2, 2), depthwise=True)
+    # the row-sliding 3x3 kernel (signed symmetric weights): eight, four, two and one output rows per thread, ragged
+    # right and bottom edges, both strides, the three ways its requantisation ends, both input signednesses
+    c["rows8_s1_c32_relu6"] = lambda: random_conv_case(27, 32, 111, 113, 32, None, 3, 3, pad=(1, 1, 1, 1), depthwise=True,
+                                                       act=(2, 6.0, 0.0), x_q=(0.05, -7))
+    c["rows4_s2_c64"] = lambda: random_conv_case(28, 32, 113, 111, 64, None, 3, 3, stride=(2, 2), pad=(0, 1, 0, 1), depthwise=True,
+                                                 x_q=(0.02, 5))
+    c["rows2_s1_u8_activations"] = lambda: random_conv_case(29, 16, 56, 56, 64, None, 3, 3, pad=(1, 1, 1, 1), depthwise=True,
+                                                            x_dtype=U8, y_dtype=U8, x_q=(0.02, 131))
+    c["rows1_s2_c96_relu"] = lambda: random_conv_case(30, 1, 15, 15, 96, None, 3, 3, stride=(2, 2), pad=(1, 1, 1, 1), depthwise=True,
+                                                      act=(1, 0., 0.), per_axis=False)
+    c["rows1_s1_c8_no_bias"] = lambda: random_conv_case(31, 3, 5, 6, 8, None, 3, 3, pad=(1, 1, 1, 1), depthwise=True, bias=False)
+    c["rows_s2_u8_activations_pad0"] = lambda: random_conv_case(32, 2, 17, 19, 24, None, 3, 3, stride=(2, 2), depthwise=True,
+                                                                x_dtype=U8, y_dtype=U8, x_q=(0.03, 128), act=(2, 6.0, 0.0))
+    c["rows4_s1_u8_everything"] = lambda: random_conv_case(33, 32, 56, 56, 64, None, 3, 3, pad=(1, 1, 1, 1), depthwise=True,
+                                                           act=(2, 6.0, 0.0), x_dtype=U8, w_dtype=U8, y_dtype=U8, per_axis=False,
+                                                           x_q=(0.02, 117), y_zp=0, y_scale=0.03)
+    c["rows2_s2_u8_everything"] = lambda: random_conv_case(34, 16, 57, 55, 96, None, 3, 3, stride=(2, 2), pad=(0, 1, 0, 1), depthwise=True,
+                                                           x_dtype=U8, w_dtype=U8, y_dtype=U8, per_axis=False, x_q=(0.02, 3))
+    c["rows1_s1_s8_weight_zero_point"] = lambda: random_conv_case(35, 2, 9, 10, 12, None, 3, 3, pad=(1, 1, 1, 1), depthwise=True,
+                                                                  per_axis=False, w_zp=-9)
     return c
 
 
