@@ -145,14 +145,116 @@ static int launch_padded(const b200k_conv2d_params* p, const PadPlan& pl, const 
     return rc;
 }
 
+// ---- 1x1 convolutions whose channel counts the tensor-core kernel cannot take as they are ---------------------------
+//
+// A 1x1, stride-1 convolution is the GEMM [M, C] x [C, OC].  Taking g consecutive pixels as one row turns it into
+// [M / g, g C] x [g C, g OC] with a block-diagonal weight matrix (g copies of the weights; every other entry the weight
+// zero point, i.e. a real zero), on the very same input and output bytes: no copy of either tensor.  g is the smallest
+// power of two that makes g C and g OC multiples of 16 (and g C at least 32: the few-channel kernels are built for
+// stems with wide filters, not for this).  The g-fold redundant multiplications are free on a layer that is bound by
+// its memory traffic.  Needs M % g == 0; the channel-padded path below takes what is left.
+struct GroupPlan {
+    bool ok;
+    int g, cg, ocg;
+    size_t w_off, bias_off, ws_off, bs_off, inner_off, pack_total;      // relative to the start of the group region
+};
+
+static GroupPlan group_plan(int oc, int kh, int kw, int c)
+{
+    GroupPlan r;
+    memset(&r, 0, sizeof(r));
+    if (kh != 1 || kw != 1 || oc <= 0 || c <= 0) return r;
+    if (c % 16 == 0 && oc % 16 == 0 && c > 16) return r;               // the kernel takes these directly
+    // only the input channels are odd: a zero-padded copy of the (small) input is cheaper than the n-tiles that g OC
+    // output columns would take
+    if (c > 16 && oc % 16 == 0 && wants_padding(oc, c)) return r;
+    int g = 1;
+    while (g <= 16 && ((g * c) % 16 != 0 || (g * oc) % 16 != 0 || g * c < 32)) g *= 2;
+    if (g < 2 || g > 16 || (long long)g * oc > 4096 || (long long)g * c > 4096) return r;
+    r.g = g; r.cg = g * c; r.ocg = g * oc;
+    size_t o = 0;
+    r.w_off = o;     o += up256((size_t)r.ocg * r.cg);
+    r.bias_off = o;  o += up256((size_t)r.ocg * 4);
+    r.ws_off = o;    o += up256((size_t)r.ocg * 4);
+    r.bs_off = o;    o += up256((size_t)r.ocg * 4);
+    r.inner_off = o; o += up256(tc_pack_bytes(r.ocg, 1, 1, r.cg));
+    r.pack_total = o;
+    r.ok = true;
+    return r;
+}
+
+// start of the group region in `packed`: behind the regular tables and the channel-padded copies
+static size_t group_region_offset(int oc, int kh, int kw, int c)
+{
+    size_t n = up256(tc_pack_bytes(oc, kh, kw, c));
+    if (wants_padding(oc, c)) {
+        b200k_conv2d_params t;
+        memset(&t, 0, sizeof(t));
+        t.oc = oc; t.kh = kh; t.kw = kw; t.c = c;
+        n += pad_plan(&t).pack_total;
+    }
+    return n;
+}
+
+static b200k_conv2d_params grouped_params(const b200k_conv2d_params* p, const GroupPlan& pl)
+{
+    b200k_conv2d_params q = *p;
+    uint8_t* region = (uint8_t*)p->packed + group_region_offset(p->oc, p->kh, p->kw, p->c);
+    const long long M = (long long)p->n * p->h * p->wd;
+    q.n = 1; q.h = 1; q.oh = 1; q.wd = (int)(M / pl.g); q.ow = q.wd;
+    q.c = pl.cg; q.oc = pl.ocg;
+    q.w.data = region + pl.w_off;
+    if (p->w.scales) q.w.scales = (const float*)(region + pl.ws_off);
+    if (p->bias.data) {
+        q.bias.data = region + pl.bias_off;
+        if (p->bias.scales) q.bias.scales = (const float*)(region + pl.bs_off);
+    }
+    q.packed = region + pl.inner_off;
+    q.scratch = nullptr; q.scratch_bytes = 0;
+    return q;
+}
+
+static bool grouped_path_eligible(const b200k_conv2d_params* p, b200k_conv2d_params& q)
+{
+    if (p->add_operand.data || !p->packed || !p->x.data || !p->w.data || !p->y.data) return false;
+    if (p->kh != 1 || p->kw != 1 || p->stride_h != 1 || p->stride_w != 1 || p->dil_h != 1 || p->dil_w != 1) return false;
+    if (p->pad_top != 0 || p->pad_left != 0 || p->oh != p->h || p->ow != p->wd) return false;
+    if (p->n <= 0 || p->h <= 0 || p->wd <= 0) return false;
+    const GroupPlan pl = group_plan(p->oc, p->kh, p->kw, p->c);
+    const long long M = (long long)p->n * p->h * p->wd;
+    if (!pl.ok || M % pl.g != 0 || M / pl.g > 0x7fffffff) return false;
+    q = grouped_params(p, pl);
+    return q.c > 16 && conv_tc_eligible(&q);
+}
+
+// wp[j oc + o][i c + ch] = w[o][ch] on the diagonal blocks (i == j), the weight zero point elsewhere
+__global__ void group_weights_kernel(const uint8_t* w, uint8_t* wp, int oc, int c, int g, int fill)
+{
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const int cg = g * c;
+    if (i >= (long long)g * oc * cg) return;
+    const int col = (int)(i % cg), row = (int)(i / cg);
+    const int bj = row / oc, o = row - bj * oc, bi = col / c, ch = col - bi * c;
+    wp[i] = bi == bj ? w[(long long)o * c + ch] : (uint8_t)fill;
+}
+
+__global__ void group_vec_kernel(const uint32_t* src, uint32_t* dst, int n, int g)
+{
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n * g) dst[i] = src[i % n];
+}
+
 int conv2d_dispatch(const b200k_conv2d_params* p, cudaStream_t stream)
 {
     B200K_REQUIRE(p, B200K_E_INVALID, "conv2d_q8: null params");
     B200K_REQUIRE(p->algo >= 0 && p->algo <= 2, B200K_E_INVALID, "conv2d_q8: algo %d not in {0,1,2}", p->algo);
     if (p->algo != 1) {
-        if (conv_tc_eligible(p)) return launch_conv_tc(p, stream, 0);
-        PadPlan pl;
         b200k_conv2d_params q;
+        // (1x1 with at most 16 channels: grouped pixels rather than the few-channel kernels)
+        if (p->c <= 16 && grouped_path_eligible(p, q)) return launch_conv_tc(&q, stream, 0);
+        if (conv_tc_eligible(p)) return launch_conv_tc(p, stream, 0);
+        if (grouped_path_eligible(p, q)) return launch_conv_tc(&q, stream, 0);
+        PadPlan pl;
         if (wants_padding(p->oc, p->c) && padded_path_eligible(p, pl, q)) return launch_padded(p, pl, q, stream);
         B200K_REQUIRE(p->algo != 2, B200K_E_UNSUPPORTED, "conv2d_q8: shape/alignment not eligible for the tcgen05 kernel");
     }
@@ -171,13 +273,9 @@ extern "C" int b200k_conv2d_q8(const b200k_conv2d_params* p, void* stream)
 extern "C" size_t b200k_conv2d_pack_bytes(int32_t oc, int32_t kh, int32_t kw, int32_t c)
 {
     if (oc <= 0 || kh <= 0 || kw <= 0) return 0;
-    size_t n = up256(tc_pack_bytes(oc, kh, kw, c));
-    if (wants_padding(oc, c)) {
-        b200k_conv2d_params p;
-        memset(&p, 0, sizeof(p));
-        p.oc = oc; p.kh = kh; p.kw = kw; p.c = c;
-        n += pad_plan(&p).pack_total;
-    }
+    size_t n = group_region_offset(oc, kh, kw, c);
+    const GroupPlan gp = group_plan(oc, kh, kw, c);
+    if (gp.ok) n += gp.pack_total;
     return n;
 }
 
@@ -197,7 +295,28 @@ int conv2d_pack_impl(const b200k_conv2d_params* p, void* packed, cudaStream_t s,
     int rc = tc_pack(p, packed, s);
     if (rc) return rc;
     if (host_tables) rc = tc_pack_host_tables(p, packed, s);
-    if (rc || !wants_padding(p->oc, p->c)) return rc;
+    if (rc) return rc;
+    const GroupPlan gp = group_plan(p->oc, p->kh, p->kw, p->c);
+    if (gp.ok) {
+        // block-diagonal weights, g-fold bias and per-channel scales, and the tables of the grouped problem
+        uint8_t* region = (uint8_t*)packed + group_region_offset(p->oc, p->kh, p->kw, p->c);
+        group_weights_kernel<<<div_up((long long)gp.ocg * gp.cg, 256), 256, 0, s>>>(
+            (const uint8_t*)p->w.data, region + gp.w_off, p->oc, p->c, gp.g, p->w.scales ? 0 : (p->w.zero_point & 0xff));
+        rc = check_launch("group_weights_kernel");
+        if (rc) return rc;
+        if (p->bias.data)   group_vec_kernel<<<div_up(gp.ocg, 128), 128, 0, s>>>((const uint32_t*)p->bias.data, (uint32_t*)(region + gp.bias_off), p->oc, gp.g);
+        if (p->w.scales)    group_vec_kernel<<<div_up(gp.ocg, 128), 128, 0, s>>>((const uint32_t*)p->w.scales, (uint32_t*)(region + gp.ws_off), p->oc, gp.g);
+        if (p->bias.scales) group_vec_kernel<<<div_up(gp.ocg, 128), 128, 0, s>>>((const uint32_t*)p->bias.scales, (uint32_t*)(region + gp.bs_off), p->oc, gp.g);
+        rc = check_launch("group_vec_kernel");
+        if (rc) return rc;
+        b200k_conv2d_params q = *p;
+        q.c = gp.cg; q.oc = gp.ocg;
+        q.w.data = region + gp.w_off;
+        q.add_operand.data = nullptr; q.add_out.data = nullptr;
+        rc = tc_pack(&q, region + gp.inner_off, s);
+        if (rc) return rc;
+    }
+    if (!wants_padding(p->oc, p->c)) return rc;
     // zero-padded copies of the weights, the bias and the per-channel scales, and the tables of the padded problem
     const PadPlan pl = pad_plan(p);
     uint8_t* region = (uint8_t*)packed + up256(tc_pack_bytes(p->oc, p->kh, p->kw, p->c));

@@ -1391,6 +1391,11 @@ static bool axis_classes(int out, int in, int k, int stride, int pad, int dil, u
     n = 0;
     memset(cls, 0, 256);
     bool seen[256] = {false};
+    // output positions o_lo .. o_hi have their whole window inside the image (one class): the walk skips from the first
+    // of them to the last (a 1x1 convolution over a GEMM-shaped tensor has hundreds of thousands of them)
+    const int o_lo = pad <= 0 ? 0 : (pad + stride - 1) / stride;
+    const long long last_full = (long long)in - 1 - (long long)(k - 1) * dil + pad;
+    const int o_hi = last_full < 0 ? -1 : (int)(last_full / stride < out - 1 ? last_full / stride : out - 1);
     for (int o = 0; o < out; ++o) {
         const int i0 = o * stride - pad;
         int k0 = i0 < 0 ? (-i0 + dil - 1) / dil : 0;
@@ -1398,12 +1403,14 @@ static bool axis_classes(int out, int in, int k, int stride, int pad, int dil, u
         if (k0 > k) k0 = k;
         if (k1 < k0) k1 = k0;
         const int code = k0 * 16 + k1;
-        if (seen[code]) continue;
-        if (n == 16) return false;
-        seen[code] = true;
-        pairs[n] = (uint8_t)code;
-        cls[code] = (uint8_t)n;
-        ++n;
+        if (!seen[code]) {
+            if (n == 16) return false;
+            seen[code] = true;
+            pairs[n] = (uint8_t)code;
+            cls[code] = (uint8_t)n;
+            ++n;
+        }
+        if (o >= o_lo && o < o_hi) o = o_hi - 1;          // (the next one visited is o_hi)
     }
     return n > 0;
 }

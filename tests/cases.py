@@ -36,6 +36,20 @@ def conv_cases():
     c["fused_add_relu_1x1"] = lambda: random_conv_case(14, 2, 14, 14, 64, 256, 1, 1, act=(1, 0, 0), fused_add=True)
     c["fused_add_3x3_odd"] = lambda: random_conv_case(15, 1, 7, 9, 12, 20, 3, 3, pad=(1, 1, 1, 1), fused_add=True)
     c["fused_add_u8"] = lambda: random_conv_case(16, 1, 8, 8, 16, 24, 1, 1, x_dtype=U8, y_dtype=U8, x_q=(0.5, 128), fused_add=True)
+    # 1x1 convolutions that run as a GEMM over groups of 2, 4 or 8 consecutive pixels (block-diagonal weights): the
+    # MobileNet-v2 bottleneck shapes, every weight type, a pixel count the group does not divide (another path)
+    c["grouped_c16_oc96_u8_everything"] = lambda: random_conv_case(17, 2, 28, 28, 16, 96, 1, 1, x_dtype=U8, w_dtype=U8, y_dtype=U8,
+                                                                   per_axis=False, x_q=(0.02, 117), y_zp=0, act=(2, 6.0, 0.0),
+                                                                   y_scale=0.02)
+    c["c24_oc144_u8_everything_padded_input"] = lambda: random_conv_case(18, 2, 28, 28, 24, 144, 1, 1, x_dtype=U8, w_dtype=U8, y_dtype=U8,
+                                                                    per_axis=False, x_q=(0.02, 131), y_zp=0, act=(2, 6.0, 0.0),
+                                                                    y_scale=0.02)
+    c["grouped_c96_oc24_u8_everything"] = lambda: random_conv_case(19, 2, 28, 28, 96, 24, 1, 1, x_dtype=U8, w_dtype=U8, y_dtype=U8,
+                                                                   per_axis=False, x_q=(0.02, 3))
+    c["grouped_c8_oc40_per_axis"] = lambda: random_conv_case(20, 1, 12, 12, 8, 40, 1, 1, act=(1, 0, 0))
+    c["grouped_c12_oc20_s8_weight_zero_point"] = lambda: random_conv_case(21, 1, 8, 8, 12, 20, 1, 1, per_axis=False, w_zp=11)
+    c["grouped_c2_oc6_group8"] = lambda: random_conv_case(22, 1, 8, 8, 2, 6, 1, 1, bias=False)
+    c["c24_oc144_odd_pixel_count"] = lambda: random_conv_case(23, 1, 7, 9, 24, 144, 1, 1)
     return c
 
 

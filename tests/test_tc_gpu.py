@@ -176,8 +176,9 @@ def test_zero_points_outside_the_type_range_are_refused(built):
 
 def test_ineligible_shapes_are_refused_when_forced(built):
     from armnn_b200 import lib
-    # channel counts that are not multiples of 8 cannot even use the zero-padded copies
-    case = random_conv_case(232, 1, 8, 8, 20, 28, 1, 1)
+    # channel counts that are not multiples of 8 cannot even use the zero-padded copies (a 1x1 convolution could run on
+    # groups of pixels instead: 3x3 here)
+    case = random_conv_case(232, 1, 8, 8, 20, 28, 3, 3, pad=(1, 1, 1, 1))
     with pytest.raises(lib.B200KError) as e:
         case.run_gpu(algo=2)
     assert e.value.code == _abi.E_UNSUPPORTED
