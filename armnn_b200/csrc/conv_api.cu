@@ -151,7 +151,7 @@ static int launch_padded(const b200k_conv2d_params* p, const PadPlan& pl, const 
 // [M / g, g C] x [g C, g OC] with a block-diagonal weight matrix (g copies of the weights; every other entry the weight
 // zero point, i.e. a real zero), on the very same input and output bytes: no copy of either tensor.  g is the smallest
 // power of two that makes g C and g OC multiples of 16 (and g C at least 32: the few-channel kernels are built for
-// stems with wide filters, not for this).  The g-fold redundant multiplications are free on a layer that is bound by
+// stems with wide filters, not for this; and g OC at least 64, the narrowest tile of the kernel).  The g-fold redundant multiplications are free on a layer that is bound by
 // its memory traffic.  Needs M % g == 0; the channel-padded path below takes what is left.
 struct GroupPlan {
     bool ok;
@@ -164,12 +164,12 @@ static GroupPlan group_plan(int oc, int kh, int kw, int c)
     GroupPlan r;
     memset(&r, 0, sizeof(r));
     if (kh != 1 || kw != 1 || oc <= 0 || c <= 0) return r;
-    if (c % 16 == 0 && oc % 16 == 0 && c > 16) return r;               // the kernel takes these directly
+    if (c % 16 == 0 && oc % 16 == 0 && c > 16 && oc >= 64) return r;   // the kernel takes these directly
     // only the input channels are odd: a zero-padded copy of the (small) input is cheaper than the n-tiles that g OC
     // output columns would take
     if (c > 16 && oc % 16 == 0 && wants_padding(oc, c)) return r;
     int g = 1;
-    while (g <= 16 && ((g * c) % 16 != 0 || (g * oc) % 16 != 0 || g * c < 32)) g *= 2;
+    while (g <= 16 && ((g * c) % 16 != 0 || (g * oc) % 16 != 0 || g * c < 32 || g * oc < 64)) g *= 2;
     if (g < 2 || g > 16 || (long long)g * oc > 4096 || (long long)g * c > 4096) return r;
     r.g = g; r.cg = g * c; r.ocg = g * oc;
     size_t o = 0;
@@ -250,10 +250,9 @@ int conv2d_dispatch(const b200k_conv2d_params* p, cudaStream_t stream)
     B200K_REQUIRE(p->algo >= 0 && p->algo <= 2, B200K_E_INVALID, "conv2d_q8: algo %d not in {0,1,2}", p->algo);
     if (p->algo != 1) {
         b200k_conv2d_params q;
-        // (1x1 with at most 16 channels: grouped pixels rather than the few-channel kernels)
-        if (p->c <= 16 && grouped_path_eligible(p, q)) return launch_conv_tc(&q, stream, 0);
-        if (conv_tc_eligible(p)) return launch_conv_tc(p, stream, 0);
+        // (group_plan only has a plan where groups of pixels beat what the kernel would do with the tensors as they are)
         if (grouped_path_eligible(p, q)) return launch_conv_tc(&q, stream, 0);
+        if (conv_tc_eligible(p)) return launch_conv_tc(p, stream, 0);
         PadPlan pl;
         if (wants_padding(p->oc, p->c) && padded_path_eligible(p, pl, q)) return launch_padded(p, pl, q, stream);
         B200K_REQUIRE(p->algo != 2, B200K_E_UNSUPPORTED, "conv2d_q8: shape/alignment not eligible for the tcgen05 kernel");

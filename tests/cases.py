@@ -49,6 +49,9 @@ def conv_cases():
     c["grouped_c8_oc40_per_axis"] = lambda: random_conv_case(20, 1, 12, 12, 8, 40, 1, 1, act=(1, 0, 0))
     c["grouped_c12_oc20_s8_weight_zero_point"] = lambda: random_conv_case(21, 1, 8, 8, 12, 20, 1, 1, per_axis=False, w_zp=11)
     c["grouped_c2_oc6_group8"] = lambda: random_conv_case(22, 1, 8, 8, 2, 6, 1, 1, bias=False)
+    c["grouped_c32_oc16_narrow_output"] = lambda: random_conv_case(24, 2, 12, 12, 32, 16, 1, 1, x_dtype=U8, w_dtype=U8, y_dtype=U8,
+                                                                   per_axis=False, x_q=(0.02, 120))
+    c["grouped_c192_oc32_per_axis"] = lambda: random_conv_case(25, 1, 14, 14, 192, 32, 1, 1)
     c["c24_oc144_odd_pixel_count"] = lambda: random_conv_case(23, 1, 7, 9, 24, 144, 1, 1)
     return c
 
