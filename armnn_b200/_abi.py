@@ -84,6 +84,12 @@ class PadParams(C.Structure):
                 ("pad_before", C.c_int32 * 4), ("pad_after", C.c_int32 * 4), ("pad_value", C.c_float)]
 
 
+class ViewCopyParams(C.Structure):
+    _fields_ = [("x", QTensor), ("y", QTensor), ("rank", C.c_int32), ("shape", C.c_int32 * 6),
+                ("src_strides", C.c_int64 * 6), ("dst_strides", C.c_int64 * 6),
+                ("src_offset", C.c_int64), ("dst_offset", C.c_int64)]
+
+
 _P, _F, _I = C.c_void_p, C.c_float, C.c_int32
 
 
@@ -128,6 +134,7 @@ KERNEL_ENTRY_POINTS = {
     "convert_q": ConvertParams,
     "qlstm_step": QLstmParams,
     "pad_q": PadParams,
+    "view_copy_q": ViewCopyParams,
 }
 
 # every symbol include/b200k.h declares

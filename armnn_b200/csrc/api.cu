@@ -105,6 +105,7 @@ extern "C" size_t b200k_sizeof_params(int which)
         case 8: return sizeof(b200k_convert_params);
         case 9: return sizeof(b200k_qlstm_params);
         case 10: return sizeof(b200k_pad_params);
+        case 11: return sizeof(b200k_view_copy_params);
         default: return 0;
     }
 }

@@ -1,0 +1,131 @@
+// View copies: Concat, Splitter, Permute, Transpose, StridedSlice and Slice are all "a rectangular view of one tensor
+// onto a rectangular view of another", element by element through Q_y(deq_x(.)) as the reference's Decoder / Encoder
+// pair does it (src/backends/reference/workloads/Concatenate.cpp:14-85, Splitter.cpp:18-93) or byte for byte
+// (src/armnnUtils/Permute.cpp, Transpose.cpp; workloads/StridedSlice.cpp, Slice.cpp).  Bandwidth kernels:
+//   * rows: both views contiguous along the innermost dimension, equal quantisation, everything 16-byte aligned
+//     (channel-wise Concat / Splitter of NHWC tensors, Slice of whole pixels): 128-bit loads and stores;
+//   * generic: one element per thread, destination-major order (coalesced stores; loads as the source strides allow).
+#include "common.cuh"
+
+namespace b200k {
+
+struct ViewArgs {
+    QView x, y;
+    int rank;
+    int shape[6];
+    long long ss[6], ds[6];
+    long long soff, doff;
+    long long count;
+    int same;                       // equal type and quantisation: bytes move as they are
+    int esize;
+};
+
+__global__ void __launch_bounds__(256) view_copy_kernel(const ViewArgs a)
+{
+    pdl_enter();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= a.count) return;
+    long long rest = i, s = a.soff, d = a.doff;
+    #pragma unroll
+    for (int k = 5; k >= 0; --k) {
+        if (k >= a.rank) continue;
+        const long long c = rest % a.shape[k];
+        rest /= a.shape[k];
+        s += c * a.ss[k];
+        d += c * a.ds[k];
+    }
+    if (a.same) {
+        if (a.esize == 1)      ((uint8_t*)a.y.data)[d] = ((const uint8_t*)a.x.data)[s];
+        else if (a.esize == 2) ((uint16_t*)a.y.data)[d] = ((const uint16_t*)a.x.data)[s];
+        else                   ((uint32_t*)a.y.data)[d] = ((const uint32_t*)a.x.data)[s];
+    } else {
+        a.y.set(d, a.x.get(s));
+    }
+}
+
+// rows of `row16` 16-byte words: row r of the view starts at byte offsets sb / db (from the outer coordinates)
+struct ViewRowArgs {
+    const uint8_t* x; uint8_t* y;
+    int rank;                       // outer dimensions
+    int shape[6];
+    long long ssb[6], dsb[6];       // strides in bytes
+    long long rows;
+    int row16;
+};
+
+__global__ void __launch_bounds__(256) view_rows_kernel(const ViewRowArgs a)
+{
+    pdl_enter();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= a.rows * a.row16) return;
+    long long rest = i / a.row16;
+    const int w = (int)(i - rest * a.row16);
+    long long s = 0, d = 0;
+    #pragma unroll
+    for (int k = 5; k >= 0; --k) {
+        if (k >= a.rank) continue;
+        const long long c = rest % a.shape[k];
+        rest /= a.shape[k];
+        s += c * a.ssb[k];
+        d += c * a.dsb[k];
+    }
+    ((uint4*)(a.y + d))[w] = ((const uint4*)(a.x + s))[w];
+}
+
+}  // namespace b200k
+
+using namespace b200k;
+
+extern "C" int b200k_view_copy_q(const b200k_view_copy_params* p, void* stream)
+{
+    B200K_REQUIRE(p, B200K_E_INVALID, "view_copy_q: null params");
+    B200K_REQUIRE(p->x.data && p->y.data, B200K_E_INVALID, "view_copy_q: null tensor pointer");
+    B200K_REQUIRE(p->rank >= 1 && p->rank <= 6, B200K_E_UNSUPPORTED, "view_copy_q: rank %d not in [1, 6]", p->rank);
+    B200K_REQUIRE(p->x.dtype >= B200K_U8 && p->x.dtype <= B200K_F32 && p->y.dtype >= B200K_U8 && p->y.dtype <= B200K_F32,
+                  B200K_E_INVALID, "view_copy_q: unknown element type");
+    B200K_REQUIRE(p->x.dtype == p->y.dtype, B200K_E_UNSUPPORTED, "view_copy_q: input and output types differ (%d, %d)",
+                  p->x.dtype, p->y.dtype);
+    B200K_REQUIRE(p->src_offset >= 0 && p->dst_offset >= 0, B200K_E_INVALID, "view_copy_q: negative offset");
+    long long count = 1;
+    for (int d = 0; d < p->rank; ++d) {
+        B200K_REQUIRE(p->shape[d] >= 0, B200K_E_INVALID, "view_copy_q: negative extent");
+        count *= p->shape[d];
+    }
+    if (count == 0) return B200K_OK;                       // an empty view: nothing to copy
+    const bool quantised = p->x.dtype == B200K_U8 || p->x.dtype == B200K_S8 || p->x.dtype == B200K_S16;
+    const bool same = !quantised || (p->x.scale == p->y.scale && p->x.zero_point == p->y.zero_point);
+    const int es = elem_size(p->x.dtype);
+    cudaStream_t s = (cudaStream_t)stream;
+
+    // rows: innermost dimension contiguous on both sides and a whole number of aligned 16-byte words
+    const int in = p->rank - 1;
+    const long long row_bytes = (long long)p->shape[in] * es;
+    bool rows = same && p->src_strides[in] == 1 && p->dst_strides[in] == 1 && row_bytes % 16 == 0 &&
+                ((uintptr_t)p->x.data + (uintptr_t)(p->src_offset * es)) % 16 == 0 &&
+                ((uintptr_t)p->y.data + (uintptr_t)(p->dst_offset * es)) % 16 == 0 && row_bytes / 16 <= 0x7fffffff;
+    for (int d = 0; d < in && rows; ++d)
+        rows = (p->src_strides[d] * es) % 16 == 0 && (p->dst_strides[d] * es) % 16 == 0;
+    if (rows) {
+        ViewRowArgs a;
+        memset(&a, 0, sizeof(a));
+        a.x = (const uint8_t*)p->x.data + p->src_offset * es;
+        a.y = (uint8_t*)p->y.data + p->dst_offset * es;
+        a.rank = in;
+        a.rows = 1;
+        for (int d = 0; d < in; ++d) {
+            a.shape[d] = p->shape[d]; a.ssb[d] = p->src_strides[d] * es; a.dsb[d] = p->dst_strides[d] * es;
+            a.rows *= p->shape[d];
+        }
+        a.row16 = (int)(row_bytes / 16);
+        launch_pdl(view_rows_kernel, dim3(div_up(a.rows * a.row16, 256)), dim3(256), 0, s, a);
+        return check_launch("view_rows_kernel");
+    }
+    ViewArgs a;
+    memset(&a, 0, sizeof(a));
+    a.x = make_view(p->x); a.y = make_view(p->y);
+    a.rank = p->rank; a.count = count; a.same = same ? 1 : 0; a.esize = es;
+    a.soff = p->src_offset; a.doff = p->dst_offset;
+    for (int d = 0; d < p->rank; ++d) { a.shape[d] = p->shape[d]; a.ss[d] = p->src_strides[d]; a.ds[d] = p->dst_strides[d]; }
+    launch_pdl(view_copy_kernel, dim3(div_up(count, 256)), dim3(256), 0, s, a);
+    return check_launch("view_copy_kernel");
+}

@@ -256,6 +256,31 @@ typedef struct {
 
 int b200k_pad_q(const b200k_pad_params* p, void* stream);
 
+/* ---- Concat, Splitter, Permute, Transpose, StridedSlice, Slice ---------------------------------- */
+
+/* One rectangular view of a tensor copied onto a view of another one:
+ *     y[dst_offset + sum_d i_d dst_strides[d]] = Q_y(deq_x(x[src_offset + sum_d i_d src_strides[d]]))   for 0 <= i_d < shape[d]
+ * (offsets and strides in elements, outermost dimension first, rank <= 6; strides may be negative or zero).  With equal
+ * quantisation the bytes are copied as they are.  This is what the reference's data-movement workloads do element by
+ * element through a Decoder / Encoder pair or with memcpy:
+ *   armnn::Concatenate (src/backends/reference/workloads/Concatenate.cpp:14-85): one call per input view, the
+ *     destination view placed at the view's origin in the output;
+ *   armnn::Split (workloads/Splitter.cpp:18-93): one call per output view, the source view at the origin in the input;
+ *   armnnUtils::Permute / Transpose (src/armnnUtils/Permute.cpp:22-119, Transpose.cpp:22-117; RefPermuteWorkload.cpp,
+ *     RefTransposeWorkload.cpp): the source strides in the destination's order of dimensions;
+ *   armnn::StridedSlice (workloads/StridedSlice.cpp:90-223) and armnn::Slice (workloads/Slice.cpp:14-147): source
+ *     offset from the begin indices, source strides multiplied by the slice's strides.
+ * The host side (the plugin's workloads, armnn_b200/views.py) turns the layer descriptors into these views. */
+typedef struct {
+    b200k_qtensor x, y;
+    int32_t rank;
+    int32_t shape[6];
+    int64_t src_strides[6], dst_strides[6];
+    int64_t src_offset, dst_offset;
+} b200k_view_copy_params;
+
+int b200k_view_copy_q(const b200k_view_copy_params* p, void* stream);
+
 /* ---- Softmax --------------------------------------------------------------------------------- */
 
 /* armnn::Softmax (src/backends/reference/workloads/Softmax.cpp:17-70): softmax over the axis of

@@ -28,6 +28,7 @@
 #include <vector>
 
 #include "../include/b200k.h"
+#include "move_desc.h"
 
 using namespace armnn;
 
@@ -351,6 +352,107 @@ extern "C" int cpuref_pad_q(const b200k_pad_params* p)
         ITensorHandle* o = h.out(d, yi);
         h.run(LayerType::Pad, d);
         copy_out(o, const_cast<void*>(p->y.data), yi.GetNumBytes());
+    });
+}
+
+// Concat, Splitter, Permute, Transpose, StridedSlice, Slice: the real RefConcatWorkload ... RefSliceWorkload on the
+// descriptor the test states (oracle/move_desc.h).
+extern "C" int cpuref_move_q(const oracle_move_params* p)
+{
+    return guarded([&] {
+        Harness h;
+        const unsigned rank = (unsigned)p->rank;
+        auto shape_of = [&](const int32_t* s, unsigned r) {
+            unsigned dims[6];
+            for (unsigned i = 0; i < r; ++i) dims[i] = (unsigned)s[i];
+            return TensorShape(r, dims);
+        };
+        const TensorInfo whole = make_info(p->whole, shape_of(p->whole_shape, rank), 0, 0, false);
+        std::vector<TensorInfo> views;
+        for (int v = 0; v < p->n_views; ++v)
+            views.push_back(make_info(p->view[v], shape_of(p->view_shape[v], p->view_rank[v] ? (unsigned)p->view_rank[v] : rank), 0, 0, false));
+        std::vector<ITensorHandle*> outs;
+        switch (p->kind) {
+            case MOVE_CONCAT: {
+                ConcatQueueDescriptor d;
+                d.m_Parameters = OriginsDescriptor((uint32_t)p->n_views, rank);
+                for (int v = 0; v < p->n_views; ++v) {
+                    std::vector<unsigned> origin(p->view_origin[v], p->view_origin[v] + rank);
+                    for (unsigned i = 0; i < rank; ++i) d.m_Parameters.SetViewOriginCoord((uint32_t)v, i, origin[i]);
+                    d.m_ViewOrigins.emplace_back(origin);
+                    h.in(d, views[(size_t)v], p->view[v].data);
+                }
+                ITensorHandle* o = h.out(d, whole);
+                std::memcpy(o->Map(), p->whole.data, whole.GetNumBytes());      // (elements no view covers keep their value)
+                o->Unmap();
+                h.run(LayerType::Concat, d);
+                copy_out(o, const_cast<void*>(p->whole.data), whole.GetNumBytes());
+                break;
+            }
+            case MOVE_SPLIT: {
+                SplitterQueueDescriptor d;
+                d.m_Parameters = ViewsDescriptor((uint32_t)p->n_views, rank);
+                h.in(d, whole, p->whole.data);
+                for (int v = 0; v < p->n_views; ++v) {
+                    std::vector<unsigned> origin(p->view_origin[v], p->view_origin[v] + rank);
+                    for (unsigned i = 0; i < rank; ++i) {
+                        d.m_Parameters.SetViewOriginCoord((uint32_t)v, i, origin[i]);
+                        d.m_Parameters.SetViewSize((uint32_t)v, i, (uint32_t)p->view_shape[v][i]);
+                    }
+                    d.m_ViewOrigins.emplace_back(origin);
+                    outs.push_back(h.out(d, views[(size_t)v]));
+                }
+                h.run(LayerType::Splitter, d);
+                for (int v = 0; v < p->n_views; ++v) copy_out(outs[(size_t)v], const_cast<void*>(p->view[v].data), views[(size_t)v].GetNumBytes());
+                break;
+            }
+            case MOVE_PERMUTE:
+            case MOVE_TRANSPOSE: {
+                unsigned m[6];
+                for (unsigned i = 0; i < rank; ++i) m[i] = (unsigned)p->perm[i];
+                const PermutationVector pv(m, rank);
+                if (p->kind == MOVE_PERMUTE) {
+                    PermuteQueueDescriptor d;
+                    d.m_Parameters = PermuteDescriptor(pv);
+                    h.in(d, whole, p->whole.data);
+                    outs.push_back(h.out(d, views[0]));
+                    h.run(LayerType::Permute, d);
+                } else {
+                    TransposeQueueDescriptor d;
+                    d.m_Parameters = TransposeDescriptor(pv);
+                    h.in(d, whole, p->whole.data);
+                    outs.push_back(h.out(d, views[0]));
+                    h.run(LayerType::Transpose, d);
+                }
+                copy_out(outs[0], const_cast<void*>(p->view[0].data), views[0].GetNumBytes());
+                break;
+            }
+            case MOVE_STRIDED_SLICE: {
+                StridedSliceQueueDescriptor d;
+                d.m_Parameters.m_Begin.assign(p->begin, p->begin + rank);
+                d.m_Parameters.m_End.assign(p->end, p->end + rank);
+                d.m_Parameters.m_Stride.assign(p->stride, p->stride + rank);
+                d.m_Parameters.m_BeginMask = p->begin_mask;
+                d.m_Parameters.m_EndMask = p->end_mask;
+                d.m_Parameters.m_ShrinkAxisMask = p->shrink_axis_mask;
+                h.in(d, whole, p->whole.data);
+                outs.push_back(h.out(d, views[0]));
+                h.run(LayerType::StridedSlice, d);
+                copy_out(outs[0], const_cast<void*>(p->view[0].data), views[0].GetNumBytes());
+                break;
+            }
+            case MOVE_SLICE: {
+                SliceQueueDescriptor d;
+                d.m_Parameters.m_Begin.assign(p->begin, p->begin + rank);
+                d.m_Parameters.m_Size.assign(p->end, p->end + rank);
+                h.in(d, whole, p->whole.data);
+                outs.push_back(h.out(d, views[0]));
+                h.run(LayerType::Slice, d);
+                copy_out(outs[0], const_cast<void*>(p->view[0].data), views[0].GetNumBytes());
+                break;
+            }
+            default: throw InvalidArgumentException("cpuref_move_q: unknown kind");
+        }
     });
 }
 

@@ -27,6 +27,7 @@
 #include <stdlib.h>
 #include <string.h>
 #include "../include/b200k.h"
+#include "move_desc.h"
 
 /* ---- armnn::Quantize / armnn::Dequantize, src/armnn/TypesUtils.cpp:29-56 ------------------- */
 
@@ -481,6 +482,168 @@ int oracle_pad_q(const b200k_pad_params* p)
         store_f(&raw, i, p->pad_value);
     }
     return 0;
+}
+
+/* ---- Concat, Splitter, Permute, Transpose, StridedSlice, Slice ----------------------------------
+ * The reference's data-movement workloads, each walked the way the reference walks it. */
+
+static int64_t elems(const int32_t* shape, int rank)
+{
+    int64_t n = 1;
+    for (int d = 0; d < rank; ++d) n *= shape[d];
+    return n;
+}
+
+static size_t esize(int dtype) { return dtype == B200K_U8 || dtype == B200K_S8 ? 1 : (dtype == B200K_S16 ? 2 : 4); }
+
+/* flat index -> coordinates, outermost first */
+static void coords_of(int64_t i, const int32_t* shape, int rank, int32_t* c)
+{
+    for (int d = rank - 1; d >= 0; --d) { c[d] = (int32_t)(i % shape[d]); i /= shape[d]; }
+}
+
+/* Concatenate.cpp:14-85: every output element takes the value of the first input view that contains it, decoded with
+ * the input's quantisation and encoded with the output's; elements no view covers are left alone. */
+static int move_concat(const oracle_move_params* p)
+{
+    const int64_t n = elems(p->whole_shape, p->rank);
+    for (int64_t i = 0; i < n; ++i) {
+        int32_t c[6];
+        coords_of(i, p->whole_shape, p->rank, c);
+        for (int v = 0; v < p->n_views; ++v) {
+            int inside = 1;
+            for (int d = 0; d < p->rank; ++d)
+                if (c[d] < p->view_origin[v][d] || c[d] >= p->view_origin[v][d] + p->view_shape[v][d]) inside = 0;
+            if (!inside) continue;
+            int64_t idx = 0, stride = 1;
+            for (int d = p->rank - 1; d >= 0; --d) { idx += stride * (c[d] - p->view_origin[v][d]); stride *= p->view_shape[v][d]; }
+            store_f(&p->whole, i, load_f(&p->view[v], idx));
+            break;
+        }
+    }
+    return 0;
+}
+
+/* Splitter.cpp:18-93: every input element goes to the first output view that contains it. */
+static int move_split(const oracle_move_params* p)
+{
+    const int64_t n = elems(p->whole_shape, p->rank);
+    for (int64_t i = 0; i < n; ++i) {
+        int32_t c[6];
+        coords_of(i, p->whole_shape, p->rank, c);
+        for (int v = 0; v < p->n_views; ++v) {
+            int inside = 1;
+            for (int d = 0; d < p->rank; ++d)
+                if (c[d] < p->view_origin[v][d] || c[d] >= p->view_origin[v][d] + p->view_shape[v][d]) inside = 0;
+            if (!inside) continue;
+            int64_t idx = 0, stride = 1;
+            for (int d = p->rank - 1; d >= 0; --d) { idx += stride * (c[d] - p->view_origin[v][d]); stride *= p->view_shape[v][d]; }
+            store_f(&p->view[v], idx, load_f(&p->whole, i));
+            break;
+        }
+    }
+    return 0;
+}
+
+/* Permute.cpp:22-119 (mapping[i] is the destination dimension of source dimension i) and Transpose.cpp:22-117
+ * (mapping[i] is the source dimension of destination dimension i): raw elements, no re-quantisation. */
+static int move_permute(const oracle_move_params* p, int transpose)
+{
+    const size_t es = esize(p->whole.dtype);
+    const int rank = p->rank;
+    int32_t src_of_dst[6];                  /* source dimension that becomes destination dimension j */
+    for (int i = 0; i < rank; ++i) {
+        if (transpose) src_of_dst[i] = p->perm[i];
+        else           src_of_dst[p->perm[i]] = i;
+    }
+    int32_t dst_shape[6];
+    for (int j = 0; j < rank; ++j) dst_shape[j] = p->whole_shape[src_of_dst[j]];
+    for (int j = 0; j < rank; ++j) if (dst_shape[j] != p->view_shape[0][j]) return B200K_E_INVALID;
+    int64_t src_stride[6], st = 1;
+    for (int d = rank - 1; d >= 0; --d) { src_stride[d] = st; st *= p->whole_shape[d]; }
+    const int64_t n = elems(dst_shape, rank);
+    for (int64_t i = 0; i < n; ++i) {
+        int32_t c[6];
+        coords_of(i, dst_shape, rank, c);
+        int64_t src = 0;
+        for (int j = 0; j < rank; ++j) src += (int64_t)c[j] * src_stride[src_of_dst[j]];
+        memcpy((uint8_t*)p->view[0].data + (size_t)i * es, (const uint8_t*)p->whole.data + (size_t)src * es, es);
+    }
+    return 0;
+}
+
+/* StridedSliceDescriptor::GetStartForAxis / GetStopForAxis (src/armnn/Descriptors.cpp:393-453) and the loop nest of
+ * StridedSlice.cpp:188-222 (without ellipsis and new-axis masks): raw elements in the order the strided walk visits. */
+static int move_strided_slice(const oracle_move_params* p)
+{
+    const size_t es = esize(p->whole.dtype);
+    const int rank = p->rank;
+    int start[6], stop[6], count[6];
+    for (int d = 0; d < rank; ++d) {
+        const int size = p->whole_shape[d], stride = p->stride[d];
+        if (stride == 0) return B200K_E_INVALID;
+        long long b = p->begin[d];
+        if (p->begin_mask & (1 << d)) b = stride > 0 ? -2147483648LL : 2147483647LL;
+        if (b < 0) b += size;
+        start[d] = (int)(b < 0 ? 0 : (b > size - 1 ? size - 1 : b));
+        if (p->shrink_axis_mask & (1 << d)) {
+            stop[d] = start[d] + 1;
+        } else {
+            long long e = p->end[d];
+            if (p->end_mask & (1 << d)) e = stride > 0 ? 2147483647LL : -2147483648LL;
+            if (e < 0) e += size;
+            if (stride > 0) stop[d] = (int)(e < 0 ? 0 : (e > size ? size : e));
+            else            stop[d] = (int)(e < -1 ? -1 : (e > size - 1 ? size - 1 : e));
+        }
+        count[d] = 0;
+        for (int i = start[d]; stride > 0 ? i < stop[d] : i > stop[d]; i += stride) ++count[d];
+    }
+    int64_t src_stride[6], st = 1;
+    for (int d = rank - 1; d >= 0; --d) { src_stride[d] = st; st *= p->whole_shape[d]; }
+    const int64_t n = elems(count, rank);
+    for (int64_t i = 0; i < n; ++i) {
+        int32_t c[6];
+        coords_of(i, count, rank, c);
+        int64_t src = 0;
+        for (int d = 0; d < rank; ++d) src += (int64_t)(start[d] + c[d] * p->stride[d]) * src_stride[d];
+        memcpy((uint8_t*)p->view[0].data + (size_t)i * es, (const uint8_t*)p->whole.data + (size_t)src * es, es);
+    }
+    return 0;
+}
+
+/* Slice.cpp:14-147: the block of `size` elements per dimension that starts at `begin`, raw elements. */
+static int move_slice(const oracle_move_params* p)
+{
+    const size_t es = esize(p->whole.dtype);
+    const int rank = p->rank;
+    int64_t src_stride[6], st = 1;
+    for (int d = rank - 1; d >= 0; --d) {
+        if (p->begin[d] < 0 || p->end[d] < 0 || p->begin[d] + p->end[d] > p->whole_shape[d]) return B200K_E_INVALID;
+        src_stride[d] = st; st *= p->whole_shape[d];
+    }
+    const int64_t n = elems(p->end, rank);
+    for (int64_t i = 0; i < n; ++i) {
+        int32_t c[6];
+        coords_of(i, p->end, rank, c);
+        int64_t src = 0;
+        for (int d = 0; d < rank; ++d) src += (int64_t)(p->begin[d] + c[d]) * src_stride[d];
+        memcpy((uint8_t*)p->view[0].data + (size_t)i * es, (const uint8_t*)p->whole.data + (size_t)src * es, es);
+    }
+    return 0;
+}
+
+int oracle_move_q(const oracle_move_params* p)
+{
+    if (!p || p->rank < 1 || p->rank > 6 || !p->whole.data || p->n_views < 1 || p->n_views > 8) return B200K_E_INVALID;
+    switch (p->kind) {
+        case MOVE_CONCAT:        return move_concat(p);
+        case MOVE_SPLIT:         return move_split(p);
+        case MOVE_PERMUTE:       return move_permute(p, 0);
+        case MOVE_TRANSPOSE:     return move_permute(p, 1);
+        case MOVE_STRIDED_SLICE: return move_strided_slice(p);
+        case MOVE_SLICE:         return move_slice(p);
+        default: return B200K_E_INVALID;
+    }
 }
 
 /* ---- QLstm, RefQLstmWorkload.cpp:46-541 with LstmUtils.cpp:16-256 ------------------------------

@@ -5,7 +5,7 @@ padding wider than the kernel, per-axis and per-tensor quantisation, both 8-bit 
 broadcast, ragged tails that do not fill a vector or a tile."""
 import numpy as np
 
-from q8util import (RANGE, NP_OF, FcCase, SimpleCase, _abi, activation_clamp, qt, qt_out, random_conv_case,
+from q8util import (RANGE, NP_OF, FcCase, MoveCase, SimpleCase, _abi, activation_clamp, qt, qt_out, random_conv_case,
                     random_fc_case, random_qlstm_case)
 
 U8, S8, S16, S32, F32 = _abi.U8, _abi.S8, _abi.S16, _abi.S32, _abi.F32
@@ -341,9 +341,49 @@ def qlstm_cases():
     }
 
 
+def move_cases():
+    """Concat, Splitter, Permute, Transpose, StridedSlice and Slice as the reference's descriptors state them."""
+    q = (S8, 0.05, -3)
+    c = {}
+    # channel-wise Concat of NHWC tensors (the 128-bit row path), equal quantisation
+    c["concat_channels_nhwc"] = lambda: MoveCase("concat", 201, ((2, 7, 5, 80),) + q,
+                                                  [((2, 7, 5, 32),) + q, ((2, 7, 5, 48),) + q], origins=[(0, 0, 0, 0), (0, 0, 0, 32)])
+    # inputs with their own quantisation: every element goes through Q_out(deq_in(.))
+    c["concat_requantise_u8"] = lambda: MoveCase("concat", 202, ((1, 4, 6, 11), U8, 0.07, 120),
+                                                 [((1, 4, 6, 3), U8, 0.05, 128), ((1, 4, 6, 8), U8, 0.11, 100)],
+                                                 origins=[(0, 0, 0, 0), (0, 0, 0, 3)])
+    c["concat_height_three_inputs"] = lambda: MoveCase("concat", 203, ((1, 9, 4, 6),) + q,
+                                                       [((1, 2, 4, 6),) + q, ((1, 3, 4, 6),) + q, ((1, 4, 4, 6),) + q],
+                                                       origins=[(0, 0, 0, 0), (0, 2, 0, 0), (0, 5, 0, 0)])
+    c["concat_batch_rank2_float"] = lambda: MoveCase("concat", 204, ((5, 7), F32, 1.0, 0), [((2, 7), F32, 1.0, 0), ((3, 7), F32, 1.0, 0)],
+                                                     origins=[(0, 0), (2, 0)])
+    c["split_channels_nhwc"] = lambda: MoveCase("split", 205, ((2, 5, 5, 96),) + q,
+                                                [((2, 5, 5, 32),) + q, ((2, 5, 5, 64),) + q], origins=[(0, 0, 0, 0), (0, 0, 0, 32)])
+    c["split_width_requantise"] = lambda: MoveCase("split", 206, ((1, 3, 10, 4), S8, 0.05, 2),
+                                                   [((1, 3, 4, 4), S8, 0.05, 2), ((1, 3, 6, 4), S8, 0.08, -5)],
+                                                   origins=[(0, 0, 0, 0), (0, 0, 4, 0)])
+    c["split_s16_rank3"] = lambda: MoveCase("split", 207, ((4, 6, 5), S16, 0.01, 0), [((4, 2, 5), S16, 0.01, 0), ((4, 4, 5), S16, 0.01, 0)],
+                                            origins=[(0, 0, 0), (0, 2, 0)])
+    c["permute_nhwc_to_nchw"] = lambda: MoveCase("permute", 208, ((2, 5, 7, 3),) + q, [((2, 3, 5, 7),) + q], perm=(0, 2, 3, 1))
+    c["permute_rank3_u8"] = lambda: MoveCase("permute", 209, ((4, 6, 5), U8, 0.1, 7), [((5, 4, 6), U8, 0.1, 7)], perm=(1, 2, 0))
+    c["transpose_nchw_to_nhwc"] = lambda: MoveCase("transpose", 210, ((2, 3, 5, 7),) + q, [((2, 5, 7, 3),) + q], perm=(0, 2, 3, 1))
+    c["transpose_rank2_float"] = lambda: MoveCase("transpose", 211, ((9, 13), F32, 1.0, 0), [((13, 9), F32, 1.0, 0)], perm=(1, 0))
+    c["transpose_rank5"] = lambda: MoveCase("transpose", 212, ((2, 3, 4, 5, 6),) + q, [((6, 2, 5, 3, 4),) + q], perm=(4, 0, 3, 1, 2))
+    c["strided_slice_plain"] = lambda: MoveCase("strided_slice", 213, ((3, 8, 9, 4),) + q, [((2, 3, 4, 4),) + q],
+                                                begin=(1, 1, 0, 0), end=(3, 7, 8, 4), stride=(1, 2, 2, 1))
+    c["strided_slice_negative_stride_and_masks"] = lambda: MoveCase("strided_slice", 214, ((2, 6, 7, 5), U8, 0.2, 9), [((2, 6, 4, 2), U8, 0.2, 9)],
+                                                                    begin=(0, 0, -1, 1), end=(0, 0, 0, 5), stride=(1, -1, -2, 2),
+                                                                    begin_mask=0b0011, end_mask=0b0111)
+    c["strided_slice_shrink_axis"] = lambda: MoveCase("strided_slice", 215, ((4, 5, 6),) + q, [((5, 3),) + q],
+                                                      begin=(2, 0, 1), end=(3, 5, 6), stride=(1, 1, 2), shrink_axis_mask=0b001)
+    c["slice_block"] = lambda: MoveCase("slice", 216, ((2, 9, 8, 16),) + q, [((1, 4, 5, 16),) + q], begin=(1, 2, 3, 0), end=(1, 4, 5, 16))
+    c["slice_rank2_s32"] = lambda: MoveCase("slice", 217, ((7, 9), S32, 1.0, 0), [((3, 4), S32, 1.0, 0)], begin=(2, 5), end=(3, 4))
+    return c
+
+
 ALL_GROUPS = {"conv": conv_cases, "dwconv": dwconv_cases, "fc": fc_cases, "bmm": bmm_cases, "pool": pool_cases,
               "mean": mean_cases, "eltwise": eltwise_cases, "activation": activation_cases, "softmax": softmax_cases,
-              "convert": convert_cases, "pad": pad_cases, "qlstm": qlstm_cases}
+              "convert": convert_cases, "pad": pad_cases, "qlstm": qlstm_cases, "move": move_cases}
 
 
 def run_case(case, where):

@@ -403,6 +403,133 @@ class SimpleCase:
         return [mem.fetch(o) for o in outs]
 
 
+class OracleMoveParams(C.Structure):
+    """oracle/move_desc.h"""
+    _fields_ = [("kind", C.c_int32), ("rank", C.c_int32), ("whole", _abi.QTensor), ("whole_shape", C.c_int32 * 6),
+                ("n_views", C.c_int32), ("view", _abi.QTensor * 8), ("view_rank", C.c_int32 * 8), ("view_shape", (C.c_int32 * 6) * 8),
+                ("view_origin", (C.c_int32 * 6) * 8), ("perm", C.c_int32 * 6),
+                ("begin", C.c_int32 * 6), ("end", C.c_int32 * 6), ("stride", C.c_int32 * 6),
+                ("begin_mask", C.c_int32), ("end_mask", C.c_int32), ("shrink_axis_mask", C.c_int32)]
+
+
+MOVE_KINDS = {"concat": 0, "split": 1, "permute": 2, "transpose": 3, "strided_slice": 4, "slice": 5}
+
+
+class MoveCase:
+    """One data-movement layer stated as the reference's descriptor.  `whole` is the Concat output (then `parts` are the
+    inputs) or the input of every other kind (then `parts` are the outputs).  Tensors are (shape, dtype, scale, zp)."""
+
+    def __init__(self, kind, seed, whole, parts, origins=None, perm=None, begin=None, end=None, stride=None,
+                 begin_mask=0, end_mask=0, shrink_axis_mask=0):
+        self.kind, self.seed, self.whole, self.parts = kind, seed, whole, parts
+        self.origins, self.perm, self.begin, self.end, self.stride = origins, perm, begin, end, stride
+        self.masks = (begin_mask, end_mask, shrink_axis_mask)
+
+    def _data(self, mem):
+        """(whole tensor, part tensors, output handles) in `mem`, inputs filled with seeded values."""
+        rng = np.random.default_rng(self.seed)
+
+        def rand(shape, dtype):
+            if dtype == _abi.F32:
+                return rng.standard_normal(shape).astype(np.float32)
+            if dtype == _abi.S32:
+                return rng.integers(-100000, 100000, size=shape).astype(np.int32)
+            lo, hi = RANGE[dtype]
+            return rng.integers(lo, hi + 1, size=shape).astype(NP_OF[dtype])
+        outs = []
+        if self.kind == "concat":
+            parts = [qt(mem, rand(sh, dt), dt, sc, zp) for sh, dt, sc, zp in self.parts]
+            sh, dt, sc, zp = self.whole
+            whole, h = qt_out(mem, sh, dt, sc, zp)
+            outs.append(h)
+        else:
+            sh, dt, sc, zp = self.whole
+            whole = qt(mem, rand(sh, dt), dt, sc, zp)
+            parts = []
+            for sh, dt, sc, zp in self.parts:
+                t, h = qt_out(mem, sh, dt, sc, zp)
+                parts.append(t)
+                outs.append(h)
+        return whole, parts, outs
+
+    def _params(self, mem):
+        whole, parts, outs = self._data(mem)
+        p = OracleMoveParams()
+        p.kind, p.rank = MOVE_KINDS[self.kind], len(self.whole[0])
+        p.whole = whole
+        for i, n in enumerate(self.whole[0]):
+            p.whole_shape[i] = n
+        p.n_views = len(parts)
+        for v, t in enumerate(parts):
+            p.view[v] = t
+            p.view_rank[v] = len(self.parts[v][0])
+            for i, n in enumerate(self.parts[v][0]):
+                p.view_shape[v][i] = n
+            if self.origins is not None:
+                for i, o in enumerate(self.origins[v]):
+                    p.view_origin[v][i] = o
+        for name in ("perm", "begin", "end", "stride"):
+            vals = getattr(self, name)
+            if vals is not None:
+                for i, x in enumerate(vals):
+                    getattr(p, name)[i] = x
+        p.begin_mask, p.end_mask, p.shrink_axis_mask = self.masks
+        return p, outs
+
+    def run_oracle(self):
+        mem = Host()
+        p, outs = self._params(mem)
+        rc = oracle().oracle_move_q(C.byref(p))
+        assert rc == 0, "oracle_move_q returned %d" % rc
+        return outs
+
+    def run_cpuref(self):
+        mem = Host()
+        p, outs = self._params(mem)
+        rc = cpuref().cpuref_move_q(C.byref(p))
+        assert rc == 0, cpuref().cpuref_last_error().decode()
+        return outs
+
+    def views(self):
+        """[(view, source index, destination index)] with -1 for the whole tensor, else the index of the part."""
+        from armnn_b200 import views as V
+        shapes = [pt[0] for pt in self.parts]
+        if self.kind == "concat":
+            vs = V.concat_views(self.whole[0], shapes, self.origins)
+            order = list(reversed(range(len(shapes))))
+            return [(v, i, -1) for v, i in zip(vs, order)]
+        if self.kind == "split":
+            return [(v, -1, i) for i, v in enumerate(V.splitter_views(self.whole[0], shapes, self.origins))]
+        if self.kind in ("permute", "transpose"):
+            out_shape, v = V.permute_view(self.whole[0], self.perm, transpose=self.kind == "transpose")
+            assert tuple(out_shape) == tuple(shapes[0]), (out_shape, shapes[0])
+            return [(v, -1, 0)]
+        if self.kind == "strided_slice":
+            walk, out_shape, v = V.strided_slice_view(self.whole[0], self.begin, self.end, self.stride, *self.masks)
+            assert int(np.prod(walk)) == int(np.prod(shapes[0])), (walk, shapes[0])
+            return [(v, -1, 0)]
+        out_shape, v = V.slice_view(self.whole[0], self.begin, self.end)
+        assert tuple(out_shape) == tuple(shapes[0])
+        return [(v, -1, 0)]
+
+    def run_gpu(self):
+        from armnn_b200 import lib
+        from armnn_b200 import views as V
+        mem = Cuda()
+        whole, parts, outs = self._data(mem)
+        for view, si, di in self.views():
+            shape, so, ss, do, ds = V.merge_dims(view)
+            p = _abi.ViewCopyParams()
+            p.x = whole if si < 0 else parts[si]
+            p.y = whole if di < 0 else parts[di]
+            p.rank = len(shape)
+            for i in range(len(shape)):
+                p.shape[i], p.src_strides[i], p.dst_strides[i] = shape[i], ss[i], ds[i]
+            p.src_offset, p.dst_offset = so, do
+            lib.call("view_copy_q", p)
+        return [mem.fetch(o) for o in outs]
+
+
 def diff_stats(a, b):
     d = a.astype(np.int64) - b.astype(np.int64)
     return {"max_abs": int(np.abs(d).max()) if d.size else 0,
