@@ -154,6 +154,26 @@ class ArmnnNetwork:
             elif t == "Pad":
                 flat = [v for pair in d["pads"] for v in pair]
                 lid = lib.armnnc_add_pad(net, len(d["pads"]), (C.c_int32 * len(flat))(*flat), C.c_float(d["value"]))
+            elif t == "Concat":
+                flat = [x for o in d["origins"] for x in o]
+                lid = lib.armnnc_add_concat(net, len(d["origins"]), len(d["origins"][0]), (C.c_int32 * len(flat))(*flat))
+            elif t == "Splitter":
+                flat = [x for o in d["origins"] for x in o]
+                sizes = [x for o in layer.outputs for x in o.info.shape]
+                lid = lib.armnnc_add_splitter(net, len(d["origins"]), len(d["origins"][0]), (C.c_int32 * len(flat))(*flat),
+                                              (C.c_int32 * len(sizes))(*sizes))
+            elif t in ("Permute", "Transpose"):
+                m = d["mappings"]
+                lid = lib.armnnc_add_permute(net, len(m), (C.c_int32 * len(m))(*m), int(t == "Transpose"))
+                assert lid >= 0, lib.armnnc_last_error().decode()
+            elif t == "StridedSlice":
+                r = len(d["begin"])
+                arr = lambda v: (C.c_int32 * r)(*v)
+                lid = lib.armnnc_add_strided_slice(net, r, arr(d["begin"]), arr(d["end"]), arr(d["stride"]), d["begin_mask"],
+                                                   d["end_mask"], d["shrink_axis_mask"])
+            elif t == "Slice":
+                r = len(d["begin"])
+                lid = lib.armnnc_add_slice(net, r, (C.c_int32 * r)(*d["begin"]), (C.c_int32 * r)(*d["size"]))
             elif t == "Quantize":
                 lid = lib.armnnc_add_quantize(net)
             elif t == "Dequantize":

@@ -46,6 +46,12 @@ bool IsActType(const TensorInfo& t)
            t.GetDataType() == DataType::QSymmS16 || t.GetDataType() == DataType::Float32;
 }
 
+// element types the view copies move (Concat ... Slice): the activation types and Signed32
+bool IsMoveType(const TensorInfo& t)
+{
+    return IsActType(t) || t.GetDataType() == DataType::Signed32;
+}
+
 bool No(Optional<std::string&> reason, const char* why)
 {
     if (reason.has_value()) { reason.value() += std::string("B200Acc: ") + why + " "; }
@@ -120,6 +126,36 @@ public:
                 if (d.m_PaddingMode != PaddingMode::Constant) { return No(reason, "only constant padding is supported"); }
                 if (infos[0].GetNumDimensions() > 4) { return No(reason, "rank > 4"); }
                 return (IsActType(infos[0]) && IsActType(infos[1])) || No(reason, "unsupported data type");
+            }
+            case LayerType::Concat:
+            case LayerType::Splitter:
+            {
+                // RefLayerSupport.cpp:949-979 (Concat), :2597-2630 (Splitter): every tensor of the layer has one type;
+                // the quantisation parameters may differ (the copy re-quantises)
+                if (infos.empty() || infos[0].GetNumDimensions() > 6) { return No(reason, "rank > 6"); }
+                for (const TensorInfo& t : infos)
+                {
+                    if (!IsMoveType(t)) { return No(reason, "unsupported data type"); }
+                    if (t.GetDataType() != infos[0].GetDataType()) { return No(reason, "input and output types differ"); }
+                }
+                return true;
+            }
+            case LayerType::Permute:
+            case LayerType::Transpose:
+            case LayerType::Slice:
+            case LayerType::StridedSlice:
+            {
+                if (infos[0].GetNumDimensions() > 6) { return No(reason, "rank > 6"); }
+                if (!IsMoveType(infos[0]) || infos[0].GetDataType() != infos[1].GetDataType()) { return No(reason, "unsupported or mismatched data types"); }
+                if (infos[0].GetQuantizationScale() != infos[1].GetQuantizationScale() ||
+                    infos[0].GetQuantizationOffset() != infos[1].GetQuantizationOffset()) { return No(reason, "input and output quantisation differ (the reference copies raw elements)"); }
+                if (type == LayerType::StridedSlice)
+                {
+                    const auto& d = *PolymorphicDowncast<const StridedSliceDescriptor*>(&descriptor);
+                    if (d.m_EllipsisMask != 0 || d.m_NewAxisMask != 0) { return No(reason, "ellipsis and new-axis masks are not supported"); }
+                    if (infos[0].GetNumDimensions() > 4) { return No(reason, "rank > 4"); }
+                }
+                return true;
             }
             case LayerType::Mean:
             {

@@ -161,6 +161,200 @@ std::unique_ptr<IWorkload> Make(const QueueDescriptor& d, const WorkloadInfo& in
     return std::make_unique<B200Workload<QD>>(*PolymorphicDowncast<const QD*>(&d), info, ctx, std::move(fn), launchesEveryInference);
 }
 
+// ---- Concat, Splitter, Permute, Transpose, StridedSlice, Slice: rectangular view copies (b200k_view_copy_q) ----------
+// The descriptor arithmetic is the reference's (Concatenate.cpp:14-85, Splitter.cpp:18-93, src/armnnUtils/Permute.cpp,
+// Transpose.cpp, src/armnn/Descriptors.cpp:393-453 with workloads/StridedSlice.cpp:188-222, workloads/Slice.cpp:14-147);
+// armnn_b200/views.py states the same rules for the Python mirror.
+struct ViewOp
+{
+    b200k_view_copy_params p;
+    unsigned int src, dst;          // index of the workload's input / output tensor
+};
+
+struct ViewState
+{
+    explicit ViewState(const ContextPtr& ctx) : blobs(ctx) {}
+    std::vector<ViewOp> ops;
+    DeviceBlobs blobs;
+};
+
+void DenseStrides(const TensorShape& shape, int64_t* strides)
+{
+    int64_t st = 1;
+    for (unsigned int d = shape.GetNumDimensions(); d-- > 0;) { strides[d] = st; st *= shape[d]; }
+}
+
+ViewOp NewViewOp(const TensorInfo& x, const TensorInfo& y, DeviceBlobs& blobs, unsigned int src, unsigned int dst, unsigned int rank)
+{
+    if (rank < 1 || rank > 6) { throw InvalidArgumentException("B200Acc: view copies need a rank between 1 and 6"); }
+    ViewOp op;
+    std::memset(&op, 0, sizeof(op));
+    op.p.x = Operand(x, blobs); op.p.y = Operand(y, blobs);
+    op.p.rank = static_cast<int32_t>(rank);
+    op.src = src; op.dst = dst;
+    return op;
+}
+
+template <typename QD>
+std::unique_ptr<IWorkload> MakeViews(const QueueDescriptor& d, const WorkloadInfo& info, const ContextPtr& ctx, std::shared_ptr<ViewState> st)
+{
+    return Make<QD>(d, info, ctx, [st](const QD& data, cudaStream_t s)
+    {
+        for (ViewOp& op : st->ops)
+        {
+            op.p.x.data = Dev(data.m_Inputs[op.src]); op.p.y.data = Dev(data.m_Outputs[op.dst]);
+            B200CheckStatus(b200k_view_copy_q(&op.p, s));
+        }
+    });
+}
+
+// Concat: input v (dense) -> the block of the output at its view origin.  Where views overlap the reference lets the
+// first one win, so the copies are issued last view first.
+std::unique_ptr<IWorkload> MakeConcat(const QueueDescriptor& d, const WorkloadInfo& info, const ContextPtr& ctx)
+{
+    const auto& qd = *PolymorphicDowncast<const ConcatQueueDescriptor*>(&d);
+    auto st = std::make_shared<ViewState>(ctx);
+    const TensorInfo& out = info.m_OutputTensorInfos[0];
+    const unsigned int rank = out.GetNumDimensions();
+    int64_t os[6];
+    DenseStrides(out.GetShape(), os);
+    for (size_t v = qd.m_ViewOrigins.size(); v-- > 0;)
+    {
+        const TensorInfo& in = info.m_InputTensorInfos[v];
+        if (in.GetNumDimensions() != rank || qd.m_ViewOrigins[v].m_Origin.size() != rank) { throw InvalidArgumentException("B200Acc: Concat views must have the output's rank"); }
+        ViewOp op = NewViewOp(in, out, st->blobs, static_cast<unsigned int>(v), 0, rank);
+        DenseStrides(in.GetShape(), op.p.src_strides);
+        for (unsigned int i = 0; i < rank; ++i)
+        {
+            const unsigned int o = qd.m_ViewOrigins[v].m_Origin[i];
+            if (o + in.GetShape()[i] > out.GetShape()[i]) { throw InvalidArgumentException("B200Acc: Concat view outside the output"); }
+            op.p.shape[i] = static_cast<int32_t>(in.GetShape()[i]);
+            op.p.dst_strides[i] = os[i];
+            op.p.dst_offset += static_cast<int64_t>(o) * os[i];
+        }
+        st->ops.push_back(op);
+    }
+    return MakeViews<ConcatQueueDescriptor>(d, info, ctx, st);
+}
+
+// Splitter: the block of the input at view v's origin -> output v (dense).
+std::unique_ptr<IWorkload> MakeSplitter(const QueueDescriptor& d, const WorkloadInfo& info, const ContextPtr& ctx)
+{
+    const auto& qd = *PolymorphicDowncast<const SplitterQueueDescriptor*>(&d);
+    auto st = std::make_shared<ViewState>(ctx);
+    const TensorInfo& in = info.m_InputTensorInfos[0];
+    const unsigned int rank = in.GetNumDimensions();
+    int64_t is[6];
+    DenseStrides(in.GetShape(), is);
+    for (size_t v = 0; v < qd.m_ViewOrigins.size(); ++v)
+    {
+        const TensorInfo& out = info.m_OutputTensorInfos[v];
+        if (out.GetNumDimensions() != rank || qd.m_ViewOrigins[v].m_Origin.size() != rank) { throw InvalidArgumentException("B200Acc: Splitter views must have the input's rank"); }
+        ViewOp op = NewViewOp(in, out, st->blobs, 0, static_cast<unsigned int>(v), rank);
+        DenseStrides(out.GetShape(), op.p.dst_strides);
+        for (unsigned int i = 0; i < rank; ++i)
+        {
+            const unsigned int o = qd.m_ViewOrigins[v].m_Origin[i];
+            if (o + out.GetShape()[i] > in.GetShape()[i]) { throw InvalidArgumentException("B200Acc: Splitter view outside the input"); }
+            op.p.shape[i] = static_cast<int32_t>(out.GetShape()[i]);
+            op.p.src_strides[i] = is[i];
+            op.p.src_offset += static_cast<int64_t>(o) * is[i];
+        }
+        st->ops.push_back(op);
+    }
+    return MakeViews<SplitterQueueDescriptor>(d, info, ctx, st);
+}
+
+// Permute (mappings[i]: destination dimension of source dimension i) and Transpose (mappings[i]: source dimension of
+// destination dimension i): the source strides in the destination's order of dimensions.
+template <typename QD>
+std::unique_ptr<IWorkload> MakePermute(const QueueDescriptor& d, const WorkloadInfo& info, const ContextPtr& ctx, bool transpose)
+{
+    const auto& qd = *PolymorphicDowncast<const QD*>(&d);
+    const PermutationVector& m = qd.m_Parameters.m_DimMappings;
+    auto st = std::make_shared<ViewState>(ctx);
+    const TensorInfo& in = info.m_InputTensorInfos[0];
+    const TensorInfo& out = info.m_OutputTensorInfos[0];
+    const unsigned int rank = in.GetNumDimensions();
+    if (m.GetSize() != rank || out.GetNumDimensions() != rank) { throw InvalidArgumentException("B200Acc: permutation and tensor ranks differ"); }
+    int64_t is[6];
+    DenseStrides(in.GetShape(), is);
+    ViewOp op = NewViewOp(in, out, st->blobs, 0, 0, rank);
+    DenseStrides(out.GetShape(), op.p.dst_strides);
+    unsigned int srcOfDst[6] = {0, 0, 0, 0, 0, 0};
+    for (unsigned int i = 0; i < rank; ++i)
+    {
+        if (transpose) { srcOfDst[i] = m[i]; } else { srcOfDst[m[i]] = i; }
+    }
+    for (unsigned int j = 0; j < rank; ++j)
+    {
+        if (out.GetShape()[j] != in.GetShape()[srcOfDst[j]]) { throw InvalidArgumentException("B200Acc: output shape is not the permuted input shape"); }
+        op.p.shape[j] = static_cast<int32_t>(out.GetShape()[j]);
+        op.p.src_strides[j] = is[srcOfDst[j]];
+    }
+    st->ops.push_back(op);
+    return MakeViews<QD>(d, info, ctx, st);
+}
+
+// StridedSlice with begin / end / shrink-axis masks (layer support refuses ellipsis and new-axis masks).
+std::unique_ptr<IWorkload> MakeStridedSlice(const QueueDescriptor& d, const WorkloadInfo& info, const ContextPtr& ctx)
+{
+    const auto& qd = *PolymorphicDowncast<const StridedSliceQueueDescriptor*>(&d);
+    const StridedSliceDescriptor& prm = qd.m_Parameters;
+    auto st = std::make_shared<ViewState>(ctx);
+    const TensorInfo& in = info.m_InputTensorInfos[0];
+    const TensorInfo& out = info.m_OutputTensorInfos[0];
+    const unsigned int rank = in.GetNumDimensions();
+    if (prm.m_Begin.size() != rank || prm.m_End.size() != rank || prm.m_Stride.size() != rank) { throw InvalidArgumentException("B200Acc: StridedSlice needs begin / end / stride per input dimension"); }
+    int64_t is[6];
+    DenseStrides(in.GetShape(), is);
+    ViewOp op = NewViewOp(in, out, st->blobs, 0, 0, rank);
+    int64_t count = 1;
+    for (unsigned int i = 0; i < rank; ++i)
+    {
+        const int stride = prm.m_Stride[i];
+        if (stride == 0) { throw InvalidArgumentException("B200Acc: StridedSlice stride 0"); }
+        const int start = prm.GetStartForAxis(in.GetShape(), i);
+        const int stop = prm.GetStopForAxis(in.GetShape(), i, start);
+        int n = 0;
+        if (stride > 0 && stop > start) { n = (stop - start + stride - 1) / stride; }
+        if (stride < 0 && stop < start) { n = (start - stop - stride - 1) / (-stride); }
+        op.p.shape[i] = n;
+        op.p.src_strides[i] = is[i] * stride;
+        op.p.src_offset += static_cast<int64_t>(start) * is[i];
+        count *= n;
+    }
+    if (static_cast<unsigned int>(count) != out.GetNumElements()) { throw InvalidArgumentException("B200Acc: StridedSlice output shape does not match the slice"); }
+    int64_t st1 = 1;
+    for (unsigned int i = rank; i-- > 0;) { op.p.dst_strides[i] = st1; st1 *= op.p.shape[i]; }
+    st->ops.push_back(op);
+    return MakeViews<StridedSliceQueueDescriptor>(d, info, ctx, st);
+}
+
+std::unique_ptr<IWorkload> MakeSlice(const QueueDescriptor& d, const WorkloadInfo& info, const ContextPtr& ctx)
+{
+    const auto& qd = *PolymorphicDowncast<const SliceQueueDescriptor*>(&d);
+    auto st = std::make_shared<ViewState>(ctx);
+    const TensorInfo& in = info.m_InputTensorInfos[0];
+    const TensorInfo& out = info.m_OutputTensorInfos[0];
+    const unsigned int rank = in.GetNumDimensions();
+    if (qd.m_Parameters.m_Begin.size() != rank || qd.m_Parameters.m_Size.size() != rank || out.GetNumDimensions() != rank) { throw InvalidArgumentException("B200Acc: Slice needs begin / size per input dimension"); }
+    int64_t is[6];
+    DenseStrides(in.GetShape(), is);
+    ViewOp op = NewViewOp(in, out, st->blobs, 0, 0, rank);
+    DenseStrides(out.GetShape(), op.p.dst_strides);
+    for (unsigned int i = 0; i < rank; ++i)
+    {
+        const unsigned int b = qd.m_Parameters.m_Begin[i], n = qd.m_Parameters.m_Size[i];
+        if (b + n > in.GetShape()[i] || n != out.GetShape()[i]) { throw InvalidArgumentException("B200Acc: Slice block outside the input"); }
+        op.p.shape[i] = static_cast<int32_t>(n);
+        op.p.src_strides[i] = is[i];
+        op.p.src_offset += static_cast<int64_t>(b) * is[i];
+    }
+    st->ops.push_back(op);
+    return MakeViews<SliceQueueDescriptor>(d, info, ctx, st);
+}
+
 struct ConvState
 {
     explicit ConvState(const ContextPtr& ctx) : blobs(ctx) {}
@@ -665,6 +859,12 @@ std::unique_ptr<IWorkload> B200WorkloadFactory::CreateWorkload(LayerType type, c
                 B200CheckStatus(b200k_pad_q(&st->p, s));
             });
         }
+        case LayerType::Concat:       return MakeConcat(d, info, ctx);
+        case LayerType::Splitter:     return MakeSplitter(d, info, ctx);
+        case LayerType::Permute:      return MakePermute<PermuteQueueDescriptor>(d, info, ctx, false);
+        case LayerType::Transpose:    return MakePermute<TransposeQueueDescriptor>(d, info, ctx, true);
+        case LayerType::StridedSlice: return MakeStridedSlice(d, info, ctx);
+        case LayerType::Slice:        return MakeSlice(d, info, ctx);
         case LayerType::QLstm:
             return MakeQLstm(d, info, ctx);
         case LayerType::PreCompiled:

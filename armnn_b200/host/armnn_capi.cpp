@@ -316,6 +316,62 @@ int armnnc_add_pad(void* vn, int rank, const int32_t* pads, float pad_value)
     return add_layer(n, n->net->AddPadLayer(d));
 }
 
+// origins: n_views x rank coordinates of each input's block in the output
+int armnnc_add_concat(void* vn, int n_views, int rank, const int32_t* origins)
+{
+    auto* n = static_cast<CNet*>(vn);
+    OriginsDescriptor d((uint32_t)n_views, (uint32_t)rank);
+    for (int v = 0; v < n_views; ++v)
+        for (int i = 0; i < rank; ++i) d.SetViewOriginCoord((uint32_t)v, (uint32_t)i, (uint32_t)origins[v * rank + i]);
+    return add_layer(n, n->net->AddConcatLayer(d));
+}
+
+// origins / sizes: n_views x rank
+int armnnc_add_splitter(void* vn, int n_views, int rank, const int32_t* origins, const int32_t* sizes)
+{
+    auto* n = static_cast<CNet*>(vn);
+    ViewsDescriptor d((uint32_t)n_views, (uint32_t)rank);
+    for (int v = 0; v < n_views; ++v)
+        for (int i = 0; i < rank; ++i) {
+            d.SetViewOriginCoord((uint32_t)v, (uint32_t)i, (uint32_t)origins[v * rank + i]);
+            d.SetViewSize((uint32_t)v, (uint32_t)i, (uint32_t)sizes[v * rank + i]);
+        }
+    return add_layer(n, n->net->AddSplitterLayer(d));
+}
+
+int armnnc_add_permute(void* vn, int rank, const int32_t* mappings, int transpose)
+{
+    auto* n = static_cast<CNet*>(vn);
+    unsigned m[6] = {0, 0, 0, 0, 0, 0};
+    for (int i = 0; i < rank && i < 6; ++i) m[i] = (unsigned)mappings[i];
+    try {
+        const PermutationVector pv(m, (unsigned)rank);
+        if (transpose) return add_layer(n, n->net->AddTransposeLayer(TransposeDescriptor(pv)));
+        return add_layer(n, n->net->AddPermuteLayer(PermuteDescriptor(pv)));
+    } catch (const std::exception& e) { g_err = e.what(); return -1; }
+}
+
+int armnnc_add_strided_slice(void* vn, int rank, const int32_t* begin, const int32_t* end, const int32_t* stride,
+                             int begin_mask, int end_mask, int shrink_axis_mask)
+{
+    auto* n = static_cast<CNet*>(vn);
+    StridedSliceDescriptor d;
+    d.m_Begin.assign(begin, begin + rank);
+    d.m_End.assign(end, end + rank);
+    d.m_Stride.assign(stride, stride + rank);
+    d.m_BeginMask = begin_mask; d.m_EndMask = end_mask; d.m_ShrinkAxisMask = shrink_axis_mask;
+    return add_layer(n, n->net->AddStridedSliceLayer(d));
+}
+
+int armnnc_add_slice(void* vn, int rank, const int32_t* begin, const int32_t* size)
+{
+    auto* n = static_cast<CNet*>(vn);
+    SliceDescriptor d;
+    d.m_Begin.assign(begin, begin + rank);
+    d.m_Size.assign(size, size + rank);
+    return add_layer(n, n->net->AddSliceLayer(d));
+}
+
 int armnnc_add_quantize(void* vn)   { auto* n = static_cast<CNet*>(vn); return add_layer(n, n->net->AddQuantizeLayer()); }
 int armnnc_add_dequantize(void* vn) { auto* n = static_cast<CNet*>(vn); return add_layer(n, n->net->AddDequantizeLayer()); }
 

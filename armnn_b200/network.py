@@ -19,7 +19,7 @@ from enum import IntEnum
 
 import numpy as np
 
-from . import _abi, lib
+from . import _abi, lib, views
 
 
 class DataType(IntEnum):            # include/armnn/Types.hpp:48-60
@@ -228,6 +228,34 @@ class INetwork:
         armnn::Pad takes it (src/backends/reference/workloads/Pad.cpp:76-83)."""
         return self._add(Layer("Pad", name, 1, 1, {"pads": tuple((int(a), int(b)) for a, b in pad_list), "value": float(pad_value)}))
 
+    def AddConcatLayer(self, view_origins, name=None):
+        """view_origins: per input, the coordinates of its block in the output (armnn::OriginsDescriptor)."""
+        origins = tuple(tuple(int(x) for x in o) for o in view_origins)
+        return self._add(Layer("Concat", name, len(origins), 1, {"origins": origins}))
+
+    def AddSplitterLayer(self, view_origins, name=None):
+        """view_origins: per output, the coordinates of its block in the input (armnn::ViewsDescriptor); the view sizes
+        are the outputs' shapes."""
+        origins = tuple(tuple(int(x) for x in o) for o in view_origins)
+        return self._add(Layer("Splitter", name, 1, len(origins), {"origins": origins}))
+
+    def AddPermuteLayer(self, dim_mappings, name=None):
+        """dim_mappings[i]: the destination dimension of source dimension i (armnn::PermuteDescriptor)."""
+        return self._add(Layer("Permute", name, 1, 1, {"mappings": tuple(int(x) for x in dim_mappings)}))
+
+    def AddTransposeLayer(self, dim_mappings, name=None):
+        """dim_mappings[i]: the source dimension of destination dimension i (armnn::TransposeDescriptor)."""
+        return self._add(Layer("Transpose", name, 1, 1, {"mappings": tuple(int(x) for x in dim_mappings)}))
+
+    def AddStridedSliceLayer(self, begin, end, stride, begin_mask=0, end_mask=0, shrink_axis_mask=0, name=None):
+        """armnn::StridedSliceDescriptor without ellipsis and new-axis masks."""
+        return self._add(Layer("StridedSlice", name, 1, 1, {"begin": tuple(int(x) for x in begin), "end": tuple(int(x) for x in end),
+                                                            "stride": tuple(int(x) for x in stride), "begin_mask": int(begin_mask),
+                                                            "end_mask": int(end_mask), "shrink_axis_mask": int(shrink_axis_mask)}))
+
+    def AddSliceLayer(self, begin, size, name=None):
+        return self._add(Layer("Slice", name, 1, 1, {"begin": tuple(int(x) for x in begin), "size": tuple(int(x) for x in size)}))
+
     def AddQuantizeLayer(self, name=None):
         return self._add(Layer("Quantize", name, 1, 1))
 
@@ -301,6 +329,17 @@ def IsLayerSupported(layer):
     if t == "Pad":
         if len(ins[0].shape) > 4:
             return False, "Pad: rank > 4"
+        return True, ""
+    if t in ("Concat", "Splitter"):
+        # RefLayerSupport.cpp:949-979, 2597-2630: one element type for every tensor; quantisation may differ
+        if len(ins[0].shape) > 6 or any(i.dtype != ins[0].dtype for i in list(ins) + list(outs)):
+            return False, "%s: rank > 6 or mismatched data types" % t
+        return True, ""
+    if t in ("Permute", "Transpose", "StridedSlice", "Slice"):
+        if len(ins[0].shape) > (4 if t == "StridedSlice" else 6):
+            return False, "%s: rank not supported" % t
+        if ins[0].dtype != outs[0].dtype or not outs[0].same_quantization(ins[0]):
+            return False, "%s: input and output must share type and quantisation (the reference copies raw elements)" % t
         return True, ""
     if t == "QLstm":
         if ins[0].dtype != DataType.QAsymmS8 or ins[2].dtype != DataType.QSymmS16:
@@ -524,7 +563,9 @@ class GraphProgram:
                 continue
             for o in layer.outputs:
                 self.tensors[id(o)] = self._alloc(o.info)
-            self.workloads.append((layer,) + getattr(self, "_make_" + t)(layer))
+            made = getattr(self, "_make_" + t)(layer)
+            for entry_and_params in (made if isinstance(made, list) else [made]):
+                self.workloads.append((layer,) + entry_and_params)
 
     def _conv_params(self, layer, depthwise):
         x, w = layer.inputs[0].source, layer.inputs[1].source
@@ -664,6 +705,56 @@ class GraphProgram:
             p.shape[i], p.pad_before[i], p.pad_after[i] = x.info.shape[i], before, after
         p.pad_value = layer.desc["value"]
         return "pad_q", p
+
+    # -- Concat, Splitter, Permute, Transpose, StridedSlice, Slice: rectangular view copies (armnn_b200/views.py) --
+    def _view_copy(self, x, y, view):
+        shape, so, ss, do, ds = views.merge_dims(view)
+        p = _abi.ViewCopyParams()
+        p.x, p.y = self._operand(x), self._operand(y)
+        p.rank = len(shape)
+        for i in range(len(shape)):
+            p.shape[i], p.src_strides[i], p.dst_strides[i] = shape[i], ss[i], ds[i]
+        p.src_offset, p.dst_offset = so, do
+        return "view_copy_q", p
+
+    def _make_Concat(self, layer):
+        y = layer.outputs[0]
+        srcs = [s.source for s in layer.inputs]
+        vs = views.concat_views(y.info.shape, [x.info.shape for x in srcs], layer.desc["origins"])
+        return [self._view_copy(x, y, v) for x, v in zip(reversed(srcs), vs)]
+
+    def _make_Splitter(self, layer):
+        x = layer.inputs[0].source
+        vs = views.splitter_views(x.info.shape, [o.info.shape for o in layer.outputs], layer.desc["origins"])
+        return [self._view_copy(x, o, v) for o, v in zip(layer.outputs, vs)]
+
+    def _make_permute(self, layer, transpose):
+        x, y = layer.inputs[0].source, layer.outputs[0]
+        out_shape, v = views.permute_view(x.info.shape, layer.desc["mappings"], transpose)
+        if tuple(out_shape) != tuple(y.info.shape):
+            raise InvalidArgumentException("%s: output shape %s is not the permuted input shape %s" % (layer.type, y.info.shape, out_shape))
+        return self._view_copy(x, y, v)
+
+    def _make_Permute(self, layer):
+        return self._make_permute(layer, False)
+
+    def _make_Transpose(self, layer):
+        return self._make_permute(layer, True)
+
+    def _make_StridedSlice(self, layer):
+        x, y, d = layer.inputs[0].source, layer.outputs[0], layer.desc
+        walk, out_shape, v = views.strided_slice_view(x.info.shape, d["begin"], d["end"], d["stride"], d["begin_mask"], d["end_mask"],
+                                                      d["shrink_axis_mask"])
+        if y.info.GetNumElements() != int(np.prod(walk)):
+            raise InvalidArgumentException("StridedSlice: output shape %s does not hold the slice %s" % (y.info.shape, walk))
+        return self._view_copy(x, y, v)
+
+    def _make_Slice(self, layer):
+        x, y = layer.inputs[0].source, layer.outputs[0]
+        out_shape, v = views.slice_view(x.info.shape, layer.desc["begin"], layer.desc["size"])
+        if tuple(out_shape) != tuple(y.info.shape):
+            raise InvalidArgumentException("Slice: output shape %s is not the block %s" % (y.info.shape, out_shape))
+        return self._view_copy(x, y, v)
 
     def _make_QLstm(self, layer):
         x, h, c = (s.source for s in layer.inputs)

@@ -632,6 +632,26 @@ static int move_slice(const oracle_move_params* p)
     return 0;
 }
 
+/* The view copy of include/b200k.h as the graph-level oracle executor calls it: element by element through
+ * Decoder / Encoder when the quantisation differs, raw elements otherwise. */
+int oracle_view_copy_q(const b200k_view_copy_params* p)
+{
+    if (!p || !p->x.data || !p->y.data || p->rank < 1 || p->rank > 6 || p->x.dtype != p->y.dtype) return B200K_E_INVALID;
+    const int quantised = p->x.dtype == B200K_U8 || p->x.dtype == B200K_S8 || p->x.dtype == B200K_S16;
+    const int same = !quantised || (p->x.scale == p->y.scale && p->x.zero_point == p->y.zero_point);
+    const size_t es = esize(p->x.dtype);
+    const int64_t n = elems(p->shape, p->rank);
+    for (int64_t i = 0; i < n; ++i) {
+        int32_t c[6];
+        coords_of(i, p->shape, p->rank, c);
+        int64_t s = p->src_offset, d = p->dst_offset;
+        for (int k = 0; k < p->rank; ++k) { s += c[k] * p->src_strides[k]; d += c[k] * p->dst_strides[k]; }
+        if (same) memcpy((uint8_t*)p->y.data + (size_t)d * es, (const uint8_t*)p->x.data + (size_t)s * es, es);
+        else      store_f(&p->y, d, load_f(&p->x, s));
+    }
+    return 0;
+}
+
 int oracle_move_q(const oracle_move_params* p)
 {
     if (!p || p->rank < 1 || p->rank > 6 || !p->whole.data || p->n_views < 1 || p->n_views > 8) return B200K_E_INVALID;

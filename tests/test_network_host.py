@@ -121,3 +121,20 @@ def test_qlstm_stack_three_steps_oracle_vs_armnn_cpuref(built):
         for k in want:
             assert np.array_equal(want[k], got[k]), (step, k)
         state = {k: want[k] for k in state}
+
+
+@needs_cpuref
+def test_data_movement_graph_mirror_views_vs_armnn_cpuref(built):
+    """Splitter, Transpose, Permute, StridedSlice, Slice and a re-quantising Concat in one graph: the views the Python
+    mirror derives from the descriptors (armnn_b200/views.py), executed by the oracle, against the real runtime on
+    CpuRef.  Copies and fp32-faithful re-quantisation: identical bytes."""
+    import hostnet
+    from test_plugin import _data_movement_net
+    net, info = _data_movement_net()
+    x = np.random.default_rng(12).integers(-128, 128, size=info["input_shape"]).astype(np.int8)
+    want = hostnet.ArmnnNetwork(net, "CpuRef").run({0: x})
+    got = hostnet.OracleNetwork(Optimize(net)).run({0: x})
+    assert sorted(want) == sorted(got) == [0, 1]
+    for k in want:
+        assert want[k].shape == got[k].shape and np.array_equal(want[k], got[k]), k
+    assert np.array_equal(got[1], x[..., :16])

@@ -390,3 +390,87 @@ def test_device_id_model_option_selects_the_gpu_per_network():
     for t in threads:
         t.join()
     assert np.array_equal(results["a"], want) and np.array_equal(results["b"], want)
+
+
+def _data_movement_net(batch=2):
+    """Splitter (channels) -> [Transpose to NCHW and back | StridedSlice + Slice path] -> Concat with re-quantisation:
+    every data-movement layer of the view-copy kernel in one graph, two outputs."""
+    from armnn_b200.network import DataType, INetwork, TensorInfo
+    net = INetwork.Create()
+    q = dict(dtype=DataType.QAsymmS8, scale=0.05, offset=-3)
+
+    def info(shape, scale=0.05, offset=-3):
+        return TensorInfo(tuple(shape), DataType.QAsymmS8, scale, offset)
+    il = net.AddInputLayer(0, "input")
+    il.GetOutputSlot(0).SetTensorInfo(info((batch, 8, 6, 48)))
+    sp = net.AddSplitterLayer([(0, 0, 0, 0), (0, 0, 0, 16)], "split")
+    il.GetOutputSlot(0).Connect(sp.GetInputSlot(0))
+    sp.GetOutputSlot(0).SetTensorInfo(info((batch, 8, 6, 16)))
+    sp.GetOutputSlot(1).SetTensorInfo(info((batch, 8, 6, 32), 0.07, 4))          # a view with its own quantisation
+    # branch a: NHWC -> NCHW (Transpose) -> NHWC (Permute)
+    tr = net.AddTransposeLayer((0, 3, 1, 2), "to_nchw")
+    sp.GetOutputSlot(0).Connect(tr.GetInputSlot(0))
+    tr.GetOutputSlot(0).SetTensorInfo(info((batch, 16, 8, 6)))
+    pm = net.AddPermuteLayer((0, 3, 1, 2), "to_nhwc")                             # source dim 1 (C) -> destination dim 3
+    tr.GetOutputSlot(0).Connect(pm.GetInputSlot(0))
+    pm.GetOutputSlot(0).SetTensorInfo(info((batch, 8, 6, 16)))
+    # branch b: every second row, reversed columns (StridedSlice), then a block of it (Slice)
+    ss = net.AddStridedSliceLayer((0, 0, -1, 0), (0, 8, 0, 32), (1, 2, -1, 1), begin_mask=0b0001, end_mask=0b0101, name="strided")
+    sp.GetOutputSlot(1).Connect(ss.GetInputSlot(0))
+    ss.GetOutputSlot(0).SetTensorInfo(info((batch, 4, 6, 32), 0.07, 4))
+    sl = net.AddSliceLayer((0, 1, 2, 8), (batch, 3, 4, 16), "slice")
+    ss.GetOutputSlot(0).Connect(sl.GetInputSlot(0))
+    sl.GetOutputSlot(0).SetTensorInfo(info((batch, 3, 4, 16), 0.07, 4))
+    # Concat along H of a Slice of branch a with branch b: inputs with different quantisation -> re-quantised
+    sa = net.AddSliceLayer((0, 0, 1, 0), (batch, 2, 4, 16), "slice_a")
+    pm.GetOutputSlot(0).Connect(sa.GetInputSlot(0))
+    sa.GetOutputSlot(0).SetTensorInfo(info((batch, 2, 4, 16)))
+    cc = net.AddConcatLayer([(0, 0, 0, 0), (0, 2, 0, 0)], "concat")
+    sa.GetOutputSlot(0).Connect(cc.GetInputSlot(0))
+    sl.GetOutputSlot(0).Connect(cc.GetInputSlot(1))
+    cc.GetOutputSlot(0).SetTensorInfo(info((batch, 5, 4, 16), 0.06, 1))
+    o0 = net.AddOutputLayer(0, "out_concat")
+    cc.GetOutputSlot(0).Connect(o0.GetInputSlot(0))
+    o1 = net.AddOutputLayer(1, "out_nhwc")
+    pm.GetOutputSlot(0).Connect(o1.GetInputSlot(0))
+    return net, {"input_shape": (batch, 8, 6, 48)}
+
+
+@needs_plugin
+@pytest.mark.gpu
+def test_data_movement_layers_through_the_runtime_match_cpuref_and_the_python_mirror():
+    """Concat, Splitter, Permute, Transpose, StridedSlice and Slice: the plugin's view workloads inside the real runtime
+    against CpuRef on the same graph (bit-exact: copies and fp32-faithful re-quantisation), and the Python mirror."""
+    from armnn_b200 import network
+    net, info = _data_movement_net()
+    x = np.random.default_rng(11).integers(-128, 128, size=info["input_shape"]).astype(np.int8)
+    ref = hostnet.ArmnnNetwork(net, "CpuRef").run({0: x})
+    got = hostnet.ArmnnNetwork(net, "B200Acc").run({0: x})
+    assert sorted(ref) == sorted(got) == [0, 1]
+    for k in ref:
+        assert ref[k].shape == got[k].shape and np.array_equal(ref[k], got[k]), k
+    # Transpose to NCHW followed by Permute back is the identity on the first 16 channels
+    assert np.array_equal(got[1], x[..., :16])
+    rt = network.IRuntime.Create(0)
+    ln = rt.GetLoadedNetwork(rt.LoadNetwork(network.Optimize(net)))
+    ys = {0: np.zeros(ref[0].shape, np.int8), 1: np.zeros(ref[1].shape, np.int8)}
+    ln.EnqueueWorkload({0: x}, ys)
+    assert np.array_equal(ys[0], ref[0]) and np.array_equal(ys[1], ref[1])
+
+
+@needs_plugin
+def test_transpose_that_changes_the_quantisation_is_refused_by_layer_support():
+    """The reference's Transpose copies raw elements (src/armnnUtils/Transpose.cpp:22-117): B200Acc refuses a layer whose
+    output claims another quantisation instead of silently re-quantising."""
+    from armnn_b200.network import DataType, INetwork, TensorInfo
+    net = INetwork.Create()
+    il = net.AddInputLayer(0, "input")
+    t = TensorInfo((2, 4, 4, 8), DataType.QAsymmS8, 0.05, 0)
+    il.GetOutputSlot(0).SetTensorInfo(t)
+    tr = net.AddTransposeLayer((0, 2, 1, 3), "swap_h_w")
+    il.GetOutputSlot(0).Connect(tr.GetInputSlot(0))
+    tr.GetOutputSlot(0).SetTensorInfo(TensorInfo((2, 4, 4, 8), DataType.QAsymmS8, 0.07, 0))       # quantisation changes: refused
+    ol = net.AddOutputLayer(0, "output")
+    tr.GetOutputSlot(0).Connect(ol.GetInputSlot(0))
+    with pytest.raises(Exception):
+        hostnet.ArmnnNetwork(net, "B200Acc", optimize_only=True)
