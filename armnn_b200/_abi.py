@@ -90,6 +90,12 @@ class ViewCopyParams(C.Structure):
                 ("src_offset", C.c_int64), ("dst_offset", C.c_int64)]
 
 
+class ResizeParams(C.Structure):
+    _fields_ = [("x", QTensor), ("y", QTensor), ("n", C.c_int32), ("c", C.c_int32), ("in_h", C.c_int32), ("in_w", C.c_int32),
+                ("out_h", C.c_int32), ("out_w", C.c_int32), ("method", C.c_int32), ("align_corners", C.c_int32),
+                ("half_pixel_centers", C.c_int32), ("nchw", C.c_int32)]
+
+
 _P, _F, _I = C.c_void_p, C.c_float, C.c_int32
 
 
@@ -135,6 +141,7 @@ KERNEL_ENTRY_POINTS = {
     "qlstm_step": QLstmParams,
     "pad_q": PadParams,
     "view_copy_q": ViewCopyParams,
+    "resize_q": ResizeParams,
 }
 
 # every symbol include/b200k.h declares

@@ -127,6 +127,14 @@ public:
                 if (infos[0].GetNumDimensions() > 4) { return No(reason, "rank > 4"); }
                 return (IsActType(infos[0]) && IsActType(infos[1])) || No(reason, "unsupported data type");
             }
+            case LayerType::Resize:
+            {
+                const auto& d = *PolymorphicDowncast<const ResizeDescriptor*>(&descriptor);
+                if (d.m_AlignCorners && d.m_HalfPixelCenters) { return No(reason, "align corners and half pixel centres cannot both be set"); }
+                if (infos[0].GetNumDimensions() != 4 || infos[1].GetNumDimensions() != 4) { return No(reason, "Resize needs 4-D tensors"); }
+                if (!IsActType(infos[0]) || infos[0].GetDataType() != infos[1].GetDataType()) { return No(reason, "unsupported or mismatched data types"); }
+                return true;
+            }
             case LayerType::Concat:
             case LayerType::Splitter:
             {

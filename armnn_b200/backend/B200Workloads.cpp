@@ -859,6 +859,30 @@ std::unique_ptr<IWorkload> B200WorkloadFactory::CreateWorkload(LayerType type, c
                 B200CheckStatus(b200k_pad_q(&st->p, s));
             });
         }
+        case LayerType::Resize:
+        {
+            const auto& qd = *PolymorphicDowncast<const ResizeQueueDescriptor*>(&d);
+            auto st = std::make_shared<SimpleState<b200k_resize_params>>(ctx);
+            b200k_resize_params& p = st->p;
+            std::memset(&p, 0, sizeof(p));
+            const TensorInfo& x = info.m_InputTensorInfos[0];
+            const TensorInfo& y = info.m_OutputTensorInfos[0];
+            p.x = Operand(x, st->blobs); p.y = Operand(y, st->blobs);
+            const bool nchw = qd.m_Parameters.m_DataLayout == DataLayout::NCHW;
+            const unsigned int hi = nchw ? 2 : 1, wi = nchw ? 3 : 2, ci = nchw ? 1 : 3;
+            p.n = static_cast<int32_t>(x.GetShape()[0]); p.c = static_cast<int32_t>(x.GetShape()[ci]);
+            p.in_h = static_cast<int32_t>(x.GetShape()[hi]); p.in_w = static_cast<int32_t>(x.GetShape()[wi]);
+            p.out_h = static_cast<int32_t>(y.GetShape()[hi]); p.out_w = static_cast<int32_t>(y.GetShape()[wi]);
+            p.method = qd.m_Parameters.m_Method == ResizeMethod::Bilinear ? 0 : 1;
+            p.align_corners = qd.m_Parameters.m_AlignCorners ? 1 : 0;
+            p.half_pixel_centers = qd.m_Parameters.m_HalfPixelCenters ? 1 : 0;
+            p.nchw = nchw ? 1 : 0;
+            return Make<ResizeQueueDescriptor>(d, info, ctx, [st](const ResizeQueueDescriptor& data, cudaStream_t s)
+            {
+                st->p.x.data = Dev(data.m_Inputs[0]); st->p.y.data = Dev(data.m_Outputs[0]);
+                B200CheckStatus(b200k_resize_q(&st->p, s));
+            });
+        }
         case LayerType::Concat:       return MakeConcat(d, info, ctx);
         case LayerType::Splitter:     return MakeSplitter(d, info, ctx);
         case LayerType::Permute:      return MakePermute<PermuteQueueDescriptor>(d, info, ctx, false);

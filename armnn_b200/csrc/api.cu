@@ -106,6 +106,7 @@ extern "C" size_t b200k_sizeof_params(int which)
         case 9: return sizeof(b200k_qlstm_params);
         case 10: return sizeof(b200k_pad_params);
         case 11: return sizeof(b200k_view_copy_params);
+        case 12: return sizeof(b200k_resize_params);
         default: return 0;
     }
 }

@@ -372,6 +372,17 @@ int armnnc_add_slice(void* vn, int rank, const int32_t* begin, const int32_t* si
     return add_layer(n, n->net->AddSliceLayer(d));
 }
 
+int armnnc_add_resize(void* vn, int height, int width, int method, int align_corners, int half_pixel_centers, int nchw)
+{
+    auto* n = static_cast<CNet*>(vn);
+    ResizeDescriptor d;
+    d.m_TargetHeight = (uint32_t)height; d.m_TargetWidth = (uint32_t)width;
+    d.m_Method = method == 0 ? ResizeMethod::Bilinear : ResizeMethod::NearestNeighbor;
+    d.m_DataLayout = nchw ? DataLayout::NCHW : DataLayout::NHWC;
+    d.m_AlignCorners = align_corners != 0; d.m_HalfPixelCenters = half_pixel_centers != 0;
+    return add_layer(n, n->net->AddResizeLayer(d));
+}
+
 int armnnc_add_quantize(void* vn)   { auto* n = static_cast<CNet*>(vn); return add_layer(n, n->net->AddQuantizeLayer()); }
 int armnnc_add_dequantize(void* vn) { auto* n = static_cast<CNet*>(vn); return add_layer(n, n->net->AddDequantizeLayer()); }
 

@@ -256,6 +256,13 @@ class INetwork:
     def AddSliceLayer(self, begin, size, name=None):
         return self._add(Layer("Slice", name, 1, 1, {"begin": tuple(int(x) for x in begin), "size": tuple(int(x) for x in size)}))
 
+    def AddResizeLayer(self, target_height, target_width, method=0, align_corners=False, half_pixel_centers=False,
+                       nchw=False, name=None):
+        """armnn::ResizeDescriptor; method 0 = Bilinear, 1 = NearestNeighbor (armnn::ResizeMethod)."""
+        return self._add(Layer("Resize", name, 1, 1, {"height": int(target_height), "width": int(target_width), "method": int(method),
+                                                      "align_corners": bool(align_corners),
+                                                      "half_pixel_centers": bool(half_pixel_centers), "nchw": bool(nchw)}))
+
     def AddQuantizeLayer(self, name=None):
         return self._add(Layer("Quantize", name, 1, 1))
 
@@ -329,6 +336,13 @@ def IsLayerSupported(layer):
     if t == "Pad":
         if len(ins[0].shape) > 4:
             return False, "Pad: rank > 4"
+        return True, ""
+    if t == "Resize":
+        ok = (DataType.QAsymmU8, DataType.QAsymmS8, DataType.QSymmS16, DataType.Float32)
+        if ins[0].dtype not in ok or outs[0].dtype != ins[0].dtype or len(ins[0].shape) != 4:
+            return False, "Resize: 4-D tensors of one supported data type only"
+        if layer.desc["align_corners"] and layer.desc["half_pixel_centers"]:
+            return False, "Resize: align_corners and half_pixel_centers cannot both be set"
         return True, ""
     if t in ("Concat", "Splitter"):
         # RefLayerSupport.cpp:949-979, 2597-2630: one element type for every tensor; quantisation may differ
@@ -705,6 +719,22 @@ class GraphProgram:
             p.shape[i], p.pad_before[i], p.pad_after[i] = x.info.shape[i], before, after
         p.pad_value = layer.desc["value"]
         return "pad_q", p
+
+    def _make_Resize(self, layer):
+        x, y, d = layer.inputs[0].source, layer.outputs[0], layer.desc
+        p = _abi.ResizeParams()
+        p.x, p.y = self._operand(x), self._operand(y)
+        if d["nchw"]:
+            p.n, p.c, p.in_h, p.in_w = x.info.shape
+            oh, ow = y.info.shape[2], y.info.shape[3]
+        else:
+            p.n, p.in_h, p.in_w, p.c = x.info.shape
+            oh, ow = y.info.shape[1], y.info.shape[2]
+        if (oh, ow) != (d["height"], d["width"]):
+            raise InvalidArgumentException("Resize: output shape %s does not match the target size %dx%d" % (y.info.shape, d["height"], d["width"]))
+        p.out_h, p.out_w = oh, ow
+        p.method, p.align_corners, p.half_pixel_centers, p.nchw = d["method"], int(d["align_corners"]), int(d["half_pixel_centers"]), int(d["nchw"])
+        return "resize_q", p
 
     # -- Concat, Splitter, Permute, Transpose, StridedSlice, Slice: rectangular view copies (armnn_b200/views.py) --
     def _view_copy(self, x, y, view):

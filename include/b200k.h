@@ -281,6 +281,22 @@ typedef struct {
 
 int b200k_view_copy_q(const b200k_view_copy_params* p, void* stream);
 
+/* ---- Resize ----------------------------------------------------------------------------------- */
+
+/* armnn::Resize (src/backends/reference/workloads/Resize.cpp:72-216): bilinear (method 0) or nearest-neighbour
+ * (method 1, armnn::ResizeMethod) resampling of H and W, NHWC (nchw = 0) or NCHW; every sample is decoded to fp32,
+ * interpolated with the reference's own sequence of fp32 operations (Lerp = w * b + (1 - w) * a, unfused) and encoded
+ * with y's quantisation.  align_corners and half_pixel_centers as in armnn::ResizeDescriptor (not both). */
+typedef struct {
+    b200k_qtensor x, y;
+    int32_t n, c, in_h, in_w, out_h, out_w;
+    int32_t method;
+    int32_t align_corners, half_pixel_centers;
+    int32_t nchw;
+} b200k_resize_params;
+
+int b200k_resize_q(const b200k_resize_params* p, void* stream);
+
 /* ---- Softmax --------------------------------------------------------------------------------- */
 
 /* armnn::Softmax (src/backends/reference/workloads/Softmax.cpp:17-70): softmax over the axis of

@@ -355,6 +355,28 @@ extern "C" int cpuref_pad_q(const b200k_pad_params* p)
     });
 }
 
+extern "C" int cpuref_resize_q(const b200k_resize_params* p)
+{
+    return guarded([&] {
+        Harness h;
+        ResizeQueueDescriptor d;
+        d.m_Parameters.m_TargetHeight = (uint32_t)p->out_h;
+        d.m_Parameters.m_TargetWidth = (uint32_t)p->out_w;
+        d.m_Parameters.m_Method = p->method == 0 ? ResizeMethod::Bilinear : ResizeMethod::NearestNeighbor;
+        d.m_Parameters.m_DataLayout = p->nchw ? DataLayout::NCHW : DataLayout::NHWC;
+        d.m_Parameters.m_AlignCorners = p->align_corners != 0;
+        d.m_Parameters.m_HalfPixelCenters = p->half_pixel_centers != 0;
+        const unsigned N = (unsigned)p->n, C = (unsigned)p->c;
+        const TensorShape xs = p->nchw ? TensorShape({N, C, (unsigned)p->in_h, (unsigned)p->in_w}) : TensorShape({N, (unsigned)p->in_h, (unsigned)p->in_w, C});
+        const TensorShape ys = p->nchw ? TensorShape({N, C, (unsigned)p->out_h, (unsigned)p->out_w}) : TensorShape({N, (unsigned)p->out_h, (unsigned)p->out_w, C});
+        TensorInfo xi = make_info(p->x, xs, 0, 0, false), yi = make_info(p->y, ys, 0, 0, false);
+        h.in(d, xi, p->x.data);
+        ITensorHandle* o = h.out(d, yi);
+        h.run(LayerType::Resize, d);
+        copy_out(o, const_cast<void*>(p->y.data), yi.GetNumBytes());
+    });
+}
+
 // Concat, Splitter, Permute, Transpose, StridedSlice, Slice: the real RefConcatWorkload ... RefSliceWorkload on the
 // descriptor the test states (oracle/move_desc.h).
 extern "C" int cpuref_move_q(const oracle_move_params* p)

@@ -484,6 +484,66 @@ int oracle_pad_q(const b200k_pad_params* p)
     return 0;
 }
 
+/* ---- Resize, Resize.cpp:17-216 ---------------------------------------------------------------------
+ * The reference's fp32 operations in the reference's order (this file is built with -ffp-contract=off): scale,
+ * PixelScaler, floor (or armnn::roundf for nearest neighbour with aligned corners), the four texels, three Lerps. */
+static float lerp_ref(float a, float b, float w) { return w * b + (1.f - w) * a; }
+static float round_ref(float v) { return v < 0.f ? floorf(v - 0.5f) : floorf(v + 0.5f); }      /* include/armnn/Utils.hpp:43-47 */
+static float pixel_scaler(int pixel, float scale, int half, int method)
+{
+    if (half && method == 0) return ((float)pixel + 0.5f) * scale - 0.5f;
+    if (half && method == 1) return ((float)pixel + 0.5f) * scale;
+    return (float)pixel * scale;
+}
+static int mini(int a, int b) { return a < b ? a : b; }
+
+int oracle_resize_q(const b200k_resize_params* p)
+{
+    if (!p || !p->x.data || !p->y.data || (p->method != 0 && p->method != 1) || (p->align_corners && p->half_pixel_centers))
+        return B200K_E_INVALID;
+    const int N = p->n, C = p->c, IH = p->in_h, IW = p->in_w, OH = p->out_h, OW = p->out_w;
+    const float scale_y = (p->align_corners && OH > 1) ? (float)(IH - 1) / (float)(OH - 1) : (float)IH / (float)OH;
+    const float scale_x = (p->align_corners && OW > 1) ? (float)(IW - 1) / (float)(OW - 1) : (float)IW / (float)OW;
+    const int nn_round = p->method == 1 && p->align_corners;
+    for (int n = 0; n < N; ++n)
+        for (int c = 0; c < C; ++c)
+            for (int y = 0; y < OH; ++y) {
+                const float iy = pixel_scaler(y, scale_y, p->half_pixel_centers, p->method);
+                const float fiy = nn_round ? round_ref(iy) : floorf(iy);
+                const int y0 = mini((int)(fiy > 0.f ? fiy : 0.f), IH - 1);
+                const float yw = iy - fiy;
+                for (int x = 0; x < OW; ++x) {
+                    const float ix = pixel_scaler(x, scale_x, p->half_pixel_centers, p->method);
+                    const float fix = nn_round ? round_ref(ix) : floorf(ix);
+                    const int x0 = mini((int)(fix > 0.f ? fix : 0.f), IW - 1);
+                    const float xw = ix - fix;
+                    int x1, y1;
+                    if (p->half_pixel_centers) {
+                        const float cx = ceilf(ix), cy = ceilf(iy);
+                        x1 = mini((int)(cx > 0.f ? cx : 0.f), IW - 1);
+                        y1 = mini((int)(cy > 0.f ? cy : 0.f), IH - 1);
+                    } else {
+                        x1 = mini(x0 + 1, IW - 1);
+                        y1 = mini(y0 + 1, IH - 1);
+                    }
+#define RS_AT(t, yy, xx, HH, WW) (p->nchw ? (((int64_t)n * C + c) * (HH) + (yy)) * (WW) + (xx) : (((int64_t)n * (HH) + (yy)) * (WW) + (xx)) * C + c)
+                    float v;
+                    if (p->method == 0) {
+                        const float ly0 = lerp_ref(load_f(&p->x, RS_AT(x, y0, x0, IH, IW)), load_f(&p->x, RS_AT(x, y0, x1, IH, IW)), xw);
+                        const float ly1 = lerp_ref(load_f(&p->x, RS_AT(x, y1, x0, IH, IW)), load_f(&p->x, RS_AT(x, y1, x1, IH, IW)), xw);
+                        v = lerp_ref(ly0, ly1, yw);
+                    } else {
+                        /* of the four neighbours the one at distance 0 from (fix, fiy) wins: (x0, y0), as the scaled
+                         * coordinates are never negative (Resize.cpp:162-206) */
+                        v = load_f(&p->x, RS_AT(x, y0, x0, IH, IW));
+                    }
+                    store_f(&p->y, RS_AT(y, y, x, OH, OW), v);
+#undef RS_AT
+                }
+            }
+    return 0;
+}
+
 /* ---- Concat, Splitter, Permute, Transpose, StridedSlice, Slice ----------------------------------
  * The reference's data-movement workloads, each walked the way the reference walks it. */
 

@@ -341,6 +341,34 @@ def qlstm_cases():
     }
 
 
+def resize_cases():
+    """Resize: both methods, both coordinate conventions, both layouts, up- and down-sampling, re-quantisation."""
+    def make(seed, n, c, ih, iw, oh, ow, method, align=0, half=0, nchw=0, dtype=S8, xq=(0.05, -3), yq=None):
+        def build(mem):
+            rng = np.random.default_rng(seed)
+            p = _abi.ResizeParams()
+            in_shape = (n, c, ih, iw) if nchw else (n, ih, iw, c)
+            out_shape = (n, c, oh, ow) if nchw else (n, oh, ow, c)
+            p.x = qt(mem, _rand(rng, dtype, in_shape) if dtype != F32 else rng.standard_normal(in_shape).astype(np.float32), dtype, *xq)
+            p.y, y = qt_out(mem, out_shape, dtype, *(yq or xq))
+            p.n, p.c, p.in_h, p.in_w, p.out_h, p.out_w = n, c, ih, iw, oh, ow
+            p.method, p.align_corners, p.half_pixel_centers, p.nchw = method, align, half, nchw
+            return p, [y]
+        return lambda: SimpleCase("resize_q", build)
+    return {
+        "bilinear_up2_nhwc": make(301, 2, 16, 7, 9, 14, 18, 0),
+        "bilinear_up_odd_align_corners": make(302, 1, 5, 6, 5, 11, 13, 0, align=1),
+        "bilinear_up_half_pixel": make(303, 1, 8, 5, 7, 15, 14, 0, half=1),
+        "bilinear_down_u8_requantise": make(304, 2, 3, 17, 19, 5, 8, 0, dtype=U8, xq=(0.1, 128), yq=(0.07, 100)),
+        "bilinear_nchw_float": make(305, 1, 4, 6, 6, 9, 13, 0, nchw=1, dtype=F32, xq=(1.0, 0)),
+        "bilinear_down_half_pixel_nchw": make(306, 1, 3, 16, 12, 5, 7, 0, half=1, nchw=1),
+        "nearest_up2_nhwc": make(307, 2, 24, 6, 5, 12, 10, 1),
+        "nearest_align_corners": make(308, 1, 7, 5, 9, 12, 4, 1, align=1),
+        "nearest_half_pixel_down": make(309, 1, 4, 13, 11, 6, 5, 1, half=1, dtype=U8, xq=(0.2, 9)),
+        "nearest_nchw_s16": make(310, 1, 3, 4, 6, 10, 9, 1, nchw=1, dtype=S16, xq=(0.01, 0)),
+    }
+
+
 def move_cases():
     """Concat, Splitter, Permute, Transpose, StridedSlice and Slice as the reference's descriptors state them."""
     q = (S8, 0.05, -3)
@@ -383,7 +411,7 @@ def move_cases():
 
 ALL_GROUPS = {"conv": conv_cases, "dwconv": dwconv_cases, "fc": fc_cases, "bmm": bmm_cases, "pool": pool_cases,
               "mean": mean_cases, "eltwise": eltwise_cases, "activation": activation_cases, "softmax": softmax_cases,
-              "convert": convert_cases, "pad": pad_cases, "qlstm": qlstm_cases, "move": move_cases}
+              "convert": convert_cases, "pad": pad_cases, "qlstm": qlstm_cases, "move": move_cases, "resize": resize_cases}
 
 
 def run_case(case, where):

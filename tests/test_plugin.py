@@ -474,3 +474,59 @@ def test_transpose_that_changes_the_quantisation_is_refused_by_layer_support():
     tr.GetOutputSlot(0).Connect(ol.GetInputSlot(0))
     with pytest.raises(Exception):
         hostnet.ArmnnNetwork(net, "B200Acc", optimize_only=True)
+
+
+def _resize_net(batch=2):
+    """Bilinear x2 up-sampling with half-pixel centres -> 3x3 convolution + ReLU -> nearest-neighbour down-sampling
+    (the decoder pattern of segmentation networks), plus an align-corners bilinear branch as a second output."""
+    from armnn_b200.network import ActivationFunction, DataType, INetwork, TensorInfo
+    rng = np.random.default_rng(78)
+    net = INetwork.Create()
+
+    def info(shape, scale=0.05, offset=-3):
+        return TensorInfo(tuple(shape), DataType.QAsymmS8, scale, offset)
+    il = net.AddInputLayer(0, "input")
+    il.GetOutputSlot(0).SetTensorInfo(info((batch, 9, 7, 32)))
+    up = net.AddResizeLayer(18, 14, method=0, half_pixel_centers=True, name="up")
+    il.GetOutputSlot(0).Connect(up.GetInputSlot(0))
+    up.GetOutputSlot(0).SetTensorInfo(info((batch, 18, 14, 32), 0.06, 2))
+    w_scales = rng.uniform(0.002, 0.01, size=32).astype(np.float32)
+    wq = rng.integers(-127, 128, size=(32, 3, 3, 32)).astype(np.int8)
+    bq = rng.integers(-500, 501, size=32).astype(np.int32)
+    wl = net.AddConstantLayer(wq, TensorInfo(wq.shape, DataType.QSymmS8, scales=w_scales, quant_dim=0), "w")
+    bl = net.AddConstantLayer(bq, TensorInfo(bq.shape, DataType.Signed32, scales=(np.float32(0.06) * w_scales), quant_dim=0), "b")
+    cl = net.AddConvolution2dLayer((1, 1), (1, 1, 1, 1), (1, 1), True, "conv")
+    up.GetOutputSlot(0).Connect(cl.GetInputSlot(0))
+    wl.GetOutputSlot(0).Connect(cl.GetInputSlot(1))
+    bl.GetOutputSlot(0).Connect(cl.GetInputSlot(2))
+    y_info = info((batch, 18, 14, 32), 0.08, -128)
+    cl.GetOutputSlot(0).SetTensorInfo(y_info)
+    al = net.AddActivationLayer(ActivationFunction.ReLu, name="relu")
+    cl.GetOutputSlot(0).Connect(al.GetInputSlot(0))
+    al.GetOutputSlot(0).SetTensorInfo(y_info)
+    dn = net.AddResizeLayer(6, 5, method=1, name="down")
+    al.GetOutputSlot(0).Connect(dn.GetInputSlot(0))
+    dn.GetOutputSlot(0).SetTensorInfo(info((batch, 6, 5, 32), 0.08, -128))
+    ac = net.AddResizeLayer(13, 4, method=0, align_corners=True, name="align")
+    il.GetOutputSlot(0).Connect(ac.GetInputSlot(0))
+    ac.GetOutputSlot(0).SetTensorInfo(info((batch, 13, 4, 32)))
+    o0 = net.AddOutputLayer(0, "out")
+    dn.GetOutputSlot(0).Connect(o0.GetInputSlot(0))
+    o1 = net.AddOutputLayer(1, "out_align")
+    ac.GetOutputSlot(0).Connect(o1.GetInputSlot(0))
+    return net, {"input_shape": (batch, 9, 7, 32)}
+
+
+@needs_plugin
+@pytest.mark.gpu
+def test_resize_layers_through_the_runtime_match_cpuref():
+    """Resize (bilinear with half-pixel centres, bilinear with aligned corners, nearest neighbour) around a convolution:
+    B200Acc inside the real runtime against CpuRef; the Resize-only output is bit-exact, the one behind the convolution
+    within the convolution's +-1 LSB."""
+    net, info = _resize_net()
+    x = np.random.default_rng(13).integers(-128, 128, size=info["input_shape"]).astype(np.int8)
+    ref = hostnet.ArmnnNetwork(net, "CpuRef").run({0: x})
+    got = hostnet.ArmnnNetwork(net, "B200Acc").run({0: x})
+    assert np.array_equal(ref[1], got[1])
+    st = diff_stats(ref[0], got[0])
+    assert st["max_abs"] <= 1 and st["mismatch_frac"] < 5e-3, st
