@@ -90,6 +90,11 @@ class ViewCopyParams(C.Structure):
                 ("src_offset", C.c_int64), ("dst_offset", C.c_int64)]
 
 
+class ReduceParams(C.Structure):
+    _fields_ = [("x", QTensor), ("y", QTensor), ("rank", C.c_int32), ("shape", C.c_int32 * 6), ("axis_mask", C.c_int32),
+                ("op", C.c_int32)]
+
+
 class ResizeParams(C.Structure):
     _fields_ = [("x", QTensor), ("y", QTensor), ("n", C.c_int32), ("c", C.c_int32), ("in_h", C.c_int32), ("in_w", C.c_int32),
                 ("out_h", C.c_int32), ("out_w", C.c_int32), ("method", C.c_int32), ("align_corners", C.c_int32),
@@ -142,6 +147,7 @@ KERNEL_ENTRY_POINTS = {
     "pad_q": PadParams,
     "view_copy_q": ViewCopyParams,
     "resize_q": ResizeParams,
+    "reduce_q": ReduceParams,
 }
 
 # every symbol include/b200k.h declares

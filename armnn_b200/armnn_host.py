@@ -154,6 +154,9 @@ class ArmnnNetwork:
             elif t == "Pad":
                 flat = [v for pair in d["pads"] for v in pair]
                 lid = lib.armnnc_add_pad(net, len(d["pads"]), (C.c_int32 * len(flat))(*flat), C.c_float(d["value"]))
+            elif t == "Reduce":
+                axes = (C.c_int32 * len(d["axis"]))(*d["axis"])
+                lid = lib.armnnc_add_reduce(net, axes, len(d["axis"]), d["op"], int(d["keep_dims"]))
             elif t == "Resize":
                 lid = lib.armnnc_add_resize(net, d["height"], d["width"], d["method"], int(d["align_corners"]),
                                             int(d["half_pixel_centers"]), int(d["nchw"]))

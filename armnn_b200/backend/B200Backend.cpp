@@ -166,9 +166,11 @@ public:
                 return true;
             }
             case LayerType::Mean:
+            case LayerType::Reduce:
             {
-                const auto& d = *PolymorphicDowncast<const MeanDescriptor*>(&descriptor);
-                if (infos[0].GetNumDimensions() != 4 || d.m_Axis != std::vector<unsigned int>{1, 2}) { return No(reason, "Mean only over H and W of an NHWC tensor"); }
+                // Mean over H and W of an NHWC tensor has its own kernel; every other choice of axes, and Reduce, runs
+                // on the general one (armnn::Reduce, src/backends/reference/workloads/Reduce.cpp:63-175)
+                if (infos[0].GetNumDimensions() > 6) { return No(reason, "rank > 6"); }
                 return (IsActType(infos[0]) && IsActType(infos[1])) || No(reason, "unsupported data type");
             }
             case LayerType::Addition:

@@ -510,6 +510,33 @@ struct SimpleState
     DeviceBlobs blobs;
 };
 
+// Reduce (and Mean over axes other than H and W): b200k_reduce_q over the descriptor's axes (none: all of them).
+template <typename QD>
+std::unique_ptr<IWorkload> MakeReduce(const QueueDescriptor& d, const WorkloadInfo& info, const ContextPtr& ctx,
+                                      const std::vector<unsigned int>& axes, int32_t op)
+{
+    auto st = std::make_shared<SimpleState<b200k_reduce_params>>(ctx);
+    b200k_reduce_params& p = st->p;
+    std::memset(&p, 0, sizeof(p));
+    const TensorInfo& x = info.m_InputTensorInfos[0];
+    p.x = Operand(x, st->blobs); p.y = Operand(info.m_OutputTensorInfos[0], st->blobs);
+    p.rank = static_cast<int32_t>(x.GetNumDimensions());
+    if (p.rank < 1 || p.rank > 6) { throw InvalidArgumentException("B200Acc: Reduce needs a rank between 1 and 6"); }
+    for (int i = 0; i < p.rank; ++i) { p.shape[i] = static_cast<int32_t>(x.GetShape()[static_cast<unsigned int>(i)]); }
+    for (unsigned int a : axes)
+    {
+        if (a >= x.GetNumDimensions()) { throw InvalidArgumentException("B200Acc: Reduce axis outside the tensor's rank"); }
+        p.axis_mask |= 1 << a;
+    }
+    p.op = op;
+    return Make<QD>(d, info, ctx, [st](const QD& data, cudaStream_t s)
+    {
+        st->p.x.data = Dev(data.m_Inputs[0]); st->p.y.data = Dev(data.m_Outputs[0]);
+        B200CheckStatus(b200k_reduce_q(&st->p, s));
+    });
+}
+
+
 std::unique_ptr<IWorkload> MakeEltwise(const QueueDescriptor& d, const WorkloadInfo& info, const ContextPtr& ctx, BinaryOperation op,
                                        const ActivationDescriptor* act)
 {
@@ -756,8 +783,19 @@ std::unique_ptr<IWorkload> B200WorkloadFactory::CreateWorkload(LayerType type, c
                 B200CheckStatus(b200k_pool2d_q8(&st->p, s));
             });
         }
+        case LayerType::Reduce:
+        {
+            const auto& qd = *PolymorphicDowncast<const ReduceQueueDescriptor*>(&d);
+            return MakeReduce<ReduceQueueDescriptor>(d, info, ctx, qd.m_Parameters.m_vAxis, static_cast<int32_t>(qd.m_Parameters.m_ReduceOperation));
+        }
         case LayerType::Mean:
         {
+            const auto& axes = PolymorphicDowncast<const MeanQueueDescriptor*>(&d)->m_Parameters.m_Axis;
+            if (info.m_InputTensorInfos[0].GetNumDimensions() != 4 || axes != std::vector<unsigned int>{1, 2})
+            {
+                // RefMeanWorkload is armnn::Reduce with ReduceOperation::Mean (RefMeanWorkload.cpp)
+                return MakeReduce<MeanQueueDescriptor>(d, info, ctx, axes, 2);
+            }
             auto st = std::make_shared<SimpleState<b200k_mean_params>>(ctx);
             b200k_mean_params& p = st->p;
             std::memset(&p, 0, sizeof(p));

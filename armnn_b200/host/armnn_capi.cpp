@@ -372,6 +372,16 @@ int armnnc_add_slice(void* vn, int rank, const int32_t* begin, const int32_t* si
     return add_layer(n, n->net->AddSliceLayer(d));
 }
 
+int armnnc_add_reduce(void* vn, const int32_t* axes, int n_axes, int operation, int keep_dims)
+{
+    auto* n = static_cast<CNet*>(vn);
+    ReduceDescriptor d;
+    for (int i = 0; i < n_axes; ++i) d.m_vAxis.push_back((uint32_t)axes[i]);
+    d.m_ReduceOperation = static_cast<ReduceOperation>(operation);
+    d.m_KeepDims = keep_dims != 0;
+    return add_layer(n, n->net->AddReduceLayer(d));
+}
+
 int armnnc_add_resize(void* vn, int height, int width, int method, int align_corners, int half_pixel_centers, int nchw)
 {
     auto* n = static_cast<CNet*>(vn);

@@ -256,6 +256,10 @@ class INetwork:
     def AddSliceLayer(self, begin, size, name=None):
         return self._add(Layer("Slice", name, 1, 1, {"begin": tuple(int(x) for x in begin), "size": tuple(int(x) for x in size)}))
 
+    def AddReduceLayer(self, axis, operation, keep_dims=False, name=None):
+        """armnn::ReduceDescriptor; operation follows armnn::ReduceOperation (0 Sum, 1 Max, 2 Mean, 3 Min, 4 Prod)."""
+        return self._add(Layer("Reduce", name, 1, 1, {"axis": tuple(int(a) for a in axis), "op": int(operation), "keep_dims": bool(keep_dims)}))
+
     def AddResizeLayer(self, target_height, target_width, method=0, align_corners=False, half_pixel_centers=False,
                        nchw=False, name=None):
         """armnn::ResizeDescriptor; method 0 = Bilinear, 1 = NearestNeighbor (armnn::ResizeMethod)."""
@@ -322,12 +326,10 @@ def IsLayerSupported(layer):
         if any(i.dtype not in _Q8 for i in ins) or outs[0].dtype not in _Q8:
             return False, "BatchMatMul: 8-bit quantised tensors only"
         return True, ""
-    if t in ("Pooling2d", "Mean", "ElementwiseBinary", "Activation", "Softmax"):
+    if t in ("Pooling2d", "Mean", "Reduce", "ElementwiseBinary", "Activation", "Softmax"):
         ok = (DataType.QAsymmU8, DataType.QAsymmS8, DataType.QSymmS16, DataType.Float32)
         if any(i.dtype not in ok for i in ins) or outs[0].dtype not in ok:
             return False, "%s: unsupported data type" % t
-        if t == "Mean" and tuple(layer.desc["axis"]) != (1, 2):
-            return False, "Mean: only reduction over H and W of an NHWC tensor is supported"
         if t == "ElementwiseBinary" and len(outs[0].shape) > 4:
             return False, "ElementwiseBinary: rank > 4"
         return True, ""
@@ -659,8 +661,24 @@ class GraphProgram:
         p.pool_type, p.padding_method = int(layer.desc["type"]), int(layer.desc["method"])
         return "pool2d_q8", p
 
+    def _reduce(self, layer, axes, op):
+        x, y = layer.inputs[0].source, layer.outputs[0]
+        p = _abi.ReduceParams()
+        p.x, p.y = self._operand(x), self._operand(y)
+        p.rank = len(x.info.shape)
+        for i, n in enumerate(x.info.shape):
+            p.shape[i] = n
+        p.axis_mask = sum(1 << int(a) for a in axes)
+        p.op = int(op)
+        return "reduce_q", p
+
+    def _make_Reduce(self, layer):
+        return self._reduce(layer, layer.desc["axis"], layer.desc["op"])
+
     def _make_Mean(self, layer):
         x, y = layer.inputs[0].source, layer.outputs[0]
+        if len(x.info.shape) != 4 or tuple(layer.desc["axis"]) != (1, 2):
+            return self._reduce(layer, layer.desc["axis"], 2)        # RefMeanWorkload: armnn::Reduce with Mean
         p = _abi.MeanParams()
         p.x, p.y = self._operand(x), self._operand(y)
         p.n, p.h, p.wd, p.c = x.info.shape

@@ -281,6 +281,24 @@ typedef struct {
 
 int b200k_view_copy_q(const b200k_view_copy_params* p, void* stream);
 
+/* ---- Reduce ----------------------------------------------------------------------------------- */
+
+/* armnn::Reduce (src/backends/reference/workloads/Reduce.cpp:63-175, RefReduceWorkload.cpp): op follows
+ * armnn::ReduceOperation (0 Sum, 1 Max, 2 Mean, 3 Min, 4 Prod) over the dimensions whose bit is set in axis_mask (0: all
+ * of them).  Every input element is decoded to fp32 and folded into its output's fp32 accumulator in the order of the
+ * flat input index (the order matters for Sum, Mean and Prod); Mean divides by the number of folded elements; the
+ * result is encoded with y's quantisation.  The output holds the kept dimensions in order (keep_dims only changes its
+ * shape, not its bytes). */
+typedef struct {
+    b200k_qtensor x, y;
+    int32_t rank;
+    int32_t shape[6];
+    int32_t axis_mask;
+    int32_t op;
+} b200k_reduce_params;
+
+int b200k_reduce_q(const b200k_reduce_params* p, void* stream);
+
 /* ---- Resize ----------------------------------------------------------------------------------- */
 
 /* armnn::Resize (src/backends/reference/workloads/Resize.cpp:72-216): bilinear (method 0) or nearest-neighbour

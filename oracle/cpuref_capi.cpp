@@ -355,6 +355,29 @@ extern "C" int cpuref_pad_q(const b200k_pad_params* p)
     });
 }
 
+extern "C" int cpuref_reduce_q(const b200k_reduce_params* p)
+{
+    return guarded([&] {
+        Harness h;
+        ReduceQueueDescriptor d;
+        d.m_Parameters.m_KeepDims = false;
+        d.m_Parameters.m_ReduceOperation = static_cast<ReduceOperation>(p->op);
+        unsigned in_dims[6], out_dims[6], nout = 0;
+        for (int i = 0; i < p->rank; ++i) {
+            in_dims[i] = (unsigned)p->shape[i];
+            if (p->axis_mask & (1 << i)) d.m_Parameters.m_vAxis.push_back((uint32_t)i);
+            else if (p->axis_mask) out_dims[nout++] = (unsigned)p->shape[i];
+        }
+        if (nout == 0) out_dims[nout++] = 1;
+        TensorInfo xi = make_info(p->x, TensorShape((unsigned)p->rank, in_dims), 0, 0, false);
+        TensorInfo yi = make_info(p->y, TensorShape(nout, out_dims), 0, 0, false);
+        h.in(d, xi, p->x.data);
+        ITensorHandle* o = h.out(d, yi);
+        h.run(LayerType::Reduce, d);
+        copy_out(o, const_cast<void*>(p->y.data), yi.GetNumBytes());
+    });
+}
+
 extern "C" int cpuref_resize_q(const b200k_resize_params* p)
 {
     return guarded([&] {

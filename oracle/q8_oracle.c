@@ -692,6 +692,38 @@ static int move_slice(const oracle_move_params* p)
     return 0;
 }
 
+/* ---- Reduce, Reduce.cpp:63-175 -------------------------------------------------------------------
+ * One fp32 accumulator per output element; the input is walked once in flat index order and every element is folded
+ * into the accumulator of the output it belongs to (ReducedOutputOffset: the kept coordinates, in order). */
+int oracle_reduce_q(const b200k_reduce_params* p)
+{
+    if (!p || !p->x.data || !p->y.data || p->rank < 1 || p->rank > 6 || p->op < 0 || p->op > 4) return B200K_E_INVALID;
+    const int mask = p->axis_mask ? p->axis_mask : (1 << p->rank) - 1;
+    int64_t outputs = 1, reduced = 1;
+    for (int d = 0; d < p->rank; ++d) { if (mask & (1 << d)) reduced *= p->shape[d]; else outputs *= p->shape[d]; }
+    float* tmp = (float*)malloc(sizeof(float) * (size_t)outputs);
+    if (!tmp) return B200K_E_INVALID;
+    const float init = (p->op == 0 || p->op == 2) ? 0.f : (p->op == 4 ? 1.f : (p->op == 1 ? -3.402823466e+38f : 3.402823466e+38f));
+    for (int64_t o = 0; o < outputs; ++o) tmp[o] = init;
+    const int64_t n = outputs * reduced;
+    for (int64_t i = 0; i < n; ++i) {
+        int32_t c[6];
+        coords_of(i, p->shape, p->rank, c);
+        int64_t o = 0;
+        for (int d = 0; d < p->rank; ++d) if (!(mask & (1 << d))) o = o * p->shape[d] + c[d];
+        const float v = load_f(&p->x, i);
+        switch (p->op) {
+            case 0: case 2: tmp[o] += v; break;
+            case 4: tmp[o] *= v; break;
+            case 1: if (v > tmp[o]) tmp[o] = v; break;
+            default: if (v < tmp[o]) tmp[o] = v; break;
+        }
+    }
+    for (int64_t o = 0; o < outputs; ++o) store_f(&p->y, o, p->op == 2 ? tmp[o] / (float)reduced : tmp[o]);
+    free(tmp);
+    return 0;
+}
+
 /* The view copy of include/b200k.h as the graph-level oracle executor calls it: element by element through
  * Decoder / Encoder when the quantisation differs, raw elements otherwise. */
 int oracle_view_copy_q(const b200k_view_copy_params* p)

@@ -341,6 +341,37 @@ def qlstm_cases():
     }
 
 
+def reduce_cases():
+    """Reduce: every operation, inner / outer / several / all axes, re-quantisation, float."""
+    def make(seed, shape, axes, op, dtype=S8, xq=(0.05, -3), yq=None):
+        def build(mem):
+            rng = np.random.default_rng(seed)
+            p = _abi.ReduceParams()
+            p.x = qt(mem, _rand(rng, dtype, shape) if dtype != F32 else rng.standard_normal(shape).astype(np.float32), dtype, *xq)
+            out_shape = tuple(s for d, s in enumerate(shape) if d not in axes) or (1,)
+            p.y, y = qt_out(mem, out_shape, dtype, *(yq or xq))
+            p.rank = len(shape)
+            for i, s in enumerate(shape):
+                p.shape[i] = s
+            p.axis_mask = sum(1 << d for d in axes)
+            p.op = op
+            return p, [y]
+        return lambda: SimpleCase("reduce_q", build)
+    SUM, MAX, MEAN, MIN, PROD = 0, 1, 2, 3, 4
+    return {
+        "sum_channels_nhwc": make(321, (2, 5, 6, 24), (3,), SUM, yq=(0.4, 10)),
+        "sum_hw_u8": make(322, (2, 7, 9, 16), (1, 2), SUM, dtype=U8, xq=(0.02, 128), yq=(0.3, 120)),
+        "mean_hw_requantise": make(323, (3, 6, 5, 20), (1, 2), MEAN, yq=(0.03, 4)),
+        "mean_outer_axis": make(324, (9, 4, 11), (0,), MEAN),
+        "max_width": make(325, (2, 4, 13, 8), (2,), MAX),
+        "min_batch_and_channels": make(326, (3, 5, 4, 7), (0, 3), MIN, dtype=U8, xq=(0.1, 77)),
+        "prod_small_float": make(327, (4, 3, 5), (1,), PROD, dtype=F32, xq=(1.0, 0)),
+        "prod_quantised": make(328, (2, 3, 6), (1,), PROD, xq=(0.02, 1), yq=(0.05, 0)),
+        "sum_all_axes_float": make(329, (3, 7, 5), (0, 1, 2), SUM, dtype=F32, xq=(1.0, 0)),
+        "max_rank1_s16": make(330, (37,), (0,), MAX, dtype=S16, xq=(0.01, 0)),
+    }
+
+
 def resize_cases():
     """Resize: both methods, both coordinate conventions, both layouts, up- and down-sampling, re-quantisation."""
     def make(seed, n, c, ih, iw, oh, ow, method, align=0, half=0, nchw=0, dtype=S8, xq=(0.05, -3), yq=None):
@@ -411,7 +442,7 @@ def move_cases():
 
 ALL_GROUPS = {"conv": conv_cases, "dwconv": dwconv_cases, "fc": fc_cases, "bmm": bmm_cases, "pool": pool_cases,
               "mean": mean_cases, "eltwise": eltwise_cases, "activation": activation_cases, "softmax": softmax_cases,
-              "convert": convert_cases, "pad": pad_cases, "qlstm": qlstm_cases, "move": move_cases, "resize": resize_cases}
+              "convert": convert_cases, "pad": pad_cases, "qlstm": qlstm_cases, "move": move_cases, "resize": resize_cases, "reduce": reduce_cases}
 
 
 def run_case(case, where):

@@ -530,3 +530,28 @@ def test_resize_layers_through_the_runtime_match_cpuref():
     assert np.array_equal(ref[1], got[1])
     st = diff_stats(ref[0], got[0])
     assert st["max_abs"] <= 1 and st["mismatch_frac"] < 5e-3, st
+
+
+@needs_plugin
+@pytest.mark.gpu
+def test_reduce_and_general_mean_through_the_runtime_match_cpuref():
+    """Reduce (Sum over channels, Max over H and W) and a Mean over the channel axis (not the H, W case that has its own
+    kernel): B200Acc inside the real runtime against CpuRef, identical bytes (fp32 accumulation in the same order)."""
+    from armnn_b200.network import DataType, INetwork, TensorInfo
+    net = INetwork.Create()
+    il = net.AddInputLayer(0, "input")
+    il.GetOutputSlot(0).SetTensorInfo(TensorInfo((2, 6, 5, 24), DataType.QAsymmS8, 0.05, -3))
+    outs = []
+    for i, (layer, shape, q) in enumerate([
+            (net.AddReduceLayer((3,), 0, name="sum_c"), (2, 6, 5), (0.4, 7)),
+            (net.AddReduceLayer((1, 2), 1, name="max_hw"), (2, 24), (0.05, -3)),
+            (net.AddMeanLayer((3,), False, "mean_c"), (2, 6, 5), (0.03, 1))]):
+        il.GetOutputSlot(0).Connect(layer.GetInputSlot(0))
+        layer.GetOutputSlot(0).SetTensorInfo(TensorInfo(shape, DataType.QAsymmS8, *q))
+        ol = net.AddOutputLayer(i, "out%d" % i)
+        layer.GetOutputSlot(0).Connect(ol.GetInputSlot(0))
+    x = np.random.default_rng(14).integers(-128, 128, size=(2, 6, 5, 24)).astype(np.int8)
+    ref = hostnet.ArmnnNetwork(net, "CpuRef").run({0: x})
+    got = hostnet.ArmnnNetwork(net, "B200Acc").run({0: x})
+    for k in (0, 1, 2):
+        assert ref[k].shape == got[k].shape and np.array_equal(ref[k], got[k]), k
