@@ -119,6 +119,9 @@ class ArmnnNetwork:
                 ids[id(layer)] = lib.armnnc_add_input(net, d["id"], *info_args(layer.outputs[0].info))
                 self.in_infos.append((d["id"], layer.outputs[0].info))
                 continue
+            if t == "Constant" and layer.outputs[0].connections and all(
+                    s.layer.type == "TransposeConvolution2d" and s.index > 0 for s in layer.outputs[0].connections):
+                continue                              # travels inside the TransposeConvolution2d layer (ConstTensor arguments)
             if t == "Constant":
                 info = layer.outputs[0].info
                 sc = info.scales
@@ -154,6 +157,23 @@ class ArmnnNetwork:
             elif t == "Pad":
                 flat = [v for pair in d["pads"] for v in pair]
                 lid = lib.armnnc_add_pad(net, len(d["pads"]), (C.c_int32 * len(flat))(*flat), C.c_float(d["value"]))
+            elif t == "TransposeConvolution2d":
+                wl = layer.inputs[1].source.layer
+                wi = wl.outputs[0].info
+                wsc = wi.scales
+                bdata = bsc = None
+                bscale = 0.0
+                if d["bias"]:
+                    bl = layer.inputs[2].source.layer
+                    bdata, bsc, bscale = bl.const_data, bl.outputs[0].info.scales, bl.outputs[0].info.scale
+                lid = lib.armnnc_add_transpose_conv2d(
+                    net, d["stride"][0], d["stride"][1], d["pad"][0], d["pad"][1], d["pad"][2], d["pad"][3],
+                    _ABI_DTYPE[wi.dtype], _shape_arr(wi.shape), C.c_float(wi.scale), wi.offset,
+                    wsc.ctypes.data_as(C.c_void_p) if wsc is not None else None, len(wsc) if wsc is not None else 0,
+                    wl.const_data.ctypes.data_as(C.c_void_p),
+                    bdata.ctypes.data_as(C.c_void_p) if bdata is not None else None, C.c_float(bscale),
+                    bsc.ctypes.data_as(C.c_void_p) if bsc is not None else None, len(bsc) if bsc is not None else 0)
+                assert lid >= 0, lib.armnnc_last_error().decode()
             elif t == "Reduce":
                 axes = (C.c_int32 * len(d["axis"]))(*d["axis"])
                 lid = lib.armnnc_add_reduce(net, axes, len(d["axis"]), d["op"], int(d["keep_dims"]))
@@ -199,6 +219,8 @@ class ArmnnNetwork:
                 self.out_infos.append((layer.desc["id"], src.info))
                 continue
             for s in layer.inputs:
+                if layer.type == "TransposeConvolution2d" and s.index > 0:
+                    continue
                 lib.armnnc_connect(net, ids[id(s.source.layer)], s.source.index, ids[id(layer)], s.index)
         if optimize_only:
             need = lib.armnnc_optimized_layers(rt, net, backends.encode(), None, C.c_size_t(0))

@@ -127,6 +127,15 @@ public:
                 if (infos[0].GetNumDimensions() > 4) { return No(reason, "rank > 4"); }
                 return (IsActType(infos[0]) && IsActType(infos[1])) || No(reason, "unsupported data type");
             }
+            case LayerType::TransposeConvolution2d:
+            {
+                // infos: input, output, weights[, bias] (RefLayerSupport.cpp: IsTransposeConvolution2dSupported)
+                const auto& d = *PolymorphicDowncast<const TransposeConvolution2dDescriptor*>(&descriptor);
+                if (d.m_DataLayout != DataLayout::NHWC) { return No(reason, "only NHWC is supported"); }
+                if (infos.size() < 3 || !Is8Bit(infos[0]) || !Is8Bit(infos[1]) || !Is8Bit(infos[2])) { return No(reason, "8-bit quantised tensors only"); }
+                if (d.m_BiasEnabled && (infos.size() < 4 || infos[3].GetDataType() != DataType::Signed32)) { return No(reason, "bias must be Signed32"); }
+                return true;
+            }
             case LayerType::Resize:
             {
                 const auto& d = *PolymorphicDowncast<const ResizeDescriptor*>(&descriptor);

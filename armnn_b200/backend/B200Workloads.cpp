@@ -783,6 +783,40 @@ std::unique_ptr<IWorkload> B200WorkloadFactory::CreateWorkload(LayerType type, c
                 B200CheckStatus(b200k_pool2d_q8(&st->p, s));
             });
         }
+        case LayerType::TransposeConvolution2d:
+        {
+            // weights [OC, KH, KW, C] and bias are constant members of the queue descriptor (not input tensors): one
+            // upload at workload creation
+            const auto& qd = *PolymorphicDowncast<const TransposeConvolution2dQueueDescriptor*>(&d);
+            if (qd.m_Parameters.m_DataLayout != DataLayout::NHWC || !qd.m_Weight) { throw InvalidArgumentException("B200Acc: TransposeConvolution2d needs NHWC and constant weights"); }
+            auto st = std::make_shared<SimpleState<b200k_conv2d_params>>(ctx);
+            b200k_conv2d_params& p = st->p;
+            std::memset(&p, 0, sizeof(p));
+            const TensorInfo& x = info.m_InputTensorInfos[0];
+            const TensorInfo& y = info.m_OutputTensorInfos[0];
+            const TensorInfo& w = qd.m_Weight->GetTensorInfo();
+            p.x = Operand(x, st->blobs); p.y = Operand(y, st->blobs); p.w = Operand(w, st->blobs);
+            p.w.data = st->blobs.Upload(qd.m_Weight->GetConstTensor<void>(), w.GetNumBytes());
+            if (qd.m_Parameters.m_BiasEnabled && qd.m_Bias)
+            {
+                const TensorInfo& b = qd.m_Bias->GetTensorInfo();
+                p.bias = Operand(b, st->blobs);
+                p.bias.data = st->blobs.Upload(qd.m_Bias->GetConstTensor<void>(), b.GetNumBytes());
+            }
+            p.n = x.GetShape()[0]; p.h = x.GetShape()[1]; p.wd = x.GetShape()[2]; p.c = x.GetShape()[3];
+            p.oh = y.GetShape()[1]; p.ow = y.GetShape()[2]; p.oc = y.GetShape()[3];
+            p.kh = w.GetShape()[1]; p.kw = w.GetShape()[2];
+            if (w.GetShape()[0] != y.GetShape()[3] || w.GetShape()[3] != x.GetShape()[3]) { throw InvalidArgumentException("B200Acc: TransposeConvolution2d weights do not match the channel counts"); }
+            p.stride_h = qd.m_Parameters.m_StrideY; p.stride_w = qd.m_Parameters.m_StrideX;
+            p.pad_top = qd.m_Parameters.m_PadTop; p.pad_left = qd.m_Parameters.m_PadLeft;
+            p.dil_h = p.dil_w = 1;
+            Clamp(qd.GetAdditionalInformation<ActivationDescriptor>(), y, p.clamp_lo, p.clamp_hi);
+            return Make<TransposeConvolution2dQueueDescriptor>(d, info, ctx, [st](const TransposeConvolution2dQueueDescriptor& data, cudaStream_t s)
+            {
+                st->p.x.data = Dev(data.m_Inputs[0]); st->p.y.data = Dev(data.m_Outputs[0]);
+                B200CheckStatus(b200k_transpose_conv2d_q8(&st->p, s));
+            });
+        }
         case LayerType::Reduce:
         {
             const auto& qd = *PolymorphicDowncast<const ReduceQueueDescriptor*>(&d);

@@ -256,6 +256,12 @@ class INetwork:
     def AddSliceLayer(self, begin, size, name=None):
         return self._add(Layer("Slice", name, 1, 1, {"begin": tuple(int(x) for x in begin), "size": tuple(int(x) for x in size)}))
 
+    def AddTransposeConvolution2dLayer(self, stride=(1, 1), pad=(0, 0, 0, 0), bias_enabled=True, name=None):
+        """pad = (top, bottom, left, right); NHWC; inputs: 0 data, 1 weights [O,H,W,I], 2 bias (Constant layers: the Arm NN
+        API takes them as ConstTensor arguments of the layer, armnn::INetwork::AddTransposeConvolution2dLayer)."""
+        return self._add(Layer("TransposeConvolution2d", name, 3 if bias_enabled else 2, 1,
+                               {"stride": tuple(stride), "pad": tuple(pad), "bias": bool(bias_enabled)}))
+
     def AddReduceLayer(self, axis, operation, keep_dims=False, name=None):
         """armnn::ReduceDescriptor; operation follows armnn::ReduceOperation (0 Sum, 1 Max, 2 Mean, 3 Min, 4 Prod)."""
         return self._add(Layer("Reduce", name, 1, 1, {"axis": tuple(int(a) for a in axis), "op": int(operation), "keep_dims": bool(keep_dims)}))
@@ -339,6 +345,12 @@ def IsLayerSupported(layer):
         if len(ins[0].shape) > 4:
             return False, "Pad: rank > 4"
         return True, ""
+    if t == "TransposeConvolution2d":
+        if ins[0].dtype not in _Q8 or outs[0].dtype not in _Q8 or ins[1].dtype not in _Q8:
+            return False, "TransposeConvolution2d: 8-bit quantised tensors only"
+        if any(s.source.layer.type != "Constant" for s in layer.inputs[1:]):
+            return False, "TransposeConvolution2d: weights and bias must be constant"
+        return True, ""
     if t == "Resize":
         ok = (DataType.QAsymmU8, DataType.QAsymmS8, DataType.QSymmS16, DataType.Float32)
         if ins[0].dtype not in ok or outs[0].dtype != ins[0].dtype or len(ins[0].shape) != 4:
@@ -364,7 +376,7 @@ def IsLayerSupported(layer):
     return False, "layer type %s is not on the B200Acc hot path" % t
 
 
-_FUSABLE_PRODUCERS = ("Convolution2d", "DepthwiseConvolution2d", "FullyConnected", "ElementwiseBinary")
+_FUSABLE_PRODUCERS = ("Convolution2d", "DepthwiseConvolution2d", "FullyConnected", "ElementwiseBinary", "TransposeConvolution2d")
 
 
 class OptimizedNetwork:
@@ -660,6 +672,23 @@ class GraphProgram:
         p.pad_top, p.pad_bottom, p.pad_left, p.pad_right = layer.desc["pad"]
         p.pool_type, p.padding_method = int(layer.desc["type"]), int(layer.desc["method"])
         return "pool2d_q8", p
+
+    def _make_TransposeConvolution2d(self, layer):
+        x, w, y = layer.inputs[0].source, layer.inputs[1].source, layer.outputs[0]
+        p = _abi.Conv2dParams()
+        p.x, p.w, p.y = self._operand(x), self._operand(w), self._operand(y)
+        if layer.desc["bias"]:
+            p.bias = self._operand(layer.inputs[2].source)
+        p.n, p.h, p.wd, p.c = x.info.shape
+        _, p.oh, p.ow, p.oc = y.info.shape
+        oc, p.kh, p.kw, c = w.info.shape
+        if oc != p.oc or c != p.c:
+            raise InvalidArgumentException("TransposeConvolution2d: weights %s do not match %d -> %d channels" % (w.info.shape, p.c, p.oc))
+        p.stride_h, p.stride_w = layer.desc["stride"]
+        p.pad_top, p.pad_left = layer.desc["pad"][0], layer.desc["pad"][2]
+        p.dil_h = p.dil_w = 1
+        p.clamp_lo, p.clamp_hi = _clamp(layer, y.info)
+        return "transpose_conv2d_q8", p
 
     def _reduce(self, layer, axes, op):
         x, y = layer.inputs[0].source, layer.outputs[0]

@@ -281,6 +281,15 @@ typedef struct {
 
 int b200k_view_copy_q(const b200k_view_copy_params* p, void* stream);
 
+/* ---- TransposeConvolution2d ----------------------------------------------------------------- */
+
+/* armnn::TransposeConvolution2dImpl (src/backends/reference/workloads/TransposeConvolution2d.cpp:14-160), NHWC,
+ * weights [OC, KH, KW, C]: every input pixel (yi, xi) adds x * w to the outputs (yi * stride_h - pad_top + ky,
+ * xi * stride_w - pad_left + kx) that lie inside the output; then the bias; then Q_y.  Takes the convolution's parameter
+ * struct: h, wd are the input's and oh, ow the output's extents; dilation, add_operand, packed, scratch, algo are unused.  Like the
+ * other contractions: exact int32 accumulation of (x - zx)(w - zw), one fp32 requantisation. */
+int b200k_transpose_conv2d_q8(const b200k_conv2d_params* p, void* stream);
+
 /* ---- Reduce ----------------------------------------------------------------------------------- */
 
 /* armnn::Reduce (src/backends/reference/workloads/Reduce.cpp:63-175, RefReduceWorkload.cpp): op follows

@@ -173,6 +173,35 @@ extern "C" int cpuref_conv2d_q8(const b200k_conv2d_params* p, int depthwise, int
     });
 }
 
+extern "C" int cpuref_transpose_conv2d_q8(const b200k_conv2d_params* p)
+{
+    return guarded([&] {
+        Harness h;
+        const unsigned N = p->n, H = p->h, W = p->wd, C = p->c, OH = p->oh, OW = p->ow, OC = p->oc, KH = p->kh, KW = p->kw;
+        TensorInfo xi = make_info(p->x, TensorShape({N, H, W, C}), 0, 0, false);
+        TensorInfo wi = make_info(p->w, TensorShape({OC, KH, KW, C}), 0, OC, true);
+        TensorInfo yi = make_info(p->y, TensorShape({N, OH, OW, OC}), 0, 0, false);
+        TransposeConvolution2dQueueDescriptor d;
+        d.m_Parameters.m_PadTop = p->pad_top; d.m_Parameters.m_PadLeft = p->pad_left;
+        d.m_Parameters.m_PadBottom = 0; d.m_Parameters.m_PadRight = 0;
+        d.m_Parameters.m_StrideX = p->stride_w; d.m_Parameters.m_StrideY = p->stride_h;
+        d.m_Parameters.m_BiasEnabled = p->bias.data != nullptr;
+        d.m_Parameters.m_DataLayout = DataLayout::NHWC;
+        ScopedTensorHandle weights(wi), bias(p->bias.data ? make_info(p->bias, TensorShape({OC}), 0, OC, true) : TensorInfo({1}, DataType::Signed32));
+        weights.Allocate(); bias.Allocate();
+        std::memcpy(weights.GetTensor<void>(), p->w.data, wi.GetNumBytes());
+        d.m_Weight = &weights;
+        if (p->bias.data) {
+            std::memcpy(bias.GetTensor<void>(), p->bias.data, OC * sizeof(int32_t));
+            d.m_Bias = &bias;
+        }
+        h.in(d, xi, p->x.data);
+        ITensorHandle* o = h.out(d, yi);
+        h.run(LayerType::TransposeConvolution2d, d);
+        copy_out(o, const_cast<void*>(p->y.data), yi.GetNumBytes());
+    });
+}
+
 extern "C" int cpuref_fully_connected_q8(const b200k_fc_params* p, int act_kind, float act_a, float act_b)
 {
     return guarded([&] {

@@ -208,6 +208,48 @@ static int conv_impl(const b200k_conv2d_params* p, int depthwise)
 int oracle_conv2d_q8(const b200k_conv2d_params* p)   { return conv_impl(p, 0); }
 int oracle_dwconv2d_q8(const b200k_conv2d_params* p) { return conv_impl(p, 1); }
 
+/* ---- TransposeConvolution2dImpl, TransposeConvolution2d.cpp:14-160 (NHWC, weights [O,H,W,I]) ---
+ * The reference's scatter loop nest with an exact int32 accumulator per output element instead of its float buffer,
+ * then bias and quantisation through the contractions' one requantisation. */
+int oracle_transpose_conv2d_q8(const b200k_conv2d_params* p)
+{
+    if (!p || !p->x.data || !p->w.data || !p->y.data) return B200K_E_INVALID;
+    const int N = p->n, H = p->h, W = p->wd, C = p->c, OH = p->oh, OW = p->ow, OC = p->oc, KH = p->kh, KW = p->kw;
+    const int zx = p->x.zero_point, zw = p->w.zero_point;
+    const int64_t total = (int64_t)N * OH * OW * OC;
+    int32_t* acc = (int32_t*)calloc((size_t)total, sizeof(int32_t));
+    if (!acc) return B200K_E_INVALID;
+    for (int b = 0; b < N; ++b)
+    for (int yi = 0; yi < H; ++yi)
+    for (int xi = 0; xi < W; ++xi) {
+        const int xo0 = xi * p->stride_w - p->pad_left, yo0 = yi * p->stride_h - p->pad_top;      /* :61-62 */
+        for (int co = 0; co < OC; ++co)
+        for (int ky = 0; ky < KH; ++ky)
+        for (int kx = 0; kx < KW; ++kx) {
+            const int yo = yo0 + ky, xo = xo0 + kx;
+            if (yo < 0 || yo >= OH || xo < 0 || xo >= OW) continue;                               /* :73 (unsigned compare) */
+            const int64_t xb = (((int64_t)b * H + yi) * W + xi) * C;
+            const int64_t wb = (((int64_t)co * KH + ky) * KW + kx) * C;
+            int32_t s = 0;
+            for (int ci = 0; ci < C; ++ci)
+                s += (load_q(p->x.data, p->x.dtype, xb + ci) - zx) * (load_q(p->w.data, p->w.dtype, wb + ci) - zw);
+            acc[(((int64_t)b * OH + yo) * OW + xo) * OC + co] += s;
+        }
+    }
+    for (int64_t i = 0; i < total; ++i) {
+        const int co = (int)(i % OC);
+        if (p->acc_out) p->acc_out[i] = acc[i];
+        const float sw = p->w.scales ? p->w.scales[co] : p->w.scale;
+        const int has_bias = p->bias.data != NULL;
+        const int32_t bq = has_bias ? ((const int32_t*)p->bias.data)[co] : 0;
+        const float sb = p->bias.scales ? p->bias.scales[co] : p->bias.scale;
+        store_q((void*)p->y.data, p->y.dtype, i,
+                requant(acc[i], p->x.scale, sw, has_bias, bq, sb, p->y.scale, p->y.zero_point, p->y.dtype, p->clamp_lo, p->clamp_hi));
+    }
+    free(acc);
+    return 0;
+}
+
 /* ---- FullyConnected, FullyConnected.cpp:13-65 --------------------------------------------- */
 
 int oracle_fully_connected_q8(const b200k_fc_params* p)

@@ -341,6 +341,50 @@ def qlstm_cases():
     }
 
 
+def tconv_cases():
+    """TransposeConvolution2d (NHWC, weights OHWI): the up-sampling shapes of decoder networks, every operand type,
+    channel counts with and without the 4-byte vector path, padding that crops the output."""
+    def make(seed, n, h, w, c, oc, k, stride, pad=(0, 0), x_dtype=S8, w_dtype=S8, y_dtype=S8, per_axis=True, x_q=(0.02, -3),
+             bias=True, out_pad=(0, 0)):
+        def build(mem):
+            rng = np.random.default_rng(seed)
+            oh = (h - 1) * stride[0] + k[0] - 2 * pad[0] + out_pad[0]
+            ow = (w - 1) * stride[1] + k[1] - 2 * pad[1] + out_pad[1]
+            p = _abi.Conv2dParams()
+            p.x = qt(mem, _rand(rng, x_dtype, (n, h, w, c)), x_dtype, *x_q)
+            wq = _rand(rng, w_dtype, (oc, k[0], k[1], c))
+            if per_axis and w_dtype == S8:
+                ws = rng.uniform(0.001, 0.01, size=oc).astype(np.float32)
+                p.w = qt(mem, wq, w_dtype, 1.0, 0, scales=ws)
+                bs = (np.float32(x_q[0]) * ws).astype(np.float32)
+                mean_sw = float(ws.mean())
+            else:
+                sw = float(np.float32(rng.uniform(0.001, 0.01)))
+                zw = 0 if w_dtype == S8 else int(rng.integers(100, 156))
+                p.w = qt(mem, wq, w_dtype, sw, zw)
+                bs, mean_sw = None, sw
+            if bias:
+                bq = rng.integers(-1000, 1001, size=oc).astype(np.int32)
+                p.bias = qt(mem, bq, S32, float(np.float32(x_q[0]) * np.float32(mean_sw)), 0, scales=bs)
+            taps = max(1, (k[0] // stride[0]) * (k[1] // stride[1])) * c
+            y_scale = float(np.float32(x_q[0] * mean_sw * 74.0 * 74.0 * np.sqrt(taps) * 3.0 / 127.0))
+            p.y, y = qt_out(mem, (n, oh, ow, oc), y_dtype, y_scale, 0 if y_dtype == S8 else 128)
+            p.n, p.h, p.wd, p.c, p.oh, p.ow, p.oc, p.kh, p.kw = n, h, w, c, oh, ow, oc, k[0], k[1]
+            p.stride_h, p.stride_w, p.pad_top, p.pad_left, p.dil_h, p.dil_w = stride[0], stride[1], pad[0], pad[1], 1, 1
+            lo, hi = RANGE[y_dtype]
+            p.clamp_lo, p.clamp_hi = lo, hi
+            return p, [y]
+        return lambda: SimpleCase("transpose_conv2d_q8", build)
+    return {
+        "up2_k2_s2": make(341, 2, 7, 6, 16, 24, (2, 2), (2, 2)),
+        "up2_k4_s2_pad1": make(342, 1, 6, 5, 32, 16, (4, 4), (2, 2), pad=(1, 1)),
+        "k3_s1_pad1_same_size": make(343, 1, 9, 8, 12, 20, (3, 3), (1, 1), pad=(1, 1)),
+        "u8_everything_k3_s2": make(344, 1, 5, 7, 8, 12, (3, 3), (2, 2), x_dtype=U8, w_dtype=U8, y_dtype=U8, per_axis=False, x_q=(0.02, 121)),
+        "odd_channels_c5_oc7_no_bias": make(345, 2, 4, 4, 5, 7, (3, 2), (2, 3), bias=False),
+        "u8_activations_s8_weights_s3": make(346, 1, 4, 5, 16, 8, (5, 5), (3, 3), pad=(2, 2), x_dtype=U8, y_dtype=U8, x_q=(0.03, 100)),
+    }
+
+
 def reduce_cases():
     """Reduce: every operation, inner / outer / several / all axes, re-quantisation, float."""
     def make(seed, shape, axes, op, dtype=S8, xq=(0.05, -3), yq=None):
@@ -442,7 +486,7 @@ def move_cases():
 
 ALL_GROUPS = {"conv": conv_cases, "dwconv": dwconv_cases, "fc": fc_cases, "bmm": bmm_cases, "pool": pool_cases,
               "mean": mean_cases, "eltwise": eltwise_cases, "activation": activation_cases, "softmax": softmax_cases,
-              "convert": convert_cases, "pad": pad_cases, "qlstm": qlstm_cases, "move": move_cases, "resize": resize_cases, "reduce": reduce_cases}
+              "convert": convert_cases, "pad": pad_cases, "qlstm": qlstm_cases, "move": move_cases, "resize": resize_cases, "reduce": reduce_cases, "tconv": tconv_cases}
 
 
 def run_case(case, where):

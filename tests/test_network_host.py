@@ -138,3 +138,14 @@ def test_data_movement_graph_mirror_views_vs_armnn_cpuref(built):
     for k in want:
         assert want[k].shape == got[k].shape and np.array_equal(want[k], got[k]), k
     assert np.array_equal(got[1], x[..., :16])
+
+
+@needs_cpuref
+def test_transpose_convolution_graph_oracle_vs_armnn_cpuref(built):
+    """Two TransposeConvolution2d layers (per-axis weights + bias + fused ReLU; per-tensor weights without bias) through
+    the real runtime on CpuRef versus the mirror's graph on the integer oracle: +-1 LSB."""
+    from test_plugin import _tconv_net
+    want, got = _run_pair(*_tconv_net(), np.int8)
+    assert want.shape == got.shape
+    st = diff_stats(want, got)
+    assert st["max_abs"] <= 1 and st["mismatch_frac"] < 5e-3, st

@@ -555,3 +555,46 @@ def test_reduce_and_general_mean_through_the_runtime_match_cpuref():
     got = hostnet.ArmnnNetwork(net, "B200Acc").run({0: x})
     for k in (0, 1, 2):
         assert ref[k].shape == got[k].shape and np.array_equal(ref[k], got[k]), k
+
+
+def _tconv_net(batch=2):
+    """A decoder step: TransposeConvolution2d (4x4, stride 2, pad 1: exact x2 up-sampling) + ReLU, then a second one
+    without bias on per-tensor unsigned weights."""
+    from armnn_b200.network import ActivationFunction, DataType, INetwork, TensorInfo
+    rng = np.random.default_rng(79)
+    net = INetwork.Create()
+    il = net.AddInputLayer(0, "input")
+    il.GetOutputSlot(0).SetTensorInfo(TensorInfo((batch, 6, 5, 16), DataType.QAsymmS8, 0.05, -3))
+    w_scales = rng.uniform(0.002, 0.01, size=24).astype(np.float32)
+    wq = rng.integers(-127, 128, size=(24, 4, 4, 16)).astype(np.int8)
+    bq = rng.integers(-500, 501, size=24).astype(np.int32)
+    wl = net.AddConstantLayer(wq, TensorInfo(wq.shape, DataType.QSymmS8, scales=w_scales, quant_dim=0), "w")
+    bl = net.AddConstantLayer(bq, TensorInfo(bq.shape, DataType.Signed32, scales=(np.float32(0.05) * w_scales), quant_dim=0), "b")
+    t1 = net.AddTransposeConvolution2dLayer((2, 2), (1, 1, 1, 1), True, "up1")
+    il.GetOutputSlot(0).Connect(t1.GetInputSlot(0))
+    wl.GetOutputSlot(0).Connect(t1.GetInputSlot(1))
+    bl.GetOutputSlot(0).Connect(t1.GetInputSlot(2))
+    y1 = TensorInfo((batch, 12, 10, 24), DataType.QAsymmS8, 0.12, -128)
+    t1.GetOutputSlot(0).SetTensorInfo(y1)
+    al = net.AddActivationLayer(ActivationFunction.ReLu, name="relu")
+    t1.GetOutputSlot(0).Connect(al.GetInputSlot(0))
+    al.GetOutputSlot(0).SetTensorInfo(y1)
+    w2 = rng.integers(-127, 128, size=(8, 2, 2, 24)).astype(np.int8)
+    w2l = net.AddConstantLayer(w2, TensorInfo(w2.shape, DataType.QAsymmS8, 0.004, 0), "w2")
+    t2 = net.AddTransposeConvolution2dLayer((2, 2), (0, 0, 0, 0), False, "up2")
+    al.GetOutputSlot(0).Connect(t2.GetInputSlot(0))
+    w2l.GetOutputSlot(0).Connect(t2.GetInputSlot(1))
+    t2.GetOutputSlot(0).SetTensorInfo(TensorInfo((batch, 24, 20, 8), DataType.QAsymmS8, 0.2, 3))
+    ol = net.AddOutputLayer(0, "output")
+    t2.GetOutputSlot(0).Connect(ol.GetInputSlot(0))
+    return net, {"input_shape": (batch, 6, 5, 16), "output_shape": (batch, 24, 20, 8)}
+
+
+@needs_plugin
+@pytest.mark.gpu
+def test_transpose_convolution_through_the_runtime_matches_cpuref():
+    net, info = _tconv_net()
+    _, ref, got = _pair(net, info, np.int8)
+    assert ref.shape == got.shape
+    st = diff_stats(ref, got)
+    assert st["max_abs"] <= 1 and st["mismatch_frac"] < 5e-3, st
