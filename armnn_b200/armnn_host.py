@@ -196,7 +196,8 @@ class ArmnnNetwork:
                 r = len(d["begin"])
                 arr = lambda v: (C.c_int32 * r)(*v)
                 lid = lib.armnnc_add_strided_slice(net, r, arr(d["begin"]), arr(d["end"]), arr(d["stride"]), d["begin_mask"],
-                                                   d["end_mask"], d["shrink_axis_mask"])
+                                                   d["end_mask"], d["shrink_axis_mask"], d.get("ellipsis_mask", 0),
+                                                   d.get("new_axis_mask", 0))
             elif t == "Slice":
                 r = len(d["begin"])
                 lid = lib.armnnc_add_slice(net, r, (C.c_int32 * r)(*d["begin"]), (C.c_int32 * r)(*d["size"]))

@@ -352,10 +352,11 @@ int armnnc_add_permute(void* vn, int rank, const int32_t* mappings, int transpos
 }
 
 int armnnc_add_strided_slice(void* vn, int rank, const int32_t* begin, const int32_t* end, const int32_t* stride,
-                             int begin_mask, int end_mask, int shrink_axis_mask)
+                             int begin_mask, int end_mask, int shrink_axis_mask, int ellipsis_mask, int new_axis_mask)
 {
     auto* n = static_cast<CNet*>(vn);
     StridedSliceDescriptor d;
+    d.m_EllipsisMask = ellipsis_mask; d.m_NewAxisMask = new_axis_mask;
     d.m_Begin.assign(begin, begin + rank);
     d.m_End.assign(end, end + rank);
     d.m_Stride.assign(stride, stride + rank);

@@ -366,6 +366,8 @@ def IsLayerSupported(layer):
     if t in ("Permute", "Transpose", "StridedSlice", "Slice"):
         if len(ins[0].shape) > (4 if t == "StridedSlice" else 6):
             return False, "%s: rank not supported" % t
+        if t == "StridedSlice" and (layer.desc.get("ellipsis_mask", 0) or layer.desc.get("new_axis_mask", 0)):
+            return False, "StridedSlice: ellipsis and new-axis masks are not supported"
         if ins[0].dtype != outs[0].dtype or not outs[0].same_quantization(ins[0]):
             return False, "%s: input and output must share type and quantisation (the reference copies raw elements)" % t
         return True, ""
