@@ -1,0 +1,91 @@
+"""armnn_b200/views.py (descriptor -> rectangular view copies) against numpy's own indexing, on the CPU: the host logic
+behind Concat, Splitter, Permute, Transpose, StridedSlice and Slice.  (The same descriptors run against the real CpuRef
+workloads in test_oracle_vs_cpuref.py and on the GPU in test_kernels_gpu.py.)"""
+import numpy as np
+import pytest
+
+from armnn_b200 import views as V
+
+
+def apply_view(src, dst, view):
+    """The copy `b200k_view_copy_q` performs, in numpy, through flat buffers."""
+    shape, so, ss, do, ds = view
+    s, d = src.reshape(-1), dst.reshape(-1)
+    for idx in np.ndindex(*shape):
+        d[do + sum(i * st for i, st in zip(idx, ds))] = s[so + sum(i * st for i, st in zip(idx, ss))]
+
+
+def test_permute_and_transpose_views_match_numpy():
+    rng = np.random.default_rng(1)
+    x = rng.integers(-128, 128, size=(2, 3, 4, 5)).astype(np.int8)
+    for perm in [(0, 2, 3, 1), (3, 2, 1, 0), (1, 0, 3, 2), (0, 1, 2, 3)]:
+        # Transpose: destination dimension i is source dimension perm[i] (numpy's convention)
+        out_shape, view = V.permute_view(x.shape, perm, transpose=True)
+        want = np.transpose(x, perm)
+        assert tuple(out_shape) == want.shape
+        got = np.zeros(out_shape, np.int8)
+        apply_view(x, got, view)
+        assert np.array_equal(got, want)
+        # Permute: source dimension i goes to destination dimension perm[i] (the inverse permutation for numpy)
+        out_shape, view = V.permute_view(x.shape, perm, transpose=False)
+        want = np.transpose(x, np.argsort(perm))
+        assert tuple(out_shape) == want.shape
+        got = np.zeros(out_shape, np.int8)
+        apply_view(x, got, view)
+        assert np.array_equal(got, want)
+    with pytest.raises(ValueError):
+        V.permute_view((2, 3), (0, 0))
+
+
+def test_concat_and_splitter_views_match_numpy():
+    rng = np.random.default_rng(2)
+    a = rng.integers(0, 255, size=(2, 3, 4)).astype(np.uint8)
+    b = rng.integers(0, 255, size=(2, 5, 4)).astype(np.uint8)
+    want = np.concatenate([a, b], axis=1)
+    got = np.zeros_like(want)
+    vs = V.concat_views(want.shape, [a.shape, b.shape], [(0, 0, 0), (0, 3, 0)])
+    for src, view in zip([b, a], vs):                      # (issued last view first)
+        apply_view(src, got, view)
+    assert np.array_equal(got, want)
+    outs = [np.zeros_like(a), np.zeros_like(b)]
+    for out, view in zip(outs, V.splitter_views(want.shape, [a.shape, b.shape], [(0, 0, 0), (0, 3, 0)])):
+        apply_view(want, out, view)
+    assert np.array_equal(outs[0], a) and np.array_equal(outs[1], b)
+    with pytest.raises(ValueError):
+        V.concat_views((2, 4), [(2, 3)], [(0, 2)])
+
+
+@pytest.mark.parametrize("begin,end,stride,bm,em,sm,py", [
+    ((1, 0, 2), (3, 5, 6), (1, 2, 1), 0, 0, 0, (slice(1, 3), slice(0, 5, 2), slice(2, 6))),
+    ((0, -1, 0), (0, 0, 0), (1, -1, 2), 0b001, 0b111, 0, (slice(None), slice(None, None, -1), slice(None, None, 2))),
+    ((2, 1, 0), (0, 4, 0), (1, 1, 1), 0, 0b100, 0b001, (2, slice(1, 4), slice(None))),
+    ((-3, 0, -2), (-1, 5, 7), (1, 3, 1), 0, 0, 0, (slice(-3, -1), slice(0, 5, 3), slice(-2, 7))),
+])
+def test_strided_slice_views_match_numpy(begin, end, stride, bm, em, sm, py):
+    x = np.arange(4 * 5 * 7, dtype=np.int16).reshape(4, 5, 7)
+    walk, out_shape, view = V.strided_slice_view(x.shape, begin, end, stride, bm, em, sm)
+    want = x[py]
+    assert tuple(out_shape) == want.shape
+    got = np.zeros(walk, np.int16)
+    apply_view(x, got, view)
+    assert np.array_equal(got.reshape(want.shape), want)
+
+
+def test_slice_view_and_dimension_merging():
+    x = np.arange(2 * 6 * 8 * 16, dtype=np.int32).reshape(2, 6, 8, 16)
+    out_shape, view = V.slice_view(x.shape, (1, 2, 0, 0), (1, 3, 8, 16))
+    got = np.zeros(out_shape, np.int32)
+    apply_view(x, got, view)
+    assert np.array_equal(got, x[1:2, 2:5])
+    # whole rows and whole pixels are contiguous on both sides: one long row after merging
+    merged = V.merge_dims(view)
+    assert merged[0] == (3 * 8 * 16,) and merged[2] == [1] and merged[4] == [1]
+    got2 = np.zeros(out_shape, np.int32)
+    apply_view(x, got2, merged)
+    assert np.array_equal(got2, got)
+    # a channel slice keeps the pixel dimension apart
+    _, view = V.slice_view(x.shape, (0, 0, 0, 4), (2, 6, 8, 8))
+    merged = V.merge_dims(view)
+    assert merged[0] == (2 * 6 * 8, 8)
+    with pytest.raises(ValueError):
+        V.slice_view(x.shape, (0, 0, 0, 10), (2, 6, 8, 8))
