@@ -174,6 +174,13 @@ class ArmnnNetwork:
                     bdata.ctypes.data_as(C.c_void_p) if bdata is not None else None, C.c_float(bscale),
                     bsc.ctypes.data_as(C.c_void_p) if bsc is not None else None, len(bsc) if bsc is not None else 0)
                 assert lid >= 0, lib.armnnc_last_error().decode()
+            elif t in ("DepthToSpace", "SpaceToDepth"):
+                lid = lib.armnnc_add_depth_to_space(net, d["block"], int(d["nchw"]), int(t == "SpaceToDepth"))
+            elif t == "ChannelShuffle":
+                lid = lib.armnnc_add_channel_shuffle(net, d["axis"], d["groups"])
+            elif t == "Stack":
+                ish = layer.inputs[0].source.info.shape
+                lid = lib.armnnc_add_stack(net, d["axis"], len(layer.inputs), len(ish), _shape_arr(ish))
             elif t == "Reduce":
                 axes = (C.c_int32 * len(d["axis"]))(*d["axis"])
                 lid = lib.armnnc_add_reduce(net, axes, len(d["axis"]), d["op"], int(d["keep_dims"]))

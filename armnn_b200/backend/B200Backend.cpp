@@ -157,10 +157,22 @@ public:
                 }
                 return true;
             }
+            case LayerType::SpaceToDepth:
+            case LayerType::ChannelShuffle:
+            case LayerType::Stack:
+            {
+                // through Decoder / Encoder in the reference: one element type, the quantisation may differ
+                for (const TensorInfo& t : infos)
+                {
+                    if (!IsMoveType(t) || t.GetDataType() != infos[0].GetDataType() || t.GetNumDimensions() > 6) { return No(reason, "unsupported or mismatched data types, or rank > 6"); }
+                }
+                return true;
+            }
             case LayerType::Permute:
             case LayerType::Transpose:
             case LayerType::Slice:
             case LayerType::StridedSlice:
+            case LayerType::DepthToSpace:
             {
                 if (infos[0].GetNumDimensions() > 6) { return No(reason, "rank > 6"); }
                 if (!IsMoveType(infos[0]) || infos[0].GetDataType() != infos[1].GetDataType()) { return No(reason, "unsupported or mismatched data types"); }

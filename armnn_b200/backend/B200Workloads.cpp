@@ -331,6 +331,96 @@ std::unique_ptr<IWorkload> MakeStridedSlice(const QueueDescriptor& d, const Work
     return MakeViews<StridedSliceQueueDescriptor>(d, info, ctx, st);
 }
 
+// One view over a walk of up to six dimensions given as (extent, source stride) pairs; the destination is dense.
+template <typename QD>
+std::unique_ptr<IWorkload> MakeWalk(const QueueDescriptor& d, const WorkloadInfo& info, const ContextPtr& ctx,
+                                    const std::vector<std::pair<int64_t, int64_t>>& walk)
+{
+    auto st = std::make_shared<ViewState>(ctx);
+    ViewOp op = NewViewOp(info.m_InputTensorInfos[0], info.m_OutputTensorInfos[0], st->blobs, 0, 0, static_cast<unsigned int>(walk.size()));
+    int64_t count = 1, dstStride = 1;
+    for (size_t i = walk.size(); i-- > 0;)
+    {
+        op.p.shape[i] = static_cast<int32_t>(walk[i].first);
+        op.p.src_strides[i] = walk[i].second;
+        op.p.dst_strides[i] = dstStride;
+        dstStride *= walk[i].first;
+        count *= walk[i].first;
+    }
+    if (static_cast<unsigned int>(count) != info.m_OutputTensorInfos[0].GetNumElements() ||
+        info.m_InputTensorInfos[0].GetNumElements() != info.m_OutputTensorInfos[0].GetNumElements())
+    {
+        throw InvalidArgumentException("B200Acc: output shape does not match the layer's rearrangement of the input");
+    }
+    st->ops.push_back(op);
+    return MakeViews<QD>(d, info, ctx, st);
+}
+
+// DepthToSpace (workloads/DepthToSpace.cpp:15-100) and SpaceToDepth (workloads/SpaceToDepth.cpp:42-104), both layouts.
+template <typename QD>
+std::unique_ptr<IWorkload> MakeDepthSpace(const QueueDescriptor& d, const WorkloadInfo& info, const ContextPtr& ctx, bool toSpace)
+{
+    const auto& qd = *PolymorphicDowncast<const QD*>(&d);
+    const TensorShape& s = info.m_InputTensorInfos[0].GetShape();
+    if (s.GetNumDimensions() != 4 || qd.m_Parameters.m_BlockSize == 0) { throw InvalidArgumentException("B200Acc: DepthToSpace / SpaceToDepth need 4-D tensors and a block size"); }
+    const bool nchw = qd.m_Parameters.m_DataLayout == DataLayout::NCHW;
+    const int64_t b = qd.m_Parameters.m_BlockSize;
+    int64_t is[6];
+    DenseStrides(s, is);
+    const int64_t n = s[0], c = nchw ? s[1] : s[3], h = nchw ? s[2] : s[1], w = nchw ? s[3] : s[2];
+    if (toSpace)
+    {
+        if (c % (b * b) != 0) { throw InvalidArgumentException("B200Acc: DepthToSpace channels are not a multiple of the block size squared"); }
+        const int64_t co = c / (b * b);
+        if (nchw) { return MakeWalk<QD>(d, info, ctx, {{n, is[0]}, {co, is[1]}, {h, is[2]}, {b, b * co * is[1]}, {w, is[3]}, {b, co * is[1]}}); }
+        return MakeWalk<QD>(d, info, ctx, {{n, is[0]}, {h, is[1]}, {b, b * co}, {w, is[2]}, {b, co}, {co, 1}});
+    }
+    if (h % b != 0 || w % b != 0) { throw InvalidArgumentException("B200Acc: SpaceToDepth height / width are not multiples of the block size"); }
+    if (nchw) { return MakeWalk<QD>(d, info, ctx, {{n, is[0]}, {b, is[2]}, {b, is[3]}, {c, is[1]}, {h / b, b * is[2]}, {w / b, b * is[3]}}); }
+    return MakeWalk<QD>(d, info, ctx, {{n, is[0]}, {h / b, b * is[1]}, {w / b, b * is[2]}, {b, is[1]}, {b, is[2]}, {c, 1}});
+}
+
+// ChannelShuffle (RefChannelShuffleWorkload.cpp:28-76): output channel i g + j is input channel i + j s.
+std::unique_ptr<IWorkload> MakeChannelShuffle(const QueueDescriptor& d, const WorkloadInfo& info, const ContextPtr& ctx)
+{
+    const auto& qd = *PolymorphicDowncast<const ChannelShuffleQueueDescriptor*>(&d);
+    const TensorShape& s = info.m_InputTensorInfos[0].GetShape();
+    const unsigned int axis = qd.m_Parameters.m_Axis, g = qd.m_Parameters.m_NumGroups;
+    if (axis >= s.GetNumDimensions() || g == 0 || s[axis] % g != 0) { throw InvalidArgumentException("B200Acc: ChannelShuffle groups do not divide the channel count"); }
+    int64_t outer = 1, inner = 1;
+    for (unsigned int i = 0; i < axis; ++i) { outer *= s[i]; }
+    for (unsigned int i = axis + 1; i < s.GetNumDimensions(); ++i) { inner *= s[i]; }
+    const int64_t size = s[axis] / g;
+    return MakeWalk<ChannelShuffleQueueDescriptor>(d, info, ctx, {{outer, s[axis] * inner}, {size, inner}, {g, size * inner}, {inner, 1}});
+}
+
+// Stack (workloads/Stack.cpp:14-120): input i becomes index i of the new dimension.
+std::unique_ptr<IWorkload> MakeStack(const QueueDescriptor& d, const WorkloadInfo& info, const ContextPtr& ctx)
+{
+    const auto& qd = *PolymorphicDowncast<const StackQueueDescriptor*>(&d);
+    auto st = std::make_shared<ViewState>(ctx);
+    const TensorInfo& out = info.m_OutputTensorInfos[0];
+    const unsigned int axis = qd.m_Parameters.m_Axis, inRank = info.m_InputTensorInfos[0].GetNumDimensions();
+    if (axis > inRank || out.GetNumDimensions() != inRank + 1 || inRank + 1 > 6) { throw InvalidArgumentException("B200Acc: Stack axis or rank not supported"); }
+    int64_t os[6];
+    DenseStrides(out.GetShape(), os);
+    for (unsigned int v = 0; v < info.m_InputTensorInfos.size(); ++v)
+    {
+        const TensorInfo& in = info.m_InputTensorInfos[v];
+        if (in.GetShape() != info.m_InputTensorInfos[0].GetShape()) { throw InvalidArgumentException("B200Acc: Stack inputs must share one shape"); }
+        ViewOp op = NewViewOp(in, out, st->blobs, v, 0, inRank);
+        DenseStrides(in.GetShape(), op.p.src_strides);
+        for (unsigned int i = 0; i < inRank; ++i)
+        {
+            op.p.shape[i] = static_cast<int32_t>(in.GetShape()[i]);
+            op.p.dst_strides[i] = os[i < axis ? i : i + 1];
+        }
+        op.p.dst_offset = static_cast<int64_t>(v) * os[axis];
+        st->ops.push_back(op);
+    }
+    return MakeViews<StackQueueDescriptor>(d, info, ctx, st);
+}
+
 std::unique_ptr<IWorkload> MakeSlice(const QueueDescriptor& d, const WorkloadInfo& info, const ContextPtr& ctx)
 {
     const auto& qd = *PolymorphicDowncast<const SliceQueueDescriptor*>(&d);
@@ -961,6 +1051,10 @@ std::unique_ptr<IWorkload> B200WorkloadFactory::CreateWorkload(LayerType type, c
         case LayerType::Transpose:    return MakePermute<TransposeQueueDescriptor>(d, info, ctx, true);
         case LayerType::StridedSlice: return MakeStridedSlice(d, info, ctx);
         case LayerType::Slice:        return MakeSlice(d, info, ctx);
+        case LayerType::DepthToSpace: return MakeDepthSpace<DepthToSpaceQueueDescriptor>(d, info, ctx, true);
+        case LayerType::SpaceToDepth: return MakeDepthSpace<SpaceToDepthQueueDescriptor>(d, info, ctx, false);
+        case LayerType::ChannelShuffle: return MakeChannelShuffle(d, info, ctx);
+        case LayerType::Stack:        return MakeStack(d, info, ctx);
         case LayerType::QLstm:
             return MakeQLstm(d, info, ctx);
         case LayerType::PreCompiled:

@@ -399,6 +399,32 @@ int armnnc_add_transpose_conv2d(void* vn, int stride_h, int stride_w, int pad_to
     } catch (const std::exception& e) { g_err = e.what(); return -1; }
 }
 
+int armnnc_add_depth_to_space(void* vn, int block, int nchw, int inverse)
+{
+    auto* n = static_cast<CNet*>(vn);
+    SpaceToDepthDescriptor d;              // (DepthToSpaceDescriptor is an alias of it)
+    d.m_BlockSize = (unsigned)block;
+    d.m_DataLayout = nchw ? DataLayout::NCHW : DataLayout::NHWC;
+    return add_layer(n, inverse ? n->net->AddSpaceToDepthLayer(d) : n->net->AddDepthToSpaceLayer(d));
+}
+
+int armnnc_add_channel_shuffle(void* vn, int axis, int groups)
+{
+    auto* n = static_cast<CNet*>(vn);
+    ChannelShuffleDescriptor d;
+    d.m_Axis = (uint32_t)axis; d.m_NumGroups = (uint32_t)groups;
+    return add_layer(n, n->net->AddChannelShuffleLayer(d));
+}
+
+int armnnc_add_stack(void* vn, int axis, int num_inputs, int rank, const int32_t* input_shape)
+{
+    auto* n = static_cast<CNet*>(vn);
+    unsigned dims[6] = {1, 1, 1, 1, 1, 1};
+    for (int i = 0; i < rank && i < 6; ++i) dims[i] = (unsigned)input_shape[i];
+    StackDescriptor d((uint32_t)axis, (uint32_t)num_inputs, TensorShape((unsigned)rank, dims));
+    return add_layer(n, n->net->AddStackLayer(d));
+}
+
 int armnnc_add_reduce(void* vn, const int32_t* axes, int n_axes, int operation, int keep_dims)
 {
     auto* n = static_cast<CNet*>(vn);

@@ -256,6 +256,19 @@ class INetwork:
     def AddSliceLayer(self, begin, size, name=None):
         return self._add(Layer("Slice", name, 1, 1, {"begin": tuple(int(x) for x in begin), "size": tuple(int(x) for x in size)}))
 
+    def AddDepthToSpaceLayer(self, block_size, nchw=False, name=None):
+        return self._add(Layer("DepthToSpace", name, 1, 1, {"block": int(block_size), "nchw": bool(nchw)}))
+
+    def AddSpaceToDepthLayer(self, block_size, nchw=False, name=None):
+        return self._add(Layer("SpaceToDepth", name, 1, 1, {"block": int(block_size), "nchw": bool(nchw)}))
+
+    def AddChannelShuffleLayer(self, axis, num_groups, name=None):
+        return self._add(Layer("ChannelShuffle", name, 1, 1, {"axis": int(axis), "groups": int(num_groups)}))
+
+    def AddStackLayer(self, axis, num_inputs, name=None):
+        """armnn::StackDescriptor (the input shape is taken from the connected inputs)."""
+        return self._add(Layer("Stack", name, int(num_inputs), 1, {"axis": int(axis)}))
+
     def AddTransposeConvolution2dLayer(self, stride=(1, 1), pad=(0, 0, 0, 0), bias_enabled=True, name=None):
         """pad = (top, bottom, left, right); NHWC; inputs: 0 data, 1 weights [O,H,W,I], 2 bias (Constant layers: the Arm NN
         API takes them as ConstTensor arguments of the layer, armnn::INetwork::AddTransposeConvolution2dLayer)."""
@@ -363,7 +376,12 @@ def IsLayerSupported(layer):
         if len(ins[0].shape) > 6 or any(i.dtype != ins[0].dtype for i in list(ins) + list(outs)):
             return False, "%s: rank > 6 or mismatched data types" % t
         return True, ""
-    if t in ("Permute", "Transpose", "StridedSlice", "Slice"):
+    if t in ("SpaceToDepth", "ChannelShuffle", "Stack"):
+        # through Decoder / Encoder in the reference: one element type, quantisation may differ
+        if len(outs[0].shape) > 6 or any(i.dtype != outs[0].dtype for i in ins):
+            return False, "%s: rank > 6 or mismatched data types" % t
+        return True, ""
+    if t in ("Permute", "Transpose", "StridedSlice", "Slice", "DepthToSpace"):
         if len(ins[0].shape) > (4 if t == "StridedSlice" else 6):
             return False, "%s: rank not supported" % t
         if t == "StridedSlice" and (layer.desc.get("ellipsis_mask", 0) or layer.desc.get("new_axis_mask", 0)):
@@ -827,6 +845,34 @@ class GraphProgram:
         if y.info.GetNumElements() != int(np.prod(walk)):
             raise InvalidArgumentException("StridedSlice: output shape %s does not hold the slice %s" % (y.info.shape, walk))
         return self._view_copy(x, y, v)
+
+    def _make_DepthToSpace(self, layer):
+        x, y = layer.inputs[0].source, layer.outputs[0]
+        out_shape, v = views.depth_to_space_view(x.info.shape, layer.desc["block"], layer.desc["nchw"])
+        if tuple(out_shape) != tuple(y.info.shape):
+            raise InvalidArgumentException("DepthToSpace: output shape %s, expected %s" % (y.info.shape, out_shape))
+        return self._view_copy(x, y, v)
+
+    def _make_SpaceToDepth(self, layer):
+        x, y = layer.inputs[0].source, layer.outputs[0]
+        out_shape, v = views.space_to_depth_view(x.info.shape, layer.desc["block"], layer.desc["nchw"])
+        if tuple(out_shape) != tuple(y.info.shape):
+            raise InvalidArgumentException("SpaceToDepth: output shape %s, expected %s" % (y.info.shape, out_shape))
+        return self._view_copy(x, y, v)
+
+    def _make_ChannelShuffle(self, layer):
+        x, y = layer.inputs[0].source, layer.outputs[0]
+        if tuple(x.info.shape) != tuple(y.info.shape):
+            raise InvalidArgumentException("ChannelShuffle: input and output shapes differ")
+        return self._view_copy(x, y, views.channel_shuffle_view(x.info.shape, layer.desc["axis"], layer.desc["groups"]))
+
+    def _make_Stack(self, layer):
+        y = layer.outputs[0]
+        srcs = [s.source for s in layer.inputs]
+        out_shape, vs = views.stack_views(srcs[0].info.shape, len(srcs), layer.desc["axis"])
+        if tuple(out_shape) != tuple(y.info.shape) or any(tuple(x.info.shape) != tuple(srcs[0].info.shape) for x in srcs):
+            raise InvalidArgumentException("Stack: inputs must share one shape and the output must be %s" % (out_shape,))
+        return [self._view_copy(x, y, v) for x, v in zip(srcs, vs)]
 
     def _make_Slice(self, layer):
         x, y = layer.inputs[0].source, layer.outputs[0]

@@ -12,6 +12,7 @@ rules once in a form that is easy to test against CpuRef:
   Transpose (`src/armnnUtils/Transpose.cpp:22-117`): `mappings[i]` is the source dimension of destination dimension i.
 * StridedSlice (`src/armnn/Descriptors.cpp:393-453`, `workloads/StridedSlice.cpp:188-222`) with begin / end / shrink-axis
   masks (ellipsis and new-axis masks are refused by layer support); Slice (`workloads/Slice.cpp:14-147`).
+* DepthToSpace, SpaceToDepth, ChannelShuffle and Stack: six- or four-dimensional walks over the same bytes.
 """
 
 INT_MIN, INT_MAX = -(1 << 31), (1 << 31) - 1
@@ -103,6 +104,82 @@ def slice_view(in_shape, begin, size):
     ss = dense_strides(in_shape)
     out_shape = tuple(int(s) for s in size)
     return out_shape, (out_shape, sum(b * s for b, s in zip(begin, ss)), ss, 0, dense_strides(out_shape))
+
+
+def depth_to_space_view(in_shape, block, nchw=False):
+    """(out_shape, view) of DepthToSpace (`workloads/DepthToSpace.cpp:15-100`): the input read as
+    [N, H, W, block, block, C'] (NHWC) or [N, block, block, C', H, W] (NCHW) and permuted to
+    [N, H, block, W, block, C'] / [N, C', H, block, W, block]."""
+    b = int(block)
+    ss = dense_strides(in_shape)
+    if nchw:
+        n, c, h, w = in_shape
+        if b < 1 or c % (b * b):
+            raise ValueError("DepthToSpace: %d channels are not a multiple of block size %d squared" % (c, b))
+        co = c // (b * b)
+        out_shape = (n, co, h * b, w * b)
+        # destination order n, c', h, i, w, j; source index ((i * b + j) * co + c') in the channel dimension
+        walk = (n, co, h, b, w, b)
+        src = [ss[0], ss[1], ss[2], b * co * ss[1], ss[3], co * ss[1]]
+    else:
+        n, h, w, c = in_shape
+        if b < 1 or c % (b * b):
+            raise ValueError("DepthToSpace: %d channels are not a multiple of block size %d squared" % (c, b))
+        co = c // (b * b)
+        out_shape = (n, h * b, w * b, co)
+        walk = (n, h, b, w, b, co)
+        src = [ss[0], ss[1], b * co, ss[2], co, 1]
+    return out_shape, (walk, 0, src, 0, dense_strides(walk))
+
+
+def space_to_depth_view(in_shape, block, nchw=False):
+    """(out_shape, view) of SpaceToDepth (`workloads/SpaceToDepth.cpp:42-104`): output channel oc reads input channel
+    oc % C at the spatial offset (oc / C) / block, (oc / C) % block inside the block."""
+    b = int(block)
+    ss = dense_strides(in_shape)
+    if nchw:
+        n, c, h, w = in_shape
+        if b < 1 or h % b or w % b:
+            raise ValueError("SpaceToDepth: %dx%d is not a multiple of block size %d" % (h, w, b))
+        out_shape = (n, c * b * b, h // b, w // b)
+        walk = (n, b, b, c, h // b, w // b)
+        src = [ss[0], ss[2], ss[3], ss[1], b * ss[2], b * ss[3]]
+    else:
+        n, h, w, c = in_shape
+        if b < 1 or h % b or w % b:
+            raise ValueError("SpaceToDepth: %dx%d is not a multiple of block size %d" % (h, w, b))
+        out_shape = (n, h // b, w // b, c * b * b)
+        walk = (n, h // b, w // b, b, b, c)
+        src = [ss[0], b * ss[1], b * ss[2], ss[1], ss[2], 1]
+    return out_shape, (walk, 0, src, 0, dense_strides(walk))
+
+
+def channel_shuffle_view(shape, axis, groups):
+    """View of ChannelShuffle (`workloads/RefChannelShuffleWorkload.cpp:28-76`): with g groups of s channels, output
+    channel i * g + j is input channel i + j * s."""
+    rank = len(shape)
+    if not (0 <= axis < rank) or groups < 1 or shape[axis] % groups:
+        raise ValueError("ChannelShuffle: %d channels cannot be split into %d groups" % (shape[axis], groups))
+    size = shape[axis] // groups
+    outer = 1
+    for d in shape[:axis]:
+        outer *= int(d)
+    inner = 1
+    for d in shape[axis + 1:]:
+        inner *= int(d)
+    walk = (outer, size, groups, inner)
+    return (walk, 0, [shape[axis] * inner, inner, size * inner, 1], 0, dense_strides(walk))
+
+
+def stack_views(in_shape, num_inputs, axis):
+    """(out_shape, views) of Stack (`workloads/Stack.cpp:14-120`): input i becomes index i of a new dimension `axis`."""
+    rank = len(in_shape)
+    if not (0 <= axis <= rank) or num_inputs < 1:
+        raise ValueError("Stack: axis %d outside [0, %d]" % (axis, rank))
+    out_shape = tuple(in_shape[:axis]) + (num_inputs,) + tuple(in_shape[axis:])
+    os_ = dense_strides(out_shape)
+    ds = os_[:axis] + os_[axis + 1:]
+    return out_shape, [(tuple(in_shape), 0, dense_strides(in_shape), i * os_[axis], ds) for i in range(num_inputs)]
 
 
 def merge_dims(view, max_rank=6):

@@ -256,7 +256,7 @@ typedef struct {
 
 int b200k_pad_q(const b200k_pad_params* p, void* stream);
 
-/* ---- Concat, Splitter, Permute, Transpose, StridedSlice, Slice ---------------------------------- */
+/* ---- Concat, Splitter, Permute, Transpose, StridedSlice, Slice, DepthToSpace, SpaceToDepth, ChannelShuffle, Stack ---- */
 
 /* One rectangular view of a tensor copied onto a view of another one:
  *     y[dst_offset + sum_d i_d dst_strides[d]] = Q_y(deq_x(x[src_offset + sum_d i_d src_strides[d]]))   for 0 <= i_d < shape[d]
@@ -269,7 +269,10 @@ int b200k_pad_q(const b200k_pad_params* p, void* stream);
  *   armnnUtils::Permute / Transpose (src/armnnUtils/Permute.cpp:22-119, Transpose.cpp:22-117; RefPermuteWorkload.cpp,
  *     RefTransposeWorkload.cpp): the source strides in the destination's order of dimensions;
  *   armnn::StridedSlice (workloads/StridedSlice.cpp:90-223) and armnn::Slice (workloads/Slice.cpp:14-147): source
- *     offset from the begin indices, source strides multiplied by the slice's strides.
+ *     offset from the begin indices, source strides multiplied by the slice's strides;
+ *   armnn::DepthToSpace (workloads/DepthToSpace.cpp:15-100), SpaceToDepth (workloads/SpaceToDepth.cpp:42-104),
+ *     ChannelShuffle (RefChannelShuffleWorkload.cpp:28-76): six- or four-dimensional walks over the same elements;
+ *   armnn::Stack (workloads/Stack.cpp:14-120): one call per input, placed at its index of the new dimension.
  * The host side (the plugin's workloads, armnn_b200/views.py) turns the layer descriptors into these views. */
 typedef struct {
     b200k_qtensor x, y;

@@ -525,6 +525,47 @@ extern "C" int cpuref_move_q(const oracle_move_params* p)
                 copy_out(outs[0], const_cast<void*>(p->view[0].data), views[0].GetNumBytes());
                 break;
             }
+            case MOVE_DEPTH_TO_SPACE: {
+                DepthToSpaceQueueDescriptor d;
+                d.m_Parameters.m_BlockSize = (unsigned)p->perm[0];
+                d.m_Parameters.m_DataLayout = p->perm[1] ? DataLayout::NCHW : DataLayout::NHWC;
+                h.in(d, whole, p->whole.data);
+                outs.push_back(h.out(d, views[0]));
+                h.run(LayerType::DepthToSpace, d);
+                copy_out(outs[0], const_cast<void*>(p->view[0].data), views[0].GetNumBytes());
+                break;
+            }
+            case MOVE_SPACE_TO_DEPTH: {
+                SpaceToDepthQueueDescriptor d;
+                d.m_Parameters.m_BlockSize = (unsigned)p->perm[0];
+                d.m_Parameters.m_DataLayout = p->perm[1] ? DataLayout::NCHW : DataLayout::NHWC;
+                h.in(d, whole, p->whole.data);
+                outs.push_back(h.out(d, views[0]));
+                h.run(LayerType::SpaceToDepth, d);
+                copy_out(outs[0], const_cast<void*>(p->view[0].data), views[0].GetNumBytes());
+                break;
+            }
+            case MOVE_CHANNEL_SHUFFLE: {
+                ChannelShuffleQueueDescriptor d;
+                d.m_Parameters.m_Axis = (uint32_t)p->perm[0];
+                d.m_Parameters.m_NumGroups = (uint32_t)p->perm[1];
+                h.in(d, whole, p->whole.data);
+                outs.push_back(h.out(d, views[0]));
+                h.run(LayerType::ChannelShuffle, d);
+                copy_out(outs[0], const_cast<void*>(p->view[0].data), views[0].GetNumBytes());
+                break;
+            }
+            case MOVE_STACK: {
+                StackQueueDescriptor d;
+                d.m_Parameters.m_Axis = (uint32_t)p->perm[0];
+                d.m_Parameters.m_NumInputs = (uint32_t)p->n_views;
+                d.m_Parameters.m_InputShape = views[0].GetShape();
+                for (int v = 0; v < p->n_views; ++v) h.in(d, views[(size_t)v], p->view[v].data);
+                ITensorHandle* o = h.out(d, whole);
+                h.run(LayerType::Stack, d);
+                copy_out(o, const_cast<void*>(p->whole.data), whole.GetNumBytes());
+                break;
+            }
             default: throw InvalidArgumentException("cpuref_move_q: unknown kind");
         }
     });

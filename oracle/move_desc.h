@@ -5,7 +5,10 @@
 #define ORACLE_MOVE_DESC_H
 #include "../include/b200k.h"
 
-enum { MOVE_CONCAT = 0, MOVE_SPLIT = 1, MOVE_PERMUTE = 2, MOVE_TRANSPOSE = 3, MOVE_STRIDED_SLICE = 4, MOVE_SLICE = 5 };
+enum { MOVE_CONCAT = 0, MOVE_SPLIT = 1, MOVE_PERMUTE = 2, MOVE_TRANSPOSE = 3, MOVE_STRIDED_SLICE = 4, MOVE_SLICE = 5,
+       MOVE_DEPTH_TO_SPACE = 6, MOVE_SPACE_TO_DEPTH = 7,      /* perm[0] = block size, perm[1] = 1 for NCHW */
+       MOVE_CHANNEL_SHUFFLE = 8,                              /* perm[0] = axis, perm[1] = groups */
+       MOVE_STACK = 9 };                                      /* perm[0] = axis; whole = the output, views = the inputs */
 
 typedef struct {
     int32_t kind, rank;

@@ -786,6 +786,85 @@ int oracle_view_copy_q(const b200k_view_copy_params* p)
     return 0;
 }
 
+/* DepthToSpace.cpp:15-100: per batch, the permutation [H, W, b, b, C'] -> [H, b, W, b, C'] (NHWC) or
+ * [b, b, C', H, W] -> [C', H, b, W, b] (NCHW) of raw elements, i.e. out(n, h b + i, w b + j, c') = in(n, h, w, (i b + j) C' + c'). */
+static int move_depth_to_space(const oracle_move_params* p)
+{
+    const size_t es = esize(p->whole.dtype);
+    const int b = p->perm[0], nchw = p->perm[1];
+    const int N = p->whole_shape[0];
+    const int C = nchw ? p->whole_shape[1] : p->whole_shape[3], H = nchw ? p->whole_shape[2] : p->whole_shape[1],
+              W = nchw ? p->whole_shape[3] : p->whole_shape[2];
+    if (b < 1 || C % (b * b)) return B200K_E_INVALID;
+    const int Co = C / (b * b), OH = H * b, OW = W * b;
+    for (int n = 0; n < N; ++n) for (int h = 0; h < H; ++h) for (int w = 0; w < W; ++w)
+    for (int i = 0; i < b; ++i) for (int j = 0; j < b; ++j) for (int c = 0; c < Co; ++c) {
+        const int ci = (i * b + j) * Co + c, oh = h * b + i, ow = w * b + j;
+        const int64_t src = nchw ? (((int64_t)n * C + ci) * H + h) * W + w : (((int64_t)n * H + h) * W + w) * C + ci;
+        const int64_t dst = nchw ? (((int64_t)n * Co + c) * OH + oh) * OW + ow : (((int64_t)n * OH + oh) * OW + ow) * Co + c;
+        memcpy((uint8_t*)p->view[0].data + (size_t)dst * es, (const uint8_t*)p->whole.data + (size_t)src * es, es);
+    }
+    return 0;
+}
+
+/* SpaceToDepth.cpp:42-104: output channel oc reads input channel oc % C at (oh b + (oc / C) / b, ow b + (oc / C) % b),
+ * through Decoder / Encoder. */
+static int move_space_to_depth(const oracle_move_params* p)
+{
+    const int b = p->perm[0], nchw = p->perm[1];
+    const int N = p->whole_shape[0];
+    const int C = nchw ? p->whole_shape[1] : p->whole_shape[3], H = nchw ? p->whole_shape[2] : p->whole_shape[1],
+              W = nchw ? p->whole_shape[3] : p->whole_shape[2];
+    if (b < 1 || H % b || W % b) return B200K_E_INVALID;
+    const int OC = C * b * b, OH = H / b, OW = W / b;
+    for (int oc = 0; oc < OC; ++oc) {
+        const int ic = oc % C, sw = (oc / C) % b, sh = (oc / C) / b;
+        for (int oh = 0; oh < OH; ++oh) for (int ow = 0; ow < OW; ++ow) for (int n = 0; n < N; ++n) {
+            const int ih = oh * b + sh, iw = ow * b + sw;
+            const int64_t src = nchw ? (((int64_t)n * C + ic) * H + ih) * W + iw : (((int64_t)n * H + ih) * W + iw) * C + ic;
+            const int64_t dst = nchw ? (((int64_t)n * OC + oc) * OH + oh) * OW + ow : (((int64_t)n * OH + oh) * OW + ow) * OC + oc;
+            store_f(&p->view[0], dst, load_f(&p->whole, src));
+        }
+    }
+    return 0;
+}
+
+/* RefChannelShuffleWorkload.cpp:28-76: with g groups of s channels along `axis`, output channel i g + j takes input
+ * channel i + j s, through Decoder / Encoder. */
+static int move_channel_shuffle(const oracle_move_params* p)
+{
+    const int axis = p->perm[0], g = p->perm[1];
+    if (axis < 0 || axis >= p->rank || g < 1 || p->whole_shape[axis] % g) return B200K_E_INVALID;
+    const int ch = p->whole_shape[axis], s = ch / g;
+    int64_t outer = 1, inner = 1;
+    for (int d = 0; d < axis; ++d) outer *= p->whole_shape[d];
+    for (int d = axis + 1; d < p->rank; ++d) inner *= p->whole_shape[d];
+    for (int64_t o = 0; o < outer; ++o) for (int64_t in = 0; in < inner; ++in)
+    for (int i = 0; i < s; ++i) for (int j = 0; j < g; ++j)
+        store_f(&p->view[0], (o * ch + (i * g + j)) * inner + in, load_f(&p->whole, (o * ch + (i + j * s)) * inner + in));
+    return 0;
+}
+
+/* Stack.cpp:14-120: input i becomes index i of the new dimension `axis` of the output, through Decoder / Encoder. */
+static int move_stack(const oracle_move_params* p)
+{
+    const int axis = p->perm[0], in_rank = p->rank - 1;
+    if (axis < 0 || axis > in_rank) return B200K_E_INVALID;
+    int64_t os[6], st = 1;
+    for (int d = p->rank - 1; d >= 0; --d) { os[d] = st; st *= p->whole_shape[d]; }
+    for (int v = 0; v < p->n_views; ++v) {
+        const int64_t n = elems(p->view_shape[v], in_rank);
+        for (int64_t i = 0; i < n; ++i) {
+            int32_t c[6];
+            coords_of(i, p->view_shape[v], in_rank, c);
+            int64_t dst = (int64_t)v * os[axis];
+            for (int d = 0; d < in_rank; ++d) dst += (int64_t)c[d] * os[d < axis ? d : d + 1];
+            store_f(&p->whole, dst, load_f(&p->view[v], i));
+        }
+    }
+    return 0;
+}
+
 int oracle_move_q(const oracle_move_params* p)
 {
     if (!p || p->rank < 1 || p->rank > 6 || !p->whole.data || p->n_views < 1 || p->n_views > 8) return B200K_E_INVALID;
@@ -796,6 +875,10 @@ int oracle_move_q(const oracle_move_params* p)
         case MOVE_TRANSPOSE:     return move_permute(p, 1);
         case MOVE_STRIDED_SLICE: return move_strided_slice(p);
         case MOVE_SLICE:         return move_slice(p);
+        case MOVE_DEPTH_TO_SPACE:  return move_depth_to_space(p);
+        case MOVE_SPACE_TO_DEPTH:  return move_space_to_depth(p);
+        case MOVE_CHANNEL_SHUFFLE: return move_channel_shuffle(p);
+        case MOVE_STACK:           return move_stack(p);
         default: return B200K_E_INVALID;
     }
 }

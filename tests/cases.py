@@ -480,6 +480,18 @@ def move_cases():
     c["strided_slice_shrink_axis"] = lambda: MoveCase("strided_slice", 215, ((4, 5, 6),) + q, [((5, 3),) + q],
                                                       begin=(2, 0, 1), end=(3, 5, 6), stride=(1, 1, 2), shrink_axis_mask=0b001)
     c["slice_block"] = lambda: MoveCase("slice", 216, ((2, 9, 8, 16),) + q, [((1, 4, 5, 16),) + q], begin=(1, 2, 3, 0), end=(1, 4, 5, 16))
+    c["depth_to_space_nhwc_block2"] = lambda: MoveCase("depth_to_space", 218, ((2, 3, 5, 32),) + q, [((2, 6, 10, 8),) + q], perm=(2, 0))
+    c["depth_to_space_nchw_block3"] = lambda: MoveCase("depth_to_space", 219, ((1, 18, 4, 3), U8, 0.1, 7), [((1, 2, 12, 9), U8, 0.1, 7)], perm=(3, 1))
+    c["space_to_depth_nhwc_block2"] = lambda: MoveCase("space_to_depth", 220, ((2, 6, 10, 8),) + q, [((2, 3, 5, 32),) + q], perm=(2, 0))
+    c["space_to_depth_nchw_requantise"] = lambda: MoveCase("space_to_depth", 221, ((1, 3, 6, 9), S8, 0.05, 1), [((1, 27, 2, 3), S8, 0.08, -4)],
+                                                           perm=(3, 1))
+    c["channel_shuffle_nhwc_groups4"] = lambda: MoveCase("channel_shuffle", 222, ((2, 5, 4, 24),) + q, [((2, 5, 4, 24),) + q], perm=(3, 4))
+    c["channel_shuffle_nchw_axis1_requantise"] = lambda: MoveCase("channel_shuffle", 223, ((2, 12, 3, 5), U8, 0.1, 100), [((2, 12, 3, 5), U8, 0.07, 90)],
+                                                                  perm=(1, 3))
+    c["stack_axis0"] = lambda: MoveCase("stack", 224, ((3, 4, 5),) + q, [((4, 5),) + q] * 3, perm=(0,))
+    c["stack_axis2_rank4_out"] = lambda: MoveCase("stack", 225, ((2, 3, 2, 7), U8, 0.1, 9), [((2, 3, 7), U8, 0.1, 9)] * 2, perm=(2,))
+    c["stack_last_axis_requantise"] = lambda: MoveCase("stack", 226, ((4, 6, 3), S8, 0.06, 2), [((4, 6), S8, 0.05, -1), ((4, 6), S8, 0.07, 3), ((4, 6), S8, 0.06, 2)],
+                                                       perm=(2,))
     c["slice_rank2_s32"] = lambda: MoveCase("slice", 217, ((7, 9), S32, 1.0, 0), [((3, 4), S32, 1.0, 0)], begin=(2, 5), end=(3, 4))
     return c
 

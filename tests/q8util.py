@@ -412,7 +412,8 @@ class OracleMoveParams(C.Structure):
                 ("begin_mask", C.c_int32), ("end_mask", C.c_int32), ("shrink_axis_mask", C.c_int32)]
 
 
-MOVE_KINDS = {"concat": 0, "split": 1, "permute": 2, "transpose": 3, "strided_slice": 4, "slice": 5}
+MOVE_KINDS = {"concat": 0, "split": 1, "permute": 2, "transpose": 3, "strided_slice": 4, "slice": 5,
+              "depth_to_space": 6, "space_to_depth": 7, "channel_shuffle": 8, "stack": 9}
 
 
 class MoveCase:
@@ -437,7 +438,7 @@ class MoveCase:
             lo, hi = RANGE[dtype]
             return rng.integers(lo, hi + 1, size=shape).astype(NP_OF[dtype])
         outs = []
-        if self.kind == "concat":
+        if self.kind in ("concat", "stack"):
             parts = [qt(mem, rand(sh, dt), dt, sc, zp) for sh, dt, sc, zp in self.parts]
             sh, dt, sc, zp = self.whole
             whole, h = qt_out(mem, sh, dt, sc, zp)
@@ -500,6 +501,17 @@ class MoveCase:
             return [(v, i, -1) for v, i in zip(vs, order)]
         if self.kind == "split":
             return [(v, -1, i) for i, v in enumerate(V.splitter_views(self.whole[0], shapes, self.origins))]
+        if self.kind == "stack":
+            out_shape, vs = V.stack_views(shapes[0], len(shapes), self.perm[0])
+            assert tuple(out_shape) == tuple(self.whole[0]), (out_shape, self.whole[0])
+            return [(v, i, -1) for i, v in enumerate(vs)]
+        if self.kind in ("depth_to_space", "space_to_depth"):
+            fn = V.depth_to_space_view if self.kind == "depth_to_space" else V.space_to_depth_view
+            out_shape, v = fn(self.whole[0], self.perm[0], bool(self.perm[1]))
+            assert tuple(out_shape) == tuple(shapes[0]), (out_shape, shapes[0])
+            return [(v, -1, 0)]
+        if self.kind == "channel_shuffle":
+            return [(V.channel_shuffle_view(self.whole[0], self.perm[0], self.perm[1]), -1, 0)]
         if self.kind in ("permute", "transpose"):
             out_shape, v = V.permute_view(self.whole[0], self.perm, transpose=self.kind == "transpose")
             assert tuple(out_shape) == tuple(shapes[0]), (out_shape, shapes[0])

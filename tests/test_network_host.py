@@ -149,3 +149,15 @@ def test_transpose_convolution_graph_oracle_vs_armnn_cpuref(built):
     assert want.shape == got.shape
     st = diff_stats(want, got)
     assert st["max_abs"] <= 1 and st["mismatch_frac"] < 5e-3, st
+
+
+@needs_cpuref
+def test_space_depth_shuffle_stack_graph_mirror_views_vs_armnn_cpuref(built):
+    import hostnet
+    from test_plugin import _shuffle_net
+    net, info = _shuffle_net()
+    x = np.random.default_rng(16).integers(-128, 128, size=info["input_shape"]).astype(np.int8)
+    want = hostnet.ArmnnNetwork(net, "CpuRef").run({0: x})
+    got = hostnet.OracleNetwork(Optimize(net)).run({0: x})
+    for k in (0, 1):
+        assert want[k].shape == got[k].shape and np.array_equal(want[k], got[k]), k

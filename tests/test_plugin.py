@@ -600,3 +600,50 @@ def test_transpose_convolution_through_the_runtime_matches_cpuref():
     assert ref.shape == got.shape
     st = diff_stats(ref, got)
     assert st["max_abs"] <= 1 and st["mismatch_frac"] < 5e-3, st
+
+
+def _shuffle_net(batch=2):
+    """SpaceToDepth -> ChannelShuffle -> DepthToSpace (a ShuffleNet-style rearrangement) and a Stack of the input with
+    a re-quantised copy of itself: the remaining view-copy layers in one graph."""
+    from armnn_b200.network import DataType, INetwork, TensorInfo
+
+    def info(shape, scale=0.05, offset=-3):
+        return TensorInfo(tuple(shape), DataType.QAsymmS8, scale, offset)
+    net = INetwork.Create()
+    il = net.AddInputLayer(0, "input")
+    il.GetOutputSlot(0).SetTensorInfo(info((batch, 6, 4, 8)))
+    sd = net.AddSpaceToDepthLayer(2, name="s2d")
+    il.GetOutputSlot(0).Connect(sd.GetInputSlot(0))
+    sd.GetOutputSlot(0).SetTensorInfo(info((batch, 3, 2, 32), 0.06, 1))          # re-quantised by the copy
+    cs = net.AddChannelShuffleLayer(3, 4, name="shuffle")
+    sd.GetOutputSlot(0).Connect(cs.GetInputSlot(0))
+    cs.GetOutputSlot(0).SetTensorInfo(info((batch, 3, 2, 32), 0.06, 1))
+    ds = net.AddDepthToSpaceLayer(2, name="d2s")
+    cs.GetOutputSlot(0).Connect(ds.GetInputSlot(0))
+    ds.GetOutputSlot(0).SetTensorInfo(info((batch, 6, 4, 8), 0.06, 1))
+    stk = net.AddStackLayer(1, 2, name="stack")
+    il.GetOutputSlot(0).Connect(stk.GetInputSlot(0))
+    il.GetOutputSlot(0).Connect(stk.GetInputSlot(1))
+    stk.GetOutputSlot(0).SetTensorInfo(info((batch, 2, 6, 4, 8), 0.07, 2))
+    o0 = net.AddOutputLayer(0, "out_shuffled")
+    ds.GetOutputSlot(0).Connect(o0.GetInputSlot(0))
+    o1 = net.AddOutputLayer(1, "out_stacked")
+    stk.GetOutputSlot(0).Connect(o1.GetInputSlot(0))
+    return net, {"input_shape": (batch, 6, 4, 8)}
+
+
+@needs_plugin
+@pytest.mark.gpu
+def test_space_depth_shuffle_stack_through_the_runtime_match_cpuref_and_the_python_mirror():
+    from armnn_b200 import network
+    net, info = _shuffle_net()
+    x = np.random.default_rng(15).integers(-128, 128, size=info["input_shape"]).astype(np.int8)
+    ref = hostnet.ArmnnNetwork(net, "CpuRef").run({0: x})
+    got = hostnet.ArmnnNetwork(net, "B200Acc").run({0: x})
+    for k in (0, 1):
+        assert ref[k].shape == got[k].shape and np.array_equal(ref[k], got[k]), k
+    rt = network.IRuntime.Create(0)
+    ln = rt.GetLoadedNetwork(rt.LoadNetwork(network.Optimize(net)))
+    ys = {k: np.zeros(ref[k].shape, np.int8) for k in (0, 1)}
+    ln.EnqueueWorkload({0: x}, ys)
+    assert np.array_equal(ys[0], ref[0]) and np.array_equal(ys[1], ref[1])
