@@ -136,6 +136,9 @@ KERNEL_ENTRY_POINTS = {
     "conv2d_q8": Conv2dParams,
     "dwconv2d_q8": Conv2dParams,
     "transpose_conv2d_q8": Conv2dParams,
+    "conv2d_f32": Conv2dParams,
+    "dwconv2d_f32": Conv2dParams,
+    "fully_connected_f32": FcParams,
     "fully_connected_q8": FcParams,
     "batch_matmul_q8": BmmParams,
     "pool2d_q8": Pool2dParams,

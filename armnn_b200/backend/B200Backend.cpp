@@ -52,6 +52,16 @@ bool IsMoveType(const TensorInfo& t)
     return IsActType(t) || t.GetDataType() == DataType::Signed32;
 }
 
+// every tensor of the layer is Float32 (an absent bias is an empty TensorInfo)
+bool AllFloat32(const std::vector<TensorInfo>& infos)
+{
+    for (const TensorInfo& t : infos)
+    {
+        if (t != TensorInfo() && t.GetDataType() != DataType::Float32) { return false; }
+    }
+    return !infos.empty();
+}
+
 bool No(Optional<std::string&> reason, const char* why)
 {
     if (reason.has_value()) { reason.value() += std::string("B200Acc: ") + why + " "; }
@@ -88,8 +98,9 @@ public:
                     ? PolymorphicDowncast<const Convolution2dDescriptor*>(&descriptor)->m_DataLayout
                     : PolymorphicDowncast<const DepthwiseConvolution2dDescriptor*>(&descriptor)->m_DataLayout;
                 if (layout != DataLayout::NHWC) { return No(reason, "only NHWC is supported"); }
-                if (!Is8Bit(infos[0]) || !Is8Bit(infos[1]) || !Is8Bit(infos[2])) { return No(reason, "input, output and weights must be 8-bit quantised"); }
                 if (!infos[2].IsConstant()) { return No(reason, "non-constant weights are not supported"); }
+                if (AllFloat32(infos)) { return true; }                 // the fp32 variant (b200k_conv2d_f32 / b200k_dwconv2d_f32)
+                if (!Is8Bit(infos[0]) || !Is8Bit(infos[1]) || !Is8Bit(infos[2])) { return No(reason, "input, output and weights must be 8-bit quantised or all Float32"); }
                 if (infos[3] != TensorInfo() && infos[3].GetDataType() != DataType::Signed32) { return No(reason, "bias must be Signed32"); }
                 if (infos[2].HasPerAxisQuantization())
                 {
@@ -100,8 +111,9 @@ public:
             }
             case LayerType::FullyConnected:
             {
-                if (!Is8Bit(infos[0]) || !Is8Bit(infos[1]) || !Is8Bit(infos[2])) { return No(reason, "input, output and weights must be 8-bit quantised"); }
                 if (!infos[2].IsConstant()) { return No(reason, "non-constant weights are not supported"); }
+                if (AllFloat32(infos)) { return true; }                 // the fp32 variant (b200k_fully_connected_f32)
+                if (!Is8Bit(infos[0]) || !Is8Bit(infos[1]) || !Is8Bit(infos[2])) { return No(reason, "input, output and weights must be 8-bit quantised or all Float32"); }
                 const auto& d = *PolymorphicDowncast<const FullyConnectedDescriptor*>(&descriptor);
                 if (d.m_BiasEnabled && infos[3].GetDataType() != DataType::Signed32) { return No(reason, "bias must be Signed32"); }
                 return true;
@@ -565,6 +577,8 @@ OptimizationViews B200Backend::OptimizeSubgraphView(const SubgraphView& subgraph
             if (base.GetAdditionalInformation<ActivationDescriptor>() != nullptr) { continue; }
             OutputSlot& out = base.GetOutputSlot(0);
             if (out.GetNumConnections() != 1) { continue; }
+            // the fp32 contractions have no fused clamp: their activations stay layers of their own
+            if (t != LayerType::ElementwiseBinary && out.GetTensorInfo().GetDataType() == DataType::Float32) { continue; }
             Layer& child = out.GetConnection(0)->GetOwningLayer();
             if (child.GetType() != LayerType::Activation || untouched.find(child.GetGuid()) == untouched.end()) { continue; }
             auto* act = PolymorphicDowncast<ActivationLayer*>(&child);

@@ -499,6 +499,19 @@ std::unique_ptr<IWorkload> MakeConv(const QueueDescriptor& d, const WorkloadInfo
     const TensorInfo& y = info.m_OutputTensorInfos[0];
     FillConv(*st, qd.m_Parameters, info.m_InputTensorInfos[0], info.m_InputTensorInfos[1],
              info.m_InputTensorInfos.size() > 2 ? &info.m_InputTensorInfos[2] : nullptr, y, depthwise);
+    if (y.GetDataType() == DataType::Float32)
+    {
+        // the fp32 variant (activations are never fused into it: B200Backend::OptimizeSubgraphView)
+        return Make<QD>(d, info, ctx, [st, depthwise](const QD& data, cudaStream_t s)
+        {
+            b200k_conv2d_params& q = st->p;
+            q.x.data = Dev(data.m_Inputs[0]);
+            q.w.data = Dev(data.m_Inputs[1]);
+            if (q.bias.dtype == B200K_F32 && data.m_Inputs.size() > 2) { q.bias.data = Dev(data.m_Inputs[2]); }
+            q.y.data = Dev(data.m_Outputs[0]);
+            B200CheckStatus(depthwise ? b200k_dwconv2d_f32(&q, s) : b200k_conv2d_f32(&q, s));
+        });
+    }
     Clamp(qd.template GetAdditionalInformation<ActivationDescriptor>(), y, st->p.clamp_lo, st->p.clamp_hi);
     return Make<QD>(d, info, ctx, [st, depthwise](const QD& data, cudaStream_t s)
     {
@@ -568,6 +581,19 @@ std::unique_ptr<IWorkload> MakeFc(const QueueDescriptor& d, const WorkloadInfo& 
     p.k = x.GetNumElements() / x.GetShape()[0];          // inputs of rank > 2 are flattened (FullyConnected.cpp:16-24)
     p.n = y.GetShape()[y.GetNumDimensions() - 1];
     p.transpose_w = qd.m_Parameters.m_TransposeWeightMatrix ? 1 : 0;
+    if (x.GetDataType() == DataType::Float32)
+    {
+        // the fp32 variant (activations are never fused into it: B200Backend::OptimizeSubgraphView)
+        return Make<FullyConnectedQueueDescriptor>(d, info, ctx, [st](const FullyConnectedQueueDescriptor& data, cudaStream_t s)
+        {
+            b200k_fc_params& q = st->p;
+            q.x.data = Dev(data.m_Inputs[0]);
+            q.w.data = Dev(data.m_Inputs[1]);
+            if (q.bias.dtype == B200K_F32 && data.m_Inputs.size() > 2) { q.bias.data = Dev(data.m_Inputs[2]); }
+            q.y.data = Dev(data.m_Outputs[0]);
+            B200CheckStatus(b200k_fully_connected_f32(&q, s));
+        });
+    }
     Clamp(qd.GetAdditionalInformation<ActivationDescriptor>(), y, p.clamp_lo, p.clamp_hi);
     if (p.transpose_w) { st->packed = st->blobs.Alloc(b200k_conv2d_pack_bytes(p.n, 1, 1, p.k)); }
     return Make<FullyConnectedQueueDescriptor>(d, info, ctx, [st](const FullyConnectedQueueDescriptor& data, cudaStream_t s)

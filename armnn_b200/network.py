@@ -326,10 +326,12 @@ def IsLayerSupported(layer):
         return True, ""
     if t in ("Convolution2d", "DepthwiseConvolution2d", "FullyConnected"):
         x, w, y = ins[0], ins[1], outs[0]
-        if x.dtype not in _Q8 or y.dtype not in _Q8 or w.dtype not in _Q8:
-            return False, "%s: input, weights and output must be 8-bit quantised" % t
         if not w.constant:
             return False, "%s: non-constant weights are not supported" % t
+        if all(i.dtype == DataType.Float32 for i in list(ins) + list(outs)):
+            return True, ""                                  # the fp32 variant (b200k_*_f32)
+        if x.dtype not in _Q8 or y.dtype not in _Q8 or w.dtype not in _Q8:
+            return False, "%s: input, weights and output must be 8-bit quantised or all Float32" % t
         if len(ins) > 2 and ins[2].dtype != DataType.Signed32:
             return False, "%s: bias must be Signed32" % t
         if w.HasPerAxisQuantization():
@@ -629,6 +631,8 @@ class GraphProgram:
         p.stride_h, p.stride_w = layer.desc["stride"]
         p.pad_top, p.pad_left = layer.desc["pad"][0], layer.desc["pad"][2]
         p.dil_h, p.dil_w = layer.desc["dilation"]
+        if y.info.dtype == DataType.Float32:
+            return p                                         # the fp32 variant: no clamp, no tables
         p.clamp_lo, p.clamp_hi = _clamp(layer, y.info)
         fused = getattr(layer, "fused_add", None)
         if fused is not None:
@@ -642,9 +646,13 @@ class GraphProgram:
         return p
 
     def _make_Convolution2d(self, layer):
+        if layer.outputs[0].info.dtype == DataType.Float32:
+            return "conv2d_f32", self._conv_params(layer, False)
         return "conv2d_q8", self._conv_params(layer, False)
 
     def _make_DepthwiseConvolution2d(self, layer):
+        if layer.outputs[0].info.dtype == DataType.Float32:
+            return "dwconv2d_f32", self._conv_params(layer, True)
         return "dwconv2d_q8", self._conv_params(layer, True)
 
     def _make_FullyConnected(self, layer):
@@ -657,6 +665,8 @@ class GraphProgram:
         p.k = int(np.prod(x.info.shape[1:]))                 # 4-D inputs are flattened (FullyConnected.cpp:16-24)
         p.n = y.info.shape[-1]
         p.transpose_w = int(layer.desc["transpose"])
+        if y.info.dtype == DataType.Float32:
+            return "fully_connected_f32", p
         p.clamp_lo, p.clamp_hi = _clamp(layer, y.info)
         if p.transpose_w:
             c = _abi.Conv2dParams()

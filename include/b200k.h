@@ -284,6 +284,18 @@ typedef struct {
 
 int b200k_view_copy_q(const b200k_view_copy_params* p, void* stream);
 
+/* ---- Float32 Convolution2d / DepthwiseConvolution2d / FullyConnected ------------------------- */
+
+/* The fp32 variants of the contractions: every tensor Float32 (x, w, y and the optional bias), same parameter structs,
+ * NHWC.  The sum runs in the reference's own order with a rounded product and a rounded sum per term
+ * (sum += w * x over input channel, filter row, filter column: src/backends/reference/workloads/ConvImpl.cpp:118-204;
+ * over the input channel: workloads/FullyConnected.cpp:32-58), so the results are CpuRef's bit for bit; padding taps
+ * add w * 0.  CUDA-core kernels: correctness and coverage, not throughput.  clamp_lo / clamp_hi, add_operand, packed,
+ * scratch and algo are unused (activations stay layers of their own for fp32 tensors). */
+int b200k_conv2d_f32(const b200k_conv2d_params* p, void* stream);
+int b200k_dwconv2d_f32(const b200k_conv2d_params* p, void* stream);
+int b200k_fully_connected_f32(const b200k_fc_params* p, void* stream);
+
 /* ---- TransposeConvolution2d ----------------------------------------------------------------- */
 
 /* armnn::TransposeConvolution2dImpl (src/backends/reference/workloads/TransposeConvolution2d.cpp:14-160), NHWC,

@@ -173,6 +173,11 @@ extern "C" int cpuref_conv2d_q8(const b200k_conv2d_params* p, int depthwise, int
     });
 }
 
+extern "C" int cpuref_conv2d_f32(const b200k_conv2d_params* p)   { return cpuref_conv2d_q8(p, 0, 0, 0.f, 0.f); }
+extern "C" int cpuref_dwconv2d_f32(const b200k_conv2d_params* p) { return cpuref_conv2d_q8(p, 1, 0, 0.f, 0.f); }
+extern "C" int cpuref_fully_connected_q8(const b200k_fc_params* p, int act_kind, float act_a, float act_b);
+extern "C" int cpuref_fully_connected_f32(const b200k_fc_params* p) { return cpuref_fully_connected_q8(p, 0, 0.f, 0.f); }
+
 extern "C" int cpuref_transpose_conv2d_q8(const b200k_conv2d_params* p)
 {
     return guarded([&] {

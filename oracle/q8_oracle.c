@@ -208,6 +208,55 @@ static int conv_impl(const b200k_conv2d_params* p, int depthwise)
 int oracle_conv2d_q8(const b200k_conv2d_params* p)   { return conv_impl(p, 0); }
 int oracle_dwconv2d_q8(const b200k_conv2d_params* p) { return conv_impl(p, 1); }
 
+/* ---- Float32 Convolve (ConvImpl.cpp:118-232) and FullyConnected (FullyConnected.cpp:32-62) -------
+ * The reference's loops and its fp32 accumulation order (this file is built with -ffp-contract=off: a rounded
+ * product and a rounded sum per term); padding taps add w * 0. */
+static int conv_f32_impl(const b200k_conv2d_params* p, int depthwise)
+{
+    if (!p || !p->x.data || !p->w.data || !p->y.data || p->x.dtype != B200K_F32 || p->w.dtype != B200K_F32 || p->y.dtype != B200K_F32)
+        return B200K_E_INVALID;
+    const int N = p->n, H = p->h, W = p->wd, C = p->c, OH = p->oh, OW = p->ow, OC = p->oc, KH = p->kh, KW = p->kw;
+    const float* x = (const float*)p->x.data; const float* w = (const float*)p->w.data;
+    const float* bias = (const float*)p->bias.data; float* y = (float*)p->y.data;
+    const int dm = depthwise ? OC / C : 1;
+    for (int b = 0; b < N; ++b) for (int co = 0; co < OC; ++co) for (int oy = 0; oy < OH; ++oy) for (int ox = 0; ox < OW; ++ox) {
+        float sum = 0.0f;
+        for (int c = 0; c < (depthwise ? 1 : C); ++c) {
+            const int ci = depthwise ? co / dm : c;
+            for (int ky = 0; ky < KH; ++ky) for (int kx = 0; kx < KW; ++kx) {
+                const int iy = oy * p->stride_h + ky * p->dil_h - p->pad_top, ix = ox * p->stride_w + kx * p->dil_w - p->pad_left;
+                const float wv = depthwise ? w[((int64_t)ky * KW + kx) * OC + co] : w[(((int64_t)co * KH + ky) * KW + kx) * C + ci];
+                const float xv = (iy < 0 || iy >= H || ix < 0 || ix >= W) ? 0.0f : x[(((int64_t)b * H + iy) * W + ix) * C + ci];
+                sum += wv * xv;
+            }
+        }
+        if (bias) sum += bias[co];
+        y[(((int64_t)b * OH + oy) * OW + ox) * OC + co] = sum;
+    }
+    return 0;
+}
+
+int oracle_conv2d_f32(const b200k_conv2d_params* p)   { return conv_f32_impl(p, 0); }
+int oracle_dwconv2d_f32(const b200k_conv2d_params* p) { return conv_f32_impl(p, 1); }
+
+int oracle_fully_connected_f32(const b200k_fc_params* p)
+{
+    if (!p || !p->x.data || !p->w.data || !p->y.data || p->x.dtype != B200K_F32 || p->w.dtype != B200K_F32 || p->y.dtype != B200K_F32)
+        return B200K_E_INVALID;
+    const float* x = (const float*)p->x.data; const float* w = (const float*)p->w.data;
+    const float* bias = (const float*)p->bias.data; float* y = (float*)p->y.data;
+    for (int m = 0; m < p->m; ++m) for (int o = 0; o < p->n; ++o) {
+        float out = 0.f;
+        for (int k = 0; k < p->k; ++k) {
+            const float wv = p->transpose_w ? w[(int64_t)o * p->k + k] : w[(int64_t)k * p->n + o];
+            out += wv * x[(int64_t)m * p->k + k];
+        }
+        if (bias) out += bias[o];
+        y[(int64_t)m * p->n + o] = out;
+    }
+    return 0;
+}
+
 /* ---- TransposeConvolution2dImpl, TransposeConvolution2d.cpp:14-160 (NHWC, weights [O,H,W,I]) ---
  * The reference's scatter loop nest with an exact int32 accumulator per output element instead of its float buffer,
  * then bias and quantisation through the contractions' one requantisation. */

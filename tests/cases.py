@@ -341,6 +341,48 @@ def qlstm_cases():
     }
 
 
+def f32_cases():
+    """The Float32 variants of Convolution2d, DepthwiseConvolution2d and FullyConnected: bit-exact against CpuRef."""
+    def conv(seed, n, h, w, c, oc, k, stride=(1, 1), pad=(0, 0), dil=(1, 1), depthwise=False, bias=True):
+        def build(mem):
+            rng = np.random.default_rng(seed)
+            oh = (h + 2 * pad[0] - dil[0] * (k[0] - 1) - 1) // stride[0] + 1
+            ow = (w + 2 * pad[1] - dil[1] * (k[1] - 1) - 1) // stride[1] + 1
+            p = _abi.Conv2dParams()
+            p.x = qt(mem, rng.standard_normal((n, h, w, c)).astype(np.float32), F32)
+            wshape = (1, k[0], k[1], oc) if depthwise else (oc, k[0], k[1], c)
+            p.w = qt(mem, (rng.standard_normal(wshape) * 0.2).astype(np.float32), F32)
+            if bias:
+                p.bias = qt(mem, rng.standard_normal(oc).astype(np.float32), F32)
+            p.y, y = qt_out(mem, (n, oh, ow, oc), F32)
+            p.n, p.h, p.wd, p.c, p.oh, p.ow, p.oc, p.kh, p.kw = n, h, w, c, oh, ow, oc, k[0], k[1]
+            p.stride_h, p.stride_w, p.pad_top, p.pad_left, p.dil_h, p.dil_w = stride[0], stride[1], pad[0], pad[1], dil[0], dil[1]
+            return p, [y]
+        return lambda: SimpleCase("dwconv2d_f32" if depthwise else "conv2d_f32", build)
+
+    def fc(seed, m, k, n, transpose=True, bias=True):
+        def build(mem):
+            rng = np.random.default_rng(seed)
+            p = _abi.FcParams()
+            p.x = qt(mem, rng.standard_normal((m, k)).astype(np.float32), F32)
+            p.w = qt(mem, (rng.standard_normal((n, k) if transpose else (k, n)) * 0.1).astype(np.float32), F32)
+            if bias:
+                p.bias = qt(mem, rng.standard_normal(n).astype(np.float32), F32)
+            p.y, y = qt_out(mem, (m, n), F32)
+            p.m, p.k, p.n, p.transpose_w = m, k, n, int(transpose)
+            return p, [y]
+        return lambda: SimpleCase("fully_connected_f32", build)
+    return {
+        "conv3x3_pad1": conv(351, 2, 9, 8, 12, 20, (3, 3), pad=(1, 1)),
+        "conv1x1": conv(352, 1, 7, 7, 32, 16, (1, 1), bias=False),
+        "conv5x5_s2_dilation2": conv(353, 1, 17, 15, 5, 7, (5, 5), stride=(2, 2), pad=(4, 4), dil=(2, 2)),
+        "dwconv3x3_s1": conv(354, 2, 10, 9, 16, 16, (3, 3), pad=(1, 1), depthwise=True),
+        "dwconv3x3_s2_multiplier2": conv(355, 1, 11, 11, 6, 12, (3, 3), stride=(2, 2), pad=(1, 1), depthwise=True),
+        "fc_m5_k64_n24": fc(356, 5, 64, 24),
+        "fc_not_transposed_no_bias": fc(357, 3, 37, 11, transpose=False, bias=False),
+    }
+
+
 def tconv_cases():
     """TransposeConvolution2d (NHWC, weights OHWI): the up-sampling shapes of decoder networks, every operand type,
     channel counts with and without the 4-byte vector path, padding that crops the output."""
@@ -498,7 +540,7 @@ def move_cases():
 
 ALL_GROUPS = {"conv": conv_cases, "dwconv": dwconv_cases, "fc": fc_cases, "bmm": bmm_cases, "pool": pool_cases,
               "mean": mean_cases, "eltwise": eltwise_cases, "activation": activation_cases, "softmax": softmax_cases,
-              "convert": convert_cases, "pad": pad_cases, "qlstm": qlstm_cases, "move": move_cases, "resize": resize_cases, "reduce": reduce_cases, "tconv": tconv_cases}
+              "convert": convert_cases, "pad": pad_cases, "qlstm": qlstm_cases, "move": move_cases, "resize": resize_cases, "reduce": reduce_cases, "tconv": tconv_cases, "f32": f32_cases}
 
 
 def run_case(case, where):

@@ -161,3 +161,16 @@ def test_space_depth_shuffle_stack_graph_mirror_views_vs_armnn_cpuref(built):
     got = hostnet.OracleNetwork(Optimize(net)).run({0: x})
     for k in (0, 1):
         assert want[k].shape == got[k].shape and np.array_equal(want[k], got[k]), k
+
+
+@needs_cpuref
+def test_float32_graph_oracle_equals_armnn_cpuref(built):
+    """The fp32 Convolution2d / DepthwiseConvolution2d / FullyConnected restatements inside a graph (with a separate
+    ReLU): identical bits to the real runtime on CpuRef."""
+    import hostnet
+    from test_plugin import _float_net
+    net, info = _float_net()
+    x = np.random.default_rng(18).standard_normal(info["input_shape"]).astype(np.float32)
+    want = hostnet.ArmnnNetwork(net, "CpuRef").run({0: x})[0]
+    got = hostnet.OracleNetwork(Optimize(net)).run({0: x})[0]
+    assert want.shape == got.shape and np.array_equal(want, got)

@@ -647,3 +647,58 @@ def test_space_depth_shuffle_stack_through_the_runtime_match_cpuref_and_the_pyth
     ys = {k: np.zeros(ref[k].shape, np.int8) for k in (0, 1)}
     ln.EnqueueWorkload({0: x}, ys)
     assert np.array_equal(ys[0], ref[0]) and np.array_equal(ys[1], ref[1])
+
+
+def _float_net(batch=2):
+    """A Float32 graph: Convolution2d + ReLU -> DepthwiseConvolution2d -> FullyConnected, on the fp32 variants of the
+    contraction kernels (activations stay layers of their own)."""
+    from armnn_b200.network import ActivationFunction, DataType, INetwork, TensorInfo
+    rng = np.random.default_rng(80)
+    net = INetwork.Create()
+
+    def f(shape):
+        return TensorInfo(tuple(shape), DataType.Float32)
+    il = net.AddInputLayer(0, "input")
+    il.GetOutputSlot(0).SetTensorInfo(f((batch, 8, 8, 6)))
+    w1 = (rng.standard_normal((10, 3, 3, 6)) * 0.2).astype(np.float32)
+    b1 = rng.standard_normal(10).astype(np.float32)
+    w1l = net.AddConstantLayer(w1, f(w1.shape), "w1")
+    b1l = net.AddConstantLayer(b1, f(b1.shape), "b1")
+    c1 = net.AddConvolution2dLayer((1, 1), (1, 1, 1, 1), (1, 1), True, "conv")
+    il.GetOutputSlot(0).Connect(c1.GetInputSlot(0))
+    w1l.GetOutputSlot(0).Connect(c1.GetInputSlot(1))
+    b1l.GetOutputSlot(0).Connect(c1.GetInputSlot(2))
+    c1.GetOutputSlot(0).SetTensorInfo(f((batch, 8, 8, 10)))
+    al = net.AddActivationLayer(ActivationFunction.ReLu, name="relu")
+    c1.GetOutputSlot(0).Connect(al.GetInputSlot(0))
+    al.GetOutputSlot(0).SetTensorInfo(f((batch, 8, 8, 10)))
+    w2 = (rng.standard_normal((1, 3, 3, 10)) * 0.3).astype(np.float32)
+    w2l = net.AddConstantLayer(w2, f(w2.shape), "w2")
+    d2 = net.AddDepthwiseConvolution2dLayer((2, 2), (1, 1, 1, 1), (1, 1), False, "dw")
+    al.GetOutputSlot(0).Connect(d2.GetInputSlot(0))
+    w2l.GetOutputSlot(0).Connect(d2.GetInputSlot(1))
+    d2.GetOutputSlot(0).SetTensorInfo(f((batch, 4, 4, 10)))
+    w3 = (rng.standard_normal((7, 160)) * 0.1).astype(np.float32)
+    b3 = rng.standard_normal(7).astype(np.float32)
+    w3l = net.AddConstantLayer(w3, f(w3.shape), "w3")
+    b3l = net.AddConstantLayer(b3, f(b3.shape), "b3")
+    fc = net.AddFullyConnectedLayer(True, True, "fc")
+    d2.GetOutputSlot(0).Connect(fc.GetInputSlot(0))
+    w3l.GetOutputSlot(0).Connect(fc.GetInputSlot(1))
+    b3l.GetOutputSlot(0).Connect(fc.GetInputSlot(2))
+    fc.GetOutputSlot(0).SetTensorInfo(f((batch, 7)))
+    ol = net.AddOutputLayer(0, "output")
+    fc.GetOutputSlot(0).Connect(ol.GetInputSlot(0))
+    return net, {"input_shape": (batch, 8, 8, 6)}
+
+
+@needs_plugin
+@pytest.mark.gpu
+def test_float32_contractions_through_the_runtime_equal_cpuref():
+    """Convolution2d, DepthwiseConvolution2d and FullyConnected on Float32 tensors: the kernels add the terms in the
+    reference's order with the reference's rounding, so B200Acc and CpuRef return identical bits."""
+    net, info = _float_net()
+    x = np.random.default_rng(17).standard_normal(info["input_shape"]).astype(np.float32)
+    ref = hostnet.ArmnnNetwork(net, "CpuRef").run({0: x})[0]
+    got = hostnet.ArmnnNetwork(net, "B200Acc").run({0: x})[0]
+    assert ref.shape == got.shape and np.array_equal(ref, got)
