@@ -29,6 +29,8 @@ namespace b200k {
 constexpr int FS_WARPS = 8;                          // consumer warps
 constexpr int FS_THREADS = 32 * (FS_WARPS + 1);      // + the producer warp
 constexpr int FS_MAX_STAGES = 16;
+constexpr int FS_BATCH = 4;                          // units whose partial sums are added behind one barrier
+constexpr int FS_TAB_UNITS = 32;                     // units per CTA whose per-channel constants are staged ahead of the wait
 constexpr long long FS_WAIT_LIMIT_CYCLES = 4000000000ll;
 
 __device__ int g_fs_status = 0;
@@ -99,15 +101,18 @@ __global__ void __launch_bounds__(FS_THREADS, 2) fc_stream_kernel(const FsArgs a
 {
     extern __shared__ __align__(128) uint8_t fs_smem[];
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    // [mp input rows][pitch] | ring [stages][R][pitch] | partial sums [2][FS_WARPS][16 * 8] | weight-row sums [2][FS_WARPS][8]
-    // | input-row sums [16] | barriers full[16], empty[16]
+    // [mp input rows][pitch] | ring [stages][R][pitch] | partial sums [FS_BATCH][FS_WARPS][M * 8] | weight-row sums [FS_BATCH][FS_WARPS][8]
+    // | input-row sums [16] | barriers full[16], empty[16] | per-channel multiplier and bias term of the CTA's first
+    // FS_TAB_UNITS units [2][FS_TAB_UNITS][8]
     uint8_t* s_x = fs_smem;
     uint8_t* s_ring = s_x + (size_t)a.mp * a.pitch;
     int* s_part = (int*)(s_ring + (size_t)a.stages * a.R * a.pitch);
-    int* s_wpart = s_part + 2 * FS_WARPS * 128;
-    int* s_xsum = s_wpart + 2 * FS_WARPS * 8;
+    int* s_wpart = s_part + FS_BATCH * FS_WARPS * a.M * 8;
+    int* s_xsum = s_wpart + FS_BATCH * FS_WARPS * 8;
     uint64_t* full = (uint64_t*)(s_xsum + 16);
     uint64_t* empty = full + FS_MAX_STAGES;
+    float* s_mm = (float*)(empty + FS_MAX_STAGES);
+    float* s_bb = s_mm + FS_TAB_UNITS * 8;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int units = (a.N + a.R - 1) / a.R;
 
@@ -141,8 +146,17 @@ __global__ void __launch_bounds__(FS_THREADS, 2) fc_stream_kernel(const FsArgs a
     }
 
     // ===================== consumers =====================
-    asm volatile("griddepcontrol.wait;" ::: "memory");                 // the input rows come from the kernel before this one
     const int ctid = threadIdx.x;                                         // 0 .. 255
+    // Scales and bias do not depend on the kernel before this one either: the requantisation constants of this CTA's
+    // units are formed now, so that no global load sits between a unit's sums and its stores later on.
+    for (int i = ctid; i < FS_TAB_UNITS * 8; i += 32 * FS_WARPS) {
+        const int n = (blockIdx.x + (i >> 3) * gridDim.x) * a.R + (i & 7);
+        if ((i & 7) < a.R && n < a.N) {
+            s_mm[i] = __fmul_rn(a.sx, a.w_scales ? a.w_scales[n] : a.w_scale);
+            s_bb[i] = a.bias ? __fmul_rn(__int2float_rn(a.bias[n]), a.b_scales ? a.b_scales[n] : a.b_scale) : 0.f;
+        }
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");                 // the input rows come from the kernel before this one
     {
         const int kv = a.K / 16;
         for (int i = ctid; i < a.mp * kv; i += 32 * FS_WARPS) {
@@ -174,75 +188,95 @@ __global__ void __launch_bounds__(FS_THREADS, 2) fc_stream_kernel(const FsArgs a
     const uint32_t xb_addr = xa_addr + (uint32_t)(8 * a.pitch);
     const bool row_a = g < a.M, row_b = g + 8 < a.M;        // fragment rows without an input row are zero
     const int nblk = a.K / 64;
-    int s = 0; uint32_t ph = 0, it = 0;
+    int s = 0; uint32_t ph = 0;
     bool dead = false;
-    for (int u = blockIdx.x; u < units; u += gridDim.x, ++it) {
-        const int n0 = u * a.R;
-        const int rows = min(a.R, a.N - n0);
-        if (!dead && !fs_wait(&full[s], ph, a.wait_limit)) { atomicExch(&g_fs_status, 2); dead = true; }
-        // four independent accumulator sets: consecutive MMAs do not wait for one another (a dependent mma.sync chain,
-        // not the weight stream, would otherwise set the time per unit)
-        int acc[4][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}, {0, 0, 0, 0}, {0, 0, 0, 0}};
-        int wl = 0;                                          // this lane's share of sum w of weight row g
-        const uint32_t w_addr = fs_smem_u32(s_ring) + (uint32_t)((s * a.R + g) * a.pitch + t * 16);
-        if (!dead) {
-            const bool wrow = g < rows;
-            #pragma unroll 2
-            for (int b = warp; b < nblk; b += 2 * FS_WARPS) {
-                const int b2 = b + FS_WARPS;
-                const bool second = b2 < nblk;
-                const uint4 xa0 = row_a ? fs_lds128(xa_addr + b * 64) : make_uint4(0, 0, 0, 0);
-                const uint4 xb0 = row_b ? fs_lds128(xb_addr + b * 64) : make_uint4(0, 0, 0, 0);
-                const uint4 wv0 = wrow ? fs_lds128(w_addr + b * 64) : make_uint4(0, 0, 0, 0);
-                const uint4 xa1 = (second && row_a) ? fs_lds128(xa_addr + b2 * 64) : make_uint4(0, 0, 0, 0);
-                const uint4 xb1 = (second && row_b) ? fs_lds128(xb_addr + b2 * 64) : make_uint4(0, 0, 0, 0);
-                const uint4 wv1 = (second && wrow) ? fs_lds128(w_addr + b2 * 64) : make_uint4(0, 0, 0, 0);
-                fs_mma<XU, WU>(acc[0], xa0.x, xb0.x, xa0.y, xb0.y, wv0.x, wv0.y);
-                fs_mma<XU, WU>(acc[1], xa0.z, xb0.z, xa0.w, xb0.w, wv0.z, wv0.w);
-                fs_mma<XU, WU>(acc[2], xa1.x, xb1.x, xa1.y, xb1.y, wv1.x, wv1.y);
-                fs_mma<XU, WU>(acc[3], xa1.z, xb1.z, xa1.w, xb1.w, wv1.z, wv1.w);
-                if (a.zx != 0) {
-                    wl = dp4a_mixed<WU, true>(wv0.x, 0x01010101u, wl); wl = dp4a_mixed<WU, true>(wv0.y, 0x01010101u, wl);
-                    wl = dp4a_mixed<WU, true>(wv0.z, 0x01010101u, wl); wl = dp4a_mixed<WU, true>(wv0.w, 0x01010101u, wl);
-                    wl = dp4a_mixed<WU, true>(wv1.x, 0x01010101u, wl); wl = dp4a_mixed<WU, true>(wv1.y, 0x01010101u, wl);
-                    wl = dp4a_mixed<WU, true>(wv1.z, 0x01010101u, wl); wl = dp4a_mixed<WU, true>(wv1.w, 0x01010101u, wl);
+    // The CTA's units are worked off in batches of FS_BATCH: every warp runs through its share of K for all units of
+    // the batch without meeting the other warps (it only waits for the weights), then the partial sums of the whole
+    // batch are added and requantised behind one barrier.  [unit of the batch][warp][input row][8 weight rows]
+    const int my_units = units > (int)blockIdx.x ? (units - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+    for (int base = 0; base < my_units; base += FS_BATCH) {
+        const int nb = min(FS_BATCH, my_units - base);
+        #pragma unroll
+        for (int j = 0; j < FS_BATCH; ++j) {
+            if (j >= nb) break;
+            const int u = (int)blockIdx.x + (base + j) * (int)gridDim.x;
+            const int rows = min(a.R, a.N - u * a.R);
+            if (!dead && !fs_wait(&full[s], ph, a.wait_limit)) { atomicExch(&g_fs_status, 2); dead = true; }
+            // four independent accumulator sets: consecutive MMAs do not wait for one another (a dependent mma.sync
+            // chain, not the weight stream, would otherwise set the time per unit)
+            int acc[4][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}, {0, 0, 0, 0}, {0, 0, 0, 0}};
+            int wl = 0;                                      // this lane's share of sum w of weight row g
+            const uint32_t w_addr = fs_smem_u32(s_ring) + (uint32_t)((s * a.R + g) * a.pitch + t * 16);
+            if (!dead) {
+                const bool wrow = g < rows;
+                #pragma unroll 2
+                for (int b = warp; b < nblk; b += 2 * FS_WARPS) {
+                    const int b2 = b + FS_WARPS;
+                    const bool second = b2 < nblk;
+                    const uint4 xa0 = row_a ? fs_lds128(xa_addr + b * 64) : make_uint4(0, 0, 0, 0);
+                    const uint4 xb0 = row_b ? fs_lds128(xb_addr + b * 64) : make_uint4(0, 0, 0, 0);
+                    const uint4 wv0 = wrow ? fs_lds128(w_addr + b * 64) : make_uint4(0, 0, 0, 0);
+                    const uint4 xa1 = (second && row_a) ? fs_lds128(xa_addr + b2 * 64) : make_uint4(0, 0, 0, 0);
+                    const uint4 xb1 = (second && row_b) ? fs_lds128(xb_addr + b2 * 64) : make_uint4(0, 0, 0, 0);
+                    const uint4 wv1 = (second && wrow) ? fs_lds128(w_addr + b2 * 64) : make_uint4(0, 0, 0, 0);
+                    fs_mma<XU, WU>(acc[0], xa0.x, xb0.x, xa0.y, xb0.y, wv0.x, wv0.y);
+                    fs_mma<XU, WU>(acc[1], xa0.z, xb0.z, xa0.w, xb0.w, wv0.z, wv0.w);
+                    fs_mma<XU, WU>(acc[2], xa1.x, xb1.x, xa1.y, xb1.y, wv1.x, wv1.y);
+                    fs_mma<XU, WU>(acc[3], xa1.z, xb1.z, xa1.w, xb1.w, wv1.z, wv1.w);
+                    if (a.zx != 0) {
+                        wl = dp4a_mixed<WU, true>(wv0.x, 0x01010101u, wl); wl = dp4a_mixed<WU, true>(wv0.y, 0x01010101u, wl);
+                        wl = dp4a_mixed<WU, true>(wv0.z, 0x01010101u, wl); wl = dp4a_mixed<WU, true>(wv0.w, 0x01010101u, wl);
+                        wl = dp4a_mixed<WU, true>(wv1.x, 0x01010101u, wl); wl = dp4a_mixed<WU, true>(wv1.y, 0x01010101u, wl);
+                        wl = dp4a_mixed<WU, true>(wv1.z, 0x01010101u, wl); wl = dp4a_mixed<WU, true>(wv1.w, 0x01010101u, wl);
+                    }
                 }
             }
+            #pragma unroll
+            for (int c = 0; c < 4; ++c) acc[0][c] += acc[1][c] + acc[2][c] + acc[3][c];
+            // sum w of row g: the four lanes of a group hold the four 16-byte columns
+            wl += __shfl_xor_sync(0xffffffffu, wl, 1);
+            wl += __shfl_xor_sync(0xffffffffu, wl, 2);
+            // this warp has read its part of the stage
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(fs_smem_u32(&empty[s])) : "memory");
+            if (++s == a.stages) { s = 0; ph ^= 1u; }
+            // partial sums of this warp: C fragment (row g: columns 2t, 2t + 1; row g + 8 likewise); rows without an
+            // input row are not kept
+            int* part = s_part + (j * FS_WARPS + warp) * (a.M * 8);
+            if (row_a) { part[g * 8 + 2 * t] = acc[0][0]; part[g * 8 + 2 * t + 1] = acc[0][1]; }
+            if (row_b) { part[(g + 8) * 8 + 2 * t] = acc[0][2]; part[(g + 8) * 8 + 2 * t + 1] = acc[0][3]; }
+            if (t == 0) s_wpart[(j * FS_WARPS + warp) * 8 + g] = wl;
         }
-        #pragma unroll
-        for (int c = 0; c < 4; ++c) acc[0][c] += acc[1][c] + acc[2][c] + acc[3][c];
-        // sum w of row g: the four lanes of a group hold the four 16-byte columns
-        wl += __shfl_xor_sync(0xffffffffu, wl, 1);
-        wl += __shfl_xor_sync(0xffffffffu, wl, 2);
-        // this warp has read its part of the stage
-        __syncwarp();
-        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(fs_smem_u32(&empty[s])) : "memory");
-        if (++s == a.stages) { s = 0; ph ^= 1u; }
-        // partial sums of this warp: C fragment (row g: columns 2t, 2t + 1; row g + 8 likewise)
-        int* part = s_part + ((it & 1) * FS_WARPS + warp) * 128;
-        part[g * 8 + 2 * t] = acc[0][0]; part[g * 8 + 2 * t + 1] = acc[0][1];
-        part[(g + 8) * 8 + 2 * t] = acc[0][2]; part[(g + 8) * 8 + 2 * t + 1] = acc[0][3];
-        int* wpart = s_wpart + ((it & 1) * FS_WARPS + warp) * 8;
-        if (t == 0) wpart[g] = wl;
         fs_consumer_barrier();
-        if (ctid < 128) {
-            const int m = ctid >> 3, nl = ctid & 7;
+        for (int o = ctid; o < nb * a.M * 8; o += 32 * FS_WARPS) {
+            const int j = o / (a.M * 8), r = o - j * (a.M * 8);
+            const int m = r >> 3, nl = r & 7;
+            const int it = base + j;
+            const int n0 = ((int)blockIdx.x + it * (int)gridDim.x) * a.R;
+            const int rows = min(a.R, a.N - n0);
             int total = 0, ws = 0;
             #pragma unroll
             for (int w8 = 0; w8 < FS_WARPS; ++w8) {
-                total += s_part[((it & 1) * FS_WARPS + w8) * 128 + ctid];
-                ws += s_wpart[((it & 1) * FS_WARPS + w8) * 8 + nl];
+                total += s_part[(j * FS_WARPS + w8) * (a.M * 8) + r];
+                ws += s_wpart[(j * FS_WARPS + w8) * 8 + nl];
             }
-            if (m < a.M && nl < rows && !dead) {
+            if (nl < rows && !dead) {
                 const int n = n0 + nl;
                 total = total - a.zw * s_xsum[m] - a.zx * ws + a.K * a.zx * a.zw;
-                const long long o = (long long)m * a.N + n;
-                if (a.acc_out) a.acc_out[o] = total;
-                const float mm = __fmul_rn(a.sx, a.w_scales ? a.w_scales[n] : a.w_scale);
-                const float bb = a.bias ? __fmul_rn(__int2float_rn(a.bias[n]), a.b_scales ? a.b_scales[n] : a.b_scale) : 0.f;
-                a.y[o] = (uint8_t)requant_fast(total, mm, bb, a.bias != nullptr, a.sy, a.inv_sy, a.zy, a.lo, a.hi);
+                const long long oi = (long long)m * a.N + n;
+                if (a.acc_out) a.acc_out[oi] = total;
+                float mm, bb;
+                if (it < FS_TAB_UNITS) {
+                    mm = s_mm[it * 8 + nl]; bb = s_bb[it * 8 + nl];
+                } else {
+                    mm = __fmul_rn(a.sx, a.w_scales ? a.w_scales[n] : a.w_scale);
+                    bb = a.bias ? __fmul_rn(__int2float_rn(a.bias[n]), a.b_scales ? a.b_scales[n] : a.b_scale) : 0.f;
+                }
+                a.y[oi] = (uint8_t)requant_fast(total, mm, bb, a.bias != nullptr, a.sy, a.inv_sy, a.zy, a.lo, a.hi);
             }
         }
+        // the partial sums are overwritten by the next batch
+        if (base + FS_BATCH < my_units) fs_consumer_barrier();
     }
 }
 
@@ -285,7 +319,8 @@ int launch_fc_stream(const b200k_fc_params* p, cudaStream_t stream)
     // two input rows, say.  Otherwise one CTA per SM with all of the shared memory.
     // Rows per unit (at most 8, the MMA's width): the fewest rounds of units over the SMs, each round costing a fixed
     // quarter of a microsecond (barrier, reduction, requantisation) plus the unit's share of the SM's 43 GB/s of HBM.
-    const size_t fixed = (size_t)a.mp * a.pitch + (2 * FS_WARPS * 128 + 2 * FS_WARPS * 8 + 16) * 4 + 2 * FS_MAX_STAGES * 8 + 128;
+    const size_t fixed = (size_t)a.mp * a.pitch + (size_t)(FS_BATCH * FS_WARPS * a.mp * 8 + FS_BATCH * FS_WARPS * 8 + 16) * 4 + 2 * FS_MAX_STAGES * 8 + 128 +
+                         2 * FS_TAB_UNITS * 8 * 4;
     const size_t budget = fixed + 90 * 1024 <= 112 * 1024 ? 112 * 1024 : 227 * 1024;
     a.R = 0;
     {
