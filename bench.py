@@ -355,13 +355,17 @@ def run_b200(args):
     e2e = None
     if args.api == "plugin" and armnn_host.available() and os.path.exists(armnn_host.PLUGIN_PATH):
         sampler.start()
+        # every LoadedNetwork has a host thread that spins in its stream synchronisation: with N ranks on one host no more
+        # threads than half the cores (8 ranks x 4 threads on 32 cores gave 244 k images/s, 8 x 2 gave 302 k)
+        cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 8)
+        n_nets = max(1, min(args.e2e_nets, max(2, cores // (2 * world))))
         e2e_s, h2d, d2h, glaunches, gkernels = _plugin_e2e(torch, configs.resnet50(per_gpu, IMAGE)[0], info, local, args.steps,
-                                                           args.warmup, barrier, max_over_ranks, rank, args.e2e_nets)
+                                                           args.warmup, barrier, max_over_ranks, rank, n_nets)
         sampler.pause()
         e2e = {"value": GLOBAL_BATCH * args.steps / e2e_s, "unit": "images/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                "ms_per_step": e2e_s / args.steps * 1e3,
                "api": "IRuntime::EnqueueWorkload on the B200Acc plugin inside the unmodified Arm NN runtime, pre-imported "
-                      "pinned host buffers, %d LoadedNetworks / host threads per GPU" % args.e2e_nets,
+                      "pinned host buffers, %d LoadedNetworks / host threads per GPU" % n_nets,
                "graph_launches": glaunches, "graph_kernels": gkernels}
     else:
         # the Python mirror's pipelined requests (the Arm NN runtime library is not present on this machine)
