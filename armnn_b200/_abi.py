@@ -90,6 +90,10 @@ class ViewCopyParams(C.Structure):
                 ("src_offset", C.c_int64), ("dst_offset", C.c_int64)]
 
 
+class UnaryParams(C.Structure):
+    _fields_ = [("x", QTensor), ("y", QTensor), ("count", C.c_int64), ("operation", C.c_int32)]
+
+
 class ReduceParams(C.Structure):
     _fields_ = [("x", QTensor), ("y", QTensor), ("rank", C.c_int32), ("shape", C.c_int32 * 6), ("axis_mask", C.c_int32),
                 ("op", C.c_int32)]
@@ -152,6 +156,7 @@ KERNEL_ENTRY_POINTS = {
     "view_copy_q": ViewCopyParams,
     "resize_q": ResizeParams,
     "reduce_q": ReduceParams,
+    "unary_q": UnaryParams,
 }
 
 # every symbol include/b200k.h declares

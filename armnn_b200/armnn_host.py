@@ -181,6 +181,8 @@ class ArmnnNetwork:
             elif t == "Stack":
                 ish = layer.inputs[0].source.info.shape
                 lid = lib.armnnc_add_stack(net, d["axis"], len(layer.inputs), len(ish), _shape_arr(ish))
+            elif t == "ElementwiseUnary":
+                lid = lib.armnnc_add_elementwise_unary(net, d["op"])
             elif t == "Reduce":
                 axes = (C.c_int32 * len(d["axis"]))(*d["axis"])
                 lid = lib.armnnc_add_reduce(net, axes, len(d["axis"]), d["op"], int(d["keep_dims"]))

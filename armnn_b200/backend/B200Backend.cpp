@@ -148,6 +148,13 @@ public:
                 if (d.m_BiasEnabled && (infos.size() < 4 || infos[3].GetDataType() != DataType::Signed32)) { return No(reason, "bias must be Signed32"); }
                 return true;
             }
+            case LayerType::ElementwiseUnary:
+            {
+                const auto op = PolymorphicDowncast<const ElementwiseUnaryDescriptor*>(&descriptor)->m_Operation;
+                if (op == UnaryOperation::LogicalNot) { return No(reason, "LogicalNot is not supported"); }
+                if (!IsActType(infos[0]) || infos[0].GetDataType() != infos[1].GetDataType()) { return No(reason, "unsupported or mismatched data types"); }
+                return true;
+            }
             case LayerType::Resize:
             {
                 const auto& d = *PolymorphicDowncast<const ResizeDescriptor*>(&descriptor);

@@ -933,6 +933,22 @@ std::unique_ptr<IWorkload> B200WorkloadFactory::CreateWorkload(LayerType type, c
                 B200CheckStatus(b200k_transpose_conv2d_q8(&st->p, s));
             });
         }
+        case LayerType::ElementwiseUnary:
+        {
+            const auto& qd = *PolymorphicDowncast<const ElementwiseUnaryQueueDescriptor*>(&d);
+            auto st = std::make_shared<SimpleState<b200k_unary_params>>(ctx);
+            b200k_unary_params& p = st->p;
+            std::memset(&p, 0, sizeof(p));
+            const TensorInfo& x = info.m_InputTensorInfos[0];
+            p.x = Operand(x, st->blobs); p.y = Operand(info.m_OutputTensorInfos[0], st->blobs);
+            p.count = static_cast<int64_t>(x.GetNumElements());
+            p.operation = static_cast<int32_t>(qd.m_Parameters.m_Operation);
+            return Make<ElementwiseUnaryQueueDescriptor>(d, info, ctx, [st](const ElementwiseUnaryQueueDescriptor& data, cudaStream_t s)
+            {
+                st->p.x.data = Dev(data.m_Inputs[0]); st->p.y.data = Dev(data.m_Outputs[0]);
+                B200CheckStatus(b200k_unary_q(&st->p, s));
+            });
+        }
         case LayerType::Reduce:
         {
             const auto& qd = *PolymorphicDowncast<const ReduceQueueDescriptor*>(&d);

@@ -108,6 +108,7 @@ extern "C" size_t b200k_sizeof_params(int which)
         case 11: return sizeof(b200k_view_copy_params);
         case 12: return sizeof(b200k_resize_params);
         case 13: return sizeof(b200k_reduce_params);
+        case 14: return sizeof(b200k_unary_params);
         default: return 0;
     }
 }

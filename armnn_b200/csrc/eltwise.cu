@@ -78,6 +78,15 @@ __device__ __forceinline__ float activation_f(int fn, float in, float a, float b
         case 8:  return __fsqrt_rn(in);
         case 9:  return __fmul_rn(in, in);
         case 10: return (in >= 0) ? in : __fmul_rn(a, __fsub_rn(expf(in), 1.f));
+        // armnn::UnaryOperation + 100 (ElementwiseUnary): Abs, Exp, Sqrt, Rsqrt, Neg, -, Log, Sin, Ceil
+        case 100: return fabsf(in);
+        case 101: return expf(in);
+        case 102: return __fsqrt_rn(in);
+        case 103: return __fdiv_rn(1.f, __fsqrt_rn(in));
+        case 104: return -in;
+        case 106: return logf(in);
+        case 107: return sinf(in);
+        case 108: return ceilf(in);
         default: return __fdiv_rn(__fmul_rn(in, fminf(fmaxf(__fadd_rn(in, 3.f), 0.0f), 6.0f)), 6.f);
     }
 }
@@ -165,6 +174,14 @@ extern "C" int b200k_activation_q8(const b200k_activation_params* p, void* strea
     B200K_REQUIRE(p, B200K_E_INVALID, "activation_q8: null params");
     B200K_REQUIRE(p->function >= 0 && p->function <= 11, B200K_E_UNSUPPORTED, "activation_q8: unsupported activation function %d", p->function);
     return launch_unary(p->x, p->y, p->count, p->function, p->a, p->b, stream, "activation_q8");
+}
+
+extern "C" int b200k_unary_q(const b200k_unary_params* p, void* stream)
+{
+    B200K_REQUIRE(p, B200K_E_INVALID, "unary_q: null params");
+    B200K_REQUIRE(p->operation >= 0 && p->operation <= 8 && p->operation != 5, B200K_E_UNSUPPORTED,
+                  "unary_q: unsupported unary operation %d", p->operation);
+    return launch_unary(p->x, p->y, p->count, 100 + p->operation, 0.f, 0.f, stream, "unary_q");
 }
 
 extern "C" int b200k_convert_q(const b200k_convert_params* p, void* stream)

@@ -425,6 +425,12 @@ int armnnc_add_stack(void* vn, int axis, int num_inputs, int rank, const int32_t
     return add_layer(n, n->net->AddStackLayer(d));
 }
 
+int armnnc_add_elementwise_unary(void* vn, int operation)
+{
+    auto* n = static_cast<CNet*>(vn);
+    return add_layer(n, n->net->AddElementwiseUnaryLayer(ElementwiseUnaryDescriptor(static_cast<UnaryOperation>(operation))));
+}
+
 int armnnc_add_reduce(void* vn, const int32_t* axes, int n_axes, int operation, int keep_dims)
 {
     auto* n = static_cast<CNet*>(vn);

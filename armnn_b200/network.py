@@ -275,6 +275,10 @@ class INetwork:
         return self._add(Layer("TransposeConvolution2d", name, 3 if bias_enabled else 2, 1,
                                {"stride": tuple(stride), "pad": tuple(pad), "bias": bool(bias_enabled)}))
 
+    def AddElementwiseUnaryLayer(self, operation, name=None):
+        """armnn::UnaryOperation: 0 Abs, 1 Exp, 2 Sqrt, 3 Rsqrt, 4 Neg, 6 Log, 7 Sin, 8 Ceil (5 LogicalNot is not supported)."""
+        return self._add(Layer("ElementwiseUnary", name, 1, 1, {"op": int(operation)}))
+
     def AddReduceLayer(self, axis, operation, keep_dims=False, name=None):
         """armnn::ReduceDescriptor; operation follows armnn::ReduceOperation (0 Sum, 1 Max, 2 Mean, 3 Min, 4 Prod)."""
         return self._add(Layer("Reduce", name, 1, 1, {"axis": tuple(int(a) for a in axis), "op": int(operation), "keep_dims": bool(keep_dims)}))
@@ -359,6 +363,13 @@ def IsLayerSupported(layer):
     if t == "Pad":
         if len(ins[0].shape) > 4:
             return False, "Pad: rank > 4"
+        return True, ""
+    if t == "ElementwiseUnary":
+        ok = (DataType.QAsymmU8, DataType.QAsymmS8, DataType.QSymmS16, DataType.Float32)
+        if ins[0].dtype not in ok or outs[0].dtype != ins[0].dtype:
+            return False, "ElementwiseUnary: unsupported or mismatched data types"
+        if layer.desc["op"] not in (0, 1, 2, 3, 4, 6, 7, 8):
+            return False, "ElementwiseUnary: operation %d is not supported" % layer.desc["op"]
         return True, ""
     if t == "TransposeConvolution2d":
         if ins[0].dtype not in _Q8 or outs[0].dtype not in _Q8 or ins[1].dtype not in _Q8:
@@ -719,6 +730,13 @@ class GraphProgram:
         p.dil_h = p.dil_w = 1
         p.clamp_lo, p.clamp_hi = _clamp(layer, y.info)
         return "transpose_conv2d_q8", p
+
+    def _make_ElementwiseUnary(self, layer):
+        x, y = layer.inputs[0].source, layer.outputs[0]
+        p = _abi.UnaryParams()
+        p.x, p.y = self._operand(x), self._operand(y)
+        p.count, p.operation = x.info.GetNumElements(), layer.desc["op"]
+        return "unary_q", p
 
     def _reduce(self, layer, axes, op):
         x, y = layer.inputs[0].source, layer.outputs[0]

@@ -241,6 +241,18 @@ typedef struct {
 
 int b200k_activation_q8(const b200k_activation_params* p, void* stream);
 
+/* armnn::ElementwiseUnary (src/backends/reference/workloads/RefElementwiseUnaryWorkload.cpp:36-110 with Abs.hpp, Exp.hpp,
+ * Sqrt.hpp, Rsqrt.hpp, Log.hpp, Sin.hpp, Ceil.hpp and std::negate): y = Q_y(f(deq_x(x))); operation follows
+ * armnn::UnaryOperation (0 Abs, 1 Exp, 2 Sqrt, 3 Rsqrt = 1 / sqrt, 4 Neg, 6 Log, 7 Sin, 8 Ceil; 5 LogicalNot is a
+ * Boolean operation and not supported). */
+typedef struct {
+    b200k_qtensor x, y;
+    int64_t count;
+    int32_t operation;
+} b200k_unary_params;
+
+int b200k_unary_q(const b200k_unary_params* p, void* stream);
+
 /* armnn::Pad with PaddingMode::Constant (src/backends/reference/workloads/Pad.cpp:21-170, RefPadWorkload.cpp):
  * y has shape[d] + pad_before[d] + pad_after[d] elements along dimension d (rank <= 4, outermost first); elements
  * outside the copied block hold pad_value — for a quantised y a quantised number already (the reference encodes it with

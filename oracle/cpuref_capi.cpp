@@ -389,6 +389,21 @@ extern "C" int cpuref_pad_q(const b200k_pad_params* p)
     });
 }
 
+extern "C" int cpuref_unary_q(const b200k_unary_params* p)
+{
+    return guarded([&] {
+        Harness h;
+        ElementwiseUnaryQueueDescriptor d;
+        d.m_Parameters.m_Operation = static_cast<UnaryOperation>(p->operation);
+        const TensorShape shape({(unsigned)p->count});
+        TensorInfo xi = make_info(p->x, shape, 0, 0, false), yi = make_info(p->y, shape, 0, 0, false);
+        h.in(d, xi, p->x.data);
+        ITensorHandle* o = h.out(d, yi);
+        h.run(LayerType::ElementwiseUnary, d);
+        copy_out(o, const_cast<void*>(p->y.data), yi.GetNumBytes());
+    });
+}
+
 extern "C" int cpuref_reduce_q(const b200k_reduce_params* p)
 {
     return guarded([&] {

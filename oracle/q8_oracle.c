@@ -496,6 +496,28 @@ static float activation_f(float in, int fn, float a, float b)
     }
 }
 
+/* ElementwiseUnary, RefElementwiseUnaryWorkload.cpp:36-110: y = Q_y(f(deq_x(x))) with the std:: function of the operation */
+int oracle_unary_q(const b200k_unary_params* p)
+{
+    if (!p || !p->x.data || !p->y.data || p->operation < 0 || p->operation > 8 || p->operation == 5) return B200K_E_INVALID;
+    for (int64_t i = 0; i < p->count; ++i) {
+        const float in = load_f(&p->x, i);
+        float r;
+        switch (p->operation) {
+            case 0: r = fabsf(in); break;
+            case 1: r = expf(in); break;
+            case 2: r = sqrtf(in); break;
+            case 3: r = 1 / sqrtf(in); break;
+            case 4: r = -in; break;
+            case 6: r = logf(in); break;
+            case 7: r = sinf(in); break;
+            default: r = ceilf(in); break;
+        }
+        store_f(&p->y, i, r);
+    }
+    return 0;
+}
+
 int oracle_activation_q8(const b200k_activation_params* p)
 {
     if (!p->x.data || !p->y.data || p->function < 0 || p->function > 11) return B200K_E_INVALID;

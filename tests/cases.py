@@ -427,6 +427,44 @@ def tconv_cases():
     }
 
 
+# unary operations whose result depends on libm's exp / log / sin (the device functions differ in the last bit)
+TRANSCENDENTAL_UNARY = ("exp_s8", "log_u8", "sin_s8", "exp_float")
+
+
+def unary_cases():
+    """ElementwiseUnary: every supported operation on quantised and float tensors."""
+    def make(seed, count, op, dtype=S8, xq=(0.05, -3), yq=None, positive=False):
+        def build(mem):
+            rng = np.random.default_rng(seed)
+            p = _abi.UnaryParams()
+            if dtype == F32:
+                x = rng.standard_normal(count).astype(np.float32) * 2
+                x = np.abs(x) + np.float32(0.1) if positive else x
+            else:
+                x = _rand(rng, dtype, (count,))
+                if positive:                              # dequantised values > 0
+                    lo, hi = RANGE[dtype]
+                    x = np.clip(x, xq[1] + 1, hi).astype(NP_OF[dtype])
+            p.x = qt(mem, x, dtype, *xq)
+            p.y, y = qt_out(mem, (count,), dtype, *(yq or xq))
+            p.count, p.operation = count, op
+            return p, [y]
+        return lambda: SimpleCase("unary_q", build)
+    ABS, EXP, SQRT, RSQRT, NEG, LOG, SIN, CEIL = 0, 1, 2, 3, 4, 6, 7, 8
+    return {
+        "abs_s8": make(361, 1000, ABS),
+        "neg_u8_requantise": make(362, 777, NEG, dtype=U8, xq=(0.1, 128), yq=(0.12, 120)),
+        "sqrt_u8": make(363, 513, SQRT, dtype=U8, xq=(0.07, 10), yq=(0.02, 0), positive=True),
+        "rsqrt_s8": make(364, 300, RSQRT, xq=(0.05, -100), yq=(0.05, -128), positive=True),
+        "ceil_s16": make(365, 999, CEIL, dtype=S16, xq=(0.013, 0), yq=(0.5, 0)),
+        "ceil_float": make(366, 257, CEIL, dtype=F32, xq=(1.0, 0)),
+        "exp_s8": make(367, 1000, EXP, xq=(0.02, 5), yq=(0.1, -128)),
+        "log_u8": make(368, 900, LOG, dtype=U8, xq=(0.05, 0), yq=(0.05, 128), positive=True),
+        "sin_s8": make(369, 1111, SIN, xq=(0.05, 0), yq=(0.008, 0)),
+        "exp_float": make(370, 400, EXP, dtype=F32, xq=(1.0, 0)),
+    }
+
+
 def reduce_cases():
     """Reduce: every operation, inner / outer / several / all axes, re-quantisation, float."""
     def make(seed, shape, axes, op, dtype=S8, xq=(0.05, -3), yq=None):
@@ -540,7 +578,7 @@ def move_cases():
 
 ALL_GROUPS = {"conv": conv_cases, "dwconv": dwconv_cases, "fc": fc_cases, "bmm": bmm_cases, "pool": pool_cases,
               "mean": mean_cases, "eltwise": eltwise_cases, "activation": activation_cases, "softmax": softmax_cases,
-              "convert": convert_cases, "pad": pad_cases, "qlstm": qlstm_cases, "move": move_cases, "resize": resize_cases, "reduce": reduce_cases, "tconv": tconv_cases, "f32": f32_cases}
+              "convert": convert_cases, "pad": pad_cases, "qlstm": qlstm_cases, "move": move_cases, "resize": resize_cases, "reduce": reduce_cases, "tconv": tconv_cases, "f32": f32_cases, "unary": unary_cases}
 
 
 def run_case(case, where):

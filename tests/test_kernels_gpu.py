@@ -29,7 +29,8 @@ def test_cuda_matches_oracle(built, group, name, factory):
     want = cases.run_case(case, "oracle")
     got = cases.run_case(case, "gpu")
     assert len(want) == len(got)
-    exact = group in EXACT_GROUPS or (group == "activation" and name not in cases.TRANSCENDENTAL_ACTIVATIONS)
+    exact = (group in EXACT_GROUPS or (group == "activation" and name not in cases.TRANSCENDENTAL_ACTIVATIONS) or
+             (group == "unary" and name not in cases.TRANSCENDENTAL_UNARY))
     for w, g in zip(want, got):
         assert w.shape == g.shape and w.dtype == g.dtype
         if exact:
@@ -37,6 +38,9 @@ def test_cuda_matches_oracle(built, group, name, factory):
                 assert np.array_equal(w, g), (group, name)
             else:
                 assert np.array_equal(w, g), (group, name, diff_stats(w, g))
+        elif w.dtype == np.float32:
+            # libm against the device's exp / log / sin: a few units in the last place
+            assert np.allclose(w, g, rtol=1e-6, atol=1e-7), (group, name)
         else:
             st = diff_stats(w, g)
             # int16 cell state of the QLstm: +-2 (two chained transcendental roundings), everything else +-1

@@ -702,3 +702,26 @@ def test_float32_contractions_through_the_runtime_equal_cpuref():
     ref = hostnet.ArmnnNetwork(net, "CpuRef").run({0: x})[0]
     got = hostnet.ArmnnNetwork(net, "B200Acc").run({0: x})[0]
     assert ref.shape == got.shape and np.array_equal(ref, got)
+
+
+@needs_plugin
+@pytest.mark.gpu
+def test_elementwise_unary_through_the_runtime_matches_cpuref():
+    """Abs -> Sqrt -> Neg -> Ceil (exact operations) on a quantised tensor: identical bytes to CpuRef."""
+    from armnn_b200.network import DataType, INetwork, TensorInfo
+    net = INetwork.Create()
+    il = net.AddInputLayer(0, "input")
+    t = TensorInfo((2, 5, 6, 16), DataType.QAsymmS8, 0.05, -3)
+    il.GetOutputSlot(0).SetTensorInfo(t)
+    prev = il
+    for i, (op, q) in enumerate([(0, (0.05, -128)), (2, (0.02, -128)), (4, (0.02, 127)), (8, (1.0, 0))]):
+        l = net.AddElementwiseUnaryLayer(op, "unary%d" % i)
+        prev.GetOutputSlot(0).Connect(l.GetInputSlot(0))
+        l.GetOutputSlot(0).SetTensorInfo(TensorInfo((2, 5, 6, 16), DataType.QAsymmS8, *q))
+        prev = l
+    ol = net.AddOutputLayer(0, "output")
+    prev.GetOutputSlot(0).Connect(ol.GetInputSlot(0))
+    x = np.random.default_rng(19).integers(-128, 128, size=(2, 5, 6, 16)).astype(np.int8)
+    ref = hostnet.ArmnnNetwork(net, "CpuRef").run({0: x})[0]
+    got = hostnet.ArmnnNetwork(net, "B200Acc").run({0: x})[0]
+    assert np.array_equal(ref, got)
