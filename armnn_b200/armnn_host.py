@@ -176,11 +176,18 @@ class ArmnnNetwork:
                 assert lid >= 0, lib.armnnc_last_error().decode()
             elif t in ("DepthToSpace", "SpaceToDepth"):
                 lid = lib.armnnc_add_depth_to_space(net, d["block"], int(d["nchw"]), int(t == "SpaceToDepth"))
+            elif t in ("BatchToSpaceNd", "SpaceToBatchNd"):
+                blk = (C.c_int32 * len(d["block"]))(*d["block"])
+                flat = [v for pair in d["edges"] for v in pair]
+                lid = lib.armnnc_add_batch_to_space(net, blk, (C.c_int32 * len(flat))(*flat), len(d["block"]), int(d["nchw"]),
+                                                    int(t == "SpaceToBatchNd"))
             elif t == "ChannelShuffle":
                 lid = lib.armnnc_add_channel_shuffle(net, d["axis"], d["groups"])
             elif t == "Stack":
                 ish = layer.inputs[0].source.info.shape
                 lid = lib.armnnc_add_stack(net, d["axis"], len(layer.inputs), len(ish), _shape_arr(ish))
+            elif t == "Prelu":
+                lid = lib.armnnc_add_prelu(net)
             elif t == "ElementwiseUnary":
                 lid = lib.armnnc_add_elementwise_unary(net, d["op"])
             elif t == "Reduce":

@@ -176,6 +176,10 @@ public:
                 }
                 return true;
             }
+            case LayerType::BatchToSpaceNd:
+            case LayerType::SpaceToBatchNd:
+                if (infos[0].GetNumDimensions() != 3 && infos[0].GetNumDimensions() != 4) { return No(reason, "3 or 4 dimensions only"); }
+                ARMNN_FALLTHROUGH;
             case LayerType::SpaceToDepth:
             case LayerType::ChannelShuffle:
             case LayerType::Stack:
@@ -215,14 +219,19 @@ public:
             }
             case LayerType::Addition:
             case LayerType::Multiplication:
+            case LayerType::Subtraction:
+            case LayerType::Division:
+            case LayerType::Maximum:
+            case LayerType::Minimum:
+            case LayerType::Prelu:
             case LayerType::ElementwiseBinary:
             {
-                if (type == LayerType::ElementwiseBinary)
-                {
-                    const auto op = PolymorphicDowncast<const ElementwiseBinaryDescriptor*>(&descriptor)->m_Operation;
-                    if (op == BinaryOperation::Power || op == BinaryOperation::FloorDiv) { return No(reason, "Power / FloorDiv are not supported"); }
-                }
                 if (infos[2].GetNumDimensions() > 4) { return No(reason, "rank > 4"); }
+                if (type != LayerType::Prelu && (infos[0].GetNumDimensions() != infos[2].GetNumDimensions() ||
+                                                 infos[1].GetNumDimensions() != infos[2].GetNumDimensions()))
+                {
+                    return No(reason, "operands of different rank");
+                }
                 return (IsActType(infos[0]) && IsActType(infos[1]) && IsActType(infos[2])) || No(reason, "unsupported data type");
             }
             case LayerType::Activation:

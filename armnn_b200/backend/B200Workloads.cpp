@@ -169,6 +169,7 @@ struct ViewOp
 {
     b200k_view_copy_params p;
     unsigned int src, dst;          // index of the workload's input / output tensor
+    const void* fixedSrc;           // non-null: a device constant owned by the workload instead of input `src`
 };
 
 struct ViewState
@@ -202,7 +203,8 @@ std::unique_ptr<IWorkload> MakeViews(const QueueDescriptor& d, const WorkloadInf
     {
         for (ViewOp& op : st->ops)
         {
-            op.p.x.data = Dev(data.m_Inputs[op.src]); op.p.y.data = Dev(data.m_Outputs[op.dst]);
+            op.p.x.data = op.fixedSrc ? op.fixedSrc : Dev(data.m_Inputs[op.src]);
+            op.p.y.data = Dev(data.m_Outputs[op.dst]);
             B200CheckStatus(b200k_view_copy_q(&op.p, s));
         }
     });
@@ -378,6 +380,101 @@ std::unique_ptr<IWorkload> MakeDepthSpace(const QueueDescriptor& d, const Worklo
     if (h % b != 0 || w % b != 0) { throw InvalidArgumentException("B200Acc: SpaceToDepth height / width are not multiples of the block size"); }
     if (nchw) { return MakeWalk<QD>(d, info, ctx, {{n, is[0]}, {b, is[2]}, {b, is[3]}, {c, is[1]}, {h / b, b * is[2]}, {w / b, b * is[3]}}); }
     return MakeWalk<QD>(d, info, ctx, {{n, is[0]}, {h / b, b * is[1]}, {w / b, b * is[2]}, {b, is[1]}, {b, is[2]}, {c, 1}});
+}
+
+// BatchToSpaceNd (workloads/BatchToSpaceNd.cpp:50-117) and SpaceToBatchNd (workloads/SpaceToBatchNd.cpp:49-131), ranks 3
+// and 4, both layouts.  With the batch-side tensor B [nb * bh * bw, hb, wb, c] and the space-side tensor S [nb, hs, ws, c],
+// batch (i * bw + j) * nb + b of B pairs its pixel (y, x) with pixel (y * bh + i - top, x * bw + j - left) of S: one
+// strided block per (i, j).  BatchToSpaceNd copies B -> S (top / left: crops); SpaceToBatchNd copies S -> B (top / left:
+// padding) after filling B with its encoding of 0.0 when there is any padding.
+template <typename QD>
+std::unique_ptr<IWorkload> MakeBatchSpace(const QueueDescriptor& d, const WorkloadInfo& info, const ContextPtr& ctx,
+                                          const std::vector<unsigned int>& block,
+                                          const std::vector<std::pair<unsigned int, unsigned int>>& edges, DataLayout layout, bool toSpace)
+{
+    auto st = std::make_shared<ViewState>(ctx);
+    const TensorInfo& in = info.m_InputTensorInfos[0];
+    const TensorInfo& out = info.m_OutputTensorInfos[0];
+    const TensorInfo& B = toSpace ? in : out;
+    const TensorInfo& S = toSpace ? out : in;
+    const unsigned int rank = in.GetNumDimensions();
+    if ((rank != 3 && rank != 4) || out.GetNumDimensions() != rank || block.size() != rank - 2 || edges.size() != rank - 2)
+    {
+        throw InvalidArgumentException("B200Acc: BatchToSpaceNd / SpaceToBatchNd need 3 or 4 dimensions and one block extent per spatial dimension");
+    }
+    const bool nchw = layout == DataLayout::NCHW;
+    const unsigned int hI = nchw ? 2 : 1, wI = nchw ? 3 : 2, cI = nchw ? 1 : rank - 1;
+    auto dim = [&](const TensorInfo& t, unsigned int i) { return (i < rank) ? static_cast<int64_t>(t.GetShape()[i]) : int64_t(1); };
+    int64_t bs[6] = {0, 0, 0, 0, 0, 0}, ss[6] = {0, 0, 0, 0, 0, 0};
+    DenseStrides(B.GetShape(), bs);
+    DenseStrides(S.GetShape(), ss);
+    const bool hasW = rank == 4;
+    const int64_t bh = block[0], bw = hasW ? block[1] : 1;
+    const int64_t top = edges[0].first, bottom = edges[0].second, left = hasW ? edges[1].first : 0, right = hasW ? edges[1].second : 0;
+    const int64_t nb = dim(S, 0), hb = dim(B, hI), wb = hasW ? dim(B, wI) : 1, c = dim(B, cI);
+    const int64_t hs = dim(S, hI), wsz = hasW ? dim(S, wI) : 1;
+    if (bh < 1 || bw < 1 || dim(B, 0) != nb * bh * bw || dim(S, cI) != c || hb * bh != hs + top + bottom || wb * bw != wsz + left + right)
+    {
+        throw InvalidArgumentException("B200Acc: BatchToSpaceNd / SpaceToBatchNd shapes do not match the block shape and crops / padding");
+    }
+    const int64_t bsH = bs[hI], bsW = hasW ? bs[wI] : 0, bsC = bs[cI], ssH = ss[hI], ssW = hasW ? ss[wI] : 0, ssC = ss[cI];
+    if (!toSpace && (top || bottom || left || right))
+    {
+        // every element of the output <- one element holding Q_out(0.0) (source strides 0)
+        uint8_t zero[4] = {0, 0, 0, 0};
+        const DataType t = out.GetDataType();
+        if (t == DataType::QSymmS16)
+        {
+            const int16_t v = static_cast<int16_t>(std::min(std::max(out.GetQuantizationOffset(), -32768), 32767));
+            std::memcpy(zero, &v, 2);
+        }
+        else if (t == DataType::QAsymmU8) { zero[0] = static_cast<uint8_t>(std::min(std::max(out.GetQuantizationOffset(), 0), 255)); }
+        else if (t == DataType::QAsymmS8 || t == DataType::QSymmS8)
+        {
+            zero[0] = static_cast<uint8_t>(static_cast<int8_t>(std::min(std::max(out.GetQuantizationOffset(), -128), 127)));
+        }
+        ViewOp op = NewViewOp(out, out, st->blobs, 0, 0, rank);
+        op.fixedSrc = st->blobs.Upload(zero, sizeof(zero));
+        DenseStrides(out.GetShape(), op.p.dst_strides);
+        for (unsigned int i = 0; i < rank; ++i) { op.p.shape[i] = static_cast<int32_t>(out.GetShape()[i]); }
+        st->ops.push_back(op);
+    }
+    auto span = [](int64_t loNum, int64_t hiNum, int64_t blk, int64_t limit, int64_t& first, int64_t& count)
+    {
+        // indices n in [0, limit) with loNum <= n * blk <= hiNum
+        first = loNum <= 0 ? 0 : (loNum + blk - 1) / blk;
+        const int64_t last = hiNum < 0 ? -1 : std::min(limit - 1, hiNum / blk);
+        count = std::max<int64_t>(0, last - first + 1);
+    };
+    for (int64_t i = 0; i < bh; ++i)
+    {
+        int64_t h0, nh;
+        span(top - i, hs - 1 + top - i, bh, hb, h0, nh);
+        for (int64_t j = 0; j < bw; ++j)
+        {
+            int64_t w0, nw;
+            span(left - j, wsz - 1 + left - j, bw, wb, w0, nw);
+            if (nh == 0 || nw == 0) { continue; }
+            // the walk in the destination's memory order: (batch, h, w, c) for NHWC, (batch, c, h, w) for NCHW
+            const int64_t ext[4] = {nb, nh, nw, c};
+            const int64_t bStr[4] = {bs[0], bsH, bsW, bsC}, sStr[4] = {ss[0], ssH * bh, ssW * bw, ssC};
+            const int64_t bOff = (i * bw + j) * nb * bs[0] + h0 * bsH + w0 * bsW;
+            const int64_t sOff = (h0 * bh + i - top) * ssH + (w0 * bw + j - left) * ssW;
+            const int orderNhwc[4] = {0, 1, 2, 3}, orderNchw[4] = {0, 3, 1, 2};
+            const int* order = nchw ? orderNchw : orderNhwc;
+            ViewOp op = NewViewOp(in, out, st->blobs, 0, 0, 4);
+            for (int k = 0; k < 4; ++k)
+            {
+                op.p.shape[k] = static_cast<int32_t>(ext[order[k]]);
+                op.p.src_strides[k] = toSpace ? bStr[order[k]] : sStr[order[k]];
+                op.p.dst_strides[k] = toSpace ? sStr[order[k]] : bStr[order[k]];
+            }
+            op.p.src_offset = toSpace ? bOff : sOff;
+            op.p.dst_offset = toSpace ? sOff : bOff;
+            st->ops.push_back(op);
+        }
+    }
+    return MakeViews<QD>(d, info, ctx, st);
 }
 
 // ChannelShuffle (RefChannelShuffleWorkload.cpp:28-76): output channel i g + j is input channel i + j s.
@@ -653,7 +750,30 @@ std::unique_ptr<IWorkload> MakeReduce(const QueueDescriptor& d, const WorkloadIn
 }
 
 
-std::unique_ptr<IWorkload> MakeEltwise(const QueueDescriptor& d, const WorkloadInfo& info, const ContextPtr& ctx, BinaryOperation op,
+/// The workload class is a template over the queue descriptor; the legacy layer types (Addition, Subtraction, ...) and
+/// Prelu each have their own descriptor type around the same two inputs and one output.
+template <typename... Ds>
+struct EltwiseWrap;
+template <>
+struct EltwiseWrap<>
+{
+    template <typename Fn>
+    static std::unique_ptr<IWorkload> Make(const QueueDescriptor&, const WorkloadInfo&, const ContextPtr&, Fn&&) { return nullptr; }
+};
+template <typename D, typename... Ds>
+struct EltwiseWrap<D, Ds...>
+{
+    template <typename Fn>
+    static std::unique_ptr<IWorkload> Make(const QueueDescriptor& d, const WorkloadInfo& info, const ContextPtr& ctx, Fn&& fn)
+    {
+        if (auto* e = dynamic_cast<const D*>(&d)) { return std::make_unique<B200Workload<D>>(*e, info, ctx, fn); }
+        return EltwiseWrap<Ds...>::Make(d, info, ctx, fn);
+    }
+};
+
+/// op: armnn::BinaryOperation, or B200K_ELTWISE_PRELU with the alpha tensor as second operand.  A second operand of lower
+/// rank (Prelu's alpha, src/armnn/layers/PreluLayer.cpp:38-103) is aligned to the innermost dimensions.
+std::unique_ptr<IWorkload> MakeEltwise(const QueueDescriptor& d, const WorkloadInfo& info, const ContextPtr& ctx, int32_t op,
                                        const ActivationDescriptor* act)
 {
     auto st = std::make_shared<SimpleState<b200k_eltwise_params>>(ctx);
@@ -664,15 +784,19 @@ std::unique_ptr<IWorkload> MakeEltwise(const QueueDescriptor& d, const WorkloadI
     const TensorInfo& o = info.m_OutputTensorInfos[0];
     p.a = Operand(a, st->blobs); p.b = Operand(b, st->blobs); p.out = Operand(o, st->blobs);
     p.rank = static_cast<int32_t>(o.GetNumDimensions());
-    if (p.rank > 4 || a.GetNumDimensions() != o.GetNumDimensions() || b.GetNumDimensions() != o.GetNumDimensions())
+    const int ra = static_cast<int>(a.GetNumDimensions()), rb = static_cast<int>(b.GetNumDimensions());
+    if (p.rank > 4 || ra > p.rank || rb > p.rank || ((ra != p.rank || rb != p.rank) && op != B200K_ELTWISE_PRELU))
     {
         throw InvalidArgumentException("B200Acc: elementwise operands must share a rank <= 4");
     }
     for (int i = 0; i < p.rank; ++i)
     {
-        p.shape_a[i] = a.GetShape()[i]; p.shape_b[i] = b.GetShape()[i]; p.shape_out[i] = o.GetShape()[i];
+        const int ia = i - (p.rank - ra), ib = i - (p.rank - rb);
+        p.shape_a[i] = ia < 0 ? 1 : static_cast<int32_t>(a.GetShape()[static_cast<unsigned>(ia)]);
+        p.shape_b[i] = ib < 0 ? 1 : static_cast<int32_t>(b.GetShape()[static_cast<unsigned>(ib)]);
+        p.shape_out[i] = static_cast<int32_t>(o.GetShape()[static_cast<unsigned>(i)]);
     }
-    p.op = static_cast<int32_t>(op);
+    p.op = op;
     if (o.GetDataType() != DataType::Float32) { Clamp(act, o, p.clamp_lo, p.clamp_hi); }
     auto fn = [st](const QueueDescriptor& data, cudaStream_t s)
     {
@@ -680,19 +804,11 @@ std::unique_ptr<IWorkload> MakeEltwise(const QueueDescriptor& d, const WorkloadI
         q.a.data = Dev(data.m_Inputs[0]); q.b.data = Dev(data.m_Inputs[1]); q.out.data = Dev(data.m_Outputs[0]);
         B200CheckStatus(b200k_eltwise_q8(&q, s));
     };
-    if (auto* e = dynamic_cast<const ElementwiseBinaryQueueDescriptor*>(&d))
-    {
-        return std::make_unique<B200Workload<ElementwiseBinaryQueueDescriptor>>(*e, info, ctx, fn);
-    }
-    if (auto* e = dynamic_cast<const AdditionQueueDescriptor*>(&d))
-    {
-        return std::make_unique<B200Workload<AdditionQueueDescriptor>>(*e, info, ctx, fn);
-    }
-    if (auto* e = dynamic_cast<const MultiplicationQueueDescriptor*>(&d))
-    {
-        return std::make_unique<B200Workload<MultiplicationQueueDescriptor>>(*e, info, ctx, fn);
-    }
-    return nullptr;
+    ARMNN_NO_DEPRECATE_WARN_BEGIN
+    return EltwiseWrap<ElementwiseBinaryQueueDescriptor, AdditionQueueDescriptor, MultiplicationQueueDescriptor,
+                       SubtractionQueueDescriptor, DivisionQueueDescriptor, MaximumQueueDescriptor, MinimumQueueDescriptor,
+                       PreluQueueDescriptor>::Make(d, info, ctx, fn);
+    ARMNN_NO_DEPRECATE_WARN_END
 }
 
 // Device copies of the QLstm weights: the descriptor's ConstTensorHandles are released by the layer right after
@@ -855,12 +971,22 @@ std::unique_ptr<IWorkload> B200WorkloadFactory::CreateWorkload(LayerType type, c
         case LayerType::ElementwiseBinary:
         {
             const auto& qd = *PolymorphicDowncast<const ElementwiseBinaryQueueDescriptor*>(&d);
-            return MakeEltwise(d, info, ctx, qd.m_Parameters.m_Operation, qd.GetAdditionalInformation<ActivationDescriptor>());
+            return MakeEltwise(d, info, ctx, static_cast<int32_t>(qd.m_Parameters.m_Operation), qd.GetAdditionalInformation<ActivationDescriptor>());
         }
         case LayerType::Addition:
-            return MakeEltwise(d, info, ctx, BinaryOperation::Add, d.GetAdditionalInformation<ActivationDescriptor>());
+            return MakeEltwise(d, info, ctx, static_cast<int32_t>(BinaryOperation::Add), d.GetAdditionalInformation<ActivationDescriptor>());
         case LayerType::Multiplication:
-            return MakeEltwise(d, info, ctx, BinaryOperation::Mul, d.GetAdditionalInformation<ActivationDescriptor>());
+            return MakeEltwise(d, info, ctx, static_cast<int32_t>(BinaryOperation::Mul), d.GetAdditionalInformation<ActivationDescriptor>());
+        case LayerType::Subtraction:
+            return MakeEltwise(d, info, ctx, static_cast<int32_t>(BinaryOperation::Sub), d.GetAdditionalInformation<ActivationDescriptor>());
+        case LayerType::Division:
+            return MakeEltwise(d, info, ctx, static_cast<int32_t>(BinaryOperation::Div), d.GetAdditionalInformation<ActivationDescriptor>());
+        case LayerType::Maximum:
+            return MakeEltwise(d, info, ctx, static_cast<int32_t>(BinaryOperation::Maximum), d.GetAdditionalInformation<ActivationDescriptor>());
+        case LayerType::Minimum:
+            return MakeEltwise(d, info, ctx, static_cast<int32_t>(BinaryOperation::Minimum), d.GetAdditionalInformation<ActivationDescriptor>());
+        case LayerType::Prelu:
+            return MakeEltwise(d, info, ctx, B200K_ELTWISE_PRELU, nullptr);
         case LayerType::Activation:
         {
             const auto& qd = *PolymorphicDowncast<const ActivationQueueDescriptor*>(&d);
@@ -1095,6 +1221,16 @@ std::unique_ptr<IWorkload> B200WorkloadFactory::CreateWorkload(LayerType type, c
         case LayerType::Slice:        return MakeSlice(d, info, ctx);
         case LayerType::DepthToSpace: return MakeDepthSpace<DepthToSpaceQueueDescriptor>(d, info, ctx, true);
         case LayerType::SpaceToDepth: return MakeDepthSpace<SpaceToDepthQueueDescriptor>(d, info, ctx, false);
+        case LayerType::BatchToSpaceNd:
+        {
+            const auto& prm = PolymorphicDowncast<const BatchToSpaceNdQueueDescriptor*>(&d)->m_Parameters;
+            return MakeBatchSpace<BatchToSpaceNdQueueDescriptor>(d, info, ctx, prm.m_BlockShape, prm.m_Crops, prm.m_DataLayout, true);
+        }
+        case LayerType::SpaceToBatchNd:
+        {
+            const auto& prm = PolymorphicDowncast<const SpaceToBatchNdQueueDescriptor*>(&d)->m_Parameters;
+            return MakeBatchSpace<SpaceToBatchNdQueueDescriptor>(d, info, ctx, prm.m_BlockShape, prm.m_PadList, prm.m_DataLayout, false);
+        }
         case LayerType::ChannelShuffle: return MakeChannelShuffle(d, info, ctx);
         case LayerType::Stack:        return MakeStack(d, info, ctx);
         case LayerType::QLstm:

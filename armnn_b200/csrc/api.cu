@@ -109,6 +109,7 @@ extern "C" size_t b200k_sizeof_params(int which)
         case 12: return sizeof(b200k_resize_params);
         case 13: return sizeof(b200k_reduce_params);
         case 14: return sizeof(b200k_unary_params);
+        case 15: return sizeof(b200k_arg_min_max_params);
         default: return 0;
     }
 }

@@ -1,4 +1,4 @@
-// ElementwiseBinary (Add / Mul / Sub / Div / Maximum / Minimum / SqDiff) with numpy-style broadcast,
+// ElementwiseBinary (Add / Mul / Sub / Div / Maximum / Minimum / SqDiff / Power / FloorDiv) and Prelu with numpy-style broadcast,
 // standalone Activation, and Quantize / Dequantize / requantize.  All bandwidth-bound: same-shape 8-bit
 // operands take a 128-bit vector path (16 elements per thread), everything else a scalar path.
 // Arithmetic is CpuRef's: dequantise each operand with its own scale/offset, apply the fp32 operation
@@ -17,6 +17,9 @@ __device__ __forceinline__ float binary_op(int op, float a, float b)
         case 3:  return a < b ? a : b;
         case 4:  return __fmul_rn(a, b);
         case 5:  return __fsub_rn(a, b);
+        case 7:  return powf(a, b);
+        case 8:  return (float)floor((double)a / (double)b);
+        case 100: return a < 0.f ? __fmul_rn(b, a) : a;      // Prelu: b is alpha
         default: { float d = __fsub_rn(a, b); return __fmul_rn(d, d); }
     }
 }
@@ -117,7 +120,7 @@ extern "C" int b200k_eltwise_q8(const b200k_eltwise_params* p, void* stream)
     B200K_REQUIRE(p, B200K_E_INVALID, "eltwise_q8: null params");
     B200K_REQUIRE(p->a.data && p->b.data && p->out.data, B200K_E_INVALID, "eltwise_q8: null tensor pointer");
     B200K_REQUIRE(p->rank >= 1 && p->rank <= 4, B200K_E_UNSUPPORTED, "eltwise_q8: rank %d not in [1,4]", p->rank);
-    B200K_REQUIRE(p->op >= 0 && p->op <= 6, B200K_E_UNSUPPORTED, "eltwise_q8: unsupported binary operation %d", p->op);
+    B200K_REQUIRE((p->op >= 0 && p->op <= 8) || p->op == B200K_ELTWISE_PRELU, B200K_E_UNSUPPORTED, "eltwise_q8: unsupported binary operation %d", p->op);
     B200K_REQUIRE(p->a.dtype != B200K_S32 && p->b.dtype != B200K_S32 && p->out.dtype != B200K_S32, B200K_E_UNSUPPORTED,
                   "eltwise_q8: Signed32 not supported");
     EltArgs e;

@@ -408,6 +408,28 @@ int armnnc_add_depth_to_space(void* vn, int block, int nchw, int inverse)
     return add_layer(n, inverse ? n->net->AddSpaceToDepthLayer(d) : n->net->AddDepthToSpaceLayer(d));
 }
 
+/// edges: (before, after) per spatial dimension, flattened.  inverse = 0: BatchToSpaceNd with crops; 1: SpaceToBatchNd with padding.
+int armnnc_add_batch_to_space(void* vn, const int32_t* block, const int32_t* edges, int n_spatial, int nchw, int inverse)
+{
+    auto* n = static_cast<CNet*>(vn);
+    std::vector<unsigned int> blockShape;
+    std::vector<std::pair<unsigned int, unsigned int>> pairs;
+    for (int i = 0; i < n_spatial; ++i)
+    {
+        blockShape.push_back(static_cast<unsigned int>(block[i]));
+        pairs.emplace_back(static_cast<unsigned int>(edges[2 * i]), static_cast<unsigned int>(edges[2 * i + 1]));
+    }
+    if (inverse)
+    {
+        SpaceToBatchNdDescriptor d(blockShape, pairs);
+        d.m_DataLayout = nchw ? DataLayout::NCHW : DataLayout::NHWC;
+        return add_layer(n, n->net->AddSpaceToBatchNdLayer(d));
+    }
+    BatchToSpaceNdDescriptor d(blockShape, pairs);
+    d.m_DataLayout = nchw ? DataLayout::NCHW : DataLayout::NHWC;
+    return add_layer(n, n->net->AddBatchToSpaceNdLayer(d));
+}
+
 int armnnc_add_channel_shuffle(void* vn, int axis, int groups)
 {
     auto* n = static_cast<CNet*>(vn);
@@ -429,6 +451,12 @@ int armnnc_add_elementwise_unary(void* vn, int operation)
 {
     auto* n = static_cast<CNet*>(vn);
     return add_layer(n, n->net->AddElementwiseUnaryLayer(ElementwiseUnaryDescriptor(static_cast<UnaryOperation>(operation))));
+}
+
+int armnnc_add_prelu(void* vn)
+{
+    auto* n = static_cast<CNet*>(vn);
+    return add_layer(n, n->net->AddPreluLayer());
 }
 
 int armnnc_add_reduce(void* vn, const int32_t* axes, int n_axes, int operation, int keep_dims)

@@ -54,6 +54,8 @@ class BinaryOperation(IntEnum):     # include/armnn/Types.hpp:138-149
     Mul = 4
     Sub = 5
     SqDiff = 6
+    Power = 7
+    FloorDiv = 8
 
 
 class PoolingAlgorithm(IntEnum):
@@ -71,6 +73,8 @@ _ABI_DTYPE = {DataType.Float32: _abi.F32, DataType.QAsymmU8: _abi.U8, DataType.S
               DataType.QSymmS16: _abi.S16, DataType.QSymmS8: _abi.S8, DataType.QAsymmS8: _abi.S8}
 _NP_DTYPE = {DataType.Float32: np.float32, DataType.QAsymmU8: np.uint8, DataType.Signed32: np.int32,
              DataType.QSymmS16: np.int16, DataType.QSymmS8: np.int8, DataType.QAsymmS8: np.int8}
+_TYPE_RANGE = {DataType.QAsymmU8: (0, 255), DataType.QAsymmS8: (-128, 127), DataType.QSymmS8: (-128, 127),
+               DataType.QSymmS16: (-32768, 32767), DataType.Signed32: (-(1 << 31), (1 << 31) - 1)}
 
 
 class InvalidArgumentException(ValueError):
@@ -213,6 +217,23 @@ class INetwork:
     def AddMultiplicationLayer(self, name=None):
         return self.AddElementwiseBinaryLayer(BinaryOperation.Mul, name)
 
+    def AddSubtractionLayer(self, name=None):
+        return self.AddElementwiseBinaryLayer(BinaryOperation.Sub, name)
+
+    def AddDivisionLayer(self, name=None):
+        return self.AddElementwiseBinaryLayer(BinaryOperation.Div, name)
+
+    def AddMaximumLayer(self, name=None):
+        return self.AddElementwiseBinaryLayer(BinaryOperation.Maximum, name)
+
+    def AddMinimumLayer(self, name=None):
+        return self.AddElementwiseBinaryLayer(BinaryOperation.Minimum, name)
+
+    def AddPreluLayer(self, name=None):
+        """armnn::INetwork::AddPreluLayer: input 0 is the tensor, input 1 alpha (broadcast, aligned to the innermost
+        dimensions when its rank is lower)."""
+        return self._add(Layer("Prelu", name, 2, 1, {}))
+
     def AddSoftmaxLayer(self, beta=1.0, axis=-1, name=None):
         return self._add(Layer("Softmax", name, 1, 1, {"beta": float(beta), "axis": int(axis)}))
 
@@ -261,6 +282,16 @@ class INetwork:
 
     def AddSpaceToDepthLayer(self, block_size, nchw=False, name=None):
         return self._add(Layer("SpaceToDepth", name, 1, 1, {"block": int(block_size), "nchw": bool(nchw)}))
+
+    def AddBatchToSpaceNdLayer(self, block_shape, crops, nchw=False, name=None):
+        """armnn::BatchToSpaceNdDescriptor: one block extent and one (before, after) crop pair per spatial dimension."""
+        return self._add(Layer("BatchToSpaceNd", name, 1, 1, {"block": tuple(int(b) for b in block_shape),
+                                                              "edges": tuple((int(a), int(b)) for a, b in crops), "nchw": bool(nchw)}))
+
+    def AddSpaceToBatchNdLayer(self, block_shape, pad_list, nchw=False, name=None):
+        """armnn::SpaceToBatchNdDescriptor: one block extent and one (before, after) padding pair per spatial dimension."""
+        return self._add(Layer("SpaceToBatchNd", name, 1, 1, {"block": tuple(int(b) for b in block_shape),
+                                                              "edges": tuple((int(a), int(b)) for a, b in pad_list), "nchw": bool(nchw)}))
 
     def AddChannelShuffleLayer(self, axis, num_groups, name=None):
         return self._add(Layer("ChannelShuffle", name, 1, 1, {"axis": int(axis), "groups": int(num_groups)}))
@@ -351,12 +382,12 @@ def IsLayerSupported(layer):
         if any(i.dtype not in _Q8 for i in ins) or outs[0].dtype not in _Q8:
             return False, "BatchMatMul: 8-bit quantised tensors only"
         return True, ""
-    if t in ("Pooling2d", "Mean", "Reduce", "ElementwiseBinary", "Activation", "Softmax"):
+    if t in ("Pooling2d", "Mean", "Reduce", "ElementwiseBinary", "Prelu", "Activation", "Softmax"):
         ok = (DataType.QAsymmU8, DataType.QAsymmS8, DataType.QSymmS16, DataType.Float32)
         if any(i.dtype not in ok for i in ins) or outs[0].dtype not in ok:
             return False, "%s: unsupported data type" % t
-        if t == "ElementwiseBinary" and len(outs[0].shape) > 4:
-            return False, "ElementwiseBinary: rank > 4"
+        if t in ("ElementwiseBinary", "Prelu") and len(outs[0].shape) > 4:
+            return False, "%s: rank > 4" % t
         return True, ""
     if t in ("Quantize", "Dequantize"):
         return True, ""
@@ -389,10 +420,12 @@ def IsLayerSupported(layer):
         if len(ins[0].shape) > 6 or any(i.dtype != ins[0].dtype for i in list(ins) + list(outs)):
             return False, "%s: rank > 6 or mismatched data types" % t
         return True, ""
-    if t in ("SpaceToDepth", "ChannelShuffle", "Stack"):
+    if t in ("SpaceToDepth", "ChannelShuffle", "Stack", "BatchToSpaceNd", "SpaceToBatchNd"):
         # through Decoder / Encoder in the reference: one element type, quantisation may differ
         if len(outs[0].shape) > 6 or any(i.dtype != outs[0].dtype for i in ins):
             return False, "%s: rank > 6 or mismatched data types" % t
+        if t in ("BatchToSpaceNd", "SpaceToBatchNd") and len(ins[0].shape) not in (3, 4):
+            return False, "%s: 3 or 4 dimensions only" % t
         return True, ""
     if t in ("Permute", "Transpose", "StridedSlice", "Slice", "DepthToSpace"):
         if len(ins[0].shape) > (4 if t == "StridedSlice" else 6):
@@ -766,14 +799,21 @@ class GraphProgram:
         p = _abi.EltwiseParams()
         p.a, p.b, p.out = self._operand(a), self._operand(b), self._operand(o)
         rank = len(o.info.shape)
-        if len(a.info.shape) != rank or len(b.info.shape) != rank:
+        prelu = layer.type == "Prelu"
+        if (len(a.info.shape) != rank or len(b.info.shape) != rank) and not prelu:
             raise InvalidArgumentException("ElementwiseBinary: inputs and output must have the same rank")
+        if len(a.info.shape) > rank or len(b.info.shape) > rank:
+            raise InvalidArgumentException("Prelu: an operand has more dimensions than the output")
+        sa = (1,) * (rank - len(a.info.shape)) + tuple(a.info.shape)
+        sb = (1,) * (rank - len(b.info.shape)) + tuple(b.info.shape)
         p.rank = rank
         for i in range(rank):
-            p.shape_a[i], p.shape_b[i], p.shape_out[i] = a.info.shape[i], b.info.shape[i], o.info.shape[i]
-        p.op = int(layer.desc["op"])
+            p.shape_a[i], p.shape_b[i], p.shape_out[i] = sa[i], sb[i], o.info.shape[i]
+        p.op = 100 if prelu else int(layer.desc["op"])
         p.clamp_lo, p.clamp_hi = _clamp(layer, o.info) if o.info.dtype != DataType.Float32 else (0, 0)
         return "eltwise_q8", p
+
+    _make_Prelu = _make_ElementwiseBinary
 
     def _make_Activation(self, layer):
         x, y = layer.inputs[0].source, layer.outputs[0]
@@ -880,6 +920,35 @@ class GraphProgram:
         if tuple(out_shape) != tuple(y.info.shape):
             raise InvalidArgumentException("DepthToSpace: output shape %s, expected %s" % (y.info.shape, out_shape))
         return self._view_copy(x, y, v)
+
+    def _make_BatchToSpaceNd(self, layer):
+        x, y, d = layer.inputs[0].source, layer.outputs[0], layer.desc
+        out_shape, vs = views.batch_to_space_views(x.info.shape, d["block"], d["edges"], d["nchw"])
+        if tuple(out_shape) != tuple(y.info.shape):
+            raise InvalidArgumentException("BatchToSpaceNd: output shape %s, expected %s" % (y.info.shape, out_shape))
+        return [self._view_copy(x, y, v) for v in vs]
+
+    def _make_SpaceToBatchNd(self, layer):
+        x, y, d = layer.inputs[0].source, layer.outputs[0], layer.desc
+        out_shape, vs, padded = views.space_to_batch_views(x.info.shape, d["block"], d["edges"], d["nchw"])
+        if tuple(out_shape) != tuple(y.info.shape):
+            raise InvalidArgumentException("SpaceToBatchNd: output shape %s, expected %s" % (y.info.shape, out_shape))
+        work = []
+        if padded:
+            # the padding holds the output's encoding of 0.0 (workloads/SpaceToBatchNd.cpp:98-101): one element of it,
+            # read with stride 0 over the whole output, before the blocks of the input are copied in
+            info = y.info
+            if info.dtype == DataType.Float32:
+                zero = np.zeros(1, np.float32)
+            else:
+                lo, hi = _TYPE_RANGE[info.dtype]
+                zero = np.array([min(max(info.offset, lo), hi)], _NP_DTYPE[info.dtype])
+            dev = self._upload(zero)
+            self.aux.append(dev)
+            name, p = self._view_copy(y, y, views.fill_view(out_shape))
+            p.x.data = self._ptr(dev)
+            work.append((name, p))
+        return work + [self._view_copy(x, y, v) for v in vs]
 
     def _make_SpaceToDepth(self, layer):
         x, y = layer.inputs[0].source, layer.outputs[0]

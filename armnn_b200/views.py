@@ -13,6 +13,8 @@ rules once in a form that is easy to test against CpuRef:
 * StridedSlice (`src/armnn/Descriptors.cpp:393-453`, `workloads/StridedSlice.cpp:188-222`) with begin / end / shrink-axis
   masks (ellipsis and new-axis masks are refused by layer support); Slice (`workloads/Slice.cpp:14-147`).
 * DepthToSpace, SpaceToDepth, ChannelShuffle and Stack: six- or four-dimensional walks over the same bytes.
+* BatchToSpaceNd (`workloads/BatchToSpaceNd.cpp:50-117`) and SpaceToBatchNd (`workloads/SpaceToBatchNd.cpp:49-131`): one
+  strided block per position inside the spatial block; one six-dimensional walk when nothing is cropped or padded.
 """
 
 INT_MIN, INT_MAX = -(1 << 31), (1 << 31) - 1
@@ -180,6 +182,115 @@ def stack_views(in_shape, num_inputs, axis):
     os_ = dense_strides(out_shape)
     ds = os_[:axis] + os_[axis + 1:]
     return out_shape, [(tuple(in_shape), 0, dense_strides(in_shape), i * os_[axis], ds) for i in range(num_inputs)]
+
+
+def _spatial(shape, nchw):
+    """(batch, height, width, channels) and the index of each in `shape` (rank 3: no width; rank 4)."""
+    rank = len(shape)
+    if rank == 4:
+        idx = (0, 2, 3, 1) if nchw else (0, 1, 2, 3)
+    elif rank == 3:
+        idx = (0, 2, None, 1) if nchw else (0, 1, None, 2)
+    else:
+        raise ValueError("rank %d: BatchToSpaceNd / SpaceToBatchNd take 3 or 4 dimensions" % rank)
+    dims = tuple(1 if i is None else int(shape[i]) for i in idx)
+    return dims, idx
+
+
+def _shape_from(idx, rank, b, h, w, c):
+    out = [0] * rank
+    for i, v in zip(idx, (b, h, w, c)):
+        if i is not None:
+            out[i] = v
+    return tuple(out)
+
+
+def _span(lo_num, hi_num, block, limit):
+    """Indices n in [0, limit) with lo_num <= n * block <= hi_num: (first, count)."""
+    first = max(0, -(-lo_num // block))
+    last = min(limit - 1, hi_num // block)
+    return first, max(0, last - first + 1)
+
+
+def batch_to_space_views(in_shape, block, crops, nchw=False):
+    """(out_shape, views) of BatchToSpaceNd: input batch (i * block_w + j) * out_batch + b holds, for output batch b,
+    the pixels (y * block_h + i - crop_top, x * block_w + j - crop_left).  block: one entry per spatial dimension;
+    crops: (before, after) per spatial dimension."""
+    (ib, ih, iw, c), idx = _spatial(in_shape, nchw)
+    rank = len(in_shape)
+    block, crops = [int(v) for v in block], [(int(a), int(b)) for a, b in crops]
+    if len(block) != rank - 2 or len(crops) != rank - 2 or any(v < 1 for v in block) or any(a < 0 or b < 0 for a, b in crops):
+        raise ValueError("BatchToSpaceNd: block shape / crops do not match a tensor of rank %d" % rank)
+    bh, (ct, cb) = block[0], crops[0]
+    bw, (cl, cr) = (block[1], crops[1]) if rank == 4 else (1, (0, 0))
+    if ib % (bh * bw):
+        raise ValueError("BatchToSpaceNd: batch %d is not a multiple of the block size %d" % (ib, bh * bw))
+    ob, oh, ow = ib // (bh * bw), ih * bh - ct - cb, iw * bw - cl - cr
+    if oh < 1 or ow < 1:
+        raise ValueError("BatchToSpaceNd: the crops leave nothing")
+    out_shape = _shape_from(idx, rank, ob, oh, ow, c)
+    ss4, ds4 = dense_strides(in_shape), dense_strides(out_shape)
+    pick = lambda st: [0 if i is None else st[i] for i in idx]          # strides as (batch, height, width, channel)
+    (sb, sh, sw, sc), (db, dh, dw, dc) = pick(ss4), pick(ds4)
+    order = (0, 3, 1, 2) if nchw else (0, 1, 2, 3)                      # walk in the destination's memory order
+    def arrange(vals):
+        return [vals[k] for k in order]
+    if not (ct or cb or cl or cr):
+        # [ob, ih, bh, iw, bw, c] (NHWC) / [ob, c, ih, bh, iw, bw] (NCHW) over the dense output
+        walk = {"b": (ob, sb, db), "h": (ih, sh, dh * bh), "i": (bh, bw * ob * sb, dh), "w": (iw, sw, dw * bw),
+                "j": (bw, ob * sb, dw), "c": (c, sc, dc)}
+        keys = "bchiwj" if nchw else "bhiwjc"
+        return out_shape, [(tuple(walk[k][0] for k in keys), 0, [walk[k][1] for k in keys], 0, [walk[k][2] for k in keys])]
+    out = []
+    for i in range(bh):
+        h0, nh = _span(ct - i, oh - 1 + ct - i, bh, ih)
+        for j in range(bw):
+            w0, nw = _span(cl - j, ow - 1 + cl - j, bw, iw)
+            if nh == 0 or nw == 0:
+                continue
+            out.append((tuple(arrange([ob, nh, nw, c])), (i * bw + j) * ob * sb + h0 * sh + w0 * sw, arrange([sb, sh, sw, sc]),
+                        (h0 * bh + i - ct) * dh + (w0 * bw + j - cl) * dw, arrange([db, dh * bh, dw * bw, dc])))
+    return out_shape, out
+
+
+def space_to_batch_views(in_shape, block, pads, nchw=False):
+    """(out_shape, views, padded) of SpaceToBatchNd: output batch (i * block_w + j) * in_batch + b holds, for input
+    batch b, the pixels (y * block_h + i - pad_top, x * block_w + j - pad_left); positions outside the input hold
+    Q(0), which the caller writes first when `padded` is set."""
+    (ib, ih, iw, c), idx = _spatial(in_shape, nchw)
+    rank = len(in_shape)
+    block, pads = [int(v) for v in block], [(int(a), int(b)) for a, b in pads]
+    if len(block) != rank - 2 or len(pads) != rank - 2 or any(v < 1 for v in block) or any(a < 0 or b < 0 for a, b in pads):
+        raise ValueError("SpaceToBatchNd: block shape / padding do not match a tensor of rank %d" % rank)
+    bh, (pt, pb) = block[0], pads[0]
+    bw, (pl, pr) = (block[1], pads[1]) if rank == 4 else (1, (0, 0))
+    if (ih + pt + pb) % bh or (iw + pl + pr) % bw:
+        raise ValueError("SpaceToBatchNd: the padded size %dx%d is not a multiple of the block %dx%d"
+                         % (ih + pt + pb, iw + pl + pr, bh, bw))
+    oh, ow = (ih + pt + pb) // bh, (iw + pl + pr) // bw
+    out_shape = _shape_from(idx, rank, ib * bh * bw, oh, ow, c)
+    ss4, ds4 = dense_strides(in_shape), dense_strides(out_shape)
+    pick = lambda st: [0 if i is None else st[i] for i in idx]
+    (sb, sh, sw, sc), (db, dh, dw, dc) = pick(ss4), pick(ds4)
+    order = (0, 3, 1, 2) if nchw else (0, 1, 2, 3)
+    def arrange(vals):
+        return [vals[k] for k in order]
+    out = []
+    for i in range(bh):
+        h0, nh = _span(pt - i, ih - 1 + pt - i, bh, oh)
+        for j in range(bw):
+            w0, nw = _span(pl - j, iw - 1 + pl - j, bw, ow)
+            if nh == 0 or nw == 0:
+                continue
+            out.append((tuple(arrange([ib, nh, nw, c])), (h0 * bh + i - pt) * sh + (w0 * bw + j - pl) * sw,
+                        arrange([sb, sh * bh, sw * bw, sc]),
+                        (i * bw + j) * ib * db + h0 * dh + w0 * dw, arrange([db, dh, dw, dc])))
+    return out_shape, out, bool(pt or pb or pl or pr)
+
+
+def fill_view(shape):
+    """The whole dense tensor read from one element (all source strides 0): a constant fill."""
+    return (tuple(int(n) for n in shape), 0, [0] * len(shape), 0, dense_strides(shape))
 
 
 def merge_dims(view, max_rank=6):

@@ -216,8 +216,11 @@ int b200k_mean_hw_q8(const b200k_mean_params* p, void* stream);
 /* ElementwiseBinaryFunction<std::plus / std::multiplies / ...> with BroadcastLoop
  * (RefElementwiseBinaryWorkload.cpp:27-132, ElementwiseFunction.cpp:25-34, Broadcast.hpp:13-104).
  * op follows armnn::BinaryOperation (include/armnn/Types.hpp:138-149): 0 Add, 1 Div, 2 Maximum,
- * 3 Minimum, 4 Mul, 5 Sub, 6 SqDiff.  Shapes have equal rank <= 4 (padded with leading 1s); a
- * dimension of size 1 broadcasts.  out = Q(deq(a) op deq(b)), then the clamp. */
+ * 3 Minimum, 4 Mul, 5 Sub, 6 SqDiff, 7 Power (Power.hpp:19-24), 8 FloorDiv (FloorDiv.hpp:15-19: the quotient in
+ * double precision, floored); B200K_ELTWISE_PRELU is armnn::Prelu (PreluImpl.cpp:14-33): a < 0 ? b * a : a with b the
+ * alpha tensor.  Shapes have equal rank <= 4 (padded with leading 1s); a dimension of size 1 broadcasts.
+ * out = Q(deq(a) op deq(b)), then the clamp. */
+#define B200K_ELTWISE_PRELU 100
 typedef struct {
     b200k_qtensor a, b, out;
     int32_t rank;
@@ -268,7 +271,8 @@ typedef struct {
 
 int b200k_pad_q(const b200k_pad_params* p, void* stream);
 
-/* ---- Concat, Splitter, Permute, Transpose, StridedSlice, Slice, DepthToSpace, SpaceToDepth, ChannelShuffle, Stack ---- */
+/* ---- Concat, Splitter, Permute, Transpose, StridedSlice, Slice, DepthToSpace, SpaceToDepth, ChannelShuffle, Stack,
+ *      BatchToSpaceNd, SpaceToBatchNd ---- */
 
 /* One rectangular view of a tensor copied onto a view of another one:
  *     y[dst_offset + sum_d i_d dst_strides[d]] = Q_y(deq_x(x[src_offset + sum_d i_d src_strides[d]]))   for 0 <= i_d < shape[d]
@@ -284,7 +288,10 @@ int b200k_pad_q(const b200k_pad_params* p, void* stream);
  *     offset from the begin indices, source strides multiplied by the slice's strides;
  *   armnn::DepthToSpace (workloads/DepthToSpace.cpp:15-100), SpaceToDepth (workloads/SpaceToDepth.cpp:42-104),
  *     ChannelShuffle (RefChannelShuffleWorkload.cpp:28-76): six- or four-dimensional walks over the same elements;
- *   armnn::Stack (workloads/Stack.cpp:14-120): one call per input, placed at its index of the new dimension.
+ *   armnn::Stack (workloads/Stack.cpp:14-120): one call per input, placed at its index of the new dimension;
+ *   armnn::BatchToSpaceNd (workloads/BatchToSpaceNd.cpp:50-117) and SpaceToBatchNd (workloads/SpaceToBatchNd.cpp:49-131):
+ *     one strided block per position inside the spatial block (a single six-dimensional walk without crops); the
+ *     padding of SpaceToBatchNd is a fill from one element holding Q_y(0.0), read with source strides 0.
  * The host side (the plugin's workloads, armnn_b200/views.py) turns the layer descriptors into these views. */
 typedef struct {
     b200k_qtensor x, y;
@@ -363,6 +370,28 @@ typedef struct {
 
 int b200k_softmax_q8(const b200k_softmax_params* p, void* stream);
 
+/* armnn::LogSoftmax (src/backends/reference/workloads/LogSoftmax.cpp:30-88): (x - max) * beta - log(sum exp((x - max) * beta))
+ * over the same rows. */
+int b200k_log_softmax_q(const b200k_softmax_params* p, void* stream);
+
+/* armnn::L2Normalization (src/backends/reference/workloads/RefL2NormalizationWorkload.cpp:29-93): every element divided by
+ * sqrt(max(sum of squares over the channel axis, eps)); the channel axis is the row axis here (NHWC: inner = 1, NCHW:
+ * inner = H * W) and `beta` carries eps. */
+int b200k_l2_normalization_q(const b200k_softmax_params* p, void* stream);
+
+/* armnn::ArgMinMax (src/backends/reference/workloads/ArgMinMax.cpp:16-48): the index of the smallest (function 0) or
+ * largest (function 1) decoded element of each row, the first one among equals; y is a device array of outer * inner
+ * int32 (out_int64 = 0) or int64 (out_int64 = 1) indices. */
+typedef struct {
+    b200k_qtensor x;
+    void* y;
+    int32_t outer, axis_size, inner;
+    int32_t function;
+    int32_t out_int64;
+} b200k_arg_min_max_params;
+
+int b200k_arg_min_max_q(const b200k_arg_min_max_params* p, void* stream);
+
 /* ---- Quantize / Dequantize ----------------------------------------------------------------- */
 
 /* QuantizeImpl (RefQuantizeWorkload.cpp:14-45) and armnn::Dequantize
@@ -428,7 +457,7 @@ unsigned long long b200k_kernel_launches(void);
 
 /* sizeof() of a parameter struct as compiled into the library, for bindings in other languages to check their
  * own declarations: 0 conv2d, 1 fc, 2 bmm, 3 pool2d, 4 mean, 5 eltwise, 6 activation, 7 softmax, 8 convert,
- * 9 qlstm, 10 pad.  No counterpart in the reference (its backends are linked as C++). */
+ * 9 qlstm, 10 pad, 11 view_copy, 12 resize, 13 reduce, 14 unary, 15 arg_min_max.  No counterpart in the reference (its backends are linked as C++). */
 size_t b200k_sizeof_params(int which);
 
 #ifdef __cplusplus

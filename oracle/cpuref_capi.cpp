@@ -301,13 +301,25 @@ extern "C" int cpuref_eltwise_q8(const b200k_eltwise_params* p, int act_kind, fl
         TensorInfo ai = make_info(p->a, shape(p->shape_a), 0, 0, false);
         TensorInfo bi = make_info(p->b, shape(p->shape_b), 0, 0, false);
         TensorInfo oi = make_info(p->out, shape(p->shape_out), 0, 0, false);
-        ElementwiseBinaryQueueDescriptor d;
-        d.m_Parameters.m_Operation = static_cast<BinaryOperation>(p->op);
-        h.in(d, ai, p->a.data);
-        h.in(d, bi, p->b.data);
-        auto* o = h.out(d, oi);
-        h.run(LayerType::ElementwiseBinary, d);
-        copy_out(o, const_cast<void*>(p->out.data), oi.GetNumBytes());
+        if (p->op == B200K_ELTWISE_PRELU)
+        {
+            PreluQueueDescriptor d;
+            h.in(d, ai, p->a.data);
+            h.in(d, bi, p->b.data);
+            auto* o = h.out(d, oi);
+            h.run(LayerType::Prelu, d);
+            copy_out(o, const_cast<void*>(p->out.data), oi.GetNumBytes());
+        }
+        else
+        {
+            ElementwiseBinaryQueueDescriptor d;
+            d.m_Parameters.m_Operation = static_cast<BinaryOperation>(p->op);
+            h.in(d, ai, p->a.data);
+            h.in(d, bi, p->b.data);
+            auto* o = h.out(d, oi);
+            h.run(LayerType::ElementwiseBinary, d);
+            copy_out(o, const_cast<void*>(p->out.data), oi.GetNumBytes());
+        }
         run_activation(act_kind, act_a, act_b, oi, const_cast<void*>(p->out.data));
     });
 }
@@ -572,6 +584,38 @@ extern "C" int cpuref_move_q(const oracle_move_params* p)
                 h.in(d, whole, p->whole.data);
                 outs.push_back(h.out(d, views[0]));
                 h.run(LayerType::ChannelShuffle, d);
+                copy_out(outs[0], const_cast<void*>(p->view[0].data), views[0].GetNumBytes());
+                break;
+            }
+            case MOVE_BATCH_TO_SPACE: {
+                BatchToSpaceNdQueueDescriptor d;
+                const unsigned sp = (unsigned)p->rank - 2;
+                d.m_Parameters.m_DataLayout = p->perm[0] ? DataLayout::NCHW : DataLayout::NHWC;
+                d.m_Parameters.m_BlockShape.clear(); d.m_Parameters.m_Crops.clear();
+                for (unsigned i = 0; i < sp; ++i)
+                {
+                    d.m_Parameters.m_BlockShape.push_back((unsigned)p->begin[i]);
+                    d.m_Parameters.m_Crops.emplace_back((unsigned)p->end[i], (unsigned)p->stride[i]);
+                }
+                h.in(d, whole, p->whole.data);
+                outs.push_back(h.out(d, views[0]));
+                h.run(LayerType::BatchToSpaceNd, d);
+                copy_out(outs[0], const_cast<void*>(p->view[0].data), views[0].GetNumBytes());
+                break;
+            }
+            case MOVE_SPACE_TO_BATCH: {
+                SpaceToBatchNdQueueDescriptor d;
+                const unsigned sp = (unsigned)p->rank - 2;
+                d.m_Parameters.m_DataLayout = p->perm[0] ? DataLayout::NCHW : DataLayout::NHWC;
+                d.m_Parameters.m_BlockShape.clear(); d.m_Parameters.m_PadList.clear();
+                for (unsigned i = 0; i < sp; ++i)
+                {
+                    d.m_Parameters.m_BlockShape.push_back((unsigned)p->begin[i]);
+                    d.m_Parameters.m_PadList.emplace_back((unsigned)p->end[i], (unsigned)p->stride[i]);
+                }
+                h.in(d, whole, p->whole.data);
+                outs.push_back(h.out(d, views[0]));
+                h.run(LayerType::SpaceToBatchNd, d);
                 copy_out(outs[0], const_cast<void*>(p->view[0].data), views[0].GetNumBytes());
                 break;
             }

@@ -8,7 +8,9 @@
 enum { MOVE_CONCAT = 0, MOVE_SPLIT = 1, MOVE_PERMUTE = 2, MOVE_TRANSPOSE = 3, MOVE_STRIDED_SLICE = 4, MOVE_SLICE = 5,
        MOVE_DEPTH_TO_SPACE = 6, MOVE_SPACE_TO_DEPTH = 7,      /* perm[0] = block size, perm[1] = 1 for NCHW */
        MOVE_CHANNEL_SHUFFLE = 8,                              /* perm[0] = axis, perm[1] = groups */
-       MOVE_STACK = 9 };                                      /* perm[0] = axis; whole = the output, views = the inputs */
+       MOVE_STACK = 9,                                        /* perm[0] = axis; whole = the output, views = the inputs */
+       MOVE_BATCH_TO_SPACE = 10, MOVE_SPACE_TO_BATCH = 11 };  /* perm[0] = 1 for NCHW; begin = block shape, end / stride =
+                                                                 crops or padding before / after, per spatial dimension */
 
 typedef struct {
     int32_t kind, rank;

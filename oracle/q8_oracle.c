@@ -465,6 +465,9 @@ int oracle_eltwise_q8(const b200k_eltwise_params* p)
             case 4: r = a * b; break;
             case 5: r = a - b; break;
             case 6: { volatile float d = a - b; r = d * d; break; }
+            case 7: r = powf(a, b); break;                                    /* Power.hpp:19-24 */
+            case 8: r = (float)floor((double)a / (double)b); break;           /* FloorDiv.hpp:15-19 */
+            case B200K_ELTWISE_PRELU: r = a < 0 ? b * a : a; break;           /* PreluImpl.cpp:25-28 */
             default: return B200K_E_INVALID;
         }
         if (p->out.dtype == B200K_F32) { ((float*)p->out.data)[io] = r; continue; }
@@ -900,6 +903,76 @@ static int move_space_to_depth(const oracle_move_params* p)
     return 0;
 }
 
+/* Offset of (batch, height, width, channel) in a tensor of rank 3 (no width) or 4, BatchToSpaceNd.cpp:14-46. */
+static int64_t nd_offset(const int32_t* shape, int rank, int nchw, int b, int h, int w, int c)
+{
+    if (rank == 3) return nchw ? ((int64_t)b * shape[1] + c) * shape[2] + h : ((int64_t)b * shape[1] + h) * shape[2] + c;
+    return nchw ? (((int64_t)b * shape[1] + c) * shape[2] + h) * shape[3] + w
+                : (((int64_t)b * shape[1] + h) * shape[2] + w) * shape[3] + c;
+}
+
+static void nd_dims(const int32_t* shape, int rank, int nchw, int* h, int* w, int* c)
+{
+    if (rank == 3) { *h = nchw ? shape[2] : shape[1]; *w = 1; *c = nchw ? shape[1] : shape[2]; }
+    else { *h = nchw ? shape[2] : shape[1]; *w = nchw ? shape[3] : shape[2]; *c = nchw ? shape[1] : shape[3]; }
+}
+
+/* BatchToSpaceNd.cpp:50-117: input batch ib = so * OB + ob carries the spatial offset so = i * BW + j; its pixel
+ * (ih, iw) lands at (ih * BH + i - crop_top, iw * BW + j - crop_left) when that is inside the output. */
+static int move_batch_to_space(const oracle_move_params* p)
+{
+    const int nchw = p->perm[0], rank = p->rank;
+    if (rank != 3 && rank != 4) return B200K_E_INVALID;
+    int IH, IW, C, OH, OW, OC;
+    nd_dims(p->whole_shape, rank, nchw, &IH, &IW, &C);
+    nd_dims(p->view_shape[0], rank, nchw, &OH, &OW, &OC);
+    const int IB = p->whole_shape[0], OB = p->view_shape[0][0];
+    const int BH = p->begin[0], BW = rank == 3 ? 1 : p->begin[1];
+    const int ct = p->end[0], cl = rank == 3 ? 0 : p->end[1];
+    if (BH < 1 || BW < 1 || OB < 1 || OC != C) return B200K_E_INVALID;
+    for (int ib = 0; ib < IB; ++ib) {
+        const int ob = ib % OB, so = ib / OB;
+        for (int ih = 0; ih < IH; ++ih) {
+            const int oh = ih * BH + so / BW - ct;
+            if (oh < 0 || oh >= OH) continue;
+            for (int iw = 0; iw < IW; ++iw) {
+                const int ow = iw * BW + so % BW - cl;
+                if (ow < 0 || ow >= OW) continue;
+                for (int c = 0; c < C; ++c)
+                    store_f(&p->view[0], nd_offset(p->view_shape[0], rank, nchw, ob, oh, ow, c),
+                            load_f(&p->whole, nd_offset(p->whole_shape, rank, nchw, ib, ih, iw, c)));
+            }
+        }
+    }
+    return 0;
+}
+
+/* SpaceToBatchNd.cpp:49-131: output batch ob = (i * BW + j) * IB + ib reads pixel (oh * BH + i - pad_top,
+ * ow * BW + j - pad_left) of input batch ib; outside the input the encoder stores 0.0. */
+static int move_space_to_batch(const oracle_move_params* p)
+{
+    const int nchw = p->perm[0], rank = p->rank;
+    if (rank != 3 && rank != 4) return B200K_E_INVALID;
+    int IH, IW, C, OH, OW, OC;
+    nd_dims(p->whole_shape, rank, nchw, &IH, &IW, &C);
+    nd_dims(p->view_shape[0], rank, nchw, &OH, &OW, &OC);
+    const int IB = p->whole_shape[0], OB = p->view_shape[0][0];
+    const int BH = p->begin[0], BW = rank == 3 ? 1 : p->begin[1];
+    const int pt = p->end[0], pl = rank == 3 ? 0 : p->end[1];
+    if (BH < 1 || BW < 1 || IB < 1 || OC != C) return B200K_E_INVALID;
+    for (int ob = 0; ob < OB; ++ob) {
+        const int ib = ob % IB, sw = (ob / IB) % BW, sh = (ob / IB) / BW;
+        for (int oh = 0; oh < OH; ++oh) for (int ow = 0; ow < OW; ++ow) {
+            const int ih = oh * BH + sh - pt, iw = ow * BW + sw - pl;
+            const int inside = ih >= 0 && ih < IH && iw >= 0 && iw < IW;
+            for (int c = 0; c < C; ++c)
+                store_f(&p->view[0], nd_offset(p->view_shape[0], rank, nchw, ob, oh, ow, c),
+                        inside ? load_f(&p->whole, nd_offset(p->whole_shape, rank, nchw, ib, ih, iw, c)) : 0.0f);
+        }
+    }
+    return 0;
+}
+
 /* RefChannelShuffleWorkload.cpp:28-76: with g groups of s channels along `axis`, output channel i g + j takes input
  * channel i + j s, through Decoder / Encoder. */
 static int move_channel_shuffle(const oracle_move_params* p)
@@ -950,6 +1023,8 @@ int oracle_move_q(const oracle_move_params* p)
         case MOVE_SPACE_TO_DEPTH:  return move_space_to_depth(p);
         case MOVE_CHANNEL_SHUFFLE: return move_channel_shuffle(p);
         case MOVE_STACK:           return move_stack(p);
+        case MOVE_BATCH_TO_SPACE:  return move_batch_to_space(p);
+        case MOVE_SPACE_TO_BATCH:  return move_space_to_batch(p);
         default: return B200K_E_INVALID;
     }
 }

@@ -214,15 +214,20 @@ def mean_cases():
 
 
 def eltwise_cases():
-    def make(seed, sa, sb, op, dtype=S8, act=(0, 0., 0.), extra=()):
+    def make(seed, sa, sb, op, dtype=S8, act=(0, 0., 0.), extra=(), nonzero=False):
         def build(mem):
             rng = np.random.default_rng(seed)
             so = tuple(max(a, b) for a, b in zip(sa, sb))
             p = _abi.EltwiseParams()
             za, zb, zo = (3, -7, -128 if act[0] else 5) if dtype == S8 else (120, 131, 0 if act[0] else 128)
-            p.a = qt(mem, _rand(rng, dtype, sa), dtype, 0.031, za)
-            p.b = qt(mem, _rand(rng, dtype, sb), dtype, 0.017, zb)
-            oscale = {0: 0.05, 4: 0.06, 5: 0.05, 2: 0.035, 3: 0.035, 1: 0.5, 6: 0.3}[op]
+            a, b = _rand(rng, dtype, sa), _rand(rng, dtype, sb)
+            if nonzero:
+                # strictly positive operands: no division by zero, no negative base under a fractional exponent
+                za = zb = -128 if dtype == S8 else 0
+                a, b = np.maximum(a, za + 1).astype(a.dtype), np.maximum(b, zb + 1).astype(b.dtype)
+            p.a = qt(mem, a, dtype, 0.031, za)
+            p.b = qt(mem, b, dtype, 0.017, zb)
+            oscale = {0: 0.05, 4: 0.06, 5: 0.05, 2: 0.035, 3: 0.035, 1: 0.5, 6: 0.3, 7: 0.9, 8: 0.4, 100: 0.025}[op]
             p.out, out = qt_out(mem, so, dtype, oscale, zo)
             p.rank = len(so)
             for i in range(len(so)):
@@ -243,7 +248,18 @@ def eltwise_cases():
         "mul_broadcast_scalar": make(76, (1, 1, 1, 1), (2, 4, 4, 8), 4, extra=none),
         "maximum": make(77, (3, 17), (3, 17), 2, extra=none),
         "minimum_broadcast_row": make(78, (4, 1), (4, 9), 3, extra=none),
+        "div": make(79, (2, 5, 5, 16), (2, 5, 5, 16), 1, extra=none, nonzero=True),
+        "sqdiff_u8": make(80, (1, 6, 6, 12), (1, 1, 1, 12), 6, dtype=U8, extra=none),
+        "power_u8": make(61, (1, 9, 9, 16), (1, 9, 9, 16), 7, dtype=U8, extra=none, nonzero=True),
+        "floor_div": make(62, (3, 7, 11), (3, 7, 11), 8, extra=none, nonzero=True),
+        "floor_div_broadcast_u8": make(63, (2, 4, 4, 8), (1, 1, 1, 8), 8, dtype=U8, extra=none, nonzero=True),
+        "prelu_channel_alpha": make(64, (2, 9, 9, 24), (1, 1, 1, 24), 100, extra=none),
+        "prelu_u8_same_shape": make(65, (1, 5, 5, 32), (1, 5, 5, 32), 100, dtype=U8, extra=none),
     }
+
+
+# std::pow: the CUDA and glibc implementations may differ in the last ulp
+TRANSCENDENTAL_ELTWISE = ("power_u8",)
 
 
 def activation_cases():
@@ -573,6 +589,23 @@ def move_cases():
     c["stack_last_axis_requantise"] = lambda: MoveCase("stack", 226, ((4, 6, 3), S8, 0.06, 2), [((4, 6), S8, 0.05, -1), ((4, 6), S8, 0.07, 3), ((4, 6), S8, 0.06, 2)],
                                                        perm=(2,))
     c["slice_rank2_s32"] = lambda: MoveCase("slice", 217, ((7, 9), S32, 1.0, 0), [((3, 4), S32, 1.0, 0)], begin=(2, 5), end=(3, 4))
+    # BatchToSpaceNd / SpaceToBatchNd: begin = block shape, end / stride = crops or padding before / after
+    c["batch_to_space_2x2"] = lambda: MoveCase("batch_to_space", 227, ((8, 5, 6, 16),) + q, [((2, 10, 12, 16),) + q],
+                                               perm=(0,), begin=(2, 2), end=(0, 0), stride=(0, 0))
+    c["batch_to_space_crops"] = lambda: MoveCase("batch_to_space", 228, ((12, 4, 5, 7), U8, 0.1, 9), [((2, 5, 11, 7), U8, 0.1, 9)],
+                                                 perm=(0,), begin=(2, 3), end=(1, 3), stride=(2, 1))
+    c["batch_to_space_nchw_requantise"] = lambda: MoveCase("batch_to_space", 229, ((6, 3, 4, 5), S8, 0.05, 2), [((1, 3, 11, 9), S8, 0.08, -4)],
+                                                           perm=(1,), begin=(3, 2), end=(0, 1), stride=(1, 0))
+    c["batch_to_space_rank3"] = lambda: MoveCase("batch_to_space", 230, ((6, 5, 9),) + q, [((2, 12, 9),) + q],
+                                                 perm=(0,), begin=(3,), end=(2,), stride=(1,))
+    c["space_to_batch_2x2"] = lambda: MoveCase("space_to_batch", 231, ((2, 8, 6, 16),) + q, [((8, 4, 3, 16),) + q],
+                                               perm=(0,), begin=(2, 2), end=(0, 0), stride=(0, 0))
+    c["space_to_batch_padded_u8"] = lambda: MoveCase("space_to_batch", 232, ((2, 5, 7, 6), U8, 0.1, 131), [((12, 4, 4, 6), U8, 0.1, 131)],
+                                                     perm=(0,), begin=(2, 3), end=(1, 3), stride=(2, 2))
+    c["space_to_batch_nchw_requantise"] = lambda: MoveCase("space_to_batch", 233, ((1, 3, 7, 5), S8, 0.05, 2), [((6, 3, 3, 3), S8, 0.08, -4)],
+                                                           perm=(1,), begin=(3, 2), end=(2, 0), stride=(0, 1))
+    c["space_to_batch_rank3_dilation"] = lambda: MoveCase("space_to_batch", 234, ((2, 13, 8),) + q, [((8, 4, 8),) + q],
+                                                          perm=(0,), begin=(4,), end=(2,), stride=(1,))
     return c
 
 

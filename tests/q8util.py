@@ -413,7 +413,8 @@ class OracleMoveParams(C.Structure):
 
 
 MOVE_KINDS = {"concat": 0, "split": 1, "permute": 2, "transpose": 3, "strided_slice": 4, "slice": 5,
-              "depth_to_space": 6, "space_to_depth": 7, "channel_shuffle": 8, "stack": 9}
+              "depth_to_space": 6, "space_to_depth": 7, "channel_shuffle": 8, "stack": 9,
+              "batch_to_space": 10, "space_to_batch": 11}
 
 
 class MoveCase:
@@ -492,7 +493,8 @@ class MoveCase:
         return outs
 
     def views(self):
-        """[(view, source index, destination index)] with -1 for the whole tensor, else the index of the part."""
+        """[(view, source index, destination index)] with -1 for the whole tensor, -2 for one element holding the
+        destination's encoding of 0.0, else the index of the part."""
         from armnn_b200 import views as V
         shapes = [pt[0] for pt in self.parts]
         if self.kind == "concat":
@@ -510,6 +512,16 @@ class MoveCase:
             out_shape, v = fn(self.whole[0], self.perm[0], bool(self.perm[1]))
             assert tuple(out_shape) == tuple(shapes[0]), (out_shape, shapes[0])
             return [(v, -1, 0)]
+        if self.kind in ("batch_to_space", "space_to_batch"):
+            sp = len(self.whole[0]) - 2
+            block, edges = self.begin[:sp], list(zip(self.end[:sp], self.stride[:sp]))
+            if self.kind == "batch_to_space":
+                out_shape, vs = V.batch_to_space_views(self.whole[0], block, edges, bool(self.perm[0]))
+                padded = False
+            else:
+                out_shape, vs, padded = V.space_to_batch_views(self.whole[0], block, edges, bool(self.perm[0]))
+            assert tuple(out_shape) == tuple(shapes[0]), (out_shape, shapes[0])
+            return ([(V.fill_view(out_shape), -2, 0)] if padded else []) + [(v, -1, 0) for v in vs]
         if self.kind == "channel_shuffle":
             return [(V.channel_shuffle_view(self.whole[0], self.perm[0], self.perm[1]), -1, 0)]
         if self.kind in ("permute", "transpose"):
@@ -532,7 +544,13 @@ class MoveCase:
         for view, si, di in self.views():
             shape, so, ss, do, ds = V.merge_dims(view)
             p = _abi.ViewCopyParams()
-            p.x = whole if si < 0 else parts[si]
+            if si == -2:
+                _, dt, sc, zp = self.parts[di]
+                lo, hi = RANGE.get(dt, (0, 0))
+                zero = np.zeros(1, np.float32) if dt == _abi.F32 else np.array([min(max(zp, lo), hi)], NP_OF[dt])
+                p.x = qt(mem, zero, dt, sc, zp)
+            else:
+                p.x = whole if si < 0 else parts[si]
             p.y = whole if di < 0 else parts[di]
             p.rank = len(shape)
             for i in range(len(shape)):

@@ -174,3 +174,49 @@ def test_float32_graph_oracle_equals_armnn_cpuref(built):
     want = hostnet.ArmnnNetwork(net, "CpuRef").run({0: x})[0]
     got = hostnet.OracleNetwork(Optimize(net)).run({0: x})[0]
     assert want.shape == got.shape and np.array_equal(want, got)
+
+
+@needs_cpuref
+def test_space_to_batch_graph_mirror_views_vs_armnn_cpuref(built):
+    """SpaceToBatchNd (zero fill + strided blocks) -> depthwise convolution -> BatchToSpaceNd with crops, and a rank-3
+    SpaceToBatchNd that re-quantises: the mirror's views against the real runtime on CpuRef."""
+    import hostnet
+    from test_plugin import _dilated_by_batching_net
+    net = _dilated_by_batching_net()
+    rng = np.random.default_rng(32)
+    xs = {0: rng.integers(-128, 128, size=(2, 9, 11, 16)).astype(np.int8), 1: rng.integers(0, 256, size=(3, 10, 12)).astype(np.uint8)}
+    want = hostnet.ArmnnNetwork(net, "CpuRef").run(xs)
+    got = hostnet.OracleNetwork(Optimize(net)).run(xs)
+    assert want[1].shape == got[1].shape and np.array_equal(want[1], got[1])
+    # the convolution in the middle: CpuRef accumulates in fp32, the oracle exactly (a rounding tie may differ by one)
+    st = diff_stats(want[0], got[0])
+    assert want[0].shape == got[0].shape and st["max_abs"] <= 1 and st["mismatch_frac"] < 5e-3, st
+
+
+@needs_cpuref
+def test_prelu_and_binary_graph_oracle_equals_armnn_cpuref(built):
+    import hostnet
+    from armnn_b200.network import BinaryOperation, DataType, INetwork, TensorInfo
+    rng = np.random.default_rng(24)
+    shape = (2, 6, 5, 16)
+    net = INetwork.Create()
+    il = net.AddInputLayer(0, "input")
+    il.GetOutputSlot(0).SetTensorInfo(TensorInfo(shape, DataType.QAsymmS8, 0.04, 3))
+    alpha = rng.integers(-128, 128, size=(16,)).astype(np.int8)
+    al = net.AddConstantLayer(alpha, TensorInfo((16,), DataType.QAsymmS8, 0.01, 0), "alpha")
+    pl = net.AddPreluLayer("prelu")
+    il.GetOutputSlot(0).Connect(pl.GetInputSlot(0))
+    al.GetOutputSlot(0).Connect(pl.GetInputSlot(1))
+    pl.GetOutputSlot(0).SetTensorInfo(TensorInfo(shape, DataType.QAsymmS8, 0.03, -20))
+    c = np.maximum(rng.integers(-128, 128, size=(1, 1, 1, 16)), -100).astype(np.int8)
+    cl = net.AddConstantLayer(c, TensorInfo(c.shape, DataType.QAsymmS8, 0.02, -128), "divisor")
+    fd = net.AddElementwiseBinaryLayer(BinaryOperation.FloorDiv, "floor_div")
+    pl.GetOutputSlot(0).Connect(fd.GetInputSlot(0))
+    cl.GetOutputSlot(0).Connect(fd.GetInputSlot(1))
+    fd.GetOutputSlot(0).SetTensorInfo(TensorInfo(shape, DataType.QAsymmS8, 0.25, 0))
+    ol = net.AddOutputLayer(0, "output")
+    fd.GetOutputSlot(0).Connect(ol.GetInputSlot(0))
+    x = rng.integers(-128, 128, size=shape).astype(np.int8)
+    want = hostnet.ArmnnNetwork(net, "CpuRef").run({0: x})[0]
+    got = hostnet.OracleNetwork(Optimize(net)).run({0: x})[0]
+    assert np.array_equal(want, got)

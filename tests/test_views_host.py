@@ -89,3 +89,90 @@ def test_slice_view_and_dimension_merging():
     assert merged[0] == (2 * 6 * 8, 8)
     with pytest.raises(ValueError):
         V.slice_view(x.shape, (0, 0, 0, 10), (2, 6, 8, 8))
+
+
+def _to_nhwc4(x, nchw):
+    x4 = x if x.ndim == 4 else (x[:, :, :, None] if nchw else x[:, :, None, :])
+    return x4.transpose(0, 2, 3, 1) if nchw else x4
+
+
+def _from_nhwc4(y, rank, nchw):
+    y = y.transpose(0, 3, 1, 2) if nchw else y
+    if rank == 3:
+        y = y[:, :, :, 0] if nchw else y[:, :, 0, :]
+    return np.ascontiguousarray(y)
+
+
+@pytest.mark.parametrize("nchw", [False, True])
+@pytest.mark.parametrize("dims,block,edges", [
+    ((8, 3, 4, 5), (2, 2), ((0, 0), (0, 0))), ((12, 3, 4, 5), (2, 3), ((1, 2), (3, 1))),
+    ((6, 4, 2, 3), (3, 2), ((0, 5), (1, 0))), ((6, 4, None, 5), (3,), ((0, 0),)), ((4, 5, None, 3), (2,), ((1, 2),))])
+def test_batch_to_space_views_follow_the_reference_loop(dims, block, edges, nchw):
+    """`workloads/BatchToSpaceNd.cpp:86-116` restated with numpy indexing; uncropped cases are one six-dimensional walk."""
+    ib, ih, iw, c = dims
+    rank = 3 if iw is None else 4
+    shape = ((ib, c, ih) if nchw else (ib, ih, c)) if rank == 3 else ((ib, c, ih, iw) if nchw else (ib, ih, iw, c))
+    x = np.random.default_rng(3).integers(1, 255, size=shape).astype(np.uint8)
+    x4 = _to_nhwc4(x, nchw)
+    bh, bw = block[0], (block[1] if rank == 4 else 1)
+    (ct, cb), (cl, cr) = edges[0], (edges[1] if rank == 4 else (0, 0))
+    ob = ib // (bh * bw)
+    want = np.zeros((ob, x4.shape[1] * bh - ct - cb, x4.shape[2] * bw - cl - cr, c), np.uint8)
+    for b in range(ib):
+        so = b // ob
+        for h in range(x4.shape[1]):
+            for w in range(x4.shape[2]):
+                y, xx = h * bh + so // bw - ct, w * bw + so % bw - cl
+                if 0 <= y < want.shape[1] and 0 <= xx < want.shape[2]:
+                    want[b % ob, y, xx] = x4[b, h, w]
+    want = _from_nhwc4(want, rank, nchw)
+    out_shape, vs = V.batch_to_space_views(shape, block, edges, nchw)
+    assert tuple(out_shape) == want.shape
+    assert len(vs) == 1 or any(a or b for a, b in edges)
+    got = np.zeros(out_shape, np.uint8)
+    for v in vs:
+        apply_view(x, got, V.merge_dims(v))
+    assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("nchw", [False, True])
+@pytest.mark.parametrize("dims,block,edges", [
+    ((2, 4, 6, 5), (2, 2), ((0, 0), (0, 0))), ((2, 3, 5, 4), (2, 3), ((1, 2), (3, 1))),
+    ((1, 2, 2, 3), (3, 2), ((4, 3), (1, 1))), ((2, 6, None, 5), (3,), ((0, 0),)), ((2, 5, None, 3), (2,), ((1, 2),))])
+def test_space_to_batch_views_follow_the_reference_loop(dims, block, edges, nchw):
+    """`workloads/SpaceToBatchNd.cpp:82-129` restated with numpy indexing; padding positions keep the fill value."""
+    ib, ih, iw, c = dims
+    rank = 3 if iw is None else 4
+    shape = ((ib, c, ih) if nchw else (ib, ih, c)) if rank == 3 else ((ib, c, ih, iw) if nchw else (ib, ih, iw, c))
+    x = np.random.default_rng(4).integers(1, 255, size=shape).astype(np.uint8)
+    x4 = _to_nhwc4(x, nchw)
+    bh, bw = block[0], (block[1] if rank == 4 else 1)
+    (pt, pb), (pl, pr) = edges[0], (edges[1] if rank == 4 else (0, 0))
+    oh, ow = (x4.shape[1] + pt + pb) // bh, (x4.shape[2] + pl + pr) // bw
+    want = np.zeros((ib * bh * bw, oh, ow, c), np.uint8)
+    for b in range(ib * bh * bw):
+        sh, sw = (b // ib) // bw, (b // ib) % bw
+        for y in range(oh):
+            for xx in range(ow):
+                h, w = y * bh + sh - pt, xx * bw + sw - pl
+                if 0 <= h < x4.shape[1] and 0 <= w < x4.shape[2]:
+                    want[b, y, xx] = x4[b % ib, h, w]
+    want = _from_nhwc4(want, rank, nchw)
+    out_shape, vs, padded = V.space_to_batch_views(shape, block, edges, nchw)
+    assert tuple(out_shape) == want.shape and padded == any(a or b for a, b in edges)
+    got = np.full(out_shape, 77, np.uint8)
+    apply_view(np.zeros(1, np.uint8), got, V.fill_view(out_shape))
+    for v in vs:
+        apply_view(x, got, V.merge_dims(v))
+    assert np.array_equal(got, want)
+
+
+def test_batch_and_space_views_refuse_shapes_that_do_not_divide():
+    with pytest.raises(ValueError):
+        V.space_to_batch_views((1, 5, 4, 3), (2, 2), ((0, 0), (0, 0)))          # height 5 is not a multiple of 2
+    with pytest.raises(ValueError):
+        V.batch_to_space_views((6, 2, 2, 3), (2, 2), ((0, 0), (0, 0)))          # batch 6 is not a multiple of 4
+    with pytest.raises(ValueError):
+        V.batch_to_space_views((4, 1, 1, 3), (2, 2), ((1, 1), (0, 0)))          # crops leave nothing
+    with pytest.raises(ValueError):
+        V.batch_to_space_views((4, 2), (2,), ((0, 0),))                         # rank 2
