@@ -75,6 +75,11 @@ class SoftmaxParams(C.Structure):
                 ("inner", C.c_int32), ("beta", C.c_float)]
 
 
+class ArgMinMaxParams(C.Structure):
+    _fields_ = [("x", QTensor), ("y", C.c_void_p), ("outer", C.c_int32), ("axis_size", C.c_int32), ("inner", C.c_int32),
+                ("function", C.c_int32), ("out_int64", C.c_int32)]
+
+
 class ConvertParams(C.Structure):
     _fields_ = [("x", QTensor), ("y", QTensor), ("count", C.c_int64)]
 
@@ -150,6 +155,9 @@ KERNEL_ENTRY_POINTS = {
     "eltwise_q8": EltwiseParams,
     "activation_q8": ActivationParams,
     "softmax_q8": SoftmaxParams,
+    "log_softmax_q": SoftmaxParams,
+    "l2_normalization_q": SoftmaxParams,
+    "arg_min_max_q": ArgMinMaxParams,
     "convert_q": ConvertParams,
     "qlstm_step": QLstmParams,
     "pad_q": PadParams,

@@ -147,6 +147,12 @@ class ArmnnNetwork:
                 lid = lib.armnnc_add_elementwise_binary(net, int(d["op"]))
             elif t == "BatchMatMul":
                 lid = lib.armnnc_add_batch_matmul(net, int(d["tx"]), int(d["ty"]), int(d.get("ax", False)), int(d.get("ay", False)))
+            elif t == "LogSoftmax":
+                lid = lib.armnnc_add_log_softmax(net, C.c_float(d["beta"]), d["axis"])
+            elif t == "L2Normalization":
+                lid = lib.armnnc_add_l2_normalization(net, C.c_float(d["eps"]), int(d["nchw"]))
+            elif t == "ArgMinMax":
+                lid = lib.armnnc_add_arg_min_max(net, d["function"], d["axis"])
             elif t == "Softmax":
                 lid = lib.armnnc_add_softmax(net, C.c_float(d["beta"]), d["axis"])
             elif t == "Mean":

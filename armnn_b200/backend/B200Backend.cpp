@@ -242,6 +242,14 @@ public:
             }
             case LayerType::Softmax:
                 return (IsActType(infos[0]) && IsActType(infos[1])) || No(reason, "unsupported data type");
+            case LayerType::LogSoftmax:
+            case LayerType::L2Normalization:
+                if (infos[0].GetDataType() == DataType::QSymmS16 && type == LayerType::LogSoftmax) { return No(reason, "QSymmS16 is not supported"); }
+                if (type == LayerType::L2Normalization && infos[0].GetNumDimensions() > 4) { return No(reason, "rank > 4"); }
+                return (IsActType(infos[0]) && infos[1].GetDataType() == infos[0].GetDataType()) || No(reason, "unsupported or mismatched data types");
+            case LayerType::ArgMinMax:
+                if (infos[1].GetDataType() != DataType::Signed32 && infos[1].GetDataType() != DataType::Signed64) { return No(reason, "the output must be Signed32 or Signed64"); }
+                return IsActType(infos[0]) || No(reason, "unsupported input data type");
             case LayerType::Quantize:
             case LayerType::Dequantize:
                 if (infos[0].HasPerAxisQuantization()) { return No(reason, "per-axis input is not supported"); }

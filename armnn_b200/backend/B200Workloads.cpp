@@ -185,6 +185,18 @@ void DenseStrides(const TensorShape& shape, int64_t* strides)
     for (unsigned int d = shape.GetNumDimensions(); d-- > 0;) { strides[d] = st; st *= shape[d]; }
 }
 
+/// outer x axis x inner: the tensor seen as independent rows along `axis` (negative: counted from the end).
+void RowsOf(const TensorShape& shape, int axis, int32_t& outer, int32_t& axisSize, int32_t& inner)
+{
+    const int rank = static_cast<int>(shape.GetNumDimensions());
+    if (axis < 0) { axis += rank; }
+    if (axis < 0 || axis >= rank) { throw InvalidArgumentException("B200Acc: axis outside the tensor's dimensions"); }
+    outer = 1; inner = 1;
+    for (int i = 0; i < axis; ++i) { outer *= static_cast<int32_t>(shape[static_cast<unsigned int>(i)]); }
+    for (int i = axis + 1; i < rank; ++i) { inner *= static_cast<int32_t>(shape[static_cast<unsigned int>(i)]); }
+    axisSize = static_cast<int32_t>(shape[static_cast<unsigned int>(axis)]);
+}
+
 ViewOp NewViewOp(const TensorInfo& x, const TensorInfo& y, DeviceBlobs& blobs, unsigned int src, unsigned int dst, unsigned int rank)
 {
     if (rank < 1 || rank > 6) { throw InvalidArgumentException("B200Acc: view copies need a rank between 1 and 6"); }
@@ -1119,6 +1131,60 @@ std::unique_ptr<IWorkload> B200WorkloadFactory::CreateWorkload(LayerType type, c
             {
                 st->p.x.data = Dev(data.m_Inputs[0]); st->p.y.data = Dev(data.m_Outputs[0]);
                 B200CheckStatus(b200k_softmax_q8(&st->p, s));
+            });
+        }
+        case LayerType::LogSoftmax:
+        {
+            const auto& qd = *PolymorphicDowncast<const LogSoftmaxQueueDescriptor*>(&d);
+            auto st = std::make_shared<SimpleState<b200k_softmax_params>>(ctx);
+            std::memset(&st->p, 0, sizeof(st->p));
+            st->p.x = Operand(info.m_InputTensorInfos[0], st->blobs); st->p.y = Operand(info.m_OutputTensorInfos[0], st->blobs);
+            RowsOf(info.m_InputTensorInfos[0].GetShape(), qd.m_Parameters.m_Axis, st->p.outer, st->p.axis_size, st->p.inner);
+            st->p.beta = qd.m_Parameters.m_Beta;
+            return Make<LogSoftmaxQueueDescriptor>(d, info, ctx, [st](const LogSoftmaxQueueDescriptor& data, cudaStream_t s)
+            {
+                st->p.x.data = Dev(data.m_Inputs[0]); st->p.y.data = Dev(data.m_Outputs[0]);
+                B200CheckStatus(b200k_log_softmax_q(&st->p, s));
+            });
+        }
+        case LayerType::L2Normalization:
+        {
+            // the channel dimension of the shape padded to four dimensions with leading 1s
+            // (RefL2NormalizationWorkload.cpp:41-71); without one, every element is its own channel
+            const auto& qd = *PolymorphicDowncast<const L2NormalizationQueueDescriptor*>(&d);
+            auto st = std::make_shared<SimpleState<b200k_softmax_params>>(ctx);
+            std::memset(&st->p, 0, sizeof(st->p));
+            const TensorInfo& x = info.m_InputTensorInfos[0];
+            st->p.x = Operand(x, st->blobs); st->p.y = Operand(info.m_OutputTensorInfos[0], st->blobs);
+            const int rank = static_cast<int>(x.GetNumDimensions());
+            const int axis = (qd.m_Parameters.m_DataLayout == DataLayout::NCHW ? 1 : 3) - (4 - rank);
+            if (rank > 4) { throw InvalidArgumentException("B200Acc: L2Normalization takes at most 4 dimensions"); }
+            if (axis < 0) { st->p.outer = static_cast<int32_t>(x.GetNumElements()); st->p.axis_size = 1; st->p.inner = 1; }
+            else { RowsOf(x.GetShape(), axis, st->p.outer, st->p.axis_size, st->p.inner); }
+            st->p.beta = qd.m_Parameters.m_Eps;
+            return Make<L2NormalizationQueueDescriptor>(d, info, ctx, [st](const L2NormalizationQueueDescriptor& data, cudaStream_t s)
+            {
+                st->p.x.data = Dev(data.m_Inputs[0]); st->p.y.data = Dev(data.m_Outputs[0]);
+                B200CheckStatus(b200k_l2_normalization_q(&st->p, s));
+            });
+        }
+        case LayerType::ArgMinMax:
+        {
+            const auto& qd = *PolymorphicDowncast<const ArgMinMaxQueueDescriptor*>(&d);
+            auto st = std::make_shared<SimpleState<b200k_arg_min_max_params>>(ctx);
+            std::memset(&st->p, 0, sizeof(st->p));
+            st->p.x = Operand(info.m_InputTensorInfos[0], st->blobs);
+            RowsOf(info.m_InputTensorInfos[0].GetShape(), qd.m_Parameters.m_Axis, st->p.outer, st->p.axis_size, st->p.inner);
+            st->p.function = qd.m_Parameters.m_Function == ArgMinMaxFunction::Max ? 1 : 0;
+            st->p.out_int64 = info.m_OutputTensorInfos[0].GetDataType() == DataType::Signed64 ? 1 : 0;
+            if (info.m_OutputTensorInfos[0].GetNumElements() != static_cast<unsigned int>(st->p.outer) * static_cast<unsigned int>(st->p.inner))
+            {
+                throw InvalidArgumentException("B200Acc: ArgMinMax output shape does not drop the axis");
+            }
+            return Make<ArgMinMaxQueueDescriptor>(d, info, ctx, [st](const ArgMinMaxQueueDescriptor& data, cudaStream_t s)
+            {
+                st->p.x.data = Dev(data.m_Inputs[0]); st->p.y = Dev(data.m_Outputs[0]);
+                B200CheckStatus(b200k_arg_min_max_q(&st->p, s));
             });
         }
         case LayerType::Quantize:

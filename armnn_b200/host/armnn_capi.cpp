@@ -224,6 +224,27 @@ int armnnc_add_elementwise_binary(void* vn, int op)
     return add_layer(n, n->net->AddElementwiseBinaryLayer(ElementwiseBinaryDescriptor(static_cast<BinaryOperation>(op))));
 }
 
+int armnnc_add_log_softmax(void* vn, float beta, int axis)
+{
+    auto* n = static_cast<CNet*>(vn);
+    LogSoftmaxDescriptor d; d.m_Beta = beta; d.m_Axis = axis;
+    return add_layer(n, n->net->AddLogSoftmaxLayer(d));
+}
+
+int armnnc_add_l2_normalization(void* vn, float eps, int nchw)
+{
+    auto* n = static_cast<CNet*>(vn);
+    L2NormalizationDescriptor d; d.m_Eps = eps; d.m_DataLayout = nchw ? DataLayout::NCHW : DataLayout::NHWC;
+    return add_layer(n, n->net->AddL2NormalizationLayer(d));
+}
+
+int armnnc_add_arg_min_max(void* vn, int function, int axis)
+{
+    auto* n = static_cast<CNet*>(vn);
+    ArgMinMaxDescriptor d; d.m_Function = function ? ArgMinMaxFunction::Max : ArgMinMaxFunction::Min; d.m_Axis = axis;
+    return add_layer(n, n->net->AddArgMinMaxLayer(d));
+}
+
 int armnnc_add_softmax(void* vn, float beta, int axis)
 {
     auto* n = static_cast<CNet*>(vn);

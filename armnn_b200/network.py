@@ -237,6 +237,19 @@ class INetwork:
     def AddSoftmaxLayer(self, beta=1.0, axis=-1, name=None):
         return self._add(Layer("Softmax", name, 1, 1, {"beta": float(beta), "axis": int(axis)}))
 
+    def AddLogSoftmaxLayer(self, beta=1.0, axis=-1, name=None):
+        return self._add(Layer("LogSoftmax", name, 1, 1, {"beta": float(beta), "axis": int(axis)}))
+
+    def AddL2NormalizationLayer(self, eps=1e-12, nchw=False, name=None):
+        """armnn::L2NormalizationDescriptor: normalises over the channel dimension of a tensor of up to 4 dimensions."""
+        return self._add(Layer("L2Normalization", name, 1, 1, {"eps": float(eps), "nchw": bool(nchw)}))
+
+    def AddArgMinMaxLayer(self, function, axis=-1, name=None):
+        """armnn::ArgMinMaxDescriptor: function 0 Min, 1 Max; the output (Signed32) drops the axis."""
+        if int(function) not in (0, 1):
+            raise InvalidArgumentException("ArgMinMax: function must be 0 (Min) or 1 (Max)")
+        return self._add(Layer("ArgMinMax", name, 1, 1, {"function": int(function), "axis": int(axis)}))
+
     def AddMeanLayer(self, axis=(1, 2), keep_dims=False, name=None):
         return self._add(Layer("Mean", name, 1, 1, {"axis": tuple(axis), "keep_dims": keep_dims}))
 
@@ -388,6 +401,19 @@ def IsLayerSupported(layer):
             return False, "%s: unsupported data type" % t
         if t in ("ElementwiseBinary", "Prelu") and len(outs[0].shape) > 4:
             return False, "%s: rank > 4" % t
+        return True, ""
+    if t in ("LogSoftmax", "L2Normalization"):
+        ok = (DataType.QAsymmU8, DataType.QAsymmS8, DataType.Float32) + ((DataType.QSymmS16,) if t == "L2Normalization" else ())
+        if ins[0].dtype not in ok or outs[0].dtype != ins[0].dtype:
+            return False, "%s: unsupported or mismatched data types" % t
+        if t == "L2Normalization" and len(ins[0].shape) > 4:
+            return False, "L2Normalization: rank > 4"
+        return True, ""
+    if t == "ArgMinMax":
+        if ins[0].dtype not in (DataType.QAsymmU8, DataType.QAsymmS8, DataType.QSymmS16, DataType.Float32):
+            return False, "ArgMinMax: unsupported input data type"
+        if outs[0].dtype != DataType.Signed32:
+            return False, "ArgMinMax: the output must be Signed32"
         return True, ""
     if t in ("Quantize", "Dequantize"):
         return True, ""
@@ -834,6 +860,48 @@ class GraphProgram:
         p.inner = int(np.prod(shape[axis + 1:])) if axis + 1 < len(shape) else 1
         p.beta = layer.desc["beta"]
         return "softmax_q8", p
+
+    def _rows(self, x, axis):
+        shape = x.info.shape
+        axis = axis % len(shape)
+        outer = int(np.prod(shape[:axis])) if axis > 0 else 1
+        inner = int(np.prod(shape[axis + 1:])) if axis + 1 < len(shape) else 1
+        return outer, int(shape[axis]), inner
+
+    def _make_LogSoftmax(self, layer):
+        x, y = layer.inputs[0].source, layer.outputs[0]
+        p = _abi.SoftmaxParams()
+        p.x, p.y = self._operand(x), self._operand(y)
+        p.outer, p.axis_size, p.inner = self._rows(x, layer.desc["axis"])
+        p.beta = layer.desc["beta"]
+        return "log_softmax_q", p
+
+    def _make_L2Normalization(self, layer):
+        """The channel dimension of the tensor padded to 4 dimensions with leading 1s
+        (RefL2NormalizationWorkload.cpp:41-71): the last one for NHWC, the second of four for NCHW."""
+        x, y = layer.inputs[0].source, layer.outputs[0]
+        rank = len(x.info.shape)
+        p = _abi.SoftmaxParams()
+        p.x, p.y = self._operand(x), self._operand(y)
+        axis = (1 if layer.desc["nchw"] else 3) - (4 - rank)
+        if axis < 0:
+            # no channel dimension: one channel per element
+            p.outer, p.axis_size, p.inner = x.info.GetNumElements(), 1, 1
+        else:
+            p.outer, p.axis_size, p.inner = self._rows(x, axis)
+        p.beta = layer.desc["eps"]
+        return "l2_normalization_q", p
+
+    def _make_ArgMinMax(self, layer):
+        x, y = layer.inputs[0].source, layer.outputs[0]
+        p = _abi.ArgMinMaxParams()
+        p.x = self._operand(x)
+        p.y = self._ptr(self._dev(y))
+        p.outer, p.axis_size, p.inner = self._rows(x, layer.desc["axis"])
+        if y.info.GetNumElements() != p.outer * p.inner:
+            raise InvalidArgumentException("ArgMinMax: output shape %s does not drop the axis of %s" % (y.info.shape, x.info.shape))
+        p.function, p.out_int64 = layer.desc["function"], 0
+        return "arg_min_max_q", p
 
     def _make_convert(self, layer):
         x, y = layer.inputs[0].source, layer.outputs[0]

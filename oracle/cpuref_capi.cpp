@@ -358,6 +358,59 @@ extern "C" int cpuref_softmax_q8(const b200k_softmax_params* p)
     });
 }
 
+extern "C" int cpuref_log_softmax_q(const b200k_softmax_params* p)
+{
+    return guarded([&] {
+        Harness h;
+        TensorShape s({(unsigned)p->outer, (unsigned)p->axis_size, (unsigned)p->inner});
+        TensorInfo xi = make_info(p->x, s, 0, 0, false);
+        TensorInfo yi = make_info(p->y, s, 0, 0, false);
+        LogSoftmaxQueueDescriptor d;
+        d.m_Parameters.m_Beta = p->beta;
+        d.m_Parameters.m_Axis = 1;
+        h.in(d, xi, p->x.data);
+        auto* o = h.out(d, yi);
+        h.run(LayerType::LogSoftmax, d);
+        copy_out(o, const_cast<void*>(p->y.data), yi.GetNumBytes());
+    });
+}
+
+extern "C" int cpuref_l2_normalization_q(const b200k_softmax_params* p)
+{
+    return guarded([&] {
+        Harness h;
+        // the channel axis is the row axis: NHWC [outer, 1, 1, axis] when it is contiguous, else NCHW [outer, axis, 1, inner]
+        const bool nhwc = p->inner == 1;
+        TensorShape s = nhwc ? TensorShape({(unsigned)p->outer, 1u, 1u, (unsigned)p->axis_size})
+                             : TensorShape({(unsigned)p->outer, (unsigned)p->axis_size, 1u, (unsigned)p->inner});
+        TensorInfo xi = make_info(p->x, s, 0, 0, false);
+        TensorInfo yi = make_info(p->y, s, 0, 0, false);
+        L2NormalizationQueueDescriptor d;
+        d.m_Parameters.m_Eps = p->beta;
+        d.m_Parameters.m_DataLayout = nhwc ? DataLayout::NHWC : DataLayout::NCHW;
+        h.in(d, xi, p->x.data);
+        auto* o = h.out(d, yi);
+        h.run(LayerType::L2Normalization, d);
+        copy_out(o, const_cast<void*>(p->y.data), yi.GetNumBytes());
+    });
+}
+
+extern "C" int cpuref_arg_min_max_q(const b200k_arg_min_max_params* p)
+{
+    return guarded([&] {
+        Harness h;
+        TensorInfo xi = make_info(p->x, TensorShape({(unsigned)p->outer, (unsigned)p->axis_size, (unsigned)p->inner}), 0, 0, false);
+        TensorInfo yi(TensorShape({(unsigned)p->outer, (unsigned)p->inner}), p->out_int64 ? DataType::Signed64 : DataType::Signed32);
+        ArgMinMaxQueueDescriptor d;
+        d.m_Parameters.m_Function = p->function ? ArgMinMaxFunction::Max : ArgMinMaxFunction::Min;
+        d.m_Parameters.m_Axis = 1;
+        h.in(d, xi, p->x.data);
+        auto* o = h.out(d, yi);
+        h.run(LayerType::ArgMinMax, d);
+        copy_out(o, p->y, yi.GetNumBytes());
+    });
+}
+
 extern "C" int cpuref_convert_q(const b200k_convert_params* p)
 {
     return guarded([&] {

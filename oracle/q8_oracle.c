@@ -559,6 +559,82 @@ int oracle_softmax_q8(const b200k_softmax_params* p)
     return 0;
 }
 
+/* ---- LogSoftmax, LogSoftmax.cpp:30-88 ----------------------------------------------------------- */
+
+int oracle_log_softmax_q(const b200k_softmax_params* p)
+{
+    if (!p->x.data || !p->y.data) return B200K_E_INVALID;
+    for (int o = 0; o < p->outer; ++o)
+    for (int in = 0; in < p->inner; ++in) {
+        int64_t base = (int64_t)o * p->axis_size * p->inner + in;
+        float mx = load_f(&p->x, base);
+        for (int i = 1; i < p->axis_size; ++i) {
+            float v = load_f(&p->x, base + (int64_t)i * p->inner);
+            if (v > mx) mx = v;
+        }
+        float sum = 0.0f;
+        for (int i = 0; i < p->axis_size; ++i) {
+            volatile float d = load_f(&p->x, base + (int64_t)i * p->inner) - mx;
+            volatile float t = d * p->beta;
+            volatile float s = sum + expf(t);
+            sum = s;
+        }
+        const float log_sum = logf(sum);
+        for (int i = 0; i < p->axis_size; ++i) {
+            volatile float d = load_f(&p->x, base + (int64_t)i * p->inner) - mx;
+            volatile float t = d * p->beta;
+            volatile float r = t - log_sum;
+            store_f(&p->y, base + (int64_t)i * p->inner, r);
+        }
+    }
+    return 0;
+}
+
+/* ---- L2Normalization, RefL2NormalizationWorkload.cpp:29-93: beta carries eps --------------------- */
+
+int oracle_l2_normalization_q(const b200k_softmax_params* p)
+{
+    if (!p->x.data || !p->y.data) return B200K_E_INVALID;
+    for (int o = 0; o < p->outer; ++o)
+    for (int in = 0; in < p->inner; ++in) {
+        int64_t base = (int64_t)o * p->axis_size * p->inner + in;
+        float reduction = 0.0f;
+        for (int i = 0; i < p->axis_size; ++i) {
+            const float v = load_f(&p->x, base + (int64_t)i * p->inner);
+            volatile float sq = v * v;
+            volatile float s = reduction + sq;
+            reduction = s;
+        }
+        const float maximum = reduction < p->beta ? p->beta : reduction;
+        const float scale = 1.0f / sqrtf(maximum);
+        for (int i = 0; i < p->axis_size; ++i) {
+            volatile float r = load_f(&p->x, base + (int64_t)i * p->inner) * scale;
+            store_f(&p->y, base + (int64_t)i * p->inner, r);
+        }
+    }
+    return 0;
+}
+
+/* ---- ArgMinMax, ArgMinMax.cpp:16-48 ------------------------------------------------------------- */
+
+int oracle_arg_min_max_q(const b200k_arg_min_max_params* p)
+{
+    if (!p->x.data || !p->y) return B200K_E_INVALID;
+    for (int o = 0; o < p->outer; ++o)
+    for (int in = 0; in < p->inner; ++in) {
+        int64_t base = (int64_t)o * p->axis_size * p->inner + in;
+        float best = load_f(&p->x, base);
+        int idx = 0;
+        for (int i = 1; i < p->axis_size; ++i) {
+            const float v = load_f(&p->x, base + (int64_t)i * p->inner);
+            if ((p->function == 0 && v < best) || (p->function == 1 && v > best)) { best = v; idx = i; }
+        }
+        const int64_t at = (int64_t)o * p->inner + in;
+        if (p->out_int64) ((int64_t*)p->y)[at] = idx; else ((int32_t*)p->y)[at] = idx;
+    }
+    return 0;
+}
+
 /* ---- Quantize / Dequantize / requantize, RefQuantizeWorkload.cpp:14-45, Dequantize.cpp:11-28 - */
 
 int oracle_convert_q(const b200k_convert_params* p)

@@ -301,6 +301,77 @@ def softmax_cases():
             "inner_axis": make(103, 3, 7, 4, beta=0.5), "single_element": make(104, 4, 1, 1)}
 
 
+def rows_cases():
+    """LogSoftmax, L2Normalization and ArgMinMax: independent rows along one axis (outer x inner of them)."""
+    def log_softmax(seed, outer, axis, inner, dtype=S8, beta=1.0):
+        def build(mem):
+            rng = np.random.default_rng(seed)
+            p = _abi.SoftmaxParams()
+            if dtype == F32:
+                p.x = qt(mem, (rng.standard_normal((outer, axis, inner)) * 3).astype(np.float32), F32)
+                p.y, y = qt_out(mem, (outer, axis, inner), F32)
+            else:
+                p.x = qt(mem, _rand(rng, dtype, (outer, axis, inner)), dtype, 0.06, 0 if dtype == S8 else 128)
+                p.y, y = qt_out(mem, (outer, axis, inner), dtype, 1 / 16., 127 if dtype == S8 else 255)
+            p.outer, p.axis_size, p.inner, p.beta = outer, axis, inner, beta
+            return p, [y]
+        return lambda: SimpleCase("log_softmax_q", build)
+
+    def l2norm(seed, outer, axis, inner, dtype=S8, eps=1e-12, zero_rows=False):
+        def build(mem):
+            rng = np.random.default_rng(seed)
+            p = _abi.SoftmaxParams()
+            if dtype == F32:
+                p.x = qt(mem, rng.standard_normal((outer, axis, inner)).astype(np.float32), F32)
+                p.y, y = qt_out(mem, (outer, axis, inner), F32)
+            else:
+                zp = 3 if dtype == S8 else (128 if dtype == U8 else 0)
+                x = _rand(rng, dtype, (outer, axis, inner))
+                if zero_rows:
+                    x[0] = zp                       # a row of zeros: the sum of squares is below eps
+                p.x = qt(mem, x, dtype, 0.04, zp)
+                p.y, y = qt_out(mem, (outer, axis, inner), dtype, 1 / 128. if dtype != S16 else 1 / 32768., 0 if dtype != U8 else 128)
+            p.outer, p.axis_size, p.inner, p.beta = outer, axis, inner, eps
+            return p, [y]
+        return lambda: SimpleCase("l2_normalization_q", build)
+
+    def argminmax(seed, outer, axis, inner, function, dtype=S8, out64=False, few_values=False):
+        def build(mem):
+            rng = np.random.default_rng(seed)
+            p = _abi.ArgMinMaxParams()
+            if dtype == F32:
+                p.x = qt(mem, rng.standard_normal((outer, axis, inner)).astype(np.float32), F32)
+            else:
+                x = _rand(rng, dtype, (outer, axis, inner))
+                if few_values:
+                    x = (x % 3).astype(x.dtype)    # many equal elements: the first one must win
+                p.x = qt(mem, x, dtype, 0.05, 1)
+            y, p.y = mem.out((outer, inner), np.int64 if out64 else np.int32)
+            p.outer, p.axis_size, p.inner, p.function, p.out_int64 = outer, axis, inner, function, int(out64)
+            return p, [y]
+        return lambda: SimpleCase("arg_min_max_q", build)
+    return {
+        "log_softmax_classifier_1001": log_softmax(301, 4, 1001, 1),
+        "log_softmax_u8_inner_axis": log_softmax(302, 3, 9, 5, dtype=U8, beta=0.5),
+        "log_softmax_float": log_softmax(303, 6, 40, 1, dtype=F32, beta=2.0),
+        "l2norm_nhwc_channels": l2norm(304, 50, 64, 1),
+        "l2norm_nchw_u8": l2norm(305, 2, 24, 35, dtype=U8),
+        "l2norm_eps_and_zero_row": l2norm(306, 3, 16, 1, eps=0.5, zero_rows=True),
+        "l2norm_s16": l2norm(307, 4, 33, 1, dtype=S16),
+        "l2norm_float": l2norm(308, 7, 19, 3, dtype=F32),
+        "argmax_classifier_1001": argminmax(309, 16, 1001, 1, 1),
+        "argmax_segmentation_inner": argminmax(310, 2, 21, 33 * 17, 1, dtype=U8),
+        "argmin_ties_first_wins": argminmax(311, 9, 200, 1, 0, few_values=True),
+        "argmax_ties_inner_int64": argminmax(312, 3, 50, 7, 1, out64=True, few_values=True),
+        "argmin_float_short_axis": argminmax(313, 10, 5, 1, 0, dtype=F32),
+        "argmax_s16_single_element": argminmax(314, 4, 1, 3, 1, dtype=S16),
+    }
+
+
+# expf / logf of the device against glibc: the last ulp may move a value across a rounding boundary
+TRANSCENDENTAL_ROWS = ("log_softmax_classifier_1001", "log_softmax_u8_inner_axis", "log_softmax_float")
+
+
 def convert_cases():
     def make(seed, xd, yd, count=1001, xq=(0.05, 3), yq=(0.07, -4)):
         def build(mem):
@@ -611,7 +682,8 @@ def move_cases():
 
 ALL_GROUPS = {"conv": conv_cases, "dwconv": dwconv_cases, "fc": fc_cases, "bmm": bmm_cases, "pool": pool_cases,
               "mean": mean_cases, "eltwise": eltwise_cases, "activation": activation_cases, "softmax": softmax_cases,
-              "convert": convert_cases, "pad": pad_cases, "qlstm": qlstm_cases, "move": move_cases, "resize": resize_cases, "reduce": reduce_cases, "tconv": tconv_cases, "f32": f32_cases, "unary": unary_cases}
+              "convert": convert_cases, "pad": pad_cases, "qlstm": qlstm_cases, "move": move_cases, "resize": resize_cases, "reduce": reduce_cases, "tconv": tconv_cases, "f32": f32_cases, "unary": unary_cases,
+              "rows": rows_cases}
 
 
 def run_case(case, where):

@@ -220,3 +220,16 @@ def test_prelu_and_binary_graph_oracle_equals_armnn_cpuref(built):
     want = hostnet.ArmnnNetwork(net, "CpuRef").run({0: x})[0]
     got = hostnet.OracleNetwork(Optimize(net)).run({0: x})[0]
     assert np.array_equal(want, got)
+
+
+@needs_cpuref
+def test_l2_normalization_arg_max_log_softmax_graph_oracle_equals_armnn_cpuref(built):
+    import hostnet
+    from test_plugin import _rows_net
+    net, shape = _rows_net()
+    x = np.random.default_rng(38).integers(-128, 128, size=shape).astype(np.int8)
+    want = hostnet.ArmnnNetwork(net, "CpuRef").run({0: x})
+    got = hostnet.OracleNetwork(Optimize(net)).run({0: x})
+    assert want[1].dtype == np.int32
+    for k in (0, 1, 2):
+        assert want[k].shape == got[k].shape and np.array_equal(want[k], got[k]), k

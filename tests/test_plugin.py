@@ -816,3 +816,46 @@ def test_space_to_batch_and_back_through_the_runtime_match_cpuref_and_the_python
     assert np.array_equal(got[0], ys[0])
     st = diff_stats(ref[0], got[0])
     assert ref[0].shape == got[0].shape and st["max_abs"] <= 1 and st["mismatch_frac"] < 5e-3, st
+
+
+def _rows_net():
+    """L2Normalization, ArgMinMax (Max over the channels, Signed32 indices) and LogSoftmax of one input."""
+    from armnn_b200.network import DataType, INetwork, TensorInfo
+    shape = (2, 5, 6, 16)
+    net = INetwork.Create()
+    il = net.AddInputLayer(0, "input")
+    il.GetOutputSlot(0).SetTensorInfo(TensorInfo(shape, DataType.QAsymmS8, 0.05, -3))
+    l2 = net.AddL2NormalizationLayer(1e-12, name="l2")
+    il.GetOutputSlot(0).Connect(l2.GetInputSlot(0))
+    l2.GetOutputSlot(0).SetTensorInfo(TensorInfo(shape, DataType.QAsymmS8, 1 / 128., 0))
+    am = net.AddArgMinMaxLayer(1, 3, name="argmax")
+    il.GetOutputSlot(0).Connect(am.GetInputSlot(0))
+    am.GetOutputSlot(0).SetTensorInfo(TensorInfo(shape[:3], DataType.Signed32))
+    ls = net.AddLogSoftmaxLayer(1.0, -1, name="log_softmax")
+    il.GetOutputSlot(0).Connect(ls.GetInputSlot(0))
+    ls.GetOutputSlot(0).SetTensorInfo(TensorInfo(shape, DataType.QAsymmS8, 1 / 16., 127))
+    for k, l in enumerate((l2, am, ls)):
+        o = net.AddOutputLayer(k, "out%d" % k)
+        l.GetOutputSlot(0).Connect(o.GetInputSlot(0))
+    return net, shape
+
+
+@needs_plugin
+@pytest.mark.gpu
+def test_l2_normalization_arg_max_log_softmax_through_the_runtime_match_cpuref():
+    from armnn_b200 import network
+    net, shape = _rows_net()
+    x = np.random.default_rng(37).integers(-128, 128, size=shape).astype(np.int8)
+    ref = hostnet.ArmnnNetwork(net, "CpuRef").run({0: x})
+    got = hostnet.ArmnnNetwork(net, "B200Acc").run({0: x})
+    rt = network.IRuntime.Create(0)
+    ln = rt.GetLoadedNetwork(rt.LoadNetwork(network.Optimize(net)))
+    ys = {k: np.zeros(ref[k].shape, ref[k].dtype) for k in (0, 1, 2)}
+    ln.EnqueueWorkload({0: x}, ys)
+    assert ref[1].dtype == np.int32
+    for k in (0, 1):
+        assert np.array_equal(ref[k], got[k]) and np.array_equal(ref[k], ys[k]), k
+    # logf / expf of the device against glibc: a rounding boundary may move by one step
+    for y in (got[2], ys[2]):
+        st = diff_stats(ref[2], y)
+        assert st["max_abs"] <= 1 and st["mismatch_frac"] <= 0.01, st
