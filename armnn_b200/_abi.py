@@ -80,6 +80,22 @@ class ArgMinMaxParams(C.Structure):
                 ("function", C.c_int32), ("out_int64", C.c_int32)]
 
 
+class GatherParams(C.Structure):
+    _fields_ = [("x", QTensor), ("y", QTensor), ("indices", C.c_void_p), ("outer", C.c_int32), ("axis_size", C.c_int32),
+                ("inner", C.c_int32), ("n_indices", C.c_int32)]
+
+
+class BatchNormParams(C.Structure):
+    _fields_ = [("x", QTensor), ("y", QTensor), ("mean", QTensor), ("variance", QTensor), ("beta", QTensor), ("gamma", QTensor),
+                ("n", C.c_int32), ("c", C.c_int32), ("hw", C.c_int64), ("nchw", C.c_int32), ("eps", C.c_float),
+                ("scratch", C.c_void_p)]
+
+
+class InstanceNormParams(C.Structure):
+    _fields_ = [("x", QTensor), ("y", QTensor), ("n", C.c_int32), ("c", C.c_int32), ("hw", C.c_int64), ("nchw", C.c_int32),
+                ("gamma", C.c_float), ("beta", C.c_float), ("eps", C.c_float)]
+
+
 class ConvertParams(C.Structure):
     _fields_ = [("x", QTensor), ("y", QTensor), ("count", C.c_int64)]
 
@@ -158,6 +174,9 @@ KERNEL_ENTRY_POINTS = {
     "log_softmax_q": SoftmaxParams,
     "l2_normalization_q": SoftmaxParams,
     "arg_min_max_q": ArgMinMaxParams,
+    "gather_q": GatherParams,
+    "batch_norm_q": BatchNormParams,
+    "instance_norm_q": InstanceNormParams,
     "convert_q": ConvertParams,
     "qlstm_step": QLstmParams,
     "pad_q": PadParams,

@@ -147,6 +147,19 @@ class ArmnnNetwork:
                 lid = lib.armnnc_add_elementwise_binary(net, int(d["op"]))
             elif t == "BatchMatMul":
                 lid = lib.armnnc_add_batch_matmul(net, int(d["tx"]), int(d["ty"]), int(d.get("ax", False)), int(d.get("ay", False)))
+            elif t == "Gather":
+                lid = lib.armnnc_add_gather(net, d["axis"])
+            elif t == "BatchNormalization":
+                keys = ("mean", "variance", "beta", "gamma")
+                arrs = [np.ascontiguousarray(np.asarray(layer.bn_params[k][0]).astype(_NP_DTYPE[layer.bn_params[k][1].dtype])) for k in keys]
+                infos = [layer.bn_params[k][1] for k in keys]
+                self._keep = getattr(self, "_keep", []) + arrs
+                lid = lib.armnnc_add_batch_norm(
+                    net, C.c_float(d["eps"]), int(d["nchw"]), int(arrs[0].size),
+                    (C.c_int32 * 4)(*[_ABI_DTYPE[i.dtype] for i in infos]), (C.c_float * 4)(*[i.scale for i in infos]),
+                    (C.c_int32 * 4)(*[i.offset for i in infos]), (C.c_void_p * 4)(*[a.ctypes.data for a in arrs]))
+            elif t == "InstanceNormalization":
+                lid = lib.armnnc_add_instance_norm(net, C.c_float(d["gamma"]), C.c_float(d["beta"]), C.c_float(d["eps"]), int(d["nchw"]))
             elif t == "LogSoftmax":
                 lid = lib.armnnc_add_log_softmax(net, C.c_float(d["beta"]), d["axis"])
             elif t == "L2Normalization":

@@ -247,6 +247,16 @@ public:
                 if (infos[0].GetDataType() == DataType::QSymmS16 && type == LayerType::LogSoftmax) { return No(reason, "QSymmS16 is not supported"); }
                 if (type == LayerType::L2Normalization && infos[0].GetNumDimensions() > 4) { return No(reason, "rank > 4"); }
                 return (IsActType(infos[0]) && infos[1].GetDataType() == infos[0].GetDataType()) || No(reason, "unsupported or mismatched data types");
+            case LayerType::Gather:
+                if (infos[1].GetDataType() != DataType::Signed32) { return No(reason, "indices must be Signed32"); }
+                return (IsMoveType(infos[0]) && infos[2].GetDataType() == infos[0].GetDataType()) || No(reason, "unsupported or mismatched data types");
+            case LayerType::BatchNormalization:
+                if (infos[0].GetNumDimensions() != 4) { return No(reason, "4-D tensors only"); }
+                for (const TensorInfo& t : infos) { if (!IsActType(t)) { return No(reason, "unsupported data type"); } }
+                return true;
+            case LayerType::InstanceNormalization:
+                return (infos[0].GetNumDimensions() == 4 && infos[0].GetDataType() == DataType::Float32 && infos[1].GetDataType() == DataType::Float32) ||
+                       No(reason, "4-D Float32 tensors only");
             case LayerType::ArgMinMax:
                 if (infos[1].GetDataType() != DataType::Signed32 && infos[1].GetDataType() != DataType::Signed64) { return No(reason, "the output must be Signed32 or Signed64"); }
                 return IsActType(infos[0]) || No(reason, "unsupported input data type");

@@ -1133,6 +1133,76 @@ std::unique_ptr<IWorkload> B200WorkloadFactory::CreateWorkload(LayerType type, c
                 B200CheckStatus(b200k_softmax_q8(&st->p, s));
             });
         }
+        case LayerType::Gather:
+        {
+            const auto& qd = *PolymorphicDowncast<const GatherQueueDescriptor*>(&d);
+            auto st = std::make_shared<SimpleState<b200k_gather_params>>(ctx);
+            std::memset(&st->p, 0, sizeof(st->p));
+            st->p.x = Operand(info.m_InputTensorInfos[0], st->blobs); st->p.y = Operand(info.m_OutputTensorInfos[0], st->blobs);
+            RowsOf(info.m_InputTensorInfos[0].GetShape(), qd.m_Parameters.m_Axis, st->p.outer, st->p.axis_size, st->p.inner);
+            st->p.n_indices = static_cast<int32_t>(info.m_InputTensorInfos[1].GetNumElements());
+            if (info.m_OutputTensorInfos[0].GetNumElements() !=
+                static_cast<unsigned int>(st->p.outer) * static_cast<unsigned int>(st->p.n_indices) * static_cast<unsigned int>(st->p.inner))
+            {
+                throw InvalidArgumentException("B200Acc: Gather output shape does not match the gathered input");
+            }
+            return Make<GatherQueueDescriptor>(d, info, ctx, [st](const GatherQueueDescriptor& data, cudaStream_t s)
+            {
+                st->p.x.data = Dev(data.m_Inputs[0]); st->p.indices = static_cast<const int32_t*>(Dev(data.m_Inputs[1]));
+                st->p.y.data = Dev(data.m_Outputs[0]);
+                B200CheckStatus(b200k_gather_q(&st->p, s));
+            });
+        }
+        case LayerType::BatchNormalization:
+        {
+            // the descriptor's constant handles are only valid during workload creation: the workload owns device copies
+            const auto& qd = *PolymorphicDowncast<const BatchNormalizationQueueDescriptor*>(&d);
+            auto st = std::make_shared<SimpleState<b200k_batch_norm_params>>(ctx);
+            b200k_batch_norm_params& p = st->p;
+            std::memset(&p, 0, sizeof(p));
+            const TensorInfo& x = info.m_InputTensorInfos[0];
+            if (x.GetNumDimensions() != 4 || !qd.m_Mean || !qd.m_Variance || !qd.m_Beta || !qd.m_Gamma) { throw InvalidArgumentException("B200Acc: BatchNormalization needs a 4-D input and four parameter tensors"); }
+            p.x = Operand(x, st->blobs); p.y = Operand(info.m_OutputTensorInfos[0], st->blobs);
+            p.nchw = qd.m_Parameters.m_DataLayout == DataLayout::NCHW ? 1 : 0;
+            p.n = static_cast<int32_t>(x.GetShape()[0]);
+            p.c = static_cast<int32_t>(p.nchw ? x.GetShape()[1] : x.GetShape()[3]);
+            p.hw = p.nchw ? static_cast<int64_t>(x.GetShape()[2]) * x.GetShape()[3] : static_cast<int64_t>(x.GetShape()[1]) * x.GetShape()[2];
+            p.eps = qd.m_Parameters.m_Eps;
+            auto constant = [&](const ConstTensorHandle* t)
+            {
+                if (t->GetTensorInfo().GetNumElements() != static_cast<unsigned int>(p.c)) { throw InvalidArgumentException("B200Acc: BatchNormalization parameters must hold one value per channel"); }
+                b200k_qtensor q = Operand(t->GetTensorInfo(), st->blobs);
+                q.data = st->blobs.Upload(t->GetConstTensor<void>(), t->GetTensorInfo().GetNumBytes());
+                return q;
+            };
+            p.mean = constant(qd.m_Mean); p.variance = constant(qd.m_Variance); p.beta = constant(qd.m_Beta); p.gamma = constant(qd.m_Gamma);
+            p.scratch = st->blobs.Alloc(2 * static_cast<size_t>(p.c) * sizeof(float));
+            return Make<BatchNormalizationQueueDescriptor>(d, info, ctx, [st](const BatchNormalizationQueueDescriptor& data, cudaStream_t s)
+            {
+                st->p.x.data = Dev(data.m_Inputs[0]); st->p.y.data = Dev(data.m_Outputs[0]);
+                B200CheckStatus(b200k_batch_norm_q(&st->p, s));
+            });
+        }
+        case LayerType::InstanceNormalization:
+        {
+            const auto& qd = *PolymorphicDowncast<const InstanceNormalizationQueueDescriptor*>(&d);
+            auto st = std::make_shared<SimpleState<b200k_instance_norm_params>>(ctx);
+            b200k_instance_norm_params& p = st->p;
+            std::memset(&p, 0, sizeof(p));
+            const TensorInfo& x = info.m_InputTensorInfos[0];
+            if (x.GetNumDimensions() != 4) { throw InvalidArgumentException("B200Acc: InstanceNormalization needs a 4-D input"); }
+            p.x = Operand(x, st->blobs); p.y = Operand(info.m_OutputTensorInfos[0], st->blobs);
+            p.nchw = qd.m_Parameters.m_DataLayout == DataLayout::NCHW ? 1 : 0;
+            p.n = static_cast<int32_t>(x.GetShape()[0]);
+            p.c = static_cast<int32_t>(p.nchw ? x.GetShape()[1] : x.GetShape()[3]);
+            p.hw = p.nchw ? static_cast<int64_t>(x.GetShape()[2]) * x.GetShape()[3] : static_cast<int64_t>(x.GetShape()[1]) * x.GetShape()[2];
+            p.gamma = qd.m_Parameters.m_Gamma; p.beta = qd.m_Parameters.m_Beta; p.eps = qd.m_Parameters.m_Eps;
+            return Make<InstanceNormalizationQueueDescriptor>(d, info, ctx, [st](const InstanceNormalizationQueueDescriptor& data, cudaStream_t s)
+            {
+                st->p.x.data = Dev(data.m_Inputs[0]); st->p.y.data = Dev(data.m_Outputs[0]);
+                B200CheckStatus(b200k_instance_norm_q(&st->p, s));
+            });
+        }
         case LayerType::LogSoftmax:
         {
             const auto& qd = *PolymorphicDowncast<const LogSoftmaxQueueDescriptor*>(&d);

@@ -110,6 +110,9 @@ extern "C" size_t b200k_sizeof_params(int which)
         case 13: return sizeof(b200k_reduce_params);
         case 14: return sizeof(b200k_unary_params);
         case 15: return sizeof(b200k_arg_min_max_params);
+        case 16: return sizeof(b200k_gather_params);
+        case 17: return sizeof(b200k_batch_norm_params);
+        case 18: return sizeof(b200k_instance_norm_params);
         default: return 0;
     }
 }

@@ -72,9 +72,90 @@ __global__ void __launch_bounds__(256) view_rows_kernel(const ViewRowArgs a)
     ((uint4*)(a.y + d))[w] = ((const uint4*)(a.x + s))[w];
 }
 
+// Gather (src/backends/reference/workloads/Gather.cpp:16-94): y[o, j, k] = Q_y(deq_x(x[o, indices[j], k])); a negative
+// index counts from the end of the axis.  The reference throws on an index outside the axis; here such an index reads
+// nothing and stores the encoding of 0.0.
+struct GatherArgs {
+    QView x, y;
+    const int* indices;
+    long long axis, inner, n_idx, count;
+    int same, esize;
+};
+
+__global__ void __launch_bounds__(256) gather_kernel(const GatherArgs a)
+{
+    pdl_enter();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= a.count) return;
+    const long long k = i % a.inner, oj = i / a.inner;
+    const long long j = oj % a.n_idx, o = oj / a.n_idx;
+    long long idx = a.indices[j];
+    if (idx < 0) idx += a.axis;
+    if (idx < 0 || idx >= a.axis) { a.y.set(i, 0.0f); return; }
+    const long long s = (o * a.axis + idx) * a.inner + k;
+    if (a.same) {
+        if (a.esize == 1)      ((uint8_t*)a.y.data)[i] = ((const uint8_t*)a.x.data)[s];
+        else if (a.esize == 2) ((uint16_t*)a.y.data)[i] = ((const uint16_t*)a.x.data)[s];
+        else                   ((uint32_t*)a.y.data)[i] = ((const uint32_t*)a.x.data)[s];
+    } else {
+        a.y.set(i, a.x.get(s));
+    }
+}
+
+// rows of whole 16-byte words (an embedding table with equal quantisation on both sides)
+struct GatherRowArgs { const uint8_t* x; uint8_t* y; const int* indices; long long axis, n_idx, rows; int row16; };
+
+__global__ void __launch_bounds__(256) gather_rows_kernel(const GatherRowArgs a)
+{
+    pdl_enter();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= a.rows * a.row16) return;
+    const long long r = i / a.row16;
+    const int w = (int)(i - r * a.row16);
+    const long long j = r % a.n_idx, o = r / a.n_idx;
+    long long idx = a.indices[j];
+    if (idx < 0) idx += a.axis;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (idx >= 0 && idx < a.axis) v = ((const uint4*)a.x)[((o * a.axis + idx) * a.row16) + w];
+    ((uint4*)a.y)[i] = v;
+}
+
 }  // namespace b200k
 
 using namespace b200k;
+
+extern "C" int b200k_gather_q(const b200k_gather_params* p, void* stream)
+{
+    B200K_REQUIRE(p, B200K_E_INVALID, "gather_q: null params");
+    B200K_REQUIRE(p->x.data && p->y.data && p->indices, B200K_E_INVALID, "gather_q: null tensor pointer");
+    B200K_REQUIRE(p->outer > 0 && p->axis_size > 0 && p->inner > 0 && p->n_indices >= 0, B200K_E_INVALID, "gather_q: bad shape");
+    B200K_REQUIRE(p->x.dtype >= B200K_U8 && p->x.dtype <= B200K_F32, B200K_E_INVALID, "gather_q: unknown element type");
+    B200K_REQUIRE(p->x.dtype == p->y.dtype, B200K_E_UNSUPPORTED, "gather_q: input and output types differ (%d, %d)", p->x.dtype, p->y.dtype);
+    const long long count = (long long)p->outer * p->n_indices * p->inner;
+    if (count == 0) return B200K_OK;
+    const bool quantised = p->x.dtype == B200K_U8 || p->x.dtype == B200K_S8 || p->x.dtype == B200K_S16;
+    const bool same = !quantised || (p->x.scale == p->y.scale && p->x.zero_point == p->y.zero_point);
+    const int es = elem_size(p->x.dtype);
+    cudaStream_t s = (cudaStream_t)stream;
+    const long long row_bytes = (long long)p->inner * es;
+    // the zero fill of an out-of-range index is only the encoding of 0.0 when the zero point is 0
+    if (same && row_bytes % 16 == 0 && (uintptr_t)p->x.data % 16 == 0 && (uintptr_t)p->y.data % 16 == 0 &&
+        (!quantised || p->y.zero_point == 0) && row_bytes / 16 <= 0x7fffffff) {
+        GatherRowArgs a;
+        a.x = (const uint8_t*)p->x.data; a.y = (uint8_t*)p->y.data; a.indices = p->indices;
+        a.axis = p->axis_size; a.n_idx = p->n_indices; a.rows = (long long)p->outer * p->n_indices;
+        a.row16 = (int)(row_bytes / 16);
+        launch_pdl(gather_rows_kernel, dim3(div_up(a.rows * a.row16, 256)), dim3(256), 0, s, a);
+        return check_launch("gather_rows_kernel");
+    }
+    GatherArgs a;
+    memset(&a, 0, sizeof(a));
+    a.x = make_view(p->x); a.y = make_view(p->y); a.indices = p->indices;
+    a.axis = p->axis_size; a.inner = p->inner; a.n_idx = p->n_indices; a.count = count;
+    a.same = same ? 1 : 0; a.esize = es;
+    launch_pdl(gather_kernel, dim3(div_up(count, 256)), dim3(256), 0, s, a);
+    return check_launch("gather_kernel");
+}
 
 extern "C" int b200k_view_copy_q(const b200k_view_copy_params* p, void* stream)
 {

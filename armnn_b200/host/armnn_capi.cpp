@@ -224,6 +224,38 @@ int armnnc_add_elementwise_binary(void* vn, int op)
     return add_layer(n, n->net->AddElementwiseBinaryLayer(ElementwiseBinaryDescriptor(static_cast<BinaryOperation>(op))));
 }
 
+int armnnc_add_gather(void* vn, int axis)
+{
+    auto* n = static_cast<CNet*>(vn);
+    GatherDescriptor d; d.m_Axis = axis;
+    return add_layer(n, n->net->AddGatherLayer(d));
+}
+
+/// dtypes / scales / zps / data: mean, variance, beta, gamma (one value per channel each, copied).
+int armnnc_add_batch_norm(void* vn, float eps, int nchw, int channels, const int32_t* dtypes, const float* scales,
+                          const int32_t* zps, const void* const* data)
+{
+    auto* n = static_cast<CNet*>(vn);
+    BatchNormalizationDescriptor d; d.m_Eps = eps; d.m_DataLayout = nchw ? DataLayout::NCHW : DataLayout::NHWC;
+    std::vector<ConstTensor> ts;
+    const int32_t shape[1] = {channels};
+    for (int i = 0; i < 4; ++i)
+    {
+        TensorInfo info = info_from(dtypes[i], 1, shape, scales[i], zps[i], nullptr, 0, 0, true);
+        n->blobs.emplace_back((const uint8_t*)data[i], (const uint8_t*)data[i] + info.GetNumBytes());
+        ts.emplace_back(info, n->blobs.back().data());
+    }
+    return add_layer(n, n->net->AddBatchNormalizationLayer(d, ts[0], ts[1], ts[2], ts[3]));
+}
+
+int armnnc_add_instance_norm(void* vn, float gamma, float beta, float eps, int nchw)
+{
+    auto* n = static_cast<CNet*>(vn);
+    InstanceNormalizationDescriptor d; d.m_Gamma = gamma; d.m_Beta = beta; d.m_Eps = eps;
+    d.m_DataLayout = nchw ? DataLayout::NCHW : DataLayout::NHWC;
+    return add_layer(n, n->net->AddInstanceNormalizationLayer(d));
+}
+
 int armnnc_add_log_softmax(void* vn, float beta, int axis)
 {
     auto* n = static_cast<CNet*>(vn);

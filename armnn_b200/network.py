@@ -340,6 +340,21 @@ class INetwork:
     def AddDequantizeLayer(self, name=None):
         return self._add(Layer("Dequantize", name, 1, 1))
 
+    def AddGatherLayer(self, axis=0, name=None):
+        """armnn::GatherDescriptor: input 0 the tensor, input 1 the Signed32 indices."""
+        return self._add(Layer("Gather", name, 2, 1, {"axis": int(axis)}))
+
+    def AddBatchNormalizationLayer(self, eps, mean, variance, beta, gamma, nchw=False, name=None):
+        """armnn::INetwork::AddBatchNormalizationLayer: mean, variance, beta, gamma are (ndarray, TensorInfo) pairs of one
+        value per channel."""
+        layer = self._add(Layer("BatchNormalization", name, 1, 1, {"eps": float(eps), "nchw": bool(nchw)}))
+        layer.bn_params = {"mean": mean, "variance": variance, "beta": beta, "gamma": gamma}
+        return layer
+
+    def AddInstanceNormalizationLayer(self, gamma=1.0, beta=0.0, eps=1e-12, nchw=False, name=None):
+        return self._add(Layer("InstanceNormalization", name, 1, 1, {"gamma": float(gamma), "beta": float(beta), "eps": float(eps),
+                                                                      "nchw": bool(nchw)}))
+
     def AddQLstmLayer(self, descriptor, params, name=None):
         """descriptor: dict of armnn::QLstmDescriptor fields; params: dict name -> (ndarray, TensorInfo) of the
         LstmInputParams members.  Inputs: input, outputStateIn, cellStateIn.  Outputs: outputStateOut,
@@ -408,6 +423,22 @@ def IsLayerSupported(layer):
             return False, "%s: unsupported or mismatched data types" % t
         if t == "L2Normalization" and len(ins[0].shape) > 4:
             return False, "L2Normalization: rank > 4"
+        return True, ""
+    if t == "Gather":
+        ok = (DataType.QAsymmU8, DataType.QAsymmS8, DataType.QSymmS16, DataType.Float32, DataType.Signed32)
+        if ins[0].dtype not in ok or outs[0].dtype != ins[0].dtype or ins[1].dtype != DataType.Signed32:
+            return False, "Gather: one supported element type for input and output, Signed32 indices"
+        return True, ""
+    if t == "BatchNormalization":
+        ok = (DataType.QAsymmU8, DataType.QAsymmS8, DataType.QSymmS16, DataType.Float32)
+        if ins[0].dtype not in ok or outs[0].dtype not in ok or len(ins[0].shape) != 4:
+            return False, "BatchNormalization: 4-D tensors of a supported data type only"
+        if any(info.dtype not in ok for _, info in layer.bn_params.values()):
+            return False, "BatchNormalization: unsupported parameter data type"
+        return True, ""
+    if t == "InstanceNormalization":
+        if ins[0].dtype != DataType.Float32 or outs[0].dtype != DataType.Float32 or len(ins[0].shape) != 4:
+            return False, "InstanceNormalization: 4-D Float32 tensors only (as in the reference)"
         return True, ""
     if t == "ArgMinMax":
         if ins[0].dtype not in (DataType.QAsymmU8, DataType.QAsymmS8, DataType.QSymmS16, DataType.Float32):
@@ -902,6 +933,49 @@ class GraphProgram:
             raise InvalidArgumentException("ArgMinMax: output shape %s does not drop the axis of %s" % (y.info.shape, x.info.shape))
         p.function, p.out_int64 = layer.desc["function"], 0
         return "arg_min_max_q", p
+
+    def _make_Gather(self, layer):
+        x, idx, y = layer.inputs[0].source, layer.inputs[1].source, layer.outputs[0]
+        p = _abi.GatherParams()
+        p.x, p.y = self._operand(x), self._operand(y)
+        p.indices = self._ptr(self._dev(idx))
+        p.outer, p.axis_size, p.inner = self._rows(x, layer.desc["axis"])
+        p.n_indices = idx.info.GetNumElements()
+        if y.info.GetNumElements() != p.outer * p.n_indices * p.inner:
+            raise InvalidArgumentException("Gather: output shape %s does not match input %s gathered with %s indices"
+                                           % (y.info.shape, x.info.shape, idx.info.shape))
+        return "gather_q", p
+
+    @staticmethod
+    def _planes(info, nchw):
+        n, a, b, c = info.shape
+        return (n, a, b * c) if nchw else (n, c, a * b)          # (batch, channels, pixels per plane)
+
+    def _make_BatchNormalization(self, layer):
+        x, y = layer.inputs[0].source, layer.outputs[0]
+        p = _abi.BatchNormParams()
+        p.x, p.y = self._operand(x), self._operand(y)
+        p.n, p.c, p.hw = self._planes(x.info, layer.desc["nchw"])
+        p.nchw, p.eps = int(layer.desc["nchw"]), layer.desc["eps"]
+        for key in ("mean", "variance", "beta", "gamma"):
+            data, info = layer.bn_params[key]
+            if info.GetNumElements() != p.c:
+                raise InvalidArgumentException("BatchNormalization: %s must hold one value per channel" % key)
+            dev = self._upload(np.ascontiguousarray(np.asarray(data).astype(_NP_DTYPE[info.dtype])))
+            self.aux.append(dev)
+            setattr(p, key, _qt(info, self._ptr(dev), None))
+        scratch = self._upload(np.zeros(2 * p.c, np.float32))
+        self.aux.append(scratch)
+        p.scratch = self._ptr(scratch)
+        return "batch_norm_q", p
+
+    def _make_InstanceNormalization(self, layer):
+        x, y, d = layer.inputs[0].source, layer.outputs[0], layer.desc
+        p = _abi.InstanceNormParams()
+        p.x, p.y = self._operand(x), self._operand(y)
+        p.n, p.c, p.hw = self._planes(x.info, d["nchw"])
+        p.nchw, p.gamma, p.beta, p.eps = int(d["nchw"]), d["gamma"], d["beta"], d["eps"]
+        return "instance_norm_q", p
 
     def _make_convert(self, layer):
         x, y = layer.inputs[0].source, layer.outputs[0]

@@ -358,6 +358,49 @@ typedef struct {
 
 int b200k_resize_q(const b200k_resize_params* p, void* stream);
 
+/* armnn::Gather (src/backends/reference/workloads/Gather.cpp:16-94): with x seen as [outer, axis_size, inner],
+ *     y[o, j, k] = Q_y(deq_x(x[o, indices[j], k]))        0 <= j < n_indices
+ * indices: device int32 (Signed32 tensor), a negative one counts from the end of the axis.  The reference throws on an
+ * index outside the axis (its workload, RefGatherWorkload.cpp:40-47, on any negative index); here that position of y holds the
+ * encoding of 0.0 and nothing is read. */
+typedef struct {
+    b200k_qtensor x, y;
+    const int32_t* indices;
+    int32_t outer, axis_size, inner, n_indices;
+} b200k_gather_params;
+
+int b200k_gather_q(const b200k_gather_params* p, void* stream);
+
+/* ---- BatchNormalization, InstanceNormalization ------------------------------------------------ */
+
+/* armnn::BatchNormImpl (src/backends/reference/workloads/BatchNormImpl.cpp:16-63): per channel
+ *     mult = gamma / sqrt(variance + eps), add = beta - mult * mean, y = Q_y(mult * deq_x(x) + add)
+ * on a tensor [n, hw, c] (nchw = 0) or [n, c, hw] (nchw = 1); mean, variance, beta, gamma: [c] tensors of any supported
+ * type.  scratch: 2 * c floats of device memory the call may overwrite (the per-channel constants). */
+typedef struct {
+    b200k_qtensor x, y, mean, variance, beta, gamma;
+    int32_t n, c;
+    int64_t hw;
+    int32_t nchw;
+    float eps;
+    void* scratch;
+} b200k_batch_norm_params;
+
+int b200k_batch_norm_q(const b200k_batch_norm_params* p, void* stream);
+
+/* armnn::InstanceNorm (src/backends/reference/workloads/InstanceNorm.cpp:16-84): per (batch, channel) plane the mean and
+ * the (biased) variance over hw, summed in row-major order, then y = (x - mean) * gamma / sqrt(var + eps) + beta.
+ * Float32 tensors only, as in the reference (InstanceNormalizationQueueDescriptor::Validate). */
+typedef struct {
+    b200k_qtensor x, y;
+    int32_t n, c;
+    int64_t hw;
+    int32_t nchw;
+    float gamma, beta, eps;
+} b200k_instance_norm_params;
+
+int b200k_instance_norm_q(const b200k_instance_norm_params* p, void* stream);
+
 /* ---- Softmax --------------------------------------------------------------------------------- */
 
 /* armnn::Softmax (src/backends/reference/workloads/Softmax.cpp:17-70): softmax over the axis of
@@ -457,7 +500,7 @@ unsigned long long b200k_kernel_launches(void);
 
 /* sizeof() of a parameter struct as compiled into the library, for bindings in other languages to check their
  * own declarations: 0 conv2d, 1 fc, 2 bmm, 3 pool2d, 4 mean, 5 eltwise, 6 activation, 7 softmax, 8 convert,
- * 9 qlstm, 10 pad, 11 view_copy, 12 resize, 13 reduce, 14 unary, 15 arg_min_max.  No counterpart in the reference (its backends are linked as C++). */
+ * 9 qlstm, 10 pad, 11 view_copy, 12 resize, 13 reduce, 14 unary, 15 arg_min_max, 16 gather, 17 batch_norm, 18 instance_norm.  No counterpart in the reference (its backends are linked as C++). */
 size_t b200k_sizeof_params(int which);
 
 #ifdef __cplusplus

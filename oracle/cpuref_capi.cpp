@@ -341,6 +341,69 @@ extern "C" int cpuref_activation_q8(const b200k_activation_params* p)
     });
 }
 
+extern "C" int cpuref_gather_q(const b200k_gather_params* p)
+{
+    return guarded([&] {
+        Harness h;
+        TensorInfo xi = make_info(p->x, TensorShape({(unsigned)p->outer, (unsigned)p->axis_size, (unsigned)p->inner}), 0, 0, false);
+        TensorInfo ii(TensorShape({(unsigned)p->n_indices}), DataType::Signed32);
+        TensorInfo yi = make_info(p->y, TensorShape({(unsigned)p->outer, (unsigned)p->n_indices, (unsigned)p->inner}), 0, 0, false);
+        GatherQueueDescriptor d;
+        d.m_Parameters.m_Axis = 1;
+        h.in(d, xi, p->x.data);
+        h.in(d, ii, p->indices);
+        auto* o = h.out(d, yi);
+        h.run(LayerType::Gather, d);
+        copy_out(o, const_cast<void*>(p->y.data), yi.GetNumBytes());
+    });
+}
+
+extern "C" int cpuref_batch_norm_q(const b200k_batch_norm_params* p)
+{
+    return guarded([&] {
+        Harness h;
+        TensorShape s = p->nchw ? TensorShape({(unsigned)p->n, (unsigned)p->c, 1u, (unsigned)p->hw})
+                                : TensorShape({(unsigned)p->n, 1u, (unsigned)p->hw, (unsigned)p->c});
+        TensorInfo xi = make_info(p->x, s, 0, 0, false);
+        TensorInfo yi = make_info(p->y, s, 0, 0, false);
+        BatchNormalizationQueueDescriptor d;
+        d.m_Parameters.m_Eps = p->eps;
+        d.m_Parameters.m_DataLayout = p->nchw ? DataLayout::NCHW : DataLayout::NHWC;
+        TensorShape cs({(unsigned)p->c});
+        auto constant = [&](const b200k_qtensor& t) {
+            TensorInfo ti = make_info(t, cs, 0, 0, true);
+            auto handle = std::make_unique<ScopedTensorHandle>(ti);
+            handle->Allocate();
+            std::memcpy(handle->GetTensor<void>(), t.data, ti.GetNumBytes());
+            return handle;
+        };
+        auto mean = constant(p->mean), var = constant(p->variance), beta = constant(p->beta), gamma = constant(p->gamma);
+        d.m_Mean = mean.get(); d.m_Variance = var.get(); d.m_Beta = beta.get(); d.m_Gamma = gamma.get();
+        h.in(d, xi, p->x.data);
+        auto* o = h.out(d, yi);
+        h.run(LayerType::BatchNormalization, d);
+        copy_out(o, const_cast<void*>(p->y.data), yi.GetNumBytes());
+    });
+}
+
+extern "C" int cpuref_instance_norm_q(const b200k_instance_norm_params* p)
+{
+    return guarded([&] {
+        Harness h;
+        TensorShape s = p->nchw ? TensorShape({(unsigned)p->n, (unsigned)p->c, 1u, (unsigned)p->hw})
+                                : TensorShape({(unsigned)p->n, 1u, (unsigned)p->hw, (unsigned)p->c});
+        TensorInfo xi = make_info(p->x, s, 0, 0, false);
+        TensorInfo yi = make_info(p->y, s, 0, 0, false);
+        InstanceNormalizationQueueDescriptor d;
+        d.m_Parameters.m_Gamma = p->gamma; d.m_Parameters.m_Beta = p->beta; d.m_Parameters.m_Eps = p->eps;
+        d.m_Parameters.m_DataLayout = p->nchw ? DataLayout::NCHW : DataLayout::NHWC;
+        h.in(d, xi, p->x.data);
+        auto* o = h.out(d, yi);
+        h.run(LayerType::InstanceNormalization, d);
+        copy_out(o, const_cast<void*>(p->y.data), yi.GetNumBytes());
+    });
+}
+
 extern "C" int cpuref_softmax_q8(const b200k_softmax_params* p)
 {
     return guarded([&] {

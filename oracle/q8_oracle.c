@@ -635,6 +635,78 @@ int oracle_arg_min_max_q(const b200k_arg_min_max_params* p)
     return 0;
 }
 
+/* ---- Gather, Gather.cpp:16-94 --------------------------------------------------------------------
+ * An index outside the axis makes the reference throw; here it yields the encoding of 0.0 (what the CUDA path stores). */
+
+int oracle_gather_q(const b200k_gather_params* p)
+{
+    if (!p->x.data || !p->y.data || !p->indices) return B200K_E_INVALID;
+    int64_t out = 0;
+    for (int o = 0; o < p->outer; ++o)
+    for (int j = 0; j < p->n_indices; ++j) {
+        int64_t idx = p->indices[j];
+        if (idx < 0) idx += p->axis_size;
+        for (int k = 0; k < p->inner; ++k, ++out) {
+            if (idx < 0 || idx >= p->axis_size) { store_f(&p->y, out, 0.0f); continue; }
+            store_f(&p->y, out, load_f(&p->x, ((int64_t)o * p->axis_size + idx) * p->inner + k));
+        }
+    }
+    return 0;
+}
+
+/* ---- BatchNormalization, BatchNormImpl.cpp:16-63 -------------------------------------------------- */
+
+int oracle_batch_norm_q(const b200k_batch_norm_params* p)
+{
+    if (!p->x.data || !p->y.data) return B200K_E_INVALID;
+    for (int c = 0; c < p->c; ++c) {
+        const float mean = load_f(&p->mean, c), var = load_f(&p->variance, c), beta = load_f(&p->beta, c), gamma = load_f(&p->gamma, c);
+        volatile float ve = var + p->eps;
+        const float mult = gamma / sqrtf(ve);
+        volatile float mm = mult * mean;
+        const float add = beta - mm;
+        for (int n = 0; n < p->n; ++n)
+        for (int64_t k = 0; k < p->hw; ++k) {
+            const int64_t at = p->nchw ? ((int64_t)n * p->c + c) * p->hw + k : ((int64_t)n * p->hw + k) * p->c + c;
+            volatile float m = mult * load_f(&p->x, at);
+            volatile float r = m + add;
+            store_f(&p->y, at, r);
+        }
+    }
+    return 0;
+}
+
+/* ---- InstanceNormalization, InstanceNorm.cpp:16-84 ------------------------------------------------ */
+
+int oracle_instance_norm_q(const b200k_instance_norm_params* p)
+{
+    if (!p->x.data || !p->y.data) return B200K_E_INVALID;
+    for (int n = 0; n < p->n; ++n)
+    for (int c = 0; c < p->c; ++c) {
+        const int64_t base = p->nchw ? ((int64_t)n * p->c + c) * p->hw : (int64_t)n * p->hw * p->c + c;
+        const int64_t step = p->nchw ? 1 : p->c;
+        volatile float mean = 0, var = 0;
+        for (int64_t k = 0; k < p->hw; ++k) mean = mean + load_f(&p->x, base + k * step);
+        mean = mean / (float)p->hw;
+        for (int64_t k = 0; k < p->hw; ++k) {
+            volatile float d = load_f(&p->x, base + k * step) - mean;
+            volatile float sq = d * d;
+            var = var + sq;
+        }
+        var = var / (float)p->hw;
+        volatile float ve = var + p->eps;
+        const float root = sqrtf(ve);
+        for (int64_t k = 0; k < p->hw; ++k) {
+            volatile float d = load_f(&p->x, base + k * step) - mean;
+            volatile float g = d * p->gamma;
+            volatile float q = g / root;
+            volatile float r = q + p->beta;
+            store_f(&p->y, base + k * step, r);
+        }
+    }
+    return 0;
+}
+
 /* ---- Quantize / Dequantize / requantize, RefQuantizeWorkload.cpp:14-45, Dequantize.cpp:11-28 - */
 
 int oracle_convert_q(const b200k_convert_params* p)

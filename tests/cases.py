@@ -372,6 +372,91 @@ def rows_cases():
 TRANSCENDENTAL_ROWS = ("log_softmax_classifier_1001", "log_softmax_u8_inner_axis", "log_softmax_float")
 
 
+def norm_cases():
+    """Gather, BatchNormalization and InstanceNormalization."""
+    def gather(seed, outer, axis, inner, n_idx, dtype=S8, requant=False, negative=False):
+        def build(mem):
+            rng = np.random.default_rng(seed)
+            p = _abi.GatherParams()
+            xq = (0.05, 0) if dtype != F32 else (1.0, 0)
+            yq = (0.07, 5) if requant else xq
+            if dtype == F32:
+                p.x = qt(mem, rng.standard_normal((outer, axis, inner)).astype(np.float32), F32)
+            else:
+                p.x = qt(mem, _rand(rng, dtype, (outer, axis, inner)), dtype, *xq)
+            idx = rng.integers(-axis if negative else 0, axis, size=(n_idx,)).astype(np.int32)
+            p.indices = mem.inp(idx)
+            p.y, y = qt_out(mem, (outer, n_idx, inner), dtype, *yq)
+            p.outer, p.axis_size, p.inner, p.n_indices = outer, axis, inner, n_idx
+            return p, [y]
+        return lambda: SimpleCase("gather_q", build)
+
+    def batch_norm(seed, n, c, hw, nchw=False, dtype=S8, param_dtype=None):
+        def build(mem):
+            rng = np.random.default_rng(seed)
+            p = _abi.BatchNormParams()
+            pd = dtype if param_dtype is None else param_dtype
+            shape = (n, c, hw) if nchw else (n, hw, c)
+            if dtype == F32:
+                p.x = qt(mem, rng.standard_normal(shape).astype(np.float32), F32)
+                p.y, y = qt_out(mem, shape, F32)
+            else:
+                p.x = qt(mem, _rand(rng, dtype, shape), dtype, 0.05, 3 if dtype == S8 else 120)
+                p.y, y = qt_out(mem, shape, dtype, 0.04, -5 if dtype == S8 else 110)
+            if pd == F32:
+                p.mean = qt(mem, rng.standard_normal(c).astype(np.float32), F32)
+                p.variance = qt(mem, (rng.random(c) * 2 + 0.1).astype(np.float32), F32)
+                p.beta = qt(mem, rng.standard_normal(c).astype(np.float32), F32)
+                p.gamma = qt(mem, (rng.standard_normal(c) + 1).astype(np.float32), F32)
+            else:
+                lo = RANGE_LO[pd]
+                p.mean = qt(mem, _rand(rng, pd, (c,)), pd, 0.02, lo + 128)
+                p.variance = qt(mem, _rand(rng, pd, (c,)), pd, 0.01, lo)            # never negative
+                p.beta = qt(mem, _rand(rng, pd, (c,)), pd, 0.02, lo + 100)
+                p.gamma = qt(mem, _rand(rng, pd, (c,)), pd, 0.01, lo + 20)
+            p.n, p.c, p.hw, p.nchw, p.eps = n, c, hw, int(nchw), 1e-3
+            _, p.scratch = mem.out((2 * c,), np.float32)
+            return p, [y]
+        return lambda: SimpleCase("batch_norm_q", build)
+
+    def instance_norm(seed, n, c, hw, nchw=False, dtype=S8, gamma=1.3, beta=-0.2):
+        def build(mem):
+            rng = np.random.default_rng(seed)
+            p = _abi.InstanceNormParams()
+            shape = (n, c, hw) if nchw else (n, hw, c)
+            if dtype == F32:
+                p.x = qt(mem, rng.standard_normal(shape).astype(np.float32), F32)
+                p.y, y = qt_out(mem, shape, F32)
+            else:
+                p.x = qt(mem, _rand(rng, dtype, shape), dtype, 0.05, 3 if dtype == S8 else 120)
+                p.y, y = qt_out(mem, shape, dtype, 0.03, 0 if dtype == S8 else 128)
+            p.n, p.c, p.hw, p.nchw = n, c, hw, int(nchw)
+            p.gamma, p.beta, p.eps = gamma, beta, 1e-5
+            return p, [y]
+        return lambda: SimpleCase("instance_norm_q", build)
+    return {
+        "gather_embedding_rows": gather(321, 1, 500, 64, 37),
+        "gather_axis1_requantise": gather(322, 3, 11, 5, 7, dtype=U8, requant=True),
+        "gather_negative_indices_s16": gather(323, 2, 9, 3, 12, dtype=S16, negative=True),
+        "gather_float_scalars": gather(324, 1, 40, 1, 25, dtype=F32),
+        "gather_float_rows_aligned": gather(325, 2, 30, 8, 9, dtype=F32, negative=True),
+        "batch_norm_nhwc": batch_norm(326, 2, 24, 35),
+        "batch_norm_nchw_u8": batch_norm(327, 2, 10, 49, nchw=True, dtype=U8),
+        "batch_norm_float": batch_norm(328, 3, 17, 20, dtype=F32),
+        "batch_norm_s8_float_parameters": batch_norm(329, 1, 32, 64, param_dtype=F32),
+        "instance_norm_nhwc": instance_norm(330, 2, 16, 13 * 11, dtype=F32),
+        "instance_norm_nchw": instance_norm(331, 2, 5, 100, nchw=True, dtype=F32),
+        "instance_norm_one_channel": instance_norm(332, 1, 1, 333, dtype=F32, gamma=0.7, beta=0.1),
+    }
+
+
+RANGE_LO = {U8: 0, S8: -128, S16: -32768}
+
+# RefGatherWorkload.cpp:40-47 throws on a negative index before armnn::Gather (Gather.cpp:55-57), which would wrap it,
+# runs: these cases have no CpuRef output and pin the wrapping against the restatement of Gather.cpp only
+CPUREF_REFUSES = {("norm", "gather_negative_indices_s16"), ("norm", "gather_float_rows_aligned")}
+
+
 def convert_cases():
     def make(seed, xd, yd, count=1001, xq=(0.05, 3), yq=(0.07, -4)):
         def build(mem):
@@ -683,7 +768,7 @@ def move_cases():
 ALL_GROUPS = {"conv": conv_cases, "dwconv": dwconv_cases, "fc": fc_cases, "bmm": bmm_cases, "pool": pool_cases,
               "mean": mean_cases, "eltwise": eltwise_cases, "activation": activation_cases, "softmax": softmax_cases,
               "convert": convert_cases, "pad": pad_cases, "qlstm": qlstm_cases, "move": move_cases, "resize": resize_cases, "reduce": reduce_cases, "tconv": tconv_cases, "f32": f32_cases, "unary": unary_cases,
-              "rows": rows_cases}
+              "rows": rows_cases, "norm": norm_cases}
 
 
 def run_case(case, where):

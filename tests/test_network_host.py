@@ -233,3 +233,14 @@ def test_l2_normalization_arg_max_log_softmax_graph_oracle_equals_armnn_cpuref(b
     assert want[1].dtype == np.int32
     for k in (0, 1, 2):
         assert want[k].shape == got[k].shape and np.array_equal(want[k], got[k]), k
+
+
+@needs_cpuref
+def test_gather_batch_norm_instance_norm_graph_oracle_equals_armnn_cpuref(built):
+    import hostnet
+    from test_plugin import _norm_inputs, _norm_net
+    net, xs = _norm_net(), _norm_inputs(44)
+    want = hostnet.ArmnnNetwork(net, "CpuRef").run(xs)
+    got = hostnet.OracleNetwork(Optimize(net)).run(xs)
+    for k in (0, 1):
+        assert want[k].shape == got[k].shape and np.array_equal(want[k], got[k]), k

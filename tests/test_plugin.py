@@ -859,3 +859,57 @@ def test_l2_normalization_arg_max_log_softmax_through_the_runtime_match_cpuref()
     for y in (got[2], ys[2]):
         st = diff_stats(ref[2], y)
         assert st["max_abs"] <= 1 and st["mismatch_frac"] <= 0.01, st
+
+
+def _norm_net():
+    """Gather over the batch axis of a quantised tensor -> BatchNormalization with quantised parameters; and
+    InstanceNormalization of a Float32 input."""
+    from armnn_b200.network import DataType, INetwork, TensorInfo
+    rng = np.random.default_rng(41)
+    net = INetwork.Create()
+    il = net.AddInputLayer(0, "table")
+    il.GetOutputSlot(0).SetTensorInfo(TensorInfo((6, 4, 5, 16), DataType.QAsymmS8, 0.05, -3))
+    ix = net.AddInputLayer(1, "indices")
+    ix.GetOutputSlot(0).SetTensorInfo(TensorInfo((3,), DataType.Signed32))
+    ga = net.AddGatherLayer(0, "gather")
+    il.GetOutputSlot(0).Connect(ga.GetInputSlot(0))
+    ix.GetOutputSlot(0).Connect(ga.GetInputSlot(1))
+    ga.GetOutputSlot(0).SetTensorInfo(TensorInfo((3, 4, 5, 16), DataType.QAsymmS8, 0.05, -3))
+
+    def param(lo, hi, scale, zp):
+        return rng.integers(lo, hi, size=(16,)).astype(np.int8), TensorInfo((16,), DataType.QAsymmS8, scale, zp)
+    bn = net.AddBatchNormalizationLayer(1e-3, param(-128, 128, 0.02, 0), param(-127, 128, 0.01, -128), param(-128, 128, 0.02, -28),
+                                        param(-128, 128, 0.01, -108), name="bn")
+    ga.GetOutputSlot(0).Connect(bn.GetInputSlot(0))
+    bn.GetOutputSlot(0).SetTensorInfo(TensorInfo((3, 4, 5, 16), DataType.QAsymmS8, 0.06, 4))
+    o0 = net.AddOutputLayer(0, "out")
+    bn.GetOutputSlot(0).Connect(o0.GetInputSlot(0))
+    fl = net.AddInputLayer(2, "image")
+    fl.GetOutputSlot(0).SetTensorInfo(TensorInfo((2, 7, 9, 5), DataType.Float32))
+    inl = net.AddInstanceNormalizationLayer(1.5, -0.25, 1e-5, name="instance_norm")
+    fl.GetOutputSlot(0).Connect(inl.GetInputSlot(0))
+    inl.GetOutputSlot(0).SetTensorInfo(TensorInfo((2, 7, 9, 5), DataType.Float32))
+    o1 = net.AddOutputLayer(1, "out_normalised")
+    inl.GetOutputSlot(0).Connect(o1.GetInputSlot(0))
+    return net
+
+
+def _norm_inputs(seed):
+    rng = np.random.default_rng(seed)
+    return {0: rng.integers(-128, 128, size=(6, 4, 5, 16)).astype(np.int8), 1: np.array([5, 0, 2], np.int32),
+            2: rng.standard_normal((2, 7, 9, 5)).astype(np.float32)}
+
+
+@needs_plugin
+@pytest.mark.gpu
+def test_gather_batch_norm_instance_norm_through_the_runtime_equal_cpuref():
+    from armnn_b200 import network
+    net, xs = _norm_net(), _norm_inputs(43)
+    ref = hostnet.ArmnnNetwork(net, "CpuRef").run(xs)
+    got = hostnet.ArmnnNetwork(net, "B200Acc").run(xs)
+    rt = network.IRuntime.Create(0)
+    ln = rt.GetLoadedNetwork(rt.LoadNetwork(network.Optimize(net)))
+    ys = {k: np.zeros(ref[k].shape, ref[k].dtype) for k in (0, 1)}
+    ln.EnqueueWorkload(xs, ys)
+    for k in (0, 1):
+        assert ref[k].shape == got[k].shape and np.array_equal(ref[k], got[k]) and np.array_equal(ref[k], ys[k]), k
