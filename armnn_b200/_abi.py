@@ -96,6 +96,12 @@ class InstanceNormParams(C.Structure):
                 ("gamma", C.c_float), ("beta", C.c_float), ("eps", C.c_float)]
 
 
+class NormalizationParams(C.Structure):
+    _fields_ = [("x", QTensor), ("y", QTensor), ("n", C.c_int32), ("c", C.c_int32), ("h", C.c_int32), ("w", C.c_int32),
+                ("nchw", C.c_int32), ("channel_type", C.c_int32), ("norm_size", C.c_uint32),
+                ("alpha", C.c_float), ("beta", C.c_float), ("kappa", C.c_float)]
+
+
 class ConvertParams(C.Structure):
     _fields_ = [("x", QTensor), ("y", QTensor), ("count", C.c_int64)]
 
@@ -177,6 +183,7 @@ KERNEL_ENTRY_POINTS = {
     "gather_q": GatherParams,
     "batch_norm_q": BatchNormParams,
     "instance_norm_q": InstanceNormParams,
+    "normalization_q": NormalizationParams,
     "convert_q": ConvertParams,
     "qlstm_step": QLstmParams,
     "pad_q": PadParams,

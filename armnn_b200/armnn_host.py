@@ -147,6 +147,9 @@ class ArmnnNetwork:
                 lid = lib.armnnc_add_elementwise_binary(net, int(d["op"]))
             elif t == "BatchMatMul":
                 lid = lib.armnnc_add_batch_matmul(net, int(d["tx"]), int(d["ty"]), int(d.get("ax", False)), int(d.get("ay", False)))
+            elif t == "Normalization":
+                lid = lib.armnnc_add_normalization(net, d["channel_type"], C.c_uint(d["norm_size"]), C.c_float(d["alpha"]),
+                                                   C.c_float(d["beta"]), C.c_float(d["k"]), int(d["nchw"]))
             elif t == "Gather":
                 lid = lib.armnnc_add_gather(net, d["axis"])
             elif t == "BatchNormalization":
@@ -200,6 +203,10 @@ class ArmnnNetwork:
                 flat = [v for pair in d["edges"] for v in pair]
                 lid = lib.armnnc_add_batch_to_space(net, blk, (C.c_int32 * len(flat))(*flat), len(d["block"]), int(d["nchw"]),
                                                     int(t == "SpaceToBatchNd"))
+            elif t == "Tile":
+                lid = lib.armnnc_add_tile(net, (C.c_int32 * len(d["multiples"]))(*d["multiples"]), len(d["multiples"]))
+            elif t == "BroadcastTo":
+                lid = lib.armnnc_add_broadcast_to(net, _shape_arr(d["shape"]), len(d["shape"]))
             elif t == "ChannelShuffle":
                 lid = lib.armnnc_add_channel_shuffle(net, d["axis"], d["groups"])
             elif t == "Stack":

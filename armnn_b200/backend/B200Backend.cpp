@@ -176,6 +176,21 @@ public:
                 }
                 return true;
             }
+            case LayerType::Tile:
+            case LayerType::BroadcastTo:
+            {
+                // a Tile of a tensor of rank r walks up to 2 r dimensions; dimensions of extent or multiple 1 drop out
+                unsigned int dims = 0;
+                if (type == LayerType::Tile)
+                {
+                    const auto& m = PolymorphicDowncast<const TileDescriptor*>(&descriptor)->m_Multiples;
+                    if (m.size() != infos[0].GetNumDimensions()) { return No(reason, "one multiple per dimension"); }
+                    for (unsigned int i = 0; i < m.size(); ++i) { dims += (m[i] > 1 ? 1u : 0u) + (infos[0].GetShape()[i] > 1 ? 1u : 0u); }
+                }
+                else { dims = infos[1].GetNumDimensions(); }
+                if (dims > 6) { return No(reason, "more than six dimensions to walk"); }
+                return (IsMoveType(infos[0]) && infos[1].GetDataType() == infos[0].GetDataType()) || No(reason, "unsupported or mismatched data types");
+            }
             case LayerType::BatchToSpaceNd:
             case LayerType::SpaceToBatchNd:
                 if (infos[0].GetNumDimensions() != 3 && infos[0].GetNumDimensions() != 4) { return No(reason, "3 or 4 dimensions only"); }
@@ -254,6 +269,13 @@ public:
                 if (infos[0].GetNumDimensions() != 4) { return No(reason, "4-D tensors only"); }
                 for (const TensorInfo& t : infos) { if (!IsActType(t)) { return No(reason, "unsupported data type"); } }
                 return true;
+            case LayerType::Normalization:
+                if (PolymorphicDowncast<const NormalizationDescriptor*>(&descriptor)->m_NormMethodType != NormalizationAlgorithmMethod::LocalBrightness)
+                {
+                    return No(reason, "LocalContrast is not supported");
+                }
+                return (infos[0].GetNumDimensions() == 4 && IsActType(infos[0]) && infos[1].GetDataType() == infos[0].GetDataType()) ||
+                       No(reason, "4-D tensors of one supported data type only");
             case LayerType::InstanceNormalization:
                 return (infos[0].GetNumDimensions() == 4 && infos[0].GetDataType() == DataType::Float32 && infos[1].GetDataType() == DataType::Float32) ||
                        No(reason, "4-D Float32 tensors only");

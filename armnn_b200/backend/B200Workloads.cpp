@@ -489,6 +489,80 @@ std::unique_ptr<IWorkload> MakeBatchSpace(const QueueDescriptor& d, const Worklo
     return MakeViews<QD>(d, info, ctx, st);
 }
 
+/// Appends one dimension to a view, dropping extents of 1 and folding a dimension into its outer neighbour when the two
+/// are contiguous on both sides, so that walks over pairs of dimensions (Tile) fit the kernel's six.
+void PushDim(ViewOp& op, int64_t extent, int64_t srcStride, int64_t dstStride)
+{
+    if (extent == 1) { return; }
+    const int r = op.p.rank;
+    if (r > 0 && op.p.src_strides[r - 1] == srcStride * extent && op.p.dst_strides[r - 1] == dstStride * extent)
+    {
+        op.p.shape[r - 1] = static_cast<int32_t>(op.p.shape[r - 1] * extent);
+        op.p.src_strides[r - 1] = srcStride; op.p.dst_strides[r - 1] = dstStride;
+        return;
+    }
+    if (r >= 6) { throw InvalidArgumentException("B200Acc: the rearrangement needs more than six dimensions"); }
+    op.p.shape[r] = static_cast<int32_t>(extent); op.p.src_strides[r] = srcStride; op.p.dst_strides[r] = dstStride;
+    op.p.rank = r + 1;
+}
+
+void FinishDims(ViewOp& op)
+{
+    if (op.p.rank == 0) { op.p.rank = 1; op.p.shape[0] = 1; op.p.src_strides[0] = 1; op.p.dst_strides[0] = 1; }
+}
+
+// Tile (workloads/Tile.cpp:47-103): every dimension becomes a (repeat, size) pair whose repeat part has source stride 0.
+std::unique_ptr<IWorkload> MakeTile(const QueueDescriptor& d, const WorkloadInfo& info, const ContextPtr& ctx)
+{
+    const auto& qd = *PolymorphicDowncast<const TileQueueDescriptor*>(&d);
+    auto st = std::make_shared<ViewState>(ctx);
+    const TensorInfo& in = info.m_InputTensorInfos[0];
+    const TensorInfo& out = info.m_OutputTensorInfos[0];
+    const unsigned int rank = in.GetNumDimensions();
+    if (qd.m_Parameters.m_Multiples.size() != rank || out.GetNumDimensions() != rank || rank > 6) { throw InvalidArgumentException("B200Acc: Tile needs one multiple per dimension"); }
+    int64_t is[6], os[6];
+    DenseStrides(in.GetShape(), is);
+    DenseStrides(out.GetShape(), os);
+    ViewOp op = NewViewOp(in, out, st->blobs, 0, 0, 1);
+    op.p.rank = 0;
+    for (unsigned int i = 0; i < rank; ++i)
+    {
+        const int64_t m = qd.m_Parameters.m_Multiples[i], n = in.GetShape()[i];
+        if (m < 1 || out.GetShape()[i] != n * m) { throw InvalidArgumentException("B200Acc: Tile output shape is not input shape x multiples"); }
+        PushDim(op, m, 0, n * os[i]);
+        PushDim(op, n, is[i], os[i]);
+    }
+    FinishDims(op);
+    st->ops.push_back(op);
+    return MakeViews<TileQueueDescriptor>(d, info, ctx, st);
+}
+
+// BroadcastTo (RefBroadcastToWorkload.cpp:29-44): the input aligned to the innermost dimensions of the output, extents of
+// 1 (or absent dimensions) repeated with source stride 0.
+std::unique_ptr<IWorkload> MakeBroadcastTo(const QueueDescriptor& d, const WorkloadInfo& info, const ContextPtr& ctx)
+{
+    auto st = std::make_shared<ViewState>(ctx);
+    const TensorInfo& in = info.m_InputTensorInfos[0];
+    const TensorInfo& out = info.m_OutputTensorInfos[0];
+    const unsigned int ir = in.GetNumDimensions(), orank = out.GetNumDimensions();
+    if (ir > orank || orank > 6) { throw InvalidArgumentException("B200Acc: BroadcastTo needs an output of at least the input's rank (at most 6)"); }
+    int64_t is[6], os[6];
+    DenseStrides(in.GetShape(), is);
+    DenseStrides(out.GetShape(), os);
+    ViewOp op = NewViewOp(in, out, st->blobs, 0, 0, 1);
+    op.p.rank = 0;
+    for (unsigned int i = 0; i < orank; ++i)
+    {
+        const int id = static_cast<int>(i) - static_cast<int>(orank - ir);
+        const int64_t n = id < 0 ? 1 : static_cast<int64_t>(in.GetShape()[static_cast<unsigned int>(id)]);
+        if (n != 1 && n != out.GetShape()[i]) { throw InvalidArgumentException("B200Acc: BroadcastTo shapes are not compatible"); }
+        PushDim(op, out.GetShape()[i], n == 1 ? 0 : is[id], os[i]);
+    }
+    FinishDims(op);
+    st->ops.push_back(op);
+    return MakeViews<BroadcastToQueueDescriptor>(d, info, ctx, st);
+}
+
 // ChannelShuffle (RefChannelShuffleWorkload.cpp:28-76): output channel i g + j is input channel i + j s.
 std::unique_ptr<IWorkload> MakeChannelShuffle(const QueueDescriptor& d, const WorkloadInfo& info, const ContextPtr& ctx)
 {
@@ -1183,6 +1257,36 @@ std::unique_ptr<IWorkload> B200WorkloadFactory::CreateWorkload(LayerType type, c
                 B200CheckStatus(b200k_batch_norm_q(&st->p, s));
             });
         }
+        case LayerType::Normalization:
+        {
+            // the reference encodes the output with the input's TensorInfo (RefNormalizationWorkload.cpp:176-177) and its
+            // Within variant reads the shape as [N, C, H, W] whatever the layout says (lines 25-28): both kept
+            const auto& qd = *PolymorphicDowncast<const NormalizationQueueDescriptor*>(&d);
+            auto st = std::make_shared<SimpleState<b200k_normalization_params>>(ctx);
+            b200k_normalization_params& p = st->p;
+            std::memset(&p, 0, sizeof(p));
+            const TensorInfo& x = info.m_InputTensorInfos[0];
+            if (x.GetNumDimensions() != 4 || qd.m_Parameters.m_NormMethodType != NormalizationAlgorithmMethod::LocalBrightness) { throw InvalidArgumentException("B200Acc: Normalization needs a 4-D input and the LocalBrightness method"); }
+            p.x = Operand(x, st->blobs); p.y = Operand(x, st->blobs);
+            p.channel_type = qd.m_Parameters.m_NormChannelType == NormalizationAlgorithmChannel::Within ? 1 : 0;
+            const TensorShape& s = x.GetShape();
+            p.n = static_cast<int32_t>(s[0]);
+            if (p.channel_type == 1 || qd.m_Parameters.m_DataLayout == DataLayout::NCHW)
+            {
+                p.c = static_cast<int32_t>(s[1]); p.h = static_cast<int32_t>(s[2]); p.w = static_cast<int32_t>(s[3]); p.nchw = 1;
+            }
+            else
+            {
+                p.h = static_cast<int32_t>(s[1]); p.w = static_cast<int32_t>(s[2]); p.c = static_cast<int32_t>(s[3]); p.nchw = 0;
+            }
+            p.norm_size = qd.m_Parameters.m_NormSize;
+            p.alpha = qd.m_Parameters.m_Alpha; p.beta = qd.m_Parameters.m_Beta; p.kappa = qd.m_Parameters.m_K;
+            return Make<NormalizationQueueDescriptor>(d, info, ctx, [st](const NormalizationQueueDescriptor& data, cudaStream_t s2)
+            {
+                st->p.x.data = Dev(data.m_Inputs[0]); st->p.y.data = Dev(data.m_Outputs[0]);
+                B200CheckStatus(b200k_normalization_q(&st->p, s2));
+            });
+        }
         case LayerType::InstanceNormalization:
         {
             const auto& qd = *PolymorphicDowncast<const InstanceNormalizationQueueDescriptor*>(&d);
@@ -1367,6 +1471,8 @@ std::unique_ptr<IWorkload> B200WorkloadFactory::CreateWorkload(LayerType type, c
             const auto& prm = PolymorphicDowncast<const SpaceToBatchNdQueueDescriptor*>(&d)->m_Parameters;
             return MakeBatchSpace<SpaceToBatchNdQueueDescriptor>(d, info, ctx, prm.m_BlockShape, prm.m_PadList, prm.m_DataLayout, false);
         }
+        case LayerType::Tile:         return MakeTile(d, info, ctx);
+        case LayerType::BroadcastTo:  return MakeBroadcastTo(d, info, ctx);
         case LayerType::ChannelShuffle: return MakeChannelShuffle(d, info, ctx);
         case LayerType::Stack:        return MakeStack(d, info, ctx);
         case LayerType::QLstm:

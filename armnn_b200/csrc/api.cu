@@ -113,6 +113,7 @@ extern "C" size_t b200k_sizeof_params(int which)
         case 16: return sizeof(b200k_gather_params);
         case 17: return sizeof(b200k_batch_norm_params);
         case 18: return sizeof(b200k_instance_norm_params);
+        case 19: return sizeof(b200k_normalization_params);
         default: return 0;
     }
 }

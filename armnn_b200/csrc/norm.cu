@@ -97,3 +97,67 @@ extern "C" int b200k_instance_norm_q(const b200k_instance_norm_params* p, void* 
     launch_pdl(instance_norm_kernel, dim3(div_up((long long)p->n * p->c, 128)), dim3(128), 0, (cudaStream_t)stream, a);
     return check_launch("instance_norm_kernel");
 }
+
+// ---- Normalization (local response normalisation) --------------------------------------------------------------
+// RefNormalizationWorkload.cpp:19-140 of the Arm NN tree, LocalBrightness only (the reference supports nothing else):
+//   Across: s = sum of squares over the channels c - r .. c + r at the same pixel, y = x * powf(kappa + s * alpha, -beta);
+//   Within: s = sum of squares over the (2 r + 1)^2 window around the pixel in the same channel, indexed as NCHW
+//           whatever the layout says, y = x / powf(kappa + s * alpha, beta).
+// r = norm_size / 2; positions outside the tensor are skipped; sums run in the reference's order.
+namespace b200k {
+
+struct LrnArgs { QView x, y; int n, c, h, w, nchw, within, radius; float alpha, beta, kappa; long long count; };
+
+__global__ void __launch_bounds__(256) normalization_kernel(const LrnArgs a)
+{
+    pdl_enter();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= a.count) return;
+    float acc = 0.f;
+    if (a.within) {
+        const int w = (int)(i % a.w), h = (int)((i / a.w) % a.h);
+        const long long plane = i - ((long long)h * a.w + w);
+        for (int y = -a.radius; y <= a.radius; ++y)
+            for (int x = -a.radius; x <= a.radius; ++x) {
+                const int ix = w + x, iy = h + y;
+                if (ix < 0 || ix >= a.w || iy < 0 || iy >= a.h) continue;
+                const float v = a.x.get(plane + (long long)iy * a.w + ix);
+                acc = __fadd_rn(acc, __fmul_rn(v, v));
+            }
+        a.y.set(i, __fdiv_rn(a.x.get(i), powf(__fadd_rn(a.kappa, __fmul_rn(acc, a.alpha)), a.beta)));
+        return;
+    }
+    const long long hw = (long long)a.h * a.w;
+    const int c = a.nchw ? (int)((i / hw) % a.c) : (int)(i % a.c);
+    const long long cstride = a.nchw ? hw : 1;
+    for (int z = -a.radius; z <= a.radius; ++z) {
+        const int k = c + z;
+        if (k < 0 || k >= a.c) continue;
+        const float v = a.x.get(i + (long long)z * cstride);
+        acc = __fadd_rn(acc, __fmul_rn(v, v));
+    }
+    const float scale = powf(__fadd_rn(a.kappa, __fmul_rn(acc, a.alpha)), -a.beta);
+    a.y.set(i, __fmul_rn(scale, a.x.get(i)));
+}
+
+}  // namespace b200k
+
+extern "C" int b200k_normalization_q(const b200k_normalization_params* p, void* stream)
+{
+    B200K_REQUIRE(p, B200K_E_INVALID, "normalization_q: null params");
+    B200K_REQUIRE(p->x.data && p->y.data, B200K_E_INVALID, "normalization_q: null tensor pointer");
+    B200K_REQUIRE(p->n > 0 && p->c > 0 && p->h > 0 && p->w > 0, B200K_E_INVALID, "normalization_q: bad shape");
+    B200K_REQUIRE(act_type(p->x.dtype) && act_type(p->y.dtype), B200K_E_UNSUPPORTED, "normalization_q: unsupported data type");
+    B200K_REQUIRE(p->channel_type == 0 || p->channel_type == 1, B200K_E_INVALID, "normalization_q: channel type %d is neither Across (0) nor Within (1)", p->channel_type);
+    B200K_REQUIRE(p->channel_type == 0 || p->nchw, B200K_E_UNSUPPORTED, "normalization_q: Within indexes the tensor as NCHW (as the reference does): pass nchw = 1");
+    B200K_REQUIRE(p->norm_size >= 1, B200K_E_INVALID, "normalization_q: norm_size must be positive");
+    b200k::LrnArgs a;
+    a.x = make_view(p->x); a.y = make_view(p->y);
+    a.n = p->n; a.c = p->c; a.h = p->h; a.w = p->w; a.nchw = p->nchw ? 1 : 0; a.within = p->channel_type;
+    a.radius = (int)(p->norm_size / 2);
+    a.alpha = p->alpha; a.beta = p->beta; a.kappa = p->kappa;
+    a.count = (long long)p->n * p->c * p->h * p->w;
+    B200K_REQUIRE(a.count / 256 < (1ll << 31) - 1, B200K_E_TOOBIG, "normalization_q: tensor too large");
+    launch_pdl(b200k::normalization_kernel, dim3(div_up(a.count, 256)), dim3(256), 0, (cudaStream_t)stream, a);
+    return check_launch("normalization_kernel");
+}

@@ -224,6 +224,17 @@ int armnnc_add_elementwise_binary(void* vn, int op)
     return add_layer(n, n->net->AddElementwiseBinaryLayer(ElementwiseBinaryDescriptor(static_cast<BinaryOperation>(op))));
 }
 
+int armnnc_add_normalization(void* vn, int channel_type, unsigned norm_size, float alpha, float beta, float k, int nchw)
+{
+    auto* n = static_cast<CNet*>(vn);
+    NormalizationDescriptor d;
+    d.m_NormChannelType = channel_type ? NormalizationAlgorithmChannel::Within : NormalizationAlgorithmChannel::Across;
+    d.m_NormMethodType = NormalizationAlgorithmMethod::LocalBrightness;
+    d.m_NormSize = norm_size; d.m_Alpha = alpha; d.m_Beta = beta; d.m_K = k;
+    d.m_DataLayout = nchw ? DataLayout::NCHW : DataLayout::NHWC;
+    return add_layer(n, n->net->AddNormalizationLayer(d));
+}
+
 int armnnc_add_gather(void* vn, int axis)
 {
     auto* n = static_cast<CNet*>(vn);
@@ -481,6 +492,24 @@ int armnnc_add_batch_to_space(void* vn, const int32_t* block, const int32_t* edg
     BatchToSpaceNdDescriptor d(blockShape, pairs);
     d.m_DataLayout = nchw ? DataLayout::NCHW : DataLayout::NHWC;
     return add_layer(n, n->net->AddBatchToSpaceNdLayer(d));
+}
+
+int armnnc_add_tile(void* vn, const int32_t* multiples, int rank)
+{
+    auto* n = static_cast<CNet*>(vn);
+    TileDescriptor d;
+    d.m_Multiples.assign(multiples, multiples + rank);
+    return add_layer(n, n->net->AddTileLayer(d));
+}
+
+int armnnc_add_broadcast_to(void* vn, const int32_t* shape, int rank)
+{
+    auto* n = static_cast<CNet*>(vn);
+    unsigned dims[6] = {0, 0, 0, 0, 0, 0};
+    for (int i = 0; i < rank && i < 6; ++i) dims[i] = (unsigned)shape[i];
+    BroadcastToDescriptor d;
+    d.m_BroadcastToShape = TensorShape((unsigned)rank, dims);
+    return add_layer(n, n->net->AddBroadcastToLayer(d));
 }
 
 int armnnc_add_channel_shuffle(void* vn, int axis, int groups)

@@ -306,6 +306,12 @@ class INetwork:
         return self._add(Layer("SpaceToBatchNd", name, 1, 1, {"block": tuple(int(b) for b in block_shape),
                                                               "edges": tuple((int(a), int(b)) for a, b in pad_list), "nchw": bool(nchw)}))
 
+    def AddTileLayer(self, multiples, name=None):
+        return self._add(Layer("Tile", name, 1, 1, {"multiples": tuple(int(m) for m in multiples)}))
+
+    def AddBroadcastToLayer(self, shape, name=None):
+        return self._add(Layer("BroadcastTo", name, 1, 1, {"shape": tuple(int(n) for n in shape)}))
+
     def AddChannelShuffleLayer(self, axis, num_groups, name=None):
         return self._add(Layer("ChannelShuffle", name, 1, 1, {"axis": int(axis), "groups": int(num_groups)}))
 
@@ -339,6 +345,14 @@ class INetwork:
 
     def AddDequantizeLayer(self, name=None):
         return self._add(Layer("Dequantize", name, 1, 1))
+
+    def AddNormalizationLayer(self, channel_type, norm_size, alpha, beta, k, nchw=False, name=None):
+        """armnn::NormalizationDescriptor with NormalizationAlgorithmMethod::LocalBrightness; channel_type 0 Across,
+        1 Within."""
+        if int(channel_type) not in (0, 1):
+            raise InvalidArgumentException("Normalization: channel type must be 0 (Across) or 1 (Within)")
+        return self._add(Layer("Normalization", name, 1, 1, {"channel_type": int(channel_type), "norm_size": int(norm_size),
+                                                              "alpha": float(alpha), "beta": float(beta), "k": float(k), "nchw": bool(nchw)}))
 
     def AddGatherLayer(self, axis=0, name=None):
         """armnn::GatherDescriptor: input 0 the tensor, input 1 the Signed32 indices."""
@@ -436,6 +450,11 @@ def IsLayerSupported(layer):
         if any(info.dtype not in ok for _, info in layer.bn_params.values()):
             return False, "BatchNormalization: unsupported parameter data type"
         return True, ""
+    if t == "Normalization":
+        ok = (DataType.QAsymmU8, DataType.QAsymmS8, DataType.QSymmS16, DataType.Float32)
+        if ins[0].dtype not in ok or outs[0].dtype != ins[0].dtype or len(ins[0].shape) != 4:
+            return False, "Normalization: 4-D tensors of one supported data type only"
+        return True, ""
     if t == "InstanceNormalization":
         if ins[0].dtype != DataType.Float32 or outs[0].dtype != DataType.Float32 or len(ins[0].shape) != 4:
             return False, "InstanceNormalization: 4-D Float32 tensors only (as in the reference)"
@@ -476,6 +495,16 @@ def IsLayerSupported(layer):
         # RefLayerSupport.cpp:949-979, 2597-2630: one element type for every tensor; quantisation may differ
         if len(ins[0].shape) > 6 or any(i.dtype != ins[0].dtype for i in list(ins) + list(outs)):
             return False, "%s: rank > 6 or mismatched data types" % t
+        return True, ""
+    if t in ("Tile", "BroadcastTo"):
+        if any(i.dtype != outs[0].dtype for i in ins):
+            return False, "%s: mismatched data types" % t
+        try:
+            v = (views.tile_view(ins[0].shape, layer.desc["multiples"])[1] if t == "Tile"
+                 else views.broadcast_to_view(ins[0].shape, outs[0].shape))
+            views.merge_dims(v)
+        except ValueError as e:
+            return False, "%s: %s" % (t, e)
         return True, ""
     if t in ("SpaceToDepth", "ChannelShuffle", "Stack", "BatchToSpaceNd", "SpaceToBatchNd"):
         # through Decoder / Encoder in the reference: one element type, quantisation may differ
@@ -969,6 +998,22 @@ class GraphProgram:
         p.scratch = self._ptr(scratch)
         return "batch_norm_q", p
 
+    def _make_Normalization(self, layer):
+        """The reference encodes the output with the input's quantisation (RefNormalizationWorkload.cpp:176-177) and its
+        Within variant indexes the tensor as NCHW whatever the layout says (lines 25-28): both kept."""
+        x, y, d = layer.inputs[0].source, layer.outputs[0], layer.desc
+        p = _abi.NormalizationParams()
+        p.x, p.y = self._operand(x), self._operand(y)
+        p.y.scale, p.y.zero_point = p.x.scale, p.x.zero_point
+        shape = x.info.shape
+        if d["channel_type"] == 1 or d["nchw"]:
+            p.n, p.c, p.h, p.w, p.nchw = shape[0], shape[1], shape[2], shape[3], 1
+        else:
+            p.n, p.h, p.w, p.c, p.nchw = shape[0], shape[1], shape[2], shape[3], 0
+        p.channel_type, p.norm_size = d["channel_type"], d["norm_size"]
+        p.alpha, p.beta, p.kappa = d["alpha"], d["beta"], d["k"]
+        return "normalization_q", p
+
     def _make_InstanceNormalization(self, layer):
         x, y, d = layer.inputs[0].source, layer.outputs[0], layer.desc
         p = _abi.InstanceNormParams()
@@ -1062,6 +1107,19 @@ class GraphProgram:
         if tuple(out_shape) != tuple(y.info.shape):
             raise InvalidArgumentException("DepthToSpace: output shape %s, expected %s" % (y.info.shape, out_shape))
         return self._view_copy(x, y, v)
+
+    def _make_Tile(self, layer):
+        x, y = layer.inputs[0].source, layer.outputs[0]
+        out_shape, v = views.tile_view(x.info.shape, layer.desc["multiples"])
+        if tuple(out_shape) != tuple(y.info.shape):
+            raise InvalidArgumentException("Tile: output shape %s, expected %s" % (y.info.shape, out_shape))
+        return self._view_copy(x, y, v)
+
+    def _make_BroadcastTo(self, layer):
+        x, y = layer.inputs[0].source, layer.outputs[0]
+        if tuple(layer.desc["shape"]) != tuple(y.info.shape):
+            raise InvalidArgumentException("BroadcastTo: output shape %s is not the descriptor's %s" % (y.info.shape, layer.desc["shape"]))
+        return self._view_copy(x, y, views.broadcast_to_view(x.info.shape, y.info.shape))
 
     def _make_BatchToSpaceNd(self, layer):
         x, y, d = layer.inputs[0].source, layer.outputs[0], layer.desc

@@ -15,6 +15,7 @@ rules once in a form that is easy to test against CpuRef:
 * DepthToSpace, SpaceToDepth, ChannelShuffle and Stack: six- or four-dimensional walks over the same bytes.
 * BatchToSpaceNd (`workloads/BatchToSpaceNd.cpp:50-117`) and SpaceToBatchNd (`workloads/SpaceToBatchNd.cpp:49-131`): one
   strided block per position inside the spatial block; one six-dimensional walk when nothing is cropped or padded.
+* Tile and BroadcastTo: repeated dimensions read with source stride 0.
 """
 
 INT_MIN, INT_MAX = -(1 << 31), (1 << 31) - 1
@@ -286,6 +287,33 @@ def space_to_batch_views(in_shape, block, pads, nchw=False):
                         arrange([sb, sh * bh, sw * bw, sc]),
                         (i * bw + j) * ib * db + h0 * dh + w0 * dw, arrange([db, dh, dw, dc])))
     return out_shape, out, bool(pt or pb or pl or pr)
+
+
+def tile_view(in_shape, multiples):
+    """(out_shape, view) of Tile (`workloads/Tile.cpp:47-103`): output coordinate o reads input coordinate o % size in
+    every dimension: each dimension becomes a (repeat, size) pair whose repeat part has source stride 0."""
+    if len(multiples) != len(in_shape) or any(int(m) < 1 for m in multiples):
+        raise ValueError("Tile: one positive multiple per dimension")
+    out_shape = tuple(int(n) * int(m) for n, m in zip(in_shape, multiples))
+    ss, ds = dense_strides(in_shape), dense_strides(out_shape)
+    shape, src, dst = [], [], []
+    for n, m, a, b in zip(in_shape, multiples, ss, ds):
+        shape += [int(m), int(n)]
+        src += [0, a]
+        dst += [int(n) * b, b]
+    return out_shape, (tuple(shape), 0, src, 0, dst)
+
+
+def broadcast_to_view(in_shape, out_shape):
+    """View of BroadcastTo (`workloads/RefBroadcastToWorkload.cpp:29-44`): the input aligned to the innermost dimensions
+    of the output, dimensions of extent 1 (or absent) repeated with source stride 0."""
+    if len(in_shape) > len(out_shape):
+        raise ValueError("BroadcastTo: the input has more dimensions than the output")
+    padded = (1,) * (len(out_shape) - len(in_shape)) + tuple(int(n) for n in in_shape)
+    if any(a != b and a != 1 for a, b in zip(padded, out_shape)):
+        raise ValueError("BroadcastTo: %s cannot be broadcast to %s" % (list(in_shape), list(out_shape)))
+    ss = dense_strides(padded)
+    return (tuple(int(n) for n in out_shape), 0, [0 if a == 1 else st for a, st in zip(padded, ss)], 0, dense_strides(out_shape))
 
 
 def fill_view(shape):

@@ -401,6 +401,25 @@ typedef struct {
 
 int b200k_instance_norm_q(const b200k_instance_norm_params* p, void* stream);
 
+/* armnn::Normalization, LocalBrightness (src/backends/reference/workloads/RefNormalizationWorkload.cpp:19-140), with
+ * r = norm_size / 2 and positions outside the tensor skipped:
+ *   channel_type 0 (Across): s = sum of x^2 over channels c - r .. c + r of the pixel, y = x * powf(kappa + s * alpha, -beta);
+ *   channel_type 1 (Within): s = sum of x^2 over the (2 r + 1)^2 window in the same channel, y = x / powf(kappa + s * alpha, beta);
+ *     the reference indexes the tensor as NCHW whatever the descriptor's layout: pass c, h, w = shape[1], shape[2], shape[3]
+ *     and nchw = 1.
+ * The reference encodes the output with the INPUT's quantisation (line 176): a caller that wants its bytes passes x's
+ * scale and zero point in y. */
+typedef struct {
+    b200k_qtensor x, y;
+    int32_t n, c, h, w;
+    int32_t nchw;
+    int32_t channel_type;
+    uint32_t norm_size;
+    float alpha, beta, kappa;
+} b200k_normalization_params;
+
+int b200k_normalization_q(const b200k_normalization_params* p, void* stream);
+
 /* ---- Softmax --------------------------------------------------------------------------------- */
 
 /* armnn::Softmax (src/backends/reference/workloads/Softmax.cpp:17-70): softmax over the axis of
@@ -500,7 +519,7 @@ unsigned long long b200k_kernel_launches(void);
 
 /* sizeof() of a parameter struct as compiled into the library, for bindings in other languages to check their
  * own declarations: 0 conv2d, 1 fc, 2 bmm, 3 pool2d, 4 mean, 5 eltwise, 6 activation, 7 softmax, 8 convert,
- * 9 qlstm, 10 pad, 11 view_copy, 12 resize, 13 reduce, 14 unary, 15 arg_min_max, 16 gather, 17 batch_norm, 18 instance_norm.  No counterpart in the reference (its backends are linked as C++). */
+ * 9 qlstm, 10 pad, 11 view_copy, 12 resize, 13 reduce, 14 unary, 15 arg_min_max, 16 gather, 17 batch_norm, 18 instance_norm, 19 normalization.  No counterpart in the reference (its backends are linked as C++). */
 size_t b200k_sizeof_params(int which);
 
 #ifdef __cplusplus

@@ -404,6 +404,27 @@ extern "C" int cpuref_instance_norm_q(const b200k_instance_norm_params* p)
     });
 }
 
+extern "C" int cpuref_normalization_q(const b200k_normalization_params* p)
+{
+    return guarded([&] {
+        Harness h;
+        TensorShape s = p->nchw ? TensorShape({(unsigned)p->n, (unsigned)p->c, (unsigned)p->h, (unsigned)p->w})
+                                : TensorShape({(unsigned)p->n, (unsigned)p->h, (unsigned)p->w, (unsigned)p->c});
+        TensorInfo xi = make_info(p->x, s, 0, 0, false);
+        TensorInfo yi = make_info(p->y, s, 0, 0, false);
+        NormalizationQueueDescriptor d;
+        d.m_Parameters.m_NormChannelType = p->channel_type ? NormalizationAlgorithmChannel::Within : NormalizationAlgorithmChannel::Across;
+        d.m_Parameters.m_NormMethodType = NormalizationAlgorithmMethod::LocalBrightness;
+        d.m_Parameters.m_NormSize = p->norm_size;
+        d.m_Parameters.m_Alpha = p->alpha; d.m_Parameters.m_Beta = p->beta; d.m_Parameters.m_K = p->kappa;
+        d.m_Parameters.m_DataLayout = p->nchw ? DataLayout::NCHW : DataLayout::NHWC;
+        h.in(d, xi, p->x.data);
+        auto* o = h.out(d, yi);
+        h.run(LayerType::Normalization, d);
+        copy_out(o, const_cast<void*>(p->y.data), yi.GetNumBytes());
+    });
+}
+
 extern "C" int cpuref_softmax_q8(const b200k_softmax_params* p)
 {
     return guarded([&] {
@@ -732,6 +753,25 @@ extern "C" int cpuref_move_q(const oracle_move_params* p)
                 h.in(d, whole, p->whole.data);
                 outs.push_back(h.out(d, views[0]));
                 h.run(LayerType::SpaceToBatchNd, d);
+                copy_out(outs[0], const_cast<void*>(p->view[0].data), views[0].GetNumBytes());
+                break;
+            }
+            case MOVE_TILE: {
+                TileQueueDescriptor d;
+                d.m_Parameters.m_Multiples.clear();
+                for (int i = 0; i < p->rank; ++i) d.m_Parameters.m_Multiples.push_back((uint32_t)p->perm[i]);
+                h.in(d, whole, p->whole.data);
+                outs.push_back(h.out(d, views[0]));
+                h.run(LayerType::Tile, d);
+                copy_out(outs[0], const_cast<void*>(p->view[0].data), views[0].GetNumBytes());
+                break;
+            }
+            case MOVE_BROADCAST_TO: {
+                BroadcastToQueueDescriptor d;
+                d.m_Parameters.m_BroadcastToShape = views[0].GetShape();
+                h.in(d, whole, p->whole.data);
+                outs.push_back(h.out(d, views[0]));
+                h.run(LayerType::BroadcastTo, d);
                 copy_out(outs[0], const_cast<void*>(p->view[0].data), views[0].GetNumBytes());
                 break;
             }

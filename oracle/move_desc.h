@@ -9,6 +9,8 @@ enum { MOVE_CONCAT = 0, MOVE_SPLIT = 1, MOVE_PERMUTE = 2, MOVE_TRANSPOSE = 3, MO
        MOVE_DEPTH_TO_SPACE = 6, MOVE_SPACE_TO_DEPTH = 7,      /* perm[0] = block size, perm[1] = 1 for NCHW */
        MOVE_CHANNEL_SHUFFLE = 8,                              /* perm[0] = axis, perm[1] = groups */
        MOVE_STACK = 9,                                        /* perm[0] = axis; whole = the output, views = the inputs */
+       MOVE_TILE = 12,                                        /* perm = multiples */
+       MOVE_BROADCAST_TO = 13,                                /* view_shape[0] = the shape to broadcast to */
        MOVE_BATCH_TO_SPACE = 10, MOVE_SPACE_TO_BATCH = 11 };  /* perm[0] = 1 for NCHW; begin = block shape, end / stride =
                                                                  crops or padding before / after, per spatial dimension */
 

@@ -707,6 +707,53 @@ int oracle_instance_norm_q(const b200k_instance_norm_params* p)
     return 0;
 }
 
+/* ---- Normalization (LocalBrightness), RefNormalizationWorkload.cpp:19-140 -------------------------- */
+
+int oracle_normalization_q(const b200k_normalization_params* p)
+{
+    if (!p->x.data || !p->y.data) return B200K_E_INVALID;
+    const int radius = (int)(p->norm_size / 2);
+    const int64_t hw = (int64_t)p->h * p->w;
+    if (p->channel_type == 1) {
+        if (!p->nchw) return B200K_E_UNSUPPORTED;
+        for (int n = 0; n < p->n; ++n) for (int c = 0; c < p->c; ++c)
+        for (int h = 0; h < p->h; ++h) for (int w = 0; w < p->w; ++w) {
+            volatile float acc = 0.0f;
+            for (int y = -radius; y <= radius; ++y) for (int x = -radius; x <= radius; ++x) {
+                const int i = w + x, j = h + y;
+                if (i < 0 || i >= p->w || j < 0 || j >= p->h) continue;
+                const float v = load_f(&p->x, ((int64_t)n * p->c + c) * hw + (int64_t)j * p->w + i);
+                volatile float sq = v * v;
+                acc = acc + sq;
+            }
+            const int64_t at = ((int64_t)n * p->c + c) * hw + (int64_t)h * p->w + w;
+            volatile float sa = acc * p->alpha;
+            volatile float base = p->kappa + sa;
+            volatile float r = load_f(&p->x, at) / powf(base, p->beta);
+            store_f(&p->y, at, r);
+        }
+        return 0;
+    }
+    if (p->channel_type != 0) return B200K_E_INVALID;
+    for (int n = 0; n < p->n; ++n) for (int c = 0; c < p->c; ++c)
+    for (int64_t k = 0; k < hw; ++k) {
+        volatile float acc = 0.0f;
+        for (int z = -radius; z <= radius; ++z) {
+            const int cc = c + z;
+            if (cc < 0 || cc >= p->c) continue;
+            const float v = load_f(&p->x, p->nchw ? ((int64_t)n * p->c + cc) * hw + k : ((int64_t)n * hw + k) * p->c + cc);
+            volatile float sq = v * v;
+            acc = acc + sq;
+        }
+        const int64_t at = p->nchw ? ((int64_t)n * p->c + c) * hw + k : ((int64_t)n * hw + k) * p->c + c;
+        volatile float sa = acc * p->alpha;
+        volatile float base = p->kappa + sa;
+        volatile float r = powf(base, -p->beta) * load_f(&p->x, at);
+        store_f(&p->y, at, r);
+    }
+    return 0;
+}
+
 /* ---- Quantize / Dequantize / requantize, RefQuantizeWorkload.cpp:14-45, Dequantize.cpp:11-28 - */
 
 int oracle_convert_q(const b200k_convert_params* p)
@@ -1121,6 +1168,51 @@ static int move_space_to_batch(const oracle_move_params* p)
     return 0;
 }
 
+/* Tile.cpp:47-103: output coordinate o reads input coordinate o % size in every dimension. */
+static int move_tile(const oracle_move_params* p)
+{
+    int64_t total = 1;
+    int32_t out_shape[6];
+    for (int d = 0; d < p->rank; ++d) {
+        if (p->perm[d] < 1) return B200K_E_INVALID;
+        out_shape[d] = p->whole_shape[d] * p->perm[d];
+        total *= out_shape[d];
+    }
+    for (int64_t o = 0; o < total; ++o) {
+        int64_t rest = o, src = 0, stride = 1;
+        for (int d = p->rank - 1; d >= 0; --d) {
+            const int64_t c = rest % out_shape[d];
+            rest /= out_shape[d];
+            src += (c % p->whole_shape[d]) * stride;
+            stride *= p->whole_shape[d];
+        }
+        store_f(&p->view[0], o, load_f(&p->whole, src));
+    }
+    return 0;
+}
+
+/* RefBroadcastToWorkload.cpp:29-44 with Broadcast.hpp: the input aligned to the innermost dimensions of the output. */
+static int move_broadcast_to(const oracle_move_params* p)
+{
+    const int orank = p->view_rank[0] ? p->view_rank[0] : p->rank;
+    if (orank < p->rank) return B200K_E_INVALID;
+    int64_t total = 1;
+    for (int d = 0; d < orank; ++d) total *= p->view_shape[0][d];
+    for (int64_t o = 0; o < total; ++o) {
+        int64_t rest = o, src = 0, stride = 1;
+        for (int d = orank - 1; d >= 0; --d) {
+            const int64_t c = rest % p->view_shape[0][d];
+            rest /= p->view_shape[0][d];
+            const int id = d - (orank - p->rank);
+            if (id < 0) continue;
+            if (p->whole_shape[id] != 1) src += c * stride;
+            stride *= p->whole_shape[id];
+        }
+        store_f(&p->view[0], o, load_f(&p->whole, src));
+    }
+    return 0;
+}
+
 /* RefChannelShuffleWorkload.cpp:28-76: with g groups of s channels along `axis`, output channel i g + j takes input
  * channel i + j s, through Decoder / Encoder. */
 static int move_channel_shuffle(const oracle_move_params* p)
@@ -1171,6 +1263,8 @@ int oracle_move_q(const oracle_move_params* p)
         case MOVE_SPACE_TO_DEPTH:  return move_space_to_depth(p);
         case MOVE_CHANNEL_SHUFFLE: return move_channel_shuffle(p);
         case MOVE_STACK:           return move_stack(p);
+        case MOVE_TILE:            return move_tile(p);
+        case MOVE_BROADCAST_TO:    return move_broadcast_to(p);
         case MOVE_BATCH_TO_SPACE:  return move_batch_to_space(p);
         case MOVE_SPACE_TO_BATCH:  return move_space_to_batch(p);
         default: return B200K_E_INVALID;

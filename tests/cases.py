@@ -434,7 +434,29 @@ def norm_cases():
             p.gamma, p.beta, p.eps = gamma, beta, 1e-5
             return p, [y]
         return lambda: SimpleCase("instance_norm_q", build)
+    def lrn(seed, n, c, h, w, channel_type, size, nchw=False, dtype=S8, alpha=1e-2, beta=0.75, kappa=1.0):
+        def build(mem):
+            rng = np.random.default_rng(seed)
+            p = _abi.NormalizationParams()
+            shape = (n, c, h, w) if nchw else (n, h, w, c)
+            if dtype == F32:
+                p.x = qt(mem, (rng.standard_normal(shape) * 3).astype(np.float32), F32)
+                p.y, y = qt_out(mem, shape, F32)
+            else:
+                # the reference encodes the output with the input's quantisation
+                q = (0.05, 3) if dtype == S8 else (0.05, 120)
+                p.x = qt(mem, _rand(rng, dtype, shape), dtype, *q)
+                p.y, y = qt_out(mem, shape, dtype, *q)
+            p.n, p.c, p.h, p.w, p.nchw, p.channel_type, p.norm_size = n, c, h, w, int(nchw), channel_type, size
+            p.alpha, p.beta, p.kappa = alpha, beta, kappa
+            return p, [y]
+        return lambda: SimpleCase("normalization_q", build)
     return {
+        "lrn_across_nhwc": lrn(333, 2, 24, 6, 7, 0, 5),
+        "lrn_across_nchw_u8": lrn(334, 1, 9, 5, 8, 0, 3, nchw=True, dtype=U8, alpha=1e-1, beta=0.5, kappa=2.0),
+        "lrn_across_float": lrn(335, 2, 16, 4, 4, 0, 5, dtype=F32, alpha=1e-4),
+        "lrn_within_nchw": lrn(336, 2, 3, 9, 10, 1, 3, nchw=True),
+        "lrn_within_float": lrn(337, 1, 4, 7, 5, 1, 5, nchw=True, dtype=F32, alpha=2e-2, beta=1.0),
         "gather_embedding_rows": gather(321, 1, 500, 64, 37),
         "gather_axis1_requantise": gather(322, 3, 11, 5, 7, dtype=U8, requant=True),
         "gather_negative_indices_s16": gather(323, 2, 9, 3, 12, dtype=S16, negative=True),
@@ -451,6 +473,9 @@ def norm_cases():
 
 
 RANGE_LO = {U8: 0, S8: -128, S16: -32768}
+
+# powf of the device against glibc: the last ulp may move a value across a rounding boundary
+TRANSCENDENTAL_NORM = ("lrn_across_nhwc", "lrn_across_nchw_u8", "lrn_across_float", "lrn_within_nchw", "lrn_within_float")
 
 # RefGatherWorkload.cpp:40-47 throws on a negative index before armnn::Gather (Gather.cpp:55-57), which would wrap it,
 # runs: these cases have no CpuRef output and pin the wrapping against the restatement of Gather.cpp only
@@ -745,6 +770,12 @@ def move_cases():
     c["stack_last_axis_requantise"] = lambda: MoveCase("stack", 226, ((4, 6, 3), S8, 0.06, 2), [((4, 6), S8, 0.05, -1), ((4, 6), S8, 0.07, 3), ((4, 6), S8, 0.06, 2)],
                                                        perm=(2,))
     c["slice_rank2_s32"] = lambda: MoveCase("slice", 217, ((7, 9), S32, 1.0, 0), [((3, 4), S32, 1.0, 0)], begin=(2, 5), end=(3, 4))
+    c["tile_rank3"] = lambda: MoveCase("tile", 235, ((2, 3, 5),) + q, [((4, 9, 5),) + q], perm=(2, 3, 1))
+    c["tile_rank4_requantise_u8"] = lambda: MoveCase("tile", 236, ((1, 2, 3, 4), U8, 0.1, 9), [((2, 2, 6, 12), U8, 0.13, 20)], perm=(2, 1, 2, 3))
+    c["tile_all_ones_float"] = lambda: MoveCase("tile", 237, ((3, 7), F32, 1.0, 0), [((3, 7), F32, 1.0, 0)], perm=(1, 1))
+    c["broadcast_to_channels"] = lambda: MoveCase("broadcast_to", 238, ((1, 1, 1, 16),) + q, [((2, 5, 6, 16),) + q])
+    c["broadcast_to_higher_rank_requantise"] = lambda: MoveCase("broadcast_to", 239, ((3, 1), S8, 0.05, 2), [((4, 2, 3, 7), S8, 0.08, -4)])
+    c["broadcast_to_scalar_float"] = lambda: MoveCase("broadcast_to", 240, ((1,), F32, 1.0, 0), [((5, 9), F32, 1.0, 0)])
     # BatchToSpaceNd / SpaceToBatchNd: begin = block shape, end / stride = crops or padding before / after
     c["batch_to_space_2x2"] = lambda: MoveCase("batch_to_space", 227, ((8, 5, 6, 16),) + q, [((2, 10, 12, 16),) + q],
                                                perm=(0,), begin=(2, 2), end=(0, 0), stride=(0, 0))

@@ -414,7 +414,7 @@ class OracleMoveParams(C.Structure):
 
 MOVE_KINDS = {"concat": 0, "split": 1, "permute": 2, "transpose": 3, "strided_slice": 4, "slice": 5,
               "depth_to_space": 6, "space_to_depth": 7, "channel_shuffle": 8, "stack": 9,
-              "batch_to_space": 10, "space_to_batch": 11}
+              "batch_to_space": 10, "space_to_batch": 11, "tile": 12, "broadcast_to": 13}
 
 
 class MoveCase:
@@ -522,6 +522,12 @@ class MoveCase:
                 out_shape, vs, padded = V.space_to_batch_views(self.whole[0], block, edges, bool(self.perm[0]))
             assert tuple(out_shape) == tuple(shapes[0]), (out_shape, shapes[0])
             return ([(V.fill_view(out_shape), -2, 0)] if padded else []) + [(v, -1, 0) for v in vs]
+        if self.kind == "tile":
+            out_shape, v = V.tile_view(self.whole[0], self.perm)
+            assert tuple(out_shape) == tuple(shapes[0]), (out_shape, shapes[0])
+            return [(v, -1, 0)]
+        if self.kind == "broadcast_to":
+            return [(V.broadcast_to_view(self.whole[0], shapes[0]), -1, 0)]
         if self.kind == "channel_shuffle":
             return [(V.channel_shuffle_view(self.whole[0], self.perm[0], self.perm[1]), -1, 0)]
         if self.kind in ("permute", "transpose"):

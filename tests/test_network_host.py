@@ -244,3 +244,24 @@ def test_gather_batch_norm_instance_norm_graph_oracle_equals_armnn_cpuref(built)
     got = hostnet.OracleNetwork(Optimize(net)).run(xs)
     for k in (0, 1):
         assert want[k].shape == got[k].shape and np.array_equal(want[k], got[k]), k
+
+
+@needs_cpuref
+def test_tile_and_broadcast_to_graph_mirror_views_vs_armnn_cpuref(built):
+    import hostnet
+    from test_plugin import _repeat_inputs, _repeat_net
+    net, xs = _repeat_net(), _repeat_inputs(48)
+    want = hostnet.ArmnnNetwork(net, "CpuRef").run(xs)[0]
+    got = hostnet.OracleNetwork(Optimize(net)).run(xs)[0]
+    assert want.shape == got.shape and np.array_equal(want, got)
+
+
+@needs_cpuref
+def test_normalization_graph_oracle_equals_armnn_cpuref(built):
+    import hostnet
+    from test_plugin import _lrn_net
+    net = _lrn_net()
+    x = np.random.default_rng(54).integers(0, 256, size=(2, 6, 7, 16)).astype(np.uint8)
+    want = hostnet.ArmnnNetwork(net, "CpuRef").run({0: x})[0]
+    got = hostnet.OracleNetwork(Optimize(net)).run({0: x})[0]
+    assert want.shape == got.shape and np.array_equal(want, got)

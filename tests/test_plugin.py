@@ -913,3 +913,77 @@ def test_gather_batch_norm_instance_norm_through_the_runtime_equal_cpuref():
     ln.EnqueueWorkload(xs, ys)
     for k in (0, 1):
         assert ref[k].shape == got[k].shape and np.array_equal(ref[k], got[k]) and np.array_equal(ref[k], ys[k]), k
+
+
+def _repeat_net():
+    """Tile of a feature map and BroadcastTo of a per-channel vector, added together."""
+    from armnn_b200.network import BinaryOperation, DataType, INetwork, TensorInfo
+
+    def info(shape, scale=0.05, offset=-3):
+        return TensorInfo(tuple(shape), DataType.QAsymmS8, scale, offset)
+    net = INetwork.Create()
+    il = net.AddInputLayer(0, "map")
+    il.GetOutputSlot(0).SetTensorInfo(info((1, 3, 4, 16)))
+    tl = net.AddTileLayer((2, 2, 1, 1), "tile")
+    il.GetOutputSlot(0).Connect(tl.GetInputSlot(0))
+    tl.GetOutputSlot(0).SetTensorInfo(info((2, 6, 4, 16), 0.06, 1))                # re-quantised by the copy
+    iv = net.AddInputLayer(1, "vector")
+    iv.GetOutputSlot(0).SetTensorInfo(info((16,), 0.02, 5))
+    bl = net.AddBroadcastToLayer((2, 6, 4, 16), "broadcast")
+    iv.GetOutputSlot(0).Connect(bl.GetInputSlot(0))
+    bl.GetOutputSlot(0).SetTensorInfo(info((2, 6, 4, 16), 0.02, 5))
+    ad = net.AddElementwiseBinaryLayer(BinaryOperation.Add, "add")
+    tl.GetOutputSlot(0).Connect(ad.GetInputSlot(0))
+    bl.GetOutputSlot(0).Connect(ad.GetInputSlot(1))
+    ad.GetOutputSlot(0).SetTensorInfo(info((2, 6, 4, 16), 0.07, 0))
+    ol = net.AddOutputLayer(0, "out")
+    ad.GetOutputSlot(0).Connect(ol.GetInputSlot(0))
+    return net
+
+
+def _repeat_inputs(seed):
+    rng = np.random.default_rng(seed)
+    return {0: rng.integers(-128, 128, size=(1, 3, 4, 16)).astype(np.int8), 1: rng.integers(-128, 128, size=(16,)).astype(np.int8)}
+
+
+@needs_plugin
+@pytest.mark.gpu
+def test_tile_and_broadcast_to_through_the_runtime_equal_cpuref():
+    from armnn_b200 import network
+    net, xs = _repeat_net(), _repeat_inputs(47)
+    ref = hostnet.ArmnnNetwork(net, "CpuRef").run(xs)[0]
+    got = hostnet.ArmnnNetwork(net, "B200Acc").run(xs)[0]
+    rt = network.IRuntime.Create(0)
+    ln = rt.GetLoadedNetwork(rt.LoadNetwork(network.Optimize(net)))
+    ys = {0: np.zeros(ref.shape, ref.dtype)}
+    ln.EnqueueWorkload(xs, ys)
+    assert np.array_equal(ref, got) and np.array_equal(ref, ys[0])
+
+
+def _lrn_net():
+    """AlexNet-style local response normalisation across channels, then the within-channel variant (NCHW indexing)."""
+    from armnn_b200.network import DataType, INetwork, TensorInfo
+    net = INetwork.Create()
+    il = net.AddInputLayer(0, "input")
+    t = TensorInfo((2, 6, 7, 16), DataType.QAsymmU8, 0.05, 120)
+    il.GetOutputSlot(0).SetTensorInfo(t)
+    a = net.AddNormalizationLayer(0, 5, 1e-2, 0.75, 1.0, name="lrn_across")
+    il.GetOutputSlot(0).Connect(a.GetInputSlot(0))
+    a.GetOutputSlot(0).SetTensorInfo(t)
+    w = net.AddNormalizationLayer(1, 3, 2e-2, 0.5, 2.0, nchw=True, name="lrn_within")
+    a.GetOutputSlot(0).Connect(w.GetInputSlot(0))
+    w.GetOutputSlot(0).SetTensorInfo(t)
+    ol = net.AddOutputLayer(0, "out")
+    w.GetOutputSlot(0).Connect(ol.GetInputSlot(0))
+    return net
+
+
+@needs_plugin
+@pytest.mark.gpu
+def test_normalization_through_the_runtime_matches_cpuref():
+    net = _lrn_net()
+    x = np.random.default_rng(53).integers(0, 256, size=(2, 6, 7, 16)).astype(np.uint8)
+    ref = hostnet.ArmnnNetwork(net, "CpuRef").run({0: x})[0]
+    got = hostnet.ArmnnNetwork(net, "B200Acc").run({0: x})[0]
+    st = diff_stats(ref, got)           # powf of the device against glibc: a rounding boundary may move by one step
+    assert ref.shape == got.shape and st["max_abs"] <= 1 and st["mismatch_frac"] <= 0.01, st

@@ -176,3 +176,38 @@ def test_batch_and_space_views_refuse_shapes_that_do_not_divide():
         V.batch_to_space_views((4, 1, 1, 3), (2, 2), ((1, 1), (0, 0)))          # crops leave nothing
     with pytest.raises(ValueError):
         V.batch_to_space_views((4, 2), (2,), ((0, 0),))                         # rank 2
+
+
+def _move_cases():
+    import cases
+    return sorted(cases.move_cases().items())
+
+
+@pytest.mark.parametrize("name,factory", _move_cases(), ids=[n for n, _ in _move_cases()])
+def test_views_of_every_data_movement_case_reproduce_the_oracle(built, name, factory):
+    """The views the product derives from each descriptor, applied with numpy, against the CPU restatement of the
+    reference's loops (cases that re-quantise are covered on the GPU only: the views carry no arithmetic)."""
+    case = factory()
+    tensors = [case.whole] + list(case.parts)
+    if any(t[1:] != tensors[0][1:] for t in tensors):
+        pytest.skip("re-quantising case")
+    from q8util import Host
+    mem = Host()
+    whole, parts, outs = case._data(mem)
+    want = [o.copy() for o in case.run_oracle()]
+
+    def array(t, spec):
+        import ctypes
+        from q8util import NP_OF
+        n = int(np.prod(spec[0]))
+        return np.ctypeslib.as_array(ctypes.cast(t.data, ctypes.POINTER(np.ctypeslib.as_ctypes_type(NP_OF[spec[1]]))), shape=(n,))
+    whole_a = array(whole, case.whole)
+    part_a = [array(t, spec) for t, spec in zip(parts, case.parts)]
+    for view, si, di in case.views():
+        src = np.zeros(1, whole_a.dtype) if si == -2 else (whole_a if si < 0 else part_a[si])
+        if si == -2:
+            src[0] = case.parts[di][3]                  # the zero point: the encoding of 0.0
+        dst = whole_a if di < 0 else part_a[di]
+        apply_view(src, dst, V.merge_dims(view))
+    for w, o in zip(want, outs):
+        assert np.array_equal(w, o)
