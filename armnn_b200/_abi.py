@@ -108,7 +108,7 @@ class ConvertParams(C.Structure):
 
 class PadParams(C.Structure):
     _fields_ = [("x", QTensor), ("y", QTensor), ("rank", C.c_int32), ("shape", C.c_int32 * 4),
-                ("pad_before", C.c_int32 * 4), ("pad_after", C.c_int32 * 4), ("pad_value", C.c_float)]
+                ("pad_before", C.c_int32 * 4), ("pad_after", C.c_int32 * 4), ("pad_value", C.c_float), ("mode", C.c_int32)]
 
 
 class ViewCopyParams(C.Structure):

@@ -178,7 +178,9 @@ class ArmnnNetwork:
                 lid = lib.armnnc_add_reshape(net, len(d["shape"]), _shape_arr(d["shape"]))
             elif t == "Pad":
                 flat = [v for pair in d["pads"] for v in pair]
-                lid = lib.armnnc_add_pad(net, len(d["pads"]), (C.c_int32 * len(flat))(*flat), C.c_float(d["value"]))
+                lid = lib.armnnc_add_pad(net, len(d["pads"]), (C.c_int32 * len(flat))(*flat), C.c_float(d["value"]), int(d.get("mode", 0)))
+            elif t == "Floor":
+                lid = lib.armnnc_add_floor(net)
             elif t == "TransposeConvolution2d":
                 wl = layer.inputs[1].source.layer
                 wi = wl.outputs[0].info

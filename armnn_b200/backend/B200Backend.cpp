@@ -135,7 +135,18 @@ public:
                 // TfLite parser emits them for explicit padding, src/armnnTfLiteParser/TfLiteParser.cpp:829-830); the
                 // others run as a workload of their own
                 const auto& d = *PolymorphicDowncast<const PadDescriptor*>(&descriptor);
-                if (d.m_PaddingMode != PaddingMode::Constant) { return No(reason, "only constant padding is supported"); }
+                if (d.m_PaddingMode != PaddingMode::Constant)
+                {
+                    // MirrorPad.cpp:66-74: a mirrored border is at most as wide as the tensor (less the edge for Reflect)
+                    const unsigned int edge = d.m_PaddingMode == PaddingMode::Reflect ? 1u : 0u;
+                    for (unsigned int i = 0; i < d.m_PadList.size() && i < infos[0].GetNumDimensions(); ++i)
+                    {
+                        if (d.m_PadList[i].first + edge > infos[0].GetShape()[i] || d.m_PadList[i].second + edge > infos[0].GetShape()[i])
+                        {
+                            return No(reason, "mirrored padding wider than the tensor");
+                        }
+                    }
+                }
                 if (infos[0].GetNumDimensions() > 4) { return No(reason, "rank > 4"); }
                 return (IsActType(infos[0]) && IsActType(infos[1])) || No(reason, "unsupported data type");
             }
@@ -252,11 +263,12 @@ public:
             case LayerType::Activation:
             {
                 const auto fn = PolymorphicDowncast<const ActivationDescriptor*>(&descriptor)->m_Function;
-                if (fn == ActivationFunction::Gelu) { return No(reason, "Gelu is not supported"); }
                 return (IsActType(infos[0]) && IsActType(infos[1])) || No(reason, "unsupported data type");
             }
             case LayerType::Softmax:
                 return (IsActType(infos[0]) && IsActType(infos[1])) || No(reason, "unsupported data type");
+            case LayerType::Floor:
+                return (infos[0].GetDataType() == DataType::Float32 && infos[1].GetDataType() == DataType::Float32) || No(reason, "Float32 only");
             case LayerType::LogSoftmax:
             case LayerType::L2Normalization:
                 if (infos[0].GetDataType() == DataType::QSymmS16 && type == LayerType::LogSoftmax) { return No(reason, "QSymmS16 is not supported"); }
@@ -581,6 +593,7 @@ namespace
         if (!src || src->GetOwningLayer().GetType() != LayerType::Pad) { return nullptr; }
         auto* padLayer = PolymorphicDowncast<PadLayer*>(&src->GetOwningLayer());
         if (untouched.find(padLayer->GetGuid()) == untouched.end() || padLayer->GetOutputSlot(0).GetNumConnections() != 1) { return nullptr; }
+        if (padLayer->GetParameters().m_PaddingMode != PaddingMode::Constant) { return nullptr; }      // a mirrored border is no padding value
         bool ok;
         if constexpr (std::is_same<DescriptorT, Pooling2dDescriptor>::value)
         {

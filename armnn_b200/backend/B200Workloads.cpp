@@ -1307,6 +1307,19 @@ std::unique_ptr<IWorkload> B200WorkloadFactory::CreateWorkload(LayerType type, c
                 B200CheckStatus(b200k_instance_norm_q(&st->p, s));
             });
         }
+        case LayerType::Floor:
+        {
+            auto st = std::make_shared<SimpleState<b200k_unary_params>>(ctx);
+            std::memset(&st->p, 0, sizeof(st->p));
+            st->p.x = Operand(info.m_InputTensorInfos[0], st->blobs); st->p.y = Operand(info.m_OutputTensorInfos[0], st->blobs);
+            st->p.count = info.m_InputTensorInfos[0].GetNumElements();
+            st->p.operation = 9;
+            return Make<FloorQueueDescriptor>(d, info, ctx, [st](const FloorQueueDescriptor& data, cudaStream_t s)
+            {
+                st->p.x.data = Dev(data.m_Inputs[0]); st->p.y.data = Dev(data.m_Outputs[0]);
+                B200CheckStatus(b200k_unary_q(&st->p, s));
+            });
+        }
         case LayerType::LogSoftmax:
         {
             const auto& qd = *PolymorphicDowncast<const LogSoftmaxQueueDescriptor*>(&d);
@@ -1423,6 +1436,7 @@ std::unique_ptr<IWorkload> B200WorkloadFactory::CreateWorkload(LayerType type, c
                 p.pad_after[i] = qd.m_Parameters.m_PadList[i].second;
             }
             p.pad_value = qd.m_Parameters.m_PadValue;
+            p.mode = qd.m_Parameters.m_PaddingMode == PaddingMode::Reflect ? 1 : qd.m_Parameters.m_PaddingMode == PaddingMode::Symmetric ? 2 : 0;
             return Make<PadQueueDescriptor>(d, info, ctx, [st](const PadQueueDescriptor& data, cudaStream_t s)
             {
                 st->p.x.data = Dev(data.m_Inputs[0]); st->p.y.data = Dev(data.m_Outputs[0]);

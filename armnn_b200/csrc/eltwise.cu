@@ -81,7 +81,8 @@ __device__ __forceinline__ float activation_f(int fn, float in, float a, float b
         case 8:  return __fsqrt_rn(in);
         case 9:  return __fmul_rn(in, in);
         case 10: return (in >= 0) ? in : __fmul_rn(a, __fsub_rn(expf(in), 1.f));
-        // armnn::UnaryOperation + 100 (ElementwiseUnary): Abs, Exp, Sqrt, Rsqrt, Neg, -, Log, Sin, Ceil
+        case 12: return __fmul_rn(in, __fmul_rn(0.5f, __fadd_rn(1.0f, erff((float)((double)in / 1.4142135623730951)))));
+        // armnn::UnaryOperation + 100 (ElementwiseUnary): Abs, Exp, Sqrt, Rsqrt, Neg, -, Log, Sin, Ceil; 109: the Floor layer
         case 100: return fabsf(in);
         case 101: return expf(in);
         case 102: return __fsqrt_rn(in);
@@ -90,6 +91,7 @@ __device__ __forceinline__ float activation_f(int fn, float in, float a, float b
         case 106: return logf(in);
         case 107: return sinf(in);
         case 108: return ceilf(in);
+        case 109: return floorf(in);
         default: return __fdiv_rn(__fmul_rn(in, fminf(fmaxf(__fadd_rn(in, 3.f), 0.0f), 6.0f)), 6.f);
     }
 }
@@ -175,14 +177,14 @@ static int launch_unary(const b200k_qtensor& x, const b200k_qtensor& y, long lon
 extern "C" int b200k_activation_q8(const b200k_activation_params* p, void* stream)
 {
     B200K_REQUIRE(p, B200K_E_INVALID, "activation_q8: null params");
-    B200K_REQUIRE(p->function >= 0 && p->function <= 11, B200K_E_UNSUPPORTED, "activation_q8: unsupported activation function %d", p->function);
+    B200K_REQUIRE(p->function >= 0 && p->function <= 12, B200K_E_UNSUPPORTED, "activation_q8: unsupported activation function %d", p->function);
     return launch_unary(p->x, p->y, p->count, p->function, p->a, p->b, stream, "activation_q8");
 }
 
 extern "C" int b200k_unary_q(const b200k_unary_params* p, void* stream)
 {
     B200K_REQUIRE(p, B200K_E_INVALID, "unary_q: null params");
-    B200K_REQUIRE(p->operation >= 0 && p->operation <= 8 && p->operation != 5, B200K_E_UNSUPPORTED,
+    B200K_REQUIRE(p->operation >= 0 && p->operation <= 9 && p->operation != 5, B200K_E_UNSUPPORTED,
                   "unary_q: unsupported unary operation %d", p->operation);
     return launch_unary(p->x, p->y, p->count, 100 + p->operation, 0.f, 0.f, stream, "unary_q");
 }
@@ -197,7 +199,7 @@ extern "C" int b200k_convert_q(const b200k_convert_params* p, void* stream)
 
 namespace b200k {
 
-struct PadArgs { QView x, y; int rank; int in_shape[4], out_shape[4], before[4]; float pad_value; long long count; };
+struct PadArgs { QView x, y; int rank; int in_shape[4], out_shape[4], before[4]; float pad_value; long long count; int mode; };
 
 // armnn::Pad (src/backends/reference/workloads/Pad.cpp:37-170): every output element is either the input element at
 // the shifted position, re-encoded with the output's quantisation, or the pad value.  For a quantised output the
@@ -213,7 +215,13 @@ __global__ void __launch_bounds__(256) pad_kernel(const PadArgs a)
     int coord[4];
     for (int d = a.rank - 1; d >= 0; --d) { coord[d] = (int)(rest % a.out_shape[d]); rest /= a.out_shape[d]; }
     for (int d = a.rank - 1; d >= 0; --d) {
-        const int c = coord[d] - a.before[d];
+        int c = coord[d] - a.before[d];
+        if (a.mode != 0) {
+            // armnn::MirrorPad (MirrorPad.cpp:95-125): Reflect (1) mirrors about the edge element, Symmetric (2) repeats it
+            const int n = a.in_shape[d], edge = a.mode == 1 ? 0 : 1;
+            if (c < 0) c = -c - edge;
+            else if (c >= n) c = 2 * n - 2 + edge - c;
+        }
         inside = inside && c >= 0 && c < a.in_shape[d];
         src += (long long)c * stride;
         stride *= a.in_shape[d];
@@ -233,11 +241,15 @@ extern "C" int b200k_pad_q(const b200k_pad_params* p, void* stream)
     B200K_REQUIRE(p->x.dtype != B200K_S32 && p->y.dtype != B200K_S32, B200K_E_UNSUPPORTED, "pad_q: Signed32 not supported");
     PadArgs a;
     a.x = make_view(p->x); a.y = make_view(p->y);
-    a.rank = p->rank; a.pad_value = p->pad_value;
+    a.rank = p->rank; a.pad_value = p->pad_value; a.mode = p->mode;
+    B200K_REQUIRE(p->mode >= 0 && p->mode <= 2, B200K_E_INVALID, "pad_q: padding mode %d is not Constant (0), Reflect (1) or Symmetric (2)", p->mode);
     a.count = 1;
     for (int d = 0; d < 4; ++d) { a.in_shape[d] = a.out_shape[d] = 1; a.before[d] = 0; }
     for (int d = 0; d < p->rank; ++d) {
         B200K_REQUIRE(p->shape[d] > 0 && p->pad_before[d] >= 0 && p->pad_after[d] >= 0, B200K_E_INVALID, "pad_q: bad shape / padding");
+        // MirrorPad.cpp:66-74: a mirrored border cannot be wider than the tensor (less its edge element for Reflect)
+        B200K_REQUIRE(p->mode == 0 || (p->pad_before[d] <= p->shape[d] - (p->mode == 1) && p->pad_after[d] <= p->shape[d] - (p->mode == 1)),
+                      B200K_E_INVALID, "pad_q: mirrored padding wider than dimension %d", d);
         a.in_shape[d] = p->shape[d]; a.before[d] = p->pad_before[d];
         a.out_shape[d] = p->shape[d] + p->pad_before[d] + p->pad_after[d];
         a.count *= a.out_shape[d];

@@ -371,12 +371,19 @@ int armnnc_add_qlstm(void* vn, const b200k_qlstm_params* p)
 }
 
 // pads: rank pairs (before, after), outermost dimension first
-int armnnc_add_pad(void* vn, int rank, const int32_t* pads, float pad_value)
+int armnnc_add_floor(void* vn)
+{
+    auto* n = static_cast<CNet*>(vn);
+    return add_layer(n, n->net->AddFloorLayer());
+}
+
+int armnnc_add_pad(void* vn, int rank, const int32_t* pads, float pad_value, int mode)
 {
     auto* n = static_cast<CNet*>(vn);
     PadDescriptor d;
     for (int i = 0; i < rank; ++i) d.m_PadList.emplace_back((unsigned)pads[2 * i], (unsigned)pads[2 * i + 1]);
     d.m_PadValue = pad_value;
+    d.m_PaddingMode = mode == 1 ? PaddingMode::Reflect : mode == 2 ? PaddingMode::Symmetric : PaddingMode::Constant;
     return add_layer(n, n->net->AddPadLayer(d));
 }
 

@@ -44,6 +44,7 @@ class ActivationFunction(IntEnum):  # include/armnn/Types.hpp:86-101
     Square = 9
     Elu = 10
     HardSwish = 11
+    Gelu = 12
 
 
 class BinaryOperation(IntEnum):     # include/armnn/Types.hpp:138-149
@@ -256,11 +257,16 @@ class INetwork:
     def AddReshapeLayer(self, target_shape, name=None):
         return self._add(Layer("Reshape", name, 1, 1, {"shape": tuple(target_shape)}))
 
-    def AddPadLayer(self, pad_list, pad_value=0.0, name=None):
+    def AddPadLayer(self, pad_list, pad_value=0.0, name=None, padding_mode=0):
         """pad_list: one (before, after) pair per dimension, outermost first (armnn::PadDescriptor::m_PadList);
         constant padding with pad_value — for quantised tensors a quantised number (normally the zero point), as
-        armnn::Pad takes it (src/backends/reference/workloads/Pad.cpp:76-83)."""
-        return self._add(Layer("Pad", name, 1, 1, {"pads": tuple((int(a), int(b)) for a, b in pad_list), "value": float(pad_value)}))
+        armnn::Pad takes it (src/backends/reference/workloads/Pad.cpp:76-83).  padding_mode follows armnn::PaddingMode:
+        0 Constant, 1 Reflect, 2 Symmetric (workloads/MirrorPad.cpp)."""
+        return self._add(Layer("Pad", name, 1, 1, {"pads": tuple((int(a), int(b)) for a, b in pad_list), "value": float(pad_value),
+                                                   "mode": int(padding_mode)}))
+
+    def AddFloorLayer(self, name=None):
+        return self._add(Layer("Floor", name, 1, 1, {}))
 
     def AddConcatLayer(self, view_origins, name=None):
         """view_origins: per input, the coordinates of its block in the output (armnn::OriginsDescriptor)."""
@@ -470,6 +476,15 @@ def IsLayerSupported(layer):
     if t == "Pad":
         if len(ins[0].shape) > 4:
             return False, "Pad: rank > 4"
+        mode = layer.desc.get("mode", 0)
+        if mode not in (0, 1, 2):
+            return False, "Pad: unknown padding mode"
+        if mode and any(max(a, b) + (mode == 1) > n for (a, b), n in zip(layer.desc["pads"], ins[0].shape)):
+            return False, "Pad: mirrored padding wider than the tensor"
+        return True, ""
+    if t == "Floor":
+        if ins[0].dtype != DataType.Float32 or outs[0].dtype != DataType.Float32:
+            return False, "Floor: Float32 only"
         return True, ""
     if t == "ElementwiseUnary":
         ok = (DataType.QAsymmU8, DataType.QAsymmS8, DataType.QSymmS16, DataType.Float32)
@@ -1040,7 +1055,15 @@ class GraphProgram:
         for i, (before, after) in enumerate(layer.desc["pads"]):
             p.shape[i], p.pad_before[i], p.pad_after[i] = x.info.shape[i], before, after
         p.pad_value = layer.desc["value"]
+        p.mode = layer.desc.get("mode", 0)
         return "pad_q", p
+
+    def _make_Floor(self, layer):
+        x, y = layer.inputs[0].source, layer.outputs[0]
+        p = _abi.UnaryParams()
+        p.x, p.y = self._operand(x), self._operand(y)
+        p.count, p.operation = x.info.GetNumElements(), 9
+        return "unary_q", p
 
     def _make_Resize(self, layer):
         x, y, d = layer.inputs[0].source, layer.outputs[0], layer.desc

@@ -234,7 +234,7 @@ int b200k_eltwise_q8(const b200k_eltwise_params* p, void* stream);
 /* armnn::Activation (src/backends/reference/workloads/Activation.cpp:13-119).
  * function follows armnn::ActivationFunction numbering (include/armnn/Types.hpp):
  * 0 Sigmoid, 1 TanH, 2 Linear, 3 ReLu, 4 BoundedReLu, 5 SoftReLu, 6 LeakyReLu, 7 Abs, 8 Sqrt,
- * 9 Square, 10 Elu, 11 HardSwish. */
+ * 9 Square, 10 Elu, 11 HardSwish, 12 Gelu (x / 2 * (1 + erf(x / sqrt(2))), the quotient in double precision). */
 typedef struct {
     b200k_qtensor x, y;
     int64_t count;
@@ -247,7 +247,7 @@ int b200k_activation_q8(const b200k_activation_params* p, void* stream);
 /* armnn::ElementwiseUnary (src/backends/reference/workloads/RefElementwiseUnaryWorkload.cpp:36-110 with Abs.hpp, Exp.hpp,
  * Sqrt.hpp, Rsqrt.hpp, Log.hpp, Sin.hpp, Ceil.hpp and std::negate): y = Q_y(f(deq_x(x))); operation follows
  * armnn::UnaryOperation (0 Abs, 1 Exp, 2 Sqrt, 3 Rsqrt = 1 / sqrt, 4 Neg, 6 Log, 7 Sin, 8 Ceil; 5 LogicalNot is a
- * Boolean operation and not supported). */
+ * Boolean operation and not supported); 9 is the separate armnn::Floor layer (RefFloorWorkload.cpp: floorf). */
 typedef struct {
     b200k_qtensor x, y;
     int64_t count;
@@ -267,6 +267,7 @@ typedef struct {
     int32_t shape[4];
     int32_t pad_before[4], pad_after[4];
     float pad_value;
+    int32_t mode;               /* armnn::PaddingMode: 0 Constant, 1 Reflect, 2 Symmetric (MirrorPad.cpp:42-150; pad_value unused) */
 } b200k_pad_params;
 
 int b200k_pad_q(const b200k_pad_params* p, void* stream);

@@ -529,6 +529,7 @@ extern "C" int cpuref_pad_q(const b200k_pad_params* p)
             d.m_Parameters.m_PadList.emplace_back((unsigned)p->pad_before[i], (unsigned)p->pad_after[i]);
         }
         d.m_Parameters.m_PadValue = p->pad_value;
+        d.m_Parameters.m_PaddingMode = p->mode == 1 ? PaddingMode::Reflect : p->mode == 2 ? PaddingMode::Symmetric : PaddingMode::Constant;
         TensorInfo xi = make_info(p->x, TensorShape((unsigned)p->rank, in_dims), 0, 0, false);
         TensorInfo yi = make_info(p->y, TensorShape((unsigned)p->rank, out_dims), 0, 0, false);
         h.in(d, xi, p->x.data);
@@ -542,10 +543,19 @@ extern "C" int cpuref_unary_q(const b200k_unary_params* p)
 {
     return guarded([&] {
         Harness h;
-        ElementwiseUnaryQueueDescriptor d;
-        d.m_Parameters.m_Operation = static_cast<UnaryOperation>(p->operation);
         const TensorShape shape({(unsigned)p->count});
         TensorInfo xi = make_info(p->x, shape, 0, 0, false), yi = make_info(p->y, shape, 0, 0, false);
+        if (p->operation == 9)                     // the Floor layer
+        {
+            FloorQueueDescriptor fd;
+            h.in(fd, xi, p->x.data);
+            ITensorHandle* fo = h.out(fd, yi);
+            h.run(LayerType::Floor, fd);
+            copy_out(fo, const_cast<void*>(p->y.data), yi.GetNumBytes());
+            return;
+        }
+        ElementwiseUnaryQueueDescriptor d;
+        d.m_Parameters.m_Operation = static_cast<UnaryOperation>(p->operation);
         h.in(d, xi, p->x.data);
         ITensorHandle* o = h.out(d, yi);
         h.run(LayerType::ElementwiseUnary, d);

@@ -495,6 +495,7 @@ static float activation_f(float in, int fn, float a, float b)
         case 10: return (in >= 0) ? in : a * (expf(in) - 1);
         case 11: { volatile float t = in + 3; float r = t > 0.0f ? t : 0.0f; r = r < 6.0f ? r : 6.0f;
                    volatile float m = in * r; return m / 6; }
+        case 12: return in * (0.5f * (1.0f + erff((float)(in / sqrt(2.0)))));          /* Activation.cpp:85-91 */
         default: return NAN;
     }
 }
@@ -502,7 +503,7 @@ static float activation_f(float in, int fn, float a, float b)
 /* ElementwiseUnary, RefElementwiseUnaryWorkload.cpp:36-110: y = Q_y(f(deq_x(x))) with the std:: function of the operation */
 int oracle_unary_q(const b200k_unary_params* p)
 {
-    if (!p || !p->x.data || !p->y.data || p->operation < 0 || p->operation > 8 || p->operation == 5) return B200K_E_INVALID;
+    if (!p || !p->x.data || !p->y.data || p->operation < 0 || p->operation > 9 || p->operation == 5) return B200K_E_INVALID;
     for (int64_t i = 0; i < p->count; ++i) {
         const float in = load_f(&p->x, i);
         float r;
@@ -514,6 +515,7 @@ int oracle_unary_q(const b200k_unary_params* p)
             case 4: r = -in; break;
             case 6: r = logf(in); break;
             case 7: r = sinf(in); break;
+            case 9: r = floorf(in); break;                 /* RefFloorWorkload.cpp */
             default: r = ceilf(in); break;
         }
         store_f(&p->y, i, r);
@@ -523,7 +525,7 @@ int oracle_unary_q(const b200k_unary_params* p)
 
 int oracle_activation_q8(const b200k_activation_params* p)
 {
-    if (!p->x.data || !p->y.data || p->function < 0 || p->function > 11) return B200K_E_INVALID;
+    if (!p->x.data || !p->y.data || p->function < 0 || p->function > 12) return B200K_E_INVALID;
     for (int64_t i = 0; i < p->count; ++i)
         store_f(&p->y, i, activation_f(load_f(&p->x, i), p->function, p->a, p->b));
     return 0;
@@ -782,7 +784,12 @@ int oracle_pad_q(const b200k_pad_params* p)
         int coord[4] = {0, 0, 0, 0}, inside = 1;
         for (int d = p->rank - 1; d >= 0; --d) { coord[d] = (int)(rest % out_shape[d]); rest /= out_shape[d]; }
         for (int d = p->rank - 1; d >= 0; --d) {
-            const int c = coord[d] - before[d];
+            int c = coord[d] - before[d];
+            if (p->mode != 0) {                            /* MirrorPad.cpp:95-125 */
+                const int n = in_shape[d], edge = p->mode == 1 ? 0 : 1;
+                if (c < 0) c = -c - edge;
+                else if (c >= n) c = 2 * n - 2 + edge - c;
+            }
             if (c < 0 || c >= in_shape[d]) inside = 0;
             src += (int64_t)c * stride;
             stride *= in_shape[d];

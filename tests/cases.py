@@ -279,12 +279,13 @@ def activation_cases():
         "leaky_relu": make(86, 6, 0.1, 0), "abs": make(87, 7, 0, 0), "square": make(88, 9, 0, 0, out_q=(0.3, -128)),
         "hard_swish": make(89, 11, 0, 0, count=1003), "sqrt_u8": make(90, 8, 0, 0, dtype=U8, in_q=(0.05, 0), out_q=(0.02, 0)),
         "elu": make(91, 10, 1.0, 0), "soft_relu": make(92, 5, 0, 0),
+        "gelu": make(93, 12, 0, 0, in_q=(0.04, 0), out_q=(0.04, 0)), "gelu_u8": make(94, 12, 0, 0, dtype=U8, in_q=(0.03, 128), out_q=(0.016, 11)),
     }
 
 
 # activations that go through libm exp / tanh / log: the CUDA and glibc implementations may differ in the last
 # ulp, which can move a value across a rounding boundary
-TRANSCENDENTAL_ACTIVATIONS = ("sigmoid_u8", "tanh", "elu", "soft_relu")
+TRANSCENDENTAL_ACTIVATIONS = ("sigmoid_u8", "tanh", "elu", "soft_relu", "gelu", "gelu_u8")
 
 
 def softmax_cases():
@@ -503,10 +504,11 @@ def convert_cases():
 
 
 def pad_cases():
-    def make(seed, shape, pads, value, dtype=S8, xq=(0.05, -7), yq=None):
+    def make(seed, shape, pads, value, dtype=S8, xq=(0.05, -7), yq=None, mode=0):
         def build(mem):
             rng = np.random.default_rng(seed)
             p = _abi.PadParams()
+            p.mode = mode
             p.x = qt(mem, _rand(rng, dtype, shape) if dtype != F32 else rng.standard_normal(shape).astype(np.float32), dtype, *xq)
             out_shape = tuple(s + a + b for s, (a, b) in zip(shape, pads))
             p.y, y = qt_out(mem, out_shape, dtype, *(yq or xq))
@@ -522,6 +524,10 @@ def pad_cases():
         "rank2_requantise": make(133, (7, 11), ((3, 0), (0, 5)), 9, xq=(0.05, 2), yq=(0.08, -4)),
         "rank1": make(134, (33,), ((4, 4),), -128),
         "rank3_float": make(135, (3, 4, 5), ((1, 0), (0, 2), (1, 1)), 1.5, dtype=F32, xq=(1.0, 0)),
+        "reflect_nhwc_hw": make(136, (2, 6, 5, 8), ((0, 0), (2, 3), (4, 1), (0, 0)), 0, mode=1),
+        "reflect_widest_u8_requantise": make(137, (3, 4), ((2, 2), (3, 3)), 0, dtype=U8, xq=(0.1, 128), yq=(0.13, 100), mode=1),
+        "symmetric_nhwc_hw": make(138, (1, 5, 7, 6), ((0, 0), (1, 2), (3, 3), (0, 0)), 0, mode=2),
+        "symmetric_widest_float": make(139, (2, 3, 4), ((2, 2), (3, 3), (0, 4)), 0, dtype=F32, xq=(1.0, 0), mode=2),
     }
 
 
@@ -647,8 +653,9 @@ def unary_cases():
             p.count, p.operation = count, op
             return p, [y]
         return lambda: SimpleCase("unary_q", build)
-    ABS, EXP, SQRT, RSQRT, NEG, LOG, SIN, CEIL = 0, 1, 2, 3, 4, 6, 7, 8
+    ABS, EXP, SQRT, RSQRT, NEG, LOG, SIN, CEIL, FLOOR = 0, 1, 2, 3, 4, 6, 7, 8, 9
     return {
+        "floor_layer_float": make(371, 333, FLOOR, dtype=F32, xq=(1.0, 0)),
         "abs_s8": make(361, 1000, ABS),
         "neg_u8_requantise": make(362, 777, NEG, dtype=U8, xq=(0.1, 128), yq=(0.12, 120)),
         "sqrt_u8": make(363, 513, SQRT, dtype=U8, xq=(0.07, 10), yq=(0.02, 0), positive=True),

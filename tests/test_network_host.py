@@ -265,3 +265,14 @@ def test_normalization_graph_oracle_equals_armnn_cpuref(built):
     want = hostnet.ArmnnNetwork(net, "CpuRef").run({0: x})[0]
     got = hostnet.OracleNetwork(Optimize(net)).run({0: x})[0]
     assert want.shape == got.shape and np.array_equal(want, got)
+
+
+@needs_cpuref
+def test_mirror_pad_gelu_floor_graph_oracle_equals_armnn_cpuref(built):
+    import hostnet
+    from test_plugin import _gelu_floor_mirror_inputs, _gelu_floor_mirror_net
+    net, xs = _gelu_floor_mirror_net(), _gelu_floor_mirror_inputs(60)
+    want = hostnet.ArmnnNetwork(net, "CpuRef").run(xs)
+    got = hostnet.OracleNetwork(Optimize(net)).run(xs)
+    for k in range(4):
+        assert want[k].shape == got[k].shape and np.array_equal(want[k], got[k]), k

@@ -987,3 +987,49 @@ def test_normalization_through_the_runtime_matches_cpuref():
     got = hostnet.ArmnnNetwork(net, "B200Acc").run({0: x})[0]
     st = diff_stats(ref, got)           # powf of the device against glibc: a rounding boundary may move by one step
     assert ref.shape == got.shape and st["max_abs"] <= 1 and st["mismatch_frac"] <= 0.01, st
+
+
+def _gelu_floor_mirror_net():
+    """Float32: MirrorPad (Reflect) -> Gelu -> Floor; quantised: MirrorPad (Symmetric) -> Gelu."""
+    from armnn_b200.network import ActivationFunction, DataType, INetwork, TensorInfo
+    net = INetwork.Create()
+    fi = net.AddInputLayer(0, "float_input")
+    fi.GetOutputSlot(0).SetTensorInfo(TensorInfo((1, 5, 6, 4), DataType.Float32))
+    fp = net.AddPadLayer(((0, 0), (2, 1), (3, 3), (0, 0)), 0.0, "reflect", padding_mode=1)
+    fi.GetOutputSlot(0).Connect(fp.GetInputSlot(0))
+    fp.GetOutputSlot(0).SetTensorInfo(TensorInfo((1, 8, 12, 4), DataType.Float32))
+    fg = net.AddActivationLayer(ActivationFunction.Gelu, name="gelu_float")
+    fp.GetOutputSlot(0).Connect(fg.GetInputSlot(0))
+    fg.GetOutputSlot(0).SetTensorInfo(TensorInfo((1, 8, 12, 4), DataType.Float32))
+    ff = net.AddFloorLayer("floor")
+    fp.GetOutputSlot(0).Connect(ff.GetInputSlot(0))
+    ff.GetOutputSlot(0).SetTensorInfo(TensorInfo((1, 8, 12, 4), DataType.Float32))
+    qi = net.AddInputLayer(1, "quantised_input")
+    qi.GetOutputSlot(0).SetTensorInfo(TensorInfo((2, 4, 5, 8), DataType.QAsymmS8, 0.04, 2))
+    qp = net.AddPadLayer(((0, 0), (4, 2), (1, 5), (0, 0)), 0.0, "symmetric", padding_mode=2)
+    qi.GetOutputSlot(0).Connect(qp.GetInputSlot(0))
+    qp.GetOutputSlot(0).SetTensorInfo(TensorInfo((2, 10, 11, 8), DataType.QAsymmS8, 0.04, 2))
+    qg = net.AddActivationLayer(ActivationFunction.Gelu, name="gelu_quantised")
+    qp.GetOutputSlot(0).Connect(qg.GetInputSlot(0))
+    qg.GetOutputSlot(0).SetTensorInfo(TensorInfo((2, 10, 11, 8), DataType.QAsymmS8, 0.04, -100))
+    for k, l in enumerate((fg, ff, qp, qg)):
+        o = net.AddOutputLayer(k, "out%d" % k)
+        l.GetOutputSlot(0).Connect(o.GetInputSlot(0))
+    return net
+
+
+def _gelu_floor_mirror_inputs(seed):
+    rng = np.random.default_rng(seed)
+    return {0: (rng.standard_normal((1, 5, 6, 4)) * 2).astype(np.float32), 1: rng.integers(-128, 128, size=(2, 4, 5, 8)).astype(np.int8)}
+
+
+@needs_plugin
+@pytest.mark.gpu
+def test_mirror_pad_gelu_floor_through_the_runtime_match_cpuref():
+    net, xs = _gelu_floor_mirror_net(), _gelu_floor_mirror_inputs(59)
+    ref = hostnet.ArmnnNetwork(net, "CpuRef").run(xs)
+    got = hostnet.ArmnnNetwork(net, "B200Acc").run(xs)
+    assert np.array_equal(ref[1], got[1]) and np.array_equal(ref[2], got[2])          # Floor of the mirrored tensor, the mirrored bytes
+    assert np.allclose(ref[0], got[0], rtol=1e-6, atol=1e-7)                          # erff of the device against glibc
+    st = diff_stats(ref[3], got[3])
+    assert st["max_abs"] <= 1 and st["mismatch_frac"] <= 0.01, st
