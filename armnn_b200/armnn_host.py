@@ -15,7 +15,17 @@ import os
 import numpy as np
 
 from . import _abi
-from .network import _ABI_DTYPE, _NP_DTYPE
+from .network import _ABI_DTYPE as _KERNEL_DTYPE, _NP_DTYPE, DataType
+
+
+class _BridgeDtype(dict):
+    """Element type codes of the bridge to the Arm NN runtime: the C ABI's codes, plus 5 for Boolean (which the kernels see
+    as bytes)."""
+    def __missing__(self, key):
+        return 5 if key == DataType.Boolean else _KERNEL_DTYPE[key]
+
+
+_ABI_DTYPE = _BridgeDtype()
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(_HERE)
@@ -145,6 +155,10 @@ class ArmnnNetwork:
                                             d["stride"][1], d["pad"][0], d["pad"][1], d["pad"][2], d["pad"][3])
             elif t == "ElementwiseBinary":
                 lid = lib.armnnc_add_elementwise_binary(net, int(d["op"]))
+            elif t == "Comparison":
+                lid = lib.armnnc_add_comparison(net, d["op"])
+            elif t == "LogicalBinary":
+                lid = lib.armnnc_add_logical_binary(net, d["op"])
             elif t == "BatchMatMul":
                 lid = lib.armnnc_add_batch_matmul(net, int(d["tx"]), int(d["ty"]), int(d.get("ax", False)), int(d.get("ay", False)))
             elif t == "Normalization":

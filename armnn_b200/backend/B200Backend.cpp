@@ -162,7 +162,10 @@ public:
             case LayerType::ElementwiseUnary:
             {
                 const auto op = PolymorphicDowncast<const ElementwiseUnaryDescriptor*>(&descriptor)->m_Operation;
-                if (op == UnaryOperation::LogicalNot) { return No(reason, "LogicalNot is not supported"); }
+                if (op == UnaryOperation::LogicalNot)
+                {
+                    return (infos[0].GetDataType() == DataType::Boolean && infos[1].GetDataType() == DataType::Boolean) || No(reason, "LogicalNot takes Boolean tensors");
+                }
                 if (!IsActType(infos[0]) || infos[0].GetDataType() != infos[1].GetDataType()) { return No(reason, "unsupported or mismatched data types"); }
                 return true;
             }
@@ -242,6 +245,17 @@ public:
                 // on the general one (armnn::Reduce, src/backends/reference/workloads/Reduce.cpp:63-175)
                 if (infos[0].GetNumDimensions() > 6) { return No(reason, "rank > 6"); }
                 return (IsActType(infos[0]) && IsActType(infos[1])) || No(reason, "unsupported data type");
+            }
+            case LayerType::Comparison:
+            case LayerType::LogicalBinary:
+            {
+                const bool logical = type == LayerType::LogicalBinary;
+                if (infos[2].GetDataType() != DataType::Boolean) { return No(reason, "the output must be Boolean"); }
+                if (infos[2].GetNumDimensions() > 4 || infos[0].GetNumDimensions() != infos[2].GetNumDimensions() ||
+                    infos[1].GetNumDimensions() != infos[2].GetNumDimensions()) { return No(reason, "operands of one rank <= 4"); }
+                if (infos[0].GetDataType() != infos[1].GetDataType()) { return No(reason, "input types differ"); }
+                if (logical) { return infos[0].GetDataType() == DataType::Boolean || No(reason, "LogicalBinary takes Boolean tensors"); }
+                return (IsActType(infos[0]) || infos[0].GetDataType() == DataType::Boolean) || No(reason, "unsupported data type");
             }
             case LayerType::Addition:
             case LayerType::Multiplication:

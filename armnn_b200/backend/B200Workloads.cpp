@@ -32,6 +32,7 @@ int ToB200k(DataType t)
 {
     switch (t)
     {
+        case DataType::Boolean:                           // one byte per element; Operand() gives it scale 1, zero point 0
         case DataType::QAsymmU8: return B200K_U8;
         case DataType::QAsymmS8:
         case DataType::QSymmS8:  return B200K_S8;
@@ -883,7 +884,8 @@ std::unique_ptr<IWorkload> MakeEltwise(const QueueDescriptor& d, const WorkloadI
         p.shape_out[i] = static_cast<int32_t>(o.GetShape()[static_cast<unsigned>(i)]);
     }
     p.op = op;
-    if (o.GetDataType() != DataType::Float32) { Clamp(act, o, p.clamp_lo, p.clamp_hi); }
+    if (o.GetDataType() == DataType::Boolean) { p.clamp_lo = 0; p.clamp_hi = 255; }
+    else if (o.GetDataType() != DataType::Float32) { Clamp(act, o, p.clamp_lo, p.clamp_hi); }
     auto fn = [st](const QueueDescriptor& data, cudaStream_t s)
     {
         b200k_eltwise_params& q = st->p;
@@ -893,7 +895,7 @@ std::unique_ptr<IWorkload> MakeEltwise(const QueueDescriptor& d, const WorkloadI
     ARMNN_NO_DEPRECATE_WARN_BEGIN
     return EltwiseWrap<ElementwiseBinaryQueueDescriptor, AdditionQueueDescriptor, MultiplicationQueueDescriptor,
                        SubtractionQueueDescriptor, DivisionQueueDescriptor, MaximumQueueDescriptor, MinimumQueueDescriptor,
-                       PreluQueueDescriptor>::Make(d, info, ctx, fn);
+                       PreluQueueDescriptor, ComparisonQueueDescriptor, LogicalBinaryQueueDescriptor>::Make(d, info, ctx, fn);
     ARMNN_NO_DEPRECATE_WARN_END
 }
 
@@ -1073,6 +1075,10 @@ std::unique_ptr<IWorkload> B200WorkloadFactory::CreateWorkload(LayerType type, c
             return MakeEltwise(d, info, ctx, static_cast<int32_t>(BinaryOperation::Minimum), d.GetAdditionalInformation<ActivationDescriptor>());
         case LayerType::Prelu:
             return MakeEltwise(d, info, ctx, B200K_ELTWISE_PRELU, nullptr);
+        case LayerType::Comparison:
+            return MakeEltwise(d, info, ctx, 200 + static_cast<int32_t>(PolymorphicDowncast<const ComparisonQueueDescriptor*>(&d)->m_Parameters.m_Operation), nullptr);
+        case LayerType::LogicalBinary:
+            return MakeEltwise(d, info, ctx, 210 + static_cast<int32_t>(PolymorphicDowncast<const LogicalBinaryQueueDescriptor*>(&d)->m_Parameters.m_Operation), nullptr);
         case LayerType::Activation:
         {
             const auto& qd = *PolymorphicDowncast<const ActivationQueueDescriptor*>(&d);

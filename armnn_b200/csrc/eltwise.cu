@@ -20,6 +20,15 @@ __device__ __forceinline__ float binary_op(int op, float a, float b)
         case 7:  return powf(a, b);
         case 8:  return (float)floor((double)a / (double)b);
         case 100: return a < 0.f ? __fmul_rn(b, a) : a;      // Prelu: b is alpha
+        // armnn::ComparisonOperation + 200 and armnn::LogicalBinaryOperation + 210: 1.0 or 0.0, stored as a Boolean byte
+        case 200: return a == b ? 1.f : 0.f;
+        case 201: return a > b ? 1.f : 0.f;
+        case 202: return a >= b ? 1.f : 0.f;
+        case 203: return a < b ? 1.f : 0.f;
+        case 204: return a <= b ? 1.f : 0.f;
+        case 205: return a != b ? 1.f : 0.f;
+        case 210: return (a != 0.f && b != 0.f) ? 1.f : 0.f;
+        case 211: return (a != 0.f || b != 0.f) ? 1.f : 0.f;
         default: { float d = __fsub_rn(a, b); return __fmul_rn(d, d); }
     }
 }
@@ -88,6 +97,7 @@ __device__ __forceinline__ float activation_f(int fn, float in, float a, float b
         case 102: return __fsqrt_rn(in);
         case 103: return __fdiv_rn(1.f, __fsqrt_rn(in));
         case 104: return -in;
+        case 105: return in != 0.f ? 0.f : 1.f;           // LogicalNot of a Boolean byte
         case 106: return logf(in);
         case 107: return sinf(in);
         case 108: return ceilf(in);
@@ -122,7 +132,8 @@ extern "C" int b200k_eltwise_q8(const b200k_eltwise_params* p, void* stream)
     B200K_REQUIRE(p, B200K_E_INVALID, "eltwise_q8: null params");
     B200K_REQUIRE(p->a.data && p->b.data && p->out.data, B200K_E_INVALID, "eltwise_q8: null tensor pointer");
     B200K_REQUIRE(p->rank >= 1 && p->rank <= 4, B200K_E_UNSUPPORTED, "eltwise_q8: rank %d not in [1,4]", p->rank);
-    B200K_REQUIRE((p->op >= 0 && p->op <= 8) || p->op == B200K_ELTWISE_PRELU, B200K_E_UNSUPPORTED, "eltwise_q8: unsupported binary operation %d", p->op);
+    B200K_REQUIRE((p->op >= 0 && p->op <= 8) || p->op == B200K_ELTWISE_PRELU || (p->op >= 200 && p->op <= 205) || p->op == 210 || p->op == 211,
+                  B200K_E_UNSUPPORTED, "eltwise_q8: unsupported binary operation %d", p->op);
     B200K_REQUIRE(p->a.dtype != B200K_S32 && p->b.dtype != B200K_S32 && p->out.dtype != B200K_S32, B200K_E_UNSUPPORTED,
                   "eltwise_q8: Signed32 not supported");
     EltArgs e;
@@ -184,7 +195,7 @@ extern "C" int b200k_activation_q8(const b200k_activation_params* p, void* strea
 extern "C" int b200k_unary_q(const b200k_unary_params* p, void* stream)
 {
     B200K_REQUIRE(p, B200K_E_INVALID, "unary_q: null params");
-    B200K_REQUIRE(p->operation >= 0 && p->operation <= 9 && p->operation != 5, B200K_E_UNSUPPORTED,
+    B200K_REQUIRE(p->operation >= 0 && p->operation <= 9, B200K_E_UNSUPPORTED,
                   "unary_q: unsupported unary operation %d", p->operation);
     return launch_unary(p->x, p->y, p->count, 100 + p->operation, 0.f, 0.f, stream, "unary_q");
 }

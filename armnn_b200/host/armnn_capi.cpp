@@ -31,6 +31,7 @@ DataType act_type(int dt)
         case B200K_S8:  return DataType::QAsymmS8;
         case B200K_S16: return DataType::QSymmS16;
         case B200K_S32: return DataType::Signed32;
+        case 5:         return DataType::Boolean;         // bridge only: the kernels see a Boolean tensor as bytes
         default:        return DataType::Float32;
     }
 }
@@ -44,7 +45,7 @@ TensorInfo make_info(const b200k_qtensor& t, const TensorShape& shape, unsigned 
         if (t.dtype == B200K_S8) info.SetDataType(DataType::QSymmS8);
         info.SetQuantizationScales(std::vector<float>(t.scales, t.scales + n_axis));
         info.SetQuantizationDim(Optional<unsigned int>(axis_dim));
-    } else if (t.dtype != B200K_F32) {
+    } else if (t.dtype != B200K_F32 && t.dtype != 5) {
         info.SetQuantizationScale(t.scale);
         info.SetQuantizationOffset(t.zero_point);
     }
@@ -286,6 +287,18 @@ int armnnc_add_arg_min_max(void* vn, int function, int axis)
     auto* n = static_cast<CNet*>(vn);
     ArgMinMaxDescriptor d; d.m_Function = function ? ArgMinMaxFunction::Max : ArgMinMaxFunction::Min; d.m_Axis = axis;
     return add_layer(n, n->net->AddArgMinMaxLayer(d));
+}
+
+int armnnc_add_comparison(void* vn, int op)
+{
+    auto* n = static_cast<CNet*>(vn);
+    return add_layer(n, n->net->AddComparisonLayer(ComparisonDescriptor(static_cast<ComparisonOperation>(op))));
+}
+
+int armnnc_add_logical_binary(void* vn, int op)
+{
+    auto* n = static_cast<CNet*>(vn);
+    return add_layer(n, n->net->AddLogicalBinaryLayer(LogicalBinaryDescriptor(static_cast<LogicalBinaryOperation>(op))));
 }
 
 int armnnc_add_softmax(void* vn, float beta, int axis)

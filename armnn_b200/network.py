@@ -26,6 +26,7 @@ class DataType(IntEnum):            # include/armnn/Types.hpp:48-60
     Float32 = 1
     QAsymmU8 = 2
     Signed32 = 3
+    Boolean = 4
     QSymmS16 = 5
     QSymmS8 = 6
     QAsymmS8 = 7
@@ -70,10 +71,11 @@ class PaddingMethod(IntEnum):
     Exclude = 1
 
 
+# a Boolean tensor travels through the C ABI as bytes with scale 1 and zero point 0 (non-zero = true, results 0 or 1)
 _ABI_DTYPE = {DataType.Float32: _abi.F32, DataType.QAsymmU8: _abi.U8, DataType.Signed32: _abi.S32,
-              DataType.QSymmS16: _abi.S16, DataType.QSymmS8: _abi.S8, DataType.QAsymmS8: _abi.S8}
+              DataType.QSymmS16: _abi.S16, DataType.QSymmS8: _abi.S8, DataType.QAsymmS8: _abi.S8, DataType.Boolean: _abi.U8}
 _NP_DTYPE = {DataType.Float32: np.float32, DataType.QAsymmU8: np.uint8, DataType.Signed32: np.int32,
-             DataType.QSymmS16: np.int16, DataType.QSymmS8: np.int8, DataType.QAsymmS8: np.int8}
+             DataType.QSymmS16: np.int16, DataType.QSymmS8: np.int8, DataType.QAsymmS8: np.int8, DataType.Boolean: np.uint8}
 _TYPE_RANGE = {DataType.QAsymmU8: (0, 255), DataType.QAsymmS8: (-128, 127), DataType.QSymmS8: (-128, 127),
                DataType.QSymmS16: (-32768, 32767), DataType.Signed32: (-(1 << 31), (1 << 31) - 1)}
 
@@ -217,6 +219,19 @@ class INetwork:
 
     def AddMultiplicationLayer(self, name=None):
         return self.AddElementwiseBinaryLayer(BinaryOperation.Mul, name)
+
+    def AddComparisonLayer(self, operation, name=None):
+        """armnn::ComparisonDescriptor: 0 Equal, 1 Greater, 2 GreaterOrEqual, 3 Less, 4 LessOrEqual, 5 NotEqual; the
+        output is a Boolean tensor."""
+        if int(operation) not in range(6):
+            raise InvalidArgumentException("Comparison: unknown operation %d" % operation)
+        return self._add(Layer("Comparison", name, 2, 1, {"op": int(operation)}))
+
+    def AddLogicalBinaryLayer(self, operation, name=None):
+        """armnn::LogicalBinaryDescriptor: 0 LogicalAnd, 1 LogicalOr, on Boolean tensors."""
+        if int(operation) not in (0, 1):
+            raise InvalidArgumentException("LogicalBinary: unknown operation %d" % operation)
+        return self._add(Layer("LogicalBinary", name, 2, 1, {"op": int(operation)}))
 
     def AddSubtractionLayer(self, name=None):
         return self.AddElementwiseBinaryLayer(BinaryOperation.Sub, name)
@@ -444,6 +459,14 @@ def IsLayerSupported(layer):
         if t == "L2Normalization" and len(ins[0].shape) > 4:
             return False, "L2Normalization: rank > 4"
         return True, ""
+    if t in ("Comparison", "LogicalBinary"):
+        ok = ((DataType.QAsymmU8, DataType.QAsymmS8, DataType.QSymmS16, DataType.Float32, DataType.Boolean) if t == "Comparison"
+              else (DataType.Boolean,))
+        if any(i.dtype not in ok for i in ins) or ins[0].dtype != ins[1].dtype or outs[0].dtype != DataType.Boolean:
+            return False, "%s: inputs of one supported type and a Boolean output" % t
+        if len(outs[0].shape) > 4 or any(len(i.shape) != len(outs[0].shape) for i in ins):
+            return False, "%s: operands of one rank <= 4" % t
+        return True, ""
     if t == "Gather":
         ok = (DataType.QAsymmU8, DataType.QAsymmS8, DataType.QSymmS16, DataType.Float32, DataType.Signed32)
         if ins[0].dtype not in ok or outs[0].dtype != ins[0].dtype or ins[1].dtype != DataType.Signed32:
@@ -488,10 +511,12 @@ def IsLayerSupported(layer):
         return True, ""
     if t == "ElementwiseUnary":
         ok = (DataType.QAsymmU8, DataType.QAsymmS8, DataType.QSymmS16, DataType.Float32)
+        if layer.desc["op"] == 5:
+            ok = (DataType.Boolean,)                      # LogicalNot
+        elif layer.desc["op"] not in (0, 1, 2, 3, 4, 6, 7, 8):
+            return False, "ElementwiseUnary: operation %d is not supported" % layer.desc["op"]
         if ins[0].dtype not in ok or outs[0].dtype != ins[0].dtype:
             return False, "ElementwiseUnary: unsupported or mismatched data types"
-        if layer.desc["op"] not in (0, 1, 2, 3, 4, 6, 7, 8):
-            return False, "ElementwiseUnary: operation %d is not supported" % layer.desc["op"]
         return True, ""
     if t == "TransposeConvolution2d":
         if ins[0].dtype not in _Q8 or outs[0].dtype not in _Q8 or ins[1].dtype not in _Q8:
@@ -640,8 +665,7 @@ def _qt(info, ptr, scales_ptr=None):
     t = _abi.QTensor()
     t.data = ptr
     t.dtype = _ABI_DTYPE[info.dtype]
-    t.scale = info.scale
-    t.zero_point = info.offset
+    t.scale, t.zero_point = (1.0, 0) if info.dtype == DataType.Boolean else (info.scale, info.offset)
     t.scales = scales_ptr
     return t
 
@@ -910,11 +934,16 @@ class GraphProgram:
         p.rank = rank
         for i in range(rank):
             p.shape_a[i], p.shape_b[i], p.shape_out[i] = sa[i], sb[i], o.info.shape[i]
-        p.op = 100 if prelu else int(layer.desc["op"])
-        p.clamp_lo, p.clamp_hi = _clamp(layer, o.info) if o.info.dtype != DataType.Float32 else (0, 0)
+        p.op = 100 if prelu else int(layer.desc["op"]) + {"Comparison": 200, "LogicalBinary": 210}.get(layer.type, 0)
+        if o.info.dtype == DataType.Boolean:
+            p.clamp_lo, p.clamp_hi = 0, 255
+        else:
+            p.clamp_lo, p.clamp_hi = _clamp(layer, o.info) if o.info.dtype != DataType.Float32 else (0, 0)
         return "eltwise_q8", p
 
     _make_Prelu = _make_ElementwiseBinary
+    _make_Comparison = _make_ElementwiseBinary
+    _make_LogicalBinary = _make_ElementwiseBinary
 
     def _make_Activation(self, layer):
         x, y = layer.inputs[0].source, layer.outputs[0]

@@ -218,7 +218,11 @@ int b200k_mean_hw_q8(const b200k_mean_params* p, void* stream);
  * op follows armnn::BinaryOperation (include/armnn/Types.hpp:138-149): 0 Add, 1 Div, 2 Maximum,
  * 3 Minimum, 4 Mul, 5 Sub, 6 SqDiff, 7 Power (Power.hpp:19-24), 8 FloorDiv (FloorDiv.hpp:15-19: the quotient in
  * double precision, floored); B200K_ELTWISE_PRELU is armnn::Prelu (PreluImpl.cpp:14-33): a < 0 ? b * a : a with b the
- * alpha tensor.  Shapes have equal rank <= 4 (padded with leading 1s); a dimension of size 1 broadcasts.
+ * alpha tensor; 200 + armnn::ComparisonOperation (0 Equal, 1 Greater, 2 GreaterOrEqual, 3 Less, 4 LessOrEqual,
+ * 5 NotEqual; RefComparisonWorkload.cpp) and 210 + armnn::LogicalBinaryOperation (0 LogicalAnd, 1 LogicalOr;
+ * RefLogicalBinaryWorkload.cpp) produce 1.0 or 0.0.  A Boolean tensor is a B200K_U8 tensor with scale 1 and zero point 0:
+ * one byte per element, non-zero = true, results 0 or 1 (BooleanDecoder / BooleanEncoder, BaseIterator.hpp:427-700).
+ * Shapes have equal rank <= 4 (padded with leading 1s); a dimension of size 1 broadcasts.
  * out = Q(deq(a) op deq(b)), then the clamp. */
 #define B200K_ELTWISE_PRELU 100
 typedef struct {
@@ -246,8 +250,8 @@ int b200k_activation_q8(const b200k_activation_params* p, void* stream);
 
 /* armnn::ElementwiseUnary (src/backends/reference/workloads/RefElementwiseUnaryWorkload.cpp:36-110 with Abs.hpp, Exp.hpp,
  * Sqrt.hpp, Rsqrt.hpp, Log.hpp, Sin.hpp, Ceil.hpp and std::negate): y = Q_y(f(deq_x(x))); operation follows
- * armnn::UnaryOperation (0 Abs, 1 Exp, 2 Sqrt, 3 Rsqrt = 1 / sqrt, 4 Neg, 6 Log, 7 Sin, 8 Ceil; 5 LogicalNot is a
- * Boolean operation and not supported); 9 is the separate armnn::Floor layer (RefFloorWorkload.cpp: floorf). */
+ * armnn::UnaryOperation (0 Abs, 1 Exp, 2 Sqrt, 3 Rsqrt = 1 / sqrt, 4 Neg, 5 LogicalNot of a Boolean tensor
+ * (B200K_U8, scale 1, zero point 0; RefLogicalUnaryWorkload.cpp), 6 Log, 7 Sin, 8 Ceil); 9 is the separate armnn::Floor layer (RefFloorWorkload.cpp: floorf). */
 typedef struct {
     b200k_qtensor x, y;
     int64_t count;

@@ -301,6 +301,34 @@ extern "C" int cpuref_eltwise_q8(const b200k_eltwise_params* p, int act_kind, fl
         TensorInfo ai = make_info(p->a, shape(p->shape_a), 0, 0, false);
         TensorInfo bi = make_info(p->b, shape(p->shape_b), 0, 0, false);
         TensorInfo oi = make_info(p->out, shape(p->shape_out), 0, 0, false);
+        if (p->op >= 200)
+        {
+            // Comparison (any input type) and LogicalBinary (Boolean inputs): Boolean output, one byte per element
+            oi = TensorInfo(shape(p->shape_out), DataType::Boolean);
+            if (p->op >= 210)
+            {
+                ai = TensorInfo(shape(p->shape_a), DataType::Boolean);
+                bi = TensorInfo(shape(p->shape_b), DataType::Boolean);
+                LogicalBinaryQueueDescriptor d;
+                d.m_Parameters.m_Operation = p->op == 210 ? LogicalBinaryOperation::LogicalAnd : LogicalBinaryOperation::LogicalOr;
+                h.in(d, ai, p->a.data);
+                h.in(d, bi, p->b.data);
+                auto* o = h.out(d, oi);
+                h.run(LayerType::LogicalBinary, d);
+                copy_out(o, const_cast<void*>(p->out.data), oi.GetNumBytes());
+            }
+            else
+            {
+                ComparisonQueueDescriptor d;
+                d.m_Parameters.m_Operation = static_cast<ComparisonOperation>(p->op - 200);
+                h.in(d, ai, p->a.data);
+                h.in(d, bi, p->b.data);
+                auto* o = h.out(d, oi);
+                h.run(LayerType::Comparison, d);
+                copy_out(o, const_cast<void*>(p->out.data), oi.GetNumBytes());
+            }
+            return;
+        }
         if (p->op == B200K_ELTWISE_PRELU)
         {
             PreluQueueDescriptor d;
@@ -545,6 +573,17 @@ extern "C" int cpuref_unary_q(const b200k_unary_params* p)
         Harness h;
         const TensorShape shape({(unsigned)p->count});
         TensorInfo xi = make_info(p->x, shape, 0, 0, false), yi = make_info(p->y, shape, 0, 0, false);
+        if (p->operation == 5)                     // LogicalNot: Boolean tensors
+        {
+            TensorInfo bx(shape, DataType::Boolean), by(shape, DataType::Boolean);
+            ElementwiseUnaryQueueDescriptor ld;
+            ld.m_Parameters.m_Operation = UnaryOperation::LogicalNot;
+            h.in(ld, bx, p->x.data);
+            ITensorHandle* lo = h.out(ld, by);
+            h.run(LayerType::ElementwiseUnary, ld);
+            copy_out(lo, const_cast<void*>(p->y.data), by.GetNumBytes());
+            return;
+        }
         if (p->operation == 9)                     // the Floor layer
         {
             FloorQueueDescriptor fd;

@@ -468,6 +468,15 @@ int oracle_eltwise_q8(const b200k_eltwise_params* p)
             case 7: r = powf(a, b); break;                                    /* Power.hpp:19-24 */
             case 8: r = (float)floor((double)a / (double)b); break;           /* FloorDiv.hpp:15-19 */
             case B200K_ELTWISE_PRELU: r = a < 0 ? b * a : a; break;           /* PreluImpl.cpp:25-28 */
+            /* RefComparisonWorkload.cpp:60-104 and RefLogicalBinaryWorkload.cpp:33-56: a Boolean byte, 0 or 1 */
+            case 200: r = a == b; break;
+            case 201: r = a > b; break;
+            case 202: r = a >= b; break;
+            case 203: r = a < b; break;
+            case 204: r = a <= b; break;
+            case 205: r = a != b; break;
+            case 210: r = (a != 0) && (b != 0); break;
+            case 211: r = (a != 0) || (b != 0); break;
             default: return B200K_E_INVALID;
         }
         if (p->out.dtype == B200K_F32) { ((float*)p->out.data)[io] = r; continue; }
@@ -503,7 +512,7 @@ static float activation_f(float in, int fn, float a, float b)
 /* ElementwiseUnary, RefElementwiseUnaryWorkload.cpp:36-110: y = Q_y(f(deq_x(x))) with the std:: function of the operation */
 int oracle_unary_q(const b200k_unary_params* p)
 {
-    if (!p || !p->x.data || !p->y.data || p->operation < 0 || p->operation > 9 || p->operation == 5) return B200K_E_INVALID;
+    if (!p || !p->x.data || !p->y.data || p->operation < 0 || p->operation > 9) return B200K_E_INVALID;
     for (int64_t i = 0; i < p->count; ++i) {
         const float in = load_f(&p->x, i);
         float r;
@@ -513,6 +522,7 @@ int oracle_unary_q(const b200k_unary_params* p)
             case 2: r = sqrtf(in); break;
             case 3: r = 1 / sqrtf(in); break;
             case 4: r = -in; break;
+            case 5: r = in != 0 ? 0.f : 1.f; break;        /* RefLogicalUnaryWorkload.cpp: LogicalNot of a Boolean byte */
             case 6: r = logf(in); break;
             case 7: r = sinf(in); break;
             case 9: r = floorf(in); break;                 /* RefFloorWorkload.cpp */

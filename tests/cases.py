@@ -236,6 +236,30 @@ def eltwise_cases():
             p.clamp_lo, p.clamp_hi = activation_clamp(act[0], act[1], act[2], oscale, zo, dtype)
             return p, [out]
         return lambda: SimpleCase("eltwise_q8", build, extra)
+    def boolean(seed, sa, sb, op, dtype=S8, coarse=False):
+        """Comparison (op 200 + ComparisonOperation) of quantised tensors, or LogicalBinary (210 / 211) of Boolean ones;
+        the output is a Boolean tensor: B200K_U8, scale 1, zero point 0."""
+        def build(mem):
+            rng = np.random.default_rng(seed)
+            so = tuple(max(a, b) for a, b in zip(sa, sb))
+            p = _abi.EltwiseParams()
+            if op >= 210:
+                p.a = qt(mem, rng.integers(0, 3, size=sa).astype(np.uint8), U8, 1.0, 0)
+                p.b = qt(mem, rng.integers(0, 3, size=sb).astype(np.uint8), U8, 1.0, 0)
+            else:
+                a, b = _rand(rng, dtype, sa), _rand(rng, dtype, sb)
+                if coarse:                              # few distinct values with one quantisation: many equal pairs
+                    a, b = (a // 64 * 64).astype(a.dtype), (b // 64 * 64).astype(b.dtype)
+                q = (0.05, 3) if dtype == S8 else (0.05, 120)
+                p.a = qt(mem, a, dtype, *q)
+                p.b = qt(mem, b, dtype, *(q if coarse else (0.04, q[1] - 2)))
+            p.out, out = qt_out(mem, so, U8, 1.0, 0)
+            p.rank = len(so)
+            for i in range(len(so)):
+                p.shape_a[i], p.shape_b[i], p.shape_out[i] = sa[i], sb[i], so[i]
+            p.op, p.clamp_lo, p.clamp_hi = op, 0, 255
+            return p, [out]
+        return lambda: SimpleCase("eltwise_q8", build, none)
     import ctypes as C
     relu = (C.c_int(1), C.c_float(0), C.c_float(0))
     none = (C.c_int(0), C.c_float(0), C.c_float(0))
@@ -255,6 +279,14 @@ def eltwise_cases():
         "floor_div_broadcast_u8": make(63, (2, 4, 4, 8), (1, 1, 1, 8), 8, dtype=U8, extra=none, nonzero=True),
         "prelu_channel_alpha": make(64, (2, 9, 9, 24), (1, 1, 1, 24), 100, extra=none),
         "prelu_u8_same_shape": make(65, (1, 5, 5, 32), (1, 5, 5, 32), 100, dtype=U8, extra=none),
+        "equal_coarse": boolean(66, (2, 5, 5, 16), (2, 5, 5, 16), 200, coarse=True),
+        "greater_broadcast": boolean(67, (2, 6, 6, 10), (1, 1, 1, 10), 201),
+        "greater_or_equal_u8_coarse": boolean(68, (3, 17), (3, 17), 202, dtype=U8, coarse=True),
+        "less": boolean(69, (1, 7, 7, 24), (1, 7, 7, 24), 203),
+        "less_or_equal_coarse": boolean(70, (4, 1), (4, 9), 204, coarse=True),
+        "not_equal_coarse_u8": boolean(56, (1, 3, 5, 7), (1, 3, 5, 7), 205, dtype=U8, coarse=True),
+        "logical_and": boolean(57, (2, 5, 5, 16), (2, 5, 5, 16), 210),
+        "logical_or_broadcast": boolean(58, (2, 4, 4, 8), (1, 1, 1, 8), 211),
     }
 
 
@@ -654,7 +686,17 @@ def unary_cases():
             return p, [y]
         return lambda: SimpleCase("unary_q", build)
     ABS, EXP, SQRT, RSQRT, NEG, LOG, SIN, CEIL, FLOOR = 0, 1, 2, 3, 4, 6, 7, 8, 9
+
+    def logical_not():
+        def build(mem):
+            p = _abi.UnaryParams()
+            p.x = qt(mem, np.random.default_rng(372).integers(0, 3, size=(500,)).astype(np.uint8), U8, 1.0, 0)
+            p.y, y = qt_out(mem, (500,), U8, 1.0, 0)
+            p.count, p.operation = 500, 5
+            return p, [y]
+        return SimpleCase("unary_q", build)
     return {
+        "logical_not_boolean": logical_not,
         "floor_layer_float": make(371, 333, FLOOR, dtype=F32, xq=(1.0, 0)),
         "abs_s8": make(361, 1000, ABS),
         "neg_u8_requantise": make(362, 777, NEG, dtype=U8, xq=(0.1, 128), yq=(0.12, 120)),

@@ -276,3 +276,14 @@ def test_mirror_pad_gelu_floor_graph_oracle_equals_armnn_cpuref(built):
     got = hostnet.OracleNetwork(Optimize(net)).run(xs)
     for k in range(4):
         assert want[k].shape == got[k].shape and np.array_equal(want[k], got[k]), k
+
+
+@needs_cpuref
+def test_comparison_and_logical_graph_oracle_equals_armnn_cpuref(built):
+    import hostnet
+    from test_plugin import _boolean_inputs, _boolean_net
+    net, shape = _boolean_net()
+    xs = _boolean_inputs(62, shape)
+    want = hostnet.ArmnnNetwork(net, "CpuRef").run(xs)[0]
+    got = hostnet.OracleNetwork(Optimize(net)).run(xs)[0]
+    assert set(np.unique(want)) <= {0, 1} and np.array_equal(want, got)

@@ -1033,3 +1033,54 @@ def test_mirror_pad_gelu_floor_through_the_runtime_match_cpuref():
     assert np.allclose(ref[0], got[0], rtol=1e-6, atol=1e-7)                          # erff of the device against glibc
     st = diff_stats(ref[3], got[3])
     assert st["max_abs"] <= 1 and st["mismatch_frac"] <= 0.01, st
+
+
+def _boolean_net():
+    """(a > b) AND NOT (a == c): Comparison, LogicalBinary and ElementwiseUnary(LogicalNot) on Boolean tensors."""
+    from armnn_b200.network import DataType, INetwork, TensorInfo
+    shape = (2, 5, 6, 16)
+    net = INetwork.Create()
+    ins = []
+    for k, (scale, zp) in enumerate([(0.05, 3), (0.04, 1), (0.05, 3)]):
+        il = net.AddInputLayer(k, "in%d" % k)
+        il.GetOutputSlot(0).SetTensorInfo(TensorInfo(shape, DataType.QAsymmS8, scale, zp))
+        ins.append(il)
+    b = TensorInfo(shape, DataType.Boolean)
+    gt = net.AddComparisonLayer(1, "greater")
+    ins[0].GetOutputSlot(0).Connect(gt.GetInputSlot(0)); ins[1].GetOutputSlot(0).Connect(gt.GetInputSlot(1))
+    gt.GetOutputSlot(0).SetTensorInfo(b)
+    eq = net.AddComparisonLayer(0, "equal")
+    ins[0].GetOutputSlot(0).Connect(eq.GetInputSlot(0)); ins[2].GetOutputSlot(0).Connect(eq.GetInputSlot(1))
+    eq.GetOutputSlot(0).SetTensorInfo(b)
+    nt = net.AddElementwiseUnaryLayer(5, "not")
+    eq.GetOutputSlot(0).Connect(nt.GetInputSlot(0))
+    nt.GetOutputSlot(0).SetTensorInfo(b)
+    an = net.AddLogicalBinaryLayer(0, "and")
+    gt.GetOutputSlot(0).Connect(an.GetInputSlot(0)); nt.GetOutputSlot(0).Connect(an.GetInputSlot(1))
+    an.GetOutputSlot(0).SetTensorInfo(b)
+    ol = net.AddOutputLayer(0, "out")
+    an.GetOutputSlot(0).Connect(ol.GetInputSlot(0))
+    return net, shape
+
+
+def _boolean_inputs(seed, shape):
+    rng = np.random.default_rng(seed)
+    a = rng.integers(-128, 128, size=shape).astype(np.int8)
+    c = np.where(rng.random(shape) < 0.5, a, rng.integers(-128, 128, size=shape)).astype(np.int8)      # half of them equal a
+    return {0: a, 1: rng.integers(-128, 128, size=shape).astype(np.int8), 2: c}
+
+
+@needs_plugin
+@pytest.mark.gpu
+def test_comparison_and_logical_layers_through_the_runtime_equal_cpuref():
+    from armnn_b200 import network
+    net, shape = _boolean_net()
+    xs = _boolean_inputs(61, shape)
+    ref = hostnet.ArmnnNetwork(net, "CpuRef").run(xs)[0]
+    got = hostnet.ArmnnNetwork(net, "B200Acc").run(xs)[0]
+    rt = network.IRuntime.Create(0)
+    ln = rt.GetLoadedNetwork(rt.LoadNetwork(network.Optimize(net)))
+    ys = {0: np.zeros(ref.shape, ref.dtype)}
+    ln.EnqueueWorkload(xs, ys)
+    assert 0.1 < ref.mean() < 0.9 and set(np.unique(ref)) <= {0, 1}
+    assert np.array_equal(ref, got) and np.array_equal(ref, ys[0])
