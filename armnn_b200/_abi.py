@@ -185,6 +185,7 @@ KERNEL_ENTRY_POINTS = {
     "instance_norm_q": InstanceNormParams,
     "normalization_q": NormalizationParams,
     "convert_q": ConvertParams,
+    "cast_q": ConvertParams,
     "qlstm_step": QLstmParams,
     "pad_q": PadParams,
     "view_copy_q": ViewCopyParams,

@@ -193,6 +193,10 @@ class ArmnnNetwork:
             elif t == "Pad":
                 flat = [v for pair in d["pads"] for v in pair]
                 lid = lib.armnnc_add_pad(net, len(d["pads"]), (C.c_int32 * len(flat))(*flat), C.c_float(d["value"]), int(d.get("mode", 0)))
+            elif t == "Cast":
+                lid = lib.armnnc_add_cast(net)
+            elif t == "Fill":
+                lid = lib.armnnc_add_fill(net, C.c_float(d["value"]))
             elif t == "Floor":
                 lid = lib.armnnc_add_floor(net)
             elif t == "TransposeConvolution2d":

@@ -281,6 +281,12 @@ public:
             }
             case LayerType::Softmax:
                 return (IsActType(infos[0]) && IsActType(infos[1])) || No(reason, "unsupported data type");
+            case LayerType::Cast:
+                return (IsMoveType(infos[0]) && IsMoveType(infos[1]) && infos[0].GetNumElements() == infos[1].GetNumElements()) ||
+                       No(reason, "unsupported data type or mismatched sizes");
+            case LayerType::Fill:
+                return ((infos[1].GetDataType() == DataType::Float32 || infos[1].GetDataType() == DataType::Signed32) &&
+                        infos[1].GetNumDimensions() >= 1 && infos[1].GetNumDimensions() <= 6) || No(reason, "Float32 or Signed32 output of 1 to 6 dimensions");
             case LayerType::Floor:
                 return (infos[0].GetDataType() == DataType::Float32 && infos[1].GetDataType() == DataType::Float32) || No(reason, "Float32 only");
             case LayerType::LogSoftmax:

@@ -1313,6 +1313,37 @@ std::unique_ptr<IWorkload> B200WorkloadFactory::CreateWorkload(LayerType type, c
                 B200CheckStatus(b200k_instance_norm_q(&st->p, s));
             });
         }
+        case LayerType::Cast:
+        {
+            auto st = std::make_shared<SimpleState<b200k_convert_params>>(ctx);
+            std::memset(&st->p, 0, sizeof(st->p));
+            st->p.x = Operand(info.m_InputTensorInfos[0], st->blobs);
+            st->p.y = Operand(info.m_OutputTensorInfos[0], st->blobs);
+            st->p.count = info.m_InputTensorInfos[0].GetNumElements();
+            return Make<CastQueueDescriptor>(d, info, ctx, [st](const CastQueueDescriptor& data, cudaStream_t s)
+            {
+                st->p.x.data = Dev(data.m_Inputs[0]); st->p.y.data = Dev(data.m_Outputs[0]);
+                B200CheckStatus(b200k_cast_q(&st->p, s));
+            });
+        }
+        case LayerType::Fill:
+        {
+            // every element of the output <- one element holding the value in the output's type (workloads/Fill.cpp:13-23)
+            const auto& qd = *PolymorphicDowncast<const FillQueueDescriptor*>(&d);
+            auto st = std::make_shared<ViewState>(ctx);
+            const TensorInfo& out = info.m_OutputTensorInfos[0];
+            const unsigned int rank = out.GetNumDimensions();
+            if (rank < 1 || rank > 6) { throw InvalidArgumentException("B200Acc: Fill needs an output of 1 to 6 dimensions"); }
+            uint8_t bytes[4];
+            if (out.GetDataType() == DataType::Signed32) { const int32_t v = static_cast<int32_t>(qd.m_Parameters.m_Value); std::memcpy(bytes, &v, 4); }
+            else { const float v = qd.m_Parameters.m_Value; std::memcpy(bytes, &v, 4); }
+            ViewOp op = NewViewOp(out, out, st->blobs, 0, 0, rank);
+            op.fixedSrc = st->blobs.Upload(bytes, sizeof(bytes));
+            DenseStrides(out.GetShape(), op.p.dst_strides);
+            for (unsigned int i = 0; i < rank; ++i) { op.p.shape[i] = static_cast<int32_t>(out.GetShape()[i]); }
+            st->ops.push_back(op);
+            return MakeViews<FillQueueDescriptor>(d, info, ctx, st);
+        }
         case LayerType::Floor:
         {
             auto st = std::make_shared<SimpleState<b200k_unary_params>>(ctx);

@@ -172,12 +172,12 @@ extern "C" int b200k_eltwise_q8(const b200k_eltwise_params* p, void* stream)
 }
 
 static int launch_unary(const b200k_qtensor& x, const b200k_qtensor& y, long long count, int fn, float a, float b,
-                        void* stream, const char* what)
+                        void* stream, const char* what, bool s32_out = false)
 {
     B200K_REQUIRE(x.data && y.data, B200K_E_INVALID, "%s: null tensor pointer", what);
     B200K_REQUIRE(count >= 0, B200K_E_INVALID, "%s: negative element count", what);
     B200K_REQUIRE(x.dtype >= B200K_U8 && x.dtype <= B200K_F32 && y.dtype >= B200K_U8 && y.dtype <= B200K_F32 &&
-                  y.dtype != B200K_S32, B200K_E_UNSUPPORTED, "%s: unsupported data type", what);
+                  (y.dtype != B200K_S32 || s32_out), B200K_E_UNSUPPORTED, "%s: unsupported data type", what);
     if (count == 0) return B200K_OK;
     UnaryArgs u;
     u.x = make_view(x); u.y = make_view(y); u.count = count; u.fn = fn; u.a = a; u.b = b;
@@ -198,6 +198,17 @@ extern "C" int b200k_unary_q(const b200k_unary_params* p, void* stream)
     B200K_REQUIRE(p->operation >= 0 && p->operation <= 9, B200K_E_UNSUPPORTED,
                   "unary_q: unsupported unary operation %d", p->operation);
     return launch_unary(p->x, p->y, p->count, 100 + p->operation, 0.f, 0.f, stream, "unary_q");
+}
+
+// armnn::Cast (RefCastWorkload.cpp:13-36, 95-106): both tensors read with scale 1 and offset 0 whatever their TensorInfo
+// says; floor before an integer output, the value itself for a float output.
+extern "C" int b200k_cast_q(const b200k_convert_params* p, void* stream)
+{
+    B200K_REQUIRE(p, B200K_E_INVALID, "cast_q: null params");
+    b200k_qtensor x = p->x, y = p->y;
+    x.scale = 1.0f; x.zero_point = 0; x.scales = nullptr;
+    y.scale = 1.0f; y.zero_point = 0; y.scales = nullptr;
+    return launch_unary(x, y, p->count, y.dtype == B200K_F32 ? -1 : 109, 0.f, 0.f, stream, "cast_q", true);
 }
 
 extern "C" int b200k_convert_q(const b200k_convert_params* p, void* stream)

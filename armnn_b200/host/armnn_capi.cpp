@@ -384,6 +384,19 @@ int armnnc_add_qlstm(void* vn, const b200k_qlstm_params* p)
 }
 
 // pads: rank pairs (before, after), outermost dimension first
+int armnnc_add_cast(void* vn)
+{
+    auto* n = static_cast<CNet*>(vn);
+    return add_layer(n, n->net->AddCastLayer());
+}
+
+int armnnc_add_fill(void* vn, float value)
+{
+    auto* n = static_cast<CNet*>(vn);
+    FillDescriptor d; d.m_Value = value;
+    return add_layer(n, n->net->AddFillLayer(d));
+}
+
 int armnnc_add_floor(void* vn)
 {
     auto* n = static_cast<CNet*>(vn);

@@ -280,6 +280,13 @@ class INetwork:
         return self._add(Layer("Pad", name, 1, 1, {"pads": tuple((int(a), int(b)) for a, b in pad_list), "value": float(pad_value),
                                                    "mode": int(padding_mode)}))
 
+    def AddCastLayer(self, name=None):
+        return self._add(Layer("Cast", name, 1, 1, {}))
+
+    def AddFillLayer(self, value, name=None):
+        """armnn::FillDescriptor: the input is the (ignored) shape tensor, every output element is `value`."""
+        return self._add(Layer("Fill", name, 1, 1, {"value": float(value)}))
+
     def AddFloorLayer(self, name=None):
         return self._add(Layer("Floor", name, 1, 1, {}))
 
@@ -504,6 +511,15 @@ def IsLayerSupported(layer):
             return False, "Pad: unknown padding mode"
         if mode and any(max(a, b) + (mode == 1) > n for (a, b), n in zip(layer.desc["pads"], ins[0].shape)):
             return False, "Pad: mirrored padding wider than the tensor"
+        return True, ""
+    if t == "Cast":
+        ok = (DataType.QAsymmU8, DataType.QAsymmS8, DataType.QSymmS8, DataType.QSymmS16, DataType.Signed32, DataType.Float32)
+        if ins[0].dtype not in ok or outs[0].dtype not in ok or ins[0].GetNumElements() != outs[0].GetNumElements():
+            return False, "Cast: unsupported data type or mismatched sizes"
+        return True, ""
+    if t == "Fill":
+        if outs[0].dtype not in (DataType.Float32, DataType.Signed32):
+            return False, "Fill: Float32 or Signed32 output only (as in the reference)"
         return True, ""
     if t == "Floor":
         if ins[0].dtype != DataType.Float32 or outs[0].dtype != DataType.Float32:
@@ -1086,6 +1102,24 @@ class GraphProgram:
         p.pad_value = layer.desc["value"]
         p.mode = layer.desc.get("mode", 0)
         return "pad_q", p
+
+    def _make_Cast(self, layer):
+        x, y = layer.inputs[0].source, layer.outputs[0]
+        p = _abi.ConvertParams()
+        p.x, p.y = self._operand(x), self._operand(y)
+        p.count = x.info.GetNumElements()
+        return "cast_q", p
+
+    def _make_Fill(self, layer):
+        """One element holding the value in the output's type, read with stride 0 over the whole output
+        (workloads/Fill.cpp:13-23; Signed32: the value truncated)."""
+        y = layer.outputs[0]
+        value = np.array([layer.desc["value"]], np.float32).astype(_NP_DTYPE[y.info.dtype])
+        dev = self._upload(value)
+        self.aux.append(dev)
+        name, p = self._view_copy(y, y, views.fill_view(y.info.shape))
+        p.x.data = self._ptr(dev)
+        return name, p
 
     def _make_Floor(self, layer):
         x, y = layer.inputs[0].source, layer.outputs[0]

@@ -471,6 +471,12 @@ typedef struct {
 
 int b200k_convert_q(const b200k_convert_params* p, void* stream);
 
+/* armnn::Cast (src/backends/reference/workloads/RefCastWorkload.cpp:13-36, 95-106): the numbers stored in x become the
+ * numbers stored in y: both tensors are read with scale 1 and offset 0 whatever x.scale / y.scale say, the value is
+ * floored before an integer output (and clamped to the type's range), kept as it is for a float output.  Any of
+ * U8/S8/S16/S32/F32 on either side. */
+int b200k_cast_q(const b200k_convert_params* p, void* stream);
+
 /* ---- QLstm ----------------------------------------------------------------------------------- */
 
 /* One RefQLstmWorkload::Execute step (src/backends/reference/workloads/RefQLstmWorkload.cpp:46-541,

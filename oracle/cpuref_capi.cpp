@@ -453,6 +453,20 @@ extern "C" int cpuref_normalization_q(const b200k_normalization_params* p)
     });
 }
 
+extern "C" int cpuref_cast_q(const b200k_convert_params* p)
+{
+    return guarded([&] {
+        Harness h;
+        const TensorShape shape({(unsigned)p->count});
+        TensorInfo xi = make_info(p->x, shape, 0, 0, false), yi = make_info(p->y, shape, 0, 0, false);
+        CastQueueDescriptor d;
+        h.in(d, xi, p->x.data);
+        ITensorHandle* o = h.out(d, yi);
+        h.run(LayerType::Cast, d);
+        copy_out(o, const_cast<void*>(p->y.data), yi.GetNumBytes());
+    });
+}
+
 extern "C" int cpuref_softmax_q8(const b200k_softmax_params* p)
 {
     return guarded([&] {

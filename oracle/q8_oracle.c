@@ -775,6 +775,25 @@ int oracle_convert_q(const b200k_convert_params* p)
     return 0;
 }
 
+/* ---- Cast, RefCastWorkload.cpp:13-36, 95-106: scale 1 and offset 0 on both sides, floor before an integer output - */
+
+int oracle_cast_q(const b200k_convert_params* p)
+{
+    if (!p->x.data || !p->y.data) return B200K_E_INVALID;
+    b200k_qtensor x = p->x, y = p->y;
+    x.scale = 1.0f; x.zero_point = 0; y.scale = 1.0f; y.zero_point = 0;
+    for (int64_t i = 0; i < p->count; ++i) {
+        const float v = load_f(&x, i);
+        if (y.dtype == B200K_F32) ((float*)y.data)[i] = v;
+        else if (y.dtype == B200K_S32) {
+            const float f = floorf(v);
+            ((int32_t*)y.data)[i] = f >= 2147483648.0f ? INT32_MAX : f <= -2147483648.0f ? INT32_MIN : (int32_t)f;
+        }
+        else store_f(&y, i, floorf(v));
+    }
+    return 0;
+}
+
 /* ---- Pad (constant), Pad.cpp:37-170 -----------------------------------------------------------
  * Every output element is the decoded input element at the shifted position encoded with the
  * output's quantisation, or the pad value; for a quantised output the pad value is encoded with

@@ -516,23 +516,29 @@ CPUREF_REFUSES = {("norm", "gather_negative_indices_s16"), ("norm", "gather_floa
 
 
 def convert_cases():
-    def make(seed, xd, yd, count=1001, xq=(0.05, 3), yq=(0.07, -4)):
+    def make(seed, xd, yd, count=1001, xq=(0.05, 3), yq=(0.07, -4), entry="convert_q", fscale=4):
         def build(mem):
             rng = np.random.default_rng(seed)
             p = _abi.ConvertParams()
             if xd == F32:
-                x = (rng.standard_normal(count) * 4).astype(np.float32)
+                x = (rng.standard_normal(count) * fscale).astype(np.float32)
                 p.x = qt(mem, x, F32)
+            elif xd == S32:
+                p.x = qt(mem, rng.integers(-70000, 70000, size=(count,)).astype(np.int32), S32, 1.0, 0)
             else:
                 p.x = qt(mem, _rand(rng, xd, (count,)), xd, *xq)
             p.y, y = qt_out(mem, (count,), yd, *yq)
             p.count = count
             return p, [y]
-        return lambda: SimpleCase("convert_q", build)
+        return lambda: SimpleCase(entry, build)
     return {"quantize_f32_s8": make(111, F32, S8), "quantize_f32_u8": make(112, F32, U8, yq=(0.05, 128)),
             "quantize_f32_s16": make(113, F32, S16, yq=(0.001, 0)), "dequantize_s8": make(114, S8, F32),
             "dequantize_u8": make(115, U8, F32, xq=(0.1, 120)), "requantize_u8_s8": make(116, U8, S8, xq=(0.05, 128)),
-            "requantize_s16_s8": make(117, S16, S8, xq=(0.0005, 0))}
+            "requantize_s16_s8": make(117, S16, S8, xq=(0.0005, 0)),
+            # Cast ignores both quantisations: the stored numbers are converted
+            "cast_f32_s8": make(118, F32, S8, entry="cast_q", fscale=40), "cast_f32_s32": make(119, F32, S32, entry="cast_q", fscale=1e5),
+            "cast_u8_f32": make(120, U8, F32, entry="cast_q", xq=(0.1, 120)), "cast_s16_u8": make(110, S16, U8, entry="cast_q", xq=(0.0005, 0)),
+            "cast_s32_s16": make(109, S32, S16, entry="cast_q"), "cast_s8_s32": make(108, S8, S32, entry="cast_q")}
 
 
 def pad_cases():

@@ -287,3 +287,14 @@ def test_comparison_and_logical_graph_oracle_equals_armnn_cpuref(built):
     want = hostnet.ArmnnNetwork(net, "CpuRef").run(xs)[0]
     got = hostnet.OracleNetwork(Optimize(net)).run(xs)[0]
     assert set(np.unique(want)) <= {0, 1} and np.array_equal(want, got)
+
+
+@needs_cpuref
+def test_cast_and_fill_graph_oracle_equals_armnn_cpuref(built):
+    import hostnet
+    from test_plugin import _cast_fill_net
+    net, shape = _cast_fill_net()
+    xs = {0: np.random.default_rng(68).integers(-128, 128, size=shape).astype(np.int8), 1: np.array(shape, np.int32)}
+    want = hostnet.ArmnnNetwork(net, "CpuRef").run(xs)[0]
+    got = hostnet.OracleNetwork(Optimize(net)).run(xs)[0]
+    assert want.dtype == np.int32 and np.array_equal(want, got)

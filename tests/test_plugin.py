@@ -1084,3 +1084,41 @@ def test_comparison_and_logical_layers_through_the_runtime_equal_cpuref():
     ln.EnqueueWorkload(xs, ys)
     assert 0.1 < ref.mean() < 0.9 and set(np.unique(ref)) <= {0, 1}
     assert np.array_equal(ref, got) and np.array_equal(ref, ys[0])
+
+
+def _cast_fill_net():
+    """Cast of quantised bytes to Float32 (the stored numbers, not the dequantised ones) and back to Signed32 after a Floor;
+    Fill of a Float32 tensor added to the cast."""
+    from armnn_b200.network import BinaryOperation, DataType, INetwork, TensorInfo
+    shape = (2, 3, 4, 8)
+    net = INetwork.Create()
+    il = net.AddInputLayer(0, "input")
+    il.GetOutputSlot(0).SetTensorInfo(TensorInfo(shape, DataType.QAsymmS8, 0.05, -3))
+    c1 = net.AddCastLayer("to_float")
+    il.GetOutputSlot(0).Connect(c1.GetInputSlot(0))
+    c1.GetOutputSlot(0).SetTensorInfo(TensorInfo(shape, DataType.Float32))
+    sh = net.AddInputLayer(1, "shape")
+    sh.GetOutputSlot(0).SetTensorInfo(TensorInfo((4,), DataType.Signed32))
+    fl = net.AddFillLayer(2.75, "fill")
+    sh.GetOutputSlot(0).Connect(fl.GetInputSlot(0))
+    fl.GetOutputSlot(0).SetTensorInfo(TensorInfo(shape, DataType.Float32))
+    ad = net.AddElementwiseBinaryLayer(BinaryOperation.Mul, "scale")
+    c1.GetOutputSlot(0).Connect(ad.GetInputSlot(0)); fl.GetOutputSlot(0).Connect(ad.GetInputSlot(1))
+    ad.GetOutputSlot(0).SetTensorInfo(TensorInfo(shape, DataType.Float32))
+    c2 = net.AddCastLayer("to_int")
+    ad.GetOutputSlot(0).Connect(c2.GetInputSlot(0))
+    c2.GetOutputSlot(0).SetTensorInfo(TensorInfo(shape, DataType.Signed32))
+    ol = net.AddOutputLayer(0, "out")
+    c2.GetOutputSlot(0).Connect(ol.GetInputSlot(0))
+    return net, shape
+
+
+@needs_plugin
+@pytest.mark.gpu
+def test_cast_and_fill_through_the_runtime_equal_cpuref():
+    net, shape = _cast_fill_net()
+    xs = {0: np.random.default_rng(67).integers(-128, 128, size=shape).astype(np.int8), 1: np.array(shape, np.int32)}
+    ref = hostnet.ArmnnNetwork(net, "CpuRef").run(xs)[0]
+    got = hostnet.ArmnnNetwork(net, "B200Acc").run(xs)[0]
+    assert ref.dtype == np.int32 and np.array_equal(ref, np.floor(xs[0].astype(np.float32) * np.float32(2.75)).astype(np.int32))
+    assert np.array_equal(ref, got)
