@@ -102,6 +102,18 @@ class NormalizationParams(C.Structure):
                 ("alpha", C.c_float), ("beta", C.c_float), ("kappa", C.c_float)]
 
 
+class Conv3dParams(C.Structure):
+    _fields_ = [("x", QTensor), ("w", QTensor), ("bias", QTensor), ("y", QTensor)] + [(k, C.c_int32) for k in (
+        "n", "d", "h", "wd", "c", "od", "oh", "ow", "oc", "kd", "kh", "kw", "stride_d", "stride_h", "stride_w",
+        "pad_front", "pad_top", "pad_left", "dil_d", "dil_h", "dil_w", "clamp_lo", "clamp_hi")]
+
+
+class Pool3dParams(C.Structure):
+    _fields_ = [("x", QTensor), ("y", QTensor)] + [(k, C.c_int32) for k in (
+        "n", "d", "h", "wd", "c", "od", "oh", "ow", "pool_d", "pool_h", "pool_w", "stride_d", "stride_h", "stride_w",
+        "pad_front", "pad_back", "pad_top", "pad_bottom", "pad_left", "pad_right", "pool_type", "padding_method")]
+
+
 class ConvertParams(C.Structure):
     _fields_ = [("x", QTensor), ("y", QTensor), ("count", C.c_int64)]
 
@@ -184,6 +196,8 @@ KERNEL_ENTRY_POINTS = {
     "batch_norm_q": BatchNormParams,
     "instance_norm_q": InstanceNormParams,
     "normalization_q": NormalizationParams,
+    "conv3d_q": Conv3dParams,
+    "pool3d_q": Pool3dParams,
     "convert_q": ConvertParams,
     "cast_q": ConvertParams,
     "qlstm_step": QLstmParams,

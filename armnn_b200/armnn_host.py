@@ -153,6 +153,12 @@ class ArmnnNetwork:
             elif t == "Pooling2d":
                 lid = lib.armnnc_add_pool2d(net, int(d["type"]), int(d["method"]), d["pool"][0], d["pool"][1], d["stride"][0],
                                             d["stride"][1], d["pad"][0], d["pad"][1], d["pad"][2], d["pad"][3])
+            elif t == "Convolution3d":
+                lid = lib.armnnc_add_conv3d(net, (C.c_int32 * 3)(*d["stride"]), (C.c_int32 * 6)(*d["pad"]), (C.c_int32 * 3)(*d["dilation"]),
+                                            int(d["bias"]))
+            elif t == "Pooling3d":
+                lid = lib.armnnc_add_pool3d(net, int(d["type"]), int(d["method"]), (C.c_int32 * 3)(*d["pool"]), (C.c_int32 * 3)(*d["stride"]),
+                                            (C.c_int32 * 6)(*d["pad"]))
             elif t == "ElementwiseBinary":
                 lid = lib.armnnc_add_elementwise_binary(net, int(d["op"]))
             elif t == "Comparison":

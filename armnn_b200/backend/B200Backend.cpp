@@ -281,6 +281,26 @@ public:
             }
             case LayerType::Softmax:
                 return (IsActType(infos[0]) && IsActType(infos[1])) || No(reason, "unsupported data type");
+            case LayerType::Convolution3d:
+            {
+                // infos: input, output, weights[, bias]
+                const auto& d = *PolymorphicDowncast<const Convolution3dDescriptor*>(&descriptor);
+                if (d.m_DataLayout != DataLayout::NDHWC) { return No(reason, "NDHWC only"); }
+                if (infos[0].GetNumDimensions() != 5 || infos[1].GetNumDimensions() != 5 || infos[2].GetNumDimensions() != 5) { return No(reason, "5-D tensors only"); }
+                if (AllFloat32(infos)) { return true; }
+                auto q8 = [](const TensorInfo& t) { return t.GetDataType() == DataType::QAsymmU8 || t.GetDataType() == DataType::QAsymmS8; };
+                if (!q8(infos[0]) || !q8(infos[1]) || !(q8(infos[2]) || infos[2].GetDataType() == DataType::QSymmS8)) { return No(reason, "8-bit quantised tensors or Float32 throughout"); }
+                if (infos.size() > 3 && infos[3].GetNumElements() > 0 && infos[3].GetDataType() != DataType::Signed32) { return No(reason, "bias must be Signed32"); }
+                if (infos[2].HasPerAxisQuantization() && infos[2].GetQuantizationDim().value() != 4) { return No(reason, "per-axis weights must be quantised along the output channels"); }
+                return true;
+            }
+            case LayerType::Pooling3d:
+            {
+                const auto& d = *PolymorphicDowncast<const Pooling3dDescriptor*>(&descriptor);
+                if (d.m_DataLayout != DataLayout::NDHWC) { return No(reason, "NDHWC only"); }
+                return (infos[0].GetNumDimensions() == 5 && IsActType(infos[0]) && infos[1].GetDataType() == infos[0].GetDataType()) ||
+                       No(reason, "5-D tensors of one supported data type");
+            }
             case LayerType::Cast:
                 return (IsMoveType(infos[0]) && IsMoveType(infos[1]) && infos[0].GetNumElements() == infos[1].GetNumElements()) ||
                        No(reason, "unsupported data type or mismatched sizes");

@@ -1313,6 +1313,66 @@ std::unique_ptr<IWorkload> B200WorkloadFactory::CreateWorkload(LayerType type, c
                 B200CheckStatus(b200k_instance_norm_q(&st->p, s));
             });
         }
+        case LayerType::Convolution3d:
+        {
+            const auto& qd = *PolymorphicDowncast<const Convolution3dQueueDescriptor*>(&d);
+            const auto& prm = qd.m_Parameters;
+            auto st = std::make_shared<SimpleState<b200k_conv3d_params>>(ctx);
+            b200k_conv3d_params& p = st->p;
+            std::memset(&p, 0, sizeof(p));
+            const TensorInfo& x = info.m_InputTensorInfos[0];
+            const TensorInfo& w = info.m_InputTensorInfos[1];
+            const TensorInfo& y = info.m_OutputTensorInfos[0];
+            if (prm.m_DataLayout != DataLayout::NDHWC || x.GetNumDimensions() != 5 || w.GetNumDimensions() != 5 || y.GetNumDimensions() != 5)
+            {
+                throw InvalidArgumentException("B200Acc: Convolution3d needs 5-D NDHWC tensors");
+            }
+            p.x = Operand(x, st->blobs); p.w = Operand(w, st->blobs); p.y = Operand(y, st->blobs);
+            const bool bias = prm.m_BiasEnabled && info.m_InputTensorInfos.size() > 2;
+            if (bias) { p.bias = Operand(info.m_InputTensorInfos[2], st->blobs); }
+            p.n = static_cast<int32_t>(x.GetShape()[0]); p.d = static_cast<int32_t>(x.GetShape()[1]); p.h = static_cast<int32_t>(x.GetShape()[2]);
+            p.wd = static_cast<int32_t>(x.GetShape()[3]); p.c = static_cast<int32_t>(x.GetShape()[4]);
+            p.od = static_cast<int32_t>(y.GetShape()[1]); p.oh = static_cast<int32_t>(y.GetShape()[2]); p.ow = static_cast<int32_t>(y.GetShape()[3]);
+            p.oc = static_cast<int32_t>(y.GetShape()[4]);
+            p.kd = static_cast<int32_t>(w.GetShape()[0]); p.kh = static_cast<int32_t>(w.GetShape()[1]); p.kw = static_cast<int32_t>(w.GetShape()[2]);
+            if (w.GetShape()[3] != x.GetShape()[4] || w.GetShape()[4] != y.GetShape()[4]) { throw InvalidArgumentException("B200Acc: Convolution3d weights do not match the channel counts"); }
+            p.stride_d = static_cast<int32_t>(prm.m_StrideZ); p.stride_h = static_cast<int32_t>(prm.m_StrideY); p.stride_w = static_cast<int32_t>(prm.m_StrideX);
+            p.pad_front = static_cast<int32_t>(prm.m_PadFront); p.pad_top = static_cast<int32_t>(prm.m_PadTop); p.pad_left = static_cast<int32_t>(prm.m_PadLeft);
+            p.dil_d = static_cast<int32_t>(prm.m_DilationZ); p.dil_h = static_cast<int32_t>(prm.m_DilationY); p.dil_w = static_cast<int32_t>(prm.m_DilationX);
+            if (y.GetDataType() != DataType::Float32) { Clamp(qd.GetAdditionalInformation<ActivationDescriptor>(), y, p.clamp_lo, p.clamp_hi); }
+            return Make<Convolution3dQueueDescriptor>(d, info, ctx, [st, bias](const Convolution3dQueueDescriptor& data, cudaStream_t s)
+            {
+                st->p.x.data = Dev(data.m_Inputs[0]); st->p.w.data = Dev(data.m_Inputs[1]);
+                if (bias) { st->p.bias.data = Dev(data.m_Inputs[2]); }
+                st->p.y.data = Dev(data.m_Outputs[0]);
+                B200CheckStatus(b200k_conv3d_q(&st->p, s));
+            });
+        }
+        case LayerType::Pooling3d:
+        {
+            const auto& prm = PolymorphicDowncast<const Pooling3dQueueDescriptor*>(&d)->m_Parameters;
+            auto st = std::make_shared<SimpleState<b200k_pool3d_params>>(ctx);
+            b200k_pool3d_params& p = st->p;
+            std::memset(&p, 0, sizeof(p));
+            const TensorInfo& x = info.m_InputTensorInfos[0];
+            const TensorInfo& y = info.m_OutputTensorInfos[0];
+            if (prm.m_DataLayout != DataLayout::NDHWC || x.GetNumDimensions() != 5 || y.GetNumDimensions() != 5) { throw InvalidArgumentException("B200Acc: Pooling3d needs 5-D NDHWC tensors"); }
+            p.x = Operand(x, st->blobs); p.y = Operand(y, st->blobs);
+            p.n = static_cast<int32_t>(x.GetShape()[0]); p.d = static_cast<int32_t>(x.GetShape()[1]); p.h = static_cast<int32_t>(x.GetShape()[2]);
+            p.wd = static_cast<int32_t>(x.GetShape()[3]); p.c = static_cast<int32_t>(x.GetShape()[4]);
+            p.od = static_cast<int32_t>(y.GetShape()[1]); p.oh = static_cast<int32_t>(y.GetShape()[2]); p.ow = static_cast<int32_t>(y.GetShape()[3]);
+            p.pool_d = static_cast<int32_t>(prm.m_PoolDepth); p.pool_h = static_cast<int32_t>(prm.m_PoolHeight); p.pool_w = static_cast<int32_t>(prm.m_PoolWidth);
+            p.stride_d = static_cast<int32_t>(prm.m_StrideZ); p.stride_h = static_cast<int32_t>(prm.m_StrideY); p.stride_w = static_cast<int32_t>(prm.m_StrideX);
+            p.pad_front = static_cast<int32_t>(prm.m_PadFront); p.pad_back = static_cast<int32_t>(prm.m_PadBack); p.pad_top = static_cast<int32_t>(prm.m_PadTop);
+            p.pad_bottom = static_cast<int32_t>(prm.m_PadBottom); p.pad_left = static_cast<int32_t>(prm.m_PadLeft); p.pad_right = static_cast<int32_t>(prm.m_PadRight);
+            p.pool_type = static_cast<int32_t>(prm.m_PoolType);
+            p.padding_method = prm.m_PaddingMethod == PaddingMethod::Exclude ? 1 : 0;
+            return Make<Pooling3dQueueDescriptor>(d, info, ctx, [st](const Pooling3dQueueDescriptor& data, cudaStream_t s)
+            {
+                st->p.x.data = Dev(data.m_Inputs[0]); st->p.y.data = Dev(data.m_Outputs[0]);
+                B200CheckStatus(b200k_pool3d_q(&st->p, s));
+            });
+        }
         case LayerType::Cast:
         {
             auto st = std::make_shared<SimpleState<b200k_convert_params>>(ctx);

@@ -114,6 +114,8 @@ extern "C" size_t b200k_sizeof_params(int which)
         case 17: return sizeof(b200k_batch_norm_params);
         case 18: return sizeof(b200k_instance_norm_params);
         case 19: return sizeof(b200k_normalization_params);
+        case 20: return sizeof(b200k_conv3d_params);
+        case 21: return sizeof(b200k_pool3d_params);
         default: return 0;
     }
 }

@@ -219,6 +219,33 @@ int armnnc_add_pool2d(void* vn, int pool_type, int padding_method, int pool_h, i
     return add_layer(n, n->net->AddPooling2dLayer(d));
 }
 
+/// strides / dilations: (depth, height, width); pads: (front, back, top, bottom, left, right); NDHWC
+int armnnc_add_conv3d(void* vn, const int32_t* strides, const int32_t* pads, const int32_t* dilations, int bias_enabled)
+{
+    auto* n = static_cast<CNet*>(vn);
+    Convolution3dDescriptor d;
+    d.m_StrideZ = (unsigned)strides[0]; d.m_StrideY = (unsigned)strides[1]; d.m_StrideX = (unsigned)strides[2];
+    d.m_PadFront = (unsigned)pads[0]; d.m_PadBack = (unsigned)pads[1]; d.m_PadTop = (unsigned)pads[2]; d.m_PadBottom = (unsigned)pads[3];
+    d.m_PadLeft = (unsigned)pads[4]; d.m_PadRight = (unsigned)pads[5];
+    d.m_DilationZ = (unsigned)dilations[0]; d.m_DilationY = (unsigned)dilations[1]; d.m_DilationX = (unsigned)dilations[2];
+    d.m_BiasEnabled = bias_enabled != 0; d.m_DataLayout = DataLayout::NDHWC;
+    return add_layer(n, n->net->AddConvolution3dLayer(d));
+}
+
+int armnnc_add_pool3d(void* vn, int pool_type, int padding_method, const int32_t* pool, const int32_t* strides, const int32_t* pads)
+{
+    auto* n = static_cast<CNet*>(vn);
+    Pooling3dDescriptor d;
+    d.m_PoolType = static_cast<PoolingAlgorithm>(pool_type);
+    d.m_PaddingMethod = padding_method == 1 ? PaddingMethod::Exclude : PaddingMethod::IgnoreValue;
+    d.m_PoolDepth = (unsigned)pool[0]; d.m_PoolHeight = (unsigned)pool[1]; d.m_PoolWidth = (unsigned)pool[2];
+    d.m_StrideZ = (unsigned)strides[0]; d.m_StrideY = (unsigned)strides[1]; d.m_StrideX = (unsigned)strides[2];
+    d.m_PadFront = (unsigned)pads[0]; d.m_PadBack = (unsigned)pads[1]; d.m_PadTop = (unsigned)pads[2]; d.m_PadBottom = (unsigned)pads[3];
+    d.m_PadLeft = (unsigned)pads[4]; d.m_PadRight = (unsigned)pads[5];
+    d.m_OutputShapeRounding = OutputShapeRounding::Floor; d.m_DataLayout = DataLayout::NDHWC;
+    return add_layer(n, n->net->AddPooling3dLayer(d));
+}
+
 int armnnc_add_elementwise_binary(void* vn, int op)
 {
     auto* n = static_cast<CNet*>(vn);

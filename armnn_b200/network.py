@@ -190,6 +190,19 @@ class INetwork:
         return self._add(Layer("Convolution2d", name, 3 if bias_enabled else 2, 1,
                                {"stride": stride, "pad": pad, "dilation": dilation, "bias": bias_enabled}))
 
+    def AddConvolution3dLayer(self, stride=(1, 1, 1), pad=(0, 0, 0, 0, 0, 0), dilation=(1, 1, 1), bias_enabled=True, name=None):
+        """armnn::Convolution3dDescriptor, NDHWC: stride / dilation = (depth, height, width), pad = (front, back, top,
+        bottom, left, right); inputs: 0 data [N,D,H,W,C], 1 weights [D,H,W,I,O], 2 bias."""
+        return self._add(Layer("Convolution3d", name, 3 if bias_enabled else 2, 1,
+                               {"stride": tuple(stride), "pad": tuple(pad), "dilation": tuple(dilation), "bias": bias_enabled}))
+
+    def AddPooling3dLayer(self, pool_type, pool=(2, 2, 2), stride=(2, 2, 2), pad=(0, 0, 0, 0, 0, 0),
+                          padding_method=PaddingMethod.Exclude, name=None):
+        """armnn::Pooling3dDescriptor, NDHWC: pool / stride = (depth, height, width), pad = (front, back, top, bottom,
+        left, right)."""
+        return self._add(Layer("Pooling3d", name, 1, 1, {"type": PoolingAlgorithm(pool_type), "pool": tuple(pool), "stride": tuple(stride),
+                                                          "pad": tuple(pad), "method": PaddingMethod(padding_method)}))
+
     def AddDepthwiseConvolution2dLayer(self, stride=(1, 1), pad=(0, 0, 0, 0), dilation=(1, 1), bias_enabled=True, name=None):
         """weights [1,H,W,I*M]"""
         return self._add(Layer("DepthwiseConvolution2d", name, 3 if bias_enabled else 2, 1,
@@ -512,6 +525,26 @@ def IsLayerSupported(layer):
         if mode and any(max(a, b) + (mode == 1) > n for (a, b), n in zip(layer.desc["pads"], ins[0].shape)):
             return False, "Pad: mirrored padding wider than the tensor"
         return True, ""
+    if t == "Convolution3d":
+        q8 = (DataType.QAsymmU8, DataType.QAsymmS8)
+        if len(ins[0].shape) != 5 or len(ins[1].shape) != 5:
+            return False, "Convolution3d: 5-D input and weights"
+        if ins[0].dtype == DataType.Float32:
+            if any(i.dtype != DataType.Float32 for i in list(ins) + list(outs)):
+                return False, "Convolution3d: a Float32 input needs Float32 weights, bias and output"
+            return True, ""
+        if ins[0].dtype not in q8 or outs[0].dtype not in q8 or ins[1].dtype not in q8 + (DataType.QSymmS8,):
+            return False, "Convolution3d: 8-bit quantised tensors or Float32 only"
+        if len(ins) > 2 and ins[2].dtype != DataType.Signed32:
+            return False, "Convolution3d: bias must be Signed32"
+        if ins[1].scales is not None and ins[1].quant_dim != 4:
+            return False, "Convolution3d: per-axis weights must be quantised along the output channels"
+        return True, ""
+    if t == "Pooling3d":
+        ok = (DataType.QAsymmU8, DataType.QAsymmS8, DataType.QSymmS16, DataType.Float32)
+        if len(ins[0].shape) != 5 or ins[0].dtype not in ok or outs[0].dtype != ins[0].dtype:
+            return False, "Pooling3d: 5-D tensors of one supported data type"
+        return True, ""
     if t == "Cast":
         ok = (DataType.QAsymmU8, DataType.QAsymmS8, DataType.QSymmS8, DataType.QSymmS16, DataType.Signed32, DataType.Float32)
         if ins[0].dtype not in ok or outs[0].dtype not in ok or ins[0].GetNumElements() != outs[0].GetNumElements():
@@ -829,6 +862,36 @@ class GraphProgram:
             p.packed = self._pack_weights(p)
             self._attach_scratch(p)
         return p
+
+    def _make_Convolution3d(self, layer):
+        x, w, y, d = layer.inputs[0].source, layer.inputs[1].source, layer.outputs[0], layer.desc
+        p = _abi.Conv3dParams()
+        p.x, p.w, p.y = self._operand(x), self._operand(w), self._operand(y)
+        if d["bias"]:
+            p.bias = self._operand(layer.inputs[2].source)
+        p.n, p.d, p.h, p.wd, p.c = x.info.shape
+        _, p.od, p.oh, p.ow, p.oc = y.info.shape
+        p.kd, p.kh, p.kw = w.info.shape[:3]
+        if tuple(w.info.shape[3:]) != (p.c, p.oc):
+            raise InvalidArgumentException("Convolution3d: weights %s do not match %d input and %d output channels" % (w.info.shape, p.c, p.oc))
+        p.stride_d, p.stride_h, p.stride_w = d["stride"]
+        p.pad_front, p.pad_top, p.pad_left = d["pad"][0], d["pad"][2], d["pad"][4]
+        p.dil_d, p.dil_h, p.dil_w = d["dilation"]
+        if y.info.dtype != DataType.Float32:
+            p.clamp_lo, p.clamp_hi = _clamp(layer, y.info)
+        return "conv3d_q", p
+
+    def _make_Pooling3d(self, layer):
+        x, y, d = layer.inputs[0].source, layer.outputs[0], layer.desc
+        p = _abi.Pool3dParams()
+        p.x, p.y = self._operand(x), self._operand(y)
+        p.n, p.d, p.h, p.wd, p.c = x.info.shape
+        _, p.od, p.oh, p.ow, _ = y.info.shape
+        p.pool_d, p.pool_h, p.pool_w = d["pool"]
+        p.stride_d, p.stride_h, p.stride_w = d["stride"]
+        p.pad_front, p.pad_back, p.pad_top, p.pad_bottom, p.pad_left, p.pad_right = d["pad"]
+        p.pool_type, p.padding_method = int(d["type"]), int(d["method"])
+        return "pool3d_q", p
 
     def _make_Convolution2d(self, layer):
         if layer.outputs[0].info.dtype == DataType.Float32:

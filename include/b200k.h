@@ -211,6 +211,38 @@ typedef struct {
 
 int b200k_mean_hw_q8(const b200k_mean_params* p, void* stream);
 
+/* ---- Convolution3d, Pooling3d --------------------------------------------------------------- */
+
+/* armnn::Convolve3d (src/backends/reference/workloads/Conv3dImpl.cpp:14-177), DataLayout::NDHWC: x [n, d, h, wd, c],
+ * weights [kd, kh, kw, c, oc] (per-tensor, or per-axis scales along oc), bias [oc] Signed32, y [n, od, oh, ow, oc].
+ * Quantised tensors: exact int32 accumulation of (x - zx)(w - zw) and the epilogue of b200k_conv2d_q8; Float32
+ * throughout: the reference's term order (z, y, x, input channel), products and sums rounded separately. */
+typedef struct {
+    b200k_qtensor x, w, bias, y;
+    int32_t n, d, h, wd, c;
+    int32_t od, oh, ow, oc;
+    int32_t kd, kh, kw;
+    int32_t stride_d, stride_h, stride_w;
+    int32_t pad_front, pad_top, pad_left;
+    int32_t dil_d, dil_h, dil_w;
+    int32_t clamp_lo, clamp_hi;
+} b200k_conv3d_params;
+
+int b200k_conv3d_q(const b200k_conv3d_params* p, void* stream);
+
+/* armnn::Pooling3d (src/backends/reference/workloads/Pooling3d.cpp:138-328), DataLayout::NDHWC.  pool_type and
+ * padding_method as in b200k_pool2d_params; a window that lies in the padding only yields 0. */
+typedef struct {
+    b200k_qtensor x, y;
+    int32_t n, d, h, wd, c;
+    int32_t od, oh, ow;
+    int32_t pool_d, pool_h, pool_w, stride_d, stride_h, stride_w;
+    int32_t pad_front, pad_back, pad_top, pad_bottom, pad_left, pad_right;
+    int32_t pool_type, padding_method;
+} b200k_pool3d_params;
+
+int b200k_pool3d_q(const b200k_pool3d_params* p, void* stream);
+
 /* ---- ElementwiseBinary / Activation ------------------------------------------------------- */
 
 /* ElementwiseBinaryFunction<std::plus / std::multiplies / ...> with BroadcastLoop
@@ -530,7 +562,7 @@ unsigned long long b200k_kernel_launches(void);
 
 /* sizeof() of a parameter struct as compiled into the library, for bindings in other languages to check their
  * own declarations: 0 conv2d, 1 fc, 2 bmm, 3 pool2d, 4 mean, 5 eltwise, 6 activation, 7 softmax, 8 convert,
- * 9 qlstm, 10 pad, 11 view_copy, 12 resize, 13 reduce, 14 unary, 15 arg_min_max, 16 gather, 17 batch_norm, 18 instance_norm, 19 normalization.  No counterpart in the reference (its backends are linked as C++). */
+ * 9 qlstm, 10 pad, 11 view_copy, 12 resize, 13 reduce, 14 unary, 15 arg_min_max, 16 gather, 17 batch_norm, 18 instance_norm, 19 normalization, 20 conv3d, 21 pool3d.  No counterpart in the reference (its backends are linked as C++). */
 size_t b200k_sizeof_params(int which);
 
 #ifdef __cplusplus

@@ -467,6 +467,54 @@ extern "C" int cpuref_cast_q(const b200k_convert_params* p)
     });
 }
 
+extern "C" int cpuref_conv3d_q(const b200k_conv3d_params* p)
+{
+    return guarded([&] {
+        Harness h;
+        const unsigned OC = (unsigned)p->oc;
+        TensorInfo xi = make_info(p->x, TensorShape({(unsigned)p->n, (unsigned)p->d, (unsigned)p->h, (unsigned)p->wd, (unsigned)p->c}), 0, 0, false);
+        TensorInfo wi = make_info(p->w, TensorShape({(unsigned)p->kd, (unsigned)p->kh, (unsigned)p->kw, (unsigned)p->c, OC}), 4, OC, true);
+        TensorInfo yi = make_info(p->y, TensorShape({(unsigned)p->n, (unsigned)p->od, (unsigned)p->oh, (unsigned)p->ow, OC}), 0, 0, false);
+        Convolution3dQueueDescriptor d;
+        auto& q = d.m_Parameters;
+        q.m_PadFront = (unsigned)p->pad_front; q.m_PadTop = (unsigned)p->pad_top; q.m_PadLeft = (unsigned)p->pad_left;
+        q.m_PadBack = 0; q.m_PadBottom = 0; q.m_PadRight = 0;          // only shape inference reads them
+        q.m_StrideX = (unsigned)p->stride_w; q.m_StrideY = (unsigned)p->stride_h; q.m_StrideZ = (unsigned)p->stride_d;
+        q.m_DilationX = (unsigned)p->dil_w; q.m_DilationY = (unsigned)p->dil_h; q.m_DilationZ = (unsigned)p->dil_d;
+        q.m_BiasEnabled = p->bias.data != nullptr;
+        q.m_DataLayout = DataLayout::NDHWC;
+        h.in(d, xi, p->x.data);
+        h.in(d, wi, p->w.data);
+        if (p->bias.data) h.in(d, make_info(p->bias, TensorShape({OC}), 0, OC, true), p->bias.data);
+        ITensorHandle* o = h.out(d, yi);
+        h.run(LayerType::Convolution3d, d);
+        copy_out(o, const_cast<void*>(p->y.data), yi.GetNumBytes());
+    });
+}
+
+extern "C" int cpuref_pool3d_q(const b200k_pool3d_params* p)
+{
+    return guarded([&] {
+        Harness h;
+        TensorInfo xi = make_info(p->x, TensorShape({(unsigned)p->n, (unsigned)p->d, (unsigned)p->h, (unsigned)p->wd, (unsigned)p->c}), 0, 0, false);
+        TensorInfo yi = make_info(p->y, TensorShape({(unsigned)p->n, (unsigned)p->od, (unsigned)p->oh, (unsigned)p->ow, (unsigned)p->c}), 0, 0, false);
+        Pooling3dQueueDescriptor d;
+        auto& q = d.m_Parameters;
+        q.m_PoolType = static_cast<PoolingAlgorithm>(p->pool_type);
+        q.m_PaddingMethod = p->padding_method == 1 ? PaddingMethod::Exclude : PaddingMethod::IgnoreValue;
+        q.m_PoolDepth = (unsigned)p->pool_d; q.m_PoolHeight = (unsigned)p->pool_h; q.m_PoolWidth = (unsigned)p->pool_w;
+        q.m_StrideZ = (unsigned)p->stride_d; q.m_StrideY = (unsigned)p->stride_h; q.m_StrideX = (unsigned)p->stride_w;
+        q.m_PadFront = (unsigned)p->pad_front; q.m_PadBack = (unsigned)p->pad_back; q.m_PadTop = (unsigned)p->pad_top;
+        q.m_PadBottom = (unsigned)p->pad_bottom; q.m_PadLeft = (unsigned)p->pad_left; q.m_PadRight = (unsigned)p->pad_right;
+        q.m_OutputShapeRounding = OutputShapeRounding::Floor;
+        q.m_DataLayout = DataLayout::NDHWC;
+        h.in(d, xi, p->x.data);
+        ITensorHandle* o = h.out(d, yi);
+        h.run(LayerType::Pooling3d, d);
+        copy_out(o, const_cast<void*>(p->y.data), yi.GetNumBytes());
+    });
+}
+
 extern "C" int cpuref_softmax_q8(const b200k_softmax_params* p)
 {
     return guarded([&] {

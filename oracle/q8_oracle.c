@@ -766,6 +766,92 @@ int oracle_normalization_q(const b200k_normalization_params* p)
     return 0;
 }
 
+/* ---- Convolution3d, Conv3dImpl.cpp:14-177 (NDHWC, weights [D, H, W, I, O]) ------------------------- */
+
+int oracle_conv3d_q(const b200k_conv3d_params* p)
+{
+    if (!p->x.data || !p->w.data || !p->y.data) return B200K_E_INVALID;
+    const int f32 = p->x.dtype == B200K_F32;
+    const int zx = p->x.zero_point, zw = p->w.zero_point;
+    #pragma omp parallel for collapse(2) schedule(static)
+    for (int b = 0; b < p->n; ++b)
+    for (int oz = 0; oz < p->od; ++oz)
+    for (int oy = 0; oy < p->oh; ++oy)
+    for (int ox = 0; ox < p->ow; ++ox)
+    for (int co = 0; co < p->oc; ++co) {
+        int32_t acc = 0;
+        volatile float sum = 0.0f;
+        for (int kz = 0; kz < p->kd; ++kz) {
+            const int iz = oz * p->stride_d + kz * p->dil_d - p->pad_front;
+            for (int ky = 0; ky < p->kh; ++ky) {
+                const int iy = oy * p->stride_h + ky * p->dil_h - p->pad_top;
+                for (int kx = 0; kx < p->kw; ++kx) {
+                    const int ix = ox * p->stride_w + kx * p->dil_w - p->pad_left;
+                    const int inside = iz >= 0 && iz < p->d && iy >= 0 && iy < p->h && ix >= 0 && ix < p->wd;
+                    const int64_t xb = ((((int64_t)b * p->d + iz) * p->h + iy) * p->wd + ix) * p->c;
+                    const int64_t wb = ((((int64_t)kz * p->kh + ky) * p->kw + kx) * p->c) * p->oc + co;
+                    for (int ci = 0; ci < p->c; ++ci) {
+                        if (f32) {
+                            const float xv = inside ? ((const float*)p->x.data)[xb + ci] : 0.0f;      /* :96-103 */
+                            volatile float prod = ((const float*)p->w.data)[wb + (int64_t)ci * p->oc] * xv;
+                            sum = sum + prod;
+                        } else if (inside) {
+                            acc += (load_q(p->x.data, p->x.dtype, xb + ci) - zx) *
+                                   (load_q(p->w.data, p->w.dtype, wb + (int64_t)ci * p->oc) - zw);
+                        }
+                    }
+                }
+            }
+        }
+        const int64_t oi = ((((int64_t)b * p->od + oz) * p->oh + oy) * p->ow + ox) * p->oc + co;
+        if (f32) {
+            if (p->bias.data) sum = sum + ((const float*)p->bias.data)[co];
+            ((float*)p->y.data)[oi] = sum;
+            continue;
+        }
+        const float sw = p->w.scales ? p->w.scales[co] : p->w.scale;
+        const int has_bias = p->bias.data != NULL;
+        const int32_t bq = has_bias ? ((const int32_t*)p->bias.data)[co] : 0;
+        const float sb = p->bias.scales ? p->bias.scales[co] : p->bias.scale;
+        store_q((void*)p->y.data, p->y.dtype, oi,
+                requant(acc, p->x.scale, sw, has_bias, bq, sb, p->y.scale, p->y.zero_point, p->y.dtype, p->clamp_lo, p->clamp_hi));
+    }
+    return 0;
+}
+
+/* ---- Pooling3d, Pooling3d.cpp:138-328 (NDHWC) -------------------------------------------------------- */
+
+/* clamp_range above is Pooling3d.cpp:100-111 as well */
+int oracle_pool3d_q(const b200k_pool3d_params* p)
+{
+    if (!p->x.data || !p->y.data || p->pool_type < 0 || p->pool_type > 2) return B200K_E_INVALID;
+    for (int n = 0; n < p->n; ++n) for (int c = 0; c < p->c; ++c)
+    for (int oz = 0; oz < p->od; ++oz) for (int oy = 0; oy < p->oh; ++oy) for (int ox = 0; ox < p->ow; ++ox) {
+        int ds = oz * p->stride_d - p->pad_front, de = ds + p->pool_d;
+        if (de > p->d + p->pad_back) de = p->d + p->pad_back;
+        int hs = oy * p->stride_h - p->pad_top, he = hs + p->pool_h;
+        if (he > p->h + p->pad_bottom) he = p->h + p->pad_bottom;
+        int ws = ox * p->stride_w - p->pad_left, we = ws + p->pool_w;
+        if (we > p->wd + p->pad_right) we = p->wd + p->pad_right;
+        float pool = (float)((de - ds) * (he - hs) * (we - ws));
+        const int dcl = clamp_range(&ds, &de, p->d), hcl = clamp_range(&hs, &he, p->h), wcl = clamp_range(&ws, &we, p->wd);
+        const int64_t oi = ((((int64_t)n * p->od + oz) * p->oh + oy) * p->ow + ox) * p->c + c;
+        if (de <= 0 || ds > p->d || he <= 0 || hs > p->h || we <= 0 || ws > p->wd) { store_f(&p->y, oi, 0.0f); continue; }
+        if ((dcl || hcl || wcl) && p->padding_method == 1) pool = (float)((de - ds) * (he - hs) * (we - ws));
+        volatile float result = p->pool_type == 0 ? -3.402823466e+38f : 0.0f;
+        for (int z = ds; z < de; ++z) for (int y = hs; y < he; ++y) for (int x = ws; x < we; ++x) {
+            const float v = load_f(&p->x, ((((int64_t)n * p->d + z) * p->h + y) * p->wd + x) * p->c + c);
+            if (p->pool_type == 0) { if (v > result) result = v; }
+            else if (p->pool_type == 1) result = result + v;
+            else { volatile float sq = v * v; result = result + sq; }
+        }
+        if (p->pool_type == 1) result = result / pool;
+        else if (p->pool_type == 2) { volatile float q = result / pool; result = sqrtf(q); }
+        store_f(&p->y, oi, result);
+    }
+    return 0;
+}
+
 /* ---- Quantize / Dequantize / requantize, RefQuantizeWorkload.cpp:14-45, Dequantize.cpp:11-28 - */
 
 int oracle_convert_q(const b200k_convert_params* p)

@@ -515,6 +515,86 @@ TRANSCENDENTAL_NORM = ("lrn_across_nhwc", "lrn_across_nchw_u8", "lrn_across_floa
 CPUREF_REFUSES = {("norm", "gather_negative_indices_s16"), ("norm", "gather_float_rows_aligned")}
 
 
+def volume_cases():
+    """Convolution3d and Pooling3d on NDHWC tensors."""
+    def conv3d(seed, n, dims, c, oc, k, stride=(1, 1, 1), pad=(0, 0, 0, 0, 0, 0), dil=(1, 1, 1), dtype=S8, per_axis=False, bias=True):
+        def build(mem):
+            rng = np.random.default_rng(seed)
+            p = _abi.Conv3dParams()
+            d, h, w = dims
+            pf, pb, pt, pbm, pl, pr = pad
+            od = (d + pf + pb - dil[0] * (k[0] - 1) - 1) // stride[0] + 1
+            oh = (h + pt + pbm - dil[1] * (k[1] - 1) - 1) // stride[1] + 1
+            ow = (w + pl + pr - dil[2] * (k[2] - 1) - 1) // stride[2] + 1
+            if dtype == F32:
+                p.x = qt(mem, rng.standard_normal((n, d, h, w, c)).astype(np.float32), F32)
+                p.w = qt(mem, (rng.standard_normal(k + (c, oc)) * 0.3).astype(np.float32), F32)
+                if bias:
+                    p.bias = qt(mem, rng.standard_normal(oc).astype(np.float32), F32)
+                p.y, y = qt_out(mem, (n, od, oh, ow, oc), F32)
+            else:
+                sx = 0.05
+                p.x = qt(mem, _rand(rng, dtype, (n, d, h, w, c)), dtype, sx, 3 if dtype == S8 else 120)
+                wd = S8 if (per_axis or dtype == S8) else U8
+                wdata = _rand(rng, wd, k + (c, oc))
+                if per_axis:
+                    scales = (rng.random(oc) * 0.02 + 0.005).astype(np.float32)
+                    p.w = qt(mem, wdata, S8, 1.0, 0, scales=scales)
+                    bsc = (scales * np.float32(sx)).astype(np.float32)
+                    if bias:
+                        p.bias = qt(mem, rng.integers(-2000, 2000, size=(oc,)).astype(np.int32), S32, 1.0, 0, scales=bsc)
+                else:
+                    sw = 0.01
+                    p.w = qt(mem, wdata, wd, sw, 0 if wd == S8 else 131)
+                    if bias:
+                        p.bias = qt(mem, rng.integers(-2000, 2000, size=(oc,)).astype(np.int32), S32, sx * sw, 0)
+                fan = k[0] * k[1] * k[2] * c
+                p.y, y = qt_out(mem, (n, od, oh, ow, oc), dtype, 0.05 * 0.01 * 64 * np.sqrt(fan), -5 if dtype == S8 else 110)
+                lo, hi = RANGE[dtype]
+                p.clamp_lo, p.clamp_hi = lo, hi
+            p.n, p.d, p.h, p.wd, p.c, p.od, p.oh, p.ow, p.oc = n, d, h, w, c, od, oh, ow, oc
+            p.kd, p.kh, p.kw = k
+            p.stride_d, p.stride_h, p.stride_w = stride
+            p.pad_front, p.pad_top, p.pad_left = pf, pt, pl
+            p.dil_d, p.dil_h, p.dil_w = dil
+            return p, [y]
+        return lambda: SimpleCase("conv3d_q", build)
+
+    def pool3d(seed, n, dims, c, pool, stride, pad=(0, 0, 0, 0, 0, 0), pool_type=0, method=1, dtype=S8):
+        def build(mem):
+            rng = np.random.default_rng(seed)
+            p = _abi.Pool3dParams()
+            d, h, w = dims
+            pf, pb, pt, pbm, pl, pr = pad
+            od, oh, ow = (d + pf + pb - pool[0]) // stride[0] + 1, (h + pt + pbm - pool[1]) // stride[1] + 1, (w + pl + pr - pool[2]) // stride[2] + 1
+            if dtype == F32:
+                p.x = qt(mem, rng.standard_normal((n, d, h, w, c)).astype(np.float32), F32)
+                p.y, y = qt_out(mem, (n, od, oh, ow, c), F32)
+            else:
+                q = (0.05, 3) if dtype == S8 else (0.05, 120)
+                p.x = qt(mem, _rand(rng, dtype, (n, d, h, w, c)), dtype, *q)
+                p.y, y = qt_out(mem, (n, od, oh, ow, c), dtype, *q)
+            p.n, p.d, p.h, p.wd, p.c, p.od, p.oh, p.ow = n, d, h, w, c, od, oh, ow
+            p.pool_d, p.pool_h, p.pool_w = pool
+            p.stride_d, p.stride_h, p.stride_w = stride
+            p.pad_front, p.pad_back, p.pad_top, p.pad_bottom, p.pad_left, p.pad_right = pad
+            p.pool_type, p.padding_method = pool_type, method
+            return p, [y]
+        return lambda: SimpleCase("pool3d_q", build)
+    return {
+        "conv3d_3x3x3_same": conv3d(401, 1, (5, 6, 7), 4, 8, (3, 3, 3), pad=(1, 1, 1, 1, 1, 1)),
+        "conv3d_u8_stride2_ragged": conv3d(402, 2, (6, 5, 7), 3, 5, (2, 3, 2), stride=(2, 1, 2), pad=(0, 0, 1, 0, 0, 1), dtype=U8),
+        "conv3d_per_axis_dilated": conv3d(403, 1, (7, 7, 6), 6, 10, (2, 2, 2), dil=(2, 1, 3), per_axis=True),
+        "conv3d_no_bias_1x1x1": conv3d(404, 2, (3, 4, 5), 16, 7, (1, 1, 1), bias=False),
+        "conv3d_float": conv3d(405, 1, (4, 5, 6), 3, 6, (3, 2, 3), stride=(1, 2, 1), pad=(1, 1, 0, 1, 1, 1), dtype=F32),
+        "pool3d_max_2x2x2": pool3d(406, 2, (6, 8, 6), 5, (2, 2, 2), (2, 2, 2)),
+        "pool3d_average_exclude_padded_u8": pool3d(407, 1, (5, 6, 7), 3, (3, 3, 3), (2, 2, 2), pad=(1, 1, 1, 1, 1, 1), pool_type=1, dtype=U8),
+        "pool3d_average_ignore_value_padded": pool3d(408, 1, (4, 5, 5), 4, (2, 3, 2), (1, 2, 2), pad=(1, 0, 1, 1, 0, 1), pool_type=1, method=0),
+        "pool3d_l2_float": pool3d(409, 2, (4, 4, 6), 3, (2, 2, 3), (2, 2, 3), pool_type=2, dtype=F32),
+        "pool3d_max_padded_float": pool3d(410, 1, (5, 5, 5), 2, (3, 3, 3), (2, 2, 2), pad=(1, 1, 1, 1, 1, 1), dtype=F32),
+    }
+
+
 def convert_cases():
     def make(seed, xd, yd, count=1001, xq=(0.05, 3), yq=(0.07, -4), entry="convert_q", fscale=4):
         def build(mem):
@@ -854,7 +934,7 @@ def move_cases():
 ALL_GROUPS = {"conv": conv_cases, "dwconv": dwconv_cases, "fc": fc_cases, "bmm": bmm_cases, "pool": pool_cases,
               "mean": mean_cases, "eltwise": eltwise_cases, "activation": activation_cases, "softmax": softmax_cases,
               "convert": convert_cases, "pad": pad_cases, "qlstm": qlstm_cases, "move": move_cases, "resize": resize_cases, "reduce": reduce_cases, "tconv": tconv_cases, "f32": f32_cases, "unary": unary_cases,
-              "rows": rows_cases, "norm": norm_cases}
+              "rows": rows_cases, "norm": norm_cases, "volume": volume_cases}
 
 
 def run_case(case, where):

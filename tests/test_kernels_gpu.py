@@ -19,7 +19,7 @@ from q8util import diff_stats
 
 pytestmark = pytest.mark.gpu
 
-EXACT_GROUPS = ("conv", "dwconv", "fc", "bmm", "pool", "mean", "eltwise", "convert", "pad", "move", "resize", "reduce", "tconv", "f32", "norm")
+EXACT_GROUPS = ("conv", "dwconv", "fc", "bmm", "pool", "mean", "eltwise", "convert", "pad", "move", "resize", "reduce", "tconv", "f32", "norm", "volume")
 ALL = [(g, n, f) for g, fn in cases.ALL_GROUPS.items() for n, f in fn().items()]
 
 

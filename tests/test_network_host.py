@@ -298,3 +298,15 @@ def test_cast_and_fill_graph_oracle_equals_armnn_cpuref(built):
     want = hostnet.ArmnnNetwork(net, "CpuRef").run(xs)[0]
     got = hostnet.OracleNetwork(Optimize(net)).run(xs)[0]
     assert want.dtype == np.int32 and np.array_equal(want, got)
+
+
+@needs_cpuref
+def test_volume_graph_oracle_vs_armnn_cpuref(built):
+    import hostnet
+    from test_plugin import _volume_net
+    net = _volume_net()
+    x = np.random.default_rng(74).integers(-128, 128, size=(1, 6, 8, 8, 4)).astype(np.int8)
+    want = hostnet.ArmnnNetwork(net, "CpuRef").run({0: x})[0]
+    got = hostnet.OracleNetwork(Optimize(net)).run({0: x})[0]
+    st = diff_stats(want, got)
+    assert want.shape == got.shape and st["max_abs"] <= 1 and st["mismatch_frac"] < 5e-3, st

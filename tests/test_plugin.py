@@ -1122,3 +1122,46 @@ def test_cast_and_fill_through_the_runtime_equal_cpuref():
     got = hostnet.ArmnnNetwork(net, "B200Acc").run(xs)[0]
     assert ref.dtype == np.int32 and np.array_equal(ref, np.floor(xs[0].astype(np.float32) * np.float32(2.75)).astype(np.int32))
     assert np.array_equal(ref, got)
+
+
+def _volume_net():
+    """A small volumetric network: Convolution3d (per-axis weights, bias) -> Pooling3d (Max) -> Pooling3d (Average, padded)."""
+    from armnn_b200.network import DataType, INetwork, PoolingAlgorithm, TensorInfo
+    rng = np.random.default_rng(71)
+    net = INetwork.Create()
+    il = net.AddInputLayer(0, "volume")
+    il.GetOutputSlot(0).SetTensorInfo(TensorInfo((1, 6, 8, 8, 4), DataType.QAsymmS8, 0.05, 3))
+    w = rng.integers(-127, 128, size=(3, 3, 3, 4, 8)).astype(np.int8)
+    scales = (rng.random(8) * 0.01 + 0.004).astype(np.float32)
+    wl = net.AddConstantLayer(w, TensorInfo(w.shape, DataType.QSymmS8, scales=scales, quant_dim=4, constant=True), "weights")
+    b = rng.integers(-1500, 1500, size=(8,)).astype(np.int32)
+    bl = net.AddConstantLayer(b, TensorInfo((8,), DataType.Signed32, scales=(scales * np.float32(0.05)).astype(np.float32), quant_dim=0, constant=True), "bias")
+    cv = net.AddConvolution3dLayer((1, 1, 1), (1, 1, 1, 1, 1, 1), (1, 1, 1), True, "conv3d")
+    il.GetOutputSlot(0).Connect(cv.GetInputSlot(0)); wl.GetOutputSlot(0).Connect(cv.GetInputSlot(1)); bl.GetOutputSlot(0).Connect(cv.GetInputSlot(2))
+    cv.GetOutputSlot(0).SetTensorInfo(TensorInfo((1, 6, 8, 8, 8), DataType.QAsymmS8, 0.25, -4))
+    p1 = net.AddPooling3dLayer(PoolingAlgorithm.Max, (2, 2, 2), (2, 2, 2), name="max")
+    cv.GetOutputSlot(0).Connect(p1.GetInputSlot(0))
+    p1.GetOutputSlot(0).SetTensorInfo(TensorInfo((1, 3, 4, 4, 8), DataType.QAsymmS8, 0.25, -4))
+    p2 = net.AddPooling3dLayer(PoolingAlgorithm.Average, (3, 3, 3), (1, 1, 1), (1, 1, 1, 1, 1, 1), name="average")
+    p1.GetOutputSlot(0).Connect(p2.GetInputSlot(0))
+    p2.GetOutputSlot(0).SetTensorInfo(TensorInfo((1, 3, 4, 4, 8), DataType.QAsymmS8, 0.25, -4))
+    ol = net.AddOutputLayer(0, "out")
+    p2.GetOutputSlot(0).Connect(ol.GetInputSlot(0))
+    return net
+
+
+@needs_plugin
+@pytest.mark.gpu
+def test_convolution3d_and_pooling3d_through_the_runtime_match_cpuref():
+    from armnn_b200 import network
+    net = _volume_net()
+    x = np.random.default_rng(73).integers(-128, 128, size=(1, 6, 8, 8, 4)).astype(np.int8)
+    ref = hostnet.ArmnnNetwork(net, "CpuRef").run({0: x})[0]
+    got = hostnet.ArmnnNetwork(net, "B200Acc").run({0: x})[0]
+    rt = network.IRuntime.Create(0)
+    ln = rt.GetLoadedNetwork(rt.LoadNetwork(network.Optimize(net)))
+    ys = {0: np.zeros(ref.shape, ref.dtype)}
+    ln.EnqueueWorkload({0: x}, ys)
+    assert np.array_equal(got, ys[0])
+    st = diff_stats(ref, got)       # CpuRef accumulates the convolution in fp32, the kernels exactly: a tie may round the other way
+    assert ref.shape == got.shape and st["max_abs"] <= 1 and st["mismatch_frac"] < 5e-3, st
