@@ -184,6 +184,7 @@ KERNEL_ENTRY_POINTS = {
     "fully_connected_f32": FcParams,
     "fully_connected_q8": FcParams,
     "batch_matmul_q8": BmmParams,
+    "batch_matmul_f32": BmmParams,
     "pool2d_q8": Pool2dParams,
     "mean_hw_q8": MeanParams,
     "eltwise_q8": EltwiseParams,

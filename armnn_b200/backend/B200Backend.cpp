@@ -123,7 +123,8 @@ public:
                 const auto& d = *PolymorphicDowncast<const BatchMatMulDescriptor*>(&descriptor);
                 if (d.m_AdjointX || d.m_AdjointY) { return No(reason, "adjoint inputs are not supported"); }
                 if (d.m_DataLayoutX != DataLayout::NCHW || d.m_DataLayoutY != DataLayout::NCHW) { return No(reason, "only the default axis choice is supported"); }
-                if (!Is8Bit(infos[0]) || !Is8Bit(infos[1]) || !Is8Bit(infos[2])) { return No(reason, "8-bit quantised tensors only"); }
+                if (AllFloat32(infos)) { return true; }
+                if (!Is8Bit(infos[0]) || !Is8Bit(infos[1]) || !Is8Bit(infos[2])) { return No(reason, "8-bit quantised tensors, or Float32 throughout"); }
                 return true;
             }
             case LayerType::Pooling2d:

@@ -1506,10 +1506,11 @@ std::unique_ptr<IWorkload> B200WorkloadFactory::CreateWorkload(LayerType type, c
             const int by = static_cast<int>(y.GetNumElements() / (y.GetShape()[ry - 1] * y.GetShape()[ry - 2]));
             p.batch_stride_x = (bx == p.batch && p.batch > 1) ? static_cast<int64_t>(p.m) * p.k : 0;
             p.batch_stride_y = (by == p.batch && p.batch > 1) ? static_cast<int64_t>(p.k) * p.n : 0;
-            return Make<BatchMatMulQueueDescriptor>(d, info, ctx, [st](const BatchMatMulQueueDescriptor& data, cudaStream_t s)
+            const bool f32 = info.m_OutputTensorInfos[0].GetDataType() == DataType::Float32;
+            return Make<BatchMatMulQueueDescriptor>(d, info, ctx, [st, f32](const BatchMatMulQueueDescriptor& data, cudaStream_t s)
             {
                 st->p.x.data = Dev(data.m_Inputs[0]); st->p.y.data = Dev(data.m_Inputs[1]); st->p.out.data = Dev(data.m_Outputs[0]);
-                B200CheckStatus(b200k_batch_matmul_q8(&st->p, s));
+                B200CheckStatus(f32 ? b200k_batch_matmul_f32(&st->p, s) : b200k_batch_matmul_q8(&st->p, s));
             });
         }
         case LayerType::Pad:

@@ -60,6 +60,28 @@ __global__ void __launch_bounds__(256) fc_f32_kernel(const FcF32Args a)
     a.y[i] = out;
 }
 
+struct BmmF32Args { const float* x; const float* y; float* out; int B, M, K, N, tx, ty; long long bsx, bsy; };
+
+// BatchMatMulImpl.cpp:15-139: every output is the sum over k, in order, of separately rounded products
+__global__ void __launch_bounds__(256) bmm_f32_kernel(const BmmF32Args a)
+{
+    pdl_enter();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)a.B * a.M * a.N) return;
+    const int n = (int)(i % a.N);
+    const long long t = i / a.N;
+    const int m = (int)(t % a.M), b = (int)(t / a.M);
+    const float* x = a.x + b * a.bsx;
+    const float* y = a.y + b * a.bsy;
+    float sum = 0.f;
+    for (int k = 0; k < a.K; ++k) {
+        const float xv = a.tx ? x[(long long)k * a.M + m] : x[(long long)m * a.K + k];
+        const float yv = a.ty ? y[(long long)n * a.K + k] : y[(long long)k * a.N + n];
+        sum = __fadd_rn(sum, __fmul_rn(xv, yv));
+    }
+    a.out[i] = sum;
+}
+
 static int launch_conv_f32(const b200k_conv2d_params* p, cudaStream_t s, bool depthwise, const char* who)
 {
     B200K_REQUIRE(p, B200K_E_INVALID, "%s: null params", who);
@@ -107,4 +129,20 @@ extern "C" int b200k_fully_connected_f32(const b200k_fc_params* p, void* stream)
     a.M = p->m; a.K = p->k; a.N = p->n; a.transpose_w = p->transpose_w;
     launch_pdl(fc_f32_kernel, dim3(div_up((long long)p->m * p->n, 256)), dim3(256), 0, (cudaStream_t)stream, a);
     return check_launch("fc_f32_kernel");
+}
+
+extern "C" int b200k_batch_matmul_f32(const b200k_bmm_params* p, void* stream)
+{
+    B200K_REQUIRE(p, B200K_E_INVALID, "batch_matmul_f32: null params");
+    B200K_REQUIRE(p->x.data && p->y.data && p->out.data, B200K_E_INVALID, "batch_matmul_f32: null tensor pointer");
+    B200K_REQUIRE(p->x.dtype == B200K_F32 && p->y.dtype == B200K_F32 && p->out.dtype == B200K_F32, B200K_E_UNSUPPORTED,
+                  "batch_matmul_f32: every tensor must be Float32");
+    B200K_REQUIRE(p->batch > 0 && p->m > 0 && p->k > 0 && p->n > 0 && p->batch_stride_x >= 0 && p->batch_stride_y >= 0,
+                  B200K_E_INVALID, "batch_matmul_f32: bad shape");
+    BmmF32Args a;
+    a.x = (const float*)p->x.data; a.y = (const float*)p->y.data; a.out = (float*)p->out.data;
+    a.B = p->batch; a.M = p->m; a.K = p->k; a.N = p->n; a.tx = p->transpose_x; a.ty = p->transpose_y;
+    a.bsx = p->batch_stride_x; a.bsy = p->batch_stride_y;
+    launch_pdl(bmm_f32_kernel, dim3(div_up((long long)p->batch * p->m * p->n, 256)), dim3(256), 0, (cudaStream_t)stream, a);
+    return check_launch("bmm_f32_kernel");
 }

@@ -462,8 +462,10 @@ def IsLayerSupported(layer):
     if t == "BatchMatMul":
         if layer.desc["ax"] or layer.desc["ay"]:
             return False, "BatchMatMul: adjoint inputs are not supported"
+        if all(i.dtype == DataType.Float32 for i in list(ins) + list(outs)):
+            return True, ""                                  # the fp32 variant (b200k_batch_matmul_f32)
         if any(i.dtype not in _Q8 for i in ins) or outs[0].dtype not in _Q8:
-            return False, "BatchMatMul: 8-bit quantised tensors only"
+            return False, "BatchMatMul: 8-bit quantised tensors, or Float32 throughout"
         return True, ""
     if t in ("Pooling2d", "Mean", "Reduce", "ElementwiseBinary", "Prelu", "Activation", "Softmax"):
         ok = (DataType.QAsymmU8, DataType.QAsymmS8, DataType.QSymmS16, DataType.Float32)
@@ -937,7 +939,7 @@ class GraphProgram:
         p.batch_stride_x = xs[-1] * xs[-2] if bx == p.batch and p.batch > 1 else 0
         p.batch_stride_y = ys[-1] * ys[-2] if by == p.batch and p.batch > 1 else 0
         p.transpose_x, p.transpose_y = int(layer.desc["tx"]), int(layer.desc["ty"])
-        return "batch_matmul_q8", p
+        return ("batch_matmul_f32" if o.info.dtype == DataType.Float32 else "batch_matmul_q8"), p
 
     def _make_Pooling2d(self, layer):
         x, y = layer.inputs[0].source, layer.outputs[0]

@@ -177,6 +177,10 @@ typedef struct {
 
 int b200k_batch_matmul_q8(const b200k_bmm_params* p, void* stream);
 
+/* The same on Float32 tensors: every output is the sum over k, in order, of separately rounded products
+ * (BatchMatMulImpl.cpp:15-139); acc_out and algo are ignored. */
+int b200k_batch_matmul_f32(const b200k_bmm_params* p, void* stream);
+
 /* ---- DepthwiseConvolution2d ---------------------------------------------------------------- */
 
 /* armnn::Convolve with depthwise = true (ConvImpl.cpp:100, 128-146) from

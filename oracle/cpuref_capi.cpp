@@ -250,6 +250,8 @@ extern "C" int cpuref_batch_matmul_q8(const b200k_bmm_params* p)
     });
 }
 
+extern "C" int cpuref_batch_matmul_f32(const b200k_bmm_params* p) { return cpuref_batch_matmul_q8(p); }
+
 extern "C" int cpuref_pool2d_q8(const b200k_pool2d_params* p)
 {
     return guarded([&] {

@@ -355,6 +355,25 @@ int oracle_batch_matmul_q8(const b200k_bmm_params* p)
     return 0;
 }
 
+int oracle_batch_matmul_f32(const b200k_bmm_params* p)
+{
+    const int B = p->batch, M = p->m, K = p->k, N = p->n;
+    if (!p->x.data || !p->y.data || !p->out.data) return B200K_E_INVALID;
+    for (int b = 0; b < B; ++b)
+    for (int m = 0; m < M; ++m)
+    for (int n = 0; n < N; ++n) {
+        volatile float sum = 0.0f;
+        for (int k = 0; k < K; ++k) {
+            const int64_t xi = b * p->batch_stride_x + (p->transpose_x ? (int64_t)k * M + m : (int64_t)m * K + k);
+            const int64_t yi = b * p->batch_stride_y + (p->transpose_y ? (int64_t)n * K + k : (int64_t)k * N + n);
+            volatile float prod = ((const float*)p->x.data)[xi] * ((const float*)p->y.data)[yi];
+            sum = sum + prod;
+        }
+        ((float*)p->out.data)[((int64_t)b * M + m) * N + n] = sum;
+    }
+    return 0;
+}
+
 /* ---- Pooling2d, Pooling2d.cpp:142-303 ----------------------------------------------------- */
 
 static int clamp_range(int* s, int* e, int maxr)       /* Pooling2d.cpp:121-134 */

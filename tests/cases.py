@@ -693,7 +693,21 @@ def f32_cases():
             p.m, p.k, p.n, p.transpose_w = m, k, n, int(transpose)
             return p, [y]
         return lambda: SimpleCase("fully_connected_f32", build)
+
+    def bmm(seed, batch, m, k, n, tx=False, ty=False, bcast_y=False):
+        def build(mem):
+            rng = np.random.default_rng(seed)
+            p = _abi.BmmParams()
+            p.x = qt(mem, rng.standard_normal((batch, k, m) if tx else (batch, m, k)).astype(np.float32), F32)
+            p.y = qt(mem, rng.standard_normal(((1,) if bcast_y else (batch,)) + ((n, k) if ty else (k, n))).astype(np.float32), F32)
+            p.out, out = qt_out(mem, (batch, m, n), F32)
+            p.batch, p.m, p.k, p.n, p.transpose_x, p.transpose_y = batch, m, k, n, int(tx), int(ty)
+            p.batch_stride_x, p.batch_stride_y = m * k, 0 if bcast_y else k * n
+            return p, [out]
+        return lambda: SimpleCase("batch_matmul_f32", build)
     return {
+        "bmm_plain": bmm(358, 3, 17, 33, 9), "bmm_transpose_both": bmm(359, 2, 8, 40, 12, tx=True, ty=True),
+        "bmm_attention_qk_broadcast_y": bmm(360, 4, 16, 64, 16, ty=True, bcast_y=True),
         "conv3x3_pad1": conv(351, 2, 9, 8, 12, 20, (3, 3), pad=(1, 1)),
         "conv1x1": conv(352, 1, 7, 7, 32, 16, (1, 1), bias=False),
         "conv5x5_s2_dilation2": conv(353, 1, 17, 15, 5, 7, (5, 5), stride=(2, 2), pad=(4, 4), dil=(2, 2)),

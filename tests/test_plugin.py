@@ -1165,3 +1165,24 @@ def test_convolution3d_and_pooling3d_through_the_runtime_match_cpuref():
     assert np.array_equal(got, ys[0])
     st = diff_stats(ref, got)       # CpuRef accumulates the convolution in fp32, the kernels exactly: a tie may round the other way
     assert ref.shape == got.shape and st["max_abs"] <= 1 and st["mismatch_frac"] < 5e-3, st
+
+
+@needs_plugin
+@pytest.mark.gpu
+def test_float32_batch_matmul_through_the_runtime_equals_cpuref():
+    """Attention scores in Float32: Q x K^T over heads, identical bits to CpuRef (products and sums in its order)."""
+    from armnn_b200.network import DataType, INetwork, TensorInfo
+    net = INetwork.Create()
+    q = net.AddInputLayer(0, "q"); k = net.AddInputLayer(1, "k")
+    q.GetOutputSlot(0).SetTensorInfo(TensorInfo((2, 4, 16, 32), DataType.Float32))
+    k.GetOutputSlot(0).SetTensorInfo(TensorInfo((2, 4, 16, 32), DataType.Float32))
+    mm = net.AddBatchMatMulLayer(False, True, name="scores")
+    q.GetOutputSlot(0).Connect(mm.GetInputSlot(0)); k.GetOutputSlot(0).Connect(mm.GetInputSlot(1))
+    mm.GetOutputSlot(0).SetTensorInfo(TensorInfo((2, 4, 16, 16), DataType.Float32))
+    ol = net.AddOutputLayer(0, "out")
+    mm.GetOutputSlot(0).Connect(ol.GetInputSlot(0))
+    rng = np.random.default_rng(79)
+    xs = {0: rng.standard_normal((2, 4, 16, 32)).astype(np.float32), 1: rng.standard_normal((2, 4, 16, 32)).astype(np.float32)}
+    ref = hostnet.ArmnnNetwork(net, "CpuRef").run(xs)[0]
+    got = hostnet.ArmnnNetwork(net, "B200Acc").run(xs)[0]
+    assert ref.shape == got.shape and np.array_equal(ref, got)
