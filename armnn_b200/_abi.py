@@ -85,6 +85,11 @@ class GatherParams(C.Structure):
                 ("inner", C.c_int32), ("n_indices", C.c_int32)]
 
 
+class GatherNdParams(C.Structure):
+    _fields_ = [("x", QTensor), ("y", QTensor), ("indices", C.c_void_p), ("n_indices", C.c_int32), ("nd", C.c_int32),
+                ("inner", C.c_int32), ("dims", C.c_int32 * 8)]
+
+
 class BatchNormParams(C.Structure):
     _fields_ = [("x", QTensor), ("y", QTensor), ("mean", QTensor), ("variance", QTensor), ("beta", QTensor), ("gamma", QTensor),
                 ("n", C.c_int32), ("c", C.c_int32), ("hw", C.c_int64), ("nchw", C.c_int32), ("eps", C.c_float),
@@ -194,6 +199,7 @@ KERNEL_ENTRY_POINTS = {
     "l2_normalization_q": SoftmaxParams,
     "arg_min_max_q": ArgMinMaxParams,
     "gather_q": GatherParams,
+    "gather_nd_q": GatherNdParams,
     "batch_norm_q": BatchNormParams,
     "instance_norm_q": InstanceNormParams,
     "normalization_q": NormalizationParams,

@@ -170,6 +170,8 @@ class ArmnnNetwork:
             elif t == "Normalization":
                 lid = lib.armnnc_add_normalization(net, d["channel_type"], C.c_uint(d["norm_size"]), C.c_float(d["alpha"]),
                                                    C.c_float(d["beta"]), C.c_float(d["k"]), int(d["nchw"]))
+            elif t == "GatherNd":
+                lid = lib.armnnc_add_gather_nd(net)
             elif t == "Gather":
                 lid = lib.armnnc_add_gather(net, d["axis"])
             elif t == "BatchNormalization":
@@ -199,6 +201,8 @@ class ArmnnNetwork:
             elif t == "Pad":
                 flat = [v for pair in d["pads"] for v in pair]
                 lid = lib.armnnc_add_pad(net, len(d["pads"]), (C.c_int32 * len(flat))(*flat), C.c_float(d["value"]), int(d.get("mode", 0)))
+            elif t in ("Shape", "Rank"):
+                lid = lib.armnnc_add_shape(net, int(t == "Rank"))
             elif t == "Cast":
                 lid = lib.armnnc_add_cast(net)
             elif t == "Fill":

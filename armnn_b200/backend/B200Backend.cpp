@@ -302,6 +302,9 @@ public:
                 return (infos[0].GetNumDimensions() == 5 && IsActType(infos[0]) && infos[1].GetDataType() == infos[0].GetDataType()) ||
                        No(reason, "5-D tensors of one supported data type");
             }
+            case LayerType::Shape:
+            case LayerType::Rank:
+                return infos[1].GetDataType() == DataType::Signed32 || No(reason, "the output must be Signed32");
             case LayerType::Cast:
                 return (IsMoveType(infos[0]) && IsMoveType(infos[1]) && infos[0].GetNumElements() == infos[1].GetNumElements()) ||
                        No(reason, "unsupported data type or mismatched sizes");
@@ -318,6 +321,13 @@ public:
             case LayerType::Gather:
                 if (infos[1].GetDataType() != DataType::Signed32) { return No(reason, "indices must be Signed32"); }
                 return (IsMoveType(infos[0]) && infos[2].GetDataType() == infos[0].GetDataType()) || No(reason, "unsupported or mismatched data types");
+            case LayerType::GatherNd:
+            {
+                if (infos[1].GetDataType() != DataType::Signed32 || infos[1].GetNumDimensions() < 1) { return No(reason, "indices must be Signed32"); }
+                const unsigned int nd = infos[1].GetShape()[infos[1].GetNumDimensions() - 1];
+                if (nd < 1 || nd > 8 || nd > infos[0].GetNumDimensions()) { return No(reason, "index tuples longer than the tensor's rank (or than 8)"); }
+                return (IsMoveType(infos[0]) && infos[2].GetDataType() == infos[0].GetDataType()) || No(reason, "unsupported or mismatched data types");
+            }
             case LayerType::BatchNormalization:
                 if (infos[0].GetNumDimensions() != 4) { return No(reason, "4-D tensors only"); }
                 for (const TensorInfo& t : infos) { if (!IsActType(t)) { return No(reason, "unsupported data type"); } }

@@ -1233,6 +1233,34 @@ std::unique_ptr<IWorkload> B200WorkloadFactory::CreateWorkload(LayerType type, c
                 B200CheckStatus(b200k_gather_q(&st->p, s));
             });
         }
+        case LayerType::GatherNd:
+        {
+            auto st = std::make_shared<SimpleState<b200k_gather_nd_params>>(ctx);
+            b200k_gather_nd_params& p = st->p;
+            std::memset(&p, 0, sizeof(p));
+            const TensorInfo& x = info.m_InputTensorInfos[0];
+            const TensorInfo& idx = info.m_InputTensorInfos[1];
+            p.x = Operand(x, st->blobs); p.y = Operand(info.m_OutputTensorInfos[0], st->blobs);
+            const unsigned int nd = idx.GetShape()[idx.GetNumDimensions() - 1];
+            if (nd < 1 || nd > 8 || nd > x.GetNumDimensions()) { throw InvalidArgumentException("B200Acc: GatherNd index tuples do not fit the tensor"); }
+            p.nd = static_cast<int32_t>(nd);
+            p.n_indices = static_cast<int32_t>(idx.GetNumElements() / nd);
+            p.inner = 1;
+            for (unsigned int i = 0; i < x.GetNumDimensions(); ++i)
+            {
+                if (i < nd) { p.dims[i] = static_cast<int32_t>(x.GetShape()[i]); } else { p.inner *= static_cast<int32_t>(x.GetShape()[i]); }
+            }
+            if (info.m_OutputTensorInfos[0].GetNumElements() != static_cast<unsigned int>(p.n_indices) * static_cast<unsigned int>(p.inner))
+            {
+                throw InvalidArgumentException("B200Acc: GatherNd output shape does not match the gathered slices");
+            }
+            return Make<GatherNdQueueDescriptor>(d, info, ctx, [st](const GatherNdQueueDescriptor& data, cudaStream_t s)
+            {
+                st->p.x.data = Dev(data.m_Inputs[0]); st->p.indices = static_cast<const int32_t*>(Dev(data.m_Inputs[1]));
+                st->p.y.data = Dev(data.m_Outputs[0]);
+                B200CheckStatus(b200k_gather_nd_q(&st->p, s));
+            });
+        }
         case LayerType::BatchNormalization:
         {
             // the descriptor's constant handles are only valid during workload creation: the workload owns device copies
@@ -1372,6 +1400,25 @@ std::unique_ptr<IWorkload> B200WorkloadFactory::CreateWorkload(LayerType type, c
                 st->p.x.data = Dev(data.m_Inputs[0]); st->p.y.data = Dev(data.m_Outputs[0]);
                 B200CheckStatus(b200k_pool3d_q(&st->p, s));
             });
+        }
+        case LayerType::Shape:
+        case LayerType::Rank:
+        {
+            // known when the network is loaded (RefShapeWorkload.hpp, RefRankWorkload.hpp write it at every execution):
+            // a device constant copied into the output tensor
+            auto st = std::make_shared<ViewState>(ctx);
+            const TensorInfo& in = info.m_InputTensorInfos[0];
+            const TensorInfo& out = info.m_OutputTensorInfos[0];
+            std::vector<int32_t> values;
+            if (type == LayerType::Shape) { for (unsigned int i = 0; i < in.GetNumDimensions(); ++i) { values.push_back(static_cast<int32_t>(in.GetShape()[i])); } }
+            else { values.push_back(static_cast<int32_t>(in.GetNumDimensions())); }
+            if (out.GetDataType() != DataType::Signed32 || out.GetNumElements() != values.size()) { throw InvalidArgumentException("B200Acc: Shape / Rank need a Signed32 output of the right size"); }
+            ViewOp op = NewViewOp(out, out, st->blobs, 0, 0, 1);
+            op.fixedSrc = st->blobs.Upload(values.data(), values.size() * sizeof(int32_t));
+            op.p.shape[0] = static_cast<int32_t>(values.size()); op.p.src_strides[0] = 1; op.p.dst_strides[0] = 1;
+            st->ops.push_back(op);
+            if (type == LayerType::Shape) { return MakeViews<ShapeQueueDescriptor>(d, info, ctx, st); }
+            return MakeViews<RankQueueDescriptor>(d, info, ctx, st);
         }
         case LayerType::Cast:
         {

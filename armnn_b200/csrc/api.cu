@@ -116,6 +116,7 @@ extern "C" size_t b200k_sizeof_params(int which)
         case 19: return sizeof(b200k_normalization_params);
         case 20: return sizeof(b200k_conv3d_params);
         case 21: return sizeof(b200k_pool3d_params);
+        case 22: return sizeof(b200k_gather_nd_params);
         default: return 0;
     }
 }

@@ -80,6 +80,8 @@ struct GatherArgs {
     const int* indices;
     long long axis, inner, n_idx, count;
     int same, esize;
+    int nd;                         // 0: one index per row (Gather); else index tuples of nd entries (GatherNd)
+    long long coeff[8];             // GatherNd: the row number is sum_d tuple[d] * coeff[d]
 };
 
 __global__ void __launch_bounds__(256) gather_kernel(const GatherArgs a)
@@ -89,8 +91,20 @@ __global__ void __launch_bounds__(256) gather_kernel(const GatherArgs a)
     if (i >= a.count) return;
     const long long k = i % a.inner, oj = i / a.inner;
     const long long j = oj % a.n_idx, o = oj / a.n_idx;
-    long long idx = a.indices[j];
-    if (idx < 0) idx += a.axis;
+    long long idx;
+    if (a.nd == 0) {
+        idx = a.indices[j];
+        if (idx < 0) idx += a.axis;
+    } else {
+        idx = 0;
+        bool ok = true;
+        for (int d = 0; d < a.nd; ++d) {
+            const long long t = a.indices[j * a.nd + d];
+            ok = ok && t >= 0;
+            idx += t * a.coeff[d];
+        }
+        if (!ok) idx = -1;
+    }
     if (idx < 0 || idx >= a.axis) { a.y.set(i, 0.0f); return; }
     const long long s = (o * a.axis + idx) * a.inner + k;
     if (a.same) {
@@ -209,4 +223,33 @@ extern "C" int b200k_view_copy_q(const b200k_view_copy_params* p, void* stream)
     for (int d = 0; d < p->rank; ++d) { a.shape[d] = p->shape[d]; a.ss[d] = p->src_strides[d]; a.ds[d] = p->dst_strides[d]; }
     launch_pdl(view_copy_kernel, dim3(div_up(count, 256)), dim3(256), 0, s, a);
     return check_launch("view_copy_kernel");
+}
+
+// GatherNd (src/backends/reference/workloads/RefGatherNdWorkload.cpp:20-92): the index tuples are flattened to row numbers
+// of the tensor seen as [rows, inner] and the rows gathered.
+extern "C" int b200k_gather_nd_q(const b200k_gather_nd_params* p, void* stream)
+{
+    B200K_REQUIRE(p, B200K_E_INVALID, "gather_nd_q: null params");
+    B200K_REQUIRE(p->x.data && p->y.data && p->indices, B200K_E_INVALID, "gather_nd_q: null tensor pointer");
+    B200K_REQUIRE(p->nd >= 1 && p->nd <= 8 && p->n_indices >= 0 && p->inner > 0, B200K_E_INVALID, "gather_nd_q: bad shape");
+    B200K_REQUIRE(p->x.dtype >= B200K_U8 && p->x.dtype <= B200K_F32, B200K_E_INVALID, "gather_nd_q: unknown element type");
+    B200K_REQUIRE(p->x.dtype == p->y.dtype, B200K_E_UNSUPPORTED, "gather_nd_q: input and output types differ (%d, %d)", p->x.dtype, p->y.dtype);
+    const long long count = (long long)p->n_indices * p->inner;
+    if (count == 0) return B200K_OK;
+    GatherArgs a;
+    memset(&a, 0, sizeof(a));
+    a.x = make_view(p->x); a.y = make_view(p->y); a.indices = p->indices;
+    a.inner = p->inner; a.n_idx = p->n_indices; a.count = count; a.nd = p->nd;
+    a.axis = 1;
+    for (int d = 0; d < p->nd; ++d) {
+        B200K_REQUIRE(p->dims[d] > 0, B200K_E_INVALID, "gather_nd_q: non-positive dimension");
+        a.axis *= p->dims[d];
+    }
+    long long c = 1;
+    for (int d = p->nd - 1; d >= 0; --d) { a.coeff[d] = c; c *= p->dims[d]; }
+    const bool quantised = p->x.dtype == B200K_U8 || p->x.dtype == B200K_S8 || p->x.dtype == B200K_S16;
+    a.same = (!quantised || (p->x.scale == p->y.scale && p->x.zero_point == p->y.zero_point)) ? 1 : 0;
+    a.esize = elem_size(p->x.dtype);
+    launch_pdl(gather_kernel, dim3(div_up(count, 256)), dim3(256), 0, (cudaStream_t)stream, a);
+    return check_launch("gather_kernel");
 }

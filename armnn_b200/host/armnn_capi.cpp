@@ -263,6 +263,12 @@ int armnnc_add_normalization(void* vn, int channel_type, unsigned norm_size, flo
     return add_layer(n, n->net->AddNormalizationLayer(d));
 }
 
+int armnnc_add_gather_nd(void* vn)
+{
+    auto* n = static_cast<CNet*>(vn);
+    return add_layer(n, n->net->AddGatherNdLayer());
+}
+
 int armnnc_add_gather(void* vn, int axis)
 {
     auto* n = static_cast<CNet*>(vn);
@@ -411,6 +417,12 @@ int armnnc_add_qlstm(void* vn, const b200k_qlstm_params* p)
 }
 
 // pads: rank pairs (before, after), outermost dimension first
+int armnnc_add_shape(void* vn, int rank_only)
+{
+    auto* n = static_cast<CNet*>(vn);
+    return add_layer(n, rank_only ? n->net->AddRankLayer() : n->net->AddShapeLayer());
+}
+
 int armnnc_add_cast(void* vn)
 {
     auto* n = static_cast<CNet*>(vn);

@@ -293,6 +293,14 @@ class INetwork:
         return self._add(Layer("Pad", name, 1, 1, {"pads": tuple((int(a), int(b)) for a, b in pad_list), "value": float(pad_value),
                                                    "mode": int(padding_mode)}))
 
+    def AddShapeLayer(self, name=None):
+        """armnn::ShapeLayer: the input's shape as a Signed32 vector."""
+        return self._add(Layer("Shape", name, 1, 1, {}))
+
+    def AddRankLayer(self, name=None):
+        """armnn::RankLayer: the input's number of dimensions as one Signed32 element."""
+        return self._add(Layer("Rank", name, 1, 1, {}))
+
     def AddCastLayer(self, name=None):
         return self._add(Layer("Cast", name, 1, 1, {}))
 
@@ -399,6 +407,11 @@ class INetwork:
         """armnn::GatherDescriptor: input 0 the tensor, input 1 the Signed32 indices."""
         return self._add(Layer("Gather", name, 2, 1, {"axis": int(axis)}))
 
+    def AddGatherNdLayer(self, name=None):
+        """armnn::INetwork::AddGatherNdLayer (no batch dimensions): input 0 the tensor, input 1 Signed32 index tuples
+        [..., nd]."""
+        return self._add(Layer("GatherNd", name, 2, 1, {}))
+
     def AddBatchNormalizationLayer(self, eps, mean, variance, beta, gamma, nchw=False, name=None):
         """armnn::INetwork::AddBatchNormalizationLayer: mean, variance, beta, gamma are (ndarray, TensorInfo) pairs of one
         value per channel."""
@@ -494,6 +507,13 @@ def IsLayerSupported(layer):
         if ins[0].dtype not in ok or outs[0].dtype != ins[0].dtype or ins[1].dtype != DataType.Signed32:
             return False, "Gather: one supported element type for input and output, Signed32 indices"
         return True, ""
+    if t == "GatherNd":
+        ok = (DataType.QAsymmU8, DataType.QAsymmS8, DataType.QSymmS16, DataType.Float32, DataType.Signed32)
+        if ins[0].dtype not in ok or outs[0].dtype != ins[0].dtype or ins[1].dtype != DataType.Signed32:
+            return False, "GatherNd: one supported element type for input and output, Signed32 indices"
+        if not (1 <= ins[1].shape[-1] <= min(8, len(ins[0].shape))):
+            return False, "GatherNd: index tuples longer than the tensor's rank (or than 8)"
+        return True, ""
     if t == "BatchNormalization":
         ok = (DataType.QAsymmU8, DataType.QAsymmS8, DataType.QSymmS16, DataType.Float32)
         if ins[0].dtype not in ok or outs[0].dtype not in ok or len(ins[0].shape) != 4:
@@ -546,6 +566,11 @@ def IsLayerSupported(layer):
         ok = (DataType.QAsymmU8, DataType.QAsymmS8, DataType.QSymmS16, DataType.Float32)
         if len(ins[0].shape) != 5 or ins[0].dtype not in ok or outs[0].dtype != ins[0].dtype:
             return False, "Pooling3d: 5-D tensors of one supported data type"
+        return True, ""
+    if t in ("Shape", "Rank"):
+        want = len(ins[0].shape) if t == "Shape" else 1
+        if outs[0].dtype != DataType.Signed32 or outs[0].GetNumElements() != want:
+            return False, "%s: the output must hold %d Signed32 element(s)" % (t, want)
         return True, ""
     if t == "Cast":
         ok = (DataType.QAsymmU8, DataType.QAsymmS8, DataType.QSymmS8, DataType.QSymmS16, DataType.Signed32, DataType.Float32)
@@ -1100,6 +1125,20 @@ class GraphProgram:
                                            % (y.info.shape, x.info.shape, idx.info.shape))
         return "gather_q", p
 
+    def _make_GatherNd(self, layer):
+        x, idx, y = layer.inputs[0].source, layer.inputs[1].source, layer.outputs[0]
+        p = _abi.GatherNdParams()
+        p.x, p.y = self._operand(x), self._operand(y)
+        p.indices = self._ptr(self._dev(idx))
+        p.nd = idx.info.shape[-1]
+        p.n_indices = idx.info.GetNumElements() // p.nd
+        p.inner = int(np.prod(x.info.shape[p.nd:])) if p.nd < len(x.info.shape) else 1
+        for i in range(p.nd):
+            p.dims[i] = x.info.shape[i]
+        if y.info.GetNumElements() != p.n_indices * p.inner:
+            raise InvalidArgumentException("GatherNd: output shape %s does not match %d tuples of %d elements" % (y.info.shape, p.n_indices, p.inner))
+        return "gather_nd_q", p
+
     @staticmethod
     def _planes(info, nchw):
         n, a, b, c = info.shape
@@ -1167,6 +1206,19 @@ class GraphProgram:
         p.pad_value = layer.desc["value"]
         p.mode = layer.desc.get("mode", 0)
         return "pad_q", p
+
+    def _make_Shape(self, layer):
+        """The shape is known when the network is loaded (RefShapeWorkload.hpp, RefRankWorkload.hpp write it at every
+        execution): a device constant copied into the output tensor."""
+        x, y = layer.inputs[0].source, layer.outputs[0]
+        values = np.array(x.info.shape if layer.type == "Shape" else [len(x.info.shape)], np.int32)
+        dev = self._upload(values)
+        self.aux.append(dev)
+        name, p = self._view_copy(y, y, ((len(values),), 0, [1], 0, [1]))
+        p.x.data = self._ptr(dev)
+        return name, p
+
+    _make_Rank = _make_Shape
 
     def _make_Cast(self, layer):
         x, y = layer.inputs[0].source, layer.outputs[0]

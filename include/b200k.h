@@ -412,6 +412,19 @@ typedef struct {
 
 int b200k_gather_q(const b200k_gather_params* p, void* stream);
 
+/* armnn::GatherNd without batch dimensions (src/backends/reference/workloads/RefGatherNdWorkload.cpp:20-92): indices is
+ * [n_indices, nd] (device int32); tuple j addresses the first nd dimensions (extents dims[0 .. nd-1]) of x, and
+ *     y[j, k] = Q_y(deq_x(x[tuple j flattened, k]))        0 <= k < inner = product of the remaining dimensions.
+ * A tuple outside the tensor (the reference throws on a negative entry) yields the encoding of 0.0. */
+typedef struct {
+    b200k_qtensor x, y;
+    const int32_t* indices;
+    int32_t n_indices, nd, inner;
+    int32_t dims[8];
+} b200k_gather_nd_params;
+
+int b200k_gather_nd_q(const b200k_gather_nd_params* p, void* stream);
+
 /* ---- BatchNormalization, InstanceNormalization ------------------------------------------------ */
 
 /* armnn::BatchNormImpl (src/backends/reference/workloads/BatchNormImpl.cpp:16-63): per channel
@@ -566,7 +579,7 @@ unsigned long long b200k_kernel_launches(void);
 
 /* sizeof() of a parameter struct as compiled into the library, for bindings in other languages to check their
  * own declarations: 0 conv2d, 1 fc, 2 bmm, 3 pool2d, 4 mean, 5 eltwise, 6 activation, 7 softmax, 8 convert,
- * 9 qlstm, 10 pad, 11 view_copy, 12 resize, 13 reduce, 14 unary, 15 arg_min_max, 16 gather, 17 batch_norm, 18 instance_norm, 19 normalization, 20 conv3d, 21 pool3d.  No counterpart in the reference (its backends are linked as C++). */
+ * 9 qlstm, 10 pad, 11 view_copy, 12 resize, 13 reduce, 14 unary, 15 arg_min_max, 16 gather, 17 batch_norm, 18 instance_norm, 19 normalization, 20 conv3d, 21 pool3d, 22 gather_nd.  No counterpart in the reference (its backends are linked as C++). */
 size_t b200k_sizeof_params(int which);
 
 #ifdef __cplusplus

@@ -388,6 +388,25 @@ extern "C" int cpuref_gather_q(const b200k_gather_params* p)
     });
 }
 
+extern "C" int cpuref_gather_nd_q(const b200k_gather_nd_params* p)
+{
+    return guarded([&] {
+        Harness h;
+        unsigned dims[6];
+        for (int d = 0; d < p->nd; ++d) dims[d] = (unsigned)p->dims[d];
+        dims[p->nd] = (unsigned)p->inner;
+        TensorInfo xi = make_info(p->x, TensorShape((unsigned)p->nd + 1, dims), 0, 0, false);
+        TensorInfo ii(TensorShape({(unsigned)p->n_indices, (unsigned)p->nd}), DataType::Signed32);
+        TensorInfo yi = make_info(p->y, TensorShape({(unsigned)p->n_indices, (unsigned)p->inner}), 0, 0, false);
+        GatherNdQueueDescriptor d;
+        h.in(d, xi, p->x.data);
+        h.in(d, ii, p->indices);
+        auto* o = h.out(d, yi);
+        h.run(LayerType::GatherNd, d);
+        copy_out(o, const_cast<void*>(p->y.data), yi.GetNumBytes());
+    });
+}
+
 extern "C" int cpuref_batch_norm_q(const b200k_batch_norm_params* p)
 {
     return guarded([&] {

@@ -685,6 +685,31 @@ int oracle_gather_q(const b200k_gather_params* p)
     return 0;
 }
 
+/* ---- GatherNd without batch dimensions, RefGatherNdWorkload.cpp:20-92 ------------------------------ */
+
+int oracle_gather_nd_q(const b200k_gather_nd_params* p)
+{
+    if (!p->x.data || !p->y.data || !p->indices || p->nd < 1 || p->nd > 8) return B200K_E_INVALID;
+    int64_t rows = 1, coeff[8];
+    for (int d = p->nd - 1; d >= 0; --d) { coeff[d] = rows; rows *= p->dims[d]; }
+    for (int j = 0; j < p->n_indices; ++j) {
+        int64_t flat = 0;
+        int ok = 1;
+        for (int d = 0; d < p->nd; ++d) {
+            const int32_t t = p->indices[(int64_t)j * p->nd + d];
+            if (t < 0) ok = 0;
+            flat += (int64_t)t * coeff[d];
+        }
+        if (flat >= rows) ok = 0;
+        for (int k = 0; k < p->inner; ++k) {
+            const int64_t out = (int64_t)j * p->inner + k;
+            if (!ok) { store_f(&p->y, out, 0.0f); continue; }
+            store_f(&p->y, out, load_f(&p->x, flat * p->inner + k));
+        }
+    }
+    return 0;
+}
+
 /* ---- BatchNormalization, BatchNormImpl.cpp:16-63 -------------------------------------------------- */
 
 int oracle_batch_norm_q(const b200k_batch_norm_params* p)

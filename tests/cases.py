@@ -484,7 +484,29 @@ def norm_cases():
             p.alpha, p.beta, p.kappa = alpha, beta, kappa
             return p, [y]
         return lambda: SimpleCase("normalization_q", build)
+    def gather_nd(seed, dims, inner, n_idx, dtype=S8, requant=False):
+        def build(mem):
+            rng = np.random.default_rng(seed)
+            p = _abi.GatherNdParams()
+            shape = tuple(dims) + (inner,)
+            xq = (0.05, 0) if dtype != F32 else (1.0, 0)
+            yq = (0.07, 5) if requant else xq
+            if dtype == F32:
+                p.x = qt(mem, rng.standard_normal(shape).astype(np.float32), F32)
+            else:
+                p.x = qt(mem, _rand(rng, dtype, shape), dtype, *xq)
+            idx = np.stack([rng.integers(0, n, size=(n_idx,)) for n in dims], axis=1).astype(np.int32)
+            p.indices = mem.inp(idx)
+            p.y, y = qt_out(mem, (n_idx, inner), dtype, *yq)
+            p.n_indices, p.nd, p.inner = n_idx, len(dims), inner
+            for i, n in enumerate(dims):
+                p.dims[i] = n
+            return p, [y]
+        return lambda: SimpleCase("gather_nd_q", build)
     return {
+        "gather_nd_pixels": gather_nd(338, (2, 7, 9), 16, 40),
+        "gather_nd_u8_requantise": gather_nd(339, (5, 4), 3, 11, dtype=U8, requant=True),
+        "gather_nd_float_rank1_tuples": gather_nd(340, (30,), 5, 12, dtype=F32),
         "lrn_across_nhwc": lrn(333, 2, 24, 6, 7, 0, 5),
         "lrn_across_nchw_u8": lrn(334, 1, 9, 5, 8, 0, 3, nchw=True, dtype=U8, alpha=1e-1, beta=0.5, kappa=2.0),
         "lrn_across_float": lrn(335, 2, 16, 4, 4, 0, 5, dtype=F32, alpha=1e-4),

@@ -310,3 +310,26 @@ def test_volume_graph_oracle_vs_armnn_cpuref(built):
     got = hostnet.OracleNetwork(Optimize(net)).run({0: x})[0]
     st = diff_stats(want, got)
     assert want.shape == got.shape and st["max_abs"] <= 1 and st["mismatch_frac"] < 5e-3, st
+
+
+@needs_cpuref
+def test_shape_and_rank_graph_mirror_equals_armnn_cpuref(built):
+    import hostnet
+    from test_plugin import _shape_rank_net
+    x = np.zeros((2, 3, 5, 7), np.uint8)
+    want = hostnet.ArmnnNetwork(_shape_rank_net(with_rank=False), "CpuRef").run({0: x})
+    got = hostnet.OracleNetwork(Optimize(_shape_rank_net())).run({0: x})
+    assert list(want[0]) == [2, 3, 5, 7] and list(got[2]) == [4]
+    for k in range(2):
+        assert np.array_equal(want[k], got[k]), k
+
+
+@needs_cpuref
+def test_gather_nd_graph_oracle_equals_armnn_cpuref(built):
+    import hostnet
+    from test_plugin import _gather_nd_inputs, _gather_nd_net
+    net, xs = _gather_nd_net(), _gather_nd_inputs(84)
+    want = hostnet.ArmnnNetwork(net, "CpuRef").run(xs)
+    got = hostnet.OracleNetwork(Optimize(net)).run(xs)
+    for k in (0, 1):
+        assert want[k].shape == got[k].shape and np.array_equal(want[k], got[k]), k

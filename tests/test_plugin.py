@@ -1186,3 +1186,86 @@ def test_float32_batch_matmul_through_the_runtime_equals_cpuref():
     ref = hostnet.ArmnnNetwork(net, "CpuRef").run(xs)[0]
     got = hostnet.ArmnnNetwork(net, "B200Acc").run(xs)[0]
     assert ref.shape == got.shape and np.array_equal(ref, got)
+
+
+def _shape_rank_net(with_rank=True):
+    """Shape and Rank of a quantised tensor (Signed32 outputs), beside a Cast of the shape to Float32.  (The bridge to the
+    Arm NN runtime cannot state the scalar TensorShape RankLayer infers: with_rank=False for graphs that go through it.)"""
+    from armnn_b200.network import DataType, INetwork, TensorInfo
+    net = INetwork.Create()
+    il = net.AddInputLayer(0, "input")
+    il.GetOutputSlot(0).SetTensorInfo(TensorInfo((2, 3, 5, 7), DataType.QAsymmU8, 0.1, 128))
+    sh = net.AddShapeLayer("shape")
+    il.GetOutputSlot(0).Connect(sh.GetInputSlot(0))
+    sh.GetOutputSlot(0).SetTensorInfo(TensorInfo((4,), DataType.Signed32))
+    ct = net.AddCastLayer("shape_as_float")
+    sh.GetOutputSlot(0).Connect(ct.GetInputSlot(0))
+    ct.GetOutputSlot(0).SetTensorInfo(TensorInfo((4,), DataType.Float32))
+    outs = [sh, ct]
+    if with_rank:
+        rk = net.AddRankLayer("rank")
+        il.GetOutputSlot(0).Connect(rk.GetInputSlot(0))
+        rk.GetOutputSlot(0).SetTensorInfo(TensorInfo((1,), DataType.Signed32))
+        outs.append(rk)
+    for k, l in enumerate(outs):
+        o = net.AddOutputLayer(k, "out%d" % k)
+        l.GetOutputSlot(0).Connect(o.GetInputSlot(0))
+    return net
+
+
+@needs_plugin
+@pytest.mark.gpu
+def test_shape_and_rank_through_the_runtime_equal_cpuref():
+    from armnn_b200 import network
+    net = _shape_rank_net(with_rank=False)
+    x = np.zeros((2, 3, 5, 7), np.uint8)
+    ref = hostnet.ArmnnNetwork(net, "CpuRef").run({0: x})
+    got = hostnet.ArmnnNetwork(net, "B200Acc").run({0: x})
+    assert list(ref[0]) == [2, 3, 5, 7] and list(ref[1]) == [2.0, 3.0, 5.0, 7.0]
+    for k in range(2):
+        assert ref[k].dtype == got[k].dtype and np.array_equal(ref[k], got[k]), k
+    rt = network.IRuntime.Create(0)
+    ln = rt.GetLoadedNetwork(rt.LoadNetwork(network.Optimize(_shape_rank_net())))
+    ys = {0: np.zeros(4, np.int32), 1: np.zeros(4, np.float32), 2: np.zeros(1, np.int32)}
+    ln.EnqueueWorkload({0: x}, ys)
+    assert list(ys[0]) == [2, 3, 5, 7] and list(ys[2]) == [4]
+
+
+def _gather_nd_net():
+    """GatherNd of pixels (two-entry tuples over a [H, W, C] map) and of single elements (full-rank tuples)."""
+    from armnn_b200.network import DataType, INetwork, TensorInfo
+    net = INetwork.Create()
+    il = net.AddInputLayer(0, "map")
+    il.GetOutputSlot(0).SetTensorInfo(TensorInfo((6, 7, 16), DataType.QAsymmS8, 0.05, -3))
+    i1 = net.AddInputLayer(1, "pixels")
+    i1.GetOutputSlot(0).SetTensorInfo(TensorInfo((5, 2), DataType.Signed32))
+    g1 = net.AddGatherNdLayer("gather_pixels")
+    il.GetOutputSlot(0).Connect(g1.GetInputSlot(0)); i1.GetOutputSlot(0).Connect(g1.GetInputSlot(1))
+    g1.GetOutputSlot(0).SetTensorInfo(TensorInfo((5, 16), DataType.QAsymmS8, 0.05, -3))
+    i2 = net.AddInputLayer(2, "elements")
+    i2.GetOutputSlot(0).SetTensorInfo(TensorInfo((4, 3), DataType.Signed32))
+    g2 = net.AddGatherNdLayer("gather_elements")
+    il.GetOutputSlot(0).Connect(g2.GetInputSlot(0)); i2.GetOutputSlot(0).Connect(g2.GetInputSlot(1))
+    g2.GetOutputSlot(0).SetTensorInfo(TensorInfo((4,), DataType.QAsymmS8, 0.08, 2))             # re-quantised
+    for k, l in enumerate((g1, g2)):
+        o = net.AddOutputLayer(k, "out%d" % k)
+        l.GetOutputSlot(0).Connect(o.GetInputSlot(0))
+    return net
+
+
+def _gather_nd_inputs(seed):
+    rng = np.random.default_rng(seed)
+    return {0: rng.integers(-128, 128, size=(6, 7, 16)).astype(np.int8),
+            1: np.stack([rng.integers(0, 6, 5), rng.integers(0, 7, 5)], axis=1).astype(np.int32),
+            2: np.stack([rng.integers(0, 6, 4), rng.integers(0, 7, 4), rng.integers(0, 16, 4)], axis=1).astype(np.int32)}
+
+
+@needs_plugin
+@pytest.mark.gpu
+def test_gather_nd_through_the_runtime_equals_cpuref():
+    net, xs = _gather_nd_net(), _gather_nd_inputs(83)
+    ref = hostnet.ArmnnNetwork(net, "CpuRef").run(xs)
+    got = hostnet.ArmnnNetwork(net, "B200Acc").run(xs)
+    assert np.array_equal(ref[0], xs[0][xs[1][:, 0], xs[1][:, 1]])
+    for k in (0, 1):
+        assert ref[k].shape == got[k].shape and np.array_equal(ref[k], got[k]), k
