@@ -179,6 +179,15 @@ class QLstmParams(C.Structure):
     ]
 
 
+class LstmParams(C.Structure):
+    _fields_ = ([("batch", _I), ("input_size", _I), ("num_units", _I), ("output_size", _I),
+                 ("input", _P), ("input_stride", C.c_int64), ("output_state_in", _P), ("cell_state_in", _P),
+                 ("output_state_out", _P), ("cell_state_out", _P), ("output", _P), ("output_stride", C.c_int64)] +
+                [(k, _P) for k in ("w_i2i", "w_i2f", "w_i2c", "w_i2o", "w_r2i", "w_r2f", "w_r2c", "w_r2o", "w_c2i", "w_c2f", "w_c2o",
+                                   "b_i", "b_f", "b_c", "b_o", "ln_i", "ln_f", "ln_c", "ln_o", "w_proj", "b_proj")] +
+                [("activation", _I), ("cell_clip", _F), ("projection_clip", _F), ("layer_norm_eps", _F)])
+
+
 # name -> (parameter struct, takes a stream argument in the product library)
 KERNEL_ENTRY_POINTS = {
     "conv2d_q8": Conv2dParams,
@@ -208,6 +217,7 @@ KERNEL_ENTRY_POINTS = {
     "convert_q": ConvertParams,
     "cast_q": ConvertParams,
     "qlstm_step": QLstmParams,
+    "lstm_step_f32": LstmParams,
     "pad_q": PadParams,
     "view_copy_q": ViewCopyParams,
     "resize_q": ResizeParams,

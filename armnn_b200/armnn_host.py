@@ -277,6 +277,9 @@ class ArmnnNetwork:
                 lid = lib.armnnc_add_quantize(net)
             elif t == "Dequantize":
                 lid = lib.armnnc_add_dequantize(net)
+            elif t in ("Lstm", "UnidirectionalSequenceLstm"):
+                lid = lib.armnnc_add_lstm(net, C.byref(self._lstm_params(layer)), int(t != "Lstm"), int(bool(d.get("TimeMajor", False))))
+                assert lid >= 0, lib.armnnc_last_error().decode()
             elif t == "QLstm":
                 lid = lib.armnnc_add_qlstm(net, C.byref(self._qlstm_params(layer)))
                 assert lid >= 0, lib.armnnc_last_error().decode()
@@ -322,6 +325,33 @@ class ArmnnNetwork:
                      "InputLayerNormWeights": ("ln_i", "s_lni"), "ForgetLayerNormWeights": ("ln_f", "s_lnf"),
                      "CellLayerNormWeights": ("ln_c", "s_lnc"), "OutputLayerNormWeights": ("ln_o", "s_lno"),
                      "ProjectionWeights": ("w_proj", "s_proj"), "ProjectionBias": ("b_proj", "s_bproj")}
+
+    def _lstm_params(self, layer):
+        """b200k_lstm_params with HOST weight pointers, as armnnc_add_lstm wants."""
+        from .network import GraphProgram
+        d = layer.desc
+        p = _abi.LstmParams()
+        x, h, c = (s.source.info for s in layer.inputs)
+        p.input_size, p.output_size, p.num_units = x.shape[-1], h.shape[1], c.shape[1]
+        self._keep = getattr(self, "_keep", [])
+        for key, field in GraphProgram._LSTM_FIELDS.items():
+            item = layer.qlstm_params.get(key)
+            if item is None:
+                continue
+            arr = np.ascontiguousarray(np.asarray(item[0], np.float32))
+            self._keep.append(arr)
+            setattr(p, field, arr.ctypes.data)
+        if d.get("CifgEnabled"):
+            p.w_i2i = p.w_r2i = p.w_c2i = p.b_i = p.ln_i = None
+        if not d.get("PeepholeEnabled"):
+            p.w_c2i = p.w_c2f = p.w_c2o = None
+        if not d.get("LayerNormEnabled"):
+            p.ln_i = p.ln_f = p.ln_c = p.ln_o = None
+        if not d.get("ProjectionEnabled"):
+            p.w_proj = p.b_proj = None
+        p.activation = int(d.get("ActivationFunc", 4))
+        p.cell_clip, p.projection_clip = float(d.get("ClippingThresCell", 0.0)), float(d.get("ClippingThresProj", 0.0))
+        return p
 
     def _qlstm_params(self, layer):
         """b200k_qlstm_params with HOST weight pointers, as armnnc_add_qlstm wants."""

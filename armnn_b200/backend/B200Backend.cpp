@@ -78,7 +78,7 @@ class B200LayerSupport : public LayerSupportBase
 {
 public:
     bool IsLayerSupported(const LayerType& type, const std::vector<TensorInfo>& infos, const BaseDescriptor& descriptor,
-                          const Optional<LstmInputParamsInfo>&, const Optional<QuantizedLstmInputParamsInfo>&,
+                          const Optional<LstmInputParamsInfo>& lstmParamsInfo, const Optional<QuantizedLstmInputParamsInfo>&,
                           Optional<std::string&> reason) const override
     {
         switch (type)
@@ -349,6 +349,18 @@ public:
             case LayerType::Dequantize:
                 if (infos[0].HasPerAxisQuantization()) { return No(reason, "per-axis input is not supported"); }
                 return (IsActType(infos[0]) && IsActType(infos[1])) || No(reason, "unsupported data type");
+            case LayerType::Lstm:
+            case LayerType::UnidirectionalSequenceLstm:
+            {
+                // infos: input, outputStateIn, cellStateIn, then the outputs; the weights travel in lstmParamsInfo
+                for (const TensorInfo& t : infos) { if (t.GetDataType() != DataType::Float32) { return No(reason, "Float32 tensors only"); } }
+                const auto& d = *PolymorphicDowncast<const LstmDescriptor*>(&descriptor);
+                const uint32_t f = d.m_ActivationFunc;
+                if (f != 0 && f != 1 && f != 3 && f != 4 && f != 6) { return No(reason, "unsupported activation function"); }
+                if (lstmParamsInfo.has_value() && lstmParamsInfo.value().m_InputToForgetWeights &&
+                    lstmParamsInfo.value().m_InputToForgetWeights->GetDataType() != DataType::Float32) { return No(reason, "Float32 weights only"); }
+                return true;
+            }
             case LayerType::QLstm:
                 if (infos[0].GetDataType() != DataType::QAsymmS8 || infos[2].GetDataType() != DataType::QSymmS16) { return No(reason, "QLstm needs QAsymmS8 input and QSymmS16 cell state"); }
                 return true;

@@ -899,6 +899,91 @@ std::unique_ptr<IWorkload> MakeEltwise(const QueueDescriptor& d, const WorkloadI
     ARMNN_NO_DEPRECATE_WARN_END
 }
 
+// Lstm and UnidirectionalSequenceLstm on Float32 tensors: one b200k_lstm_step_f32 per time step.  LstmQueueDescriptor and
+// UnidirectionalSequenceLstmQueueDescriptor carry the same members under the same names.
+template <typename QD>
+std::unique_ptr<IWorkload> MakeLstm(const QueueDescriptor& d, const WorkloadInfo& info, const ContextPtr& ctx, bool sequence)
+{
+    const auto& qd = *PolymorphicDowncast<const QD*>(&d);
+    const auto& prm = qd.m_Parameters;
+    struct State
+    {
+        explicit State(const ContextPtr& c) : blobs(c) {}
+        b200k_lstm_params p;
+        DeviceBlobs blobs;
+        int64_t steps = 1, stepIn = 0, stepOut = 0;          // elements between two time steps of the sequence tensors
+    };
+    auto st = std::make_shared<State>(ctx);
+    b200k_lstm_params& p = st->p;
+    std::memset(&p, 0, sizeof(p));
+    const TensorInfo& x = info.m_InputTensorInfos[0];
+    const TensorInfo& h = info.m_InputTensorInfos[1];
+    const TensorInfo& c = info.m_InputTensorInfos[2];
+    p.output_size = static_cast<int32_t>(h.GetShape()[1]); p.num_units = static_cast<int32_t>(c.GetShape()[1]);
+    if (sequence)
+    {
+        if (x.GetNumDimensions() != 3) { throw InvalidArgumentException("B200Acc: UnidirectionalSequenceLstm needs a 3-D input"); }
+        const int64_t d0 = x.GetShape()[0], d1 = x.GetShape()[1];
+        p.input_size = static_cast<int32_t>(x.GetShape()[2]);
+        st->steps = prm.m_TimeMajor ? d0 : d1;
+        p.batch = static_cast<int32_t>(prm.m_TimeMajor ? d1 : d0);
+        // time major [T, B, I]: a step is a dense [B, I] block; batch major [B, T, I]: its rows are T * I apart
+        p.input_stride = prm.m_TimeMajor ? p.input_size : st->steps * p.input_size;
+        p.output_stride = prm.m_TimeMajor ? p.output_size : st->steps * p.output_size;
+        st->stepIn = prm.m_TimeMajor ? static_cast<int64_t>(p.batch) * p.input_size : p.input_size;
+        st->stepOut = prm.m_TimeMajor ? static_cast<int64_t>(p.batch) * p.output_size : p.output_size;
+    }
+    else
+    {
+        p.batch = static_cast<int32_t>(x.GetShape()[0]); p.input_size = static_cast<int32_t>(x.GetShape()[1]);
+        p.input_stride = p.input_size; p.output_stride = p.output_size;
+    }
+    auto up = [&](const ConstTensorHandle* t) -> const float*
+    {
+        if (!t) { return nullptr; }
+        return static_cast<const float*>(st->blobs.Upload(t->GetConstTensor<void>(), t->GetTensorInfo().GetNumBytes()));
+    };
+    if (!prm.m_CifgEnabled) { p.w_i2i = up(qd.m_InputToInputWeights); p.w_r2i = up(qd.m_RecurrentToInputWeights); p.b_i = up(qd.m_InputGateBias); }
+    p.w_i2f = up(qd.m_InputToForgetWeights); p.w_i2c = up(qd.m_InputToCellWeights); p.w_i2o = up(qd.m_InputToOutputWeights);
+    p.w_r2f = up(qd.m_RecurrentToForgetWeights); p.w_r2c = up(qd.m_RecurrentToCellWeights); p.w_r2o = up(qd.m_RecurrentToOutputWeights);
+    p.b_f = up(qd.m_ForgetGateBias); p.b_c = up(qd.m_CellBias); p.b_o = up(qd.m_OutputGateBias);
+    if (prm.m_PeepholeEnabled)
+    {
+        if (!prm.m_CifgEnabled) { p.w_c2i = up(qd.m_CellToInputWeights); }
+        p.w_c2f = up(qd.m_CellToForgetWeights); p.w_c2o = up(qd.m_CellToOutputWeights);
+    }
+    if (prm.m_LayerNormEnabled)
+    {
+        if (!prm.m_CifgEnabled) { p.ln_i = up(qd.m_InputLayerNormWeights); }
+        p.ln_f = up(qd.m_ForgetLayerNormWeights); p.ln_c = up(qd.m_CellLayerNormWeights); p.ln_o = up(qd.m_OutputLayerNormWeights);
+    }
+    if (prm.m_ProjectionEnabled) { p.w_proj = up(qd.m_ProjectionWeights); p.b_proj = up(qd.m_ProjectionBias); }
+    p.activation = static_cast<int32_t>(prm.m_ActivationFunc);
+    p.cell_clip = prm.m_ClippingThresCell; p.projection_clip = prm.m_ClippingThresProj;
+    p.layer_norm_eps = 1e-8f;                                  // RefLstmWorkload.hpp: m_LayerNormEpsilon
+    // outputs: Lstm: scratch, outputStateOut, cellStateOut, output; the sequence layer: outputStateOut, cellStateOut, output
+    // (the reference's sequence workload leaves its two state outputs unwritten, RefUnidirectionalSequenceLstmWorkload.cpp:
+    // 95-123; here they hold the running and finally the last states)
+    const unsigned int o0 = sequence ? 0u : 1u;
+    return Make<QD>(d, info, ctx, [st, o0](const QD& data, cudaStream_t s)
+    {
+        b200k_lstm_params q = st->p;
+        const float* x0 = static_cast<const float*>(Dev(data.m_Inputs[0]));
+        float* out0 = static_cast<float*>(Dev(data.m_Outputs[o0 + 2]));
+        q.output_state_out = static_cast<float*>(Dev(data.m_Outputs[o0]));
+        q.cell_state_out = static_cast<float*>(Dev(data.m_Outputs[o0 + 1]));
+        for (int64_t t = 0; t < st->steps; ++t)
+        {
+            // the first step reads the state inputs, the others update the state outputs in place
+            q.output_state_in = t == 0 ? static_cast<const float*>(Dev(data.m_Inputs[1])) : q.output_state_out;
+            q.cell_state_in = t == 0 ? static_cast<const float*>(Dev(data.m_Inputs[2])) : q.cell_state_out;
+            q.input = x0 + t * st->stepIn;
+            q.output = out0 + t * st->stepOut;
+            B200CheckStatus(b200k_lstm_step_f32(&q, s));
+        }
+    });
+}
+
 // Device copies of the QLstm weights: the descriptor's ConstTensorHandles are released by the layer right after
 // CreateWorkload (src/armnn/LoadedNetwork.cpp:396), as RefQLstmWorkload's AssignScopedTensorHandle copies show.
 std::unique_ptr<IWorkload> MakeQLstm(const QueueDescriptor& d, const WorkloadInfo& info, const ContextPtr& ctx)
@@ -1636,6 +1721,10 @@ std::unique_ptr<IWorkload> B200WorkloadFactory::CreateWorkload(LayerType type, c
         case LayerType::Stack:        return MakeStack(d, info, ctx);
         case LayerType::QLstm:
             return MakeQLstm(d, info, ctx);
+        case LayerType::Lstm:
+            return MakeLstm<LstmQueueDescriptor>(d, info, ctx, false);
+        case LayerType::UnidirectionalSequenceLstm:
+            return MakeLstm<UnidirectionalSequenceLstmQueueDescriptor>(d, info, ctx, true);
         case LayerType::PreCompiled:
         {
             const auto& qd = *PolymorphicDowncast<const PreCompiledQueueDescriptor*>(&d);

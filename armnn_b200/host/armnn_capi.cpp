@@ -366,6 +366,43 @@ int armnnc_add_reshape(void* vn, int rank, const int32_t* shape)
     return add_layer(n, n->net->AddReshapeLayer(d));
 }
 
+// Lstm (sequence = 0) or UnidirectionalSequenceLstm (sequence = 1) layer on Float32 tensors from a b200k_lstm_params whose
+// weight pointers are HOST pointers (copied by Arm NN); only the sizes, weights and option fields are read.
+int armnnc_add_lstm(void* vn, const b200k_lstm_params* p, int sequence, int time_major)
+{
+    auto* n = static_cast<CNet*>(vn);
+    const unsigned I = p->input_size, U = p->num_units, O = p->output_size;
+    LstmDescriptor d;
+    d.m_CifgEnabled = p->w_i2i == nullptr;
+    d.m_PeepholeEnabled = p->w_c2f != nullptr;
+    d.m_ProjectionEnabled = p->w_proj != nullptr;
+    d.m_LayerNormEnabled = p->ln_f != nullptr;
+    d.m_ActivationFunc = (uint32_t)p->activation;
+    d.m_ClippingThresCell = p->cell_clip; d.m_ClippingThresProj = p->projection_clip;
+    d.m_TimeMajor = time_major != 0;
+    std::vector<std::unique_ptr<ConstTensor>> keep;
+    auto ct = [&](const float* data, TensorShape shape) -> const ConstTensor* {
+        if (!data) return nullptr;
+        TensorInfo info(shape, DataType::Float32);
+        info.SetConstant(true);
+        keep.push_back(std::make_unique<ConstTensor>(info, data));
+        return keep.back().get();
+    };
+    LstmInputParams q;
+    q.m_InputToInputWeights = ct(p->w_i2i, {U, I}); q.m_InputToForgetWeights = ct(p->w_i2f, {U, I});
+    q.m_InputToCellWeights = ct(p->w_i2c, {U, I}); q.m_InputToOutputWeights = ct(p->w_i2o, {U, I});
+    q.m_RecurrentToInputWeights = ct(p->w_r2i, {U, O}); q.m_RecurrentToForgetWeights = ct(p->w_r2f, {U, O});
+    q.m_RecurrentToCellWeights = ct(p->w_r2c, {U, O}); q.m_RecurrentToOutputWeights = ct(p->w_r2o, {U, O});
+    q.m_CellToInputWeights = ct(p->w_c2i, {U}); q.m_CellToForgetWeights = ct(p->w_c2f, {U}); q.m_CellToOutputWeights = ct(p->w_c2o, {U});
+    q.m_InputGateBias = ct(p->b_i, {U}); q.m_ForgetGateBias = ct(p->b_f, {U}); q.m_CellBias = ct(p->b_c, {U}); q.m_OutputGateBias = ct(p->b_o, {U});
+    q.m_InputLayerNormWeights = ct(p->ln_i, {U}); q.m_ForgetLayerNormWeights = ct(p->ln_f, {U});
+    q.m_CellLayerNormWeights = ct(p->ln_c, {U}); q.m_OutputLayerNormWeights = ct(p->ln_o, {U});
+    q.m_ProjectionWeights = ct(p->w_proj, {O, U}); q.m_ProjectionBias = ct(p->b_proj, {O});
+    try {
+        return add_layer(n, sequence ? n->net->AddUnidirectionalSequenceLstmLayer(d, q) : n->net->AddLstmLayer(d, q));
+    } catch (const std::exception& e) { g_err = e.what(); return -1; }
+}
+
 // QLstm layer from a b200k_qlstm_params whose weight pointers are HOST pointers (copied by Arm NN); only the weight,
 // scale and descriptor fields are read.  Optional weights are null pointers.
 int armnnc_add_qlstm(void* vn, const b200k_qlstm_params* p)

@@ -423,6 +423,22 @@ class INetwork:
         return self._add(Layer("InstanceNormalization", name, 1, 1, {"gamma": float(gamma), "beta": float(beta), "eps": float(eps),
                                                                       "nchw": bool(nchw)}))
 
+    def AddLstmLayer(self, descriptor, params, name=None):
+        """armnn::INetwork::AddLstmLayer on Float32 tensors.  descriptor: dict of armnn::LstmDescriptor fields
+        (ActivationFunc, ClippingThresCell, ClippingThresProj, CifgEnabled, PeepholeEnabled, ProjectionEnabled,
+        LayerNormEnabled); params: dict name -> (ndarray, TensorInfo) of the LstmInputParams members.  Inputs: input,
+        outputStateIn, cellStateIn.  Outputs: scratchBuffer, outputStateOut, cellStateOut, output."""
+        layer = self._add(Layer("Lstm", name, 3, 4, dict(descriptor)))
+        layer.qlstm_params = params
+        return layer
+
+    def AddUnidirectionalSequenceLstmLayer(self, descriptor, params, name=None):
+        """armnn::INetwork::AddUnidirectionalSequenceLstmLayer on Float32 tensors: the LstmDescriptor fields plus TimeMajor;
+        input [batch, time, input] (or [time, batch, input]).  Outputs: outputStateOut, cellStateOut, output."""
+        layer = self._add(Layer("UnidirectionalSequenceLstm", name, 3, 3, dict(descriptor)))
+        layer.qlstm_params = params
+        return layer
+
     def AddQLstmLayer(self, descriptor, params, name=None):
         """descriptor: dict of armnn::QLstmDescriptor fields; params: dict name -> (ndarray, TensorInfo) of the
         LstmInputParams members.  Inputs: input, outputStateIn, cellStateIn.  Outputs: outputStateOut,
@@ -636,6 +652,14 @@ def IsLayerSupported(layer):
             return False, "StridedSlice: ellipsis and new-axis masks are not supported"
         if ins[0].dtype != outs[0].dtype or not outs[0].same_quantization(ins[0]):
             return False, "%s: input and output must share type and quantisation (the reference copies raw elements)" % t
+        return True, ""
+    if t in ("Lstm", "UnidirectionalSequenceLstm"):
+        if any(i.dtype != DataType.Float32 for i in list(ins) + list(outs)):
+            return False, "%s: Float32 tensors only" % t
+        if any(info.dtype != DataType.Float32 for item in layer.qlstm_params.values() if item is not None for info in [item[1]]):
+            return False, "%s: Float32 weights only" % t
+        if layer.desc.get("ActivationFunc", 4) not in (0, 1, 3, 4, 6):
+            return False, "%s: unsupported activation function" % t
         return True, ""
     if t == "QLstm":
         if ins[0].dtype != DataType.QAsymmS8 or ins[2].dtype != DataType.QSymmS16:
@@ -1380,6 +1404,78 @@ class GraphProgram:
         if tuple(out_shape) != tuple(y.info.shape):
             raise InvalidArgumentException("Slice: output shape %s is not the block %s" % (y.info.shape, out_shape))
         return self._view_copy(x, y, v)
+
+    _LSTM_FIELDS = {"InputToInputWeights": "w_i2i", "InputToForgetWeights": "w_i2f", "InputToCellWeights": "w_i2c",
+                    "InputToOutputWeights": "w_i2o", "RecurrentToInputWeights": "w_r2i", "RecurrentToForgetWeights": "w_r2f",
+                    "RecurrentToCellWeights": "w_r2c", "RecurrentToOutputWeights": "w_r2o", "CellToInputWeights": "w_c2i",
+                    "CellToForgetWeights": "w_c2f", "CellToOutputWeights": "w_c2o", "InputGateBias": "b_i", "ForgetGateBias": "b_f",
+                    "CellBias": "b_c", "OutputGateBias": "b_o", "InputLayerNormWeights": "ln_i", "ForgetLayerNormWeights": "ln_f",
+                    "CellLayerNormWeights": "ln_c", "OutputLayerNormWeights": "ln_o", "ProjectionWeights": "w_proj",
+                    "ProjectionBias": "b_proj"}
+
+    def _lstm_weights(self, layer, p):
+        """Device copies of the weights (the descriptor's handles die after workload creation) and the option switches."""
+        d = layer.desc
+        for key, field in self._LSTM_FIELDS.items():
+            item = layer.qlstm_params.get(key)
+            if item is None:
+                continue
+            dev = self._upload(np.ascontiguousarray(np.asarray(item[0], np.float32)))
+            self.aux.append(dev)
+            setattr(p, field, self._ptr(dev))
+        if d.get("CifgEnabled"):
+            p.w_i2i = p.w_r2i = p.w_c2i = p.b_i = p.ln_i = None
+        if not d.get("PeepholeEnabled"):
+            p.w_c2i = p.w_c2f = p.w_c2o = None
+        if not d.get("LayerNormEnabled"):
+            p.ln_i = p.ln_f = p.ln_c = p.ln_o = None
+        if not d.get("ProjectionEnabled"):
+            p.w_proj = p.b_proj = None
+        p.activation = int(d.get("ActivationFunc", 4))
+        p.cell_clip, p.projection_clip = float(d.get("ClippingThresCell", 0.0)), float(d.get("ClippingThresProj", 0.0))
+        p.layer_norm_eps = 1e-8                                     # RefLstmWorkload.hpp: m_LayerNormEpsilon
+
+    def _make_Lstm(self, layer):
+        x, h, c = (s.source for s in layer.inputs)
+        _, hout, cout, out = layer.outputs
+        p = _abi.LstmParams()
+        p.batch, p.input_size = x.info.shape
+        p.output_size, p.num_units = h.info.shape[1], c.info.shape[1]
+        p.input, p.input_stride = self._ptr(self._dev(x)), p.input_size
+        p.output_state_in, p.cell_state_in = self._ptr(self._dev(h)), self._ptr(self._dev(c))
+        p.output_state_out, p.cell_state_out = self._ptr(self._dev(hout)), self._ptr(self._dev(cout))
+        p.output, p.output_stride = self._ptr(self._dev(out)), p.output_size
+        self._lstm_weights(layer, p)
+        return "lstm_step_f32", p
+
+    def _make_UnidirectionalSequenceLstm(self, layer):
+        """One step per time index (RefUnidirectionalSequenceLstmWorkload.cpp:160-293): the first reads the state inputs,
+        the others update the state outputs in place; a step's rows are `input_stride` apart in the sequence tensor, so
+        neither layout needs a transposed copy."""
+        x, h, c = (s.source for s in layer.inputs)
+        hout, cout, out = layer.outputs
+        time_major = bool(layer.desc.get("TimeMajor", False))
+        steps, batch = (x.info.shape[0], x.info.shape[1]) if time_major else (x.info.shape[1], x.info.shape[0])
+        n_in, n_out, units = x.info.shape[2], h.info.shape[1], c.info.shape[1]
+        work = []
+        for t in range(steps):
+            p = _abi.LstmParams()
+            p.batch, p.input_size, p.num_units, p.output_size = batch, n_in, units, n_out
+            p.input = self._ptr(self._dev(x)) + 4 * (t * batch * n_in if time_major else t * n_in)
+            p.input_stride = n_in if time_major else steps * n_in
+            p.output = self._ptr(self._dev(out)) + 4 * (t * batch * n_out if time_major else t * n_out)
+            p.output_stride = n_out if time_major else steps * n_out
+            p.output_state_in = self._ptr(self._dev(h if t == 0 else hout))
+            p.cell_state_in = self._ptr(self._dev(c if t == 0 else cout))
+            p.output_state_out, p.cell_state_out = self._ptr(self._dev(hout)), self._ptr(self._dev(cout))
+            if t == 0:
+                self._lstm_weights(layer, p)
+                first = p
+            else:
+                for field in list(self._LSTM_FIELDS.values()) + ["activation", "cell_clip", "projection_clip", "layer_norm_eps"]:
+                    setattr(p, field, getattr(first, field))
+            work.append(("lstm_step_f32", p))
+        return work
 
     def _make_QLstm(self, layer):
         x, h, c = (s.source for s in layer.inputs)

@@ -561,6 +561,35 @@ typedef struct {
 
 int b200k_qlstm_step(const b200k_qlstm_params* p, void* stream);
 
+/* One step of armnn::LstmImpl on Float32 tensors (src/backends/reference/workloads/Lstm.cpp:14-259 with LstmUtils.cpp;
+ * the Lstm layer, and every time step of UnidirectionalSequenceLstm): gate pre-activations accumulated term by term in
+ * the reference's order (bias, input weights over the input, recurrent weights over the previous output, peephole),
+ * optional layer normalisation, sigmoid gates, the cell activation, cell update and clipping, optional projection with
+ * clipping.  Row-major matrices [rows = units (or outputs), columns].
+ *   w_i2i == NULL: CIFG (no input gate; it becomes 1 - forget gate);  w_c2f == NULL: no peephole;
+ *   ln_f == NULL: no layer normalisation;  w_proj == NULL: no projection (output_size == num_units then).
+ *   activation (armnn::LstmDescriptor::m_ActivationFunc): 0 none, 1 ReLu, 3 ReLu6, 4 TanH, 6 Sigmoid.
+ *   input_stride / output_stride: elements between the rows of two batch entries (a time step of a sequence tensor).
+ * output_state_out / cell_state_out may be the state inputs themselves (the steps of a sequence update them in place).
+ * The layer's scratch-buffer output is working memory in the reference and is not written. */
+typedef struct {
+    int32_t batch, input_size, num_units, output_size;
+    const float* input; int64_t input_stride;
+    const float* output_state_in; const float* cell_state_in;
+    float* output_state_out; float* cell_state_out;
+    float* output; int64_t output_stride;
+    const float *w_i2i, *w_i2f, *w_i2c, *w_i2o;
+    const float *w_r2i, *w_r2f, *w_r2c, *w_r2o;
+    const float *w_c2i, *w_c2f, *w_c2o;
+    const float *b_i, *b_f, *b_c, *b_o;
+    const float *ln_i, *ln_f, *ln_c, *ln_o;
+    const float *w_proj, *b_proj;
+    int32_t activation;
+    float cell_clip, projection_clip, layer_norm_eps;
+} b200k_lstm_params;
+
+int b200k_lstm_step_f32(const b200k_lstm_params* p, void* stream);
+
 /* Status of the bounded device-side waits of the tcgen05 kernels: B200K_OK, or B200K_E_TIMEOUT when a wait
  * gave up since the last poll (the status word is then cleared).  Synchronises the device.  No counterpart in
  * the reference. */
@@ -579,7 +608,7 @@ unsigned long long b200k_kernel_launches(void);
 
 /* sizeof() of a parameter struct as compiled into the library, for bindings in other languages to check their
  * own declarations: 0 conv2d, 1 fc, 2 bmm, 3 pool2d, 4 mean, 5 eltwise, 6 activation, 7 softmax, 8 convert,
- * 9 qlstm, 10 pad, 11 view_copy, 12 resize, 13 reduce, 14 unary, 15 arg_min_max, 16 gather, 17 batch_norm, 18 instance_norm, 19 normalization, 20 conv3d, 21 pool3d, 22 gather_nd.  No counterpart in the reference (its backends are linked as C++). */
+ * 9 qlstm, 10 pad, 11 view_copy, 12 resize, 13 reduce, 14 unary, 15 arg_min_max, 16 gather, 17 batch_norm, 18 instance_norm, 19 normalization, 20 conv3d, 21 pool3d, 22 gather_nd, 23 lstm.  No counterpart in the reference (its backends are linked as C++). */
 size_t b200k_sizeof_params(int which);
 
 #ifdef __cplusplus

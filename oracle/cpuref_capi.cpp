@@ -991,3 +991,55 @@ extern "C" int cpuref_qlstm_step(const b200k_qlstm_params* p)
     });
 }
 
+
+// The Lstm layer on Float32 tensors (RefLstmWorkload); input_stride / output_stride must be the dense ones here.
+extern "C" int cpuref_lstm_step_f32(const b200k_lstm_params* p)
+{
+    return guarded([&] {
+        Harness h;
+        const unsigned B = p->batch, I = p->input_size, U = p->num_units, O = p->output_size;
+        if (p->input_stride != (int64_t)I || p->output_stride != (int64_t)O) throw InvalidArgumentException("dense rows only");
+        TensorInfo xi({B, I}, DataType::Float32), hi({B, O}, DataType::Float32), ci({B, U}, DataType::Float32);
+        LstmQueueDescriptor d;
+        auto& q = d.m_Parameters;
+        q.m_CifgEnabled = p->w_i2i == nullptr;
+        q.m_PeepholeEnabled = p->w_c2f != nullptr;
+        q.m_ProjectionEnabled = p->w_proj != nullptr;
+        q.m_LayerNormEnabled = p->ln_f != nullptr;
+        q.m_ActivationFunc = (uint32_t)p->activation;
+        q.m_ClippingThresCell = p->cell_clip; q.m_ClippingThresProj = p->projection_clip;
+        TensorInfo scratch({B, U * (q.m_CifgEnabled ? 3u : 4u)}, DataType::Float32);
+        std::vector<std::unique_ptr<ScopedTensorHandle>> keep;
+        auto weight = [&](const float* data, TensorShape shape) -> const ConstTensorHandle* {
+            if (!data) return nullptr;
+            TensorInfo info(shape, DataType::Float32);
+            info.SetConstant(true);
+            auto t = std::make_unique<ScopedTensorHandle>(info);
+            t->Allocate();
+            std::memcpy(t->GetTensor<void>(), data, info.GetNumBytes());
+            keep.push_back(std::move(t));
+            return keep.back().get();
+        };
+        d.m_InputToInputWeights  = weight(p->w_i2i, {U, I}); d.m_InputToForgetWeights = weight(p->w_i2f, {U, I});
+        d.m_InputToCellWeights   = weight(p->w_i2c, {U, I}); d.m_InputToOutputWeights = weight(p->w_i2o, {U, I});
+        d.m_RecurrentToInputWeights  = weight(p->w_r2i, {U, O}); d.m_RecurrentToForgetWeights = weight(p->w_r2f, {U, O});
+        d.m_RecurrentToCellWeights   = weight(p->w_r2c, {U, O}); d.m_RecurrentToOutputWeights = weight(p->w_r2o, {U, O});
+        d.m_CellToInputWeights = weight(p->w_c2i, {U}); d.m_CellToForgetWeights = weight(p->w_c2f, {U}); d.m_CellToOutputWeights = weight(p->w_c2o, {U});
+        d.m_InputGateBias = weight(p->b_i, {U}); d.m_ForgetGateBias = weight(p->b_f, {U});
+        d.m_CellBias = weight(p->b_c, {U}); d.m_OutputGateBias = weight(p->b_o, {U});
+        d.m_InputLayerNormWeights = weight(p->ln_i, {U}); d.m_ForgetLayerNormWeights = weight(p->ln_f, {U});
+        d.m_CellLayerNormWeights = weight(p->ln_c, {U}); d.m_OutputLayerNormWeights = weight(p->ln_o, {U});
+        d.m_ProjectionWeights = weight(p->w_proj, {O, U}); d.m_ProjectionBias = weight(p->b_proj, {O});
+        h.in(d, xi, p->input);
+        h.in(d, hi, p->output_state_in);
+        h.in(d, ci, p->cell_state_in);
+        h.out(d, scratch);
+        auto* o1 = h.out(d, hi);
+        auto* o2 = h.out(d, ci);
+        auto* o3 = h.out(d, hi);
+        h.run(LayerType::Lstm, d);
+        copy_out(o1, p->output_state_out, hi.GetNumBytes());
+        copy_out(o2, p->cell_state_out, ci.GetNumBytes());
+        copy_out(o3, p->output, hi.GetNumBytes());
+    });
+}

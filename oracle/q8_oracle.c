@@ -1620,3 +1620,100 @@ int oracle_qlstm_step(const b200k_qlstm_params* p)
     free(gi); free(gf); free(gc); free(go); free(hidden); free(out16);
     return 0;
 }
+
+/* ---- Float32 LSTM step, Lstm.cpp:14-259 with LstmUtils.cpp (the Lstm layer and each time step of
+ * UnidirectionalSequenceLstm).  Every sum is accumulated term by term in the reference's order. ---------------------- */
+
+static float lstm_act(float in, int fn)                         /* LstmUtils.cpp:258-297 + Activation.cpp */
+{
+    switch (fn) {
+        case 1: return in > 0.f ? in : 0.f;
+        case 3: { float t = in > 0.f ? in : 0.f; return t < 6.f ? t : 6.f; }
+        case 4: return tanhf(in);
+        case 6: return 1.f / (1.f + expf(-in));
+        default: return in;
+    }
+}
+
+static void lstm_gate(const b200k_lstm_params* p, const float* x, const float* h, const float* wi, const float* wr,
+                      const float* peephole, const float* cell, const float* bias, const float* ln, float* out)
+{
+    const int U = p->num_units;
+    for (int u = 0; u < U; ++u) {
+        volatile float acc = ln ? 0.0f : bias[u];               /* :59-82 */
+        for (int k = 0; k < p->input_size; ++k) { volatile float t = wi[(int64_t)u * p->input_size + k] * x[k]; acc = acc + t; }
+        for (int k = 0; k < p->output_size; ++k) { volatile float t = wr[(int64_t)u * p->output_size + k] * h[k]; acc = acc + t; }
+        if (peephole) { volatile float t = peephole[u] * cell[u]; acc = acc + t; }
+        out[u] = acc;
+    }
+    if (ln) {                                                   /* LstmUtils.cpp:40-74 */
+        volatile float sum = 0.0f, sum_sq = 0.0f;
+        for (int u = 0; u < U; ++u) { sum = sum + out[u]; volatile float sq = out[u] * out[u]; sum_sq = sum_sq + sq; }
+        const float mean = sum / (float)U;
+        volatile float m2 = mean * mean;
+        volatile float ms = sum_sq / (float)U;
+        const float variance = ms - m2;
+        const float stddev_inv = variance == 0 ? 1.0f / sqrtf(p->layer_norm_eps) : 1.0f / sqrtf(variance);
+        for (int u = 0; u < U; ++u) {
+            volatile float d = out[u] - mean;
+            volatile float n = d * stddev_inv;
+            volatile float w = ln[u] * n;
+            out[u] = w + bias[u];
+        }
+    }
+}
+
+int oracle_lstm_step_f32(const b200k_lstm_params* p)
+{
+    if (!p->input || !p->output_state_in || !p->cell_state_in || !p->output_state_out || !p->cell_state_out || !p->output) return B200K_E_INVALID;
+    const int U = p->num_units, O = p->output_size;
+    const int cifg = p->w_i2i == NULL, ln = p->ln_f != NULL;
+    if (!p->w_proj && O != U) return B200K_E_INVALID;
+    float* gi = (float*)malloc(sizeof(float) * U * 5);
+    float *gf = gi + U, *gc = gf + U, *go = gc + U, *act = go + U;
+    for (int b = 0; b < p->batch; ++b) {
+        const float* x = p->input + b * p->input_stride;
+        const float* h = p->output_state_in + (int64_t)b * O;
+        const float* c_in = p->cell_state_in + (int64_t)b * U;
+        float* c_out = p->cell_state_out + (int64_t)b * U;
+        float* out = p->output + b * p->output_stride;
+        if (!cifg) {
+            lstm_gate(p, x, h, p->w_i2i, p->w_r2i, p->w_c2i, c_in, p->b_i, ln ? p->ln_i : NULL, gi);
+            for (int u = 0; u < U; ++u) gi[u] = lstm_act(gi[u], 6);
+        }
+        lstm_gate(p, x, h, p->w_i2f, p->w_r2f, p->w_c2f, c_in, p->b_f, ln ? p->ln_f : NULL, gf);
+        for (int u = 0; u < U; ++u) gf[u] = lstm_act(gf[u], 6);
+        lstm_gate(p, x, h, p->w_i2c, p->w_r2c, NULL, NULL, p->b_c, ln ? p->ln_c : NULL, gc);
+        for (int u = 0; u < U; ++u) {
+            volatile float c = gf[u] * c_in[u];                                  /* :170 */
+            if (p->activation > 0) gc[u] = lstm_act(gc[u], p->activation);       /* :176-181 */
+            volatile float gate = cifg ? 1.0f - gf[u] : gi[u];                   /* :182-192 */
+            volatile float t = gc[u] * gate;
+            c = c + t;
+            if (p->cell_clip > 0.0f) c = c > p->cell_clip ? p->cell_clip : (c < -p->cell_clip ? -p->cell_clip : c);
+            c_out[u] = c;
+        }
+        /* the output gate's peephole reads the new cell state (:198-202); its matrix terms come first */
+        lstm_gate(p, x, h, p->w_i2o, p->w_r2o, p->w_c2o, c_out, p->b_o, ln ? p->ln_o : NULL, go);
+        for (int u = 0; u < U; ++u) {
+            const float og = lstm_act(go[u], 6);
+            /* without an activation function the cell scratch still holds the cell gate (:216-222) */
+            const float cs = p->activation > 0 ? lstm_act(c_out[u], p->activation) : gc[u];
+            volatile float r = og * cs;
+            act[u] = r;
+        }
+        if (p->w_proj) {
+            for (int o = 0; o < O; ++o) {
+                volatile float acc = p->b_proj ? p->b_proj[o] : 0.0f;
+                for (int k = 0; k < U; ++k) { volatile float t = p->w_proj[(int64_t)o * U + k] * act[k]; acc = acc + t; }
+                if (p->projection_clip > 0.0f) acc = acc > p->projection_clip ? p->projection_clip : (acc < -p->projection_clip ? -p->projection_clip : acc);
+                out[o] = acc;
+            }
+        } else {
+            for (int o = 0; o < O; ++o) out[o] = act[o];
+        }
+        for (int o = 0; o < O; ++o) p->output_state_out[(int64_t)b * O + o] = out[o];
+    }
+    free(gi);
+    return 0;
+}

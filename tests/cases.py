@@ -617,6 +617,44 @@ def volume_cases():
     }
 
 
+def lstm_cases():
+    """One Float32 LSTM step with every combination of options the reference implements."""
+    def make(seed, batch, n_in, units, n_out, cifg=False, peephole=False, layer_norm=False, projection=False, activation=4,
+             cell_clip=0.0, proj_clip=0.0):
+        def build(mem):
+            rng = np.random.default_rng(seed)
+            p = _abi.LstmParams()
+            f = lambda *shape, s=0.4: mem.inp((rng.standard_normal(shape) * s).astype(np.float32))
+            p.batch, p.input_size, p.num_units, p.output_size = batch, n_in, units, n_out
+            p.input, p.input_stride = f(batch, n_in, s=1.0), n_in
+            p.output_state_in, p.cell_state_in = f(batch, n_out, s=0.7), f(batch, units, s=0.7)
+            hs, p.output_state_out = mem.out((batch, n_out), np.float32)
+            cs, p.cell_state_out = mem.out((batch, units), np.float32)
+            out, p.output = mem.out((batch, n_out), np.float32)
+            p.output_stride = n_out
+            for g in "ifco":
+                if g == "i" and cifg:
+                    continue
+                setattr(p, "w_i2" + g, f(units, n_in)); setattr(p, "w_r2" + g, f(units, n_out)); setattr(p, "b_" + g, f(units))
+                if peephole and g != "c":
+                    setattr(p, "w_c2" + g, f(units))
+                if layer_norm:
+                    setattr(p, "ln_" + g, f(units, s=1.0))
+            if projection:
+                p.w_proj, p.b_proj = f(n_out, units), f(n_out)
+            p.activation, p.cell_clip, p.projection_clip, p.layer_norm_eps = activation, cell_clip, proj_clip, 1e-8
+            return p, [hs, cs, out]
+        return lambda: SimpleCase("lstm_step_f32", build)
+    return {
+        "plain_tanh": make(421, 3, 20, 32, 32),
+        "cifg_peephole": make(422, 2, 12, 24, 24, cifg=True, peephole=True),
+        "layer_norm_projection": make(423, 4, 40, 64, 24, layer_norm=True, projection=True, cell_clip=1.5, proj_clip=0.8),
+        "everything_relu6": make(424, 2, 16, 48, 20, peephole=True, layer_norm=True, projection=True, activation=3, cell_clip=3.0),
+        "no_activation_cifg_layer_norm": make(425, 2, 10, 16, 16, cifg=True, layer_norm=True, activation=0),
+        "sigmoid_wide": make(426, 1, 300, 520, 520, activation=6),
+    }
+
+
 def convert_cases():
     def make(seed, xd, yd, count=1001, xq=(0.05, 3), yq=(0.07, -4), entry="convert_q", fscale=4):
         def build(mem):
@@ -970,7 +1008,7 @@ def move_cases():
 ALL_GROUPS = {"conv": conv_cases, "dwconv": dwconv_cases, "fc": fc_cases, "bmm": bmm_cases, "pool": pool_cases,
               "mean": mean_cases, "eltwise": eltwise_cases, "activation": activation_cases, "softmax": softmax_cases,
               "convert": convert_cases, "pad": pad_cases, "qlstm": qlstm_cases, "move": move_cases, "resize": resize_cases, "reduce": reduce_cases, "tconv": tconv_cases, "f32": f32_cases, "unary": unary_cases,
-              "rows": rows_cases, "norm": norm_cases, "volume": volume_cases}
+              "rows": rows_cases, "norm": norm_cases, "volume": volume_cases, "lstm": lstm_cases}
 
 
 def run_case(case, where):

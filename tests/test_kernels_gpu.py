@@ -42,8 +42,10 @@ def test_cuda_matches_oracle(built, group, name, factory):
             else:
                 assert np.array_equal(w, g), (group, name, diff_stats(w, g))
         elif w.dtype == np.float32:
-            # libm against the device's exp / log / sin: a few units in the last place
-            assert np.allclose(w, g, rtol=1e-6, atol=1e-7), (group, name)
+            # libm against the device's exp / log / sin: a few units in the last place; an LSTM step sums dozens of
+            # such values (projection, layer norm), so its differences add up
+            rtol, atol = (2e-5, 2e-6) if group == "lstm" else (1e-6, 1e-7)
+            assert np.allclose(w, g, rtol=rtol, atol=atol), (group, name, float(np.abs(w - g).max()))
         else:
             st = diff_stats(w, g)
             # int16 cell state of the QLstm: +-2 (two chained transcendental roundings), everything else +-1

@@ -333,3 +333,19 @@ def test_gather_nd_graph_oracle_equals_armnn_cpuref(built):
     got = hostnet.OracleNetwork(Optimize(net)).run(xs)
     for k in (0, 1):
         assert want[k].shape == got[k].shape and np.array_equal(want[k], got[k]), k
+
+
+@needs_cpuref
+@pytest.mark.parametrize("sequence,time_major", [(False, False), (True, False), (True, True)])
+def test_float_lstm_graph_oracle_equals_armnn_cpuref(built, sequence, time_major):
+    """The Lstm layer and UnidirectionalSequenceLstm in both layouts: the restatement run step by step through the mirror
+    returns the real runtime's bits."""
+    import hostnet
+    from test_plugin import _lstm_net
+    net, xs = _lstm_net(sequence, time_major)
+    want = hostnet.ArmnnNetwork(net, "CpuRef").run(xs)
+    got = hostnet.OracleNetwork(Optimize(net)).run(xs)
+    # the reference's sequence workload keeps the states in buffers of its own and leaves its two state outputs unwritten
+    # (RefUnidirectionalSequenceLstmWorkload.cpp:95-123); here they receive the final states
+    for k in ((2,) if sequence else range(3)):
+        assert want[k].shape == got[k].shape and np.array_equal(want[k], got[k]), k
