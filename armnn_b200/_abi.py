@@ -85,6 +85,11 @@ class GatherParams(C.Structure):
                 ("inner", C.c_int32), ("n_indices", C.c_int32)]
 
 
+class ReverseParams(C.Structure):
+    _fields_ = [("x", QTensor), ("y", QTensor), ("axes", C.c_void_p), ("n_axes", C.c_int32), ("rank", C.c_int32),
+                ("shape", C.c_int32 * 6)]
+
+
 class GatherNdParams(C.Structure):
     _fields_ = [("x", QTensor), ("y", QTensor), ("indices", C.c_void_p), ("n_indices", C.c_int32), ("nd", C.c_int32),
                 ("inner", C.c_int32), ("dims", C.c_int32 * 8)]
@@ -208,6 +213,7 @@ KERNEL_ENTRY_POINTS = {
     "l2_normalization_q": SoftmaxParams,
     "arg_min_max_q": ArgMinMaxParams,
     "gather_q": GatherParams,
+    "reverse_q": ReverseParams,
     "gather_nd_q": GatherNdParams,
     "batch_norm_q": BatchNormParams,
     "instance_norm_q": InstanceNormParams,

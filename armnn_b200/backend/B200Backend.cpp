@@ -321,6 +321,9 @@ public:
             case LayerType::Gather:
                 if (infos[1].GetDataType() != DataType::Signed32) { return No(reason, "indices must be Signed32"); }
                 return (IsMoveType(infos[0]) && infos[2].GetDataType() == infos[0].GetDataType()) || No(reason, "unsupported or mismatched data types");
+            case LayerType::ReverseV2:
+                if (infos[1].GetDataType() != DataType::Signed32 || infos[0].GetNumDimensions() > 6) { return No(reason, "Signed32 axes and rank <= 6"); }
+                return (IsMoveType(infos[0]) && infos[2].GetDataType() == infos[0].GetDataType()) || No(reason, "unsupported or mismatched data types");
             case LayerType::GatherNd:
             {
                 if (infos[1].GetDataType() != DataType::Signed32 || infos[1].GetNumDimensions() < 1) { return No(reason, "indices must be Signed32"); }

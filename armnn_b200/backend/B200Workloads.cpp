@@ -1318,6 +1318,24 @@ std::unique_ptr<IWorkload> B200WorkloadFactory::CreateWorkload(LayerType type, c
                 B200CheckStatus(b200k_gather_q(&st->p, s));
             });
         }
+        case LayerType::ReverseV2:
+        {
+            auto st = std::make_shared<SimpleState<b200k_reverse_params>>(ctx);
+            b200k_reverse_params& p = st->p;
+            std::memset(&p, 0, sizeof(p));
+            const TensorInfo& x = info.m_InputTensorInfos[0];
+            if (x.GetNumDimensions() > 6) { throw InvalidArgumentException("B200Acc: ReverseV2 takes at most 6 dimensions"); }
+            p.x = Operand(x, st->blobs); p.y = Operand(info.m_OutputTensorInfos[0], st->blobs);
+            p.n_axes = static_cast<int32_t>(info.m_InputTensorInfos[1].GetNumElements());
+            p.rank = static_cast<int32_t>(x.GetNumDimensions());
+            for (unsigned int i = 0; i < x.GetNumDimensions(); ++i) { p.shape[i] = static_cast<int32_t>(x.GetShape()[i]); }
+            return Make<ReverseV2QueueDescriptor>(d, info, ctx, [st](const ReverseV2QueueDescriptor& data, cudaStream_t s)
+            {
+                st->p.x.data = Dev(data.m_Inputs[0]); st->p.axes = static_cast<const int32_t*>(Dev(data.m_Inputs[1]));
+                st->p.y.data = Dev(data.m_Outputs[0]);
+                B200CheckStatus(b200k_reverse_q(&st->p, s));
+            });
+        }
         case LayerType::GatherNd:
         {
             auto st = std::make_shared<SimpleState<b200k_gather_nd_params>>(ctx);

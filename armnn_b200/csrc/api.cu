@@ -118,6 +118,7 @@ extern "C" size_t b200k_sizeof_params(int which)
         case 21: return sizeof(b200k_pool3d_params);
         case 22: return sizeof(b200k_gather_nd_params);
         case 23: return sizeof(b200k_lstm_params);
+        case 24: return sizeof(b200k_reverse_params);
         default: return 0;
     }
 }

@@ -134,9 +134,67 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(const GatherRowArgs a)
     ((uint4*)a.y)[i] = v;
 }
 
+// ReverseV2 (src/backends/reference/workloads/ReverseV2Impl.cpp:14-133): the axes are a run-time tensor, so the flip flags
+// are read on the device; element i of the input goes to the position with the flagged coordinates mirrored.
+struct ReverseArgs { QView x, y; const int* axes; int n_axes, rank; int shape[6]; long long count; int same, esize; };
+
+__global__ void __launch_bounds__(256) reverse_kernel(const ReverseArgs a)
+{
+    pdl_enter();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= a.count) return;
+    unsigned flags = 0;
+    for (int k = 0; k < a.n_axes; ++k) {
+        int ax = a.axes[k];
+        if (ax < 0) ax += a.rank;
+        if (ax >= 0 && ax < a.rank) flags |= 1u << ax;
+    }
+    long long rest = i, dst = 0, stride = 1;
+    #pragma unroll
+    for (int d = 5; d >= 0; --d) {
+        if (d >= a.rank) continue;
+        long long c = rest % a.shape[d];
+        rest /= a.shape[d];
+        if (flags & (1u << d)) c = a.shape[d] - 1 - c;
+        dst += c * stride;
+        stride *= a.shape[d];
+    }
+    if (a.same) {
+        if (a.esize == 1)      ((uint8_t*)a.y.data)[dst] = ((const uint8_t*)a.x.data)[i];
+        else if (a.esize == 2) ((uint16_t*)a.y.data)[dst] = ((const uint16_t*)a.x.data)[i];
+        else                   ((uint32_t*)a.y.data)[dst] = ((const uint32_t*)a.x.data)[i];
+    } else {
+        a.y.set(dst, a.x.get(i));
+    }
+}
+
 }  // namespace b200k
 
 using namespace b200k;
+
+extern "C" int b200k_reverse_q(const b200k_reverse_params* p, void* stream)
+{
+    B200K_REQUIRE(p, B200K_E_INVALID, "reverse_q: null params");
+    B200K_REQUIRE(p->x.data && p->y.data && (p->axes || p->n_axes == 0), B200K_E_INVALID, "reverse_q: null tensor pointer");
+    B200K_REQUIRE(p->rank >= 1 && p->rank <= 6 && p->n_axes >= 0, B200K_E_UNSUPPORTED, "reverse_q: rank %d not in [1, 6]", p->rank);
+    B200K_REQUIRE(p->x.dtype >= B200K_U8 && p->x.dtype <= B200K_F32 && p->x.dtype == p->y.dtype, B200K_E_UNSUPPORTED,
+                  "reverse_q: one supported element type for input and output");
+    ReverseArgs a;
+    memset(&a, 0, sizeof(a));
+    a.x = make_view(p->x); a.y = make_view(p->y); a.axes = p->axes; a.n_axes = p->n_axes; a.rank = p->rank;
+    a.count = 1;
+    for (int d = 0; d < p->rank; ++d) {
+        B200K_REQUIRE(p->shape[d] >= 0, B200K_E_INVALID, "reverse_q: negative extent");
+        a.shape[d] = p->shape[d];
+        a.count *= p->shape[d];
+    }
+    if (a.count == 0) return B200K_OK;
+    const bool quantised = p->x.dtype == B200K_U8 || p->x.dtype == B200K_S8 || p->x.dtype == B200K_S16;
+    a.same = (!quantised || (p->x.scale == p->y.scale && p->x.zero_point == p->y.zero_point)) ? 1 : 0;
+    a.esize = elem_size(p->x.dtype);
+    launch_pdl(reverse_kernel, dim3(div_up(a.count, 256)), dim3(256), 0, (cudaStream_t)stream, a);
+    return check_launch("reverse_kernel");
+}
 
 extern "C" int b200k_gather_q(const b200k_gather_params* p, void* stream)
 {

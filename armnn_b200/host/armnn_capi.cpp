@@ -263,6 +263,12 @@ int armnnc_add_normalization(void* vn, int channel_type, unsigned norm_size, flo
     return add_layer(n, n->net->AddNormalizationLayer(d));
 }
 
+int armnnc_add_reverse_v2(void* vn)
+{
+    auto* n = static_cast<CNet*>(vn);
+    return add_layer(n, n->net->AddReverseV2Layer());
+}
+
 int armnnc_add_gather_nd(void* vn)
 {
     auto* n = static_cast<CNet*>(vn);

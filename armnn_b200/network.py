@@ -407,6 +407,10 @@ class INetwork:
         """armnn::GatherDescriptor: input 0 the tensor, input 1 the Signed32 indices."""
         return self._add(Layer("Gather", name, 2, 1, {"axis": int(axis)}))
 
+    def AddReverseV2Layer(self, name=None):
+        """armnn::INetwork::AddReverseV2Layer: input 0 the tensor, input 1 the Signed32 axes to mirror."""
+        return self._add(Layer("ReverseV2", name, 2, 1, {}))
+
     def AddGatherNdLayer(self, name=None):
         """armnn::INetwork::AddGatherNdLayer (no batch dimensions): input 0 the tensor, input 1 Signed32 index tuples
         [..., nd]."""
@@ -522,6 +526,11 @@ def IsLayerSupported(layer):
         ok = (DataType.QAsymmU8, DataType.QAsymmS8, DataType.QSymmS16, DataType.Float32, DataType.Signed32)
         if ins[0].dtype not in ok or outs[0].dtype != ins[0].dtype or ins[1].dtype != DataType.Signed32:
             return False, "Gather: one supported element type for input and output, Signed32 indices"
+        return True, ""
+    if t == "ReverseV2":
+        ok = (DataType.QAsymmU8, DataType.QAsymmS8, DataType.QSymmS16, DataType.Float32, DataType.Signed32)
+        if ins[0].dtype not in ok or outs[0].dtype != ins[0].dtype or ins[1].dtype != DataType.Signed32 or len(ins[0].shape) > 6:
+            return False, "ReverseV2: one supported element type, Signed32 axes, rank <= 6"
         return True, ""
     if t == "GatherNd":
         ok = (DataType.QAsymmU8, DataType.QAsymmS8, DataType.QSymmS16, DataType.Float32, DataType.Signed32)
@@ -1148,6 +1157,16 @@ class GraphProgram:
             raise InvalidArgumentException("Gather: output shape %s does not match input %s gathered with %s indices"
                                            % (y.info.shape, x.info.shape, idx.info.shape))
         return "gather_q", p
+
+    def _make_ReverseV2(self, layer):
+        x, axes, y = layer.inputs[0].source, layer.inputs[1].source, layer.outputs[0]
+        p = _abi.ReverseParams()
+        p.x, p.y = self._operand(x), self._operand(y)
+        p.axes, p.n_axes = self._ptr(self._dev(axes)), axes.info.GetNumElements()
+        p.rank = len(x.info.shape)
+        for i, n in enumerate(x.info.shape):
+            p.shape[i] = n
+        return "reverse_q", p
 
     def _make_GatherNd(self, layer):
         x, idx, y = layer.inputs[0].source, layer.inputs[1].source, layer.outputs[0]

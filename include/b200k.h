@@ -399,6 +399,17 @@ typedef struct {
 
 int b200k_resize_q(const b200k_resize_params* p, void* stream);
 
+/* armnn::ReverseV2 (src/backends/reference/workloads/ReverseV2Impl.cpp:14-133): y is x mirrored along every dimension
+ * listed in `axes` (device int32, n_axes entries, negative ones counted from the end; the layer's second input). */
+typedef struct {
+    b200k_qtensor x, y;
+    const int32_t* axes;
+    int32_t n_axes, rank;
+    int32_t shape[6];
+} b200k_reverse_params;
+
+int b200k_reverse_q(const b200k_reverse_params* p, void* stream);
+
 /* armnn::Gather (src/backends/reference/workloads/Gather.cpp:16-94): with x seen as [outer, axis_size, inner],
  *     y[o, j, k] = Q_y(deq_x(x[o, indices[j], k]))        0 <= j < n_indices
  * indices: device int32 (Signed32 tensor), a negative one counts from the end of the axis.  The reference throws on an
@@ -608,7 +619,7 @@ unsigned long long b200k_kernel_launches(void);
 
 /* sizeof() of a parameter struct as compiled into the library, for bindings in other languages to check their
  * own declarations: 0 conv2d, 1 fc, 2 bmm, 3 pool2d, 4 mean, 5 eltwise, 6 activation, 7 softmax, 8 convert,
- * 9 qlstm, 10 pad, 11 view_copy, 12 resize, 13 reduce, 14 unary, 15 arg_min_max, 16 gather, 17 batch_norm, 18 instance_norm, 19 normalization, 20 conv3d, 21 pool3d, 22 gather_nd, 23 lstm.  No counterpart in the reference (its backends are linked as C++). */
+ * 9 qlstm, 10 pad, 11 view_copy, 12 resize, 13 reduce, 14 unary, 15 arg_min_max, 16 gather, 17 batch_norm, 18 instance_norm, 19 normalization, 20 conv3d, 21 pool3d, 22 gather_nd, 23 lstm, 24 reverse.  No counterpart in the reference (its backends are linked as C++). */
 size_t b200k_sizeof_params(int which);
 
 #ifdef __cplusplus

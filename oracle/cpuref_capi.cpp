@@ -388,6 +388,24 @@ extern "C" int cpuref_gather_q(const b200k_gather_params* p)
     });
 }
 
+extern "C" int cpuref_reverse_q(const b200k_reverse_params* p)
+{
+    return guarded([&] {
+        Harness h;
+        unsigned dims[6];
+        for (int d = 0; d < p->rank; ++d) dims[d] = (unsigned)p->shape[d];
+        TensorInfo xi = make_info(p->x, TensorShape((unsigned)p->rank, dims), 0, 0, false);
+        TensorInfo ai(TensorShape({(unsigned)p->n_axes}), DataType::Signed32);
+        TensorInfo yi = make_info(p->y, TensorShape((unsigned)p->rank, dims), 0, 0, false);
+        ReverseV2QueueDescriptor d;
+        h.in(d, xi, p->x.data);
+        h.in(d, ai, p->axes);
+        auto* o = h.out(d, yi);
+        h.run(LayerType::ReverseV2, d);
+        copy_out(o, const_cast<void*>(p->y.data), yi.GetNumBytes());
+    });
+}
+
 extern "C" int cpuref_gather_nd_q(const b200k_gather_nd_params* p)
 {
     return guarded([&] {

@@ -685,6 +685,33 @@ int oracle_gather_q(const b200k_gather_params* p)
     return 0;
 }
 
+/* ---- ReverseV2, ReverseV2Impl.cpp:14-133 --------------------------------------------------------------- */
+
+int oracle_reverse_q(const b200k_reverse_params* p)
+{
+    if (!p->x.data || !p->y.data || p->rank < 1 || p->rank > 6) return B200K_E_INVALID;
+    int flag[6] = {0, 0, 0, 0, 0, 0};
+    for (int k = 0; k < p->n_axes; ++k) {
+        int ax = p->axes[k];
+        if (ax < 0) ax += p->rank;
+        if (ax >= 0 && ax < p->rank) flag[ax] = 1;
+    }
+    int64_t count = 1;
+    for (int d = 0; d < p->rank; ++d) count *= p->shape[d];
+    for (int64_t i = 0; i < count; ++i) {
+        int64_t rest = i, dst = 0, stride = 1;
+        for (int d = p->rank - 1; d >= 0; --d) {
+            int64_t c = rest % p->shape[d];
+            rest /= p->shape[d];
+            if (flag[d]) c = p->shape[d] - 1 - c;
+            dst += c * stride;
+            stride *= p->shape[d];
+        }
+        store_f(&p->y, dst, load_f(&p->x, i));
+    }
+    return 0;
+}
+
 /* ---- GatherNd without batch dimensions, RefGatherNdWorkload.cpp:20-92 ------------------------------ */
 
 int oracle_gather_nd_q(const b200k_gather_nd_params* p)

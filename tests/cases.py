@@ -503,7 +503,26 @@ def norm_cases():
                 p.dims[i] = n
             return p, [y]
         return lambda: SimpleCase("gather_nd_q", build)
+    def reverse(seed, shape, axes, dtype=S8, requant=False):
+        def build(mem):
+            rng = np.random.default_rng(seed)
+            p = _abi.ReverseParams()
+            xq = (0.05, -3) if dtype != F32 else (1.0, 0)
+            if dtype == F32:
+                p.x = qt(mem, rng.standard_normal(shape).astype(np.float32), F32)
+            else:
+                p.x = qt(mem, _rand(rng, dtype, shape), dtype, *xq)
+            p.y, y = qt_out(mem, shape, dtype, *((0.07, 5) if requant else xq))
+            p.axes = mem.inp(np.array(axes, np.int32))
+            p.n_axes, p.rank = len(axes), len(shape)
+            for i, n in enumerate(shape):
+                p.shape[i] = n
+            return p, [y]
+        return lambda: SimpleCase("reverse_q", build)
     return {
+        "reverse_width_and_batch": reverse(341, (2, 5, 7, 8), (2, 0)),
+        "reverse_negative_axis_u8_requantise": reverse(342, (4, 6, 5), (-1,), dtype=U8, requant=True),
+        "reverse_all_axes_float": reverse(343, (3, 4, 5), (0, 1, 2), dtype=F32),
         "gather_nd_pixels": gather_nd(338, (2, 7, 9), 16, 40),
         "gather_nd_u8_requantise": gather_nd(339, (5, 4), 3, 11, dtype=U8, requant=True),
         "gather_nd_float_rank1_tuples": gather_nd(340, (30,), 5, 12, dtype=F32),

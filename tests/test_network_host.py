@@ -349,3 +349,14 @@ def test_float_lstm_graph_oracle_equals_armnn_cpuref(built, sequence, time_major
     # (RefUnidirectionalSequenceLstmWorkload.cpp:95-123); here they receive the final states
     for k in ((2,) if sequence else range(3)):
         assert want[k].shape == got[k].shape and np.array_equal(want[k], got[k]), k
+
+
+@needs_cpuref
+def test_reverse_v2_graph_oracle_equals_armnn_cpuref(built):
+    import hostnet
+    from test_plugin import _reverse_net
+    net = _reverse_net()
+    xs = {0: np.random.default_rng(98).integers(-128, 128, size=(2, 5, 6, 8)).astype(np.int8), 1: np.array([2, -3], np.int32)}
+    want = hostnet.ArmnnNetwork(net, "CpuRef").run(xs)[0]
+    got = hostnet.OracleNetwork(Optimize(net)).run(xs)[0]
+    assert np.array_equal(want, xs[0][:, ::-1, ::-1, :]) and np.array_equal(want, got)

@@ -1338,3 +1338,28 @@ def test_float_lstm_through_the_runtime_matches_cpuref(sequence, time_major):
     for k in ((2,) if sequence else range(3)):
         # expf / tanhf of the device against glibc, carried through the recurrence
         assert ref[k].shape == got[k].shape and np.allclose(ref[k], got[k], rtol=2e-5, atol=2e-6), (k, np.abs(ref[k] - got[k]).max())
+
+
+def _reverse_net():
+    from armnn_b200.network import DataType, INetwork, TensorInfo
+    net = INetwork.Create()
+    il = net.AddInputLayer(0, "input")
+    il.GetOutputSlot(0).SetTensorInfo(TensorInfo((2, 5, 6, 8), DataType.QAsymmS8, 0.05, -3))
+    ax = net.AddInputLayer(1, "axes")
+    ax.GetOutputSlot(0).SetTensorInfo(TensorInfo((2,), DataType.Signed32))
+    rv = net.AddReverseV2Layer("reverse")
+    il.GetOutputSlot(0).Connect(rv.GetInputSlot(0)); ax.GetOutputSlot(0).Connect(rv.GetInputSlot(1))
+    rv.GetOutputSlot(0).SetTensorInfo(TensorInfo((2, 5, 6, 8), DataType.QAsymmS8, 0.05, -3))
+    ol = net.AddOutputLayer(0, "out")
+    rv.GetOutputSlot(0).Connect(ol.GetInputSlot(0))
+    return net
+
+
+@needs_plugin
+@pytest.mark.gpu
+def test_reverse_v2_through_the_runtime_equals_cpuref():
+    net = _reverse_net()
+    xs = {0: np.random.default_rng(97).integers(-128, 128, size=(2, 5, 6, 8)).astype(np.int8), 1: np.array([2, -3], np.int32)}
+    ref = hostnet.ArmnnNetwork(net, "CpuRef").run(xs)[0]
+    got = hostnet.ArmnnNetwork(net, "B200Acc").run(xs)[0]
+    assert np.array_equal(ref, xs[0][:, ::-1, ::-1, :]) and np.array_equal(ref, got)
