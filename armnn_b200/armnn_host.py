@@ -205,6 +205,10 @@ class ArmnnNetwork:
                 lid = lib.armnnc_add_pad(net, len(d["pads"]), (C.c_int32 * len(flat))(*flat), C.c_float(d["value"]), int(d.get("mode", 0)))
             elif t in ("Shape", "Rank"):
                 lid = lib.armnnc_add_shape(net, int(t == "Rank"))
+            elif t == "FakeQuantization":
+                # armnn::INetwork has no AddFakeQuantizationLayer (the layer only enters a graph through the optimizer's
+                # internals), so the bridge cannot state it
+                raise NotImplementedError("ArmnnNetwork: FakeQuantization cannot be added through armnn::INetwork")
             elif t == "Cast":
                 lid = lib.armnnc_add_cast(net)
             elif t == "Fill":

@@ -305,6 +305,12 @@ public:
             case LayerType::Shape:
             case LayerType::Rank:
                 return infos[1].GetDataType() == DataType::Signed32 || No(reason, "the output must be Signed32");
+            case LayerType::FakeQuantization:
+            {
+                const auto& d = *PolymorphicDowncast<const FakeQuantizationDescriptor*>(&descriptor);
+                if (!(d.m_Max > d.m_Min)) { return No(reason, "min must be below max"); }
+                return (infos[0].GetDataType() == DataType::Float32 && infos[1].GetDataType() == DataType::Float32) || No(reason, "Float32 only");
+            }
             case LayerType::Cast:
                 return (IsMoveType(infos[0]) && IsMoveType(infos[1]) && infos[0].GetNumElements() == infos[1].GetNumElements()) ||
                        No(reason, "unsupported data type or mismatched sizes");

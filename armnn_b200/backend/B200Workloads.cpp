@@ -1523,6 +1523,20 @@ std::unique_ptr<IWorkload> B200WorkloadFactory::CreateWorkload(LayerType type, c
             if (type == LayerType::Shape) { return MakeViews<ShapeQueueDescriptor>(d, info, ctx, st); }
             return MakeViews<RankQueueDescriptor>(d, info, ctx, st);
         }
+        case LayerType::FakeQuantization:
+        {
+            const auto& prm = PolymorphicDowncast<const FakeQuantizationQueueDescriptor*>(&d)->m_Parameters;
+            auto st = std::make_shared<SimpleState<b200k_activation_params>>(ctx);
+            std::memset(&st->p, 0, sizeof(st->p));
+            st->p.x = Operand(info.m_InputTensorInfos[0], st->blobs); st->p.y = Operand(info.m_OutputTensorInfos[0], st->blobs);
+            st->p.count = info.m_InputTensorInfos[0].GetNumElements();
+            st->p.function = B200K_ACTIVATION_FAKE_QUANTIZATION; st->p.a = prm.m_Min; st->p.b = prm.m_Max;
+            return Make<FakeQuantizationQueueDescriptor>(d, info, ctx, [st](const FakeQuantizationQueueDescriptor& data, cudaStream_t s)
+            {
+                st->p.x.data = Dev(data.m_Inputs[0]); st->p.y.data = Dev(data.m_Outputs[0]);
+                B200CheckStatus(b200k_activation_q8(&st->p, s));
+            });
+        }
         case LayerType::Cast:
         {
             auto st = std::make_shared<SimpleState<b200k_convert_params>>(ctx);

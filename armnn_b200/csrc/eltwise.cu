@@ -91,6 +91,13 @@ __device__ __forceinline__ float activation_f(int fn, float in, float a, float b
         case 9:  return __fmul_rn(in, in);
         case 10: return (in >= 0) ? in : __fmul_rn(a, __fsub_rn(expf(in), 1.f));
         case 12: return __fmul_rn(in, __fmul_rn(0.5f, __fadd_rn(1.0f, erff((float)((double)in / 1.4142135623730951)))));
+        // FakeQuantization (RefFakeQuantizationFloat32Workload.cpp:15-27): a = min, b = max; the value as an 8-bit code
+        case 50: {
+            const float range = __fsub_rn(b, a);
+            const float scale = __fdiv_rn(range, 255.f);
+            const int offset = (int)__fdiv_rn(__fmul_rn(-a, 255.f), range);
+            return (float)quantize_dev(in, scale, offset, 0.f, 255.f);
+        }
         // armnn::UnaryOperation + 100 (ElementwiseUnary): Abs, Exp, Sqrt, Rsqrt, Neg, -, Log, Sin, Ceil; 109: the Floor layer
         case 100: return fabsf(in);
         case 101: return expf(in);
@@ -188,7 +195,10 @@ static int launch_unary(const b200k_qtensor& x, const b200k_qtensor& y, long lon
 extern "C" int b200k_activation_q8(const b200k_activation_params* p, void* stream)
 {
     B200K_REQUIRE(p, B200K_E_INVALID, "activation_q8: null params");
-    B200K_REQUIRE(p->function >= 0 && p->function <= 12, B200K_E_UNSUPPORTED, "activation_q8: unsupported activation function %d", p->function);
+    B200K_REQUIRE((p->function >= 0 && p->function <= 12) || p->function == B200K_ACTIVATION_FAKE_QUANTIZATION, B200K_E_UNSUPPORTED,
+                  "activation_q8: unsupported activation function %d", p->function);
+    B200K_REQUIRE(p->function != B200K_ACTIVATION_FAKE_QUANTIZATION || (p->x.dtype == B200K_F32 && p->y.dtype == B200K_F32 && p->b > p->a),
+                  B200K_E_INVALID, "activation_q8: FakeQuantization takes Float32 tensors and min < max");
     return launch_unary(p->x, p->y, p->count, p->function, p->a, p->b, stream, "activation_q8");
 }
 

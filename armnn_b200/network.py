@@ -301,6 +301,10 @@ class INetwork:
         """armnn::RankLayer: the input's number of dimensions as one Signed32 element."""
         return self._add(Layer("Rank", name, 1, 1, {}))
 
+    def AddFakeQuantizationLayer(self, minimum, maximum, name=None):
+        """armnn::FakeQuantizationDescriptor (Float32 tensors): every value becomes its 8-bit code over [min, max]."""
+        return self._add(Layer("FakeQuantization", name, 1, 1, {"min": float(minimum), "max": float(maximum)}))
+
     def AddCastLayer(self, name=None):
         return self._add(Layer("Cast", name, 1, 1, {}))
 
@@ -596,6 +600,10 @@ def IsLayerSupported(layer):
         want = len(ins[0].shape) if t == "Shape" else 1
         if outs[0].dtype != DataType.Signed32 or outs[0].GetNumElements() != want:
             return False, "%s: the output must hold %d Signed32 element(s)" % (t, want)
+        return True, ""
+    if t == "FakeQuantization":
+        if ins[0].dtype != DataType.Float32 or outs[0].dtype != DataType.Float32 or not layer.desc["max"] > layer.desc["min"]:
+            return False, "FakeQuantization: Float32 tensors and min < max"
         return True, ""
     if t == "Cast":
         ok = (DataType.QAsymmU8, DataType.QAsymmS8, DataType.QSymmS8, DataType.QSymmS16, DataType.Signed32, DataType.Float32)
@@ -1262,6 +1270,13 @@ class GraphProgram:
         return name, p
 
     _make_Rank = _make_Shape
+
+    def _make_FakeQuantization(self, layer):
+        x, y = layer.inputs[0].source, layer.outputs[0]
+        p = _abi.ActivationParams()
+        p.x, p.y = self._operand(x), self._operand(y)
+        p.count, p.function, p.a, p.b = x.info.GetNumElements(), 50, layer.desc["min"], layer.desc["max"]
+        return "activation_q8", p
 
     def _make_Cast(self, layer):
         x, y = layer.inputs[0].source, layer.outputs[0]

@@ -274,7 +274,10 @@ int b200k_eltwise_q8(const b200k_eltwise_params* p, void* stream);
 /* armnn::Activation (src/backends/reference/workloads/Activation.cpp:13-119).
  * function follows armnn::ActivationFunction numbering (include/armnn/Types.hpp):
  * 0 Sigmoid, 1 TanH, 2 Linear, 3 ReLu, 4 BoundedReLu, 5 SoftReLu, 6 LeakyReLu, 7 Abs, 8 Sqrt,
- * 9 Square, 10 Elu, 11 HardSwish, 12 Gelu (x / 2 * (1 + erf(x / sqrt(2))), the quotient in double precision). */
+ * 9 Square, 10 Elu, 11 HardSwish, 12 Gelu (x / 2 * (1 + erf(x / sqrt(2))), the quotient in double precision).
+ * B200K_ACTIVATION_FAKE_QUANTIZATION is the FakeQuantization layer (RefFakeQuantizationFloat32Workload.cpp:15-27), Float32
+ * only: a = min, b = max; y = float(Quantize<uint8>(x, (max - min) / 255, int(-min * 255 / (max - min)))). */
+#define B200K_ACTIVATION_FAKE_QUANTIZATION 50
 typedef struct {
     b200k_qtensor x, y;
     int64_t count;

@@ -360,6 +360,19 @@ extern "C" int cpuref_activation_q8(const b200k_activation_params* p)
         Harness h;
         TensorInfo xi = make_info(p->x, TensorShape({(unsigned)p->count}), 0, 0, false);
         TensorInfo yi = make_info(p->y, TensorShape({(unsigned)p->count}), 0, 0, false);
+        if (p->function == B200K_ACTIVATION_FAKE_QUANTIZATION)
+        {
+            FakeQuantizationQueueDescriptor fq;
+            fq.m_Parameters.m_Min = p->a; fq.m_Parameters.m_Max = p->b;
+            // the queue descriptor's Validate wants two dimensions
+            TensorInfo x2 = make_info(p->x, TensorShape({1u, (unsigned)p->count}), 0, 0, false);
+            TensorInfo y2 = make_info(p->y, TensorShape({1u, (unsigned)p->count}), 0, 0, false);
+            h.in(fq, x2, p->x.data);
+            auto* fo = h.out(fq, y2);
+            h.run(LayerType::FakeQuantization, fq);
+            copy_out(fo, const_cast<void*>(p->y.data), yi.GetNumBytes());
+            return;
+        }
         ActivationQueueDescriptor d;
         d.m_Parameters.m_Function = static_cast<ActivationFunction>(p->function);
         d.m_Parameters.m_A = p->a;

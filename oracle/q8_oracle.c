@@ -524,6 +524,13 @@ static float activation_f(float in, int fn, float a, float b)
         case 11: { volatile float t = in + 3; float r = t > 0.0f ? t : 0.0f; r = r < 6.0f ? r : 6.0f;
                    volatile float m = in * r; return m / 6; }
         case 12: return in * (0.5f * (1.0f + erff((float)(in / sqrt(2.0)))));          /* Activation.cpp:85-91 */
+        case B200K_ACTIVATION_FAKE_QUANTIZATION: {                  /* RefFakeQuantizationFloat32Workload.cpp:15-27 */
+            volatile float range = b - a;
+            const float scale = range / 255.f;
+            volatile float num = -a * 255.f;
+            const int32_t offset = (int32_t)(num / range);
+            return (float)quantize_f(in, scale, offset, B200K_U8);
+        }
         default: return NAN;
     }
 }
@@ -554,7 +561,7 @@ int oracle_unary_q(const b200k_unary_params* p)
 
 int oracle_activation_q8(const b200k_activation_params* p)
 {
-    if (!p->x.data || !p->y.data || p->function < 0 || p->function > 12) return B200K_E_INVALID;
+    if (!p->x.data || !p->y.data || p->function < 0 || (p->function > 12 && p->function != B200K_ACTIVATION_FAKE_QUANTIZATION)) return B200K_E_INVALID;
     for (int64_t i = 0; i < p->count; ++i)
         store_f(&p->y, i, activation_f(load_f(&p->x, i), p->function, p->a, p->b));
     return 0;

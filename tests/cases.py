@@ -304,6 +304,15 @@ def activation_cases():
             p.count, p.function, p.a, p.b = count, fn, a, b
             return p, [y]
         return lambda: SimpleCase("activation_q8", build)
+
+    def make_fake(seed, lo, hi, count=777):
+        def build(mem):
+            p = _abi.ActivationParams()
+            p.x = qt(mem, (np.random.default_rng(seed).standard_normal(count) * 3).astype(np.float32), F32)
+            p.y, y = qt_out(mem, (count,), F32)
+            p.count, p.function, p.a, p.b = count, 50, lo, hi
+            return p, [y]
+        return lambda: SimpleCase("activation_q8", build)
     return {
         "relu": make(81, 3, 0, 0), "bounded_relu6": make(82, 4, 6.0, 0.0, out_q=(0.03, -128)),
         "sigmoid_u8": make(83, 0, 0, 0, dtype=U8, in_q=(0.05, 128), out_q=(1 / 256., 0)),
@@ -311,6 +320,7 @@ def activation_cases():
         "leaky_relu": make(86, 6, 0.1, 0), "abs": make(87, 7, 0, 0), "square": make(88, 9, 0, 0, out_q=(0.3, -128)),
         "hard_swish": make(89, 11, 0, 0, count=1003), "sqrt_u8": make(90, 8, 0, 0, dtype=U8, in_q=(0.05, 0), out_q=(0.02, 0)),
         "elu": make(91, 10, 1.0, 0), "soft_relu": make(92, 5, 0, 0),
+        "fake_quantization_float": make_fake(95, -3.0, 5.0), "fake_quantization_float_narrow": make_fake(96, -0.5, 0.25),
         "gelu": make(93, 12, 0, 0, in_q=(0.04, 0), out_q=(0.04, 0)), "gelu_u8": make(94, 12, 0, 0, dtype=U8, in_q=(0.03, 128), out_q=(0.016, 11)),
     }
 

@@ -360,3 +360,24 @@ def test_reverse_v2_graph_oracle_equals_armnn_cpuref(built):
     want = hostnet.ArmnnNetwork(net, "CpuRef").run(xs)[0]
     got = hostnet.OracleNetwork(Optimize(net)).run(xs)[0]
     assert np.array_equal(want, xs[0][:, ::-1, ::-1, :]) and np.array_equal(want, got)
+
+
+def test_fake_quantization_in_the_mirror_matches_the_formula(built):
+    """armnn::INetwork cannot state a FakeQuantization layer, so the runtime bridge cannot either: the mirror's layer runs
+    on the restatement (itself checked against the real RefFakeQuantizationFloat32Workload) and against the formula."""
+    import hostnet
+    from armnn_b200.network import DataType, INetwork, TensorInfo
+    net = INetwork.Create()
+    il = net.AddInputLayer(0, "input")
+    il.GetOutputSlot(0).SetTensorInfo(TensorInfo((3, 50), DataType.Float32))
+    fq = net.AddFakeQuantizationLayer(-2.0, 6.0, "fake_quantization")
+    il.GetOutputSlot(0).Connect(fq.GetInputSlot(0))
+    fq.GetOutputSlot(0).SetTensorInfo(TensorInfo((3, 50), DataType.Float32))
+    ol = net.AddOutputLayer(0, "out")
+    fq.GetOutputSlot(0).Connect(ol.GetInputSlot(0))
+    x = (np.random.default_rng(101).standard_normal((3, 50)) * 4).astype(np.float32)
+    got = hostnet.OracleNetwork(Optimize(net)).run({0: x})[0]
+    scale, offset = np.float32(8.0) / np.float32(255.0), int(np.float32(2.0 * 255.0) / np.float32(8.0))
+    q = x / scale
+    want = np.clip(np.where(q >= 0, np.floor(q + np.float32(0.5)), np.ceil(q - np.float32(0.5))) + offset, 0, 255).astype(np.float32)
+    assert np.array_equal(got, want)
