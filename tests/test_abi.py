@@ -51,3 +51,57 @@ def test_no_device_is_an_error_code_not_a_crash():
     if l.b200k_device_count() == 0:
         assert l.b200k_device_open(0) == _abi.E_NODEVICE
         assert b"no CUDA device" in l.b200k_last_error()
+
+
+def _refused(l, name, params, code, text):
+    rc = getattr(l, "b200k_" + name)(ctypes.byref(params), None)
+    assert rc == code, (name, rc, l.b200k_last_error())
+    assert text in l.b200k_last_error(), (name, l.b200k_last_error())
+
+
+def test_malformed_parameters_are_refused_before_any_launch():
+    """Argument checks of the layer entry points run on the host: they return an error code and a message, with or
+    without a device."""
+    l = lib.load_library()
+    buf = (ctypes.c_uint8 * 4096)()
+    ptr = ctypes.addressof(buf)
+
+    def tensor(dtype=_abi.S8, scale=0.05):
+        t = _abi.QTensor()
+        t.data, t.dtype, t.scale, t.zero_point = ptr, dtype, scale, 0
+        return t
+    p = _abi.ViewCopyParams(); p.x, p.y, p.rank = tensor(), tensor(), 7
+    _refused(l, "view_copy_q", p, _abi.E_UNSUPPORTED, b"rank 7")
+    p = _abi.ViewCopyParams(); p.x, p.y, p.rank = tensor(_abi.S8), tensor(_abi.U8), 1
+    _refused(l, "view_copy_q", p, _abi.E_UNSUPPORTED, b"types differ")
+    p = _abi.EltwiseParams(); p.a, p.b, p.out, p.rank, p.op = tensor(), tensor(), tensor(), 1, 9
+    _refused(l, "eltwise_q8", p, _abi.E_UNSUPPORTED, b"unsupported binary operation")
+    p = _abi.UnaryParams(); p.x, p.y, p.count, p.operation = tensor(), tensor(), 4, 10
+    _refused(l, "unary_q", p, _abi.E_UNSUPPORTED, b"unsupported unary operation")
+    p = _abi.ActivationParams(); p.x, p.y, p.count, p.function, p.a, p.b = tensor(), tensor(), 4, 50, 0.0, 1.0
+    _refused(l, "activation_q8", p, _abi.E_INVALID, b"FakeQuantization takes Float32")
+    p = _abi.PadParams(); p.x, p.y, p.rank, p.mode = tensor(), tensor(), 1, 1
+    p.shape[0], p.pad_before[0], p.pad_after[0] = 4, 4, 0
+    _refused(l, "pad_q", p, _abi.E_INVALID, b"mirrored padding wider")
+    p = _abi.ArgMinMaxParams(); p.x, p.y, p.outer, p.axis_size, p.inner, p.function = tensor(), ptr, 1, 4, 1, 2
+    _refused(l, "arg_min_max_q", p, _abi.E_INVALID, b"neither Min")
+    p = _abi.GatherNdParams(); p.x, p.y, p.indices, p.n_indices, p.nd, p.inner = tensor(), tensor(), ptr, 1, 9, 1
+    _refused(l, "gather_nd_q", p, _abi.E_INVALID, b"bad shape")
+    p = _abi.InstanceNormParams(); p.x, p.y, p.n, p.c, p.hw = tensor(), tensor(), 1, 1, 4
+    _refused(l, "instance_norm_q", p, _abi.E_UNSUPPORTED, b"Float32 tensors only")
+    p = _abi.NormalizationParams(); p.x, p.y, p.n, p.c, p.h, p.w, p.channel_type, p.norm_size = tensor(), tensor(), 1, 2, 2, 2, 1, 3
+    _refused(l, "normalization_q", p, _abi.E_UNSUPPORTED, b"Within indexes the tensor as NCHW")
+    p = _abi.Conv3dParams(); p.x, p.w, p.y = tensor(_abi.F32), tensor(_abi.S8), tensor(_abi.F32)
+    for k in ("n", "d", "h", "wd", "c", "od", "oh", "ow", "oc", "kd", "kh", "kw", "stride_d", "stride_h", "stride_w", "dil_d", "dil_h", "dil_w"):
+        setattr(p, k, 1)
+    _refused(l, "conv3d_q", p, _abi.E_UNSUPPORTED, b"Float32 input needs Float32 weights")
+    p = _abi.LstmParams(); p.batch, p.input_size, p.num_units, p.output_size = 1, 2, 4, 3
+    for k in ("input", "output_state_in", "cell_state_in", "output_state_out", "cell_state_out", "output",
+              "w_i2f", "w_i2c", "w_i2o", "w_r2f", "w_r2c", "w_r2o", "b_f", "b_c", "b_o"):
+        setattr(p, k, ptr)
+    p.activation = 4
+    _refused(l, "lstm_step_f32", p, _abi.E_INVALID, b"without projection the output size")
+    p.output_size, p.activation = 4, 2
+    _refused(l, "lstm_step_f32", p, _abi.E_UNSUPPORTED, b"unsupported activation function")
+    p = _abi.ReverseParams(); p.x, p.y, p.axes, p.rank = tensor(), tensor(_abi.U8), ptr, 2
+    _refused(l, "reverse_q", p, _abi.E_UNSUPPORTED, b"one supported element type")
