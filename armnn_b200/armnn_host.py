@@ -145,14 +145,14 @@ class ArmnnNetwork:
             if t in ("Convolution2d", "DepthwiseConvolution2d"):
                 lid = lib.armnnc_add_conv2d(net, int(t == "DepthwiseConvolution2d"), d["stride"][0], d["stride"][1],
                                             d["pad"][0], d["pad"][1], d["pad"][2], d["pad"][3], d["dilation"][0],
-                                            d["dilation"][1], int(d["bias"]))
+                                            d["dilation"][1], int(d["bias"]), int(d.get("nchw", False)))
             elif t == "FullyConnected":
                 lid = lib.armnnc_add_fully_connected(net, int(d["transpose"]), int(d["bias"]))
             elif t == "Activation":
                 lid = lib.armnnc_add_activation(net, int(d["function"]), C.c_float(d["a"]), C.c_float(d["b"]))
             elif t == "Pooling2d":
                 lid = lib.armnnc_add_pool2d(net, int(d["type"]), int(d["method"]), d["pool"][0], d["pool"][1], d["stride"][0],
-                                            d["stride"][1], d["pad"][0], d["pad"][1], d["pad"][2], d["pad"][3])
+                                            d["stride"][1], d["pad"][0], d["pad"][1], d["pad"][2], d["pad"][3], int(d.get("nchw", False)))
             elif t == "Convolution3d":
                 lid = lib.armnnc_add_conv3d(net, (C.c_int32 * 3)(*d["stride"]), (C.c_int32 * 6)(*d["pad"]), (C.c_int32 * 3)(*d["dilation"]),
                                             int(d["bias"]))

@@ -97,7 +97,9 @@ public:
                 const DataLayout layout = type == LayerType::Convolution2d
                     ? PolymorphicDowncast<const Convolution2dDescriptor*>(&descriptor)->m_DataLayout
                     : PolymorphicDowncast<const DepthwiseConvolution2dDescriptor*>(&descriptor)->m_DataLayout;
-                if (layout != DataLayout::NHWC) { return No(reason, "only NHWC is supported"); }
+                // NCHW layers run through a re-layout around the NHWC kernels (B200Workloads.cpp: MakeConv); their per-axis
+                // weights are quantised along dimension 0 ([O, I, H, W]) like the NHWC ones ([O, H, W, I])
+                if (layout != DataLayout::NHWC && layout != DataLayout::NCHW) { return No(reason, "NHWC or NCHW only"); }
                 if (!infos[2].IsConstant()) { return No(reason, "non-constant weights are not supported"); }
                 if (AllFloat32(infos)) { return true; }                 // the fp32 variant (b200k_conv2d_f32 / b200k_dwconv2d_f32)
                 if (!Is8Bit(infos[0]) || !Is8Bit(infos[1]) || !Is8Bit(infos[2])) { return No(reason, "input, output and weights must be 8-bit quantised or all Float32"); }
@@ -128,7 +130,6 @@ public:
                 return true;
             }
             case LayerType::Pooling2d:
-                if (PolymorphicDowncast<const Pooling2dDescriptor*>(&descriptor)->m_DataLayout != DataLayout::NHWC) { return No(reason, "only NHWC is supported"); }
                 return (IsActType(infos[0]) && IsActType(infos[1])) || No(reason, "unsupported data type");
             case LayerType::Pad:
             {

@@ -675,37 +675,103 @@ void LaunchConv(ConvState& st, cudaStream_t s)
     B200CheckStatus(b200k_conv2d_q8(&q, s));
 }
 
+// NCHW tensors around the NHWC kernels: a layer that arrives in NCHW (the ONNX and Caffe conventions) runs as
+// re-layout -> NHWC kernel -> re-layout, through scratch tensors the workload owns.  The re-layouts are view copies between
+// tensors of one quantisation: the bytes move as they are.
+TensorInfo NhwcOf(const TensorInfo& nchw)
+{
+    TensorInfo t = nchw;
+    const TensorShape& s = nchw.GetShape();
+    t.SetShape(TensorShape({s[0], s[2], s[3], s[1]}));
+    return t;
+}
+
+/// Copy of a 4-D tensor [d0, d1, d2, d3] into the order `order` of its dimensions (destination dense).
+b200k_view_copy_params Relayout(const TensorInfo& src, const unsigned int (&order)[4], DeviceBlobs& blobs)
+{
+    b200k_view_copy_params v;
+    std::memset(&v, 0, sizeof(v));
+    v.x = Operand(src, blobs); v.y = v.x;
+    v.rank = 4;
+    int64_t ss[6];
+    DenseStrides(src.GetShape(), ss);
+    int64_t dst = 1;
+    for (int k = 3; k >= 0; --k)
+    {
+        v.shape[k] = static_cast<int32_t>(src.GetShape()[order[k]]);
+        v.src_strides[k] = ss[order[k]];
+        v.dst_strides[k] = dst;
+        dst *= v.shape[k];
+    }
+    return v;
+}
+
+constexpr unsigned int kNchwToNhwc[4] = {0, 2, 3, 1};
+constexpr unsigned int kNhwcToNchw[4] = {0, 3, 1, 2};
+
+struct LayoutState
+{
+    b200k_view_copy_params in, out, weights;      // NCHW -> NHWC input, NHWC -> NCHW output, OIHW -> OHWI weights
+    void* x = nullptr; void* y = nullptr; void* w = nullptr;
+};
+
 template <typename QD>
 std::unique_ptr<IWorkload> MakeConv(const QueueDescriptor& d, const WorkloadInfo& info, const ContextPtr& ctx, bool depthwise)
 {
     const QD& qd = *PolymorphicDowncast<const QD*>(&d);
     auto st = std::make_shared<ConvState>(ctx);
-    const TensorInfo& y = info.m_OutputTensorInfos[0];
-    FillConv(*st, qd.m_Parameters, info.m_InputTensorInfos[0], info.m_InputTensorInfos[1],
-             info.m_InputTensorInfos.size() > 2 ? &info.m_InputTensorInfos[2] : nullptr, y, depthwise);
-    if (y.GetDataType() == DataType::Float32)
+    const bool nchw = qd.m_Parameters.m_DataLayout == DataLayout::NCHW;
+    auto lay = std::make_shared<LayoutState>();
+    auto prm = qd.m_Parameters;
+    prm.m_DataLayout = DataLayout::NHWC;
+    TensorInfo xi = info.m_InputTensorInfos[0], wi = info.m_InputTensorInfos[1], yi = info.m_OutputTensorInfos[0];
+    if (nchw)
     {
-        // the fp32 variant (activations are never fused into it: B200Backend::OptimizeSubgraphView)
-        return Make<QD>(d, info, ctx, [st, depthwise](const QD& data, cudaStream_t s)
+        lay->in = Relayout(xi, kNchwToNhwc, st->blobs);
+        lay->x = st->blobs.Alloc(xi.GetNumBytes());
+        xi = NhwcOf(xi);
+        const TensorInfo yNhwc = NhwcOf(yi);
+        lay->out = Relayout(yNhwc, kNhwcToNchw, st->blobs);
+        lay->y = st->blobs.Alloc(yi.GetNumBytes());
+        yi = yNhwc;
+        if (!depthwise)
         {
-            b200k_conv2d_params& q = st->p;
-            q.x.data = Dev(data.m_Inputs[0]);
-            q.w.data = Dev(data.m_Inputs[1]);
-            if (q.bias.dtype == B200K_F32 && data.m_Inputs.size() > 2) { q.bias.data = Dev(data.m_Inputs[2]); }
-            q.y.data = Dev(data.m_Outputs[0]);
-            B200CheckStatus(depthwise ? b200k_dwconv2d_f32(&q, s) : b200k_conv2d_f32(&q, s));
-        });
+            // Convolution2d weights are [O, I, H, W] in an NCHW layer; the depthwise ones are [1, H, W, I * M] in both layouts
+            lay->weights = Relayout(wi, kNchwToNhwc, st->blobs);
+            lay->w = st->blobs.Alloc(wi.GetNumBytes());
+            wi = NhwcOf(wi);
+        }
     }
-    Clamp(qd.template GetAdditionalInformation<ActivationDescriptor>(), y, st->p.clamp_lo, st->p.clamp_hi);
-    return Make<QD>(d, info, ctx, [st, depthwise](const QD& data, cudaStream_t s)
+    FillConv(*st, prm, xi, wi, info.m_InputTensorInfos.size() > 2 ? &info.m_InputTensorInfos[2] : nullptr, yi, depthwise);
+    const bool f32 = yi.GetDataType() == DataType::Float32;
+    // (activations are never fused into the fp32 variant: B200Backend::OptimizeSubgraphView)
+    if (!f32) { Clamp(qd.template GetAdditionalInformation<ActivationDescriptor>(), yi, st->p.clamp_lo, st->p.clamp_hi); }
+    const int biasType = f32 ? B200K_F32 : B200K_S32;
+    return Make<QD>(d, info, ctx, [st, lay, depthwise, f32, nchw, biasType](const QD& data, cudaStream_t s)
     {
         b200k_conv2d_params& q = st->p;
         q.x.data = Dev(data.m_Inputs[0]);
         q.w.data = Dev(data.m_Inputs[1]);
-        if (q.bias.dtype == B200K_S32 && data.m_Inputs.size() > 2) { q.bias.data = Dev(data.m_Inputs[2]); }
+        if (q.bias.dtype == biasType && data.m_Inputs.size() > 2) { q.bias.data = Dev(data.m_Inputs[2]); }
         q.y.data = Dev(data.m_Outputs[0]);
-        if (depthwise) { B200CheckStatus(b200k_dwconv2d_q8(&q, s)); return; }
-        LaunchConv(*st, s);
+        if (nchw)
+        {
+            lay->in.x.data = q.x.data; lay->in.y.data = lay->x;
+            B200CheckStatus(b200k_view_copy_q(&lay->in, s));
+            q.x.data = lay->x;
+            if (lay->w)
+            {
+                lay->weights.x.data = q.w.data; lay->weights.y.data = lay->w;
+                B200CheckStatus(b200k_view_copy_q(&lay->weights, s));
+                q.w.data = lay->w;
+            }
+            lay->out.x.data = lay->y; lay->out.y.data = q.y.data;
+            q.y.data = lay->y;
+        }
+        if (f32) { B200CheckStatus(depthwise ? b200k_dwconv2d_f32(&q, s) : b200k_conv2d_f32(&q, s)); }
+        else if (depthwise) { B200CheckStatus(b200k_dwconv2d_q8(&q, s)); }
+        else { LaunchConv(*st, s); }
+        if (nchw) { B200CheckStatus(b200k_view_copy_q(&lay->out, s)); }
     });
 }
 
@@ -1184,22 +1250,41 @@ std::unique_ptr<IWorkload> B200WorkloadFactory::CreateWorkload(LayerType type, c
         {
             const auto& qd = *PolymorphicDowncast<const Pooling2dQueueDescriptor*>(&d);
             const auto& q = qd.m_Parameters;
-            if (q.m_DataLayout != DataLayout::NHWC) { throw InvalidArgumentException("B200Acc: NHWC only"); }
             auto st = std::make_shared<SimpleState<b200k_pool2d_params>>(ctx);
             b200k_pool2d_params& p = st->p;
             std::memset(&p, 0, sizeof(p));
-            const TensorInfo& x = info.m_InputTensorInfos[0];
-            const TensorInfo& y = info.m_OutputTensorInfos[0];
+            // an NCHW layer runs as re-layout -> NHWC kernel -> re-layout (see MakeConv)
+            const bool nchw = q.m_DataLayout == DataLayout::NCHW;
+            auto lay = std::make_shared<LayoutState>();
+            TensorInfo x = info.m_InputTensorInfos[0], y = info.m_OutputTensorInfos[0];
+            if (nchw)
+            {
+                lay->in = Relayout(x, kNchwToNhwc, st->blobs);
+                lay->x = st->blobs.Alloc(x.GetNumBytes());
+                x = NhwcOf(x);
+                const TensorInfo yNhwc = NhwcOf(y);
+                lay->out = Relayout(yNhwc, kNhwcToNchw, st->blobs);
+                lay->y = st->blobs.Alloc(y.GetNumBytes());
+                y = yNhwc;
+            }
             p.x = Operand(x, st->blobs); p.y = Operand(y, st->blobs);
             p.n = x.GetShape()[0]; p.h = x.GetShape()[1]; p.wd = x.GetShape()[2]; p.c = x.GetShape()[3];
             p.oh = y.GetShape()[1]; p.ow = y.GetShape()[2];
             p.pool_h = q.m_PoolHeight; p.pool_w = q.m_PoolWidth; p.stride_h = q.m_StrideY; p.stride_w = q.m_StrideX;
             p.pad_top = q.m_PadTop; p.pad_bottom = q.m_PadBottom; p.pad_left = q.m_PadLeft; p.pad_right = q.m_PadRight;
             p.pool_type = static_cast<int32_t>(q.m_PoolType); p.padding_method = static_cast<int32_t>(q.m_PaddingMethod);
-            return Make<Pooling2dQueueDescriptor>(d, info, ctx, [st](const Pooling2dQueueDescriptor& data, cudaStream_t s)
+            return Make<Pooling2dQueueDescriptor>(d, info, ctx, [st, lay, nchw](const Pooling2dQueueDescriptor& data, cudaStream_t s)
             {
                 st->p.x.data = Dev(data.m_Inputs[0]); st->p.y.data = Dev(data.m_Outputs[0]);
+                if (nchw)
+                {
+                    lay->in.x.data = st->p.x.data; lay->in.y.data = lay->x;
+                    B200CheckStatus(b200k_view_copy_q(&lay->in, s));
+                    lay->out.x.data = lay->y; lay->out.y.data = st->p.y.data;
+                    st->p.x.data = lay->x; st->p.y.data = lay->y;
+                }
                 B200CheckStatus(b200k_pool2d_q8(&st->p, s));
+                if (nchw) { B200CheckStatus(b200k_view_copy_q(&lay->out, s)); }
             });
         }
         case LayerType::TransposeConvolution2d:

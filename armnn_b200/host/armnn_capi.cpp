@@ -174,20 +174,21 @@ void armnnc_set_output_info(void* vn, int layer, int slot, int dtype, int rank, 
 }
 
 int armnnc_add_conv2d(void* vn, int depthwise, int stride_h, int stride_w, int pad_top, int pad_bottom, int pad_left,
-                      int pad_right, int dil_h, int dil_w, int bias_enabled)
+                      int pad_right, int dil_h, int dil_w, int bias_enabled, int nchw)
 {
     auto* n = static_cast<CNet*>(vn);
+    const DataLayout layout = nchw ? DataLayout::NCHW : DataLayout::NHWC;
     if (depthwise) {
         DepthwiseConvolution2dDescriptor d;
         d.m_StrideX = stride_w; d.m_StrideY = stride_h; d.m_PadTop = pad_top; d.m_PadBottom = pad_bottom;
         d.m_PadLeft = pad_left; d.m_PadRight = pad_right; d.m_DilationX = dil_w; d.m_DilationY = dil_h;
-        d.m_BiasEnabled = bias_enabled != 0; d.m_DataLayout = DataLayout::NHWC;
+        d.m_BiasEnabled = bias_enabled != 0; d.m_DataLayout = layout;
         return add_layer(n, n->net->AddDepthwiseConvolution2dLayer(d));
     }
     Convolution2dDescriptor d;
     d.m_StrideX = stride_w; d.m_StrideY = stride_h; d.m_PadTop = pad_top; d.m_PadBottom = pad_bottom;
     d.m_PadLeft = pad_left; d.m_PadRight = pad_right; d.m_DilationX = dil_w; d.m_DilationY = dil_h;
-    d.m_BiasEnabled = bias_enabled != 0; d.m_DataLayout = DataLayout::NHWC;
+    d.m_BiasEnabled = bias_enabled != 0; d.m_DataLayout = layout;
     return add_layer(n, n->net->AddConvolution2dLayer(d));
 }
 
@@ -208,14 +209,14 @@ int armnnc_add_activation(void* vn, int function, float a, float b)
 }
 
 int armnnc_add_pool2d(void* vn, int pool_type, int padding_method, int pool_h, int pool_w, int stride_h, int stride_w,
-                      int pad_top, int pad_bottom, int pad_left, int pad_right)
+                      int pad_top, int pad_bottom, int pad_left, int pad_right, int nchw)
 {
     auto* n = static_cast<CNet*>(vn);
     Pooling2dDescriptor d;
     d.m_PoolType = static_cast<PoolingAlgorithm>(pool_type); d.m_PaddingMethod = static_cast<PaddingMethod>(padding_method);
     d.m_PoolHeight = pool_h; d.m_PoolWidth = pool_w; d.m_StrideX = stride_w; d.m_StrideY = stride_h;
     d.m_PadTop = pad_top; d.m_PadBottom = pad_bottom; d.m_PadLeft = pad_left; d.m_PadRight = pad_right;
-    d.m_OutputShapeRounding = OutputShapeRounding::Floor; d.m_DataLayout = DataLayout::NHWC;
+    d.m_OutputShapeRounding = OutputShapeRounding::Floor; d.m_DataLayout = nchw ? DataLayout::NCHW : DataLayout::NHWC;
     return add_layer(n, n->net->AddPooling2dLayer(d));
 }
 

@@ -185,10 +185,12 @@ class INetwork:
         layer.outputs[0].SetTensorInfo(info)
         return layer
 
-    def AddConvolution2dLayer(self, stride=(1, 1), pad=(0, 0, 0, 0), dilation=(1, 1), bias_enabled=True, name=None):
-        """pad = (top, bottom, left, right); NHWC; inputs: 0 data, 1 weights [O,H,W,I], 2 bias."""
+    def AddConvolution2dLayer(self, stride=(1, 1), pad=(0, 0, 0, 0), dilation=(1, 1), bias_enabled=True, name=None, nchw=False):
+        """pad = (top, bottom, left, right); NHWC; inputs: 0 data, 1 weights [O,H,W,I], 2 bias.  nchw=True states the layer
+        in DataLayout::NCHW (weights [O,I,H,W]): the B200Acc plugin runs it through a re-layout around the NHWC kernels;
+        this Python runtime executes NHWC graphs only."""
         return self._add(Layer("Convolution2d", name, 3 if bias_enabled else 2, 1,
-                               {"stride": stride, "pad": pad, "dilation": dilation, "bias": bias_enabled}))
+                               {"stride": stride, "pad": pad, "dilation": dilation, "bias": bias_enabled, "nchw": bool(nchw)}))
 
     def AddConvolution3dLayer(self, stride=(1, 1, 1), pad=(0, 0, 0, 0, 0, 0), dilation=(1, 1, 1), bias_enabled=True, name=None):
         """armnn::Convolution3dDescriptor, NDHWC: stride / dilation = (depth, height, width), pad = (front, back, top,
@@ -203,10 +205,10 @@ class INetwork:
         return self._add(Layer("Pooling3d", name, 1, 1, {"type": PoolingAlgorithm(pool_type), "pool": tuple(pool), "stride": tuple(stride),
                                                           "pad": tuple(pad), "method": PaddingMethod(padding_method)}))
 
-    def AddDepthwiseConvolution2dLayer(self, stride=(1, 1), pad=(0, 0, 0, 0), dilation=(1, 1), bias_enabled=True, name=None):
-        """weights [1,H,W,I*M]"""
+    def AddDepthwiseConvolution2dLayer(self, stride=(1, 1), pad=(0, 0, 0, 0), dilation=(1, 1), bias_enabled=True, name=None, nchw=False):
+        """weights [1,H,W,I*M] (in both data layouts)"""
         return self._add(Layer("DepthwiseConvolution2d", name, 3 if bias_enabled else 2, 1,
-                               {"stride": stride, "pad": pad, "dilation": dilation, "bias": bias_enabled}))
+                               {"stride": stride, "pad": pad, "dilation": dilation, "bias": bias_enabled, "nchw": bool(nchw)}))
 
     def AddFullyConnectedLayer(self, transpose_weights=False, bias_enabled=True, name=None):
         return self._add(Layer("FullyConnected", name, 3 if bias_enabled else 2, 1,
@@ -220,9 +222,9 @@ class INetwork:
         return self._add(Layer("Activation", name, 1, 1, {"function": ActivationFunction(function), "a": float(a), "b": float(b)}))
 
     def AddPooling2dLayer(self, pool_type, pool=(2, 2), stride=(2, 2), pad=(0, 0, 0, 0),
-                          padding_method=PaddingMethod.Exclude, name=None):
+                          padding_method=PaddingMethod.Exclude, name=None, nchw=False):
         return self._add(Layer("Pooling2d", name, 1, 1, {"type": PoolingAlgorithm(pool_type), "pool": pool, "stride": stride,
-                                                          "pad": pad, "method": PaddingMethod(padding_method)}))
+                                                          "pad": pad, "method": PaddingMethod(padding_method), "nchw": bool(nchw)}))
 
     def AddElementwiseBinaryLayer(self, operation, name=None):
         return self._add(Layer("ElementwiseBinary", name, 2, 1, {"op": BinaryOperation(operation)}))
@@ -479,6 +481,8 @@ def IsLayerSupported(layer):
     t = layer.type
     if t in ("Input", "Output", "Constant", "Reshape"):
         return True, ""
+    if t in ("Convolution2d", "DepthwiseConvolution2d", "Pooling2d") and layer.desc.get("nchw"):
+        return False, "%s: this runtime executes NHWC graphs only (the plugin re-lays NCHW layers out)" % t
     if t in ("Convolution2d", "DepthwiseConvolution2d", "FullyConnected"):
         x, w, y = ins[0], ins[1], outs[0]
         if not w.constant:

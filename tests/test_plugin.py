@@ -1363,3 +1363,61 @@ def test_reverse_v2_through_the_runtime_equals_cpuref():
     ref = hostnet.ArmnnNetwork(net, "CpuRef").run(xs)[0]
     got = hostnet.ArmnnNetwork(net, "B200Acc").run(xs)[0]
     assert np.array_equal(ref, xs[0][:, ::-1, ::-1, :]) and np.array_equal(ref, got)
+
+
+def _nchw_net(float32=False):
+    """An NCHW graph as the ONNX parser states it: Convolution2d ([O, I, H, W] weights, bias) -> ReLU -> DepthwiseConvolution2d
+    (stride 2) -> Pooling2d (Max, padded)."""
+    from armnn_b200.network import ActivationFunction, DataType, INetwork, PoolingAlgorithm, TensorInfo
+    rng = np.random.default_rng(103)
+
+    def act(shape, scale=0.05, offset=-3):
+        return TensorInfo(tuple(shape), DataType.Float32) if float32 else TensorInfo(tuple(shape), DataType.QAsymmS8, scale, offset)
+
+    def const(net, shape, scale, name, dtype=DataType.QSymmS8, lo=-127, hi=128):
+        if float32:
+            data, info = (rng.standard_normal(shape) * 0.2).astype(np.float32), TensorInfo(shape, DataType.Float32, constant=True)
+        elif dtype == DataType.Signed32:
+            data, info = rng.integers(-800, 800, size=shape).astype(np.int32), TensorInfo(shape, dtype, scale, 0, constant=True)
+        else:
+            data, info = rng.integers(lo, hi, size=shape).astype(np.int8), TensorInfo(shape, dtype, scale, 0, constant=True)
+        return net.AddConstantLayer(data, info, name)
+    net = INetwork.Create()
+    il = net.AddInputLayer(0, "input")
+    il.GetOutputSlot(0).SetTensorInfo(act((2, 6, 9, 10)))
+    w1, b1 = const(net, (12, 6, 3, 3), 0.01, "w1"), const(net, (12,), 0.05 * 0.01, "b1", DataType.Signed32)
+    c1 = net.AddConvolution2dLayer((1, 1), (1, 1, 1, 1), (1, 1), True, "conv", nchw=True)
+    il.GetOutputSlot(0).Connect(c1.GetInputSlot(0)); w1.GetOutputSlot(0).Connect(c1.GetInputSlot(1)); b1.GetOutputSlot(0).Connect(c1.GetInputSlot(2))
+    c1.GetOutputSlot(0).SetTensorInfo(act((2, 12, 9, 10), 0.08, -128))
+    r1 = net.AddActivationLayer(ActivationFunction.ReLu, name="relu")
+    c1.GetOutputSlot(0).Connect(r1.GetInputSlot(0))
+    r1.GetOutputSlot(0).SetTensorInfo(act((2, 12, 9, 10), 0.08, -128))
+    w2 = const(net, (1, 3, 3, 12), 0.02, "w2")
+    d2 = net.AddDepthwiseConvolution2dLayer((2, 2), (1, 1, 1, 1), (1, 1), False, "depthwise", nchw=True)
+    r1.GetOutputSlot(0).Connect(d2.GetInputSlot(0)); w2.GetOutputSlot(0).Connect(d2.GetInputSlot(1))
+    d2.GetOutputSlot(0).SetTensorInfo(act((2, 12, 5, 5), 0.3, 2))
+    p3 = net.AddPooling2dLayer(PoolingAlgorithm.Max, (3, 3), (2, 2), (1, 1, 1, 1), name="max", nchw=True)
+    d2.GetOutputSlot(0).Connect(p3.GetInputSlot(0))
+    p3.GetOutputSlot(0).SetTensorInfo(act((2, 12, 3, 3), 0.3, 2))
+    ol = net.AddOutputLayer(0, "out")
+    p3.GetOutputSlot(0).Connect(ol.GetInputSlot(0))
+    return net
+
+
+@needs_plugin
+@pytest.mark.gpu
+@pytest.mark.parametrize("float32", [False, True])
+def test_nchw_graph_through_the_runtime_matches_cpuref(float32):
+    """NCHW Convolution2d, DepthwiseConvolution2d and Pooling2d run through a re-layout around the NHWC kernels, all on
+    B200Acc."""
+    net = _nchw_net(float32)
+    rng = np.random.default_rng(107)
+    x = rng.standard_normal((2, 6, 9, 10)).astype(np.float32) if float32 else rng.integers(-128, 128, size=(2, 6, 9, 10)).astype(np.int8)
+    ref = hostnet.ArmnnNetwork(net, "CpuRef").run({0: x})[0]
+    got = hostnet.ArmnnNetwork(net, "B200Acc").run({0: x})[0]
+    assert ref.shape == got.shape == (2, 12, 3, 3)
+    if float32:
+        assert np.array_equal(ref, got)
+    else:
+        st = diff_stats(ref, got)
+        assert st["max_abs"] <= 1 and st["mismatch_frac"] < 5e-3, st
