@@ -85,6 +85,10 @@ class GatherParams(C.Structure):
                 ("inner", C.c_int32), ("n_indices", C.c_int32)]
 
 
+class ConvertFp16Params(C.Structure):
+    _fields_ = [("x", C.c_void_p), ("y", C.c_void_p), ("count", C.c_int64), ("to_half", C.c_int32)]
+
+
 class ReverseParams(C.Structure):
     _fields_ = [("x", QTensor), ("y", QTensor), ("axes", C.c_void_p), ("n_axes", C.c_int32), ("rank", C.c_int32),
                 ("shape", C.c_int32 * 6)]
@@ -222,6 +226,7 @@ KERNEL_ENTRY_POINTS = {
     "pool3d_q": Pool3dParams,
     "convert_q": ConvertParams,
     "cast_q": ConvertParams,
+    "convert_fp16": ConvertFp16Params,
     "qlstm_step": QLstmParams,
     "lstm_step_f32": LstmParams,
     "pad_q": PadParams,

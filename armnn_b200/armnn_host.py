@@ -20,9 +20,9 @@ from .network import _ABI_DTYPE as _KERNEL_DTYPE, _NP_DTYPE, DataType
 
 class _BridgeDtype(dict):
     """Element type codes of the bridge to the Arm NN runtime: the C ABI's codes, plus 5 for Boolean (which the kernels see
-    as bytes)."""
+    as bytes) and 6 for Float16 (which only the two conversion layers touch)."""
     def __missing__(self, key):
-        return 5 if key == DataType.Boolean else _KERNEL_DTYPE[key]
+        return {DataType.Boolean: 5, DataType.Float16: 6}.get(key) or _KERNEL_DTYPE[key]
 
 
 _ABI_DTYPE = _BridgeDtype()
@@ -209,6 +209,9 @@ class ArmnnNetwork:
                 # armnn::INetwork has no AddFakeQuantizationLayer (the layer only enters a graph through the optimizer's
                 # internals), so the bridge cannot state it
                 raise NotImplementedError("ArmnnNetwork: FakeQuantization cannot be added through armnn::INetwork")
+            elif t in ("ConvertFp16ToFp32", "ConvertFp32ToFp16"):
+                # armnn::INetwork has no call for these: the optimizer inserts them around layers a backend only runs in Float32
+                raise NotImplementedError("ArmnnNetwork: the fp16 conversion layers cannot be added through armnn::INetwork")
             elif t == "Cast":
                 lid = lib.armnnc_add_cast(net)
             elif t == "Fill":

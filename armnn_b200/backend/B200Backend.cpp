@@ -312,6 +312,10 @@ public:
                 if (!(d.m_Max > d.m_Min)) { return No(reason, "min must be below max"); }
                 return (infos[0].GetDataType() == DataType::Float32 && infos[1].GetDataType() == DataType::Float32) || No(reason, "Float32 only");
             }
+            case LayerType::ConvertFp16ToFp32:
+                return (infos[0].GetDataType() == DataType::Float16 && infos[1].GetDataType() == DataType::Float32) || No(reason, "Float16 -> Float32 only");
+            case LayerType::ConvertFp32ToFp16:
+                return (infos[0].GetDataType() == DataType::Float32 && infos[1].GetDataType() == DataType::Float16) || No(reason, "Float32 -> Float16 only");
             case LayerType::Cast:
                 return (IsMoveType(infos[0]) && IsMoveType(infos[1]) && infos[0].GetNumElements() == infos[1].GetNumElements()) ||
                        No(reason, "unsupported data type or mismatched sizes");

@@ -1622,6 +1622,21 @@ std::unique_ptr<IWorkload> B200WorkloadFactory::CreateWorkload(LayerType type, c
                 B200CheckStatus(b200k_activation_q8(&st->p, s));
             });
         }
+        case LayerType::ConvertFp16ToFp32:
+        case LayerType::ConvertFp32ToFp16:
+        {
+            auto st = std::make_shared<SimpleState<b200k_convert_fp16_params>>(ctx);
+            std::memset(&st->p, 0, sizeof(st->p));
+            st->p.count = info.m_InputTensorInfos[0].GetNumElements();
+            st->p.to_half = type == LayerType::ConvertFp32ToFp16 ? 1 : 0;
+            auto fn = [st](const QueueDescriptor& data, cudaStream_t s)
+            {
+                st->p.x = Dev(data.m_Inputs[0]); st->p.y = Dev(data.m_Outputs[0]);
+                B200CheckStatus(b200k_convert_fp16(&st->p, s));
+            };
+            if (type == LayerType::ConvertFp32ToFp16) { return Make<ConvertFp32ToFp16QueueDescriptor>(d, info, ctx, fn); }
+            return Make<ConvertFp16ToFp32QueueDescriptor>(d, info, ctx, fn);
+        }
         case LayerType::Cast:
         {
             auto st = std::make_shared<SimpleState<b200k_convert_params>>(ctx);

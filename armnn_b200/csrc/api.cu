@@ -119,6 +119,7 @@ extern "C" size_t b200k_sizeof_params(int which)
         case 22: return sizeof(b200k_gather_nd_params);
         case 23: return sizeof(b200k_lstm_params);
         case 24: return sizeof(b200k_reverse_params);
+        case 25: return sizeof(b200k_convert_fp16_params);
         default: return 0;
     }
 }

@@ -5,6 +5,7 @@
 // unfused, re-quantise (RefElementwiseBinaryWorkload.cpp:27-132, Activation.cpp:13-119,
 // RefQuantizeWorkload.cpp:14-45, Dequantize.cpp:11-28 of the Arm NN tree).
 #include "common.cuh"
+#include <cuda_fp16.h>
 
 namespace b200k {
 
@@ -225,6 +226,41 @@ extern "C" int b200k_convert_q(const b200k_convert_params* p, void* stream)
 {
     B200K_REQUIRE(p, B200K_E_INVALID, "convert_q: null params");
     return launch_unary(p->x, p->y, p->count, -1, 0.f, 0.f, stream, "convert_q");
+}
+
+// ---- ConvertFp16ToFp32 / ConvertFp32ToFp16 ---------------------------------------------------------------------
+// armnnUtils::FloatingPointConverter (src/armnnUtils/FloatingPointConverter.cpp:17-45) over half_float::half with
+// round-to-nearest, ties to even (src/armnnUtils/Half.hpp:11-16): widening is exact, narrowing is cvt.rn.f16.f32 with
+// infinities replaced by the largest finite half.
+
+namespace b200k {
+
+__global__ void __launch_bounds__(256) convert_fp16_kernel(const void* x, void* y, long long count, int to_half)
+{
+    pdl_enter();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= count) return;
+    if (to_half) {
+        // FloatingPointConverter.cpp:32-40: a result of infinity (overflow, or an infinite input) becomes the largest finite half
+        unsigned short h = __half_as_ushort(__float2half_rn(((const float*)x)[i]));
+        if ((h & 0x7fffu) == 0x7c00u) h = (unsigned short)((h & 0x8000u) | 0x7bffu);
+        ((unsigned short*)y)[i] = h;
+    }
+    else         ((float*)y)[i] = __half2float(((const __half*)x)[i]);
+}
+
+}  // namespace b200k
+
+extern "C" int b200k_convert_fp16(const b200k_convert_fp16_params* p, void* stream)
+{
+    B200K_REQUIRE(p, B200K_E_INVALID, "convert_fp16: null params");
+    B200K_REQUIRE(p->x && p->y, B200K_E_INVALID, "convert_fp16: null tensor pointer");
+    B200K_REQUIRE(p->count >= 0, B200K_E_INVALID, "convert_fp16: negative element count");
+    if (p->count == 0) return B200K_OK;
+    B200K_REQUIRE(p->count / 256 < (1ll << 31) - 1, B200K_E_TOOBIG, "convert_fp16: tensor too large");
+    launch_pdl(b200k::convert_fp16_kernel, dim3(div_up(p->count, 256)), dim3(256), 0, (cudaStream_t)stream, p->x, p->y,
+               (long long)p->count, (int)p->to_half);
+    return check_launch("convert_fp16_kernel");
 }
 
 // ---- Pad ------------------------------------------------------------------------------------------------------

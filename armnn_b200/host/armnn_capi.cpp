@@ -32,6 +32,7 @@ DataType act_type(int dt)
         case B200K_S16: return DataType::QSymmS16;
         case B200K_S32: return DataType::Signed32;
         case 5:         return DataType::Boolean;         // bridge only: the kernels see a Boolean tensor as bytes
+        case 6:         return DataType::Float16;         // bridge only: the operand of the two fp16 conversion layers
         default:        return DataType::Float32;
     }
 }
@@ -45,7 +46,7 @@ TensorInfo make_info(const b200k_qtensor& t, const TensorShape& shape, unsigned 
         if (t.dtype == B200K_S8) info.SetDataType(DataType::QSymmS8);
         info.SetQuantizationScales(std::vector<float>(t.scales, t.scales + n_axis));
         info.SetQuantizationDim(Optional<unsigned int>(axis_dim));
-    } else if (t.dtype != B200K_F32 && t.dtype != 5) {
+    } else if (t.dtype != B200K_F32 && t.dtype != 5 && t.dtype != 6) {
         info.SetQuantizationScale(t.scale);
         info.SetQuantizationOffset(t.zero_point);
     }

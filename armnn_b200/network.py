@@ -23,6 +23,7 @@ from . import _abi, lib, views
 
 
 class DataType(IntEnum):            # include/armnn/Types.hpp:48-60
+    Float16 = 0                     # only as the other side of ConvertFp16ToFp32 / ConvertFp32ToFp16
     Float32 = 1
     QAsymmU8 = 2
     Signed32 = 3
@@ -75,7 +76,8 @@ class PaddingMethod(IntEnum):
 _ABI_DTYPE = {DataType.Float32: _abi.F32, DataType.QAsymmU8: _abi.U8, DataType.Signed32: _abi.S32,
               DataType.QSymmS16: _abi.S16, DataType.QSymmS8: _abi.S8, DataType.QAsymmS8: _abi.S8, DataType.Boolean: _abi.U8}
 _NP_DTYPE = {DataType.Float32: np.float32, DataType.QAsymmU8: np.uint8, DataType.Signed32: np.int32,
-             DataType.QSymmS16: np.int16, DataType.QSymmS8: np.int8, DataType.QAsymmS8: np.int8, DataType.Boolean: np.uint8}
+             DataType.QSymmS16: np.int16, DataType.QSymmS8: np.int8, DataType.QAsymmS8: np.int8, DataType.Boolean: np.uint8,
+             DataType.Float16: np.float16}
 _TYPE_RANGE = {DataType.QAsymmU8: (0, 255), DataType.QAsymmS8: (-128, 127), DataType.QSymmS8: (-128, 127),
                DataType.QSymmS16: (-32768, 32767), DataType.Signed32: (-(1 << 31), (1 << 31) - 1)}
 
@@ -306,6 +308,12 @@ class INetwork:
     def AddFakeQuantizationLayer(self, minimum, maximum, name=None):
         """armnn::FakeQuantizationDescriptor (Float32 tensors): every value becomes its 8-bit code over [min, max]."""
         return self._add(Layer("FakeQuantization", name, 1, 1, {"min": float(minimum), "max": float(maximum)}))
+
+    def AddConvertFp16ToFp32Layer(self, name=None):
+        return self._add(Layer("ConvertFp16ToFp32", name, 1, 1, {}))
+
+    def AddConvertFp32ToFp16Layer(self, name=None):
+        return self._add(Layer("ConvertFp32ToFp16", name, 1, 1, {}))
 
     def AddCastLayer(self, name=None):
         return self._add(Layer("Cast", name, 1, 1, {}))
@@ -608,6 +616,11 @@ def IsLayerSupported(layer):
     if t == "FakeQuantization":
         if ins[0].dtype != DataType.Float32 or outs[0].dtype != DataType.Float32 or not layer.desc["max"] > layer.desc["min"]:
             return False, "FakeQuantization: Float32 tensors and min < max"
+        return True, ""
+    if t in ("ConvertFp16ToFp32", "ConvertFp32ToFp16"):
+        a, b = (DataType.Float16, DataType.Float32) if t == "ConvertFp16ToFp32" else (DataType.Float32, DataType.Float16)
+        if ins[0].dtype != a or outs[0].dtype != b or ins[0].GetNumElements() != outs[0].GetNumElements():
+            return False, "%s: %s input and %s output of one size" % (t, a.name, b.name)
         return True, ""
     if t == "Cast":
         ok = (DataType.QAsymmU8, DataType.QAsymmS8, DataType.QSymmS8, DataType.QSymmS16, DataType.Signed32, DataType.Float32)
@@ -1281,6 +1294,15 @@ class GraphProgram:
         p.x, p.y = self._operand(x), self._operand(y)
         p.count, p.function, p.a, p.b = x.info.GetNumElements(), 50, layer.desc["min"], layer.desc["max"]
         return "activation_q8", p
+
+    def _make_ConvertFp16ToFp32(self, layer):
+        x, y = layer.inputs[0].source, layer.outputs[0]
+        p = _abi.ConvertFp16Params()
+        p.x, p.y = self._ptr(self._dev(x)), self._ptr(self._dev(y))
+        p.count, p.to_half = x.info.GetNumElements(), int(layer.type == "ConvertFp32ToFp16")
+        return "convert_fp16", p
+
+    _make_ConvertFp32ToFp16 = _make_ConvertFp16ToFp32
 
     def _make_Cast(self, layer):
         x, y = layer.inputs[0].source, layer.outputs[0]

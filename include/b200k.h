@@ -534,6 +534,20 @@ typedef struct {
 
 int b200k_convert_q(const b200k_convert_params* p, void* stream);
 
+/* armnn::ConvertFp16ToFp32 (to_half = 0: x holds IEEE binary16, y Float32; exact) and ConvertFp32ToFp16 (to_half = 1:
+ * round to nearest, ties to even, and +-infinity — overflow or an infinite input — replaced by +-65504), as
+ * armnnUtils::FloatingPointConverter does them
+ * (src/armnnUtils/FloatingPointConverter.cpp:17-45, src/armnnUtils/Half.hpp:11-16).  With these two layers on the backend
+ * the optimizer can run a Float16 network's layers in Float32 here instead of falling back. */
+typedef struct {
+    const void* x;
+    void* y;
+    int64_t count;
+    int32_t to_half;
+} b200k_convert_fp16_params;
+
+int b200k_convert_fp16(const b200k_convert_fp16_params* p, void* stream);
+
 /* armnn::Cast (src/backends/reference/workloads/RefCastWorkload.cpp:13-36, 95-106): the numbers stored in x become the
  * numbers stored in y: both tensors are read with scale 1 and offset 0 whatever x.scale / y.scale say, the value is
  * floored before an integer output (and clamped to the type's range), kept as it is for a float output.  Any of
@@ -622,7 +636,7 @@ unsigned long long b200k_kernel_launches(void);
 
 /* sizeof() of a parameter struct as compiled into the library, for bindings in other languages to check their
  * own declarations: 0 conv2d, 1 fc, 2 bmm, 3 pool2d, 4 mean, 5 eltwise, 6 activation, 7 softmax, 8 convert,
- * 9 qlstm, 10 pad, 11 view_copy, 12 resize, 13 reduce, 14 unary, 15 arg_min_max, 16 gather, 17 batch_norm, 18 instance_norm, 19 normalization, 20 conv3d, 21 pool3d, 22 gather_nd, 23 lstm, 24 reverse.  No counterpart in the reference (its backends are linked as C++). */
+ * 9 qlstm, 10 pad, 11 view_copy, 12 resize, 13 reduce, 14 unary, 15 arg_min_max, 16 gather, 17 batch_norm, 18 instance_norm, 19 normalization, 20 conv3d, 21 pool3d, 22 gather_nd, 23 lstm, 24 reverse, 25 convert_fp16.  No counterpart in the reference (its backends are linked as C++). */
 size_t b200k_sizeof_params(int which);
 
 #ifdef __cplusplus

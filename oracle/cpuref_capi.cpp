@@ -1074,3 +1074,28 @@ extern "C" int cpuref_lstm_step_f32(const b200k_lstm_params* p)
         copy_out(o3, p->output, hi.GetNumBytes());
     });
 }
+
+extern "C" int cpuref_convert_fp16(const b200k_convert_fp16_params* p)
+{
+    return guarded([&] {
+        Harness h;
+        const TensorShape shape({(unsigned)p->count});
+        TensorInfo half(shape, DataType::Float16), single(shape, DataType::Float32);
+        if (p->to_half)
+        {
+            ConvertFp32ToFp16QueueDescriptor d;
+            h.in(d, single, p->x);
+            ITensorHandle* o = h.out(d, half);
+            h.run(LayerType::ConvertFp32ToFp16, d);
+            copy_out(o, p->y, half.GetNumBytes());
+        }
+        else
+        {
+            ConvertFp16ToFp32QueueDescriptor d;
+            h.in(d, half, p->x);
+            ITensorHandle* o = h.out(d, single);
+            h.run(LayerType::ConvertFp16ToFp32, d);
+            copy_out(o, p->y, single.GetNumBytes());
+        }
+    });
+}

@@ -1751,3 +1751,60 @@ int oracle_lstm_step_f32(const b200k_lstm_params* p)
     free(gi);
     return 0;
 }
+
+/* ---- ConvertFp16ToFp32 / ConvertFp32ToFp16, FloatingPointConverter.cpp:17-45 (half_float::half, nearest, ties to even) -- */
+
+static float half_to_float(uint16_t h)
+{
+    const uint32_t sign = (uint32_t)(h >> 15) << 31, exp = (h >> 10) & 31, man = h & 1023;
+    uint32_t bits;
+    if (exp == 0) {
+        if (man == 0) bits = sign;
+        else {                                          /* subnormal: man * 2^-24, exact in fp32 */
+            float f = (float)man * 5.9604644775390625e-08f;
+            memcpy(&bits, &f, 4);
+            bits |= sign;
+        }
+    } else if (exp == 31) bits = sign | 0x7f800000u | (man << 13);
+    else bits = sign | ((exp + 112) << 23) | (man << 13);
+    float out;
+    memcpy(&out, &bits, 4);
+    return out;
+}
+
+static uint16_t float_to_half(float f)
+{
+    uint32_t bits;
+    memcpy(&bits, &f, 4);
+    const uint16_t sign = (uint16_t)((bits >> 16) & 0x8000u);
+    const uint32_t abs = bits & 0x7fffffffu;
+    if (abs >= 0x7f800000u) return (uint16_t)(sign | 0x7c00u | (abs > 0x7f800000u ? 0x200u | ((abs >> 13) & 0x3ffu) : 0));
+    if (abs >= 0x477ff000u) return (uint16_t)(sign | 0x7c00u);            /* rounds to or beyond 65520: infinity */
+    if (abs < 0x38800000u) {                                              /* below 2^-14: subnormal half or zero */
+        /* |f| / 2^-24 rounded to nearest even is the mantissa; the magic-number addition does that rounding in fp32 */
+        float a;
+        memcpy(&a, &abs, 4);
+        volatile float r = a * 16777216.0f;                               /* exact scaling */
+        volatile float m = r + 8388608.0f;                                /* rounds to an integer, ties to even */
+        uint32_t mb;
+        float mf = m;
+        memcpy(&mb, &mf, 4);
+        return (uint16_t)(sign | (mb & 0x7ffu));                          /* up to 1024 = the smallest normal */
+    }
+    uint32_t rounded = abs + 0xfffu + ((abs >> 13) & 1u);                 /* nearest, ties to even on bit 13 */
+    return (uint16_t)(sign | ((rounded - 0x38000000u) >> 13));
+}
+
+int oracle_convert_fp16(const b200k_convert_fp16_params* p)
+{
+    if (!p->x || !p->y || p->count < 0) return B200K_E_INVALID;
+    for (int64_t i = 0; i < p->count; ++i) {
+        if (p->to_half) {
+            uint16_t hbits = float_to_half(((const float*)p->x)[i]);
+            if ((hbits & 0x7fffu) == 0x7c00u) hbits = (uint16_t)((hbits & 0x8000u) | 0x7bffu);   /* :35-39: infinity becomes the largest finite half */
+            ((uint16_t*)p->y)[i] = hbits;
+        }
+        else ((float*)p->y)[i] = half_to_float(((const uint16_t*)p->x)[i]);
+    }
+    return 0;
+}

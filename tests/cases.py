@@ -685,6 +685,27 @@ def lstm_cases():
 
 
 def convert_cases():
+    def fp16(seed, to_half):
+        def build(mem):
+            rng = np.random.default_rng(seed)
+            p = _abi.ConvertFp16Params()
+            if to_half:
+                # normal halves, ties at bit 13, the subnormal range, underflow to zero, overflow to infinity, infinities
+                x = np.concatenate([rng.standard_normal(3000) * 10 ** rng.uniform(-9, 6, 3000),
+                                    np.array([0.0, -0.0, 65504.0, 65519.9, 65520.0, -65536.0, 1e9, np.inf, -np.inf, 6.1e-5, 6.0e-8, 2.9e-8, 3.0e-8, 1e-10]),
+                                    (np.arange(2048, 4096, dtype=np.float64) + 0.5) * 2.0 ** -11,        # exact ties
+                                    (np.arange(0, 1100, dtype=np.float64) * 0.5) * 2.0 ** -24]).astype(np.float32)
+                p.x = mem.inp(x)
+                y, p.y = mem.out(x.shape, np.uint16)
+            else:
+                codes = np.arange(65536, dtype=np.uint16)
+                codes = codes[~(((codes & 0x7c00) == 0x7c00) & ((codes & 0x3ff) != 0))]                    # every code but the NaNs
+                p.x = mem.inp(codes)
+                y, p.y = mem.out(codes.shape, np.float32)
+            p.count, p.to_half = (x if to_half else codes).size, int(to_half)
+            return p, [y]
+        return lambda: SimpleCase("convert_fp16", build)
+
     def make(seed, xd, yd, count=1001, xq=(0.05, 3), yq=(0.07, -4), entry="convert_q", fscale=4):
         def build(mem):
             rng = np.random.default_rng(seed)
@@ -707,7 +728,8 @@ def convert_cases():
             # Cast ignores both quantisations: the stored numbers are converted
             "cast_f32_s8": make(118, F32, S8, entry="cast_q", fscale=40), "cast_f32_s32": make(119, F32, S32, entry="cast_q", fscale=1e5),
             "cast_u8_f32": make(120, U8, F32, entry="cast_q", xq=(0.1, 120)), "cast_s16_u8": make(110, S16, U8, entry="cast_q", xq=(0.0005, 0)),
-            "cast_s32_s16": make(109, S32, S16, entry="cast_q"), "cast_s8_s32": make(108, S8, S32, entry="cast_q")}
+            "cast_s32_s16": make(109, S32, S16, entry="cast_q"), "cast_s8_s32": make(108, S8, S32, entry="cast_q"),
+            "fp32_to_fp16_every_range": fp16(107, True), "fp16_to_fp32_every_code": fp16(106, False)}
 
 
 def pad_cases():

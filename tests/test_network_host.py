@@ -381,3 +381,17 @@ def test_fake_quantization_in_the_mirror_matches_the_formula(built):
     q = x / scale
     want = np.clip(np.where(q >= 0, np.floor(q + np.float32(0.5)), np.ceil(q - np.float32(0.5))) + offset, 0, 255).astype(np.float32)
     assert np.array_equal(got, want)
+
+
+@needs_cpuref
+def test_fp16_conversion_graph_oracle_equals_armnn_cpuref(built):
+    """The mirror's explicit conversion layers around a Float32 Activation against CpuRef's Float16 Activation (its
+    decoder widens and its encoder narrows with the same FloatingPointConverter, saturation included)."""
+    import hostnet
+    from test_plugin import _fp16_net
+    x = (np.random.default_rng(110).standard_normal((2, 40)) * 60).astype(np.float16)
+    x[0, 0], x[1, 3] = 300.0, -280.0
+    want = hostnet.ArmnnNetwork(_fp16_net(False), "CpuRef").run({0: x})[0]
+    got = hostnet.OracleNetwork(Optimize(_fp16_net(True))).run({0: x})[0]
+    assert want.dtype == np.float16 and want.max() == np.float16(65504)          # an overflowing square saturates
+    assert np.array_equal(want.view(np.uint16), got.view(np.uint16))

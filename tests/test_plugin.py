@@ -1421,3 +1421,48 @@ def test_nchw_graph_through_the_runtime_matches_cpuref(float32):
     else:
         st = diff_stats(ref, got)
         assert st["max_abs"] <= 1 and st["mismatch_frac"] < 5e-3, st
+
+
+def _fp16_net(explicit_conversions):
+    """A Float16 tensor squared.  explicit_conversions: widened, processed in Float32 and narrowed again by layers of the
+    graph (what the mirror runs); otherwise a Float16 Activation, around which the Arm NN optimizer inserts the two
+    conversion layers itself when the backend only runs the Activation in Float32 (src/armnn/Network.cpp: AssignBackends)."""
+    from armnn_b200.network import ActivationFunction, DataType, INetwork, TensorInfo
+    half, single = TensorInfo((2, 40), DataType.Float16), TensorInfo((2, 40), DataType.Float32)
+    net = INetwork.Create()
+    il = net.AddInputLayer(0, "input")
+    il.GetOutputSlot(0).SetTensorInfo(half)
+    prev = il
+    if explicit_conversions:
+        up = net.AddConvertFp16ToFp32Layer("widen")
+        prev.GetOutputSlot(0).Connect(up.GetInputSlot(0))
+        up.GetOutputSlot(0).SetTensorInfo(single)
+        prev = up
+    sq = net.AddActivationLayer(ActivationFunction.Square, name="square")
+    prev.GetOutputSlot(0).Connect(sq.GetInputSlot(0))
+    sq.GetOutputSlot(0).SetTensorInfo(single if explicit_conversions else half)
+    prev = sq
+    if explicit_conversions:
+        dn = net.AddConvertFp32ToFp16Layer("narrow")
+        prev.GetOutputSlot(0).Connect(dn.GetInputSlot(0))
+        dn.GetOutputSlot(0).SetTensorInfo(half)
+        prev = dn
+    ol = net.AddOutputLayer(0, "out")
+    prev.GetOutputSlot(0).Connect(ol.GetInputSlot(0))
+    return net
+
+
+@needs_plugin
+@pytest.mark.gpu
+def test_float16_network_runs_in_float32_between_inserted_conversions():
+    """B200Acc refuses the Float16 Activation but supports it in Float32 and supports both conversion layers, so the
+    optimizer keeps the whole graph on B200Acc; CpuRef computes the Float16 layer directly.  Same bits, overflow included."""
+    net = _fp16_net(False)
+    x = (np.random.default_rng(109).standard_normal((2, 40)) * 60).astype(np.float16)
+    x[0, 0], x[1, 3] = 300.0, -280.0                                                          # squares beyond 65504 saturate
+    ref = hostnet.ArmnnNetwork(net, "CpuRef").run({0: x})[0]
+    b200 = hostnet.ArmnnNetwork(net, "B200Acc", optimize_only=True)
+    assert [t for t, _ in b200.optimized_layers].count("ConvertFp16ToFp32") == 1, b200.optimized_layers
+    got = hostnet.ArmnnNetwork(net, "B200Acc").run({0: x})[0]
+    assert ref.dtype == np.float16 and np.isfinite(ref).all() and ref.max() == np.float16(65504)
+    assert np.array_equal(ref.view(np.uint16), got.view(np.uint16))
