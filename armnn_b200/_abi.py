@@ -89,6 +89,11 @@ class ConvertFp16Params(C.Structure):
     _fields_ = [("x", C.c_void_p), ("y", C.c_void_p), ("count", C.c_int64), ("to_half", C.c_int32)]
 
 
+class ScatterNdParams(C.Structure):
+    _fields_ = [("x", QTensor), ("updates", QTensor), ("y", QTensor), ("indices", C.c_void_p), ("n_indices", C.c_int32),
+                ("nd", C.c_int32), ("inner", C.c_int32), ("dims", C.c_int32 * 8), ("function", C.c_int32)]
+
+
 class ReverseParams(C.Structure):
     _fields_ = [("x", QTensor), ("y", QTensor), ("axes", C.c_void_p), ("n_axes", C.c_int32), ("rank", C.c_int32),
                 ("shape", C.c_int32 * 6)]
@@ -218,6 +223,7 @@ KERNEL_ENTRY_POINTS = {
     "arg_min_max_q": ArgMinMaxParams,
     "gather_q": GatherParams,
     "reverse_q": ReverseParams,
+    "scatter_nd_q": ScatterNdParams,
     "gather_nd_q": GatherNdParams,
     "batch_norm_q": BatchNormParams,
     "instance_norm_q": InstanceNormParams,

@@ -170,6 +170,8 @@ class ArmnnNetwork:
             elif t == "Normalization":
                 lid = lib.armnnc_add_normalization(net, d["channel_type"], C.c_uint(d["norm_size"]), C.c_float(d["alpha"]),
                                                    C.c_float(d["beta"]), C.c_float(d["k"]), int(d["nchw"]))
+            elif t == "ScatterNd":
+                lid = lib.armnnc_add_scatter_nd(net, d["function"], int(d["input_enabled"]))
             elif t == "ReverseV2":
                 lid = lib.armnnc_add_reverse_v2(net)
             elif t == "GatherNd":

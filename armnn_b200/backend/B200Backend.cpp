@@ -332,6 +332,18 @@ public:
             case LayerType::Gather:
                 if (infos[1].GetDataType() != DataType::Signed32) { return No(reason, "indices must be Signed32"); }
                 return (IsMoveType(infos[0]) && infos[2].GetDataType() == infos[0].GetDataType()) || No(reason, "unsupported or mismatched data types");
+            case LayerType::ScatterNd:
+            {
+                // infos: input (or shape), indices, updates, output
+                const auto& d = *PolymorphicDowncast<const ScatterNdDescriptor*>(&descriptor);
+                if (d.m_AxisEnabled) { return No(reason, "the axis option is not supported"); }
+                if (infos[1].GetDataType() != DataType::Signed32 || infos[1].GetNumDimensions() != 2) { return No(reason, "indices must be Signed32 [n, nd]"); }
+                const unsigned int nd = infos[1].GetShape()[1];
+                if (nd < 1 || nd > 8 || nd > infos[3].GetNumDimensions()) { return No(reason, "index tuples longer than the output's rank (or than 8)"); }
+                if (!IsActType(infos[3]) || infos[2].GetDataType() != infos[3].GetDataType()) { return No(reason, "unsupported or mismatched data types"); }
+                if (d.m_InputEnabled ? infos[0].GetDataType() != infos[3].GetDataType() : infos[0].GetDataType() != DataType::Signed32) { return No(reason, "first input: the tensor, or a Signed32 shape"); }
+                return true;
+            }
             case LayerType::ReverseV2:
                 if (infos[1].GetDataType() != DataType::Signed32 || infos[0].GetNumDimensions() > 6) { return No(reason, "Signed32 axes and rank <= 6"); }
                 return (IsMoveType(infos[0]) && infos[2].GetDataType() == infos[0].GetDataType()) || No(reason, "unsupported or mismatched data types");

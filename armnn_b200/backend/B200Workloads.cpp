@@ -1403,6 +1403,38 @@ std::unique_ptr<IWorkload> B200WorkloadFactory::CreateWorkload(LayerType type, c
                 B200CheckStatus(b200k_gather_q(&st->p, s));
             });
         }
+        case LayerType::ScatterNd:
+        {
+            const auto& prm = PolymorphicDowncast<const ScatterNdQueueDescriptor*>(&d)->m_Parameters;
+            auto st = std::make_shared<SimpleState<b200k_scatter_nd_params>>(ctx);
+            b200k_scatter_nd_params& p = st->p;
+            std::memset(&p, 0, sizeof(p));
+            const TensorInfo& idx = info.m_InputTensorInfos[1];
+            const TensorInfo& y = info.m_OutputTensorInfos[0];
+            if (prm.m_AxisEnabled || idx.GetNumDimensions() != 2) { throw InvalidArgumentException("B200Acc: ScatterNd without axis, indices [n, nd]"); }
+            const bool withInput = prm.m_InputEnabled;
+            if (withInput) { p.x = Operand(info.m_InputTensorInfos[0], st->blobs); }
+            p.updates = Operand(info.m_InputTensorInfos[2], st->blobs); p.y = Operand(y, st->blobs);
+            p.n_indices = static_cast<int32_t>(idx.GetShape()[0]); p.nd = static_cast<int32_t>(idx.GetShape()[1]);
+            if (p.nd < 1 || p.nd > 8 || static_cast<unsigned int>(p.nd) > y.GetNumDimensions()) { throw InvalidArgumentException("B200Acc: ScatterNd index tuples do not fit the output"); }
+            p.inner = 1;
+            for (unsigned int i = 0; i < y.GetNumDimensions(); ++i)
+            {
+                if (i < static_cast<unsigned int>(p.nd)) { p.dims[i] = static_cast<int32_t>(y.GetShape()[i]); } else { p.inner *= static_cast<int32_t>(y.GetShape()[i]); }
+            }
+            if (info.m_InputTensorInfos[2].GetNumElements() != static_cast<unsigned int>(p.n_indices) * static_cast<unsigned int>(p.inner))
+            {
+                throw InvalidArgumentException("B200Acc: ScatterNd updates do not match the index tuples");
+            }
+            p.function = static_cast<int32_t>(prm.m_Function);
+            return Make<ScatterNdQueueDescriptor>(d, info, ctx, [st, withInput](const ScatterNdQueueDescriptor& data, cudaStream_t s)
+            {
+                if (withInput) { st->p.x.data = Dev(data.m_Inputs[0]); }
+                st->p.indices = static_cast<const int32_t*>(Dev(data.m_Inputs[1]));
+                st->p.updates.data = Dev(data.m_Inputs[2]); st->p.y.data = Dev(data.m_Outputs[0]);
+                B200CheckStatus(b200k_scatter_nd_q(&st->p, s));
+            });
+        }
         case LayerType::ReverseV2:
         {
             auto st = std::make_shared<SimpleState<b200k_reverse_params>>(ctx);

@@ -120,6 +120,7 @@ extern "C" size_t b200k_sizeof_params(int which)
         case 23: return sizeof(b200k_lstm_params);
         case 24: return sizeof(b200k_reverse_params);
         case 25: return sizeof(b200k_convert_fp16_params);
+        case 26: return sizeof(b200k_scatter_nd_params);
         default: return 0;
     }
 }

@@ -168,9 +168,93 @@ __global__ void __launch_bounds__(256) reverse_kernel(const ReverseArgs a)
     }
 }
 
+// ScatterNd (src/backends/reference/workloads/ScatterNd.cpp:37-333): the output starts as the input (or as zeros when the
+// layer is given a shape instead), then every index tuple j replaces its slice by op(base slice, updates[j]) where the
+// base is the INPUT (not the running output): with tuples that address one slice the last one wins.  The reference works
+// through the tuples in order; here a tuple that a later one repeats does nothing, which is the same result.
+struct ScatterArgs {
+    QView x, upd, y;
+    const int* indices;
+    int has_x, nd, fn;
+    long long n_idx, inner, total;
+    long long coeff[8], dims[8];
+};
+
+__global__ void __launch_bounds__(256) scatter_init_kernel(const ScatterArgs a)
+{
+    pdl_enter();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= a.total) return;
+    a.y.set(i, a.has_x ? a.x.get(i) : 0.0f);
+}
+
+__device__ __forceinline__ long long scatter_row(const ScatterArgs& a, long long j)
+{
+    long long flat = 0;
+    for (int d = 0; d < a.nd; ++d) {
+        const long long t = a.indices[j * a.nd + d];
+        if (t < 0 || t >= a.dims[d]) return -1;              // the reference throws; here the tuple is skipped
+        flat += t * a.coeff[d];
+    }
+    return flat;
+}
+
+__global__ void __launch_bounds__(256) scatter_kernel(const ScatterArgs a)
+{
+    pdl_enter();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= a.n_idx * a.inner) return;
+    const long long j = i / a.inner, k = i - j * a.inner;
+    const long long row = scatter_row(a, j);
+    if (row < 0) return;
+    for (long long j2 = j + 1; j2 < a.n_idx; ++j2)
+        if (scatter_row(a, j2) == row) return;               // a later tuple addresses the same slice: it wins
+    const long long at = row * a.inner + k;
+    const float base = a.has_x ? a.x.get(at) : 0.0f;
+    const float u = a.upd.get(i);
+    float r;
+    switch (a.fn) {
+        case 0:  r = u; break;
+        case 1:  r = __fadd_rn(base, u); break;
+        case 2:  r = __fsub_rn(base, u); break;
+        case 3:  r = base < u ? u : base; break;             // std::max(input, update)
+        case 4:  r = u < base ? u : base; break;             // std::min(input, update)
+        default: r = __fmul_rn(base, u); break;
+    }
+    a.y.set(at, r);
+}
+
 }  // namespace b200k
 
 using namespace b200k;
+
+extern "C" int b200k_scatter_nd_q(const b200k_scatter_nd_params* p, void* stream)
+{
+    B200K_REQUIRE(p, B200K_E_INVALID, "scatter_nd_q: null params");
+    B200K_REQUIRE(p->updates.data && p->y.data && p->indices, B200K_E_INVALID, "scatter_nd_q: null tensor pointer");
+    B200K_REQUIRE(p->nd >= 1 && p->nd <= 8 && p->n_indices > 0 && p->inner > 0, B200K_E_INVALID, "scatter_nd_q: bad shape");
+    B200K_REQUIRE(p->function >= 0 && p->function <= 5, B200K_E_INVALID, "scatter_nd_q: unknown function %d", p->function);
+    auto ok = [](int t) { return t == B200K_U8 || t == B200K_S8 || t == B200K_S16 || t == B200K_F32; };
+    B200K_REQUIRE(ok(p->updates.dtype) && ok(p->y.dtype) && (!p->x.data || ok(p->x.dtype)), B200K_E_UNSUPPORTED, "scatter_nd_q: unsupported data type");
+    ScatterArgs a;
+    memset(&a, 0, sizeof(a));
+    a.has_x = p->x.data != nullptr;
+    if (a.has_x) a.x = make_view(p->x);
+    a.upd = make_view(p->updates); a.y = make_view(p->y); a.indices = p->indices;
+    a.nd = p->nd; a.fn = p->function; a.n_idx = p->n_indices; a.inner = p->inner;
+    long long rows = 1;
+    for (int d = p->nd - 1; d >= 0; --d) {
+        B200K_REQUIRE(p->dims[d] > 0, B200K_E_INVALID, "scatter_nd_q: non-positive dimension");
+        a.dims[d] = p->dims[d]; a.coeff[d] = rows; rows *= p->dims[d];
+    }
+    a.total = rows * p->inner;
+    cudaStream_t s = (cudaStream_t)stream;
+    launch_pdl(scatter_init_kernel, dim3(div_up(a.total, 256)), dim3(256), 0, s, a);
+    int rc = check_launch("scatter_init_kernel");
+    if (rc != B200K_OK) return rc;
+    launch_pdl(scatter_kernel, dim3(div_up(a.n_idx * a.inner, 256)), dim3(256), 0, s, a);
+    return check_launch("scatter_kernel");
+}
 
 extern "C" int b200k_reverse_q(const b200k_reverse_params* p, void* stream)
 {

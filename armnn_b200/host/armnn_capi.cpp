@@ -265,6 +265,12 @@ int armnnc_add_normalization(void* vn, int channel_type, unsigned norm_size, flo
     return add_layer(n, n->net->AddNormalizationLayer(d));
 }
 
+int armnnc_add_scatter_nd(void* vn, int function, int input_enabled)
+{
+    auto* n = static_cast<CNet*>(vn);
+    return add_layer(n, n->net->AddScatterNdLayer(ScatterNdDescriptor(static_cast<ScatterNdFunction>(function), input_enabled != 0)));
+}
+
 int armnnc_add_reverse_v2(void* vn)
 {
     auto* n = static_cast<CNet*>(vn);

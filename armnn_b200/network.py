@@ -421,6 +421,13 @@ class INetwork:
         """armnn::GatherDescriptor: input 0 the tensor, input 1 the Signed32 indices."""
         return self._add(Layer("Gather", name, 2, 1, {"axis": int(axis)}))
 
+    def AddScatterNdLayer(self, function=0, input_enabled=True, name=None):
+        """armnn::ScatterNdDescriptor (no axis): inputs are (input, or a Signed32 shape when input_enabled is False), indices
+        [n, nd] and updates; function 0 Update, 1 Add, 2 Sub, 3 Max, 4 Min, 5 Mul."""
+        if int(function) not in range(6):
+            raise InvalidArgumentException("ScatterNd: unknown function %d" % function)
+        return self._add(Layer("ScatterNd", name, 3, 1, {"function": int(function), "input_enabled": bool(input_enabled)}))
+
     def AddReverseV2Layer(self, name=None):
         """armnn::INetwork::AddReverseV2Layer: input 0 the tensor, input 1 the Signed32 axes to mirror."""
         return self._add(Layer("ReverseV2", name, 2, 1, {}))
@@ -542,6 +549,14 @@ def IsLayerSupported(layer):
         ok = (DataType.QAsymmU8, DataType.QAsymmS8, DataType.QSymmS16, DataType.Float32, DataType.Signed32)
         if ins[0].dtype not in ok or outs[0].dtype != ins[0].dtype or ins[1].dtype != DataType.Signed32:
             return False, "Gather: one supported element type for input and output, Signed32 indices"
+        return True, ""
+    if t == "ScatterNd":
+        ok = (DataType.QAsymmU8, DataType.QAsymmS8, DataType.QSymmS16, DataType.Float32)
+        first_ok = ins[0].dtype == outs[0].dtype if layer.desc["input_enabled"] else ins[0].dtype == DataType.Signed32
+        if outs[0].dtype not in ok or ins[2].dtype != outs[0].dtype or ins[1].dtype != DataType.Signed32 or not first_ok:
+            return False, "ScatterNd: one supported element type, Signed32 indices (and shape)"
+        if len(ins[1].shape) != 2 or not (1 <= ins[1].shape[1] <= min(8, len(outs[0].shape))):
+            return False, "ScatterNd: indices must be [n, nd] with nd within the output's rank (and 8)"
         return True, ""
     if t == "ReverseV2":
         ok = (DataType.QAsymmU8, DataType.QAsymmS8, DataType.QSymmS16, DataType.Float32, DataType.Signed32)
@@ -1182,6 +1197,23 @@ class GraphProgram:
             raise InvalidArgumentException("Gather: output shape %s does not match input %s gathered with %s indices"
                                            % (y.info.shape, x.info.shape, idx.info.shape))
         return "gather_q", p
+
+    def _make_ScatterNd(self, layer):
+        first, idx, upd = (s.source for s in layer.inputs)
+        y = layer.outputs[0]
+        p = _abi.ScatterNdParams()
+        if layer.desc["input_enabled"]:
+            p.x = self._operand(first)
+        p.updates, p.y = self._operand(upd), self._operand(y)
+        p.indices = self._ptr(self._dev(idx))
+        p.n_indices, p.nd = idx.info.shape
+        p.inner = int(np.prod(y.info.shape[p.nd:])) if p.nd < len(y.info.shape) else 1
+        for i in range(p.nd):
+            p.dims[i] = y.info.shape[i]
+        if upd.info.GetNumElements() != p.n_indices * p.inner:
+            raise InvalidArgumentException("ScatterNd: updates %s do not hold %d slices of %d elements" % (upd.info.shape, p.n_indices, p.inner))
+        p.function = layer.desc["function"]
+        return "scatter_nd_q", p
 
     def _make_ReverseV2(self, layer):
         x, axes, y = layer.inputs[0].source, layer.inputs[1].source, layer.outputs[0]

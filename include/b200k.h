@@ -402,6 +402,23 @@ typedef struct {
 
 int b200k_resize_q(const b200k_resize_params* p, void* stream);
 
+/* armnn::ScatterNd (src/backends/reference/workloads/ScatterNd.cpp:37-333), without the axis option (which the reference
+ * refuses too).  y [dims[0] .. dims[nd-1], inner] starts as x (x.data == NULL: as zeros, the variant whose first input is
+ * a shape), then tuple j of indices [n_indices, nd] replaces its slice:
+ *     y[tuple j, k] = Q_y(function(base[tuple j, k], deq(updates[j, k]))),  base = deq_x(x) or 0
+ * function follows armnn::ScatterNdFunction: 0 Update, 1 Add, 2 Sub, 3 Max, 4 Min, 5 Mul.  The base is the input, not the
+ * running output, so of several tuples that address one slice the last one decides (for Update the reference throws on
+ * such duplicates; a tuple outside the tensor, on which it throws as well, is skipped here). */
+typedef struct {
+    b200k_qtensor x, updates, y;
+    const int32_t* indices;
+    int32_t n_indices, nd, inner;
+    int32_t dims[8];
+    int32_t function;
+} b200k_scatter_nd_params;
+
+int b200k_scatter_nd_q(const b200k_scatter_nd_params* p, void* stream);
+
 /* armnn::ReverseV2 (src/backends/reference/workloads/ReverseV2Impl.cpp:14-133): y is x mirrored along every dimension
  * listed in `axes` (device int32, n_axes entries, negative ones counted from the end; the layer's second input). */
 typedef struct {
@@ -636,7 +653,7 @@ unsigned long long b200k_kernel_launches(void);
 
 /* sizeof() of a parameter struct as compiled into the library, for bindings in other languages to check their
  * own declarations: 0 conv2d, 1 fc, 2 bmm, 3 pool2d, 4 mean, 5 eltwise, 6 activation, 7 softmax, 8 convert,
- * 9 qlstm, 10 pad, 11 view_copy, 12 resize, 13 reduce, 14 unary, 15 arg_min_max, 16 gather, 17 batch_norm, 18 instance_norm, 19 normalization, 20 conv3d, 21 pool3d, 22 gather_nd, 23 lstm, 24 reverse, 25 convert_fp16.  No counterpart in the reference (its backends are linked as C++). */
+ * 9 qlstm, 10 pad, 11 view_copy, 12 resize, 13 reduce, 14 unary, 15 arg_min_max, 16 gather, 17 batch_norm, 18 instance_norm, 19 normalization, 20 conv3d, 21 pool3d, 22 gather_nd, 23 lstm, 24 reverse, 25 convert_fp16, 26 scatter_nd.  No counterpart in the reference (its backends are linked as C++). */
 size_t b200k_sizeof_params(int which);
 
 #ifdef __cplusplus

@@ -1099,3 +1099,28 @@ extern "C" int cpuref_convert_fp16(const b200k_convert_fp16_params* p)
         }
     });
 }
+
+extern "C" int cpuref_scatter_nd_q(const b200k_scatter_nd_params* p)
+{
+    return guarded([&] {
+        Harness h;
+        unsigned dims[9], udims[9];
+        for (int d = 0; d < p->nd; ++d) dims[d] = (unsigned)p->dims[d];
+        dims[p->nd] = (unsigned)p->inner;
+        udims[0] = (unsigned)p->n_indices; udims[1] = (unsigned)p->inner;
+        const TensorShape full((unsigned)p->nd + 1, dims);
+        TensorInfo ii(TensorShape({(unsigned)p->n_indices, (unsigned)p->nd}), DataType::Signed32);
+        TensorInfo ui = make_info(p->updates, TensorShape(2, udims), 0, 0, false);
+        TensorInfo yi = make_info(p->y, full, 0, 0, false);
+        ScatterNdQueueDescriptor d;
+        d.m_Parameters = ScatterNdDescriptor(static_cast<ScatterNdFunction>(p->function), p->x.data != nullptr);
+        std::vector<int32_t> shapeValues(dims, dims + p->nd + 1);
+        if (p->x.data) { h.in(d, make_info(p->x, full, 0, 0, false), p->x.data); }
+        else { h.in(d, TensorInfo(TensorShape({(unsigned)p->nd + 1}), DataType::Signed32), shapeValues.data()); }
+        h.in(d, ii, p->indices);
+        h.in(d, ui, p->updates.data);
+        auto* o = h.out(d, yi);
+        h.run(LayerType::ScatterNd, d);
+        copy_out(o, const_cast<void*>(p->y.data), yi.GetNumBytes());
+    });
+}

@@ -1808,3 +1808,40 @@ int oracle_convert_fp16(const b200k_convert_fp16_params* p)
     }
     return 0;
 }
+
+/* ---- ScatterNd, ScatterNd.cpp:37-333 (both variants; tuples outside the tensor, on which the reference throws, are skipped) -- */
+
+int oracle_scatter_nd_q(const b200k_scatter_nd_params* p)
+{
+    if (!p->updates.data || !p->y.data || !p->indices || p->nd < 1 || p->nd > 8) return B200K_E_INVALID;
+    int64_t rows = 1, coeff[8];
+    for (int d = p->nd - 1; d >= 0; --d) { coeff[d] = rows; rows *= p->dims[d]; }
+    const int64_t total = rows * p->inner;
+    for (int64_t i = 0; i < total; ++i) store_f(&p->y, i, p->x.data ? load_f(&p->x, i) : 0.0f);
+    for (int j = 0; j < p->n_indices; ++j) {
+        int64_t row = 0;
+        int ok = 1;
+        for (int d = 0; d < p->nd; ++d) {
+            const int32_t t = p->indices[(int64_t)j * p->nd + d];
+            if (t < 0 || t >= p->dims[d]) ok = 0;
+            row += (int64_t)t * coeff[d];
+        }
+        if (!ok) continue;
+        for (int k = 0; k < p->inner; ++k) {
+            const int64_t at = row * p->inner + k;
+            const float base = p->x.data ? load_f(&p->x, at) : 0.0f;
+            const float u = load_f(&p->updates, (int64_t)j * p->inner + k);
+            volatile float r;
+            switch (p->function) {
+                case 0: r = u; break;
+                case 1: r = base + u; break;
+                case 2: r = base - u; break;
+                case 3: r = base < u ? u : base; break;
+                case 4: r = u < base ? u : base; break;
+                default: r = base * u; break;
+            }
+            store_f(&p->y, at, r);
+        }
+    }
+    return 0;
+}

@@ -529,7 +529,35 @@ def norm_cases():
                 p.shape[i] = n
             return p, [y]
         return lambda: SimpleCase("reverse_q", build)
+    def scatter(seed, dims, inner, n_idx, fn, dtype=S8, with_input=True, duplicates=False):
+        def build(mem):
+            rng = np.random.default_rng(seed)
+            p = _abi.ScatterNdParams()
+            shape = tuple(dims) + (inner,)
+            q = (0.05, 2) if dtype == S8 else ((0.05, 120) if dtype == U8 else (1.0, 0))
+            rand = lambda sh: rng.standard_normal(sh).astype(np.float32) if dtype == F32 else _rand(rng, dtype, sh)
+            if with_input:
+                p.x = qt(mem, rand(shape), dtype, *q)
+            p.updates = qt(mem, rand((n_idx, inner)), dtype, *((0.04, -1) if dtype == S8 else q))
+            p.y, y = qt_out(mem, shape, dtype, *((0.09, 0) if dtype == S8 else q))
+            rows = int(np.prod(dims))
+            flat = rng.integers(0, rows, n_idx) if duplicates else rng.permutation(rows)[:n_idx]
+            if duplicates:
+                flat[-1] = flat[0]                         # the last tuple repeats the first: it must win
+            p.indices = mem.inp(np.stack(np.unravel_index(flat, dims), axis=1).astype(np.int32))
+            p.n_indices, p.nd, p.inner, p.function = n_idx, len(dims), inner, fn
+            for i, n in enumerate(dims):
+                p.dims[i] = n
+            return p, [y]
+        return lambda: SimpleCase("scatter_nd_q", build)
     return {
+        "scatter_update_rows": scatter(344, (12,), 16, 5, 0),
+        "scatter_add_duplicates_last_wins": scatter(345, (4, 5), 3, 9, 1, duplicates=True),
+        "scatter_sub_u8_pixels": scatter(346, (3, 4, 5), 2, 7, 2, dtype=U8),
+        "scatter_max_float_elements": scatter(347, (6, 7), 1, 10, 3, dtype=F32, duplicates=True),
+        "scatter_min_shape_variant": scatter(348, (5, 3), 4, 6, 4, with_input=False),
+        "scatter_mul_float_shape_variant": scatter(349, (9,), 8, 4, 5, dtype=F32, with_input=False),
+        "scatter_update_shape_variant_u8": scatter(350, (4, 4), 2, 8, 0, dtype=U8, with_input=False),
         "reverse_width_and_batch": reverse(341, (2, 5, 7, 8), (2, 0)),
         "reverse_negative_axis_u8_requantise": reverse(342, (4, 6, 5), (-1,), dtype=U8, requant=True),
         "reverse_all_axes_float": reverse(343, (3, 4, 5), (0, 1, 2), dtype=F32),

@@ -28,7 +28,7 @@ def test_struct_layouts_match_the_header():
     for i, name in enumerate(["conv2d_q8", "fully_connected_q8", "batch_matmul_q8", "pool2d_q8", "mean_hw_q8",
                               "eltwise_q8", "activation_q8", "softmax_q8", "convert_q", "qlstm_step", "pad_q",
                               "view_copy_q", "resize_q", "reduce_q", "unary_q", "arg_min_max_q", "gather_q",
-                              "batch_norm_q", "instance_norm_q", "normalization_q", "conv3d_q", "pool3d_q", "gather_nd_q", "lstm_step_f32", "reverse_q", "convert_fp16"]):
+                              "batch_norm_q", "instance_norm_q", "normalization_q", "conv3d_q", "pool3d_q", "gather_nd_q", "lstm_step_f32", "reverse_q", "convert_fp16", "scatter_nd_q"]):
         assert l.b200k_sizeof_params(i) == ctypes.sizeof(_abi.KERNEL_ENTRY_POINTS[name]), name
 
 

@@ -395,3 +395,14 @@ def test_fp16_conversion_graph_oracle_equals_armnn_cpuref(built):
     got = hostnet.OracleNetwork(Optimize(_fp16_net(True))).run({0: x})[0]
     assert want.dtype == np.float16 and want.max() == np.float16(65504)          # an overflowing square saturates
     assert np.array_equal(want.view(np.uint16), got.view(np.uint16))
+
+
+@needs_cpuref
+def test_scatter_nd_graph_oracle_equals_armnn_cpuref(built):
+    import hostnet
+    from test_plugin import _scatter_inputs, _scatter_net
+    net, xs = _scatter_net(), _scatter_inputs(114)
+    want = hostnet.ArmnnNetwork(net, "CpuRef").run(xs)
+    got = hostnet.OracleNetwork(Optimize(net)).run(xs)
+    for k in (0, 1):
+        assert want[k].shape == got[k].shape and np.array_equal(want[k], got[k]), k

@@ -1466,3 +1466,46 @@ def test_float16_network_runs_in_float32_between_inserted_conversions():
     got = hostnet.ArmnnNetwork(net, "B200Acc").run({0: x})[0]
     assert ref.dtype == np.float16 and np.isfinite(ref).all() and ref.max() == np.float16(65504)
     assert np.array_equal(ref.view(np.uint16), got.view(np.uint16))
+
+
+def _scatter_net():
+    """ScatterNd with an input tensor (Add, pixels of a [H, W, C] map) and in its shape variant (Update into zeros)."""
+    from armnn_b200.network import DataType, INetwork, TensorInfo
+    q = lambda *shape: TensorInfo(shape, DataType.QAsymmS8, 0.05, -3)
+    net = INetwork.Create()
+    names = [("map", q(5, 6, 8)), ("pixels", TensorInfo((4, 2), DataType.Signed32)), ("updates", q(4, 8)),
+             ("shape", TensorInfo((2,), DataType.Signed32)), ("rows", TensorInfo((3, 1), DataType.Signed32)), ("row_updates", q(3, 8))]
+    ins = []
+    for k, (name, info) in enumerate(names):
+        il = net.AddInputLayer(k, name)
+        il.GetOutputSlot(0).SetTensorInfo(info)
+        ins.append(il)
+    s1 = net.AddScatterNdLayer(1, True, "scatter_add")
+    for k in range(3):
+        ins[k].GetOutputSlot(0).Connect(s1.GetInputSlot(k))
+    s1.GetOutputSlot(0).SetTensorInfo(TensorInfo((5, 6, 8), DataType.QAsymmS8, 0.08, 1))
+    s2 = net.AddScatterNdLayer(0, False, "scatter_into_zeros")
+    for k in range(3):
+        ins[3 + k].GetOutputSlot(0).Connect(s2.GetInputSlot(k))
+    s2.GetOutputSlot(0).SetTensorInfo(q(7, 8))
+    for k, l in enumerate((s1, s2)):
+        o = net.AddOutputLayer(k, "out%d" % k)
+        l.GetOutputSlot(0).Connect(o.GetInputSlot(0))
+    return net
+
+
+def _scatter_inputs(seed):
+    rng = np.random.default_rng(seed)
+    i8 = lambda *shape: rng.integers(-128, 128, size=shape).astype(np.int8)
+    return {0: i8(5, 6, 8), 1: np.array([[0, 0], [4, 5], [2, 3], [4, 5]], np.int32), 2: i8(4, 8),
+            3: np.array([7, 8], np.int32), 4: np.array([[6], [0], [3]], np.int32), 5: i8(3, 8)}
+
+
+@needs_plugin
+@pytest.mark.gpu
+def test_scatter_nd_through_the_runtime_equals_cpuref():
+    net, xs = _scatter_net(), _scatter_inputs(113)
+    ref = hostnet.ArmnnNetwork(net, "CpuRef").run(xs)
+    got = hostnet.ArmnnNetwork(net, "B200Acc").run(xs)
+    for k in (0, 1):
+        assert ref[k].shape == got[k].shape and np.array_equal(ref[k], got[k]), k
