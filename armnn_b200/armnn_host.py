@@ -235,7 +235,8 @@ class ArmnnNetwork:
                     wsc.ctypes.data_as(C.c_void_p) if wsc is not None else None, len(wsc) if wsc is not None else 0,
                     wl.const_data.ctypes.data_as(C.c_void_p),
                     bdata.ctypes.data_as(C.c_void_p) if bdata is not None else None, C.c_float(bscale),
-                    bsc.ctypes.data_as(C.c_void_p) if bsc is not None else None, len(bsc) if bsc is not None else 0)
+                    bsc.ctypes.data_as(C.c_void_p) if bsc is not None else None, len(bsc) if bsc is not None else 0,
+                    int(d.get("nchw", False)))
                 assert lid >= 0, lib.armnnc_last_error().decode()
             elif t in ("DepthToSpace", "SpaceToDepth"):
                 lid = lib.armnnc_add_depth_to_space(net, d["block"], int(d["nchw"]), int(t == "SpaceToDepth"))

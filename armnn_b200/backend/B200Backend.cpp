@@ -156,7 +156,7 @@ public:
             {
                 // infos: input, output, weights[, bias] (RefLayerSupport.cpp: IsTransposeConvolution2dSupported)
                 const auto& d = *PolymorphicDowncast<const TransposeConvolution2dDescriptor*>(&descriptor);
-                if (d.m_DataLayout != DataLayout::NHWC) { return No(reason, "only NHWC is supported"); }
+                if (d.m_DataLayout != DataLayout::NHWC && d.m_DataLayout != DataLayout::NCHW) { return No(reason, "NHWC or NCHW only"); }
                 if (infos.size() < 3 || !Is8Bit(infos[0]) || !Is8Bit(infos[1]) || !Is8Bit(infos[2])) { return No(reason, "8-bit quantised tensors only"); }
                 if (d.m_BiasEnabled && (infos.size() < 4 || infos[3].GetDataType() != DataType::Signed32)) { return No(reason, "bias must be Signed32"); }
                 return true;

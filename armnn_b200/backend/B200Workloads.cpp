@@ -1292,15 +1292,37 @@ std::unique_ptr<IWorkload> B200WorkloadFactory::CreateWorkload(LayerType type, c
             // weights [OC, KH, KW, C] and bias are constant members of the queue descriptor (not input tensors): one
             // upload at workload creation
             const auto& qd = *PolymorphicDowncast<const TransposeConvolution2dQueueDescriptor*>(&d);
-            if (qd.m_Parameters.m_DataLayout != DataLayout::NHWC || !qd.m_Weight) { throw InvalidArgumentException("B200Acc: TransposeConvolution2d needs NHWC and constant weights"); }
+            if (!qd.m_Weight) { throw InvalidArgumentException("B200Acc: TransposeConvolution2d needs constant weights"); }
             auto st = std::make_shared<SimpleState<b200k_conv2d_params>>(ctx);
             b200k_conv2d_params& p = st->p;
             std::memset(&p, 0, sizeof(p));
-            const TensorInfo& x = info.m_InputTensorInfos[0];
-            const TensorInfo& y = info.m_OutputTensorInfos[0];
-            const TensorInfo& w = qd.m_Weight->GetTensorInfo();
+            // an NCHW layer runs as re-layout -> NHWC kernel -> re-layout (see MakeConv); its [O, I, H, W] weights are
+            // re-ordered to [O, H, W, I] on the host before the upload
+            const bool nchw = qd.m_Parameters.m_DataLayout == DataLayout::NCHW;
+            auto lay = std::make_shared<LayoutState>();
+            TensorInfo x = info.m_InputTensorInfos[0], y = info.m_OutputTensorInfos[0], w = qd.m_Weight->GetTensorInfo();
+            std::vector<uint8_t> wHost(static_cast<const uint8_t*>(qd.m_Weight->GetConstTensor<void>()),
+                                       static_cast<const uint8_t*>(qd.m_Weight->GetConstTensor<void>()) + w.GetNumBytes());
+            if (nchw)
+            {
+                lay->in = Relayout(x, kNchwToNhwc, st->blobs);
+                lay->x = st->blobs.Alloc(x.GetNumBytes());
+                x = NhwcOf(x);
+                const TensorInfo yNhwc = NhwcOf(y);
+                lay->out = Relayout(yNhwc, kNhwcToNchw, st->blobs);
+                lay->y = st->blobs.Alloc(y.GetNumBytes());
+                y = yNhwc;
+                const TensorShape ws = w.GetShape();                       // [O, I, H, W], one byte per element
+                const std::vector<uint8_t> src = wHost;
+                for (unsigned int o = 0; o < ws[0]; ++o) for (unsigned int i = 0; i < ws[1]; ++i)
+                for (unsigned int hh = 0; hh < ws[2]; ++hh) for (unsigned int ww = 0; ww < ws[3]; ++ww)
+                {
+                    wHost[((static_cast<size_t>(o) * ws[2] + hh) * ws[3] + ww) * ws[1] + i] = src[((static_cast<size_t>(o) * ws[1] + i) * ws[2] + hh) * ws[3] + ww];
+                }
+                w = NhwcOf(w);
+            }
             p.x = Operand(x, st->blobs); p.y = Operand(y, st->blobs); p.w = Operand(w, st->blobs);
-            p.w.data = st->blobs.Upload(qd.m_Weight->GetConstTensor<void>(), w.GetNumBytes());
+            p.w.data = st->blobs.Upload(wHost.data(), wHost.size());
             if (qd.m_Parameters.m_BiasEnabled && qd.m_Bias)
             {
                 const TensorInfo& b = qd.m_Bias->GetTensorInfo();
@@ -1315,10 +1337,18 @@ std::unique_ptr<IWorkload> B200WorkloadFactory::CreateWorkload(LayerType type, c
             p.pad_top = qd.m_Parameters.m_PadTop; p.pad_left = qd.m_Parameters.m_PadLeft;
             p.dil_h = p.dil_w = 1;
             Clamp(qd.GetAdditionalInformation<ActivationDescriptor>(), y, p.clamp_lo, p.clamp_hi);
-            return Make<TransposeConvolution2dQueueDescriptor>(d, info, ctx, [st](const TransposeConvolution2dQueueDescriptor& data, cudaStream_t s)
+            return Make<TransposeConvolution2dQueueDescriptor>(d, info, ctx, [st, lay, nchw](const TransposeConvolution2dQueueDescriptor& data, cudaStream_t s)
             {
                 st->p.x.data = Dev(data.m_Inputs[0]); st->p.y.data = Dev(data.m_Outputs[0]);
+                if (nchw)
+                {
+                    lay->in.x.data = st->p.x.data; lay->in.y.data = lay->x;
+                    B200CheckStatus(b200k_view_copy_q(&lay->in, s));
+                    lay->out.x.data = lay->y; lay->out.y.data = st->p.y.data;
+                    st->p.x.data = lay->x; st->p.y.data = lay->y;
+                }
                 B200CheckStatus(b200k_transpose_conv2d_q8(&st->p, s));
+                if (nchw) { B200CheckStatus(b200k_view_copy_q(&lay->out, s)); }
             });
         }
         case LayerType::ElementwiseUnary:

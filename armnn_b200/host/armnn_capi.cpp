@@ -563,14 +563,14 @@ int armnnc_add_slice(void* vn, int rank, const int32_t* begin, const int32_t* si
 // weights [OC, KH, KW, C] and the optional bias travel as ConstTensor arguments of the layer (INetwork.hpp)
 int armnnc_add_transpose_conv2d(void* vn, int stride_h, int stride_w, int pad_top, int pad_bottom, int pad_left, int pad_right,
                                 int w_dtype, const int32_t* w_shape, float w_scale, int32_t w_zp, const float* w_scales, int n_w_scales,
-                                const void* w_data, const void* b_data, float b_scale, const float* b_scales, int n_b_scales)
+                                const void* w_data, const void* b_data, float b_scale, const float* b_scales, int n_b_scales, int nchw)
 {
     auto* n = static_cast<CNet*>(vn);
     TransposeConvolution2dDescriptor d;
     d.m_StrideY = (uint32_t)stride_h; d.m_StrideX = (uint32_t)stride_w;
     d.m_PadTop = (uint32_t)pad_top; d.m_PadBottom = (uint32_t)pad_bottom; d.m_PadLeft = (uint32_t)pad_left; d.m_PadRight = (uint32_t)pad_right;
     d.m_BiasEnabled = b_data != nullptr;
-    d.m_DataLayout = DataLayout::NHWC;
+    d.m_DataLayout = nchw ? DataLayout::NCHW : DataLayout::NHWC;
     TensorInfo wi = info_from(w_dtype, 4, w_shape, w_scale, w_zp, w_scales, n_w_scales, 0, true);
     n->blobs.emplace_back((const uint8_t*)w_data, (const uint8_t*)w_data + wi.GetNumBytes());
     ConstTensor weights(wi, n->blobs.back().data());

@@ -382,11 +382,11 @@ class INetwork:
         """armnn::StackDescriptor (the input shape is taken from the connected inputs)."""
         return self._add(Layer("Stack", name, int(num_inputs), 1, {"axis": int(axis)}))
 
-    def AddTransposeConvolution2dLayer(self, stride=(1, 1), pad=(0, 0, 0, 0), bias_enabled=True, name=None):
+    def AddTransposeConvolution2dLayer(self, stride=(1, 1), pad=(0, 0, 0, 0), bias_enabled=True, name=None, nchw=False):
         """pad = (top, bottom, left, right); NHWC; inputs: 0 data, 1 weights [O,H,W,I], 2 bias (Constant layers: the Arm NN
         API takes them as ConstTensor arguments of the layer, armnn::INetwork::AddTransposeConvolution2dLayer)."""
         return self._add(Layer("TransposeConvolution2d", name, 3 if bias_enabled else 2, 1,
-                               {"stride": tuple(stride), "pad": tuple(pad), "bias": bool(bias_enabled)}))
+                               {"stride": tuple(stride), "pad": tuple(pad), "bias": bool(bias_enabled), "nchw": bool(nchw)}))
 
     def AddElementwiseUnaryLayer(self, operation, name=None):
         """armnn::UnaryOperation: 0 Abs, 1 Exp, 2 Sqrt, 3 Rsqrt, 4 Neg, 6 Log, 7 Sin, 8 Ceil (5 LogicalNot is not supported)."""
@@ -496,7 +496,7 @@ def IsLayerSupported(layer):
     t = layer.type
     if t in ("Input", "Output", "Constant", "Reshape"):
         return True, ""
-    if t in ("Convolution2d", "DepthwiseConvolution2d", "Pooling2d") and layer.desc.get("nchw"):
+    if t in ("Convolution2d", "DepthwiseConvolution2d", "Pooling2d", "TransposeConvolution2d") and layer.desc.get("nchw"):
         return False, "%s: this runtime executes NHWC graphs only (the plugin re-lays NCHW layers out)" % t
     if t in ("Convolution2d", "DepthwiseConvolution2d", "FullyConnected"):
         x, w, y = ins[0], ins[1], outs[0]

@@ -1509,3 +1509,29 @@ def test_scatter_nd_through_the_runtime_equals_cpuref():
     got = hostnet.ArmnnNetwork(net, "B200Acc").run(xs)
     for k in (0, 1):
         assert ref[k].shape == got[k].shape and np.array_equal(ref[k], got[k]), k
+
+
+@needs_plugin
+@pytest.mark.gpu
+def test_nchw_transpose_convolution_through_the_runtime_matches_cpuref():
+    """TransposeConvolution2d stated in NCHW ([O, I, H, W] weights): re-layout around the NHWC kernel, weights re-ordered on
+    the host when the workload is created."""
+    from armnn_b200.network import DataType, INetwork, TensorInfo
+    rng = np.random.default_rng(127)
+    net = INetwork.Create()
+    il = net.AddInputLayer(0, "input")
+    il.GetOutputSlot(0).SetTensorInfo(TensorInfo((2, 6, 5, 7), DataType.QAsymmS8, 0.05, -3))
+    w = rng.integers(-127, 128, size=(9, 6, 3, 3)).astype(np.int8)
+    wl = net.AddConstantLayer(w, TensorInfo(w.shape, DataType.QSymmS8, 0.01, 0, constant=True), "weights")
+    b = rng.integers(-900, 900, size=(9,)).astype(np.int32)
+    bl = net.AddConstantLayer(b, TensorInfo((9,), DataType.Signed32, 0.05 * 0.01, 0, constant=True), "bias")
+    tc = net.AddTransposeConvolution2dLayer((2, 2), (1, 1, 1, 1), True, "transpose_conv", nchw=True)
+    il.GetOutputSlot(0).Connect(tc.GetInputSlot(0)); wl.GetOutputSlot(0).Connect(tc.GetInputSlot(1)); bl.GetOutputSlot(0).Connect(tc.GetInputSlot(2))
+    tc.GetOutputSlot(0).SetTensorInfo(TensorInfo((2, 9, 9, 13), DataType.QAsymmS8, 0.12, 2))
+    ol = net.AddOutputLayer(0, "out")
+    tc.GetOutputSlot(0).Connect(ol.GetInputSlot(0))
+    x = rng.integers(-128, 128, size=(2, 6, 5, 7)).astype(np.int8)
+    ref = hostnet.ArmnnNetwork(net, "CpuRef").run({0: x})[0]
+    got = hostnet.ArmnnNetwork(net, "B200Acc").run({0: x})[0]
+    st = diff_stats(ref, got)
+    assert ref.shape == got.shape == (2, 9, 9, 13) and st["max_abs"] <= 1 and st["mismatch_frac"] < 5e-3, st
